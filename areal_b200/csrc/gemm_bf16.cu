@@ -1,0 +1,166 @@
+// bf16 GEMM on tcgen05/TMEM for forward, dgrad and wgrad of every linear layer.
+//
+//   C[M,N] (bf16 or fp32, optionally C += ...) = A * B^T (+ bias[N])
+//
+// a_mn = 0: A is stored [M,K] row-major (K contiguous);  a_mn = 1: A is stored
+// [K,M] row-major (M contiguous). Same for B with N. This covers
+//   forward  y  = x W^T      : A = x [T,in]  (K-major), B = W [out,in] (K-major)
+//   dgrad    dx = dy W       : A = dy [T,out] (K-major), B = W [out,in] read as [K=out, N=in] (MN-major)
+//   wgrad    dW = dy^T x     : A = dy [T,out] read as [K=T, M=out] (MN-major), B = x [T,in] as [K=T, N=in] (MN-major)
+// Replaces the cuBLAS calls behind nn.Linear in the reference
+// (areal/experimental/models/archon/qwen3/model/model.py:103-293).
+#include "common/gemm_core.cuh"
+#include "common/host_utils.h"
+
+namespace b200 {
+
+struct StoreEpi {
+  void* C;
+  const __nv_bfloat16* bias;
+  long long ldc;
+  int M, N;
+  int out_fp32;
+  int accumulate;
+  struct State {};
+
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m, int tiles_n,
+                                       int& m_blk, int& n_blk) const {
+    return default_tile(cta, ncta, it, tiles_m, tiles_n, m_blk, n_blk);
+  }
+  __device__ __forceinline__ void begin(State&, int, int, int) const {}
+  __device__ __forceinline__ void end(State&, int, int, int) const {}
+  __device__ __forceinline__ void chunk(State&, int row, int col0, const float (&v_in)[32]) const {
+    if (row >= M || col0 >= N) return;
+    float v[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = v_in[i];
+    const bool full = (col0 + 32 <= N);
+    if (bias) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (full || col0 + i < N) v[i] += __bfloat162float(bias[col0 + i]);
+    }
+    if (out_fp32) {
+      float* p = reinterpret_cast<float*>(C) + static_cast<long long>(row) * ldc + col0;
+      if (full && (ldc & 3) == 0) {
+        float4* p4 = reinterpret_cast<float4*>(p);
+#pragma unroll
+        for (int i = 0; i < 8; ++i) {
+          float4 o = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+          if (accumulate) {
+            float4 old = p4[i];
+            o.x += old.x; o.y += old.y; o.z += old.z; o.w += old.w;
+          }
+          p4[i] = o;
+        }
+      } else {
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < N) p[i] = accumulate ? p[i] + v[i] : v[i];
+      }
+    } else {
+      __nv_bfloat16* p = reinterpret_cast<__nv_bfloat16*>(C) + static_cast<long long>(row) * ldc + col0;
+      if (full && (ldc & 7) == 0) {
+        uint4* p4 = reinterpret_cast<uint4*>(p);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float f[8];
+#pragma unroll
+          for (int j = 0; j < 8; ++j) f[j] = v[8 * i + j];
+          if (accumulate) {
+            uint4 old = p4[i];
+            const __nv_bfloat162* ob = reinterpret_cast<const __nv_bfloat162*>(&old);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              float2 of = __bfloat1622float2(ob[j]);
+              f[2 * j] += of.x;
+              f[2 * j + 1] += of.y;
+            }
+          }
+          uint4 o;
+          __nv_bfloat162* ob2 = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) ob2[j] = __floats2bfloat162_rn(f[2 * j], f[2 * j + 1]);
+          p4[i] = o;
+        }
+      } else {
+        for (int i = 0; i < 32; ++i)
+          if (col0 + i < N) {
+            float x = v[i];
+            if (accumulate) x += __bfloat162float(p[i]);
+            p[i] = __float2bfloat16(x);
+          }
+      }
+    }
+  }
+};
+
+template <int BN, bool A_MN, bool B_MN>
+static int launch(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                  long long lda, long long ldb, long long ldc, int out_fp32, int accumulate,
+                  cudaStream_t stream) {
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc;
+  if (A_MN)
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, lda * 2, 64, 64);
+  else
+    rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, kBM, 64);
+  if (rc) return rc;
+  if (B_MN)
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, N, ldb * 2, 64, 64);
+  else
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb * 2, BN, 64);
+  if (rc) return rc;
+  StoreEpi epi{C, reinterpret_cast<const __nv_bfloat16*>(bias), ldc, M, N, out_fp32, accumulate};
+  auto kern = gemm_tcgen05_kernel<BN, A_MN, B_MN, StoreEpi>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  long long tiles = static_cast<long long>((M + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  if (grid <= 0) return 0;
+  int* status = device_status_word();
+  if (!status) return -3;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, M, N, K, epi, status);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+// Row pitches lda/ldb/ldc are in elements. All pitches and base pointers must
+// be multiples of 16 bytes (TMA requirement); K, and the contiguous extent of
+// an MN-major operand, must be multiples of 8.
+int b200_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int M, int N, int K,
+                   long long lda, long long ldb, long long ldc, int a_mn, int b_mn, int out_fp32,
+                   int accumulate, int bn, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (reinterpret_cast<uintptr_t>(A) & 15) ||
+      (reinterpret_cast<uintptr_t>(B) & 15))
+    return -100;
+#define DISPATCH(BN_)                                                                              \
+  if (!a_mn && !b_mn)                                                                              \
+    return launch<BN_, false, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_fp32, accumulate, \
+                                     stream);                                                      \
+  if (!a_mn && b_mn)                                                                               \
+    return launch<BN_, false, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_fp32, accumulate,  \
+                                    stream);                                                       \
+  if (a_mn && b_mn)                                                                                \
+    return launch<BN_, true, true>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_fp32, accumulate,   \
+                                   stream);                                                        \
+  return launch<BN_, true, false>(A, B, C, bias, M, N, K, lda, ldb, ldc, out_fp32, accumulate,    \
+                                  stream);
+  if (bn == 128) {
+    DISPATCH(128)
+  }
+  DISPATCH(256)
+#undef DISPATCH
+}
+
+}  // extern "C"

@@ -1,0 +1,150 @@
+"""bf16 GEMM on the tcgen05 kernel (``csrc/gemm_bf16.cu``) and the autograd
+``linear`` built on it.
+
+The three products of a linear layer run on one kernel by choosing operand
+majors instead of materialising transposes:
+
+* forward  ``y  = x W^T``  – both operands K-major
+* dgrad    ``dx = dy W``   – ``W`` read MN-major
+* wgrad    ``dW = dy^T x`` – both operands MN-major, fp32 output with optional
+  accumulation into a main-grad buffer.
+
+Counterpart of the cuBLAS-backed ``nn.Linear`` calls of the reference
+(areal/experimental/models/archon/qwen3/model/model.py:103-293).
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+
+def _gemm_ref(a, b, a_mn, b_mn, bias, out_dtype, out, accumulate):
+    A = a.t() if a_mn else a
+    B = b.t() if b_mn else b
+    c = A.float() @ B.float().t()
+    if bias is not None:
+        c = c + bias.float()
+    if out is not None:
+        if accumulate:
+            out.add_(c.to(out.dtype))
+        else:
+            out.copy_(c.to(out.dtype))
+        return out
+    return c.to(out_dtype)
+
+
+def gemm(
+    a: torch.Tensor,
+    b: torch.Tensor,
+    *,
+    a_mn: bool = False,
+    b_mn: bool = False,
+    bias: torch.Tensor | None = None,
+    out: torch.Tensor | None = None,
+    out_dtype: torch.dtype = torch.bfloat16,
+    accumulate: bool = False,
+    bn: int = 0,
+) -> torch.Tensor:
+    """``C[M,N] = A B^T (+bias)``.
+
+    ``a`` is ``[M,K]`` (``a_mn=False``) or ``[K,M]`` (``a_mn=True``); ``b`` is ``[N,K]``
+    or ``[K,N]`` likewise. ``out`` may be a bf16 or fp32 2-D tensor with unit
+    inner stride; ``accumulate`` adds to it.
+    """
+    if not _lib.use_cuda_kernels(a, b):
+        return _gemm_ref(a, b, a_mn, b_mn, bias, out_dtype, out, accumulate)
+    assert a.dtype == torch.bfloat16 and b.dtype == torch.bfloat16, "bf16 operands required"
+    assert a.dim() == 2 and b.dim() == 2
+    if a.stride(1) != 1 or (a.stride(0) % 8) or (a.data_ptr() % 16):
+        a = a.contiguous()
+    if b.stride(1) != 1 or (b.stride(0) % 8) or (b.data_ptr() % 16):
+        b = b.contiguous()
+    if a_mn:
+        K, M = a.shape
+    else:
+        M, K = a.shape
+    if b_mn:
+        Kb, N = b.shape
+    else:
+        N, Kb = b.shape
+    assert K == Kb, f"reduction dims differ: {K} vs {Kb}"
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+        accumulate = False
+    assert out.shape == (M, N) and out.stride(1) == 1
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    # TMA needs 16-byte aligned pitches: pad the contiguous extent when it is not.
+    need_pad = (a.shape[1] % 8) or (b.shape[1] % 8)
+    if need_pad:
+        def pad(t):
+            p = (-t.shape[1]) % 8
+            return torch.nn.functional.pad(t, (0, p)) if p else t
+        a, b = pad(a), pad(b)
+        if not a_mn:
+            K = a.shape[1]
+    if bn == 0:
+        bn = 256 if N > 128 else 128
+        if bn == 256:
+            # Prefer 128-wide tiles when 256-wide ones would leave most SMs idle.
+            tiles256 = -(-M // 128) * -(-N // 256)
+            if tiles256 < 100:
+                bn = 128
+    lib = _lib.kernels()
+    fn = lib.b200_gemm_bf16
+    fn.restype = ctypes.c_int
+    rc = fn(
+        _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias),
+        ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)),
+        ctypes.c_longlong(out.stride(0)),
+        ctypes.c_int(int(a_mn)), ctypes.c_int(int(b_mn)),
+        ctypes.c_int(int(out.dtype == torch.float32)), ctypes.c_int(int(accumulate)),
+        ctypes.c_int(bn), _lib.stream_ptr(),
+    )
+    _lib.check(rc, "b200_gemm_bf16")
+    _lib.count_launch()
+    return out
+
+
+class _Linear(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, bias):
+        shape = x.shape
+        x2 = x.reshape(-1, shape[-1])
+        y = gemm(x2, w, bias=bias, out_dtype=x.dtype)
+        ctx.save_for_backward(x2, w)
+        ctx.has_bias = bias is not None
+        ctx.in_shape = shape
+        return y.reshape(*shape[:-1], w.shape[0])
+
+    @staticmethod
+    def backward(ctx, dy):
+        x2, w = ctx.saved_tensors
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        if dy2.dtype != x2.dtype:
+            dy2 = dy2.to(x2.dtype)
+        dx = dw = db = None
+        if ctx.needs_input_grad[0]:
+            dx = gemm(dy2, w, b_mn=True, out_dtype=x2.dtype).reshape(ctx.in_shape)
+        if ctx.needs_input_grad[1]:
+            main = getattr(w, "main_grad", None)
+            if main is not None:
+                # fp32 main-grad accumulation across micro-batches, fused in the epilogue
+                gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True)
+                dw = None
+            else:
+                dw = gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)
+        if ctx.has_bias and ctx.needs_input_grad[2]:
+            db = dy2.float().sum(0).to(dy2.dtype)
+        return dx, dw, db
+
+
+def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -> torch.Tensor:
+    """``x @ w.T + bias`` with forward and both backward products on the tcgen05 kernel."""
+    if x.is_cuda and x.dtype == torch.bfloat16:
+        return _Linear.apply(x, w, bias)
+    return torch.nn.functional.linear(x, w, bias)
