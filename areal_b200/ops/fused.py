@@ -1,0 +1,233 @@
+"""RMSNorm (+residual), q/k-norm + RoPE and SwiGLU: autograd wrappers over the
+kernels in ``csrc/norm_rope_swiglu.cu`` plus fp32 PyTorch references (which are
+the CPU path and the oracles of the GPU tests).
+
+Semantics follow the reference models: RMSNorm is computed in fp32 and cast
+(areal/experimental/models/archon/qwen3/model/model.py:75-101), RoPE is the
+``rotate_half`` form (qwen2/model/rope.py), the MLP is ``w2(silu(w1 x) * w3 x)``.
+"""
+
+from __future__ import annotations
+
+import ctypes
+
+import torch
+
+from . import _lib
+
+# --------------------------------------------------------------------------- RMSNorm
+
+
+def rmsnorm_ref(x, w, eps, residual=None):
+    h = x.float() + residual.float() if residual is not None else x.float()
+    if residual is not None:
+        h = h.to(x.dtype).float()
+    y = h * torch.rsqrt(h.pow(2).mean(-1, keepdim=True) + eps) * w.float()
+    if residual is not None:
+        return y.to(x.dtype), h.to(x.dtype)
+    return y.to(x.dtype)
+
+
+class _RMSNorm(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, x, w, eps, residual):
+        H = x.shape[-1]
+        x2 = x.reshape(-1, H)
+        x2 = x2 if x2.is_contiguous() else x2.contiguous()
+        T = x2.shape[0]
+        y = torch.empty_like(x2)
+        rstd = torch.empty(T, dtype=torch.float32, device=x.device)
+        lib = _lib.kernels()
+        lib.b200_rmsnorm_fwd.restype = ctypes.c_int
+        if residual is not None:
+            r2 = residual.reshape(-1, H)
+            r2 = r2 if r2.is_contiguous() else r2.contiguous()
+            h = torch.empty_like(x2)
+        else:
+            r2, h = None, None
+        rc = lib.b200_rmsnorm_fwd(_lib.ptr(x2), _lib.ptr(r2), _lib.ptr(w), _lib.ptr(y), _lib.ptr(h),
+                                  _lib.ptr(rstd), ctypes.c_int(T), ctypes.c_int(H),
+                                  ctypes.c_float(eps), _lib.stream_ptr())
+        _lib.check(rc, "b200_rmsnorm_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(h if h is not None else x2, w, rstd)
+        ctx.has_res = residual is not None
+        ctx.shape = x.shape
+        if residual is not None:
+            return y.view(x.shape), h.view(x.shape)
+        return y.view(x.shape)
+
+    @staticmethod
+    def backward(ctx, dy, dh=None):
+        xin, w, rstd = ctx.saved_tensors
+        T, H = xin.shape
+        dy2 = dy.reshape(T, H)
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        dres = None
+        if ctx.has_res and dh is not None:
+            dres = dh.reshape(T, H)
+            dres = dres if dres.is_contiguous() else dres.contiguous()
+        lib = _lib.kernels()
+        lib.b200_rmsnorm_bwd_blocks.restype = ctypes.c_int
+        nb = lib.b200_rmsnorm_bwd_blocks(ctypes.c_int(T))
+        partial = torch.empty((nb, H), dtype=torch.float32, device=xin.device)
+        dw = torch.empty(H, dtype=torch.float32, device=xin.device)
+        dx = torch.empty_like(xin)
+        lib.b200_rmsnorm_bwd.restype = ctypes.c_int
+        rc = lib.b200_rmsnorm_bwd(_lib.ptr(dy2), _lib.ptr(xin), _lib.ptr(w), _lib.ptr(rstd),
+                                  _lib.ptr(dres), _lib.ptr(dx), _lib.ptr(partial), _lib.ptr(dw),
+                                  ctypes.c_int(0), ctypes.c_int(T), ctypes.c_int(H),
+                                  _lib.stream_ptr())
+        _lib.check(rc, "b200_rmsnorm_bwd")
+        _lib.count_launch(2)
+        dxv = dx.view(ctx.shape)
+        return dxv, dw.to(w.dtype), None, (dxv if ctx.has_res else None)
+
+
+def rmsnorm(x, w, eps: float = 1e-6, residual=None):
+    """``y = rmsnorm(x (+ residual)) * w``. With ``residual`` returns ``(y, x + residual)``."""
+    if _lib.use_cuda_kernels(x) and x.dtype == torch.bfloat16 and x.shape[-1] % 8 == 0 \
+            and x.shape[-1] <= 8192:
+        return _RMSNorm.apply(x, w, eps, residual)
+    return rmsnorm_ref(x, w, eps, residual)
+
+
+# --------------------------------------------------------------------------- RoPE
+
+
+def rope_tables(max_pos: int, dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+    inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32, device=device) / dim))
+    t = torch.arange(max_pos, dtype=torch.float32, device=device)
+    fr = torch.outer(t, inv)
+    return fr.cos().contiguous(), fr.sin().contiguous()
+
+
+def _rot_half(x):
+    d = x.shape[-1] // 2
+    return torch.cat((-x[..., d:], x[..., :d]), -1)
+
+
+def qknorm_rope_ref(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps):
+    """qkv [T, (Hq+2Hkv)*D] → q [T,Hq,D], k [T,Hkv,D], v view."""
+    T = qkv.shape[0]
+    q = qkv[:, : Hq * D].reshape(T, Hq, D)
+    k = qkv[:, Hq * D: (Hq + Hkv) * D].reshape(T, Hkv, D)
+    v = qkv[:, (Hq + Hkv) * D:].reshape(T, Hkv, D)
+    if qw is not None:
+        q = rmsnorm_ref(q, qw, eps)
+        k = rmsnorm_ref(k, kw, eps)
+    c = torch.cat((cos[pos.long()], cos[pos.long()]), -1)[:, None, :]
+    s = torch.cat((sin[pos.long()], sin[pos.long()]), -1)[:, None, :]
+    qo = (q.float() * c + _rot_half(q.float()) * s).to(qkv.dtype)
+    ko = (k.float() * c + _rot_half(k.float()) * s).to(qkv.dtype)
+    return qo, ko, v
+
+
+class _QKNormRope(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps):
+        T = qkv.shape[0]
+        qkv = qkv if qkv.is_contiguous() else qkv.contiguous()
+        has_norm = qw is not None
+        q = torch.empty((T, Hq, D), dtype=qkv.dtype, device=qkv.device)
+        k = torch.empty((T, Hkv, D), dtype=qkv.dtype, device=qkv.device)
+        rstd = torch.empty(T * (Hq + Hkv) if has_norm else 1, dtype=torch.float32,
+                           device=qkv.device)
+        lib = _lib.kernels()
+        lib.b200_qknorm_rope_fwd.restype = ctypes.c_int
+        rc = lib.b200_qknorm_rope_fwd(_lib.ptr(qkv), _lib.ptr(qw), _lib.ptr(kw), _lib.ptr(cos),
+                                      _lib.ptr(sin), _lib.ptr(pos), _lib.ptr(q), _lib.ptr(k),
+                                      _lib.ptr(rstd), ctypes.c_int(T), ctypes.c_int(Hq),
+                                      ctypes.c_int(Hkv), ctypes.c_int(D), ctypes.c_float(eps),
+                                      ctypes.c_int(int(has_norm)), _lib.stream_ptr())
+        _lib.check(rc, "b200_qknorm_rope_fwd")
+        _lib.count_launch()
+        v = qkv[:, (Hq + Hkv) * D:].view(T, Hkv, D)
+        ctx.save_for_backward(qkv, qw, kw, cos, sin, pos, rstd)
+        ctx.dims = (T, Hq, Hkv, D, has_norm)
+        ctx.mark_non_differentiable()
+        return q, k, v
+
+    @staticmethod
+    def backward(ctx, dq, dk, dv):
+        qkv, qw, kw, cos, sin, pos, rstd = ctx.saved_tensors
+        T, Hq, Hkv, D, has_norm = ctx.dims
+        dqkv = torch.empty_like(qkv)
+        # dv goes straight into the v slot of the fused gradient
+        dqkv[:, (Hq + Hkv) * D:].view(T, Hkv, D).copy_(dv)
+        dq = dq if dq.is_contiguous() else dq.contiguous()
+        dk = dk if dk.is_contiguous() else dk.contiguous()
+        dqw = torch.zeros(D, dtype=torch.float32, device=qkv.device)
+        dkw = torch.zeros(D, dtype=torch.float32, device=qkv.device)
+        lib = _lib.kernels()
+        lib.b200_qknorm_rope_bwd.restype = ctypes.c_int
+        rc = lib.b200_qknorm_rope_bwd(_lib.ptr(dq), _lib.ptr(dk), _lib.ptr(qkv), _lib.ptr(qw),
+                                      _lib.ptr(kw), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos),
+                                      _lib.ptr(rstd), _lib.ptr(dqkv), _lib.ptr(dqw), _lib.ptr(dkw),
+                                      ctypes.c_int(T), ctypes.c_int(Hq), ctypes.c_int(Hkv),
+                                      ctypes.c_int(D), ctypes.c_int(int(has_norm)),
+                                      _lib.stream_ptr())
+        _lib.check(rc, "b200_qknorm_rope_bwd")
+        _lib.count_launch()
+        if has_norm:
+            return dqkv, dqw.to(qw.dtype), dkw.to(kw.dtype), None, None, None, None, None, None, None
+        return dqkv, None, None, None, None, None, None, None, None, None
+
+
+def qknorm_rope(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps=1e-6):
+    """Splits a fused qkv projection, applies per-head RMSNorm to q and k (when
+    ``qw``/``kw`` are given, Qwen3) and rotary embedding; returns ``(q, k, v)``
+    with ``v`` a strided view of ``qkv``."""
+    if _lib.use_cuda_kernels(qkv) and qkv.dtype == torch.bfloat16 and D == 128:
+        return _QKNormRope.apply(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps)
+    return qknorm_rope_ref(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps)
+
+
+# --------------------------------------------------------------------------- SwiGLU
+
+
+def swiglu_ref(gu):
+    inter = gu.shape[-1] // 2
+    g, u = gu[..., :inter].float(), gu[..., inter:].float()
+    return (torch.nn.functional.silu(g) * u).to(gu.dtype)
+
+
+class _SwiGLU(torch.autograd.Function):
+    @staticmethod
+    def forward(ctx, gu):
+        inter = gu.shape[-1] // 2
+        g2 = gu.reshape(-1, 2 * inter)
+        g2 = g2 if g2.is_contiguous() else g2.contiguous()
+        out = torch.empty((g2.shape[0], inter), dtype=gu.dtype, device=gu.device)
+        lib = _lib.kernels()
+        lib.b200_swiglu_fwd.restype = ctypes.c_int
+        rc = lib.b200_swiglu_fwd(_lib.ptr(g2), _lib.ptr(out), ctypes.c_longlong(g2.shape[0]),
+                                 ctypes.c_int(inter), _lib.stream_ptr())
+        _lib.check(rc, "b200_swiglu_fwd")
+        _lib.count_launch()
+        ctx.save_for_backward(g2)
+        ctx.shape = gu.shape
+        return out.view(*gu.shape[:-1], inter)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (g2,) = ctx.saved_tensors
+        inter = g2.shape[1] // 2
+        dy2 = dy.reshape(-1, inter)
+        dy2 = dy2 if dy2.is_contiguous() else dy2.contiguous()
+        dgu = torch.empty_like(g2)
+        lib = _lib.kernels()
+        lib.b200_swiglu_bwd.restype = ctypes.c_int
+        rc = lib.b200_swiglu_bwd(_lib.ptr(dy2), _lib.ptr(g2), _lib.ptr(dgu),
+                                 ctypes.c_longlong(g2.shape[0]), ctypes.c_int(inter),
+                                 _lib.stream_ptr())
+        _lib.check(rc, "b200_swiglu_bwd")
+        _lib.count_launch()
+        return dgu.view(ctx.shape)
+
+
+def swiglu(gu):
+    """``silu(gu[..., :I]) * gu[..., I:]`` for a fused gate/up projection."""
+    if _lib.use_cuda_kernels(gu) and gu.dtype == torch.bfloat16 and (gu.shape[-1] // 2) % 8 == 0:
+        return _SwiGLU.apply(gu)
+    return swiglu_ref(gu)
