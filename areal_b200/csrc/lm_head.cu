@@ -1,0 +1,251 @@
+// Fused LM-head GEMM + log-softmax statistics (vocab-parallel ready) on tcgen05.
+//
+// Forward: logits = X W^T / temperature are produced tile by tile in TMEM and
+// consumed in the epilogue; only four floats per (row, vocab split) leave the
+// SM: running max, sum of exp, sum of exp*logit (for the entropy) and the
+// label's logit when the label falls inside the split. A combine kernel merges
+// the splits of all vocab shards (local splits and, under tensor parallelism,
+// the other ranks' partials) into logprob, entropy, logZ and E[logit].
+// The [T, V] logits are never written.
+//
+// Backward: the same GEMM recomputes a [rows, V_local] block of logits and its
+// epilogue writes d logits (bf16) for that row chunk,
+//   dz = (g_logp * (onehot - p) + g_ent * p * (E[y] - y)) / temperature,
+// which two plain GEMMs then turn into dX and dW. Only one row chunk of dz is
+// ever resident.
+//
+// Replaces the reference's chunked log_softmax over materialised logits and its
+// 3-4 all-reduces (areal/utils/functional/vocab_parallel.py:84-372).
+#include "common/gemm_core.cuh"
+#include "common/host_utils.h"
+
+namespace b200 {
+
+struct LmStatsEpi {
+  float* partials;          // [nsplit, T, 4] : m, l, sx, target
+  const int* labels;        // [T] global vocab ids
+  int T, N;                 // rows, local vocab size
+  int vocab_start;          // global id of local column 0
+  int nb_per;               // n-blocks per split
+  int nsplit;
+  float inv_temp;
+  struct State {
+    float m, l, sx, t;
+  };
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m, int tiles_n,
+                                       int& m_blk, int& n_blk) const {
+    const int item_local = it / nb_per;
+    const int j = it - item_local * nb_per;
+    const long long w = static_cast<long long>(item_local) * ncta + cta;
+    if (w >= static_cast<long long>(tiles_m) * nsplit) return false;
+    m_blk = static_cast<int>(w % tiles_m);
+    n_blk = static_cast<int>(w / tiles_m) * nb_per + j;
+    return true;
+  }
+  __device__ __forceinline__ void begin(State& s, int, int n_blk, int) const {
+    if (n_blk % nb_per == 0) {
+      s.m = -INFINITY;
+      s.l = 0.f;
+      s.sx = 0.f;
+      s.t = 0.f;
+    }
+  }
+  __device__ __forceinline__ void chunk(State& s, int row, int col0, const float (&v)[32]) const {
+    if (row >= T || col0 >= N) return;
+    const int label = labels[row] - vocab_start;
+    float x[32];
+    float cm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      x[i] = (col0 + i < N) ? v[i] * inv_temp : -INFINITY;
+      cm = fmaxf(cm, x[i]);
+    }
+    if (label >= col0 && label < col0 + 32) {
+#pragma unroll
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i == label) s.t = x[i];
+    }
+    const float m_new = fmaxf(s.m, cm);
+    const float sc = (s.m == -INFINITY) ? 0.f : __expf(s.m - m_new);
+    float l = 0.f, sx = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float e = __expf(x[i] - m_new);  // exp(-inf) = 0 for masked columns
+      l += e;
+      sx += (x[i] == -INFINITY) ? 0.f : e * x[i];
+    }
+    s.l = s.l * sc + l;
+    s.sx = s.sx * sc + sx;
+    s.m = m_new;
+  }
+  __device__ __forceinline__ void end(State& s, int, int n_blk, int row) const {
+    if ((n_blk + 1) % nb_per == 0 && row < T) {
+      const int split = n_blk / nb_per;
+      float4* dst = reinterpret_cast<float4*>(partials) + static_cast<long long>(split) * T + row;
+      *dst = make_float4(s.m, s.l, s.sx, s.t);
+    }
+  }
+};
+
+// Merges `nparts` partial records per row. partials: [nparts, T, 4].
+// has_target: row's label lies in exactly one part (its t is non-zero there;
+// the others wrote 0) so the target logit is the sum.
+__global__ void lm_combine_kernel(const float* __restrict__ partials, int nparts, int T,
+                                  float* __restrict__ logp, float* __restrict__ entropy,
+                                  float* __restrict__ logz, float* __restrict__ ey) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row >= T) return;
+  float M = -INFINITY;
+  for (int p = 0; p < nparts; ++p)
+    M = fmaxf(M, partials[(static_cast<long long>(p) * T + row) * 4]);
+  float L = 0.f, SX = 0.f, t = 0.f;
+  for (int p = 0; p < nparts; ++p) {
+    const float4 r = reinterpret_cast<const float4*>(partials)[static_cast<long long>(p) * T + row];
+    const float sc = (r.x == -INFINITY) ? 0.f : __expf(r.x - M);
+    L += r.y * sc;
+    SX += r.z * sc;
+    t += r.w;
+  }
+  const float lz = M + logf(L);
+  const float e = SX / L;
+  if (logp) logp[row] = t - lz;
+  if (entropy) entropy[row] = lz - e;
+  if (logz) logz[row] = lz;
+  if (ey) ey[row] = e;
+}
+
+struct LmDlogitsEpi {
+  __nv_bfloat16* dz;  // [rows, ldz]
+  const int* labels;
+  const float* g_logp;  // [T] (may be null → 0)
+  const float* g_ent;   // [T] (may be null → 0)
+  const float* logz;    // [T]
+  const float* ey;      // [T]
+  long long ldz;
+  int T, N, vocab_start;
+  float inv_temp;
+  struct State {
+    float gl, ge, lz, e;
+    int label;
+  };
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m, int tiles_n,
+                                       int& m_blk, int& n_blk) const {
+    return default_tile(cta, ncta, it, tiles_m, tiles_n, m_blk, n_blk);
+  }
+  __device__ __forceinline__ void begin(State& s, int, int, int row) const {
+    if (row < T) {
+      s.gl = g_logp ? g_logp[row] : 0.f;
+      s.ge = g_ent ? g_ent[row] : 0.f;
+      s.lz = logz[row];
+      s.e = ey[row];
+      s.label = labels[row] - vocab_start;
+    }
+  }
+  __device__ __forceinline__ void end(State&, int, int, int) const {}
+  __device__ __forceinline__ void chunk(State& s, int row, int col0, const float (&v)[32]) const {
+    if (row >= T || col0 >= N) return;
+    float d[32];
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      const float y = v[i] * inv_temp;
+      const float p = __expf(y - s.lz);
+      const float onehot = (col0 + i == s.label) ? 1.f : 0.f;
+      d[i] = (s.gl * (onehot - p) + s.ge * p * (s.e - y)) * inv_temp;
+    }
+    __nv_bfloat16* out = dz + static_cast<long long>(row) * ldz + col0;
+    if (col0 + 32 <= N && (ldz & 7) == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 pk;
+        __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pb[j] = __floats2bfloat162_rn(d[8 * i + 2 * j], d[8 * i + 2 * j + 1]);
+        reinterpret_cast<uint4*>(out)[i] = pk;
+      }
+    } else {
+      for (int i = 0; i < 32; ++i)
+        if (col0 + i < N) out[i] = __float2bfloat16(d[i]);
+    }
+  }
+};
+
+template <class Epi>
+static int launch_lm(const void* X, const void* W, int T, int V, int H, long long ldx,
+                     long long ldw, const Epi& epi, long long work_items, cudaStream_t stream) {
+  constexpr int BN = 256;
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, H, ldx * 2, kBM, 64);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, W, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, V, H, ldw * 2, BN, 64);
+  if (rc) return rc;
+  auto kern = gemm_tcgen05_kernel<BN, false, false, Epi>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  int grid = static_cast<int>(work_items < sm_count() ? work_items : sm_count());
+  if (grid <= 0) return 0;
+  int* status = device_status_word();
+  if (!status) return -3;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, T, V, H, epi, status);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace b200
+
+extern "C" {
+
+// Number of vocab splits the forward uses for (T, V): enough work items to
+// fill the SMs without making the partial buffer large.
+int b200_lm_head_nsplit(int T, int V) {
+  const int tiles_m = (T + 127) / 128;
+  const int tiles_n = (V + 255) / 256;
+  int want = (2 * b200::sm_count() + tiles_m - 1) / tiles_m;
+  if (want < 1) want = 1;
+  if (want > tiles_n) want = tiles_n;
+  const int nb_per = (tiles_n + want - 1) / want;
+  return (tiles_n + nb_per - 1) / nb_per;
+}
+
+// partials: fp32 [nsplit, T, 4] with nsplit = b200_lm_head_nsplit(T, V).
+int b200_lm_head_stats(const void* X, const void* W, const int* labels, float* partials, int T,
+                       int V, int H, long long ldx, long long ldw, int vocab_start,
+                       float inv_temp, cudaStream_t stream) {
+  using namespace b200;
+  if (T == 0 || V == 0) return 0;
+  const int tiles_m = (T + 127) / 128;
+  const int tiles_n = (V + 255) / 256;
+  const int nsplit = b200_lm_head_nsplit(T, V);
+  const int nb_per = (tiles_n + nsplit - 1) / nsplit;
+  LmStatsEpi epi{partials, labels, T, V, vocab_start, nb_per, nsplit, inv_temp};
+  return launch_lm(X, W, T, V, H, ldx, ldw, epi, static_cast<long long>(tiles_m) * nsplit,
+                   stream);
+}
+
+int b200_lm_head_combine(const float* partials, int nparts, int T, float* logp, float* entropy,
+                         float* logz, float* ey, cudaStream_t stream) {
+  if (T == 0) return 0;
+  b200::lm_combine_kernel<<<(T + 255) / 256, 256, 0, stream>>>(partials, nparts, T, logp, entropy,
+                                                               logz, ey);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// Writes dz [T, V] (bf16, pitch ldz) for the rows of X given.
+int b200_lm_head_dlogits(const void* X, const void* W, const int* labels, const float* g_logp,
+                         const float* g_ent, const float* logz, const float* ey, void* dz, int T,
+                         int V, int H, long long ldx, long long ldw, long long ldz,
+                         int vocab_start, float inv_temp, cudaStream_t stream) {
+  using namespace b200;
+  if (T == 0 || V == 0) return 0;
+  LmDlogitsEpi epi{reinterpret_cast<__nv_bfloat16*>(dz), labels, g_logp, g_ent, logz, ey, ldz, T, V,
+                   vocab_start, inv_temp};
+  const long long tiles = static_cast<long long>((T + 127) / 128) * ((V + 255) / 256);
+  return launch_lm(X, W, T, V, H, ldx, ldw, epi, tiles, stream);
+}
+
+}  // extern "C"

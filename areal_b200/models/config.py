@@ -1,0 +1,171 @@
+"""Architecture description shared by the train and rollout engines.
+
+Covers the dense Qwen2 / Qwen2.5 / Qwen3 families and Qwen3-MoE, i.e. the model
+registry of the reference's torch-native engine
+(areal/experimental/models/archon/{qwen2,qwen3}/spec.py). The field names of
+``from_hf_config`` follow the HF ``config.json`` of those checkpoints.
+"""
+
+from __future__ import annotations
+
+import json
+from dataclasses import asdict, dataclass, field
+from pathlib import Path
+
+
+@dataclass
+class ModelConfig:
+    model_type: str = "qwen3"  # qwen2 | qwen3 | qwen3_moe
+    vocab_size: int = 151936
+    hidden_size: int = 2048
+    intermediate_size: int = 6144
+    num_hidden_layers: int = 28
+    num_attention_heads: int = 16
+    num_key_value_heads: int = 8
+    head_dim: int = 128
+    rms_norm_eps: float = 1e-6
+    rope_theta: float = 1e6
+    max_position_embeddings: int = 40960
+    tie_word_embeddings: bool = True
+    attention_bias: bool = False  # Qwen2: bias on q/k/v
+    qk_norm: bool = True  # Qwen3: per-head RMSNorm on q and k
+    # MoE (qwen3_moe)
+    num_experts: int = 0
+    num_experts_per_tok: int = 0
+    moe_intermediate_size: int = 0
+    norm_topk_prob: bool = True
+    decoder_sparse_step: int = 1
+    mlp_only_layers: list[int] = field(default_factory=list)
+    # critic / reward model: scalar head instead of the LM head
+    is_critic: bool = False
+
+    @property
+    def is_moe(self) -> bool:
+        return self.num_experts > 0
+
+    def layer_is_moe(self, i: int) -> bool:
+        return (self.is_moe and i not in self.mlp_only_layers
+                and (i + 1) % max(self.decoder_sparse_step, 1) == 0)
+
+    @property
+    def q_size(self) -> int:
+        return self.num_attention_heads * self.head_dim
+
+    @property
+    def kv_size(self) -> int:
+        return self.num_key_value_heads * self.head_dim
+
+    def num_params(self) -> int:
+        h, L = self.hidden_size, self.num_hidden_layers
+        attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        if self.attention_bias:
+            attn += self.q_size + 2 * self.kv_size
+        if self.qk_norm:
+            attn += 2 * self.head_dim
+        dense_mlp = 3 * h * self.intermediate_size
+        moe_mlp = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
+        n = 0
+        for i in range(L):
+            n += attn + 2 * h + (moe_mlp if self.layer_is_moe(i) else dense_mlp)
+        n += self.vocab_size * h + h
+        if not self.tie_word_embeddings and not self.is_critic:
+            n += self.vocab_size * h
+        if self.is_critic:
+            n += h
+        return n
+
+    def flops_per_token(self, seq_len: int, backward: bool = True) -> float:
+        """Model FLOPs per token for a sequence of ``seq_len`` (causal attention)."""
+        h, L = self.hidden_size, self.num_hidden_layers
+        lin = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        act_mlp = (3 * h * self.moe_intermediate_size * self.num_experts_per_tok
+                   if self.is_moe else 3 * h * self.intermediate_size)
+        per_layer = 2 * (lin + act_mlp) + 4 * self.q_size * (seq_len / 2)
+        total = L * per_layer + 2 * h * self.vocab_size
+        return total * (3 if backward else 1)
+
+    @classmethod
+    def from_hf_config(cls, cfg: dict | str | Path, **overrides) -> "ModelConfig":
+        if not isinstance(cfg, dict):
+            p = Path(cfg)
+            p = p / "config.json" if p.is_dir() else p
+            cfg = json.loads(p.read_text())
+        mt = cfg.get("model_type", "qwen3")
+        heads = cfg["num_attention_heads"]
+        out = cls(
+            model_type=mt,
+            vocab_size=cfg["vocab_size"],
+            hidden_size=cfg["hidden_size"],
+            intermediate_size=cfg.get("intermediate_size", 0),
+            num_hidden_layers=cfg["num_hidden_layers"],
+            num_attention_heads=heads,
+            num_key_value_heads=cfg.get("num_key_value_heads", heads),
+            head_dim=cfg.get("head_dim") or cfg["hidden_size"] // heads,
+            rms_norm_eps=cfg.get("rms_norm_eps", 1e-6),
+            rope_theta=cfg.get("rope_theta", 1e4),
+            max_position_embeddings=cfg.get("max_position_embeddings", 32768),
+            tie_word_embeddings=cfg.get("tie_word_embeddings", False),
+            attention_bias=cfg.get("attention_bias", mt == "qwen2"),
+            qk_norm=mt.startswith("qwen3"),
+            num_experts=cfg.get("num_experts", 0) or 0,
+            num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
+            moe_intermediate_size=cfg.get("moe_intermediate_size", 0) or 0,
+            norm_topk_prob=cfg.get("norm_topk_prob", True),
+            decoder_sparse_step=cfg.get("decoder_sparse_step", 1) or 1,
+            mlp_only_layers=list(cfg.get("mlp_only_layers", []) or []),
+        )
+        for k, v in overrides.items():
+            setattr(out, k, v)
+        return out
+
+    def to_hf_config(self) -> dict:
+        arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
+                "qwen3_moe": "Qwen3MoeForCausalLM"}[self.model_type]
+        d = {
+            "architectures": [arch], "model_type": self.model_type,
+            "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+            "intermediate_size": self.intermediate_size,
+            "num_hidden_layers": self.num_hidden_layers,
+            "num_attention_heads": self.num_attention_heads,
+            "num_key_value_heads": self.num_key_value_heads, "head_dim": self.head_dim,
+            "rms_norm_eps": self.rms_norm_eps, "rope_theta": self.rope_theta,
+            "max_position_embeddings": self.max_position_embeddings,
+            "tie_word_embeddings": self.tie_word_embeddings,
+            "attention_bias": self.attention_bias, "hidden_act": "silu",
+            "torch_dtype": "bfloat16",
+        }
+        if self.is_moe:
+            d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                     moe_intermediate_size=self.moe_intermediate_size,
+                     norm_topk_prob=self.norm_topk_prob,
+                     decoder_sparse_step=self.decoder_sparse_step,
+                     mlp_only_layers=self.mlp_only_layers)
+        return d
+
+    def asdict(self) -> dict:
+        return asdict(self)
+
+
+# Named shapes used by the benchmark configurations (random-init, synthetic data).
+PRESETS: dict[str, ModelConfig] = {
+    "tiny-qwen2": ModelConfig(model_type="qwen2", vocab_size=1024, hidden_size=256,
+                              intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
+                              num_key_value_heads=2, head_dim=64, rope_theta=1e4,
+                              tie_word_embeddings=False, attention_bias=True, qk_norm=False),
+    "qwen3-1.7b": ModelConfig(model_type="qwen3", hidden_size=2048, intermediate_size=6144,
+                              num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
+                              tie_word_embeddings=True),
+    "qwen3-8b": ModelConfig(model_type="qwen3", hidden_size=4096, intermediate_size=12288,
+                            num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8,
+                            tie_word_embeddings=False),
+    "qwen2.5-7b": ModelConfig(model_type="qwen2", vocab_size=152064, hidden_size=3584,
+                              intermediate_size=18944, num_hidden_layers=28,
+                              num_attention_heads=28, num_key_value_heads=4, head_dim=128,
+                              rope_theta=1e6, tie_word_embeddings=False, attention_bias=True,
+                              qk_norm=False),
+    "qwen3-30b-a3b": ModelConfig(model_type="qwen3_moe", hidden_size=2048, intermediate_size=6144,
+                                 num_hidden_layers=48, num_attention_heads=32,
+                                 num_key_value_heads=4, tie_word_embeddings=False,
+                                 num_experts=128, num_experts_per_tok=8,
+                                 moe_intermediate_size=768),
+}
