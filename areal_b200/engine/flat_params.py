@@ -1,0 +1,236 @@
+"""Flat parameter / gradient storage and the sharded AdamW that runs on it.
+
+All parameters of a model live in ONE bf16 buffer (each parameter a view at a
+128-byte aligned offset) and all fp32 main gradients in a second buffer of the
+same layout. On CUDA both are symmetric-memory allocations, so
+
+* GEMM wgrad epilogues accumulate straight into ``param.main_grad`` (fp32);
+* the optimizer step is two kernels (``csrc/optim.cu``): a reduce-scatter that
+  pulls this rank's gradient slice from every data-parallel peer over NVLink
+  while computing its squared norm, and an AdamW that clips, updates the fp32
+  master shard and stores the new bf16 weights into every peer's parameter
+  buffer (the all-gather);
+* trainer→rollout weight sync is a peer copy of the same flat layout.
+
+With 180 GB of HBM the bf16 weights are replicated (no per-layer all-gather in
+forward/backward) while fp32 master weights and Adam moments are sharded —
+ZeRO-2 style. On CPU the same algorithm runs with ``torch.distributed``
+collectives, which is the oracle for the CUDA path and what the gloo tests use.
+
+Reference counterparts: FSDP2 sharding + fused AdamW + grad-norm clipping
+(areal/engine/fsdp_utils/__init__.py:62-106, grad.py:89-281, fsdp_engine.py:682-713).
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+import torch.distributed as dist
+
+from ..api.cli_args import OptimizerConfig
+from ..ops import _lib
+from ..parallel.symm_mem import SymmBarrier, SymmBuffer
+
+_ALIGN = 64  # elements: 128 bytes in bf16, 256 in fp32
+
+
+class FlatParams:
+    def __init__(self, model: torch.nn.Module, dp_group: dist.ProcessGroup | None, with_grads: bool = True):
+        params = [p for p in model.parameters()]
+        assert params, "model has no parameters"
+        self.model = model
+        self.device = params[0].device
+        self.dtype = params[0].dtype
+        self.dp_group = dp_group
+        self.dp_world = dist.get_world_size(dp_group) if dist.is_initialized() else 1
+        self.dp_rank = dist.get_rank(dp_group) if dist.is_initialized() else 0
+        self.entries: list[tuple[str, torch.nn.Parameter, int, int]] = []
+        off = 0
+        seen: dict[int, int] = {}
+        for name, p in model.named_parameters():
+            if id(p) in seen:
+                continue
+            seen[id(p)] = off
+            self.entries.append((name, p, off, p.numel()))
+            off += (p.numel() + _ALIGN - 1) // _ALIGN * _ALIGN
+        # shard boundaries must be multiples of 4 elements for the vector kernels
+        quantum = self.dp_world * _ALIGN
+        self.numel = (off + quantum - 1) // quantum * quantum
+        self.shard_numel = self.numel // self.dp_world
+        self.shard_offset = self.dp_rank * self.shard_numel
+        self.cuda = self.device.type == "cuda"
+        itemsize = torch.empty((), dtype=self.dtype).element_size()
+        if self.cuda:
+            self.param_buf = SymmBuffer(self.numel * itemsize, dp_group, self.device)
+            self.flat = self.param_buf.tensor(self.dtype, self.numel)
+            if with_grads:
+                self.grad_buf = SymmBuffer(self.numel * 4, dp_group, self.device)
+                self.main_grad = self.grad_buf.tensor(torch.float32, self.numel)
+                self.barrier = SymmBarrier(dp_group, self.device)
+        else:
+            self.flat = torch.zeros(self.numel, dtype=self.dtype)
+            self.main_grad = torch.zeros(self.numel, dtype=torch.float32) if with_grads else None
+        with torch.no_grad():
+            for name, p, o, n in self.entries:
+                view = self.flat[o:o + n].view(p.shape)
+                view.copy_(p.data)
+                p.data = view
+                if with_grads:
+                    p.main_grad = self.main_grad[o:o + n].view(p.shape)
+        self.with_grads = with_grads
+
+    def zero_grad(self):
+        if self.with_grads:
+            self.main_grad.zero_()
+        for _, p, _, _ in self.entries:
+            p.grad = None
+
+    def collect_autograd_grads(self):
+        """Adds gradients that autograd produced (norm weights, biases, router, CPU path)
+        into the fp32 main-grad buffer; GEMM weights were already accumulated there."""
+        for _, p, _, _ in self.entries:
+            if p.grad is not None:
+                p.main_grad.add_(p.grad.to(torch.float32))
+                p.grad = None
+
+    def named_offsets(self) -> dict[str, tuple[int, int, tuple]]:
+        return {name: (o, n, tuple(p.shape)) for name, p, o, n in self.entries}
+
+
+def lr_at(step: int, total_steps: int, cfg: OptimizerConfig) -> float:
+    """Warm-up followed by constant / linear / cosine decay to ``min_lr_ratio``."""
+    warm = int(cfg.warmup_steps_proportion * max(total_steps, 1))
+    if warm > 0 and step < warm:
+        return cfg.lr * (step + 1) / warm
+    if cfg.lr_scheduler_type == "constant" or total_steps <= warm:
+        return cfg.lr
+    frac = min(max((step - warm) / max(total_steps - warm, 1), 0.0), 1.0)
+    lo = cfg.min_lr_ratio
+    if cfg.lr_scheduler_type == "linear":
+        return cfg.lr * (lo + (1 - lo) * (1 - frac))
+    return cfg.lr * (lo + (1 - lo) * 0.5 * (1 + math.cos(math.pi * frac)))
+
+
+class ShardedAdamW:
+    """AdamW over the rank's shard of the flat buffers (fp32 master, m, v)."""
+
+    def __init__(self, flat: FlatParams, cfg: OptimizerConfig, total_steps: int = 1):
+        self.flat = flat
+        self.cfg = cfg
+        self.total_steps = total_steps
+        self.step_count = 0  # optimizer steps taken (bias correction)
+        self.sched_step = 0  # scheduler position
+        n, o = flat.shard_numel, flat.shard_offset
+        dev = flat.device
+        self.master = flat.flat[o:o + n].to(torch.float32).clone()
+        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.shard_grad = torch.zeros(n, dtype=torch.float32, device=dev)
+        if flat.cuda:
+            self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
+            self._skipped = torch.zeros(1, dtype=torch.int32, device=dev)
+            self._grad_table = flat.grad_buf.ptr_table()
+            self._param_table = flat.param_buf.ptr_table()
+        self.extra_param_tables: list = []  # rollout buffers that mirror the weights
+
+    @property
+    def lr(self) -> float:
+        return lr_at(self.sched_step, self.total_steps, self.cfg)
+
+    def refresh_master(self):
+        """Re-reads the master shard from the (re)loaded bf16 weights."""
+        n, o = self.flat.shard_numel, self.flat.shard_offset
+        self.master.copy_(self.flat.flat[o:o + n].to(torch.float32))
+
+    def step(self, grad_scale: float = 1.0) -> dict[str, float]:
+        self.flat.collect_autograd_grads()
+        out = self._step_cuda(grad_scale) if self.flat.cuda else self._step_torch(grad_scale)
+        self.flat.zero_grad()
+        return out
+
+    # ---------------------------------------------------------------- CUDA
+    def _step_cuda(self, grad_scale: float) -> dict[str, float]:
+        f, cfg = self.flat, self.cfg
+        lib = _lib.kernels()
+        world = f.dp_world
+        if world > 1:
+            f.barrier.sync()  # every peer finished writing its gradients
+        self._norm.zero_()
+        rc = lib.b200_reduce_scatter_sumsq(self._grad_table, ctypes.c_int(world),
+                                           ctypes.c_longlong(f.shard_offset),
+                                           ctypes.c_longlong(f.shard_numel), ctypes.c_float(grad_scale),
+                                           _lib.ptr(self.shard_grad), _lib.ptr(self._norm),
+                                           _lib.stream_ptr())
+        _lib.check(rc, "b200_reduce_scatter_sumsq")
+        if world > 1:
+            dist.all_reduce(self._norm, group=f.dp_group)
+        t = self.step_count + 1
+        lr = self.lr
+        self._skipped.zero_()
+        rc = lib.b200_adamw_bcast(_lib.ptr(self.master), _lib.ptr(self.exp_avg), _lib.ptr(self.exp_avg_sq),
+                                  _lib.ptr(self.shard_grad), self._param_table, ctypes.c_int(world),
+                                  ctypes.c_longlong(f.shard_offset), ctypes.c_longlong(f.shard_numel),
+                                  _lib.ptr(self._norm), ctypes.c_float(lr), ctypes.c_float(cfg.beta1),
+                                  ctypes.c_float(cfg.beta2), ctypes.c_float(cfg.eps),
+                                  ctypes.c_float(cfg.weight_decay), ctypes.c_float(1 - cfg.beta1 ** t),
+                                  ctypes.c_float(1 - cfg.beta2 ** t), ctypes.c_float(cfg.gradient_clipping),
+                                  _lib.ptr(self._skipped), _lib.stream_ptr())
+        _lib.check(rc, "b200_adamw_bcast")
+        _lib.count_launch(2)
+        if world > 1:
+            f.barrier.sync()  # all shards of the new weights have landed everywhere
+        vals = torch.cat([self._norm, self._skipped.float()]).tolist()
+        ok = vals[1] == 0 and math.isfinite(vals[0])
+        if ok:
+            self.step_count = t
+        return dict(grad_norm=math.sqrt(vals[0]) if vals[0] >= 0 else float("nan"),
+                    update_successful=float(ok), lr=lr)
+
+    # --------------------------------------------------------------- torch
+    def _step_torch(self, grad_scale: float) -> dict[str, float]:
+        f, cfg = self.flat, self.cfg
+        g = f.main_grad
+        if f.dp_world > 1:
+            dist.all_reduce(g, group=f.dp_group)
+        o, n = f.shard_offset, f.shard_numel
+        self.shard_grad.copy_(g[o:o + n] * grad_scale)
+        nsq = (self.shard_grad.double() ** 2).sum().float().reshape(1)
+        if f.dp_world > 1:
+            dist.all_reduce(nsq, group=f.dp_group)
+        norm = float(nsq.sqrt())
+        lr = self.lr
+        if not math.isfinite(norm):
+            return dict(grad_norm=norm, update_successful=0.0, lr=lr)
+        coef = min(1.0, cfg.gradient_clipping / (norm + 1e-6)) if cfg.gradient_clipping > 0 else 1.0
+        t = self.step_count + 1
+        gk = self.shard_grad * coef
+        self.exp_avg.mul_(cfg.beta1).add_(gk, alpha=1 - cfg.beta1)
+        self.exp_avg_sq.mul_(cfg.beta2).addcmul_(gk, gk, value=1 - cfg.beta2)
+        denom = self.exp_avg_sq.sqrt() / math.sqrt(1 - cfg.beta2 ** t) + cfg.eps
+        self.master.mul_(1 - lr * cfg.weight_decay).addcdiv_(self.exp_avg, denom, value=-lr / (1 - cfg.beta1 ** t))
+        new = self.master.to(f.dtype)
+        if f.dp_world > 1:
+            parts = [torch.empty_like(new) for _ in range(f.dp_world)]
+            dist.all_gather(parts, new, group=f.dp_group)
+            f.flat.copy_(torch.cat(parts))
+        else:
+            f.flat[o:o + n].copy_(new)
+        self.step_count = t
+        return dict(grad_norm=norm, update_successful=1.0, lr=lr)
+
+    # ------------------------------------------------------------ checkpoint
+    def state_dict(self) -> dict:
+        return dict(master=self.master, exp_avg=self.exp_avg, exp_avg_sq=self.exp_avg_sq,
+                    step_count=self.step_count, sched_step=self.sched_step,
+                    shard_offset=self.flat.shard_offset, shard_numel=self.flat.shard_numel,
+                    dp_world=self.flat.dp_world)
+
+    def load_state_dict(self, s: dict):
+        if s["dp_world"] != self.flat.dp_world or s["shard_numel"] != self.flat.shard_numel:
+            raise ValueError("optimizer shards were saved with a different data-parallel size")
+        self.master.copy_(s["master"])
+        self.exp_avg.copy_(s["exp_avg"])
+        self.exp_avg_sq.copy_(s["exp_avg_sq"])
+        self.step_count, self.sched_step = s["step_count"], s["sched_step"]

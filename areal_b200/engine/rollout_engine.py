@@ -1,0 +1,488 @@
+"""In-process rollout engine: continuous batching over a paged KV cache on this
+library's kernels, with interruptible generation and in-place weight updates.
+
+The reference has no inference engine of its own — it drives external SGLang /
+vLLM servers through HTTP (areal/infra/remote_inf_engine.py:719-884,
+areal/engine/sglang_remote.py). This engine provides the same behaviour behind
+the ``InferenceEngine`` contract:
+
+* ``agenerate`` returns token ids, per-token logprobs and the *policy version of
+  every generated token*; if generation is paused for a weight update the
+  in-flight request is aborted inside the scheduler and transparently resumed
+  with everything generated so far, so one response can span several versions;
+* ``pause_generation`` / ``continue_generation`` / ``receive_weights`` /
+  ``update_weights_from_disk`` / ``set_version``;
+* ``submit`` / ``wait`` / ``prepare_batch`` / ``rollout_batch`` through the
+  workflow executor (bounded staleness).
+
+A background thread runs the engine loop: plan (C++ scheduler) → prefill or
+decode step (model on the current CUDA stream) → fused sampling → commit.
+"""
+
+from __future__ import annotations
+
+import asyncio
+import ctypes
+import dataclasses
+import threading
+import time
+from concurrent.futures import Future
+from typing import Any
+
+import numpy as np
+import torch
+
+from ..api.cli_args import InferenceEngineConfig, NativeRolloutConfig
+from ..api.engine_api import InferenceEngine
+from ..api.io_struct import ModelRequest, ModelResponse, ParamSpec, WeightUpdateMeta
+from ..models.config import PRESETS, ModelConfig
+from ..models.qwen import build_model
+from ..ops import _lib
+from ..ops.attention import VarlenMeta
+from ..ops.rollout_ops import sample
+from ..utils import logging
+from .flat_params import FlatParams
+
+logger = logging.getLogger("RolloutEngine")
+
+_REASONS = {1: "stop", 2: "length", 3: "abort"}
+
+
+class _PlanHeader(ctypes.Structure):
+    _fields_ = [("kind", ctypes.c_int32), ("n_seqs", ctypes.c_int32), ("n_tokens", ctypes.c_int32),
+                ("max_seq_len", ctypes.c_int32)]
+
+
+class PagedScheduler:
+    """ctypes façade of ``csrc/host/rollout_scheduler.cpp``."""
+
+    def __init__(self, num_blocks, block_size, max_num_seqs, max_batched_tokens, max_blocks_per_seq):
+        self.lib = _lib.host()
+        self.lib.b200_sched_create.restype = ctypes.c_void_p
+        self.lib.b200_sched_add.restype = ctypes.c_int64
+        self.lib.b200_sched_pop_finished.restype = ctypes.c_int64
+        self.h = ctypes.c_void_p(self.lib.b200_sched_create(num_blocks, block_size, max_num_seqs,
+                                                            max_batched_tokens, max_blocks_per_seq))
+        self.max_num_seqs, self.max_blocks_per_seq = max_num_seqs, max_blocks_per_seq
+        cap = max(max_batched_tokens, max_num_seqs)
+        self.seq_ids = np.zeros(max_num_seqs, dtype=np.int64)
+        self.cu = np.zeros(max_num_seqs + 1, dtype=np.int32)
+        self.tokens = np.zeros(cap, dtype=np.int32)
+        self.positions = np.zeros(cap, dtype=np.int32)
+        self.slots = np.zeros(cap, dtype=np.int64)
+        self.seq_lens = np.zeros(max_num_seqs, dtype=np.int32)
+        self.block_table = np.zeros(max_num_seqs * max_blocks_per_seq, dtype=np.int32)
+        self.hdr = _PlanHeader()
+
+    @staticmethod
+    def _p(a):
+        return a.ctypes.data_as(ctypes.c_void_p)
+
+    def add(self, prompt, max_new, min_new, stop_ids, ignore_eos) -> int:
+        p = np.ascontiguousarray(prompt, dtype=np.int32)
+        s = np.ascontiguousarray(stop_ids, dtype=np.int32)
+        return int(self.lib.b200_sched_add(self.h, self._p(p), ctypes.c_int(len(p)), ctypes.c_int(max_new),
+                                           ctypes.c_int(min_new), self._p(s), ctypes.c_int(len(s)),
+                                           ctypes.c_int(int(ignore_eos))))
+
+    def plan(self) -> int:
+        return self.lib.b200_sched_plan(self.h, ctypes.byref(self.hdr), self._p(self.seq_ids), self._p(self.cu),
+                                        self._p(self.tokens), self._p(self.positions), self._p(self.slots),
+                                        self._p(self.seq_lens), self._p(self.block_table))
+
+    def commit(self, sampled: np.ndarray, logprobs: np.ndarray) -> int:
+        return self.lib.b200_sched_commit(self.h, self._p(np.ascontiguousarray(sampled, dtype=np.int32)),
+                                          self._p(np.ascontiguousarray(logprobs, dtype=np.float32)),
+                                          ctypes.c_int(len(sampled)))
+
+    def abort_all(self) -> int:
+        return self.lib.b200_sched_abort_all(self.h)
+
+    def abort(self, rid: int) -> int:
+        return self.lib.b200_sched_abort(self.h, ctypes.c_int64(rid))
+
+    def pop_finished(self):
+        reason, n = ctypes.c_int32(0), ctypes.c_int32(0)
+        rid = self.lib.b200_sched_pop_finished(self.h, ctypes.byref(reason), ctypes.byref(n))
+        if rid == 0:
+            return None
+        toks = np.zeros(max(n.value, 1), dtype=np.int32)
+        lps = np.zeros(max(n.value, 1), dtype=np.float32)
+        got = self.lib.b200_sched_take_output(self.h, ctypes.c_int64(rid), self._p(toks), self._p(lps),
+                                              ctypes.c_int(len(toks)))
+        return int(rid), _REASONS.get(reason.value, "stop"), toks[:got].tolist(), lps[:got].tolist()
+
+    def stats(self) -> dict[str, int]:
+        a = np.zeros(5, dtype=np.int64)
+        self.lib.b200_sched_stats(self.h, self._p(a))
+        return dict(waiting=int(a[0]), running=int(a[1]), free_blocks=int(a[2]), preemptions=int(a[3]),
+                    live=int(a[4]))
+
+    def close(self):
+        if self.h:
+            self.lib.b200_sched_destroy(self.h)
+            self.h = None
+
+
+class NativeRolloutEngine(InferenceEngine):
+    def __init__(self, config: InferenceEngineConfig):
+        self.config = config
+        self.ncfg: NativeRolloutConfig = config.native
+        self.model = None
+        self.flat: FlatParams | None = None
+        self.sched: PagedScheduler | None = None
+        self._version = 0
+        self._paused = threading.Event()
+        self._stop = threading.Event()
+        self._wake = threading.Condition()
+        self._thread: threading.Thread | None = None
+        self._pending: dict[int, tuple[asyncio.AbstractEventLoop, asyncio.Future, dict]] = {}
+        self._params: dict[int, tuple[float, int, float]] = {}
+        self._lock = threading.Lock()
+        self._executor = None
+        self._gen_tokens = 0
+        self._steps = 0
+        self._step_error: BaseException | None = None
+        self.device = None
+        self._idle = threading.Event()
+        self._idle.set()
+
+    # ------------------------------------------------------------------ setup
+    def initialize(self, engine_id: str | None = None, train_data_parallel_size: int | None = None,
+                   device=None, model=None, **kwargs):
+        ncfg = self.ncfg
+        use_cuda = torch.cuda.is_available()
+        self.device = torch.device(device) if device is not None else (
+            torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu"))
+        if ncfg.model_path:
+            mc = ModelConfig.from_hf_config(ncfg.model_path)
+        elif ncfg.model_preset:
+            mc = dataclasses.replace(PRESETS[ncfg.model_preset])
+        else:
+            raise ValueError("NativeRolloutConfig needs model_path or model_preset")
+        for k, v in (ncfg.model_overrides or {}).items():
+            setattr(mc, k, v)
+        self.model_config = mc
+        dtype = torch.float32 if self.device.type == "cpu" else getattr(torch, ncfg.dtype)
+        self.model = build_model(mc, dtype=dtype, device=self.device, seed=ncfg.seed)
+        if ncfg.model_path:
+            from ..utils.hf_io import load_hf_weights
+
+            load_hf_weights(self.model, ncfg.model_path)
+        self.model.eval()
+        for p in self.model.parameters():
+            p.requires_grad_(False)
+        # weights live in one flat buffer with the trainer's layout: weight sync is a flat copy
+        self.flat = FlatParams(self.model, kwargs.get("weight_group"), with_grads=False)
+        bs = ncfg.kv_block_size
+        max_blocks_per_seq = (ncfg.context_length + bs - 1) // bs
+        nblocks = ncfg.num_kv_blocks or self._auto_num_blocks(mc, dtype, bs)
+        self.kv_caches = [
+            (torch.zeros(nblocks, bs, mc.num_key_value_heads, mc.head_dim, dtype=dtype, device=self.device),
+             torch.zeros(nblocks, bs, mc.num_key_value_heads, mc.head_dim, dtype=dtype, device=self.device))
+            for _ in range(mc.num_hidden_layers)]
+        self.sched = PagedScheduler(nblocks, bs, ncfg.max_num_seqs, ncfg.max_num_batched_tokens,
+                                    max_blocks_per_seq)
+        self._rng = torch.Generator(device=self.device).manual_seed(ncfg.seed)
+        self._thread = threading.Thread(target=self._loop, name="rollout-engine", daemon=True)
+        self._thread.start()
+        from ..infra.workflow_executor import WorkflowExecutor
+
+        self._executor = WorkflowExecutor(self.config, self)
+        self._executor.initialize(train_data_parallel_size=train_data_parallel_size)
+        logger.info(f"rollout engine ready on {self.device}: {nblocks} KV pages of {bs} tokens")
+        return self
+
+    def _auto_num_blocks(self, mc: ModelConfig, dtype, bs: int) -> int:
+        per_block = 2 * mc.num_hidden_layers * bs * mc.num_key_value_heads * mc.head_dim * \
+            torch.empty((), dtype=dtype).element_size()
+        if self.device.type == "cuda":
+            free, total = torch.cuda.mem_get_info(self.device)
+            budget = int(free * self.ncfg.mem_fraction_static)
+        else:
+            budget = 256 << 20
+        need = self.ncfg.max_num_seqs * ((self.ncfg.context_length + bs - 1) // bs)
+        return max(16, min(budget // per_block, need))
+
+    def destroy(self):
+        self._stop.set()
+        with self._wake:
+            self._wake.notify_all()
+        if self._thread is not None:
+            self._thread.join(timeout=10)
+        if self._executor is not None:
+            self._executor.destroy()
+        if self.sched is not None:
+            self.sched.close()
+        self.kv_caches = None
+        self.model = None
+
+    # ------------------------------------------------------------- engine loop
+    def _loop(self):
+        if self.device.type == "cuda":
+            torch.cuda.set_device(self.device)
+        stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        while not self._stop.is_set():
+            try:
+                if self._paused.is_set():
+                    self._idle.set()
+                    time.sleep(0.0005)
+                    continue
+                self._idle.clear()
+                if stream is not None:
+                    with torch.cuda.stream(stream):
+                        worked = self._step()
+                else:
+                    worked = self._step()
+                if not worked:
+                    self._idle.set()
+                    with self._wake:
+                        self._wake.wait(timeout=0.002)
+            except BaseException as e:  # surface engine failures to every waiter
+                logger.error(f"rollout engine loop failed: {type(e).__name__}: {e}")
+                self._step_error = e
+                self._fail_all(e)
+                self._idle.set()
+                return
+        self._idle.set()
+
+    @torch.no_grad()
+    def _step(self) -> bool:
+        s = self.sched
+        kind = s.plan()
+        if kind == 0:
+            self._deliver()
+            return False
+        n, T = s.hdr.n_seqs, s.hdr.n_tokens
+        dev = self.device
+        ids = torch.from_numpy(s.tokens[:T].copy()).to(dev, non_blocking=True)
+        pos = torch.from_numpy(s.positions[:T].copy()).to(dev, non_blocking=True)
+        slots = torch.from_numpy(s.slots[:T].copy()).to(dev, non_blocking=True)
+        seq_ids = s.seq_ids[:n].tolist()
+        if kind == 1:
+            cu = s.cu[: n + 1].copy()
+            meta = VarlenMeta(cu.tolist(), dev)
+            hidden = self.model.prefill(ids, pos, meta, self.kv_caches, slots)
+            last = torch.from_numpy((cu[1:] - 1).astype(np.int64)).to(dev)
+            hidden = hidden.index_select(0, last)
+        else:
+            seq_lens = torch.from_numpy(s.seq_lens[:n].copy()).to(dev, non_blocking=True)
+            bt = torch.from_numpy(s.block_table[: n * s.max_blocks_per_seq].copy()).view(n, -1)
+            nb = (int(s.hdr.max_seq_len) + self.ncfg.kv_block_size - 1) // self.ncfg.kv_block_size
+            bt = bt[:, :max(nb, 1)].contiguous().to(dev, non_blocking=True)
+            hidden = self.model.decode(ids, pos, self.kv_caches, bt, seq_lens, slots,
+                                       max_seq_len=int(s.hdr.max_seq_len))
+        logits = self.model.logits(hidden, out_dtype=torch.float32)
+        with self._lock:
+            pr = [self._params.get(r, (1.0, 0, 1.0)) for r in seq_ids]
+        temp = torch.tensor([p[0] for p in pr], dtype=torch.float32, device=dev)
+        need_k = any(p[1] > 0 for p in pr)
+        need_p = any(p[2] < 1.0 for p in pr)
+        top_k = torch.tensor([p[1] for p in pr], dtype=torch.int32, device=dev) if need_k else None
+        top_p = torch.tensor([p[2] for p in pr], dtype=torch.float32, device=dev) if need_p else None
+        u = torch.rand(n, device=dev, generator=self._rng, dtype=torch.float32)
+        toks, lps = sample(logits, temp, top_k, top_p, u)
+        s.commit(toks.cpu().numpy(), lps.cpu().numpy())
+        self._gen_tokens += n
+        self._steps += 1
+        self._deliver()
+        return True
+
+    def _deliver(self):
+        while True:
+            item = self.sched.pop_finished()
+            if item is None:
+                return
+            rid, reason, toks, lps = item
+            with self._lock:
+                entry = self._pending.pop(rid, None)
+                self._params.pop(rid, None)
+            if entry is None:
+                continue
+            loop, fut, _ = entry
+            loop.call_soon_threadsafe(_set_result, fut, (reason, toks, lps))
+
+    def _fail_all(self, e: BaseException):
+        with self._lock:
+            entries = list(self._pending.values())
+            self._pending.clear()
+        for loop, fut, _ in entries:
+            loop.call_soon_threadsafe(_set_exception, fut, e)
+
+    # --------------------------------------------------------------- generate
+    async def _generate_once(self, input_ids: list[int], g, max_new: int):
+        if self._step_error is not None:
+            raise RuntimeError("rollout engine stopped") from self._step_error
+        loop = asyncio.get_running_loop()
+        fut = loop.create_future()
+        stop = list(g.stop_token_ids or [])
+        temp = 0.0 if g.greedy else float(g.temperature)
+        top_k = int(g.top_k) if 0 < int(g.top_k) < self.model_config.vocab_size else 0
+        with self._lock:
+            rid = self.sched.add(input_ids, max_new, int(g.min_new_tokens), stop, bool(g.ignore_eos))
+            if rid < 0:
+                raise ValueError(f"prompt of {len(input_ids)} tokens does not fit the rollout engine")
+            self._pending[rid] = (loop, fut, {})
+            self._params[rid] = (temp, top_k, float(g.top_p))
+        with self._wake:
+            self._wake.notify_all()
+        return await fut
+
+    async def agenerate(self, req: ModelRequest) -> ModelResponse:
+        g = req.gconfig
+        if g.n_samples != 1:
+            raise ValueError("agenerate produces one sample; use n_samples=1 and group at the workflow level")
+        max_new = min(g.max_new_tokens, max(g.max_tokens - len(req.input_ids), 0))
+        t0 = time.perf_counter()
+        out_tokens: list[int] = []
+        out_logprobs: list[float] = []
+        out_versions: list[int] = []
+        stop_reason = "length"
+        ttft = float("inf")
+        while len(out_tokens) < max_new:
+            while self._paused.is_set():
+                await asyncio.sleep(0.001)
+            version = self._version
+            reason, toks, lps = await self._generate_once(list(req.input_ids) + out_tokens, g,
+                                                          max_new - len(out_tokens))
+            if toks and ttft == float("inf"):
+                ttft = time.perf_counter() - t0
+            out_tokens += toks
+            out_logprobs += lps
+            out_versions += [version] * len(toks)
+            stop_reason = reason
+            if reason != "abort":
+                break
+        if stop_reason == "abort":
+            stop_reason = "length"
+        return ModelResponse(input_tokens=list(req.input_ids), output_tokens=out_tokens,
+                             output_logprobs=out_logprobs, output_versions=out_versions,
+                             stop_reason=stop_reason, tokenizer=req.tokenizer,
+                             latency=time.perf_counter() - t0, ttft=ttft)
+
+    # ------------------------------------------------------ pause / weights
+    def pause_generation(self):
+        """Stops the engine loop after the current step and aborts in-flight requests;
+        their callers keep the partial output and resume after ``continue_generation``."""
+        self._paused.set()
+        self._idle.wait(timeout=60)
+        with self._lock:
+            self.sched.abort_all()
+        self._deliver()
+
+    def continue_generation(self):
+        self._paused.clear()
+        with self._wake:
+            self._wake.notify_all()
+
+    def receive_weights(self, trainer, version: int | None = None):
+        """Copies the trainer's flat bf16 weights into this engine's flat buffer. Both sides
+        use the same model class, hence the same layout, so this is one device copy (a peer
+        copy over NVLink when the two engines sit on different GPUs)."""
+        src = trainer.flat.flat
+        dst = self.flat.flat
+        assert src.numel() >= dst.numel() or dst.numel() >= src.numel()
+        n = min(src.numel(), dst.numel())
+        if src.dtype == dst.dtype:
+            dst[:n].copy_(src[:n], non_blocking=True)
+        else:
+            dst[:n].copy_(src[:n].to(dst.dtype))
+        if self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
+        if version is not None:
+            self._version = version
+
+    def update_weights_from_disk(self, meta: WeightUpdateMeta) -> Future:
+        fut: Future = Future()
+        try:
+            from ..utils.hf_io import load_hf_weights
+
+            self.pause_generation()
+            load_hf_weights(self.model, meta.path)
+            if meta.version is not None:
+                self._version = meta.version
+            self.continue_generation()
+            fut.set_result(None)
+        except BaseException as e:
+            fut.set_exception(e)
+        return fut
+
+    def update_weights_from_distributed(self, meta: WeightUpdateMeta, param_specs: list[ParamSpec]) -> Future:
+        fut: Future = Future()
+        fut.set_result(None)
+        return fut
+
+    def init_weights_update_group(self, meta: WeightUpdateMeta) -> Future:
+        fut: Future = Future()
+        fut.set_result(None)
+        return fut
+
+    def set_version(self, version: int):
+        self._version = version
+        if self._executor is not None:
+            self._executor.on_version_changed(version)
+
+    def get_version(self) -> int:
+        return self._version
+
+    # ---------------------------------------------------------- workflow API
+    def submit(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1,
+               task_id=None, callback_addr=None, is_eval=False, proxy_addr=None) -> int:
+        return self._executor.submit(data, workflow, workflow_kwargs, should_accept_fn, group_size,
+                                     task_id=task_id, is_eval=is_eval)
+
+    def wait(self, count: int, timeout: float | None = None, raise_timeout: bool = True):
+        return self._executor.wait(count, timeout, raise_timeout)
+
+    def wait_for_task(self, task_id: int, timeout: float | None = None, raise_timeout: bool = True):
+        return self._executor.wait_for_task(task_id, timeout, raise_timeout)
+
+    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1):
+        return self._executor.rollout_batch(data, workflow, workflow_kwargs, should_accept_fn, group_size)
+
+    def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None,
+                      group_size=1, dynamic_bs=False):
+        return self._executor.prepare_batch(dataloader, workflow, workflow_kwargs, should_accept_fn,
+                                            group_size, dynamic_bs)
+
+    def pause(self):
+        self._executor.pause()
+
+    def resume(self):
+        self._executor.resume()
+
+    def offload(self):
+        """Releases the KV cache (colocated time-sharing with the trainer)."""
+        self.pause_generation()
+        self.kv_caches = None
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def onload(self, tags: list[str] | None = None):
+        if self.kv_caches is None:
+            mc, bs = self.model_config, self.ncfg.kv_block_size
+            dtype = next(self.model.parameters()).dtype
+            nblocks = self.sched.stats()["free_blocks"]
+            self.kv_caches = [
+                (torch.zeros(nblocks, bs, mc.num_key_value_heads, mc.head_dim, dtype=dtype, device=self.device),
+                 torch.zeros(nblocks, bs, mc.num_key_value_heads, mc.head_dim, dtype=dtype, device=self.device))
+                for _ in range(mc.num_hidden_layers)]
+        self.continue_generation()
+
+    def export_stats(self) -> dict[str, float]:
+        st = {f"rollout/{k}": float(v) for k, v in self.sched.stats().items()}
+        st["rollout/generated_tokens"] = float(self._gen_tokens)
+        st["rollout/engine_steps"] = float(self._steps)
+        if self._executor is not None:
+            st.update(self._executor.export_stats())
+        return st
+
+
+def _set_result(fut: asyncio.Future, value):
+    if not fut.done():
+        fut.set_result(value)
+
+
+def _set_exception(fut: asyncio.Future, e: BaseException):
+    if not fut.done():
+        fut.set_exception(e)

@@ -1,0 +1,425 @@
+"""The B200 train engine: packed varlen forward/backward on this library's
+kernels, flat ZeRO-style sharded optimizer with NVLink peer reduce-scatter /
+all-gather, fused LM-head logprobs, weight push to the rollout engine,
+HF-safetensors and sharded checkpoints.
+
+It implements the ``TrainEngine`` contract that the reference's FSDP / Archon
+engines implement (areal/engine/fsdp_engine.py:219-2256;
+areal/experimental/engine/archon_engine.py:147-1533): ``train_batch``,
+``forward_batch``, ``eval_batch``, ``update_weights``, ``save`` / ``load``,
+``offload`` / ``onload``. It runs on CUDA (bf16, hand-written kernels) and on CPU
+(fp32 PyTorch reference ops + gloo), the latter being the functional oracle.
+"""
+
+from __future__ import annotations
+
+import dataclasses
+import math
+import os
+import time
+from typing import Any, Callable
+
+import torch
+import torch.distributed as dist
+
+from ..api.alloc_mode import ModelAllocation, ParallelStrategy
+from ..api.cli_args import MicroBatchSpec, OptimizerConfig, TrainEngineConfig
+from ..api.engine_api import InferenceEngine, TrainEngine
+from ..api.io_struct import FinetuneSpec, ParamSpec, SaveLoadMeta, WeightUpdateMeta
+from ..models.config import PRESETS, ModelConfig
+from ..models.qwen import QwenModel, build_model
+from ..ops import _lib
+from ..ops.attention import VarlenMeta
+from ..ops.lm_head import lm_head_logprobs
+from ..utils import logging, stats_tracker
+from ..utils.data import (MicroBatchList, amend_position_ids, pack_tensor_dict, pad_mb_list,
+                          split_padded_tensor_dict_into_mb_list)
+from .flat_params import FlatParams, ShardedAdamW
+
+logger = logging.getLogger("TrainEngine")
+
+DIST_TIMEOUT_S = 7200
+
+
+def resolve_model_config(cfg: TrainEngineConfig) -> ModelConfig:
+    if cfg.path and os.path.exists(os.path.join(cfg.path, "config.json")):
+        mc = ModelConfig.from_hf_config(cfg.path)
+    elif cfg.model_preset:
+        mc = dataclasses.replace(PRESETS[cfg.model_preset])
+    else:
+        raise ValueError("TrainEngineConfig needs `path` (HF directory) or `model_preset`")
+    for k, v in (cfg.model_overrides or {}).items():
+        setattr(mc, k, v)
+    if cfg.is_critic:
+        mc.is_critic = True
+        mc.tie_word_embeddings = False
+    return mc
+
+
+class B200TrainEngine(TrainEngine):
+    def __init__(self, config: TrainEngineConfig):
+        self.config = config
+        self.optimizer_config: OptimizerConfig | None = config.optimizer
+        self.model: QwenModel | None = None
+        self.flat: FlatParams | None = None
+        self.optimizer: ShardedAdamW | None = None
+        self.model_config: ModelConfig | None = None
+        self._version = 0
+        self._initialized = False
+        self._own_pg = False
+        self.rank = 0
+        self.world_size = 1
+        self._dp_group = None
+        self._cpu_group = None
+        self.parallel = ParallelStrategy()
+        self.rollout_engine: InferenceEngine | None = None
+        self.weight_update_meta: WeightUpdateMeta | None = None
+        self._rollout_tables = None
+        self._offloaded: dict[str, torch.Tensor] | None = None
+        self.is_critic = config.is_critic
+
+    # ------------------------------------------------------------ process groups
+    def create_process_group(self, parallel_strategy: ParallelStrategy | None = None,
+                             ranks: list[int] | None = None, backend: str | None = None):
+        """Builds the data-parallel group over ``ranks`` (default: the whole world).
+        ``torch.distributed`` is initialised from the torchrun environment if needed."""
+        use_cuda = torch.cuda.is_available() and self.config.dtype != "float32_cpu"
+        if not dist.is_initialized() and "RANK" in os.environ:
+            backend = backend or ("nccl" if use_cuda else "gloo")
+            if use_cuda:
+                torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+            import datetime
+
+            dist.init_process_group(backend=backend, timeout=datetime.timedelta(seconds=DIST_TIMEOUT_S))
+            self._own_pg = True
+        if parallel_strategy is None and self.config.backend not in (None, "", "???"):
+            parallel_strategy = ModelAllocation.from_str(self.config.backend).parallel
+        self.parallel = parallel_strategy or ParallelStrategy()
+        if dist.is_initialized():
+            self.rank = dist.get_rank()
+            world = dist.get_world_size()
+            ranks = list(range(world)) if ranks is None else list(ranks)
+            self.train_ranks = ranks
+            if ranks == list(range(world)):
+                self._dp_group = dist.group.WORLD
+            else:
+                self._dp_group = dist.new_group(ranks)
+            self._cpu_group = dist.new_group(ranks, backend="gloo") if dist.get_backend() != "gloo" \
+                else self._dp_group
+            self.world_size = len(ranks)
+            self.dp_rank = ranks.index(self.rank) if self.rank in ranks else -1
+        else:
+            self.train_ranks = [0]
+            self.world_size, self.dp_rank = 1, 0
+        self.device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
+
+    @property
+    def data_parallel_group(self):
+        return self._dp_group
+
+    @property
+    def data_parallel_rank(self) -> int:
+        return self.dp_rank
+
+    @property
+    def data_parallel_world_size(self) -> int:
+        return self.world_size
+
+    @property
+    def context_and_model_parallel_group(self):
+        return None
+
+    @property
+    def cpu_group(self):
+        return self._cpu_group
+
+    def is_data_parallel_head(self) -> bool:
+        return True
+
+    def current_data_parallel_head(self) -> int:
+        return self.rank
+
+    # ----------------------------------------------------------------- init
+    def initialize(self, addr: str | None = None, ft_spec: FinetuneSpec | None = None, *args, **kwargs):
+        if not hasattr(self, "device"):
+            self.create_process_group()
+        cfg = self.config
+        self.model_config = resolve_model_config(cfg)
+        dtype = torch.float32 if self.device.type == "cpu" else getattr(torch, cfg.dtype)
+        t0 = time.perf_counter()
+        seed = kwargs.get("seed", 0)
+        self.model = build_model(self.model_config, dtype=dtype, device=self.device,
+                                 seed=seed if (cfg.init_from_scratch or not cfg.path) else None)
+        if cfg.path and not cfg.init_from_scratch:
+            from ..utils.hf_io import load_hf_weights
+
+            load_hf_weights(self.model, cfg.path)
+        self.flat = FlatParams(self.model, self._dp_group, with_grads=self.optimizer_config is not None)
+        if self.optimizer_config is not None:
+            total = ft_spec.total_train_steps if ft_spec is not None else 1
+            self.optimizer = ShardedAdamW(self.flat, self.optimizer_config, total_steps=total)
+        self.ft_spec = ft_spec
+        self._initialized = True
+        logger.info(f"engine initialised: {self.model_config.num_params() / 1e9:.2f}B params, "
+                    f"dp={self.world_size}, device={self.device}, {time.perf_counter() - t0:.1f}s")
+        return self
+
+    def destroy(self):
+        self.model = None
+        self.optimizer = None
+        self.flat = None
+        if self._own_pg and dist.is_initialized():
+            dist.destroy_process_group()
+
+    def train(self, mode: bool = True):
+        if self.model is not None:
+            self.model.train(mode)
+        return self
+
+    def set_version(self, version: int):
+        self._version = version
+
+    def get_version(self) -> int:
+        return self._version
+
+    # ----------------------------------------------------------- micro-batches
+    def _prepare_mb_list(self, input_: dict[str, Any]) -> MicroBatchList:
+        input_ = {k: v for k, v in input_.items()}
+        if "attention_mask" not in input_ and "cu_seqlens" in input_:
+            from ..utils.data import unpack_to_padded
+
+            input_ = unpack_to_padded(input_)
+        mb_list = split_padded_tensor_dict_into_mb_list(
+            input_, self.config.mb_spec,
+            group=self._cpu_group if (dist.is_initialized() and self.world_size > 1) else None)
+        return mb_list
+
+    def _mb_to_device(self, mb: dict[str, Any]) -> tuple[dict[str, Any], VarlenMeta]:
+        cu_cpu = mb["cu_seqlens"].cpu()
+        meta = VarlenMeta(cu_cpu.tolist(), self.device)
+        out = {}
+        for k, v in mb.items():
+            if torch.is_tensor(v):
+                out[k] = v.to(self.device, non_blocking=True)
+            else:
+                out[k] = v
+        out = amend_position_ids(out)
+        out["cu_seqlens"] = meta.cu_seqlens
+        return out, meta
+
+    def _forward_mb(self, mb: dict[str, Any], meta: VarlenMeta, need_entropy: bool = True):
+        """Returns ``(logprobs [T], entropy [T])`` in next-token form, or values for a critic."""
+        ids = mb["input_ids"]
+        hidden = self.model(ids, mb["position_ids"], meta)
+        if self.is_critic:
+            return self.model.values(hidden), None
+        labels = torch.roll(ids, shifts=-1, dims=0)
+        logp, ent = lm_head_logprobs(hidden, self.model.output_weight(), labels,
+                                     self.config.temperature)
+        return logp, ent
+
+    # ------------------------------------------------------------------ train
+    def optimizer_zero_grad(self):
+        self.flat.zero_grad()
+
+    def optimizer_step(self) -> dict[str, float]:
+        return self.optimizer.step()
+
+    def lr_scheduler_step(self):
+        self.optimizer.sched_step += 1
+
+    def train_batch(self, input_: dict[str, Any], loss_fn: Callable, loss_weight_fn: Callable) -> dict[str, float]:
+        """One optimizer step over ``input_`` (this rank's share of the batch), split into
+        micro-batches. ``loss_fn(logprobs, entropy, mb) -> scalar`` (``loss_fn(values, mb)``
+        for critics); ``loss_weight_fn(mb) -> weight`` (e.g. the number of loss tokens).
+        The total loss is the weight-averaged loss over all micro-batches of all ranks."""
+        assert self.optimizer is not None, "engine was created without an optimizer"
+        self.model.train()
+        mb_list = self._prepare_mb_list(input_)
+        weights = [float(loss_weight_fn(mb)) for mb in mb_list.mbs]
+        total = torch.tensor([sum(weights)], dtype=torch.float64)
+        if dist.is_initialized() and self.world_size > 1:
+            dist.all_reduce(total, group=self._cpu_group)
+        total_w = float(total)
+        assert total_w > 0, "total loss weight must be positive"
+        losses = []
+        for mb, w in zip(mb_list.mbs, weights):
+            dev_mb, meta = self._mb_to_device(mb)
+            out, ent = self._forward_mb(dev_mb, meta)
+            loss = loss_fn(out, dev_mb) if self.is_critic else loss_fn(out, ent, dev_mb)
+            (loss * (w / total_w)).backward()
+            losses.append(loss.detach() * (w / total_w))
+        stats = self.optimizer.step()
+        self.lr_scheduler_step()
+        stats["loss"] = float(torch.stack(losses).sum()) if losses else 0.0
+        stats["n_mbs"] = float(len(mb_list))
+        return stats
+
+    @torch.no_grad()
+    def eval_batch(self, input_: dict[str, Any], loss_fn: Callable, loss_weight_fn: Callable):
+        self.model.eval()
+        mb_list = self._prepare_mb_list(input_)
+        weights = [float(loss_weight_fn(mb)) for mb in mb_list.mbs]
+        acc = torch.zeros(2, dtype=torch.float64)
+        for mb, w in zip(mb_list.mbs, weights):
+            dev_mb, meta = self._mb_to_device(mb)
+            out, ent = self._forward_mb(dev_mb, meta)
+            loss = loss_fn(out, dev_mb) if self.is_critic else loss_fn(out, ent, dev_mb)
+            acc[0] += float(loss) * w
+            acc[1] += w
+        if dist.is_initialized() and self.world_size > 1:
+            dist.all_reduce(acc, group=self._cpu_group)
+        return float(acc[0] / acc[1].clamp(min=1e-12))
+
+    @torch.no_grad()
+    def forward_batch(self, input_: dict[str, Any], output_seqlens=None, aggregate_fn=None,
+                      return_entropy: bool = False):
+        """Per-token outputs for every sample, padded back to ``[B, L]`` in input order:
+        next-token logprobs (position t holds log π(x[t+1] | x[≤t])) or values for a critic."""
+        self.model.eval()
+        mb_list = self._prepare_mb_list(input_)
+        B, L = input_["attention_mask"].shape
+        result = torch.zeros(B, L, dtype=torch.float32)
+        ent_result = torch.zeros(B, L, dtype=torch.float32) if return_entropy else None
+        row = 0
+        for mb in mb_list.mbs:
+            dev_mb, meta = self._mb_to_device(mb)
+            out, ent = self._forward_mb(dev_mb, meta)
+            out = out.float().cpu()
+            ent = ent.float().cpu() if (ent is not None and return_entropy) else None
+            cu = meta.cu_cpu
+            for i in range(len(cu) - 1):
+                src = mb_list.forward_indices[row]
+                n = int(cu[i + 1] - cu[i])
+                result[src, :n] = out[cu[i]:cu[i + 1]]
+                if ent is not None:
+                    ent_result[src, :n] = ent[cu[i]:cu[i + 1]]
+                row += 1
+        if return_entropy:
+            return result, ent_result
+        return result
+
+    def forward_backward_batch(self, mb_list, process_output_fn, forward_only: bool = False):
+        outs = []
+        for mb in mb_list.mbs:
+            dev_mb, meta = self._mb_to_device(mb)
+            with torch.set_grad_enabled(not forward_only):
+                out, ent = self._forward_mb(dev_mb, meta)
+                res = process_output_fn(out, dev_mb)
+            if not forward_only and res is not None:
+                res.backward()
+            outs.append(res.detach() if torch.is_tensor(res) else res)
+        return outs
+
+    # -------------------------------------------------------------- weight sync
+    def connect_engine(self, engine: InferenceEngine, meta: WeightUpdateMeta):
+        """Registers the rollout engine that receives this engine's weights."""
+        self.rollout_engine = engine
+        self.weight_update_meta = meta
+        if meta.type == "p2p" and hasattr(engine, "register_trainer"):
+            engine.register_trainer(self)
+
+    def update_weights(self, meta: WeightUpdateMeta | None = None):
+        """Pushes the current weights to the connected rollout engine and bumps its version."""
+        meta = meta or self.weight_update_meta
+        assert self.rollout_engine is not None, "connect_engine() has not been called"
+        t0 = time.perf_counter()
+        if meta.type == "disk":
+            self.save(SaveLoadMeta(path=meta.path, weight_format="hf", with_optim=False))
+            if dist.is_initialized() and self.world_size > 1:
+                dist.barrier(group=self._cpu_group)
+            if self.dp_rank == 0:
+                self.rollout_engine.update_weights_from_disk(meta).result()
+        else:
+            self.rollout_engine.pause_generation()
+            self.rollout_engine.receive_weights(self, version=meta.version)
+            self.rollout_engine.continue_generation()
+        if meta.version is not None:
+            self.rollout_engine.set_version(meta.version)
+        dt = time.perf_counter() - t0
+        stats_tracker.scalar(**{"timeperf/update_weights": dt})
+        return dt
+
+    def get_param_specs(self, weight_chunked_mem_mb: int = 1024) -> list[list[ParamSpec]]:
+        limit = weight_chunked_mem_mb * (1 << 20)
+        groups, cur, size = [], [], 0
+        for name, t in self.model.to_hf():
+            spec = ParamSpec(name=name, shape=tuple(t.shape), dtype=str(t.dtype).replace("torch.", ""))
+            if cur and size + spec.size > limit:
+                groups.append(cur)
+                cur, size = [], 0
+            cur.append(spec)
+            size += spec.size
+        if cur:
+            groups.append(cur)
+        return groups
+
+    # ------------------------------------------------------------- checkpoints
+    def save(self, meta: SaveLoadMeta):
+        from ..utils.hf_io import save_hf_checkpoint
+
+        os.makedirs(meta.path, exist_ok=True)
+        if meta.weight_format == "hf":
+            if self.dp_rank == 0:
+                save_hf_checkpoint(self.model, self.model_config, meta.path, tokenizer=meta.tokenizer)
+        elif meta.weight_format == "dcp":
+            # sharded: every rank writes its slice of the flat weights
+            o, n = self.flat.shard_offset, self.flat.shard_numel
+            torch.save(dict(flat=self.flat.flat[o:o + n].cpu(), offset=o, numel=self.flat.numel,
+                            dp_world=self.world_size, layout=self.flat.named_offsets()),
+                       os.path.join(meta.path, f"model_world_size_{self.world_size}_rank_{self.dp_rank}.pt"))
+        else:
+            raise ValueError(f"unknown weight format {meta.weight_format}")
+        if meta.with_optim and self.optimizer is not None:
+            sd = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in self.optimizer.state_dict().items()}
+            torch.save(sd, os.path.join(meta.path, f"optim_world_size_{self.world_size}_rank_{self.dp_rank}.pt"))
+        if dist.is_initialized() and self.world_size > 1:
+            dist.barrier(group=self._cpu_group)
+
+    def load(self, meta: SaveLoadMeta):
+        from ..utils.hf_io import load_hf_weights
+
+        if meta.weight_format == "hf":
+            load_hf_weights(self.model, meta.path)
+        elif meta.weight_format == "dcp":
+            for r in range(self.world_size):
+                f = os.path.join(meta.path, f"model_world_size_{self.world_size}_rank_{r}.pt")
+                sd = torch.load(f, map_location="cpu", weights_only=False)
+                o = sd["offset"]
+                self.flat.flat[o:o + sd["flat"].numel()].copy_(sd["flat"])
+        else:
+            raise ValueError(f"unknown weight format {meta.weight_format}")
+        if self.optimizer is not None:
+            self.optimizer.refresh_master()
+            if meta.with_optim:
+                f = os.path.join(meta.path, f"optim_world_size_{self.world_size}_rank_{self.dp_rank}.pt")
+                self.optimizer.load_state_dict(torch.load(f, map_location=self.device, weights_only=False))
+
+    # ----------------------------------------------------------------- offload
+    def offload(self):
+        """Moves optimizer state to pinned host memory (colocated train/rollout time-sharing)."""
+        if self.optimizer is None or self._offloaded is not None:
+            return
+        self._offloaded = {}
+        for name in ("master", "exp_avg", "exp_avg_sq", "shard_grad"):
+            t = getattr(self.optimizer, name)
+            host = torch.empty(t.shape, dtype=t.dtype, pin_memory=self.device.type == "cuda")
+            host.copy_(t)
+            self._offloaded[name] = host
+            setattr(self.optimizer, name, torch.empty(0, dtype=t.dtype, device=self.device))
+        if self.device.type == "cuda":
+            torch.cuda.empty_cache()
+
+    def onload(self):
+        if self._offloaded is None:
+            return
+        for name, host in self._offloaded.items():
+            setattr(self.optimizer, name, host.to(self.device, non_blocking=True))
+        self._offloaded = None
+
+    def export_stats(self) -> dict[str, float]:
+        return stats_tracker.export_all(reduce_group=self._cpu_group)
+
+
+class B200PPOActorEngine(B200TrainEngine):
+    pass

@@ -174,7 +174,7 @@ class QwenModel(nn.Module):
         """Packed forward; returns the final-normed hidden states ``[T, H]``."""
         cos, sin = self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
-        x = F.embedding(input_ids.long(), self.embed)
+        x = fused.embedding(input_ids, self.embed)
         res = None
         for layer in self.layers:
             x, res = layer(x, res, cos, sin, pos, meta, attn_fn)

@@ -231,3 +231,35 @@ def swiglu(gu):
     if _lib.use_cuda_kernels(gu) and gu.dtype == torch.bfloat16 and (gu.shape[-1] // 2) % 8 == 0:
         return _SwiGLU.apply(gu)
     return swiglu_ref(gu)
+
+
+# --------------------------------------------------------------------------- embedding
+
+
+class _Embedding(torch.autograd.Function):
+    """Embedding lookup whose backward scatter-adds straight into the weight's fp32
+    ``main_grad`` (when present) instead of materialising a dense ``[V, H]`` gradient."""
+
+    @staticmethod
+    def forward(ctx, ids, w):
+        ctx.save_for_backward(ids)
+        ctx.w = w
+        return torch.nn.functional.embedding(ids, w)
+
+    @staticmethod
+    def backward(ctx, dy):
+        (ids,) = ctx.saved_tensors
+        w = ctx.w
+        main = getattr(w, "main_grad", None)
+        if main is not None:
+            main.index_add_(0, ids.reshape(-1), dy.reshape(-1, dy.shape[-1]).to(torch.float32))
+            return None, None
+        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        dw.index_add_(0, ids.reshape(-1), dy.reshape(-1, dy.shape[-1]).to(torch.float32))
+        return None, dw.to(w.dtype)
+
+
+def embedding(ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    if w.requires_grad and torch.is_grad_enabled():
+        return _Embedding.apply(ids.long(), w)
+    return torch.nn.functional.embedding(ids.long(), w)

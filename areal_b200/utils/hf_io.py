@@ -1,0 +1,71 @@
+"""HF-format checkpoint IO: sharded safetensors + ``config.json`` (+ tokenizer files).
+
+Weights are written under HF parameter names, so checkpoints interchange with
+``transformers`` and with the reference's savers
+(areal/engine/fsdp_engine.py:1627-1666). Loading streams tensors file by file
+straight into the model's fused parameters.
+"""
+
+from __future__ import annotations
+
+import json
+import os
+from pathlib import Path
+from typing import Iterator
+
+import torch
+from safetensors import safe_open
+from safetensors.torch import save_file
+
+MAX_SHARD_BYTES = 5 * (1 << 30)
+
+
+def iter_hf_tensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
+    p = Path(path)
+    files = sorted(p.glob("*.safetensors"))
+    if not files:
+        raise FileNotFoundError(f"no .safetensors files under {path}")
+    for f in files:
+        with safe_open(str(f), framework="pt", device="cpu") as sf:
+            for name in sf.keys():
+                yield name, sf.get_tensor(name)
+
+
+def load_hf_weights(model, path: str, strict: bool = True):
+    model.load_hf(iter_hf_tensors(path), strict=strict)
+    return model
+
+
+def save_hf_checkpoint(model, model_config, path: str, tokenizer=None, max_shard_bytes: int = MAX_SHARD_BYTES):
+    os.makedirs(path, exist_ok=True)
+    shards: list[dict[str, torch.Tensor]] = [{}]
+    size = 0
+    index: dict[str, str] = {}
+    for name, t in model.to_hf():
+        nbytes = t.numel() * t.element_size()
+        if shards[-1] and size + nbytes > max_shard_bytes:
+            shards.append({})
+            size = 0
+        shards[-1][name] = t.detach().to("cpu").contiguous().clone()
+        size += nbytes
+    n = len(shards)
+    total = 0
+    for i, sh in enumerate(shards):
+        fname = "model.safetensors" if n == 1 else f"model-{i + 1:05d}-of-{n:05d}.safetensors"
+        save_file(sh, os.path.join(path, fname), metadata={"format": "pt"})
+        for k, v in sh.items():
+            index[k] = fname
+            total += v.numel() * v.element_size()
+    if n > 1:
+        with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
+            json.dump({"metadata": {"total_size": total}, "weight_map": index}, f, indent=2)
+    with open(os.path.join(path, "config.json"), "w") as f:
+        json.dump(model_config.to_hf_config(), f, indent=2)
+    if tokenizer is not None and hasattr(tokenizer, "save_pretrained"):
+        tokenizer.save_pretrained(path)
+
+
+def load_hf_tokenizer(path: str, **kwargs):
+    from transformers import AutoTokenizer
+
+    return AutoTokenizer.from_pretrained(path, **kwargs)
