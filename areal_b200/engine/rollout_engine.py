@@ -146,6 +146,7 @@ class NativeRolloutEngine(InferenceEngine):
         self.device = None
         self._idle = threading.Event()
         self._idle.set()
+        self._step_lock = threading.Lock()
 
     # ------------------------------------------------------------------ setup
     def initialize(self, engine_id: str | None = None, train_data_parallel_size: int | None = None,
@@ -229,11 +230,14 @@ class NativeRolloutEngine(InferenceEngine):
                     time.sleep(0.0005)
                     continue
                 self._idle.clear()
-                if stream is not None:
-                    with torch.cuda.stream(stream):
+                with self._step_lock:
+                    if self._paused.is_set():
+                        continue
+                    if stream is not None:
+                        with torch.cuda.stream(stream):
+                            worked = self._step()
+                    else:
                         worked = self._step()
-                else:
-                    worked = self._step()
                 if not worked:
                     self._idle.set()
                     with self._wake:
@@ -365,10 +369,11 @@ class NativeRolloutEngine(InferenceEngine):
         """Stops the engine loop after the current step and aborts in-flight requests;
         their callers keep the partial output and resume after ``continue_generation``."""
         self._paused.set()
-        self._idle.wait(timeout=60)
-        with self._lock:
-            self.sched.abort_all()
-        self._deliver()
+        # no engine step is in flight once the step lock is ours
+        with self._step_lock:
+            with self._lock:
+                self.sched.abort_all()
+            self._deliver()
 
     def continue_generation(self):
         self._paused.clear()

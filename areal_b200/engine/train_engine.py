@@ -77,6 +77,9 @@ class B200TrainEngine(TrainEngine):
         self._rollout_tables = None
         self._offloaded: dict[str, torch.Tensor] | None = None
         self.is_critic = config.is_critic
+        # bytes moved host→device (pinned staging) and device→host, for the benchmark report
+        self.h2d_bytes = 0
+        self.d2h_bytes = 0
 
     # ------------------------------------------------------------ process groups
     def create_process_group(self, parallel_strategy: ParallelStrategy | None = None,
@@ -198,8 +201,12 @@ class B200TrainEngine(TrainEngine):
         cu_cpu = mb["cu_seqlens"].cpu()
         meta = VarlenMeta(cu_cpu.tolist(), self.device)
         out = {}
+        cuda = self.device.type == "cuda"
         for k, v in mb.items():
             if torch.is_tensor(v):
+                if cuda and not v.is_cuda:
+                    v = v.pin_memory()
+                    self.h2d_bytes += v.numel() * v.element_size()
                 out[k] = v.to(self.device, non_blocking=True)
             else:
                 out[k] = v
@@ -252,6 +259,7 @@ class B200TrainEngine(TrainEngine):
         stats = self.optimizer.step()
         self.lr_scheduler_step()
         stats["loss"] = float(torch.stack(losses).sum()) if losses else 0.0
+        self.d2h_bytes += 12  # grad-norm, skip flag, loss
         stats["n_mbs"] = float(len(mb_list))
         return stats
 
@@ -286,6 +294,7 @@ class B200TrainEngine(TrainEngine):
             dev_mb, meta = self._mb_to_device(mb)
             out, ent = self._forward_mb(dev_mb, meta)
             out = out.float().cpu()
+            self.d2h_bytes += out.numel() * 4
             ent = ent.float().cpu() if (ent is not None and return_entropy) else None
             cu = meta.cu_cpu
             for i in range(len(cu) - 1):

@@ -1,0 +1,216 @@
+"""Disaggregated rollout ↔ trainer plumbing inside one ``torch.distributed`` world.
+
+Rollout ranks run a :class:`NativeRolloutEngine`; trainer ranks drive them
+through :class:`RemoteRolloutClient`, which looks like an ``InferenceEngine`` to
+the trainer. Per paired (rollout rank, trainer rank):
+
+* trajectories travel rollout → trainer as pickled tensor dicts over a gloo
+  group (a few MB per step);
+* control messages (pause / resume+version / stop) travel trainer → rollout over
+  a second gloo group, served by a control thread on the rollout rank;
+* weights travel trainer → rollout **directly through peer memory**: every
+  trainer rank copies its shard of the flat bf16 weights into the flat weight
+  buffer of every rollout rank with one kernel over NVLink
+  (``b200_push_all``). No rank-0 funnel, no per-tensor broadcast.
+
+This replaces the reference's HTTP control plane plus NCCL broadcast from trainer
+rank 0 to all inference ranks (areal/engine/fsdp_engine.py:1377-1597,
+areal/infra/dist_rollout.py:29-148) and its redistribution of trajectories
+across data-parallel ranks.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+import time
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from ..api.engine_api import InferenceEngine
+from ..api.io_struct import WeightUpdateMeta
+from ..ops import _lib
+from ..parallel.symm_mem import open_ipc_handle
+from ..utils import logging
+from ..utils.data import concat_padded_tensors
+from ..utils.seqpack import balanced_greedy_partition
+
+logger = logging.getLogger("DistRollout")
+
+
+class DisaggTopology:
+    """Rank layout: ``[0, n_gen)`` rollout, ``[n_gen, n_gen + n_train)`` trainers."""
+
+    def __init__(self, n_gen: int, n_train: int):
+        self.n_gen, self.n_train = n_gen, n_train
+        self.world = dist.get_world_size()
+        assert n_gen + n_train == self.world, f"allocation {n_gen}+{n_train} != world {self.world}"
+        self.rank = dist.get_rank()
+        self.gen_ranks = list(range(n_gen))
+        self.train_ranks = list(range(n_gen, n_gen + n_train))
+        self.is_rollout = self.rank < n_gen
+        # gloo groups over the whole world: one for data, one for control
+        self.data_group = dist.new_group(list(range(self.world)), backend="gloo")
+        self.ctl_group = dist.new_group(list(range(self.world)), backend="gloo")
+        self.all_cpu_group = dist.new_group(list(range(self.world)), backend="gloo")
+
+    def trainers_of(self, gen_rank: int) -> list[int]:
+        return [t for i, t in enumerate(self.train_ranks) if i % self.n_gen == gen_rank % self.n_gen] \
+            if self.n_train >= self.n_gen else [self.train_ranks[gen_rank % self.n_train]]
+
+    def rollouts_of(self, train_rank: int) -> list[int]:
+        return [g for g in self.gen_ranks if train_rank in self.trainers_of(g)]
+
+
+def exchange_weight_buffers(topo: DisaggTopology, rollout_engine=None, device_index: int = 0) -> list[int]:
+    """Collective over the world: rollout ranks export their flat weight buffer, trainer
+    ranks map all of them. Returns the mapped pointers on trainer ranks ([] on rollout ranks)."""
+    handle = None
+    if topo.is_rollout:
+        handle = (rollout_engine.flat.param_buf.ipc_handle(), rollout_engine.flat.numel)
+    handles: list[Any] = [None] * topo.world
+    dist.all_gather_object(handles, handle, group=topo.all_cpu_group)
+    if topo.is_rollout:
+        return []
+    return [open_ipc_handle(handles[g][0], device_index) for g in topo.gen_ranks]
+
+
+class RolloutServer:
+    """Runs on a rollout rank: produces batches for its trainer(s) and obeys control messages."""
+
+    def __init__(self, topo: DisaggTopology, engine):
+        self.topo, self.engine = topo, engine
+        self.trainers = topo.trainers_of(topo.rank)
+        self._stop = threading.Event()
+        self._ctl_thread = threading.Thread(target=self._control_loop, name="rollout-ctl", daemon=True)
+        self._ctl_thread.start()
+
+    def _control_loop(self):
+        lead = self.trainers[0]
+        while not self._stop.is_set():
+            msg = [None]
+            dist.recv_object_list(msg, src=lead, group=self.topo.ctl_group)
+            cmd = msg[0]
+            if cmd[0] == "pause":
+                self.engine.pause_generation()
+                dist.send_object_list([("ack", time.time())], dst=lead, group=self.topo.ctl_group)
+            elif cmd[0] == "resume":
+                if cmd[1] is not None:
+                    self.engine.set_version(cmd[1])
+                self.engine.continue_generation()
+            elif cmd[0] == "stop":
+                self._stop.set()
+                return
+
+    def serve(self, dataloader, workflow, workflow_kwargs=None, group_size: int = 1, n_steps: int | None = None):
+        """Produces ``n_steps`` batches (forever if ``None``) and ships each, split evenly by token
+        count, to the paired trainer ranks."""
+        step = 0
+        while not self._stop.is_set() and (n_steps is None or step < n_steps):
+            batch = self.engine.prepare_batch(dataloader, workflow, workflow_kwargs, group_size=group_size)
+            parts = split_batch_by_tokens(batch, len(self.trainers), group_size)
+            for t, part in zip(self.trainers, parts):
+                dist.send_object_list([part], dst=t, group=self.topo.data_group)
+            step += 1
+
+    def wait_stop(self, timeout: float | None = None):
+        self._ctl_thread.join(timeout)
+
+
+def split_batch_by_tokens(batch: dict[str, Any], k: int, group_size: int = 1) -> list[dict[str, Any]]:
+    """Splits a padded batch into ``k`` parts with balanced token counts, keeping each
+    group of ``group_size`` consecutive samples together."""
+    if k == 1:
+        return [batch]
+    B = batch["attention_mask"].shape[0]
+    lens = batch["attention_mask"].sum(-1).tolist()
+    g = max(group_size, 1)
+    units = [sum(lens[i:i + g]) for i in range(0, B, g)]
+    parts = balanced_greedy_partition(units, k, equal_size=True)
+    out = []
+    for p in parts:
+        rows = torch.tensor([u * g + j for u in sorted(p) for j in range(g)], dtype=torch.long)
+        out.append({key: (v[rows] if torch.is_tensor(v) and v.dim() >= 1 and v.shape[0] == B else v)
+                    for key, v in batch.items()})
+    return out
+
+
+class RemoteRolloutClient(InferenceEngine):
+    """Trainer-side handle of the paired rollout rank(s)."""
+
+    def __init__(self, topo: DisaggTopology, weight_ptrs: list[int], train_cpu_group=None):
+        self.topo = topo
+        self.rollouts = topo.rollouts_of(topo.rank)
+        # the lead trainer of a rollout rank is the one that sends it control messages
+        self.led = [g for g in self.rollouts if topo.trainers_of(g)[0] == topo.rank]
+        self.weight_ptrs = weight_ptrs
+        self.train_cpu_group = train_cpu_group
+        self._version = 0
+        self._table = (ctypes.c_void_p * max(len(weight_ptrs), 1))(*weight_ptrs) if weight_ptrs else None
+        self.last_pause_latency = 0.0
+
+    def prepare_batch(self, dataloader=None, workflow=None, workflow_kwargs=None, should_accept_fn=None,
+                      group_size=1, dynamic_bs=False):
+        parts = []
+        for g in self.rollouts:
+            msg = [None]
+            dist.recv_object_list(msg, src=g, group=self.topo.data_group)
+            parts.append(msg[0])
+        return parts[0] if len(parts) == 1 else concat_padded_tensors(parts)
+
+    rollout_batch = prepare_batch
+
+    def pause_generation(self):
+        t0 = time.perf_counter()
+        for g in self.led:
+            dist.send_object_list([("pause",)], dst=g, group=self.topo.ctl_group)
+        for g in self.led:
+            msg = [None]
+            dist.recv_object_list(msg, src=g, group=self.topo.ctl_group)
+        if self.train_cpu_group is not None:
+            dist.barrier(group=self.train_cpu_group)  # every rollout rank has paused
+        self.last_pause_latency = time.perf_counter() - t0
+
+    def continue_generation(self, version: int | None = None):
+        if self.train_cpu_group is not None:
+            dist.barrier(group=self.train_cpu_group)  # every trainer's shard has landed
+        for g in self.led:
+            dist.send_object_list([("resume", version if version is not None else self._version)],
+                                  dst=g, group=self.topo.ctl_group)
+
+    def receive_weights(self, trainer, version: int | None = None):
+        """Each trainer rank writes its shard of the flat bf16 weights into every rollout
+        rank's weight buffer (peer stores over NVLink), then synchronises its stream."""
+        f = trainer.flat
+        itemsize = f.flat.element_size()
+        lib = _lib.kernels()
+        shard = f.flat[f.shard_offset: f.shard_offset + f.shard_numel]
+        rc = lib.b200_push_all(self._table, ctypes.c_int(len(self.weight_ptrs)), _lib.ptr(shard),
+                               ctypes.c_longlong(f.shard_numel * itemsize),
+                               ctypes.c_longlong(f.shard_offset * itemsize), _lib.stream_ptr())
+        _lib.check(rc, "b200_push_all")
+        _lib.count_launch()
+        torch.cuda.current_stream().synchronize()
+        if version is not None:
+            self._version = version
+
+    def set_version(self, version: int):
+        self._version = version
+
+    def get_version(self) -> int:
+        return self._version
+
+    def pause(self):
+        pass
+
+    def resume(self):
+        pass
+
+    def stop(self):
+        for g in self.led:
+            dist.send_object_list([("stop",)], dst=g, group=self.topo.ctl_group)
+
+    def export_stats(self) -> dict[str, float]:
+        return {"rollout/pause_latency": self.last_pause_latency}

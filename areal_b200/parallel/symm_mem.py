@@ -105,6 +105,13 @@ class SymmBuffer:
             arr[i] = self.peer_ptrs[r] + byte_offset
         return arr
 
+    def ipc_handle(self) -> bytes:
+        """CUDA IPC handle of the local allocation (for processes outside ``group``)."""
+        lib = _lib.kernels()
+        buf = ctypes.create_string_buffer(64)
+        _lib.check(lib.b200_ipc_get_handle(ctypes.c_void_p(self.local_ptr), buf), "b200_ipc_get_handle")
+        return bytes(buf.raw)
+
     def close(self):
         lib = _lib.kernels()
         for p in self._opened:
@@ -114,6 +121,17 @@ class SymmBuffer:
             self._local_bytes = None
             lib.b200_symm_free(ctypes.c_void_p(self.local_ptr))
             self.local_ptr = 0
+
+
+def open_ipc_handle(handle: bytes, device_index: int = 0) -> int:
+    """Maps another process's allocation; returns the device pointer in this process."""
+    lib = _lib.kernels()
+    lib.b200_ensure_device(ctypes.c_int(device_index))
+    lib.b200_ipc_open_handle.restype = ctypes.c_void_p
+    p = lib.b200_ipc_open_handle(ctypes.c_char_p(handle))
+    if not p:
+        raise RuntimeError("cudaIpcOpenMemHandle failed")
+    return int(p)
 
 
 class SymmBarrier:

@@ -1,0 +1,275 @@
+"""PPO / GRPO trainer: asynchronous RL main loop.
+
+    with PPOTrainer(config, train_dataset, valid_dataset) as trainer:
+        trainer.train(workflow="areal_b200.workflow.rlvr.RLVRWorkflow",
+                      workflow_kwargs=dict(reward_fn=..., gconfig=config.gconfig, tokenizer=tok))
+
+Every rank runs this script (SPMD). The allocation strings decide the roles:
+
+* ``rollout.backend = native:dA`` and ``actor.backend = fsdp:dB`` with ``A + B ==
+  world`` – disaggregated: the first A ranks generate, the last B ranks train;
+  trajectories and control go over gloo, weights over NVLink peer memory;
+* ``A == B == world`` (or a single process) – colocated: every rank owns both a
+  rollout engine and a trainer shard on the same GPU; generation runs in a
+  background thread / CUDA stream while the trainer consumes the previous
+  batches.
+
+One step: wait for a batch that is at most ``max_head_offpolicyness`` versions
+stale → (critic values, reference / teacher logprobs) → recompute proximal
+logprobs → advantages → ``ppo_update`` → pause rollout, push weights, bump
+version, resume → save / recover / evaluate / log. Mirrors the reference loop
+(areal/trainer/rl_trainer.py:105-824).
+"""
+
+from __future__ import annotations
+
+import os
+import time
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+from ..api.alloc_mode import ModelAllocation
+from ..api.cli_args import PPOConfig, get_log_path, save_config
+from ..api.io_struct import FinetuneSpec, StepInfo, WeightUpdateMeta
+from ..engine.rollout_engine import NativeRolloutEngine
+from ..engine.train_engine import B200TrainEngine
+from ..infra.dist_rollout import (DisaggTopology, RemoteRolloutClient, RolloutServer,
+                                  exchange_weight_buffers)
+from ..utils import logging, seeding, stats_tracker
+from ..utils.evaluator import Evaluator
+from ..utils.recover import RecoverHandler
+from ..utils.saver import Saver
+from ..utils.stats_logger import StatsLogger
+from .ppo.actor import PPOActor
+from .ppo.critic import PPOCritic
+
+logger = logging.getLogger("PPOTrainer")
+
+
+class _ListLoader:
+    """Minimal stateful dataloader over an in-memory dataset (list of dict items)."""
+
+    def __init__(self, dataset, batch_size: int, shuffle: bool, seed: int, rank: int = 0, world: int = 1,
+                 drop_last: bool = True):
+        self.dataset, self.batch_size, self.shuffle = dataset, batch_size, shuffle
+        self.seed, self.rank, self.world, self.drop_last = seed, rank, world, drop_last
+        self.epoch = 0
+        self.sampler = self
+
+    def set_epoch(self, e: int):
+        self.epoch = e
+
+    def __len__(self):
+        n = len(self.dataset) // self.world
+        return n // self.batch_size if self.drop_last else -(-n // self.batch_size)
+
+    def __iter__(self):
+        idx = list(range(len(self.dataset)))
+        if self.shuffle:
+            g = torch.Generator().manual_seed(self.seed + self.epoch)
+            idx = torch.randperm(len(idx), generator=g).tolist()
+        idx = idx[self.rank::self.world]
+        for i in range(0, len(idx) - (self.batch_size - 1 if self.drop_last else 0), self.batch_size):
+            yield [self.dataset[j] for j in idx[i:i + self.batch_size]]
+
+    def state_dict(self):
+        return {"epoch": self.epoch}
+
+    def load_state_dict(self, s):
+        self.epoch = s["epoch"]
+
+
+class PPOTrainer:
+    def __init__(self, config: PPOConfig, train_dataset, valid_dataset=None):
+        self.config = config
+        self.train_dataset, self.valid_dataset = train_dataset, valid_dataset
+        use_cuda = torch.cuda.is_available()
+        if not dist.is_initialized() and "RANK" in os.environ:
+            import datetime
+
+            if use_cuda:
+                torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+            dist.init_process_group(backend="nccl" if use_cuda else "gloo",
+                                    timeout=datetime.timedelta(seconds=7200))
+        self.rank = dist.get_rank() if dist.is_initialized() else 0
+        self.world = dist.get_world_size() if dist.is_initialized() else 1
+        seeding.set_random_seed(config.seed, f"trainer{self.rank}")
+        self.actor_alloc = ModelAllocation.from_str(config.actor.backend)
+        self.rollout_alloc = ModelAllocation.from_str(config.rollout.backend)
+        n_train, n_gen = self.actor_alloc.world_size, self.rollout_alloc.world_size
+        self.colocated = self.world == 1 or (n_train == self.world and n_gen == self.world)
+        if not self.colocated and n_train + n_gen != self.world:
+            raise ValueError(f"allocation {config.rollout.backend}+{config.actor.backend} needs "
+                             f"{n_train + n_gen} ranks, world size is {self.world}")
+        self.topo = None if self.colocated else DisaggTopology(n_gen, n_train)
+        self.is_trainer = self.colocated or not self.topo.is_rollout
+        self.is_rollout = self.colocated or self.topo.is_rollout
+        train_ranks = list(range(self.world)) if self.colocated else self.topo.train_ranks
+        dp = len(train_ranks)
+        bs = config.train_dataset.batch_size
+        self.ft_spec = FinetuneSpec(total_train_epochs=config.total_train_epochs,
+                                    dataset_size=len(train_dataset), train_batch_size=bs)
+        self.per_rank_bs = max(bs // dp, 1)
+        # every role takes part in group creation (collective)
+        self.actor_engine = B200TrainEngine(config.actor) if self.is_trainer else None
+        self.critic_engine = None
+        self.ref_engine = None
+        helper = self.actor_engine or B200TrainEngine(config.actor)
+        helper.create_process_group(self.actor_alloc.parallel, ranks=train_ranks)
+        self.train_cpu_group = helper.cpu_group
+        self.rollout = None
+        self.rollout_client = None
+        if self.is_rollout:
+            rcfg = config.rollout
+            rcfg.consumer_batch_size = bs
+            self.rollout = NativeRolloutEngine(rcfg)
+            n_gen_eff = self.world if self.colocated else n_gen
+            self.rollout.initialize(train_data_parallel_size=n_gen_eff)
+        if self.is_trainer:
+            self.actor_engine.initialize(None, self.ft_spec, seed=config.seed)
+            if config.critic is not None:
+                self.critic_engine = B200TrainEngine(config.critic)
+                self.critic_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks)
+                self.critic_engine.initialize(None, self.ft_spec, seed=config.seed + 1)
+            if config.ref is not None and config.actor.kl_ctl != 0.0:
+                self.ref_engine = B200TrainEngine(config.ref)
+                self.ref_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks)
+                self.ref_engine.initialize(None, self.ft_spec, seed=config.seed)
+        if self.colocated:
+            self.rollout_client = self.rollout
+            self.weight_meta = WeightUpdateMeta.from_p2p()
+        else:
+            dev = torch.cuda.current_device() if use_cuda else 0
+            ptrs = exchange_weight_buffers(self.topo, self.rollout, dev)
+            if self.is_trainer:
+                self.rollout_client = RemoteRolloutClient(self.topo, ptrs, self.train_cpu_group)
+            self.weight_meta = WeightUpdateMeta.from_p2p()
+        if self.is_trainer:
+            self.actor_engine.connect_engine(self.rollout_client, self.weight_meta)
+            self.actor = PPOActor(config.actor, self.actor_engine)
+            self.critic = PPOCritic(config.critic, self.critic_engine) if self.critic_engine else None
+            self.ref = PPOActor(config.ref, self.ref_engine) if self.ref_engine else None
+        self.saver = Saver(config.saver, self.ft_spec)
+        self.evaluator = Evaluator(config.evaluator, self.ft_spec)
+        self.recover = RecoverHandler(config.recover, self.ft_spec)
+        self.stats_logger = StatsLogger(config, self.ft_spec) if self.rank == train_ranks[0] else None
+        gen_rank = self.rank if self.colocated else (self.rank if self.is_rollout else 0)
+        gen_world = self.world if self.colocated else n_gen
+        self.dataloader = _ListLoader(train_dataset, self.per_rank_bs if self.colocated else max(bs // gen_world, 1),
+                                      config.train_dataset.shuffle, config.seed, gen_rank, gen_world)
+        self.step_times: list[float] = []
+        self.trained_tokens = 0
+        if self.rank == train_ranks[0]:
+            try:
+                save_config(config, get_log_path(config))
+            except Exception as e:
+                logger.warning(f"could not save the config: {e}")
+
+    def __enter__(self):
+        return self
+
+    def __exit__(self, *exc):
+        self.close()
+
+    def close(self):
+        if self.rollout_client is not None and not self.colocated:
+            self.rollout_client.stop()
+        if self.rollout is not None:
+            self.rollout.destroy()
+        for e in (self.actor_engine, self.critic_engine, self.ref_engine):
+            if e is not None:
+                e.destroy()
+        if self.stats_logger is not None:
+            self.stats_logger.close()
+
+    # -------------------------------------------------------------------- train
+    def train(self, workflow, workflow_kwargs: dict | None = None, eval_workflow=None,
+              eval_workflow_kwargs: dict | None = None, max_steps: int | None = None,
+              step_callback=None):
+        cfg = self.config
+        total = cfg.total_train_steps or self.ft_spec.total_train_steps
+        if max_steps is not None:
+            total = min(total, max_steps)
+        group = cfg.gconfig.n_samples
+        if not self.is_trainer:
+            # rollout-only rank of a disaggregated run: produce batches until told to stop
+            server = RolloutServer(self.topo, self.rollout)
+            server.serve(self.dataloader, workflow, workflow_kwargs, group_size=group, n_steps=total)
+            server.wait_stop(timeout=600)
+            return
+        start = 0
+        info = self.recover.load(self.actor_engine, self.saver, self.evaluator, self.stats_logger,
+                                 self.dataloader, self.rollout if self.colocated else None, self.weight_meta)
+        if info is not None:
+            start = info.last_step_info.global_step + 1
+        else:
+            # both sides start from identical weights and version 0
+            self.actor_engine.update_weights(self.weight_meta.with_version(0))
+        steps_per_epoch = self.ft_spec.steps_per_epoch
+        for global_step in range(start, total):
+            t_step = time.perf_counter()
+            epoch, epoch_step = divmod(global_step, steps_per_epoch)
+            with stats_tracker.record_timing("rollout"):
+                batch = self.rollout_client.prepare_batch(self.dataloader, workflow, workflow_kwargs,
+                                                          group_size=group, dynamic_bs=cfg.dynamic_bs)
+            stats = self.train_step(batch, global_step)
+            self.step_times.append(time.perf_counter() - t_step)
+            with stats_tracker.record_timing("save"):
+                self.saver.save(self.actor_engine, epoch, epoch_step, global_step)
+            with stats_tracker.record_timing("checkpoint_for_recover"):
+                self.recover.dump(self.actor_engine, StepInfo(epoch, epoch_step, global_step, steps_per_epoch),
+                                  self.saver, self.evaluator, self.stats_logger, self.dataloader)
+            if eval_workflow is not None and self.valid_dataset is not None:
+                self.evaluator.evaluate(lambda: self._evaluate(eval_workflow, eval_workflow_kwargs),
+                                        epoch, epoch_step, global_step)
+            exported = self.actor_engine.export_stats()
+            exported.update(stats)
+            if self.stats_logger is not None:
+                self.stats_logger.commit(epoch, epoch_step, global_step, exported)
+            if step_callback is not None:
+                step_callback(global_step, exported)
+
+    def train_step(self, batch: dict[str, Any], global_step: int) -> dict[str, float]:
+        """Everything between receiving a rollout batch and resuming generation."""
+        cfg = self.config
+        actor = self.actor
+        if self.critic is not None:
+            with stats_tracker.record_timing("critic_values"):
+                batch["values"] = self.critic.compute_values(batch)
+        if self.ref is not None:
+            with stats_tracker.record_timing("ref_logp"):
+                batch["ref_logp"] = self.ref.compute_logp(batch)
+        if cfg.actor.should_compute_prox_logp():
+            with stats_tracker.record_timing("recompute_logp"):
+                batch["prox_logp"] = actor.compute_logp(batch)
+        with stats_tracker.record_timing("compute_advantage"):
+            adv_batch = actor.compute_advantages(batch)
+        with stats_tracker.record_timing("train_step"):
+            train_stats = actor.ppo_update(adv_batch)
+        if self.critic is not None:
+            with stats_tracker.record_timing("critic_train_step"):
+                self.critic.ppo_update(adv_batch)
+        n_tok = int(batch["attention_mask"].sum())
+        self.trained_tokens += n_tok
+        new_version = global_step + 1
+        with stats_tracker.record_timing("update_weights"):
+            self.rollout_client.pause()
+            sync_s = self.actor_engine.update_weights(self.weight_meta.with_version(new_version))
+            self.actor_engine.set_version(new_version)
+            if self.critic_engine is not None:
+                self.critic_engine.set_version(new_version)
+            self.rollout_client.resume()
+        out = {"step/trained_tokens": float(n_tok), "step/weight_sync_s": float(sync_s),
+               "step/loss": float(train_stats[-1].get("loss", 0.0)),
+               "step/grad_norm": float(train_stats[-1].get("grad_norm", 0.0))}
+        return out
+
+    def _evaluate(self, workflow, workflow_kwargs):
+        if not self.colocated:
+            return
+        items = [self.valid_dataset[i] for i in range(self.rank, len(self.valid_dataset), self.world)]
+        batch = self.rollout.rollout_batch(items, workflow, workflow_kwargs)
+        if batch:
+            stats_tracker.get("eval").scalar(reward=float(batch["rewards"].float().mean()))

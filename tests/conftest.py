@@ -26,3 +26,10 @@ def pytest_collection_modifyitems(config, items):
     for item in items:
         if "gpu" in item.keywords or "multi_gpu" in item.keywords:
             item.add_marker(skip)
+
+
+def pytest_sessionstart(session):
+    # the native libraries are not tracked in git: build them once per session
+    from areal_b200 import build as _build
+
+    _build.build()
