@@ -46,8 +46,31 @@ __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ k,
 }
 
 // q: [B, Hq, 128]; partial outputs: o_part [B, Hq, nsplit, 128] fp32, ml_part [B, Hq, nsplit, 2].
+//
+// Bandwidth notes: a lane keeps the K and V slices of its token as raw bf16
+// (4 x 16 bytes) and the slices of the *next* warp step are requested before the
+// current ones are consumed, so every lane has 128 bytes in flight; q lives in
+// shared memory as fp32. The register budget allows 5+ CTAs per SM.
+struct KVRaw {
+  uint4 k0, k1, v0, v1;
+};
+
+__device__ __forceinline__ void load_kv(KVRaw& r, const __nv_bfloat16* __restrict__ k_cache,
+                                        const __nv_bfloat16* __restrict__ v_cache,
+                                        const int* __restrict__ bt, int t, int block_size, int Hkv,
+                                        int hk, int dl) {
+  const int blk = __ldg(bt + t / block_size);
+  const long long slot = static_cast<long long>(blk) * block_size + (t % block_size);
+  const uint4* kp = reinterpret_cast<const uint4*>(k_cache + (slot * Hkv + hk) * kHD + dl * 16);
+  const uint4* vp = reinterpret_cast<const uint4*>(v_cache + (slot * Hkv + hk) * kHD + dl * 16);
+  r.k0 = __ldcs(kp);
+  r.k1 = __ldcs(kp + 1);
+  r.v0 = __ldcs(vp);
+  r.v1 = __ldcs(vp + 1);
+}
+
 template <int G>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(128, (G <= 2 ? 5 : (G <= 4 ? 3 : 2)))
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                     const int* __restrict__ seq_lens, float* __restrict__ o_part,
@@ -62,17 +85,13 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
   const int sub = lane >> 3;  // token slot inside the warp step (0..3)
   const int dl = lane & 7;    // owns dims [16*dl, 16*dl+16)
 
-  float qv[G][16];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const __nv_bfloat16* qp = q + (static_cast<long long>(b) * Hq + hk * G + g) * kHD + dl * 16;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float2 f = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(qp)[i]);
-      qv[g][2 * i] = f.x * scale_log2;
-      qv[g][2 * i + 1] = f.y * scale_log2;
-    }
+  __shared__ __align__(16) float s_q[G][kHD];
+  for (int i = threadIdx.x; i < G * kHD; i += blockDim.x) {
+    const int g = i / kHD, d = i % kHD;
+    s_q[g][d] = __bfloat162float(q[(static_cast<long long>(b) * Hq + hk * G + g) * kHD + d]) * scale_log2;
   }
+  __syncthreads();
+
   float m[G], l[G], acc[G][16];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -82,41 +101,37 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
     for (int i = 0; i < 16; ++i) acc[g][i] = 0.f;
   }
   const int* bt = block_table + static_cast<long long>(b) * max_blocks;
-  for (int base = t_begin + warp * 4; base < t_end; base += 16) {
+  KVRaw cur, nxt;
+  cur.k0 = cur.k1 = cur.v0 = cur.v1 = make_uint4(0, 0, 0, 0);
+  int base = t_begin + warp * 4;
+  if (base + sub < t_end) load_kv(cur, k_cache, v_cache, bt, base + sub, block_size, Hkv, hk, dl);
+  for (; base < t_end; base += 16) {
     // the loop bound is warp-uniform so the shuffles below stay converged;
     // token slots past the end contribute nothing
-    const int t = base + sub;
-    const bool valid = t < t_end;
-    float kf[16], vf[16];
-    if (valid) {
-      const int blk = bt[t / block_size];
-      const long long slot = static_cast<long long>(blk) * block_size + (t % block_size);
-      const __nv_bfloat16* kp = k_cache + (slot * Hkv + hk) * kHD + dl * 16;
-      const __nv_bfloat16* vp = v_cache + (slot * Hkv + hk) * kHD + dl * 16;
-      const uint4 k0 = reinterpret_cast<const uint4*>(kp)[0];
-      const uint4 k1 = reinterpret_cast<const uint4*>(kp)[1];
-      const uint4 v0 = reinterpret_cast<const uint4*>(vp)[0];
-      const uint4 v1 = reinterpret_cast<const uint4*>(vp)[1];
-      const __nv_bfloat162* kb0 = reinterpret_cast<const __nv_bfloat162*>(&k0);
-      const __nv_bfloat162* kb1 = reinterpret_cast<const __nv_bfloat162*>(&k1);
-      const __nv_bfloat162* vb0 = reinterpret_cast<const __nv_bfloat162*>(&v0);
-      const __nv_bfloat162* vb1 = reinterpret_cast<const __nv_bfloat162*>(&v1);
+    const bool valid = base + sub < t_end;
+    nxt.k0 = nxt.k1 = nxt.v0 = nxt.v1 = make_uint4(0, 0, 0, 0);
+    if (base + 16 + sub < t_end)
+      load_kv(nxt, k_cache, v_cache, bt, base + 16 + sub, block_size, Hkv, hk, dl);
+    const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&cur.k0);  // k0,k1 contiguous
+    const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&cur.v0);
+    float vf[16];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        float2 a = __bfloat1622float2(kb0[i]), c = __bfloat1622float2(kb1[i]);
-        kf[2 * i] = a.x; kf[2 * i + 1] = a.y; kf[8 + 2 * i] = c.x; kf[8 + 2 * i + 1] = c.y;
-        float2 d = __bfloat1622float2(vb0[i]), e = __bfloat1622float2(vb1[i]);
-        vf[2 * i] = d.x; vf[2 * i + 1] = d.y; vf[8 + 2 * i] = e.x; vf[8 + 2 * i + 1] = e.y;
-      }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) { kf[i] = 0.f; vf[i] = 0.f; }
+    for (int i = 0; i < 8; ++i) {
+      const float2 f = __bfloat1622float2(vb[i]);
+      vf[2 * i] = f.x;
+      vf[2 * i + 1] = f.y;
     }
 #pragma unroll
     for (int g = 0; g < G; ++g) {
+      const float4* qs = reinterpret_cast<const float4*>(&s_q[g][dl * 16]);
       float s = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i) s += qv[g][i] * kf[i];
+      for (int i = 0; i < 4; ++i) {
+        const float4 qv = qs[i];
+        const float2 ka = __bfloat1622float2(kb[2 * i]);
+        const float2 kc = __bfloat1622float2(kb[2 * i + 1]);
+        s += qv.x * ka.x + qv.y * ka.y + qv.z * kc.x + qv.w * kc.y;
+      }
       s += __shfl_xor_sync(0xffffffffu, s, 1);
       s += __shfl_xor_sync(0xffffffffu, s, 2);
       s += __shfl_xor_sync(0xffffffffu, s, 4);
@@ -130,6 +145,7 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
         m[g] = mn;
       }
     }
+    cur = nxt;
   }
   // merge the 4 token slots of the warp (lanes with equal dl), then the 4 warps
   __shared__ float s_m[4][G], s_l[4][G], s_acc[4][G][kHD];

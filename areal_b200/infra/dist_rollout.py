@@ -68,12 +68,14 @@ def exchange_weight_buffers(topo: DisaggTopology, rollout_engine=None, device_in
     """Collective over the world: rollout ranks export their flat weight buffer, trainer
     ranks map all of them. Returns the mapped pointers on trainer ranks ([] on rollout ranks)."""
     handle = None
-    if topo.is_rollout:
+    if topo.is_rollout and rollout_engine.flat.cuda:
         handle = (rollout_engine.flat.param_buf.ipc_handle(), rollout_engine.flat.numel)
     handles: list[Any] = [None] * topo.world
     dist.all_gather_object(handles, handle, group=topo.all_cpu_group)
     if topo.is_rollout:
         return []
+    if any(handles[g] is None for g in topo.gen_ranks):
+        return []  # CPU ranks: weights travel over gloo instead (see receive_weights)
     return [open_ipc_handle(handles[g][0], device_index) for g in topo.gen_ranks]
 
 
@@ -96,6 +98,16 @@ class RolloutServer:
             if cmd[0] == "pause":
                 self.engine.pause_generation()
                 dist.send_object_list([("ack", time.time())], dst=lead, group=self.topo.ctl_group)
+            elif cmd[0] == "weights":
+                # CPU fallback: every trainer rank sends its shard of the flat weights over gloo
+                flat = self.engine.flat.flat
+                shard = cmd[1]
+                for i, t in enumerate(self.topo.train_ranks):
+                    buf = torch.empty(shard, dtype=flat.dtype)
+                    dist.recv(buf, src=t, group=self.topo.ctl_group)
+                    n = min(shard, flat.numel() - i * shard)
+                    if n > 0:
+                        flat[i * shard: i * shard + n].copy_(buf[:n])
             elif cmd[0] == "resume":
                 if cmd[1] is not None:
                     self.engine.set_version(cmd[1])
@@ -185,8 +197,18 @@ class RemoteRolloutClient(InferenceEngine):
         rank's weight buffer (peer stores over NVLink), then synchronises its stream."""
         f = trainer.flat
         itemsize = f.flat.element_size()
-        lib = _lib.kernels()
         shard = f.flat[f.shard_offset: f.shard_offset + f.shard_numel]
+        if not self.weight_ptrs:
+            for g in self.led:
+                dist.send_object_list([("weights", f.shard_numel)], dst=g, group=self.topo.ctl_group)
+            if self.train_cpu_group is not None:
+                dist.barrier(group=self.train_cpu_group)
+            for g in self.topo.gen_ranks:
+                dist.send(shard.contiguous(), dst=g, group=self.topo.ctl_group)
+            if version is not None:
+                self._version = version
+            return
+        lib = _lib.kernels()
         rc = lib.b200_push_all(self._table, ctypes.c_int(len(self.weight_ptrs)), _lib.ptr(shard),
                                ctypes.c_longlong(f.shard_numel * itemsize),
                                ctypes.c_longlong(f.shard_offset * itemsize), _lib.stream_ptr())
