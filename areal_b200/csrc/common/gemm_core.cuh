@@ -17,6 +17,7 @@
 //   struct Epi {
 //     __device__ bool tile(int cta, int ncta, int iter, int tiles_m, int tiles_n,
 //                          int& m_blk, int& n_blk) const;   // false = done
+//     __device__ bool gate(int m_blk, int n_blk, volatile int* abort, int* status) const;  // producer-side
 //     __device__ void begin(State&, int m_blk, int n_blk, int row) const;
 //     __device__ void chunk(State&, int row, int col0, const float (&v)[32]) const;
 //     __device__ void end(State&, int m_blk, int n_blk, int row) const;
@@ -117,6 +118,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       for (int it = 0; ok; ++it) {
         int m_blk, n_blk;
         if (!epi.tile(blockIdx.x, gridDim.x, it, tiles_m, tiles_n, m_blk, n_blk)) break;
+        // fused all-gather→GEMM: wait (bounded) until the rows of this tile have arrived
+        if (!epi.gate(m_blk, n_blk, abort_flag, status)) {
+          ok = false;
+          break;
+        }
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             ok = false;

@@ -27,6 +27,7 @@ struct StoreEpi {
                                        int& m_blk, int& n_blk) const {
     return default_tile(cta, ncta, it, tiles_m, tiles_n, m_blk, n_blk);
   }
+  __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
   __device__ __forceinline__ void begin(State&, int, int, int) const {}
   __device__ __forceinline__ void end(State&, int, int, int) const {}
   __device__ __forceinline__ void chunk(State&, int row, int col0, const float (&v_in)[32]) const {

@@ -42,6 +42,7 @@ struct LmStatsEpi {
     n_blk = static_cast<int>(w / tiles_m) * nb_per + j;
     return true;
   }
+  __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
   __device__ __forceinline__ void begin(State& s, int, int n_blk, int) const {
     if (n_blk % nb_per == 0) {
       s.m = -INFINITY;
@@ -132,6 +133,7 @@ struct LmDlogitsEpi {
                                        int& m_blk, int& n_blk) const {
     return default_tile(cta, ncta, it, tiles_m, tiles_n, m_blk, n_blk);
   }
+  __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
   __device__ __forceinline__ void begin(State& s, int, int, int row) const {
     if (row < T) {
       s.gl = g_logp ? g_logp[row] : 0.f;

@@ -47,51 +47,84 @@ __global__ void kv_cache_write_kernel(const __nv_bfloat16* __restrict__ k,
 
 // q: [B, Hq, 128]; partial outputs: o_part [B, Hq, nsplit, 128] fp32, ml_part [B, Hq, nsplit, 2].
 //
-// Bandwidth notes: a lane keeps the K and V slices of its token as raw bf16
-// (4 x 16 bytes) and the slices of the *next* warp step are requested before the
-// current ones are consumed, so every lane has 128 bytes in flight; q lives in
-// shared memory as fp32. The register budget allows 5+ CTAs per SM.
-struct KVRaw {
-  uint4 k0, k1, v0, v1;
-};
+// Bandwidth: K/V rows stream into shared memory through a 4-stage cp.async
+// pipeline (32 tokens = 16 KB per stage, 64 KB per CTA, 3 CTAs per SM), so
+// ~190 KB per SM are in flight regardless of register pressure. The softmax
+// running max is only raised when a score exceeds it by 2^8 (lazy rescaling),
+// which removes the per-token rescale multiplies from the common path.
+constexpr int kTok = 32;      // tokens per pipeline stage
+constexpr int kStagesD = 4;
+constexpr int kRowB = 256;    // bytes of one K (or V) row of one kv head
+constexpr int kStageB = 2 * kTok * kRowB;
 
-__device__ __forceinline__ void load_kv(KVRaw& r, const __nv_bfloat16* __restrict__ k_cache,
-                                        const __nv_bfloat16* __restrict__ v_cache,
-                                        const int* __restrict__ bt, int t, int block_size, int Hkv,
-                                        int hk, int dl) {
-  const int blk = __ldg(bt + t / block_size);
-  const long long slot = static_cast<long long>(blk) * block_size + (t % block_size);
-  const uint4* kp = reinterpret_cast<const uint4*>(k_cache + (slot * Hkv + hk) * kHD + dl * 16);
-  const uint4* vp = reinterpret_cast<const uint4*>(v_cache + (slot * Hkv + hk) * kHD + dl * 16);
-  r.k0 = __ldcs(kp);
-  r.k1 = __ldcs(kp + 1);
-  r.v0 = __ldcs(vp);
-  r.v1 = __ldcs(vp + 1);
+__device__ __forceinline__ void cp_async16(void* smem_dst, const void* gsrc) {
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(
+                   static_cast<uint32_t>(__cvta_generic_to_shared(smem_dst))),
+               "l"(gsrc)
+               : "memory");
+}
+__device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N>
+__device__ __forceinline__ void cp_async_wait() {
+  asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory");
 }
 
 template <int G>
-__global__ void __launch_bounds__(128, (G <= 2 ? 5 : (G <= 4 ? 3 : 2)))
+__global__ void __launch_bounds__(128, (G <= 2 ? 3 : (G <= 4 ? 2 : 1)))
 paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ k_cache,
                     const __nv_bfloat16* __restrict__ v_cache, const int* __restrict__ block_table,
                     const int* __restrict__ seq_lens, float* __restrict__ o_part,
                     float* __restrict__ ml_part, int Hq, int Hkv, int block_size, int max_blocks,
                     int nsplit, float scale_log2) {
+  extern __shared__ __align__(16) uint8_t dsm[];  // kStagesD stages of [K 32x256B | V 32x256B]
   const int b = blockIdx.x, hk = blockIdx.y, split = blockIdx.z;
   const int L = seq_lens[b];
   const int per = (L + nsplit - 1) / nsplit;
   const int t_begin = split * per;
   const int t_end = min(L, t_begin + per);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int sub = lane >> 3;  // token slot inside the warp step (0..3)
+  const int sub = lane >> 3;  // token slot inside a warp step (0..3)
   const int dl = lane & 7;    // owns dims [16*dl, 16*dl+16)
+  const int n_tiles = (max(t_end - t_begin, 0) + kTok - 1) / kTok;
+  const int* bt = block_table + static_cast<long long>(b) * max_blocks;
 
-  __shared__ __align__(16) float s_q[G][kHD];
-  for (int i = threadIdx.x; i < G * kHD; i += blockDim.x) {
-    const int g = i / kHD, d = i % kHD;
-    s_q[g][d] = __bfloat162float(q[(static_cast<long long>(b) * Hq + hk * G + g) * kHD + d]) * scale_log2;
+  // each thread copies 4 K chunks and 4 V chunks (16 B) per stage: chunk c = tid + 128*i,
+  // token = c / 16, piece = c % 16
+  auto issue = [&](int tile) {
+    if (tile < n_tiles) {
+      uint8_t* st = dsm + (tile % kStagesD) * kStageB;
+      const int t0 = t_begin + tile * kTok;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int c = threadIdx.x + 128 * i;
+        const int tok = c >> 4, piece = c & 15;
+        const int t = t0 + tok;
+        if (t < t_end) {
+          const int blk = __ldg(bt + t / block_size);
+          const long long slot = static_cast<long long>(blk) * block_size + (t % block_size);
+          const uint8_t* kp = reinterpret_cast<const uint8_t*>(k_cache + (slot * Hkv + hk) * kHD) + piece * 16;
+          const uint8_t* vp = reinterpret_cast<const uint8_t*>(v_cache + (slot * Hkv + hk) * kHD) + piece * 16;
+          cp_async16(st + tok * kRowB + piece * 16, kp);
+          cp_async16(st + kTok * kRowB + tok * kRowB + piece * 16, vp);
+        }
+      }
+    }
+    cp_async_commit();
+  };
+#pragma unroll
+  for (int sgi = 0; sgi < kStagesD - 1; ++sgi) issue(sgi);
+
+  float qv[G][16];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    const __nv_bfloat16* qp = q + (static_cast<long long>(b) * Hq + hk * G + g) * kHD + dl * 16;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float2 f = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(qp)[i]);
+      qv[g][2 * i] = f.x * scale_log2;
+      qv[g][2 * i + 1] = f.y * scale_log2;
+    }
   }
-  __syncthreads();
-
   float m[G], l[G], acc[G][16];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -100,53 +133,58 @@ paged_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
 #pragma unroll
     for (int i = 0; i < 16; ++i) acc[g][i] = 0.f;
   }
-  const int* bt = block_table + static_cast<long long>(b) * max_blocks;
-  KVRaw cur, nxt;
-  cur.k0 = cur.k1 = cur.v0 = cur.v1 = make_uint4(0, 0, 0, 0);
-  int base = t_begin + warp * 4;
-  if (base + sub < t_end) load_kv(cur, k_cache, v_cache, bt, base + sub, block_size, Hkv, hk, dl);
-  for (; base < t_end; base += 16) {
-    // the loop bound is warp-uniform so the shuffles below stay converged;
-    // token slots past the end contribute nothing
-    const bool valid = base + sub < t_end;
-    nxt.k0 = nxt.k1 = nxt.v0 = nxt.v1 = make_uint4(0, 0, 0, 0);
-    if (base + 16 + sub < t_end)
-      load_kv(nxt, k_cache, v_cache, bt, base + 16 + sub, block_size, Hkv, hk, dl);
-    const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(&cur.k0);  // k0,k1 contiguous
-    const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(&cur.v0);
-    float vf[16];
+
+  for (int tile = 0; tile < n_tiles; ++tile) {
+    issue(tile + kStagesD - 1);
+    cp_async_wait<kStagesD - 1>();
+    __syncthreads();
+    const uint8_t* st = dsm + (tile % kStagesD) * kStageB;
+    const int t0 = t_begin + tile * kTok;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const float2 f = __bfloat1622float2(vb[i]);
-      vf[2 * i] = f.x;
-      vf[2 * i + 1] = f.y;
-    }
+    for (int it = 0; it < 2; ++it) {
+      const int tok = warp * 8 + it * 4 + sub;
+      const bool valid = t0 + tok < t_end;
+      const uint4* kp = reinterpret_cast<const uint4*>(st + tok * kRowB + dl * 32);
+      const uint4* vp = reinterpret_cast<const uint4*>(st + kTok * kRowB + tok * kRowB + dl * 32);
+      uint4 kr[2], vr[2];
+      kr[0] = kp[0]; kr[1] = kp[1];
+      vr[0] = vp[0]; vr[1] = vp[1];
+      const __nv_bfloat162* kb = reinterpret_cast<const __nv_bfloat162*>(kr);
+      const __nv_bfloat162* vb = reinterpret_cast<const __nv_bfloat162*>(vr);
+      float kf[16], vf[16];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float4* qs = reinterpret_cast<const float4*>(&s_q[g][dl * 16]);
-      float s = 0.f;
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const float4 qv = qs[i];
-        const float2 ka = __bfloat1622float2(kb[2 * i]);
-        const float2 kc = __bfloat1622float2(kb[2 * i + 1]);
-        s += qv.x * ka.x + qv.y * ka.y + qv.z * kc.x + qv.w * kc.y;
+      for (int i = 0; i < 8; ++i) {
+        const float2 a = __bfloat1622float2(kb[i]);
+        const float2 c = __bfloat1622float2(vb[i]);
+        kf[2 * i] = a.x; kf[2 * i + 1] = a.y;
+        vf[2 * i] = c.x; vf[2 * i + 1] = c.y;
       }
-      s += __shfl_xor_sync(0xffffffffu, s, 1);
-      s += __shfl_xor_sync(0xffffffffu, s, 2);
-      s += __shfl_xor_sync(0xffffffffu, s, 4);
-      if (valid) {
-        const float mn = fmaxf(m[g], s);
-        const float sc = exp2f(m[g] - mn);  // exp2(-inf) = 0 on the first token
-        const float p = exp2f(s - mn);
-        l[g] = l[g] * sc + p;
 #pragma unroll
-        for (int i = 0; i < 16; ++i) acc[g][i] = acc[g][i] * sc + p * vf[i];
-        m[g] = mn;
+      for (int g = 0; g < G; ++g) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) s += qv[g][i] * kf[i];
+        s += __shfl_xor_sync(0xffffffffu, s, 1);
+        s += __shfl_xor_sync(0xffffffffu, s, 2);
+        s += __shfl_xor_sync(0xffffffffu, s, 4);
+        if (valid) {
+          if (s > m[g] + 8.f) {  // raise the reference max only when needed (also the first token)
+            const float sc = exp2f(m[g] - s);
+            l[g] *= sc;
+#pragma unroll
+            for (int i = 0; i < 16; ++i) acc[g][i] *= sc;
+            m[g] = s;
+          }
+          const float p = exp2f(s - m[g]);
+          l[g] += p;
+#pragma unroll
+          for (int i = 0; i < 16; ++i) acc[g][i] += p * vf[i];
+        }
       }
     }
-    cur = nxt;
+    __syncthreads();
   }
+  cp_async_wait<0>();
   // merge the 4 token slots of the warp (lanes with equal dl), then the 4 warps
   __shared__ float s_m[4][G], s_l[4][G], s_acc[4][G][kHD];
 #pragma unroll
@@ -244,7 +282,9 @@ int b200_paged_decode(const void* q, const void* k_cache, const void* v_cache,
   const float sl2 = softmax_scale * 1.4426950408889634f;
   dim3 grid(B, Hkv, nsplit);
 #define LAUNCH(G_)                                                                             \
-  paged_decode_kernel<G_><<<grid, 128, 0, stream>>>(                                           \
+  cudaFuncSetAttribute(paged_decode_kernel<G_>, cudaFuncAttributeMaxDynamicSharedMemorySize,   \
+                       kStagesD * kStageB);                                                     \
+  paged_decode_kernel<G_><<<grid, 128, kStagesD * kStageB, stream>>>(                                           \
       (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache,   \
       block_table, seq_lens, o_part, ml_part, Hq, Hkv, block_size, max_blocks, nsplit, sl2)
   switch (G) {

@@ -43,9 +43,10 @@ class FlatParams:
         self.model = model
         self.device = params[0].device
         self.dtype = params[0].dtype
+        local = isinstance(dp_group, str) and dp_group == "local"
         self.dp_group = dp_group
-        self.dp_world = dist.get_world_size(dp_group) if dist.is_initialized() else 1
-        self.dp_rank = dist.get_rank(dp_group) if dist.is_initialized() else 0
+        self.dp_world = dist.get_world_size(dp_group) if (dist.is_initialized() and not local) else 1
+        self.dp_rank = dist.get_rank(dp_group) if (dist.is_initialized() and not local) else 0
         self.entries: list[tuple[str, torch.nn.Parameter, int, int]] = []
         off = 0
         seen: dict[int, int] = {}

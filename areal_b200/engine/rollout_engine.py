@@ -174,7 +174,7 @@ class NativeRolloutEngine(InferenceEngine):
         for p in self.model.parameters():
             p.requires_grad_(False)
         # weights live in one flat buffer with the trainer's layout: weight sync is a flat copy
-        self.flat = FlatParams(self.model, kwargs.get("weight_group"), with_grads=False)
+        self.flat = FlatParams(self.model, kwargs.get("weight_group", "local"), with_grads=False)
         bs = ncfg.kv_block_size
         max_blocks_per_seq = (ncfg.context_length + bs - 1) // bs
         nblocks = ncfg.num_kv_blocks or self._auto_num_blocks(mc, dtype, bs)

@@ -43,10 +43,13 @@ class SymmBuffer:
     pass ``nbytes=0`` and only learn the pointers, e.g. trainer ranks that write
     into rollout buffers they do not themselves allocate)."""
 
-    def __init__(self, nbytes: int, group: dist.ProcessGroup | None = None, device=None):
-        self.group = group
-        self.world = dist.get_world_size(group) if dist.is_initialized() else 1
-        self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+    def __init__(self, nbytes: int, group: dist.ProcessGroup | None | str = None, device=None):
+        # group == "local": a private allocation of this process (no exchange), e.g. the rollout
+        # engine's weight buffer, which is exported separately to the trainer ranks
+        local = isinstance(group, str) and group == "local"
+        self.group = None if local else group
+        self.world = dist.get_world_size(group) if (dist.is_initialized() and not local) else 1
+        self.rank = dist.get_rank(group) if (dist.is_initialized() and not local) else 0
         self.nbytes = int(nbytes)
         self.device = torch.device(device if device is not None else
                                    ("cuda", torch.cuda.current_device()))
@@ -72,7 +75,7 @@ class SymmBuffer:
             handle = bytes(buf.raw)
         if self.world > 1:
             handles: list = [None] * self.world
-            dist.all_gather_object(handles, (handle, self.nbytes), group=group)
+            dist.all_gather_object(handles, (handle, self.nbytes), group=self.group)
             self.peer_sizes = [h[1] for h in handles]
             for r, (h, _) in enumerate(handles):
                 if r == self.rank:

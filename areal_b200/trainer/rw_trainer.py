@@ -1,0 +1,2 @@
+"""Entry point kept for source compatibility with the reference's module layout."""
+from .sl_trainer import RWTrainer  # noqa: F401

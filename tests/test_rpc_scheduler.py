@@ -1,0 +1,101 @@
+"""Serialization envelopes, RTensor handles, the RPC server and the local scheduler
+(real subprocess workers on localhost with a CPU fake engine)."""
+import asyncio
+import dataclasses
+import enum
+
+import numpy as np
+import pytest
+import torch
+
+from areal_b200.api.cli_args import GenerationHyperparameters, SchedulingSpec
+from areal_b200.api.io_struct import ModelRequest
+from areal_b200.api.scheduler_api import Job
+from areal_b200.infra.rpc import rtensor
+from areal_b200.infra.rpc.serialization import deserialize_value, serialize_value
+from areal_b200.infra.scheduler.exceptions import (EngineCallError, WorkerCreationError, WorkerFailedError,
+                                                   WorkerNotFoundError)
+from areal_b200.infra.scheduler.local import LocalScheduler
+
+
+class Color(enum.Enum):
+    RED = "r"
+
+
+def test_serialization_roundtrip():
+    v = {"t": torch.arange(6).view(2, 3), "bf": torch.randn(3).bfloat16(), "np": np.ones((2, 2), dtype=np.float32),
+         "tup": (1, "a", 2.5), "set": {1, 2}, "b": b"xyz", "e": Color.RED, "n": None,
+         "dc": ModelRequest(input_ids=[1, 2], gconfig=GenerationHyperparameters(max_new_tokens=7)), 3: "int-key"}
+    out = deserialize_value(serialize_value(v))
+    assert torch.equal(out["t"], v["t"]) and torch.equal(out["bf"], v["bf"]) and out["bf"].dtype == torch.bfloat16
+    assert np.array_equal(out["np"], v["np"]) and out["tup"] == (1, "a", 2.5) and out["set"] == {1, 2}
+    assert out["b"] == b"xyz" and out["e"] is Color.RED and out["n"] is None and out[3] == "int-key"
+    assert out["dc"].input_ids == [1, 2] and out["dc"].gconfig.max_new_tokens == 7
+    with pytest.raises(TypeError):
+        serialize_value(object())
+
+
+def test_rtensor_local_roundtrip():
+    batch = {"a": torch.randn(4, 3), "meta": {"ids": [torch.arange(3)], "k": 5}}
+    h = rtensor.remotize(batch)
+    assert isinstance(h["a"], rtensor.RTensor) and h["a"].shape == (4, 3) and h["meta"]["k"] == 5
+    assert h["a"].meta.device.type == "meta"
+    wire = deserialize_value(serialize_value(h))
+    back = rtensor.localize(wire)
+    assert torch.equal(back["a"], batch["a"]) and torch.equal(back["meta"]["ids"][0], torch.arange(3))
+    ids = [s for _, s in rtensor.collect_shard_ids(h)]
+    assert len(ids) == 2
+    rtensor.LOCAL_STORE.delete(ids)
+    with pytest.raises(KeyError):
+        rtensor.localize(h)
+
+
+@pytest.fixture
+def sched(tmp_path):
+    s = LocalScheduler(gpu_devices=[0, 1], log_dir=str(tmp_path), startup_timeout=60)
+    yield s
+    s.delete_workers()
+
+
+def test_local_scheduler_lifecycle_and_engine_calls(sched):
+    ids = sched.create_workers(Job(replicas=2, tasks=[SchedulingSpec(gpu=1)], role="actor"))
+    assert ids == ["actor/0", "actor/1"]
+    workers = sched.get_workers("actor", timeout=60)
+    assert len(workers) == 2 and sched._by_id["actor/0"].gpus != sched._by_id["actor/1"].gpus
+    with pytest.raises(WorkerCreationError):
+        sched.create_workers(Job(replicas=1, role="actor"))
+    # colocated role shares the GPUs of its target
+    from areal_b200.api.cli_args import SchedulingStrategy
+
+    sched.create_workers(Job(replicas=2, role="ref", scheduling_strategy=SchedulingStrategy("colocation", "actor")))
+    assert sched._by_id["ref/1"].gpus == sched._by_id["actor/1"].gpus
+    sched.get_workers("ref", timeout=60)
+    asyncio.run(sched.create_engine("actor/0", "tests.fake_engine.FakeTrainEngine", scale=3.0))
+    out = sched.call_engine("actor/0", "train_batch", None, {"x": torch.ones(2, 2)})
+    assert out["sum"] == pytest.approx(12.0) and out["calls"] == 1
+    out = asyncio.run(sched.async_call_engine("actor/0", "train_batch", None, {"x": torch.ones(1)}))
+    assert out["calls"] == 2
+    # tensors can stay on the worker and travel as handles
+    h = sched.call_engine("actor/0", "make_batch", None, 5, return_rtensor=True)
+    assert isinstance(h["ids"], rtensor.RTensor) and h["ids"].addr is not None
+    assert torch.equal(h["ids"].to_local(), torch.arange(5))
+    assert sched.call_engine("actor/0", "consume", None, h) == 10
+    with pytest.raises(EngineCallError):
+        sched.call_engine("actor/0", "explode", None)
+    with pytest.raises(EngineCallError):
+        sched.call_engine("actor/1", "train_batch", None, {})  # no engine on this worker
+    with pytest.raises(WorkerNotFoundError):
+        sched.call_engine("nobody/0", "x", None)
+    sched.delete_workers("ref")
+    with pytest.raises(WorkerNotFoundError):
+        sched.get_workers("ref")
+
+
+def test_dead_worker_is_detected(sched):
+    sched.create_workers(Job(replicas=1, role="w"))
+    sched.get_workers("w", timeout=60)
+    asyncio.run(sched.create_engine("w/0", "tests.fake_engine.FakeTrainEngine"))
+    sched._by_id["w/0"].process.kill()
+    sched._by_id["w/0"].process.wait()
+    with pytest.raises(WorkerFailedError):
+        sched.call_engine("w/0", "train_batch", None, {"x": torch.ones(1)})
