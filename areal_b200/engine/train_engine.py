@@ -83,9 +83,12 @@ class B200TrainEngine(TrainEngine):
 
     # ------------------------------------------------------------ process groups
     def create_process_group(self, parallel_strategy: ParallelStrategy | None = None,
-                             ranks: list[int] | None = None, backend: str | None = None):
+                             ranks: list[int] | None = None, backend: str | None = None, groups=None):
         """Builds the data-parallel group over ``ranks`` (default: the whole world).
-        ``torch.distributed`` is initialised from the torchrun environment if needed."""
+        ``torch.distributed`` is initialised from the torchrun environment if needed.
+        ``groups=(dp_group, cpu_group)`` reuses groups another engine already created (group
+        creation is collective over the whole world, so engines that only some ranks own must
+        not create their own)."""
         use_cuda = torch.cuda.is_available() and self.config.dtype != "float32_cpu"
         if not dist.is_initialized() and "RANK" in os.environ:
             backend = backend or ("nccl" if use_cuda else "gloo")
@@ -103,12 +106,15 @@ class B200TrainEngine(TrainEngine):
             world = dist.get_world_size()
             ranks = list(range(world)) if ranks is None else list(ranks)
             self.train_ranks = ranks
-            if ranks == list(range(world)):
-                self._dp_group = dist.group.WORLD
+            if groups is not None:
+                self._dp_group, self._cpu_group = groups
             else:
-                self._dp_group = dist.new_group(ranks)
-            self._cpu_group = dist.new_group(ranks, backend="gloo") if dist.get_backend() != "gloo" \
-                else self._dp_group
+                if ranks == list(range(world)):
+                    self._dp_group = dist.group.WORLD
+                else:
+                    self._dp_group = dist.new_group(ranks)
+                self._cpu_group = dist.new_group(ranks, backend="gloo") if dist.get_backend() != "gloo" \
+                    else self._dp_group
             self.world_size = len(ranks)
             self.dp_rank = ranks.index(self.rank) if self.rank in ranks else -1
         else:

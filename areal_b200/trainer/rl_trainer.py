@@ -119,6 +119,7 @@ class PPOTrainer:
         helper = self.actor_engine or B200TrainEngine(config.actor)
         helper.create_process_group(self.actor_alloc.parallel, ranks=train_ranks)
         self.train_cpu_group = helper.cpu_group
+        shared = (helper.data_parallel_group, helper.cpu_group)
         self.rollout = None
         self.rollout_client = None
         if self.is_rollout:
@@ -131,11 +132,11 @@ class PPOTrainer:
             self.actor_engine.initialize(None, self.ft_spec, seed=config.seed)
             if config.critic is not None:
                 self.critic_engine = B200TrainEngine(config.critic)
-                self.critic_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks)
+                self.critic_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks, groups=shared)
                 self.critic_engine.initialize(None, self.ft_spec, seed=config.seed + 1)
             if config.ref is not None and config.actor.kl_ctl != 0.0:
                 self.ref_engine = B200TrainEngine(config.ref)
-                self.ref_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks)
+                self.ref_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks, groups=shared)
                 self.ref_engine.initialize(None, self.ft_spec, seed=config.seed)
         if self.colocated:
             self.rollout_client = self.rollout

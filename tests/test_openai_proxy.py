@@ -1,0 +1,128 @@
+"""OpenAI-compatible client, interaction cache, tool-call parser and the proxy server (fake engine)."""
+import asyncio
+
+import pytest
+import torch
+from fastapi.testclient import TestClient
+
+from areal_b200.api.io_struct import ModelResponse
+from areal_b200.infra.rpc.serialization import deserialize_value
+from areal_b200.openai.cache import InteractionCache
+from areal_b200.openai.client import ArealOpenAI
+from areal_b200.openai.proxy.proxy_rollout_server import create_proxy_app
+from areal_b200.openai.proxy.workflow import OpenAIProxyWorkflow
+from areal_b200.openai.tool_call_parser import parse_reasoning, parse_tool_calls
+from areal_b200.openai.types import InteractionWithTokenLogpReward
+
+
+class Tok:
+    eos_token_id = 0
+
+    def apply_chat_template(self, messages, tokenize=True, add_generation_prompt=True, **kw):
+        ids = []
+        for m in messages:
+            ids += [1] + [2 + (ord(c) % 90) for c in str(m["content"])] + [1]
+        return ids + [99]
+
+    def decode(self, ids):
+        return "".join(chr(97 + (i % 26)) for i in ids)
+
+
+class Engine:
+    def __init__(self):
+        self.version = 3
+
+    async def agenerate(self, req):
+        n = min(req.gconfig.max_new_tokens, 4)
+        out = [5, 6, 7, 0][:n]
+        return ModelResponse(input_tokens=list(req.input_ids), output_tokens=out, output_logprobs=[-0.5] * len(out),
+                             output_versions=[self.version] * len(out), stop_reason="stop" if out[-1] == 0 else "length")
+
+
+def test_tool_call_and_reasoning_parsers():
+    text = 'Let me check. <tool_call>{"name": "search", "arguments": {"q": "x"}}</tool_call> <tool_call>{bad}</tool_call>'
+    content, calls = parse_tool_calls(text, [{"type": "function", "function": {"name": "search"}}])
+    assert content.startswith("Let me check.") and len(calls) == 1
+    assert calls[0]["function"]["name"] == "search" and '"q"' in calls[0]["function"]["arguments"]
+    assert parse_tool_calls('<tool_call>{"name": "other", "arguments": {}}</tool_call>', [{"function": {"name": "search"}}])[1] == []
+    assert parse_reasoning("<think>plan</think>answer") == ("plan", "answer")
+    assert parse_reasoning("no tags") == (None, "no tags")
+
+
+def _inter(iid, inp, out, reward=None):
+    return InteractionWithTokenLogpReward(interaction_id=iid, reward=reward, model_response=ModelResponse(
+        input_tokens=inp, output_tokens=out, output_logprobs=[-1.0] * len(out), output_versions=[0] * len(out)))
+
+
+def test_cache_reward_backprop_and_export_styles():
+    c = InteractionCache()
+    c.add(_inter("a", [1, 2], [3]))
+    c.add(_inter("b", [1, 2, 3, 9], [4]))       # continues a
+    c.add(_inter("x", [7], [8], reward=0.5))     # unrelated branch
+    c.set_reward(None, 0.5)
+    c.set_reward("b", 1.0)
+    out = c.export("individual", turn_discount=0.5)
+    assert out["b"].reward == 1.0 and out["a"].reward == 0.5 and out["x"].reward == 0.5
+    assert set(c.export("concat")) == {"b", "x"}
+    td = out["b"].to_tensor_dict()
+    assert td["input_ids"].tolist() == [[1, 2, 3, 9, 4]] and td["loss_mask"].tolist() == [[0, 0, 0, 0, 1]]
+    assert td["versions"].tolist() == [[-1, -1, -1, -1, 0]] and td["rewards"].tolist() == [1.0]
+    with pytest.raises(KeyError):
+        c.set_reward("nope", 1.0)
+
+
+def test_client_records_interactions():
+    async def go():
+        cl = ArealOpenAI(Engine(), Tok())
+        r1 = await cl.chat.completions.create(messages=[{"role": "user", "content": "hi"}], max_completion_tokens=8)
+        r2 = await cl.responses.create(input="hello", max_output_tokens=2)
+        cl.set_reward(r1.id, 2.0)
+        return cl, r1, r2
+
+    cl, r1, r2 = asyncio.run(go())
+    assert r1.choices[0].finish_reason == "stop" and r1.usage.completion_tokens == 4
+    assert r2.usage.output_tokens == 2 and len(cl.cache) == 2
+    exp = cl.export_interactions()
+    assert exp[r1.id].reward == 2.0 and exp[r1.id].model_response.output_versions == [3, 3, 3, 3]
+
+
+def test_proxy_server_sessions():
+    app = create_proxy_app(Engine(), Tok(), admin_api_key="adm")
+    c = TestClient(app)
+    assert c.get("/health").json()["status"] == "ok"
+    assert c.post("/rl/start_session", json={}).status_code == 401
+    adm = {"Authorization": "Bearer adm"}
+    assert c.post("/rl/start_session", json={"require_capacity": True}, headers=adm).status_code == 429
+    assert c.post("/grant_capacity", json={"count": 1}, headers=adm).json()["capacity"] == 1
+    s = c.post("/rl/start_session", json={"require_capacity": True}, headers=adm).json()
+    key = {"Authorization": f"Bearer {s['api_key']}"}
+    assert c.post("/v1/chat/completions", json={"messages": []}, headers={"Authorization": "Bearer x"}).status_code == 401
+    r = c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "2+2?"}], "max_tokens": 8}, headers=key).json()
+    assert r["object"] == "chat.completion" and r["choices"][0]["message"]["role"] == "assistant"
+    m = c.post("/v1/messages", json={"system": "be brief", "messages": [{"role": "user", "content": [{"type": "text", "text": "hi"}]}],
+                                     "max_tokens": 8}, headers=key).json()
+    assert m["type"] == "message" and m["stop_reason"] == "end_turn"
+    rr = c.post("/v1/responses", json={"input": "hey", "max_output_tokens": 8}, headers=key).json()
+    assert rr["object"] == "response" and rr["usage"]["output_tokens"] == 4
+    assert c.post("/rl/set_reward", json={"reward": 1.0, "interaction_id": r["id"]}, headers=key).status_code == 200
+    assert c.post("/rl/set_reward", json={"reward": 1.0, "interaction_id": "zz"}, headers=key).status_code == 404
+    assert c.post("/rl/end_session", json={}, headers=key).json()["n_interactions"] == 3
+    assert c.post("/v1/chat/completions", json={"messages": []}, headers=key).status_code == 409
+    ex = c.post("/export_trajectories", json={"session_id": s["session_id"], "discount": 1.0}, headers=adm).json()
+    inter = {k: deserialize_value(v) for k, v in ex["interactions"].items()}
+    assert len(inter) == 3 and inter[r["id"]]["rewards"].tolist() == [1.0]
+    assert c.post("/export_trajectories", json={"session_id": s["session_id"]}, headers=adm).status_code == 404
+
+
+class Agent:
+    async def run(self, data, client=None, **kw):
+        r = await client.chat.completions.create(messages=[{"role": "user", "content": data["q"]}], max_completion_tokens=4)
+        return {r.id: 0.25}
+
+
+@pytest.mark.parametrize("mode", ["inline", "subproc"])
+def test_proxy_workflow_inline_and_subproc(mode):
+    wf = OpenAIProxyWorkflow(Agent(), tokenizer=Tok(), mode=mode)
+    out = asyncio.run(wf.arun_episode(Engine(), {"q": "why"}))
+    (inter,) = out.values()
+    assert inter.reward == 0.25 and inter.to_tensor_dict()["rewards"].tolist() == [0.25]
