@@ -72,7 +72,6 @@ quant_block128_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_f
 #pragma unroll
   for (int i = 0; i < 8; ++i) bmax = fmaxf(bmax, s_max[i]);
   const float scale = round_scale(fmaxf(bmax, 1e-12f) / kFp8Max, ue8m0);
-  const float inv = 1.f / scale;
   if (threadIdx.x == 0) scale_inv[static_cast<long long>(bm) * gridDim.x + bn] = scale;
 #pragma unroll
   for (int r = 0; r < 16; ++r) {
@@ -80,7 +79,7 @@ quant_block128_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, __nv_f
     if (row < M && col < N) {
       __nv_fp8_e4m3 q[4];
 #pragma unroll
-      for (int c = 0; c < 4; ++c) q[c] = __nv_fp8_e4m3(fminf(fmaxf(v[r][c] * inv, -kFp8Max), kFp8Max));
+      for (int c = 0; c < 4; ++c) q[c] = __nv_fp8_e4m3(fminf(fmaxf(__fdiv_rn(v[r][c], scale), -kFp8Max), kFp8Max));
       __nv_fp8_e4m3* dst = y + static_cast<long long>(row) * ldy + col;
       if (col + 3 < N && ((ldy & 3) == 0)) {
         *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(q);
@@ -112,11 +111,10 @@ __global__ void quant_1x128_kernel(const __nv_bfloat16* __restrict__ x, long lon
   }
   const float amax = warp_max_f(fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3]))));
   const float sc = round_scale(fmaxf(amax, 1e-12f) / kFp8Max, ue8m0);
-  const float inv = 1.f / sc;
   if (lane == 0) scale[static_cast<long long>(row) * lds + g] = sc;
   __nv_fp8_e4m3 q[4];
 #pragma unroll
-  for (int c = 0; c < 4; ++c) q[c] = __nv_fp8_e4m3(fminf(fmaxf(v[c] * inv, -kFp8Max), kFp8Max));
+  for (int c = 0; c < 4; ++c) q[c] = __nv_fp8_e4m3(fminf(fmaxf(__fdiv_rn(v[c], sc), -kFp8Max), kFp8Max));
   __nv_fp8_e4m3* dst = y + static_cast<long long>(row) * ldy + col;
   if (col + 3 < K && ((ldy & 3) == 0)) {
     *reinterpret_cast<uint32_t*>(dst) = *reinterpret_cast<const uint32_t*>(q);

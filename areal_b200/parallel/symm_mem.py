@@ -51,8 +51,7 @@ class SymmBuffer:
         self.world = dist.get_world_size(group) if (dist.is_initialized() and not local) else 1
         self.rank = dist.get_rank(group) if (dist.is_initialized() and not local) else 0
         self.nbytes = int(nbytes)
-        self.device = torch.device(device if device is not None else
-                                   ("cuda", torch.cuda.current_device()))
+        self.device = torch.device(device) if device is not None else torch.device("cuda", torch.cuda.current_device())
         self.local_ptr = 0
         self.peer_ptrs: list[int] = [0] * self.world
         self._opened: list[int] = []

@@ -346,7 +346,12 @@ class Normalization:
     @staticmethod
     def _reduce(t: torch.Tensor, group, do: bool) -> torch.Tensor:
         if do and dist.is_initialized():
-            dist.all_reduce(t, group=group)
+            if not t.is_cuda and dist.get_backend(group) == "nccl":
+                dev = t.cuda()  # NCCL reduces device tensors only
+                dist.all_reduce(dev, group=group)
+                t.copy_(dev)
+            else:
+                dist.all_reduce(t, group=group)
         return t
 
     @classmethod
