@@ -13,10 +13,12 @@ def test_quant_dequant_block128(M, N, ue8m0):
     torch.manual_seed(0)
     x = (torch.randn(M, N, device="cuda") * 3).bfloat16()
     q, s = fp8.quant_fp8_block128(x, ue8m0)
-    qr, sr = fp8.quant_block128_ref(x, ue8m0)
+    _, sr = fp8.quant_block128_ref(x, ue8m0)
     torch.testing.assert_close(s, sr, rtol=1e-6, atol=0)
-    assert (q.float() - qr.float()).abs().max().item() <= 32.0  # at most one fp8 step apart near a rounding tie
-    assert ((q.float() != qr.float()).float().mean().item()) < 1e-3
+    # requantise with the kernel's own scales (a 1-ulp difference in a scale moves rounding ties)
+    full = s.repeat_interleave(128, 0)[:M].repeat_interleave(128, 1)[:, :N]
+    qr = (x.float() / full).clamp(-448, 448).to(fp8.FP8)
+    assert torch.equal(q.float(), qr.float())
     d = fp8.dequant_fp8(q, s, 128)
     torch.testing.assert_close(d.float(), x.float(), rtol=0.07, atol=0.07 * float(s.max()) * 8)
     if ue8m0:
@@ -28,9 +30,10 @@ def test_quant_1x128(M, K):
     torch.manual_seed(1)
     x = torch.randn(M, K, device="cuda").bfloat16()
     q, s = fp8.quant_fp8_1x128(x)
-    qr, sr = fp8.quant_1x128_ref(x)
+    _, sr = fp8.quant_1x128_ref(x)
     torch.testing.assert_close(s, sr, rtol=1e-6, atol=0)
-    assert ((q.float() != qr.float()).float().mean().item()) < 1e-3
+    qr = (x.float() / s.repeat_interleave(128, 1)[:, :K]).clamp(-448, 448).to(fp8.FP8)
+    assert torch.equal(q.float(), qr.float())
     d = fp8.dequant_fp8(q, s, 1)
     torch.testing.assert_close(d.float(), x.float(), rtol=0.07, atol=0.02)
 
