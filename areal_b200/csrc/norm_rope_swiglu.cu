@@ -6,6 +6,10 @@
 // Replaces the eager / Inductor-fused RMSNorm, rotate_half RoPE and SiLU*mul of
 // the reference models (areal/experimental/models/archon/qwen3/model/model.py:75-101,
 // 103-293; qwen2/model/rope.py).
+#include <cstdio>
+#include <mutex>
+
+#include "norm_static_scratch.h"
 #include <cuda_bf16.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
@@ -479,3 +483,58 @@ int b200_swiglu_bwd(const void* dy, const void* gu, void* dgu, long long T, int 
 }
 
 }  // extern "C"
+
+// ------------------------------------------ RMSNorm backward, built-in scratch ----
+// See norm_static_scratch.h. The partial sums of dw go to a file-scope device array
+// whose address is looked up once per device; nothing here allocates.
+namespace b200 {
+static __device__ __align__(256) float g_rmsnorm_bwd_scratch[static_cast<size_t>(B200_RMSNORM_STATIC_MAX_BLOCKS) *
+                                                             B200_RMSNORM_STATIC_MAX_H];
+constexpr int kMaxDevices = 64;
+static std::mutex g_scratch_mu;
+static float* g_scratch_ptr[kMaxDevices] = {};
+}  // namespace b200
+
+extern "C" int b200_rmsnorm_bwd_static(const void* dy, const void* x, const void* w, const float* rstd,
+                                       const void* dres, void* dx, float* dw, int dw_accumulate, int T, int H,
+                                       cudaStream_t stream) {
+  using namespace b200;
+  if (T == 0) return 0;
+  if (H % 8) return -100;
+  const int grid = b200_rmsnorm_bwd_blocks(T);
+  if (H > B200_RMSNORM_STATIC_MAX_H || grid > B200_RMSNORM_STATIC_MAX_BLOCKS) {
+    fprintf(stderr,
+            "b200_rmsnorm_bwd_static: H=%d (max %d) or %d blocks (max %d) exceeds the built-in scratch; "
+            "use b200_rmsnorm_bwd with a caller-provided buffer\n",
+            H, B200_RMSNORM_STATIC_MAX_H, grid, B200_RMSNORM_STATIC_MAX_BLOCKS);
+    return B200_ERR_STATIC_SCRATCH_TOO_SMALL;
+  }
+  int dev = 0;
+  B200_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return -3;
+  float* scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_scratch_mu);
+    if (!g_scratch_ptr[dev]) {
+      // the array's name is only meaningful in device code; ask the runtime for its address on
+      // the current device
+      float* p = nullptr;
+      B200_CHECK(cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_rmsnorm_bwd_scratch));
+      g_scratch_ptr[dev] = p;
+    }
+    scratch = g_scratch_ptr[dev];
+  }
+  const int wpb = 4;
+  const size_t smem = static_cast<size_t>(wpb) * H * sizeof(float);
+  int rc = dispatch_nv(H, [&](auto nv) {
+    auto k = rmsnorm_bwd_kernel<decltype(nv)::value>;
+    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    k<<<grid, wpb * 32, smem, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
+                                        rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, T, H);
+    return 0;
+  });
+  if (rc) return rc;
+  colsum_partials_kernel<<<(H + 255) / 256, 256, 0, stream>>>(scratch, dw, grid, H, dw_accumulate);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
