@@ -179,8 +179,8 @@ class NativeRolloutEngine(InferenceEngine):
         max_blocks_per_seq = (ncfg.context_length + bs - 1) // bs
         nblocks = ncfg.num_kv_blocks or self._auto_num_blocks(mc, dtype, bs)
         self.kv_caches = [
-            (torch.zeros(nblocks, bs, mc.num_key_value_heads, mc.head_dim, dtype=dtype, device=self.device),
-             torch.zeros(nblocks, bs, mc.num_key_value_heads, mc.head_dim, dtype=dtype, device=self.device))
+            (torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device),
+             torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device))
             for _ in range(mc.num_hidden_layers)]
         self.sched = PagedScheduler(nblocks, bs, ncfg.max_num_seqs, ncfg.max_num_batched_tokens,
                                     max_blocks_per_seq)
@@ -469,8 +469,8 @@ class NativeRolloutEngine(InferenceEngine):
             dtype = next(self.model.parameters()).dtype
             nblocks = self.sched.stats()["free_blocks"]
             self.kv_caches = [
-                (torch.zeros(nblocks, bs, mc.num_key_value_heads, mc.head_dim, dtype=dtype, device=self.device),
-                 torch.zeros(nblocks, bs, mc.num_key_value_heads, mc.head_dim, dtype=dtype, device=self.device))
+                (torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device),
+                 torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device))
                 for _ in range(mc.num_hidden_layers)]
         self.continue_generation()
 

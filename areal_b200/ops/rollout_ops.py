@@ -13,14 +13,16 @@ from . import _lib
 
 def kv_cache_write(k, v, slot_mapping, k_cache, v_cache):
     """Writes ``k, v [T, Hkv, D]`` (token pitch may be larger) into the paged caches
-    ``[num_blocks, block_size, Hkv, D]`` at flat slots ``slot_mapping [T]`` (int64)."""
+    ``[num_blocks, Hkv, block_size, D]`` at flat slots ``slot_mapping [T]`` (int64,
+    ``block * block_size + offset``; negative slots are skipped)."""
     T, Hkv, D = k.shape
+    bs = k_cache.shape[2]
     if not _lib.use_cuda_kernels(k, v, k_cache):
         ok = slot_mapping >= 0
-        kc = k_cache.view(-1, Hkv, D)
-        vc = v_cache.view(-1, Hkv, D)
-        kc[slot_mapping[ok]] = k[ok]
-        vc[slot_mapping[ok]] = v[ok]
+        sm = slot_mapping[ok].long()
+        blk, off = sm // bs, sm % bs
+        k_cache[blk, :, off] = k[ok].to(k_cache.dtype)
+        v_cache[blk, :, off] = v[ok].to(v_cache.dtype)
         return
     lib = _lib.kernels()
     lib.b200_kv_cache_write.restype = ctypes.c_int
@@ -28,14 +30,14 @@ def kv_cache_write(k, v, slot_mapping, k_cache, v_cache):
                                  ctypes.c_longlong(v.stride(0)),
                                  _lib.ptr(slot_mapping.to(torch.int64).contiguous()),
                                  _lib.ptr(k_cache), _lib.ptr(v_cache), ctypes.c_int(T),
-                                 ctypes.c_int(Hkv), ctypes.c_int(D), _lib.stream_ptr())
+                                 ctypes.c_int(Hkv), ctypes.c_int(D), ctypes.c_int(bs), _lib.stream_ptr())
     _lib.check(rc, "b200_kv_cache_write")
     _lib.count_launch()
 
 
 def paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale=None):
     B, Hq, D = q.shape
-    nb, bs, Hkv, _ = k_cache.shape
+    nb, Hkv, bs, _ = k_cache.shape
     scale = scale or 1.0 / math.sqrt(D)
     g = Hq // Hkv
     out = torch.zeros((B, Hq, D), dtype=torch.float32, device=q.device)
@@ -44,8 +46,8 @@ def paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale=None):
         if L == 0:
             continue
         blocks = block_table[b, : (L + bs - 1) // bs].long()
-        k = k_cache[blocks].reshape(-1, Hkv, D)[:L].float().repeat_interleave(g, 1)
-        v = v_cache[blocks].reshape(-1, Hkv, D)[:L].float().repeat_interleave(g, 1)
+        k = k_cache[blocks].transpose(1, 2).reshape(-1, Hkv, D)[:L].float().repeat_interleave(g, 1)
+        v = v_cache[blocks].transpose(1, 2).reshape(-1, Hkv, D)[:L].float().repeat_interleave(g, 1)
         s = torch.einsum("hd,lhd->hl", q[b].float(), k) * scale
         out[b] = torch.einsum("hl,lhd->hd", s.softmax(-1), v)
     return out.to(q.dtype)
@@ -56,31 +58,34 @@ def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale=None, nsplit:
     """One query token per sequence attending to its paged cache (GQA)."""
     B, Hq, D = q.shape
     scale = scale or 1.0 / math.sqrt(D)
-    if not (_lib.use_cuda_kernels(q, k_cache) and q.dtype == torch.bfloat16 and D == 128):
+    nb, Hkv, bs, _ = k_cache.shape
+    if not (_lib.use_cuda_kernels(q, k_cache) and q.dtype == torch.bfloat16 and D == 128 and bs % 16 == 0):
         return paged_decode_ref(q, k_cache, v_cache, block_table, seq_lens, scale)
-    nb, bs, Hkv, _ = k_cache.shape
     if nsplit is None:
-        # enough CTAs to fill the GPU; long sequences get more splits
+        # enough CTAs to fill the GPU (two resident per SM); long sequences get more splits
         ctas = B * Hkv
         nsplit = 1
         if max_seq_len is None:
             max_seq_len = block_table.shape[1] * bs
-        while ctas * nsplit < 296 and nsplit < 32 and max_seq_len // (nsplit * 2) >= 128:
+        while ctas * nsplit < 592 and nsplit < 32 and max_seq_len // (nsplit * 2) >= 256:
             nsplit *= 2
     q = q if q.is_contiguous() else q.contiguous()
     out = torch.empty_like(q)
-    o_part = torch.empty((B, Hq, nsplit, D), dtype=torch.float32, device=q.device)
-    ml_part = torch.empty((B, Hq, nsplit, 2), dtype=torch.float32, device=q.device)
+    if nsplit > 1:
+        o_part = torch.empty((B, Hq, nsplit, D), dtype=torch.float32, device=q.device)
+        ml_part = torch.empty((B, Hq, nsplit, 2), dtype=torch.float32, device=q.device)
+    else:
+        o_part = ml_part = None
     lib = _lib.kernels()
     lib.b200_paged_decode.restype = ctypes.c_int
     rc = lib.b200_paged_decode(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache),
                                _lib.ptr(block_table), _lib.ptr(seq_lens), _lib.ptr(out),
                                _lib.ptr(o_part), _lib.ptr(ml_part), ctypes.c_int(B),
                                ctypes.c_int(Hq), ctypes.c_int(Hkv), ctypes.c_int(D),
-                               ctypes.c_int(bs), ctypes.c_int(block_table.shape[1]),
+                               ctypes.c_int(bs), ctypes.c_int(nb), ctypes.c_int(block_table.shape[1]),
                                ctypes.c_int(nsplit), ctypes.c_float(scale), _lib.stream_ptr())
     _lib.check(rc, "b200_paged_decode")
-    _lib.count_launch(2)
+    _lib.count_launch(2 if nsplit > 1 else 1)
     return out
 
 

@@ -85,13 +85,13 @@ def test_group_norm_and_gae():
 @pytest.mark.parametrize("Hq,Hkv", [(4, 2), (16, 8), (8, 1), (4, 4)])
 def test_paged_decode_and_kv_write(Hq, Hkv):
     torch.manual_seed(2)
-    D, bs, nb = 128, 16, 64
-    lens = [1, 17, 250, 33]
+    D, bs, nb = 128, 16, 96
+    lens = [1, 17, 250, 33, 400, 16]
     B = len(lens)
-    k_cache = torch.zeros(nb, bs, Hkv, D, device="cuda", dtype=torch.bfloat16)
+    k_cache = torch.zeros(nb, Hkv, bs, D, device="cuda", dtype=torch.bfloat16)
     v_cache = torch.zeros_like(k_cache)
     perm = torch.randperm(nb)
-    max_blocks = 20
+    max_blocks = 26
     bt = torch.zeros(B, max_blocks, dtype=torch.int32)
     used = 0
     slots, ks, vs = [], [], []
@@ -110,9 +110,17 @@ def test_paged_decode_and_kv_write(Hq, Hkv):
     q = torch.randn(B, Hq, D, device="cuda", dtype=torch.bfloat16)
     bt_d = bt.cuda()
     sl = torch.tensor(lens, device="cuda", dtype=torch.int32)
+    # the kernel's write lands where the reference layout expects it
+    kc_ref, vc_ref = torch.zeros_like(k_cache), torch.zeros_like(v_cache)
+    st = torch.tensor(slots, device="cuda")
+    kc_ref[st // bs, :, st % bs] = k
+    vc_ref[st // bs, :, st % bs] = v
+    assert torch.equal(k_cache, kc_ref) and torch.equal(v_cache, vc_ref)
+    from areal_b200.ops import _lib
     for nsplit in (1, 4):
         out = rollout_ops.paged_decode(q, k_cache, v_cache, bt_d, sl, nsplit=nsplit)
         ref = rollout_ops.paged_decode_ref(q, k_cache, v_cache, bt_d, sl)
+        assert _lib.read_status() == 0
         torch.testing.assert_close(out.float(), ref.float(), atol=2e-2, rtol=2e-2)
 
 
