@@ -447,7 +447,8 @@ class NativeRolloutConfig:
     max_num_batched_tokens: int = 16384
     context_length: int = 32768
     cuda_graph: bool = True
-    cuda_graph_batch_sizes: list[int] = field(default_factory=lambda: [1, 2, 4, 8, 16, 32, 64, 128, 256, 512])
+    cuda_graph_batch_sizes: list[int] = field(
+        default_factory=lambda: [1, 2, 4, 8, 16, 32, 48, 64, 96, 128, 160, 192, 224, 256, 320, 384, 448, 512, 640, 768, 1024])
     seed: int = 1
     host: str = "127.0.0.1"
     port: int = 0

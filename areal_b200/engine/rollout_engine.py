@@ -64,6 +64,7 @@ class PagedScheduler:
         self.h = ctypes.c_void_p(self.lib.b200_sched_create(num_blocks, block_size, max_num_seqs,
                                                             max_batched_tokens, max_blocks_per_seq))
         self.max_num_seqs, self.max_blocks_per_seq = max_num_seqs, max_blocks_per_seq
+        self.block_size = block_size
         cap = max(max_batched_tokens, max_num_seqs)
         self.seq_ids = np.zeros(max_num_seqs, dtype=np.int64)
         self.cu = np.zeros(max_num_seqs + 1, dtype=np.int32)
@@ -122,6 +123,94 @@ class PagedScheduler:
         if self.h:
             self.lib.b200_sched_destroy(self.h)
             self.h = None
+
+
+class _DecodeGraphs:
+    """CUDA graphs of one full decode step (28-odd layers, LM head, sampler) for a set of padded
+    batch sizes. All graphs read the same static input tensors and share one memory pool, so a
+    step is: copy the scheduler's plan into the static inputs, replay, read tokens + logprobs.
+    Weights (flat buffer) and KV pages keep their addresses, so weight updates need no re-capture."""
+
+    def __init__(self, engine: "NativeRolloutEngine", batch_sizes: list[int]):
+        self.e = engine
+        dev = engine.device
+        mb = engine.sched.max_blocks_per_seq
+        self.sizes = sorted({b for b in batch_sizes if b <= engine.ncfg.max_num_seqs} | {engine.ncfg.max_num_seqs})
+        maxb = self.sizes[-1]
+        self.ids = torch.zeros(maxb, dtype=torch.int64, device=dev)
+        self.pos = torch.zeros(maxb, dtype=torch.int64, device=dev)
+        self.slots = torch.full((maxb,), -1, dtype=torch.int64, device=dev)
+        self.seq_lens = torch.zeros(maxb, dtype=torch.int32, device=dev)
+        self.bt = torch.zeros((maxb, mb), dtype=torch.int32, device=dev)
+        self.temp = torch.ones(maxb, dtype=torch.float32, device=dev)
+        self.u = torch.zeros(maxb, dtype=torch.float32, device=dev)
+        pin = dict(pin_memory=True)
+        self.h_ids = torch.zeros(maxb, dtype=torch.int64, **pin)
+        self.h_pos = torch.zeros(maxb, dtype=torch.int64, **pin)
+        self.h_slots = torch.zeros(maxb, dtype=torch.int64, **pin)
+        self.h_lens = torch.zeros(maxb, dtype=torch.int32, **pin)
+        self.h_bt = torch.zeros((maxb, mb), dtype=torch.int32, **pin)
+        self.h_temp = torch.ones(maxb, dtype=torch.float32, **pin)
+        self.h_tok = torch.zeros(maxb, dtype=torch.int32, **pin)
+        self.h_lp = torch.zeros(maxb, dtype=torch.float32, **pin)
+        self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor, torch.Tensor]] = {}
+        self.pool = None
+        self.prev_n = 0
+
+    def _forward(self, b: int):
+        e = self.e
+        hidden = e.model.decode(self.ids[:b], self.pos[:b], e.kv_caches, self.bt[:b], self.seq_lens[:b],
+                                self.slots[:b], max_seq_len=e.ncfg.context_length)
+        logits = e.model.logits(hidden, out_dtype=torch.float32)
+        return sample(logits, self.temp[:b], None, None, self.u[:b])
+
+    def capture_all(self, stream):
+        with torch.cuda.stream(stream), torch.no_grad():
+            for b in reversed(self.sizes):  # largest first: the shared pool is sized once
+                self._forward(b)  # warm-up outside capture (kernel attributes, workspace)
+                torch.cuda.synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g, pool=self.pool, stream=stream, capture_error_mode="thread_local"):
+                    toks, lps = self._forward(b)
+                if self.pool is None:
+                    self.pool = g.pool()
+                self.graphs[b] = (g, toks, lps)
+            torch.cuda.synchronize()
+
+    def bucket(self, n: int) -> int | None:
+        for b in self.sizes:
+            if b >= n:
+                return b if b in self.graphs else None
+        return None
+
+    def run(self, n: int, b: int, sched: "PagedScheduler", temps: list[float], rng) -> tuple[np.ndarray, np.ndarray]:
+        nbw = max((int(sched.hdr.max_seq_len) + sched.block_size - 1) // sched.block_size, 1)
+        self.h_ids[:n] = torch.from_numpy(sched.tokens[:n])
+        self.h_pos[:n] = torch.from_numpy(sched.positions[:n])
+        self.h_slots[:n] = torch.from_numpy(sched.slots[:n])
+        self.h_lens[:n] = torch.from_numpy(sched.seq_lens[:n])
+        self.h_bt[:n, :nbw] = torch.from_numpy(sched.block_table[: n * sched.max_blocks_per_seq]).view(n, -1)[:, :nbw]
+        self.h_temp[:n] = torch.tensor(temps, dtype=torch.float32)
+        stale = max(self.prev_n, n)  # rows used by the previous step but not by this one become padding
+        if stale > n:
+            self.h_lens[n:stale] = 0
+            self.h_slots[n:stale] = -1
+        m = stale
+        self.ids[:n].copy_(self.h_ids[:n], non_blocking=True)
+        self.pos[:n].copy_(self.h_pos[:n], non_blocking=True)
+        self.slots[:m].copy_(self.h_slots[:m], non_blocking=True)
+        self.seq_lens[:m].copy_(self.h_lens[:m], non_blocking=True)
+        self.bt[:n].copy_(self.h_bt[:n], non_blocking=True)
+        self.temp[:n].copy_(self.h_temp[:n], non_blocking=True)
+        self.u[:b].uniform_(generator=rng)
+        self.prev_n = n
+        g, toks, lps = self.graphs[b]
+        g.replay()
+        self.h_tok[:n].copy_(toks[:n], non_blocking=True)
+        self.h_lp[:n].copy_(lps[:n], non_blocking=True)
+        torch.cuda.current_stream().synchronize()
+        _lib.count_launch(self.e.launches_per_decode)
+        return self.h_tok[:n].numpy(), self.h_lp[:n].numpy()
 
 
 class NativeRolloutEngine(InferenceEngine):
@@ -185,6 +274,10 @@ class NativeRolloutEngine(InferenceEngine):
         self.sched = PagedScheduler(nblocks, bs, ncfg.max_num_seqs, ncfg.max_num_batched_tokens,
                                     max_blocks_per_seq)
         self._rng = torch.Generator(device=self.device).manual_seed(ncfg.seed)
+        self._graphs = None
+        self.launches_per_decode = 0
+        if self.device.type == "cuda" and ncfg.cuda_graph and _lib.use_cuda_kernels(next(self.model.parameters())):
+            self._capture_graphs()
         self._thread = threading.Thread(target=self._loop, name="rollout-engine", daemon=True)
         self._thread.start()
         from ..infra.workflow_executor import WorkflowExecutor
@@ -193,6 +286,20 @@ class NativeRolloutEngine(InferenceEngine):
         self._executor.initialize(train_data_parallel_size=train_data_parallel_size)
         logger.info(f"rollout engine ready on {self.device}: {nblocks} KV pages of {bs} tokens")
         return self
+
+    def _capture_graphs(self):
+        t0 = time.perf_counter()
+        if getattr(self, "_graph_stream", None) is None:
+            self._graph_stream = torch.cuda.Stream(self.device)
+        graphs = _DecodeGraphs(self, list(self.ncfg.cuda_graph_batch_sizes))
+        before = _lib.launch_count()
+        with torch.cuda.stream(self._graph_stream), torch.no_grad():
+            graphs._forward(graphs.sizes[0])
+        self.launches_per_decode = _lib.launch_count() - before
+        graphs.capture_all(self._graph_stream)
+        self._graphs = graphs
+        logger.info(f"captured decode graphs for batch sizes {graphs.sizes} in {time.perf_counter() - t0:.1f}s "
+                    f"({self.launches_per_decode} kernels per step)")
 
     def _auto_num_blocks(self, mc: ModelConfig, dtype, bs: int) -> int:
         per_block = 2 * mc.num_hidden_layers * bs * mc.num_key_value_heads * mc.head_dim * \
@@ -222,7 +329,9 @@ class NativeRolloutEngine(InferenceEngine):
     def _loop(self):
         if self.device.type == "cuda":
             torch.cuda.set_device(self.device)
-        stream = torch.cuda.Stream(self.device) if self.device.type == "cuda" else None
+        stream = None
+        if self.device.type == "cuda":
+            stream = self._graph_stream if self._graphs is not None else torch.cuda.Stream(self.device)
         while not self._stop.is_set():
             try:
                 if self._paused.is_set():
@@ -259,6 +368,18 @@ class NativeRolloutEngine(InferenceEngine):
             return False
         n, T = s.hdr.n_seqs, s.hdr.n_tokens
         dev = self.device
+        if kind != 1 and self._graphs is not None:
+            seq_ids = s.seq_ids[:n].tolist()
+            with self._lock:
+                pr = [self._params.get(r, (1.0, 0, 1.0)) for r in seq_ids]
+            b = self._graphs.bucket(n)
+            if b is not None and not any(p[1] > 0 or p[2] < 1.0 for p in pr):
+                toks, lps = self._graphs.run(n, b, s, [p[0] for p in pr], self._rng)
+                s.commit(toks, lps)
+                self._gen_tokens += n
+                self._steps += 1
+                self._deliver()
+                return True
         ids = torch.from_numpy(s.tokens[:T].copy()).to(dev, non_blocking=True)
         pos = torch.from_numpy(s.positions[:T].copy()).to(dev, non_blocking=True)
         slots = torch.from_numpy(s.slots[:T].copy()).to(dev, non_blocking=True)
@@ -459,6 +580,7 @@ class NativeRolloutEngine(InferenceEngine):
     def offload(self):
         """Releases the KV cache (colocated time-sharing with the trainer)."""
         self.pause_generation()
+        self._graphs = None  # the captured graphs point into the cache that is being released
         self.kv_caches = None
         if self.device.type == "cuda":
             torch.cuda.empty_cache()
@@ -472,6 +594,8 @@ class NativeRolloutEngine(InferenceEngine):
                 (torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device),
                  torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device))
                 for _ in range(mc.num_hidden_layers)]
+            if self.device.type == "cuda" and self.ncfg.cuda_graph and _lib.use_cuda_kernels(next(self.model.parameters())):
+                self._capture_graphs()
         self.continue_generation()
 
     def export_stats(self) -> dict[str, float]:
