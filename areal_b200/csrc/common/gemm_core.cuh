@@ -22,6 +22,12 @@
 //     __device__ void chunk(State&, int row, int col0, const float (&v)[32]) const;
 //     __device__ void end(State&, int m_blk, int n_blk, int row) const;
 //   };
+// Optional members for grouped (per-expert) problems; a policy without them gets the defaults:
+//     int b_offset(int m_blk)  – added to B's row coordinate (K-major B: rows of the expert's weight
+//                                inside a stacked [E*N, K] matrix; MN-major B: its reduction rows)   [0]
+//     int a_m0(int m_blk)      – A's M coordinate of the tile                              [m_blk * 128]
+//     int k_begin(int m_blk)   – first reduction element of the tile                                [0]
+//     int k_blocks(int m_blk)  – number of 64-wide reduction blocks (0 = the tile is all zeros) [K / 64]
 #pragma once
 #include "ptx.cuh"
 
@@ -60,6 +66,16 @@ __device__ __forceinline__ bool default_tile(int cta, int ncta, int iter, int ti
   n_blk = r / gsize;
   return true;
 }
+
+// Detection of the optional policy members (the int overload wins when the member exists).
+template <class E> __device__ __forceinline__ auto epi_b_offset(const E& e, int m, int) -> decltype(e.b_offset(m)) { return e.b_offset(m); }
+template <class E> __device__ __forceinline__ int epi_b_offset(const E&, int, long) { return 0; }
+template <class E> __device__ __forceinline__ auto epi_a_m0(const E& e, int m, int) -> decltype(e.a_m0(m)) { return e.a_m0(m); }
+template <class E> __device__ __forceinline__ int epi_a_m0(const E&, int m, long) { return m * kBM; }
+template <class E> __device__ __forceinline__ auto epi_k_begin(const E& e, int m, int) -> decltype(e.k_begin(m)) { return e.k_begin(m); }
+template <class E> __device__ __forceinline__ int epi_k_begin(const E&, int, long) { return 0; }
+template <class E> __device__ __forceinline__ auto epi_k_blocks(const E& e, int m, int dflt, int) -> decltype(e.k_blocks(m)) { return e.k_blocks(m); }
+template <class E> __device__ __forceinline__ int epi_k_blocks(const E&, int, int dflt, long) { return dflt; }
 
 template <int BN, bool A_MN, bool B_MN, class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
@@ -123,7 +139,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           ok = false;
           break;
         }
-        for (int kb = 0; kb < kblocks; ++kb) {
+        const int kbn = epi_k_blocks(epi, m_blk, kblocks, 0);
+        const int k0 = epi_k_begin(epi, m_blk, 0);
+        const int a_m0 = epi_a_m0(epi, m_blk, 0);
+        const int b_off = epi_b_offset(epi, m_blk, 0);
+        for (int kb = 0; kb < kbn; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
             break;
@@ -134,16 +154,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
           if (A_MN) {
 #pragma unroll
             for (int j = 0; j < kBM / 64; ++j)
-              tma_load_2d(a_dst + j * 8192, &tmA, &full[stage], m_blk * kBM + j * 64, kb * kBK);
+              tma_load_2d(a_dst + j * 8192, &tmA, &full[stage], a_m0 + j * 64, k0 + kb * kBK);
           } else {
-            tma_load_2d(a_dst, &tmA, &full[stage], kb * kBK, m_blk * kBM);
+            tma_load_2d(a_dst, &tmA, &full[stage], k0 + kb * kBK, a_m0);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
-              tma_load_2d(b_dst + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, kb * kBK);
+              tma_load_2d(b_dst + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, k0 + kb * kBK + b_off);
           } else {
-            tma_load_2d(b_dst, &tmB, &full[stage], kb * kBK, n_blk * BN);
+            tma_load_2d(b_dst, &tmB, &full[stage], k0 + kb * kBK, n_blk * BN + b_off);
           }
           if (++stage == STAGES) {
             stage = 0;
@@ -177,7 +197,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         }
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < kblocks; ++kb) {
+        const int kbn = epi_k_blocks(epi, m_blk, kblocks, 0);
+        for (int kb = 0; kb < kbn; ++kb) {
           if (!mbar_wait(&full[stage], phase, abort_flag)) {
             ok = false;
             break;
@@ -227,6 +248,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
       tc_fence_after();
       const int row = m_blk * kBM + quarter * 32 + lane;
       const uint32_t t_row = tmem_base + acc * BN + (static_cast<uint32_t>(quarter * 32) << 16);
+      const bool empty_tile = epi_k_blocks(epi, m_blk, kblocks, 0) == 0;  // nothing was accumulated
       epi.begin(st, m_blk, n_blk, row);
 #pragma unroll 1
       for (int c = 0; c < BN / 32; ++c) {
@@ -235,7 +257,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         tmem_ld_wait();
         float v[32];
 #pragma unroll
-        for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+        for (int i = 0; i < 32; ++i) v[i] = empty_tile ? 0.f : __uint_as_float(r[i]);
         epi.chunk(st, row, n_blk * BN + c * 32, v);
       }
       tc_fence_before();

@@ -130,6 +130,91 @@ static int launch(const void* A, const void* B, void* C, const void* bias, int M
   return 0;
 }
 
+
+// ---------------------------------------------------------------- grouped (per-expert) GEMMs --
+// Rows live in the padded, expert-sorted layout produced by the MoE sort: tile vm (128 rows)
+// belongs to expert tile_expert[vm]; *num_vm tiles are in use (device-side value, so no host
+// sync); weights are stacked as [E * rows_per_expert, cols].
+struct GroupedEpi {
+  StoreEpi st;
+  const int* tile_expert;
+  const int* num_vm;
+  int b_rows_per_expert;  // rows of the stacked B that belong to one expert
+  using State = StoreEpi::State;
+
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int, int tiles_n, int& m_blk, int& n_blk) const {
+    const long long t = static_cast<long long>(it) * ncta + cta;
+    if (t >= static_cast<long long>(*num_vm) * tiles_n) return false;
+    m_blk = static_cast<int>(t / tiles_n);
+    n_blk = static_cast<int>(t % tiles_n);
+    return true;
+  }
+  __device__ __forceinline__ int b_offset(int m_blk) const { return tile_expert[m_blk] * b_rows_per_expert; }
+  __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ void begin(State&, int, int, int) const {}
+  __device__ __forceinline__ void end(State&, int, int, int) const {}
+  __device__ __forceinline__ void chunk(State& s, int row, int col0, const float (&v)[32]) const {
+    st.chunk(s, row, col0, v);
+  }
+};
+
+// dW[e] = dy_e^T x_e: the M dimension runs over the stacked weight rows [E * N], the reduction over
+// the (padded, zero-filled) rows of expert e = (m_blk * 128) / N.
+struct GroupedWgradEpi {
+  StoreEpi st;
+  const int* prow0;  // [E + 1] first padded row of every expert
+  int n_per_expert;
+  using State = StoreEpi::State;
+
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m, int tiles_n, int& m_blk,
+                                       int& n_blk) const {
+    return default_tile(cta, ncta, it, tiles_m, tiles_n, m_blk, n_blk);
+  }
+  __device__ __forceinline__ int expert(int m_blk) const { return (m_blk * kBM) / n_per_expert; }
+  __device__ __forceinline__ int a_m0(int m_blk) const { return (m_blk * kBM) % n_per_expert; }
+  __device__ __forceinline__ int k_begin(int m_blk) const { return prow0[expert(m_blk)]; }
+  __device__ __forceinline__ int k_blocks(int m_blk) const {
+    const int e = expert(m_blk);
+    return (prow0[e + 1] - prow0[e]) / kBK;
+  }
+  __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ void begin(State&, int, int, int) const {}
+  __device__ __forceinline__ void end(State&, int, int, int) const {}
+  __device__ __forceinline__ void chunk(State& s, int row, int col0, const float (&v)[32]) const {
+    st.chunk(s, row, col0, v);
+  }
+};
+
+template <bool B_MN>
+static int launch_grouped(const void* A, const void* B, void* C, const int* tile_expert, const int* num_vm,
+                          int max_rows, int E, int N, int K, cudaStream_t stream) {
+  constexpr int BN = 128;
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, max_rows, K, (long long)K * 2, kBM, 64);
+  if (rc) return rc;
+  if (B_MN)  // stacked [E*K, N], N contiguous
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)E * K, N, (long long)N * 2, 64, 64);
+  else       // stacked [E*N, K], K contiguous
+    rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, (long long)E * N, K, (long long)K * 2, BN, 64);
+  if (rc) return rc;
+  GroupedEpi epi{StoreEpi{C, nullptr, N, max_rows, N, 0, 0}, tile_expert, num_vm, B_MN ? K : N};
+  auto kern = gemm_tcgen05_kernel<BN, false, B_MN, GroupedEpi>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  const long long tiles = static_cast<long long>((max_rows + kBM - 1) / kBM) * ((N + BN - 1) / BN);
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  if (grid <= 0) return 0;
+  int* status = device_status_word();
+  if (!status) return -3;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, max_rows, N, K, epi, status);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
 }  // namespace b200
 
 extern "C" {
@@ -162,6 +247,50 @@ int b200_gemm_bf16(const void* A, const void* B, void* C, const void* bias, int 
   }
   DISPATCH(256)
 #undef DISPATCH
+}
+
+// Grouped forward / dgrad over the padded expert-sorted rows:
+//   b_mn == 0:  C[r, :N] = A[r, :K] . W[e(r)]^T   with W stacked [E, N, K]
+//   b_mn == 1:  C[r, :N] = A[r, :K] . W[e(r)]     with W stacked [E, K, N]   (K % 64 == 0)
+// A is [max_rows, K] and C [max_rows, N], both contiguous bf16; N % 8 == 0, K % 8 == 0.
+int b200_gemm_grouped(const void* A, const void* B, void* C, const int* tile_expert, const int* num_vm,
+                      int max_rows, int E, int N, int K, int b_mn, cudaStream_t stream) {
+  using namespace b200;
+  if (max_rows <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N & 7) || (K & 7) || (b_mn && (K % 64))) return -100;
+  return b_mn ? launch_grouped<true>(A, B, C, tile_expert, num_vm, max_rows, E, N, K, stream)
+              : launch_grouped<false>(A, B, C, tile_expert, num_vm, max_rows, E, N, K, stream);
+}
+
+// Grouped wgrad: dW[e] (+)= dY_e^T X_e with dY [max_rows, N], X [max_rows, K] in the padded layout
+// (padding rows zero) and dW stacked [E, N, K] (fp32 when out_fp32). N % 128 == 0, K % 8 == 0.
+int b200_gemm_grouped_wgrad(const void* dY, const void* X, void* dW, const int* prow0, int max_rows, int E, int N,
+                            int K, int out_fp32, int accumulate, cudaStream_t stream) {
+  using namespace b200;
+  if (E <= 0 || N <= 0 || K <= 0) return 0;
+  if ((N % 128) || (K & 7)) return -100;
+  constexpr int BN = 128;
+  using Cfg = GemmCfg<BN>;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, dY, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, max_rows, N, (long long)N * 2, 64, 64);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, X, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, max_rows, K, (long long)K * 2, 64, 64);
+  if (rc) return rc;
+  const int M = E * N;
+  GroupedWgradEpi epi{StoreEpi{dW, nullptr, K, M, K, out_fp32, accumulate}, prow0, N};
+  auto kern = gemm_tcgen05_kernel<BN, true, true, GroupedWgradEpi>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  const long long tiles = static_cast<long long>(M / kBM) * ((K + BN - 1) / BN);
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  int* status = device_status_word();
+  if (!status) return -3;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, M, K, max_rows, epi, status);
+  B200_CHECK(cudaGetLastError());
+  return 0;
 }
 
 }  // extern "C"

@@ -37,7 +37,11 @@ _ALIGN = 64  # elements: 128 bytes in bf16, 256 in fp32
 
 
 class FlatParams:
-    def __init__(self, model: torch.nn.Module, dp_group: dist.ProcessGroup | None, with_grads: bool = True):
+    def __init__(self, model: torch.nn.Module, dp_group: dist.ProcessGroup | None, with_grads: bool = True,
+                 replicated_first=None):
+        """``replicated_first(name) -> bool`` marks parameters that are replicated over a
+        tensor-parallel group; they are laid out first, so ``flat[:rep_numel]`` is one contiguous
+        region (their gradients need one extra all-reduce over that group)."""
         params = [p for p in model.parameters()]
         assert params, "model has no parameters"
         self.model = model
@@ -50,7 +54,13 @@ class FlatParams:
         self.entries: list[tuple[str, torch.nn.Parameter, int, int]] = []
         off = 0
         seen: dict[int, int] = {}
-        for name, p in model.named_parameters():
+        named = list(model.named_parameters())
+        self.rep_numel = 0
+        if replicated_first is not None:
+            named = [x for x in named if replicated_first(x[0])] + [x for x in named if not replicated_first(x[0])]
+        for name, p in named:
+            if replicated_first is not None and not replicated_first(name) and self.rep_numel == 0:
+                self.rep_numel = off
             if id(p) in seen:
                 continue
             seen[id(p)] = off
@@ -117,9 +127,18 @@ def lr_at(step: int, total_steps: int, cfg: OptimizerConfig) -> float:
 class ShardedAdamW:
     """AdamW over the rank's shard of the flat buffers (fp32 master, m, v)."""
 
-    def __init__(self, flat: FlatParams, cfg: OptimizerConfig, total_steps: int = 1):
+    def __init__(self, flat: FlatParams, cfg: OptimizerConfig, total_steps: int = 1, tp_group=None,
+                 tp_full_grad: tuple[str, ...] = ("score",)):
+        """``tp_group``: tensor-parallel group over which the gradients of the replicated region
+        (``flat.rep_numel``) are summed before the data-parallel reduction; parameters named in
+        ``tp_full_grad`` already hold the full gradient on every tp rank."""
         self.flat = flat
         self.cfg = cfg
+        self.tp_group = tp_group
+        self.tp_size = dist.get_world_size(tp_group) if (tp_group is not None and dist.is_initialized()) else 1
+        self.tp_full_grad = tp_full_grad
+        self.norm_groups: list = []      # further groups that hold disjoint parameters (pipeline stages)
+        self.pre_step_hooks: list = []   # run after the autograd gradients were collected
         self.total_steps = total_steps
         self.step_count = 0  # optimizer steps taken (bias correction)
         self.sched_step = 0  # scheduler position
@@ -147,6 +166,13 @@ class ShardedAdamW:
 
     def step(self, grad_scale: float = 1.0) -> dict[str, float]:
         self.flat.collect_autograd_grads()
+        for hook in self.pre_step_hooks:
+            hook()
+        if self.tp_size > 1 and self.flat.rep_numel > 0:
+            for name, p, _, _ in self.flat.entries:
+                if name.endswith(self.tp_full_grad):
+                    p.main_grad.div_(self.tp_size)
+            dist.all_reduce(self.flat.main_grad[:self.flat.rep_numel], group=self.tp_group)
         out = self._step_cuda(grad_scale) if self.flat.cuda else self._step_torch(grad_scale)
         self.flat.zero_grad()
         return out
@@ -165,8 +191,13 @@ class ShardedAdamW:
                                            _lib.ptr(self.shard_grad), _lib.ptr(self._norm),
                                            _lib.stream_ptr())
         _lib.check(rc, "b200_reduce_scatter_sumsq")
+        self._dedup_replicated_norm(self._norm)
         if world > 1:
             dist.all_reduce(self._norm, group=f.dp_group)
+        if self.tp_size > 1:
+            dist.all_reduce(self._norm, group=self.tp_group)
+        for g in self.norm_groups:
+            dist.all_reduce(self._norm, group=g)
         t = self.step_count + 1
         lr = self.lr
         self._skipped.zero_()
@@ -189,6 +220,17 @@ class ShardedAdamW:
         return dict(grad_norm=math.sqrt(vals[0]) if vals[0] >= 0 else float("nan"),
                     update_successful=float(ok), lr=lr)
 
+    def _dedup_replicated_norm(self, nsq: torch.Tensor):
+        """The squared norm is summed over the tp group afterwards; entries of the replicated
+        region would count ``tp`` times, so keep only ``1/tp`` of their share here."""
+        if self.tp_size <= 1:
+            return
+        f = self.flat
+        a, b = f.shard_offset, min(f.shard_offset + f.shard_numel, f.rep_numel)
+        if b > a:
+            rep = (self.shard_grad[:b - a].double() ** 2).sum().float()
+            nsq.sub_(rep * (self.tp_size - 1) / self.tp_size)
+
     # --------------------------------------------------------------- torch
     def _step_torch(self, grad_scale: float) -> dict[str, float]:
         f, cfg = self.flat, self.cfg
@@ -198,8 +240,13 @@ class ShardedAdamW:
         o, n = f.shard_offset, f.shard_numel
         self.shard_grad.copy_(g[o:o + n] * grad_scale)
         nsq = (self.shard_grad.double() ** 2).sum().float().reshape(1)
+        self._dedup_replicated_norm(nsq)
         if f.dp_world > 1:
             dist.all_reduce(nsq, group=f.dp_group)
+        if self.tp_size > 1:
+            dist.all_reduce(nsq, group=self.tp_group)
+        for g in self.norm_groups:
+            dist.all_reduce(nsq, group=g)
         norm = float(nsq.sqrt())
         lr = self.lr
         if not math.isfinite(norm):

@@ -290,7 +290,7 @@ class NativeRolloutEngine(InferenceEngine):
     def _capture_graphs(self):
         t0 = time.perf_counter()
         if getattr(self, "_graph_stream", None) is None:
-            self._graph_stream = torch.cuda.Stream(self.device)
+            self._graph_stream = torch.cuda.Stream(self.device, priority=-1)
         graphs = _DecodeGraphs(self, list(self.ncfg.cuda_graph_batch_sizes))
         before = _lib.launch_count()
         with torch.cuda.stream(self._graph_stream), torch.no_grad():
@@ -331,7 +331,7 @@ class NativeRolloutEngine(InferenceEngine):
             torch.cuda.set_device(self.device)
         stream = None
         if self.device.type == "cuda":
-            stream = self._graph_stream if self._graphs is not None else torch.cuda.Stream(self.device)
+            stream = self._graph_stream if self._graphs is not None else torch.cuda.Stream(self.device, priority=-1)
         while not self._stop.is_set():
             try:
                 if self._paused.is_set():

@@ -101,7 +101,31 @@ class B200TrainEngine(TrainEngine):
         if parallel_strategy is None and self.config.backend not in (None, "", "???"):
             parallel_strategy = ModelAllocation.from_str(self.config.backend).parallel
         self.parallel = parallel_strategy or ParallelStrategy()
-        if dist.is_initialized():
+        self.mesh = None
+        self.pctx = None
+        ps = self.parallel
+        model_parallel = ps.tp_size * ps.cp_size * ps.pp_size > 1
+        if model_parallel:
+            assert dist.is_initialized(), "tensor / sequence / pipeline parallelism needs torch.distributed"
+            from ..parallel.context import build_mesh
+
+            self.rank = dist.get_rank()
+            world = dist.get_world_size()
+            ranks = list(range(world)) if ranks is None else list(ranks)
+            self.train_ranks = ranks
+            dp = len(ranks) // (ps.tp_size * ps.cp_size * ps.pp_size)
+            # context_parallel_size is Ulysses sequence parallelism for this engine family
+            self.mesh = build_mesh(ranks, dp=dp, sp=ps.cp_size, tp=ps.tp_size, pp=ps.pp_size)
+            self.pctx = self.mesh.ctx
+            # parameters are sharded (ZeRO) over dp x sp: those ranks hold the same weights
+            self._dp_group = self.mesh.shard_group
+            self._cpu_group = self.mesh.cpu_shard_group
+            self._data_group = self.mesh.dp_group
+            self.world_size = self.mesh.shard_size
+            self.dp_rank = self.mesh.shard_rank
+            self._data_rank, self._data_size = self.mesh.dp_rank, self.mesh.dp_size
+            self._mp_group = self.mesh.mp_group
+        elif dist.is_initialized():
             self.rank = dist.get_rank()
             world = dist.get_world_size()
             ranks = list(range(world)) if ranks is None else list(ranks)
@@ -124,29 +148,40 @@ class B200TrainEngine(TrainEngine):
 
     @property
     def data_parallel_group(self):
-        return self._dp_group
+        """Ranks that receive DIFFERENT data. (Parameters are sharded over a possibly larger
+        group that also spans the Ulysses ranks: ``self._dp_group``.)"""
+        return self._data_group if self.mesh is not None else self._dp_group
 
     @property
     def data_parallel_rank(self) -> int:
-        return self.dp_rank
+        return self._data_rank if self.mesh is not None else self.dp_rank
 
     @property
     def data_parallel_world_size(self) -> int:
-        return self.world_size
+        return self._data_size if self.mesh is not None else self.world_size
 
     @property
     def context_and_model_parallel_group(self):
-        return None
+        """Ranks that must be fed the same batch (tp x sp x pp of one data-parallel replica)."""
+        return getattr(self, "_mp_group", None)
 
     @property
     def cpu_group(self):
         return self._cpu_group
 
     def is_data_parallel_head(self) -> bool:
-        return True
+        if self.mesh is None:
+            return True
+        c = self.pctx
+        return c.tp_rank == 0 and c.sp_rank == 0 and self.mesh.pp_rank == 0
 
     def current_data_parallel_head(self) -> int:
-        return self.rank
+        if self.mesh is None:
+            return self.rank
+        ps = self.parallel
+        i = self.train_ranks.index(self.rank)
+        mp = ps.tp_size * ps.cp_size
+        return self.train_ranks[(i % (mp * self._data_size)) // mp * mp]
 
     # ----------------------------------------------------------------- init
     def initialize(self, addr: str | None = None, ft_spec: FinetuneSpec | None = None, *args, **kwargs):
@@ -157,21 +192,44 @@ class B200TrainEngine(TrainEngine):
         dtype = torch.float32 if self.device.type == "cpu" else getattr(torch, cfg.dtype)
         t0 = time.perf_counter()
         seed = kwargs.get("seed", 0)
+        pctx = self.pctx
+        if pctx is not None:
+            mc = self.model_config
+            widest = max(mc.q_size + 2 * mc.kv_size, 2 * mc.intermediate_size) // max(pctx.tp_size, 1)
+            max_tok = int(self.config.mb_spec.max_tokens_per_mb or 32768) + 1024
+            pctx.enable_fused(max_tok, mc.hidden_size, widest, self.device)
         self.model = build_model(self.model_config, dtype=dtype, device=self.device,
-                                 seed=seed if (cfg.init_from_scratch or not cfg.path) else None)
+                                 seed=seed if (cfg.init_from_scratch or not cfg.path) else None, pctx=pctx)
         if cfg.path and not cfg.init_from_scratch:
             from ..utils.hf_io import load_hf_weights
 
             load_hf_weights(self.model, cfg.path)
-        self.flat = FlatParams(self.model, self._dp_group, with_grads=self.optimizer_config is not None)
+        tp = pctx.tp_size if pctx is not None else 1
+        rep_first = None
+        if tp > 1:
+            from ..parallel.tensor_parallel import is_tp_replicated
+
+            rep_first = is_tp_replicated
+        self.flat = FlatParams(self.model, self._dp_group, with_grads=self.optimizer_config is not None,
+                               replicated_first=rep_first)
         if self.optimizer_config is not None:
             total = ft_spec.total_train_steps if ft_spec is not None else 1
-            self.optimizer = ShardedAdamW(self.flat, self.optimizer_config, total_steps=total)
+            self.optimizer = ShardedAdamW(self.flat, self.optimizer_config, total_steps=total,
+                                          tp_group=pctx.tp_group if tp > 1 else None)
+            if pctx is not None and pctx.pp_size > 1:
+                self.optimizer.norm_groups.append(pctx.pp_group)
+                if self.model_config.tie_word_embeddings and not self.is_critic and self.model.embed is not None:
+                    self.optimizer.pre_step_hooks.append(self._sum_tied_embedding_grads)
         self.ft_spec = ft_spec
         self._initialized = True
         logger.info(f"engine initialised: {self.model_config.num_params() / 1e9:.2f}B params, "
                     f"dp={self.world_size}, device={self.device}, {time.perf_counter() - t0:.1f}s")
         return self
+
+    def _sum_tied_embedding_grads(self):
+        """First and last pipeline stage each hold a copy of the tied embedding / head matrix; both
+        apply the sum of the two gradients so the copies stay identical."""
+        dist.all_reduce(self.model.embed.main_grad, group=self.pctx.pp_tie_group)
 
     def destroy(self):
         self.model = None
@@ -220,16 +278,126 @@ class B200TrainEngine(TrainEngine):
         out["cu_seqlens"] = meta.cu_seqlens
         return out, meta
 
-    def _forward_mb(self, mb: dict[str, Any], meta: VarlenMeta, need_entropy: bool = True):
-        """Returns ``(logprobs [T], entropy [T])`` in next-token form, or values for a critic."""
+    def _forward_mb(self, mb: dict[str, Any], meta: VarlenMeta, need_entropy: bool = True, stage_input=None):
+        """Returns ``(logprobs [T], entropy [T])`` in next-token form, or values for a critic. A
+        pipeline stage other than the last returns ``((x, res), None)`` instead."""
         ids = mb["input_ids"]
-        hidden = self.model(ids, mb["position_ids"], meta)
-        if self.is_critic:
-            return self.model.values(hidden), None
+        pctx = self.pctx
+        if pctx is None or (pctx.seq_shards == 1 and pctx.pp_size == 1):
+            hidden = self.model(ids, mb["position_ids"], meta)
+            if self.is_critic:
+                return self.model.values(hidden), None
+            labels = torch.roll(ids, shifts=-1, dims=0)
+            logp, ent = lm_head_logprobs(hidden, self.model.output_weight(), labels,
+                                         self.config.temperature)
+            return logp, ent
+        return self._forward_mb_parallel(mb, meta, stage_input)
+
+    def _forward_mb_parallel(self, mb: dict[str, Any], meta: VarlenMeta, stage_input=None):
+        """Tensor- and/or Ulysses-parallel forward. Every rank of the model-parallel group holds the
+        same micro-batch; the packed tokens are padded to a multiple of the shard count, each
+        Ulysses rank takes its contiguous slice (tensor parallelism shards further inside the
+        model) and the per-token outputs are re-assembled so the loss sees the whole micro-batch."""
+        from ..parallel.tensor_parallel import gather_seq_replicated
+
+        pctx = self.pctx
+        ids, pos = mb["input_ids"], mb["position_ids"]
+        T = ids.shape[0]
+        align = pctx.seq_shards * (128 if ids.is_cuda else 1)
+        Tp = (T + align - 1) // align * align
         labels = torch.roll(ids, shifts=-1, dims=0)
-        logp, ent = lm_head_logprobs(hidden, self.model.output_weight(), labels,
-                                     self.config.temperature)
-        return logp, ent
+        if Tp != T:
+            pad = Tp - T
+            ids = torch.cat([ids, ids.new_zeros(pad)])
+            pos = torch.cat([pos, torch.arange(pad, device=pos.device, dtype=pos.dtype)])
+            labels = torch.cat([labels, labels.new_zeros(pad)])
+            meta = VarlenMeta(list(meta.cu_cpu.tolist()) + [Tp], self.device)  # the padding is one more sequence
+        S, r = pctx.sp_size, pctx.sp_rank
+        n = Tp // S
+        sl = slice(r * n, (r + 1) * n)
+        hidden = self.model(ids[sl], pos[sl], meta, stage_input=stage_input)  # [n, H]: this Ulysses shard
+        if pctx.pp_size > 1 and not pctx.is_last_stage:
+            return hidden, None  # (x, res) for the next stage
+        if self.is_critic:
+            out, ent = self.model.values(hidden), None
+        else:
+            tp = pctx.tp_size
+            vloc = self.model.output_weight().shape[0]
+            out, ent = lm_head_logprobs(hidden, self.model.output_weight(), labels[sl], self.config.temperature,
+                                        tp_group=pctx.tp_group if tp > 1 else None,
+                                        vocab_start=pctx.tp_rank * vloc if tp > 1 else 0)
+        if S > 1:
+            out = gather_seq_replicated(out, pctx.sp_fused)
+            ent = gather_seq_replicated(ent, pctx.sp_fused) if ent is not None else None
+        return out[:T], (ent[:T] if ent is not None else None)
+
+    # ---------------------------------------------------------------- pipeline
+    def _stage_shapes(self, T: int):
+        """Shape of the activations that travel between stages for a micro-batch of ``T`` tokens."""
+        pctx = self.pctx
+        align = pctx.seq_shards * (128 if self.device.type == "cuda" else 1)
+        Tp = (T + align - 1) // align * align
+        return (Tp // pctx.seq_shards, self.model_config.hidden_size)
+
+    def _pipeline_forward_backward(self, mbs, scales, loss_fn, forward_only: bool = False, collect=None):
+        """All-forward-then-all-backward pipeline schedule over NCCL / gloo point-to-point.
+
+        Every stage of a replica holds the same micro-batch list, so activation shapes are known
+        without a handshake. Forward: receive ``(x, res)`` from the previous stage, run the local
+        blocks, send to the next; the last stage computes the loss. Backward (same micro-batch
+        order): receive the activation gradients from the next stage, back-propagate, send the
+        input gradients to the previous stage. Sends of stage ``i`` match receives of stage
+        ``i+1`` in program order, so blocking point-to-point calls cannot deadlock, and stage ``i``
+        works on micro-batch ``k+1`` while stage ``i+1`` works on ``k``. Returns the scaled losses
+        (last stage) or zeros (other stages; the caller broadcasts statistics).
+        Reference: areal/engine/megatron_engine.py:882 (mcore schedules) and
+        areal/experimental/models/archon/pipeline_parallel.py:349-494."""
+        pctx = self.pctx
+        first, last = pctx.is_first_stage, pctx.is_last_stage
+        dtype = next(self.model.parameters()).dtype
+        saved = []
+        losses = []
+        for mb, sc in zip(mbs, scales):
+            dev_mb, meta = self._mb_to_device(mb)
+            stage_in = None
+            if not first:
+                shape = self._stage_shapes(dev_mb["input_ids"].shape[0])
+                buf = torch.empty((2,) + shape, dtype=dtype, device=self.device)
+                dist.recv(buf, src=pctx.pp_prev)
+                x_in = buf[0].clone().requires_grad_(not forward_only)
+                r_in = buf[1].clone().requires_grad_(not forward_only)
+                stage_in = (x_in, r_in)
+            with torch.set_grad_enabled(not forward_only):
+                out, ent = self._forward_mb(dev_mb, meta, stage_input=stage_in)
+            if not last:
+                x, res = out
+                res = res if res is not None else torch.zeros_like(x)
+                dist.send(torch.stack([x.detach(), res.detach()]), dst=pctx.pp_next)
+                saved.append((stage_in, (x, res), None))
+                losses.append(torch.zeros((), device=self.device))
+            else:
+                if collect is not None:
+                    collect(out, ent, dev_mb, meta)
+                    saved.append((stage_in, None, None))
+                    continue
+                loss = loss_fn(out, dev_mb) if self.is_critic else loss_fn(out, ent, dev_mb)
+                saved.append((stage_in, None, loss * sc))
+                losses.append(loss.detach() * sc)
+        if forward_only:
+            return losses
+        for stage_in, outs, loss in saved:
+            if last:
+                loss.backward()
+            else:
+                g = torch.empty((2,) + tuple(outs[0].shape), dtype=dtype, device=self.device)
+                dist.recv(g, src=pctx.pp_next)
+                torch.autograd.backward([outs[0], outs[1]], [g[0], g[1]])
+            if not first:
+                x_in, r_in = stage_in
+                gx = x_in.grad if x_in.grad is not None else torch.zeros_like(x_in)
+                gr = r_in.grad if r_in.grad is not None else torch.zeros_like(r_in)
+                dist.send(torch.stack([gx, gr]), dst=pctx.pp_prev)
+        return losses
 
     # ------------------------------------------------------------------ train
     def optimizer_zero_grad(self):
@@ -254,17 +422,26 @@ class B200TrainEngine(TrainEngine):
         if dist.is_initialized() and self.world_size > 1:
             dist.all_reduce(total, group=self._cpu_group)
         total_w = float(total)
+        if self.pctx is not None:
+            total_w /= self.pctx.sp_size  # Ulysses ranks of one replica counted the same micro-batches
         assert total_w > 0, "total loss weight must be positive"
         losses = []
-        for mb, w in zip(mb_list.mbs, weights):
-            dev_mb, meta = self._mb_to_device(mb)
-            out, ent = self._forward_mb(dev_mb, meta)
-            loss = loss_fn(out, dev_mb) if self.is_critic else loss_fn(out, ent, dev_mb)
-            (loss * (w / total_w)).backward()
-            losses.append(loss.detach() * (w / total_w))
+        if self.pctx is not None and self.pctx.pp_size > 1:
+            losses = self._pipeline_forward_backward(mb_list.mbs, [w / total_w for w in weights], loss_fn)
+        else:
+            for mb, w in zip(mb_list.mbs, weights):
+                dev_mb, meta = self._mb_to_device(mb)
+                out, ent = self._forward_mb(dev_mb, meta)
+                loss = loss_fn(out, dev_mb) if self.is_critic else loss_fn(out, ent, dev_mb)
+                (loss * (w / total_w)).backward()
+                losses.append(loss.detach() * (w / total_w))
         stats = self.optimizer.step()
         self.lr_scheduler_step()
         stats["loss"] = float(torch.stack(losses).sum()) if losses else 0.0
+        if self.pctx is not None and self.pctx.pp_size > 1:
+            t = torch.tensor([stats["loss"]], dtype=torch.float32, device=self.device)
+            dist.all_reduce(t, group=self.pctx.pp_group)  # only the last stage holds a non-zero loss
+            stats["loss"] = float(t)
         self.d2h_bytes += 12  # grad-norm, skip flag, loss
         stats["n_mbs"] = float(len(mb_list))
         return stats
@@ -296,9 +473,19 @@ class B200TrainEngine(TrainEngine):
         result = torch.zeros(B, L, dtype=torch.float32)
         ent_result = torch.zeros(B, L, dtype=torch.float32) if return_entropy else None
         row = 0
-        for mb in mb_list.mbs:
-            dev_mb, meta = self._mb_to_device(mb)
-            out, ent = self._forward_mb(dev_mb, meta)
+        pp = self.pctx is not None and self.pctx.pp_size > 1
+        staged = []
+        if pp:
+            self._pipeline_forward_backward(mb_list.mbs, [1.0] * len(mb_list.mbs), None, forward_only=True,
+                                            collect=lambda o, e, m, mt: staged.append((o, e, mt)))
+        for i_mb, mb in enumerate(mb_list.mbs):
+            if pp:
+                if not self.pctx.is_last_stage:
+                    continue
+                out, ent, meta = staged[i_mb]
+            else:
+                dev_mb, meta = self._mb_to_device(mb)
+                out, ent = self._forward_mb(dev_mb, meta)
             out = out.float().cpu()
             self.d2h_bytes += out.numel() * 4
             ent = ent.float().cpu() if (ent is not None and return_entropy) else None
@@ -310,6 +497,13 @@ class B200TrainEngine(TrainEngine):
                 if ent is not None:
                     ent_result[src, :n] = ent[cu[i]:cu[i + 1]]
                 row += 1
+        if pp:
+            # the last stage holds the outputs: hand them to every stage of the replica
+            src = dist.get_global_rank(self.pctx.pp_group, self.pctx.pp_size - 1)
+            for t in ([result] + ([ent_result] if return_entropy else [])):
+                dev = t.to(self.device)
+                dist.broadcast(dev, src=src, group=self.pctx.pp_group)
+                t.copy_(dev.cpu())
         if return_entropy:
             return result, ent_result
         return result

@@ -31,40 +31,73 @@ from .config import ModelConfig
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device):
+    def __init__(self, cfg: ModelConfig, dtype, device, pctx=None):
         super().__init__()
         self.cfg = cfg
+        self.pctx = pctx
+        tp = pctx.tp_size if pctx is not None else 1
+        assert cfg.num_attention_heads % tp == 0 and cfg.num_key_value_heads % tp == 0, \
+            "tensor parallelism needs the head counts to divide by the tp size"
+        self.n_q, self.n_kv = cfg.num_attention_heads // tp, cfg.num_key_value_heads // tp
         h = cfg.hidden_size
-        self.qkv = nn.Parameter(torch.empty(cfg.q_size + 2 * cfg.kv_size, h, dtype=dtype, device=device))
-        self.qkv_bias = (nn.Parameter(torch.zeros(cfg.q_size + 2 * cfg.kv_size, dtype=dtype, device=device))
+        qs, ks = cfg.q_size // tp, cfg.kv_size // tp
+        self.qkv = nn.Parameter(torch.empty(qs + 2 * ks, h, dtype=dtype, device=device))
+        self.qkv_bias = (nn.Parameter(torch.zeros(qs + 2 * ks, dtype=dtype, device=device))
                          if cfg.attention_bias else None)
-        self.o = nn.Parameter(torch.empty(h, cfg.q_size, dtype=dtype, device=device))
+        self.o = nn.Parameter(torch.empty(h, qs, dtype=dtype, device=device))
         if cfg.qk_norm:
             self.q_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device))
             self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device))
         else:
             self.q_norm = self.k_norm = None
 
+    def _tp(self):
+        p = self.pctx
+        return p.tp_fused if (p is not None and p.tp_size > 1) else None
+
     def project_qkv(self, x, cos, sin, pos):
         cfg = self.cfg
-        qkv = linear(x, self.qkv, self.qkv_bias)
+        tp = self._tp()
+        if tp is not None:
+            from ..parallel.tensor_parallel import column_parallel_linear
+
+            qkv = column_parallel_linear(x, self.qkv, tp, self.qkv_bias)
+        else:
+            qkv = linear(x, self.qkv, self.qkv_bias)
         return fused.qknorm_rope(qkv, self.q_norm, self.k_norm, cos, sin, pos,
-                                 cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim,
-                                 cfg.rms_norm_eps)
+                                 self.n_q, self.n_kv, cfg.head_dim, cfg.rms_norm_eps)
 
     def forward(self, x, cos, sin, pos, meta: VarlenMeta, attn_fn=None):
+        """``pos`` are the positions of the tokens that reach the q/k projection output: all
+        tokens of this sequence-parallel shard (tensor parallelism gathers its token shards
+        inside the projection)."""
         q, k, v = self.project_qkv(x, cos, sin, pos)
         a = (attn_fn or varlen_attention)(q, k, v, meta)
-        return linear(a.reshape(a.shape[0], -1), self.o)
+        a = a.reshape(a.shape[0], -1)
+        tp = self._tp()
+        if tp is not None:
+            from ..parallel.tensor_parallel import row_parallel_linear
+
+            return row_parallel_linear(a, self.o, tp)
+        return linear(a, self.o)
 
 
 class DenseMLP(nn.Module):
-    def __init__(self, hidden, inter, dtype, device):
+    def __init__(self, hidden, inter, dtype, device, pctx=None):
         super().__init__()
-        self.gate_up = nn.Parameter(torch.empty(2 * inter, hidden, dtype=dtype, device=device))
-        self.down = nn.Parameter(torch.empty(hidden, inter, dtype=dtype, device=device))
+        self.pctx = pctx
+        tp = pctx.tp_size if pctx is not None else 1
+        assert inter % tp == 0
+        self.gate_up = nn.Parameter(torch.empty(2 * inter // tp, hidden, dtype=dtype, device=device))
+        self.down = nn.Parameter(torch.empty(hidden, inter // tp, dtype=dtype, device=device))
 
     def forward(self, x):
+        p = self.pctx
+        if p is not None and p.tp_size > 1:
+            from ..parallel.tensor_parallel import column_parallel_linear, row_parallel_linear
+
+            return row_parallel_linear(fused.swiglu(column_parallel_linear(x, self.gate_up, p.tp_fused)),
+                                       self.down, p.tp_fused)
         return linear(fused.swiglu(linear(x, self.gate_up)), self.down)
 
 
@@ -73,9 +106,10 @@ class MoEMLP(nn.Module):
     renormalisation), as in Qwen3-MoE. Expert weights are 3-D parameters
     ``gate_up [E, 2I, H]`` and ``down [E, H, I]``."""
 
-    def __init__(self, cfg: ModelConfig, dtype, device):
+    def __init__(self, cfg: ModelConfig, dtype, device, pctx=None):
         super().__init__()
         self.cfg = cfg
+        self.pctx = pctx
         E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
         self.router = nn.Parameter(torch.empty(E, H, dtype=dtype, device=device))
         self.gate_up = nn.Parameter(torch.empty(E, 2 * I, H, dtype=dtype, device=device))
@@ -85,6 +119,10 @@ class MoEMLP(nn.Module):
     def route(self, x):
         cfg = self.cfg
         logits = F.linear(x.float(), self.router.float())
+        if not (torch.is_grad_enabled() and (x.requires_grad or self.router.requires_grad)):
+            from ..ops.moe import route as route_kernel
+
+            return route_kernel(logits, cfg.num_experts_per_tok, cfg.norm_topk_prob)
         probs = logits.softmax(-1)
         w, idx = probs.topk(cfg.num_experts_per_tok, dim=-1)
         if cfg.norm_topk_prob:
@@ -100,14 +138,17 @@ class MoEMLP(nn.Module):
 
 
 class Block(nn.Module):
-    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device):
+    def __init__(self, cfg: ModelConfig, layer_idx: int, dtype, device, pctx=None):
         super().__init__()
         h = cfg.hidden_size
         self.input_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
-        self.attn = Attention(cfg, dtype, device)
+        self.attn = Attention(cfg, dtype, device, pctx)
         self.post_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
-        self.mlp = (MoEMLP(cfg, dtype, device) if cfg.layer_is_moe(layer_idx)
-                    else DenseMLP(h, cfg.intermediate_size, dtype, device))
+        if cfg.layer_is_moe(layer_idx):
+            assert pctx is None or pctx.tp_size == 1, "MoE layers shard over the expert-parallel group, not tp"
+            self.mlp = MoEMLP(cfg, dtype, device, pctx)
+        else:
+            self.mlp = DenseMLP(h, cfg.intermediate_size, dtype, device, pctx)
         self.eps = cfg.rms_norm_eps
 
     def forward(self, x, res, cos, sin, pos, meta, attn_fn=None):
@@ -121,19 +162,34 @@ class Block(nn.Module):
 
 
 class QwenModel(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu"):
+    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", pctx=None):
+        """``pctx`` (``parallel.context.ParallelContext``) turns on tensor parallelism (vocab-parallel
+        embedding / LM head, head- and column-sharded projections, token-sharded activations
+        between blocks) and Ulysses sequence parallelism; parameters then have their LOCAL shapes."""
         super().__init__()
         self.cfg = cfg
-        self.embed = nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device))
-        self.layers = nn.ModuleList(Block(cfg, i, dtype, device) for i in range(cfg.num_hidden_layers))
-        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device))
-        if cfg.is_critic:
-            self.score = nn.Parameter(torch.empty(1, cfg.hidden_size, dtype=dtype, device=device))
-            self.lm_head = None
-        else:
-            self.score = None
-            self.lm_head = (None if cfg.tie_word_embeddings else
-                            nn.Parameter(torch.empty(cfg.vocab_size, cfg.hidden_size, dtype=dtype, device=device)))
+        self.pctx = pctx
+        tp = pctx.tp_size if pctx is not None else 1
+        assert cfg.vocab_size % tp == 0
+        vloc = cfg.vocab_size // tp
+        # pipeline parallelism: this stage owns a contiguous range of blocks; the embedding lives on
+        # the first stage, the final norm and the head on the last (a tied head keeps its own copy of
+        # the embedding there; the two copies' gradients are summed before the optimizer step)
+        pp = pctx.pp_size if pctx is not None else 1
+        self.first_stage = pctx.is_first_stage if pp > 1 else True
+        self.last_stage = pctx.is_last_stage if pp > 1 else True
+        self.layer_start, self.layer_end = pctx.layer_range(cfg.num_hidden_layers) if pp > 1 else (0, cfg.num_hidden_layers)
+        mk = lambda *shape: nn.Parameter(torch.empty(*shape, dtype=dtype, device=device))
+        need_embed = self.first_stage or (self.last_stage and cfg.tie_word_embeddings and not cfg.is_critic)
+        self.embed = mk(vloc, cfg.hidden_size) if need_embed else None
+        self.layers = nn.ModuleList(Block(cfg, i, dtype, device, pctx) for i in range(self.layer_start, self.layer_end))
+        self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device)) if self.last_stage else None
+        self.score = self.lm_head = None
+        if self.last_stage:
+            if cfg.is_critic:
+                self.score = mk(1, cfg.hidden_size)
+            elif not cfg.tie_word_embeddings:
+                self.lm_head = mk(vloc, cfg.hidden_size)
         self._rope = None
 
     # ------------------------------------------------------------------ init
@@ -141,24 +197,70 @@ class QwenModel(nn.Module):
     def init_weights(self, seed: int = 0, std: float = 0.02):
         g = torch.Generator(device="cpu").manual_seed(seed)
         dev_gen = None
+        tp = self.pctx.tp_size if self.pctx is not None else 1
+        tp_rank = self.pctx.tp_rank if self.pctx is not None else 0
+        if self.layer_end - self.layer_start != self.cfg.num_hidden_layers:
+            return self._init_weights_pipeline(seed, std)
         for name, p in self.named_parameters():
             if name.endswith("norm") or "_norm" in name:
                 p.fill_(1.0)
-            elif name.endswith("bias"):
+                continue
+            if name.endswith("bias"):
                 p.zero_()
-            elif p.is_cuda:
+                continue
+            dst = p
+            if tp > 1:
+                # draw the FULL tensor (so values do not depend on the tp size), keep this rank's shard
+                from ..parallel.tensor_parallel import is_tp_replicated, tp_slice
+
+                if not is_tp_replicated(name):
+                    dst = torch.empty(self._full_shape(name, p), dtype=p.dtype, device=p.device)
+            if dst.is_cuda:
                 # large models: draw on the device (same seed ⇒ same values on every rank)
                 if dev_gen is None:
                     dev_gen = torch.Generator(device=p.device).manual_seed(seed)
-                p.normal_(0.0, std, generator=dev_gen)
+                dst.normal_(0.0, std, generator=dev_gen)
             else:
                 # generated on the host in fp32 so that every dtype sees the same values
                 chunk = 1 << 24
-                flat = p.view(-1)
+                flat = dst.view(-1)
                 for s in range(0, flat.numel(), chunk):
                     n = min(chunk, flat.numel() - s)
                     flat[s:s + n].copy_(torch.empty(n, dtype=torch.float32).normal_(0.0, std, generator=g))
+            if dst is not p:
+                p.copy_(tp_slice(name, dst, self.cfg, tp_rank, tp))
         return self
+
+    @torch.no_grad()
+    def _init_weights_pipeline(self, seed: int, std: float):
+        """A pipeline stage draws the whole model's random stream (stage-independent values) on a
+        meta-free throwaway copy and keeps what it owns. Meant for small / test models; real runs
+        load checkpoints."""
+        import copy
+        import dataclasses
+
+        from ..parallel.context import ParallelContext
+
+        p = self.pctx
+        flat_ctx = ParallelContext(tp_group=p.tp_group, tp_rank=p.tp_rank, tp_size=p.tp_size)
+        full = QwenModel(self.cfg, dtype=next(self.parameters()).dtype, device=next(self.parameters()).device,
+                         pctx=flat_ctx if p.tp_size > 1 else None)
+        full.init_weights(seed, std)
+        src = dict(full.named_parameters())
+        for name, prm in self.named_parameters():
+            if name.startswith("layers."):
+                _, idx, rest = name.split(".", 2)
+                key = f"layers.{int(idx) + self.layer_start}.{rest}"
+            else:
+                key = name
+            prm.copy_(src[key])
+        return self
+
+    def _full_shape(self, name: str, p: torch.Tensor) -> tuple[int, ...]:
+        tp = self.pctx.tp_size
+        if name.endswith(("attn.o", "mlp.down")):
+            return (p.shape[0], p.shape[1] * tp)
+        return (p.shape[0] * tp,) + tuple(p.shape[1:])
 
     def output_weight(self) -> torch.Tensor:
         return self.embed if self.lm_head is None else self.lm_head
@@ -170,15 +272,38 @@ class QwenModel(nn.Module):
         return self._rope
 
     # --------------------------------------------------------------- forward
-    def forward(self, input_ids, position_ids, meta: VarlenMeta, attn_fn=None):
-        """Packed forward; returns the final-normed hidden states ``[T, H]``."""
+    def forward(self, input_ids, position_ids, meta: VarlenMeta, attn_fn=None, stage_input=None):
+        """Packed forward; returns the final-normed hidden states ``[T, H]``. On a pipeline stage
+        other than the first, ``stage_input = (x, res)`` are the activations received from the
+        previous stage; a stage other than the last returns ``(x, res)`` for the next one."""
         cos, sin = self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
-        x = fused.embedding(input_ids, self.embed)
-        res = None
+        p = self.pctx
+        if p is not None and p.sp_size > 1 and attn_fn is None:
+            from ..parallel.ulysses import ulysses_attention
+
+            attn_fn = ulysses_attention(p)
+        if stage_input is not None:
+            x, res = stage_input
+        elif p is not None and p.tp_size > 1:
+            # input_ids / position_ids hold every token of this sequence-parallel shard; the
+            # vocab-parallel lookup leaves each tp rank with its T/tp rows
+            from ..parallel.tensor_parallel import vocab_parallel_embedding
+
+            x, res = vocab_parallel_embedding(input_ids, self.embed, p.tp_fused), None
+        else:
+            x, res = fused.embedding(input_ids, self.embed), None
         for layer in self.layers:
             x, res = layer(x, res, cos, sin, pos, meta, attn_fn)
+        if not self.last_stage:
+            return x, res
         y, _ = fused.rmsnorm(x, self.norm, self.cfg.rms_norm_eps, residual=res)
+        if p is not None and p.tp_size > 1:
+            from ..parallel.tensor_parallel import gather_seq, gather_seq_replicated
+
+            # the vocab-parallel head needs every token and returns PARTIAL input gradients (summed
+            # in the backward); a critic's value head is replicated work, so its backward only slices
+            y = gather_seq_replicated(y, p.tp_fused) if self.cfg.is_critic else gather_seq(y, p.tp_fused)
         return y
 
     def logits(self, hidden, out_dtype=torch.float32):
@@ -238,13 +363,44 @@ class QwenModel(nn.Module):
         return y
 
     # ------------------------------------------------------ HF name mapping
+    _TP_DIM0 = ("embed_tokens.weight", "lm_head.weight", "q_proj.weight", "k_proj.weight", "v_proj.weight",
+                "q_proj.bias", "k_proj.bias", "v_proj.bias", "gate_proj.weight", "up_proj.weight")
+    _TP_DIM1 = ("o_proj.weight", "down_proj.weight")
+
+    def _tp_dim(self, hf_name: str) -> int | None:
+        """Dimension along which an HF tensor is split over the tp group (None: replicated)."""
+        if self.pctx is None or self.pctx.tp_size == 1 or ".experts." in hf_name:
+            return None
+        if hf_name.endswith(self._TP_DIM0):
+            return 0
+        if hf_name.endswith(self._TP_DIM1):
+            return 1
+        return None
+
     def to_hf(self) -> Iterator[tuple[str, torch.Tensor]]:
-        """Yields ``(hf_name, tensor)`` views/slices in HF checkpoint naming."""
+        """Yields ``(hf_name, tensor)`` in HF checkpoint naming: views of the fused parameters, or,
+        under tensor parallelism, full tensors gathered over the tp group (a collective: every tp
+        rank must iterate)."""
+        import torch.distributed as dist
+
+        for name, t in self.to_hf_local():
+            d = self._tp_dim(name)
+            if d is None:
+                yield name, t
+            else:
+                parts = [torch.empty_like(t) for _ in range(self.pctx.tp_size)]
+                dist.all_gather(parts, t.contiguous(), group=self.pctx.tp_group)
+                yield name, torch.cat(parts, d)
+
+    def to_hf_local(self) -> Iterator[tuple[str, torch.Tensor]]:
+        """``(hf_name, view)`` of this rank's (tp-local) parameters."""
         cfg = self.cfg
-        yield "model.embed_tokens.weight", self.embed
-        qs, ks = cfg.q_size, cfg.kv_size
-        I = cfg.intermediate_size
-        for i, layer in enumerate(self.layers):
+        tp = self.pctx.tp_size if self.pctx is not None else 1
+        if self.embed is not None and self.first_stage:
+            yield "model.embed_tokens.weight", self.embed
+        qs, ks = cfg.q_size // tp, cfg.kv_size // tp
+        I = cfg.intermediate_size // tp
+        for i, layer in enumerate(self.layers, start=self.layer_start):
             p = f"model.layers.{i}."
             yield p + "input_layernorm.weight", layer.input_norm
             a = layer.attn
@@ -273,14 +429,15 @@ class QwenModel(nn.Module):
                     yield q + "gate_proj.weight", m.gate_up[e, :Im]
                     yield q + "up_proj.weight", m.gate_up[e, Im:]
                     yield q + "down_proj.weight", m.down[e]
-        yield "model.norm.weight", self.norm
+        if self.norm is not None:
+            yield "model.norm.weight", self.norm
         if self.score is not None:
             yield "score.weight", self.score
         elif self.lm_head is not None:
             yield "lm_head.weight", self.lm_head
 
     def hf_name_map(self) -> dict[str, torch.Tensor]:
-        return dict(self.to_hf())
+        return dict(self.to_hf_local())
 
     @torch.no_grad()
     def load_hf(self, tensors: Iterable[tuple[str, torch.Tensor]], strict: bool = True):
@@ -296,6 +453,10 @@ class QwenModel(nn.Module):
                     raise KeyError(f"unexpected tensor {name}")
                 continue
             d = dst[name]
+            dim = self._tp_dim(name)
+            if dim is not None:
+                n = t.shape[dim] // self.pctx.tp_size
+                t = t.narrow(dim, self.pctx.tp_rank * n, n)
             if d.shape != t.shape:
                 raise ValueError(f"{name}: shape {tuple(t.shape)} != {tuple(d.shape)}")
             d.copy_(t.to(device=d.device, dtype=d.dtype))
@@ -306,8 +467,8 @@ class QwenModel(nn.Module):
         return self
 
 
-def build_model(cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", seed: int | None = 0) -> QwenModel:
-    m = QwenModel(cfg, dtype=dtype, device=device)
+def build_model(cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", seed: int | None = 0, pctx=None) -> QwenModel:
+    m = QwenModel(cfg, dtype=dtype, device=device, pctx=pctx)
     if seed is not None:
         m.init_weights(seed)
     return m

@@ -1,0 +1,160 @@
+"""Model-parallel context handed to the model: tensor-parallel and Ulysses
+sequence-parallel groups plus the symmetric-memory state of the fused
+GEMM+collective kernels.
+
+Rank order inside one pipeline stage is ``[dp][sp][tp]`` with ``tp`` innermost, the
+same nesting as the reference's device meshes (areal/engine/fsdp_utils/parallel.py:86-123,
+areal/api/alloc_mode.py:32-160).
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any
+
+import torch
+import torch.distributed as dist
+
+
+@dataclass
+class ParallelContext:
+    tp_group: Any = None
+    tp_rank: int = 0
+    tp_size: int = 1
+    sp_group: Any = None
+    sp_rank: int = 0
+    sp_size: int = 1
+    ep_group: Any = None
+    ep_rank: int = 0
+    ep_size: int = 1
+    pp_group: Any = None
+    pp_rank: int = 0
+    pp_size: int = 1
+    pp_prev: int | None = None   # global ranks of the neighbouring stages
+    pp_next: int | None = None
+    pp_tie_group: Any = None     # first + last stage (tied embedding / LM-head gradients)
+
+    def layer_range(self, num_layers: int) -> tuple[int, int]:
+        """Contiguous, near-even split of the transformer blocks over the pipeline stages."""
+        base, extra = divmod(num_layers, self.pp_size)
+        start = self.pp_rank * base + min(self.pp_rank, extra)
+        return start, start + base + (1 if self.pp_rank < extra else 0)
+
+    @property
+    def is_first_stage(self) -> bool:
+        return self.pp_rank == 0
+
+    @property
+    def is_last_stage(self) -> bool:
+        return self.pp_rank == self.pp_size - 1
+    # FusedCommContext of the tp group (CUDA only; None ⇒ NCCL / gloo collectives)
+    tp_fused: Any = None
+    sp_fused: Any = None
+    extras: dict = field(default_factory=dict)
+
+    @property
+    def seq_shards(self) -> int:
+        """Number of ways the packed token dimension is split between blocks."""
+        return self.tp_size * self.sp_size
+
+    def enable_fused(self, max_tokens: int, hidden: int, widest: int, device=None):
+        """Creates the communication state of the tp / sp groups. On CUDA this allocates the
+        symmetric staging buffers of the fused kernels (``max_tokens`` rows of the widest
+        activation); on CPU the same object only carries group, rank and size."""
+        from .fused_linear import FusedCommContext
+
+        nbytes = max_tokens * max(hidden, widest) * 2
+        if self.tp_size > 1 and self.tp_fused is None:
+            self.tp_fused = FusedCommContext(self.tp_group, nbytes, device)
+        if self.sp_size > 1 and self.sp_fused is None:
+            self.sp_fused = FusedCommContext(self.sp_group, nbytes, device)
+
+
+@dataclass
+class MeshGroups:
+    dp_group: Any
+    dp_rank: int
+    dp_size: int
+    # ranks that hold the same parameter shard and see different data: dp x sp
+    shard_group: Any
+    shard_rank: int
+    shard_size: int
+    ctx: ParallelContext
+    pp_rank: int = 0
+    pp_size: int = 1
+    pp_prev: int | None = None
+    pp_next: int | None = None
+    cpu_shard_group: Any = None
+    mp_group: Any = None  # every rank of one data-parallel replica (tp x sp x pp): they share a batch
+    mp_rank: int = 0
+
+
+def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1, cpu_groups: bool = True) -> MeshGroups:
+    """Creates every group of a ``pp x dp x sp x tp`` mesh over ``ranks``. Collective over the
+    WHOLE world (``dist.new_group`` semantics): every process must call it with the same arguments,
+    whether or not it belongs to ``ranks``."""
+    assert len(ranks) == dp * sp * tp * pp, (len(ranks), dp, sp, tp, pp)
+    me = dist.get_rank() if dist.is_initialized() else 0
+    backend_is_gloo = (not dist.is_initialized()) or dist.get_backend() == "gloo"
+
+    def coord(i):
+        t = i % tp
+        s = (i // tp) % sp
+        d = (i // (tp * sp)) % dp
+        p = i // (tp * sp * dp)
+        return p, d, s, t
+
+    def make(sel):
+        """One group per distinct key; returns this rank's group, its index inside and the size."""
+        buckets: dict[Any, list[int]] = {}
+        for i, r in enumerate(ranks):
+            buckets.setdefault(sel(*coord(i)), []).append(r)
+        mine = (None, 0, 1)
+        for key in sorted(buckets):
+            members = buckets[key]
+            g = dist.new_group(members) if dist.is_initialized() else None  # size-1 groups too: None would mean WORLD
+            if me in members:
+                mine = (g, members.index(me), len(members))
+        return mine
+
+    tp_g = make(lambda p, d, s, t: (p, d, s))
+    sp_g = make(lambda p, d, s, t: (p, d, t))
+    dp_g = make(lambda p, d, s, t: (p, s, t))
+    sh_g = make(lambda p, d, s, t: (p, t))
+    mp_g = make(lambda p, d, s, t: d)
+    pp_g = make(lambda p, d, s, t: (d, s, t))
+    tie_g = (None, 0, 1)
+    if pp > 1 and dist.is_initialized():
+        stride = dp * sp * tp
+        for j in range(stride):
+            pair = [ranks[j], ranks[j + (pp - 1) * stride]]
+            g = dist.new_group(pair)
+            if me in pair:
+                tie_g = (g, pair.index(me), 2)
+    cpu_sh = (None, 0, 1)
+    if cpu_groups and dist.is_initialized() and not backend_is_gloo:
+        buckets: dict[Any, list[int]] = {}
+        for i, r in enumerate(ranks):
+            p, d, s, t = coord(i)
+            buckets.setdefault((p, t), []).append(r)
+        for key in sorted(buckets):
+            g = dist.new_group(buckets[key], backend="gloo")
+            if me in buckets[key]:
+                cpu_sh = (g, 0, 0)
+    ctx = ParallelContext(tp_group=tp_g[0], tp_rank=tp_g[1], tp_size=tp_g[2],
+                          sp_group=sp_g[0], sp_rank=sp_g[1], sp_size=sp_g[2])
+    mesh = MeshGroups(dp_group=dp_g[0], dp_rank=dp_g[1], dp_size=dp_g[2], shard_group=sh_g[0], shard_rank=sh_g[1],
+                      shard_size=sh_g[2], ctx=ctx, pp_size=pp,
+                      cpu_shard_group=cpu_sh[0] if not backend_is_gloo else sh_g[0],
+                      mp_group=mp_g[0], mp_rank=mp_g[1])
+    if me in ranks:
+        i = ranks.index(me)
+        p, d, s, t = coord(i)
+        mesh.pp_rank = p
+        stride = dp * sp * tp
+        mesh.pp_prev = ranks[i - stride] if p > 0 else None
+        mesh.pp_next = ranks[i + stride] if p < pp - 1 else None
+        ctx.pp_group, ctx.pp_rank, ctx.pp_size = pp_g[0], p, pp
+        ctx.pp_prev, ctx.pp_next = mesh.pp_prev, mesh.pp_next
+        ctx.pp_tie_group = tie_g[0]
+    return mesh

@@ -135,7 +135,17 @@ def gemm_reduce_scatter(ctx: FusedCommContext, x: torch.Tensor, w: torch.Tensor,
     return out
 
 
-def all_gather_gemm(ctx: FusedCommContext, x: torch.Tensor, w: torch.Tensor):
+def all_gather_gemm(ctx: FusedCommContext, x: torch.Tensor, w: torch.Tensor, return_gathered: bool = False):
+    """With ``return_gathered`` also returns the gathered rows ``[M, K]``; on the fused path this is
+    a view of the (local) gather buffer, valid until the next fused call on ``ctx``."""
+    if return_gathered:
+        if not (ctx.cuda and x.is_cuda) or x.shape[0] % 128 or ctx.world == 1:
+            full = ctx_all_gather(ctx, x) if ctx.world > 1 else x
+            y = gemm(full, w) if (full.is_cuda and full.dtype == torch.bfloat16) else (full.float() @ w.float().t()).to(x.dtype)
+            return y, full
+        y = all_gather_gemm(ctx, x, w)
+        M = x.shape[0] * ctx.world
+        return y, ctx.gather.tensor(x.dtype, M * x.shape[1]).view(M, x.shape[1])
     if not (ctx.cuda and x.is_cuda):
         return all_gather_gemm_ref(x, w, ctx.group)
     Ml, K = x.shape
@@ -175,9 +185,10 @@ def all_gather_gemm(ctx: FusedCommContext, x: torch.Tensor, w: torch.Tensor):
 
 
 def ctx_all_gather(ctx: FusedCommContext, x: torch.Tensor) -> torch.Tensor:
-    parts = [torch.empty_like(x) for _ in range(ctx.world)]
-    dist.all_gather(parts, x.contiguous(), group=ctx.group)
-    return torch.cat(parts, 0)
+    out = torch.empty((ctx.world * x.shape[0],) + tuple(x.shape[1:]), dtype=x.dtype, device=x.device)
+    dist.all_gather_into_tensor(out, x.contiguous(), group=ctx.group) if x.is_cuda else \
+        dist.all_gather(list(out.chunk(ctx.world, 0)), x.contiguous(), group=ctx.group)
+    return out
 
 
 def gemm_all_to_all(ctx: FusedCommContext, x: torch.Tensor, w: torch.Tensor):

@@ -185,6 +185,23 @@ class PPOTrainer:
         if self.stats_logger is not None:
             self.stats_logger.close()
 
+    def _next_batch(self, workflow, workflow_kwargs, group):
+        """The next training batch of this rank. Under tensor / sequence / pipeline parallelism only
+        the head of each data-parallel replica talks to the rollout side; the other ranks of the
+        replica receive the same batch over their model-parallel group."""
+        cfg = self.config
+        eng = self.actor_engine
+        mp = getattr(eng, "context_and_model_parallel_group", None)
+        if mp is None or dist.get_world_size(mp) == 1:
+            return self.rollout_client.prepare_batch(self.dataloader, workflow, workflow_kwargs,
+                                                     group_size=group, dynamic_bs=cfg.dynamic_bs)
+        box = [None]
+        if eng.is_data_parallel_head():
+            box[0] = self.rollout_client.prepare_batch(self.dataloader, workflow, workflow_kwargs,
+                                                       group_size=group, dynamic_bs=cfg.dynamic_bs)
+        dist.broadcast_object_list(box, src=eng.current_data_parallel_head(), group=mp)
+        return box[0]
+
     # -------------------------------------------------------------------- train
     def train(self, workflow, workflow_kwargs: dict | None = None, eval_workflow=None,
               eval_workflow_kwargs: dict | None = None, max_steps: int | None = None,
@@ -213,8 +230,7 @@ class PPOTrainer:
             t_step = time.perf_counter()
             epoch, epoch_step = divmod(global_step, steps_per_epoch)
             with stats_tracker.record_timing("rollout"):
-                batch = self.rollout_client.prepare_batch(self.dataloader, workflow, workflow_kwargs,
-                                                          group_size=group, dynamic_bs=cfg.dynamic_bs)
+                batch = self._next_batch(workflow, workflow_kwargs, group)
             stats = self.train_step(batch, global_step)
             self.step_times.append(time.perf_counter() - t_step)
             with stats_tracker.record_timing("save"):

@@ -1,0 +1,123 @@
+"""Worker: one train_batch of a tiny model under tensor / Ulysses / data parallelism (gloo, CPU)
+compared with a single-process run of the same global batch.
+
+    python run_model_parallel.py --ref FILE                 # writes loss, grad-norm and full gradients
+    torchrun ... run_model_parallel.py --tp 2 --sp 1 FILE   # every rank checks itself against FILE
+"""
+import argparse
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))))
+
+from areal_b200.api.alloc_mode import ParallelStrategy  # noqa: E402
+from areal_b200.api.cli_args import MicroBatchSpec, OptimizerConfig, TrainEngineConfig  # noqa: E402
+from areal_b200.engine.train_engine import B200TrainEngine  # noqa: E402
+from areal_b200.parallel.tensor_parallel import is_tp_replicated, tp_unslice  # noqa: E402
+
+
+def global_batch(n_seq=8, L=48, vocab=1024):
+    g = torch.Generator().manual_seed(7)
+    lens = torch.randint(L // 3, L + 1, (n_seq,), generator=g)
+    ids = torch.randint(0, vocab, (n_seq, L), generator=g)
+    mask = torch.arange(L)[None, :] < lens[:, None]
+    loss_mask = mask & (torch.arange(L)[None, :] >= 4)
+    return dict(input_ids=ids * mask, attention_mask=mask, loss_mask=loss_mask.int())
+
+
+def loss_fn(logp, ent, mb):
+    m = torch.roll(mb["loss_mask"], shifts=-1, dims=0).float()
+    return -(logp * m).sum() / m.sum().clamp(min=1)
+
+
+def weight_fn(mb):
+    return float(mb["loss_mask"].sum())
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("file")
+    ap.add_argument("--ref", action="store_true")
+    ap.add_argument("--tp", type=int, default=1)
+    ap.add_argument("--sp", type=int, default=1)
+    ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--n-mbs", type=int, default=1)
+    ap.add_argument("--critic", action="store_true")
+    args = ap.parse_args()
+    cfg = TrainEngineConfig(experiment_name="t", trial_name="t", path="", init_from_scratch=True, dtype="float32",
+                            model_preset="tiny-qwen2", mb_spec=MicroBatchSpec(n_mbs=args.n_mbs), is_critic=args.critic,
+                            optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0, gradient_clipping=1.0,
+                                                      warmup_steps_proportion=0.0, lr_scheduler_type="constant"))
+    eng = B200TrainEngine(cfg)
+    batch = global_batch()
+    if args.ref:
+        eng.create_process_group()
+        eng.initialize(seed=3)
+        data = batch
+    else:
+        dist.init_process_group("gloo")
+        world = dist.get_world_size()
+        dp = world // (args.tp * args.sp * args.pp)
+        eng.create_process_group(ParallelStrategy(tensor_parallel_size=args.tp, context_parallel_size=args.sp,
+                                                  pipeline_parallel_size=args.pp, data_parallel_size=dp))
+        eng.initialize(seed=3)
+        d = eng.data_parallel_rank
+        data = {k: v[d::dp] for k, v in batch.items()}
+    captured = {}
+    orig_step = eng.optimizer.step
+
+    def step(*a, **k):
+        eng.flat.collect_autograd_grads()
+        for name, p, _, _ in eng.flat.entries:
+            captured[name] = p.main_grad.clone()
+        return orig_step(*a, **k)
+
+    eng.optimizer.step = step
+    lf = (lambda v, mb: ((v - 0.3) ** 2 * mb["loss_mask"].float()).sum() / mb["loss_mask"].sum()) if args.critic else loss_fn
+    stats = eng.train_batch(data, lf, weight_fn)
+    if args.ref:
+        torch.save(dict(loss=stats["loss"], grad_norm=stats["grad_norm"], grads=captured), args.file)
+        print("ref", stats["loss"], stats["grad_norm"])
+        return
+    ref = torch.load(args.file)
+    pctx, mesh = eng.pctx, eng.mesh
+    full = {}
+    for name, g in captured.items():
+        g = g.clone()
+        if mesh.shard_size > 1:
+            dist.all_reduce(g, group=mesh.shard_group)
+        if pctx.tp_size > 1:
+            if is_tp_replicated(name):
+                if not name.endswith("score"):
+                    dist.all_reduce(g, group=pctx.tp_group)
+            else:
+                parts = [None] * pctx.tp_size
+                dist.all_gather_object(parts, g, group=pctx.tp_group)
+                g = tp_unslice(name, parts, eng.model_config)
+        full[name] = g
+    # the loss is the sum over this rank's micro-batches; data-parallel ranks hold different ones
+    loss = torch.tensor([stats["loss"]], dtype=torch.float64)
+    if mesh.dp_size > 1:
+        dist.all_reduce(loss, group=mesh.dp_group)
+    assert abs(float(loss) - ref["loss"]) < 1e-4 * max(1.0, abs(ref["loss"])), (float(loss), ref["loss"])
+    for name, g in full.items():
+        if name.startswith("layers."):
+            _, idx, rest = name.split(".", 2)
+            name = f"layers.{int(idx) + eng.model.layer_start}.{rest}"
+        r = ref["grads"][name]
+        err = (g - r).abs().max().item()
+        assert err <= 2e-4 * (r.abs().max().item() + 1e-6), (name, err, r.abs().max().item())
+    assert abs(stats["grad_norm"] - ref["grad_norm"]) < 2e-4 * ref["grad_norm"], (stats["grad_norm"], ref["grad_norm"])
+    # and the update itself went through on every rank
+    assert stats["update_successful"] == 1.0
+    dist.barrier()
+    if dist.get_rank() == 0:
+        print("OK", float(loss), stats["grad_norm"])
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
