@@ -246,6 +246,181 @@ __global__ void moe_combine_dw_kernel(const __nv_bfloat16* __restrict__ dout, co
   }
 }
 
+
+// ------------------------------------------------------------------ expert parallelism --
+// Experts are split over P ranks (rank d owns experts [d*E/P, (d+1)*E/P)). Each rank sorts its own
+// (token, choice) copies by GLOBAL expert; after the ranks have exchanged their per-expert counts
+// every rank can compute, without talking to the host, where each of its copies lands in the
+// owner's padded expert-sorted buffer: owner segment of the expert, then source-rank order, then
+// the source's stable order. The dispatch kernel stores rows straight into the owners' buffers over
+// NVLink, the owners run the grouped GEMMs in place, and the combine kernel pulls the result rows
+// back from the owners (weighted sum per token). No intermediate send / receive staging, no
+// host-side `tolist()` of the counts as in the reference
+// (areal/experimental/models/archon/expert_parallel.py:70-262).
+
+// One block, thread e owns global expert e. counts_all: [P, E].
+__global__ void ep_plan_kernel(const int* __restrict__ counts_all, int me, int P, int E, int* __restrict__ send_base,
+                               int* __restrict__ prow0_loc, int* __restrict__ total_loc,
+                               int* __restrict__ tile_expert_loc, int* __restrict__ num_vm) {
+  __shared__ int s_total[kMaxE], s_before[kMaxE], s_start[kMaxE + 1];
+  const int e = threadIdx.x;
+  const int el = E / P;
+  if (e < E) {
+    int tot = 0, before = 0;
+    for (int s = 0; s < P; ++s) {
+      const int c = counts_all[s * E + e];
+      if (s < me) before += c;
+      tot += c;
+    }
+    s_total[e] = tot;
+    s_before[e] = before;
+  }
+  __syncthreads();
+  if (threadIdx.x < P) {  // thread d scans the experts of owner d
+    const int d = threadIdx.x;
+    int acc = 0;
+    for (int i = 0; i < el; ++i) {
+      const int ge = d * el + i;
+      s_start[ge] = acc;
+      acc += ((s_total[ge] + 127) >> 7) << 7;
+    }
+    if (d == me) {
+      prow0_loc[el] = acc;
+      *num_vm = acc >> 7;
+    }
+  }
+  __syncthreads();
+  if (e < E) {
+    send_base[e] = s_start[e] + s_before[e];
+    if (e / el == me) {
+      const int l = e - me * el;
+      prow0_loc[l] = s_start[e];
+      total_loc[l] = s_total[e];
+      const int t0 = s_start[e] >> 7, t1 = t0 + ((s_total[e] + 127) >> 7);
+      for (int vm = t0; vm < t1; ++vm) tile_expert_loc[vm] = l;
+    }
+  }
+}
+
+// One warp per local copy i = t*k + j: store x[t] into the owner's buffer, remember the row.
+__global__ void ep_dispatch_kernel(const __nv_bfloat16* __restrict__ x, long long ldx, const int* __restrict__ idx,
+                                   const float* __restrict__ w, const int* __restrict__ dest_src,
+                                   const int* __restrict__ prow0_src, const int* __restrict__ send_base, int n, int k,
+                                   int H, int el, int cap, void* const* __restrict__ peer_x,
+                                   float* const* __restrict__ peer_w, int* __restrict__ copy_row, int* status) {
+  const int vec = H >> 3;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int i = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; i < n; i += warps) {
+    const int e = idx[i];
+    const int d = e / el;
+    const int row = send_base[e] + (dest_src[i] - prow0_src[e]);
+    if (row >= cap) {  // the owner's buffer is too small for this routing: drop the copy, flag it
+      if (lane == 0) {
+        copy_row[i] = -1;
+        atomicCAS(status, 0, 5 /* kErrBounds */);
+      }
+      continue;
+    }
+    const uint4* in = reinterpret_cast<const uint4*>(x + static_cast<long long>(i / k) * ldx);
+    uint4* out = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(peer_x[d]) + static_cast<long long>(row) * H);
+    for (int c = lane; c < vec; c += 32) out[c] = in[c];
+    if (lane == 0) {
+      copy_row[i] = row;
+      if (w) peer_w[d][row] = w[i];
+    }
+  }
+}
+
+// Owner side: zero the padding rows of every local expert segment (peers only write real rows).
+__global__ void ep_zero_pad_kernel(__nv_bfloat16* __restrict__ xbuf, float* __restrict__ row_w,
+                                   const int* __restrict__ prow0_loc, const int* __restrict__ total_loc, int el, int H) {
+  const int l = blockIdx.x;
+  if (l >= el) return;
+  const int r0 = prow0_loc[l] + total_loc[l], r1 = prow0_loc[l + 1];
+  const int vec = H >> 3;
+  for (int r = r0 + (threadIdx.x >> 5); r < r1; r += blockDim.x >> 5) {
+    uint4* o = reinterpret_cast<uint4*>(xbuf + static_cast<long long>(r) * H);
+    for (int c = threadIdx.x & 31; c < vec; c += 32) o[c] = make_uint4(0, 0, 0, 0);
+    if ((threadIdx.x & 31) == 0 && row_w) row_w[r] = 0.f;
+  }
+}
+
+// out[t] = sum_j w[t,j] * y_owner(t,j)[row(t,j)], rows read from the owners' buffers over NVLink.
+__global__ void ep_combine_kernel(void* const* __restrict__ peer_y, const int* __restrict__ idx,
+                                  const int* __restrict__ copy_row, const float* __restrict__ w, int T, int k, int H,
+                                  int el, __nv_bfloat16* __restrict__ out) {
+  const int vec = H >> 3;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int t = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; t < T; t += warps) {
+    for (int c = lane; c < vec; c += 32) {
+      float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+      for (int j = 0; j < k; ++j) {
+        const int r = copy_row[t * k + j];
+        if (r < 0) continue;
+        const int d = idx[t * k + j] / el;
+        const float s = w ? w[t * k + j] : 1.f;
+        const uint4 v = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(peer_y[d]) +
+                                                       static_cast<long long>(r) * H)[c];
+        const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          const float2 f = __bfloat1622float2(b[q]);
+          acc[2 * q] += s * f.x;
+          acc[2 * q + 1] += s * f.y;
+        }
+      }
+      uint4 o;
+      __nv_bfloat162* ob = reinterpret_cast<__nv_bfloat162*>(&o);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) ob[q] = __floats2bfloat162_rn(acc[2 * q], acc[2 * q + 1]);
+      reinterpret_cast<uint4*>(out + static_cast<long long>(t) * H)[c] = o;
+    }
+  }
+}
+
+// vals[i] = peer_s(owner of copy i)[row(i)]
+__global__ void ep_pull_scalar_kernel(float* const* __restrict__ peer_s, const int* __restrict__ idx,
+                                      const int* __restrict__ copy_row, int n, int el, float* __restrict__ vals) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= n) return;
+  const int r = copy_row[i];
+  vals[i] = r < 0 ? 0.f : peer_s[idx[i] / el][r];
+}
+
+// s[r] = <a[r], b[r]> and (optionally) a[r] *= scale[r], for the rows in use (num_vm * 128).
+__global__ void rowdot_scale_kernel(__nv_bfloat16* __restrict__ a, const __nv_bfloat16* __restrict__ b,
+                                    const float* __restrict__ scale, const int* __restrict__ num_vm, int H,
+                                    float* __restrict__ s_out) {
+  const int rows = *num_vm * 128;
+  const int vec = H >> 3;
+  const int warps = (gridDim.x * blockDim.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  for (int r = (blockIdx.x * blockDim.x + threadIdx.x) >> 5; r < rows; r += warps) {
+    uint4* pa = reinterpret_cast<uint4*>(a + static_cast<long long>(r) * H);
+    const uint4* pb = reinterpret_cast<const uint4*>(b + static_cast<long long>(r) * H);
+    const float sc = scale ? scale[r] : 1.f;
+    float s = 0.f;
+    for (int c = lane; c < vec; c += 32) {
+      uint4 va = pa[c];
+      const uint4 vb = pb[c];
+      __nv_bfloat162* xa = reinterpret_cast<__nv_bfloat162*>(&va);
+      const __nv_bfloat162* xb = reinterpret_cast<const __nv_bfloat162*>(&vb);
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const float2 fa = __bfloat1622float2(xa[q]), fb = __bfloat1622float2(xb[q]);
+        s += fa.x * fb.x + fa.y * fb.y;
+        xa[q] = __floats2bfloat162_rn(fa.x * sc, fa.y * sc);
+      }
+      if (scale) pa[c] = va;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if (lane == 0 && s_out) s_out[r] = s;
+  }
+}
+
 }  // namespace b200
 
 extern "C" {
@@ -320,6 +495,82 @@ int b200_moe_combine_dw(const void* dout, const void* y, const int* dest, int n,
   if (grid > maxg) grid = maxg;
   moe_combine_dw_kernel<<<(unsigned)grid, 256, 0, stream>>>((const __nv_bfloat16*)dout, (const __nv_bfloat16*)y, dest,
                                                            n, k, H, dw);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int b200_ep_plan(const int* counts_all, int me, int P, int E, int* send_base, int* prow0_loc, int* total_loc,
+                 int* tile_expert_loc, int* num_vm, cudaStream_t stream) {
+  using namespace b200;
+  if (E > kMaxE || E % P || P > E) return -100;
+  ep_plan_kernel<<<1, ((E + 31) / 32) * 32, 0, stream>>>(counts_all, me, P, E, send_base, prow0_loc, total_loc,
+                                                         tile_expert_loc, num_vm);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// peer_x / peer_w: device arrays of P pointers (the owners' row buffers [cap, H] bf16 and row weights [cap]).
+int b200_ep_dispatch(const void* x, long long ldx, const int* idx, const float* w, const int* dest_src,
+                     const int* prow0_src, const int* send_base, int n, int k, int H, int experts_per_rank, int cap,
+                     void* const* peer_x, float* const* peer_w, int* copy_row, cudaStream_t stream) {
+  using namespace b200;
+  if (H % 8) return -100;
+  if (n == 0) return 0;
+  int* status = device_status_word();
+  if (!status) return -3;
+  long long grid = (static_cast<long long>(n) * 32 + 255) / 256;
+  const long long maxg = static_cast<long long>(sm_count()) * 16;
+  if (grid > maxg) grid = maxg;
+  ep_dispatch_kernel<<<(unsigned)grid, 256, 0, stream>>>((const __nv_bfloat16*)x, ldx, idx, w, dest_src, prow0_src,
+                                                        send_base, n, k, H, experts_per_rank, cap, peer_x, peer_w,
+                                                        copy_row, status);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int b200_ep_zero_pad(void* xbuf, float* row_w, const int* prow0_loc, const int* total_loc, int experts_per_rank, int H,
+                     cudaStream_t stream) {
+  using namespace b200;
+  ep_zero_pad_kernel<<<experts_per_rank, 256, 0, stream>>>((__nv_bfloat16*)xbuf, row_w, prow0_loc, total_loc,
+                                                           experts_per_rank, H);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int b200_ep_combine(void* const* peer_y, const int* idx, const int* copy_row, const float* w, int T, int k, int H,
+                    int experts_per_rank, void* out, cudaStream_t stream) {
+  using namespace b200;
+  if (H % 8) return -100;
+  if (T == 0) return 0;
+  long long grid = (static_cast<long long>(T) * 32 + 255) / 256;
+  const long long maxg = static_cast<long long>(sm_count()) * 16;
+  if (grid > maxg) grid = maxg;
+  ep_combine_kernel<<<(unsigned)grid, 256, 0, stream>>>(peer_y, idx, copy_row, w, T, k, H, experts_per_rank,
+                                                       (__nv_bfloat16*)out);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int b200_ep_pull_scalar(float* const* peer_s, const int* idx, const int* copy_row, int n, int experts_per_rank,
+                        float* vals, cudaStream_t stream) {
+  using namespace b200;
+  if (n == 0) return 0;
+  ep_pull_scalar_kernel<<<(n + 255) / 256, 256, 0, stream>>>(peer_s, idx, copy_row, n, experts_per_rank, vals);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// s_out[r] = <a[r], b[r]> (s_out may be null), then a[r] *= scale[r] (scale may be null), rows < *num_vm * 128.
+int b200_rowdot_scale(void* a, const void* b, const float* scale, const int* num_vm, int max_rows, int H, float* s_out,
+                      cudaStream_t stream) {
+  using namespace b200;
+  if (H % 8) return -100;
+  if (max_rows == 0) return 0;
+  long long grid = (static_cast<long long>(max_rows) * 32 + 255) / 256;
+  const long long maxg = static_cast<long long>(sm_count()) * 16;
+  if (grid > maxg) grid = maxg;
+  rowdot_scale_kernel<<<(unsigned)grid, 256, 0, stream>>>((__nv_bfloat16*)a, (const __nv_bfloat16*)b, scale, num_vm, H,
+                                                         s_out);
   B200_CHECK(cudaGetLastError());
   return 0;
 }

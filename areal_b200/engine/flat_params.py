@@ -38,11 +38,13 @@ _ALIGN = 64  # elements: 128 bytes in bf16, 256 in fp32
 
 class FlatParams:
     def __init__(self, model: torch.nn.Module, dp_group: dist.ProcessGroup | None, with_grads: bool = True,
-                 replicated_first=None):
+                 replicated_first=None, select=None):
         """``replicated_first(name) -> bool`` marks parameters that are replicated over a
         tensor-parallel group; they are laid out first, so ``flat[:rep_numel]`` is one contiguous
         region (their gradients need one extra all-reduce over that group)."""
-        params = [p for p in model.parameters()]
+        # ``select(name) -> bool`` restricts the buffer to some parameters (e.g. expert weights, which
+        # are reduced over a different group than the rest of the model)
+        params = [p for n, p in model.named_parameters() if select is None or select(n)]
         assert params, "model has no parameters"
         self.model = model
         self.device = params[0].device
@@ -54,7 +56,7 @@ class FlatParams:
         self.entries: list[tuple[str, torch.nn.Parameter, int, int]] = []
         off = 0
         seen: dict[int, int] = {}
-        named = list(model.named_parameters())
+        named = [(n, p) for n, p in model.named_parameters() if select is None or select(n)]
         self.rep_numel = 0
         if replicated_first is not None:
             named = [x for x in named if replicated_first(x[0])] + [x for x in named if not replicated_first(x[0])]
@@ -137,6 +139,8 @@ class ShardedAdamW:
         self.tp_group = tp_group
         self.tp_size = dist.get_world_size(tp_group) if (tp_group is not None and dist.is_initialized()) else 1
         self.tp_full_grad = tp_full_grad
+        self.partner: "ShardedAdamW | None" = None  # a second optimizer (expert weights) clipped by the same norm
+        self.partner_group = None        # group over which the partner's parameters are disjoint (ep group)
         self.norm_groups: list = []      # further groups that hold disjoint parameters (pipeline stages)
         self.pre_step_hooks: list = []   # run after the autograd gradients were collected
         self.total_steps = total_steps
@@ -173,12 +177,33 @@ class ShardedAdamW:
                 if name.endswith(self.tp_full_grad):
                     p.main_grad.div_(self.tp_size)
             dist.all_reduce(self.flat.main_grad[:self.flat.rep_numel], group=self.tp_group)
-        out = self._step_cuda(grad_scale) if self.flat.cuda else self._step_torch(grad_scale)
+        partner = self.partner
+        if partner is not None:
+            partner.flat.collect_autograd_grads()
+        # phase 1: reduce gradients over the data-parallel group(s), squared norm of every part
+        nsq = self._reduce(grad_scale)
+        if partner is not None:
+            pn = partner._reduce(grad_scale)
+            if self.partner_group is not None:
+                dist.all_reduce(pn, group=self.partner_group)  # the partner's parameters differ across this group
+            nsq.add_(pn)
+            pn.copy_(nsq)
+        # phase 2: clip by the global norm, AdamW, publish the new weights
+        out = self._update(nsq)
+        if partner is not None:
+            partner._update(pn)
+            partner.flat.zero_grad()
         self.flat.zero_grad()
         return out
 
+    def _reduce(self, grad_scale: float) -> torch.Tensor:
+        return self._reduce_cuda(grad_scale) if self.flat.cuda else self._reduce_torch(grad_scale)
+
+    def _update(self, nsq: torch.Tensor) -> dict[str, float]:
+        return self._update_cuda() if self.flat.cuda else self._update_torch(nsq)
+
     # ---------------------------------------------------------------- CUDA
-    def _step_cuda(self, grad_scale: float) -> dict[str, float]:
+    def _reduce_cuda(self, grad_scale: float) -> torch.Tensor:
         f, cfg = self.flat, self.cfg
         lib = _lib.kernels()
         world = f.dp_world
@@ -198,6 +223,14 @@ class ShardedAdamW:
             dist.all_reduce(self._norm, group=self.tp_group)
         for g in self.norm_groups:
             dist.all_reduce(self._norm, group=g)
+        _lib.count_launch()
+        return self._norm
+
+    def _update_cuda(self) -> dict[str, float]:
+        """Consumes ``self._norm`` (the global squared gradient norm, on the device)."""
+        f, cfg = self.flat, self.cfg
+        lib = _lib.kernels()
+        world = f.dp_world
         t = self.step_count + 1
         lr = self.lr
         self._skipped.zero_()
@@ -210,7 +243,7 @@ class ShardedAdamW:
                                   ctypes.c_float(1 - cfg.beta2 ** t), ctypes.c_float(cfg.gradient_clipping),
                                   _lib.ptr(self._skipped), _lib.stream_ptr())
         _lib.check(rc, "b200_adamw_bcast")
-        _lib.count_launch(2)
+        _lib.count_launch()
         if world > 1:
             f.barrier.sync()  # all shards of the new weights have landed everywhere
         vals = torch.cat([self._norm, self._skipped.float()]).tolist()
@@ -232,7 +265,7 @@ class ShardedAdamW:
             nsq.sub_(rep * (self.tp_size - 1) / self.tp_size)
 
     # --------------------------------------------------------------- torch
-    def _step_torch(self, grad_scale: float) -> dict[str, float]:
+    def _reduce_torch(self, grad_scale: float) -> torch.Tensor:
         f, cfg = self.flat, self.cfg
         g = f.main_grad
         if f.dp_world > 1:
@@ -247,6 +280,11 @@ class ShardedAdamW:
             dist.all_reduce(nsq, group=self.tp_group)
         for g in self.norm_groups:
             dist.all_reduce(nsq, group=g)
+        return nsq
+
+    def _update_torch(self, nsq: torch.Tensor) -> dict[str, float]:
+        f, cfg = self.flat, self.cfg
+        o, n = f.shard_offset, f.shard_numel
         norm = float(nsq.sqrt())
         lr = self.lr
         if not math.isfinite(norm):

@@ -104,7 +104,7 @@ class B200TrainEngine(TrainEngine):
         self.mesh = None
         self.pctx = None
         ps = self.parallel
-        model_parallel = ps.tp_size * ps.cp_size * ps.pp_size > 1
+        model_parallel = ps.tp_size * ps.cp_size * ps.pp_size * ps.ep_size > 1
         if model_parallel:
             assert dist.is_initialized(), "tensor / sequence / pipeline parallelism needs torch.distributed"
             from ..parallel.context import build_mesh
@@ -115,7 +115,7 @@ class B200TrainEngine(TrainEngine):
             self.train_ranks = ranks
             dp = len(ranks) // (ps.tp_size * ps.cp_size * ps.pp_size)
             # context_parallel_size is Ulysses sequence parallelism for this engine family
-            self.mesh = build_mesh(ranks, dp=dp, sp=ps.cp_size, tp=ps.tp_size, pp=ps.pp_size)
+            self.mesh = build_mesh(ranks, dp=dp, sp=ps.cp_size, tp=ps.tp_size, pp=ps.pp_size, ep=ps.ep_size)
             self.pctx = self.mesh.ctx
             # parameters are sharded (ZeRO) over dp x sp: those ranks hold the same weights
             self._dp_group = self.mesh.shard_group
@@ -210,12 +210,31 @@ class B200TrainEngine(TrainEngine):
             from ..parallel.tensor_parallel import is_tp_replicated
 
             rep_first = is_tp_replicated
+        ep = pctx.ep_size if pctx is not None else 1
+        is_expert = (lambda n: n.endswith(("mlp.gate_up", "mlp.down")) and ".mlp." in n and
+                     dict(self.model.named_parameters())[n].dim() == 3)
         self.flat = FlatParams(self.model, self._dp_group, with_grads=self.optimizer_config is not None,
-                               replicated_first=rep_first)
+                               replicated_first=rep_first, select=(lambda n: not is_expert(n)) if ep > 1 else None)
+        self.flat_experts = None
+        if ep > 1:
+            # expert weights differ across the ep group: they are reduced only over the ranks that hold
+            # the same experts, and live in a flat buffer (and optimizer) of their own
+            edp = self.mesh.edp_group if self.mesh.edp_size > 1 else "local"
+            self.flat_experts = FlatParams(self.model, edp, with_grads=self.optimizer_config is not None,
+                                           select=is_expert)
+            if self.device.type == "cuda":
+                from ..parallel.expert_parallel import EPGroupState
+
+                mc = self.model_config
+                cap = int((self.config.mb_spec.max_tokens_per_mb or 32768) * mc.num_experts_per_tok * 2)
+                pctx.extras["ep_state"] = EPGroupState(pctx.ep_group, mc.num_experts, mc.hidden_size, cap, self.device)
         if self.optimizer_config is not None:
             total = ft_spec.total_train_steps if ft_spec is not None else 1
             self.optimizer = ShardedAdamW(self.flat, self.optimizer_config, total_steps=total,
                                           tp_group=pctx.tp_group if tp > 1 else None)
+            if self.flat_experts is not None:
+                self.optimizer.partner = ShardedAdamW(self.flat_experts, self.optimizer_config, total_steps=total)
+                self.optimizer.partner_group = pctx.ep_group
             if pctx is not None and pctx.pp_size > 1:
                 self.optimizer.norm_groups.append(pctx.pp_group)
                 if self.model_config.tie_word_embeddings and not self.is_critic and self.model.embed is not None:

@@ -152,6 +152,10 @@ PRESETS: dict[str, ModelConfig] = {
                               intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
                               num_key_value_heads=2, head_dim=64, rope_theta=1e4,
                               tie_word_embeddings=False, attention_bias=True, qk_norm=False),
+    "tiny-qwen3-moe": ModelConfig(model_type="qwen3_moe", vocab_size=1024, hidden_size=256, intermediate_size=512,
+                                  num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                                  rope_theta=1e4, tie_word_embeddings=False, num_experts=8, num_experts_per_tok=2,
+                                  moe_intermediate_size=128),
     "qwen3-1.7b": ModelConfig(model_type="qwen3", hidden_size=2048, intermediate_size=6144,
                               num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
                               tie_word_embeddings=True),

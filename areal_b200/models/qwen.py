@@ -111,9 +111,12 @@ class MoEMLP(nn.Module):
         self.cfg = cfg
         self.pctx = pctx
         E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
+        ep = pctx.ep_size if pctx is not None else 1
+        assert E % ep == 0, "the expert count must divide by the expert-parallel size"
         self.router = nn.Parameter(torch.empty(E, H, dtype=dtype, device=device))
-        self.gate_up = nn.Parameter(torch.empty(E, 2 * I, H, dtype=dtype, device=device))
-        self.down = nn.Parameter(torch.empty(E, H, I, dtype=dtype, device=device))
+        # under expert parallelism this rank owns experts [ep_rank * E/ep, (ep_rank + 1) * E/ep)
+        self.gate_up = nn.Parameter(torch.empty(E // ep, 2 * I, H, dtype=dtype, device=device))
+        self.down = nn.Parameter(torch.empty(E // ep, H, I, dtype=dtype, device=device))
         self.last_routing = None  # (topk_idx, topk_w) of the last forward, for stats / replay
 
     def route(self, x):
@@ -134,6 +137,11 @@ class MoEMLP(nn.Module):
 
         idx, w = self.route(x)
         self.last_routing = (idx.detach(), w.detach())
+        p = self.pctx
+        if p is not None and p.ep_size > 1:
+            from ..parallel.expert_parallel import ep_moe_forward
+
+            return ep_moe_forward(x, idx, w, self.gate_up, self.down, p.extras.get("ep_state", p.ep_group))
         return moe_experts_forward(x, idx, w, self.gate_up, self.down)
 
 
@@ -209,6 +217,10 @@ class QwenModel(nn.Module):
                 p.zero_()
                 continue
             dst = p
+            ep = self.pctx.ep_size if self.pctx is not None else 1
+            is_expert = ep > 1 and name.endswith(("mlp.gate_up", "mlp.down")) and p.dim() == 3
+            if is_expert:
+                dst = torch.empty((p.shape[0] * ep,) + tuple(p.shape[1:]), dtype=p.dtype, device=p.device)
             if tp > 1:
                 # draw the FULL tensor (so values do not depend on the tp size), keep this rank's shard
                 from ..parallel.tensor_parallel import is_tp_replicated, tp_slice
@@ -227,7 +239,10 @@ class QwenModel(nn.Module):
                 for s in range(0, flat.numel(), chunk):
                     n = min(chunk, flat.numel() - s)
                     flat[s:s + n].copy_(torch.empty(n, dtype=torch.float32).normal_(0.0, std, generator=g))
-            if dst is not p:
+            if is_expert:
+                n = p.shape[0]
+                p.copy_(dst[self.pctx.ep_rank * n:(self.pctx.ep_rank + 1) * n])
+            elif dst is not p:
                 p.copy_(tp_slice(name, dst, self.cfg, tp_rank, tp))
         return self
 

@@ -1,0 +1,245 @@
+"""Kernel micro-benchmarks with roofline fractions.
+
+    python -m areal_b200.ops.microbench gemm [--small] [--iters N]
+    python -m areal_b200.ops.microbench all
+
+Each benchmark times one op of this library with CUDA events on the launching stream (after
+warm-up, synchronised on both sides; an L2-sized buffer is rewritten between iterations unless
+the working set already exceeds L2), and prints one JSON line: milliseconds, the algorithmic
+FLOP/s or bytes/s, and that figure as a fraction of the measured peaks (``MEASURED_PEAKS.json``
+at the repository root when present: cuBLAS bf16 burst throughput and copy bandwidth; otherwise
+the documented fall-back figures). ``--small`` shrinks the case to a few hundred MB so that a
+profiler capture of one launch finishes quickly.
+"""
+
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+
+import torch
+
+FALLBACK = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks() -> dict:
+    path = os.path.join(os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__)))),
+                        "MEASURED_PEAKS.json")
+    try:
+        with open(path) as f:
+            d = json.load(f)
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+    except (OSError, KeyError, ValueError):
+        return dict(FALLBACK, source="fallback")
+
+
+_FLUSH = None
+
+
+def timeit(fn, iters: int, warm: int = 3, flush: bool = True) -> float:
+    """Mean milliseconds per call."""
+    global _FLUSH
+    if flush and _FLUSH is None:
+        _FLUSH = torch.empty(192 << 20, dtype=torch.uint8, device="cuda")
+    for _ in range(warm):
+        fn()
+    torch.cuda.synchronize()
+    total = 0.0
+    for _ in range(iters):
+        if flush:
+            _FLUSH.zero_()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        fn()
+        e.record()
+        torch.cuda.synchronize()
+        total += s.elapsed_time(e)
+    return total / iters
+
+
+def report(name: str, ms: float, flops: float = 0.0, nbytes: float = 0.0, **extra):
+    pk = peaks()
+    out = {"op": name, "ms": round(ms, 4)}
+    if flops:
+        tf = flops / ms / 1e9
+        out.update(tflops=round(tf, 1), frac_of_bf16_peak=round(tf / pk["bf16_tflops"], 3))
+    if nbytes:
+        gbs = nbytes / ms / 1e6
+        out.update(gbs=round(gbs, 1), frac_of_hbm_peak=round(gbs / pk["hbm_gbs"], 3))
+    out["peaks"] = pk["source"]
+    out.update(extra)
+    print(json.dumps(out), flush=True)
+    return out
+
+
+def bench_gemm(a):
+    from .gemm import gemm
+
+    M, N, K = (2048, 4096, 4096) if a.small else (8192, 8192, 8192)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = torch.randn(N, K, device="cuda").bfloat16()
+    ms = timeit(lambda: gemm(x, w), a.iters)
+    report("gemm_bf16", ms, flops=2.0 * M * N * K, shape=[M, N, K])
+    dy = torch.randn(M, N, device="cuda").bfloat16()
+    ms = timeit(lambda: gemm(dy, w, b_mn=True), a.iters)
+    report("gemm_bf16_dgrad", ms, flops=2.0 * M * N * K, shape=[M, K, N])
+    ms = timeit(lambda: gemm(dy, x, a_mn=True, b_mn=True), a.iters)
+    report("gemm_bf16_wgrad", ms, flops=2.0 * M * N * K, shape=[N, K, M])
+
+
+def bench_gemm_fp8(a):
+    from . import fp8
+
+    M, N, K = (2048, 4096, 4096) if a.small else (8192, 8192, 8192)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    a8, sa = fp8.quant_fp8_1x128(x)
+    b8, sb = fp8.quant_fp8_block128(w)
+    ms = timeit(lambda: fp8.gemm_fp8_block(a8, sa, b8, sb), a.iters)
+    report("gemm_fp8_block", ms, flops=2.0 * M * N * K, shape=[M, N, K])
+    ms = timeit(lambda: fp8.quant_fp8_1x128(x), a.iters)
+    report("quant_fp8_1x128", ms, nbytes=M * K * 3.0)
+    ms = timeit(lambda: fp8.quant_fp8_block128(w), a.iters)
+    report("quant_fp8_block128", ms, nbytes=N * K * 3.0)
+
+
+def bench_grouped_gemm(a):
+    from . import moe
+
+    T, E, k, H, I = (4096, 32, 4, 2048, 768) if a.small else (16384, 128, 8, 2048, 768)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    gate_up = (torch.randn(E, 2 * I, H, device="cuda") * H ** -0.5).bfloat16()
+    idx, w = moe.route(torch.randn(T, E, device="cuda"), k, True)
+    s = moe.sort_by_expert(idx, E)
+    xs = moe.gather_rows(x, s)
+    ms = timeit(lambda: moe.grouped_gemm(xs, gate_up, s), a.iters)
+    report("grouped_gemm_fwd", ms, flops=2.0 * T * k * 2 * I * H, experts=E, rows=T * k)
+    dy = torch.randn(s.max_rows, 2 * I, device="cuda").bfloat16()
+    ms = timeit(lambda: moe.grouped_wgrad(dy, xs, s), a.iters)
+    report("grouped_gemm_wgrad", ms, flops=2.0 * T * k * 2 * I * H, experts=E)
+    ms = timeit(lambda: moe.sort_by_expert(idx, E), a.iters)
+    report("moe_sort", ms, nbytes=T * k * 12.0)
+    ms = timeit(lambda: moe.gather_rows(x, s), a.iters)
+    report("moe_gather", ms, nbytes=T * k * H * 2.0 + T * H * 2.0)
+
+
+def _attn_inputs(a):
+    from .attention import VarlenMeta
+
+    nseq, L = (4, 4096) if a.small else (8, 8192)
+    Hq, Hkv, D = 16, 8, 128
+    T = nseq * L
+    q = torch.randn(T, Hq, D, device="cuda").bfloat16().requires_grad_()
+    k = torch.randn(T, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    v = torch.randn(T, Hkv, D, device="cuda").bfloat16().requires_grad_()
+    meta = VarlenMeta([i * L for i in range(nseq + 1)], "cuda")
+    flops = 4.0 * nseq * L * L / 2 * Hq * D
+    return q, k, v, meta, flops
+
+
+def bench_attn(a):
+    from .attention import varlen_attention
+
+    q, k, v, meta, flops = _attn_inputs(a)
+    with torch.no_grad():
+        ms = timeit(lambda: varlen_attention(q, k, v, meta), a.iters)
+    report("attn_fwd", ms, flops=flops)
+    out = varlen_attention(q, k, v, meta)
+    do = torch.randn_like(out)
+    ms = timeit(lambda: torch.autograd.grad(out, (q, k, v), do, retain_graph=True), a.iters)
+    report("attn_bwd", ms, flops=2.5 * flops)
+
+
+def bench_lm_head(a):
+    from .lm_head import lm_head_logprobs
+
+    T, H, V = (4096, 2048, 151936) if a.small else (16384, 2048, 151936)
+    x = torch.randn(T, H, device="cuda").bfloat16().requires_grad_()
+    w = (torch.randn(V, H, device="cuda") * 0.02).bfloat16().requires_grad_()
+    labels = torch.randint(0, V, (T,), device="cuda")
+    with torch.no_grad():
+        ms = timeit(lambda: lm_head_logprobs(x, w, labels), a.iters)
+    report("lm_head_fwd", ms, flops=2.0 * T * H * V)
+    lp, ent = lm_head_logprobs(x, w, labels)
+    g = torch.randn_like(lp)
+    ms = timeit(lambda: torch.autograd.grad(lp, (x, w), g, retain_graph=True), a.iters)
+    report("lm_head_bwd", ms, flops=6.0 * T * H * V)  # logits recompute + dx + dw
+
+
+def bench_decode(a):
+    from . import rollout_ops
+
+    B, ctx = (64, 2000) if a.small else (320, 2000)
+    Hq, Hkv, D, bs = 16, 8, 128, 16
+    nb_per = (ctx + bs - 1) // bs
+    nb = B * nb_per
+    kc = torch.randn(nb, Hkv, bs, D, device="cuda").bfloat16()
+    vc = torch.randn_like(kc)
+    bt = torch.randperm(nb, device="cuda").int().view(B, nb_per)
+    sl = torch.randint(ctx // 2, ctx + 1, (B,), device="cuda", dtype=torch.int32)
+    q = torch.randn(B, Hq, D, device="cuda").bfloat16()
+    nbytes = float(sl.sum()) * Hkv * D * 2 * 2
+    ms = timeit(lambda: rollout_ops.paged_decode(q, kc, vc, bt, sl, max_seq_len=ctx), a.iters, flush=False)
+    report("paged_decode", ms, nbytes=nbytes, batch=B, ctx=ctx)
+
+
+def bench_elementwise(a):
+    from . import fused
+
+    T, H, I = (8192, 2048, 6144) if a.small else (65536, 2048, 6144)
+    x = torch.randn(T, H, device="cuda").bfloat16()
+    r = torch.randn(T, H, device="cuda").bfloat16()
+    w = torch.ones(H, device="cuda").bfloat16()
+    with torch.no_grad():
+        ms = timeit(lambda: fused.rmsnorm(x, w, 1e-6, residual=r), a.iters)
+        report("rmsnorm_residual_fwd", ms, nbytes=T * H * 2.0 * 4)
+        gu = torch.randn(T, 2 * I, device="cuda").bfloat16()
+        ms = timeit(lambda: fused.swiglu(gu), a.iters)
+        report("swiglu_fwd", ms, nbytes=T * I * 2.0 * 3)
+
+
+def bench_sampler(a):
+    from .rollout_ops import sample
+
+    B, V = (64, 151936) if a.small else (512, 151936)
+    logits = torch.randn(B, V, device="cuda")
+    temp = torch.ones(B, device="cuda")
+    u = torch.rand(B, device="cuda")
+    ms = timeit(lambda: sample(logits, temp, None, None, u), a.iters)
+    report("sampler", ms, nbytes=B * V * 4.0, batch=B)
+
+
+def bench_ppo_loss(a):
+    from .rl_ops import ppo_loss_fused
+
+    T = (1 << 20) if a.small else (1 << 24)
+    mk = lambda: torch.randn(T, device="cuda") * 0.1
+    logp, old, prox, adv = mk().requires_grad_(), mk(), mk(), mk()
+    mask = (torch.rand(T, device="cuda") > 0.3).float()
+    denom = float(mask.sum())
+    with torch.no_grad():
+        ms = timeit(lambda: ppo_loss_fused(logp, prox, old, adv, mask, eps_clip=0.2, denom=denom), a.iters)
+    report("ppo_loss", ms, nbytes=T * 4.0 * 5)
+
+
+BENCHES = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "grouped_gemm": bench_grouped_gemm, "attn": bench_attn,
+           "lm_head": bench_lm_head, "decode": bench_decode, "elementwise": bench_elementwise,
+           "sampler": bench_sampler, "ppo_loss": bench_ppo_loss}
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
+    ap.add_argument("op", choices=sorted(BENCHES) + ["all"])
+    ap.add_argument("--small", action="store_true")
+    ap.add_argument("--iters", type=int, default=10)
+    a = ap.parse_args(argv)
+    if not torch.cuda.is_available():
+        raise SystemExit("microbench needs a CUDA device")
+    for name in (sorted(BENCHES) if a.op == "all" else [a.op]):
+        BENCHES[name](a)
+
+
+if __name__ == "__main__":
+    main()

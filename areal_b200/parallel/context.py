@@ -87,9 +87,15 @@ class MeshGroups:
     cpu_shard_group: Any = None
     mp_group: Any = None  # every rank of one data-parallel replica (tp x sp x pp): they share a batch
     mp_rank: int = 0
+    # expert parallelism: ep groups are blocks of consecutive ranks of the shard group; ranks with the
+    # same position in different blocks hold the same experts (expert-data-parallel group)
+    edp_group: Any = None
+    edp_rank: int = 0
+    edp_size: int = 1
 
 
-def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1, cpu_groups: bool = True) -> MeshGroups:
+def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1, cpu_groups: bool = True,
+               ep: int = 1) -> MeshGroups:
     """Creates every group of a ``pp x dp x sp x tp`` mesh over ``ranks``. Collective over the
     WHOLE world (``dist.new_group`` semantics): every process must call it with the same arguments,
     whether or not it belongs to ``ranks``."""
@@ -123,6 +129,9 @@ def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1,
     sh_g = make(lambda p, d, s, t: (p, t))
     mp_g = make(lambda p, d, s, t: d)
     pp_g = make(lambda p, d, s, t: (d, s, t))
+    assert (dp * sp) % ep == 0, "the expert-parallel size must divide dp x sp"
+    ep_g = make(lambda p, d, s, t: (p, t, (d * sp + s) // ep)) if ep > 1 else (None, 0, 1)
+    edp_g = make(lambda p, d, s, t: (p, t, (d * sp + s) % ep)) if ep > 1 else (None, 0, 1)
     tie_g = (None, 0, 1)
     if pp > 1 and dist.is_initialized():
         stride = dp * sp * tp
@@ -157,4 +166,7 @@ def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1,
         ctx.pp_group, ctx.pp_rank, ctx.pp_size = pp_g[0], p, pp
         ctx.pp_prev, ctx.pp_next = mesh.pp_prev, mesh.pp_next
         ctx.pp_tie_group = tie_g[0]
+    if ep > 1:
+        ctx.ep_group, ctx.ep_rank, ctx.ep_size = ep_g
+        mesh.edp_group, mesh.edp_rank, mesh.edp_size = edp_g
     return mesh

@@ -11,9 +11,9 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "torchrun", "run_model_parallel.py")
 
 
-def _ref(tmp_path, critic=False, n_mbs=1):
+def _ref(tmp_path, critic=False, n_mbs=1, preset="tiny-qwen2"):
     f = str(tmp_path / ("ref_c.pt" if critic else "ref.pt"))
-    cmd = [sys.executable, WORKER, "--ref", "--n-mbs", str(n_mbs), f] + (["--critic"] if critic else [])
+    cmd = [sys.executable, WORKER, "--ref", "--n-mbs", str(n_mbs), "--preset", preset, f] + (["--critic"] if critic else [])
     env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
@@ -42,3 +42,10 @@ def test_pipeline_step_matches_single_process(tmp_path, n, args):
     """Two micro-batches through a two-stage pipeline (alone and with tensor parallelism inside
     each stage)."""
     _run(n, 29660 + n, args + ["--n-mbs", "2"], _ref(tmp_path, n_mbs=2))
+
+
+@pytest.mark.parametrize("n,ep", [(2, 2), (4, 2)])
+def test_expert_parallel_step_matches_single_process(tmp_path, n, ep):
+    """MoE model with the experts split over the ep group (tokens gathered / partial outputs summed
+    on gloo; expert weights in their own flat buffer, clipped by the joint gradient norm)."""
+    _run(n, 29670 + n, ["--ep", str(ep), "--preset", "tiny-qwen3-moe"], _ref(tmp_path, preset="tiny-qwen3-moe"))

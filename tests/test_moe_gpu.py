@@ -107,3 +107,58 @@ def test_wgrad_accumulates_into_main_grad():
     assert gate_up.grad is None and down.grad is None
     torch.testing.assert_close(gate_up.main_grad - 1, g_ref, rtol=2e-2, atol=2e-2)
     torch.testing.assert_close(down.main_grad - 1, d_ref, rtol=2e-2, atol=2e-2)
+
+
+def test_expert_parallel_phases_with_virtual_ranks():
+    """Four virtual ep ranks on one GPU (their buffers are ordinary allocations and the phases run
+    rank after rank on one stream, which stands in for the barriers): forward and backward must
+    equal every rank running ALL experts on its own tokens."""
+    from areal_b200.parallel.expert_parallel import EPRank
+
+    torch.manual_seed(5)
+    P, E, k, H, I = 4, 16, 2, 256, 128
+    Ts = [200, 333, 64, 129]
+    el = E // P
+    gate_up = (torch.randn(E, 2 * I, H, device="cuda") * H ** -0.5).bfloat16()
+    down = (torch.randn(E, H, I, device="cuda") * I ** -0.5).bfloat16()
+    ranks = [EPRank(r, P, E, H, cap_rows=2 * sum(Ts) * k // P + 256, device=torch.device("cuda")) for r in range(P)]
+    ptrs = [r.pointers() for r in ranks]
+    for r in ranks:
+        r.connect(ptrs)
+    xs = [torch.randn(T, H, device="cuda").bfloat16() for T in Ts]
+    routes = [moe.route_ref(torch.randn(T, E, device="cuda"), k, True) for T in Ts]
+    douts = [torch.randn(T, H, device="cuda").bfloat16() for T in Ts]
+    sorts = [moe.sort_by_expert(idx, E) for idx, _ in routes]
+    counts_all = torch.stack([s.counts for s in sorts])
+    plans = [r.plan(counts_all) for r in ranks]
+    copy_rows = [ranks[r].dispatch(xs[r], routes[r][0].reshape(-1).contiguous(), routes[r][1].reshape(-1).contiguous(),
+                                   sorts[r], plans[r]) for r in range(P)]
+    saved = [ranks[r].experts_forward(plans[r], gate_up[r * el:(r + 1) * el].contiguous(),
+                                      down[r * el:(r + 1) * el].contiguous()) for r in range(P)]
+    outs = [ranks[r].combine(routes[r][0].reshape(-1).contiguous(), copy_rows[r], routes[r][1].reshape(-1).contiguous(),
+                             Ts[r], k) for r in range(P)]
+    assert _lib.read_status() == 0
+    # backward
+    for r in range(P):
+        ranks[r].dispatch(douts[r], routes[r][0].reshape(-1).contiguous(), None, sorts[r], plans[r])
+    wgrads = [ranks[r].experts_backward(saved[r], gate_up[r * el:(r + 1) * el].contiguous(),
+                                        down[r * el:(r + 1) * el].contiguous()) for r in range(P)]
+    dxs = [ranks[r].combine(routes[r][0].reshape(-1).contiguous(), copy_rows[r], None, Ts[r], k) for r in range(P)]
+    dws = [ranks[r].pull_weight_grads(routes[r][0].reshape(-1).contiguous(), copy_rows[r]).view(Ts[r], k) for r in range(P)]
+    assert _lib.read_status() == 0
+
+    gr, dr = gate_up.float().requires_grad_(), down.float().requires_grad_()
+    def close(a, b, tol=3e-2):
+        err = (a.float() - b).abs().max().item()
+        assert err <= tol * (b.abs().max().item() + 1e-6), (err, b.abs().max().item())
+    for r in range(P):
+        xr, wr = xs[r].float().requires_grad_(), routes[r][1].float().requires_grad_()
+        ref = _ref_fp32(xr, routes[r][0].long(), wr, gr, dr)
+        ref.backward(douts[r].float())
+        close(outs[r], ref)
+        close(dxs[r], xr.grad)
+        close(dws[r], wr.grad)
+    d_gate_up = torch.cat([g[0] for g in wgrads]).float()
+    d_down = torch.cat([g[1] for g in wgrads]).float()
+    close(d_gate_up, gr.grad)
+    close(d_down, dr.grad)

@@ -44,11 +44,13 @@ def main():
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--sp", type=int, default=1)
     ap.add_argument("--pp", type=int, default=1)
+    ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--preset", default="tiny-qwen2")
     ap.add_argument("--n-mbs", type=int, default=1)
     ap.add_argument("--critic", action="store_true")
     args = ap.parse_args()
     cfg = TrainEngineConfig(experiment_name="t", trial_name="t", path="", init_from_scratch=True, dtype="float32",
-                            model_preset="tiny-qwen2", mb_spec=MicroBatchSpec(n_mbs=args.n_mbs), is_critic=args.critic,
+                            model_preset=args.preset, mb_spec=MicroBatchSpec(n_mbs=args.n_mbs), is_critic=args.critic,
                             optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0, gradient_clipping=1.0,
                                                       warmup_steps_proportion=0.0, lr_scheduler_type="constant"))
     eng = B200TrainEngine(cfg)
@@ -62,7 +64,8 @@ def main():
         world = dist.get_world_size()
         dp = world // (args.tp * args.sp * args.pp)
         eng.create_process_group(ParallelStrategy(tensor_parallel_size=args.tp, context_parallel_size=args.sp,
-                                                  pipeline_parallel_size=args.pp, data_parallel_size=dp))
+                                                  pipeline_parallel_size=args.pp, data_parallel_size=dp,
+                                                  expert_parallel_size=args.ep))
         eng.initialize(seed=3)
         d = eng.data_parallel_rank
         data = {k: v[d::dp] for k, v in batch.items()}
@@ -71,7 +74,11 @@ def main():
 
     def step(*a, **k):
         eng.flat.collect_autograd_grads()
-        for name, p, _, _ in eng.flat.entries:
+        entries = list(eng.flat.entries)
+        if getattr(eng, "flat_experts", None) is not None:
+            eng.flat_experts.collect_autograd_grads()
+            entries += list(eng.flat_experts.entries)
+        for name, p, _, _ in entries:
             captured[name] = p.main_grad.clone()
         return orig_step(*a, **k)
 
@@ -87,6 +94,13 @@ def main():
     full = {}
     for name, g in captured.items():
         g = g.clone()
+        if pctx.ep_size > 1 and g.dim() == 3 and ".mlp." in name:
+            if mesh.edp_size > 1:
+                dist.all_reduce(g, group=mesh.edp_group)
+            parts = [None] * pctx.ep_size
+            dist.all_gather_object(parts, g, group=pctx.ep_group)
+            full[name] = torch.cat(parts, 0)
+            continue
         if mesh.shard_size > 1:
             dist.all_reduce(g, group=mesh.shard_group)
         if pctx.tp_size > 1:
