@@ -46,21 +46,32 @@ def main():
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--preset", default="tiny-qwen2")
+    ap.add_argument("--device", default="cpu", choices=["cpu", "cuda"])
     ap.add_argument("--n-mbs", type=int, default=1)
     ap.add_argument("--critic", action="store_true")
     args = ap.parse_args()
-    cfg = TrainEngineConfig(experiment_name="t", trial_name="t", path="", init_from_scratch=True, dtype="float32",
+    cuda = args.device == "cuda"
+    tol = 4e-2 if cuda else 2e-4
+    over = {}
+    if cuda:
+        # the CUDA kernels want head_dim 128 and 16-byte aligned rows
+        over = dict(head_dim=128, intermediate_size=768)
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
+        if "LOCAL_RANK" in os.environ:
+            torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    cfg = TrainEngineConfig(experiment_name="t", trial_name="t", path="", init_from_scratch=True,
+                            dtype="bfloat16" if cuda else "float32", model_overrides=over,
                             model_preset=args.preset, mb_spec=MicroBatchSpec(n_mbs=args.n_mbs), is_critic=args.critic,
                             optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0, gradient_clipping=1.0,
                                                       warmup_steps_proportion=0.0, lr_scheduler_type="constant"))
     eng = B200TrainEngine(cfg)
-    batch = global_batch()
+    batch = global_batch(L=512 if cuda else 48)
     if args.ref:
         eng.create_process_group()
         eng.initialize(seed=3)
         data = batch
     else:
-        dist.init_process_group("gloo")
+        dist.init_process_group("nccl" if cuda else "gloo")
         world = dist.get_world_size()
         dp = world // (args.tp * args.sp * args.pp)
         eng.create_process_group(ParallelStrategy(tensor_parallel_size=args.tp, context_parallel_size=args.sp,
@@ -89,7 +100,7 @@ def main():
         torch.save(dict(loss=stats["loss"], grad_norm=stats["grad_norm"], grads=captured), args.file)
         print("ref", stats["loss"], stats["grad_norm"])
         return
-    ref = torch.load(args.file)
+    ref = torch.load(args.file, map_location="cuda" if cuda else "cpu")
     pctx, mesh = eng.pctx, eng.mesh
     full = {}
     for name, g in captured.items():
@@ -97,8 +108,8 @@ def main():
         if pctx.ep_size > 1 and g.dim() == 3 and ".mlp." in name:
             if mesh.edp_size > 1:
                 dist.all_reduce(g, group=mesh.edp_group)
-            parts = [None] * pctx.ep_size
-            dist.all_gather_object(parts, g, group=pctx.ep_group)
+            parts = [torch.empty_like(g) for _ in range(pctx.ep_size)]
+            dist.all_gather(parts, g.contiguous(), group=pctx.ep_group)
             full[name] = torch.cat(parts, 0)
             continue
         if mesh.shard_size > 1:
@@ -108,23 +119,27 @@ def main():
                 if not name.endswith("score"):
                     dist.all_reduce(g, group=pctx.tp_group)
             else:
-                parts = [None] * pctx.tp_size
-                dist.all_gather_object(parts, g, group=pctx.tp_group)
+                parts = [torch.empty_like(g) for _ in range(pctx.tp_size)]
+                dist.all_gather(parts, g.contiguous(), group=pctx.tp_group)
                 g = tp_unslice(name, parts, eng.model_config)
         full[name] = g
     # the loss is the sum over this rank's micro-batches; data-parallel ranks hold different ones
-    loss = torch.tensor([stats["loss"]], dtype=torch.float64)
+    loss = torch.tensor([stats["loss"]], dtype=torch.float64, device="cuda" if cuda else "cpu")
     if mesh.dp_size > 1:
         dist.all_reduce(loss, group=mesh.dp_group)
-    assert abs(float(loss) - ref["loss"]) < 1e-4 * max(1.0, abs(ref["loss"])), (float(loss), ref["loss"])
+    assert abs(float(loss) - ref["loss"]) < (2e-2 if cuda else 1e-4) * max(1.0, abs(ref["loss"])), (float(loss), ref["loss"])
     for name, g in full.items():
         if name.startswith("layers."):
             _, idx, rest = name.split(".", 2)
             name = f"layers.{int(idx) + eng.model.layer_start}.{rest}"
         r = ref["grads"][name]
         err = (g - r).abs().max().item()
-        assert err <= 2e-4 * (r.abs().max().item() + 1e-6), (name, err, r.abs().max().item())
-    assert abs(stats["grad_norm"] - ref["grad_norm"]) < 2e-4 * ref["grad_norm"], (stats["grad_norm"], ref["grad_norm"])
+        assert err <= tol * (r.abs().max().item() + 1e-6) + (1e-3 if cuda else 0), (name, err, r.abs().max().item())
+    assert abs(stats["grad_norm"] - ref["grad_norm"]) < tol * ref["grad_norm"], (stats["grad_norm"], ref["grad_norm"])
+    if cuda:
+        from areal_b200.ops import _lib
+
+        assert _lib.read_status() == 0
     # and the update itself went through on every rank
     assert stats["update_successful"] == 1.0
     dist.barrier()
