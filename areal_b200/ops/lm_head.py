@@ -149,8 +149,9 @@ class _LMHead(torch.autograd.Function):
                 gemm(dzv, w, b_mn=True, out=dx[r0:r1])
             if need_dw:
                 gemm(dzv, xs, a_mn=True, b_mn=True, out=dw_acc, accumulate=True)
-        if need_dx and ctx.tp_group is not None and dist.get_world_size(ctx.tp_group) > 1:
-            dist.all_reduce(dx, group=ctx.tp_group)
+        # With a vocabulary shard, dx is this rank's PARTIAL input gradient (like the reference
+        # restatement above): the caller's gather of the token shards sums the partials in its
+        # backward (reduce-scatter), which moves half the bytes of an all-reduce here.
         dw = None
         if need_dw and main is None:
             dw = dw_acc.to(w.dtype)
@@ -160,7 +161,9 @@ class _LMHead(torch.autograd.Function):
 def lm_head_logprobs(x, w, labels, temperature: float = 1.0, tp_group=None, vocab_start: int = 0):
     """Per-token log-probability of ``labels`` and entropy of the next-token
     distribution ``softmax(x @ w.T / temperature)``. ``w`` may be this rank's
-    vocabulary shard starting at global id ``vocab_start``."""
+    vocabulary shard starting at global id ``vocab_start``; the gradient with respect to ``x``
+    is then this shard's partial contribution, to be summed over ``tp_group`` by the caller
+    (``parallel.tensor_parallel.gather_seq`` does so in its backward)."""
     if _lib.use_cuda_kernels(x, w) and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0:
         return _LMHead.apply(x, w, labels, temperature, tp_group, vocab_start)
     return lm_head_logprobs_ref(x, w, labels, temperature, tp_group, vocab_start)

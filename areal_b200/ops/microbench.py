@@ -224,9 +224,56 @@ def bench_ppo_loss(a):
     report("ppo_loss", ms, nbytes=T * 4.0 * 5)
 
 
+def bench_decode_step(a):
+    """One full decode step (all layers, LM head, sampler) of Qwen3-1.7B: eager and as a CUDA graph."""
+    import dataclasses
+
+    from ..models.config import PRESETS
+    from ..models.qwen import build_model
+    from .rollout_ops import sample
+
+    mc = dataclasses.replace(PRESETS["qwen3-1.7b"])
+    model = build_model(mc, dtype=torch.bfloat16, device="cuda", seed=0).eval()
+    bs = 16
+    B, ctx = (64, 1500) if a.small else (256, 1500)
+    nb_per = (ctx + bs) // bs + 1
+    nb = B * nb_per
+    caches = [(torch.zeros(nb, mc.num_key_value_heads, bs, mc.head_dim, dtype=torch.bfloat16, device="cuda"),
+               torch.zeros(nb, mc.num_key_value_heads, bs, mc.head_dim, dtype=torch.bfloat16, device="cuda"))
+              for _ in range(mc.num_hidden_layers)]
+    bt = torch.randperm(nb, device="cuda").int().view(B, nb_per)
+    sl = torch.full((B,), ctx, device="cuda", dtype=torch.int32)
+    ids = torch.randint(0, 1000, (B,), device="cuda")
+    pos = (sl - 1).long()
+    slots = bt[:, (ctx - 1) // bs].long() * bs + (ctx - 1) % bs
+    temp = torch.ones(B, device="cuda")
+    u = torch.rand(B, device="cuda")
+
+    @torch.no_grad()
+    def step():
+        h = model.decode(ids, pos, caches, bt, sl, slots, max_seq_len=ctx)
+        return sample(model.logits(h, out_dtype=torch.float32), temp, None, None, u)
+
+    kv_bytes = float(B) * ctx * mc.num_key_value_heads * mc.head_dim * 2 * 2 * mc.num_hidden_layers
+    w_bytes = mc.num_params() * 2.0
+    ms = timeit(step, a.iters, flush=False)
+    report("decode_step_eager", ms, nbytes=kv_bytes + w_bytes, batch=B, ctx=ctx)
+    g = torch.cuda.CUDAGraph()
+    st = torch.cuda.Stream()
+    st.wait_stream(torch.cuda.current_stream())
+    with torch.cuda.stream(st):
+        step()
+        torch.cuda.synchronize()
+        with torch.cuda.graph(g, stream=st):
+            step()
+    torch.cuda.synchronize()
+    ms = timeit(g.replay, a.iters, flush=False)
+    report("decode_step_graph", ms, nbytes=kv_bytes + w_bytes, batch=B, ctx=ctx, tokens_per_s=round(B / ms * 1e3))
+
+
 BENCHES = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "grouped_gemm": bench_grouped_gemm, "attn": bench_attn,
            "lm_head": bench_lm_head, "decode": bench_decode, "elementwise": bench_elementwise,
-           "sampler": bench_sampler, "ppo_loss": bench_ppo_loss}
+           "sampler": bench_sampler, "ppo_loss": bench_ppo_loss, "decode_step": bench_decode_step}
 
 
 def main(argv=None):

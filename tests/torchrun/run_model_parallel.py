@@ -134,7 +134,7 @@ def main():
             name = f"layers.{int(idx) + eng.model.layer_start}.{rest}"
         r = ref["grads"][name]
         err = (g - r).abs().max().item()
-        assert err <= tol * (r.abs().max().item() + 1e-6) + (1e-3 if cuda else 0), (name, err, r.abs().max().item())
+        assert err <= tol * (r.abs().max().item() + 1e-6) + (1e-3 if cuda else 0), (name, err, r.abs().max().item(), g.abs().max().item(), (g - 2 * r).abs().max().item())
     assert abs(stats["grad_norm"] - ref["grad_norm"]) < tol * ref["grad_norm"], (stats["grad_norm"], ref["grad_norm"])
     if cuda:
         from areal_b200.ops import _lib
