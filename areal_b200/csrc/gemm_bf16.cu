@@ -215,6 +215,66 @@ static int launch_grouped(const void* A, const void* B, void* C, const int* tile
   return 0;
 }
 
+
+// ------------------------------------------------------------------------------ split-K --
+// Skinny products (a decode step: M <= a few hundred rows against a large weight) have too few
+// output tiles to occupy 148 SMs, and each CTA would stream its whole K extent at one SM's share
+// of the HBM bandwidth. Split-K gives every (tile, K-slice) pair its own CTA: slice s of tile
+// (m, n) is the virtual row block s * tiles_m + m, its partial sums go to an fp32 workspace
+// [S, tiles_m * 128, N] and a small kernel adds the slices (+ bias) into the bf16 output.
+struct SplitKEpi {
+  StoreEpi st;   // writes the fp32 workspace, M = S * tiles_m * 128
+  int tiles_m_real, kper, kblocks_total;
+  using State = StoreEpi::State;
+
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m_virtual, int tiles_n, int& m_blk,
+                                       int& n_blk) const {
+    const long long t = static_cast<long long>(it) * ncta + cta;
+    if (t >= static_cast<long long>(tiles_m_virtual) * tiles_n) return false;
+    // consecutive CTAs take the K slices of one output tile, then the next column block
+    m_blk = static_cast<int>(t % tiles_m_virtual);
+    n_blk = static_cast<int>(t / tiles_m_virtual);
+    return true;
+  }
+  __device__ __forceinline__ int a_m0(int mv) const { return (mv % tiles_m_real) * kBM; }
+  __device__ __forceinline__ int k_begin(int mv) const { return (mv / tiles_m_real) * kper * kBK; }
+  __device__ __forceinline__ int k_blocks(int mv) const {
+    const int left = kblocks_total - (mv / tiles_m_real) * kper;
+    return left < kper ? (left > 0 ? left : 0) : kper;
+  }
+  __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ void begin(State&, int, int, int) const {}
+  __device__ __forceinline__ void end(State&, int, int, int) const {}
+  __device__ __forceinline__ void chunk(State& s, int row, int col0, const float (&v)[32]) const {
+    st.chunk(s, row, col0, v);
+  }
+};
+
+__global__ void splitk_reduce_kernel(const float* __restrict__ ws, const __nv_bfloat16* __restrict__ bias,
+                                     __nv_bfloat16* __restrict__ out, long long ldc, int M, int N, int S,
+                                     long long slice_stride) {
+  const int nq = N >> 2;
+  const long long total = static_cast<long long>(M) * nq;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < total;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const int row = static_cast<int>(i / nq), c = static_cast<int>(i % nq) * 4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < S; ++s) {
+      const float4 v = *reinterpret_cast<const float4*>(ws + s * slice_stride + static_cast<long long>(row) * N + c);
+      acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+    }
+    if (bias) {
+      acc.x += __bfloat162float(bias[c]); acc.y += __bfloat162float(bias[c + 1]);
+      acc.z += __bfloat162float(bias[c + 2]); acc.w += __bfloat162float(bias[c + 3]);
+    }
+    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x, acc.y), hi = __floats2bfloat162_rn(acc.z, acc.w);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&lo);
+    pk.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(out + static_cast<long long>(row) * ldc + c) = pk;
+  }
+}
+
 }  // namespace b200
 
 extern "C" {
@@ -289,6 +349,48 @@ int b200_gemm_grouped_wgrad(const void* dY, const void* X, void* dW, const int* 
   int* status = device_status_word();
   if (!status) return -3;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, M, K, max_rows, epi, status);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// C[M,N] (bf16) = A[M,K] . B[N,K]^T (+ bias) with the K extent split over `splits` CTAs per tile.
+// workspace: fp32 [splits * ceil(M/128)*128 * N]. N % 4 == 0, ldc % 4 == 0.
+int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, const void* bias, float* workspace, int M, int N,
+                          int K, long long lda, long long ldb, long long ldc, int splits, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (N & 3) || (ldc & 3) || splits < 1) return -100;
+  constexpr int BN = 128;
+  using Cfg = GemmCfg<BN>;
+  const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + BN - 1) / BN;
+  const int kblocks = (K + kBK - 1) / kBK;
+  const int kper = (kblocks + splits - 1) / splits;
+  const int S = (kblocks + kper - 1) / kper;  // slices that actually hold work
+  const int Mv = S * tiles_m * kBM;
+  CUtensorMap tmA, tmB;
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, kBM, 64);
+  if (rc) return rc;
+  rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb * 2, BN, 64);
+  if (rc) return rc;
+  SplitKEpi epi{StoreEpi{workspace, nullptr, N, Mv, N, 1, 0}, tiles_m, kper, kblocks};
+  auto kern = gemm_tcgen05_kernel<BN, false, false, SplitKEpi>;
+  static bool attr_set = false;
+  if (!attr_set) {
+    B200_CHECK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, Cfg::kSmemBytes));
+    attr_set = true;
+  }
+  const long long tiles = static_cast<long long>(S) * tiles_m * tiles_n;
+  const int grid = static_cast<int>(tiles < sm_count() ? tiles : sm_count());
+  int* status = device_status_word();
+  if (!status) return -3;
+  kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, Mv, N, K, epi, status);
+  B200_CHECK(cudaGetLastError());
+  const long long total = static_cast<long long>(M) * (N >> 2);
+  long long rg = (total + 255) / 256;
+  const long long maxg = static_cast<long long>(sm_count()) * 8;
+  if (rg > maxg) rg = maxg;
+  splitk_reduce_kernel<<<(unsigned)rg, 256, 0, stream>>>(workspace, (const __nv_bfloat16*)bias, (__nv_bfloat16*)C, ldc,
+                                                        M, N, S, static_cast<long long>(tiles_m) * kBM * N);
   B200_CHECK(cudaGetLastError());
   return 0;
 }

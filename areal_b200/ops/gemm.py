@@ -86,6 +86,20 @@ def gemm(
         a, b = pad(a), pad(b)
         if not a_mn:
             K = a.shape[1]
+    # skinny products (decode steps): too few output tiles for 148 SMs ⇒ split the K extent
+    if (bn == 0 and not a_mn and not b_mn and not accumulate and out.dtype == torch.bfloat16 and M <= 512
+            and N % 4 == 0 and out.stride(0) % 4 == 0 and not need_pad and K >= 1024):
+        tiles = -(-M // 128) * -(-N // 128)
+        splits = min(8, 148 // tiles, K // 256)
+        if splits >= 2:
+            ws = torch.empty((splits * -(-M // 128) * 128, N), dtype=torch.float32, device=a.device)
+            rc = _lib.kernels().b200_gemm_bf16_splitk(
+                _lib.ptr(a), _lib.ptr(b), _lib.ptr(out), _lib.ptr(bias), _lib.ptr(ws), ctypes.c_int(M), ctypes.c_int(N),
+                ctypes.c_int(K), ctypes.c_longlong(a.stride(0)), ctypes.c_longlong(b.stride(0)),
+                ctypes.c_longlong(out.stride(0)), ctypes.c_int(splits), _lib.stream_ptr())
+            _lib.check(rc, "b200_gemm_bf16_splitk")
+            _lib.count_launch(2)
+            return out
     if bn == 0:
         bn = 256 if N > 128 else 128
         if bn == 256:

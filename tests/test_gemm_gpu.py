@@ -59,3 +59,21 @@ def test_linear_autograd():
     torch.testing.assert_close(y.float(), yr, atol=0.25, rtol=2e-2)
     torch.testing.assert_close(x.grad.float(), xr.grad, atol=0.5, rtol=2e-2)
     torch.testing.assert_close(w.grad.float(), wr.grad, atol=0.5, rtol=2e-2)
+
+
+@pytest.mark.parametrize("M,N,K", [(64, 2048, 2048), (256, 2048, 6144), (300, 2048, 2048), (1, 2048, 2048)])
+def test_skinny_gemm_takes_the_split_k_path(M, N, K):
+    """Decode-step shapes: few output tiles, long K. The result must match fp32 and the launch count
+    shows that the split-K kernel plus its reduction ran."""
+    from areal_b200.ops import _lib
+
+    torch.manual_seed(4)
+    x = torch.randn(M, K, device="cuda").bfloat16()
+    w = (torch.randn(N, K, device="cuda") * K ** -0.5).bfloat16()
+    bias = torch.randn(N, device="cuda").bfloat16()
+    before = _lib.launch_count()
+    y = gemm(x, w, bias=bias)
+    assert _lib.launch_count() - before == 2
+    assert _lib.read_status() == 0
+    ref = x.float() @ w.float().t() + bias.float()
+    torch.testing.assert_close(y.float(), ref, atol=3e-2, rtol=3e-2)
