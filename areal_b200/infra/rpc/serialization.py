@@ -28,6 +28,8 @@ def _np_from_b64(s: str) -> np.ndarray:
 
 
 def serialize_value(v: Any) -> Any:
+    if isinstance(v, float) and (v != v or v in (float("inf"), float("-inf"))):
+        return {_T: "float", "value": repr(v)}  # JSON has no inf / nan
     if v is None or isinstance(v, (bool, int, float, str)):
         return v
     if torch.is_tensor(v):
@@ -84,6 +86,8 @@ def deserialize_value(v: Any) -> Any:
         return torch.from_numpy(a.copy())
     if t == "ndarray":
         return _np_from_b64(v["data"])
+    if t == "float":
+        return float(v["value"])
     if t == "bytes":
         return base64.b64decode(v["data"])
     if t == "enum":

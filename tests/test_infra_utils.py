@@ -90,3 +90,15 @@ def test_network_metadata_platform_and_concurrency(tmp_path):
 
     assert concurrent.run_async_task(f, 4) == 8
     assert asyncio.run(concurrent.gather_with_limit([f(i) for i in range(5)], 2)) == [0, 2, 4, 6, 8]
+
+
+def test_local_sandbox_runs_limits_and_scores():
+    from areal_b200.infra.sandbox import LocalSandbox, code_reward
+
+    sb = LocalSandbox(cpu_seconds=2, memory_mb=512)
+    r = sb.run("print(int(input()) * 2)", stdin="21\n")
+    assert r.ok and r.stdout.strip() == "42"
+    assert not sb.run("raise SystemExit(3)").ok
+    r = sb.run("while True: pass", timeout=1.0)
+    assert not r.ok
+    assert code_reward(sb, "print(int(input()) + 1)", [("1", "2"), ("5", "6"), ("7", "9")]) == pytest.approx(2 / 3)

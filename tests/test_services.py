@@ -1,0 +1,212 @@
+"""Gateway / router / worker micro-services, wired together in-process: every outgoing POST of a
+gateway is routed to the FastAPI app registered under the target address."""
+import pytest
+import torch
+from fastapi.testclient import TestClient
+
+from areal_b200.api.cli_args import GenerationHyperparameters
+from areal_b200.api.io_struct import ModelRequest, ModelResponse
+from areal_b200.infra.rpc.serialization import deserialize_value, serialize_value
+from areal_b200.services import agent_service, data_service, inference_service, training_service, weight_update_service
+from areal_b200.services.base import WorkerRegistry
+
+
+class Net:
+    """addr → TestClient; stands in for the network."""
+
+    def __init__(self):
+        self.apps = {}
+
+    def add(self, addr, app):
+        self.apps[addr] = TestClient(app)
+
+    def post(self, url, body):
+        addr, _, path = url[len("http://"):].partition("/")
+        r = self.apps[addr].post("/" + path, json=body)
+        if r.status_code >= 400:
+            from areal_b200.infra.utils.http import HTTPRequestError
+
+            raise HTTPRequestError(url, r.status_code, r.text)
+        return r.json()
+
+
+def test_registry_strategies_and_affinity():
+    reg = WorkerRegistry("round_robin")
+    for i in range(3):
+        reg.register(f"w{i}", f"h{i}:1")
+    assert [reg.pick().worker_id for _ in range(4)] == ["w0", "w1", "w2", "w0"]
+    first = reg.pick("sess").worker_id
+    assert all(reg.pick("sess").worker_id == first for _ in range(5))
+    reg.mark_unhealthy(first)
+    assert reg.pick("sess").worker_id != first
+    ll = WorkerRegistry("least_loaded")
+    a, b = ll.register("a", "x"), ll.register("b", "y")
+    ll.acquire(a)
+    assert ll.pick().worker_id == "b"
+    with pytest.raises(ValueError):
+        WorkerRegistry("random")
+
+
+class SquaresDataset:
+    def __init__(self, n=10):
+        self.n = n
+
+    def __len__(self):
+        return self.n
+
+    def __getitem__(self, i):
+        return {"i": i, "sq": i * i}
+
+
+def test_data_service_shards_fetches_and_prefetches():
+    net = Net()
+    for w in ("d0:1", "d1:1"):
+        net.add(w, data_service.create_worker_app())
+    gw = TestClient(data_service.create_gateway_app(token="s3cret", post=net.post))
+    assert gw.post("/register", json={"worker_id": "d0", "addr": "d0:1"}).status_code == 401
+    h = {"Authorization": "Bearer s3cret"}
+    for i in range(2):
+        assert gw.post("/register", json={"worker_id": f"d{i}", "addr": f"d{i}:1"}, headers=h).status_code == 200
+    r = gw.post("/load", json={"name": "sq", "dataset": "tests.test_services.SquaresDataset",
+                               "kwargs": serialize_value({"n": 10})}, headers=h)
+    assert r.json()["len"] == 10
+    ds = data_service.RDataset("gw", "sq", post=lambda path, body: gw.post(path, json=body, headers=h).json())
+    assert len(ds) == 10 and ds[3] == {"i": 3, "sq": 9}
+    assert [x["i"] for x in ds.fetch([7, 2, 5])] == [7, 2, 5]
+    batches = [[0, 1], [2, 3], [4, 5], [6]]
+    got = [[x["sq"] for x in b] for b in data_service.PrefetchingSampler(ds, batches, depth=2)]
+    assert got == [[0, 1], [4, 9], [16, 25], [36]]
+
+
+class EchoEngineApp:
+    """Minimal stand-in for a worker RPC server hosting a rollout engine."""
+
+    def __init__(self, name):
+        from fastapi import FastAPI, Request
+
+        self.name, self.calls, self.version = name, [], 0
+        app = FastAPI()
+
+        @app.post("/call")
+        async def call(req: Request):
+            b = await req.json()
+            args = deserialize_value(b["args"])
+            self.calls.append(b["method"])
+            if b["method"] == "generate":
+                mr = args[0]
+                out = [t + 1 for t in mr.input_ids[-2:]]
+                res = ModelResponse(input_tokens=list(mr.input_ids), output_tokens=out, output_logprobs=[-1.0] * len(out),
+                                    output_versions=[self.version] * len(out), stop_reason="stop")
+            elif b["method"] == "set_version":
+                self.version = args[0]
+                res = None
+            else:
+                res = None
+            return {"result": serialize_value(res)}
+
+        self.app = app
+
+
+def test_inference_service_sessions_pause_and_versions():
+    net = Net()
+    engines = [EchoEngineApp("e0"), EchoEngineApp("e1")]
+    for i, e in enumerate(engines):
+        net.add(f"e{i}:1", e.app)
+    gw = TestClient(inference_service.create_gateway_app(post=net.post))
+    for i in range(2):
+        gw.post("/register", json={"worker_id": f"e{i}", "addr": f"e{i}:1"})
+    sid = gw.post("/sessions/start", json={}).json()["session_id"]
+    req1 = ModelRequest(input_ids=[5, 6, 7], gconfig=GenerationHyperparameters(max_new_tokens=2))
+    r1 = deserialize_value(gw.post("/generate", json={"session_id": sid, "request": serialize_value(req1)}).json()["response"])
+    assert r1.output_tokens == [7, 8]
+    gw.post("/set_version", json={"version": 4})
+    req2 = ModelRequest(input_ids=[5, 6, 7, 7, 8, 9], gconfig=GenerationHyperparameters(max_new_tokens=2))
+    gw.post("/generate", json={"session_id": sid, "request": serialize_value(req2)})
+    # both turns of the session went to the same engine
+    assert sorted(e.calls.count("generate") for e in engines) == [0, 2]
+    traj = gw.post(f"/sessions/{sid}/finish", json={"reward": 1.0}).json()["trajectory"]
+    assert traj["input_ids"] == [5, 6, 7, 7, 8, 9, 9, 10] and traj["loss_mask"] == [0, 0, 0, 1, 1, 0, 1, 1]
+    assert traj["versions"] == [-1, -1, -1, 0, 0, -1, 4, 4] and traj["reward"] == 1.0
+    assert gw.post("/pause", json={}).json()["paused"] and gw.get("/workers").json()["paused"]
+    assert not gw.post("/continue", json={}).json()["paused"]
+    assert all("pause_generation" in e.calls and "continue_generation" in e.calls for e in engines)
+
+
+def test_training_service_splits_batches_and_merges():
+    from tests.fake_engine import FakeTrainEngine
+    from fastapi import FastAPI, Request
+
+    net = Net()
+    fakes = [FakeTrainEngine(), FakeTrainEngine()]
+
+    def worker_app(eng):
+        app = FastAPI()
+
+        @app.post("/call")
+        async def call(req: Request):
+            b = await req.json()
+            out = getattr(eng, b["method"])(*deserialize_value(b["args"]), **deserialize_value(b["kwargs"]))
+            return {"result": serialize_value(out)}
+
+        return app
+
+    for i, f in enumerate(fakes):
+        net.add(f"t{i}:1", worker_app(f))
+    gw = TestClient(training_service.create_gateway_app(post=net.post))
+    for i in range(2):
+        gw.post("/register", json={"worker_id": f"t{i}", "addr": f"t{i}:1", "rank": i})
+    B, L = 8, 6
+    batch = {"input_ids": torch.arange(B * L).view(B, L), "attention_mask": torch.ones(B, L, dtype=torch.bool)}
+    out = deserialize_value(gw.post("/call", json={"method": "forward_batch", "batch": serialize_value(batch),
+                                                   "args": serialize_value([]), "kwargs": serialize_value({}),
+                                                   "group_size": 2}).json()["result"])
+    assert torch.equal(out, batch["input_ids"].float())  # rows came back in the original order
+    gw.post("/call", json={"method": "set_version", "args": serialize_value([3]), "kwargs": serialize_value({})})
+    assert all(f.version == 3 for f in fakes)
+
+
+class CountingAgent:
+    def __init__(self, bonus=0.0):
+        self.bonus = bonus
+
+    async def run(self, data, base_url=None, api_key=None):
+        return {"reward": float(len(data["question"])) + self.bonus, "base_url": base_url}
+
+
+def test_agent_service_runs_sessions_on_workers():
+    net = Net()
+    net.add("a0:1", agent_service.create_worker_app())
+    gw = TestClient(agent_service.create_gateway_app(post=net.post))
+    gw.post("/register", json={"worker_id": "a0", "addr": "a0:1"})
+    sid = gw.post("/sessions/start", json={"base_url": "http://proxy/v1", "api_key": "k"}).json()["session_id"]
+    r = gw.post(f"/sessions/{sid}/run", json={"agent": "tests.test_services.CountingAgent",
+                                              "agent_kwargs": serialize_value({"bonus": 0.5}),
+                                              "data": serialize_value({"question": "abcd"})})
+    out = deserialize_value(r.json()["result"])
+    assert out == {"reward": 4.5, "base_url": "http://proxy/v1"}
+    assert gw.post(f"/sessions/{sid}/end", json={}).json()["runs"] == 1
+    assert gw.post(f"/sessions/{sid}/run", json={"agent": "x.y"}).status_code == 404
+
+
+def test_weight_update_service_round_and_metadata():
+    net = Net()
+    engines = [EchoEngineApp("e0"), EchoEngineApp("e1"), EchoEngineApp("e2")]
+    for i, e in enumerate(engines):
+        net.add(f"e{i}:1", e.app)
+    gw = TestClient(weight_update_service.create_gateway_app(post=net.post))
+    assert gw.post("/update_weights", json={}).status_code == 409
+    for i in range(3):
+        gw.post("/connect", json={"role": "inference", "rank": i, "addr": f"e{i}:1", "info": serialize_value({"ipc": i})})
+    gw.post("/connect", json={"role": "train", "rank": 0, "addr": "e0:1"})
+    gw.post("/connect", json={"role": "train", "rank": 1, "addr": "e1:1"})
+    assert gw.get("/plan").json()["pairs"] == {"0": [0, 2], "1": [1]}
+    gw.put("/weight_meta/exp/trial/v1", json={"path": "/ckpt/v1"})
+    assert gw.get("/weight_meta/exp/trial/v1").json() == {"path": "/ckpt/v1"}
+    assert gw.get("/weight_meta/none").status_code == 404
+    r = gw.post("/update_weights", json={"mode": "disk", "meta": serialize_value({"path": "/ckpt/v1"})}).json()
+    assert r["version"] == 1 and all(e.version == 1 for e in engines)
+    for e in engines:
+        i = e.calls.index
+        assert i("pause_generation") < i("update_weights_from_disk") < i("set_version") < i("continue_generation")
+    assert gw.get("/status").json()["version"] == 1
+    assert weight_update_service.pair_ranks(2, 5) == {0: [0, 2, 4], 1: [1, 3]}
