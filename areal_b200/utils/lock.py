@@ -30,7 +30,7 @@ class DistributedLock:
             try:
                 owner = self.store.get(self._key("owner")).decode()
                 tok, _, exp = owner.partition(":")
-                if exp and float(exp) < time.time():
+                if tok and exp and 0 < float(exp) < time.time():  # a held lock whose lease ran out
                     if self.store.compare_set(self._key("owner"), owner, f"{self.token}:{time.time() + self.lease}").decode() \
                             .startswith(self.token):
                         self._held = True
@@ -50,7 +50,7 @@ class DistributedLock:
         except Exception:
             owner = ""
         if owner.startswith(self.token):
-            self.store.set(self._key("owner"), ":0")
+            self.store.set(self._key("owner"), "")  # free: nothing to steal
             self.store.add(self._key("count"), -1)
 
     def __enter__(self):
