@@ -53,6 +53,14 @@ def resolve_model_config(cfg: TrainEngineConfig) -> ModelConfig:
     if cfg.is_critic:
         mc.is_critic = True
         mc.tie_word_embeddings = False
+    # fp8 training: the Megatron-style (`megatron.fp8_config.mode`) and the Archon-style
+    # (`archon.fp8_config.mode: blockwise`) switches both select the block-scaled e4m3 forward GEMMs
+    meg = getattr(cfg.megatron, "fp8_config", None)
+    arch = getattr(cfg.archon, "fp8_config", None)
+    if (meg is not None and meg.mode) or (arch is not None and getattr(arch, "mode", "disabled") == "blockwise"):
+        if meg is not None and meg.mode and meg.recipe not in ("blockwise", "mxfp8"):
+            raise ValueError(f"fp8 recipe {meg.recipe!r} is not supported: this engine implements block-wise scaling")
+        mc.fp8 = True
     return mc
 
 

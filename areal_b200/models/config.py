@@ -29,6 +29,9 @@ class ModelConfig:
     tie_word_embeddings: bool = True
     attention_bias: bool = False  # Qwen2: bias on q/k/v
     qk_norm: bool = True  # Qwen3: per-head RMSNorm on q and k
+    # block-scaled fp8 forward GEMMs of the dense projections (bf16 master weights)
+    fp8: bool = False
+    fp8_ue8m0: bool = True
     # MoE (qwen3_moe)
     num_experts: int = 0
     num_experts_per_tok: int = 0

@@ -30,6 +30,15 @@ from ..ops.rollout_ops import kv_cache_write, paged_decode
 from .config import ModelConfig
 
 
+def _dense(x, w, bias, cfg: ModelConfig):
+    """Projection of a dense layer: block-scaled fp8 forward when the model is configured for it."""
+    if cfg.fp8 and bias is None and x.is_cuda and x.dtype == torch.bfloat16:
+        from ..ops.fp8 import fp8_linear
+
+        return fp8_linear(x, w, cfg.fp8_ue8m0)
+    return linear(x, w, bias)
+
+
 class Attention(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype, device, pctx=None):
         super().__init__()
@@ -63,7 +72,7 @@ class Attention(nn.Module):
 
             qkv = column_parallel_linear(x, self.qkv, tp, self.qkv_bias)
         else:
-            qkv = linear(x, self.qkv, self.qkv_bias)
+            qkv = _dense(x, self.qkv, self.qkv_bias, cfg)
         return fused.qknorm_rope(qkv, self.q_norm, self.k_norm, cos, sin, pos,
                                  self.n_q, self.n_kv, cfg.head_dim, cfg.rms_norm_eps)
 
@@ -79,13 +88,14 @@ class Attention(nn.Module):
             from ..parallel.tensor_parallel import row_parallel_linear
 
             return row_parallel_linear(a, self.o, tp)
-        return linear(a, self.o)
+        return _dense(a, self.o, None, self.cfg)
 
 
 class DenseMLP(nn.Module):
-    def __init__(self, hidden, inter, dtype, device, pctx=None):
+    def __init__(self, hidden, inter, dtype, device, pctx=None, cfg: ModelConfig | None = None):
         super().__init__()
         self.pctx = pctx
+        self.cfg = cfg
         tp = pctx.tp_size if pctx is not None else 1
         assert inter % tp == 0
         self.gate_up = nn.Parameter(torch.empty(2 * inter // tp, hidden, dtype=dtype, device=device))
@@ -98,6 +108,8 @@ class DenseMLP(nn.Module):
 
             return row_parallel_linear(fused.swiglu(column_parallel_linear(x, self.gate_up, p.tp_fused)),
                                        self.down, p.tp_fused)
+        if self.cfg is not None and self.cfg.fp8:
+            return _dense(fused.swiglu(_dense(x, self.gate_up, None, self.cfg)), self.down, None, self.cfg)
         return linear(fused.swiglu(linear(x, self.gate_up)), self.down)
 
 
@@ -156,7 +168,7 @@ class Block(nn.Module):
             assert pctx is None or pctx.tp_size == 1, "MoE layers shard over the expert-parallel group, not tp"
             self.mlp = MoEMLP(cfg, dtype, device, pctx)
         else:
-            self.mlp = DenseMLP(h, cfg.intermediate_size, dtype, device, pctx)
+            self.mlp = DenseMLP(h, cfg.intermediate_size, dtype, device, pctx, cfg)
         self.eps = cfg.rms_norm_eps
 
     def forward(self, x, res, cos, sin, pos, meta, attn_fn=None):

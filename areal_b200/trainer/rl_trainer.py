@@ -82,7 +82,8 @@ class _ListLoader:
 
 
 class PPOTrainer:
-    def __init__(self, config: PPOConfig, train_dataset, valid_dataset=None):
+    def __init__(self, config: PPOConfig, train_dataset, valid_dataset=None, tokenizer=None):
+        self.tokenizer = tokenizer
         self.config = config
         self.train_dataset, self.valid_dataset = train_dataset, valid_dataset
         use_cuda = torch.cuda.is_available()

@@ -52,7 +52,8 @@ def collate_pairs(items: list[dict[str, Any]]) -> dict[str, torch.Tensor]:
 class _SLTrainer:
     collate: Callable = staticmethod(collate_sft)
 
-    def __init__(self, config, train_dataset, valid_dataset=None):
+    def __init__(self, config, train_dataset, valid_dataset=None, tokenizer=None):
+        self.tokenizer = tokenizer
         self.config = config
         use_cuda = torch.cuda.is_available()
         if not dist.is_initialized() and "RANK" in os.environ:
@@ -162,11 +163,11 @@ class SFTTrainer(_SLTrainer):
 class RWTrainer(_SLTrainer):
     collate = staticmethod(collate_pairs)
 
-    def __init__(self, config: RWConfig, train_dataset, valid_dataset=None):
+    def __init__(self, config: RWConfig, train_dataset, valid_dataset=None, tokenizer=None):
         cfg = config.actor if getattr(config, "model", None) is None else config.model
         cfg.is_critic = True
         cfg.mb_spec.granularity = 2
-        super().__init__(config, train_dataset, valid_dataset)
+        super().__init__(config, train_dataset, valid_dataset, tokenizer)
 
     def _make_wrapper(self, actor_cfg):
         return RWEngine(self.engine)
