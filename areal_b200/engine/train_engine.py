@@ -212,6 +212,8 @@ class B200TrainEngine(TrainEngine):
             from ..utils.hf_io import load_hf_weights
 
             load_hf_weights(self.model, cfg.path)
+        if cfg.gradient_checkpointing:
+            self.model.checkpoint_every = 1
         tp = pctx.tp_size if pctx is not None else 1
         rep_first = None
         if tp > 1:

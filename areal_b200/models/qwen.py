@@ -211,6 +211,7 @@ class QwenModel(nn.Module):
             elif not cfg.tie_word_embeddings:
                 self.lm_head = mk(vloc, cfg.hidden_size)
         self._rope = None
+        self.checkpoint_every = 0  # k > 0: recompute every k-th block's activations in backward
 
     # ------------------------------------------------------------------ init
     @torch.no_grad()
@@ -320,8 +321,15 @@ class QwenModel(nn.Module):
             x, res = vocab_parallel_embedding(input_ids, self.embed, p.tp_fused), None
         else:
             x, res = fused.embedding(input_ids, self.embed), None
-        for layer in self.layers:
-            x, res = layer(x, res, cos, sin, pos, meta, attn_fn)
+        ckpt_every = getattr(self, "checkpoint_every", 0)
+        for li, layer in enumerate(self.layers):
+            if ckpt_every and torch.is_grad_enabled() and li % ckpt_every == 0:
+                # activation checkpointing: keep only the block's inputs, recompute the rest in backward
+                from torch.utils.checkpoint import checkpoint
+
+                x, res = checkpoint(layer, x, res, cos, sin, pos, meta, attn_fn, use_reentrant=False)
+            else:
+                x, res = layer(x, res, cos, sin, pos, meta, attn_fn)
         if not self.last_stage:
             return x, res
         y, _ = fused.rmsnorm(x, self.norm, self.cfg.rms_norm_eps, residual=res)

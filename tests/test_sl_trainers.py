@@ -76,3 +76,26 @@ def test_dpo_trainer(tmp_path, loss_type):
     # policy == reference at step 0: sigmoid loss is log 2, IPO loss is (0 - 1/(2β))²
     expect = math.log(2) if loss_type == "sigmoid" else 25.0
     assert losses[0] == pytest.approx(expect, rel=1e-3) and losses[-1] < losses[0]
+
+
+def test_gradient_checkpointing_gives_identical_gradients():
+    """Recomputing block activations in backward must not change a single gradient."""
+    import torch
+
+    from areal_b200.models.config import PRESETS
+    from areal_b200.models.qwen import build_model
+    from areal_b200.ops.attention import VarlenMeta
+
+    torch.manual_seed(0)
+    ids = torch.randint(0, 1000, (40,))
+    pos = torch.cat([torch.arange(25), torch.arange(15)])
+    meta = VarlenMeta([0, 25, 40], "cpu")
+    grads = []
+    for every in (0, 1):
+        m = build_model(PRESETS["tiny-qwen2"], dtype=torch.float32, seed=3)
+        m.checkpoint_every = every
+        m(ids, pos, meta).square().mean().backward()
+        grads.append({n: p.grad.clone() for n, p in m.named_parameters() if p.grad is not None})
+    assert set(grads[0]) == set(grads[1]) and len(grads[0]) > 10
+    for n in grads[0]:
+        assert torch.allclose(grads[0][n], grads[1][n], atol=1e-7), n
