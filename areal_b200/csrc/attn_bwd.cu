@@ -34,8 +34,9 @@ struct AttnBwdTile {
   int kv_len;     // valid kv rows in the block (<= 128)
   int kv_off;     // offset of the block inside its sequence
   int seq_start;  // first global token row of the sequence
-  int seq_len;
-  int pad0, pad1, pad2;
+  int seq_len;    // end of the query range (sequence-relative); queries [max(kv_off, q_begin), seq_len) are visited
+  int q_begin;    // first sequence position present in the query array (0 unless context-parallel)
+  int pad1, pad2;
 };
 
 constexpr int kTileBytes = kBT * kD * 2;  // 32 KB
@@ -89,7 +90,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 const AttnBwdTile* __restrict__ tiles, const float* __restrict__ lse,
                 const float* __restrict__ delta, float* __restrict__ dq_acc,
                 __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, int T, int Hq,
-                int Hkv, long long lddk, long long lddv, float scale, int* status) {
+                int Hkv, long long lddk, long long lddv, float scale, int* status,
+                const int* __restrict__ key_exit) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ uint64_t bars[16];
   __shared__ uint32_t tmem_holder;
@@ -121,7 +123,9 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const int hk = blockIdx.y;
   const int group = Hq / Hkv;
   // query blocks i with rows >= kv_off (causal): first block index containing kv_off
-  const int qb_first = tile.kv_off / kBT;
+  // q_begin (0 for ordinary batches): first sequence position held by the local query array
+  // (context parallelism: this rank owns the positions [q_begin, seq_len) of the sequence)
+  const int qb_first = max(tile.kv_off, tile.q_begin) / kBT;
   const int qb_count = (tile.seq_len + kBT - 1) / kBT - qb_first;
   const int n_iter = qb_count * group;  // iteration it -> (head g = it / qb_count, block i = it % qb_count)
   const float scale_log2 = scale * 1.4426950408889634f;
@@ -269,6 +273,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
     const int kv_pos = tile.kv_off + r;
     const bool kv_valid = r < tile.kv_len;
+    // tree attention: this key is visible to the queries of its own subtree only
+    const int kv_exit = (key_exit != nullptr && kv_valid) ? key_exit[tile.kv_start + r] : 0x7fffffff;
     uint8_t* psrow = sPS + r * 128;
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
@@ -302,7 +308,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int u = 0; u < 2; ++u) {
             const int col = c * 32 + 2 * e + u;  // q row inside block
             float p = exp2f(__uint_as_float(raw[2 * e + u]) * scale_log2 - s_lse[itp][col]);
-            const bool valid = kv_valid && (col < q_rows) && (!diag || (q0 + col >= kv_pos));
+            const bool valid = kv_valid && (col < q_rows) && (!diag || (q0 + col >= kv_pos)) &&
+                               (q0 + col < kv_exit);
             p2[u] = valid ? p : 0.f;
           }
           __nv_bfloat162 pb = __floats2bfloat162_rn(p2[0], p2[1]);
@@ -433,13 +440,30 @@ extern "C" {
 // delta_ws are [Hq, T] fp32; dq_acc is a zero-initialised fp32 [T, Hq*128]
 // workspace; dq (bf16, pitch lddq) receives its rounded value; dk/dv are bf16
 // with pitches lddk/lddv (they may point into a fused dqkv buffer).
+int b200_attn_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                     const float* lse, float* delta_ws, float* dq_acc, void* dq, void* dk, void* dv,
+                     const void* tiles, int n_tiles, int T, int Tkv, int Hq, int Hkv, long long ldk,
+                     long long ldv, long long lddk, long long lddv, float softmax_scale,
+                     const int* key_exit, cudaStream_t stream);
+
 int b200_attn_bwd(const void* q, const void* k, const void* v, const void* o, const void* dout,
                   const float* lse, float* delta_ws, float* dq_acc, void* dq, void* dk, void* dv,
                   const void* tiles, int n_tiles, int T, int Hq, int Hkv, long long ldk,
                   long long ldv, long long lddk, long long lddv, float softmax_scale,
                   cudaStream_t stream) {
+  return b200_attn_bwd_ex(q, k, v, o, dout, lse, delta_ws, dq_acc, dq, dk, dv, tiles, n_tiles, T, 0, Hq, Hkv, ldk,
+                          ldv, lddk, lddv, softmax_scale, nullptr, stream);
+}
+
+// Extended form, see b200_attn_fwd_ex: k, v, dk, dv have Tkv rows; key_exit enables the tree mask.
+int b200_attn_bwd_ex(const void* q, const void* k, const void* v, const void* o, const void* dout,
+                     const float* lse, float* delta_ws, float* dq_acc, void* dq, void* dk, void* dv,
+                     const void* tiles, int n_tiles, int T, int Tkv, int Hq, int Hkv, long long ldk,
+                     long long ldv, long long lddk, long long lddv, float softmax_scale,
+                     const int* key_exit, cudaStream_t stream) {
   using namespace b200;
   if (n_tiles == 0 || T == 0) return 0;
+  if (Tkv <= 0) Tkv = T;
   if (Hq % Hkv) return -100;
   {
     const long long warps = static_cast<long long>(T) * Hq;
@@ -453,10 +477,10 @@ int b200_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
   rc = make_tmap_2d(&tmdO, dout, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)Hq * kD,
                     (uint64_t)Hq * kD * 2, kBT, 64);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)Hkv * kD, ldk * 2,
+  rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tkv, (uint64_t)Hkv * kD, ldk * 2,
                     kBT, 64);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)Hkv * kD, ldv * 2,
+  rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tkv, (uint64_t)Hkv * kD, ldv * 2,
                     kBT, 64);
   if (rc) return rc;
   static bool attr_set = false;
@@ -470,7 +494,7 @@ int b200_attn_bwd(const void* q, const void* k, const void* v, const void* o, co
   dim3 grid(n_tiles, Hkv);
   attn_bwd_kernel<<<grid, kBwdThreads, kAttnBwdSmem, stream>>>(
       tmQ, tmK, tmV, tmdO, reinterpret_cast<const AttnBwdTile*>(tiles), lse, delta_ws, dq_acc,
-      (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, T, Hq, Hkv, lddk, lddv, softmax_scale, status);
+      (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, T, Hq, Hkv, lddk, lddv, softmax_scale, status, key_exit);
   B200_CHECK(cudaGetLastError());
   if (dq) {
     const long long n = static_cast<long long>(T) * Hq * kD;

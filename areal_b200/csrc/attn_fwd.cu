@@ -47,7 +47,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2)
 attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const AttnTile* __restrict__ tiles,
                 __nv_bfloat16* __restrict__ o, float* __restrict__ lse, int T, int Hq, int Hkv,
-                float scale_log2, int* status) {
+                float scale_log2, int* status, const int* __restrict__ key_exit) {
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ uint64_t bars[16];
   __shared__ uint32_t tmem_holder;
@@ -216,7 +216,18 @@ attn_fwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int kv0 = j * kKT;
       float mx = -INFINITY;
       const bool need_mask = (kv0 + kKT - 1 > tile.q_off) || (kv0 + kKT > tile.kv_len);
-      if (need_mask) {
+      if (key_exit != nullptr) {
+        // tree (trie-packed) attention: tokens are in depth-first order, key kv is an ancestor of
+        // query q_pos iff kv <= q_pos < exit[kv] (exit = end of the key's subtree)
+        const int* ex = key_exit + tile.kv_start + kv0;
+#pragma unroll
+        for (int i = 0; i < kKT; ++i) {
+          const int kv = kv0 + i;
+          const bool valid = (kv <= q_pos) && (kv < tile.kv_len) && (q_pos < __ldg(ex + i));
+          s[i] = valid ? s[i] * scale_log2 : -INFINITY;
+          mx = fmaxf(mx, s[i]);
+        }
+      } else if (need_mask) {
 #pragma unroll
         for (int i = 0; i < kKT; ++i) {
           const int kv = kv0 + i;
@@ -336,20 +347,37 @@ extern "C" {
 // q: [T, Hq*128] contiguous; k, v: rows of Hkv*128 bf16 with pitches ldk / ldv
 // (elements; multiples of 8, so k and v may be views into a fused qkv buffer).
 // tiles: device array of n_tiles AttnTile records (see attention.py).
+// Extended form: `Tkv` rows in k / v (context parallelism: local queries against gathered keys;
+// 0 = same as T) and `key_exit` (int [Tkv], sequence-relative end of every key's subtree; enables
+// the ancestor mask of tree attention, null = plain causal).
+int b200_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse,
+                     const void* tiles, int n_tiles, int T, int Tkv, int Hq, int Hkv, long long ldq,
+                     long long ldk, long long ldv, float softmax_scale, const int* key_exit,
+                     cudaStream_t stream);
+
 int b200_attn_fwd(const void* q, const void* k, const void* v, void* o, float* lse,
                   const void* tiles, int n_tiles, int T, int Hq, int Hkv, long long ldq,
                   long long ldk, long long ldv, float softmax_scale, cudaStream_t stream) {
+  return b200_attn_fwd_ex(q, k, v, o, lse, tiles, n_tiles, T, 0, Hq, Hkv, ldq, ldk, ldv, softmax_scale, nullptr,
+                          stream);
+}
+
+int b200_attn_fwd_ex(const void* q, const void* k, const void* v, void* o, float* lse,
+                     const void* tiles, int n_tiles, int T, int Tkv, int Hq, int Hkv, long long ldq,
+                     long long ldk, long long ldv, float softmax_scale, const int* key_exit,
+                     cudaStream_t stream) {
   using namespace b200;
   if (n_tiles == 0 || T == 0) return 0;
+  if (Tkv <= 0) Tkv = T;
   if (Hq % Hkv) return -100;
   CUtensorMap tmQ, tmK, tmV;
   int rc = make_tmap_2d(&tmQ, q, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)Hq * kD,
                         ldq * 2, kQT, 64);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)Hkv * kD, ldk * 2,
+  rc = make_tmap_2d(&tmK, k, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tkv, (uint64_t)Hkv * kD, ldk * 2,
                     kKT, 64);
   if (rc) return rc;
-  rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, T, (uint64_t)Hkv * kD, ldv * 2,
+  rc = make_tmap_2d(&tmV, v, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, Tkv, (uint64_t)Hkv * kD, ldv * 2,
                     kKT, 64);
   if (rc) return rc;
   static bool attr_set = false;
@@ -363,7 +391,7 @@ int b200_attn_fwd(const void* q, const void* k, const void* v, void* o, float* l
   dim3 grid(n_tiles, Hq);
   attn_fwd_kernel<<<grid, kAttnThreads, kAttnFwdSmem, stream>>>(
       tmQ, tmK, tmV, reinterpret_cast<const AttnTile*>(tiles), (__nv_bfloat16*)o, lse, T, Hq, Hkv,
-      softmax_scale * 1.4426950408889634f, status);
+      softmax_scale * 1.4426950408889634f, status, key_exit);
   B200_CHECK(cudaGetLastError());
   return 0;
 }
