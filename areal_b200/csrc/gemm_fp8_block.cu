@@ -23,7 +23,7 @@ constexpr int kF8Stages = 6;
 constexpr int kF8TileBytes = kF8BM * kF8BK;           // 16 KB
 constexpr int kF8StageBytes = 2 * kF8TileBytes;       // A + B
 constexpr int kF8Smem = kF8Stages * kF8StageBytes + 1024 + 256;
-constexpr int kF8Threads = 192;
+constexpr int kF8Threads = 320;  // TMA warp, MMA warp, 8 promotion / epilogue warps
 
 __global__ void __launch_bounds__(kF8Threads, 1)
 gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -49,7 +49,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kF8Stages; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 4); }
+    for (int a = 0; a < 2; ++a) { mbar_init(&tfull[a], 1); mbar_init(&tempty[a], 8); }
     *abort_flag = 0;
     fence_mbar_init();
     prefetch_tmap(&tmA);
@@ -130,16 +130,21 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
       }
     }
   } else {
+    // Two warps share every 32-lane quarter of TMEM (a warp may only touch lanes 32 * (warp % 4) ..),
+    // each promoting one 64-column half of the tile: the per-K-block drain is the bottleneck of this
+    // kernel, so it gets eight warps.
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
+    constexpr int kCols = kF8BN / 2;
     bool ok = true;
     long long g = 0;
     for (int it = 0; ok; ++it) {
       int m_blk, n_blk;
       if (!tile_of(it, m_blk, n_blk)) break;
       const int row = m_blk * kF8BM + quarter * 32 + lane;
-      float acc[kF8BN];
+      float acc[kCols];
 #pragma unroll
-      for (int i = 0; i < kF8BN; ++i) acc[i] = 0.f;
+      for (int i = 0; i < kCols; ++i) acc[i] = 0.f;
       for (int kb = 0; kb < kblocks && ok; ++kb, ++g) {
         const int buf = static_cast<int>(g & 1);
         const uint32_t bph = static_cast<uint32_t>((g >> 1) & 1);
@@ -147,9 +152,9 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         tc_fence_after();
         const float s = (row < M ? sa[static_cast<long long>(row) * ldsa + kb] : 0.f) *
                         sb[static_cast<long long>(n_blk) * ldsb + kb];
-        const uint32_t t_row = tmem_base + buf * kF8BN + (static_cast<uint32_t>(quarter * 32) << 16);
+        const uint32_t t_row = tmem_base + buf * kF8BN + half * kCols + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
-        for (int c = 0; c < kF8BN / 32; ++c) {
+        for (int c = 0; c < kCols / 32; ++c) {
           uint32_t r[32];
           tmem_ld_32x32(t_row + c * 32, r);
           tmem_ld_wait();
@@ -161,11 +166,11 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         if (lane == 0) mbar_arrive(&tempty[buf]);
       }
       if (ok && row < M) {
-        const int col0 = n_blk * kF8BN;
+        const int col0 = n_blk * kF8BN + half * kCols;
         __nv_bfloat16* out = C + static_cast<long long>(row) * ldc + col0;
-        if (col0 + kF8BN <= N && (ldc & 7) == 0) {
+        if (col0 + kCols <= N && (ldc & 7) == 0) {
 #pragma unroll
-          for (int i = 0; i < kF8BN / 8; ++i) {
+          for (int i = 0; i < kCols / 8; ++i) {
             uint4 pk;
             __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
 #pragma unroll
@@ -174,7 +179,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           }
         } else {
 #pragma unroll
-          for (int i = 0; i < kF8BN; ++i)
+          for (int i = 0; i < kCols; ++i)
             if (col0 + i < N) out[i] = __float2bfloat16(acc[i]);
         }
       }

@@ -56,8 +56,8 @@ def main(out_path):
     dist.all_to_all_single(ar2, a)
     res["all_to_all_err"] = float((a2a - ar2).abs().max())
     # ---- fused GEMM + collective
-    M, K, N = 4096 * world // world * world, 2048, 4096
-    M = 2048 * world
+    K, N = int(os.environ.get("FUSED_K", 2048)), int(os.environ.get("FUSED_N", 4096))
+    M = int(os.environ.get("FUSED_M", 2048 * world))
     ctx = FL.FusedCommContext(None, max(M * max(K, N) * 2, 8 << 20) * 2)
     xs = (torch.randn(M, K // world, device="cuda") * 0.1).bfloat16()
     ws = (torch.randn(N, K // world, device="cuda") * 0.1).bfloat16()
@@ -97,6 +97,19 @@ def main(out_path):
         return recv
     res["t_gemm_a2a_nccl_ms"] = timed(unfused_a2a)
     res["shape"] = dict(M=M, K=K, N=N)
+    # roofline per op: the slower of the GEMM at the measured cuBLAS peak and the bytes that must cross
+    # NVLink at the measured peer-copy bandwidth (per direction per GPU)
+    peak_flops, link = 1664.7e12, 770e9
+    frac = (world - 1) / world
+    roof = {
+        "gemm_rs": max(2.0 * M * N * (K // world) / peak_flops, frac * M * N * 2 / link),
+        "ag_gemm": max(2.0 * M * (N // world) * K / peak_flops, frac * M * K * 2 / link),
+        "gemm_a2a": max(2.0 * (M // world) * N * K / peak_flops, frac * (M // world) * N * 2 / link),
+    }
+    for k, t in roof.items():
+        res[f"roofline_{k}_ms"] = t * 1e3
+        res[f"frac_of_roofline_{k}_fused"] = t * 1e3 / res[f"t_{k}_fused_ms"]
+        res[f"frac_of_roofline_{k}_nccl"] = t * 1e3 / res[f"t_{k}_nccl_ms"]
     res["status_end"] = _lib.read_status()
     if rank == 0:
         with open(out_path, "w") as f:
