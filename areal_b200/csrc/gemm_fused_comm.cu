@@ -134,6 +134,104 @@ __global__ void reduce_slices_kernel(const __nv_bfloat16* __restrict__ stage,
   }
 }
 
+
+// Barrier-free GEMM → reduce-scatter. Like PeerScatterEpi mode 0, plus: every epilogue warp that has
+// stored its 32 rows of a tile adds 1 to the counter of that row block on the OWNER (release at
+// system scope), so the owner's reduction waits per row block instead of behind a whole-group
+// barrier, and no barrier precedes the GEMM either: the staging buffer is double-buffered, and a
+// rank can only start call i after its reduction of call i-1 has seen every peer's call-(i-1) tiles,
+// which those peers emit after finishing their own reduction of call i-2 (stream order) — so the
+// half written by call i is no longer being read anywhere.
+struct PeerScatterFlagEpi {
+  PeerScatterEpi base;
+  PeerPtrs counters;  // per rank: uint32 [tiles of rows_per_rank]
+  struct State {};
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m, int tiles_n, int& m_blk,
+                                       int& n_blk) const {
+    return base.tile(cta, ncta, it, tiles_m, tiles_n, m_blk, n_blk);
+  }
+  __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ void begin(State&, int, int, int) const {}
+  __device__ __forceinline__ void chunk(State&, int row, int col0, const float (&v)[32]) const {
+    PeerScatterEpi::State s;
+    base.chunk(s, row, col0, v);
+  }
+  __device__ __forceinline__ void end(State&, int m_blk, int, int) const {
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0) {
+      const int row0 = m_blk * kBM;
+      if (row0 < base.M) {
+        const int d = row0 / base.rows_per_rank;
+        uint32_t* cnt = reinterpret_cast<uint32_t*>(counters.p[d]) + (row0 - d * base.rows_per_rank) / kBM;
+        __threadfence_system();
+        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+      }
+    }
+  }
+};
+
+// One block per (local row block, column slab): waits (bounded) until the row block's counter
+// reaches `target`, then sums the `world` staged slices (+ add) into out.
+__global__ void reduce_slices_flag_kernel(const __nv_bfloat16* __restrict__ stage, const __nv_bfloat16* __restrict__ add,
+                                          __nv_bfloat16* __restrict__ out, const uint32_t* __restrict__ counters,
+                                          uint32_t target, int world, int rows, int N, int col_slabs, int* status) {
+  const int tile = blockIdx.x, slab = blockIdx.y;
+  __shared__ int s_ok;
+  if (threadIdx.x == 0) {
+    const uint32_t* c = counters + tile;
+    int ok = 1;
+    if (static_cast<int32_t>(ld_acquire_sys_u32(c) - target) < 0) {
+      const unsigned long long t0 = globaltimer_ns();
+      uint32_t spins = 0;
+      while (static_cast<int32_t>(ld_acquire_sys_u32(c) - target) < 0) {
+        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kWaitDeadlineNs) {
+          atomicCAS(status, 0, kErrPeerFlagTimeout);
+          ok = 0;
+          break;
+        }
+      }
+    }
+    s_ok = ok;
+  }
+  __syncthreads();
+  if (!s_ok) return;
+  const long long slice = static_cast<long long>(rows) * N;
+  const int vec_per_row = N / 8;
+  const int v0 = static_cast<int>(static_cast<long long>(vec_per_row) * slab / col_slabs);
+  const int v1 = static_cast<int>(static_cast<long long>(vec_per_row) * (slab + 1) / col_slabs);
+  const int r0 = tile * kBM, r1 = min(rows, r0 + kBM);
+  const int width = v1 - v0;
+  for (int i = threadIdx.x; i < (r1 - r0) * width; i += blockDim.x) {
+    const long long e = (static_cast<long long>(r0 + i / width) * vec_per_row + v0 + i % width) * 8;
+    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+    for (int s = 0; s < world; ++s) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(stage + s * slice + e);
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(pb[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    if (add) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(add + e);
+      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = __bfloat1622float2(pb[j]);
+        acc[2 * j] += f.x;
+        acc[2 * j + 1] += f.y;
+      }
+    }
+    uint4 pk;
+    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
+    *reinterpret_cast<uint4*>(out + e) = pk;
+  }
+}
+
 // ---------------------------------------------------------------- gated GEMM --
 struct GatedStoreEpi {
   __nv_bfloat16* C;
@@ -315,6 +413,43 @@ int b200_gemm_gated(const void* A, const void* B, void* C, const void* flags, un
   GatedStoreEpi epi{reinterpret_cast<__nv_bfloat16*>(C), ldc, M, N, reinterpret_cast<const uint32_t*>(flags),
                     epoch, rank, world, M / world / kBM};
   return launch_fused(A, B, M, N, K, lda, ldb, epi, stream);
+}
+
+// Barrier-free GEMM → reduce-scatter, first half: C_partial tiles go to the owners' staging buffers
+// (peer_stage[d] = base of the staging half in use) and bump the owners' row-block counters
+// (peer_counters[d], uint32 [M / world / 128]). M must be a multiple of world * 128.
+int b200_gemm_rs_flagged(const void* A, const void* B, void* const* peer_stage, void* const* peer_counters, int world,
+                         int rank, int M, int N, int K, long long lda, long long ldb, cudaStream_t stream) {
+  using namespace b200;
+  if (world < 1 || world > kMaxPeers) return -100;
+  if (M % (world * kBM)) return -101;
+  PeerScatterFlagEpi epi;
+  for (int i = 0; i < world; ++i) { epi.base.dst.p[i] = peer_stage[i]; epi.counters.p[i] = peer_counters[i]; }
+  epi.base.M = M; epi.base.N = N; epi.base.mode = 0; epi.base.rank = rank; epi.base.world = world;
+  epi.base.rows_per_rank = M / world;
+  epi.base.cols_per_rank = N / world;
+  return launch_fused(A, B, M, N, K, lda, ldb, epi, stream);
+}
+
+// Second half: out[rows, N] = sum over the `world` staged slices (+ add) once every row block's counter has
+// reached `target` (= counter value expected after this call: previous target + world * ceil(N/256) * 4).
+int b200_reduce_slices_flagged(const void* stage, const void* add, void* out, const void* counters, unsigned target,
+                               int world, int rows, int N, cudaStream_t stream) {
+  using namespace b200;
+  if (rows == 0) return 0;
+  if ((N & 7) || (rows % kBM)) return -101;
+  int* status = device_status_word();
+  if (!status) return -3;
+  const int tiles = rows / kBM;
+  int slabs = (2 * sm_count() + tiles - 1) / tiles;
+  if (slabs < 1) slabs = 1;
+  if (slabs > N / 8) slabs = N / 8;
+  dim3 grid(tiles, slabs);
+  reduce_slices_flag_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)stage, (const __nv_bfloat16*)add,
+                                                      (__nv_bfloat16*)out, (const uint32_t*)counters, target, world,
+                                                      rows, N, slabs, status);
+  B200_CHECK(cudaGetLastError());
+  return 0;
 }
 
 }  // extern "C"
