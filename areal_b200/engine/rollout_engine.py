@@ -66,13 +66,18 @@ class PagedScheduler:
         self.max_num_seqs, self.max_blocks_per_seq = max_num_seqs, max_blocks_per_seq
         self.block_size = block_size
         cap = max(max_batched_tokens, max_num_seqs)
+        # the plan lands in pinned host memory (when CUDA is there), so a step's inputs go to the
+        # device straight from the arrays the C++ scheduler filled; numpy views share the storage
+        pin = torch.cuda.is_available()
+        mk = lambda n, dt: torch.zeros(n, dtype=dt, pin_memory=pin)
+        self.t_tokens, self.t_positions = mk(cap, torch.int32), mk(cap, torch.int32)
+        self.t_slots, self.t_seq_lens = mk(cap, torch.int64), mk(max_num_seqs, torch.int32)
+        self.t_block_table = mk(max_num_seqs * max_blocks_per_seq, torch.int32)
         self.seq_ids = np.zeros(max_num_seqs, dtype=np.int64)
         self.cu = np.zeros(max_num_seqs + 1, dtype=np.int32)
-        self.tokens = np.zeros(cap, dtype=np.int32)
-        self.positions = np.zeros(cap, dtype=np.int32)
-        self.slots = np.zeros(cap, dtype=np.int64)
-        self.seq_lens = np.zeros(max_num_seqs, dtype=np.int32)
-        self.block_table = np.zeros(max_num_seqs * max_blocks_per_seq, dtype=np.int32)
+        self.tokens, self.positions = self.t_tokens.numpy(), self.t_positions.numpy()
+        self.slots, self.seq_lens = self.t_slots.numpy(), self.t_seq_lens.numpy()
+        self.block_table = self.t_block_table.numpy()
         self.hdr = _PlanHeader()
 
     @staticmethod
@@ -137,25 +142,23 @@ class _DecodeGraphs:
         mb = engine.sched.max_blocks_per_seq
         self.sizes = sorted({b for b in batch_sizes if b <= engine.ncfg.max_num_seqs} | {engine.ncfg.max_num_seqs})
         maxb = self.sizes[-1]
-        self.ids = torch.zeros(maxb, dtype=torch.int64, device=dev)
-        self.pos = torch.zeros(maxb, dtype=torch.int64, device=dev)
+        self.ids = torch.zeros(maxb, dtype=torch.int32, device=dev)
+        self.pos = torch.zeros(maxb, dtype=torch.int32, device=dev)
         self.slots = torch.full((maxb,), -1, dtype=torch.int64, device=dev)
         self.seq_lens = torch.zeros(maxb, dtype=torch.int32, device=dev)
         self.bt = torch.zeros((maxb, mb), dtype=torch.int32, device=dev)
         self.temp = torch.ones(maxb, dtype=torch.float32, device=dev)
         self.u = torch.zeros(maxb, dtype=torch.float32, device=dev)
         pin = dict(pin_memory=True)
-        self.h_ids = torch.zeros(maxb, dtype=torch.int64, **pin)
-        self.h_pos = torch.zeros(maxb, dtype=torch.int64, **pin)
-        self.h_slots = torch.zeros(maxb, dtype=torch.int64, **pin)
-        self.h_lens = torch.zeros(maxb, dtype=torch.int32, **pin)
-        self.h_bt = torch.zeros((maxb, mb), dtype=torch.int32, **pin)
+        self.h_pad_slots = torch.full((maxb,), -1, dtype=torch.int64, **pin)
+        self.h_pad_lens = torch.zeros(maxb, dtype=torch.int32, **pin)
         self.h_temp = torch.ones(maxb, dtype=torch.float32, **pin)
         self.h_tok = torch.zeros(maxb, dtype=torch.int32, **pin)
         self.h_lp = torch.zeros(maxb, dtype=torch.float32, **pin)
         self.graphs: dict[int, tuple[torch.cuda.CUDAGraph, torch.Tensor, torch.Tensor]] = {}
         self.pool = None
         self.prev_n = 0
+        self._last_temps = None
 
     def _forward(self, b: int):
         e = self.e
@@ -184,31 +187,32 @@ class _DecodeGraphs:
         return None
 
     def run(self, n: int, b: int, sched: "PagedScheduler", temps: list[float], rng) -> tuple[np.ndarray, np.ndarray]:
-        nbw = max((int(sched.hdr.max_seq_len) + sched.block_size - 1) // sched.block_size, 1)
-        self.h_ids[:n] = torch.from_numpy(sched.tokens[:n])
-        self.h_pos[:n] = torch.from_numpy(sched.positions[:n])
-        self.h_slots[:n] = torch.from_numpy(sched.slots[:n])
-        self.h_lens[:n] = torch.from_numpy(sched.seq_lens[:n])
-        self.h_bt[:n, :nbw] = torch.from_numpy(sched.block_table[: n * sched.max_blocks_per_seq]).view(n, -1)[:, :nbw]
-        self.h_temp[:n] = torch.tensor(temps, dtype=torch.float32)
-        stale = max(self.prev_n, n)  # rows used by the previous step but not by this one become padding
-        if stale > n:
-            self.h_lens[n:stale] = 0
-            self.h_slots[n:stale] = -1
-        m = stale
-        self.ids[:n].copy_(self.h_ids[:n], non_blocking=True)
-        self.pos[:n].copy_(self.h_pos[:n], non_blocking=True)
-        self.slots[:m].copy_(self.h_slots[:m], non_blocking=True)
-        self.seq_lens[:m].copy_(self.h_lens[:m], non_blocking=True)
-        self.bt[:n].copy_(self.h_bt[:n], non_blocking=True)
-        self.temp[:n].copy_(self.h_temp[:n], non_blocking=True)
+        ts0 = time.perf_counter()
+        mb = sched.max_blocks_per_seq
+        # inputs go to the device straight from the scheduler's pinned plan arrays
+        self.ids[:n].copy_(sched.t_tokens[:n], non_blocking=True)
+        self.pos[:n].copy_(sched.t_positions[:n], non_blocking=True)
+        self.slots[:n].copy_(sched.t_slots[:n], non_blocking=True)
+        self.seq_lens[:n].copy_(sched.t_seq_lens[:n], non_blocking=True)
+        self.bt[:n].copy_(sched.t_block_table[: n * mb].view(n, mb), non_blocking=True)
+        if self.prev_n > n:  # rows used by the previous step but not by this one become padding
+            self.slots[n:self.prev_n].copy_(self.h_pad_slots[n:self.prev_n], non_blocking=True)
+            self.seq_lens[n:self.prev_n].copy_(self.h_pad_lens[n:self.prev_n], non_blocking=True)
+        if temps != self._last_temps:
+            self.h_temp[:n] = torch.tensor(temps, dtype=torch.float32)
+            self.temp[:n].copy_(self.h_temp[:n], non_blocking=True)
+            self._last_temps = temps
         self.u[:b].uniform_(generator=rng)
         self.prev_n = n
         g, toks, lps = self.graphs[b]
         g.replay()
         self.h_tok[:n].copy_(toks[:n], non_blocking=True)
         self.h_lp[:n].copy_(lps[:n], non_blocking=True)
+        ts1 = time.perf_counter()
         torch.cuda.current_stream().synchronize()
+        ts2 = time.perf_counter()
+        self.e._phase_s["stage"] += ts1 - ts0
+        self.e._phase_s["wait"] += ts2 - ts1
         _lib.count_launch(self.e.launches_per_decode)
         return self.h_tok[:n].numpy(), self.h_lp[:n].numpy()
 
@@ -236,6 +240,8 @@ class NativeRolloutEngine(InferenceEngine):
         self._idle = threading.Event()
         self._idle.set()
         self._step_lock = threading.Lock()
+        # host seconds spent in the phases of decode steps (plan / parameter lookup / stage+replay+sync / commit)
+        self._phase_s = {"plan": 0.0, "params": 0.0, "run": 0.0, "commit_deliver": 0.0, "stage": 0.0, "wait": 0.0}
 
     # ------------------------------------------------------------------ setup
     def initialize(self, engine_id: str | None = None, train_data_parallel_size: int | None = None,
@@ -362,23 +368,33 @@ class NativeRolloutEngine(InferenceEngine):
     @torch.no_grad()
     def _step(self) -> bool:
         s = self.sched
+        tp0 = time.perf_counter()
         kind = s.plan()
+        self._phase_s["plan"] += time.perf_counter() - tp0
         if kind == 0:
             self._deliver()
             return False
         n, T = s.hdr.n_seqs, s.hdr.n_tokens
         dev = self.device
         if kind != 1 and self._graphs is not None:
+            t0 = time.perf_counter()
             seq_ids = s.seq_ids[:n].tolist()
             with self._lock:
                 pr = [self._params.get(r, (1.0, 0, 1.0)) for r in seq_ids]
             b = self._graphs.bucket(n)
             if b is not None and not any(p[1] > 0 or p[2] < 1.0 for p in pr):
+                t1 = time.perf_counter()
                 toks, lps = self._graphs.run(n, b, s, [p[0] for p in pr], self._rng)
+                t2 = time.perf_counter()
                 s.commit(toks, lps)
                 self._gen_tokens += n
                 self._steps += 1
                 self._deliver()
+                t3 = time.perf_counter()
+                tm = self._phase_s
+                tm["params"] += t1 - t0
+                tm["run"] += t2 - t1
+                tm["commit_deliver"] += t3 - t2
                 return True
         ids = torch.from_numpy(s.tokens[:T].copy()).to(dev, non_blocking=True)
         pos = torch.from_numpy(s.positions[:T].copy()).to(dev, non_blocking=True)
@@ -602,6 +618,8 @@ class NativeRolloutEngine(InferenceEngine):
         st = {f"rollout/{k}": float(v) for k, v in self.sched.stats().items()}
         st["rollout/generated_tokens"] = float(self._gen_tokens)
         st["rollout/engine_steps"] = float(self._steps)
+        for k, v in self._phase_s.items():
+            st[f"rollout/host_s/{k}"] = v
         if self._executor is not None:
             st.update(self._executor.export_stats())
         return st
