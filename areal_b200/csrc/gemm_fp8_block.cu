@@ -18,10 +18,12 @@
 
 namespace b200 {
 
-constexpr int kF8BM = 128, kF8BN = 128, kF8BK = 128;  // BK in elements == bytes
-constexpr int kF8Stages = 6;
-constexpr int kF8TileBytes = kF8BM * kF8BK;           // 16 KB
-constexpr int kF8StageBytes = 2 * kF8TileBytes;       // A + B
+constexpr int kF8BM = 128, kF8BN = 256, kF8BK = 128;  // BK in elements == bytes; a tile spans two 128-wide weight scale blocks
+constexpr int kF8Stages = 4;
+constexpr int kF8ABytes = kF8BM * kF8BK;              // 16 KB
+constexpr int kF8BBytes = kF8BN * kF8BK;              // 32 KB
+constexpr int kF8StageBytes = kF8ABytes + kF8BBytes;  // the wider tile halves the operand bytes per FLOP:
+                                                      // the kernel is bound by the shared-memory fill rate
 constexpr int kF8Smem = kF8Stages * kF8StageBytes + 1024 + 256;
 constexpr int kF8Threads = 320;  // TMA warp, MMA warp, 8 promotion / epilogue warps
 
@@ -33,7 +35,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint8_t* smem_a = smem;
-  uint8_t* smem_b = smem + kF8Stages * kF8TileBytes;
+  uint8_t* smem_b = smem + kF8Stages * kF8ABytes;
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kF8Stages * kF8StageBytes);
   uint64_t* full = bars;
   uint64_t* empty = bars + kF8Stages;
@@ -56,7 +58,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
     prefetch_tmap(&tmB);
   }
   if (warp == 1) {
-    tmem_alloc(tmem_holder, 256);
+    tmem_alloc(tmem_holder, 512);
     tmem_relinquish();
   }
   tc_fence_before();
@@ -87,8 +89,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         for (int kb = 0; kb < kblocks; ++kb) {
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
           mbar_arrive_expect_tx(&full[stage], kF8StageBytes);
-          tma_load_2d(smem_a + stage * kF8TileBytes, &tmA, &full[stage], kb * kF8BK, m_blk * kF8BM);
-          tma_load_2d(smem_b + stage * kF8TileBytes, &tmB, &full[stage], kb * kF8BK, n_blk * kF8BN);
+          tma_load_2d(smem_a + stage * kF8ABytes, &tmA, &full[stage], kb * kF8BK, m_blk * kF8BM);
+          tma_load_2d(smem_b + stage * kF8BBytes, &tmB, &full[stage], kb * kF8BK, n_blk * kF8BN);
           if (++stage == kF8Stages) { stage = 0; phase ^= 1; }
         }
       }
@@ -113,8 +115,8 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
           if (!mbar_wait(&tempty[buf], bph ^ 1, abort_flag)) { ok = false; break; }
           if (!mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
           tc_fence_after();
-          const uint32_t a_addr = smem_u32(smem_a + stage * kF8TileBytes);
-          const uint32_t b_addr = smem_u32(smem_b + stage * kF8TileBytes);
+          const uint32_t a_addr = smem_u32(smem_a + stage * kF8ABytes);
+          const uint32_t b_addr = smem_u32(smem_b + stage * kF8BBytes);
 #pragma unroll
           for (int k = 0; k < kF8BK / 32; ++k)
             umma_f8(tmem_base + buf * kF8BN, make_sdesc_sw128(a_addr + k * 32, 16, 1024),
@@ -150,8 +152,10 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
         const uint32_t bph = static_cast<uint32_t>((g >> 1) & 1);
         if (!mbar_wait(&tfull[buf], bph, abort_flag)) { ok = false; break; }
         tc_fence_after();
+        // this warp's 128 columns lie inside one 128-wide weight scale block
+        const int sb_row = min(n_blk * (kF8BN / 128) + half, (N + 127) / 128 - 1);
         const float s = (row < M ? sa[static_cast<long long>(row) * ldsa + kb] : 0.f) *
-                        sb[static_cast<long long>(n_blk) * ldsb + kb];
+                        sb[static_cast<long long>(sb_row) * ldsb + kb];
         const uint32_t t_row = tmem_base + buf * kF8BN + half * kCols + (static_cast<uint32_t>(quarter * 32) << 16);
 #pragma unroll
         for (int c = 0; c < kCols / 32; ++c) {
@@ -193,7 +197,7 @@ gemm_fp8_block_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_cons
   __syncthreads();
   if (warp == 1) {
     tc_fence_after();
-    tmem_dealloc(tmem_base, 256);
+    tmem_dealloc(tmem_base, 512);
   }
 }
 

@@ -58,44 +58,60 @@ struct PeerScatterEpi {
   __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
   __device__ __forceinline__ void begin(State&, int, int, int) const {}
   __device__ __forceinline__ void end(State&, int, int, int) const {}
-  __device__ __forceinline__ void chunk(State&, int row, int col0, const float (&v)[32]) const {
-    if (row >= M || col0 >= N) return;
-    __nv_bfloat16* base;
-    long long off;
-    int limit;  // columns of this chunk that belong to the same destination
+  // Destination of (row, col) and how many columns from col on share it.
+  __device__ __forceinline__ __nv_bfloat16* dest(int row, int col, int& run) const {
     if (mode == 0) {
       const int d = row / rows_per_rank;
-      base = reinterpret_cast<__nv_bfloat16*>(dst.p[d]);
-      off = (static_cast<long long>(rank) * rows_per_rank + (row - d * rows_per_rank)) * N + col0;
-      limit = min(32, N - col0);
-    } else {
-      const int d = col0 / cols_per_rank;
-      base = reinterpret_cast<__nv_bfloat16*>(dst.p[d]);
-      off = (static_cast<long long>(rank) * M + row) * cols_per_rank + (col0 - d * cols_per_rank);
-      limit = min(min(32, N - col0), (d + 1) * cols_per_rank - col0);
+      run = N - col;
+      return reinterpret_cast<__nv_bfloat16*>(dst.p[d]) +
+             (static_cast<long long>(rank) * rows_per_rank + (row - d * rows_per_rank)) * N + col;
     }
-    __nv_bfloat16* out = base + off;
-    if (limit == 32 && (reinterpret_cast<uintptr_t>(out) & 15) == 0) {
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        uint4 pk;
-        __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-        for (int j = 0; j < 4; ++j) pb[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
-        reinterpret_cast<uint4*>(out)[i] = pk;
-      }
-    } else {
-      // ragged edge (or a chunk straddling two destinations in mode 1): element-wise
-      for (int i = 0; i < 32 && col0 + i < N; ++i) {
-        if (mode == 1) {
-          const int c = col0 + i, d = c / cols_per_rank;
-          reinterpret_cast<__nv_bfloat16*>(dst.p[d])[(static_cast<long long>(rank) * M + row) * cols_per_rank +
-                                                     (c - d * cols_per_rank)] = __float2bfloat16(v[i]);
-        } else {
-          out[i] = __float2bfloat16(v[i]);
+    const int d = col / cols_per_rank;
+    run = (d + 1) * cols_per_rank - col;
+    return reinterpret_cast<__nv_bfloat16*>(dst.p[d]) + (static_cast<long long>(rank) * M + row) * cols_per_rank +
+           (col - d * cols_per_rank);
+  }
+
+  // A thread owns one accumulator ROW, so storing straight from registers would emit 32 scattered
+  // 16-byte writes per instruction — poison for NVLink (and poor for HBM). Each epilogue warp
+  // therefore parks two 32-column chunks (its 32 rows x 128 bytes) in shared memory and writes them
+  // out row-wise: 8 lanes cover the 128 contiguous bytes of a row, 4 rows per store instruction.
+  __device__ __forceinline__ void chunk(State&, int row, int col0, const float (&v)[32]) const {
+    __shared__ uint4 s_stage[4][32][8];  // [epilogue warp][row][16-byte piece], pieces XOR-swizzled by row
+    const int lane = threadIdx.x & 31, wq = (threadIdx.x >> 5) & 3;
+    const int pair = (col0 >> 5) & 1;  // first or second half of the 64-column group
+    const int group0 = col0 - pair * 32;
+    const bool fast = (group0 + 64 <= N) && ((N & 7) == 0) && (mode == 0 || (cols_per_rank % 64) == 0);
+    if (!fast) {  // ragged edge: element-wise, destination per element
+      if (row < M)
+        for (int i = 0; i < 32 && col0 + i < N; ++i) {
+          int run;
+          *dest(row, col0 + i, run) = __float2bfloat16(v[i]);
         }
+      return;
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 pk;
+      __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) pb[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+      s_stage[wq][lane][(pair * 4 + i) ^ (lane & 7)] = pk;
+    }
+    if (pair == 0) return;
+    __syncwarp();
+    const int row_base = row - lane;  // first row of this warp's 32
+    const int piece = lane & 7;
+#pragma unroll
+    for (int it = 0; it < 8; ++it) {
+      const int r = it * 4 + (lane >> 3);
+      if (row_base + r < M) {
+        int run;
+        __nv_bfloat16* out = dest(row_base + r, group0 + piece * 8, run);
+        *reinterpret_cast<uint4*>(out) = s_stage[wq][r][piece ^ (r & 7)];
       }
     }
+    __syncwarp();
   }
 };
 
@@ -135,102 +151,139 @@ __global__ void reduce_slices_kernel(const __nv_bfloat16* __restrict__ stage,
 }
 
 
-// Barrier-free GEMM → reduce-scatter. Like PeerScatterEpi mode 0, plus: every epilogue warp that has
-// stored its 32 rows of a tile adds 1 to the counter of that row block on the OWNER (release at
-// system scope), so the owner's reduction waits per row block instead of behind a whole-group
-// barrier, and no barrier precedes the GEMM either: the staging buffer is double-buffered, and a
-// rank can only start call i after its reduction of call i-1 has seen every peer's call-(i-1) tiles,
-// which those peers emit after finishing their own reduction of call i-2 (stream order) — so the
-// half written by call i is no longer being read anywhere.
-struct PeerScatterFlagEpi {
-  PeerScatterEpi base;
-  PeerPtrs counters;  // per rank: uint32 [tiles of rows_per_rank]
-  struct State {};
-  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m, int tiles_n, int& m_blk,
+// Barrier-free, single-kernel GEMM → reduce-scatter.
+//
+// Tiles whose rows belong to a PEER are computed first and stored (coalesced, see PeerScatterEpi) into
+// that peer's staging buffer; each epilogue warp then adds 1 to the peer's counter of that
+// (row block, column block) with release semantics at system scope. Tiles whose rows this rank OWNS
+// come last: their epilogue waits (bounded) until the counter shows that every peer's partial tile
+// has landed, adds the staged partials (and an optional residual) to its own accumulator and writes
+// the final bf16 result. No barrier, no separate reduction pass: the transfers of the first phase
+// overlap the math, and the staging buffer is double-buffered — a rank can only start call i after
+// its call i-1 kernel has consumed every peer's call-(i-1) tiles, which those peers emit after
+// finishing their own call i-2 kernel (stream order), so the half written by call i is not being
+// read anywhere.
+struct GemmReduceScatterEpi {
+  PeerScatterEpi base;                 // mode 0: destinations and coalesced peer stores
+  PeerPtrs counters;                   // per rank: uint32 [row blocks of rows_per_rank][tiles_n]
+  const __nv_bfloat16* local_stage;    // this rank's staging half: [world][rows_per_rank][N]
+  const uint32_t* local_counters;
+  const __nv_bfloat16* add;            // optional [rows_per_rank, N]
+  __nv_bfloat16* out;                  // [rows_per_rank, N]
+  uint32_t* expected;                  // local, [entries][4]: arrivals each epilogue warp has already consumed
+                                       // (kept on the device so calls of different shapes can share the counters)
+  int tiles_n, tiles_per_rank;
+  int* status;
+  struct State { int own; int ok; };
+
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m, int tiles_n_, int& m_blk,
                                        int& n_blk) const {
-    return base.tile(cta, ncta, it, tiles_m, tiles_n, m_blk, n_blk);
+    int mm;
+    if (!default_tile(cta, ncta, it, tiles_m, tiles_n_, mm, n_blk)) return false;
+    // ring order: owner rank+1 first, ..., this rank's own rows last
+    const int owner = (base.rank + 1 + mm / tiles_per_rank) % base.world;
+    m_blk = owner * tiles_per_rank + mm % tiles_per_rank;
+    return true;
   }
   __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
-  __device__ __forceinline__ void begin(State&, int, int, int) const {}
-  __device__ __forceinline__ void chunk(State&, int row, int col0, const float (&v)[32]) const {
-    PeerScatterEpi::State s;
-    base.chunk(s, row, col0, v);
-  }
-  __device__ __forceinline__ void end(State&, int m_blk, int, int) const {
-    __syncwarp();
-    if ((threadIdx.x & 31) == 0) {
-      const int row0 = m_blk * kBM;
-      if (row0 < base.M) {
-        const int d = row0 / base.rows_per_rank;
-        uint32_t* cnt = reinterpret_cast<uint32_t*>(counters.p[d]) + (row0 - d * base.rows_per_rank) / kBM;
-        __threadfence_system();
-        asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
-      }
-    }
-  }
-};
-
-// One block per (local row block, column slab): waits (bounded) until the row block's counter
-// reaches `target`, then sums the `world` staged slices (+ add) into out.
-__global__ void reduce_slices_flag_kernel(const __nv_bfloat16* __restrict__ stage, const __nv_bfloat16* __restrict__ add,
-                                          __nv_bfloat16* __restrict__ out, const uint32_t* __restrict__ counters,
-                                          uint32_t target, int world, int rows, int N, int col_slabs, int* status) {
-  const int tile = blockIdx.x, slab = blockIdx.y;
-  __shared__ int s_ok;
-  if (threadIdx.x == 0) {
-    const uint32_t* c = counters + tile;
+  __device__ __forceinline__ void begin(State& st, int m_blk, int n_blk, int) const {
+    st.own = (m_blk / tiles_per_rank) == base.rank;
+    st.ok = 1;
+    if (!st.own) return;
     int ok = 1;
-    if (static_cast<int32_t>(ld_acquire_sys_u32(c) - target) < 0) {
-      const unsigned long long t0 = globaltimer_ns();
-      uint32_t spins = 0;
-      while (static_cast<int32_t>(ld_acquire_sys_u32(c) - target) < 0) {
-        if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kWaitDeadlineNs) {
-          atomicCAS(status, 0, kErrPeerFlagTimeout);
-          ok = 0;
-          break;
+    if ((threadIdx.x & 31) == 0) {
+      const int entry = (m_blk % tiles_per_rank) * tiles_n + n_blk;
+      const uint32_t* c = local_counters + entry;
+      uint32_t* exp = expected + entry * 4 + ((threadIdx.x >> 5) & 3);
+      const uint32_t target = *exp + static_cast<uint32_t>(base.world - 1) * 4u;  // 4 warps per peer tile
+      *exp = target;
+      if (static_cast<int32_t>(ld_acquire_sys_u32(c) - target) < 0) {
+        const unsigned long long t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        while (static_cast<int32_t>(ld_acquire_sys_u32(c) - target) < 0) {
+          if ((++spins & 0xff) == 0 && globaltimer_ns() - t0 > kWaitDeadlineNs) {
+            atomicCAS(status, 0, kErrPeerFlagTimeout);
+            ok = 0;
+            break;
+          }
         }
       }
     }
-    s_ok = ok;
+    st.ok = __shfl_sync(0xffffffffu, ok, 0);
   }
-  __syncthreads();
-  if (!s_ok) return;
-  const long long slice = static_cast<long long>(rows) * N;
-  const int vec_per_row = N / 8;
-  const int v0 = static_cast<int>(static_cast<long long>(vec_per_row) * slab / col_slabs);
-  const int v1 = static_cast<int>(static_cast<long long>(vec_per_row) * (slab + 1) / col_slabs);
-  const int r0 = tile * kBM, r1 = min(rows, r0 + kBM);
-  const int width = v1 - v0;
-  for (int i = threadIdx.x; i < (r1 - r0) * width; i += blockDim.x) {
-    const long long e = (static_cast<long long>(r0 + i / width) * vec_per_row + v0 + i % width) * 8;
-    float acc[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-    for (int s = 0; s < world; ++s) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(stage + s * slice + e);
-      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+  __device__ __forceinline__ void chunk(State& st, int row, int col0, const float (&v_in)[32]) const {
+    if (!st.own) {
+      PeerScatterEpi::State s;
+      base.chunk(s, row, col0, v_in);
+      return;
+    }
+    if (row >= base.M || col0 >= base.N || !st.ok) return;
+    const int lr = row - base.rank * base.rows_per_rank;
+    const long long off = static_cast<long long>(lr) * base.N + col0;
+    const long long slice = static_cast<long long>(base.rows_per_rank) * base.N;
+    const bool full = (col0 + 32 <= base.N) && ((base.N & 7) == 0);
+    float v[32];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(pb[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
+    for (int i = 0; i < 32; ++i) v[i] = v_in[i];
+    if (full) {
+      for (int s = 0; s < base.world; ++s) {
+        if (s == base.rank) continue;
+        const uint4* p = reinterpret_cast<const uint4*>(local_stage + s * slice + off);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 raw = p[i];
+          const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(pb[j]);
+            v[8 * i + 2 * j] += f.x;
+            v[8 * i + 2 * j + 1] += f.y;
+          }
+        }
+      }
+      if (add) {
+        const uint4* p = reinterpret_cast<const uint4*>(add + off);
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          const uint4 raw = p[i];
+          const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float2 f = __bfloat1622float2(pb[j]);
+            v[8 * i + 2 * j] += f.x;
+            v[8 * i + 2 * j + 1] += f.y;
+          }
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 pk;
+        __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pb[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+        reinterpret_cast<uint4*>(out + off)[i] = pk;
+      }
+    } else {
+      for (int i = 0; i < 32 && col0 + i < base.N; ++i) {
+        float x = v[i];
+        for (int s = 0; s < base.world; ++s)
+          if (s != base.rank) x += __bfloat162float(local_stage[s * slice + off + i]);
+        if (add) x += __bfloat162float(add[off + i]);
+        out[off + i] = __float2bfloat16(x);
       }
     }
-    if (add) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(add + e);
-      const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&raw);
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float2 f = __bfloat1622float2(pb[j]);
-        acc[2 * j] += f.x;
-        acc[2 * j + 1] += f.y;
-      }
-    }
-    uint4 pk;
-    __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&pk);
-#pragma unroll
-    for (int j = 0; j < 4; ++j) po[j] = __floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]);
-    *reinterpret_cast<uint4*>(out + e) = pk;
   }
-}
+  __device__ __forceinline__ void end(State& st, int m_blk, int n_blk, int) const {
+    if (st.own) return;
+    __syncwarp();
+    if ((threadIdx.x & 31) == 0 && m_blk * kBM < base.M) {
+      const int d = m_blk / tiles_per_rank;
+      uint32_t* cnt = reinterpret_cast<uint32_t*>(counters.p[d]) + (m_blk % tiles_per_rank) * tiles_n + n_blk;
+      __threadfence_system();
+      asm volatile("red.release.sys.global.add.u32 [%0], 1;" ::"l"(cnt) : "memory");
+    }
+  }
+};
 
 // ---------------------------------------------------------------- gated GEMM --
 struct GatedStoreEpi {
@@ -415,41 +468,34 @@ int b200_gemm_gated(const void* A, const void* B, void* C, const void* flags, un
   return launch_fused(A, B, M, N, K, lda, ldb, epi, stream);
 }
 
-// Barrier-free GEMM → reduce-scatter, first half: C_partial tiles go to the owners' staging buffers
-// (peer_stage[d] = base of the staging half in use) and bump the owners' row-block counters
-// (peer_counters[d], uint32 [M / world / 128]). M must be a multiple of world * 128.
-int b200_gemm_rs_flagged(const void* A, const void* B, void* const* peer_stage, void* const* peer_counters, int world,
-                         int rank, int M, int N, int K, long long lda, long long ldb, cudaStream_t stream) {
+// Single-kernel GEMM → reduce-scatter: out[M/world, N] = rows of sum_ranks(A_r B_r^T) owned by this rank
+// (+ add). peer_stage[d] / peer_counters[d]: rank d's staging half ([world][M/world][N] bf16) and counter
+// array (uint32 [M/world/128][ceil(N/256)]) of the half in use; local_* are this rank's own; `expected`
+// is a zero-initialised local uint32 array with 4 entries per counter that the kernel maintains itself.
+// M must be a multiple of world * 128.
+int b200_gemm_rs_fused(const void* A, const void* B, void* const* peer_stage, void* const* peer_counters,
+                       const void* local_stage, const void* local_counters, void* expected, const void* add,
+                       void* out, int world, int rank, int M, int N, int K, long long lda, long long ldb,
+                       cudaStream_t stream) {
   using namespace b200;
   if (world < 1 || world > kMaxPeers) return -100;
   if (M % (world * kBM)) return -101;
-  PeerScatterFlagEpi epi;
+  int* status = device_status_word();
+  if (!status) return -3;
+  GemmReduceScatterEpi epi;
   for (int i = 0; i < world; ++i) { epi.base.dst.p[i] = peer_stage[i]; epi.counters.p[i] = peer_counters[i]; }
   epi.base.M = M; epi.base.N = N; epi.base.mode = 0; epi.base.rank = rank; epi.base.world = world;
   epi.base.rows_per_rank = M / world;
   epi.base.cols_per_rank = N / world;
+  epi.local_stage = reinterpret_cast<const __nv_bfloat16*>(local_stage);
+  epi.local_counters = reinterpret_cast<const uint32_t*>(local_counters);
+  epi.add = reinterpret_cast<const __nv_bfloat16*>(add);
+  epi.out = reinterpret_cast<__nv_bfloat16*>(out);
+  epi.expected = reinterpret_cast<uint32_t*>(expected);
+  epi.tiles_n = (N + 255) / 256;
+  epi.tiles_per_rank = M / world / kBM;
+  epi.status = status;
   return launch_fused(A, B, M, N, K, lda, ldb, epi, stream);
-}
-
-// Second half: out[rows, N] = sum over the `world` staged slices (+ add) once every row block's counter has
-// reached `target` (= counter value expected after this call: previous target + world * ceil(N/256) * 4).
-int b200_reduce_slices_flagged(const void* stage, const void* add, void* out, const void* counters, unsigned target,
-                               int world, int rows, int N, cudaStream_t stream) {
-  using namespace b200;
-  if (rows == 0) return 0;
-  if ((N & 7) || (rows % kBM)) return -101;
-  int* status = device_status_word();
-  if (!status) return -3;
-  const int tiles = rows / kBM;
-  int slabs = (2 * sm_count() + tiles - 1) / tiles;
-  if (slabs < 1) slabs = 1;
-  if (slabs > N / 8) slabs = N / 8;
-  dim3 grid(tiles, slabs);
-  reduce_slices_flag_kernel<<<grid, 256, 0, stream>>>((const __nv_bfloat16*)stage, (const __nv_bfloat16*)add,
-                                                      (__nv_bfloat16*)out, (const uint32_t*)counters, target, world,
-                                                      rows, N, slabs, status);
-  B200_CHECK(cudaGetLastError());
-  return 0;
 }
 
 }  // extern "C"

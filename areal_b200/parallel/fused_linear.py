@@ -53,7 +53,7 @@ class FusedCommContext:
             self.rs_counters.tensor(torch.int32).zero_()
             self._rs_cnt_tbl = [self.rs_counters.ptr_table(byte_offset=h * 4096 * 4) for h in range(2)]
             self._rs_stage_tbl = [self.stage.ptr_table(byte_offset=h * (max_stage_bytes // 2)) for h in range(2)]
-            self._rs_target = [0, 0]
+            self._rs_expected = torch.zeros((2, 4096 * 4), dtype=torch.int32, device=self.device)
             self._rs_calls = 0
             torch.cuda.synchronize(self.device)
             if self.world > 1:
@@ -129,24 +129,22 @@ def gemm_reduce_scatter(ctx: FusedCommContext, x: torch.Tensor, w: torch.Tensor,
     assert M % P == 0 and M * N * 2 <= ctx.max_stage_bytes
     x = x if x.is_contiguous() else x.contiguous()
     lib = _lib.kernels()
-    if P > 1 and M % (P * 128) == 0 and N % 8 == 0 and 2 * M * N * 2 <= ctx.max_stage_bytes and M // P // 128 <= 4096:
-        # barrier-free form: double-buffered staging + per-row-block arrival counters
+    n_cnt = (M // P // 128) * (-(-N // 256)) if M % (P * 128) == 0 else 1 << 30
+    if P > 1 and M % (P * 128) == 0 and N % 8 == 0 and 2 * M * N * 2 <= ctx.max_stage_bytes and n_cnt <= 4096:
+        # single kernel, no barrier: peer tiles first (stored into the owners' staging half with arrival
+        # counters), own tiles last (their epilogue adds the staged partials); halves alternate per call
         h = ctx._rs_calls & 1
         ctx._rs_calls += 1
-        ctx._rs_target[h] += P * (-(-N // 256)) * 4
-        rc = lib.b200_gemm_rs_flagged(_lib.ptr(x), _lib.ptr(w), ctx._rs_stage_tbl[h], ctx._rs_cnt_tbl[h],
-                                      ctypes.c_int(P), ctypes.c_int(ctx.rank), ctypes.c_int(M), ctypes.c_int(N),
-                                      ctypes.c_int(K), ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(w.stride(0)),
-                                      _lib.stream_ptr())
-        _lib.check(rc, "b200_gemm_rs_flagged")
-        out = torch.empty((M // P, N), dtype=x.dtype, device=x.device)
         half = ctx.max_stage_bytes // 2
-        rc = lib.b200_reduce_slices_flagged(ctypes.c_void_p(ctx.stage.local_ptr + h * half), _lib.ptr(add), _lib.ptr(out),
-                                            ctypes.c_void_p(ctx.rs_counters.local_ptr + h * 4096 * 4),
-                                            ctypes.c_uint(ctx._rs_target[h] & 0xffffffff), ctypes.c_int(P),
-                                            ctypes.c_int(M // P), ctypes.c_int(N), _lib.stream_ptr())
-        _lib.check(rc, "b200_reduce_slices_flagged")
-        _lib.count_launch(2)
+        out = torch.empty((M // P, N), dtype=x.dtype, device=x.device)
+        rc = lib.b200_gemm_rs_fused(_lib.ptr(x), _lib.ptr(w), ctx._rs_stage_tbl[h], ctx._rs_cnt_tbl[h],
+                                    ctypes.c_void_p(ctx.stage.local_ptr + h * half),
+                                    ctypes.c_void_p(ctx.rs_counters.local_ptr + h * 4096 * 4),
+                                    _lib.ptr(ctx._rs_expected[h]), _lib.ptr(add), _lib.ptr(out), ctypes.c_int(P),
+                                    ctypes.c_int(ctx.rank), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+                                    ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(w.stride(0)), _lib.stream_ptr())
+        _lib.check(rc, "b200_gemm_rs_fused")
+        _lib.count_launch()
         return out
     ctx.barrier.sync()  # peers are done reading their staging buffers from the previous call
     rc = lib.b200_gemm_peer_scatter(_lib.ptr(x), _lib.ptr(w), ctx._stage_tbl, ctypes.c_int(P), ctypes.c_int(ctx.rank),

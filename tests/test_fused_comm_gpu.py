@@ -29,7 +29,7 @@ def test_fused_comm_matches_nccl(tmp_path):
     for k in ("all_gather_err", "all_to_all_err"):
         assert res[k] == 0.0, (k, res[k])
     assert res["reduce_scatter_err"] < 1e-4 and res["all_reduce_err"] < 1e-4
-    for k in ("gemm_rs_err", "ag_gemm_err", "gemm_a2a_err"):
+    for k in ("gemm_rs_err", "ag_gemm_err", "gemm_a2a_err", "gemm_rs_mixed_shapes_err"):
         assert res[k] < 2e-2, (k, res[k])
 
 

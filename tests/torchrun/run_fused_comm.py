@@ -64,6 +64,15 @@ def main(out_path):
     out = FL.gemm_reduce_scatter(ctx, xs, ws)
     ref = FL.gemm_reduce_scatter_ref(xs, ws, None)
     res["gemm_rs_err"] = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
+    # calls of different shapes share the arrival counters: interleave them
+    worst = 0.0
+    for (m2, n2) in ((M // 2, N // 2), (M, N), (M // 2, N), (M, N // 2), (M // 2, N // 2)):
+        xa = (torch.randn(m2, K // world, device="cuda") * 0.1).bfloat16()
+        wa = (torch.randn(n2, K // world, device="cuda") * 0.1).bfloat16()
+        o2 = FL.gemm_reduce_scatter(ctx, xa, wa)
+        r2 = FL.gemm_reduce_scatter_ref(xa, wa, None)
+        worst = max(worst, float((o2.float() - r2.float()).abs().max() / r2.float().abs().max()))
+    res["gemm_rs_mixed_shapes_err"] = worst
     xl = (torch.randn(M // world, K, device="cuda") * 0.1).bfloat16()
     wc = (torch.randn(N // world, K, device="cuda") * 0.1).bfloat16()
     out = FL.all_gather_gemm(ctx, xl, wc)
