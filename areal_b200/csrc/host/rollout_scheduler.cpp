@@ -47,11 +47,17 @@ struct Request {
   int32_t cached_len = 0;  // tokens whose K/V are in the cache
   int finish = kRunning;
   int64_t arrival = 0;
+  uint64_t prompt_hash = 0;
+  bool kv_ready = false;   // the prompt's K/V have been written (its prefill step was committed)
 };
 
 struct Scheduler {
   int num_blocks, block_size, max_num_seqs, max_batched_tokens, max_blocks_per_seq;
   std::vector<int32_t> free_blocks;
+  std::vector<int32_t> refcnt;  // pages may be shared by requests with the same prompt (read-only full pages)
+  std::unordered_map<uint64_t, int64_t> prompt_leader;  // prompt hash -> request whose prompt pages can be shared
+  bool share_prompts = true;
+  int64_t n_forked = 0, n_shared_pages = 0;
   std::unordered_map<int64_t, Request> reqs;
   std::deque<int64_t> waiting;
   std::vector<int64_t> running;
@@ -68,15 +74,30 @@ struct Scheduler {
     if (need > max_blocks_per_seq) return false;
     while (static_cast<int32_t>(r.blocks.size()) < need) {
       if (free_blocks.empty()) return false;
-      r.blocks.push_back(free_blocks.back());
+      const int32_t b = free_blocks.back();
       free_blocks.pop_back();
+      refcnt[b] = 1;
+      r.blocks.push_back(b);
     }
     return true;
   }
   void release(Request& r) {
-    for (int32_t b : r.blocks) free_blocks.push_back(b);
+    for (int32_t b : r.blocks)
+      if (--refcnt[b] == 0) free_blocks.push_back(b);
     r.blocks.clear();
     r.cached_len = 0;
+    r.kv_ready = false;
+  }
+  // A running request with the same prompt whose prompt pages are in the cache, or nullptr.
+  Request* leader_for(const Request& r) {
+    auto it = prompt_leader.find(r.prompt_hash);
+    if (it == prompt_leader.end() || it->second == r.id) return nullptr;
+    auto rq = reqs.find(it->second);
+    if (rq == reqs.end()) return nullptr;
+    Request& l = rq->second;
+    if (l.finish != kRunning || l.prompt_len != r.prompt_len || l.blocks.empty()) return nullptr;
+    if (!std::equal(r.tokens.begin(), r.tokens.begin() + r.prompt_len, l.tokens.begin())) return nullptr;
+    return &l;
   }
   void finish(Request& r, int reason) {
     r.finish = reason;
@@ -101,6 +122,7 @@ void* b200_sched_create(int num_blocks, int block_size, int max_num_seqs, int ma
   s->max_batched_tokens = max_batched_tokens;
   s->max_blocks_per_seq = max_blocks_per_seq;
   s->free_blocks.reserve(num_blocks);
+  s->refcnt.assign(num_blocks, 0);
   for (int b = num_blocks - 1; b >= 0; --b) s->free_blocks.push_back(b);
   return s;
 }
@@ -126,6 +148,12 @@ int64_t b200_sched_add(void* h, const int32_t* prompt, int n_prompt, int max_new
   r.ignore_eos = ignore_eos != 0;
   r.stop_ids.assign(stop_ids, stop_ids + n_stop);
   r.arrival = s->clock++;
+  uint64_t hsh = 1469598103934665603ull;  // FNV-1a over the prompt tokens
+  for (int i = 0; i < n_prompt; ++i) {
+    hsh ^= static_cast<uint32_t>(prompt[i]);
+    hsh *= 1099511628211ull;
+  }
+  r.prompt_hash = hsh;
   const int64_t id = r.id;
   s->reqs.emplace(id, std::move(r));
   s->waiting.push_back(id);
@@ -137,18 +165,29 @@ struct PlanHeader {
   int32_t n_seqs;
   int32_t n_tokens;
   int32_t max_seq_len;
+  int32_t n_copies;  // page copies (src, dst pairs in copy_pairs) to perform before the step runs
+  int32_t pad;
 };
 
 // Buffers must hold: seq_ids[max_num_seqs], cu_seqlens[max_num_seqs+1],
 // tokens/positions/slots[max(max_batched_tokens, max_num_seqs)],
 // seq_lens[max_num_seqs], block_table[max_num_seqs * max_blocks_per_seq].
+// copy_pairs: int32 [2 * max_num_seqs].
+//
+// Prompt sharing: a fresh request whose prompt equals that of a running request with its prompt
+// already in the cache does not prefill. It references the leader's full prompt pages (read-only,
+// reference-counted), gets a private copy of the page that holds the last prompt positions, and
+// enters decoding with the LAST PROMPT TOKEN as its input: the ordinary decode step recomputes that
+// one position and samples the first new token. The n samples of a GRPO group thus prefill once, and
+// their decode attention reads the same prompt pages (adjacent sequences, so the reads hit in L2).
 int b200_sched_plan(void* h, PlanHeader* hdr, int64_t* seq_ids, int32_t* cu_seqlens,
                     int32_t* tokens, int32_t* positions, int64_t* slots, int32_t* seq_lens,
-                    int32_t* block_table) {
+                    int32_t* block_table, int32_t* copy_pairs) {
   auto* s = static_cast<Scheduler*>(h);
   std::lock_guard<std::mutex> lk(s->mu);
   hdr->kind = kIdle;
   hdr->n_seqs = hdr->n_tokens = hdr->max_seq_len = 0;
+  hdr->n_copies = 0;
   s->planned.clear();
   s->planned_kind = kIdle;
 
@@ -157,10 +196,44 @@ int b200_sched_plan(void* h, PlanHeader* hdr, int64_t* seq_ids, int32_t* cu_seql
     int budget = s->max_batched_tokens;
     int n_tok = 0;
     cu_seqlens[0] = 0;
+    std::vector<int64_t> deferred;  // followers whose leader is being prefilled by this very plan
     while (!s->waiting.empty() && static_cast<int>(s->running.size()) < s->max_num_seqs) {
       const int64_t id = s->waiting.front();
       Request& r = s->reqs[id];
       const int32_t L = static_cast<int32_t>(r.tokens.size());
+      if (s->share_prompts && copy_pairs != nullptr && L == r.prompt_len && L >= 2) {
+        if (Request* ld = s->leader_for(r)) {
+          if (!ld->kv_ready) {  // wait one step for the leader's prefill
+            s->waiting.pop_front();
+            deferred.push_back(id);
+            continue;
+          }
+          const int32_t bs = s->block_size;
+          const int32_t nshare = (L - 1) / bs, rem = (L - 1) % bs;
+          if (static_cast<int32_t>(ld->blocks.size()) > nshare) {
+            for (int32_t b = 0; b < nshare; ++b) {
+              r.blocks.push_back(ld->blocks[b]);
+              s->refcnt[ld->blocks[b]]++;
+            }
+            if (s->ensure_blocks(r, L + 1)) {
+              if (rem > 0) {
+                copy_pairs[2 * hdr->n_copies] = ld->blocks[nshare];
+                copy_pairs[2 * hdr->n_copies + 1] = r.blocks[nshare];
+                hdr->n_copies++;
+              }
+              s->waiting.pop_front();
+              r.cached_len = L - 1;
+              r.kv_ready = true;
+              s->running.push_back(id);
+              s->n_forked++;
+              s->n_shared_pages += nshare;
+              continue;
+            }
+            s->release(r);  // no page for the private tail: fall back to waiting
+            break;
+          }
+        }
+      }
       if (L > budget) break;
       // keep one page of head-room per running sequence so decode can proceed
       if (!s->ensure_blocks(r, L + 1)) {
@@ -183,7 +256,9 @@ int b200_sched_plan(void* h, PlanHeader* hdr, int64_t* seq_ids, int32_t* cu_seql
       hdr->n_seqs++;
       s->running.push_back(id);
       s->planned.push_back(id);
+      if (L == r.prompt_len) s->prompt_leader[r.prompt_hash] = id;
     }
+    for (auto it = deferred.rbegin(); it != deferred.rend(); ++it) s->waiting.push_front(*it);
     if (hdr->n_seqs > 0) {
       hdr->kind = kPrefill;
       hdr->n_tokens = n_tok;
@@ -251,12 +326,14 @@ int b200_sched_commit(void* h, const int32_t* sampled, const float* logprobs, in
   auto* s = static_cast<Scheduler*>(h);
   std::lock_guard<std::mutex> lk(s->mu);
   if (n != static_cast<int>(s->planned.size())) return -1;
+  const bool was_prefill = s->planned_kind == kPrefill;
   int done = 0;
   for (int i = 0; i < n; ++i) {
     auto it = s->reqs.find(s->planned[i]);
     if (it == s->reqs.end()) continue;
     Request& r = it->second;
     if (r.finish != kRunning) continue;  // aborted between plan and commit
+    if (was_prefill) r.kv_ready = true;
     r.tokens.push_back(sampled[i]);
     r.logprobs.push_back(logprobs[i]);
     const int32_t n_new = static_cast<int32_t>(r.tokens.size()) - r.prompt_len;
@@ -337,7 +414,8 @@ int b200_sched_take_output(void* h, int64_t id, int32_t* out_tokens, float* out_
   return n;
 }
 
-// stats[0]=waiting, [1]=running, [2]=free blocks, [3]=preemptions, [4]=live requests
+// stats[0]=waiting, [1]=running, [2]=free blocks, [3]=preemptions, [4]=live requests,
+// [5]=requests that skipped their prefill by sharing a prompt, [6]=pages shared that way (cumulative)
 void b200_sched_stats(void* h, int64_t* stats) {
   auto* s = static_cast<Scheduler*>(h);
   std::lock_guard<std::mutex> lk(s->mu);
@@ -346,6 +424,14 @@ void b200_sched_stats(void* h, int64_t* stats) {
   stats[2] = static_cast<int64_t>(s->free_blocks.size());
   stats[3] = s->n_preempt;
   stats[4] = static_cast<int64_t>(s->reqs.size());
+  stats[5] = s->n_forked;
+  stats[6] = s->n_shared_pages;
+}
+
+void b200_sched_set_prompt_sharing(void* h, int on) {
+  auto* s = static_cast<Scheduler*>(h);
+  std::lock_guard<std::mutex> lk(s->mu);
+  s->share_prompts = on != 0;
 }
 
 }  // extern "C"

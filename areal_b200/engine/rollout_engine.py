@@ -50,7 +50,7 @@ _REASONS = {1: "stop", 2: "length", 3: "abort"}
 
 class _PlanHeader(ctypes.Structure):
     _fields_ = [("kind", ctypes.c_int32), ("n_seqs", ctypes.c_int32), ("n_tokens", ctypes.c_int32),
-                ("max_seq_len", ctypes.c_int32)]
+                ("max_seq_len", ctypes.c_int32), ("n_copies", ctypes.c_int32), ("pad", ctypes.c_int32)]
 
 
 class PagedScheduler:
@@ -75,6 +75,7 @@ class PagedScheduler:
         self.t_block_table = mk(max_num_seqs * max_blocks_per_seq, torch.int32)
         self.seq_ids = np.zeros(max_num_seqs, dtype=np.int64)
         self.cu = np.zeros(max_num_seqs + 1, dtype=np.int32)
+        self.copy_pairs = np.zeros(2 * max_num_seqs, dtype=np.int32)  # (src page, dst page) of prompt forks
         self.tokens, self.positions = self.t_tokens.numpy(), self.t_positions.numpy()
         self.slots, self.seq_lens = self.t_slots.numpy(), self.t_seq_lens.numpy()
         self.block_table = self.t_block_table.numpy()
@@ -94,7 +95,7 @@ class PagedScheduler:
     def plan(self) -> int:
         return self.lib.b200_sched_plan(self.h, ctypes.byref(self.hdr), self._p(self.seq_ids), self._p(self.cu),
                                         self._p(self.tokens), self._p(self.positions), self._p(self.slots),
-                                        self._p(self.seq_lens), self._p(self.block_table))
+                                        self._p(self.seq_lens), self._p(self.block_table), self._p(self.copy_pairs))
 
     def commit(self, sampled: np.ndarray, logprobs: np.ndarray) -> int:
         return self.lib.b200_sched_commit(self.h, self._p(np.ascontiguousarray(sampled, dtype=np.int32)),
@@ -119,10 +120,13 @@ class PagedScheduler:
         return int(rid), _REASONS.get(reason.value, "stop"), toks[:got].tolist(), lps[:got].tolist()
 
     def stats(self) -> dict[str, int]:
-        a = np.zeros(5, dtype=np.int64)
+        a = np.zeros(8, dtype=np.int64)
         self.lib.b200_sched_stats(self.h, self._p(a))
         return dict(waiting=int(a[0]), running=int(a[1]), free_blocks=int(a[2]), preemptions=int(a[3]),
-                    live=int(a[4]))
+                    live=int(a[4]), prompt_forks=int(a[5]), shared_pages=int(a[6]))
+
+    def set_prompt_sharing(self, on: bool):
+        self.lib.b200_sched_set_prompt_sharing(self.h, ctypes.c_int(int(on)))
 
     def close(self):
         if self.h:
@@ -371,6 +375,8 @@ class NativeRolloutEngine(InferenceEngine):
         tp0 = time.perf_counter()
         kind = s.plan()
         self._phase_s["plan"] += time.perf_counter() - tp0
+        if s.hdr.n_copies > 0:
+            self._copy_pages(s.copy_pairs[: 2 * s.hdr.n_copies])
         if kind == 0:
             self._deliver()
             return False
@@ -428,6 +434,14 @@ class NativeRolloutEngine(InferenceEngine):
         self._steps += 1
         self._deliver()
         return True
+
+    def _copy_pages(self, pairs: np.ndarray):
+        """Private copies of the page holding a shared prompt's last positions (prompt forks)."""
+        idx = torch.from_numpy(pairs.reshape(-1, 2).astype(np.int64)).to(self.device)
+        src, dst = idx[:, 0], idx[:, 1]
+        for kc, vc in self.kv_caches:
+            kc.index_copy_(0, dst, kc.index_select(0, src))
+            vc.index_copy_(0, dst, vc.index_select(0, src))
 
     def _deliver(self):
         while True:

@@ -145,3 +145,94 @@ def test_trajectory_format_checks():
         check_trajectory_format(dict(ok, logprobs=torch.zeros(2, 4)))
     with pytest.raises(ValueError):
         check_trajectory_format([1, 2])
+
+
+def test_scheduler_shares_prompt_pages_between_identical_prompts():
+    """n samples of one prompt: the first prefills, the others reference its full prompt pages, get
+    a private copy of the tail page and start decoding from the last prompt token."""
+    import numpy as np
+
+    from areal_b200.engine.rollout_engine import PagedScheduler
+
+    bs = 16
+    s = PagedScheduler(num_blocks=64, block_size=bs, max_num_seqs=16, max_batched_tokens=4096, max_blocks_per_seq=8)
+    prompt = list(range(100, 140))  # 40 tokens: 2 full pages + 8 tokens in the third
+    other = list(range(500, 520))
+    ids = [s.add(prompt, 4, 0, [], True) for _ in range(3)] + [s.add(other, 4, 0, [], True)]
+    free0 = s.stats()["free_blocks"]
+    assert s.plan() == 1  # prefill: the leader and the unrelated prompt; the two followers wait one step
+    assert s.hdr.n_seqs == 2 and s.hdr.n_tokens == 60 and s.hdr.n_copies == 0
+    s.commit(np.array([7, 8], dtype=np.int32), np.zeros(2, dtype=np.float32))
+    assert s.plan() == 2  # decode: the followers forked in, no second prefill
+    assert s.hdr.n_copies == 2 and s.hdr.n_seqs == 4
+    st = s.stats()
+    assert st["prompt_forks"] == 2 and st["shared_pages"] == 4
+    n = s.hdr.n_seqs
+    rows = s.block_table[: n * 8].reshape(n, 8)
+    order = s.seq_ids[:n].tolist()
+    lead, f1, f2 = (rows[order.index(i)] for i in ids[:3])
+    assert (lead[:2] == f1[:2]).all() and (lead[:2] == f2[:2]).all()       # full prompt pages are shared
+    assert len({int(lead[2]), int(f1[2]), int(f2[2])}) == 3                 # the tail page is private
+    pairs = s.copy_pairs[:4].reshape(2, 2)
+    assert set(pairs[:, 0].tolist()) == {int(lead[2])} and set(pairs[:, 1].tolist()) == {int(f1[2]), int(f2[2])}
+    # followers decode the LAST PROMPT TOKEN at position 39 with a context of 40; the leader is one token ahead
+    for i, want_tok, want_pos in ((ids[0], 7, 40), (ids[1], 139, 39), (ids[2], 139, 39)):
+        j = order.index(i)
+        assert int(s.tokens[j]) == want_tok and int(s.positions[j]) == want_pos and int(s.seq_lens[j]) == want_pos + 1
+        assert int(s.slots[j]) == int(rows[j][want_pos // bs]) * bs + want_pos % bs
+    # run everything to completion: every page comes back exactly once
+    for _ in range(6):
+        k = s.plan()
+        if k == 0:
+            break
+        s.commit(np.full(s.hdr.n_seqs, 9, dtype=np.int32), np.zeros(s.hdr.n_seqs, dtype=np.float32))
+    while s.pop_finished() is not None:
+        pass
+    assert s.stats()["free_blocks"] == free0 and s.stats()["live"] == 0
+    # sharing can be switched off
+    s.set_prompt_sharing(False)
+    for _ in range(2):
+        s.add(prompt, 1, 0, [], True)
+    assert s.plan() == 1 and s.hdr.n_seqs == 2
+    s.close()
+
+
+def test_engine_prompt_sharing_does_not_change_greedy_outputs():
+    """Greedy decoding of several copies of two prompts: with prompt sharing (followers skip their
+    prefill and read the leader's pages) every copy must produce exactly the tokens it produces with
+    sharing switched off, and the same logprobs."""
+    import asyncio
+
+    from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig, NativeRolloutConfig
+    from areal_b200.api.io_struct import ModelRequest
+    from areal_b200.engine.rollout_engine import NativeRolloutEngine
+
+    def run(share: bool):
+        cfg = InferenceEngineConfig(experiment_name="e", trial_name="t", backend="native:d1", max_concurrent_rollouts=64,
+                                    consumer_batch_size=8,
+                                    native=NativeRolloutConfig(model_preset="tiny-qwen2", context_length=128, max_num_seqs=16,
+                                                               max_num_batched_tokens=1024, num_kv_blocks=128, seed=0,
+                                                               cuda_graph=False))
+        eng = NativeRolloutEngine(cfg).initialize(device="cpu")
+        eng.sched.set_prompt_sharing(share)
+        g = torch.Generator().manual_seed(5)
+        prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (37, 16)]
+        gc = GenerationHyperparameters(max_new_tokens=12, greedy=True, temperature=0.0, ignore_eos=True)
+
+        async def go():
+            reqs = [ModelRequest(rid=f"{p}-{i}", input_ids=prompts[p], gconfig=gc) for p in range(2) for i in range(3)]
+            return await asyncio.gather(*[eng.agenerate(r) for r in reqs])
+
+        out = asyncio.run(go())
+        stats = eng.sched.stats()
+        eng.destroy()
+        return [(r.output_tokens, r.output_logprobs) for r in out], stats
+
+    shared, st_on = run(True)
+    plain, st_off = run(False)
+    assert st_on["prompt_forks"] == 4 and st_off["prompt_forks"] == 0
+    for (ta, la), (tb, lb) in zip(shared, plain):
+        assert ta == tb
+        assert max(abs(x - y) for x, y in zip(la, lb)) < 1e-4
+    # and all copies of one prompt agree with each other
+    assert shared[0][0] == shared[1][0] == shared[2][0] and shared[3][0] == shared[4][0] == shared[5][0]
