@@ -344,6 +344,8 @@ class B200TrainEngine(TrainEngine):
         S, r = pctx.sp_size, pctx.sp_rank
         n = Tp // S
         sl = slice(r * n, (r + 1) * n)
+        if S > 1:
+            pctx.extras["full_positions"] = pos.to(torch.int32)  # for RoPE after the fused sequence→head exchange
         hidden = self.model(ids[sl], pos[sl], meta, stage_input=stage_input)  # [n, H]: this Ulysses shard
         if pctx.pp_size > 1 and not pctx.is_last_stage:
             return hidden, None  # (x, res) for the next stage

@@ -76,12 +76,32 @@ class Attention(nn.Module):
         return fused.qknorm_rope(qkv, self.q_norm, self.k_norm, cos, sin, pos,
                                  self.n_q, self.n_kv, cfg.head_dim, cfg.rms_norm_eps)
 
+    def _fused_ulysses(self, x, cos, sin, pos, meta):
+        """Ulysses with the projection and the sequence→head exchange fused into one kernel: the
+        q/k norms and RoPE then run after the exchange, on this rank's heads of ALL tokens."""
+        p = self.pctx
+        if (p is None or p.sp_size == 1 or p.tp_size > 1 or self.qkv_bias is not None or p.sp_fused is None
+                or "full_positions" not in p.extras):
+            return None
+        from ..parallel.ulysses import fused_qkv_seq_to_head, head_to_seq
+
+        cfg = self.cfg
+        qkv = fused_qkv_seq_to_head(x, self.qkv, p, self.n_q, self.n_kv, cfg.head_dim)
+        if qkv is None:
+            return None
+        S = p.sp_size
+        q, k, v = fused.qknorm_rope(qkv, self.q_norm, self.k_norm, cos, sin, p.extras["full_positions"],
+                                    self.n_q // S, self.n_kv // S, cfg.head_dim, cfg.rms_norm_eps)
+        return head_to_seq(varlen_attention(q, k, v, meta), p)
+
     def forward(self, x, cos, sin, pos, meta: VarlenMeta, attn_fn=None):
         """``pos`` are the positions of the tokens that reach the q/k projection output: all
         tokens of this sequence-parallel shard (tensor parallelism gathers its token shards
         inside the projection)."""
-        q, k, v = self.project_qkv(x, cos, sin, pos)
-        a = (attn_fn or varlen_attention)(q, k, v, meta)
+        a = self._fused_ulysses(x, cos, sin, pos, meta)
+        if a is None:
+            q, k, v = self.project_qkv(x, cos, sin, pos)
+            a = (attn_fn or varlen_attention)(q, k, v, meta)
         a = a.reshape(a.shape[0], -1)
         tp = self._tp()
         if tp is not None:

@@ -79,6 +79,78 @@ def head_to_seq(x, pctx):
     return _HeadToSeq.apply(x, pctx.sp_group, pctx.sp_size, pctx.sp_rank)
 
 
+# --------------------------------------------------------------------------- fused projection
+
+
+def qkv_rank_major_rows(n_q: int, n_kv: int, head_dim: int, sp: int, device) -> torch.Tensor:
+    """Row order of the fused ``[q | k | v]`` projection weight that groups, for every sp rank r,
+    ``[q heads of r | k heads of r | v heads of r]``: with it the column block r of the projection
+    output is exactly what rank r needs after the exchange."""
+    qs, ks = n_q * head_dim, n_kv * head_dim
+    q = torch.arange(qs, device=device).view(sp, -1)
+    k = (qs + torch.arange(ks, device=device)).view(sp, -1)
+    v = (qs + ks + torch.arange(ks, device=device)).view(sp, -1)
+    return torch.cat([q, k, v], 1).reshape(-1)
+
+
+class _FusedQKVSeqToHead(torch.autograd.Function):
+    """``seq_to_head(x @ w.T)`` in one kernel: the projection's epilogue stores every rank's head block
+    straight into that rank's buffer over NVLink (``fused_linear.gemm_all_to_all``). Backward: the
+    reverse exchange (NCCL all-to-all), then the two GEMMs; the weight gradient is scattered back to
+    the parameter's own row order (into ``main_grad`` when present)."""
+
+    @staticmethod
+    def forward(ctx, x, w, perm, fctx, group, world, rank):
+        from . import fused_linear as FL
+
+        w_perm = w.index_select(0, perm)
+        y = FL.gemm_all_to_all(fctx, x, w_perm)  # [t * S, N / S]
+        ctx.save_for_backward(x, w, w_perm, perm)
+        ctx.args = (group, world, rank)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.gemm import gemm
+
+        x, w, w_perm, perm = ctx.saved_tensors
+        group, world, rank = ctx.args
+        T, n_loc = dy.shape
+        t = T // world
+        # [S, t, n_loc] blocks: block s holds the tokens of rank s → send back, receive my tokens' columns of every rank
+        send = dy.contiguous().view(world, t, n_loc)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send, group=group)
+        g = recv.permute(1, 0, 2).reshape(t, world * n_loc).contiguous()  # columns in rank-major (w_perm) order
+        dx = gemm(g, w_perm, b_mn=True, out_dtype=x.dtype) if ctx.needs_input_grad[0] else None
+        dw = None
+        if ctx.needs_input_grad[1]:
+            dwp = gemm(g, x, a_mn=True, b_mn=True, out_dtype=torch.float32)
+            main = getattr(w, "main_grad", None)
+            if main is not None:
+                main.index_add_(0, perm, dwp)
+            else:
+                dw = torch.zeros_like(w, dtype=torch.float32).index_add_(0, perm, dwp).to(w.dtype)
+        return dx, dw, None, None, None, None, None
+
+
+def fused_qkv_seq_to_head(x, w, pctx, n_q: int, n_kv: int, head_dim: int):
+    """Projection + exchange; returns ``[T_full, (n_q + 2 n_kv) / S * head_dim]`` laid out as
+    ``[q_r | k_r | v_r]`` for this rank, or None when the fused kernel does not apply."""
+    f = pctx.sp_fused
+    S = pctx.sp_size
+    if f is None or not f.cuda or not x.is_cuda or x.dtype != torch.bfloat16 or n_kv % S or n_q % S:
+        return None
+    N = w.shape[0]
+    if S * x.shape[0] * (N // S) * 2 > f.max_stage_bytes or (N // S) % 64:
+        return None
+    key = (n_q, n_kv, head_dim, S, x.device)
+    perm = pctx.extras.setdefault("qkv_perm", {}).get(key)
+    if perm is None:
+        perm = pctx.extras["qkv_perm"][key] = qkv_rank_major_rows(n_q, n_kv, head_dim, S, x.device)
+    return _FusedQKVSeqToHead.apply(x, w, perm, f, pctx.sp_group, S, pctx.sp_rank)
+
+
 def ulysses_attention(pctx, inner=None):
     """Returns an ``attn_fn(q, k, v, meta)`` for token-sharded inputs: ``meta`` describes the FULL
     packed sequence (all sp ranks' tokens concatenated in rank order)."""

@@ -22,12 +22,14 @@ def _run(cmd):
 
 
 @pytest.mark.parametrize("args,preset,n_mbs", [(["--tp", "2"], "tiny-qwen2", 1), (["--sp", "2"], "tiny-qwen2", 1),
+                                               (["--sp", "2", "--no-bias"], "tiny-qwen2", 1),
                                                (["--pp", "2"], "tiny-qwen2", 2), (["--ep", "2"], "tiny-qwen3-moe", 1)])
 def test_two_gpu_step_matches_one_gpu(tmp_path, args, preset, n_mbs):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     ref = str(tmp_path / "ref.pt")
-    common = ["--device", "cuda", "--preset", preset, "--n-mbs", str(n_mbs)]
+    common = ["--device", "cuda", "--preset", preset, "--n-mbs", str(n_mbs)] + (["--no-bias"] if "--no-bias" in args else [])
+    args = [a for a in args if a != "--no-bias"]
     env_free = [sys.executable, WORKER, "--ref"] + common + [ref]
     clean = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
     r = subprocess.run(env_free, env=clean, capture_output=True, text=True, timeout=600)

@@ -47,6 +47,7 @@ def main():
     ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--preset", default="tiny-qwen2")
     ap.add_argument("--device", default="cpu", choices=["cpu", "cuda"])
+    ap.add_argument("--no-bias", action="store_true", help="Qwen3-style attention (no qkv bias): enables the fused Ulysses projection")
     ap.add_argument("--n-mbs", type=int, default=1)
     ap.add_argument("--critic", action="store_true")
     args = ap.parse_args()
@@ -56,6 +57,8 @@ def main():
     if cuda:
         # the CUDA kernels want head_dim 128 and 16-byte aligned rows
         over = dict(head_dim=128, intermediate_size=768)
+        if args.no_bias:
+            over["attention_bias"] = False
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         if "LOCAL_RANK" in os.environ:
             torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
@@ -140,6 +143,9 @@ def main():
         from areal_b200.ops import _lib
 
         assert _lib.read_status() == 0
+        if args.sp > 1 and args.no_bias:
+            # the projection + sequence→head exchange must have gone through the fused kernel
+            assert eng.pctx.extras.get("qkv_perm"), "fused Ulysses projection did not run"
     # and the update itself went through on every rank
     assert stats["update_successful"] == 1.0
     dist.barrier()
