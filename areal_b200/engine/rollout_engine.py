@@ -535,7 +535,7 @@ class NativeRolloutEngine(InferenceEngine):
         """Copies the trainer's flat bf16 weights into this engine's flat buffer. Both sides
         use the same model class, hence the same layout, so this is one device copy (a peer
         copy over NVLink when the two engines sit on different GPUs)."""
-        src = trainer.flat.flat
+        src = getattr(trainer, "weight_flat", trainer.flat).flat
         dst = self.flat.flat
         assert src.numel() >= dst.numel() or dst.numel() >= src.numel()
         n = min(src.numel(), dst.numel())

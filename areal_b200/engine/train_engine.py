@@ -61,6 +61,11 @@ def resolve_model_config(cfg: TrainEngineConfig) -> ModelConfig:
         if meg is not None and meg.mode and meg.recipe not in ("blockwise", "mxfp8"):
             raise ValueError(f"fp8 recipe {meg.recipe!r} is not supported: this engine implements block-wise scaling")
         mc.fp8 = True
+    if getattr(cfg, "use_lora", False):
+        if cfg.peft_type != "lora":
+            raise ValueError(f"peft_type {cfg.peft_type!r} is not supported (only 'lora')")
+        mc.lora_rank, mc.lora_alpha = int(cfg.lora_rank), float(cfg.lora_alpha)
+        mc.lora_targets = list(cfg.target_modules or [])
     return mc
 
 
@@ -223,8 +228,26 @@ class B200TrainEngine(TrainEngine):
         ep = pctx.ep_size if pctx is not None else 1
         is_expert = (lambda n: n.endswith(("mlp.gate_up", "mlp.down")) and ".mlp." in n and
                      dict(self.model.named_parameters())[n].dim() == 3)
-        self.flat = FlatParams(self.model, self._dp_group, with_grads=self.optimizer_config is not None,
-                               replicated_first=rep_first, select=(lambda n: not is_expert(n)) if ep > 1 else None)
+        self.flat_base = None
+        if self.model_config.lora_rank:
+            # adapters train, the base model is frozen: the base weights keep a flat buffer of their own
+            # (no gradients, no optimizer state; it is what the rollout engine and checkpoints read) and
+            # `self.flat` — the buffer the optimizer shards — holds the adapters only
+            from ..models.lora import is_lora_param
+
+            assert tp == 1 and ep == 1 and (pctx is None or pctx.pp_size == 1), \
+                "LoRA training runs under data / sequence parallelism only"
+            for n, p_ in self.model.named_parameters():
+                if not is_lora_param(n):
+                    p_.requires_grad_(False)
+            self.flat_base = FlatParams(self.model, self._dp_group, with_grads=False,
+                                        select=lambda n: not is_lora_param(n))
+            self.flat = FlatParams(self.model, self._dp_group, with_grads=self.optimizer_config is not None,
+                                   select=is_lora_param)
+        else:
+            self.flat = FlatParams(self.model, self._dp_group, with_grads=self.optimizer_config is not None,
+                                   replicated_first=rep_first,
+                                   select=(lambda n: not is_expert(n)) if ep > 1 else None)
         self.flat_experts = None
         if ep > 1:
             # expert weights differ across the ep group: they are reduced only over the ranks that hold
@@ -572,13 +595,29 @@ class B200TrainEngine(TrainEngine):
                 self.rollout_engine.update_weights_from_disk(meta).result()
         else:
             self.rollout_engine.pause_generation()
-            self.rollout_engine.receive_weights(self, version=meta.version)
+            with self._merged_weights():
+                self.rollout_engine.receive_weights(self, version=meta.version)
             self.rollout_engine.continue_generation()
         if meta.version is not None:
             self.rollout_engine.set_version(meta.version)
         dt = time.perf_counter() - t0
         stats_tracker.scalar(**{"timeperf/update_weights": dt})
         return dt
+
+    @property
+    def weight_flat(self) -> FlatParams:
+        """The flat buffer with the model's (base) weights: what rollout engines and checkpoints read."""
+        return self.flat_base if self.flat_base is not None else self.flat
+
+    def _merged_weights(self):
+        """Context in which the base weights include the adapters' product (no-op without LoRA)."""
+        if self.flat_base is None:
+            import contextlib
+
+            return contextlib.nullcontext()
+        from ..models.lora import merged
+
+        return merged(self.model)
 
     def get_param_specs(self, weight_chunked_mem_mb: int = 1024) -> list[list[ParamSpec]]:
         limit = weight_chunked_mem_mb * (1 << 20)
@@ -601,9 +640,16 @@ class B200TrainEngine(TrainEngine):
         os.makedirs(meta.path, exist_ok=True)
         if meta.weight_format == "hf":
             if self.dp_rank == 0:
-                save_hf_checkpoint(self.model, self.model_config, meta.path, tokenizer=meta.tokenizer)
+                # with LoRA: the merged model (loadable by any HF consumer, and by the rollout engine's
+                # disk update) plus the adapter alone in the PEFT layout
+                with self._merged_weights():
+                    save_hf_checkpoint(self.model, self.model_config, meta.path, tokenizer=meta.tokenizer)
+                if self.flat_base is not None:
+                    from ..models.lora import save_adapter
+
+                    save_adapter(self.model, self.model_config, meta.path, base_model_path=self.config.path or "")
         elif meta.weight_format == "dcp":
-            # sharded: every rank writes its slice of the flat weights
+            # sharded: every rank writes its slice of the flat (trainable) weights
             o, n = self.flat.shard_offset, self.flat.shard_numel
             torch.save(dict(flat=self.flat.flat[o:o + n].cpu(), offset=o, numel=self.flat.numel,
                             dp_world=self.world_size, layout=self.flat.named_offsets()),
@@ -620,7 +666,13 @@ class B200TrainEngine(TrainEngine):
         from ..utils.hf_io import load_hf_weights
 
         if meta.weight_format == "hf":
-            load_hf_weights(self.model, meta.path)
+            if self.flat_base is not None and os.path.exists(os.path.join(meta.path, "adapter_model.safetensors")):
+                # a LoRA checkpoint: the base model stays as loaded at initialisation, the adapter resumes
+                from ..models.lora import load_adapter
+
+                load_adapter(self.model, meta.path)
+            else:
+                load_hf_weights(self.model, meta.path)
         elif meta.weight_format == "dcp":
             for r in range(self.world_size):
                 f = os.path.join(meta.path, f"model_world_size_{self.world_size}_rank_{r}.pt")

@@ -195,7 +195,7 @@ class RemoteRolloutClient(InferenceEngine):
     def receive_weights(self, trainer, version: int | None = None):
         """Each trainer rank writes its shard of the flat bf16 weights into every rollout
         rank's weight buffer (peer stores over NVLink), then synchronises its stream."""
-        f = trainer.flat
+        f = getattr(trainer, "weight_flat", trainer.flat)
         itemsize = f.flat.element_size()
         shard = f.flat[f.shard_offset: f.shard_offset + f.shard_numel]
         if not self.weight_ptrs:

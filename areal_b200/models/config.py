@@ -32,6 +32,10 @@ class ModelConfig:
     # block-scaled fp8 forward GEMMs of the dense projections (bf16 master weights)
     fp8: bool = False
     fp8_ue8m0: bool = True
+    # low-rank adapters on the dense projections (0 = off); targets are HF module names
+    lora_rank: int = 0
+    lora_alpha: float = 16.0
+    lora_targets: list[str] = field(default_factory=list)
     # MoE (qwen3_moe)
     num_experts: int = 0
     num_experts_per_tok: int = 0

@@ -1,0 +1,192 @@
+"""Low-rank adapters (LoRA) on the fused projections.
+
+The model keeps q/k/v and gate/up as one fused weight each, while adapter
+checkpoints name one ``lora_A`` / ``lora_B`` pair per original projection
+(``q_proj``, ``k_proj`` …). One ``LoRAAdapter`` therefore serves one fused
+weight: the down-projections ``A_i`` of its targeted sub-blocks are stacked
+into one matrix (one GEMM over the input), the up-projections ``B_i`` stay
+per sub-block, and the result is laid out like the fused output.
+
+The rank is padded to a multiple of 64 internally so that both products run on
+the tcgen05 GEMM with whole K blocks; the padding rows of ``A`` and columns of
+``B`` are zero and stay zero under AdamW (their gradients are products with the
+other factor's zero padding). Exports slice the padding off.
+
+Base weights are frozen while adapters train. The rollout engine receives
+merged weights ``W + (alpha / r) * B @ A`` (``merged`` below), so generation
+runs the unmodified dense kernels.
+
+Reference behaviour: ``use_lora`` / ``lora_rank`` / ``lora_alpha`` /
+``target_modules`` of the train-engine config (areal/api/cli_args.py), applied
+with PEFT in areal/engine/fsdp_engine.py.
+"""
+
+from __future__ import annotations
+
+import json
+import math
+import os
+from contextlib import contextmanager
+from typing import Iterator, Sequence
+
+import torch
+import torch.nn as nn
+
+from ..ops.gemm import linear
+
+ALL_LINEAR = ("q_proj", "k_proj", "v_proj", "o_proj", "gate_proj", "up_proj", "down_proj")
+
+
+def normalize_targets(targets: Sequence[str] | None) -> tuple[str, ...]:
+    """``[]`` and ``["all-linear"]`` select every dense projection."""
+    if not targets or "all-linear" in targets:
+        return ALL_LINEAR
+    bad = [t for t in targets if t not in ALL_LINEAR]
+    if bad:
+        raise ValueError(f"unknown LoRA target modules {bad}; choose from {ALL_LINEAR}")
+    return tuple(targets)
+
+
+def padded_rank(rank: int) -> int:
+    return (rank + 63) // 64 * 64
+
+
+class LoRAAdapter(nn.Module):
+    """Adapter of one fused weight ``[sum(outs), in_features]``.
+
+    ``blocks``: ``(hf_module_name, out_features)`` per sub-block in the fused row order;
+    ``targeted``: the module names that get an adapter (the others contribute zeros)."""
+
+    def __init__(self, in_features: int, blocks: Sequence[tuple[str, int]], targeted: Sequence[str],
+                 rank: int, alpha: float, dtype, device, seed: int = 0):
+        super().__init__()
+        self.in_features = in_features
+        self.blocks = list(blocks)
+        self.names = [n for n, _ in self.blocks if n in targeted]
+        assert self.names, "adapter without a targeted sub-block"
+        self.rank, self.rp = rank, padded_rank(rank)
+        self.scale = float(alpha) / float(rank)
+        k = len(self.names)
+        self.lora_A = nn.Parameter(torch.zeros(k * self.rp, in_features, dtype=dtype, device=device))
+        self.lora_B = nn.ParameterDict({
+            n: nn.Parameter(torch.zeros(o, self.rp, dtype=dtype, device=device))
+            for n, o in self.blocks if n in self.names})
+        # A: uniform(-1/sqrt(in), 1/sqrt(in)) (kaiming with a=sqrt(5), the PEFT default); B: zeros, so
+        # the adapted model starts equal to the base model
+        g = torch.Generator(device="cpu").manual_seed(seed)
+        bound = 1.0 / math.sqrt(in_features)
+        with torch.no_grad():
+            for i in range(k):
+                a = (torch.rand(rank, in_features, generator=g) * 2 - 1) * bound
+                self.lora_A[i * self.rp: i * self.rp + rank].copy_(a.to(dtype))
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        """Delta of the fused projection's output, ``[T, sum(outs)]``."""
+        u = linear(x, self.lora_A)
+        parts, i = [], 0
+        for n, o in self.blocks:
+            if n in self.lora_B:
+                parts.append(linear(u[:, i * self.rp:(i + 1) * self.rp], self.lora_B[n]))
+                i += 1
+            else:
+                parts.append(x.new_zeros(x.shape[0], o))
+        d = parts[0] if len(parts) == 1 else torch.cat(parts, dim=-1)
+        return d * self.scale
+
+    @torch.no_grad()
+    def merged_delta(self) -> torch.Tensor:
+        """``scale * B @ A`` laid out like the fused weight (fp32)."""
+        rows, i = [], 0
+        for n, o in self.blocks:
+            if n in self.lora_B:
+                a = self.lora_A[i * self.rp:(i + 1) * self.rp].float()
+                rows.append(self.lora_B[n].float() @ a * self.scale)
+                i += 1
+            else:
+                rows.append(torch.zeros(o, self.in_features, dtype=torch.float32, device=self.lora_A.device))
+        return rows[0] if len(rows) == 1 else torch.cat(rows, 0)
+
+    def peft_tensors(self, prefix: str) -> Iterator[tuple[str, torch.Tensor]]:
+        """``(name, tensor)`` in the adapter-checkpoint naming, padding removed."""
+        for i, n in enumerate(self.names):
+            yield f"{prefix}{n}.lora_A.weight", self.lora_A[i * self.rp: i * self.rp + self.rank]
+            yield f"{prefix}{n}.lora_B.weight", self.lora_B[n][:, :self.rank]
+
+    @torch.no_grad()
+    def load_peft(self, tensors: dict[str, torch.Tensor], prefix: str):
+        for i, n in enumerate(self.names):
+            a, b = tensors[f"{prefix}{n}.lora_A.weight"], tensors[f"{prefix}{n}.lora_B.weight"]
+            assert a.shape == (self.rank, self.in_features) and b.shape[1] == self.rank
+            self.lora_A[i * self.rp: i * self.rp + self.rank].copy_(a)
+            self.lora_B[n][:, :self.rank].copy_(b)
+
+
+def make_adapter(cfg, in_features, blocks, dtype, device, seed) -> LoRAAdapter | None:
+    """Adapter for a fused weight, or ``None`` when LoRA is off or no sub-block is targeted."""
+    if not getattr(cfg, "lora_rank", 0):
+        return None
+    targets = normalize_targets(cfg.lora_targets)
+    if not any(n in targets for n, _ in blocks):
+        return None
+    return LoRAAdapter(in_features, blocks, targets, cfg.lora_rank, cfg.lora_alpha, dtype, device, seed)
+
+
+def is_lora_param(name: str) -> bool:
+    return ".lora_A" in name or ".lora_B." in name
+
+
+def iter_adapters(model) -> Iterator[tuple[str, torch.Tensor, LoRAAdapter]]:
+    """``(hf_prefix, fused_weight, adapter)`` for every adapter of a ``QwenModel``."""
+    for i, layer in enumerate(model.layers, start=model.layer_start):
+        p = f"base_model.model.model.layers.{i}."
+        a, m = layer.attn, layer.mlp
+        if getattr(a, "lora_qkv", None) is not None:
+            yield p + "self_attn.", a.qkv, a.lora_qkv
+        if getattr(a, "lora_o", None) is not None:
+            yield p + "self_attn.", a.o, a.lora_o
+        if getattr(m, "lora_gate_up", None) is not None:
+            yield p + "mlp.", m.gate_up, m.lora_gate_up
+        if getattr(m, "lora_down", None) is not None:
+            yield p + "mlp.", m.down, m.lora_down
+
+
+@contextmanager
+def merged(model):
+    """Inside the block the base weights hold ``W + scale * B @ A``; the exact original bits are
+    restored on exit (from a copy: subtracting the delta again would round in bf16)."""
+    saved = []
+    with torch.no_grad():
+        for _, w, ad in iter_adapters(model):
+            saved.append((w, w.detach().clone()))
+            w.add_(ad.merged_delta().to(w.dtype))
+    try:
+        yield model
+    finally:
+        with torch.no_grad():
+            for w, old in saved:
+                w.copy_(old)
+
+
+def save_adapter(model, cfg, path: str, base_model_path: str = ""):
+    """Writes ``adapter_model.safetensors`` + ``adapter_config.json`` (the layout PEFT reads)."""
+    from safetensors.torch import save_file
+
+    os.makedirs(path, exist_ok=True)
+    tensors = {}
+    for prefix, _, ad in iter_adapters(model):
+        for n, t in ad.peft_tensors(prefix):
+            tensors[n] = t.detach().to("cpu").contiguous().clone()
+    save_file(tensors, os.path.join(path, "adapter_model.safetensors"), metadata={"format": "pt"})
+    conf = {"peft_type": "LORA", "task_type": "CAUSAL_LM", "r": cfg.lora_rank, "lora_alpha": cfg.lora_alpha,
+            "target_modules": list(normalize_targets(cfg.lora_targets)), "lora_dropout": 0.0, "bias": "none",
+            "base_model_name_or_path": base_model_path, "inference_mode": True, "fan_in_fan_out": False}
+    with open(os.path.join(path, "adapter_config.json"), "w") as f:
+        json.dump(conf, f, indent=2)
+
+
+def load_adapter(model, path: str):
+    from safetensors.torch import load_file
+
+    tensors = load_file(os.path.join(path, "adapter_model.safetensors"))
+    for prefix, _, ad in iter_adapters(model):
+        ad.load_peft(tensors, prefix)

@@ -40,7 +40,7 @@ def _dense(x, w, bias, cfg: ModelConfig):
 
 
 class Attention(nn.Module):
-    def __init__(self, cfg: ModelConfig, dtype, device, pctx=None):
+    def __init__(self, cfg: ModelConfig, dtype, device, pctx=None, layer_idx: int = 0):
         super().__init__()
         self.cfg = cfg
         self.pctx = pctx
@@ -59,6 +59,11 @@ class Attention(nn.Module):
             self.k_norm = nn.Parameter(torch.ones(cfg.head_dim, dtype=dtype, device=device))
         else:
             self.q_norm = self.k_norm = None
+        from .lora import make_adapter
+
+        self.lora_qkv = make_adapter(cfg, h, [("q_proj", qs), ("k_proj", ks), ("v_proj", ks)], dtype, device,
+                                     seed=2 * layer_idx + 1000)
+        self.lora_o = make_adapter(cfg, qs, [("o_proj", h)], dtype, device, seed=2 * layer_idx + 1001)
 
     def _tp(self):
         p = self.pctx
@@ -73,6 +78,8 @@ class Attention(nn.Module):
             qkv = column_parallel_linear(x, self.qkv, tp, self.qkv_bias)
         else:
             qkv = _dense(x, self.qkv, self.qkv_bias, cfg)
+        if self.lora_qkv is not None:
+            qkv = qkv + self.lora_qkv(x)
         return fused.qknorm_rope(qkv, self.q_norm, self.k_norm, cos, sin, pos,
                                  self.n_q, self.n_kv, cfg.head_dim, cfg.rms_norm_eps)
 
@@ -81,7 +88,7 @@ class Attention(nn.Module):
         q/k norms and RoPE then run after the exchange, on this rank's heads of ALL tokens."""
         p = self.pctx
         if (p is None or p.sp_size == 1 or p.tp_size > 1 or self.qkv_bias is not None or p.sp_fused is None
-                or "full_positions" not in p.extras):
+                or "full_positions" not in p.extras or self.lora_qkv is not None):
             return None
         from ..parallel.ulysses import fused_qkv_seq_to_head, head_to_seq
 
@@ -108,11 +115,12 @@ class Attention(nn.Module):
             from ..parallel.tensor_parallel import row_parallel_linear
 
             return row_parallel_linear(a, self.o, tp)
-        return _dense(a, self.o, None, self.cfg)
+        y = _dense(a, self.o, None, self.cfg)
+        return y if self.lora_o is None else y + self.lora_o(a)
 
 
 class DenseMLP(nn.Module):
-    def __init__(self, hidden, inter, dtype, device, pctx=None, cfg: ModelConfig | None = None):
+    def __init__(self, hidden, inter, dtype, device, pctx=None, cfg: ModelConfig | None = None, layer_idx: int = 0):
         super().__init__()
         self.pctx = pctx
         self.cfg = cfg
@@ -120,6 +128,12 @@ class DenseMLP(nn.Module):
         assert inter % tp == 0
         self.gate_up = nn.Parameter(torch.empty(2 * inter // tp, hidden, dtype=dtype, device=device))
         self.down = nn.Parameter(torch.empty(hidden, inter // tp, dtype=dtype, device=device))
+        from .lora import make_adapter
+
+        self.lora_gate_up = make_adapter(cfg, hidden, [("gate_proj", inter // tp), ("up_proj", inter // tp)],
+                                         dtype, device, seed=2 * layer_idx + 2000)
+        self.lora_down = make_adapter(cfg, inter // tp, [("down_proj", hidden)], dtype, device,
+                                      seed=2 * layer_idx + 2001)
 
     def forward(self, x):
         p = self.pctx
@@ -128,9 +142,13 @@ class DenseMLP(nn.Module):
 
             return row_parallel_linear(fused.swiglu(column_parallel_linear(x, self.gate_up, p.tp_fused)),
                                        self.down, p.tp_fused)
-        if self.cfg is not None and self.cfg.fp8:
-            return _dense(fused.swiglu(_dense(x, self.gate_up, None, self.cfg)), self.down, None, self.cfg)
-        return linear(fused.swiglu(linear(x, self.gate_up)), self.down)
+        dense = (lambda t, w: _dense(t, w, None, self.cfg)) if (self.cfg is not None and self.cfg.fp8) else linear
+        gu = dense(x, self.gate_up)
+        if self.lora_gate_up is not None:
+            gu = gu + self.lora_gate_up(x)
+        a = fused.swiglu(gu)
+        y = dense(a, self.down)
+        return y if self.lora_down is None else y + self.lora_down(a)
 
 
 class MoEMLP(nn.Module):
@@ -182,13 +200,13 @@ class Block(nn.Module):
         super().__init__()
         h = cfg.hidden_size
         self.input_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
-        self.attn = Attention(cfg, dtype, device, pctx)
+        self.attn = Attention(cfg, dtype, device, pctx, layer_idx)
         self.post_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
         if cfg.layer_is_moe(layer_idx):
             assert pctx is None or pctx.tp_size == 1, "MoE layers shard over the expert-parallel group, not tp"
             self.mlp = MoEMLP(cfg, dtype, device, pctx)
         else:
-            self.mlp = DenseMLP(h, cfg.intermediate_size, dtype, device, pctx, cfg)
+            self.mlp = DenseMLP(h, cfg.intermediate_size, dtype, device, pctx, cfg, layer_idx)
         self.eps = cfg.rms_norm_eps
 
     def forward(self, x, res, cos, sin, pos, meta, attn_fn=None):
@@ -243,6 +261,8 @@ class QwenModel(nn.Module):
         if self.layer_end - self.layer_start != self.cfg.num_hidden_layers:
             return self._init_weights_pipeline(seed, std)
         for name, p in self.named_parameters():
+            if ".lora_" in name:
+                continue  # adapters initialise themselves and do not consume the base model's stream
             if name.endswith("norm") or "_norm" in name:
                 p.fill_(1.0)
                 continue
