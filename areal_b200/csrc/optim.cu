@@ -135,6 +135,64 @@ __global__ void adamw_bcast_kernel(float* __restrict__ master, float* __restrict
   }
 }
 
+// AdamW with bf16 moments and no fp32 master copy: the weight shard is read from this rank's own
+// bf16 parameter buffer and the rounding error of every update is carried in a bf16 Kahan
+// compensation buffer (6 bytes of state per parameter instead of 12).
+//   c += update;  w' = bf16(w + c);  c += w - w'
+__global__ void adamw_bf16_bcast_kernel(const __nv_bfloat16* w_local,
+                                        __nv_bfloat16* __restrict__ comp, __nv_bfloat16* __restrict__ m,
+                                        __nv_bfloat16* __restrict__ v, const float* __restrict__ grad,
+                                        PeerPtrs params, int n_peers, long long offset, long long n,
+                                        const float* __restrict__ norm_sq, AdamParams hp,
+                                        int* __restrict__ skipped) {
+  const float nsq = norm_sq ? *norm_sq : 0.f;
+  if (!isfinite(nsq)) {
+    if (blockIdx.x == 0 && threadIdx.x == 0 && skipped) *skipped = 1;
+    return;
+  }
+  float coef = 1.f;
+  if (hp.max_norm > 0.f) coef = fminf(1.f, hp.max_norm / (sqrtf(nsq) + 1e-6f));
+  const float step = hp.lr / hp.bias_corr1;
+  const float inv_bc2_sqrt = rsqrtf(hp.bias_corr2);
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float gk = grad[i] * coef;
+    const float w = __bfloat162float(w_local[i]);
+    const float mk = hp.beta1 * __bfloat162float(m[i]) + (1.f - hp.beta1) * gk;
+    const float vk = hp.beta2 * __bfloat162float(v[i]) + (1.f - hp.beta2) * gk * gk;
+    const float denom = sqrtf(vk) * inv_bc2_sqrt + hp.eps;
+    const float c = __bfloat162float(comp[i]) - hp.lr * hp.weight_decay * w - step * mk / denom;
+    const __nv_bfloat16 wn = __float2bfloat16(w + c);
+    m[i] = __float2bfloat16(mk);
+    v[i] = __float2bfloat16(vk);
+    comp[i] = __float2bfloat16(c + (w - __bfloat162float(wn)));
+    for (int p = 0; p < n_peers; ++p)
+      reinterpret_cast<__nv_bfloat16*>(params.p[p])[offset + i] = wn;
+  }
+}
+
+// Plain SGD with (coupled) weight decay on the fp32 master shard.
+__global__ void sgd_bcast_kernel(float* __restrict__ master, const float* __restrict__ grad,
+                                 PeerPtrs params, int n_peers, long long offset, long long n,
+                                 const float* __restrict__ norm_sq, AdamParams hp,
+                                 int* __restrict__ skipped) {
+  const float nsq = norm_sq ? *norm_sq : 0.f;
+  if (!isfinite(nsq)) {
+    if (blockIdx.x == 0 && threadIdx.x == 0 && skipped) *skipped = 1;
+    return;
+  }
+  float coef = 1.f;
+  if (hp.max_norm > 0.f) coef = fminf(1.f, hp.max_norm / (sqrtf(nsq) + 1e-6f));
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    const float w = master[i];
+    const float wn = w - hp.lr * (grad[i] * coef + hp.weight_decay * w);
+    master[i] = wn;
+    for (int p = 0; p < n_peers; ++p)
+      reinterpret_cast<__nv_bfloat16*>(params.p[p])[offset + i] = __float2bfloat16(wn);
+  }
+}
+
 __global__ void sumsq_kernel(const float* __restrict__ x, long long n, float* __restrict__ out) {
   float ss = 0.f;
   for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
@@ -193,6 +251,40 @@ int b200_adamw_bcast(float* master, float* m, float* v, const float* grad, void*
   AdamParams hp{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, max_norm};
   adamw_bcast_kernel<<<grid_for(n, 4), 256, 0, stream>>>(master, m, v, grad, pp, n_peers, offset, n,
                                                          norm_sq, hp, skipped);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// mode 1: bf16 moments + Kahan compensation (w_local: this rank's bf16 weight shard; comp/m/v bf16).
+int b200_adamw_bf16_bcast(const void* w_local, void* comp, void* m, void* v, const float* grad,
+                          void* const* peer_params, int n_peers, long long offset, long long n,
+                          const float* norm_sq, float lr, float beta1, float beta2, float eps,
+                          float weight_decay, float bias_corr1, float bias_corr2, float max_norm,
+                          int* skipped, cudaStream_t stream) {
+  using namespace b200;
+  if (n_peers < 1 || n_peers > kMaxPeers) return -100;
+  if (n == 0) return 0;
+  PeerPtrs pp;
+  for (int i = 0; i < n_peers; ++i) pp.p[i] = peer_params[i];
+  AdamParams hp{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, max_norm};
+  adamw_bf16_bcast_kernel<<<grid_for(n, 2), 256, 0, stream>>>(
+      (const __nv_bfloat16*)w_local, (__nv_bfloat16*)comp, (__nv_bfloat16*)m, (__nv_bfloat16*)v, grad, pp,
+      n_peers, offset, n, norm_sq, hp, skipped);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+int b200_sgd_bcast(float* master, const float* grad, void* const* peer_params, int n_peers,
+                   long long offset, long long n, const float* norm_sq, float lr, float weight_decay,
+                   float max_norm, int* skipped, cudaStream_t stream) {
+  using namespace b200;
+  if (n_peers < 1 || n_peers > kMaxPeers) return -100;
+  if (n == 0) return 0;
+  PeerPtrs pp;
+  for (int i = 0; i < n_peers; ++i) pp.p[i] = peer_params[i];
+  AdamParams hp{lr, 0.f, 0.f, 0.f, weight_decay, 1.f, 1.f, max_norm};
+  sgd_bcast_kernel<<<grid_for(n, 2), 256, 0, stream>>>(master, grad, pp, n_peers, offset, n, norm_sq, hp,
+                                                       skipped);
   B200_CHECK(cudaGetLastError());
   return 0;
 }

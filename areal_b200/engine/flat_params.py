@@ -127,7 +127,13 @@ def lr_at(step: int, total_steps: int, cfg: OptimizerConfig) -> float:
 
 
 class ShardedAdamW:
-    """AdamW over the rank's shard of the flat buffers (fp32 master, m, v)."""
+    """Optimizer over the rank's shard of the flat buffers. ``cfg.type`` selects the rule:
+
+    * ``adam`` / ``adamw``: AdamW with an fp32 master copy and fp32 moments;
+    * ``adam_bf16``: AdamW with bf16 moments and, instead of a master copy, a bf16 Kahan compensation
+      buffer that carries the rounding error of every weight update (``self.master`` is that buffer);
+      the counterpart of the reference's AnyPrecisionAdamW (areal/engine/fsdp_utils/optimizer.py);
+    * ``sgd``: plain SGD with coupled weight decay on an fp32 master copy."""
 
     def __init__(self, flat: FlatParams, cfg: OptimizerConfig, total_steps: int = 1, tp_group=None,
                  tp_full_grad: tuple[str, ...] = ("score",)):
@@ -148,9 +154,17 @@ class ShardedAdamW:
         self.sched_step = 0  # scheduler position
         n, o = flat.shard_numel, flat.shard_offset
         dev = flat.device
-        self.master = flat.flat[o:o + n].to(torch.float32).clone()
-        self.exp_avg = torch.zeros(n, dtype=torch.float32, device=dev)
-        self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, device=dev)
+        self.kind = {"adam": "adamw", "adamw": "adamw"}.get(cfg.type, cfg.type)
+        if self.kind == "adam_bf16":
+            assert flat.dtype == torch.bfloat16, "adam_bf16 keeps its state in the weights' bf16"
+            self.master = torch.zeros(n, dtype=torch.bfloat16, device=dev)  # Kahan compensation
+            self.exp_avg = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+            self.exp_avg_sq = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        else:
+            self.master = flat.flat[o:o + n].to(torch.float32).clone()
+            m = 0 if self.kind == "sgd" else n
+            self.exp_avg = torch.zeros(m, dtype=torch.float32, device=dev)
+            self.exp_avg_sq = torch.zeros(m, dtype=torch.float32, device=dev)
         self.shard_grad = torch.zeros(n, dtype=torch.float32, device=dev)
         if flat.cuda:
             self._norm = torch.zeros(1, dtype=torch.float32, device=dev)
@@ -166,7 +180,10 @@ class ShardedAdamW:
     def refresh_master(self):
         """Re-reads the master shard from the (re)loaded bf16 weights."""
         n, o = self.flat.shard_numel, self.flat.shard_offset
-        self.master.copy_(self.flat.flat[o:o + n].to(torch.float32))
+        if self.kind == "adam_bf16":
+            self.master.zero_()
+        else:
+            self.master.copy_(self.flat.flat[o:o + n].to(torch.float32))
 
     def step(self, grad_scale: float = 1.0) -> dict[str, float]:
         self.flat.collect_autograd_grads()
@@ -234,15 +251,24 @@ class ShardedAdamW:
         t = self.step_count + 1
         lr = self.lr
         self._skipped.zero_()
-        rc = lib.b200_adamw_bcast(_lib.ptr(self.master), _lib.ptr(self.exp_avg), _lib.ptr(self.exp_avg_sq),
-                                  _lib.ptr(self.shard_grad), self._param_table, ctypes.c_int(world),
-                                  ctypes.c_longlong(f.shard_offset), ctypes.c_longlong(f.shard_numel),
-                                  _lib.ptr(self._norm), ctypes.c_float(lr), ctypes.c_float(cfg.beta1),
-                                  ctypes.c_float(cfg.beta2), ctypes.c_float(cfg.eps),
-                                  ctypes.c_float(cfg.weight_decay), ctypes.c_float(1 - cfg.beta1 ** t),
-                                  ctypes.c_float(1 - cfg.beta2 ** t), ctypes.c_float(cfg.gradient_clipping),
-                                  _lib.ptr(self._skipped), _lib.stream_ptr())
-        _lib.check(rc, "b200_adamw_bcast")
+        tail = (self._param_table, ctypes.c_int(world), ctypes.c_longlong(f.shard_offset),
+                ctypes.c_longlong(f.shard_numel), _lib.ptr(self._norm), ctypes.c_float(lr))
+        adam_hp = (ctypes.c_float(cfg.beta1), ctypes.c_float(cfg.beta2), ctypes.c_float(cfg.eps),
+                   ctypes.c_float(cfg.weight_decay), ctypes.c_float(1 - cfg.beta1 ** t),
+                   ctypes.c_float(1 - cfg.beta2 ** t), ctypes.c_float(cfg.gradient_clipping),
+                   _lib.ptr(self._skipped), _lib.stream_ptr())
+        if self.kind == "sgd":
+            rc = lib.b200_sgd_bcast(_lib.ptr(self.master), _lib.ptr(self.shard_grad), *tail,
+                                    ctypes.c_float(cfg.weight_decay), ctypes.c_float(cfg.gradient_clipping),
+                                    _lib.ptr(self._skipped), _lib.stream_ptr())
+        elif self.kind == "adam_bf16":
+            w_local = f.flat[f.shard_offset: f.shard_offset + f.shard_numel]
+            rc = lib.b200_adamw_bf16_bcast(_lib.ptr(w_local), _lib.ptr(self.master), _lib.ptr(self.exp_avg),
+                                           _lib.ptr(self.exp_avg_sq), _lib.ptr(self.shard_grad), *tail, *adam_hp)
+        else:
+            rc = lib.b200_adamw_bcast(_lib.ptr(self.master), _lib.ptr(self.exp_avg), _lib.ptr(self.exp_avg_sq),
+                                      _lib.ptr(self.shard_grad), *tail, *adam_hp)
+        _lib.check(rc, "optimizer update kernel")
         _lib.count_launch()
         if world > 1:
             f.barrier.sync()  # all shards of the new weights have landed everywhere
@@ -292,11 +318,26 @@ class ShardedAdamW:
         coef = min(1.0, cfg.gradient_clipping / (norm + 1e-6)) if cfg.gradient_clipping > 0 else 1.0
         t = self.step_count + 1
         gk = self.shard_grad * coef
-        self.exp_avg.mul_(cfg.beta1).add_(gk, alpha=1 - cfg.beta1)
-        self.exp_avg_sq.mul_(cfg.beta2).addcmul_(gk, gk, value=1 - cfg.beta2)
-        denom = self.exp_avg_sq.sqrt() / math.sqrt(1 - cfg.beta2 ** t) + cfg.eps
-        self.master.mul_(1 - lr * cfg.weight_decay).addcdiv_(self.exp_avg, denom, value=-lr / (1 - cfg.beta1 ** t))
-        new = self.master.to(f.dtype)
+        if self.kind == "sgd":
+            self.master.sub_(lr * (gk + cfg.weight_decay * self.master))
+            new = self.master.to(f.dtype)
+        elif self.kind == "adam_bf16":
+            w = f.flat[o:o + n].float()
+            mk = cfg.beta1 * self.exp_avg.float() + (1 - cfg.beta1) * gk
+            vk = cfg.beta2 * self.exp_avg_sq.float() + (1 - cfg.beta2) * gk * gk
+            denom = vk.sqrt() / math.sqrt(1 - cfg.beta2 ** t) + cfg.eps
+            c = self.master.float() - lr * cfg.weight_decay * w - (lr / (1 - cfg.beta1 ** t)) * mk / denom
+            new = (w + c).to(f.dtype)
+            self.exp_avg.copy_(mk)
+            self.exp_avg_sq.copy_(vk)
+            self.master.copy_(c + (w - new.float()))
+        else:
+            self.exp_avg.mul_(cfg.beta1).add_(gk, alpha=1 - cfg.beta1)
+            self.exp_avg_sq.mul_(cfg.beta2).addcmul_(gk, gk, value=1 - cfg.beta2)
+            denom = self.exp_avg_sq.sqrt() / math.sqrt(1 - cfg.beta2 ** t) + cfg.eps
+            self.master.mul_(1 - lr * cfg.weight_decay).addcdiv_(self.exp_avg, denom,
+                                                                 value=-lr / (1 - cfg.beta1 ** t))
+            new = self.master.to(f.dtype)
         if f.dp_world > 1:
             parts = [torch.empty_like(new) for _ in range(f.dp_world)]
             dist.all_gather(parts, new, group=f.dp_group)

@@ -196,8 +196,11 @@ def test_adapter_cuda_matches_fp32_reference():
     yr.backward(gy.float())
     assert torch.allclose(y.float(), xr.detach() @ W.T, atol=2e-2, rtol=2e-2)
     assert torch.allclose(y.float(), yr, atol=2e-2, rtol=2e-2)
-    assert torch.allclose(x.grad.float(), xr.grad, atol=3e-2, rtol=3e-2)
-    assert torch.allclose(ad.lora_A.grad.float(), A.grad, atol=5e-2, rtol=5e-2)
+    def close(a, b, rel=2e-2):  # bf16 intermediates: error relative to the tensor's scale
+        return float((a.float() - b).abs().max()) <= rel * float(b.abs().max())
+
+    assert close(x.grad, xr.grad)
+    assert close(ad.lora_A.grad, A.grad)
     for i, n in enumerate(("q_proj", "k_proj", "v_proj")):
-        assert torch.allclose(ad.lora_B[n].grad.float(), Bs[i].grad, atol=5e-2, rtol=5e-2)
+        assert close(ad.lora_B[n].grad, Bs[i].grad)
     assert torch.all(ad.lora_A.grad[16:64] == 0)
