@@ -336,6 +336,8 @@ class B200TrainEngine(TrainEngine):
         ids = mb["input_ids"]
         pctx = self.pctx
         if pctx is None or (pctx.seq_shards == 1 and pctx.pp_size == 1):
+            if self.config.enable_tree_training and not self.is_critic:
+                return self._forward_mb_tree(mb, meta)
             hidden = self.model(ids, mb["position_ids"], meta)
             if self.is_critic:
                 return self.model.values(hidden), None
@@ -344,6 +346,36 @@ class B200TrainEngine(TrainEngine):
                                          self.config.temperature)
             return logp, ent
         return self._forward_mb_parallel(mb, meta, stage_input)
+
+    def _forward_mb_tree(self, mb: dict[str, Any], meta: VarlenMeta):
+        """Tree training: the micro-batch's sequences are merged into prefix tries, every distinct
+        token (trie node) runs through the trunk once under the ancestor mask, and the LM head runs
+        once per trie edge: the log-probability of node ``c``'s token given the path to its parent.
+        Position ``i`` of a sequence then reads the value of the node at position ``i + 1``; the last
+        position of every sequence has no label and yields zeros (the loss mask excludes it, as it
+        excludes the rolled-in label of the packed layout). Same outputs as the packed path within
+        floating-point reordering. Reference: areal/models/tree_attn/{tree.py:273,functional.py}."""
+        from ..ops.tree_attn import TreeMeta, build_packed_tree, tree_attention
+
+        ids = mb["input_ids"]
+        cu = meta.cu_cpu.tolist()
+        flat_ids = ids.tolist()
+        tree = build_packed_tree([flat_ids[a:b] for a, b in zip(cu[:-1], cu[1:])])
+        dev = ids.device
+        tmeta = TreeMeta(tree, dev) if dev.type == "cuda" else None
+        hidden = self.model(tree.tokens.to(dev), tree.position_ids.to(dev), meta,
+                            attn_fn=lambda q, k, v, _m: tree_attention(q, k, v, tree, tmeta))
+        parent = tree.parent.clamp(min=0).to(dev)  # roots: a dummy row, never read back
+        logp_n, ent_n = lm_head_logprobs(hidden.index_select(0, parent), self.model.output_weight(),
+                                         tree.tokens.to(dev), self.config.temperature)
+        nxt, has = [], []
+        for path in tree.seq_nodes:
+            nxt.extend(path[1:] + [0])
+            has.extend([1.0] * (len(path) - 1) + [0.0])
+        nxt = torch.tensor(nxt, dtype=torch.long, device=dev)
+        has = torch.tensor(has, dtype=logp_n.dtype, device=dev)
+        stats_tracker.scalar(**{"tree/node_ratio": tree.num_nodes / max(len(flat_ids), 1)})
+        return logp_n.index_select(0, nxt) * has, ent_n.index_select(0, nxt) * has
 
     def _forward_mb_parallel(self, mb: dict[str, Any], meta: VarlenMeta, stage_input=None):
         """Tensor- and/or Ulysses-parallel forward. Every rank of the model-parallel group holds the
