@@ -264,6 +264,9 @@ class NativeRolloutEngine(InferenceEngine):
             setattr(mc, k, v)
         self.model_config = mc
         dtype = torch.float32 if self.device.type == "cpu" else getattr(torch, ncfg.dtype)
+        if mc.is_hybrid:
+            raise NotImplementedError("the native rollout engine serves full-attention models; hybrid (linear-attention) "
+                                      "models train and score through the train engine only")
         self.model = build_model(mc, dtype=dtype, device=self.device, seed=ncfg.seed)
         if ncfg.model_path:
             from ..utils.hf_io import load_hf_weights

@@ -36,6 +36,16 @@ class ModelConfig:
     lora_rank: int = 0
     lora_alpha: float = 16.0
     lora_targets: list[str] = field(default_factory=list)
+    # hybrid models (qwen3_5): per-layer "full_attention" | "linear_attention"; empty = all full attention
+    layer_types: list[str] = field(default_factory=list)
+    partial_rotary_factor: float = 1.0   # fraction of head_dim that carries rotary embedding
+    attn_output_gate: bool = False       # q_proj emits query + sigmoid output gate per head
+    norm_one_plus: bool = False          # checkpoints store RMSNorm weights 1-centred: (1 + w) * norm(x)
+    linear_conv_kernel_dim: int = 4
+    linear_key_head_dim: int = 128
+    linear_value_head_dim: int = 128
+    linear_num_key_heads: int = 16
+    linear_num_value_heads: int = 32
     # MoE (qwen3_moe)
     num_experts: int = 0
     num_experts_per_tok: int = 0
@@ -53,6 +63,17 @@ class ModelConfig:
     def layer_is_moe(self, i: int) -> bool:
         return (self.is_moe and i not in self.mlp_only_layers
                 and (i + 1) % max(self.decoder_sparse_step, 1) == 0)
+
+    def layer_type(self, i: int) -> str:
+        return self.layer_types[i] if self.layer_types else "full_attention"
+
+    @property
+    def is_hybrid(self) -> bool:
+        return self.attn_output_gate or any(t == "linear_attention" for t in self.layer_types)
+
+    @property
+    def rotary_dim(self) -> int:
+        return int(self.head_dim * self.partial_rotary_factor) // 2 * 2
 
     @property
     def q_size(self) -> int:
@@ -97,8 +118,13 @@ class ModelConfig:
             p = Path(cfg)
             p = p / "config.json" if p.is_dir() else p
             cfg = json.loads(p.read_text())
+        if "text_config" in cfg:  # composite (vision-language) checkpoints nest the decoder's config
+            cfg = cfg["text_config"]
         mt = cfg.get("model_type", "qwen3")
+        if mt.startswith("qwen3_5"):
+            mt = "qwen3_5"
         heads = cfg["num_attention_heads"]
+        rope_params = cfg.get("rope_parameters") or {}
         out = cls(
             model_type=mt,
             vocab_size=cfg["vocab_size"],
@@ -109,7 +135,7 @@ class ModelConfig:
             num_key_value_heads=cfg.get("num_key_value_heads", heads),
             head_dim=cfg.get("head_dim") or cfg["hidden_size"] // heads,
             rms_norm_eps=cfg.get("rms_norm_eps", 1e-6),
-            rope_theta=cfg.get("rope_theta", 1e4),
+            rope_theta=cfg.get("rope_theta") or rope_params.get("rope_theta", 1e4),
             max_position_embeddings=cfg.get("max_position_embeddings", 32768),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
             attention_bias=cfg.get("attention_bias", mt == "qwen2"),
@@ -121,13 +147,24 @@ class ModelConfig:
             decoder_sparse_step=cfg.get("decoder_sparse_step", 1) or 1,
             mlp_only_layers=list(cfg.get("mlp_only_layers", []) or []),
         )
+        if mt == "qwen3_5":
+            out.layer_types = list(cfg.get("layer_types") or [])
+            out.partial_rotary_factor = (cfg.get("partial_rotary_factor")
+                                         or rope_params.get("partial_rotary_factor", 0.25))
+            out.attn_output_gate = out.norm_one_plus = True
+            for key in ("linear_conv_kernel_dim", "linear_key_head_dim", "linear_value_head_dim",
+                        "linear_num_key_heads", "linear_num_value_heads"):
+                if key in cfg:
+                    setattr(out, key, cfg[key])
+            if out.num_experts:
+                raise NotImplementedError("Qwen3.5 MoE (shared experts) is not supported; dense hybrids are")
         for k, v in overrides.items():
             setattr(out, k, v)
         return out
 
     def to_hf_config(self) -> dict:
         arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
-                "qwen3_moe": "Qwen3MoeForCausalLM"}[self.model_type]
+                "qwen3_moe": "Qwen3MoeForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM"}[self.model_type]
         d = {
             "architectures": [arch], "model_type": self.model_type,
             "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
@@ -141,6 +178,12 @@ class ModelConfig:
             "attention_bias": self.attention_bias, "hidden_act": "silu",
             "torch_dtype": "bfloat16",
         }
+        if self.model_type == "qwen3_5":
+            d.update(layer_types=self.layer_types, partial_rotary_factor=self.partial_rotary_factor,
+                     linear_conv_kernel_dim=self.linear_conv_kernel_dim,
+                     linear_key_head_dim=self.linear_key_head_dim, linear_value_head_dim=self.linear_value_head_dim,
+                     linear_num_key_heads=self.linear_num_key_heads,
+                     linear_num_value_heads=self.linear_num_value_heads)
         if self.is_moe:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size,
@@ -159,6 +202,14 @@ PRESETS: dict[str, ModelConfig] = {
                               intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
                               num_key_value_heads=2, head_dim=64, rope_theta=1e4,
                               tie_word_embeddings=False, attention_bias=True, qk_norm=False),
+    "tiny-qwen3_5": ModelConfig(model_type="qwen3_5", vocab_size=1024, hidden_size=256, intermediate_size=512,
+                                num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                                rope_theta=1e4, tie_word_embeddings=False, partial_rotary_factor=0.25,
+                                attn_output_gate=True, norm_one_plus=True,
+                                layer_types=["linear_attention", "linear_attention", "linear_attention",
+                                             "full_attention"],
+                                linear_key_head_dim=32, linear_value_head_dim=32, linear_num_key_heads=2,
+                                linear_num_value_heads=4),
     "tiny-qwen3-moe": ModelConfig(model_type="qwen3_moe", vocab_size=1024, hidden_size=256, intermediate_size=512,
                                   num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                                   rope_theta=1e4, tie_word_embeddings=False, num_experts=8, num_experts_per_tok=2,

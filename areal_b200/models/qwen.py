@@ -200,7 +200,13 @@ class Block(nn.Module):
         super().__init__()
         h = cfg.hidden_size
         self.input_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
-        self.attn = Attention(cfg, dtype, device, pctx, layer_idx)
+        if cfg.is_hybrid:
+            from .qwen3_5 import GatedAttention, GatedDeltaNet
+
+            kind = GatedDeltaNet if cfg.layer_type(layer_idx) == "linear_attention" else GatedAttention
+            self.attn = kind(cfg, dtype, device, pctx, layer_idx)
+        else:
+            self.attn = Attention(cfg, dtype, device, pctx, layer_idx)
         self.post_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
         if cfg.layer_is_moe(layer_idx):
             assert pctx is None or pctx.tp_size == 1, "MoE layers shard over the expert-parallel group, not tp"
@@ -266,6 +272,8 @@ class QwenModel(nn.Module):
             if name.endswith("norm") or "_norm" in name:
                 p.fill_(1.0)
                 continue
+            if name.endswith(("attn.conv_w", "attn.A_log", "attn.dt_bias")):
+                continue  # set by GatedDeltaNet.init_special below
             if name.endswith("bias"):
                 p.zero_()
                 continue
@@ -297,6 +305,9 @@ class QwenModel(nn.Module):
                 p.copy_(dst[self.pctx.ep_rank * n:(self.pctx.ep_rank + 1) * n])
             elif dst is not p:
                 p.copy_(tp_slice(name, dst, self.cfg, tp_rank, tp))
+        for li, layer in enumerate(self.layers):
+            if hasattr(layer.attn, "init_special"):
+                layer.attn.init_special(torch.Generator(device="cpu").manual_seed(seed * 1000 + li))
         return self
 
     @torch.no_grad()
@@ -336,7 +347,7 @@ class QwenModel(nn.Module):
     def rope(self, device, max_pos=None):
         max_pos = max_pos or self.cfg.max_position_embeddings
         if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < max_pos:
-            self._rope = fused.rope_tables(max_pos, self.cfg.head_dim, self.cfg.rope_theta, device)
+            self._rope = fused.rope_tables(max_pos, self.cfg.rotary_dim, self.cfg.rope_theta, device)
         return self._rope
 
     # --------------------------------------------------------------- forward
@@ -458,7 +469,7 @@ class QwenModel(nn.Module):
         rank must iterate)."""
         import torch.distributed as dist
 
-        for name, t in self.to_hf_local():
+        for name, t in self.to_hf_local(export=True):
             d = self._tp_dim(name)
             if d is None:
                 yield name, t
@@ -467,9 +478,13 @@ class QwenModel(nn.Module):
                 dist.all_gather(parts, t.contiguous(), group=self.pctx.tp_group)
                 yield name, torch.cat(parts, d)
 
-    def to_hf_local(self) -> Iterator[tuple[str, torch.Tensor]]:
-        """``(hf_name, view)`` of this rank's (tp-local) parameters."""
+    def to_hf_local(self, export: bool = False) -> Iterator[tuple[str, torch.Tensor]]:
+        """``(hf_name, view)`` of this rank's (tp-local) parameters. Families whose checkpoints store
+        RMSNorm weights 1-centred get ``w - 1`` copies instead of views when ``export`` is set."""
         cfg = self.cfg
+        if cfg.is_hybrid:
+            yield from self._to_hf_hybrid(export)
+            return
         tp = self.pctx.tp_size if self.pctx is not None else 1
         if self.embed is not None and self.first_stage:
             yield "model.embed_tokens.weight", self.embed
@@ -511,6 +526,32 @@ class QwenModel(nn.Module):
         elif self.lm_head is not None:
             yield "lm_head.weight", self.lm_head
 
+    def _to_hf_hybrid(self, export: bool):
+        from .qwen3_5 import hf_tensors
+
+        cfg = self.cfg
+        nw = (lambda t: t - 1) if (export and cfg.norm_one_plus) else (lambda t: t)
+        if self.embed is not None and self.first_stage:
+            yield "model.embed_tokens.weight", self.embed
+        I = cfg.intermediate_size
+        for i, layer in enumerate(self.layers, start=self.layer_start):
+            p = f"model.layers.{i}."
+            yield p + "input_layernorm.weight", nw(layer.input_norm)
+            yield from hf_tensors(layer.attn, p, cfg, nw)
+            yield p + "post_attention_layernorm.weight", nw(layer.post_norm)
+            yield p + "mlp.gate_proj.weight", layer.mlp.gate_up[:I]
+            yield p + "mlp.up_proj.weight", layer.mlp.gate_up[I:]
+            yield p + "mlp.down_proj.weight", layer.mlp.down
+        if self.norm is not None:
+            yield "model.norm.weight", nw(self.norm)
+        if self.score is not None:
+            yield "score.weight", self.score
+        elif self.lm_head is not None:
+            yield "lm_head.weight", self.lm_head
+
+    _ONE_PLUS = ("input_layernorm.weight", "post_attention_layernorm.weight", "model.norm.weight",
+                 "self_attn.q_norm.weight", "self_attn.k_norm.weight")
+
     def hf_name_map(self) -> dict[str, torch.Tensor]:
         return dict(self.to_hf_local())
 
@@ -520,6 +561,10 @@ class QwenModel(nn.Module):
         dst = self.hf_name_map()
         seen = set()
         for name, t in tensors:
+            if name.startswith("model.language_model."):  # decoder of a composite checkpoint
+                name = "model." + name[len("model.language_model."):]
+            if self.cfg.norm_one_plus and name.endswith(self._ONE_PLUS):
+                t = t.float() + 1.0
             if name == "lm_head.weight" and self.lm_head is None and self.score is None:
                 seen.add(name)
                 continue  # tied

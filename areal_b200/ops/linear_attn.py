@@ -1,8 +1,9 @@
 """Linear-attention ops for hybrid models on packed sequences (``csrc/linear_attn.cu``):
 causal depthwise conv1d (+SiLU) with forward and backward kernels, and the gated delta rule /
 simple gated linear attention recurrences. The recurrences run their CUDA kernel whenever no
-gradient is needed (rollout, logprob recomputation); under autograd they run the PyTorch
-restatement below, which is also the test oracle.
+gradient is needed (rollout, logprob recomputation); under autograd they run the chunk-parallel
+PyTorch form below (``linear_attn_chunked``: one sequential step per 64 tokens). The per-token
+restatement (``linear_attn_ref``) is the test oracle of both.
 
 Reference call sites: causal_conv1d_fn and fla ``chunk_gated_delta_rule``
 (areal/experimental/models/archon/qwen3_5/model/model.py:244,291), fla ``chunk_simple_gla``
@@ -115,6 +116,63 @@ def linear_attn_ref(q, k, v, a, b, cu, scale: float, mode: str):
     return torch.stack(out).to(q.dtype) if out else torch.zeros_like(v)
 
 
+def linear_attn_chunked(q, k, v, a, b, cu, scale: float, mode: str, chunk: int = 64):
+    """The same recurrences in chunk-parallel form (differentiable; the training path).
+
+    Inside a chunk that starts from state ``S0``, with ``G_i`` the running sum of ``log a`` and
+    ``D_ij = exp(G_i - G_j)`` for ``j <= i``:
+
+    * the delta-rule writes ``u_i = b_i (v_i - (a_i S_{i-1})^T k_i)`` solve the unit lower-triangular
+      system ``(I + A) U = diag(b) (V - diag(exp G) K S0)`` with ``A_ij = b_i D_ij (k_i . k_j)``, ``j < i``
+      (``U = V`` for ``simple_gla``);
+    * ``O = scale * (diag(exp G) Q S0 + (D o Q K^T) U)`` and ``S_C = exp(G_C) S0 + (K o exp(G_C - G))^T U``.
+
+    ``(I + A)^-1`` does not depend on the state, so it is computed for all chunks of a sequence at
+    once; only the small ``S0`` recursion is sequential (one step per chunk, not per token)."""
+    T, H, DK = q.shape
+    DV = v.shape[2]
+    delta = mode == "gated_delta"
+    outs = []
+    cu_l = [int(c) for c in cu]
+    for s0, s1 in zip(cu_l[:-1], cu_l[1:]):
+        L = s1 - s0
+        if L == 0:
+            continue
+        n = -(-L // chunk)
+        pad = n * chunk - L
+
+        def prep(t, fill=0.0):  # [L, H, ...] -> [H, n, chunk, ...]
+            t = t[s0:s1].float()
+            if pad:
+                t = torch.cat([t, t.new_full((pad,) + tuple(t.shape[1:]), fill)], 0)
+            return t.reshape(n, chunk, *t.shape[1:]).movedim(2, 0)
+
+        Q, K, V = prep(q), prep(k), prep(v)
+        G = prep(a, 1.0).clamp_min(1e-30).log().cumsum(-1)             # [H, n, C]
+        Dm = (G[..., :, None] - G[..., None, :]).tril().exp().tril()   # D_ij, j <= i
+        eg = G.exp()[..., None]
+        if delta:
+            Bt = prep(b)[..., None]                                     # [H, n, C, 1]
+            A = (Bt * Dm * (K @ K.transpose(-1, -2))).tril(-1)
+            eye = torch.eye(chunk, device=q.device, dtype=torch.float32)
+            rhs = torch.cat([Bt * V, Bt * eg * K], -1)                  # one solve for W_v and W_k
+            sol = torch.linalg.solve_triangular(A + eye, rhs, upper=False, unitriangular=True)
+            Wv, Wk = sol[..., :DV], sol[..., DV:]
+        QK = Dm * (Q @ K.transpose(-1, -2))
+        Kd = K * (G[..., -1:, None] - G[..., None]).exp()               # k_j exp(G_C - G_j)
+        S = torch.zeros(H, DK, DV, dtype=torch.float32, device=q.device)
+        o_chunks = []
+        for c in range(n):
+            U = (Wv[:, c] - Wk[:, c] @ S) if delta else V[:, c]
+            o_chunks.append((eg[:, c] * Q[:, c]) @ S + QK[:, c] @ U)
+            S = eg[:, c, -1][..., None] * S + Kd[:, c].transpose(-1, -2) @ U
+        o = torch.stack(o_chunks, 1).reshape(H, n * chunk, DV)[:, :L]
+        outs.append(o.transpose(0, 1))
+    if not outs:
+        return torch.zeros_like(v)
+    return (torch.cat(outs, 0) * scale).to(q.dtype)
+
+
 def linear_attn(q, k, v, a, b, cu, scale: float | None = None, mode: str = "gated_delta"):
     """``o_t = scale * S_t^T q_t`` with ``S_t = a_t S_{t-1} + k_t v_t^T`` (``simple_gla``) or the gated
     delta rule ``S_t = a_t S_{t-1} + b_t k_t (v_t - (a_t S_{t-1})^T k_t)^T``."""
@@ -124,8 +182,11 @@ def linear_attn(q, k, v, a, b, cu, scale: float | None = None, mode: str = "gate
     DV = v.shape[2]
     scale = scale if scale is not None else DK ** -0.5
     needs_grad = torch.is_grad_enabled() and any(t is not None and t.requires_grad for t in (q, k, v, a, b))
-    if needs_grad or not (_lib.use_cuda_kernels(q, k, v) and q.dtype == torch.bfloat16 and DK in (64, 128) and DV <= 256):
-        return linear_attn_ref(q, k, v, a, b, cu, scale, mode)
+    if needs_grad:
+        return linear_attn_chunked(q, k, v, a, b, cu, scale, mode)
+    if not (_lib.use_cuda_kernels(q, k, v) and q.dtype == torch.bfloat16 and DK in (64, 128) and DV <= 256):
+        return linear_attn_chunked(q, k, v, a, b, cu, scale, mode) if T > 256 else \
+            linear_attn_ref(q, k, v, a, b, cu, scale, mode)
     q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
     a32 = a.float().contiguous()
     b32 = b.float().contiguous() if b is not None else None

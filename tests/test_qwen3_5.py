@@ -1,0 +1,223 @@
+"""Qwen3.5 hybrid family: chunk-parallel gated delta rule against the per-token recurrence, the two
+layer types against explicit restatements built from checkpoint-named tensors, checkpoint round
+trip (1-centred norm weights), and training through the engine."""
+import dataclasses
+import json
+import math
+import os
+
+import pytest
+import torch
+import torch.nn.functional as F
+
+from areal_b200.models.config import PRESETS, ModelConfig
+from areal_b200.models.qwen import build_model
+from areal_b200.ops.attention import VarlenMeta
+from areal_b200.ops.linear_attn import linear_attn_chunked, linear_attn_ref
+
+CFG = PRESETS["tiny-qwen3_5"]
+
+
+@pytest.mark.parametrize("mode", ["gated_delta", "simple_gla"])
+def test_chunked_recurrence_matches_per_token(mode):
+    torch.manual_seed(0)
+    T, H, DK, DV = 150, 3, 16, 24
+    cu = torch.tensor([0, 70, 71, 150])
+    base = [F.normalize(torch.randn(T, H, DK), dim=-1), F.normalize(torch.randn(T, H, DK), dim=-1),
+            torch.randn(T, H, DV), torch.rand(T, H) * 0.6 + 0.4, torch.rand(T, H)]
+    a = [t.clone().requires_grad_(True) for t in base]
+    b = [t.clone().requires_grad_(True) for t in base]
+    o1 = linear_attn_ref(*a, cu, 0.25, mode)
+    o2 = linear_attn_chunked(*b, cu, 0.25, mode, chunk=32)
+    assert torch.allclose(o1, o2, atol=1e-5)
+    gy = torch.randn_like(o1)
+    o1.backward(gy)
+    o2.backward(gy)
+    for x, y in zip(a, b):
+        if x.grad is not None:
+            assert torch.allclose(x.grad, y.grad, atol=2e-5)
+
+
+def _setup(lens=(23, 41)):
+    torch.manual_seed(1)
+    m = build_model(CFG, dtype=torch.float32, seed=5)
+    with torch.no_grad():  # move norms away from their initial ones so that the 1-centring is exercised
+        for n, p in m.named_parameters():
+            if n.endswith("norm") or "_norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+    T = sum(lens)
+    cu = [0]
+    for n in lens:
+        cu.append(cu[-1] + n)
+    pos = torch.cat([torch.arange(n) for n in lens])
+    meta = VarlenMeta(torch.tensor(cu, dtype=torch.int32), "cpu")
+    return m, T, cu, pos, meta
+
+
+def test_gated_delta_net_layer_matches_restatement():
+    m, T, cu, pos, meta = _setup()
+    layer = m.layers[0].attn
+    hf = {k: v.detach() for k, v in m.to_hf()}
+    p = "model.layers.0.linear_attn."
+    x = torch.randn(T, CFG.hidden_size)
+    cos, sin = m.rope("cpu")
+    got = layer(x, cos, sin, pos, meta)
+    nk, nv, dk, dv = CFG.linear_num_key_heads, CFG.linear_num_value_heads, CFG.linear_key_head_dim, CFG.linear_value_head_dim
+    outs = []
+    for s, e in zip(cu[:-1], cu[1:]):
+        xs = x[s:e]
+        mixed = xs @ hf[p + "in_proj_qkv.weight"].T
+        z = xs @ hf[p + "in_proj_z.weight"].T
+        a = xs @ hf[p + "in_proj_a.weight"].T
+        b = xs @ hf[p + "in_proj_b.weight"].T
+        conv = F.conv1d(mixed.T[None], hf[p + "conv1d.weight"], padding=CFG.linear_conv_kernel_dim - 1,
+                        groups=mixed.shape[1])[0, :, :e - s].T
+        mixed = F.silu(conv)
+        q, k, v = mixed.split([nk * dk, nk * dk, nv * dv], -1)
+        q = F.normalize(q.reshape(-1, nk, dk), dim=-1, eps=0).repeat_interleave(nv // nk, 1)
+        k = F.normalize(k.reshape(-1, nk, dk), dim=-1, eps=0).repeat_interleave(nv // nk, 1)
+        v = v.reshape(-1, nv, dv)
+        beta = torch.sigmoid(b)
+        g = -hf[p + "A_log"].exp() * F.softplus(a + hf[p + "dt_bias"])
+        S = torch.zeros(nv, dk, dv)
+        o = []
+        for t in range(e - s):
+            S = S * g[t].exp()[:, None, None]
+            u = beta[t][:, None] * (v[t] - torch.einsum("hkv,hk->hv", S, k[t]))
+            S = S + torch.einsum("hk,hv->hkv", k[t], u)
+            o.append(torch.einsum("hkv,hk->hv", S, q[t]) * dk ** -0.5)
+        o = torch.stack(o)
+        o = o * torch.rsqrt(o.pow(2).mean(-1, keepdim=True) + CFG.rms_norm_eps) * hf[p + "norm.weight"]
+        o = o * F.silu(z.reshape(-1, nv, dv))
+        outs.append(o.reshape(e - s, -1) @ hf[p + "out_proj.weight"].T)
+    want = torch.cat(outs)
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), float((got - want).abs().max())
+
+
+def test_gated_attention_layer_matches_restatement():
+    m, T, cu, pos, meta = _setup()
+    li = CFG.layer_types.index("full_attention")
+    layer = m.layers[li].attn
+    hf = {k: v.detach() for k, v in m.to_hf()}
+    p = f"model.layers.{li}.self_attn."
+    x = torch.randn(T, CFG.hidden_size)
+    cos, sin = m.rope("cpu")
+    got = layer(x, cos, sin, pos, meta)
+    nq, nkv, D = CFG.num_attention_heads, CFG.num_key_value_heads, CFG.head_dim
+    R = int(D * CFG.partial_rotary_factor)
+    inv = 1.0 / (CFG.rope_theta ** (torch.arange(0, R, 2).float() / R))
+
+    def norm1p(t, w):  # checkpoint semantics: (1 + w) * norm(x)
+        return t * torch.rsqrt(t.pow(2).mean(-1, keepdim=True) + CFG.rms_norm_eps) * (1 + w)
+
+    def rope(t, positions):
+        fr = torch.outer(positions.float(), inv)
+        c, s = torch.cat([fr.cos()] * 2, -1)[:, None], torch.cat([fr.sin()] * 2, -1)[:, None]
+        tr, tp = t[..., :R], t[..., R:]
+        rot = torch.cat([-tr[..., R // 2:], tr[..., :R // 2]], -1)
+        return torch.cat([tr * c + rot * s, tp], -1)
+
+    outs = []
+    for s, e in zip(cu[:-1], cu[1:]):
+        xs, L = x[s:e], e - s
+        qg = (xs @ hf[p + "q_proj.weight"].T).view(L, nq, 2 * D)
+        q, gate = qg[..., :D], qg[..., D:].reshape(L, -1)
+        k = (xs @ hf[p + "k_proj.weight"].T).view(L, nkv, D)
+        v = (xs @ hf[p + "v_proj.weight"].T).view(L, nkv, D)
+        q, k = rope(norm1p(q, hf[p + "q_norm.weight"]), pos[s:e]), rope(norm1p(k, hf[p + "k_norm.weight"]), pos[s:e])
+        k, v = k.repeat_interleave(nq // nkv, 1), v.repeat_interleave(nq // nkv, 1)
+        att = torch.einsum("ihd,jhd->hij", q, k) / math.sqrt(D)
+        att = att.masked_fill(~torch.ones(L, L, dtype=torch.bool).tril(), float("-inf")).softmax(-1)
+        o = torch.einsum("hij,jhd->ihd", att, v).reshape(L, -1) * torch.sigmoid(gate)
+        outs.append(o @ hf[p + "o_proj.weight"].T)
+    want = torch.cat(outs)
+    assert torch.allclose(got, want, atol=2e-4, rtol=1e-3), float((got - want).abs().max())
+
+
+def test_checkpoint_round_trip(tmp_path):
+    from areal_b200.utils.hf_io import load_hf_weights, save_hf_checkpoint
+
+    m, T, cu, pos, meta = _setup()
+    ids = torch.randint(0, CFG.vocab_size, (T,))
+    with torch.no_grad():
+        h0 = m(ids, pos, meta)
+    fresh = build_model(CFG, dtype=torch.float32, seed=9)
+    hf = dict(fresh.to_hf())
+    assert float(hf["model.norm.weight"].detach().abs().max()) == 0.0  # initial multiplier 1 is stored as 0
+    save_hf_checkpoint(m, CFG, str(tmp_path))
+    conf = json.load(open(os.path.join(tmp_path, "config.json")))
+    assert conf["model_type"] == "qwen3_5" and conf["layer_types"] == CFG.layer_types
+    cfg2 = ModelConfig.from_hf_config(str(tmp_path))
+    assert cfg2.layer_types == CFG.layer_types and cfg2.norm_one_plus and cfg2.attn_output_gate
+    assert cfg2.partial_rotary_factor == CFG.partial_rotary_factor and cfg2.linear_num_value_heads == 4
+    m2 = build_model(cfg2, dtype=torch.float32, seed=None)
+    load_hf_weights(m2, str(tmp_path))
+    with torch.no_grad():
+        h1 = m2(ids, pos, meta)
+    assert torch.allclose(h0, h1, atol=1e-5)
+
+
+def test_engine_trains_hybrid_model(tmp_path):
+    from areal_b200.api.cli_args import MicroBatchSpec, OptimizerConfig, SFTConfig, TrainEngineConfig, _propagate_names
+    from areal_b200.trainer.sl_trainer import SFTTrainer
+
+    g = torch.Generator().manual_seed(0)
+    data = []
+    for _ in range(8):
+        n = int(torch.randint(12, 24, (1,), generator=g))
+        data.append(dict(input_ids=torch.randint(0, 1024, (n,), generator=g).tolist(), loss_mask=[0] * 4 + [1] * (n - 4)))
+    cfg = SFTConfig(actor=TrainEngineConfig(
+        backend="fsdp:d1", model_preset="tiny-qwen3_5", init_from_scratch=True,
+        optimizer=OptimizerConfig(lr=2e-3, warmup_steps_proportion=0.0, weight_decay=0.0),
+        mb_spec=MicroBatchSpec(max_tokens_per_mb=512)))
+    cfg.experiment_name, cfg.trial_name = "t", "t"
+    cfg.cluster.fileroot = str(tmp_path)
+    cfg.train_dataset.batch_size = 8
+    cfg.train_dataset.shuffle = False
+    cfg.total_train_epochs = 6
+    _propagate_names(cfg)
+    losses = []
+    with SFTTrainer(cfg, data, data) as tr:
+        tr.train(max_steps=6, step_callback=lambda s, st: losses.append(st["step/loss"]))
+    assert len(losses) == 6 and losses[-1] < losses[0]
+
+
+@pytest.mark.gpu
+def test_hybrid_model_cuda_matches_fp32_reference():
+    from areal_b200.ops import _lib
+    from areal_b200.ops.lm_head import lm_head_logprobs
+
+    cfg = dataclasses.replace(CFG, hidden_size=512, intermediate_size=1024, head_dim=128, vocab_size=4096,
+                              linear_key_head_dim=64, linear_value_head_dim=64)
+    m = build_model(cfg, dtype=torch.bfloat16, device="cuda", seed=0)
+    ref = build_model(cfg, dtype=torch.float32, device="cuda", seed=None)
+    ref.load_state_dict({k: v.float() for k, v in m.state_dict().items()})
+    lens = [100, 37, 260]
+    T = sum(lens)
+    ids = torch.randint(0, cfg.vocab_size, (T,), device="cuda")
+    pos = torch.cat([torch.arange(n) for n in lens]).cuda()
+    labels = torch.roll(ids, -1)
+    meta = VarlenMeta([0, 100, 137, 397], "cuda")
+    h = m(ids, pos, meta)
+    logp, _ = lm_head_logprobs(h, m.output_weight(), labels, 1.0)
+    (-logp.mean()).backward()
+    assert _lib.read_status() == 0
+    with torch.no_grad():
+        h_ng = m(ids, pos, meta)  # no-grad path: the recurrence runs its CUDA kernel
+    os.environ["AREAL_B200_FORCE_TORCH"] = "1"
+    try:
+        hr = ref(ids, pos, meta)
+        logp_r, _ = lm_head_logprobs(hr, ref.output_weight(), labels, 1.0)
+        (-logp_r.mean()).backward()
+    finally:
+        del os.environ["AREAL_B200_FORCE_TORCH"]
+    assert float((h.float() - hr).abs().max()) < 0.25 and float((h_ng.float() - hr).abs().max()) < 0.25
+    torch.testing.assert_close(logp, logp_r, atol=0.15, rtol=0.05)
+    gm = dict(m.named_parameters())
+    for name, pr in ref.named_parameters():
+        if pr.grad is None:
+            continue
+        g = gm[name].grad
+        assert g is not None, name
+        rel = (g.float() - pr.grad).norm().item() / (pr.grad.norm().item() + 1e-8)
+        assert rel < 0.1, f"{name}: rel grad err {rel:.4f}"
