@@ -136,7 +136,8 @@ class ShardedAdamW:
     * ``sgd``: plain SGD with coupled weight decay on an fp32 master copy."""
 
     def __init__(self, flat: FlatParams, cfg: OptimizerConfig, total_steps: int = 1, tp_group=None,
-                 tp_full_grad: tuple[str, ...] = ("score",)):
+                 tp_full_grad: tuple[str, ...] = ("score",), host_state: bool = False, prefetch: int = 1,
+                 chunk_numel: int = 1 << 24):
         """``tp_group``: tensor-parallel group over which the gradients of the replicated region
         (``flat.rep_numel``) are summed before the data-parallel reduction; parameters named in
         ``tp_full_grad`` already hold the full gradient on every tp rank."""
@@ -155,11 +156,29 @@ class ShardedAdamW:
         n, o = flat.shard_numel, flat.shard_offset
         dev = flat.device
         self.kind = {"adam": "adamw", "adamw": "adamw"}.get(cfg.type, cfg.type)
+        # host_state: master weights and moments live in pinned host memory and stream through the GPU
+        # in chunks during the step (H2D of chunk i+1 and D2H of chunk i-1 overlap the update of chunk
+        # i on separate streams); the counterpart of the reference's PerLayerOptimWrapper
+        # (areal/engine/fsdp_utils/optimizer.py:324-633), chunked by flat offset instead of by layer
+        self.host_state = bool(host_state) and flat.cuda
+        if self.host_state and self.kind != "adamw":
+            raise ValueError("host-resident optimizer state requires optimizer type 'adam'")
+        self._chunk = max(int(chunk_numel) // 4 * 4, 4)
+        self._slots = max(int(prefetch), 0) + 2
         if self.kind == "adam_bf16":
             assert flat.dtype == torch.bfloat16, "adam_bf16 keeps its state in the weights' bf16"
             self.master = torch.zeros(n, dtype=torch.bfloat16, device=dev)  # Kahan compensation
             self.exp_avg = torch.zeros(n, dtype=torch.bfloat16, device=dev)
             self.exp_avg_sq = torch.zeros(n, dtype=torch.bfloat16, device=dev)
+        elif self.host_state:
+            self.master = torch.empty(n, dtype=torch.float32, pin_memory=True)
+            self.master.copy_(flat.flat[o:o + n].to(torch.float32))
+            self.exp_avg = torch.zeros(n, dtype=torch.float32, pin_memory=True)
+            self.exp_avg_sq = torch.zeros(n, dtype=torch.float32, pin_memory=True)
+            c = min(self._chunk, max(n, 4))
+            self._stage = [[torch.empty(c, dtype=torch.float32, device=dev) for _ in range(3)]
+                           for _ in range(self._slots)]
+            self._h2d, self._d2h = torch.cuda.Stream(dev), torch.cuda.Stream(dev)
         else:
             self.master = flat.flat[o:o + n].to(torch.float32).clone()
             m = 0 if self.kind == "sgd" else n
@@ -257,7 +276,9 @@ class ShardedAdamW:
                    ctypes.c_float(cfg.weight_decay), ctypes.c_float(1 - cfg.beta1 ** t),
                    ctypes.c_float(1 - cfg.beta2 ** t), ctypes.c_float(cfg.gradient_clipping),
                    _lib.ptr(self._skipped), _lib.stream_ptr())
-        if self.kind == "sgd":
+        if self.host_state:
+            rc = self._update_streamed(lib, lr, adam_hp)
+        elif self.kind == "sgd":
             rc = lib.b200_sgd_bcast(_lib.ptr(self.master), _lib.ptr(self.shard_grad), *tail,
                                     ctypes.c_float(cfg.weight_decay), ctypes.c_float(cfg.gradient_clipping),
                                     _lib.ptr(self._skipped), _lib.stream_ptr())
@@ -269,7 +290,8 @@ class ShardedAdamW:
             rc = lib.b200_adamw_bcast(_lib.ptr(self.master), _lib.ptr(self.exp_avg), _lib.ptr(self.exp_avg_sq),
                                       _lib.ptr(self.shard_grad), *tail, *adam_hp)
         _lib.check(rc, "optimizer update kernel")
-        _lib.count_launch()
+        if not self.host_state:
+            _lib.count_launch()
         if world > 1:
             f.barrier.sync()  # all shards of the new weights have landed everywhere
         vals = torch.cat([self._norm, self._skipped.float()]).tolist()
@@ -278,6 +300,55 @@ class ShardedAdamW:
             self.step_count = t
         return dict(grad_norm=math.sqrt(vals[0]) if vals[0] >= 0 else float("nan"),
                     update_successful=float(ok), lr=lr)
+
+    def _update_streamed(self, lib, lr: float, adam_hp) -> int:
+        """AdamW over host-resident state: chunk ``i`` is updated on the current stream while chunk
+        ``i+1..`` loads and chunk ``i-1`` stores on two copy streams; a staging slot is reloaded only
+        after its previous contents were written back."""
+        f = self.flat
+        n, chunk, slots = f.shard_numel, self._chunk, self._slots
+        spans = [(s, min(chunk, n - s)) for s in range(0, n, chunk)]
+        host = (self.master, self.exp_avg, self.exp_avg_sq)
+        cur = torch.cuda.current_stream(f.device)
+        loaded = [torch.cuda.Event() for _ in spans]
+        stored = [torch.cuda.Event() for _ in spans]
+
+        def load(i):
+            s, m = spans[i]
+            with torch.cuda.stream(self._h2d):
+                for dst, src in zip(self._stage[i % slots], host):
+                    dst[:m].copy_(src[s:s + m], non_blocking=True)
+                loaded[i].record(self._h2d)
+
+        self._h2d.wait_stream(cur)  # the staging buffers' previous users are done
+        for i in range(min(slots - 1, len(spans))):
+            load(i)
+        rc = 0
+        for i, (s, m) in enumerate(spans):
+            st = self._stage[i % slots]
+            cur.wait_event(loaded[i])
+            rc = lib.b200_adamw_bcast(_lib.ptr(st[0]), _lib.ptr(st[1]), _lib.ptr(st[2]),
+                                      _lib.ptr(self.shard_grad[s:s + m]), self._param_table, ctypes.c_int(f.dp_world),
+                                      ctypes.c_longlong(f.shard_offset + s), ctypes.c_longlong(m),
+                                      _lib.ptr(self._norm), ctypes.c_float(lr), *adam_hp)
+            if rc != 0:
+                break
+            _lib.count_launch()
+            done = torch.cuda.Event()
+            done.record(cur)
+            with torch.cuda.stream(self._d2h):
+                self._d2h.wait_event(done)
+                for src, dst in zip(st, host):
+                    dst[s:s + m].copy_(src[:m], non_blocking=True)
+                stored[i].record(self._d2h)
+            nxt = i + slots - 1
+            if nxt < len(spans):
+                if nxt - slots >= 0:
+                    self._h2d.wait_event(stored[nxt - slots])  # that slot's write-back has finished
+                load(nxt)
+        cur.wait_stream(self._d2h)
+        cur.wait_stream(self._h2d)
+        return rc
 
     def _dedup_replicated_norm(self, nsq: torch.Tensor):
         """The squared norm is summed over the tp group afterwards; entries of the replicated

@@ -263,8 +263,11 @@ class B200TrainEngine(TrainEngine):
                 pctx.extras["ep_state"] = EPGroupState(pctx.ep_group, mc.num_experts, mc.hidden_size, cap, self.device)
         if self.optimizer_config is not None:
             total = ft_spec.total_train_steps if ft_spec is not None else 1
+            fs = cfg.fsdp
             self.optimizer = ShardedAdamW(self.flat, self.optimizer_config, total_steps=total,
-                                          tp_group=pctx.tp_group if tp > 1 else None)
+                                          tp_group=pctx.tp_group if tp > 1 else None,
+                                          host_state=bool(getattr(fs, "per_layer_optim_step", False)),
+                                          prefetch=int(getattr(fs, "optim_step_prefetch_layers", 1)))
             if self.flat_experts is not None:
                 self.optimizer.partner = ShardedAdamW(self.flat_experts, self.optimizer_config, total_steps=total)
                 self.optimizer.partner_group = pctx.ep_group
@@ -725,7 +728,8 @@ class B200TrainEngine(TrainEngine):
         if self.optimizer is None or self._offloaded is not None:
             return
         self._offloaded = {}
-        for name in ("master", "exp_avg", "exp_avg_sq", "shard_grad"):
+        names = ("shard_grad",) if self.optimizer.host_state else ("master", "exp_avg", "exp_avg_sq", "shard_grad")
+        for name in names:
             t = getattr(self.optimizer, name)
             host = torch.empty(t.shape, dtype=t.dtype, pin_memory=self.device.type == "cuda")
             host.copy_(t)

@@ -78,3 +78,26 @@ def test_cuda_kernels_match_torch(kind):
     for a, b in zip(got, want):
         # weights are published in bf16: one ulp of the largest weights (~4) is 0.03
         assert (a - b).abs().max() < (0.05 if kind == "adam_bf16" else 0.02)
+
+
+@pytest.mark.gpu
+def test_host_resident_state_streams_to_the_same_result():
+    """Master weights and moments in pinned host memory, streamed through the GPU in chunks
+    (several chunks, staging slots reused): bitwise the same weights as device-resident state."""
+    def run(host):
+        m = _Toy(torch.bfloat16, "cuda")
+        big = torch.nn.Parameter(torch.randn(70001, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda())
+        m.big = big
+        cfg = OptimizerConfig(type="adam", lr=1e-2, weight_decay=0.1, warmup_steps_proportion=0.0, gradient_clipping=0.5)
+        flat = FlatParams(m, "local")
+        opt = ShardedAdamW(flat, cfg, total_steps=5, host_state=host, prefetch=1, chunk_numel=8192)
+        g = torch.Generator().manual_seed(1)
+        for _ in range(5):
+            flat.main_grad.copy_((torch.randn(flat.numel, generator=g) * 0.1).cuda())
+            assert opt.step()["update_successful"] == 1.0
+        return flat.flat.clone(), opt
+
+    w_dev, _ = run(False)
+    w_host, opt = run(True)
+    assert opt.host_state and opt.master.is_pinned() and not opt.master.is_cuda
+    assert torch.equal(w_dev, w_host)
