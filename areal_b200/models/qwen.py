@@ -242,7 +242,14 @@ class QwenModel(nn.Module):
         pp = pctx.pp_size if pctx is not None else 1
         self.first_stage = pctx.is_first_stage if pp > 1 else True
         self.last_stage = pctx.is_last_stage if pp > 1 else True
-        self.layer_start, self.layer_end = pctx.layer_range(cfg.num_hidden_layers) if pp > 1 else (0, cfg.num_hidden_layers)
+        if pp > 1:
+            # the last stage also runs the LM head (or value head) and the loss: weigh it in units of one block
+            per_layer = max((cfg.num_params() - cfg.vocab_size * cfg.hidden_size *
+                             (1 if (cfg.tie_word_embeddings or cfg.is_critic) else 2)) / cfg.num_hidden_layers, 1.0)
+            head = 0.0 if cfg.is_critic else cfg.vocab_size * cfg.hidden_size / per_layer
+            self.layer_start, self.layer_end = pctx.layer_range(cfg.num_hidden_layers, last_extra=head)
+        else:
+            self.layer_start, self.layer_end = 0, cfg.num_hidden_layers
         mk = lambda *shape: nn.Parameter(torch.empty(*shape, dtype=dtype, device=device))
         need_embed = self.first_stage or (self.last_stage and cfg.tie_word_embeddings and not cfg.is_critic)
         self.embed = mk(vloc, cfg.hidden_size) if need_embed else None

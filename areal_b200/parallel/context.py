@@ -16,6 +16,40 @@ import torch
 import torch.distributed as dist
 
 
+def partition_layers(costs, stages: int, first_extra: float = 0.0, last_extra: float = 0.0) -> list[tuple[int, int]]:
+    """Min-max contiguous partition of ``costs`` into ``stages`` non-empty ranges (dynamic program
+    over prefix sums; ties keep the earlier cut, so every rank derives the same split). Reference:
+    areal/engine/megatron_utils/pipeline_parallel.py:17-160."""
+    n = len(costs)
+    if stages > n:
+        raise ValueError(f"{stages} pipeline stages need at least as many layers (got {n})")
+    pre = [0.0]
+    for c in costs:
+        pre.append(pre[-1] + float(c))
+
+    def seg(a, b, k):  # cost of layers [a, b) as stage k
+        return pre[b] - pre[a] + (first_extra if k == 0 else 0.0) + (last_extra if k == stages - 1 else 0.0)
+
+    inf = float("inf")
+    best = [[inf] * (n + 1) for _ in range(stages + 1)]  # best[k][b]: first k stages cover [0, b)
+    cut = [[0] * (n + 1) for _ in range(stages + 1)]
+    best[0][0] = 0.0
+    for k in range(1, stages + 1):
+        for b in range(k, n - (stages - k) + 1):
+            for a in range(k - 1, b):
+                if best[k - 1][a] == inf:
+                    continue
+                v = max(best[k - 1][a], seg(a, b, k - 1))
+                if v < best[k][b] - 1e-12:
+                    best[k][b], cut[k][b] = v, a
+    out, b = [], n
+    for k in range(stages, 0, -1):
+        a = cut[k][b]
+        out.append((a, b))
+        b = a
+    return out[::-1]
+
+
 @dataclass
 class ParallelContext:
     tp_group: Any = None
@@ -34,11 +68,12 @@ class ParallelContext:
     pp_next: int | None = None
     pp_tie_group: Any = None     # first + last stage (tied embedding / LM-head gradients)
 
-    def layer_range(self, num_layers: int) -> tuple[int, int]:
-        """Contiguous, near-even split of the transformer blocks over the pipeline stages."""
-        base, extra = divmod(num_layers, self.pp_size)
-        start = self.pp_rank * base + min(self.pp_rank, extra)
-        return start, start + base + (1 if self.pp_rank < extra else 0)
+    def layer_range(self, num_layers: int, layer_costs=None, first_extra: float = 0.0,
+                    last_extra: float = 0.0) -> tuple[int, int]:
+        """This stage's contiguous block range: the split that minimises the most expensive stage,
+        where the first stage also pays ``first_extra`` (embedding) and the last ``last_extra``
+        (final norm, LM head and loss), in the units of ``layer_costs`` (default: one per block)."""
+        return partition_layers(layer_costs or [1.0] * num_layers, self.pp_size, first_extra, last_extra)[self.pp_rank]
 
     @property
     def is_first_stage(self) -> bool:

@@ -71,3 +71,24 @@ def test_allocate_divisor_and_min_groups():
     assert len(groups) % 2 == 0 and len(groups) >= 5
     groups = seqpack.allocate(sizes, None, min_groups=4, algorithm="kk")
     assert len(groups) == 4
+
+
+def test_pipeline_layer_partition_minimises_the_slowest_stage():
+    import itertools
+
+    from areal_b200.parallel.context import partition_layers
+
+    def cost(ranges, costs, fe, le):
+        return max(sum(costs[a:b]) + (fe if i == 0 else 0) + (le if i == len(ranges) - 1 else 0)
+                   for i, (a, b) in enumerate(ranges))
+
+    for costs, k, fe, le in [([1.0] * 28, 4, 0.0, 6.2), ([1, 1, 4, 1, 1, 1], 3, 0.0, 0.0), ([1.0] * 7, 3, 0.5, 2.0),
+                             ([1.0] * 2, 2, 0.0, 0.4)]:
+        got = partition_layers(costs, k, fe, le)
+        assert got[0][0] == 0 and got[-1][1] == len(costs) and all(a < b for a, b in got)
+        assert all(got[i][1] == got[i + 1][0] for i in range(k - 1))
+        best = min(cost(list(zip((0,) + cuts, cuts + (len(costs),))), costs, fe, le)
+                   for cuts in itertools.combinations(range(1, len(costs)), k - 1))
+        assert abs(cost(got, costs, fe, le) - best) < 1e-9
+    with pytest.raises(ValueError):
+        partition_layers([1.0, 1.0], 3)
