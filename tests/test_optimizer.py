@@ -17,7 +17,7 @@ class _Toy(torch.nn.Module):
 
 def _run(kind, device, dtype, steps=20, lr=1e-2, wd=0.1, clip=0.0):
     m = _Toy(dtype, device)
-    ref = [p.detach().float().clone().requires_grad_(True) for p in (m.a, m.b)]
+    ref = [p.detach().float().cpu().clone().requires_grad_(True) for p in (m.a, m.b)]
     cfg = OptimizerConfig(type=kind, lr=lr, weight_decay=wd, warmup_steps_proportion=0.0, gradient_clipping=clip)
     flat = FlatParams(m, "local")
     opt = ShardedAdamW(flat, cfg, total_steps=steps)

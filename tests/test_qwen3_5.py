@@ -211,7 +211,9 @@ def test_hybrid_model_cuda_matches_fp32_reference():
         (-logp_r.mean()).backward()
     finally:
         del os.environ["AREAL_B200_FORCE_TORCH"]
-    assert float((h.float() - hr).abs().max()) < 0.25 and float((h_ng.float() - hr).abs().max()) < 0.25
+    hr = hr.detach()
+    for got in (h.detach().float(), h_ng.float()):  # bf16 through 4 blocks: error relative to the activations' norm
+        assert float((got - hr).norm() / hr.norm()) < 0.03
     torch.testing.assert_close(logp, logp_r, atol=0.15, rtol=0.05)
     gm = dict(m.named_parameters())
     for name, pr in ref.named_parameters():
