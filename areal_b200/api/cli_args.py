@@ -255,6 +255,9 @@ class MegatronEngineConfig:
     moe_token_dispatcher_type: str = "alltoall"
     moe_permute_fusion: bool = False
     fp8_config: FP8EngineConfig | None = None
+    # context parallelism of the Megatron-style engine: "allgather" / "p2p" = zig-zag chunks with gathered K/V,
+    # "a2a" = Ulysses head exchange (what the FSDP-style engine always uses)
+    cp_comm_type: str = "allgather"
     use_sequence_parallel: bool = True
     bridge_type: str = "native"
 

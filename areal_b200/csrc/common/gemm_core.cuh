@@ -77,6 +77,15 @@ template <class E> __device__ __forceinline__ int epi_k_begin(const E&, int, lon
 template <class E> __device__ __forceinline__ auto epi_k_blocks(const E& e, int m, int dflt, int) -> decltype(e.k_blocks(m)) { return e.k_blocks(m); }
 template <class E> __device__ __forceinline__ int epi_k_blocks(const E&, int, int dflt, long) { return dflt; }
 
+// k_load(m_blk, kb, ax, ay, bx, abort, status): per-K-block hook of the TMA producer. It may remap the
+// K block (operand coordinates ax/ay for A, bx for B; K-major operands only) and wait, bounded, until
+// the block's source has arrived; returning false aborts the kernel.
+template <class E> __device__ __forceinline__ auto epi_k_load(const E& e, int m, int kb, int& ax, int& ay, int& bx,
+                                                              volatile int* ab, int* st, int)
+    -> decltype(e.k_load(m, kb, ax, ay, bx, ab, st)) { return e.k_load(m, kb, ax, ay, bx, ab, st); }
+template <class E> __device__ __forceinline__ bool epi_k_load(const E&, int, int, int&, int&, int&, volatile int*, int*,
+                                                              long) { return true; }
+
 template <int BN, bool A_MN, bool B_MN, class Epi>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
@@ -144,6 +153,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
         const int a_m0 = epi_a_m0(epi, m_blk, 0);
         const int b_off = epi_b_offset(epi, m_blk, 0);
         for (int kb = 0; kb < kbn; ++kb) {
+          int ax = k0 + kb * kBK, ay = a_m0, bx = k0 + kb * kBK;
+          if (!epi_k_load(epi, m_blk, kb, ax, ay, bx, abort_flag, status, 0)) {
+            ok = false;
+            break;
+          }
           if (!mbar_wait(&empty[stage], phase ^ 1, abort_flag)) {
             ok = false;
             break;
@@ -156,14 +170,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_consta
             for (int j = 0; j < kBM / 64; ++j)
               tma_load_2d(a_dst + j * 8192, &tmA, &full[stage], a_m0 + j * 64, k0 + kb * kBK);
           } else {
-            tma_load_2d(a_dst, &tmA, &full[stage], k0 + kb * kBK, a_m0);
+            tma_load_2d(a_dst, &tmA, &full[stage], ax, ay);
           }
           if (B_MN) {
 #pragma unroll
             for (int j = 0; j < BN / 64; ++j)
               tma_load_2d(b_dst + j * 8192, &tmB, &full[stage], n_blk * BN + j * 64, k0 + kb * kBK + b_off);
           } else {
-            tma_load_2d(b_dst, &tmB, &full[stage], k0 + kb * kBK, n_blk * BN + b_off);
+            tma_load_2d(b_dst, &tmB, &full[stage], bx, n_blk * BN + b_off);
           }
           if (++stage == STAGES) {
             stage = 0;

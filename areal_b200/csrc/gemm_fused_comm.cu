@@ -350,6 +350,101 @@ struct GatedStoreEpi {
   }
 };
 
+// all-to-all → GEMM: the reduction dimension is split by source rank. Operand A lives in the local
+// gather buffer as `world` chunks [rows, 64 * kb_per_chunk] (chunk s pushed by rank s, this rank's own
+// chunk copied locally); K blocks are visited own chunk first, then the peers in ring order, and the
+// producer waits (bounded) for a chunk's flag before its first block is loaded.
+struct KChunkGatedEpi {
+  __nv_bfloat16* C;
+  long long ldc;
+  int M, N;
+  const uint32_t* flags;  // local, [world]
+  uint32_t epoch;
+  int rank, world;
+  int kb_per_chunk;
+  int rows;  // rows of one chunk in the gather buffer
+  struct State {};
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m, int tiles_n, int& m_blk,
+                                       int& n_blk) const {
+    return default_tile(cta, ncta, it, tiles_m, tiles_n, m_blk, n_blk);
+  }
+  __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ bool k_load(int m_blk, int kb, int& ax, int& ay, int& bx, volatile int* abort_flag,
+                                         int* status) const {
+    const int total = kb_per_chunk * world;
+    int kbp = kb + rank * kb_per_chunk;
+    if (kbp >= total) kbp -= total;
+    const int src = kbp / kb_per_chunk;
+    const int kk = kbp - src * kb_per_chunk;
+    if (src != rank && kk == 0) {
+      const uint32_t* f = flags + src;
+      if (static_cast<int32_t>(ld_acquire_sys_u32(f) - epoch) < 0) {
+        const unsigned long long t0 = globaltimer_ns();
+        uint32_t spins = 0;
+        while (static_cast<int32_t>(ld_acquire_sys_u32(f) - epoch) < 0) {
+          if ((++spins & 0xff) == 0) {
+            if (*abort_flag) return false;
+            if (globaltimer_ns() - t0 > kWaitDeadlineNs) {
+              atomicCAS(status, 0, kErrPeerFlagTimeout);
+              return false;
+            }
+          }
+        }
+      }
+      asm volatile("fence.proxy.async;" ::: "memory");  // TMA reads of the chunk come after the acquire
+    }
+    ax = kk * kBK;
+    ay = src * rows + m_blk * kBM;
+    bx = kbp * kBK;
+    return true;
+  }
+  __device__ __forceinline__ void begin(State&, int, int, int) const {}
+  __device__ __forceinline__ void end(State&, int, int, int) const {}
+  __device__ __forceinline__ void chunk(State&, int row, int col0, const float (&v)[32]) const {
+    if (row >= M || col0 >= N) return;
+    __nv_bfloat16* out = C + static_cast<long long>(row) * ldc + col0;
+    if (col0 + 32 <= N && (ldc & 7) == 0) {
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        uint4 pk;
+        __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&pk);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) pb[j] = __floats2bfloat162_rn(v[8 * i + 2 * j], v[8 * i + 2 * j + 1]);
+        reinterpret_cast<uint4*>(out)[i] = pk;
+      }
+    } else {
+      for (int i = 0; i < 32 && col0 + i < N; ++i) out[i] = __float2bfloat16(v[i]);
+    }
+  }
+};
+
+// All-to-all push: row block d (rows [d * rows, (d+1) * rows) of src [world * rows, row16 * 16 bytes]) goes
+// to rank d's gather buffer at chunk slot `rank`; flag[rank] on rank d is raised as soon as ITS block has
+// landed (one completion counter per destination). Destinations are served in the order in which their
+// GEMMs will ask for this rank's chunk: d = rank-1 first (its K loop visits rank-1, rank, ...: this
+// rank's chunk right after its own), then rank-2, and so on.
+__global__ void push_a2a_kernel(PeerPtrs bufs, PeerPtrs flags, int world, int rank, const uint4* __restrict__ src,
+                                long long block16, uint32_t epoch, unsigned int* done_counters) {
+  for (int step = 1; step < world; ++step) {
+    const int d = (rank - step + world) % world;
+    const uint4* s = src + static_cast<long long>(d) * block16;
+    uint4* dst = reinterpret_cast<uint4*>(bufs.p[d]) + static_cast<long long>(rank) * block16;
+    for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < block16;
+         i += static_cast<long long>(gridDim.x) * blockDim.x)
+      dst[i] = s[i];
+    __threadfence_system();
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      const unsigned int prev = atomicAdd(done_counters + d, 1u);
+      if (prev == gridDim.x - 1) {
+        done_counters[d] = 0;
+        __threadfence_system();
+        st_release_sys_u32(reinterpret_cast<uint32_t*>(flags.p[d]) + rank, epoch);
+      }
+    }
+  }
+}
+
 // Copies this rank's rows into every peer's gather buffer (at row offset rank * rows) and
 // then raises flag[rank] = epoch on every peer. One launch; the last block to finish signals.
 __global__ void push_chunks_kernel(PeerPtrs bufs, PeerPtrs flags, int world, int rank,
@@ -376,11 +471,13 @@ __global__ void push_chunks_kernel(PeerPtrs bufs, PeerPtrs flags, int world, int
 
 template <class Epi>
 static int launch_fused(const void* A, const void* B, int M, int N, int K, long long lda, long long ldb,
-                        const Epi& epi, cudaStream_t stream) {
+                        const Epi& epi, cudaStream_t stream, int a_rows = -1, int a_cols = -1) {
   constexpr int BN = 256;
   using Cfg = GemmCfg<BN>;
   CUtensorMap tmA, tmB;
-  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, M, K, lda * 2, kBM, 64);
+  // a_rows / a_cols: shape of operand A in memory when it differs from the logical [M, K] (K-chunked A)
+  int rc = make_tmap_2d(&tmA, A, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, a_rows < 0 ? M : a_rows,
+                        a_cols < 0 ? K : a_cols, lda * 2, kBM, 64);
   if (rc) return rc;
   rc = make_tmap_2d(&tmB, B, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K, ldb * 2, BN, 64);
   if (rc) return rc;
@@ -466,6 +563,38 @@ int b200_gemm_gated(const void* A, const void* B, void* C, const void* flags, un
   GatedStoreEpi epi{reinterpret_cast<__nv_bfloat16*>(C), ldc, M, N, reinterpret_cast<const uint32_t*>(flags),
                     epoch, rank, world, M / world / kBM};
   return launch_fused(A, B, M, N, K, lda, ldb, epi, stream);
+}
+
+// All-to-all push for b200_gemm_kchunk_gated: src [world * rows, cols] bf16 row-major (block_bytes =
+// rows * cols * 2 per destination, a multiple of 16). done_counters: `world` zero-initialised uint32.
+int b200_push_a2a(void* const* peer_bufs, void* const* peer_flags, int world, int rank, const void* src,
+                  long long block_bytes, unsigned epoch, void* done_counters, cudaStream_t stream) {
+  using namespace b200;
+  if (world < 1 || world > kMaxPeers) return -100;
+  if (block_bytes & 15) return -101;
+  if (world == 1) return 0;
+  PeerPtrs b, f;
+  for (int i = 0; i < world; ++i) { b.p[i] = peer_bufs[i]; f.p[i] = peer_flags[i]; }
+  long long g = (block_bytes / 16 + 255) / 256;
+  if (g > 64) g = 64;
+  if (g < 1) g = 1;
+  push_a2a_kernel<<<(unsigned)g, 256, 0, stream>>>(b, f, world, rank, (const uint4*)src, block_bytes / 16, epoch,
+                                                   reinterpret_cast<unsigned int*>(done_counters));
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// C[M,N] = sum_s A_s[M,Kc] * B[:, s*Kc:(s+1)*Kc]^T where A_s is chunk s of the local gather buffer
+// ([world, M, Kc] bf16, filled by b200_push_a2a and a local copy of this rank's own chunk).
+// Kc must be a multiple of 64; flags: local uint32 [world].
+int b200_gemm_kchunk_gated(const void* A, const void* B, void* C, const void* flags, unsigned epoch, int world,
+                           int rank, int M, int N, int Kc, long long ldb, long long ldc, cudaStream_t stream) {
+  using namespace b200;
+  if (world < 1 || world > kMaxPeers) return -100;
+  if (Kc % kBK) return -101;
+  KChunkGatedEpi epi{reinterpret_cast<__nv_bfloat16*>(C), ldc, M, N, reinterpret_cast<const uint32_t*>(flags),
+                     epoch, rank, world, Kc / kBK, M};
+  return launch_fused(A, B, M, N, Kc * world, Kc, ldb, epi, stream, world * M, Kc);
 }
 
 // Single-kernel GEMM → reduce-scatter: out[M/world, N] = rows of sum_ranks(A_r B_r^T) owned by this rank

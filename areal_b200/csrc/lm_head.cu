@@ -23,6 +23,11 @@ namespace b200 {
 
 struct LmStatsEpi {
   float* partials;          // [nsplit, T, 4] : m, l, sx, target
+  // vocab-parallel: the records go straight into every tensor-parallel peer's buffer
+  // ([n_peers * nsplit, T, 4], this rank's records at slot_base) instead of `partials`
+  float* peers[8];
+  int n_peers;
+  int slot_base;
   const int* labels;        // [T] global vocab ids
   int T, N;                 // rows, local vocab size
   int vocab_start;          // global id of local column 0
@@ -82,8 +87,13 @@ struct LmStatsEpi {
   __device__ __forceinline__ void end(State& s, int, int n_blk, int row) const {
     if ((n_blk + 1) % nb_per == 0 && row < T) {
       const int split = n_blk / nb_per;
-      float4* dst = reinterpret_cast<float4*>(partials) + static_cast<long long>(split) * T + row;
-      *dst = make_float4(s.m, s.l, s.sx, s.t);
+      const float4 rec = make_float4(s.m, s.l, s.sx, s.t);
+      if (n_peers == 0) {
+        reinterpret_cast<float4*>(partials)[static_cast<long long>(split) * T + row] = rec;
+      } else {
+        const long long at = static_cast<long long>(slot_base + split) * T + row;
+        for (int p = 0; p < n_peers; ++p) reinterpret_cast<float4*>(peers[p])[at] = rec;
+      }
     }
   }
 };
@@ -223,9 +233,28 @@ int b200_lm_head_stats(const void* X, const void* W, const int* labels, float* p
   const int tiles_n = (V + 255) / 256;
   const int nsplit = b200_lm_head_nsplit(T, V);
   const int nb_per = (tiles_n + nsplit - 1) / nsplit;
-  LmStatsEpi epi{partials, labels, T, V, vocab_start, nb_per, nsplit, inv_temp};
+  LmStatsEpi epi{partials, {}, 0, 0, labels, T, V, vocab_start, nb_per, nsplit, inv_temp};
   return launch_lm(X, W, T, V, H, ldx, ldw, epi, static_cast<long long>(tiles_m) * nsplit,
                    stream);
+}
+
+// Vocab-parallel form: the epilogue stores this rank's records into every peer's buffer
+// (peer_partials[p]: fp32 [n_peers * nsplit, T, 4] on rank p, this rank's slots starting at
+// rank * nsplit), so the all-gather of the softmax statistics happens inside the GEMM kernel. A barrier
+// among the ranks must separate this launch from b200_lm_head_combine over the local buffer.
+int b200_lm_head_stats_peers(const void* X, const void* W, const int* labels, void* const* peer_partials,
+                             int n_peers, int rank, int T, int V, int H, long long ldx, long long ldw,
+                             int vocab_start, float inv_temp, cudaStream_t stream) {
+  using namespace b200;
+  if (n_peers < 1 || n_peers > 8) return -100;
+  if (T == 0 || V == 0) return 0;
+  const int tiles_m = (T + 127) / 128;
+  const int tiles_n = (V + 255) / 256;
+  const int nsplit = b200_lm_head_nsplit(T, V);
+  const int nb_per = (tiles_n + nsplit - 1) / nsplit;
+  LmStatsEpi epi{nullptr, {}, n_peers, rank * nsplit, labels, T, V, vocab_start, nb_per, nsplit, inv_temp};
+  for (int p = 0; p < n_peers; ++p) epi.peers[p] = reinterpret_cast<float*>(peer_partials[p]);
+  return launch_lm(X, W, T, V, H, ldx, ldw, epi, static_cast<long long>(tiles_m) * nsplit, stream);
 }
 
 int b200_lm_head_combine(const float* partials, int nparts, int T, float* logp, float* entropy,

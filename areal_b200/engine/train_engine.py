@@ -130,6 +130,9 @@ class B200TrainEngine(TrainEngine):
             # context_parallel_size is Ulysses sequence parallelism for this engine family
             self.mesh = build_mesh(ranks, dp=dp, sp=ps.cp_size, tp=ps.tp_size, pp=ps.pp_size, ep=ps.ep_size)
             self.pctx = self.mesh.ctx
+            if ps.cp_size > 1 and self.config.backend.split(":")[0] == "megatron" and \
+                    getattr(self.config.megatron, "cp_comm_type", "a2a") in ("allgather", "p2p"):
+                self.pctx.extras["cp_mode"] = "zigzag"
             # parameters are sharded (ZeRO) over dp x sp: those ranks hold the same weights
             self._dp_group = self.mesh.shard_group
             self._cpu_group = self.mesh.cpu_shard_group
@@ -388,6 +391,8 @@ class B200TrainEngine(TrainEngine):
         from ..parallel.tensor_parallel import gather_seq_replicated
 
         pctx = self.pctx
+        if pctx.extras.get("cp_mode") == "zigzag" and pctx.sp_size > 1:
+            return self._forward_mb_zigzag(mb, meta, stage_input)
         ids, pos = mb["input_ids"], mb["position_ids"]
         T = ids.shape[0]
         align = pctx.seq_shards * (128 if ids.is_cuda else 1)
@@ -414,11 +419,44 @@ class B200TrainEngine(TrainEngine):
             vloc = self.model.output_weight().shape[0]
             out, ent = lm_head_logprobs(hidden, self.model.output_weight(), labels[sl], self.config.temperature,
                                         tp_group=pctx.tp_group if tp > 1 else None,
-                                        vocab_start=pctx.tp_rank * vloc if tp > 1 else 0)
+                                        vocab_start=pctx.tp_rank * vloc if tp > 1 else 0,
+                                        tp_fused=pctx.tp_fused if tp > 1 else None)
         if S > 1:
             out = gather_seq_replicated(out, pctx.sp_fused)
             ent = gather_seq_replicated(ent, pctx.sp_fused) if ent is not None else None
         return out[:T], (ent[:T] if ent is not None else None)
+
+    def _forward_mb_zigzag(self, mb: dict[str, Any], meta: VarlenMeta, stage_input=None):
+        """Context-parallel forward with zig-zag chunks: every sequence is padded to a multiple of
+        ``2 * cp * 128`` tokens and cut into ``2 * cp`` chunks, rank ``r`` holds chunks ``r`` and
+        ``2cp - 1 - r`` (balanced causal work); attention gathers K/V over the group, everything else
+        is token-local. Unlike the head exchange this does not limit ``cp`` by the number of kv heads.
+        Outputs are gathered back and un-padded, so the loss sees the micro-batch in packed order.
+        Reference: areal/engine/megatron_utils/packed_context_parallel.py:14-185."""
+        from ..parallel.context_parallel import CPLayout, cp_attention
+        from ..parallel.tensor_parallel import gather_seq_replicated
+
+        pctx = self.pctx
+        assert pctx.tp_size == 1 and pctx.pp_size == 1, "zig-zag context parallelism combines with data parallelism"
+        ids, pos = mb["input_ids"], mb["position_ids"]
+        cu = meta.cu_cpu.tolist()
+        seqlens = [b - a for a, b in zip(cu[:-1], cu[1:])]
+        lay = CPLayout(seqlens, pctx.sp_size, pctx.sp_rank, device=ids.device)
+        labels = torch.roll(ids, shifts=-1, dims=0)
+        ids_l, pos_l, lab_l = (lay.split(lay.pad_packed(t)) for t in (ids, pos, labels))
+        hidden = self.model(ids_l, pos_l, meta,
+                            attn_fn=lambda q, k, v, _m: cp_attention(q, k, v, lay, pctx.sp_group))
+        if self.is_critic:
+            out, ent = self.model.values(hidden), None
+        else:
+            out, ent = lm_head_logprobs(hidden, self.model.output_weight(), lab_l, self.config.temperature)
+        keep = torch.cat([torch.arange(int(lay.full_cu[s]), int(lay.full_cu[s]) + L) for s, L in enumerate(seqlens)])
+        index = lay.gather_to_seq.to(out.device)[keep.to(out.device)]  # packed token -> row of the rank-major gather
+
+        def back(t):
+            return gather_seq_replicated(t, pctx.sp_fused).index_select(0, index)
+
+        return back(out), (back(ent) if ent is not None else None)
 
     # ---------------------------------------------------------------- pipeline
     def _stage_shapes(self, T: int):

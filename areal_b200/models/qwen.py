@@ -83,11 +83,13 @@ class Attention(nn.Module):
         return fused.qknorm_rope(qkv, self.q_norm, self.k_norm, cos, sin, pos,
                                  self.n_q, self.n_kv, cfg.head_dim, cfg.rms_norm_eps)
 
-    def _fused_ulysses(self, x, cos, sin, pos, meta):
+    def _fused_ulysses(self, x, cos, sin, pos, meta, attn_fn=None):
         """Ulysses with the projection and the sequence→head exchange fused into one kernel: the
         q/k norms and RoPE then run after the exchange, on this rank's heads of ALL tokens."""
         p = self.pctx
-        if (p is None or p.sp_size == 1 or p.tp_size > 1 or self.qkv_bias is not None or p.sp_fused is None
+        external = attn_fn is not None and not getattr(attn_fn, "is_ulysses", False)  # tree / zig-zag attention
+        if (external or p is None or p.sp_size == 1 or p.tp_size > 1 or self.qkv_bias is not None
+                or p.sp_fused is None or p.extras.get("cp_mode") == "zigzag"
                 or "full_positions" not in p.extras or self.lora_qkv is not None):
             return None
         from ..parallel.ulysses import fused_qkv_seq_to_head, head_to_seq
@@ -99,16 +101,28 @@ class Attention(nn.Module):
         S = p.sp_size
         q, k, v = fused.qknorm_rope(qkv, self.q_norm, self.k_norm, cos, sin, p.extras["full_positions"],
                                     self.n_q // S, self.n_kv // S, cfg.head_dim, cfg.rms_norm_eps)
-        return head_to_seq(varlen_attention(q, k, v, meta), p)
+        a = varlen_attention(q, k, v, meta)
+        if not cfg.fp8 and self.lora_o is None:
+            from ..parallel.ulysses import fused_head_to_seq_proj
+
+            # the head→sequence exchange fused into the output projection (K loop split by source rank)
+            y = fused_head_to_seq_proj(a.reshape(a.shape[0], -1), self.o, p)
+            if y is not None:
+                return y, True
+        return head_to_seq(a, p), False
 
     def forward(self, x, cos, sin, pos, meta: VarlenMeta, attn_fn=None):
         """``pos`` are the positions of the tokens that reach the q/k projection output: all
         tokens of this sequence-parallel shard (tensor parallelism gathers its token shards
         inside the projection)."""
-        a = self._fused_ulysses(x, cos, sin, pos, meta)
-        if a is None:
+        fused_out = self._fused_ulysses(x, cos, sin, pos, meta, attn_fn)
+        if fused_out is not None and fused_out[1]:
+            return fused_out[0]  # the output projection ran inside the fused exchange
+        if fused_out is None:
             q, k, v = self.project_qkv(x, cos, sin, pos)
             a = (attn_fn or varlen_attention)(q, k, v, meta)
+        else:
+            a = fused_out[0]
         a = a.reshape(a.shape[0], -1)
         tp = self._tp()
         if tp is not None:

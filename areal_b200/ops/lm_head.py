@@ -64,7 +64,7 @@ class _AllReduceSum(torch.autograd.Function):
 
 class _LMHead(torch.autograd.Function):
     @staticmethod
-    def forward(ctx, x, w, labels, temperature, tp_group, vocab_start):
+    def forward(ctx, x, w, labels, temperature, tp_group, vocab_start, tp_fused=None):
         T, H = x.shape
         V = w.shape[0]
         x = x if x.is_contiguous() else x.contiguous()
@@ -74,6 +74,25 @@ class _LMHead(torch.autograd.Function):
         nsplit = lib.b200_lm_head_nsplit(ctypes.c_int(T), ctypes.c_int(V))
         partials = torch.empty((nsplit, T, 4), dtype=torch.float32, device=x.device)
         inv_t = 1.0 / float(temperature)
+        tp = dist.get_world_size(tp_group) if tp_group is not None else 1
+        if tp > 1 and tp_fused is not None and getattr(tp_fused, "cuda", False):
+            # vocab-parallel, fused: the GEMM epilogue stores every row's (max, sum-exp, sum x·exp, target)
+            # record into all tp peers' buffers over NVLink, so the exchange of the softmax statistics is
+            # part of the kernel; one device-side barrier later every rank combines its local copy.
+            # Buffers alternate between calls: a rank can only be one barrier ahead of the slowest, so
+            # the copy being combined is never overwritten.
+            bufs, tables, calls = _peer_partials(tp_fused, tp * nsplit * T * 16)
+            h = calls & 1
+            rc = lib.b200_lm_head_stats_peers(_lib.ptr(x), _lib.ptr(w), _lib.ptr(labels), tables[h], ctypes.c_int(tp),
+                                              ctypes.c_int(tp_fused.rank), ctypes.c_int(T), ctypes.c_int(V),
+                                              ctypes.c_int(H), ctypes.c_longlong(x.stride(0)),
+                                              ctypes.c_longlong(w.stride(0)), ctypes.c_int(vocab_start),
+                                              ctypes.c_float(inv_t), _lib.stream_ptr())
+            _lib.check(rc, "b200_lm_head_stats_peers")
+            tp_fused.barrier.sync()
+            half = bufs.nbytes // 2
+            partials = bufs.tensor(torch.float32, tp * nsplit * T * 4, byte_offset=h * half).view(tp * nsplit, T, 4)
+            return _LMHead._finish(ctx, lib, partials, tp * nsplit, x, w, labels, inv_t, tp_group, vocab_start)
         lib.b200_lm_head_stats.restype = ctypes.c_int
         rc = lib.b200_lm_head_stats(_lib.ptr(x), _lib.ptr(w), _lib.ptr(labels), _lib.ptr(partials),
                                     ctypes.c_int(T), ctypes.c_int(V), ctypes.c_int(H),
@@ -81,7 +100,6 @@ class _LMHead(torch.autograd.Function):
                                     ctypes.c_int(vocab_start), ctypes.c_float(inv_t),
                                     _lib.stream_ptr())
         _lib.check(rc, "b200_lm_head_stats")
-        tp = dist.get_world_size(tp_group) if tp_group is not None else 1
         if tp > 1:
             # ranks may pick different split counts only if their shard sizes differ; pad to max
             ns = torch.tensor([nsplit], device=x.device)
@@ -96,6 +114,11 @@ class _LMHead(torch.autograd.Function):
             partials, nparts = gathered, tp * nmax
         else:
             nparts = nsplit
+        return _LMHead._finish(ctx, lib, partials, nparts, x, w, labels, inv_t, tp_group, vocab_start)
+
+    @staticmethod
+    def _finish(ctx, lib, partials, nparts, x, w, labels, inv_t, tp_group, vocab_start):
+        T = x.shape[0]
         logp = torch.empty(T, dtype=torch.float32, device=x.device)
         ent = torch.empty_like(logp)
         logz = torch.empty_like(logp)
@@ -155,15 +178,39 @@ class _LMHead(torch.autograd.Function):
         dw = None
         if need_dw and main is None:
             dw = dw_acc.to(w.dtype)
-        return dx, dw, None, None, None, None
+        return dx, dw, None, None, None, None, None
 
 
-def lm_head_logprobs(x, w, labels, temperature: float = 1.0, tp_group=None, vocab_start: int = 0):
+def _peer_partials(fctx, nbytes: int):
+    """Two symmetric buffers (one allocation, halves alternate per call) for the vocab-parallel
+    statistics, sized on first use and grown collectively when a larger micro-batch arrives (every
+    rank of the group sees the same shapes, so every rank reallocates at the same call)."""
+    from ..parallel.symm_mem import SymmBuffer
+
+    st = getattr(fctx, "_lm_partials", None)
+    need = (nbytes + 255) // 256 * 256
+    if st is None or st[0].nbytes < 2 * need:
+        if st is not None:
+            fctx.barrier.sync()
+            torch.cuda.synchronize(fctx.device)
+            st[0].close()
+        size = 2 * max(need, 1 << 20)
+        buf = SymmBuffer(size, fctx.group, fctx.device)
+        st = [buf, [buf.ptr_table(byte_offset=h * (size // 2)) for h in range(2)], 0]
+        fctx._lm_partials = st
+    calls = st[2]
+    st[2] += 1
+    return st[0], st[1], calls
+
+
+def lm_head_logprobs(x, w, labels, temperature: float = 1.0, tp_group=None, vocab_start: int = 0, tp_fused=None):
     """Per-token log-probability of ``labels`` and entropy of the next-token
     distribution ``softmax(x @ w.T / temperature)``. ``w`` may be this rank's
     vocabulary shard starting at global id ``vocab_start``; the gradient with respect to ``x``
     is then this shard's partial contribution, to be summed over ``tp_group`` by the caller
-    (``parallel.tensor_parallel.gather_seq`` does so in its backward)."""
+    (``parallel.tensor_parallel.gather_seq`` does so in its backward). With ``tp_fused`` (the tp group's
+    ``FusedCommContext``) the statistics are exchanged by peer stores from the GEMM epilogue instead
+    of an NCCL all-gather."""
     if _lib.use_cuda_kernels(x, w) and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0:
-        return _LMHead.apply(x, w, labels, temperature, tp_group, vocab_start)
+        return _LMHead.apply(x, w, labels, temperature, tp_group, vocab_start, tp_fused)
     return lm_head_logprobs_ref(x, w, labels, temperature, tp_group, vocab_start)

@@ -116,6 +116,27 @@ def gemm_all_to_all_ref(x, w, group):
     return torch.cat(recv, 0)
 
 
+def all_to_all_gemm_ref(a, w, group):
+    """Ulysses output projection: ``a [P*M, Kc]`` (all tokens, this rank's heads), ``w [N, P*Kc]`` →
+    ``[M, N]`` for this rank's tokens: the head→sequence exchange followed by the projection."""
+    world = dist.get_world_size(group) if dist.is_initialized() else 1
+    if world == 1:
+        return (a.float() @ w.float().t()).to(a.dtype)
+    M = a.shape[0] // world
+    send = a.contiguous().view(world, M, a.shape[1])
+    recv = torch.empty_like(send)
+    if a.is_cuda:
+        dist.all_to_all_single(recv, send, group=group)
+    else:
+        rank = dist.get_rank(group)
+        for r in range(world):
+            dst = list(recv.unbind(0)) if rank == r else None
+            dist.gather(send[r].contiguous(), dst, dst=dist.get_global_rank(group, r) if group is not None else r,
+                        group=group)
+    full = recv.permute(1, 0, 2).reshape(M, -1)  # columns in source-rank order = head order
+    return (full.float() @ w.float().t()).to(a.dtype)
+
+
 # --------------------------------------------------------------------------- fused (CUDA)
 
 
@@ -236,3 +257,47 @@ def gemm_all_to_all(ctx: FusedCommContext, x: torch.Tensor, w: torch.Tensor):
     ctx.barrier.sync()
     _lib.count_launch()
     return ctx.stage.tensor(x.dtype, P * M * (N // P)).view(P * M, N // P).clone()
+
+
+def all_to_all_gemm(ctx: FusedCommContext, a: torch.Tensor, w: torch.Tensor, return_chunks: bool = False):
+    """``head_to_seq(a) @ w.T`` in one GEMM kernel whose reduction dimension is split by source rank:
+    every rank pushes the row block of each destination into that rank's gather buffer (peer stores,
+    one arrival flag per source), and the GEMM's TMA producer starts with the local chunk and waits for
+    a peer's chunk only when its K loop reaches it, so the exchange overlaps the math. With
+    ``return_chunks`` also returns the received operand ``[P, M, Kc]`` (a copy; for the backward)."""
+    P = ctx.world
+    Kc = a.shape[1]
+    M = a.shape[0] // P
+    if not (ctx.cuda and a.is_cuda) or P == 1 or Kc % 64 or a.dtype != torch.bfloat16 or \
+            a.numel() * 2 > ctx.max_stage_bytes:
+        y = all_to_all_gemm_ref(a, w, ctx.group)
+        return (y, None) if return_chunks else y
+    N = w.shape[0]
+    a = a if a.is_contiguous() else a.contiguous()
+    w = w if w.is_contiguous() else w.contiguous()
+    lib = _lib.kernels()
+    epoch = ctx.next_epoch()
+    gather = ctx.gather.tensor(a.dtype, P * M * Kc).view(P, M, Kc)
+    ctx.barrier.sync()  # nobody still reads the gather buffer of the previous call
+    cur = torch.cuda.current_stream()
+    gather[ctx.rank].copy_(a[ctx.rank * M:(ctx.rank + 1) * M])
+    if not hasattr(ctx, "_a2a_done"):
+        ctx._a2a_done = torch.zeros(8, dtype=torch.int32, device=ctx.device)
+    ctx.side_stream.wait_stream(cur)
+    with torch.cuda.stream(ctx.side_stream):
+        rc = lib.b200_push_a2a(ctx._gather_tbl, ctx._flag_tbl, ctypes.c_int(P), ctypes.c_int(ctx.rank), _lib.ptr(a),
+                               ctypes.c_longlong(M * Kc * 2), ctypes.c_uint(epoch), _lib.ptr(ctx._a2a_done),
+                               _lib.stream_ptr())
+        _lib.check(rc, "b200_push_a2a")
+    out = torch.empty((M, N), dtype=a.dtype, device=a.device)
+    rc = lib.b200_gemm_kchunk_gated(ctypes.c_void_p(ctx.gather.local_ptr), _lib.ptr(w), _lib.ptr(out),
+                                    ctypes.c_void_p(ctx.flags.local_ptr), ctypes.c_uint(epoch), ctypes.c_int(P),
+                                    ctypes.c_int(ctx.rank), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(Kc),
+                                    ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(out.stride(0)),
+                                    _lib.stream_ptr())
+    _lib.check(rc, "b200_gemm_kchunk_gated")
+    cur.wait_stream(ctx.side_stream)
+    _lib.count_launch(2)
+    if return_chunks:
+        return out, gather.clone()
+    return out

@@ -151,6 +151,61 @@ def fused_qkv_seq_to_head(x, w, pctx, n_q: int, n_kv: int, head_dim: int):
     return _FusedQKVSeqToHead.apply(x, w, perm, f, pctx.sp_group, S, pctx.sp_rank)
 
 
+class _FusedHeadToSeqProj(torch.autograd.Function):
+    """``head_to_seq(a) @ w.T`` through ``fused_linear.all_to_all_gemm`` (the exchange rides inside the
+    projection's K loop). Backward: ``dA = dy @ w`` for this rank's tokens and all heads, sent back with
+    the reverse exchange (NCCL all-to-all); the weight gradient is one GEMM per received chunk, written
+    into its column block (of ``main_grad`` when present)."""
+
+    @staticmethod
+    def forward(ctx, a, w, fctx, group, world):
+        from . import fused_linear as FL
+
+        y, chunks = FL.all_to_all_gemm(fctx, a, w, return_chunks=True)
+        if chunks is None:  # shapes the kernel does not take: the exchange ran unfused
+            M = a.shape[0] // world
+            send = a.contiguous().view(world, M, a.shape[1])
+            chunks = torch.empty_like(send)
+            dist.all_to_all_single(chunks, send, group=group)
+        ctx.save_for_backward(chunks, w)
+        ctx.args = (group, world)
+        return y
+
+    @staticmethod
+    def backward(ctx, dy):
+        from ..ops.gemm import gemm
+
+        chunks, w = ctx.saved_tensors  # [S, M, Kc]
+        group, world = ctx.args
+        S, M, Kc = chunks.shape
+        dy = dy.contiguous()
+        da = None
+        if ctx.needs_input_grad[0]:
+            g = gemm(dy, w, b_mn=True, out_dtype=dy.dtype)  # [M, S * Kc]: my tokens, every rank's heads
+            send = g.view(M, S, Kc).permute(1, 0, 2).contiguous()
+            recv = torch.empty_like(send)
+            dist.all_to_all_single(recv, send, group=group)
+            da = recv.view(S * M, Kc)
+        dw = None
+        if ctx.needs_input_grad[1]:
+            main = getattr(w, "main_grad", None)
+            acc = main if main is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+            for s_ in range(S):
+                gemm(dy, chunks[s_], a_mn=True, b_mn=True, out=acc[:, s_ * Kc:(s_ + 1) * Kc], accumulate=True)
+            dw = None if main is not None else acc.to(w.dtype)
+        return da, dw, None, None, None
+
+
+def fused_head_to_seq_proj(a, w, pctx):
+    """``a [T_full, heads_local * D]`` → ``[T_full / S, hidden]``; None when the fused kernel does not apply."""
+    f = pctx.sp_fused
+    S = pctx.sp_size
+    if f is None or not f.cuda or not a.is_cuda or a.dtype != torch.bfloat16 or a.shape[0] % S or a.shape[1] % 64 \
+            or a.numel() * 2 > f.max_stage_bytes:
+        return None
+    return _FusedHeadToSeqProj.apply(a, w, f, pctx.sp_group, S)
+
+
 def ulysses_attention(pctx, inner=None):
     """Returns an ``attn_fn(q, k, v, meta)`` for token-sharded inputs: ``meta`` describes the FULL
     packed sequence (all sp ranks' tokens concatenated in rank order)."""
@@ -169,4 +224,5 @@ def ulysses_attention(pctx, inner=None):
         out = inner(qf, kf, vf, meta)
         return head_to_seq(out, pctx)
 
+    attn.is_ulysses = True
     return attn

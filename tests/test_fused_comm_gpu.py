@@ -29,7 +29,8 @@ def test_fused_comm_matches_nccl(tmp_path):
     for k in ("all_gather_err", "all_to_all_err"):
         assert res[k] == 0.0, (k, res[k])
     assert res["reduce_scatter_err"] < 1e-4 and res["all_reduce_err"] < 1e-4
-    for k in ("gemm_rs_err", "ag_gemm_err", "gemm_a2a_err", "gemm_rs_mixed_shapes_err"):
+    assert res["a2a_gemm_repeat_err"] == 0.0
+    for k in ("gemm_rs_err", "ag_gemm_err", "gemm_a2a_err", "gemm_rs_mixed_shapes_err", "a2a_gemm_err"):
         assert res[k] < 2e-2, (k, res[k])
 
 
@@ -51,3 +52,29 @@ def test_bounded_peer_wait_times_out_and_context_survives():
     assert _lib.read_status() == 0  # cleared
     x = torch.ones(1024, device="cuda")
     assert float((x * 2).sum()) == 2048.0
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("rank", [0, 2])
+def test_kchunk_gated_gemm_single_gpu(rank):
+    """The all-to-all → GEMM kernel with four emulated source ranks on one GPU: the gather buffer holds
+    the chunks [world, M, Kc], every flag already carries the epoch, and the K loop starts at chunk
+    `rank`; the result must equal the plain product over the concatenated reduction dimension."""
+    from areal_b200.ops import _lib
+
+    lib = _lib.kernels()
+    world, M, Kc, N = 4, 300, 128, 520
+    torch.manual_seed(rank)
+    chunks = (torch.randn(world, M, Kc, device="cuda") * 0.1).bfloat16()
+    w = (torch.randn(N, world * Kc, device="cuda") * 0.1).bfloat16()
+    flags = torch.full((64,), 7, dtype=torch.int32, device="cuda")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    rc = lib.b200_gemm_kchunk_gated(_lib.ptr(chunks), _lib.ptr(w), _lib.ptr(out), _lib.ptr(flags), ctypes.c_uint(7),
+                                    ctypes.c_int(world), ctypes.c_int(rank), ctypes.c_int(M), ctypes.c_int(N),
+                                    ctypes.c_int(Kc), ctypes.c_longlong(w.stride(0)), ctypes.c_longlong(out.stride(0)),
+                                    _lib.stream_ptr())
+    assert rc == 0
+    torch.cuda.synchronize()
+    assert _lib.read_status() == 0
+    ref = chunks.permute(1, 0, 2).reshape(M, world * Kc).float() @ w.float().t()
+    assert float((out.float() - ref).abs().max() / ref.abs().max()) < 1e-2

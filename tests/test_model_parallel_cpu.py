@@ -33,6 +33,11 @@ def test_lm_step_matches_single_process(tmp_path, n, args):
     _run(n, 29640 + n + len(args), args, _ref(tmp_path))
 
 
+def test_zigzag_context_parallel_matches_single_process(tmp_path):
+    """cp 2 with zig-zag chunks and gathered K/V (sequences padded to 2 * cp * 128 tokens inside)."""
+    _run(2, 29655, ["--sp", "2", "--zigzag"], _ref(tmp_path))
+
+
 def test_critic_step_matches_single_process(tmp_path):
     _run(2, 29651, ["--tp", "2", "--critic"], _ref(tmp_path, critic=True))
 

@@ -23,6 +23,7 @@ def _run(cmd):
 
 @pytest.mark.parametrize("args,preset,n_mbs", [(["--tp", "2"], "tiny-qwen2", 1), (["--sp", "2"], "tiny-qwen2", 1),
                                                (["--sp", "2", "--no-bias"], "tiny-qwen2", 1),
+                                               (["--sp", "2", "--zigzag"], "tiny-qwen2", 1),
                                                (["--pp", "2"], "tiny-qwen2", 2), (["--ep", "2"], "tiny-qwen3-moe", 1)])
 def test_two_gpu_step_matches_one_gpu(tmp_path, args, preset, n_mbs):
     if torch.cuda.device_count() < 2:

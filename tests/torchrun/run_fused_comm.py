@@ -82,6 +82,14 @@ def main(out_path):
     out = FL.gemm_all_to_all(ctx, xl, wq)
     ref = FL.gemm_all_to_all_ref(xl, wq, None)
     res["gemm_a2a_err"] = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
+    # all-to-all → GEMM (Ulysses output projection): a [M, K/world] = all tokens x local heads
+    ah = (torch.randn(M, K // world, device="cuda") * 0.1).bfloat16()
+    wo = (torch.randn(N, K, device="cuda") * 0.1).bfloat16()
+    out = FL.all_to_all_gemm(ctx, ah, wo)
+    ref = FL.all_to_all_gemm_ref(ah, wo, None)
+    res["a2a_gemm_err"] = float((out.float() - ref.float()).abs().max() / ref.float().abs().max())
+    out2, chunks = FL.all_to_all_gemm(ctx, ah, wo, return_chunks=True)
+    res["a2a_gemm_repeat_err"] = float((out2.float() - out.float()).abs().max())
     res["status"] = _lib.read_status()
     # ---- timings: fused vs NCCL + own GEMM
     res["t_gemm_rs_fused_ms"] = timed(lambda: FL.gemm_reduce_scatter(ctx, xs, ws))
@@ -105,6 +113,13 @@ def main(out_path):
         dist.all_to_all_single(recv, send)
         return recv
     res["t_gemm_a2a_nccl_ms"] = timed(unfused_a2a)
+    res["t_a2a_gemm_fused_ms"] = timed(lambda: FL.all_to_all_gemm(ctx, ah, wo))
+    def unfused_a2a_gemm():
+        send = ah.view(world, M // world, K // world)
+        recv = torch.empty_like(send)
+        dist.all_to_all_single(recv, send)
+        return gemm(recv.permute(1, 0, 2).reshape(M // world, K), wo)
+    res["t_a2a_gemm_nccl_ms"] = timed(unfused_a2a_gemm)
     res["shape"] = dict(M=M, K=K, N=N)
     # roofline per op: the slower of the GEMM at the measured cuBLAS peak and the bytes that must cross
     # NVLink at the measured peer-copy bandwidth (per direction per GPU)
@@ -114,6 +129,7 @@ def main(out_path):
         "gemm_rs": max(2.0 * M * N * (K // world) / peak_flops, frac * M * N * 2 / link),
         "ag_gemm": max(2.0 * M * (N // world) * K / peak_flops, frac * M * K * 2 / link),
         "gemm_a2a": max(2.0 * (M // world) * N * K / peak_flops, frac * (M // world) * N * 2 / link),
+        "a2a_gemm": max(2.0 * (M // world) * N * K / peak_flops, frac * M * (K // world) * 2 / link),
     }
     for k, t in roof.items():
         res[f"roofline_{k}_ms"] = t * 1e3

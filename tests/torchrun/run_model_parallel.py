@@ -50,6 +50,8 @@ def main():
     ap.add_argument("--no-bias", action="store_true", help="Qwen3-style attention (no qkv bias): enables the fused Ulysses projection")
     ap.add_argument("--n-mbs", type=int, default=1)
     ap.add_argument("--critic", action="store_true")
+    ap.add_argument("--zigzag", action="store_true", help="context parallelism with zig-zag chunks and gathered K/V "
+                                                          "(the Megatron-style engine's mode) instead of Ulysses")
     args = ap.parse_args()
     cuda = args.device == "cuda"
     tol = 4e-2 if cuda else 2e-4
@@ -67,6 +69,8 @@ def main():
                             model_preset=args.preset, mb_spec=MicroBatchSpec(n_mbs=args.n_mbs), is_critic=args.critic,
                             optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0, gradient_clipping=1.0,
                                                       warmup_steps_proportion=0.0, lr_scheduler_type="constant"))
+    if args.zigzag:
+        cfg.backend = "megatron:d1"
     eng = B200TrainEngine(cfg)
     batch = global_batch(L=512 if cuda else 48)
     if args.ref:
