@@ -457,6 +457,8 @@ class NativeRolloutConfig:
     port: int = 0
     kv_cache_dtype: str = "auto"
     num_kv_blocks: int | None = None
+    # samples of one prompt prefill once and read the same (read-only) prompt pages
+    prompt_sharing: bool = True
 
 
 @dataclass

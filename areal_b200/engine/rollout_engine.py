@@ -286,6 +286,7 @@ class NativeRolloutEngine(InferenceEngine):
             for _ in range(mc.num_hidden_layers)]
         self.sched = PagedScheduler(nblocks, bs, ncfg.max_num_seqs, ncfg.max_num_batched_tokens,
                                     max_blocks_per_seq)
+        self.sched.set_prompt_sharing(bool(getattr(ncfg, "prompt_sharing", True)))
         self._rng = torch.Generator(device=self.device).manual_seed(ncfg.seed)
         self._graphs = None
         self.launches_per_decode = 0

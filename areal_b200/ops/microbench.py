@@ -198,6 +198,38 @@ def bench_elementwise(a):
         gu = torch.randn(T, 2 * I, device="cuda").bfloat16()
         ms = timeit(lambda: fused.swiglu(gu), a.iters)
         report("swiglu_fwd", ms, nbytes=T * I * 2.0 * 3)
+        del gu
+        Hq, Hkv, D = 16, 8, 128
+        qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+        qw, kw = torch.ones(D, device="cuda").bfloat16(), torch.ones(D, device="cuda").bfloat16()
+        cos, sin = fused.rope_tables(4096, D, 1e6, "cuda")
+        pos = (torch.arange(T, device="cuda") % 4096).int()
+        ms = timeit(lambda: fused.qknorm_rope(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, 1e-6), a.iters)
+        report("qknorm_rope_fwd", ms, nbytes=T * (Hq + Hkv) * D * 2.0 * 2)
+
+
+def bench_optimizer(a):
+    """Sharded AdamW update (fp32 master + moments in, new bf16 weights out) on one rank's shard."""
+    from ..api.cli_args import OptimizerConfig
+    from ..engine.flat_params import FlatParams, ShardedAdamW
+
+    n = (1 << 25) if a.small else (1 << 28)
+
+    class M(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.w = torch.nn.Parameter(torch.randn(n, device="cuda").bfloat16())
+
+    for kind, per_elem in (("adam", 4 * 4 + 3 * 4 + 2), ("adam_bf16", 4 + 4 * 2 + 4 * 2)):
+        m = M()
+        flat = FlatParams(m, "local")
+        opt = ShardedAdamW(flat, OptimizerConfig(type=kind, lr=1e-3, gradient_clipping=1.0), total_steps=100)
+        opt.shard_grad.normal_()
+        opt._norm.fill_(float(n))
+        ms = timeit(lambda: opt._update_cuda(), a.iters)
+        report(f"optimizer_update_{kind}", ms, nbytes=float(n) * per_elem, numel=n)
+        del opt, flat, m
+        torch.cuda.empty_cache()
 
 
 def bench_sampler(a):
@@ -272,7 +304,7 @@ def bench_decode_step(a):
 
 
 BENCHES = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "grouped_gemm": bench_grouped_gemm, "attn": bench_attn,
-           "lm_head": bench_lm_head, "decode": bench_decode, "elementwise": bench_elementwise,
+           "lm_head": bench_lm_head, "decode": bench_decode, "elementwise": bench_elementwise, "optimizer": bench_optimizer,
            "sampler": bench_sampler, "ppo_loss": bench_ppo_loss, "decode_step": bench_decode_step}
 
 
