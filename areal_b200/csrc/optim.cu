@@ -154,18 +154,53 @@ __global__ void adamw_bf16_bcast_kernel(const __nv_bfloat16* w_local,
   if (hp.max_norm > 0.f) coef = fminf(1.f, hp.max_norm / (sqrtf(nsq) + 1e-6f));
   const float step = hp.lr / hp.bias_corr1;
   const float inv_bc2_sqrt = rsqrtf(hp.bias_corr2);
-  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
-       i += static_cast<long long>(gridDim.x) * blockDim.x) {
-    const float gk = grad[i] * coef;
-    const float w = __bfloat162float(w_local[i]);
-    const float mk = hp.beta1 * __bfloat162float(m[i]) + (1.f - hp.beta1) * gk;
-    const float vk = hp.beta2 * __bfloat162float(v[i]) + (1.f - hp.beta2) * gk * gk;
+  auto update = [&](float w, float gk, float& mk, float& vk, float& c) -> __nv_bfloat16 {
+    gk *= coef;
+    mk = hp.beta1 * mk + (1.f - hp.beta1) * gk;
+    vk = hp.beta2 * vk + (1.f - hp.beta2) * gk * gk;
     const float denom = sqrtf(vk) * inv_bc2_sqrt + hp.eps;
-    const float c = __bfloat162float(comp[i]) - hp.lr * hp.weight_decay * w - step * mk / denom;
+    c = c - hp.lr * hp.weight_decay * w - step * mk / denom;
     const __nv_bfloat16 wn = __float2bfloat16(w + c);
+    c += w - __bfloat162float(wn);
+    return wn;
+  };
+  // 8 elements per thread: one 16-byte access per bf16 array, two per fp32 gradient (offset and the
+  // shard's base pointers are 16-byte aligned: offset is a multiple of 8 elements in this path)
+  const long long n8 = ((offset & 7) == 0) ? (n >> 3) : 0;
+  for (long long i = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n8;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    uint4 w8 = reinterpret_cast<const uint4*>(w_local)[i];
+    uint4 m8 = reinterpret_cast<uint4*>(m)[i];
+    uint4 v8 = reinterpret_cast<uint4*>(v)[i];
+    uint4 c8 = reinterpret_cast<uint4*>(comp)[i];
+    const float4 g0 = reinterpret_cast<const float4*>(grad)[2 * i];
+    const float4 g1 = reinterpret_cast<const float4*>(grad)[2 * i + 1];
+    const float g[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    __nv_bfloat16* wb = reinterpret_cast<__nv_bfloat16*>(&w8);
+    __nv_bfloat16* mb = reinterpret_cast<__nv_bfloat16*>(&m8);
+    __nv_bfloat16* vb = reinterpret_cast<__nv_bfloat16*>(&v8);
+    __nv_bfloat16* cb = reinterpret_cast<__nv_bfloat16*>(&c8);
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      float mk = __bfloat162float(mb[k]), vk = __bfloat162float(vb[k]), c = __bfloat162float(cb[k]);
+      wb[k] = update(__bfloat162float(wb[k]), g[k], mk, vk, c);
+      mb[k] = __float2bfloat16(mk);
+      vb[k] = __float2bfloat16(vk);
+      cb[k] = __float2bfloat16(c);
+    }
+    reinterpret_cast<uint4*>(m)[i] = m8;
+    reinterpret_cast<uint4*>(v)[i] = v8;
+    reinterpret_cast<uint4*>(comp)[i] = c8;
+    for (int p = 0; p < n_peers; ++p)
+      reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(params.p[p]) + offset)[i] = w8;
+  }
+  for (long long i = (n8 << 3) + static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<long long>(gridDim.x) * blockDim.x) {
+    float mk = __bfloat162float(m[i]), vk = __bfloat162float(v[i]), c = __bfloat162float(comp[i]);
+    const __nv_bfloat16 wn = update(__bfloat162float(w_local[i]), grad[i], mk, vk, c);
     m[i] = __float2bfloat16(mk);
     v[i] = __float2bfloat16(vk);
-    comp[i] = __float2bfloat16(c + (w - __bfloat162float(wn)));
+    comp[i] = __float2bfloat16(c);
     for (int p = 0; p < n_peers; ++p)
       reinterpret_cast<__nv_bfloat16*>(params.p[p])[offset + i] = wn;
   }
@@ -267,7 +302,7 @@ int b200_adamw_bf16_bcast(const void* w_local, void* comp, void* m, void* v, con
   PeerPtrs pp;
   for (int i = 0; i < n_peers; ++i) pp.p[i] = peer_params[i];
   AdamParams hp{lr, beta1, beta2, eps, weight_decay, bias_corr1, bias_corr2, max_norm};
-  adamw_bf16_bcast_kernel<<<grid_for(n, 2), 256, 0, stream>>>(
+  adamw_bf16_bcast_kernel<<<grid_for(n, 8), 256, 0, stream>>>(
       (const __nv_bfloat16*)w_local, (__nv_bfloat16*)comp, (__nv_bfloat16*)m, (__nv_bfloat16*)v, grad, pp,
       n_peers, offset, n, norm_sq, hp, skipped);
   B200_CHECK(cudaGetLastError());
