@@ -81,7 +81,8 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
             f.unlink()
     nvcc = _nvcc()
     cu_srcs = sorted(CSRC.glob("*.cu")) + sorted((CSRC / "common").glob("*.cu"))
-    cpp_srcs = sorted((CSRC / "host").glob("*.cpp"))
+    # selftest.cpp is a standalone sanitizer driver with its own main(), not part of the library
+    cpp_srcs = sorted(p for p in (CSRC / "host").glob("*.cpp") if p.name != "selftest.cpp")
     flags = list(NVCC_FLAGS) + (["-Xptxas", "-v"] if ptxas_info else [])
     jobs = []
     cu_objs, cpp_objs = [], []

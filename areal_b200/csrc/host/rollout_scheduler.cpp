@@ -408,8 +408,10 @@ int b200_sched_take_output(void* h, int64_t id, int32_t* out_tokens, float* out_
   const Request& r = it->second;
   const int n = static_cast<int>(r.tokens.size()) - r.prompt_len;
   if (n > cap) return -2;
-  std::memcpy(out_tokens, r.tokens.data() + r.prompt_len, n * sizeof(int32_t));
-  std::memcpy(out_logprobs, r.logprobs.data(), n * sizeof(float));
+  if (n > 0) {  // an aborted request may have produced nothing: its vectors hold no storage to copy from
+    std::memcpy(out_tokens, r.tokens.data() + r.prompt_len, n * sizeof(int32_t));
+    std::memcpy(out_logprobs, r.logprobs.data(), n * sizeof(float));
+  }
   s->reqs.erase(it);
   return n;
 }
