@@ -126,3 +126,56 @@ def test_proxy_workflow_inline_and_subproc(mode):
     out = asyncio.run(wf.arun_episode(Engine(), {"q": "why"}))
     (inter,) = out.values()
     assert inter.reward == 0.25 and inter.to_tensor_dict()["rewards"].tolist() == [0.25]
+
+
+class _ScriptedEngine:
+    """Engine whose completions follow a script of texts (token = index into the script's table)."""
+
+    def __init__(self, texts):
+        self.texts, self.calls, self.prompts = list(texts), 0, []
+
+    async def agenerate(self, req):
+        self.prompts.append(list(req.input_ids))
+        tok = 1000 + self.calls
+        self.calls += 1
+        return ModelResponse(input_tokens=list(req.input_ids), output_tokens=[tok, 0], output_logprobs=[-0.1, -0.1],
+                             output_versions=[1, 1], stop_reason="stop")
+
+
+class _ScriptTok(Tok):
+    def __init__(self, texts):
+        self.texts = texts
+
+    def decode(self, ids):
+        return "".join(self.texts[i - 1000] for i in ids if i >= 1000)
+
+
+def test_math_agents_single_multi_turn_and_tools():
+    from areal_b200.workflow.agents import MathAgent, MathToolAgent, MultiTurnMathAgent, math_reward_fn
+    from areal_b200.workflow.agents.math_agent import call_tool
+
+    assert math_reward_fn("so the answer is \\boxed{42}", "#### 42") == 1.0 and math_reward_fn("41", "42") == 0.0
+    assert call_tool("divide", '{"a": 1, "b": 0}').startswith("error") and call_tool("sqrt", {"a": 9}) == "3.0"
+    data = {"messages": [{"role": "user", "content": "what is 6 * 7?"}], "answer": "42"}
+
+    def episode(agent, texts, **kw):
+        eng = _ScriptedEngine(texts)
+        wf = OpenAIProxyWorkflow(agent, tokenizer=_ScriptTok(texts), mode="inline", **kw)
+        return asyncio.run(wf.arun_episode(eng, data)), eng
+
+    out, _ = episode(MathAgent(), ["\\boxed{42}"])
+    (one,) = out.values()
+    assert one.reward == 1.0
+    # wrong, then right: two rewarded completions, the second prompt contains the retry request
+    out, eng = episode(MultiTurnMathAgent(max_turns=4), ["\\boxed{41}", "\\boxed{42}", "unused"])
+    assert sorted(i.reward for i in out.values()) == [0.0, 1.0] and eng.calls == 2
+    assert len(eng.prompts[1]) > len(eng.prompts[0])
+    # tool use: first completion asks for multiply(6, 7), second answers with the tool's result
+    texts = ['<tool_call>{"name": "multiply", "arguments": {"a": 6, "b": 7}}</tool_call>', "The result is \\boxed{42}"]
+    out, eng = episode(MathToolAgent(max_turns=4), texts)
+    assert eng.calls == 2 and len(out) == 2
+    assert sorted(i.reward for i in out.values()) == [0.0, 1.0]  # the final answer carries the reward
+    first, second = list(out.values())
+    assert first.completion["choices"][0]["finish_reason"] == "tool_calls"
+    assert first.completion["choices"][0]["message"]["tool_calls"][0]["function"]["name"] == "multiply"
+    assert len(eng.prompts[1]) > len(eng.prompts[0])  # assistant turn + the tool's result went back in

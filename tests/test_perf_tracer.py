@@ -60,3 +60,27 @@ def test_session_tracer(tmp_path):
     assert [r["status"] for r in recs] == ["accepted", "rejected"]
     assert [p["name"] for p in recs[0]["phases"]] == ["generate", "reward"] and recs[0]["meta"]["reward"] == 1.0
     pt.configure(None)
+
+
+def test_trace_converter_cli_and_engine_profiler(tmp_path, capsys):
+    """The converter tool merges rank files and summarises; the engine profiler runs on the CPU path."""
+    import json
+
+    from areal_b200.tools import perf_trace_converter, profile_engines
+
+    for r in range(2):
+        with open(tmp_path / f"traces-r{r}.jsonl", "w") as f:
+            f.write(json.dumps(dict(name="fwd", cat="compute", ph="X", ts=10 + r, dur=2000, pid=r, tid=0)) + "\n")
+            f.write(json.dumps(dict(name="allreduce", cat="comm", ph="X", ts=5000, dur=500, pid=r, tid=1)) + "\n")
+    out = str(tmp_path / "merged.json")
+    assert perf_trace_converter.main([str(tmp_path), "-o", out, "--summary"]) == 0
+    ev = json.load(open(out))["traceEvents"]
+    assert len(ev) == 4 and [e["ts"] for e in ev] == sorted(e["ts"] for e in ev)
+    rows = perf_trace_converter.summarize(out)
+    assert rows[0][:3] == ("compute", "fwd", 2) and rows[0][3] == 4.0 and rows[1][3] == 1.0
+    capsys.readouterr()
+    assert profile_engines.main(["--preset", "tiny-qwen2", "--device", "cpu", "--tokens", "256", "--seq-len", "64",
+                                 "--steps", "1", "--warmup", "1"]) == 0
+    text = capsys.readouterr().out
+    rep = json.loads(text[text.index("{"):])
+    assert rep["tokens_per_step"] == 256 and rep["train"]["tokens_per_s"] > 0 and rep["forward"]["ms_per_step"] > 0
