@@ -94,6 +94,28 @@ class FlatParams:
                     p.main_grad = self.main_grad[o:o + n].view(p.shape)
         self.with_grads = with_grads
 
+    def close(self):
+        """Returns the device buffers of a single-rank instance to the driver (the parameters must no
+        longer be used). Buffers shared with peers over CUDA IPC are left to process exit: freeing memory
+        that another process still has mapped is undefined, and a teardown barrier could hang on a dead rank."""
+        if not self.cuda or self.dp_world > 1:
+            return
+        for _, p, _, _ in self.entries:
+            p.data = torch.empty(0, dtype=p.dtype, device=self.device)
+            if hasattr(p, "main_grad"):
+                del p.main_grad
+        self.flat = None
+        self.main_grad = None
+        for name in ("param_buf", "grad_buf"):
+            buf = getattr(self, name, None)
+            if buf is not None:
+                buf.close()
+                setattr(self, name, None)
+        bar = getattr(self, "barrier", None)
+        if bar is not None:
+            bar.buf.close()
+            self.barrier = None
+
     def zero_grad(self):
         if self.with_grads:
             self.main_grad.zero_()

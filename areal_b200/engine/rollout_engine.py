@@ -23,6 +23,7 @@ from __future__ import annotations
 
 import asyncio
 import ctypes
+import os
 import dataclasses
 import threading
 import time
@@ -287,6 +288,14 @@ class NativeRolloutEngine(InferenceEngine):
         self.sched = PagedScheduler(nblocks, bs, ncfg.max_num_seqs, ncfg.max_num_batched_tokens,
                                     max_blocks_per_seq)
         self.sched.set_prompt_sharing(bool(getattr(ncfg, "prompt_sharing", True)))
+        # The engine thread shares the interpreter with trainer / workflow threads; CPython hands the GIL over
+        # every 5 ms by default, which is half a decode step. A shorter interval keeps the step loop's short
+        # host phases from queueing behind another thread's Python.
+        import sys as _sys
+
+        want = float(os.environ.get("AREAL_B200_SWITCH_INTERVAL", "0.0005"))
+        if want > 0 and _sys.getswitchinterval() > want:
+            _sys.setswitchinterval(want)
         self._rng = torch.Generator(device=self.device).manual_seed(ncfg.seed)
         self._graphs = None
         self.launches_per_decode = 0

@@ -292,7 +292,13 @@ class B200TrainEngine(TrainEngine):
     def destroy(self):
         self.model = None
         self.optimizer = None
-        self.flat = None
+        if self.device.type == "cuda" if hasattr(self, "device") else False:
+            torch.cuda.synchronize(self.device)
+        for name in ("flat", "flat_base", "flat_experts"):
+            f = getattr(self, name, None)
+            if f is not None:
+                f.close()
+            setattr(self, name, None)
         if self._own_pg and dist.is_initialized():
             dist.destroy_process_group()
 

@@ -208,6 +208,31 @@ def bench_elementwise(a):
         report("qknorm_rope_fwd", ms, nbytes=T * (Hq + Hkv) * D * 2.0 * 2)
 
 
+def bench_kchunk_gemm(a):
+    """The all-to-all → GEMM kernel's main loop on one GPU: four emulated source ranks whose chunks are
+    already in the gather buffer and whose flags already carry the epoch, so the K loop runs its rotated
+    chunk order and flag checks without waiting (the exchange itself needs two or more GPUs)."""
+    import ctypes
+
+    world, rank = 4, 1
+    M, Kc, N = (2048, 1024, 4096) if a.small else (8192, 1024, 4096)
+    chunks = (torch.randn(world, M, Kc, device="cuda") * 0.1).bfloat16()
+    w = (torch.randn(N, world * Kc, device="cuda") * 0.1).bfloat16()
+    flags = torch.full((64,), 3, dtype=torch.int32, device="cuda")
+    out = torch.empty(M, N, dtype=torch.bfloat16, device="cuda")
+    lib = _lib.kernels()
+
+    def run():
+        rc = lib.b200_gemm_kchunk_gated(_lib.ptr(chunks), _lib.ptr(w), _lib.ptr(out), _lib.ptr(flags), ctypes.c_uint(3),
+                                        ctypes.c_int(world), ctypes.c_int(rank), ctypes.c_int(M), ctypes.c_int(N),
+                                        ctypes.c_int(Kc), ctypes.c_longlong(w.stride(0)),
+                                        ctypes.c_longlong(out.stride(0)), _lib.stream_ptr())
+        _lib.check(rc, "b200_gemm_kchunk_gated")
+
+    ms = timeit(run, a.iters)
+    report("gemm_kchunk_gated_emulated", ms, flops=2.0 * M * N * world * Kc, shape=[M, N, world * Kc])
+
+
 def bench_optimizer(a):
     """Sharded AdamW update (fp32 master + moments in, new bf16 weights out) on one rank's shard."""
     from ..api.cli_args import OptimizerConfig
@@ -304,7 +329,7 @@ def bench_decode_step(a):
 
 
 BENCHES = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "grouped_gemm": bench_grouped_gemm, "attn": bench_attn,
-           "lm_head": bench_lm_head, "decode": bench_decode, "elementwise": bench_elementwise, "optimizer": bench_optimizer,
+           "lm_head": bench_lm_head, "decode": bench_decode, "elementwise": bench_elementwise, "optimizer": bench_optimizer, "kchunk_gemm": bench_kchunk_gemm,
            "sampler": bench_sampler, "ppo_loss": bench_ppo_loss, "decode_step": bench_decode_step}
 
 

@@ -293,6 +293,17 @@ def main():
                 "gpu_launches": int(marks["launches"]),
                 "weight_sync_latency_s": sync_max,
             }
+    if os.environ.get("AREAL_B200_BENCH_DIAG"):
+        # host-side view of the rollout engine (stderr only): scheduler counters and where its loop spent time
+        eng = getattr(trainer, "rollout", None)
+        inner = getattr(eng, "engine", eng)
+        if inner is not None and hasattr(inner, "export_stats"):
+            try:
+                st = inner.export_stats()
+                print("rollout diag: " + json.dumps({k: round(float(v), 3) for k, v in sorted(st.items())}),
+                      file=sys.stderr, flush=True)
+            except Exception as e:  # diagnostics must never change the run's outcome
+                print(f"rollout diag unavailable: {e}", file=sys.stderr)
     trainer.close()
     if result is not None:
         print(json.dumps(result), flush=True)
