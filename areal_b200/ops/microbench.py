@@ -214,6 +214,8 @@ def bench_kchunk_gemm(a):
     chunk order and flag checks without waiting (the exchange itself needs two or more GPUs)."""
     import ctypes
 
+    from . import _lib
+
     world, rank = 4, 1
     M, Kc, N = (2048, 1024, 4096) if a.small else (8192, 1024, 4096)
     chunks = (torch.randn(world, M, Kc, device="cuda") * 0.1).bfloat16()
