@@ -18,7 +18,6 @@ import os
 import re
 import types
 import typing
-from dataclasses import MISSING as _DC_MISSING
 from dataclasses import asdict, dataclass, field, fields, is_dataclass
 from pathlib import Path
 from typing import Any, ClassVar, TypeVar

@@ -28,7 +28,6 @@ import dataclasses
 import threading
 import time
 from concurrent.futures import Future
-from typing import Any
 
 import numpy as np
 import torch

@@ -14,7 +14,6 @@ areal/experimental/engine/archon_engine.py:147-1533): ``train_batch``,
 from __future__ import annotations
 
 import dataclasses
-import math
 import os
 import time
 from typing import Any, Callable
@@ -23,17 +22,15 @@ import torch
 import torch.distributed as dist
 
 from ..api.alloc_mode import ModelAllocation, ParallelStrategy
-from ..api.cli_args import MicroBatchSpec, OptimizerConfig, TrainEngineConfig
+from ..api.cli_args import OptimizerConfig, TrainEngineConfig
 from ..api.engine_api import InferenceEngine, TrainEngine
 from ..api.io_struct import FinetuneSpec, ParamSpec, SaveLoadMeta, WeightUpdateMeta
 from ..models.config import PRESETS, ModelConfig
 from ..models.qwen import QwenModel, build_model
-from ..ops import _lib
 from ..ops.attention import VarlenMeta
 from ..ops.lm_head import lm_head_logprobs
 from ..utils import logging, stats_tracker
-from ..utils.data import (MicroBatchList, amend_position_ids, pack_tensor_dict, pad_mb_list,
-                          split_padded_tensor_dict_into_mb_list)
+from ..utils.data import MicroBatchList, amend_position_ids, split_padded_tensor_dict_into_mb_list
 from .flat_params import FlatParams, ShardedAdamW
 
 logger = logging.getLogger("TrainEngine")

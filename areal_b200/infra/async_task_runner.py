@@ -14,7 +14,7 @@ import threading
 import time
 import traceback
 from dataclasses import dataclass, field
-from typing import Any, Awaitable, Callable, Generic, TypeVar
+from typing import Awaitable, Callable, Generic, TypeVar
 
 from ..utils import logging
 

@@ -23,7 +23,6 @@ from ...api.cli_args import SchedulingSpec, TrainEngineConfig
 from ...api.io_struct import FinetuneSpec, SaveLoadMeta, WeightUpdateMeta
 from ...api.scheduler_api import Job, Scheduler, Worker
 from ...utils import logging
-from ...utils.data import concat_padded_tensors
 from ...utils.seqpack import balanced_greedy_partition
 from ..rpc.rpc_server import find_free_ports
 from ..rpc.rtensor import RTensor

@@ -30,7 +30,6 @@ import torch
 import torch.distributed as dist
 
 from ..api.engine_api import InferenceEngine
-from ..api.io_struct import WeightUpdateMeta
 from ..ops import _lib
 from ..parallel.symm_mem import open_ipc_handle
 from ..utils import logging

@@ -15,11 +15,10 @@ import uuid
 from dataclasses import dataclass
 from typing import Any
 
-import numpy as np
 import requests
 import torch
 
-from .serialization import _np_from_b64, _np_to_b64, deserialize_value, serialize_value
+from .serialization import deserialize_value, serialize_value
 
 
 class ShardStore:

@@ -13,7 +13,7 @@ import time
 from ...api.cli_args import SchedulingSpec
 from ...api.scheduler_api import Job, Worker
 from ...utils import logging
-from .exceptions import WorkerCreationError, WorkerFailedError, WorkerNotFoundError
+from .exceptions import WorkerCreationError
 from .local import LocalScheduler, _WorkerInfo
 
 logger = logging.getLogger("RayScheduler")

@@ -16,7 +16,6 @@ HF checkpoint names are the interchange format (``to_hf`` / ``from_hf``).
 
 from __future__ import annotations
 
-import math
 from typing import Iterable, Iterator
 
 import torch
@@ -337,7 +336,6 @@ class QwenModel(nn.Module):
         meta-free throwaway copy and keeps what it owns. Meant for small / test models; real runs
         load checkpoints."""
         import copy
-        import dataclasses
 
         from ..parallel.context import ParallelContext
 

@@ -18,7 +18,6 @@ import asyncio
 import secrets
 import time
 import uuid
-from typing import Any
 
 from fastapi import FastAPI, HTTPException, Request
 

@@ -72,7 +72,6 @@ class _LMHead(torch.autograd.Function):
         lib = _lib.kernels()
         lib.b200_lm_head_nsplit.restype = ctypes.c_int
         nsplit = lib.b200_lm_head_nsplit(ctypes.c_int(T), ctypes.c_int(V))
-        partials = torch.empty((nsplit, T, 4), dtype=torch.float32, device=x.device)
         inv_t = 1.0 / float(temperature)
         tp = dist.get_world_size(tp_group) if tp_group is not None else 1
         if tp > 1 and tp_fused is not None and getattr(tp_fused, "cuda", False):
@@ -93,6 +92,7 @@ class _LMHead(torch.autograd.Function):
             half = bufs.nbytes // 2
             partials = bufs.tensor(torch.float32, tp * nsplit * T * 4, byte_offset=h * half).view(tp * nsplit, T, 4)
             return _LMHead._finish(ctx, lib, partials, tp * nsplit, x, w, labels, inv_t, tp_group, vocab_start)
+        partials = torch.empty((nsplit, T, 4), dtype=torch.float32, device=x.device)
         lib.b200_lm_head_stats.restype = ctypes.c_int
         rc = lib.b200_lm_head_stats(_lib.ptr(x), _lib.ptr(w), _lib.ptr(labels), _lib.ptr(partials),
                                     ctypes.c_int(T), ctypes.c_int(V), ctypes.c_int(H),

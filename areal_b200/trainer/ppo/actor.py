@@ -17,10 +17,8 @@ from typing import Any
 
 import torch
 
-from ...api.cli_args import (PROX_LOGP_METHOD_LOGLINEAR, PROX_LOGP_METHOD_METRICS,
-                             PROX_LOGP_METHOD_RECOMPUTE, MicroBatchSpec, PPOActorConfig)
+from ...api.cli_args import PROX_LOGP_METHOD_METRICS, PROX_LOGP_METHOD_RECOMPUTE, MicroBatchSpec, PPOActorConfig
 from ...api.engine_api import TrainEngine
-from ...ops import _lib
 from ...utils import functional as Fn
 from ...utils import stats_tracker
 from ...utils.data import KLEstimator, Normalization, split_padded_tensor_dict_into_mb_list

@@ -1,2 +1,4 @@
 """Entry point kept for source compatibility with the reference's module layout."""
 from .sl_trainer import SFTTrainer  # noqa: F401
+
+__all__ = ["SFTTrainer"]

@@ -15,7 +15,7 @@ import torch
 import torch.distributed as dist
 
 from ..api.alloc_mode import ModelAllocation
-from ..api.cli_args import DPOConfig, RWConfig, SFTConfig
+from ..api.cli_args import RWConfig
 from ..api.io_struct import FinetuneSpec, StepInfo
 from ..engine.train_engine import B200TrainEngine
 from ..utils import logging, seeding, stats_tracker

@@ -10,7 +10,7 @@ packed form: every ``[B, L]`` tensor flattened to ``[T]`` over valid tokens plus
 
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+from dataclasses import dataclass
 from typing import Any, Sequence
 
 import numpy as np

@@ -9,7 +9,6 @@ the layout the trainer expects (areal/workflow/rlvr.py:49-178 in the reference).
 from __future__ import annotations
 
 import asyncio
-import inspect
 import uuid
 from typing import Any, Callable
 

@@ -66,7 +66,6 @@ def synthetic_reward(prompt, completion, prompt_ids, completion_ids, **kw):
 def make_workflow_cls():
     import torch
 
-    from areal_b200.api.io_struct import ModelRequest
     from areal_b200.workflow.rlvr import RLVRWorkflow
 
     class SyntheticLengthWorkflow(RLVRWorkflow):
