@@ -14,9 +14,11 @@
 //   dQ_i = dS K_j               (tcgen05 into the S^T columns; both operands MN-major;
 //                                then red.global.add.v4.f32 into an fp32 dQ buffer)
 //
-// Working on the transposed score tile makes each of the 128 compute threads
-// own one key row, so P^T and dS^T are written row-per-thread as K-major A
-// operands and no tile is ever transposed in memory.
+// Working on the transposed score tile makes each compute thread own (part of)
+// one key row, so P^T and dS^T are written row-per-thread as K-major A operands
+// and no tile is ever transposed in memory. The kernel is a template on the number
+// of compute warps: with 8, warps w and w+4 read the same 32 TMEM lanes and take
+// the lower / upper 64 columns of every 128-column tile.
 //
 // Replaces flash-attn's backward / aten._flash_attention_backward in the
 // reference (areal/experimental/models/archon/attention/varlen.py:116).
@@ -27,7 +29,8 @@ namespace b200 {
 
 constexpr int kD = 128;
 constexpr int kBT = 128;  // rows of every tile (q and kv)
-constexpr int kBwdThreads = 192;
+// NCW compute warps (4 or 8) + TMA producer + MMA issuer
+template <int NCW> constexpr int bwd_threads() { return NCW * 32 + 64; }
 
 struct AttnBwdTile {
   int kv_start;   // first global token row of this kv block
@@ -84,7 +87,11 @@ __device__ __forceinline__ void red_add_v4(float* addr, float a, float b, float 
                : "memory");
 }
 
-__global__ void __launch_bounds__(kBwdThreads, 1)
+// TREE: keys carry a subtree end (`key_exit`) that bounds the queries they are visible to. It is a
+// template flag because the 4-warp variant sits at the register limit: the extra compare in the
+// innermost loop cost the ordinary causal path a third of its speed when it was a run-time test.
+template <int NCW, bool TREE>
+__global__ void __launch_bounds__(NCW * 32 + 64, 1)
 attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__ CUtensorMap tmK,
                 const __grid_constant__ CUtensorMap tmV, const __grid_constant__ CUtensorMap tmdO,
                 const AttnBwdTile* __restrict__ tiles, const float* __restrict__ lse,
@@ -92,6 +99,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
                 __nv_bfloat16* __restrict__ dk, __nv_bfloat16* __restrict__ dv, int T, int Hq,
                 int Hkv, long long lddk, long long lddv, float scale, int* status,
                 const int* __restrict__ key_exit) {
+  constexpr int kCompute = NCW * 32;     // compute threads
+  constexpr int kChunks = 4 / (NCW / 4);  // 32-column chunks of a 128-column tile per compute warp
   extern __shared__ __align__(1024) uint8_t smem[];
   __shared__ uint64_t bars[16];
   __shared__ uint32_t tmem_holder;
@@ -140,11 +149,11 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     }
     mbar_init(s_full, 1);
     mbar_init(dp_full, 1);
-    mbar_init(pt_ready, 128);
+    mbar_init(pt_ready, kCompute);
     mbar_init(pbuf_free, 1);
-    mbar_init(dst_ready, 128);
+    mbar_init(dst_ready, kCompute);
     mbar_init(dq_full, 1);
-    mbar_init(dq_read, 128);
+    mbar_init(dq_read, kCompute);
     mbar_init(acc_done, 1);
     fence_mbar_init();
     prefetch_tmap(&tmQ);
@@ -152,7 +161,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
     prefetch_tmap(&tmV);
     prefetch_tmap(&tmdO);
   }
-  if (warp == 5) {
+  if (warp == NCW + 1) {
     tmem_alloc(&tmem_holder, 512);
     tmem_relinquish();
   }
@@ -167,7 +176,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
   const bool bad_align = (abort_word != 0);
 
   if (bad_align) {
-  } else if (warp == 4) {
+  } else if (warp == NCW) {
     // ------------------------------------------------------ TMA producer --
     if (elect_one_sync()) {
       mbar_arrive_expect_tx(kv_full, 2 * kTileBytes);
@@ -196,7 +205,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         while (globaltimer_ns() - t0 < 2000000ull) __nanosleep(1000);
       }
     }
-  } else if (warp == 5) {
+  } else if (warp == NCW + 1) {
     // -------------------------------------------------------- MMA issuer --
     if (elect_one_sync()) {
       // all tiles are [128 rows][2 halves of 64 columns], 128B-swizzled.
@@ -268,13 +277,15 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       }
     }
   } else {
-    // ------------------------------------------------- compute warps 0..3 --
-    const int r = warp * 32 + lane;  // kv row inside the block == TMEM lane (q row for dQ)
-    const uint32_t lane_addr = static_cast<uint32_t>(warp * 32) << 16;
+    // ---------------------------------------------------- compute warps --
+    const int quad = warp & 3;    // TMEM lane quarter this warp may read
+    const int cpart = warp >> 2;  // which part of the columns of every 128-column tile this warp handles
+    const int r = quad * 32 + lane;  // kv row inside the block == TMEM lane (q row for dQ)
+    const uint32_t lane_addr = static_cast<uint32_t>(quad * 32) << 16;
     const int kv_pos = tile.kv_off + r;
     const bool kv_valid = r < tile.kv_len;
     // tree attention: this key is visible to the queries of its own subtree only
-    const int kv_exit = (key_exit != nullptr && kv_valid) ? key_exit[tile.kv_start + r] : 0x7fffffff;
+    const int kv_exit = (TREE && kv_valid) ? key_exit[tile.kv_start + r] : 0x7fffffff;
     uint8_t* psrow = sPS + r * 128;
     bool ok = true;
     for (int it = 0; it < n_iter && ok; ++it) {
@@ -284,20 +295,21 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       const int q0 = i * kBT;  // offset of the q block inside the sequence
       const int q_rows = min(kBT, tile.seq_len - q0);
       // stage lse / delta of this q block (log2 units for lse)
-      {
+      if (cpart == 0) {
         const int qi = q0 + r;
         const long long idx = static_cast<long long>(h) * T + tile.seq_start + qi;
         const bool v = r < q_rows;
         s_lse[itp][r] = v ? lse[idx] * 1.4426950408889634f : INFINITY;
         s_delta[itp][r] = v ? delta[idx] : 0.f;
       }
-      named_bar_sync(1, 128);
+      named_bar_sync(1, kCompute);
       if (!mbar_wait(s_full, itp, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      uint32_t p_packed[kBT / 2];
+      uint32_t p_packed[kChunks * 16];  // this warp's columns
       const bool diag = (q0 < tile.kv_off + kBT);  // block touches the causal diagonal
 #pragma unroll
-      for (int c = 0; c < kBT / 32; ++c) {
+      for (int cl = 0; cl < kChunks; ++cl) {
+        const int c = cpart * kChunks + cl;
         uint32_t raw[32];
         tmem_ld_32x32(tm_S + lane_addr + c * 32, raw);
         tmem_ld_wait();
@@ -308,12 +320,12 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
           for (int u = 0; u < 2; ++u) {
             const int col = c * 32 + 2 * e + u;  // q row inside block
             float p = exp2f(__uint_as_float(raw[2 * e + u]) * scale_log2 - s_lse[itp][col]);
-            const bool valid = kv_valid && (col < q_rows) && (!diag || (q0 + col >= kv_pos)) &&
-                               (q0 + col < kv_exit);
+            bool valid = kv_valid && (col < q_rows) && (!diag || (q0 + col >= kv_pos));
+            if (TREE) valid = valid && (q0 + col < kv_exit);
             p2[u] = valid ? p : 0.f;
           }
           __nv_bfloat162 pb = __floats2bfloat162_rn(p2[0], p2[1]);
-          p_packed[c * 16 + e] = *reinterpret_cast<uint32_t*>(&pb);
+          p_packed[cl * 16 + e] = *reinterpret_cast<uint32_t*>(&pb);
         }
       }
       // the buffer still holds dS^T of the previous iteration until dK/dQ MMAs finished
@@ -321,9 +333,10 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         if (!mbar_wait(dq_full, (it - 1) & 1, abort_flag)) { ok = false; break; }
       }
 #pragma unroll
-      for (int c = 0; c < kBT / 8; ++c) {
-        uint4 pk = make_uint4(p_packed[c * 4], p_packed[c * 4 + 1], p_packed[c * 4 + 2],
-                              p_packed[c * 4 + 3]);
+      for (int cp = 0; cp < kChunks * 4; ++cp) {  // 16-byte pieces of this warp's part of the row
+        uint4 pk = make_uint4(p_packed[cp * 4], p_packed[cp * 4 + 1], p_packed[cp * 4 + 2],
+                              p_packed[cp * 4 + 3]);
+        const int c = cpart * kChunks * 4 + cp;
         const int half = c >> 3, cc = c & 7;
         *reinterpret_cast<uint4*>(psrow + half * (kTileBytes / 2) + ((cc ^ (r & 7)) << 4)) = pk;
       }
@@ -333,28 +346,30 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
       // iteration was only issued after dq_read(it-1), so dQ(it-1) is already drained.
       if (!mbar_wait(dp_full, itp, abort_flag)) { ok = false; break; }
       tc_fence_after();
-      uint32_t ds_packed[kBT / 2];
+      uint32_t ds_packed[kChunks * 16];
 #pragma unroll
-      for (int c = 0; c < kBT / 32; ++c) {
+      for (int cl = 0; cl < kChunks; ++cl) {
+        const int c = cpart * kChunks + cl;
         uint32_t raw[32];
         tmem_ld_32x32(tm_dP + lane_addr + c * 32, raw);
         tmem_ld_wait();
 #pragma unroll
         for (int e = 0; e < 16; ++e) {
-          const __nv_bfloat162 pb = *reinterpret_cast<__nv_bfloat162*>(&p_packed[c * 16 + e]);
+          const __nv_bfloat162 pb = *reinterpret_cast<__nv_bfloat162*>(&p_packed[cl * 16 + e]);
           const float2 p = __bfloat1622float2(pb);
           const int col = c * 32 + 2 * e;
           const float d0 = p.x * (__uint_as_float(raw[2 * e]) - s_delta[itp][col]) * scale;
           const float d1 = p.y * (__uint_as_float(raw[2 * e + 1]) - s_delta[itp][col + 1]) * scale;
           __nv_bfloat162 db = __floats2bfloat162_rn(d0, d1);
-          ds_packed[c * 16 + e] = *reinterpret_cast<uint32_t*>(&db);
+          ds_packed[cl * 16 + e] = *reinterpret_cast<uint32_t*>(&db);
         }
       }
       if (!mbar_wait(pbuf_free, itp, abort_flag)) { ok = false; break; }
 #pragma unroll
-      for (int c = 0; c < kBT / 8; ++c) {
-        uint4 pk = make_uint4(ds_packed[c * 4], ds_packed[c * 4 + 1], ds_packed[c * 4 + 2],
-                              ds_packed[c * 4 + 3]);
+      for (int cp = 0; cp < kChunks * 4; ++cp) {
+        uint4 pk = make_uint4(ds_packed[cp * 4], ds_packed[cp * 4 + 1], ds_packed[cp * 4 + 2],
+                              ds_packed[cp * 4 + 3]);
+        const int c = cpart * kChunks * 4 + cp;
         const int half = c >> 3, cc = c & 7;
         *reinterpret_cast<uint4*>(psrow + half * (kTileBytes / 2) + ((cc ^ (r & 7)) << 4)) = pk;
       }
@@ -368,7 +383,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         const bool qv = r < q_rows;
         float* dq_row = dq_acc + (static_cast<long long>(tile.seq_start + q0 + r) * Hq + h) * kD;
 #pragma unroll 1
-        for (int c = 0; c < kD / 32; ++c) {
+        for (int cl = 0; cl < kChunks; ++cl) {
+          const int c = cpart * kChunks + cl;
           uint32_t raw[32];
           tmem_ld_32x32(tm_S + lane_addr + c * 32, raw);
           tmem_ld_wait();
@@ -395,7 +411,8 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
         __nv_bfloat16* dst = which ? dv_row : dk_row;
         const uint32_t tm = which ? tm_dV : tm_dK;
 #pragma unroll 1
-        for (int c = 0; c < kD / 32; ++c) {
+        for (int cl = 0; cl < kChunks; ++cl) {
+          const int c = cpart * kChunks + cl;
           uint32_t raw[32];
           if (n_iter > 0) {
             tmem_ld_32x32(tm + lane_addr + c * 32, raw);
@@ -426,7 +443,7 @@ attn_bwd_kernel(const __grid_constant__ CUtensorMap tmQ, const __grid_constant__
 
   tc_fence_before();
   __syncthreads();
-  if (warp == 5) {
+  if (warp == NCW + 1) {
     tc_fence_after();
     tmem_dealloc(tmem_base, 512);
   }
@@ -484,17 +501,36 @@ int b200_attn_bwd_ex(const void* q, const void* k, const void* v, const void* o,
                     kBT, 64);
   if (rc) return rc;
   static bool attr_set = false;
+  static int compute_warps = 8;
   if (!attr_set) {
-    B200_CHECK(cudaFuncSetAttribute(attn_bwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    B200_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<4, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                     kAttnBwdSmem));
+    B200_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<4, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kAttnBwdSmem));
+    B200_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<8, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kAttnBwdSmem));
+    B200_CHECK(cudaFuncSetAttribute(attn_bwd_kernel<8, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                    kAttnBwdSmem));
+    // 8 compute warps by default (measured 472 vs 403 TFLOP/s); AREAL_B200_ATTN_BWD_WARPS=4 selects the
+    // variant in which one warp handles all 128 columns of its rows
+    const char* e = getenv("AREAL_B200_ATTN_BWD_WARPS");
+    if (e && atoi(e) == 4) compute_warps = 4;
     attr_set = true;
   }
   int* status = device_status_word();
   if (!status) return -3;
   dim3 grid(n_tiles, Hkv);
-  attn_bwd_kernel<<<grid, kBwdThreads, kAttnBwdSmem, stream>>>(
-      tmQ, tmK, tmV, tmdO, reinterpret_cast<const AttnBwdTile*>(tiles), lse, delta_ws, dq_acc,
-      (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, T, Hq, Hkv, lddk, lddv, softmax_scale, status, key_exit);
+#define B200_ATTN_BWD_LAUNCH(NCW, TREE)                                                                   \
+  attn_bwd_kernel<NCW, TREE><<<grid, bwd_threads<NCW>(), kAttnBwdSmem, stream>>>(                         \
+      tmQ, tmK, tmV, tmdO, reinterpret_cast<const AttnBwdTile*>(tiles), lse, delta_ws, dq_acc,            \
+      (__nv_bfloat16*)dk, (__nv_bfloat16*)dv, T, Hq, Hkv, lddk, lddv, softmax_scale, status, key_exit)
+  const bool tree = key_exit != nullptr;
+  if (compute_warps == 8) {
+    if (tree) B200_ATTN_BWD_LAUNCH(8, true); else B200_ATTN_BWD_LAUNCH(8, false);
+  } else {
+    if (tree) B200_ATTN_BWD_LAUNCH(4, true); else B200_ATTN_BWD_LAUNCH(4, false);
+  }
+#undef B200_ATTN_BWD_LAUNCH
   B200_CHECK(cudaGetLastError());
   if (dq) {
     const long long n = static_cast<long long>(T) * Hq * kD;
