@@ -275,6 +275,79 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ ws, const __nv_bf
   }
 }
 
+// Split-K reduction fused with the residual add and RMSNorm that follow a projection in a decoder
+// block: one warp per row sums the S fp32 slices (+ bias), rounds to bf16 (the projection's output
+// precision), adds the bf16 residual stream, stores the new residual (bf16) and the normalised row.
+// Every rounding step of the unfused sequence (GEMM → bf16, residual add → bf16, norm) is kept, so
+// the results are bit-identical to it. N = 256 * NV at most (a lane owns NV groups of 8 columns).
+template <int NV>
+__global__ void splitk_reduce_rmsnorm_kernel(const float* __restrict__ ws, const __nv_bfloat16* __restrict__ bias,
+                                             const __nv_bfloat16* __restrict__ res, const __nv_bfloat16* __restrict__ w,
+                                             __nv_bfloat16* __restrict__ y, __nv_bfloat16* __restrict__ res_out,
+                                             int M, int N, int S, long long slice_stride, float eps) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int lane = threadIdx.x & 31;
+  const int nvec = N >> 3;
+  for (long long row = static_cast<long long>(blockIdx.x) * warps_per_block + (threadIdx.x >> 5); row < M;
+       row += static_cast<long long>(gridDim.x) * warps_per_block) {
+    float v[NV][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        float acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};
+        for (int sl = 0; sl < S; ++sl) {
+          const float4* src = reinterpret_cast<const float4*>(ws + sl * slice_stride + row * N + c * 8);
+          const float4 a = src[0], b = src[1];
+          acc[0] += a.x; acc[1] += a.y; acc[2] += a.z; acc[3] += a.w;
+          acc[4] += b.x; acc[5] += b.y; acc[6] += b.z; acc[7] += b.w;
+        }
+        if (bias) {
+#pragma unroll
+          for (int j = 0; j < 8; ++j) acc[j] += __bfloat162float(bias[c * 8 + j]);
+        }
+        uint4 rraw = res ? reinterpret_cast<const uint4*>(res + row * N)[c] : make_uint4(0, 0, 0, 0);
+        const __nv_bfloat162* rp = reinterpret_cast<const __nv_bfloat162*>(&rraw);
+        uint4 hraw;
+        __nv_bfloat162* hp = reinterpret_cast<__nv_bfloat162*>(&hraw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // projection output in bf16, then the residual add in fp32, then the bf16 residual stream
+          const float2 a2 = __bfloat1622float2(__floats2bfloat162_rn(acc[2 * j], acc[2 * j + 1]));
+          const float2 r2 = __bfloat1622float2(rp[j]);
+          hp[j] = res ? __floats2bfloat162_rn(a2.x + r2.x, a2.y + r2.y) : __floats2bfloat162_rn(a2.x, a2.y);
+          const float2 h2 = __bfloat1622float2(hp[j]);
+          v[i][2 * j] = h2.x;
+          v[i][2 * j + 1] = h2.y;
+          ss += h2.x * h2.x;  // same accumulation order as the stand-alone RMSNorm kernel
+          ss += h2.y * h2.y;
+        }
+        reinterpret_cast<uint4*>(res_out + row * N)[c] = hraw;
+      }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);
+    const float rs = rsqrtf(ss / N + eps);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = lane + 32 * i;
+      if (c < nvec) {
+        const uint4 wraw = reinterpret_cast<const uint4*>(w)[c];
+        const __nv_bfloat162* wp = reinterpret_cast<const __nv_bfloat162*>(&wraw);
+        uint4 oraw;
+        __nv_bfloat162* op = reinterpret_cast<__nv_bfloat162*>(&oraw);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float2 w2 = __bfloat1622float2(wp[j]);
+          op[j] = __floats2bfloat162_rn(v[i][2 * j] * rs * w2.x, v[i][2 * j + 1] * rs * w2.y);
+        }
+        reinterpret_cast<uint4*>(y + row * N)[c] = oraw;
+      }
+    }
+  }
+}
+
 }  // namespace b200
 
 extern "C" {
@@ -353,13 +426,11 @@ int b200_gemm_grouped_wgrad(const void* dY, const void* X, void* dW, const int* 
   return 0;
 }
 
-// C[M,N] (bf16) = A[M,K] . B[N,K]^T (+ bias) with the K extent split over `splits` CTAs per tile.
-// workspace: fp32 [splits * ceil(M/128)*128 * N]. N % 4 == 0, ldc % 4 == 0.
-int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, const void* bias, float* workspace, int M, int N,
-                          int K, long long lda, long long ldb, long long ldc, int splits, cudaStream_t stream) {
+// Launches the split-K GEMM proper: fp32 partial tiles into `workspace`. Returns the number of slices
+// through *S_out and the slice stride (elements) through *stride_out.
+static int launch_splitk_partials(const void* A, const void* B, float* workspace, int M, int N, int K, long long lda,
+                                  long long ldb, int splits, int* S_out, long long* stride_out, cudaStream_t stream) {
   using namespace b200;
-  if (M <= 0 || N <= 0 || K <= 0) return 0;
-  if ((lda & 7) || (ldb & 7) || (N & 3) || (ldc & 3) || splits < 1) return -100;
   constexpr int BN = 128;
   using Cfg = GemmCfg<BN>;
   const int tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + BN - 1) / BN;
@@ -385,12 +456,60 @@ int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, const void* bia
   if (!status) return -3;
   kern<<<grid, kGemmThreads, Cfg::kSmemBytes, stream>>>(tmA, tmB, Mv, N, K, epi, status);
   B200_CHECK(cudaGetLastError());
+  *S_out = S;
+  *stride_out = static_cast<long long>(tiles_m) * kBM * N;
+  return 0;
+}
+
+// C[M,N] (bf16) = A[M,K] . B[N,K]^T (+ bias) with the K extent split over `splits` CTAs per tile.
+// workspace: fp32 [splits * ceil(M/128)*128 * N]. N % 4 == 0, ldc % 4 == 0.
+int b200_gemm_bf16_splitk(const void* A, const void* B, void* C, const void* bias, float* workspace, int M, int N,
+                          int K, long long lda, long long ldb, long long ldc, int splits, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (N & 3) || (ldc & 3) || splits < 1) return -100;
+  int S = 0;
+  long long stride = 0;
+  const int rc = launch_splitk_partials(A, B, workspace, M, N, K, lda, ldb, splits, &S, &stride, stream);
+  if (rc) return rc;
   const long long total = static_cast<long long>(M) * (N >> 2);
   long long rg = (total + 255) / 256;
   const long long maxg = static_cast<long long>(sm_count()) * 8;
   if (rg > maxg) rg = maxg;
   splitk_reduce_kernel<<<(unsigned)rg, 256, 0, stream>>>(workspace, (const __nv_bfloat16*)bias, (__nv_bfloat16*)C, ldc,
-                                                        M, N, S, static_cast<long long>(tiles_m) * kBM * N);
+                                                        M, N, S, stride);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// Split-K projection followed, in the reduction kernel, by the residual add and RMSNorm:
+//   h = bf16(A . B^T + bias) + residual;  res_out = bf16(h);  y = rmsnorm(res_out) * norm_w
+// residual may be null (then res_out = bf16(A . B^T + bias)). y and res_out are contiguous [M, N] bf16;
+// N % 8 == 0 and N <= 8192. Two launches instead of three (GEMM, reduce, norm).
+int b200_gemm_bf16_splitk_rmsnorm(const void* A, const void* B, const void* bias, float* workspace, int M, int N, int K,
+                                  long long lda, long long ldb, int splits, const void* residual, const void* norm_w,
+                                  void* y, void* res_out, float eps, cudaStream_t stream) {
+  using namespace b200;
+  if (M <= 0 || N <= 0 || K <= 0) return 0;
+  if ((lda & 7) || (ldb & 7) || (N & 7) || N > 8192 || splits < 1) return -100;
+  int S = 0;
+  long long stride = 0;
+  const int rc = launch_splitk_partials(A, B, workspace, M, N, K, lda, ldb, splits, &S, &stride, stream);
+  if (rc) return rc;
+  const int nv = (N / 8 + 31) / 32;
+  const int wpb = 8;
+  const unsigned grid = static_cast<unsigned>((M + wpb - 1) / wpb);
+#define B200_LAUNCH_RN(NV_)                                                                                  \
+  splitk_reduce_rmsnorm_kernel<NV_><<<grid, wpb * 32, 0, stream>>>(                                          \
+      workspace, (const __nv_bfloat16*)bias, (const __nv_bfloat16*)residual, (const __nv_bfloat16*)norm_w,   \
+      (__nv_bfloat16*)y, (__nv_bfloat16*)res_out, M, N, S, stride, eps)
+  if (nv <= 1) B200_LAUNCH_RN(1);
+  else if (nv <= 2) B200_LAUNCH_RN(2);
+  else if (nv <= 4) B200_LAUNCH_RN(4);
+  else if (nv <= 8) B200_LAUNCH_RN(8);
+  else if (nv <= 16) B200_LAUNCH_RN(16);
+  else B200_LAUNCH_RN(32);
+#undef B200_LAUNCH_RN
   B200_CHECK(cudaGetLastError());
   return 0;
 }

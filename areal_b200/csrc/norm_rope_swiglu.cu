@@ -236,6 +236,66 @@ __global__ void qknorm_rope_fwd_kernel(const __nv_bfloat16* __restrict__ qkv,
   reinterpret_cast<__nv_bfloat162*>(dst + 64)[lane] = __floats2bfloat162_rn(ob.x, ob.y);
 }
 
+// Decode / prefill form of the kernel above: q is written out as before, k goes straight into the
+// paged K cache and v is copied into the paged V cache (`[page, kv head, slot in page, D]`), so the
+// separate cache-write launch disappears. One warp per (token, head) over q, k AND v heads.
+// slot_mapping[t] = page * block_size + offset, negative to skip the token's cache write.
+__global__ void qknorm_rope_kvwrite_kernel(const __nv_bfloat16* __restrict__ qkv, const __nv_bfloat16* __restrict__ qw,
+                                           const __nv_bfloat16* __restrict__ kw, const float* __restrict__ cos_t,
+                                           const float* __restrict__ sin_t, const int* __restrict__ pos,
+                                           __nv_bfloat16* __restrict__ q_out,
+                                           const long long* __restrict__ slot_mapping,
+                                           __nv_bfloat16* __restrict__ k_cache, __nv_bfloat16* __restrict__ v_cache,
+                                           int T, int Hq, int Hkv, int block_size, float eps, int has_norm) {
+  constexpr int D = 128;
+  const int lane = threadIdx.x & 31;
+  const long long gw = (static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x) >> 5;
+  const int heads = Hq + 2 * Hkv;
+  if (gw >= static_cast<long long>(T) * heads) return;
+  const int t = static_cast<int>(gw / heads);
+  const int h = static_cast<int>(gw % heads);
+  const __nv_bfloat16* src = qkv + (static_cast<long long>(t) * heads + h) * D;
+  const bool is_q = h < Hq;
+  const bool is_v = h >= Hq + Hkv;
+  __nv_bfloat16* dst;
+  if (is_q) {
+    dst = q_out + (static_cast<long long>(t) * Hq + h) * D;
+  } else {
+    const long long slot = slot_mapping[t];
+    if (slot < 0) return;
+    const long long blk = slot / block_size, off = slot % block_size;
+    const int hk = is_v ? h - Hq - Hkv : h - Hq;
+    dst = (is_v ? v_cache : k_cache) + ((blk * Hkv + hk) * block_size + off) * D;
+  }
+  if (is_v) {
+    reinterpret_cast<uint2*>(dst)[lane] = reinterpret_cast<const uint2*>(src)[lane];
+    return;
+  }
+  const __nv_bfloat16* w = is_q ? qw : kw;
+  float2 a = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src)[lane]);
+  float2 b = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(src + 64)[lane]);
+  if (has_norm) {
+    float ss = warp_sum(a.x * a.x + a.y * a.y + b.x * b.x + b.y * b.y);
+    const float rs = rsqrtf(ss / D + eps);
+    float2 wa = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(w)[lane]);
+    float2 wb = __bfloat1622float2(reinterpret_cast<const __nv_bfloat162*>(w + 64)[lane]);
+    a.x = __bfloat162float(__float2bfloat16(a.x * rs * wa.x));
+    a.y = __bfloat162float(__float2bfloat16(a.y * rs * wa.y));
+    b.x = __bfloat162float(__float2bfloat16(b.x * rs * wb.x));
+    b.y = __bfloat162float(__float2bfloat16(b.y * rs * wb.y));
+  }
+  const int p = pos[t];
+  const float2 c = reinterpret_cast<const float2*>(cos_t + static_cast<long long>(p) * 64)[lane];
+  const float2 s = reinterpret_cast<const float2*>(sin_t + static_cast<long long>(p) * 64)[lane];
+  float2 oa, ob;
+  oa.x = a.x * c.x - b.x * s.x;
+  oa.y = a.y * c.y - b.y * s.y;
+  ob.x = b.x * c.x + a.x * s.x;
+  ob.y = b.y * c.y + a.y * s.y;
+  reinterpret_cast<__nv_bfloat162*>(dst)[lane] = __floats2bfloat162_rn(oa.x, oa.y);
+  reinterpret_cast<__nv_bfloat162*>(dst + 64)[lane] = __floats2bfloat162_rn(ob.x, ob.y);
+}
+
 // Backward: un-rotate dq/dk, then per-head RMSNorm backward; writes into the
 // q and k slots of dqkv and accumulates dqw / dkw [D] with atomics (fp32).
 __global__ void qknorm_rope_bwd_kernel(const __nv_bfloat16* __restrict__ dq,
@@ -431,6 +491,26 @@ int b200_qknorm_rope_fwd(const void* qkv, const void* qw, const void* kw, const 
   qknorm_rope_fwd_kernel<<<(unsigned)grid, tpb, 0, stream>>>(
       (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, cos_t, sin_t,
       pos, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_out, rstd, T, Hq, Hkv, eps, has_norm);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// q/k norm + RoPE of a fused qkv projection whose k and v go straight into the paged KV caches
+// ([num_blocks, Hkv, block_size, 128] bf16) at slot_mapping[t] (int64; negative = skip).
+int b200_qknorm_rope_kvwrite(const void* qkv, const void* qw, const void* kw, const float* cos_t,
+                             const float* sin_t, const int* pos, void* q_out, const long long* slot_mapping,
+                             void* k_cache, void* v_cache, int T, int Hq, int Hkv, int D, int block_size,
+                             float eps, int has_norm, cudaStream_t stream) {
+  using namespace b200;
+  if (D != 128) return -100;
+  if (T == 0) return 0;
+  const long long warps = static_cast<long long>(T) * (Hq + 2 * Hkv);
+  const int tpb = 256;
+  const long long grid = (warps * 32 + tpb - 1) / tpb;
+  qknorm_rope_kvwrite_kernel<<<(unsigned)grid, tpb, 0, stream>>>(
+      (const __nv_bfloat16*)qkv, (const __nv_bfloat16*)qw, (const __nv_bfloat16*)kw, cos_t, sin_t, pos,
+      (__nv_bfloat16*)q_out, slot_mapping, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, T, Hq, Hkv,
+      block_size, eps, has_norm);
   B200_CHECK(cudaGetLastError());
   return 0;
 }

@@ -24,7 +24,7 @@ import torch.nn.functional as F
 
 from ..ops import fused
 from ..ops.attention import VarlenMeta, varlen_attention
-from ..ops.gemm import gemm, linear
+from ..ops.gemm import gemm, linear, linear_rmsnorm
 from ..ops.rollout_ops import kv_cache_write, paged_decode
 from .config import ModelConfig
 
@@ -81,6 +81,20 @@ class Attention(nn.Module):
             qkv = qkv + self.lora_qkv(x)
         return fused.qknorm_rope(qkv, self.q_norm, self.k_norm, cos, sin, pos,
                                  self.n_q, self.n_kv, cfg.head_dim, cfg.rms_norm_eps)
+
+    def project_q_write_kv(self, x, cos, sin, pos, slot_mapping, k_cache, v_cache):
+        """Decode-step form of :meth:`project_qkv`: returns ``q`` only; the normalised, rotated ``k`` and
+        ``v`` go into the paged caches inside the same kernel (no separate cache-write launch)."""
+        cfg = self.cfg
+        if self._tp() is not None:
+            q, k, v = self.project_qkv(x, cos, sin, pos)
+            kv_cache_write(k, v, slot_mapping, k_cache, v_cache)
+            return q
+        qkv = _dense(x, self.qkv, self.qkv_bias, cfg)
+        if self.lora_qkv is not None:
+            qkv = qkv + self.lora_qkv(x)
+        return fused.qknorm_rope_kvwrite(qkv, self.q_norm, self.k_norm, cos, sin, pos, self.n_q, self.n_kv,
+                                         cfg.head_dim, cfg.rms_norm_eps, slot_mapping, k_cache, v_cache)
 
     def _fused_ulysses(self, x, cos, sin, pos, meta, attn_fn=None):
         """Ulysses with the projection and the sequence→head exchange fused into one kernel: the
@@ -452,19 +466,39 @@ class QwenModel(nn.Module):
         pos = position_ids.to(torch.int32)
         x = F.embedding(input_ids.long(), self.embed)
         res = None
+        y = None  # normalised input of the next block, when the previous projection already produced it
+        # A block of a plain dense model runs 9 kernels here instead of 13: k/v go into the cache from the
+        # q/k-norm + RoPE kernel, and each residual add + RMSNorm runs inside the split-K reduction of the
+        # projection in front of it (o-proj → post-norm, down-proj → the next block's input norm).
+        tp1 = self.pctx is None or self.pctx.tp_size == 1
+        plain = tp1 and not self.cfg.fp8 and not self.cfg.is_hybrid
+        n_layers = len(self.layers)
         for i, layer in enumerate(self.layers):
-            if res is None:
-                y, res = fused.rmsnorm(x, layer.input_norm, layer.eps), x
-            else:
-                y, res = fused.rmsnorm(x, layer.input_norm, layer.eps, residual=res)
-            q, k, v = layer.attn.project_qkv(y, cos, sin, pos)
-            kv_cache_write(k, v, slot_mapping, kv_caches[i][0], kv_caches[i][1])
+            if y is None:
+                if res is None:
+                    y, res = fused.rmsnorm(x, layer.input_norm, layer.eps), x
+                else:
+                    y, res = fused.rmsnorm(x, layer.input_norm, layer.eps, residual=res)
+            q = layer.attn.project_q_write_kv(y, cos, sin, pos, slot_mapping, kv_caches[i][0], kv_caches[i][1])
             a = paged_decode(q, kv_caches[i][0], kv_caches[i][1], block_table, seq_lens,
                              max_seq_len=max_seq_len)
-            a = linear(a.reshape(a.shape[0], -1), layer.attn.o)
-            y, res = fused.rmsnorm(a, layer.post_norm, layer.eps, residual=res)
-            x = layer.mlp(y)
-        y, _ = fused.rmsnorm(x, self.norm, self.cfg.rms_norm_eps, residual=res)
+            a = a.reshape(a.shape[0], -1)
+            if plain and layer.attn.lora_o is None:
+                y, res = linear_rmsnorm(a, layer.attn.o, layer.post_norm, layer.eps, res)
+            else:
+                y, res = fused.rmsnorm(linear(a, layer.attn.o), layer.post_norm, layer.eps, residual=res)
+            m = layer.mlp
+            if plain and isinstance(m, DenseMLP) and m.lora_gate_up is None and m.lora_down is None:
+                nxt_w, nxt_eps = ((self.layers[i + 1].input_norm, self.layers[i + 1].eps) if i + 1 < n_layers
+                                  else (self.norm, self.cfg.rms_norm_eps))
+                h = fused.swiglu(linear(y, m.gate_up))
+                y, res = linear_rmsnorm(h, m.down, nxt_w, nxt_eps, res)
+                x = None
+            else:
+                x = m(y)
+                y = None
+        if y is None:
+            y, _ = fused.rmsnorm(x, self.norm, self.cfg.rms_norm_eps, residual=res)
         return y
 
     # ------------------------------------------------------ HF name mapping

@@ -183,6 +183,30 @@ def qknorm_rope(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps=1e-6):
     return qknorm_rope_ref(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps)
 
 
+@torch.no_grad()
+def qknorm_rope_kvwrite(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps, slot_mapping, k_cache, v_cache):
+    """Inference form of :func:`qknorm_rope`: returns ``q [T, Hq, D]`` and writes the normalised,
+    rotated ``k`` and the raw ``v`` into the paged caches ``[num_blocks, Hkv, block_size, D]`` at
+    ``slot_mapping [T]`` (int64, negative = skip) in the same kernel."""
+    if not (_lib.use_cuda_kernels(qkv, k_cache) and qkv.dtype == torch.bfloat16 and D == 128 and qkv.is_contiguous()):
+        from .rollout_ops import kv_cache_write
+
+        q, k, v = qknorm_rope(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps)
+        kv_cache_write(k, v, slot_mapping, k_cache, v_cache)
+        return q
+    T = qkv.shape[0]
+    q = torch.empty((T, Hq, D), dtype=qkv.dtype, device=qkv.device)
+    slots = slot_mapping if slot_mapping.dtype == torch.int64 else slot_mapping.to(torch.int64)
+    rc = _lib.kernels().b200_qknorm_rope_kvwrite(
+        _lib.ptr(qkv), _lib.ptr(qw), _lib.ptr(kw), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), _lib.ptr(q),
+        _lib.ptr(slots.contiguous()), _lib.ptr(k_cache), _lib.ptr(v_cache), ctypes.c_int(T), ctypes.c_int(Hq),
+        ctypes.c_int(Hkv), ctypes.c_int(D), ctypes.c_int(k_cache.shape[2]), ctypes.c_float(eps),
+        ctypes.c_int(int(qw is not None)), _lib.stream_ptr())
+    _lib.check(rc, "b200_qknorm_rope_kvwrite")
+    _lib.count_launch()
+    return q
+
+
 # --------------------------------------------------------------------------- SwiGLU
 
 

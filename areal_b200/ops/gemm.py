@@ -124,6 +124,47 @@ def gemm(
     return out
 
 
+def _splitk_plan(M: int, N: int, K: int) -> int:
+    """Number of K splits the skinny-GEMM path uses for this shape (0: not a split-K shape)."""
+    if M > 512 or N % 4 or K < 1024:
+        return 0
+    tiles = -(-M // 128) * -(-N // 128)
+    splits = min(8, 148 // tiles, K // 256)
+    return splits if splits >= 2 else 0
+
+
+@torch.no_grad()
+def linear_rmsnorm(x: torch.Tensor, w: torch.Tensor, norm_w: torch.Tensor, eps: float,
+                   residual: torch.Tensor | None = None):
+    """``h = x @ w.T (+ residual)``; returns ``(rmsnorm(h) * norm_w, h)``: a decoder block's projection,
+    residual add and following norm. For skinny (decode-step) shapes the residual add and the norm
+    run inside the split-K reduction kernel (two launches instead of three, bit-identical results);
+    other shapes run the separate kernels. Inference only."""
+    from . import fused
+
+    M, K = x.shape
+    N = w.shape[0]
+    splits = _splitk_plan(M, N, K) if (_lib.use_cuda_kernels(x, w) and x.dtype == torch.bfloat16) else 0
+    ok = (splits and N % 8 == 0 and N <= 8192 and K % 8 == 0 and x.stride(1) == 1 and w.stride(1) == 1
+          and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+          and (residual is None or residual.is_contiguous()) and norm_w.is_contiguous())
+    if not ok:
+        a = linear(x, w)
+        if residual is None:
+            return fused.rmsnorm(a, norm_w, eps), a
+        return fused.rmsnorm(a, norm_w, eps, residual=residual)
+    ws = torch.empty((splits * -(-M // 128) * 128, N), dtype=torch.float32, device=x.device)
+    y = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    res_out = torch.empty((M, N), dtype=x.dtype, device=x.device)
+    rc = _lib.kernels().b200_gemm_bf16_splitk_rmsnorm(
+        _lib.ptr(x), _lib.ptr(w), None, _lib.ptr(ws), ctypes.c_int(M), ctypes.c_int(N), ctypes.c_int(K),
+        ctypes.c_longlong(x.stride(0)), ctypes.c_longlong(w.stride(0)), ctypes.c_int(splits), _lib.ptr(residual),
+        _lib.ptr(norm_w), _lib.ptr(y), _lib.ptr(res_out), ctypes.c_float(eps), _lib.stream_ptr())
+    _lib.check(rc, "b200_gemm_bf16_splitk_rmsnorm")
+    _lib.count_launch(2)
+    return y, res_out
+
+
 class _Linear(torch.autograd.Function):
     @staticmethod
     def forward(ctx, x, w, bias):

@@ -154,3 +154,53 @@ def test_sampler():
     freq = torch.bincount(toks.long(), minlength=64).float() / n
     p = torch.softmax(row[0], -1)
     assert (freq - p).abs().max().item() < 0.02
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,N,with_res", [(64, 2048, 2048, True), (200, 6144, 2048, True), (7, 2048, 2048, False),
+                                            (256, 1024, 1024, True), (300, 256, 2048, True)])
+def test_linear_rmsnorm_matches_separate_kernels(M, K, N, with_res):
+    """Residual add + RMSNorm inside the split-K reduction: bit-identical to projection, then norm
+    (the last shape does not split and takes the separate kernels)."""
+    from areal_b200.ops import fused
+    from areal_b200.ops.gemm import linear, linear_rmsnorm
+
+    torch.manual_seed(M + N)
+    x = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.05).bfloat16()
+    nw = (1 + 0.1 * torch.randn(N, device="cuda")).bfloat16()
+    res = torch.randn(M, N, device="cuda").bfloat16() if with_res else None
+    y, h = linear_rmsnorm(x, w, nw, 1e-6, res)
+    a = linear(x, w)
+    if with_res:
+        y_ref, h_ref = fused.rmsnorm(a, nw, 1e-6, residual=res)
+    else:
+        y_ref, h_ref = fused.rmsnorm(a, nw, 1e-6), a
+    assert torch.equal(h, h_ref) and torch.equal(y, y_ref)
+    hf = (x.float() @ w.float().t()) + (res.float() if with_res else 0)
+    yf = hf * torch.rsqrt(hf.pow(2).mean(-1, keepdim=True) + 1e-6) * nw.float()
+    assert float((y.float() - yf).abs().max()) < 0.06 * float(yf.abs().max())
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("has_norm", [True, False])
+def test_qknorm_rope_kvwrite_matches_separate_kernels(has_norm):
+    from areal_b200.ops import fused
+    from areal_b200.ops.rollout_ops import kv_cache_write
+
+    torch.manual_seed(3)
+    T, Hq, Hkv, D, bs, nb = 37, 16, 8, 128, 16, 12
+    qkv = torch.randn(T, (Hq + 2 * Hkv) * D, device="cuda").bfloat16()
+    qw = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16() if has_norm else None
+    kw = (1 + 0.1 * torch.randn(D, device="cuda")).bfloat16() if has_norm else None
+    cos, sin = fused.rope_tables(512, D, 1e6, "cuda")
+    pos = torch.randint(0, 512, (T,), device="cuda", dtype=torch.int32)
+    slots = torch.randperm(nb * bs, device="cuda")[:T].to(torch.int64)
+    slots[5] = -1  # a padded row of a captured batch: no cache write
+    kc1, vc1 = (torch.zeros(nb, Hkv, bs, D, device="cuda", dtype=torch.bfloat16) for _ in range(2))
+    kc2, vc2 = torch.zeros_like(kc1), torch.zeros_like(vc1)
+    q1 = fused.qknorm_rope_kvwrite(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, 1e-6, slots, kc1, vc1)
+    q2, k2, v2 = fused.qknorm_rope(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, 1e-6)
+    kv_cache_write(k2, v2, slots, kc2, vc2)
+    assert torch.equal(q1, q2) and torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert float(kc1.abs().sum()) > 0
