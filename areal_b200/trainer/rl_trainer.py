@@ -100,14 +100,20 @@ class PPOTrainer:
         self.actor_alloc = ModelAllocation.from_str(config.actor.backend)
         self.rollout_alloc = ModelAllocation.from_str(config.rollout.backend)
         n_train, n_gen = self.actor_alloc.world_size, self.rollout_alloc.world_size
-        self.colocated = self.world == 1 or (n_train == self.world and n_gen == self.world)
+        # External rollout servers (this repo's HTTP server on other nodes, SGLang, vLLM): every rank of
+        # this job trains, generation goes over HTTP and weights travel through a checkpoint directory.
+        self.external_rollout = (self.rollout_alloc.backend in ("sglang", "vllm")
+                                 or bool(os.environ.get("AREAL_LLM_SERVER_ADDRS")))
+        if self.external_rollout:
+            n_gen = 0
+        self.colocated = not self.external_rollout and (self.world == 1 or (n_train == self.world and n_gen == self.world))
         if not self.colocated and n_train + n_gen != self.world:
             raise ValueError(f"allocation {config.rollout.backend}+{config.actor.backend} needs "
                              f"{n_train + n_gen} ranks, world size is {self.world}")
-        self.topo = None if self.colocated else DisaggTopology(n_gen, n_train)
-        self.is_trainer = self.colocated or not self.topo.is_rollout
-        self.is_rollout = self.colocated or self.topo.is_rollout
-        train_ranks = list(range(self.world)) if self.colocated else self.topo.train_ranks
+        self.topo = None if (self.colocated or self.external_rollout) else DisaggTopology(n_gen, n_train)
+        self.is_trainer = self.colocated or self.external_rollout or not self.topo.is_rollout
+        self.is_rollout = not self.external_rollout and (self.colocated or self.topo.is_rollout)
+        train_ranks = list(range(self.world)) if self.topo is None else self.topo.train_ranks
         dp = len(train_ranks)
         bs = config.train_dataset.batch_size
         self.ft_spec = FinetuneSpec(total_train_epochs=config.total_train_epochs,
@@ -139,7 +145,15 @@ class PPOTrainer:
                 self.ref_engine = B200TrainEngine(config.ref)
                 self.ref_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks, groups=shared)
                 self.ref_engine.initialize(None, self.ft_spec, seed=config.seed)
-        if self.colocated:
+        if self.external_rollout:
+            from ..infra.remote_inf_engine import RemoteInfEngine
+
+            rcfg = config.rollout
+            rcfg.consumer_batch_size = bs
+            self.rollout_client = RemoteInfEngine(rcfg).initialize(train_data_parallel_size=dp)
+            self.weight_meta = WeightUpdateMeta(type="disk", path=os.path.join(
+                config.cluster.fileroot, "weight_update", str(config.experiment_name), str(config.trial_name)))
+        elif self.colocated:
             self.rollout_client = self.rollout
             self.weight_meta = WeightUpdateMeta.from_p2p()
         else:
@@ -157,9 +171,10 @@ class PPOTrainer:
         self.evaluator = Evaluator(config.evaluator, self.ft_spec)
         self.recover = RecoverHandler(config.recover, self.ft_spec)
         self.stats_logger = StatsLogger(config, self.ft_spec) if self.rank == train_ranks[0] else None
-        gen_rank = self.rank if self.colocated else (self.rank if self.is_rollout else 0)
-        gen_world = self.world if self.colocated else n_gen
-        self.dataloader = _ListLoader(train_dataset, self.per_rank_bs if self.colocated else max(bs // gen_world, 1),
+        local_gen = self.colocated or self.external_rollout  # this rank asks for its own share of every batch
+        gen_rank = self.rank if local_gen else (self.rank if self.is_rollout else 0)
+        gen_world = self.world if local_gen else n_gen
+        self.dataloader = _ListLoader(train_dataset, self.per_rank_bs if local_gen else max(bs // gen_world, 1),
                                       config.train_dataset.shuffle, config.seed, gen_rank, gen_world)
         self.step_times: list[float] = []
         self.trained_tokens = 0
@@ -176,7 +191,9 @@ class PPOTrainer:
         self.close()
 
     def close(self):
-        if self.rollout_client is not None and not self.colocated:
+        if self.rollout_client is not None and self.external_rollout:
+            self.rollout_client.destroy()
+        elif self.rollout_client is not None and not self.colocated:
             self.rollout_client.stop()
         if self.rollout is not None:
             self.rollout.destroy()

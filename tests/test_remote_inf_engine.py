@@ -200,3 +200,46 @@ def test_launch_server_subprocess():
     finally:
         cli.destroy()
     assert info.process.poll() is not None  # torn down with the client
+
+
+def test_trainer_with_external_http_server(tmp_path, monkeypatch):
+    """PPOTrainer against a rollout server reached over HTTP: generation through RemoteInfEngine, weights
+    through a checkpoint directory, versions bumped on the server after every step."""
+    from areal_b200.api.cli_args import (GRPOConfig, MicroBatchSpec, NormConfig, OptimizerConfig, PPOActorConfig,
+                                         _propagate_names)
+    from areal_b200.trainer.rl_trainer import PPOTrainer
+    from areal_b200.workflow.rlvr import RLVRWorkflow
+
+    srv = _Server(0)
+    try:
+        monkeypatch.setenv("AREAL_LLM_SERVER_ADDRS", srv.addr)
+        cfg = GRPOConfig(experiment_name="ext", trial_name="t")
+        cfg.cluster.fileroot = str(tmp_path)
+        cfg.train_dataset.batch_size = 4
+        cfg.train_dataset.shuffle = False
+        cfg.gconfig = GenerationHyperparameters(n_samples=2, max_new_tokens=8, temperature=1.0, ignore_eos=True)
+        cfg.actor = PPOActorConfig(backend="fsdp:d1", model_preset="tiny-qwen2", init_from_scratch=True,
+                                   optimizer=OptimizerConfig(lr=1e-3, warmup_steps_proportion=0.0),
+                                   mb_spec=MicroBatchSpec(max_tokens_per_mb=1024), ppo_n_minibatches=1,
+                                   reward_norm=NormConfig(mean_level="group", std_level="group", group_size=2),
+                                   kl_ctl=0.0, use_decoupled_loss=True, recompute_logprob=True)
+        cfg.rollout = InferenceEngineConfig(backend="native:d1", max_head_offpolicyness=0, max_concurrent_rollouts=16,
+                                            setup_timeout=30.0, request_timeout=60.0)
+        _propagate_names(cfg)
+        g = torch.Generator().manual_seed(0)
+        ds = [dict(input_ids=torch.randint(0, 1024, (12,), generator=g).tolist()) for _ in range(16)]
+        before = srv.engine.flat.flat.clone()
+        seen = []
+        with PPOTrainer(cfg, ds) as tr:
+            assert tr.external_rollout and tr.rollout is None
+            tr.train(workflow=RLVRWorkflow, workflow_kwargs=dict(
+                reward_fn=lambda p, c, pi, ci, **kw: float(sum(ci) % 2), gconfig=cfg.gconfig, reward_in_process=True),
+                max_steps=2, step_callback=lambda s, st: seen.append(st))
+            trained = tr.actor_engine.flat.flat.clone()
+        assert len(seen) == 2 and all(s["step/trained_tokens"] > 0 for s in seen)
+        assert srv.engine.get_version() == 2
+        n = min(trained.numel(), srv.engine.flat.flat.numel())
+        assert torch.allclose(srv.engine.flat.flat[:n].float(), trained[:n].float(), atol=1e-6)
+        assert not torch.equal(srv.engine.flat.flat, before)
+    finally:
+        srv.stop()
