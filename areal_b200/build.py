@@ -124,8 +124,13 @@ def build(force: bool = False, verbose: bool = False, ptxas_info: bool = False) 
     return out
 
 
-if __name__ == "__main__":
-    libs = build(force="--force" in sys.argv, verbose="-v" in sys.argv,
-                 ptxas_info="--ptxas" in sys.argv)
+def main(argv: list[str] | None = None) -> int:
+    argv = sys.argv[1:] if argv is None else argv
+    libs = build(force="--force" in argv, verbose="-v" in argv, ptxas_info="--ptxas" in argv)
     for k, v in libs.items():
         print(f"{k}: {v}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

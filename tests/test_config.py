@@ -81,3 +81,10 @@ def test_defaults_match_documented_surface():
     assert a.should_compute_prox_logp() is False
     assert C.PPOActorConfig(use_decoupled_loss=True).should_compute_prox_logp() is True
     assert C.PPOActorConfig(use_decoupled_loss=True, prox_logp_method="loglinear").should_compute_prox_logp() is False
+
+
+def test_cli_reference_is_current():
+    """docs/cli_reference.md is generated from the dataclasses; regenerate it when a field changes."""
+    from areal_b200.tools import gen_cli_reference
+
+    assert gen_cli_reference.main(["--check"]) == 0
