@@ -84,3 +84,27 @@ def test_trace_converter_cli_and_engine_profiler(tmp_path, capsys):
     text = capsys.readouterr().out
     rep = json.loads(text[text.index("{"):])
     assert rep["tokens_per_step"] == 256 and rep["train"]["tokens_per_s"] > 0 and rep["forward"]["ms_per_step"] > 0
+
+
+def test_session_trace_summary_and_timeline(tmp_path, capsys):
+    import json
+
+    from areal_b200.tools import plot_session_trace
+    from areal_b200.utils.perf_tracer import SessionTracer
+
+    tr = SessionTracer(None, str(tmp_path), rank=0)
+    for k in range(3):
+        sid = tr.start_session(task_id=k)
+        with tr.phase(sid, "generate"):
+            pass
+        with tr.phase(sid, "reward"):
+            pass
+        tr.end_session(sid, status="accepted" if k < 2 else "rejected")
+    tr.flush(force=True)
+    recs = plot_session_trace.load(str(tmp_path))
+    s = plot_session_trace.summarize(recs)
+    assert s["sessions"] == 3 and s["status"] == {"accepted": 2, "rejected": 1}
+    assert set(s["phases"]) == {"generate", "reward"} and s["phases"]["generate"]["n"] == 3
+    assert plot_session_trace.main([str(tmp_path)]) == 0
+    page = open(tmp_path / "sessions.html").read()
+    assert page.count("<rect") == 9 and "generate" in page and "#d00" in page
