@@ -188,15 +188,25 @@ class WorkflowExecutor:
         return tid
 
     async def _episode(self, wf: RolloutWorkflow, data, should_accept_fn):
+        from ..utils import perf_tracer
+
         accepted = False
+        st = perf_tracer.get_session_tracer() if self.config.enable_rollout_tracing else None
+        sid = st.start_session() if st is not None else None
         try:
-            traj = await wf.arun_episode(self.engine, data)
+            if st is not None:
+                with st.phase(sid, "episode"):
+                    traj = await wf.arun_episode(self.engine, data)
+            else:
+                traj = await wf.arun_episode(self.engine, data)
             if self.config.check_trajectory_format:
                 check_trajectory_format(traj)
             traj = _to_tensor_dict(traj)
             accepted = traj is not None and (should_accept_fn is None or bool(should_accept_fn(traj)))
             return traj if accepted else None
         finally:
+            if st is not None:
+                st.end_session(sid, status="accepted" if accepted else "rejected")
             if accepted:
                 self.staleness.on_rollout_accepted()
             else:

@@ -178,6 +178,9 @@ class PPOTrainer:
                                       config.train_dataset.shuffle, config.seed, gen_rank, gen_world)
         self.step_times: list[float] = []
         self.trained_tokens = 0
+        from ..utils.step_profiling import StepProfiling
+
+        self.profiling = StepProfiling(config, self.rank, "trainer" if self.is_trainer else "rollout")
         if self.rank == train_ranks[0]:
             try:
                 save_config(config, get_log_path(config))
@@ -202,6 +205,7 @@ class PPOTrainer:
                 e.destroy()
         if self.stats_logger is not None:
             self.stats_logger.close()
+        self.profiling.close()
 
     def _next_batch(self, workflow, workflow_kwargs, group):
         """The next training batch of this rank. Under tensor / sequence / pipeline parallelism only
@@ -247,9 +251,10 @@ class PPOTrainer:
         for global_step in range(start, total):
             t_step = time.perf_counter()
             epoch, epoch_step = divmod(global_step, steps_per_epoch)
-            with stats_tracker.record_timing("rollout"):
-                batch = self._next_batch(workflow, workflow_kwargs, group)
-            stats = self.train_step(batch, global_step)
+            with self.profiling.step(global_step):
+                with stats_tracker.record_timing("rollout"):
+                    batch = self._next_batch(workflow, workflow_kwargs, group)
+                stats = self.train_step(batch, global_step)
             self.step_times.append(time.perf_counter() - t_step)
             with stats_tracker.record_timing("save"):
                 self.saver.save(self.actor_engine, epoch, epoch_step, global_step)

@@ -85,6 +85,9 @@ class _SLTrainer:
         self.recover = RecoverHandler(config.recover, self.ft_spec)
         self.stats_logger = StatsLogger(config, self.ft_spec) if self.rank == 0 else None
         self.wrapper = self._make_wrapper(actor_cfg)
+        from ..utils.step_profiling import StepProfiling
+
+        self.profiling = StepProfiling(config, self.rank, "trainer")
 
     def _make_wrapper(self, actor_cfg):
         raise NotImplementedError
@@ -105,6 +108,7 @@ class _SLTrainer:
         self.engine.destroy()
         if self.stats_logger is not None:
             self.stats_logger.close()
+        self.profiling.close()
 
     def train(self, max_steps: int | None = None, step_callback=None):
         cfg = self.config
@@ -124,7 +128,7 @@ class _SLTrainer:
                 if step >= total:
                     return
                 batch = self.collate(items)
-                with stats_tracker.record_timing("train_step"):
+                with self.profiling.step(step), stats_tracker.record_timing("train_step"):
                     st = self._train_step(batch)
                 self.engine.set_version(step + 1)
                 with stats_tracker.record_timing("save"):

@@ -57,9 +57,12 @@ class DistributedStatsTracker:
 
     @contextmanager
     def record_timing(self, key: str):
+        from . import perf_tracer  # every timed phase is also a scope of the perf trace (when one is configured)
+
         t0 = time.perf_counter()
         try:
-            yield
+            with perf_tracer.trace_scope(key, perf_tracer.Category.COMPUTE):
+                yield
         finally:
             self._scalars["/".join(["timeperf", key])].append(time.perf_counter() - t0)
             self._reduce.setdefault("timeperf/" + key, ReduceType.SCALAR)

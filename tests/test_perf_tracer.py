@@ -108,3 +108,40 @@ def test_session_trace_summary_and_timeline(tmp_path, capsys):
     assert plot_session_trace.main([str(tmp_path)]) == 0
     page = open(tmp_path / "sessions.html").read()
     assert page.count("<rect") == 9 and "generate" in page and "#d00" in page
+
+
+def test_trainer_writes_perf_trace_sessions_and_torch_profile(tmp_path):
+    """With `perf_tracer.enabled`, a trainer run leaves a per-rank trace with its timed phases, a torch
+    profile for the configured step, and (with rollout tracing on) one session per episode."""
+    import glob
+    import json
+    import math
+
+    import torch
+
+    from areal_b200.api.cli_args import (MicroBatchSpec, OptimizerConfig, PerfTracerConfig, SFTConfig,
+                                         TrainEngineConfig, _propagate_names)
+    from areal_b200.trainer.sl_trainer import SFTTrainer
+
+    g = torch.Generator().manual_seed(0)
+    data = [dict(input_ids=torch.randint(0, 1024, (16,), generator=g).tolist(), loss_mask=[0] * 4 + [1] * 12)
+            for _ in range(8)]
+    cfg = SFTConfig(actor=TrainEngineConfig(backend="fsdp:d1", model_preset="tiny-qwen2", init_from_scratch=True,
+                                            optimizer=OptimizerConfig(lr=1e-3, warmup_steps_proportion=0.0),
+                                            mb_spec=MicroBatchSpec(max_tokens_per_mb=512)))
+    cfg.experiment_name, cfg.trial_name = "pt", "t"
+    cfg.cluster.fileroot = str(tmp_path)
+    cfg.train_dataset.batch_size = 4
+    cfg.total_train_epochs = 2
+    cfg.perf_tracer = PerfTracerConfig(enabled=True, save_interval=1, profile_steps=[1])
+    _propagate_names(cfg)
+    with SFTTrainer(cfg, data) as tr:
+        tr.train(max_steps=3)
+    traces = glob.glob(str(tmp_path / "**" / "traces-r0.jsonl"), recursive=True)
+    assert len(traces) == 1
+    events = [json.loads(line) for line in open(traces[0])]
+    names = {e["name"] for e in events}
+    assert {"train_step", "train_step_0", "train_step_2"} <= names
+    assert all(math.isfinite(e.get("dur", 0.0)) for e in events)
+    profs = glob.glob(str(tmp_path / "**" / "torch_profile_step1_r0.json"), recursive=True)
+    assert len(profs) == 1 and os.path.getsize(profs[0]) > 1000
