@@ -275,6 +275,19 @@ class RemoteInfEngine(InferenceEngine):
                              output_versions=out_versions, stop_reason=stop_reason, tokenizer=req.tokenizer,
                              latency=time.perf_counter() - t0, ttft=ttft)
 
+    def generate(self, req: ModelRequest) -> ModelResponse:
+        """Blocking form for callers without an event loop: runs one private loop and closes the HTTP
+        session that belongs to it (sessions are per loop)."""
+        from .workflow_context import close_clients
+
+        async def run():
+            try:
+                return await self.agenerate(req)
+            finally:
+                await close_clients()
+
+        return asyncio.run(run())
+
     # -------------------------------------------------------------- control
     def _fanout(self, http: HttpRequest | None, timeout: float | None = None) -> list[Any]:
         if http is None:
