@@ -264,9 +264,6 @@ class NativeRolloutEngine(InferenceEngine):
             setattr(mc, k, v)
         self.model_config = mc
         dtype = torch.float32 if self.device.type == "cpu" else getattr(torch, ncfg.dtype)
-        if mc.is_hybrid:
-            raise NotImplementedError("the native rollout engine serves full-attention models; hybrid (linear-attention) "
-                                      "models train and score through the train engine only")
         self.model = build_model(mc, dtype=dtype, device=self.device, seed=ncfg.seed)
         if ncfg.model_path:
             from ..utils.hf_io import load_hf_weights
@@ -280,13 +277,21 @@ class NativeRolloutEngine(InferenceEngine):
         bs = ncfg.kv_block_size
         max_blocks_per_seq = (ncfg.context_length + bs - 1) // bs
         nblocks = ncfg.num_kv_blocks or self._auto_num_blocks(mc, dtype, bs)
-        self.kv_caches = [
-            (torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device),
-             torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device))
-            for _ in range(mc.num_hidden_layers)]
+        self.kv_caches = self._alloc_kv(nblocks, dtype)
         self.sched = PagedScheduler(nblocks, bs, ncfg.max_num_seqs, ncfg.max_num_batched_tokens,
                                     max_blocks_per_seq)
-        self.sched.set_prompt_sharing(bool(getattr(ncfg, "prompt_sharing", True)))
+        # Hybrid models: per-sequence state of the linear-attention layers, addressed by a slot that a
+        # request keeps from its first prefill until it finishes. Prompts are not shared (a shared page
+        # says nothing about the recurrent state) and decode steps run eagerly.
+        self.hybrid_state = None
+        self._state_slot: dict[int, int] = {}
+        self._free_state_slots: list[int] = []
+        if mc.is_hybrid:
+            from ..models.qwen3_5 import HybridState
+
+            self.hybrid_state = HybridState(mc, ncfg.max_num_seqs, dtype, self.device)
+            self._free_state_slots = list(range(ncfg.max_num_seqs - 1, -1, -1))
+        self.sched.set_prompt_sharing(bool(getattr(ncfg, "prompt_sharing", True)) and not mc.is_hybrid)
         # The engine thread shares the interpreter with trainer / workflow threads; CPython hands the GIL over
         # every 5 ms by default, which is half a decode step. A shorter interval keeps the step loop's short
         # host phases from queueing behind another thread's Python.
@@ -298,7 +303,8 @@ class NativeRolloutEngine(InferenceEngine):
         self._rng = torch.Generator(device=self.device).manual_seed(ncfg.seed)
         self._graphs = None
         self.launches_per_decode = 0
-        if self.device.type == "cuda" and ncfg.cuda_graph and _lib.use_cuda_kernels(next(self.model.parameters())):
+        if (self.device.type == "cuda" and ncfg.cuda_graph and not mc.is_hybrid
+                and _lib.use_cuda_kernels(next(self.model.parameters()))):
             self._capture_graphs()
         self._thread = threading.Thread(target=self._loop, name="rollout-engine", daemon=True)
         self._thread.start()
@@ -308,6 +314,22 @@ class NativeRolloutEngine(InferenceEngine):
         self._executor.initialize(train_data_parallel_size=train_data_parallel_size)
         logger.info(f"rollout engine ready on {self.device}: {nblocks} KV pages of {bs} tokens")
         return self
+
+    def _alloc_kv(self, nblocks: int, dtype):
+        """Paged K/V caches, one pair per layer (None for linear-attention layers of a hybrid model)."""
+        mc, bs = self.model_config, self.ncfg.kv_block_size
+        mk = lambda: torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device)
+        return [(mk(), mk()) if mc.layer_type(i) == "full_attention" else None for i in range(mc.num_hidden_layers)]
+
+    def _state_slots_of(self, seq_ids: list[int]):
+        """Slots of these requests in the hybrid state (assigned on first sight, freed when they finish)."""
+        out = []
+        for r in seq_ids:
+            slot = self._state_slot.get(r)
+            if slot is None:
+                slot = self._state_slot[r] = self._free_state_slots.pop()
+            out.append(slot)
+        return torch.tensor(out, dtype=torch.long, device=self.device)
 
     def _capture_graphs(self):
         t0 = time.perf_counter()
@@ -421,7 +443,9 @@ class NativeRolloutEngine(InferenceEngine):
         if kind == 1:
             cu = s.cu[: n + 1].copy()
             meta = VarlenMeta(cu.tolist(), dev)
-            hidden = self.model.prefill(ids, pos, meta, self.kv_caches, slots)
+            extra = dict(hybrid_state=self.hybrid_state, state_slots=self._state_slots_of(seq_ids)) \
+                if self.hybrid_state is not None else {}
+            hidden = self.model.prefill(ids, pos, meta, self.kv_caches, slots, **extra)
             last = torch.from_numpy((cu[1:] - 1).astype(np.int64)).to(dev)
             hidden = hidden.index_select(0, last)
         else:
@@ -429,8 +453,10 @@ class NativeRolloutEngine(InferenceEngine):
             bt = torch.from_numpy(s.block_table[: n * s.max_blocks_per_seq].copy()).view(n, -1)
             nb = (int(s.hdr.max_seq_len) + self.ncfg.kv_block_size - 1) // self.ncfg.kv_block_size
             bt = bt[:, :max(nb, 1)].contiguous().to(dev, non_blocking=True)
+            extra = dict(hybrid_state=self.hybrid_state, state_slots=self._state_slots_of(seq_ids)) \
+                if self.hybrid_state is not None else {}
             hidden = self.model.decode(ids, pos, self.kv_caches, bt, seq_lens, slots,
-                                       max_seq_len=int(s.hdr.max_seq_len))
+                                       max_seq_len=int(s.hdr.max_seq_len), **extra)
         logits = self.model.logits(hidden, out_dtype=torch.float32)
         with self._lock:
             pr = [self._params.get(r, (1.0, 0, 1.0)) for r in seq_ids]
@@ -451,7 +477,10 @@ class NativeRolloutEngine(InferenceEngine):
         """Private copies of the page holding a shared prompt's last positions (prompt forks)."""
         idx = torch.from_numpy(pairs.reshape(-1, 2).astype(np.int64)).to(self.device)
         src, dst = idx[:, 0], idx[:, 1]
-        for kc, vc in self.kv_caches:
+        for pair in self.kv_caches:
+            if pair is None:
+                continue
+            kc, vc = pair
             kc.index_copy_(0, dst, kc.index_select(0, src))
             vc.index_copy_(0, dst, vc.index_select(0, src))
 
@@ -461,6 +490,9 @@ class NativeRolloutEngine(InferenceEngine):
             if item is None:
                 return
             rid, reason, toks, lps = item
+            slot = self._state_slot.pop(rid, None)
+            if slot is not None:
+                self._free_state_slots.append(slot)
             with self._lock:
                 entry = self._pending.pop(rid, None)
                 self._params.pop(rid, None)
@@ -632,11 +664,9 @@ class NativeRolloutEngine(InferenceEngine):
             mc, bs = self.model_config, self.ncfg.kv_block_size
             dtype = next(self.model.parameters()).dtype
             nblocks = self.sched.stats()["free_blocks"]
-            self.kv_caches = [
-                (torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device),
-                 torch.zeros(nblocks, mc.num_key_value_heads, bs, mc.head_dim, dtype=dtype, device=self.device))
-                for _ in range(mc.num_hidden_layers)]
-            if self.device.type == "cuda" and self.ncfg.cuda_graph and _lib.use_cuda_kernels(next(self.model.parameters())):
+            self.kv_caches = self._alloc_kv(nblocks, dtype)
+            if (self.device.type == "cuda" and self.ncfg.cuda_graph and not self.model_config.is_hybrid
+                    and _lib.use_cuda_kernels(next(self.model.parameters()))):
                 self._capture_graphs()
         self.continue_generation()
 

@@ -436,9 +436,15 @@ class QwenModel(nn.Module):
 
     # -------------------------------------------------- rollout (paged cache)
     @torch.no_grad()
-    def prefill(self, input_ids, position_ids, meta: VarlenMeta, kv_caches, slot_mapping):
+    def prefill(self, input_ids, position_ids, meta: VarlenMeta, kv_caches, slot_mapping, hybrid_state=None,
+                state_slots=None):
         """Packed prompt forward that also writes K/V of every layer into the
-        paged caches; returns hidden states of all tokens."""
+        paged caches; returns hidden states of all tokens. Hybrid models also take the per-sequence
+        state of their linear-attention layers and the slot of every sequence in it."""
+        if self.cfg.is_hybrid:
+            from .qwen3_5 import hybrid_prefill
+
+            return hybrid_prefill(self, input_ids, position_ids, meta, kv_caches, slot_mapping, hybrid_state, state_slots)
         cos, sin = self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
         x = F.embedding(input_ids.long(), self.embed)
@@ -459,9 +465,14 @@ class QwenModel(nn.Module):
 
     @torch.no_grad()
     def decode(self, input_ids, position_ids, kv_caches, block_table, seq_lens, slot_mapping,
-               max_seq_len=None):
+               max_seq_len=None, hybrid_state=None, state_slots=None):
         """One new token per sequence: ``input_ids [B]`` at ``position_ids [B]``;
         ``seq_lens`` already counts the new token."""
+        if self.cfg.is_hybrid:
+            from .qwen3_5 import hybrid_decode
+
+            return hybrid_decode(self, input_ids, position_ids, kv_caches, block_table, seq_lens, slot_mapping,
+                                 hybrid_state, state_slots, max_seq_len)
         cos, sin = self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
         x = F.embedding(input_ids.long(), self.embed)

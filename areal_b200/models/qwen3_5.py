@@ -17,8 +17,13 @@ Kernels: the projections run on the tcgen05 GEMM, the convolution on ``csrc/line
 (forward and backward), the recurrence on its forward kernel when no gradient is needed and on the
 chunk-parallel form (``ops.linear_attn.linear_attn_chunked``) under autograd; attention with head
 dimension 128 runs the tcgen05 attention kernels, other head dimensions (Qwen3.5 ships 256) fall
-back to PyTorch scaled-dot-product attention per sequence. These layers train and score
-(log-probabilities, values); the rollout engine's paged decode does not serve hybrid models.
+back to PyTorch scaled-dot-product attention per sequence.
+
+Rollout: full-attention layers use the paged KV cache like every other family; a linear-attention
+layer keeps, per running sequence, its recurrent state ``S [heads, dk, dv]`` (fp32) and the last
+``K - 1`` inputs of its convolution (:class:`HybridState`). Prefill computes both from the prompt
+(the recurrence kernel returns its final state), a decode step advances them by one token with
+batched tensor ops (:func:`hybrid_prefill`, :func:`hybrid_decode`).
 
 Reference: areal/experimental/models/archon/qwen3_5/model/model.py (GatedDeltaNet :141-336,
 GatedAttention :344-470, norms :31-92), rope.py :90-126, state_dict_adapter.py :45-88.
@@ -35,7 +40,8 @@ import torch.nn.functional as F
 from ..ops import fused
 from ..ops.attention import VarlenMeta, attention_ref, varlen_attention
 from ..ops.gemm import linear
-from ..ops.linear_attn import causal_conv1d, linear_attn
+from ..ops.linear_attn import causal_conv1d, linear_attn, linear_attn_prefill, linear_attn_step
+from ..ops.rollout_ops import kv_cache_write, paged_decode
 from .config import ModelConfig
 
 
@@ -103,6 +109,42 @@ class GatedAttention(nn.Module):
         return linear(a.reshape(T, nq * D), self.o)
 
 
+    # -- rollout ------------------------------------------------------------------------------
+    def _qkv_gate(self, x, cos, sin, pos):
+        cfg = self.cfg
+        T, D, nq, nkv = x.shape[0], cfg.head_dim, self.n_q, self.n_kv
+        qkv = linear(x, self.qkv)
+        qg = qkv[:, :2 * nq * D].view(T, nq, 2 * D)
+        q, gate = qg[..., :D], qg[..., D:]
+        k = qkv[:, 2 * nq * D: (2 * nq + nkv) * D].view(T, nkv, D)
+        v = qkv[:, (2 * nq + nkv) * D:].view(T, nkv, D)
+        q = fused.rmsnorm_ref(q, self.q_norm, cfg.rms_norm_eps)
+        k = fused.rmsnorm_ref(k, self.k_norm, cfg.rms_norm_eps)
+        q = _partial_rope(q, cos, sin, pos, cfg.rotary_dim).contiguous()
+        k = _partial_rope(k, cos, sin, pos, cfg.rotary_dim).contiguous()
+        return q, k, v.contiguous(), gate
+
+    def _finish(self, a, gate, dtype):
+        a = (a.float() * torch.sigmoid(gate.float())).to(dtype)
+        return linear(a.reshape(a.shape[0], -1), self.o)
+
+    @torch.no_grad()
+    def prefill(self, x, cos, sin, pos, meta, slot_mapping, k_cache, v_cache):
+        q, k, v, gate = self._qkv_gate(x, cos, sin, pos)
+        kv_cache_write(k, v, slot_mapping, k_cache, v_cache)
+        D = self.cfg.head_dim
+        scale = 1.0 / math.sqrt(D)
+        a = varlen_attention(q, k, v, meta, scale) if D == 128 else _sdpa_varlen(q, k, v, meta, scale)
+        return self._finish(a, gate, x.dtype)
+
+    @torch.no_grad()
+    def decode(self, x, cos, sin, pos, k_cache, v_cache, block_table, seq_lens, slot_mapping, max_seq_len=None):
+        q, k, v, gate = self._qkv_gate(x, cos, sin, pos)
+        kv_cache_write(k, v, slot_mapping, k_cache, v_cache)
+        a = paged_decode(q, k_cache, v_cache, block_table, seq_lens, max_seq_len=max_seq_len)
+        return self._finish(a, gate, x.dtype)
+
+
 class GatedDeltaNet(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype, device, pctx=None, layer_idx: int = 0):
         super().__init__()
@@ -163,6 +205,136 @@ class GatedDeltaNet(nn.Module):
         of = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + self.cfg.rms_norm_eps)
         of = (self.gate_norm.float() * of.to(x.dtype).float()) * F.silu(z.reshape(T, nv, dv).float())
         return linear(of.to(x.dtype).reshape(T, self.value_dim), self.out_proj)
+
+
+def _gdn_project(m: "GatedDeltaNet", x):
+    y = linear(x, m.in_proj)
+    c, vd, nv = m.conv_dim, m.value_dim, m.nv
+    return y[:, :c], y[:, c:c + vd], y[:, c + vd:c + vd + nv], y[:, c + vd + nv:]
+
+
+def _gdn_heads(m: "GatedDeltaNet", mixed, a, b, dtype):
+    """Conv output → L2-normalised q/k, v, decay and write strength, all per value head."""
+    T = mixed.shape[0]
+    q = mixed[:, :m.key_dim].reshape(T, m.nk, m.dk).float()
+    k = mixed[:, m.key_dim: 2 * m.key_dim].reshape(T, m.nk, m.dk).float()
+    v = mixed[:, 2 * m.key_dim:].reshape(T, m.nv, m.dv)
+    q = (q * torch.rsqrt(q.pow(2).sum(-1, keepdim=True) + 1e-6)).to(dtype)
+    k = (k * torch.rsqrt(k.pow(2).sum(-1, keepdim=True) + 1e-6)).to(dtype)
+    if m.nv > m.nk:
+        q = q.repeat_interleave(m.nv // m.nk, dim=1)
+        k = k.repeat_interleave(m.nv // m.nk, dim=1)
+    beta = torch.sigmoid(b.float())
+    decay = torch.exp(-torch.exp(m.A_log.float()) * F.softplus(a.float() + m.dt_bias.float()))
+    return q, k, v, decay, beta
+
+
+def _gdn_out(m: "GatedDeltaNet", o, z, dtype):
+    T = o.shape[0]
+    of = o.float()
+    of = of * torch.rsqrt(of.pow(2).mean(-1, keepdim=True) + m.cfg.rms_norm_eps)
+    of = (m.gate_norm.float() * of.to(dtype).float()) * F.silu(z.reshape(T, m.nv, m.dv).float())
+    return linear(of.to(dtype).reshape(T, m.value_dim), m.out_proj)
+
+
+@torch.no_grad()
+def gdn_prefill(m: "GatedDeltaNet", x, meta: VarlenMeta, conv_state, rec_state, state_slots):
+    """Prompt forward of a linear-attention layer that also leaves, for every sequence, the last ``K - 1``
+    convolution inputs and the final recurrent state in ``conv_state`` / ``rec_state`` at ``state_slots``."""
+    mixed_in, z, a, b = _gdn_project(m, x)
+    mixed_in = mixed_in.contiguous()
+    cu = meta.cu_seqlens
+    mixed = causal_conv1d(mixed_in, m.conv_w, None, cu, activation=True)
+    q, k, v, decay, beta = _gdn_heads(m, mixed, a, b, x.dtype)
+    o, final = linear_attn_prefill(q, k, v, decay, beta, cu, scale=m.dk ** -0.5, mode="gated_delta")
+    K1 = m.conv_w.shape[1] - 1
+    cu_l = [int(c) for c in meta.cu_cpu]
+    for i, (s0, s1) in enumerate(zip(cu_l[:-1], cu_l[1:])):
+        tail = mixed_in[max(s0, s1 - K1):s1]                    # [<=K-1, C]
+        st = conv_state[state_slots[i]]
+        st.zero_()
+        if tail.shape[0]:
+            st[:, K1 - tail.shape[0]:] = tail.t()
+    rec_state.index_copy_(0, state_slots, final)
+    return _gdn_out(m, o, z, x.dtype)
+
+
+@torch.no_grad()
+def gdn_decode(m: "GatedDeltaNet", x, conv_state, rec_state, state_slots):
+    """One token per sequence: advances the convolution window and the recurrent state in place."""
+    mixed_in, z, a, b = _gdn_project(m, x)
+    win = torch.cat([conv_state.index_select(0, state_slots), mixed_in.unsqueeze(-1).to(conv_state.dtype)], -1)  # [B, C, K]
+    conv_state.index_copy_(0, state_slots, win[..., 1:].contiguous())
+    mixed = F.silu((win.float() * m.conv_w.float()).sum(-1)).to(x.dtype)
+    q, k, v, decay, beta = _gdn_heads(m, mixed, a, b, x.dtype)
+    S = rec_state.index_select(0, state_slots)
+    o, S = linear_attn_step(q, k, v, decay, beta, S, scale=m.dk ** -0.5, mode="gated_delta")
+    rec_state.index_copy_(0, state_slots, S)
+    return _gdn_out(m, o, z, x.dtype)
+
+
+class HybridState:
+    """Per-sequence state of the linear-attention layers of a rollout engine: for layer ``i`` (None for
+    full-attention layers) ``conv[i] [slots, conv_dim, K - 1]`` and ``rec[i] [slots, heads, dk, dv]`` (fp32)."""
+
+    def __init__(self, cfg: ModelConfig, max_slots: int, dtype, device):
+        self.conv, self.rec = [], []
+        nk, nv = cfg.linear_num_key_heads, cfg.linear_num_value_heads
+        conv_dim = 2 * nk * cfg.linear_key_head_dim + nv * cfg.linear_value_head_dim
+        for i in range(cfg.num_hidden_layers):
+            if cfg.layer_type(i) == "linear_attention":
+                self.conv.append(torch.zeros(max_slots, conv_dim, cfg.linear_conv_kernel_dim - 1, dtype=dtype, device=device))
+                self.rec.append(torch.zeros(max_slots, nv, cfg.linear_key_head_dim, cfg.linear_value_head_dim,
+                                            dtype=torch.float32, device=device))
+            else:
+                self.conv.append(None)
+                self.rec.append(None)
+
+
+def _run_blocks(model, x, attn_step):
+    """The residual / norm / MLP skeleton shared by prefill and decode; ``attn_step(i, layer, y)`` runs the
+    token mixer of block ``i``."""
+    res = None
+    for i, layer in enumerate(model.layers):
+        if res is None:
+            y, res = fused.rmsnorm(x, layer.input_norm, layer.eps), x
+        else:
+            y, res = fused.rmsnorm(x, layer.input_norm, layer.eps, residual=res)
+        a = attn_step(i, layer, y)
+        y, res = fused.rmsnorm(a, layer.post_norm, layer.eps, residual=res)
+        x = layer.mlp(y)
+    y, _ = fused.rmsnorm(x, model.norm, model.cfg.rms_norm_eps, residual=res)
+    return y
+
+
+@torch.no_grad()
+def hybrid_prefill(model, input_ids, position_ids, meta, kv_caches, slot_mapping, state: HybridState, state_slots):
+    cos, sin = model.rope(input_ids.device)
+    pos = position_ids.to(torch.int32)
+    x = F.embedding(input_ids.long(), model.embed)
+
+    def step(i, layer, y):
+        if isinstance(layer.attn, GatedDeltaNet):
+            return gdn_prefill(layer.attn, y, meta, state.conv[i], state.rec[i], state_slots)
+        return layer.attn.prefill(y, cos, sin, pos, meta, slot_mapping, kv_caches[i][0], kv_caches[i][1])
+
+    return _run_blocks(model, x, step)
+
+
+@torch.no_grad()
+def hybrid_decode(model, input_ids, position_ids, kv_caches, block_table, seq_lens, slot_mapping, state: HybridState,
+                  state_slots, max_seq_len=None):
+    cos, sin = model.rope(input_ids.device)
+    pos = position_ids.to(torch.int32)
+    x = F.embedding(input_ids.long(), model.embed)
+
+    def step(i, layer, y):
+        if isinstance(layer.attn, GatedDeltaNet):
+            return gdn_decode(layer.attn, y, state.conv[i], state.rec[i], state_slots)
+        return layer.attn.decode(y, cos, sin, pos, kv_caches[i][0], kv_caches[i][1], block_table, seq_lens,
+                                 slot_mapping, max_seq_len)
+
+    return _run_blocks(model, x, step)
 
 
 def hf_tensors(layer_attn, prefix: str, cfg: ModelConfig, norm_out):

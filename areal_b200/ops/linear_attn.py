@@ -116,7 +116,7 @@ def linear_attn_ref(q, k, v, a, b, cu, scale: float, mode: str):
     return torch.stack(out).to(q.dtype) if out else torch.zeros_like(v)
 
 
-def linear_attn_chunked(q, k, v, a, b, cu, scale: float, mode: str, chunk: int = 64):
+def linear_attn_chunked(q, k, v, a, b, cu, scale: float, mode: str, chunk: int = 64, return_state: bool = False):
     """The same recurrences in chunk-parallel form (differentiable; the training path).
 
     Inside a chunk that starts from state ``S0``, with ``G_i`` the running sum of ``log a`` and
@@ -133,10 +133,12 @@ def linear_attn_chunked(q, k, v, a, b, cu, scale: float, mode: str, chunk: int =
     DV = v.shape[2]
     delta = mode == "gated_delta"
     outs = []
+    finals = []  # per sequence: the state after its last token (``return_state``)
     cu_l = [int(c) for c in cu]
     for s0, s1 in zip(cu_l[:-1], cu_l[1:]):
         L = s1 - s0
         if L == 0:
+            finals.append(torch.zeros(H, DK, DV, dtype=torch.float32, device=q.device))
             continue
         n = -(-L // chunk)
         pad = n * chunk - L
@@ -168,9 +170,11 @@ def linear_attn_chunked(q, k, v, a, b, cu, scale: float, mode: str, chunk: int =
             S = eg[:, c, -1][..., None] * S + Kd[:, c].transpose(-1, -2) @ U
         o = torch.stack(o_chunks, 1).reshape(H, n * chunk, DV)[:, :L]
         outs.append(o.transpose(0, 1))
-    if not outs:
-        return torch.zeros_like(v)
-    return (torch.cat(outs, 0) * scale).to(q.dtype)
+        finals.append(S)  # padding rows have a = 1, k = v = 0: they leave the state untouched
+    out = (torch.cat(outs, 0) * scale).to(q.dtype) if outs else torch.zeros_like(v)
+    if return_state:
+        return out, (torch.stack(finals) if finals else torch.zeros(0, H, DK, DV, device=q.device))
+    return out
 
 
 def linear_attn(q, k, v, a, b, cu, scale: float | None = None, mode: str = "gated_delta"):
@@ -199,3 +203,46 @@ def linear_attn(q, k, v, a, b, cu, scale: float | None = None, mode: str = "gate
     _lib.check(rc, "b200_linear_attn_fwd")
     _lib.count_launch()
     return o
+
+
+@torch.no_grad()
+def linear_attn_prefill(q, k, v, a, b, cu, scale: float | None = None, mode: str = "gated_delta"):
+    """Inference prefill: outputs of every token AND the recurrent state after each sequence's last
+    token (``[n_seq, H, DK, DV]`` fp32), which a decode step continues from."""
+    T, H, DK = q.shape
+    DV = v.shape[2]
+    scale = scale if scale is not None else DK ** -0.5
+    n_seq = int(cu.numel()) - 1
+    if not (_lib.use_cuda_kernels(q, k, v) and q.dtype == torch.bfloat16 and DK in (64, 128) and DV <= 256):
+        return linear_attn_chunked(q, k, v, a, b, cu, scale, mode, return_state=True)
+    q, k, v = q.contiguous(), k.contiguous(), v.contiguous()
+    a32 = a.float().contiguous()
+    b32 = b.float().contiguous() if b is not None else None
+    cu = cu.int().contiguous()
+    o = torch.empty_like(v)
+    state = torch.empty((n_seq, H, DK, DV), dtype=torch.float32, device=q.device)
+    rc = _lib.kernels().b200_linear_attn_fwd(_lib.ptr(q), _lib.ptr(k), _lib.ptr(v), _lib.ptr(a32), _lib.ptr(b32),
+                                             _lib.ptr(cu), _lib.ptr(o), _lib.ptr(state), ctypes.c_int(n_seq),
+                                             ctypes.c_int(H), ctypes.c_int(DK), ctypes.c_int(DV), ctypes.c_float(scale),
+                                             ctypes.c_int(1 if mode == "gated_delta" else 0), _lib.stream_ptr())
+    _lib.check(rc, "b200_linear_attn_fwd")
+    _lib.count_launch()
+    return o, state
+
+
+@torch.no_grad()
+def linear_attn_step(q, k, v, a, b, state, scale: float | None = None, mode: str = "gated_delta"):
+    """One decode step for a batch of sequences: ``q, k [B, H, DK]``, ``v [B, H, DV]``, ``a, b [B, H]``,
+    ``state [B, H, DK, DV]`` fp32. Returns ``(o [B, H, DV], new_state)``; the same recurrence as
+    :func:`linear_attn_ref` applied to one token (batched tensor ops: the state read / write dominates)."""
+    DK = q.shape[-1]
+    scale = scale if scale is not None else DK ** -0.5
+    S = state * a.float()[..., None, None]
+    kf, vf = k.float(), v.float()
+    if mode == "gated_delta":
+        u = torch.einsum("bhkv,bhk->bhv", S, kf)
+        S = S + torch.einsum("bhk,bhv->bhkv", kf, b.float()[..., None] * (vf - u))
+    else:
+        S = S + torch.einsum("bhk,bhv->bhkv", kf, vf)
+    o = torch.einsum("bhkv,bhk->bhv", S, q.float()) * scale
+    return o.to(v.dtype), S

@@ -17,7 +17,7 @@ def kv_cache_write(k, v, slot_mapping, k_cache, v_cache):
     ``block * block_size + offset``; negative slots are skipped)."""
     T, Hkv, D = k.shape
     bs = k_cache.shape[2]
-    if not _lib.use_cuda_kernels(k, v, k_cache):
+    if not (_lib.use_cuda_kernels(k, v, k_cache) and D == 128):  # the kernel is written for head_dim 128
         ok = slot_mapping >= 0
         sm = slot_mapping[ok].long()
         blk, off = sm // bs, sm % bs
