@@ -174,6 +174,10 @@ class AsyncTaskRunner(Generic[T]):
             t.cancel()
         if tasks:
             await asyncio.gather(*tasks, return_exceptions=True)
+        # HTTP sessions that workflows opened on this loop end with it
+        from .workflow_context import close_clients
+
+        await close_clients()
 
     async def _wrap(self, tid, ctime, fn, args, kwargs):
         try:

@@ -115,7 +115,12 @@ def test_generation_survives_a_pause(servers):
             await loop.run_in_executor(None, lambda: cli.set_version(1))
             await asyncio.sleep(0.1)
             await loop.run_in_executor(None, cli.continue_generation)
-            return await task
+            try:
+                return await task
+            finally:
+                from areal_b200.infra.workflow_context import close_clients
+
+                await close_clients()
 
         r = asyncio.run(go())
         assert len(r.output_tokens) == 150 and r.stop_reason == "length"
