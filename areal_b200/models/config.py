@@ -51,6 +51,8 @@ class ModelConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    # shared expert that every token passes through, scaled by a sigmoid gate (Qwen2-MoE / Qwen3.5-MoE); 0 = none
+    shared_expert_intermediate_size: int = 0
     decoder_sparse_step: int = 1
     mlp_only_layers: list[int] = field(default_factory=list)
     # critic / reward model: scalar head instead of the LM head
@@ -92,6 +94,8 @@ class ModelConfig:
             attn += 2 * self.head_dim
         dense_mlp = 3 * h * self.intermediate_size
         moe_mlp = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
+        if self.shared_expert_intermediate_size:
+            moe_mlp += 3 * h * self.shared_expert_intermediate_size + h
         n = 0
         for i in range(L):
             n += attn + 2 * h + (moe_mlp if self.layer_is_moe(i) else dense_mlp)
@@ -144,6 +148,7 @@ class ModelConfig:
             num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=cfg.get("moe_intermediate_size", 0) or 0,
             norm_topk_prob=cfg.get("norm_topk_prob", True),
+            shared_expert_intermediate_size=cfg.get("shared_expert_intermediate_size", 0) or 0,
             decoder_sparse_step=cfg.get("decoder_sparse_step", 1) or 1,
             mlp_only_layers=list(cfg.get("mlp_only_layers", []) or []),
         )
@@ -156,8 +161,6 @@ class ModelConfig:
                         "linear_num_key_heads", "linear_num_value_heads"):
                 if key in cfg:
                     setattr(out, key, cfg[key])
-            if out.num_experts:
-                raise NotImplementedError("Qwen3.5 MoE (shared experts) is not supported; dense hybrids are")
         for k, v in overrides.items():
             setattr(out, k, v)
         return out
@@ -165,6 +168,8 @@ class ModelConfig:
     def to_hf_config(self) -> dict:
         arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                 "qwen3_moe": "Qwen3MoeForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM"}[self.model_type]
+        if self.model_type == "qwen3_5" and self.is_moe:
+            arch = "Qwen3_5MoeForCausalLM"
         d = {
             "architectures": [arch], "model_type": self.model_type,
             "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
@@ -188,6 +193,7 @@ class ModelConfig:
             d.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
                      moe_intermediate_size=self.moe_intermediate_size,
                      norm_topk_prob=self.norm_topk_prob,
+                     shared_expert_intermediate_size=self.shared_expert_intermediate_size,
                      decoder_sparse_step=self.decoder_sparse_step,
                      mlp_only_layers=self.mlp_only_layers)
         return d

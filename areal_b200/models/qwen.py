@@ -195,6 +195,20 @@ class MoEMLP(nn.Module):
         self.gate_up = nn.Parameter(torch.empty(E // ep, 2 * I, H, dtype=dtype, device=device))
         self.down = nn.Parameter(torch.empty(E // ep, H, I, dtype=dtype, device=device))
         self.last_routing = None  # (topk_idx, topk_w) of the last forward, for stats / replay
+        # shared expert: a dense SwiGLU MLP applied to every token, scaled by sigmoid(x . w_gate); replicated
+        # over the expert-parallel group (every rank applies it to its own tokens)
+        Is = cfg.shared_expert_intermediate_size
+        if Is:
+            self.shared_gate_up = nn.Parameter(torch.empty(2 * Is, H, dtype=dtype, device=device))
+            self.shared_down = nn.Parameter(torch.empty(H, Is, dtype=dtype, device=device))
+            self.shared_gate = nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
+        else:
+            self.shared_gate_up = self.shared_down = self.shared_gate = None
+
+    def _shared(self, x):
+        y = linear(fused.swiglu(linear(x, self.shared_gate_up)), self.shared_down)
+        g = torch.sigmoid(F.linear(x.float(), self.shared_gate.float()))
+        return (y.float() * g).to(x.dtype)
 
     def route(self, x):
         cfg = self.cfg
@@ -218,8 +232,10 @@ class MoEMLP(nn.Module):
         if p is not None and p.ep_size > 1:
             from ..parallel.expert_parallel import ep_moe_forward
 
-            return ep_moe_forward(x, idx, w, self.gate_up, self.down, p.extras.get("ep_state", p.ep_group))
-        return moe_experts_forward(x, idx, w, self.gate_up, self.down)
+            y = ep_moe_forward(x, idx, w, self.gate_up, self.down, p.extras.get("ep_state", p.ep_group))
+        else:
+            y = moe_experts_forward(x, idx, w, self.gate_up, self.down)
+        return y if self.shared_gate_up is None else y + self._shared(x)
 
 
 class Block(nn.Module):
@@ -583,12 +599,22 @@ class QwenModel(nn.Module):
                     yield q + "gate_proj.weight", m.gate_up[e, :Im]
                     yield q + "up_proj.weight", m.gate_up[e, Im:]
                     yield q + "down_proj.weight", m.down[e]
+                yield from self._shared_expert_hf(p, m)
         if self.norm is not None:
             yield "model.norm.weight", self.norm
         if self.score is not None:
             yield "score.weight", self.score
         elif self.lm_head is not None:
             yield "lm_head.weight", self.lm_head
+
+    def _shared_expert_hf(self, p: str, m):
+        if getattr(m, "shared_gate_up", None) is None:
+            return
+        Is = self.cfg.shared_expert_intermediate_size
+        yield p + "mlp.shared_expert.gate_proj.weight", m.shared_gate_up[:Is]
+        yield p + "mlp.shared_expert.up_proj.weight", m.shared_gate_up[Is:]
+        yield p + "mlp.shared_expert.down_proj.weight", m.shared_down
+        yield p + "mlp.shared_expert_gate.weight", m.shared_gate
 
     def _to_hf_hybrid(self, export: bool):
         from .qwen3_5 import hf_tensors
@@ -603,9 +629,20 @@ class QwenModel(nn.Module):
             yield p + "input_layernorm.weight", nw(layer.input_norm)
             yield from hf_tensors(layer.attn, p, cfg, nw)
             yield p + "post_attention_layernorm.weight", nw(layer.post_norm)
-            yield p + "mlp.gate_proj.weight", layer.mlp.gate_up[:I]
-            yield p + "mlp.up_proj.weight", layer.mlp.gate_up[I:]
-            yield p + "mlp.down_proj.weight", layer.mlp.down
+            m = layer.mlp
+            if isinstance(m, DenseMLP):
+                yield p + "mlp.gate_proj.weight", m.gate_up[:I]
+                yield p + "mlp.up_proj.weight", m.gate_up[I:]
+                yield p + "mlp.down_proj.weight", m.down
+            else:
+                Im = cfg.moe_intermediate_size
+                yield p + "mlp.gate.weight", m.router
+                for e in range(cfg.num_experts):
+                    q = p + f"mlp.experts.{e}."
+                    yield q + "gate_proj.weight", m.gate_up[e, :Im]
+                    yield q + "up_proj.weight", m.gate_up[e, Im:]
+                    yield q + "down_proj.weight", m.down[e]
+                yield from self._shared_expert_hf(p, m)
         if self.norm is not None:
             yield "model.norm.weight", nw(self.norm)
         if self.score is not None:

@@ -310,3 +310,54 @@ def test_rollout_engine_serves_hybrid_model_cuda():
             assert float((got - want).abs().max()) < 0.15
     finally:
         eng.destroy()
+
+
+def test_moe_with_shared_expert_and_hybrid_moe(tmp_path):
+    """Routed experts plus a sigmoid-gated shared expert (Qwen2-MoE / Qwen3.5-MoE): the block against a
+    restatement from checkpoint-named tensors, and a hybrid MoE model through checkpoint round trip."""
+    from areal_b200.models.qwen import MoEMLP
+    from areal_b200.utils.hf_io import load_hf_weights, save_hf_checkpoint
+
+    cfg = dataclasses.replace(CFG, num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
+                              shared_expert_intermediate_size=96, norm_topk_prob=True)
+    m = build_model(cfg, dtype=torch.float32, seed=11)
+    assert all(isinstance(l.mlp, MoEMLP) and l.mlp.shared_gate_up is not None for l in m.layers)
+    hf = {k: v.detach() for k, v in m.to_hf()}
+    p = "model.layers.1.mlp."
+    x = torch.randn(13, cfg.hidden_size)
+    with torch.no_grad():
+        got = m.layers[1].mlp(x)
+    probs = (x @ hf[p + "gate.weight"].T).softmax(-1)
+    w, idx = probs.topk(2, -1)
+    w = w / w.sum(-1, keepdim=True)
+    want = torch.zeros_like(x)
+    for t in range(x.shape[0]):
+        for j in range(2):
+            e = int(idx[t, j])
+            q = p + f"experts.{e}."
+            h = F.silu(x[t] @ hf[q + "gate_proj.weight"].T) * (x[t] @ hf[q + "up_proj.weight"].T)
+            want[t] += w[t, j] * (h @ hf[q + "down_proj.weight"].T)
+    hs = F.silu(x @ hf[p + "shared_expert.gate_proj.weight"].T) * (x @ hf[p + "shared_expert.up_proj.weight"].T)
+    want += torch.sigmoid(x @ hf[p + "shared_expert_gate.weight"].T) * (hs @ hf[p + "shared_expert.down_proj.weight"].T)
+    assert torch.allclose(got, want, atol=1e-4, rtol=1e-3), float((got - want).abs().max())
+    # round trip of the whole hybrid MoE model
+    ids = torch.randint(0, cfg.vocab_size, (30,))
+    pos = torch.arange(30)
+    meta = VarlenMeta(torch.tensor([0, 30], dtype=torch.int32), "cpu")
+    with torch.no_grad():
+        h0 = m(ids, pos, meta)
+    save_hf_checkpoint(m, cfg, str(tmp_path))
+    conf = json.load(open(os.path.join(tmp_path, "config.json")))
+    assert conf["architectures"] == ["Qwen3_5MoeForCausalLM"] and conf["shared_expert_intermediate_size"] == 96
+    cfg2 = ModelConfig.from_hf_config(str(tmp_path))
+    assert cfg2.num_experts == 4 and cfg2.shared_expert_intermediate_size == 96 and cfg2.layer_types == cfg.layer_types
+    m2 = build_model(cfg2, dtype=torch.float32, seed=None)
+    load_hf_weights(m2, str(tmp_path))
+    with torch.no_grad():
+        assert torch.allclose(m2(ids, pos, meta), h0, atol=1e-5)
+    # gradients reach the shared expert and its gate
+    out = m(ids, pos, meta)
+    out.sum().backward()
+    mlp = m.layers[0].mlp
+    assert mlp.shared_gate.grad is not None and float(mlp.shared_gate.grad.abs().sum()) > 0
+    assert float(mlp.shared_down.grad.abs().sum()) > 0
