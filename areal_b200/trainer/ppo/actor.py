@@ -145,7 +145,8 @@ class PPOActor:
         # re-pad each mini-batch (the engine splits it further into token-bounded micro-batches)
         from ...utils.data import unpack_to_padded
 
-        loss_fn = functools.partial(grpo_loss_fn, config=cfg, current_version=self.engine.get_version())
+        loss_fn = functools.partial(grpo_loss_fn, config=cfg, current_version=self.engine.get_version(),
+                                    distill=getattr(self, "distill_weights", None))
         all_stats = []
         self.engine.train()
         for mb in mbs.mbs:
@@ -175,9 +176,12 @@ class PPOActor:
 
 
 def grpo_loss_fn(logprobs: torch.Tensor, entropy: torch.Tensor | None, input_data: dict[str, Any],
-                 config: PPOActorConfig, current_version: int | None = None) -> torch.Tensor:
+                 config: PPOActorConfig, current_version: int | None = None,
+                 distill: tuple[float, float] | None = None) -> torch.Tensor:
     """Policy loss of one packed micro-batch. ``logprobs`` / ``entropy`` are the engine's
-    next-token outputs ``[T]``; ``input_data`` holds the packed batch on the same device."""
+    next-token outputs ``[T]``; ``input_data`` holds the packed batch on the same device.
+    ``distill = (rl_loss_weight, distill_loss_weight)`` mixes in the distillation term when the batch
+    carries ``teacher_logp``."""
     cfg = config
     old_logp = input_data["logprobs"].float()
     adv = input_data["advantages"].float()
@@ -230,8 +234,8 @@ def grpo_loss_fn(logprobs: torch.Tensor, entropy: torch.Tensor | None, input_dat
                                           importance_sampling_level=cfg.importance_sampling_level,
                                           cu_seqlens=cu)
     if teacher is not None:
-        rl_w = float(input_data.get("rl_loss_weight", 1.0))
-        kd_w = float(input_data.get("distill_loss_weight", 0.0))
+        rl_w, kd_w = distill if distill is not None else (float(input_data.get("rl_loss_weight", 1.0)),
+                                                         float(input_data.get("distill_loss_weight", 0.0)))
         denom = loss_mask.count_nonzero().clamp(min=1)
         lp = logprobs.float()
         if rl_w == 0.0:

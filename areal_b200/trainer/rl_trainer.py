@@ -122,6 +122,8 @@ class PPOTrainer:
         # every role takes part in group creation (collective)
         self.actor_engine = B200TrainEngine(config.actor) if self.is_trainer else None
         self.critic_engine = None
+        self.teacher_engine = None
+        self.teacher = None
         self.ref_engine = None
         helper = self.actor_engine or B200TrainEngine(config.actor)
         helper.create_process_group(self.actor_alloc.parallel, ranks=train_ranks)
@@ -141,6 +143,13 @@ class PPOTrainer:
                 self.critic_engine = B200TrainEngine(config.critic)
                 self.critic_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks, groups=shared)
                 self.critic_engine.initialize(None, self.ft_spec, seed=config.seed + 1)
+            if getattr(config, "teacher", None) is not None:
+                # distillation: a frozen teacher scores every batch; the actor's loss mixes the RL term with
+                # the reverse-KL term towards it (TeacherConfig.rl_loss_weight / distill_loss_weight)
+                config.teacher.optimizer = None
+                self.teacher_engine = B200TrainEngine(config.teacher)
+                self.teacher_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks, groups=shared)
+                self.teacher_engine.initialize(None, self.ft_spec, seed=config.seed + 2)
             if config.ref is not None and config.actor.kl_ctl != 0.0:
                 self.ref_engine = B200TrainEngine(config.ref)
                 self.ref_engine.create_process_group(self.actor_alloc.parallel, ranks=train_ranks, groups=shared)
@@ -167,6 +176,10 @@ class PPOTrainer:
             self.actor = PPOActor(config.actor, self.actor_engine)
             self.critic = PPOCritic(config.critic, self.critic_engine) if self.critic_engine else None
             self.ref = PPOActor(config.ref, self.ref_engine) if self.ref_engine else None
+            self.teacher = PPOActor(config.teacher, self.teacher_engine) if self.teacher_engine else None
+            if self.teacher is not None:
+                self.actor.distill_weights = (float(config.teacher.rl_loss_weight),
+                                              float(config.teacher.distill_loss_weight))
         self.saver = Saver(config.saver, self.ft_spec)
         self.evaluator = Evaluator(config.evaluator, self.ft_spec)
         self.recover = RecoverHandler(config.recover, self.ft_spec)
@@ -200,7 +213,7 @@ class PPOTrainer:
             self.rollout_client.stop()
         if self.rollout is not None:
             self.rollout.destroy()
-        for e in (self.actor_engine, self.critic_engine, self.ref_engine):
+        for e in (self.actor_engine, self.critic_engine, self.ref_engine, getattr(self, "teacher_engine", None)):
             if e is not None:
                 e.destroy()
         if self.stats_logger is not None:
@@ -281,6 +294,9 @@ class PPOTrainer:
         if self.ref is not None:
             with stats_tracker.record_timing("ref_logp"):
                 batch["ref_logp"] = self.ref.compute_logp(batch)
+        if getattr(self, "teacher", None) is not None:
+            with stats_tracker.record_timing("teacher_logp"):
+                batch["teacher_logp"] = self.teacher.compute_logp(batch)
         if cfg.actor.should_compute_prox_logp():
             with stats_tracker.record_timing("recompute_logp"):
                 batch["prox_logp"] = actor.compute_logp(batch)
