@@ -664,11 +664,20 @@ class B200TrainEngine(TrainEngine):
         assert self.rollout_engine is not None, "connect_engine() has not been called"
         t0 = time.perf_counter()
         if meta.type == "disk":
-            self.save(SaveLoadMeta(path=meta.path, weight_format="hf", with_optim=False))
+            # one directory per version (`weight_update_v{N}`), the previous one removed once the servers
+            # have loaded the new weights
+            vdir = os.path.join(meta.path, f"weight_update_v{meta.version}") if meta.version is not None else meta.path
+            self.save(SaveLoadMeta(path=vdir, weight_format="hf", with_optim=False))
             if dist.is_initialized() and self.world_size > 1:
                 dist.barrier(group=self._cpu_group)
             if self.dp_rank == 0:
-                self.rollout_engine.update_weights_from_disk(meta).result()
+                self.rollout_engine.update_weights_from_disk(dataclasses.replace(meta, path=vdir)).result()
+                prev = getattr(self, "_last_weight_dir", None)
+                if prev and prev != vdir and os.path.isdir(prev):
+                    import shutil
+
+                    shutil.rmtree(prev, ignore_errors=True)
+                self._last_weight_dir = vdir
         else:
             self.rollout_engine.pause_generation()
             with self._merged_weights():
