@@ -9,6 +9,7 @@ from __future__ import annotations
 
 import asyncio
 import concurrent.futures as cf
+import multiprocessing
 import threading
 from concurrent.futures.process import BrokenProcessPool
 from typing import Any, Callable
@@ -32,14 +33,14 @@ class AsyncRewardWrapper:
         self.default = default
         with self._lock:
             if self.max_workers not in self._pools:
-                self._pools[self.max_workers] = cf.ProcessPoolExecutor(self.max_workers)
+                self._pools[self.max_workers] = _new_pool(self.max_workers)
                 self._refs[self.max_workers] = 0
             self._refs[self.max_workers] += 1
 
     def _pool(self) -> cf.ProcessPoolExecutor:
         with self._lock:
             if self.max_workers not in self._pools:
-                self._pools[self.max_workers] = cf.ProcessPoolExecutor(self.max_workers)
+                self._pools[self.max_workers] = _new_pool(self.max_workers)
             return self._pools[self.max_workers]
 
     def _rebuild(self):
@@ -47,7 +48,7 @@ class AsyncRewardWrapper:
             old = self._pools.pop(self.max_workers, None)
             if old is not None:
                 old.shutdown(wait=False, cancel_futures=True)
-            self._pools[self.max_workers] = cf.ProcessPoolExecutor(self.max_workers)
+            self._pools[self.max_workers] = _new_pool(self.max_workers)
 
     async def __call__(self, *args: Any, **kwargs: Any) -> float:
         loop = asyncio.get_running_loop()
@@ -77,6 +78,12 @@ class AsyncRewardWrapper:
                         pool.shutdown(wait=False, cancel_futures=True)
         except Exception:
             pass
+
+
+def _new_pool(n: int) -> cf.ProcessPoolExecutor:
+    # "spawn": the callers are multi-threaded processes that hold a CUDA context; forking one of those
+    # hands the child locks and device state it must not touch
+    return cf.ProcessPoolExecutor(n, mp_context=multiprocessing.get_context("spawn"))
 
 
 def _call(fn, args, kwargs):
