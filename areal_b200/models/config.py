@@ -51,6 +51,12 @@ class ModelConfig:
     num_experts_per_tok: int = 0
     moe_intermediate_size: int = 0
     norm_topk_prob: bool = True
+    # router variants (defaults = Qwen3-MoE): score function, scale on the routing weights, and aux-loss-free load
+    # balancing (a per-expert bias that only affects WHICH experts are picked, nudged by `moe_load_balance_coeff`
+    # towards the mean load after every training forward; 0 = off)
+    moe_score_func: str = "softmax"  # softmax | sigmoid
+    moe_route_scale: float = 1.0
+    moe_load_balance_coeff: float = 0.0
     # shared expert that every token passes through, scaled by a sigmoid gate (Qwen2-MoE / Qwen3.5-MoE); 0 = none
     shared_expert_intermediate_size: int = 0
     decoder_sparse_step: int = 1

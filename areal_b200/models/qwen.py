@@ -195,6 +195,11 @@ class MoEMLP(nn.Module):
         self.gate_up = nn.Parameter(torch.empty(E // ep, 2 * I, H, dtype=dtype, device=device))
         self.down = nn.Parameter(torch.empty(E // ep, H, I, dtype=dtype, device=device))
         self.last_routing = None  # (topk_idx, topk_w) of the last forward, for stats / replay
+        # aux-loss-free balancing: a selection-only bias, a buffer (not trained by the optimizer, replicated)
+        if cfg.moe_load_balance_coeff > 0:
+            self.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32, device=device))
+        else:
+            self.expert_bias = None
         # shared expert: a dense SwiGLU MLP applied to every token, scaled by sigmoid(x . w_gate); replicated
         # over the expert-parallel group (every rank applies it to its own tokens)
         Is = cfg.shared_expert_intermediate_size
@@ -213,6 +218,9 @@ class MoEMLP(nn.Module):
     def route(self, x):
         cfg = self.cfg
         logits = F.linear(x.float(), self.router.float())
+        plain = cfg.moe_score_func == "softmax" and cfg.moe_route_scale == 1.0 and self.expert_bias is None
+        if not plain:
+            return self._route_general(logits)
         if not (torch.is_grad_enabled() and (x.requires_grad or self.router.requires_grad)):
             from ..ops.moe import route as route_kernel
 
@@ -222,6 +230,27 @@ class MoEMLP(nn.Module):
         if cfg.norm_topk_prob:
             w = w / w.sum(-1, keepdim=True)
         return idx, w
+
+    def _route_general(self, logits):
+        """Sigmoid or softmax scores; experts are PICKED by ``score + expert_bias`` but weighted by the plain
+        score (so the bias steers load without entering the gradient); optional renormalisation and scale.
+        After a training forward the bias moves by ``coeff * sign(mean_load - load)`` per expert. The bias
+        is a buffer of the trainer's model: it is saved with ``state_dict`` but is not part of the flat
+        weight buffer, so rollout engines route by the plain scores and the decoupled loss's
+        behaviour-policy weights absorb the difference."""
+        cfg = self.cfg
+        scores = torch.sigmoid(logits) if cfg.moe_score_func == "sigmoid" else logits.softmax(-1)
+        pick = scores if self.expert_bias is None else scores + self.expert_bias
+        idx = pick.topk(cfg.num_experts_per_tok, dim=-1).indices
+        w = scores.gather(-1, idx)
+        if cfg.norm_topk_prob:
+            w = w / (w.sum(-1, keepdim=True) + 1e-20)
+        w = w * cfg.moe_route_scale
+        if self.expert_bias is not None and self.training and torch.is_grad_enabled():
+            with torch.no_grad():
+                load = torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).float()
+                self.expert_bias.add_(cfg.moe_load_balance_coeff * torch.sign(load.mean() - load))
+        return idx.to(torch.int32), w
 
     def forward(self, x):
         from ..ops.moe import moe_experts_forward

@@ -361,3 +361,44 @@ def test_moe_with_shared_expert_and_hybrid_moe(tmp_path):
     mlp = m.layers[0].mlp
     assert mlp.shared_gate.grad is not None and float(mlp.shared_gate.grad.abs().sum()) > 0
     assert float(mlp.shared_down.grad.abs().sum()) > 0
+
+
+def test_router_variants_sigmoid_scale_and_bias_balancing():
+    """Sigmoid scoring with a route scale, and aux-loss-free balancing: the bias changes which experts are
+    picked but not their weights, and it moves towards under-loaded experts during training."""
+    from areal_b200.models.qwen import MoEMLP
+
+    base = dataclasses.replace(PRESETS["tiny-qwen3-moe"], moe_score_func="sigmoid", moe_route_scale=2.5,
+                               norm_topk_prob=True, moe_load_balance_coeff=0.01)
+    torch.manual_seed(0)
+    mlp = MoEMLP(base, torch.float32, "cpu")
+    for p in mlp.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    x = torch.randn(64, base.hidden_size)
+    mlp.eval()
+    with torch.no_grad():
+        idx, w = mlp.route(x)
+    s = torch.sigmoid(x @ mlp.router.T)
+    top = s.topk(base.num_experts_per_tok, -1)
+    assert torch.equal(idx.long(), top.indices)
+    assert torch.allclose(w, top.values / top.values.sum(-1, keepdim=True) * 2.5, atol=1e-6)
+    # a large bias on expert 0 forces it into every token's selection, with its plain score as weight
+    mlp.expert_bias[0] = 10.0
+    with torch.no_grad():
+        idx2, w2 = mlp.route(x)
+    assert bool((idx2 == 0).any(-1).all())
+    pos = (idx2 == 0).float().argmax(-1)
+    got = w2.gather(1, pos[:, None]).squeeze(1)
+    picked = s.gather(1, idx2.long())
+    assert torch.allclose(got, (s[:, 0] / picked.sum(-1)) * 2.5, atol=1e-5)
+    # training: the over-loaded expert's bias goes down, eval leaves it alone
+    mlp.train()
+    before = mlp.expert_bias.clone()
+    mlp(x.requires_grad_(True)).sum().backward()
+    assert float(mlp.expert_bias[0]) < float(before[0]) and mlp.router.grad is not None
+    mlp.eval()
+    frozen = mlp.expert_bias.clone()
+    with torch.no_grad():
+        mlp(x.detach())
+    assert torch.equal(mlp.expert_bias, frozen)
+    assert "expert_bias" in mlp.state_dict() and "expert_bias" not in dict(mlp.named_parameters())
