@@ -190,6 +190,11 @@ class ModelConfig:
             "torch_dtype": "bfloat16",
         }
         if self.model_type == "qwen3_5":
+            # transformers reads the text decoder as `qwen3_5_text` (`qwen3_5_moe_text` with experts), with the
+            # rotary settings inside `rope_parameters`
+            d["model_type"] = "qwen3_5_moe_text" if self.is_moe else "qwen3_5_text"
+            d["rope_parameters"] = {"rope_type": "default", "rope_theta": self.rope_theta,
+                                    "partial_rotary_factor": self.partial_rotary_factor}
             d.update(layer_types=self.layer_types, partial_rotary_factor=self.partial_rotary_factor,
                      linear_conv_kernel_dim=self.linear_conv_kernel_dim,
                      linear_key_head_dim=self.linear_key_head_dim, linear_value_head_dim=self.linear_value_head_dim,

@@ -146,7 +146,7 @@ def test_checkpoint_round_trip(tmp_path):
     assert float(hf["model.norm.weight"].detach().abs().max()) == 0.0  # initial multiplier 1 is stored as 0
     save_hf_checkpoint(m, CFG, str(tmp_path))
     conf = json.load(open(os.path.join(tmp_path, "config.json")))
-    assert conf["model_type"] == "qwen3_5" and conf["layer_types"] == CFG.layer_types
+    assert conf["model_type"] == "qwen3_5_text" and conf["layer_types"] == CFG.layer_types
     cfg2 = ModelConfig.from_hf_config(str(tmp_path))
     assert cfg2.layer_types == CFG.layer_types and cfg2.norm_one_plus and cfg2.attn_output_gate
     assert cfg2.partial_rotary_factor == CFG.partial_rotary_factor and cfg2.linear_num_value_heads == 4
