@@ -72,3 +72,18 @@ def test_qwen3_5_moe_matches_transformers(tmp_path):
     cfg = dataclasses.replace(PRESETS["tiny-qwen3_5"], num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
                               shared_expert_intermediate_size=96, norm_topk_prob=True)
     _roundtrip(cfg, tmp_path, atol=5e-4)
+
+
+def test_critic_matches_transformers_token_classification(tmp_path):
+    """A critic / reward model (scalar head) exports to what `AutoModelForTokenClassification(num_labels=1)` reads."""
+    cfg = dataclasses.replace(PRESETS["tiny-qwen2"], is_critic=True, tie_word_embeddings=False)
+    m = build_model(cfg, dtype=torch.float32, seed=4)
+    save_hf_checkpoint(m, cfg, str(tmp_path))
+    hf = transformers.AutoModelForTokenClassification.from_pretrained(str(tmp_path), num_labels=1, torch_dtype=torch.float32)
+    hf.eval()
+    ids = torch.randint(0, cfg.vocab_size, (29,), generator=torch.Generator().manual_seed(5))
+    meta = VarlenMeta(torch.tensor([0, 29], dtype=torch.int32), "cpu")
+    with torch.no_grad():
+        mine = m.values(m(ids, torch.arange(29), meta))
+        theirs = hf(input_ids=ids[None]).logits[0, :, 0]
+    assert float((mine - theirs).abs().max()) < 2e-4
