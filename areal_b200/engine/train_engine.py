@@ -347,7 +347,7 @@ class B200TrainEngine(TrainEngine):
         if pctx is None or (pctx.seq_shards == 1 and pctx.pp_size == 1):
             if self.config.enable_tree_training and not self.is_critic:
                 return self._forward_mb_tree(mb, meta)
-            hidden = self.model(ids, mb["position_ids"], meta)
+            hidden = self.model(ids, mb["position_ids"], meta, **self._vision_inputs(mb))
             if self.is_critic:
                 return self.model.values(hidden), None
             labels = torch.roll(ids, shifts=-1, dims=0)
@@ -355,6 +355,26 @@ class B200TrainEngine(TrainEngine):
                                          self.config.temperature)
             return logp, ent
         return self._forward_mb_parallel(mb, meta, stage_input)
+
+    def _vision_inputs(self, mb: dict[str, Any]) -> dict[str, Any]:
+        """Pixel rows and patch grids of the micro-batch's images, concatenated in sequence order.
+        ``multi_modal_input`` holds one dict per sequence (what the image processor returned for it, empty for
+        a text-only sample), as areal/workflow/vision_rlvr.py of the reference stores it in a trajectory."""
+        mm = mb.get("multi_modal_input")
+        if not mm or not self.model_config.is_vl:
+            if mm and any(d and d.get("pixel_values") is not None for d in mm):
+                raise NotImplementedError(f"{self.model_config.model_type} is a text-only model: the batch has images")
+            return {}
+        pix = [torch.as_tensor(d["pixel_values"]) for d in mm if d and d.get("pixel_values") is not None]
+        grid = [torch.as_tensor(d["image_grid_thw"]).view(-1, 3) for d in mm
+                if d and d.get("pixel_values") is not None]
+        if not pix:
+            return {}
+        pv = torch.cat(pix, 0)
+        if self.device.type == "cuda" and not pv.is_cuda:
+            pv = pv.pin_memory()
+            self.h2d_bytes += pv.numel() * pv.element_size()
+        return {"pixel_values": pv.to(self.device, non_blocking=True), "image_grid_thw": torch.cat(grid, 0)}
 
     def _forward_mb_tree(self, mb: dict[str, Any], meta: VarlenMeta):
         """Tree training: the micro-batch's sequences are merged into prefix tries, every distinct

@@ -63,6 +63,18 @@ class ModelConfig:
     mlp_only_layers: list[int] = field(default_factory=list)
     # critic / reward model: scalar head instead of the LM head
     is_critic: bool = False
+    # vision-language models (qwen2_5_vl): the vision tower's config (HF `vision_config` keys; empty = text-only),
+    # the split of the rotary frequencies over the (temporal, height, width) position axes, and the placeholder ids
+    vision: dict = field(default_factory=dict)
+    mrope_section: list[int] = field(default_factory=list)
+    image_token_id: int = -1
+    video_token_id: int = -1
+    vision_start_token_id: int = -1
+    vision_end_token_id: int = -1
+
+    @property
+    def is_vl(self) -> bool:
+        return bool(self.vision)
 
     @property
     def is_moe(self) -> bool:
@@ -128,9 +140,12 @@ class ModelConfig:
             p = Path(cfg)
             p = p / "config.json" if p.is_dir() else p
             cfg = json.loads(p.read_text())
+        top = cfg
         if "text_config" in cfg:  # composite (vision-language) checkpoints nest the decoder's config
             cfg = cfg["text_config"]
         mt = cfg.get("model_type", "qwen3")
+        if top.get("model_type") == "qwen2_5_vl":
+            mt = "qwen2_5_vl"
         if mt.startswith("qwen3_5"):
             mt = "qwen3_5"
         heads = cfg["num_attention_heads"]
@@ -148,7 +163,7 @@ class ModelConfig:
             rope_theta=cfg.get("rope_theta") or rope_params.get("rope_theta", 1e4),
             max_position_embeddings=cfg.get("max_position_embeddings", 32768),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
-            attention_bias=cfg.get("attention_bias", mt == "qwen2"),
+            attention_bias=cfg.get("attention_bias", mt in ("qwen2", "qwen2_5_vl")),
             qk_norm=mt.startswith("qwen3"),
             num_experts=cfg.get("num_experts", 0) or 0,
             num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
@@ -167,11 +182,21 @@ class ModelConfig:
                         "linear_num_key_heads", "linear_num_value_heads"):
                 if key in cfg:
                     setattr(out, key, cfg[key])
+        if mt == "qwen2_5_vl":
+            out.vision = {k: v for k, v in (top.get("vision_config") or {}).items() if k in _VISION_KEYS}
+            rope_scaling = cfg.get("rope_scaling") or top.get("rope_scaling") or {}
+            out.mrope_section = list(rope_params.get("mrope_section") or rope_scaling.get("mrope_section")
+                                     or [out.head_dim // 8, 3 * out.head_dim // 16, 3 * out.head_dim // 16])
+            out.tie_word_embeddings = top.get("tie_word_embeddings", out.tie_word_embeddings)
+            for key in ("image_token_id", "video_token_id", "vision_start_token_id", "vision_end_token_id"):
+                setattr(out, key, top.get(key, cfg.get(key, -1)))
         for k, v in overrides.items():
             setattr(out, k, v)
         return out
 
     def to_hf_config(self) -> dict:
+        if self.is_vl:
+            return self._to_hf_config_vl()
         arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                 "qwen3_moe": "Qwen3MoeForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM"}[self.model_type]
         if self.model_type == "qwen3_5" and self.is_moe:
@@ -209,9 +234,30 @@ class ModelConfig:
                      mlp_only_layers=self.mlp_only_layers)
         return d
 
+    def _to_hf_config_vl(self) -> dict:
+        text = {
+            "model_type": "qwen2_5_vl_text", "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+            "intermediate_size": self.intermediate_size, "num_hidden_layers": self.num_hidden_layers,
+            "num_attention_heads": self.num_attention_heads, "num_key_value_heads": self.num_key_value_heads,
+            "rms_norm_eps": self.rms_norm_eps, "max_position_embeddings": self.max_position_embeddings,
+            "tie_word_embeddings": self.tie_word_embeddings, "hidden_act": "silu", "rope_theta": self.rope_theta,
+            "rope_parameters": {"rope_type": "default", "rope_theta": self.rope_theta,
+                                "mrope_section": list(self.mrope_section)},
+        }
+        return {"architectures": ["Qwen2_5_VLForConditionalGeneration"], "model_type": "qwen2_5_vl",
+                "text_config": text, "vision_config": dict(self.vision, model_type="qwen2_5_vl"),
+                "image_token_id": self.image_token_id, "video_token_id": self.video_token_id,
+                "vision_start_token_id": self.vision_start_token_id,
+                "vision_end_token_id": self.vision_end_token_id,
+                "tie_word_embeddings": self.tie_word_embeddings, "torch_dtype": "bfloat16"}
+
     def asdict(self) -> dict:
         return asdict(self)
 
+
+_VISION_KEYS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_channels", "patch_size",
+                "spatial_merge_size", "temporal_patch_size", "tokens_per_second", "window_size", "out_hidden_size",
+                "fullatt_block_indexes", "hidden_act")
 
 # Named shapes used by the benchmark configurations (random-init, synthetic data).
 PRESETS: dict[str, ModelConfig] = {
@@ -219,6 +265,15 @@ PRESETS: dict[str, ModelConfig] = {
                               intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
                               num_key_value_heads=2, head_dim=64, rope_theta=1e4,
                               tie_word_embeddings=False, attention_bias=True, qk_norm=False),
+    "tiny-qwen2_5-vl": ModelConfig(model_type="qwen2_5_vl", vocab_size=1024, hidden_size=256, intermediate_size=688,
+                                   num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                                   rope_theta=1e4, tie_word_embeddings=False, attention_bias=True, qk_norm=False,
+                                   mrope_section=[8, 12, 12], image_token_id=1000, video_token_id=1001,
+                                   vision_start_token_id=1002, vision_end_token_id=1003,
+                                   vision=dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=2,
+                                               in_channels=3, patch_size=14, spatial_merge_size=2,
+                                               temporal_patch_size=2, tokens_per_second=1, window_size=56,
+                                               out_hidden_size=256, fullatt_block_indexes=[1], hidden_act="silu")),
     "tiny-qwen3_5": ModelConfig(model_type="qwen3_5", vocab_size=1024, hidden_size=256, intermediate_size=512,
                                 num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                                 rope_theta=1e4, tie_word_embeddings=False, partial_rotary_factor=0.25,

@@ -429,11 +429,15 @@ class QwenModel(nn.Module):
         return self._rope
 
     # --------------------------------------------------------------- forward
-    def forward(self, input_ids, position_ids, meta: VarlenMeta, attn_fn=None, stage_input=None):
+    def forward(self, input_ids, position_ids, meta: VarlenMeta, attn_fn=None, stage_input=None,
+                embeds=None, rope=None):
         """Packed forward; returns the final-normed hidden states ``[T, H]``. On a pipeline stage
         other than the first, ``stage_input = (x, res)`` are the activations received from the
-        previous stage; a stage other than the last returns ``(x, res)`` for the next one."""
-        cos, sin = self.rope(input_ids.device)
+        previous stage; a stage other than the last returns ``(x, res)`` for the next one.
+        ``embeds`` replaces the embedding lookup and ``rope = (cos, sin)`` the rotary tables that
+        ``position_ids`` index (a vision-language model passes image features merged into the token
+        embeddings and one table row per token)."""
+        cos, sin = rope if rope is not None else self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
         p = self.pctx
         if p is not None and p.sp_size > 1 and attn_fn is None:
@@ -442,6 +446,9 @@ class QwenModel(nn.Module):
             attn_fn = ulysses_attention(p)
         if stage_input is not None:
             x, res = stage_input
+        elif embeds is not None:
+            assert p is None or p.tp_size == 1, "precomputed embeddings are not sharded over tensor parallel ranks"
+            x, res = embeds, None
         elif p is not None and p.tp_size > 1:
             # input_ids / position_ids hold every token of this sequence-parallel shard; the
             # vocab-parallel lookup leaves each tp rank with its T/tp rows
@@ -718,7 +725,12 @@ class QwenModel(nn.Module):
 
 
 def build_model(cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", seed: int | None = 0, pctx=None) -> QwenModel:
-    m = QwenModel(cfg, dtype=dtype, device=device, pctx=pctx)
+    if cfg.is_vl:
+        from .qwen_vl import QwenVLModel
+
+        m = QwenVLModel(cfg, dtype=dtype, device=device, pctx=pctx)
+    else:
+        m = QwenModel(cfg, dtype=dtype, device=device, pctx=pctx)
     if seed is not None:
         m.init_weights(seed)
     return m

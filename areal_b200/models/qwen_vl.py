@@ -1,0 +1,352 @@
+"""Qwen2.5-VL: a windowed vision transformer in front of the Qwen2 decoder with multimodal rotary positions.
+
+The decoder is the package's ``QwenModel`` unchanged (fused projections, own kernels); this module adds
+
+* ``VisionTower``: patch embedding (the 3-D convolution with stride = kernel is one GEMM over flattened
+  patches), blocks of RMSNorm → attention with 2-D rotary embedding → SwiGLU MLP, where most blocks attend inside
+  windows of ``window_size`` pixels and the ``fullatt_block_indexes`` blocks inside a whole image, and the
+  merger that turns each ``spatial_merge_size²`` group of patches into one decoder token;
+* ``mrope_position_ids`` / ``mrope_tables``: every token gets a (temporal, height, width) position triple (text
+  tokens: three equal values; image tokens: their grid coordinates offset by the running position) and the rotary
+  frequencies are split over the three axes by ``mrope_section``. The decoder's rotary kernels read a table row per
+  token, so the multimodal table is built per packed batch and indexed by the token's row number;
+* ``QwenVLModel``: embeds tokens, overwrites the rows of image placeholders with the tower's output and runs the
+  decoder. Without pixel inputs it is exactly the text model.
+
+The tower runs on PyTorch library operators (its head size of 80 and non-causal windowed attention are outside the
+shapes the package's attention kernels take); segments of equal length are batched into one attention call.
+
+Reference behaviour: the vision-language path of areal/engine/fsdp_engine.py (``multi_modal_input`` carrying
+``pixel_values`` / ``image_grid_thw``, positions from the HF model's ``get_rope_index``) and
+areal/models/transformers/qwen2_vl.py.
+"""
+
+from __future__ import annotations
+
+from typing import Iterable, Iterator, Sequence
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+from ..ops import fused
+from ..ops.attention import VarlenMeta
+from .config import ModelConfig
+from .qwen import QwenModel
+
+
+# ------------------------------------------------------------------------------------------ positions
+
+
+def mrope_position_ids(input_ids: Sequence[int], cu_seqlens: Sequence[int], grids: Sequence[Sequence[int]],
+                       cfg: ModelConfig, second_per_grid: Sequence[float] | None = None):
+    """Position triples of a packed batch.
+
+    ``grids``: ``(t, h, w)`` patch counts of every image / video in the order their placeholder runs appear.
+    Returns ``(pos [3, T] int64, deltas)``; ``deltas[i]`` = (next position after sequence ``i``) − (its length): a
+    generation step ``k`` tokens past the prompt sits at position ``len + k + delta`` on all three axes."""
+    merge = int(cfg.vision.get("spatial_merge_size", 2))
+    tps = float(cfg.vision.get("tokens_per_second", 1))
+    vis = (cfg.image_token_id, cfg.video_token_id)
+    ids = list(input_ids)
+    out = torch.empty(3, len(ids), dtype=torch.long)
+    deltas, gi = [], 0
+    for a, b in zip(cu_seqlens[:-1], cu_seqlens[1:]):
+        cur, i = 0, a
+        while i < b:
+            if ids[i] not in vis:
+                j = i
+                while j < b and ids[j] not in vis:
+                    j += 1
+                out[:, i:j] = torch.arange(cur, cur + j - i)
+                cur += j - i
+                i = j
+                continue
+            if gi >= len(grids):
+                raise ValueError("more image placeholder runs than image grids")
+            t, h, w = (int(x) for x in grids[gi])
+            hh, ww = h // merge, w // merge
+            n = t * hh * ww
+            if i + n > b or any(ids[k] != ids[i] for k in range(i, i + n)):
+                raise ValueError(f"image {gi} needs {n} placeholder tokens in a row at offset {i - a}")
+            if ids[i] == cfg.video_token_id:
+                sec = float(second_per_grid[gi]) if second_per_grid is not None else 1.0
+                tt = (torch.arange(t).float() * sec * tps).long()
+            else:
+                tt = torch.zeros(t, dtype=torch.long)
+            out[0, i:i + n] = cur + tt.repeat_interleave(hh * ww)
+            out[1, i:i + n] = cur + torch.arange(hh).repeat_interleave(ww).repeat(t)
+            out[2, i:i + n] = cur + torch.arange(ww).repeat(t * hh)
+            cur = int(out[:, i:i + n].max()) + 1
+            gi += 1
+            i += n
+        deltas.append(cur - (b - a))
+    if gi != len(grids):
+        raise ValueError(f"{len(grids)} image grids but only {gi} placeholder runs")
+    return out, deltas
+
+
+def mrope_tables(pos3: torch.Tensor, rotary_dim: int, theta: float, sections: Sequence[int]):
+    """``cos, sin [T, rotary_dim / 2]``: frequency ``j`` rotates by the position on the axis that owns it
+    (the first ``sections[0]`` frequencies follow the temporal axis, the next the height, the rest the width)."""
+    assert sum(sections) == rotary_dim // 2, f"mrope_section {list(sections)} must sum to {rotary_dim // 2}"
+    dev = pos3.device
+    inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32, device=dev) / rotary_dim))
+    axis = torch.repeat_interleave(torch.arange(3, device=dev), torch.tensor(list(sections), device=dev))
+    fr = pos3[axis].t().float() * inv
+    return fr.cos().contiguous(), fr.sin().contiguous()
+
+
+# ------------------------------------------------------------------------------------------ vision tower
+
+
+def _rot_half(x):
+    d = x.shape[-1] // 2
+    return torch.cat((-x[..., d:], x[..., :d]), -1)
+
+
+def _segment_attention(q, k, v, cu: list[int]):
+    """Bidirectional attention inside each ``[cu[i], cu[i+1])`` segment. ``q, k, v``: ``[N, heads, d]``.
+    Segments of one length share a batched call (windows of a block all have the same few sizes)."""
+    out = torch.empty_like(q)
+    by_len: dict[int, list[int]] = {}
+    for a, b in zip(cu[:-1], cu[1:]):
+        if b > a:
+            by_len.setdefault(b - a, []).append(a)
+    for n, starts in by_len.items():
+        idx = (torch.tensor(starts, device=q.device)[:, None] + torch.arange(n, device=q.device)[None, :]).reshape(-1)
+        qs, ks, vs = (x.index_select(0, idx).view(len(starts), n, x.shape[1], x.shape[2]).transpose(1, 2)
+                      for x in (q, k, v))
+        o = F.scaled_dot_product_attention(qs, ks, vs)
+        out.index_copy_(0, idx, o.transpose(1, 2).reshape(-1, q.shape[1], q.shape[2]))
+    return out
+
+
+class VisionBlock(nn.Module):
+    def __init__(self, dim: int, inter: int, heads: int, dtype, device):
+        super().__init__()
+        mk = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype, device=device))
+        self.heads = heads
+        self.attn_norm, self.mlp_norm = mk(dim), mk(dim)
+        self.qkv, self.qkv_bias = mk(3 * dim, dim), mk(3 * dim)
+        self.proj, self.proj_bias = mk(dim, dim), mk(dim)
+        self.gate_up, self.gate_up_bias = mk(2 * inter, dim), mk(2 * inter)
+        self.down, self.down_bias = mk(dim, inter), mk(dim)
+
+    def forward(self, x, cos, sin, cu: list[int], eps: float = 1e-6):
+        n, dim = x.shape
+        h = fused.rmsnorm_ref(x, self.attn_norm, eps)
+        q, k, v = F.linear(h, self.qkv, self.qkv_bias).view(n, 3, self.heads, dim // self.heads).unbind(1)
+        qf, kf = q.float(), k.float()
+        q = (qf * cos + _rot_half(qf) * sin).to(x.dtype)
+        k = (kf * cos + _rot_half(kf) * sin).to(x.dtype)
+        x = x + F.linear(_segment_attention(q, k, v, cu).reshape(n, dim), self.proj, self.proj_bias)
+        h = fused.rmsnorm_ref(x, self.mlp_norm, eps)
+        g, u = F.linear(h, self.gate_up, self.gate_up_bias).chunk(2, -1)
+        return x + F.linear(F.silu(g) * u, self.down, self.down_bias)
+
+
+class VisionTower(nn.Module):
+    """``forward(pixel_values [N, C·tp·p·p], grid_thw [n_img, 3]) → [N / merge², out_hidden_size]``, one row per
+    image placeholder token, images in input order and rows in raster order of the merged grid."""
+
+    def __init__(self, vc: dict, dtype, device):
+        super().__init__()
+        self.vc = vc
+        dim, self.heads = vc["hidden_size"], vc["num_heads"]
+        self.merge = vc.get("spatial_merge_size", 2)
+        self.unit = self.merge * self.merge
+        self.patch_dim = vc.get("in_channels", 3) * vc.get("temporal_patch_size", 2) * vc["patch_size"] ** 2
+        mk = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype, device=device))
+        self.patch_embed = mk(dim, self.patch_dim)
+        self.blocks = nn.ModuleList(VisionBlock(dim, vc["intermediate_size"], self.heads, dtype, device)
+                                    for _ in range(vc["depth"]))
+        self.merger_norm = mk(dim)
+        self.merger_fc1, self.merger_fc1_bias = mk(dim * self.unit, dim * self.unit), mk(dim * self.unit)
+        self.merger_fc2, self.merger_fc2_bias = mk(vc["out_hidden_size"], dim * self.unit), mk(vc["out_hidden_size"])
+
+    # patch order: the image processor emits patches grouped by merge unit (each 2×2 block contiguous), images
+    # one after another; `_grid_coords` reproduces the (row, column) of every patch in that order
+    def _grid_coords(self, grids: list[list[int]]) -> torch.Tensor:
+        m, out = self.merge, []
+        for t, h, w in grids:
+            r = torch.arange(h)[:, None].expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).reshape(-1)
+            c = torch.arange(w)[None, :].expand(h, w).reshape(h // m, m, w // m, m).permute(0, 2, 1, 3).reshape(-1)
+            out.append(torch.stack((r, c), -1).repeat(t, 1))
+        return torch.cat(out, 0)
+
+    def _windows(self, grids: list[list[int]]):
+        """Permutation of merge units that makes every attention window contiguous, and the windows' bounds in
+        patches. A window covers ``window_size`` pixels per side = ``window_size / patch / merge`` units."""
+        m = self.merge
+        ws = self.vc.get("window_size", 112) // m // self.vc["patch_size"]
+        order, cu, base = [], [0], 0
+        for t, h, w in grids:
+            gh, gw = h // m, w // m
+            idx = torch.arange(t * gh * gw).view(t, gh, gw)
+            ph, pw = ws - gh % ws, ws - gw % ws  # a full extra window of padding when already a multiple
+            idx = F.pad(idx, (0, pw, 0, ph), value=-1)
+            nh, nw = (gh + ph) // ws, (gw + pw) // ws
+            idx = idx.view(t, nh, ws, nw, ws).permute(0, 1, 3, 2, 4).reshape(t * nh * nw, ws * ws)
+            for row in idx:
+                keep = row[row >= 0]
+                if keep.numel():
+                    order.append(keep + base)
+                    cu.append(cu[-1] + keep.numel() * self.unit)
+            base += t * gh * gw
+        return torch.cat(order), cu
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
+        grids = [[int(v) for v in g] for g in (grid_thw.tolist() if torch.is_tensor(grid_thw) else grid_thw)]
+        dev, dt = self.patch_embed.device, self.patch_embed.dtype
+        x = F.linear(pixel_values.to(device=dev, dtype=dt).view(-1, self.patch_dim), self.patch_embed)
+        n, dim = x.shape
+        assert n == sum(t * h * w for t, h, w in grids), "pixel_values rows do not match image_grid_thw"
+        hd = dim // self.heads
+        # 2-D rotary: the first half of the rotated pairs turns with the patch's row, the second with its column
+        inv = 1.0 / (10000.0 ** (torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2)))
+        rc = self._grid_coords(grids).float()
+        fr = torch.cat((rc[:, :1] * inv, rc[:, 1:] * inv), -1)  # [N, hd / 2]
+        order, cu_win = self._windows(grids)
+        pidx = (order[:, None] * self.unit + torch.arange(self.unit)[None, :]).reshape(-1)
+        x = x.index_select(0, pidx.to(dev))
+        fr = fr.index_select(0, pidx).to(dev)
+        emb = torch.cat((fr, fr), -1)
+        cos, sin = emb.cos()[:, None, :], emb.sin()[:, None, :]
+        cu_img = [0]
+        for t, h, w in grids:
+            for _ in range(t):
+                cu_img.append(cu_img[-1] + h * w)
+        full = set(self.vc.get("fullatt_block_indexes", []))
+        for i, blk in enumerate(self.blocks):
+            x = blk(x, cos, sin, cu_img if i in full else cu_win)
+        x = fused.rmsnorm_ref(x, self.merger_norm, 1e-6).view(-1, dim * self.unit)
+        x = F.linear(F.gelu(F.linear(x, self.merger_fc1, self.merger_fc1_bias)), self.merger_fc2, self.merger_fc2_bias)
+        return x.index_select(0, torch.argsort(order).to(dev))
+
+    # HF names (without the tower's prefix) ↔ parameters; fused gate/up are two HF tensors
+    def hf_tensors(self) -> Iterator[tuple[str, torch.Tensor]]:
+        vc = self.vc
+        yield "patch_embed.proj.weight", self.patch_embed.view(
+            -1, vc.get("in_channels", 3), vc.get("temporal_patch_size", 2), vc["patch_size"], vc["patch_size"])
+        inter = vc["intermediate_size"]
+        for i, b in enumerate(self.blocks):
+            p = f"blocks.{i}."
+            yield p + "norm1.weight", b.attn_norm
+            yield p + "norm2.weight", b.mlp_norm
+            yield p + "attn.qkv.weight", b.qkv
+            yield p + "attn.qkv.bias", b.qkv_bias
+            yield p + "attn.proj.weight", b.proj
+            yield p + "attn.proj.bias", b.proj_bias
+            yield p + "mlp.gate_proj.weight", b.gate_up[:inter]
+            yield p + "mlp.gate_proj.bias", b.gate_up_bias[:inter]
+            yield p + "mlp.up_proj.weight", b.gate_up[inter:]
+            yield p + "mlp.up_proj.bias", b.gate_up_bias[inter:]
+            yield p + "mlp.down_proj.weight", b.down
+            yield p + "mlp.down_proj.bias", b.down_bias
+        yield "merger.ln_q.weight", self.merger_norm
+        yield "merger.mlp.0.weight", self.merger_fc1
+        yield "merger.mlp.0.bias", self.merger_fc1_bias
+        yield "merger.mlp.2.weight", self.merger_fc2
+        yield "merger.mlp.2.bias", self.merger_fc2_bias
+
+
+# ------------------------------------------------------------------------------------------ full model
+
+
+class QwenVLModel(QwenModel):
+    """The decoder plus ``self.visual``. ``forward`` takes the packed token ids as usual and, optionally,
+    ``pixel_values`` / ``image_grid_thw`` of all images of the packed batch in order of appearance."""
+
+    def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", pctx=None):
+        if pctx is not None and (pctx.tp_size > 1 or pctx.pp_size > 1 or pctx.seq_shards > 1):
+            raise NotImplementedError("the vision-language model runs data-parallel only")
+        super().__init__(cfg, dtype=dtype, device=device, pctx=pctx)
+        assert cfg.vision["out_hidden_size"] == cfg.hidden_size
+        self.visual = VisionTower(cfg.vision, dtype, device)
+
+    @torch.no_grad()
+    def init_weights(self, seed: int = 0, std: float = 0.02):
+        super().init_weights(seed, std)  # draws every matrix, zeroes every bias
+        for name, p in self.visual.named_parameters():
+            if name.endswith("norm"):
+                p.fill_(1.0)
+        return self
+
+    def positions(self, input_ids, meta: VarlenMeta, image_grid_thw=None, video_second_per_grid=None):
+        grids = [] if image_grid_thw is None else (
+            image_grid_thw.tolist() if torch.is_tensor(image_grid_thw) else list(image_grid_thw))
+        return mrope_position_ids(input_ids.tolist(), meta.cu_cpu.tolist(), grids, self.cfg, video_second_per_grid)
+
+    def embed_inputs(self, input_ids, pixel_values=None, image_grid_thw=None):
+        """Token embeddings with the image placeholder rows replaced by the tower's output."""
+        x = fused.embedding(input_ids, self.embed)
+        if pixel_values is None or pixel_values.numel() == 0:
+            return x
+        feats = self.visual(pixel_values, image_grid_thw).to(x.dtype)
+        mask = (input_ids == self.cfg.image_token_id) | (input_ids == self.cfg.video_token_id)
+        rows = mask.nonzero().squeeze(-1)
+        if rows.numel() != feats.shape[0]:
+            raise ValueError(f"{rows.numel()} image placeholder tokens but {feats.shape[0]} image features")
+        return x.index_copy(0, rows, feats)
+
+    def forward(self, input_ids, position_ids, meta: VarlenMeta, attn_fn=None, stage_input=None,
+                pixel_values=None, image_grid_thw=None, mrope_pos=None):
+        """``mrope_pos [3, T]`` overrides the position triples derived from the token ids (a caller that
+        already holds them, e.g. from a processor). ``position_ids`` is ignored when there are images: the
+        rotary table is built per token."""
+        if mrope_pos is None:
+            if pixel_values is None or pixel_values.numel() == 0:
+                mrope_pos = position_ids.to(torch.long)[None, :].expand(3, -1)
+            else:
+                mrope_pos, _ = self.positions(input_ids, meta, image_grid_thw)
+        mrope_pos = mrope_pos.to(input_ids.device)
+        cos, sin = mrope_tables(mrope_pos, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.mrope_section)
+        rows = torch.arange(input_ids.shape[0], dtype=torch.int32, device=input_ids.device)
+        x = self.embed_inputs(input_ids, pixel_values, image_grid_thw)
+        return super().forward(input_ids, rows, meta, attn_fn=attn_fn, embeds=x, rope=(cos, sin))
+
+    # ------------------------------------------------------------------ HF layout
+    _LM = "model.language_model."
+    _VIS = "model.visual."
+
+    def to_hf_local(self, export: bool = False) -> Iterator[tuple[str, torch.Tensor]]:
+        for name, t in super().to_hf_local(export):
+            yield (self._LM + name[len("model."):] if name.startswith("model.") else name), t
+        for name, t in self.visual.hf_tensors():
+            yield self._VIS + name, t
+
+    def to_hf(self) -> Iterator[tuple[str, torch.Tensor]]:
+        return self.to_hf_local(export=True)
+
+    @torch.no_grad()
+    def load_hf(self, tensors: Iterable[tuple[str, torch.Tensor]], strict: bool = True):
+        """Accepts the current layout (``model.language_model.*`` / ``model.visual.*``) and the older one
+        (``model.*`` / ``visual.*``)."""
+        def rename():
+            for name, t in tensors:
+                if name.startswith("visual."):
+                    name = "model." + name
+                elif name.startswith("model.") and not name.startswith((self._LM, self._VIS)):
+                    name = self._LM + name[len("model."):]
+                yield name, t
+
+        dst = dict(self.to_hf_local())
+        seen = set()
+        for name, t in rename():
+            if name == "lm_head.weight" and self.lm_head is None and self.score is None:
+                seen.add(name)
+                continue
+            if name not in dst:
+                if strict:
+                    raise KeyError(f"unexpected tensor {name}")
+                continue
+            d = dst[name]
+            if d.shape != t.shape:
+                raise ValueError(f"{name}: shape {tuple(t.shape)} != {tuple(d.shape)}")
+            d.copy_(t.to(device=d.device, dtype=d.dtype))
+            seen.add(name)
+        missing = set(dst) - seen
+        if strict and missing:
+            raise KeyError(f"missing tensors: {sorted(missing)[:8]} ...")
+        return self

@@ -33,9 +33,18 @@ logger = logging.getLogger("SLTrainer")
 
 
 def collate_sft(items: list[dict[str, Any]]) -> dict[str, torch.Tensor]:
-    """Items carry ``input_ids`` and ``loss_mask`` (1 on answer tokens)."""
-    return pad_sequences_to_tensors([dict(input_ids=torch.as_tensor(x["input_ids"]),
-                                          loss_mask=torch.as_tensor(x["loss_mask"])) for x in items])
+    """Items carry ``input_ids`` and ``loss_mask`` (1 on answer tokens); vision-language items also
+    ``multi_modal_input`` (a one-element list with the image processor's ``pixel_values`` / ``image_grid_thw``),
+    which becomes one dict per row of the batch."""
+    batch = pad_sequences_to_tensors([dict(input_ids=torch.as_tensor(x["input_ids"]),
+                                           loss_mask=torch.as_tensor(x["loss_mask"])) for x in items])
+    if any(x.get("multi_modal_input") for x in items):
+        mm = []
+        for x in items:
+            v = x.get("multi_modal_input") or {}
+            mm.append(v[0] if isinstance(v, (list, tuple)) else v)
+        batch["multi_modal_input"] = mm
+    return batch
 
 
 def collate_pairs(items: list[dict[str, Any]]) -> dict[str, torch.Tensor]:

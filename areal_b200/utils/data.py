@@ -42,11 +42,16 @@ def pad_sequences_to_tensors(seqs: list[dict[str, Any]], pad_value: float = 0.0)
     if not seqs:
         return {}
     skip = {"rewards"}
-    max_len = max(len(s[k]) for s in seqs for k in s if k not in skip and hasattr(s[k], "__len__")
+    skip_len = lambda k: k in skip or k.startswith("multi_modal_input")
+    max_len = max(len(s[k]) for s in seqs for k in s if not skip_len(k) and hasattr(s[k], "__len__")
                   and not isinstance(s[k], str))
     out: dict[str, Any] = {}
     for k in seqs[0]:
         vals = [s[k] for s in seqs]
+        if k.startswith("multi_modal_input"):
+            # per-sequence image tensors: one dict per row of the batch (a trajectory stores a one-element list)
+            out[k] = [(v[0] if isinstance(v, (list, tuple)) and v else (v or {})) for v in vals]
+            continue
         if k in skip or not hasattr(vals[0], "__len__"):
             out[k] = torch.as_tensor(vals)
             continue
@@ -55,7 +60,7 @@ def pad_sequences_to_tensors(seqs: list[dict[str, Any]], pad_value: float = 0.0)
             t = torch.as_tensor(v)
             rows.append(torch.nn.functional.pad(t, (0, max_len - t.shape[0]), value=pad_value))
         out[k] = torch.stack(rows)
-    lens = [len(next(v for kk, v in s.items() if kk not in skip and hasattr(v, "__len__"))) for s in seqs]
+    lens = [len(next(v for kk, v in s.items() if not skip_len(kk) and hasattr(v, "__len__"))) for s in seqs]
     out["attention_mask"] = torch.arange(max_len)[None, :] < torch.tensor(lens)[:, None]
     return out
 
