@@ -28,6 +28,7 @@ import dataclasses
 import threading
 import time
 from concurrent.futures import Future
+from typing import Any
 
 import numpy as np
 import torch
@@ -235,6 +236,9 @@ class NativeRolloutEngine(InferenceEngine):
         self._thread: threading.Thread | None = None
         self._pending: dict[int, tuple[asyncio.AbstractEventLoop, asyncio.Future, dict]] = {}
         self._params: dict[int, tuple[float, int, float]] = {}
+        # vision-language requests: rid → pixel rows, patch grids, position triples of the prompt and the offset
+        # of the positions that follow it
+        self._mm: dict[int, dict[str, Any]] = {}
         self._lock = threading.Lock()
         self._executor = None
         self._gen_tokens = 0
@@ -291,7 +295,9 @@ class NativeRolloutEngine(InferenceEngine):
 
             self.hybrid_state = HybridState(mc, ncfg.max_num_seqs, dtype, self.device)
             self._free_state_slots = list(range(ncfg.max_num_seqs - 1, -1, -1))
-        self.sched.set_prompt_sharing(bool(getattr(ncfg, "prompt_sharing", True)) and not mc.is_hybrid)
+        # prompts are shared by token ids: two prompts with equal ids but different images must not share pages
+        self.sched.set_prompt_sharing(bool(getattr(ncfg, "prompt_sharing", True)) and not mc.is_hybrid
+                                      and not mc.is_vl)
         # The engine thread shares the interpreter with trainer / workflow threads; CPython hands the GIL over
         # every 5 ms by default, which is half a decode step. A shorter interval keeps the step loop's short
         # host phases from queueing behind another thread's Python.
@@ -303,7 +309,7 @@ class NativeRolloutEngine(InferenceEngine):
         self._rng = torch.Generator(device=self.device).manual_seed(ncfg.seed)
         self._graphs = None
         self.launches_per_decode = 0
-        if (self.device.type == "cuda" and ncfg.cuda_graph and not mc.is_hybrid
+        if (self.device.type == "cuda" and ncfg.cuda_graph and not mc.is_hybrid and not mc.is_vl
                 and _lib.use_cuda_kernels(next(self.model.parameters()))):
             self._capture_graphs()
         self._thread = threading.Thread(target=self._loop, name="rollout-engine", daemon=True)
@@ -445,6 +451,9 @@ class NativeRolloutEngine(InferenceEngine):
             meta = VarlenMeta(cu.tolist(), dev)
             extra = dict(hybrid_state=self.hybrid_state, state_slots=self._state_slots_of(seq_ids)) \
                 if self.hybrid_state is not None else {}
+            if self.model_config.is_vl:
+                extra.update(self._vision_prefill_inputs(ids, seq_ids, cu))
+                pos = torch.arange(T, dtype=torch.int32, device=dev) if "rope" in extra else pos
             hidden = self.model.prefill(ids, pos, meta, self.kv_caches, slots, **extra)
             last = torch.from_numpy((cu[1:] - 1).astype(np.int64)).to(dev)
             hidden = hidden.index_select(0, last)
@@ -455,6 +464,11 @@ class NativeRolloutEngine(InferenceEngine):
             bt = bt[:, :max(nb, 1)].contiguous().to(dev, non_blocking=True)
             extra = dict(hybrid_state=self.hybrid_state, state_slots=self._state_slots_of(seq_ids)) \
                 if self.hybrid_state is not None else {}
+            if self._mm:
+                # text after an image continues from the largest grid coordinate, not from the token count
+                with self._lock:
+                    delta = [self._mm[r]["delta"] if r in self._mm else 0 for r in seq_ids]
+                pos = pos + torch.tensor(delta, dtype=pos.dtype, device=dev)
             hidden = self.model.decode(ids, pos, self.kv_caches, bt, seq_lens, slots,
                                        max_seq_len=int(s.hdr.max_seq_len), **extra)
         logits = self.model.logits(hidden, out_dtype=torch.float32)
@@ -472,6 +486,60 @@ class NativeRolloutEngine(InferenceEngine):
         self._steps += 1
         self._deliver()
         return True
+
+    def _vision_prefill_inputs(self, ids: torch.Tensor, seq_ids: list[int], cu: np.ndarray) -> dict[str, Any]:
+        """Embeddings with image features and the per-token rotary table of a prefill plan; empty when no
+        sequence of the plan has images (the ordinary tables then serve: the three axes agree on text)."""
+        from ..models.qwen_vl import mrope_tables
+
+        with self._lock:
+            mms = [self._mm.get(r) for r in seq_ids]
+        if not any(mms):
+            return {}
+        pos3, pix, grids = [], [], []
+        for i, mm in enumerate(mms):
+            n = int(cu[i + 1] - cu[i])
+            if mm is None:
+                pos3.append(torch.arange(n)[None].expand(3, -1))
+            else:
+                assert mm["pos3"].shape[1] == n, "an image prompt is prefilled whole"
+                pos3.append(mm["pos3"])
+                pix.append(mm["pixel_values"])
+                grids.append(mm["image_grid_thw"])
+        mc = self.model_config
+        pos3 = torch.cat(pos3, 1).to(self.device)
+        x = self.model.embed_inputs(ids.long(), torch.cat(pix, 0), torch.cat(grids, 0))
+        return dict(embeds=x, rope=mrope_tables(pos3, mc.rotary_dim, mc.rope_theta, mc.mrope_section))
+
+    @property
+    def supports_images(self) -> bool:
+        return self.model_config is not None and self.model_config.is_vl
+
+    def _image_inputs(self, req: ModelRequest) -> dict[str, torch.Tensor] | None:
+        """``pixel_values`` / ``image_grid_thw`` of a request: taken from ``metadata["multi_modal_input"]``
+        when the caller already ran the processor, else computed from ``image_data`` (base64-encoded images)
+        with the request's processor."""
+        mm = req.metadata.get("multi_modal_input") if req.metadata else None
+        if isinstance(mm, (list, tuple)):
+            mm = mm[0] if mm else None
+        if not mm and not req.image_data:
+            return None
+        if not self.supports_images:
+            raise NotImplementedError(f"{self.model_config.model_type} is a text-only model: it cannot serve images")
+        if not mm:
+            import base64
+            import io
+
+            from PIL import Image
+
+            if req.processor is None:
+                raise ValueError("a request with image_data needs its processor (or precomputed multi_modal_input)")
+            images = [Image.open(io.BytesIO(base64.b64decode(b))) if isinstance(b, (str, bytes)) else b
+                      for b in req.image_data]
+            ip = getattr(req.processor, "image_processor", req.processor)
+            mm = ip(images=images, return_tensors="pt")
+        return dict(pixel_values=torch.as_tensor(mm["pixel_values"]),
+                    image_grid_thw=torch.as_tensor(mm["image_grid_thw"]).view(-1, 3))
 
     def _copy_pages(self, pairs: np.ndarray):
         """Private copies of the page holding a shared prompt's last positions (prompt forks)."""
@@ -496,6 +564,7 @@ class NativeRolloutEngine(InferenceEngine):
             with self._lock:
                 entry = self._pending.pop(rid, None)
                 self._params.pop(rid, None)
+                self._mm.pop(rid, None)
             if entry is None:
                 continue
             loop, fut, _ = entry
@@ -509,7 +578,7 @@ class NativeRolloutEngine(InferenceEngine):
             loop.call_soon_threadsafe(_set_exception, fut, e)
 
     # --------------------------------------------------------------- generate
-    async def _generate_once(self, input_ids: list[int], g, max_new: int):
+    async def _generate_once(self, input_ids: list[int], g, max_new: int, images=None):
         if self._step_error is not None:
             raise RuntimeError("rollout engine stopped") from self._step_error
         loop = asyncio.get_running_loop()
@@ -517,12 +586,21 @@ class NativeRolloutEngine(InferenceEngine):
         stop = list(g.stop_token_ids or [])
         temp = 0.0 if g.greedy else float(g.temperature)
         top_k = int(g.top_k) if 0 < int(g.top_k) < self.model_config.vocab_size else 0
+        mm_state = None
+        if images is not None:
+            from ..models.qwen_vl import mrope_position_ids
+
+            pos3, deltas = mrope_position_ids(input_ids, [0, len(input_ids)], images["image_grid_thw"].tolist(),
+                                              self.model_config)
+            mm_state = dict(images, pos3=pos3, delta=int(deltas[0]))
         with self._lock:
             rid = self.sched.add(input_ids, max_new, int(g.min_new_tokens), stop, bool(g.ignore_eos))
             if rid < 0:
                 raise ValueError(f"prompt of {len(input_ids)} tokens does not fit the rollout engine")
             self._pending[rid] = (loop, fut, {})
             self._params[rid] = (temp, top_k, float(g.top_p))
+            if mm_state is not None:
+                self._mm[rid] = mm_state
         with self._wake:
             self._wake.notify_all()
         return await fut
@@ -532,6 +610,7 @@ class NativeRolloutEngine(InferenceEngine):
         if g.n_samples != 1:
             raise ValueError("agenerate produces one sample; use n_samples=1 and group at the workflow level")
         max_new = min(g.max_new_tokens, max(g.max_tokens - len(req.input_ids), 0))
+        images = self._image_inputs(req)
         t0 = time.perf_counter()
         out_tokens: list[int] = []
         out_logprobs: list[float] = []
@@ -543,7 +622,7 @@ class NativeRolloutEngine(InferenceEngine):
                 await asyncio.sleep(0.001)
             version = self._version
             reason, toks, lps = await self._generate_once(list(req.input_ids) + out_tokens, g,
-                                                          max_new - len(out_tokens))
+                                                          max_new - len(out_tokens), images)
             if toks and ttft == float("inf"):
                 ttft = time.perf_counter() - t0
             out_tokens += toks
@@ -666,6 +745,7 @@ class NativeRolloutEngine(InferenceEngine):
             nblocks = self.sched.stats()["free_blocks"]
             self.kv_caches = self._alloc_kv(nblocks, dtype)
             if (self.device.type == "cuda" and self.ncfg.cuda_graph and not self.model_config.is_hybrid
+                    and not self.model_config.is_vl
                     and _lib.use_cuda_kernels(next(self.model.parameters()))):
                 self._capture_graphs()
         self.continue_generation()

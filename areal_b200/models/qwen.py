@@ -489,17 +489,18 @@ class QwenModel(nn.Module):
     # -------------------------------------------------- rollout (paged cache)
     @torch.no_grad()
     def prefill(self, input_ids, position_ids, meta: VarlenMeta, kv_caches, slot_mapping, hybrid_state=None,
-                state_slots=None):
+                state_slots=None, embeds=None, rope=None):
         """Packed prompt forward that also writes K/V of every layer into the
         paged caches; returns hidden states of all tokens. Hybrid models also take the per-sequence
-        state of their linear-attention layers and the slot of every sequence in it."""
+        state of their linear-attention layers and the slot of every sequence in it. ``embeds`` /
+        ``rope`` as in :meth:`forward` (image features merged into the embeddings, one rotary row per token)."""
         if self.cfg.is_hybrid:
             from .qwen3_5 import hybrid_prefill
 
             return hybrid_prefill(self, input_ids, position_ids, meta, kv_caches, slot_mapping, hybrid_state, state_slots)
-        cos, sin = self.rope(input_ids.device)
+        cos, sin = rope if rope is not None else self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
-        x = F.embedding(input_ids.long(), self.embed)
+        x = embeds if embeds is not None else F.embedding(input_ids.long(), self.embed)
         res = None
         for i, layer in enumerate(self.layers):
             if res is None:

@@ -3,9 +3,10 @@
 The processor turns ``messages`` + ``images`` into token ids and pixel tensors; the request
 carries the images (base64 PNG) to the inference engine and the trajectory keeps the processor's
 ``multi_modal_input`` next to the usual token-level fields so a vision-language train engine can
-recompute logprobs. Behaviour of areal/workflow/vision_rlvr.py in the reference. The rollout and
-train engines of this package are text-only; an engine that does not accept images rejects the
-request with a clear error rather than silently dropping them.
+recompute logprobs. Behaviour of areal/workflow/vision_rlvr.py in the reference. The in-process
+rollout engine serves Qwen2.5-VL and reads the processor's tensors straight from the request's
+metadata; an engine that does not accept images (a text-only model) rejects the request with a
+clear error rather than silently dropping them.
 """
 
 from __future__ import annotations
@@ -42,8 +43,12 @@ class VisionRLVRWorkflow(RLVRWorkflow):
             if "messages" in data else data["prompt"]
         proc = self.processor(images=images or None, text=text, padding=False, return_tensors="pt")
         input_ids = proc["input_ids"][0].tolist()
+        mm = {k: v for k, v in proc.items() if k not in ("input_ids", "attention_mask")}
+        # an in-process engine reads the processor's tensors from the metadata; a remote server gets the encoded
+        # images and runs its own processor
         req = ModelRequest(rid=uuid.uuid4().hex, input_ids=input_ids, gconfig=self.gconfig, tokenizer=self.tokenizer,
-                           image_data=[image_to_base64(i) for i in images] or None)
+                           image_data=[image_to_base64(i) for i in images] or None, processor=self.processor,
+                           metadata={"multi_modal_input": [mm]} if images else {})
         if images and not getattr(engine, "supports_images", False):
             raise NotImplementedError(f"{type(engine).__name__} is a text-only engine: it cannot serve image prompts")
         resp = await engine.agenerate(req)
@@ -53,7 +58,6 @@ class VisionRLVRWorkflow(RLVRWorkflow):
         stats_tracker.get("rollout").scalar(reward=reward, gen_len=float(resp.output_len))
         seq = resp.input_tokens + resp.output_tokens
         n_in, n_out = resp.input_len, resp.output_len
-        mm = {k: v for k, v in proc.items() if k not in ("input_ids", "attention_mask")}
         return dict(
             input_ids=torch.tensor(seq, dtype=torch.int32).unsqueeze(0),
             attention_mask=torch.ones(1, len(seq), dtype=torch.bool),

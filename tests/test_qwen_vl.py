@@ -150,3 +150,149 @@ def test_engine_trains_on_images(tmp_path):
         tr.train(max_steps=6, step_callback=lambda s, st: losses.append(st["step/loss"]))
         assert losses[-1] < losses[0]
         assert not torch.equal(eng.model.visual.patch_embed, w0), "the vision tower must train"
+
+
+def _rollout_engine(device="cpu", **over):
+    from areal_b200.api.cli_args import InferenceEngineConfig, NativeRolloutConfig
+    from areal_b200.engine.rollout_engine import NativeRolloutEngine
+
+    cfg = InferenceEngineConfig(experiment_name="e", trial_name="t", backend="native:d1", max_concurrent_rollouts=16,
+                                consumer_batch_size=4,
+                                native=NativeRolloutConfig(model_preset="tiny-qwen2_5-vl", context_length=128,
+                                                           max_num_seqs=8, max_num_batched_tokens=512,
+                                                           num_kv_blocks=64, seed=3, **over))
+    return NativeRolloutEngine(cfg).initialize(**({"device": device} if device == "cpu" else {}))
+
+
+def test_rollout_engine_serves_image_prompts():
+    """Greedy generation for a mix of image and text prompts equals re-running the whole model on the growing
+    sequence (image features in the prefill, positions after an image offset by the prompt's delta)."""
+    import asyncio
+
+    from areal_b200.api.cli_args import GenerationHyperparameters
+    from areal_b200.api.io_struct import ModelRequest
+
+    eng = _rollout_engine()
+    try:
+        assert eng.supports_images
+        reqs = []
+        for i, grid in enumerate([(1, 4, 6), None, (1, 4, 4), (1, 6, 8)]):
+            if grid is None:
+                reqs.append((torch.randint(0, 900, (11,), generator=torch.Generator().manual_seed(i)).tolist(), None))
+            else:
+                ids, pix = _sample([grid], [3 + i, 2], seed=20 + i)
+                reqs.append((ids, dict(pixel_values=pix, image_grid_thw=torch.tensor([grid]))))
+        gc = GenerationHyperparameters(max_new_tokens=7, greedy=True, ignore_eos=True)
+
+        async def go():
+            return await asyncio.gather(*[
+                eng.agenerate(ModelRequest(rid=str(i), input_ids=ids, gconfig=gc,
+                                           metadata={"multi_modal_input": [mm]} if mm else {}))
+                for i, (ids, mm) in enumerate(reqs)])
+
+        outs = asyncio.run(go())
+        model = eng.model
+        for (p, mm), r in zip(reqs, outs):
+            seq = list(p)
+            for _ in range(7):
+                ids = torch.tensor(seq)
+                meta = VarlenMeta(torch.tensor([0, len(seq)], dtype=torch.int32), "cpu")
+                with torch.no_grad():
+                    h = model(ids, torch.arange(len(seq)), meta, **(mm or {}))
+                    seq.append(int(model.logits(h[-1:]).argmax(-1)))
+            assert r.output_tokens == seq[len(p):], (r.output_tokens, seq[len(p):])
+        assert not eng._mm
+        # encoded images need the request's processor
+        with pytest.raises(ValueError):
+            asyncio.run(eng.agenerate(ModelRequest(rid="x", input_ids=reqs[0][0], gconfig=gc, image_data=["AAAA"])))
+    finally:
+        eng.destroy()
+
+
+class _ToyTok:
+    eos_token_id = 1023
+    pad_token_id = 0
+
+    def decode(self, ids, **kw):
+        return " ".join(str(int(i)) for i in ids)
+
+
+class _ToyVLProcessor:
+    """Stands in for the HF processor: the "image" is bytes naming its patch grid (``b"4x6"``), the text is a
+    string of token ids in which ``<img>`` marks where the image goes."""
+
+    def __init__(self):
+        self.tokenizer = _ToyTok()
+
+    def __call__(self, images=None, text=None, padding=False, return_tensors="pt"):
+        ids, grids, pix = [], [], []
+        it = iter(images or [])
+        for w in text.split():
+            if w == "<img>":
+                h, wd = (int(x) for x in next(it).decode().split("x"))
+                grids.append([1, h, wd])
+                g = torch.Generator().manual_seed(h * 100 + wd)
+                pix.append(torch.randn(h * wd, 3 * 2 * 14 * 14, generator=g))
+                ids += [CFG.vision_start_token_id] + [IMG] * (h * wd // 4) + [CFG.vision_end_token_id]
+            else:
+                ids.append(int(w))
+        out = {"input_ids": torch.tensor([ids]), "attention_mask": torch.ones(1, len(ids), dtype=torch.long)}
+        if grids:
+            out["pixel_values"] = torch.cat(pix, 0)
+            out["image_grid_thw"] = torch.tensor(grids)
+        return out
+
+
+def _even_reward(prompt, completion, prompt_ids, completion_ids, **kw):
+    return 1.0 if sum(1 for t in completion_ids if t % 2 == 0) > len(completion_ids) / 2 else 0.0
+
+
+def test_grpo_step_with_images(tmp_path):
+    """Rollout → logprob recomputation → PPO update → weight push, with image prompts, in one process: the
+    trajectories keep each sample's images through batching and micro-batch splitting, the recomputed
+    logprobs agree with the rollout's, and the rollout engine ends up with the trained vision tower."""
+    from areal_b200.api.cli_args import (GenerationHyperparameters, GRPOConfig, InferenceEngineConfig, MicroBatchSpec,
+                                         NativeRolloutConfig, NormConfig, OptimizerConfig, PPOActorConfig,
+                                         _propagate_names)
+    from areal_b200.trainer.rl_trainer import PPOTrainer
+    from areal_b200.workflow.vision_rlvr import VisionRLVRWorkflow
+
+    cfg = GRPOConfig(experiment_name="vl", trial_name="t")
+    cfg.seed = 0
+    cfg.cluster.fileroot = str(tmp_path)
+    cfg.train_dataset.batch_size = 4
+    cfg.train_dataset.shuffle = False
+    cfg.gconfig = GenerationHyperparameters(n_samples=2, max_new_tokens=8, temperature=1.0, ignore_eos=True)
+    cfg.actor = PPOActorConfig(backend="fsdp:d1", model_preset="tiny-qwen2_5-vl", init_from_scratch=True,
+                               dtype="float32", optimizer=OptimizerConfig(lr=1e-3, warmup_steps_proportion=0.0),
+                               mb_spec=MicroBatchSpec(max_tokens_per_mb=64), ppo_n_minibatches=1,
+                               reward_norm=NormConfig(mean_level="group", std_level="group", group_size=2),
+                               kl_ctl=0.0, use_decoupled_loss=True, recompute_logprob=True)
+    cfg.rollout = InferenceEngineConfig(backend="native:d1", max_head_offpolicyness=0, max_concurrent_rollouts=16,
+                                        native=NativeRolloutConfig(model_preset="tiny-qwen2_5-vl", context_length=128,
+                                                                   max_num_seqs=8, max_num_batched_tokens=512,
+                                                                   num_kv_blocks=64, seed=0, dtype="float32"))
+    _propagate_names(cfg)
+    ds = [dict(prompt=f"{3 + i} 17 <img> 5 {40 + i}", images=[b"4x6" if i % 2 else b"4x4"]) for i in range(7)]
+    ds.append(dict(prompt="9 8 7 6 5", images=[]))  # one text-only prompt
+    seen = []
+    with PPOTrainer(cfg, ds) as tr:
+        w0 = tr.actor_engine.model.visual.patch_embed.detach().clone()
+        tr.train(workflow=VisionRLVRWorkflow,
+                 workflow_kwargs=dict(reward_fn=_even_reward, gconfig=cfg.gconfig, tokenizer=_ToyTok(),
+                                      processor=_ToyVLProcessor(), reward_in_process=True),
+                 max_steps=2, step_callback=lambda s, st: seen.append(st))
+        assert len(seen) == 2 and all(s["step/grad_norm"] > 0 for s in seen)
+        assert not torch.equal(tr.actor_engine.model.visual.patch_embed, w0)
+        assert torch.equal(tr.rollout.model.visual.patch_embed, tr.actor_engine.model.visual.patch_embed)
+        # behaviour logprobs (rollout engine: prefill with image features + decode at offset positions) equal the
+        # train engine's recomputation on the finished trajectory
+        import asyncio
+
+        wf = VisionRLVRWorkflow(_even_reward, cfg.gconfig.new(n_samples=1), _ToyTok(), _ToyVLProcessor(),
+                                reward_in_process=True)
+        traj = asyncio.run(wf.arun_episode(tr.rollout, ds[1]))
+        n_in = int((traj["loss_mask"][0] == 0).sum())
+        logp = tr.actor_engine.forward({k: v for k, v in traj.items() if k != "rewards"})
+        L = traj["input_ids"].shape[1]
+        assert torch.allclose(logp[0, n_in - 1:L - 1], traj["logprobs"][0, n_in:], atol=1e-4)
