@@ -30,6 +30,16 @@ from ..api.cli_args import GenerationHyperparameters, InferenceEngineConfig, Nat
 from ..api.io_struct import WeightUpdateMeta
 
 
+def _image_processor(engine):
+    """The image processor of the served checkpoint, loaded once (``engine.image_processor`` overrides it)."""
+    proc = getattr(engine, "image_processor", None)
+    if proc is None and getattr(engine.ncfg, "model_path", None):
+        from transformers import AutoImageProcessor
+
+        proc = engine.image_processor = AutoImageProcessor.from_pretrained(engine.ncfg.model_path)
+    return proc
+
+
 def create_app(engine) -> FastAPI:
     """FastAPI application around an initialised ``NativeRolloutEngine``."""
     app = FastAPI()
@@ -63,8 +73,17 @@ def create_app(engine) -> FastAPI:
             reason, toks, lps = "abort", [], []  # "abort before prefill": nothing was generated
         else:
             try:
-                reason, toks, lps = await engine._generate_once(ids, g, g.max_new_tokens)
-            except ValueError as e:
+                images = None
+                if body.get("image_data"):
+                    # base64 images, as SGLang's /generate takes them; the server's own image processor (from the
+                    # model directory) turns them into pixel rows and patch grids
+                    from ..api.io_struct import ModelRequest
+
+                    proc = _image_processor(engine)
+                    images = engine._image_inputs(ModelRequest(input_ids=ids, image_data=list(body["image_data"]),
+                                                               processor=proc))
+                reason, toks, lps = await engine._generate_once(ids, g, g.max_new_tokens, images)
+            except (ValueError, NotImplementedError) as e:
                 return JSONResponse({"error": str(e)}, status_code=400)
         return {"output_ids": toks,
                 "meta_info": {"finish_reason": {"type": reason}, "version": version,

@@ -162,6 +162,9 @@ BACKENDS = {"native": NativeBackend, "sglang": SGLangBackend, "vllm": VLLMBacken
 
 
 class RemoteInfEngine(InferenceEngine):
+    # encoded images travel in the request body; whether the served model takes them is the server's answer
+    supports_images = True
+
     def __init__(self, config: InferenceEngineConfig, backend: Any = None):
         self.config = config
         kind = (config.backend or "native").split(":")[0] if isinstance(config.backend, str) else "native"

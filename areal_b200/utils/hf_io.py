@@ -69,3 +69,12 @@ def load_hf_tokenizer(path: str, **kwargs):
     from transformers import AutoTokenizer
 
     return AutoTokenizer.from_pretrained(path, **kwargs)
+
+
+def load_hf_processor_and_tokenizer(path: str, **kwargs):
+    """``(processor, tokenizer)`` of a vision-language checkpoint (the processor expands image placeholders and
+    produces ``pixel_values`` / ``image_grid_thw``)."""
+    from transformers import AutoProcessor
+
+    processor = AutoProcessor.from_pretrained(path, **kwargs)
+    return processor, getattr(processor, "tokenizer", None) or load_hf_tokenizer(path, **kwargs)

@@ -296,3 +296,134 @@ def test_grpo_step_with_images(tmp_path):
         logp = tr.actor_engine.forward({k: v for k, v in traj.items() if k != "rewards"})
         L = traj["input_ids"].shape[1]
         assert torch.allclose(logp[0, n_in - 1:L - 1], traj["logprobs"][0, n_in:], atol=1e-4)
+
+
+def _png(h, w, seed=0):
+    import io
+
+    import numpy as np
+    from PIL import Image
+
+    rng = np.random.default_rng(seed)
+    buf = io.BytesIO()
+    Image.fromarray((rng.random((h, w, 3)) * 255).astype("uint8")).save(buf, format="PNG")
+    return buf.getvalue()
+
+
+def test_encoded_images_through_the_hf_image_processor():
+    """A request that carries base64 PNGs (what a remote caller sends) is decoded and run through the
+    request's processor; the result equals handing over the processor's tensors directly."""
+    import asyncio
+    import base64
+    import io
+
+    transformers = pytest.importorskip("transformers")
+    from PIL import Image
+
+    from areal_b200.api.cli_args import GenerationHyperparameters
+    from areal_b200.api.io_struct import ModelRequest
+
+    ip = transformers.Qwen2VLImageProcessor(min_pixels=28 * 28, max_pixels=112 * 112)
+    png = _png(70, 90)
+    direct = ip(images=[Image.open(io.BytesIO(png))], return_tensors="pt")
+    t, h, w = direct["image_grid_thw"][0].tolist()
+    assert direct["pixel_values"].shape == (t * h * w, 1176)
+    ids = [5, 6, CFG.vision_start_token_id] + [IMG] * (t * h * w // 4) + [CFG.vision_end_token_id, 7]
+    gc = GenerationHyperparameters(max_new_tokens=5, greedy=True, ignore_eos=True)
+    eng = _rollout_engine()
+    try:
+        a = asyncio.run(eng.agenerate(ModelRequest(rid="a", input_ids=ids, gconfig=gc, processor=ip,
+                                                   image_data=[base64.b64encode(png).decode()])))
+        b = asyncio.run(eng.agenerate(ModelRequest(rid="b", input_ids=ids, gconfig=gc,
+                                                   metadata={"multi_modal_input": [dict(direct)]})))
+        assert a.output_tokens == b.output_tokens and a.output_logprobs == pytest.approx(b.output_logprobs, abs=1e-6)
+    finally:
+        eng.destroy()
+
+
+def test_clevr_sft_builder(tmp_path):
+    """Dataset builder: placeholder expansion by the processor, loss on the answer tokens, pixel tensors kept."""
+    import json
+
+    from areal_b200.dataset import get_custom_dataset
+
+    class Tok:
+        eos_token = "<eos>"
+
+        def encode(self, text, add_special_tokens=False):
+            return [int(w) for w in text.split()]
+
+    class Proc(_ToyVLProcessor):
+        def __init__(self):
+            self.tokenizer = Tok()
+
+        def __call__(self, text=None, images=None, **kw):
+            text = text[0].replace("<|vision_start|><|image_pad|><|vision_end|>", " <img> ").replace("<eos>", " 1023")
+            return super().__call__(images=[im.encode() for im in images] if images else None, text=text)
+
+    d = tmp_path / "clevr_count_70k"
+    d.mkdir()
+    rows = [dict(problem="<image>4 5 6 ", answer="3", images=["4x6"]), dict(problem="7 8 ", answer="2 2", images=[])]
+    (d / "train.jsonl").write_text("\n".join(json.dumps(r) for r in rows))
+    items = get_custom_dataset(path=str(d), type="sft", split="train", processor=Proc())
+    a, b = items
+    assert a["input_ids"][0] == CFG.vision_start_token_id and a["input_ids"].count(IMG) == 6
+    assert a["loss_mask"] == [0] * (len(a["input_ids"]) - 2) + [1, 1] and a["input_ids"][-2:] == [3, 1023]
+    assert a["multi_modal_input"][0]["pixel_values"].shape == (24, 1176)
+    assert "multi_modal_input" not in b and b["loss_mask"] == [0, 0, 1, 1, 1]
+    from areal_b200.trainer.sl_trainer import collate_sft
+
+    batch = collate_sft(items)
+    assert batch["input_ids"].shape[0] == 2 and batch["multi_modal_input"][1] == {}
+
+
+def test_image_prompt_over_http():
+    """The HTTP front takes SGLang-style ``image_data`` and the client engine forwards it: same tokens as the
+    in-process call."""
+    import asyncio
+    import base64
+    import io
+    import socket
+    import threading
+
+    transformers = pytest.importorskip("transformers")
+    uvicorn = pytest.importorskip("uvicorn")
+    from PIL import Image
+
+    from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig
+    from areal_b200.api.io_struct import ModelRequest
+    from areal_b200.engine.native_server import create_app
+    from areal_b200.infra.remote_inf_engine import RemoteInfEngine
+
+    ip = transformers.Qwen2VLImageProcessor(min_pixels=28 * 28, max_pixels=112 * 112)
+    png = _png(60, 60, seed=2)
+    direct = ip(images=[Image.open(io.BytesIO(png))], return_tensors="pt")
+    t, h, w = direct["image_grid_thw"][0].tolist()
+    ids = [9, CFG.vision_start_token_id] + [IMG] * (t * h * w // 4) + [CFG.vision_end_token_id, 11, 12]
+    gc = GenerationHyperparameters(max_new_tokens=6, greedy=True, ignore_eos=True)
+    eng = _rollout_engine()
+    eng.image_processor = ip
+    sock = socket.socket()
+    sock.bind(("127.0.0.1", 0))
+    port = sock.getsockname()[1]
+    sock.close()
+    server = uvicorn.Server(uvicorn.Config(create_app(eng), host="127.0.0.1", port=port, log_level="error"))
+    th = threading.Thread(target=server.run, daemon=True)
+    th.start()
+    client = None
+    try:
+        cfg = InferenceEngineConfig(experiment_name="e", trial_name="t", backend="native:d1", max_concurrent_rollouts=4,
+                                    consumer_batch_size=1, setup_timeout=30.0, request_timeout=60.0)
+        client = RemoteInfEngine(cfg).initialize(addr=[f"127.0.0.1:{port}"])
+        assert client.supports_images
+        req = ModelRequest(rid="r", input_ids=ids, gconfig=gc, image_data=[base64.b64encode(png).decode()])
+        remote = client.generate(req)
+        local = asyncio.run(eng.agenerate(ModelRequest(rid="l", input_ids=ids, gconfig=gc,
+                                                       metadata={"multi_modal_input": [dict(direct)]})))
+        assert remote.output_tokens == local.output_tokens
+    finally:
+        if client is not None:
+            client.destroy()
+        server.should_exit = True
+        th.join(timeout=10)
+        eng.destroy()
