@@ -144,8 +144,8 @@ class ModelConfig:
         if "text_config" in cfg:  # composite (vision-language) checkpoints nest the decoder's config
             cfg = cfg["text_config"]
         mt = cfg.get("model_type", "qwen3")
-        if top.get("model_type") == "qwen2_5_vl":
-            mt = "qwen2_5_vl"
+        if top.get("model_type") in ("qwen2_5_vl", "qwen2_vl"):
+            mt = top["model_type"]
         if mt.startswith("qwen3_5"):
             mt = "qwen3_5"
         heads = cfg["num_attention_heads"]
@@ -163,7 +163,7 @@ class ModelConfig:
             rope_theta=cfg.get("rope_theta") or rope_params.get("rope_theta", 1e4),
             max_position_embeddings=cfg.get("max_position_embeddings", 32768),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
-            attention_bias=cfg.get("attention_bias", mt in ("qwen2", "qwen2_5_vl")),
+            attention_bias=cfg.get("attention_bias", mt in ("qwen2", "qwen2_5_vl", "qwen2_vl")),
             qk_norm=mt.startswith("qwen3"),
             num_experts=cfg.get("num_experts", 0) or 0,
             num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
@@ -182,8 +182,13 @@ class ModelConfig:
                         "linear_num_key_heads", "linear_num_value_heads"):
                 if key in cfg:
                     setattr(out, key, cfg[key])
-        if mt == "qwen2_5_vl":
-            out.vision = {k: v for k, v in (top.get("vision_config") or {}).items() if k in _VISION_KEYS}
+        if mt in ("qwen2_5_vl", "qwen2_vl"):
+            vc = dict(top.get("vision_config") or {})
+            if mt == "qwen2_vl":
+                # Qwen2-VL names the tower width `embed_dim`, the merger's output `hidden_size` and the MLP by ratio
+                vc = dict(vc, hidden_size=vc["embed_dim"], out_hidden_size=vc["hidden_size"],
+                          intermediate_size=int(vc["embed_dim"] * vc.get("mlp_ratio", 4)), variant="qwen2_vl")
+            out.vision = {k: v for k, v in vc.items() if k in _VISION_KEYS}
             rope_scaling = cfg.get("rope_scaling") or top.get("rope_scaling") or {}
             out.mrope_section = list(rope_params.get("mrope_section") or rope_scaling.get("mrope_section")
                                      or [out.head_dim // 8, 3 * out.head_dim // 16, 3 * out.head_dim // 16])
@@ -235,8 +240,16 @@ class ModelConfig:
         return d
 
     def _to_hf_config_vl(self) -> dict:
+        v2 = self.model_type == "qwen2_vl"
+        vision = dict(self.vision, model_type=self.model_type)
+        vision.pop("variant", None)
+        if v2:
+            vision = {k: v for k, v in vision.items() if k not in ("intermediate_size", "out_hidden_size")}
+            vision.update(embed_dim=self.vision["hidden_size"], hidden_size=self.vision["out_hidden_size"],
+                          mlp_ratio=self.vision["intermediate_size"] // self.vision["hidden_size"],
+                          hidden_act="quick_gelu")
         text = {
-            "model_type": "qwen2_5_vl_text", "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
+            "model_type": self.model_type + "_text", "vocab_size": self.vocab_size, "hidden_size": self.hidden_size,
             "intermediate_size": self.intermediate_size, "num_hidden_layers": self.num_hidden_layers,
             "num_attention_heads": self.num_attention_heads, "num_key_value_heads": self.num_key_value_heads,
             "rms_norm_eps": self.rms_norm_eps, "max_position_embeddings": self.max_position_embeddings,
@@ -244,8 +257,9 @@ class ModelConfig:
             "rope_parameters": {"rope_type": "default", "rope_theta": self.rope_theta,
                                 "mrope_section": list(self.mrope_section)},
         }
-        return {"architectures": ["Qwen2_5_VLForConditionalGeneration"], "model_type": "qwen2_5_vl",
-                "text_config": text, "vision_config": dict(self.vision, model_type="qwen2_5_vl"),
+        arch = "Qwen2VLForConditionalGeneration" if v2 else "Qwen2_5_VLForConditionalGeneration"
+        return {"architectures": [arch], "model_type": self.model_type,
+                "text_config": text, "vision_config": vision,
                 "image_token_id": self.image_token_id, "video_token_id": self.video_token_id,
                 "vision_start_token_id": self.vision_start_token_id,
                 "vision_end_token_id": self.vision_end_token_id,
@@ -257,7 +271,7 @@ class ModelConfig:
 
 _VISION_KEYS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_channels", "patch_size",
                 "spatial_merge_size", "temporal_patch_size", "tokens_per_second", "window_size", "out_hidden_size",
-                "fullatt_block_indexes", "hidden_act")
+                "fullatt_block_indexes", "hidden_act", "variant")
 
 # Named shapes used by the benchmark configurations (random-init, synthetic data).
 PRESETS: dict[str, ModelConfig] = {
@@ -274,6 +288,14 @@ PRESETS: dict[str, ModelConfig] = {
                                                in_channels=3, patch_size=14, spatial_merge_size=2,
                                                temporal_patch_size=2, tokens_per_second=1, window_size=56,
                                                out_hidden_size=256, fullatt_block_indexes=[1], hidden_act="silu")),
+    "tiny-qwen2-vl": ModelConfig(model_type="qwen2_vl", vocab_size=1024, hidden_size=256, intermediate_size=688,
+                                 num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                                 rope_theta=1e4, tie_word_embeddings=False, attention_bias=True, qk_norm=False,
+                                 mrope_section=[8, 12, 12], image_token_id=1000, video_token_id=1001,
+                                 vision_start_token_id=1002, vision_end_token_id=1003,
+                                 vision=dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=2,
+                                             in_channels=3, patch_size=14, spatial_merge_size=2,
+                                             temporal_patch_size=2, out_hidden_size=256, variant="qwen2_vl")),
     "tiny-qwen3_5": ModelConfig(model_type="qwen3_5", vocab_size=1024, hidden_size=256, intermediate_size=512,
                                 num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                                 rope_theta=1e4, tie_word_embeddings=False, partial_rotary_factor=0.25,

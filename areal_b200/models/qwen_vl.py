@@ -1,11 +1,12 @@
-"""Qwen2.5-VL: a windowed vision transformer in front of the Qwen2 decoder with multimodal rotary positions.
+"""Qwen2.5-VL and Qwen2-VL: a vision transformer in front of the Qwen2 decoder with multimodal rotary positions.
 
 The decoder is the package's ``QwenModel`` unchanged (fused projections, own kernels); this module adds
 
 * ``VisionTower``: patch embedding (the 3-D convolution with stride = kernel is one GEMM over flattened
   patches), blocks of RMSNorm → attention with 2-D rotary embedding → SwiGLU MLP, where most blocks attend inside
   windows of ``window_size`` pixels and the ``fullatt_block_indexes`` blocks inside a whole image, and the
-  merger that turns each ``spatial_merge_size²`` group of patches into one decoder token;
+  merger that turns each ``spatial_merge_size²`` group of patches into one decoder token. The Qwen2-VL tower is
+  the same skeleton with LayerNorm, a fc1 → quick-GELU → fc2 MLP and no windows;
 * ``mrope_position_ids`` / ``mrope_tables``: every token gets a (temporal, height, width) position triple (text
   tokens: three equal values; image tokens: their grid coordinates offset by the running position) and the rotary
   frequencies are split over the three axes by ``mrope_section``. The decoder's rotary kernels read a table row per
@@ -122,28 +123,43 @@ def _segment_attention(q, k, v, cu: list[int]):
     return out
 
 
+def _norm(x, w, shift, eps: float = 1e-6):
+    """RMSNorm (Qwen2.5-VL, ``shift`` None) or LayerNorm with bias (Qwen2-VL)."""
+    if shift is None:
+        return fused.rmsnorm_ref(x, w, eps)
+    return F.layer_norm(x, (x.shape[-1],), w, shift, eps)
+
+
 class VisionBlock(nn.Module):
-    def __init__(self, dim: int, inter: int, heads: int, dtype, device):
+    """``gated``: RMSNorm + SwiGLU MLP (Qwen2.5-VL); otherwise LayerNorm + fc1 → quick-GELU → fc2 (Qwen2-VL)."""
+
+    def __init__(self, dim: int, inter: int, heads: int, dtype, device, gated: bool = True):
         super().__init__()
         mk = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype, device=device))
-        self.heads = heads
+        self.heads, self.gated = heads, gated
         self.attn_norm, self.mlp_norm = mk(dim), mk(dim)
+        self.attn_shift, self.mlp_shift = (None, None) if gated else (mk(dim), mk(dim))
         self.qkv, self.qkv_bias = mk(3 * dim, dim), mk(3 * dim)
         self.proj, self.proj_bias = mk(dim, dim), mk(dim)
-        self.gate_up, self.gate_up_bias = mk(2 * inter, dim), mk(2 * inter)
+        # SwiGLU keeps gate and up fused; the plain MLP's fc1 has the same role with half the rows
+        self.gate_up, self.gate_up_bias = mk((2 if gated else 1) * inter, dim), mk((2 if gated else 1) * inter)
         self.down, self.down_bias = mk(dim, inter), mk(dim)
 
-    def forward(self, x, cos, sin, cu: list[int], eps: float = 1e-6):
+    def forward(self, x, cos, sin, cu: list[int]):
         n, dim = x.shape
-        h = fused.rmsnorm_ref(x, self.attn_norm, eps)
+        h = _norm(x, self.attn_norm, self.attn_shift)
         q, k, v = F.linear(h, self.qkv, self.qkv_bias).view(n, 3, self.heads, dim // self.heads).unbind(1)
         qf, kf = q.float(), k.float()
         q = (qf * cos + _rot_half(qf) * sin).to(x.dtype)
         k = (kf * cos + _rot_half(kf) * sin).to(x.dtype)
         x = x + F.linear(_segment_attention(q, k, v, cu).reshape(n, dim), self.proj, self.proj_bias)
-        h = fused.rmsnorm_ref(x, self.mlp_norm, eps)
-        g, u = F.linear(h, self.gate_up, self.gate_up_bias).chunk(2, -1)
-        return x + F.linear(F.silu(g) * u, self.down, self.down_bias)
+        h = F.linear(_norm(x, self.mlp_norm, self.mlp_shift), self.gate_up, self.gate_up_bias)
+        if self.gated:
+            g, u = h.chunk(2, -1)
+            h = F.silu(g) * u
+        else:
+            h = h * torch.sigmoid(1.702 * h)  # quick GELU
+        return x + F.linear(h, self.down, self.down_bias)
 
 
 class VisionTower(nn.Module):
@@ -153,15 +169,17 @@ class VisionTower(nn.Module):
     def __init__(self, vc: dict, dtype, device):
         super().__init__()
         self.vc = vc
+        self.gated = vc.get("variant", "qwen2_5_vl") != "qwen2_vl"
         dim, self.heads = vc["hidden_size"], vc["num_heads"]
         self.merge = vc.get("spatial_merge_size", 2)
         self.unit = self.merge * self.merge
         self.patch_dim = vc.get("in_channels", 3) * vc.get("temporal_patch_size", 2) * vc["patch_size"] ** 2
         mk = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype, device=device))
         self.patch_embed = mk(dim, self.patch_dim)
-        self.blocks = nn.ModuleList(VisionBlock(dim, vc["intermediate_size"], self.heads, dtype, device)
+        self.blocks = nn.ModuleList(VisionBlock(dim, vc["intermediate_size"], self.heads, dtype, device, self.gated)
                                     for _ in range(vc["depth"]))
         self.merger_norm = mk(dim)
+        self.merger_shift = None if self.gated else mk(dim)
         self.merger_fc1, self.merger_fc1_bias = mk(dim * self.unit, dim * self.unit), mk(dim * self.unit)
         self.merger_fc2, self.merger_fc2_bias = mk(vc["out_hidden_size"], dim * self.unit), mk(vc["out_hidden_size"])
 
@@ -207,7 +225,10 @@ class VisionTower(nn.Module):
         inv = 1.0 / (10000.0 ** (torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2)))
         rc = self._grid_coords(grids).float()
         fr = torch.cat((rc[:, :1] * inv, rc[:, 1:] * inv), -1)  # [N, hd / 2]
-        order, cu_win = self._windows(grids)
+        if self.gated:
+            order, cu_win = self._windows(grids)
+        else:  # Qwen2-VL: every block attends inside a whole frame, patches stay in input order
+            order, cu_win = torch.arange(n // self.unit), None
         pidx = (order[:, None] * self.unit + torch.arange(self.unit)[None, :]).reshape(-1)
         x = x.index_select(0, pidx.to(dev))
         fr = fr.index_select(0, pidx).to(dev)
@@ -219,8 +240,8 @@ class VisionTower(nn.Module):
                 cu_img.append(cu_img[-1] + h * w)
         full = set(self.vc.get("fullatt_block_indexes", []))
         for i, blk in enumerate(self.blocks):
-            x = blk(x, cos, sin, cu_img if i in full else cu_win)
-        x = fused.rmsnorm_ref(x, self.merger_norm, 1e-6).view(-1, dim * self.unit)
+            x = blk(x, cos, sin, cu_img if (cu_win is None or i in full) else cu_win)
+        x = _norm(x, self.merger_norm, self.merger_shift).view(-1, dim * self.unit)
         x = F.linear(F.gelu(F.linear(x, self.merger_fc1, self.merger_fc1_bias)), self.merger_fc2, self.merger_fc2_bias)
         return x.index_select(0, torch.argsort(order).to(dev))
 
@@ -238,12 +259,22 @@ class VisionTower(nn.Module):
             yield p + "attn.qkv.bias", b.qkv_bias
             yield p + "attn.proj.weight", b.proj
             yield p + "attn.proj.bias", b.proj_bias
-            yield p + "mlp.gate_proj.weight", b.gate_up[:inter]
-            yield p + "mlp.gate_proj.bias", b.gate_up_bias[:inter]
-            yield p + "mlp.up_proj.weight", b.gate_up[inter:]
-            yield p + "mlp.up_proj.bias", b.gate_up_bias[inter:]
-            yield p + "mlp.down_proj.weight", b.down
-            yield p + "mlp.down_proj.bias", b.down_bias
+            if self.gated:
+                yield p + "mlp.gate_proj.weight", b.gate_up[:inter]
+                yield p + "mlp.gate_proj.bias", b.gate_up_bias[:inter]
+                yield p + "mlp.up_proj.weight", b.gate_up[inter:]
+                yield p + "mlp.up_proj.bias", b.gate_up_bias[inter:]
+                yield p + "mlp.down_proj.weight", b.down
+                yield p + "mlp.down_proj.bias", b.down_bias
+            else:
+                yield p + "norm1.bias", b.attn_shift
+                yield p + "norm2.bias", b.mlp_shift
+                yield p + "mlp.fc1.weight", b.gate_up
+                yield p + "mlp.fc1.bias", b.gate_up_bias
+                yield p + "mlp.fc2.weight", b.down
+                yield p + "mlp.fc2.bias", b.down_bias
+        if not self.gated:
+            yield "merger.ln_q.bias", self.merger_shift
         yield "merger.ln_q.weight", self.merger_norm
         yield "merger.mlp.0.weight", self.merger_fc1
         yield "merger.mlp.0.bias", self.merger_fc1_bias
@@ -271,6 +302,8 @@ class QwenVLModel(QwenModel):
         for name, p in self.visual.named_parameters():
             if name.endswith("norm"):
                 p.fill_(1.0)
+            elif name.endswith("shift"):
+                p.zero_()
         return self
 
     def positions(self, input_ids, meta: VarlenMeta, image_grid_thw=None, video_second_per_grid=None):

@@ -15,12 +15,12 @@ CFG = PRESETS["tiny-qwen2_5-vl"]
 IMG = CFG.image_token_id
 
 
-def _model(seed=0):
-    m = build_model(CFG, dtype=torch.float32, seed=seed)
+def _model(seed=0, cfg=CFG):
+    m = build_model(cfg, dtype=torch.float32, seed=seed)
     g = torch.Generator().manual_seed(seed + 100)
     with torch.no_grad():  # biases and norm weights start at 0 / 1: perturb them so that parity exercises them
         for n, p in m.named_parameters():
-            if n.endswith("bias") or n.endswith("norm"):
+            if n.endswith(("bias", "norm", "shift")):
                 p.add_(torch.randn(p.shape, generator=g) * 0.05)
     return m
 
@@ -61,12 +61,15 @@ def test_position_triples():
     assert torch.allclose(cos, c0) and torch.allclose(sin, s0)
 
 
-def test_matches_transformers(tmp_path):
+@pytest.mark.parametrize("preset,hf_cls", [("tiny-qwen2_5-vl", "Qwen2_5_VLForConditionalGeneration"),
+                                           ("tiny-qwen2-vl", "Qwen2VLForConditionalGeneration")])
+def test_matches_transformers(tmp_path, preset, hf_cls):
     transformers = pytest.importorskip("transformers")
-    m = _model()
+    CFG = PRESETS[preset]
+    m = _model(cfg=CFG)
     assert isinstance(m, QwenVLModel)
     save_hf_checkpoint(m, CFG, str(tmp_path))
-    hf = transformers.Qwen2_5_VLForConditionalGeneration.from_pretrained(str(tmp_path), torch_dtype=torch.float32)
+    hf = getattr(transformers, hf_cls).from_pretrained(str(tmp_path), torch_dtype=torch.float32)
     hf.eval()
     grids = [(1, 6, 8), (1, 4, 4)]  # 3×4 merged units (ragged 2×2 windows) and 2×2
     ids, pix = _sample(grids, [5, 4, 6], seed=3)
@@ -79,6 +82,9 @@ def test_matches_transformers(tmp_path):
         assert float((feats - theirs_feats).abs().max()) < 1e-4
         mine = m.logits(m(ids_t, torch.arange(len(ids)), meta, pixel_values=pix, image_grid_thw=grid_t))
         pos, _ = m.positions(ids_t, meta, grid_t)
+        hf_pos, _ = hf.model.get_rope_index(ids_t[None], mm_token_type_ids=(ids_t == IMG).long()[None],
+                                            image_grid_thw=grid_t)
+        assert torch.equal(hf_pos[:, 0], pos)
         theirs = hf(input_ids=ids_t[None], pixel_values=pix, image_grid_thw=grid_t,
                     position_ids=pos[:, None, :]).logits[0]
     assert float((mine - theirs).abs().max()) < 5e-4
