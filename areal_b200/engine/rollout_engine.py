@@ -508,8 +508,9 @@ class NativeRolloutEngine(InferenceEngine):
                 grids.append(mm["image_grid_thw"])
         mc = self.model_config
         pos3 = torch.cat(pos3, 1).to(self.device)
-        x = self.model.embed_inputs(ids.long(), torch.cat(pix, 0), torch.cat(grids, 0))
-        return dict(embeds=x, rope=mrope_tables(pos3, mc.rotary_dim, mc.rope_theta, mc.mrope_section))
+        x, adds = self.model.embed_inputs(ids.long(), torch.cat(pix, 0), torch.cat(grids, 0))
+        return dict(embeds=x, layer_adds=adds,
+                    rope=mrope_tables(pos3, mc.rotary_dim, mc.rope_theta, mc.mrope_section, mc.mrope_interleaved))
 
     @property
     def supports_images(self) -> bool:

@@ -67,6 +67,7 @@ class ModelConfig:
     # the split of the rotary frequencies over the (temporal, height, width) position axes, and the placeholder ids
     vision: dict = field(default_factory=dict)
     mrope_section: list[int] = field(default_factory=list)
+    mrope_interleaved: bool = False  # Qwen3-VL: the three axes alternate over the rotary frequencies
     image_token_id: int = -1
     video_token_id: int = -1
     vision_start_token_id: int = -1
@@ -144,7 +145,7 @@ class ModelConfig:
         if "text_config" in cfg:  # composite (vision-language) checkpoints nest the decoder's config
             cfg = cfg["text_config"]
         mt = cfg.get("model_type", "qwen3")
-        if top.get("model_type") in ("qwen2_5_vl", "qwen2_vl"):
+        if top.get("model_type") in _VL_TYPES:
             mt = top["model_type"]
         if mt.startswith("qwen3_5"):
             mt = "qwen3_5"
@@ -182,8 +183,11 @@ class ModelConfig:
                         "linear_num_key_heads", "linear_num_value_heads"):
                 if key in cfg:
                     setattr(out, key, cfg[key])
-        if mt in ("qwen2_5_vl", "qwen2_vl"):
+        if mt in _VL_TYPES:
             vc = dict(top.get("vision_config") or {})
+            if mt == "qwen3_vl":
+                vc["variant"] = "qwen3_vl"
+                out.mrope_interleaved = bool(rope_params.get("mrope_interleaved", True))
             if mt == "qwen2_vl":
                 # Qwen2-VL names the tower width `embed_dim`, the merger's output `hidden_size` and the MLP by ratio
                 vc = dict(vc, hidden_size=vc["embed_dim"], out_hidden_size=vc["hidden_size"],
@@ -257,7 +261,11 @@ class ModelConfig:
             "rope_parameters": {"rope_type": "default", "rope_theta": self.rope_theta,
                                 "mrope_section": list(self.mrope_section)},
         }
-        arch = "Qwen2VLForConditionalGeneration" if v2 else "Qwen2_5_VLForConditionalGeneration"
+        if self.model_type == "qwen3_vl":
+            text.update(head_dim=self.head_dim, attention_bias=self.attention_bias)
+            text["rope_parameters"]["mrope_interleaved"] = self.mrope_interleaved
+        arch = {"qwen2_vl": "Qwen2VLForConditionalGeneration", "qwen3_vl": "Qwen3VLForConditionalGeneration"}.get(
+            self.model_type, "Qwen2_5_VLForConditionalGeneration")
         return {"architectures": [arch], "model_type": self.model_type,
                 "text_config": text, "vision_config": vision,
                 "image_token_id": self.image_token_id, "video_token_id": self.video_token_id,
@@ -271,7 +279,9 @@ class ModelConfig:
 
 _VISION_KEYS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_channels", "patch_size",
                 "spatial_merge_size", "temporal_patch_size", "tokens_per_second", "window_size", "out_hidden_size",
-                "fullatt_block_indexes", "hidden_act", "variant")
+                "fullatt_block_indexes", "hidden_act", "variant", "num_position_embeddings",
+                "deepstack_visual_indexes")
+_VL_TYPES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl")
 
 # Named shapes used by the benchmark configurations (random-init, synthetic data).
 PRESETS: dict[str, ModelConfig] = {
@@ -296,6 +306,16 @@ PRESETS: dict[str, ModelConfig] = {
                                  vision=dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=2,
                                              in_channels=3, patch_size=14, spatial_merge_size=2,
                                              temporal_patch_size=2, out_hidden_size=256, variant="qwen2_vl")),
+    "tiny-qwen3-vl": ModelConfig(model_type="qwen3_vl", vocab_size=1024, hidden_size=256, intermediate_size=512,
+                                 num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                                 rope_theta=1e4, tie_word_embeddings=False, attention_bias=False, qk_norm=True,
+                                 mrope_section=[12, 10, 10], mrope_interleaved=True, image_token_id=1000,
+                                 video_token_id=1001, vision_start_token_id=1002, vision_end_token_id=1003,
+                                 vision=dict(depth=3, hidden_size=64, intermediate_size=128, num_heads=2,
+                                             in_channels=3, patch_size=14, spatial_merge_size=2,
+                                             temporal_patch_size=2, out_hidden_size=256, variant="qwen3_vl",
+                                             num_position_embeddings=64, deepstack_visual_indexes=[0, 1],
+                                             hidden_act="gelu_pytorch_tanh")),
     "tiny-qwen3_5": ModelConfig(model_type="qwen3_5", vocab_size=1024, hidden_size=256, intermediate_size=512,
                                 num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                                 rope_theta=1e4, tie_word_embeddings=False, partial_rotary_factor=0.25,

@@ -430,13 +430,14 @@ class QwenModel(nn.Module):
 
     # --------------------------------------------------------------- forward
     def forward(self, input_ids, position_ids, meta: VarlenMeta, attn_fn=None, stage_input=None,
-                embeds=None, rope=None):
+                embeds=None, rope=None, layer_adds=None):
         """Packed forward; returns the final-normed hidden states ``[T, H]``. On a pipeline stage
         other than the first, ``stage_input = (x, res)`` are the activations received from the
         previous stage; a stage other than the last returns ``(x, res)`` for the next one.
         ``embeds`` replaces the embedding lookup and ``rope = (cos, sin)`` the rotary tables that
         ``position_ids`` index (a vision-language model passes image features merged into the token
-        embeddings and one table row per token)."""
+        embeddings and one table row per token). ``layer_adds = (rows, [f_0, f_1, …])`` adds ``f_l`` to the
+        hidden states of ``rows`` after block ``l`` (deep-stack vision features)."""
         cos, sin = rope if rope is not None else self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
         p = self.pctx
@@ -466,6 +467,8 @@ class QwenModel(nn.Module):
                 x, res = checkpoint(layer, x, res, cos, sin, pos, meta, attn_fn, use_reentrant=False)
             else:
                 x, res = layer(x, res, cos, sin, pos, meta, attn_fn)
+            if layer_adds is not None and li < len(layer_adds[1]):
+                x = x.index_add(0, layer_adds[0], layer_adds[1][li].to(x.dtype))  # hidden = x + res: add to x
         if not self.last_stage:
             return x, res
         y, _ = fused.rmsnorm(x, self.norm, self.cfg.rms_norm_eps, residual=res)
@@ -489,7 +492,7 @@ class QwenModel(nn.Module):
     # -------------------------------------------------- rollout (paged cache)
     @torch.no_grad()
     def prefill(self, input_ids, position_ids, meta: VarlenMeta, kv_caches, slot_mapping, hybrid_state=None,
-                state_slots=None, embeds=None, rope=None):
+                state_slots=None, embeds=None, rope=None, layer_adds=None):
         """Packed prompt forward that also writes K/V of every layer into the
         paged caches; returns hidden states of all tokens. Hybrid models also take the per-sequence
         state of their linear-attention layers and the slot of every sequence in it. ``embeds`` /
@@ -513,6 +516,8 @@ class QwenModel(nn.Module):
             a = linear(a.reshape(a.shape[0], -1), layer.attn.o)
             y, res = fused.rmsnorm(a, layer.post_norm, layer.eps, residual=res)
             x = layer.mlp(y)
+            if layer_adds is not None and i < len(layer_adds[1]):
+                x = x.index_add(0, layer_adds[0], layer_adds[1][i].to(x.dtype))
         y, _ = fused.rmsnorm(x, self.norm, self.cfg.rms_norm_eps, residual=res)
         return y
 

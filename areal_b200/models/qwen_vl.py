@@ -1,4 +1,4 @@
-"""Qwen2.5-VL and Qwen2-VL: a vision transformer in front of the Qwen2 decoder with multimodal rotary positions.
+"""Qwen2.5-VL, Qwen2-VL and Qwen3-VL: a vision transformer in front of the Qwen2 decoder with multimodal rotary positions.
 
 The decoder is the package's ``QwenModel`` unchanged (fused projections, own kernels); this module adds
 
@@ -6,7 +6,9 @@ The decoder is the package's ``QwenModel`` unchanged (fused projections, own ker
   patches), blocks of RMSNorm → attention with 2-D rotary embedding → SwiGLU MLP, where most blocks attend inside
   windows of ``window_size`` pixels and the ``fullatt_block_indexes`` blocks inside a whole image, and the
   merger that turns each ``spatial_merge_size²`` group of patches into one decoder token. The Qwen2-VL tower is
-  the same skeleton with LayerNorm, a fc1 → quick-GELU → fc2 MLP and no windows;
+  the same skeleton with LayerNorm, a fc1 → quick-GELU → fc2 MLP and no windows; the Qwen3-VL tower adds a learned
+  position table (interpolated to each image's grid) and "deep-stack" mergers whose outputs are added to the
+  decoder's hidden states at the image rows after its first blocks;
 * ``mrope_position_ids`` / ``mrope_tables``: every token gets a (temporal, height, width) position triple (text
   tokens: three equal values; image tokens: their grid coordinates offset by the running position) and the rotary
   frequencies are split over the three axes by ``mrope_section``. The decoder's rotary kernels read a table row per
@@ -87,13 +89,22 @@ def mrope_position_ids(input_ids: Sequence[int], cu_seqlens: Sequence[int], grid
     return out, deltas
 
 
-def mrope_tables(pos3: torch.Tensor, rotary_dim: int, theta: float, sections: Sequence[int]):
-    """``cos, sin [T, rotary_dim / 2]``: frequency ``j`` rotates by the position on the axis that owns it
-    (the first ``sections[0]`` frequencies follow the temporal axis, the next the height, the rest the width)."""
+def mrope_tables(pos3: torch.Tensor, rotary_dim: int, theta: float, sections: Sequence[int],
+                 interleaved: bool = False):
+    """``cos, sin [T, rotary_dim / 2]``: frequency ``j`` rotates by the position on the axis that owns it.
+    Chunked layout (Qwen2-VL / 2.5-VL): the first ``sections[0]`` frequencies follow the temporal axis, the next
+    the height, the rest the width. Interleaved (Qwen3-VL): axes alternate t, h, w, t, h, w, … while the height
+    and width sections last, the remaining frequencies are temporal."""
     assert sum(sections) == rotary_dim // 2, f"mrope_section {list(sections)} must sum to {rotary_dim // 2}"
     dev = pos3.device
     inv = 1.0 / (theta ** (torch.arange(0, rotary_dim, 2, dtype=torch.float32, device=dev) / rotary_dim))
-    axis = torch.repeat_interleave(torch.arange(3, device=dev), torch.tensor(list(sections), device=dev))
+    if interleaved:
+        j = torch.arange(rotary_dim // 2, device=dev)
+        axis = torch.zeros_like(j)
+        for a in (1, 2):
+            axis[(j % 3 == a) & (j < 3 * sections[a])] = a
+    else:
+        axis = torch.repeat_interleave(torch.arange(3, device=dev), torch.tensor(list(sections), device=dev))
     fr = pos3[axis].t().float() * inv
     return fr.cos().contiguous(), fr.sin().contiguous()
 
@@ -133,10 +144,10 @@ def _norm(x, w, shift, eps: float = 1e-6):
 class VisionBlock(nn.Module):
     """``gated``: RMSNorm + SwiGLU MLP (Qwen2.5-VL); otherwise LayerNorm + fc1 → quick-GELU → fc2 (Qwen2-VL)."""
 
-    def __init__(self, dim: int, inter: int, heads: int, dtype, device, gated: bool = True):
+    def __init__(self, dim: int, inter: int, heads: int, dtype, device, gated: bool = True, act: str = "quick_gelu"):
         super().__init__()
         mk = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype, device=device))
-        self.heads, self.gated = heads, gated
+        self.heads, self.gated, self.act = heads, gated, act
         self.attn_norm, self.mlp_norm = mk(dim), mk(dim)
         self.attn_shift, self.mlp_shift = (None, None) if gated else (mk(dim), mk(dim))
         self.qkv, self.qkv_bias = mk(3 * dim, dim), mk(3 * dim)
@@ -157,9 +168,26 @@ class VisionBlock(nn.Module):
         if self.gated:
             g, u = h.chunk(2, -1)
             h = F.silu(g) * u
+        elif self.act == "quick_gelu":
+            h = h * torch.sigmoid(1.702 * h)
         else:
-            h = h * torch.sigmoid(1.702 * h)  # quick GELU
+            h = F.gelu(h, approximate="tanh")
         return x + F.linear(h, self.down, self.down_bias)
+
+
+class DeepStackMerger(nn.Module):
+    """Qwen3-VL: an extra merger on an intermediate block's output (LayerNorm over the merged group)."""
+
+    def __init__(self, dim: int, unit: int, out: int, dtype, device):
+        super().__init__()
+        mk = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype, device=device))
+        self.norm, self.shift = mk(dim * unit), mk(dim * unit)
+        self.fc1, self.fc1_bias = mk(dim * unit, dim * unit), mk(dim * unit)
+        self.fc2, self.fc2_bias = mk(out, dim * unit), mk(out)
+
+    def forward(self, x):
+        x = _norm(x.view(-1, self.norm.shape[0]), self.norm, self.shift)
+        return F.linear(F.gelu(F.linear(x, self.fc1, self.fc1_bias)), self.fc2, self.fc2_bias)
 
 
 class VisionTower(nn.Module):
@@ -169,14 +197,24 @@ class VisionTower(nn.Module):
     def __init__(self, vc: dict, dtype, device):
         super().__init__()
         self.vc = vc
-        self.gated = vc.get("variant", "qwen2_5_vl") != "qwen2_vl"
+        self.variant = vc.get("variant", "qwen2_5_vl")
+        self.gated = self.variant == "qwen2_5_vl"
+        v3 = self.variant == "qwen3_vl"
         dim, self.heads = vc["hidden_size"], vc["num_heads"]
         self.merge = vc.get("spatial_merge_size", 2)
         self.unit = self.merge * self.merge
         self.patch_dim = vc.get("in_channels", 3) * vc.get("temporal_patch_size", 2) * vc["patch_size"] ** 2
         mk = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype, device=device))
         self.patch_embed = mk(dim, self.patch_dim)
-        self.blocks = nn.ModuleList(VisionBlock(dim, vc["intermediate_size"], self.heads, dtype, device, self.gated)
+        # Qwen3-VL: bias on the patch projection, a learned position table (a square grid, interpolated to each
+        # image's patch grid) and extra mergers on the outputs of the `deepstack_visual_indexes` blocks
+        self.patch_embed_bias = mk(dim) if v3 else None
+        self.pos_embed = mk(vc["num_position_embeddings"], dim) if v3 else None
+        self.deepstack_at = list(vc.get("deepstack_visual_indexes", [])) if v3 else []
+        self.deepstack = nn.ModuleList(DeepStackMerger(dim, self.unit, vc["out_hidden_size"], dtype, device)
+                                       for _ in self.deepstack_at)
+        act = "gelu_tanh" if v3 else "quick_gelu"
+        self.blocks = nn.ModuleList(VisionBlock(dim, vc["intermediate_size"], self.heads, dtype, device, self.gated, act)
                                     for _ in range(vc["depth"]))
         self.merger_norm = mk(dim)
         self.merger_shift = None if self.gated else mk(dim)
@@ -214,12 +252,34 @@ class VisionTower(nn.Module):
             base += t * gh * gw
         return torch.cat(order), cu
 
-    def forward(self, pixel_values: torch.Tensor, grid_thw) -> torch.Tensor:
+    def _pos_embed(self, grids: list[list[int]]) -> torch.Tensor:
+        """Bilinear interpolation of the square position table onto each image's ``h × w`` patch grid, rows in
+        the processor's patch order (merge groups contiguous)."""
+        side = int(self.pos_embed.shape[0] ** 0.5)
+        m, out = self.merge, []
+        for t, h, w in grids:
+            hi, wi = torch.linspace(0, side - 1, h), torch.linspace(0, side - 1, w)
+            h0, w0 = hi.int(), wi.int()
+            h1, w1 = (h0 + 1).clip(max=side - 1), (w0 + 1).clip(max=side - 1)
+            dh, dw = (hi - h0)[:, None], (wi - w0)[None, :]
+            e = 0
+            for hh, ww, wt in ((h0, w0, (1 - dh) * (1 - dw)), (h0, w1, (1 - dh) * dw), (h1, w0, dh * (1 - dw)),
+                               (h1, w1, dh * dw)):
+                idx = (hh[:, None] * side + ww[None, :]).reshape(-1).long().to(self.pos_embed.device)
+                e = e + self.pos_embed.index_select(0, idx) * wt.reshape(-1, 1).to(self.pos_embed)
+            e = e.view(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
+            out.append(e.repeat(t, 1))
+        return torch.cat(out, 0)
+
+    def forward(self, pixel_values: torch.Tensor, grid_thw, return_deepstack: bool = False):
         grids = [[int(v) for v in g] for g in (grid_thw.tolist() if torch.is_tensor(grid_thw) else grid_thw)]
         dev, dt = self.patch_embed.device, self.patch_embed.dtype
-        x = F.linear(pixel_values.to(device=dev, dtype=dt).view(-1, self.patch_dim), self.patch_embed)
+        x = F.linear(pixel_values.to(device=dev, dtype=dt).view(-1, self.patch_dim), self.patch_embed,
+                     self.patch_embed_bias)
         n, dim = x.shape
         assert n == sum(t * h * w for t, h, w in grids), "pixel_values rows do not match image_grid_thw"
+        if self.pos_embed is not None:
+            x = x + self._pos_embed(grids)
         hd = dim // self.heads
         # 2-D rotary: the first half of the rotated pairs turns with the patch's row, the second with its column
         inv = 1.0 / (10000.0 ** (torch.arange(0, hd // 2, 2, dtype=torch.float32) / (hd // 2)))
@@ -239,11 +299,15 @@ class VisionTower(nn.Module):
             for _ in range(t):
                 cu_img.append(cu_img[-1] + h * w)
         full = set(self.vc.get("fullatt_block_indexes", []))
+        deep = []
         for i, blk in enumerate(self.blocks):
             x = blk(x, cos, sin, cu_img if (cu_win is None or i in full) else cu_win)
+            if i in self.deepstack_at:
+                deep.append(self.deepstack[self.deepstack_at.index(i)](x))
         x = _norm(x, self.merger_norm, self.merger_shift).view(-1, dim * self.unit)
         x = F.linear(F.gelu(F.linear(x, self.merger_fc1, self.merger_fc1_bias)), self.merger_fc2, self.merger_fc2_bias)
-        return x.index_select(0, torch.argsort(order).to(dev))
+        x = x.index_select(0, torch.argsort(order).to(dev)) if cu_win is not None else x
+        return (x, deep) if return_deepstack else x
 
     # HF names (without the tower's prefix) ↔ parameters; fused gate/up are two HF tensors
     def hf_tensors(self) -> Iterator[tuple[str, torch.Tensor]]:
@@ -251,6 +315,19 @@ class VisionTower(nn.Module):
         yield "patch_embed.proj.weight", self.patch_embed.view(
             -1, vc.get("in_channels", 3), vc.get("temporal_patch_size", 2), vc["patch_size"], vc["patch_size"])
         inter = vc["intermediate_size"]
+        v3 = self.variant == "qwen3_vl"
+        fc1, fc2 = ("mlp.linear_fc1", "mlp.linear_fc2") if v3 else ("mlp.fc1", "mlp.fc2")
+        if v3:
+            yield "patch_embed.proj.bias", self.patch_embed_bias
+            yield "pos_embed.weight", self.pos_embed
+            for i, d in enumerate(self.deepstack):
+                q = f"deepstack_merger_list.{i}."
+                yield q + "norm.weight", d.norm
+                yield q + "norm.bias", d.shift
+                yield q + "linear_fc1.weight", d.fc1
+                yield q + "linear_fc1.bias", d.fc1_bias
+                yield q + "linear_fc2.weight", d.fc2
+                yield q + "linear_fc2.bias", d.fc2_bias
         for i, b in enumerate(self.blocks):
             p = f"blocks.{i}."
             yield p + "norm1.weight", b.attn_norm
@@ -269,17 +346,18 @@ class VisionTower(nn.Module):
             else:
                 yield p + "norm1.bias", b.attn_shift
                 yield p + "norm2.bias", b.mlp_shift
-                yield p + "mlp.fc1.weight", b.gate_up
-                yield p + "mlp.fc1.bias", b.gate_up_bias
-                yield p + "mlp.fc2.weight", b.down
-                yield p + "mlp.fc2.bias", b.down_bias
+                yield p + fc1 + ".weight", b.gate_up
+                yield p + fc1 + ".bias", b.gate_up_bias
+                yield p + fc2 + ".weight", b.down
+                yield p + fc2 + ".bias", b.down_bias
+        ln, m1, m2 = ("norm", "linear_fc1", "linear_fc2") if v3 else ("ln_q", "mlp.0", "mlp.2")
         if not self.gated:
-            yield "merger.ln_q.bias", self.merger_shift
-        yield "merger.ln_q.weight", self.merger_norm
-        yield "merger.mlp.0.weight", self.merger_fc1
-        yield "merger.mlp.0.bias", self.merger_fc1_bias
-        yield "merger.mlp.2.weight", self.merger_fc2
-        yield "merger.mlp.2.bias", self.merger_fc2_bias
+            yield f"merger.{ln}.bias", self.merger_shift
+        yield f"merger.{ln}.weight", self.merger_norm
+        yield f"merger.{m1}.weight", self.merger_fc1
+        yield f"merger.{m1}.bias", self.merger_fc1_bias
+        yield f"merger.{m2}.weight", self.merger_fc2
+        yield f"merger.{m2}.bias", self.merger_fc2_bias
 
 
 # ------------------------------------------------------------------------------------------ full model
@@ -312,16 +390,18 @@ class QwenVLModel(QwenModel):
         return mrope_position_ids(input_ids.tolist(), meta.cu_cpu.tolist(), grids, self.cfg, video_second_per_grid)
 
     def embed_inputs(self, input_ids, pixel_values=None, image_grid_thw=None):
-        """Token embeddings with the image placeholder rows replaced by the tower's output."""
+        """``(x, layer_adds)``: token embeddings with the image placeholder rows replaced by the tower's output,
+        and (Qwen3-VL) ``(rows, [features…])`` to add to those rows after the first decoder layers."""
         x = fused.embedding(input_ids, self.embed)
         if pixel_values is None or pixel_values.numel() == 0:
-            return x
-        feats = self.visual(pixel_values, image_grid_thw).to(x.dtype)
+            return x, None
+        feats, deep = self.visual(pixel_values, image_grid_thw, return_deepstack=True)
         mask = (input_ids == self.cfg.image_token_id) | (input_ids == self.cfg.video_token_id)
         rows = mask.nonzero().squeeze(-1)
         if rows.numel() != feats.shape[0]:
             raise ValueError(f"{rows.numel()} image placeholder tokens but {feats.shape[0]} image features")
-        return x.index_copy(0, rows, feats)
+        adds = (rows, [d.to(x.dtype) for d in deep]) if deep else None
+        return x.index_copy(0, rows, feats.to(x.dtype)), adds
 
     def forward(self, input_ids, position_ids, meta: VarlenMeta, attn_fn=None, stage_input=None,
                 pixel_values=None, image_grid_thw=None, mrope_pos=None):
@@ -334,10 +414,11 @@ class QwenVLModel(QwenModel):
             else:
                 mrope_pos, _ = self.positions(input_ids, meta, image_grid_thw)
         mrope_pos = mrope_pos.to(input_ids.device)
-        cos, sin = mrope_tables(mrope_pos, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.mrope_section)
+        cos, sin = mrope_tables(mrope_pos, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.mrope_section,
+                                self.cfg.mrope_interleaved)
         rows = torch.arange(input_ids.shape[0], dtype=torch.int32, device=input_ids.device)
-        x = self.embed_inputs(input_ids, pixel_values, image_grid_thw)
-        return super().forward(input_ids, rows, meta, attn_fn=attn_fn, embeds=x, rope=(cos, sin))
+        x, adds = self.embed_inputs(input_ids, pixel_values, image_grid_thw)
+        return super().forward(input_ids, rows, meta, attn_fn=attn_fn, embeds=x, rope=(cos, sin), layer_adds=adds)
 
     # ------------------------------------------------------------------ HF layout
     _LM = "model.language_model."

@@ -62,7 +62,8 @@ def test_position_triples():
 
 
 @pytest.mark.parametrize("preset,hf_cls", [("tiny-qwen2_5-vl", "Qwen2_5_VLForConditionalGeneration"),
-                                           ("tiny-qwen2-vl", "Qwen2VLForConditionalGeneration")])
+                                           ("tiny-qwen2-vl", "Qwen2VLForConditionalGeneration"),
+                                           ("tiny-qwen3-vl", "Qwen3VLForConditionalGeneration")])
 def test_matches_transformers(tmp_path, preset, hf_cls):
     transformers = pytest.importorskip("transformers")
     CFG = PRESETS[preset]
@@ -158,27 +159,29 @@ def test_engine_trains_on_images(tmp_path):
         assert not torch.equal(eng.model.visual.patch_embed, w0), "the vision tower must train"
 
 
-def _rollout_engine(device="cpu", **over):
+def _rollout_engine(device="cpu", preset="tiny-qwen2_5-vl", **over):
     from areal_b200.api.cli_args import InferenceEngineConfig, NativeRolloutConfig
     from areal_b200.engine.rollout_engine import NativeRolloutEngine
 
     cfg = InferenceEngineConfig(experiment_name="e", trial_name="t", backend="native:d1", max_concurrent_rollouts=16,
                                 consumer_batch_size=4,
-                                native=NativeRolloutConfig(model_preset="tiny-qwen2_5-vl", context_length=128,
+                                native=NativeRolloutConfig(model_preset=preset, context_length=128,
                                                            max_num_seqs=8, max_num_batched_tokens=512,
                                                            num_kv_blocks=64, seed=3, **over))
     return NativeRolloutEngine(cfg).initialize(**({"device": device} if device == "cpu" else {}))
 
 
-def test_rollout_engine_serves_image_prompts():
+@pytest.mark.parametrize("preset", ["tiny-qwen2_5-vl", "tiny-qwen3-vl"])
+def test_rollout_engine_serves_image_prompts(preset):
     """Greedy generation for a mix of image and text prompts equals re-running the whole model on the growing
-    sequence (image features in the prefill, positions after an image offset by the prompt's delta)."""
+    sequence (image features in the prefill, deep-stack features after the first blocks for Qwen3-VL, positions
+    after an image offset by the prompt's delta)."""
     import asyncio
 
     from areal_b200.api.cli_args import GenerationHyperparameters
     from areal_b200.api.io_struct import ModelRequest
 
-    eng = _rollout_engine()
+    eng = _rollout_engine(preset=preset)
     try:
         assert eng.supports_images
         reqs = []
