@@ -219,6 +219,10 @@ class B200TrainEngine(TrainEngine):
             load_hf_weights(self.model, cfg.path)
         if cfg.gradient_checkpointing:
             self.model.checkpoint_every = 1
+        if self.model_config.is_vl:
+            if cfg.enable_tree_training or (pctx is not None and pctx.extras.get("cp_mode") == "zigzag"):
+                raise NotImplementedError("vision-language models train packed, under data / Ulysses parallelism")
+            self.model.shard_vision = bool(cfg.fsdp.shard_vision_across_sp)
         tp = pctx.tp_size if pctx is not None else 1
         rep_first = None
         if tp > 1:
@@ -432,7 +436,11 @@ class B200TrainEngine(TrainEngine):
         sl = slice(r * n, (r + 1) * n)
         if S > 1:
             pctx.extras["full_positions"] = pos.to(torch.int32)  # for RoPE after the fused sequence→head exchange
-        hidden = self.model(ids[sl], pos[sl], meta, stage_input=stage_input)  # [n, H]: this Ulysses shard
+        if self.model_config.is_vl:
+            # image features and the per-token rotary table are built for the whole micro-batch, then sliced
+            hidden = self.model(ids, pos, meta, seq_slice=sl, **self._vision_inputs(mb))
+        else:
+            hidden = self.model(ids[sl], pos[sl], meta, stage_input=stage_input)  # [n, H]: this Ulysses shard
         if pctx.pp_size > 1 and not pctx.is_last_stage:
             return hidden, None  # (x, res) for the next stage
         if self.is_critic:

@@ -21,7 +21,7 @@ shapes the package's attention kernels take); segments of equal length are batch
 
 Reference behaviour: the vision-language path of areal/engine/fsdp_engine.py (``multi_modal_input`` carrying
 ``pixel_values`` / ``image_grid_thw``, positions from the HF model's ``get_rope_index``) and
-areal/models/transformers/qwen2_vl.py.
+areal/models/transformers/{qwen2_vl,qwen3_vl}.py.
 """
 
 from __future__ import annotations
@@ -363,16 +363,42 @@ class VisionTower(nn.Module):
 # ------------------------------------------------------------------------------------------ full model
 
 
+class _GatherSumGrad(torch.autograd.Function):
+    """All-gather of equally shaped tensors; the backward sums every rank's gradient of the gathered result and
+    hands each rank the part it contributed."""
+
+    @staticmethod
+    def forward(ctx, x, group, rank):
+        import torch.distributed as dist
+
+        ctx.group, ctx.rank = group, rank
+        parts = [torch.empty_like(x) for _ in range(dist.get_world_size(group))]
+        dist.all_gather(parts, x.contiguous(), group=group)
+        return torch.stack(parts, 0)
+
+    @staticmethod
+    def backward(ctx, g):
+        import torch.distributed as dist
+
+        g = g.contiguous()
+        dist.all_reduce(g, group=ctx.group)
+        return g[ctx.rank], None, None
+
+
 class QwenVLModel(QwenModel):
     """The decoder plus ``self.visual``. ``forward`` takes the packed token ids as usual and, optionally,
     ``pixel_values`` / ``image_grid_thw`` of all images of the packed batch in order of appearance."""
 
     def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", pctx=None):
-        if pctx is not None and (pctx.tp_size > 1 or pctx.pp_size > 1 or pctx.seq_shards > 1):
-            raise NotImplementedError("the vision-language model runs data-parallel only")
+        if pctx is not None and (pctx.tp_size > 1 or pctx.pp_size > 1):
+            raise NotImplementedError("the vision-language model runs under data and Ulysses sequence parallelism "
+                                      "only (no tensor or pipeline parallelism)")
         super().__init__(cfg, dtype=dtype, device=device, pctx=pctx)
         assert cfg.vision["out_hidden_size"] == cfg.hidden_size
         self.visual = VisionTower(cfg.vision, dtype, device)
+        # set by the engine (`shard_vision_across_sp`): the images of a micro-batch are divided over the
+        # sequence-parallel ranks instead of every rank running the tower on all of them
+        self.shard_vision = False
 
     @torch.no_grad()
     def init_weights(self, seed: int = 0, std: float = 0.02):
@@ -395,7 +421,11 @@ class QwenVLModel(QwenModel):
         x = fused.embedding(input_ids, self.embed)
         if pixel_values is None or pixel_values.numel() == 0:
             return x, None
-        feats, deep = self.visual(pixel_values, image_grid_thw, return_deepstack=True)
+        p = self.pctx
+        if self.shard_vision and p is not None and p.sp_size > 1:
+            feats, deep = self._sharded_visual(pixel_values, image_grid_thw)
+        else:
+            feats, deep = self.visual(pixel_values, image_grid_thw, return_deepstack=True)
         mask = (input_ids == self.cfg.image_token_id) | (input_ids == self.cfg.video_token_id)
         rows = mask.nonzero().squeeze(-1)
         if rows.numel() != feats.shape[0]:
@@ -403,11 +433,50 @@ class QwenVLModel(QwenModel):
         adds = (rows, [d.to(x.dtype) for d in deep]) if deep else None
         return x.index_copy(0, rows, feats.to(x.dtype)), adds
 
+    def _sharded_visual(self, pixel_values, image_grid_thw):
+        """Tower work divided over the sequence-parallel group: image ``i`` runs on rank ``i mod S``, the
+        features (and deep-stack features) are all-gathered; in the backward every rank's gradient of the
+        gathered features is summed onto the owner. Reference: areal/models/transformers/vision_sp_shard.py."""
+        p = self.pctx
+        S, r = p.sp_size, p.sp_rank
+        grids = [[int(v) for v in g] for g in (image_grid_thw.tolist() if torch.is_tensor(image_grid_thw)
+                                               else image_grid_thw)]
+        unit = self.visual.unit
+        n_patch = [t * h * w for t, h, w in grids]
+        starts = [0]
+        for n in n_patch:
+            starts.append(starts[-1] + n)
+        mine = [i for i in range(len(grids)) if i % S == r]
+        n_deep = len(self.visual.deepstack_at)
+        H = self.cfg.hidden_size
+        dev, dt = self.embed.device, self.embed.dtype
+        if mine:
+            pix = torch.cat([pixel_values[starts[i]:starts[i + 1]] for i in mine], 0)
+            f, deep = self.visual(pix, [grids[i] for i in mine], return_deepstack=True)
+            local = torch.cat([f] + list(deep), -1)
+        else:
+            # a rank without images still takes part in the gather and (so that its backward runs) in the
+            # gradient sum
+            local = torch.zeros(0, (1 + n_deep) * H, dtype=dt, device=dev, requires_grad=torch.is_grad_enabled())
+        per_rank = [sum(n_patch[i] // unit for i in range(len(grids)) if i % S == k) for k in range(S)]
+        width = max(per_rank)
+        local = F.pad(local, (0, 0, 0, width - local.shape[0]))
+        allf = _GatherSumGrad.apply(local, p.sp_group, r)  # [S, width, C]
+        rows, offs = [], [0] * S
+        for i, n in enumerate(n_patch):
+            k, m = i % S, n // unit
+            rows.append(allf[k, offs[k]:offs[k] + m])
+            offs[k] += m
+        full = torch.cat(rows, 0)
+        return full[:, :H], [full[:, (j + 1) * H:(j + 2) * H] for j in range(n_deep)]
+
     def forward(self, input_ids, position_ids, meta: VarlenMeta, attn_fn=None, stage_input=None,
-                pixel_values=None, image_grid_thw=None, mrope_pos=None):
+                pixel_values=None, image_grid_thw=None, mrope_pos=None, seq_slice: slice | None = None):
         """``mrope_pos [3, T]`` overrides the position triples derived from the token ids (a caller that
         already holds them, e.g. from a processor). ``position_ids`` is ignored when there are images: the
-        rotary table is built per token."""
+        rotary table is built per token. Under Ulysses sequence parallelism the caller passes ALL tokens of the
+        (padded) micro-batch and ``seq_slice``, this rank's rows: embeddings, image features and the rotary
+        table are built for the whole batch, the decoder runs on the slice."""
         if mrope_pos is None:
             if pixel_values is None or pixel_values.numel() == 0:
                 mrope_pos = position_ids.to(torch.long)[None, :].expand(3, -1)
@@ -418,6 +487,14 @@ class QwenVLModel(QwenModel):
                                 self.cfg.mrope_interleaved)
         rows = torch.arange(input_ids.shape[0], dtype=torch.int32, device=input_ids.device)
         x, adds = self.embed_inputs(input_ids, pixel_values, image_grid_thw)
+        if seq_slice is not None:
+            # the rotary table stays whole: local rows index it before the sequence→head exchange, all rows after
+            self.pctx.extras["full_positions"] = rows
+            lo, hi = seq_slice.start, seq_slice.stop
+            if adds is not None:
+                keep = ((adds[0] >= lo) & (adds[0] < hi)).nonzero().squeeze(-1)
+                adds = (adds[0].index_select(0, keep) - lo, [f.index_select(0, keep) for f in adds[1]])
+            input_ids, rows, x = input_ids[seq_slice], rows[seq_slice], x[seq_slice]
         return super().forward(input_ids, rows, meta, attn_fn=attn_fn, embeds=x, rope=(cos, sin), layer_adds=adds)
 
     # ------------------------------------------------------------------ HF layout

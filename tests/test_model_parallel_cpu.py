@@ -11,9 +11,10 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "torchrun", "run_model_parallel.py")
 
 
-def _ref(tmp_path, critic=False, n_mbs=1, preset="tiny-qwen2"):
+def _ref(tmp_path, critic=False, n_mbs=1, preset="tiny-qwen2", images=False, extra=()):
     f = str(tmp_path / ("ref_c.pt" if critic else "ref.pt"))
     cmd = [sys.executable, WORKER, "--ref", "--n-mbs", str(n_mbs), "--preset", preset, f] + (["--critic"] if critic else [])
+    cmd += (["--images"] if images else []) + list(extra)
     env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=300)
     assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
@@ -54,3 +55,16 @@ def test_expert_parallel_step_matches_single_process(tmp_path, n, ep):
     """MoE model with the experts split over the ep group (tokens gathered / partial outputs summed
     on gloo; expert weights in their own flat buffer, clipped by the joint gradient norm)."""
     _run(n, 29670 + n, ["--ep", str(ep), "--preset", "tiny-qwen3-moe"], _ref(tmp_path, preset="tiny-qwen3-moe"))
+
+
+@pytest.mark.parametrize("n,preset,extra", [(2, "tiny-qwen2_5-vl", []), (2, "tiny-qwen3-vl", ["--shard-vision"]),
+                                            (4, "tiny-qwen3-vl", ["--n-mbs", "2"]),
+                                            (2, "tiny-qwen2_5-vl", ["--shard-vision", "--one-image"])])
+def test_vision_language_step_under_ulysses(tmp_path, n, preset, extra):
+    """Image prompts under Ulysses sequence parallelism (image features and the per-token rotary table built for
+    the whole micro-batch, the decoder on this rank's rows; optionally the tower's images divided over the ranks):
+    same loss and gradients, vision tower included, as one process."""
+    n_mbs = 2 if "--n-mbs" in extra else 1
+    _run(n, 29680 + n + len(extra), ["--sp", "2", "--preset", preset, "--images"] + extra,
+         _ref(tmp_path, preset=preset, images=True, n_mbs=n_mbs,
+              extra=["--one-image"] if "--one-image" in extra else []))

@@ -19,13 +19,29 @@ from areal_b200.engine.train_engine import B200TrainEngine  # noqa: E402
 from areal_b200.parallel.tensor_parallel import is_tp_replicated, tp_unslice  # noqa: E402
 
 
-def global_batch(n_seq=8, L=48, vocab=1024):
+def global_batch(n_seq=8, L=48, vocab=1024, images=False, one_image=False):
     g = torch.Generator().manual_seed(7)
     lens = torch.randint(L // 3, L + 1, (n_seq,), generator=g)
-    ids = torch.randint(0, vocab, (n_seq, L), generator=g)
+    ids = torch.randint(0, 900 if images else vocab, (n_seq, L), generator=g)
     mask = torch.arange(L)[None, :] < lens[:, None]
     loss_mask = mask & (torch.arange(L)[None, :] >= 4)
-    return dict(input_ids=ids * mask, attention_mask=mask, loss_mask=loss_mask.int())
+    out = dict(input_ids=ids * mask, attention_mask=mask, loss_mask=loss_mask.int())
+    if images:
+        # every sequence but the third starts with one image: <start> pads <end>; placeholder ids of the tiny presets
+        mm = []
+        for i in range(n_seq):
+            if i % 3 == 2 or (one_image and i > 0):
+                mm.append({})
+                continue
+            h, w = [(4, 4), (4, 6)][i % 2]
+            n = h * w // 4
+            out["input_ids"][i, 0] = 1002
+            out["input_ids"][i, 1:1 + n] = 1000
+            out["input_ids"][i, 1 + n] = 1003
+            mm.append(dict(pixel_values=torch.randn(h * w, 3 * 2 * 14 * 14, generator=g),
+                           image_grid_thw=torch.tensor([[1, h, w]])))
+        out["multi_modal_input"] = mm
+    return out
 
 
 def loss_fn(logp, ent, mb):
@@ -50,6 +66,9 @@ def main():
     ap.add_argument("--no-bias", action="store_true", help="Qwen3-style attention (no qkv bias): enables the fused Ulysses projection")
     ap.add_argument("--n-mbs", type=int, default=1)
     ap.add_argument("--critic", action="store_true")
+    ap.add_argument("--images", action="store_true", help="image prompts (vision-language presets)")
+    ap.add_argument("--one-image", action="store_true", help="only the first sequence carries an image")
+    ap.add_argument("--shard-vision", action="store_true", help="divide the vision tower's images over the sp ranks")
     ap.add_argument("--zigzag", action="store_true", help="context parallelism with zig-zag chunks and gathered K/V "
                                                           "(the Megatron-style engine's mode) instead of Ulysses")
     args = ap.parse_args()
@@ -71,8 +90,9 @@ def main():
                                                       warmup_steps_proportion=0.0, lr_scheduler_type="constant"))
     if args.zigzag:
         cfg.backend = "megatron:d1"
+    cfg.fsdp.shard_vision_across_sp = args.shard_vision
     eng = B200TrainEngine(cfg)
-    batch = global_batch(L=512 if cuda else 48)
+    batch = global_batch(L=512 if cuda else 48, images=args.images, one_image=args.one_image)
     if args.ref:
         eng.create_process_group()
         eng.initialize(seed=3)
@@ -86,7 +106,7 @@ def main():
                                                   expert_parallel_size=args.ep))
         eng.initialize(seed=3)
         d = eng.data_parallel_rank
-        data = {k: v[d::dp] for k, v in batch.items()}
+        data = {k: v[d::dp] for k, v in batch.items()}  # tensors and the per-sequence image list alike
     captured = {}
     orig_step = eng.optimizer.step
 
