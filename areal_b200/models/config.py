@@ -185,7 +185,7 @@ class ModelConfig:
                     setattr(out, key, cfg[key])
         if mt in _VL_TYPES:
             vc = dict(top.get("vision_config") or {})
-            if mt == "qwen3_vl":
+            if mt.startswith("qwen3_vl"):
                 vc["variant"] = "qwen3_vl"
                 out.mrope_interleaved = bool(rope_params.get("mrope_interleaved", True))
             if mt == "qwen2_vl":
@@ -261,10 +261,15 @@ class ModelConfig:
             "rope_parameters": {"rope_type": "default", "rope_theta": self.rope_theta,
                                 "mrope_section": list(self.mrope_section)},
         }
-        if self.model_type == "qwen3_vl":
+        if self.model_type.startswith("qwen3_vl"):
             text.update(head_dim=self.head_dim, attention_bias=self.attention_bias)
             text["rope_parameters"]["mrope_interleaved"] = self.mrope_interleaved
-        arch = {"qwen2_vl": "Qwen2VLForConditionalGeneration", "qwen3_vl": "Qwen3VLForConditionalGeneration"}.get(
+        if self.is_moe:
+            text.update(num_experts=self.num_experts, num_experts_per_tok=self.num_experts_per_tok,
+                        moe_intermediate_size=self.moe_intermediate_size, norm_topk_prob=self.norm_topk_prob,
+                        decoder_sparse_step=self.decoder_sparse_step, mlp_only_layers=self.mlp_only_layers)
+        arch = {"qwen2_vl": "Qwen2VLForConditionalGeneration", "qwen3_vl": "Qwen3VLForConditionalGeneration",
+                "qwen3_vl_moe": "Qwen3VLMoeForConditionalGeneration"}.get(
             self.model_type, "Qwen2_5_VLForConditionalGeneration")
         return {"architectures": [arch], "model_type": self.model_type,
                 "text_config": text, "vision_config": vision,
@@ -281,7 +286,7 @@ _VISION_KEYS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_ch
                 "spatial_merge_size", "temporal_patch_size", "tokens_per_second", "window_size", "out_hidden_size",
                 "fullatt_block_indexes", "hidden_act", "variant", "num_position_embeddings",
                 "deepstack_visual_indexes")
-_VL_TYPES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl")
+_VL_TYPES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe")
 
 # Named shapes used by the benchmark configurations (random-init, synthetic data).
 PRESETS: dict[str, ModelConfig] = {
@@ -316,6 +321,17 @@ PRESETS: dict[str, ModelConfig] = {
                                              temporal_patch_size=2, out_hidden_size=256, variant="qwen3_vl",
                                              num_position_embeddings=64, deepstack_visual_indexes=[0, 1],
                                              hidden_act="gelu_pytorch_tanh")),
+    "tiny-qwen3-vl-moe": ModelConfig(model_type="qwen3_vl_moe", vocab_size=1024, hidden_size=256, intermediate_size=512,
+                                     num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+                                     rope_theta=1e4, tie_word_embeddings=False, attention_bias=False, qk_norm=True,
+                                     num_experts=4, num_experts_per_tok=2, moe_intermediate_size=64,
+                                     mrope_section=[12, 10, 10], mrope_interleaved=True, image_token_id=1000,
+                                     video_token_id=1001, vision_start_token_id=1002, vision_end_token_id=1003,
+                                     vision=dict(depth=2, hidden_size=64, intermediate_size=128, num_heads=2,
+                                                 in_channels=3, patch_size=14, spatial_merge_size=2,
+                                                 temporal_patch_size=2, out_hidden_size=256, variant="qwen3_vl",
+                                                 num_position_embeddings=64, deepstack_visual_indexes=[0],
+                                                 hidden_act="gelu_pytorch_tanh")),
     "tiny-qwen3_5": ModelConfig(model_type="qwen3_5", vocab_size=1024, hidden_size=256, intermediate_size=512,
                                 num_hidden_layers=4, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                                 rope_theta=1e4, tie_word_embeddings=False, partial_rotary_factor=0.25,

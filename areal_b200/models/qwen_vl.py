@@ -1,4 +1,4 @@
-"""Qwen2.5-VL, Qwen2-VL and Qwen3-VL: a vision transformer in front of the Qwen2 decoder with multimodal rotary positions.
+"""Qwen2.5-VL, Qwen2-VL, Qwen3-VL and Qwen3-VL-MoE: a vision transformer in front of the Qwen2 decoder with multimodal rotary positions.
 
 The decoder is the package's ``QwenModel`` unchanged (fused projections, own kernels); this module adds
 
@@ -390,9 +390,9 @@ class QwenVLModel(QwenModel):
     ``pixel_values`` / ``image_grid_thw`` of all images of the packed batch in order of appearance."""
 
     def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", pctx=None):
-        if pctx is not None and (pctx.tp_size > 1 or pctx.pp_size > 1):
+        if pctx is not None and (pctx.tp_size > 1 or pctx.pp_size > 1 or getattr(pctx, "ep_size", 1) > 1):
             raise NotImplementedError("the vision-language model runs under data and Ulysses sequence parallelism "
-                                      "only (no tensor or pipeline parallelism)")
+                                      "only (no tensor, pipeline or expert parallelism)")
         super().__init__(cfg, dtype=dtype, device=device, pctx=pctx)
         assert cfg.vision["out_hidden_size"] == cfg.hidden_size
         self.visual = VisionTower(cfg.vision, dtype, device)
@@ -503,7 +503,17 @@ class QwenVLModel(QwenModel):
 
     def to_hf_local(self, export: bool = False) -> Iterator[tuple[str, torch.Tensor]]:
         for name, t in super().to_hf_local(export):
+            if ".mlp.experts." in name:
+                continue  # written fused below
             yield (self._LM + name[len("model."):] if name.startswith("model.") else name), t
+        if self.cfg.is_moe:
+            # Qwen3-VL-MoE checkpoints hold all experts of a layer in two tensors, input dimension first:
+            # gate_up_proj [E, H, 2I], down_proj [E, I, H] (transposed views of the fused parameters)
+            for i, layer in enumerate(self.layers, start=self.layer_start):
+                if hasattr(layer.mlp, "router"):
+                    p = f"{self._LM}layers.{i}.mlp.experts."
+                    yield p + "gate_up_proj", layer.mlp.gate_up.transpose(1, 2)
+                    yield p + "down_proj", layer.mlp.down.transpose(1, 2)
         for name, t in self.visual.hf_tensors():
             yield self._VIS + name, t
 
@@ -533,6 +543,9 @@ class QwenVLModel(QwenModel):
                     raise KeyError(f"unexpected tensor {name}")
                 continue
             d = dst[name]
+            if d.shape != t.shape and name.endswith(("experts.gate_up_proj", "experts.down_proj")) \
+                    and t.dim() == 3 and d.shape == t.transpose(1, 2).shape:
+                t = t.transpose(1, 2)  # written output dimension first (what transformers holds in memory)
             if d.shape != t.shape:
                 raise ValueError(f"{name}: shape {tuple(t.shape)} != {tuple(d.shape)}")
             d.copy_(t.to(device=d.device, dtype=d.dtype))

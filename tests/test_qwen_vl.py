@@ -63,7 +63,8 @@ def test_position_triples():
 
 @pytest.mark.parametrize("preset,hf_cls", [("tiny-qwen2_5-vl", "Qwen2_5_VLForConditionalGeneration"),
                                            ("tiny-qwen2-vl", "Qwen2VLForConditionalGeneration"),
-                                           ("tiny-qwen3-vl", "Qwen3VLForConditionalGeneration")])
+                                           ("tiny-qwen3-vl", "Qwen3VLForConditionalGeneration"),
+                                           ("tiny-qwen3-vl-moe", "Qwen3VLMoeForConditionalGeneration")])
 def test_matches_transformers(tmp_path, preset, hf_cls):
     transformers = pytest.importorskip("transformers")
     CFG = PRESETS[preset]
