@@ -13,6 +13,7 @@ object (or, out of process, the proxy's ``base_url``)
 
 from __future__ import annotations
 
+import re
 import time
 import uuid
 from types import SimpleNamespace
@@ -78,11 +79,43 @@ class _Responses:
                               "output_tokens": comp["usage"]["completion_tokens"]}})
 
 
+_DATA_URI = re.compile(r"^data:image/[a-zA-Z0-9.+-]+;base64,(.+)$", re.DOTALL)
+
+
+def extract_images(messages: list[dict[str, Any]]) -> tuple[list[str], list[dict[str, Any]]]:
+    """``image_url`` content parts of chat messages → ``(image_data, messages_for_template)``: the base64
+    payloads (data URIs stripped to their payload, other URLs kept as they are) in order of appearance, and the
+    messages with every such part replaced by ``{"type": "image"}``, which is what a vision-language chat
+    template turns into its image placeholder. Reference: areal/experimental/openai/client.py:151-237."""
+    images, out = [], []
+    for m in messages:
+        c = m.get("content")
+        if not isinstance(c, list):
+            out.append(m)
+            continue
+        parts = []
+        for part in c:
+            if isinstance(part, dict) and part.get("type") == "image_url":
+                url = part.get("image_url")
+                url = url.get("url") if isinstance(url, dict) else url
+                hit = _DATA_URI.match(url or "")
+                images.append(hit.group(1) if hit else url)
+                parts.append({"type": "image"})
+            else:
+                parts.append(part)
+        out.append(dict(m, content=parts))
+    return images, out
+
+
 class ArealOpenAI:
     def __init__(self, engine, tokenizer, gconfig: GenerationHyperparameters | None = None,
                  tool_call_parser: str = "qwen", reasoning_parser: str | None = None,
-                 chat_template_type: str = "hf", engine_max_tokens: int | None = None):
+                 chat_template_type: str = "hf", engine_max_tokens: int | None = None, processor=None):
+        """``processor``: the HF processor of a vision-language model. With it, image prompts are expanded to
+        their placeholder tokens and pixel tensors here (what the in-process rollout engine and the train engine
+        need); without it the encoded images travel as ``image_data`` and the serving side expands them."""
         self.engine, self.tokenizer = engine, tokenizer
+        self.processor = processor
         self.gconfig = gconfig or GenerationHyperparameters()
         self.reasoning_parser = reasoning_parser
         self.chat_template_type = chat_template_type
@@ -95,6 +128,26 @@ class ArealOpenAI:
         kw = {"tools": tools} if tools else {}
         ids = self.tokenizer.apply_chat_template(messages, tokenize=True, add_generation_prompt=True, **kw)
         return list(ids)
+
+    def _process_images(self, messages, image_data, tools):
+        """Chat template as text, then the processor on text + decoded images: token ids with the image
+        placeholders expanded to one token per merged patch, and the pixel tensors."""
+        import base64
+        import io
+
+        from PIL import Image
+
+        kw = {"tools": tools} if tools else {}
+        text = self.processor.apply_chat_template(messages, tokenize=False, add_generation_prompt=True, **kw)
+        images = []
+        for b in image_data:
+            try:
+                images.append(Image.open(io.BytesIO(base64.b64decode(b, validate=True))))
+            except Exception as e:
+                raise ValueError("image_url must carry a base64 data URI (remote URLs are not fetched)") from e
+        proc = self.processor(text=[text], images=images, padding=False, return_tensors="pt")
+        mm = {k: v for k, v in proc.items() if k not in ("input_ids", "attention_mask")}
+        return proc["input_ids"][0].tolist(), mm
 
     async def _complete(self, messages, model, tools, max_new, temperature, top_p, stop, as_dict):
         g = self.gconfig.new(n_samples=1)
@@ -110,11 +163,18 @@ class ArealOpenAI:
         eos = getattr(self.tokenizer, "eos_token_id", None)
         if eos is not None and eos not in g.stop_token_ids:
             g.stop_token_ids = list(g.stop_token_ids) + [eos]
-        ids = self._tokenize(messages, tools)
+        image_data, tmpl_messages = extract_images(messages)
+        mm: dict[str, Any] = {}
+        if image_data and self.processor is not None:
+            ids, mm = self._process_images(tmpl_messages, image_data, tools)
+        else:
+            ids = self._tokenize(tmpl_messages if image_data else messages, tools)
         if self.engine_max_tokens is not None:
             g.max_new_tokens = max(min(g.max_new_tokens, self.engine_max_tokens - len(ids)), 1)
-        resp = await self.engine.agenerate(ModelRequest(rid=uuid.uuid4().hex, input_ids=ids, gconfig=g,
-                                                        tokenizer=self.tokenizer))
+        resp = await self.engine.agenerate(ModelRequest(
+            rid=uuid.uuid4().hex, input_ids=ids, gconfig=g, tokenizer=self.tokenizer,
+            image_data=image_data or None, processor=self.processor,
+            metadata={"multi_modal_input": [mm]} if mm else {}))
         out = resp.output_tokens
         if eos is not None and out and out[-1] == eos:
             text = self.tokenizer.decode(out[:-1])
@@ -130,7 +190,7 @@ class ArealOpenAI:
         self.cache.add(InteractionWithTokenLogpReward(
             interaction_id=cid, messages=list(messages), completion=comp, model_response=resp,
             output_message=comp["choices"][0]["message"], chat_template_type=self.chat_template_type,
-            created_at=time.time()))
+            created_at=time.time(), multi_modal_input=mm))
         return comp if as_dict else _ns(comp)
 
     # ------------------------------------------------------------- rewards / export

@@ -23,6 +23,8 @@ class InteractionWithTokenLogpReward:
     output_message: dict[str, Any] | None = None
     chat_template_type: str = "hf"
     created_at: float = 0.0
+    # image prompts: the processor's pixel tensors of this interaction's prompt ({} for text)
+    multi_modal_input: dict[str, Any] = field(default_factory=dict)
 
     @property
     def input_len(self) -> int:
@@ -45,7 +47,7 @@ class InteractionWithTokenLogpReward:
         loss_mask = [0] * n_in + [1] * n_out
         logprobs = [0.0] * n_in + list(r.output_logprobs)
         versions = [-1] * n_in + list(r.output_versions)
-        return dict(
+        out = dict(
             input_ids=torch.tensor(seq, dtype=torch.int32).unsqueeze(0),
             attention_mask=torch.ones(1, len(seq), dtype=torch.bool),
             loss_mask=torch.tensor(loss_mask, dtype=torch.int32).unsqueeze(0),
@@ -53,3 +55,6 @@ class InteractionWithTokenLogpReward:
             versions=torch.tensor(versions, dtype=torch.int32).unsqueeze(0),
             rewards=torch.tensor([float(self.reward or 0.0)], dtype=torch.float32),
         )
+        if self.multi_modal_input:
+            out["multi_modal_input"] = [self.multi_modal_input]
+        return out

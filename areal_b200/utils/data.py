@@ -72,10 +72,13 @@ def concat_padded_tensors(dicts: Sequence[dict[str, Any]], pad_value: float = 0.
         return {}
     max_len = max(d["attention_mask"].shape[1] for d in dicts)
     out: dict[str, Any] = {}
-    for k in dicts[0]:
+    # text-only trajectories carry no image entry: give them one empty dict per row when others have images
+    mm_keys = {k for d in dicts for k in d if k.startswith("multi_modal_input")}
+    keys = list(dicts[0]) + [k for k in sorted(mm_keys) if k not in dicts[0]]
+    for k in keys:
         parts = []
         for d in dicts:
-            v = d[k]
+            v = d[k] if k in d else [{} for _ in range(d["attention_mask"].shape[0])]
             if torch.is_tensor(v) and v.dim() >= 2 and v.shape[1] == d["attention_mask"].shape[1]:
                 pad = max_len - v.shape[1]
                 if pad:

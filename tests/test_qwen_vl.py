@@ -437,3 +437,60 @@ def test_image_prompt_over_http():
         server.should_exit = True
         th.join(timeout=10)
         eng.destroy()
+
+
+def test_openai_client_with_image_messages():
+    """``image_url`` parts of chat messages: the client swaps them for the template's image marker, lets the
+    processor expand the placeholders, hands the pixel tensors to the engine and keeps them in the exported
+    interaction; batches mix image and text interactions."""
+    import asyncio
+    import base64
+
+    from areal_b200.api.cli_args import GenerationHyperparameters
+    from areal_b200.openai.client import ArealOpenAI, extract_images
+    from areal_b200.utils.data import concat_padded_tensors
+
+    png = _png(28, 28)
+    uri = "data:image/png;base64," + base64.b64encode(png).decode()
+    msgs = [{"role": "user", "content": [{"type": "image_url", "image_url": {"url": uri}},
+                                         {"type": "text", "text": "5 6 7"}]}]
+    data, tmpl = extract_images(msgs)
+    assert data == [base64.b64encode(png).decode()] and tmpl[0]["content"][0] == {"type": "image"}
+    assert msgs[0]["content"][0]["type"] == "image_url"  # the caller's messages are not modified
+
+    class Tok(_ToyTok):
+        def apply_chat_template(self, messages, tokenize=True, add_generation_prompt=True, **kw):
+            return [int(w) for m in messages for w in str(m["content"]).split()]
+
+    class Proc(_ToyVLProcessor):
+        def apply_chat_template(self, messages, tokenize=False, add_generation_prompt=True, **kw):
+            words = []
+            for m in messages:
+                for part in m["content"] if isinstance(m["content"], list) else [{"type": "text", "text": m["content"]}]:
+                    words.append("<img>" if part["type"] == "image" else part["text"])
+            return " ".join(words)
+
+        def __call__(self, text=None, images=None, **kw):
+            assert all(im.size == (28, 28) for im in images)  # decoded PIL images arrive here
+            return super().__call__(images=[b"4x4"] * len(images), text=text[0])
+
+    eng = _rollout_engine()
+    try:
+        client = ArealOpenAI(eng, Tok(), GenerationHyperparameters(max_new_tokens=4, greedy=True), processor=Proc())
+
+        async def go():
+            a = await client.chat.completions.create(messages=msgs)
+            b = await client.chat.completions.create(messages=[{"role": "user", "content": "8 9"}])
+            return a, b
+
+        a, b = asyncio.run(go())
+        client.set_reward(a.id, 1.0)
+        client.set_reward(b.id, 0.0)
+        inter = client.export_interactions()
+        ta, tb = inter[a.id].to_tensor_dict(), inter[b.id].to_tensor_dict()
+        assert ta["multi_modal_input"][0]["pixel_values"].shape == (16, 1176) and "multi_modal_input" not in tb
+        assert int((ta["input_ids"] == IMG).sum()) == 4
+        for batch in (concat_padded_tensors([ta, tb]), concat_padded_tensors([tb, ta])):
+            assert len(batch["multi_modal_input"]) == 2 and sum(bool(d) for d in batch["multi_modal_input"]) == 1
+    finally:
+        eng.destroy()
