@@ -37,7 +37,9 @@ class Session:
 def create_proxy_app(engine, tokenizer, admin_api_key: str = "areal-admin-key",
                      gconfig: GenerationHyperparameters | None = None, tool_call_parser: str = "qwen",
                      reasoning_parser: str | None = None, session_timeout_seconds: int = 3600,
-                     engine_max_tokens: int | None = None) -> FastAPI:
+                     engine_max_tokens: int | None = None, processor=None) -> FastAPI:
+    """``processor``: the HF processor of a vision-language model; with it ``image_url`` message parts are
+    expanded on this side (see ``ArealOpenAI``)."""
     app = FastAPI()
     sessions: dict[str, Session] = {}
     by_key: dict[str, Session] = {}
@@ -83,7 +85,7 @@ def create_proxy_app(engine, tokenizer, admin_api_key: str = "areal-admin-key",
         sid = uuid.uuid4().hex
         key = "sk-sess-" + secrets.token_hex(16)
         client = ArealOpenAI(engine, tokenizer, gconfig, tool_call_parser, reasoning_parser,
-                             engine_max_tokens=engine_max_tokens)
+                             engine_max_tokens=engine_max_tokens, processor=processor)
         s = Session(sid, key, client, body.get("task_id"))
         sessions[sid] = s
         by_key[key] = s

@@ -28,7 +28,9 @@ class OpenAIProxyWorkflow(RolloutWorkflow):
     def __init__(self, agent: Any, tokenizer=None, gconfig: GenerationHyperparameters | None = None,
                  mode: str = "inline", turn_discount: float = 1.0, export_style: str = "individual",
                  proxy_url: str | None = None, admin_api_key: str = "areal-admin-key",
-                 tool_call_parser: str = "qwen", reasoning_parser: str | None = None, max_workers: int = 4):
+                 tool_call_parser: str = "qwen", reasoning_parser: str | None = None, max_workers: int = 4,
+                 processor=None):
+        self.processor = processor  # vision-language models: expands image_url message parts
         if mode not in ("inline", "subproc", "online"):
             raise ValueError(f"mode must be inline|subproc|online, got {mode}")
         self.agent, self.tokenizer, self.gconfig, self.mode = agent, tokenizer, gconfig, mode
@@ -40,7 +42,8 @@ class OpenAIProxyWorkflow(RolloutWorkflow):
     async def arun_episode(self, engine, data: dict[str, Any]):
         if self.mode == "online":
             return await self._run_online(data)
-        client = ArealOpenAI(engine, self.tokenizer, self.gconfig, self.tool_call_parser, self.reasoning_parser)
+        client = ArealOpenAI(engine, self.tokenizer, self.gconfig, self.tool_call_parser, self.reasoning_parser,
+                             processor=self.processor)
         if self.mode == "inline":
             reward = await self.agent.run(data, client=client)
         else:
