@@ -32,13 +32,33 @@ def image_to_base64(img) -> str:
     return base64.b64encode(buf.getvalue()).decode()
 
 
+def load_image(obj, decode_bytes: bool = True):
+    """What a dataset row holds for an image → PIL image: a ``{"bytes": ..., "path": ...}`` record (parquet /
+    ``datasets`` image feature), encoded bytes, or a file path; PIL images pass through. With
+    ``decode_bytes=False`` raw bytes are left alone (a processor that takes them as they are)."""
+    if isinstance(obj, dict):
+        obj = obj.get("bytes") or obj.get("path")
+    if isinstance(obj, (bytes, bytearray)) and decode_bytes:
+        from PIL import Image
+
+        try:
+            return Image.open(io.BytesIO(bytes(obj))).convert("RGB")
+        except Exception:
+            return obj  # not an encoded image: hand it to the processor unchanged
+    if isinstance(obj, str):
+        from PIL import Image
+
+        return Image.open(obj).convert("RGB")
+    return obj
+
+
 class VisionRLVRWorkflow(RLVRWorkflow):
     def __init__(self, reward_fn, gconfig, tokenizer, processor, enable_thinking: bool = False, **kw):
         super().__init__(reward_fn, gconfig, tokenizer=tokenizer, enable_thinking=enable_thinking, **kw)
         self.processor = processor
 
     async def arun_episode(self, engine, data: dict[str, Any]):
-        images = data.get("images") or []
+        images = [load_image(im) for im in (data.get("images") or [])]
         text = self.processor.apply_chat_template(data["messages"], tokenize=False, add_generation_prompt=True) \
             if "messages" in data else data["prompt"]
         proc = self.processor(images=images or None, text=text, padding=False, return_tensors="pt")

@@ -494,3 +494,15 @@ def test_openai_client_with_image_messages():
             assert len(batch["multi_modal_input"]) == 2 and sum(bool(d) for d in batch["multi_modal_input"]) == 1
     finally:
         eng.destroy()
+
+
+def test_load_image_forms(tmp_path):
+    from areal_b200.workflow.vision_rlvr import image_to_base64, load_image
+
+    png = _png(20, 30)
+    (tmp_path / "a.png").write_bytes(png)
+    for obj in (png, {"bytes": png, "path": None}, {"bytes": None, "path": str(tmp_path / "a.png")}, str(tmp_path / "a.png")):
+        im = load_image(obj)
+        assert im.size == (30, 20) and im.mode == "RGB"
+    assert load_image(im) is im and load_image(b"not an image") == b"not an image"
+    assert load_image(image_to_base64(im).encode(), decode_bytes=False) == image_to_base64(im).encode()
