@@ -1,10 +1,12 @@
 """JSON-safe envelopes for values that cross the RPC boundary: tensors, numpy arrays,
-dataclasses, enums, bytes, tuples/sets, and nested containers
+dataclasses, enums, bytes, tuples/sets, PIL images (as PNG), tokenizers / processors (by the path they
+were loaded from), mapping types such as a processor's ``BatchFeature``, and nested containers
 (role of areal/infra/rpc/serialization.py in the reference)."""
 
 from __future__ import annotations
 
 import base64
+import collections.abc
 import dataclasses
 import enum
 import importlib
@@ -60,6 +62,19 @@ def serialize_value(v: Any) -> Any:
         return [serialize_value(x) for x in v]
     if hasattr(v, "__rtensor__"):
         return v.__rtensor__()
+    if type(v).__module__.startswith("PIL.") and hasattr(v, "save"):
+        buf = io.BytesIO()
+        v.save(buf, format="PNG")
+        return {_T: "pil", "data": base64.b64encode(buf.getvalue()).decode("ascii")}
+    if hasattr(v, "name_or_path") and (hasattr(v, "apply_chat_template") or hasattr(v, "encode")):
+        # tokenizers and processors are re-loaded on the other side from where they came from
+        kind = "processor" if hasattr(v, "image_processor") else "tokenizer"
+        path = v.name_or_path or getattr(getattr(v, "tokenizer", None), "name_or_path", "")
+        if not path:
+            raise TypeError(f"cannot serialize a {kind} without name_or_path")
+        return {_T: kind, "path": path}
+    if isinstance(v, collections.abc.Mapping):
+        return serialize_value(dict(v))
     raise TypeError(f"cannot serialize value of type {type(v).__name__}")
 
 
@@ -101,6 +116,20 @@ def deserialize_value(v: Any) -> Any:
         return tuple(deserialize_value(x) for x in v["items"])
     if t == "set":
         return set(deserialize_value(x) for x in v["items"])
+    if t == "pil":
+        from PIL import Image
+
+        img = Image.open(io.BytesIO(base64.b64decode(v["data"])))
+        img.load()
+        return img
+    if t == "tokenizer":
+        from transformers import AutoTokenizer
+
+        return AutoTokenizer.from_pretrained(v["path"])
+    if t == "processor":
+        from transformers import AutoProcessor
+
+        return AutoProcessor.from_pretrained(v["path"])
     if t == "rtensor":
         from .rtensor import RTensor
 

@@ -99,3 +99,34 @@ def test_dead_worker_is_detected(sched):
     sched._by_id["w/0"].process.wait()
     with pytest.raises(WorkerFailedError):
         sched.call_engine("w/0", "train_batch", None, {"x": torch.ones(1)})
+
+
+def test_serialization_of_images_processor_outputs_and_tokenizers(monkeypatch):
+    """What a vision-language trajectory carries across RPC: PIL images, a processor's mapping-type output, and
+    tokenizers / processors by the path they were loaded from."""
+    import collections
+
+    from PIL import Image
+
+    img = Image.fromarray((np.arange(12 * 10 * 3) % 255).astype("uint8").reshape(12, 10, 3))
+    feat = collections.UserDict(pixel_values=torch.ones(4, 6), image_grid_thw=torch.tensor([[1, 2, 2]]))
+    out = deserialize_value(serialize_value({"img": img, "mm": [feat]}))
+    assert out["img"].size == (10, 12) and np.array_equal(np.asarray(out["img"]), np.asarray(img))
+    assert isinstance(out["mm"][0], dict) and torch.equal(out["mm"][0]["pixel_values"], feat["pixel_values"])
+
+    class Tok:
+        name_or_path = "/models/some-model"
+
+        def encode(self, text):
+            return []
+
+    env = serialize_value({"tok": Tok()})
+    assert env["tok"] == {"__type__": "tokenizer", "path": "/models/some-model"}
+    import transformers
+
+    loaded = []
+    monkeypatch.setattr(transformers.AutoTokenizer, "from_pretrained", classmethod(lambda cls, p: loaded.append(p) or "tok"))
+    assert deserialize_value(env)["tok"] == "tok" and loaded == ["/models/some-model"]
+    Tok.name_or_path = ""
+    with pytest.raises(TypeError):
+        serialize_value(Tok())
