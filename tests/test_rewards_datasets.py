@@ -59,3 +59,34 @@ def test_dataset_builders(tmp_path):
     assert pairs[0]["chosen_ids"][:5] == pairs[0]["rejected_ids"][:5] and sum(pairs[0]["chosen_loss_mask"]) > 0
     with pytest.raises(ValueError):
         get_custom_dataset(str(d), type="dpo")
+
+
+def test_countdown_reward_and_dataset(tmp_path):
+    from fractions import Fraction
+
+    from areal_b200.dataset import get_custom_dataset
+    from areal_b200.dataset.countdown import generate
+    from areal_b200.reward.countdown import countdown_reward_fn, countdown_score, evaluate, extract_answer
+
+    assert evaluate("(7 - (5 - 3)) * 8") == 40 and evaluate("8 / 3 * 3") == 8 and evaluate("-3 + 5") == 2
+    assert evaluate("2 +") is None and evaluate("4 / (2 - 2)") is None and evaluate("2 ** 3") is None
+    assert evaluate("__import__('os')") is None and evaluate("") is None and evaluate("(1 + 2") is None
+    assert evaluate("7 / 2") == Fraction(7, 2)
+    assert extract_answer("<think>x</think> <answer> (3 + 5) * 3 = 24 </answer>") == "(3 + 5) * 3"
+    assert countdown_score("no tags", 24, [3, 5, 3]) == 0.0
+    assert countdown_score("<answer>(3 + 5) * 3</answer>", 24, [3, 5, 3]) == 1.0
+    assert countdown_score("<answer>(3 + 5) * 4</answer>", 24, [3, 5, 3]) == 0.1      # a number that was not given
+    assert countdown_score("<answer>3 + 5 + 3</answer>", 24, [3, 5, 3]) == 0.1        # wrong value
+    assert countdown_score("<answer>3 + 5</answer>", 8, [3, 5, 3]) == 0.1             # one number unused
+    assert countdown_score("<answer>1</answer> <answer>5 * 5 - 1</answer>", 24, [5, 5, 1]) == 1.0  # the last block counts
+    d = tmp_path / "countdown"
+    generate(str(d / "train.jsonl"), 50, seed=3)
+    items = get_custom_dataset(path=str(d), type="rl", split="train")
+    assert len(items) == 50
+    import json
+
+    for it, line in zip(items, open(d / "train.jsonl")):
+        rec = json.loads(line)
+        assert str(it["target"]) in it["messages"][0]["content"] and len(it["numbers"]) == 4
+        # the recorded solution solves its own puzzle through the reward function
+        assert countdown_reward_fn("", f"<answer>{rec['solution']}</answer>", [], [], **it) == 1.0
