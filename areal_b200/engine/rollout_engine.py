@@ -22,7 +22,9 @@ decode step (model on the current CUDA stream) → fused sampling → commit.
 from __future__ import annotations
 
 import asyncio
+import collections
 import ctypes
+import hashlib
 import os
 import dataclasses
 import threading
@@ -239,6 +241,11 @@ class NativeRolloutEngine(InferenceEngine):
         # vision-language requests: rid → pixel rows, patch grids, position triples of the prompt and the offset
         # of the positions that follow it
         self._mm: dict[int, dict[str, Any]] = {}
+        # vision tower outputs by image content, valid for the current weights: the samples of a group (and a
+        # request re-submitted after an interruption that did not change the weights) share one tower pass
+        self._vis_cache: "collections.OrderedDict[bytes, tuple]" = collections.OrderedDict()
+        self._vis_cache_max = 64
+        self.vision_tower_images = 0  # images that went through the tower (cache misses)
         self._lock = threading.Lock()
         self._executor = None
         self._gen_tokens = 0
@@ -496,7 +503,7 @@ class NativeRolloutEngine(InferenceEngine):
             mms = [self._mm.get(r) for r in seq_ids]
         if not any(mms):
             return {}
-        pos3, pix, grids = [], [], []
+        pos3, keyed = [], []
         for i, mm in enumerate(mms):
             n = int(cu[i + 1] - cu[i])
             if mm is None:
@@ -504,11 +511,33 @@ class NativeRolloutEngine(InferenceEngine):
             else:
                 assert mm["pos3"].shape[1] == n, "an image prompt is prefilled whole"
                 pos3.append(mm["pos3"])
-                pix.append(mm["pixel_values"])
-                grids.append(mm["image_grid_thw"])
+                keyed.append(mm)
+        # the tower runs once per distinct image set of the plan that is not cached yet
+        todo = {}
+        for mm in keyed:
+            if mm["key"] not in self._vis_cache:
+                todo.setdefault(mm["key"], mm)
+        if todo:
+            tm = list(todo.values())
+            f, deep = self.model.visual(torch.cat([m["pixel_values"] for m in tm], 0),
+                                        torch.cat([m["image_grid_thw"] for m in tm], 0), return_deepstack=True)
+            unit, o = self.model.visual.unit, 0
+            for m in tm:
+                k = int(m["image_grid_thw"].prod(-1).sum()) // unit
+                self._vis_cache[m["key"]] = (f[o:o + k], [d[o:o + k] for d in deep])
+                self.vision_tower_images += int(m["image_grid_thw"].shape[0])
+                o += k
+        got = []
+        for mm in keyed:
+            self._vis_cache.move_to_end(mm["key"])
+            got.append(self._vis_cache[mm["key"]])
+        while len(self._vis_cache) > self._vis_cache_max:
+            self._vis_cache.popitem(last=False)
+        feats = torch.cat([g[0] for g in got], 0)
+        deep = [torch.cat([g[1][j] for g in got], 0) for j in range(len(got[0][1]))]
         mc = self.model_config
         pos3 = torch.cat(pos3, 1).to(self.device)
-        x, adds = self.model.embed_inputs(ids.long(), torch.cat(pix, 0), torch.cat(grids, 0))
+        x, adds = self.model.embed_inputs(ids.long(), features=(feats, deep))
         return dict(embeds=x, layer_adds=adds,
                     rope=mrope_tables(pos3, mc.rotary_dim, mc.rope_theta, mc.mrope_section, mc.mrope_interleaved))
 
@@ -593,7 +622,10 @@ class NativeRolloutEngine(InferenceEngine):
 
             pos3, deltas = mrope_position_ids(input_ids, [0, len(input_ids)], images["image_grid_thw"].tolist(),
                                               self.model_config)
-            mm_state = dict(images, pos3=pos3, delta=int(deltas[0]))
+            h = hashlib.blake2b(digest_size=16)
+            h.update(images["pixel_values"].contiguous().numpy().tobytes())
+            h.update(images["image_grid_thw"].contiguous().numpy().tobytes())
+            mm_state = dict(images, pos3=pos3, delta=int(deltas[0]), key=h.digest())
         with self._lock:
             rid = self.sched.add(input_ids, max_new, int(g.min_new_tokens), stop, bool(g.ignore_eos))
             if rid < 0:
@@ -649,6 +681,7 @@ class NativeRolloutEngine(InferenceEngine):
             with self._lock:
                 self.sched.abort_all()
             self._deliver()
+            self._vis_cache.clear()  # a pause precedes every weight update: cached tower outputs go stale
 
     def continue_generation(self):
         self._paused.clear()
@@ -659,6 +692,8 @@ class NativeRolloutEngine(InferenceEngine):
         """Copies the trainer's flat bf16 weights into this engine's flat buffer. Both sides
         use the same model class, hence the same layout, so this is one device copy (a peer
         copy over NVLink when the two engines sit on different GPUs)."""
+        with self._step_lock:
+            self._vis_cache.clear()
         src = getattr(trainer, "weight_flat", trainer.flat).flat
         dst = self.flat.flat
         assert src.numel() >= dst.numel() or dst.numel() >= src.numel()

@@ -415,14 +415,17 @@ class QwenVLModel(QwenModel):
             image_grid_thw.tolist() if torch.is_tensor(image_grid_thw) else list(image_grid_thw))
         return mrope_position_ids(input_ids.tolist(), meta.cu_cpu.tolist(), grids, self.cfg, video_second_per_grid)
 
-    def embed_inputs(self, input_ids, pixel_values=None, image_grid_thw=None):
+    def embed_inputs(self, input_ids, pixel_values=None, image_grid_thw=None, features=None):
         """``(x, layer_adds)``: token embeddings with the image placeholder rows replaced by the tower's output,
-        and (Qwen3-VL) ``(rows, [features…])`` to add to those rows after the first decoder layers."""
+        and (Qwen3-VL) ``(rows, [features…])`` to add to those rows after the first decoder layers.
+        ``features = (feats, deep)`` skips the tower (a caller that cached its output)."""
         x = fused.embedding(input_ids, self.embed)
-        if pixel_values is None or pixel_values.numel() == 0:
+        if features is None and (pixel_values is None or pixel_values.numel() == 0):
             return x, None
         p = self.pctx
-        if self.shard_vision and p is not None and p.sp_size > 1:
+        if features is not None:
+            feats, deep = features
+        elif self.shard_vision and p is not None and p.sp_size > 1:
             feats, deep = self._sharded_visual(pixel_values, image_grid_thw)
         else:
             feats, deep = self.visual(pixel_values, image_grid_thw, return_deepstack=True)

@@ -506,3 +506,40 @@ def test_load_image_forms(tmp_path):
         assert im.size == (30, 20) and im.mode == "RGB"
     assert load_image(im) is im and load_image(b"not an image") == b"not an image"
     assert load_image(image_to_base64(im).encode(), decode_bytes=False) == image_to_base64(im).encode()
+
+
+def test_group_samples_share_one_tower_pass():
+    """The samples of a group carry the same image: the rollout engine runs the vision tower once per distinct
+    image set (keyed by content) and drops the cached features when the weights change."""
+    import asyncio
+
+    from areal_b200.api.cli_args import GenerationHyperparameters
+    from areal_b200.api.io_struct import ModelRequest
+
+    eng = _rollout_engine(preset="tiny-qwen3-vl")
+    try:
+        ids, pix = _sample([(1, 4, 6)], [3, 2], seed=5)
+        ids2, pix2 = _sample([(1, 4, 4)], [2, 2], seed=6)
+        gc = GenerationHyperparameters(max_new_tokens=4, greedy=True, ignore_eos=True)
+
+        def req(i, ids, pix, grid):
+            # every request gets its own copy of the tensors, as separate processor calls produce
+            return ModelRequest(rid=str(i), input_ids=ids, gconfig=gc, metadata={"multi_modal_input": [
+                dict(pixel_values=pix.clone(), image_grid_thw=torch.tensor([grid]))]})
+
+        async def go():
+            return await asyncio.gather(*[eng.agenerate(req(i, ids, pix, (1, 4, 6))) for i in range(4)],
+                                        eng.agenerate(req(9, ids2, pix2, (1, 4, 4))))
+
+        outs = asyncio.run(go())
+        assert eng.vision_tower_images == 2 and len(eng._vis_cache) == 2
+        assert all(o.output_tokens == outs[0].output_tokens for o in outs[:4])
+        again = asyncio.run(eng.agenerate(req(10, ids, pix, (1, 4, 6))))
+        assert eng.vision_tower_images == 2 and again.output_tokens == outs[0].output_tokens
+        eng.pause_generation()
+        eng.continue_generation()
+        assert not eng._vis_cache
+        asyncio.run(eng.agenerate(req(11, ids, pix, (1, 4, 6))))
+        assert eng.vision_tower_images == 3
+    finally:
+        eng.destroy()
