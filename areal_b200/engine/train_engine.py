@@ -756,7 +756,8 @@ class B200TrainEngine(TrainEngine):
                 # with LoRA: the merged model (loadable by any HF consumer, and by the rollout engine's
                 # disk update) plus the adapter alone in the PEFT layout
                 with self._merged_weights():
-                    save_hf_checkpoint(self.model, self.model_config, meta.path, tokenizer=meta.tokenizer)
+                    save_hf_checkpoint(self.model, self.model_config, meta.path, tokenizer=meta.tokenizer,
+                                       processor=meta.processor)
                 if self.flat_base is not None:
                     from ..models.lora import save_adapter
 

@@ -82,8 +82,9 @@ class _ListLoader:
 
 
 class PPOTrainer:
-    def __init__(self, config: PPOConfig, train_dataset, valid_dataset=None, tokenizer=None):
+    def __init__(self, config: PPOConfig, train_dataset, valid_dataset=None, tokenizer=None, processor=None):
         self.tokenizer = tokenizer
+        self.processor = processor  # vision-language models: saved next to the weights
         self.config = config
         self.train_dataset, self.valid_dataset = train_dataset, valid_dataset
         use_cuda = torch.cuda.is_available()
@@ -270,7 +271,8 @@ class PPOTrainer:
                 stats = self.train_step(batch, global_step)
             self.step_times.append(time.perf_counter() - t_step)
             with stats_tracker.record_timing("save"):
-                self.saver.save(self.actor_engine, epoch, epoch_step, global_step)
+                self.saver.save(self.actor_engine, epoch, epoch_step, global_step, tokenizer=self.tokenizer,
+                                processor=self.processor)
             with stats_tracker.record_timing("checkpoint_for_recover"):
                 self.recover.dump(self.actor_engine, StepInfo(epoch, epoch_step, global_step, steps_per_epoch),
                                   self.saver, self.evaluator, self.stats_logger, self.dataloader)

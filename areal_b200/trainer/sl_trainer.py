@@ -61,8 +61,9 @@ def collate_pairs(items: list[dict[str, Any]]) -> dict[str, torch.Tensor]:
 class _SLTrainer:
     collate: Callable = staticmethod(collate_sft)
 
-    def __init__(self, config, train_dataset, valid_dataset=None, tokenizer=None):
+    def __init__(self, config, train_dataset, valid_dataset=None, tokenizer=None, processor=None):
         self.tokenizer = tokenizer
+        self.processor = processor  # vision-language models: saved next to the weights
         self.config = config
         use_cuda = torch.cuda.is_available()
         if not dist.is_initialized() and "RANK" in os.environ:
@@ -141,7 +142,8 @@ class _SLTrainer:
                     st = self._train_step(batch)
                 self.engine.set_version(step + 1)
                 with stats_tracker.record_timing("save"):
-                    self.saver.save(self.engine, epoch, epoch_step, step)
+                    self.saver.save(self.engine, epoch, epoch_step, step, tokenizer=self.tokenizer,
+                                    processor=self.processor)
                 self.recover.dump(self.engine, StepInfo(epoch, epoch_step, step, spe), self.saver, self.evaluator,
                                   self.stats_logger, self.train_loader)
                 if self.valid_loader is not None:

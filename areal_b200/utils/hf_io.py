@@ -36,7 +36,8 @@ def load_hf_weights(model, path: str, strict: bool = True):
     return model
 
 
-def save_hf_checkpoint(model, model_config, path: str, tokenizer=None, max_shard_bytes: int = MAX_SHARD_BYTES):
+def save_hf_checkpoint(model, model_config, path: str, tokenizer=None, max_shard_bytes: int = MAX_SHARD_BYTES,
+                       processor=None):
     os.makedirs(path, exist_ok=True)
     shards: list[dict[str, torch.Tensor]] = [{}]
     size = 0
@@ -63,6 +64,8 @@ def save_hf_checkpoint(model, model_config, path: str, tokenizer=None, max_shard
         json.dump(model_config.to_hf_config(), f, indent=2)
     if tokenizer is not None and hasattr(tokenizer, "save_pretrained"):
         tokenizer.save_pretrained(path)
+    if processor is not None and hasattr(processor, "save_pretrained"):
+        processor.save_pretrained(path)  # image preprocessing settings of a vision-language checkpoint
 
 
 def load_hf_tokenizer(path: str, **kwargs):

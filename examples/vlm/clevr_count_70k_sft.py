@@ -20,7 +20,7 @@ def main(argv):
     valid = get_custom_dataset(path=config.valid_dataset.path, type="sft", split="test", tokenizer=tokenizer,
                                processor=processor, max_length=config.valid_dataset.max_length) \
         if config.valid_dataset else None
-    with SFTTrainer(config, train, valid, tokenizer=tokenizer) as trainer:
+    with SFTTrainer(config, train, valid, tokenizer=tokenizer, processor=processor) as trainer:
         trainer.train()
 
 

@@ -30,7 +30,7 @@ def main(argv):
                            enable_thinking=False)
     eval_kwargs = dict(workflow_kwargs, gconfig=(config.eval_gconfig or config.gconfig).new(temperature=0.6))
     wf = "areal_b200.workflow.vision_rlvr.VisionRLVRWorkflow"
-    with PPOTrainer(config, train, valid, tokenizer=tokenizer) as trainer:
+    with PPOTrainer(config, train, valid, tokenizer=tokenizer, processor=processor) as trainer:
         trainer.train(workflow=wf, workflow_kwargs=workflow_kwargs, eval_workflow=wf, eval_workflow_kwargs=eval_kwargs)
 
 

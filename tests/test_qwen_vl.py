@@ -543,3 +543,37 @@ def test_group_samples_share_one_tower_pass():
         assert eng.vision_tower_images == 3
     finally:
         eng.destroy()
+
+
+def test_trainer_checkpoint_carries_tokenizer_and_processor(tmp_path):
+    """A saved vision-language checkpoint is complete: weights, composite config, and the tokenizer's and
+    processor's own files."""
+    import os
+
+    from areal_b200.api.cli_args import MicroBatchSpec, OptimizerConfig, SFTConfig, TrainEngineConfig, _propagate_names
+    from areal_b200.trainer.sl_trainer import SFTTrainer
+
+    class Saves:
+        def __init__(self, fname):
+            self.fname = fname
+
+        def save_pretrained(self, path):
+            open(os.path.join(path, self.fname), "w").write("{}")
+
+    cfg = SFTConfig(actor=TrainEngineConfig(backend="fsdp:d1", model_preset="tiny-qwen2_5-vl", init_from_scratch=True,
+                                            dtype="float32", optimizer=OptimizerConfig(lr=1e-3),
+                                            mb_spec=MicroBatchSpec(max_tokens_per_mb=128)))
+    cfg.experiment_name, cfg.trial_name = "t", "t"
+    cfg.cluster.fileroot = str(tmp_path)
+    cfg.train_dataset.batch_size = 6
+    cfg.total_train_epochs = 1
+    cfg.saver.freq_steps = 1
+    _propagate_names(cfg)
+    with SFTTrainer(cfg, _vl_items(), None, tokenizer=Saves("tokenizer_config.json"),
+                    processor=Saves("preprocessor_config.json")) as tr:
+        tr.train(max_steps=1)
+    found = [os.path.join(d, f) for d, _, fs in os.walk(tmp_path) for f in fs]
+    names = {os.path.basename(f) for f in found}
+    assert {"model.safetensors", "config.json", "tokenizer_config.json", "preprocessor_config.json"} <= names
+    ckpt = os.path.dirname(next(f for f in found if f.endswith("model.safetensors")))
+    assert ModelConfig.from_hf_config(ckpt).is_vl
