@@ -123,6 +123,24 @@ class ModelConfig:
             n += self.vocab_size * h
         if self.is_critic:
             n += h
+        return n + self.vision_params()
+
+    def vision_params(self) -> int:
+        """Parameters of the vision tower (0 for text models)."""
+        v = self.vision
+        if not v:
+            return 0
+        d, inter, unit = v["hidden_size"], v["intermediate_size"], v.get("spatial_merge_size", 2) ** 2
+        kind = v.get("variant", "qwen2_5_vl")
+        gated, ln = kind == "qwen2_5_vl", kind != "qwen2_5_vl"
+        patch = v.get("in_channels", 3) * v.get("temporal_patch_size", 2) * v["patch_size"] ** 2
+        block = 3 * d * d + 3 * d + d * d + d + (3 if gated else 2) * d * inter + (2 if gated else 1) * inter + d \
+            + 2 * d * (2 if ln else 1)
+        merger = d * (2 if ln else 1) + (d * unit) ** 2 + d * unit + d * unit * v["out_hidden_size"] + v["out_hidden_size"]
+        n = d * patch + v["depth"] * block + merger
+        if kind == "qwen3_vl":
+            deep = 2 * d * unit + (d * unit) ** 2 + d * unit + d * unit * v["out_hidden_size"] + v["out_hidden_size"]
+            n += d + v["num_position_embeddings"] * d + len(v.get("deepstack_visual_indexes", [])) * deep
         return n
 
     def flops_per_token(self, seq_len: int, backward: bool = True) -> float:

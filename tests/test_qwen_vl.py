@@ -577,3 +577,10 @@ def test_trainer_checkpoint_carries_tokenizer_and_processor(tmp_path):
     assert {"model.safetensors", "config.json", "tokenizer_config.json", "preprocessor_config.json"} <= names
     ckpt = os.path.dirname(next(f for f in found if f.endswith("model.safetensors")))
     assert ModelConfig.from_hf_config(ckpt).is_vl
+
+
+@pytest.mark.parametrize("preset", ["tiny-qwen2_5-vl", "tiny-qwen2-vl", "tiny-qwen3-vl", "tiny-qwen3-vl-moe"])
+def test_parameter_count_includes_the_tower(preset):
+    cfg = PRESETS[preset]
+    m = build_model(cfg, dtype=torch.float32, seed=None)
+    assert cfg.num_params() == sum(p.numel() for p in m.parameters()) and cfg.vision_params() > 0
