@@ -448,8 +448,7 @@ class QwenModel(nn.Module):
         if stage_input is not None:
             x, res = stage_input
         elif embeds is not None:
-            assert p is None or p.tp_size == 1, "precomputed embeddings are not sharded over tensor parallel ranks"
-            x, res = embeds, None
+            x, res = embeds, None  # under tensor parallelism: this rank's token rows, like the lookup below
         elif p is not None and p.tp_size > 1:
             # input_ids / position_ids hold every token of this sequence-parallel shard; the
             # vocab-parallel lookup leaves each tp rank with its T/tp rows

@@ -205,11 +205,11 @@ class VisionTower(nn.Module):
         self.unit = self.merge * self.merge
         self.patch_dim = vc.get("in_channels", 3) * vc.get("temporal_patch_size", 2) * vc["patch_size"] ** 2
         mk = lambda *s: nn.Parameter(torch.empty(*s, dtype=dtype, device=device))
-        self.patch_embed = mk(dim, self.patch_dim)
+        self.patch_proj = mk(dim, self.patch_dim)
         # Qwen3-VL: bias on the patch projection, a learned position table (a square grid, interpolated to each
         # image's patch grid) and extra mergers on the outputs of the `deepstack_visual_indexes` blocks
-        self.patch_embed_bias = mk(dim) if v3 else None
-        self.pos_embed = mk(vc["num_position_embeddings"], dim) if v3 else None
+        self.patch_proj_bias = mk(dim) if v3 else None
+        self.pos_table = mk(vc["num_position_embeddings"], dim) if v3 else None
         self.deepstack_at = list(vc.get("deepstack_visual_indexes", [])) if v3 else []
         self.deepstack = nn.ModuleList(DeepStackMerger(dim, self.unit, vc["out_hidden_size"], dtype, device)
                                        for _ in self.deepstack_at)
@@ -255,7 +255,7 @@ class VisionTower(nn.Module):
     def _pos_embed(self, grids: list[list[int]]) -> torch.Tensor:
         """Bilinear interpolation of the square position table onto each image's ``h × w`` patch grid, rows in
         the processor's patch order (merge groups contiguous)."""
-        side = int(self.pos_embed.shape[0] ** 0.5)
+        side = int(self.pos_table.shape[0] ** 0.5)
         m, out = self.merge, []
         for t, h, w in grids:
             hi, wi = torch.linspace(0, side - 1, h), torch.linspace(0, side - 1, w)
@@ -265,20 +265,20 @@ class VisionTower(nn.Module):
             e = 0
             for hh, ww, wt in ((h0, w0, (1 - dh) * (1 - dw)), (h0, w1, (1 - dh) * dw), (h1, w0, dh * (1 - dw)),
                                (h1, w1, dh * dw)):
-                idx = (hh[:, None] * side + ww[None, :]).reshape(-1).long().to(self.pos_embed.device)
-                e = e + self.pos_embed.index_select(0, idx) * wt.reshape(-1, 1).to(self.pos_embed)
+                idx = (hh[:, None] * side + ww[None, :]).reshape(-1).long().to(self.pos_table.device)
+                e = e + self.pos_table.index_select(0, idx) * wt.reshape(-1, 1).to(self.pos_table)
             e = e.view(h // m, m, w // m, m, -1).permute(0, 2, 1, 3, 4).reshape(h * w, -1)
             out.append(e.repeat(t, 1))
         return torch.cat(out, 0)
 
     def forward(self, pixel_values: torch.Tensor, grid_thw, return_deepstack: bool = False):
         grids = [[int(v) for v in g] for g in (grid_thw.tolist() if torch.is_tensor(grid_thw) else grid_thw)]
-        dev, dt = self.patch_embed.device, self.patch_embed.dtype
-        x = F.linear(pixel_values.to(device=dev, dtype=dt).view(-1, self.patch_dim), self.patch_embed,
-                     self.patch_embed_bias)
+        dev, dt = self.patch_proj.device, self.patch_proj.dtype
+        x = F.linear(pixel_values.to(device=dev, dtype=dt).view(-1, self.patch_dim), self.patch_proj,
+                     self.patch_proj_bias)
         n, dim = x.shape
         assert n == sum(t * h * w for t, h, w in grids), "pixel_values rows do not match image_grid_thw"
-        if self.pos_embed is not None:
+        if self.pos_table is not None:
             x = x + self._pos_embed(grids)
         hd = dim // self.heads
         # 2-D rotary: the first half of the rotated pairs turns with the patch's row, the second with its column
@@ -312,14 +312,14 @@ class VisionTower(nn.Module):
     # HF names (without the tower's prefix) ↔ parameters; fused gate/up are two HF tensors
     def hf_tensors(self) -> Iterator[tuple[str, torch.Tensor]]:
         vc = self.vc
-        yield "patch_embed.proj.weight", self.patch_embed.view(
+        yield "patch_embed.proj.weight", self.patch_proj.view(
             -1, vc.get("in_channels", 3), vc.get("temporal_patch_size", 2), vc["patch_size"], vc["patch_size"])
         inter = vc["intermediate_size"]
         v3 = self.variant == "qwen3_vl"
         fc1, fc2 = ("mlp.linear_fc1", "mlp.linear_fc2") if v3 else ("mlp.fc1", "mlp.fc2")
         if v3:
-            yield "patch_embed.proj.bias", self.patch_embed_bias
-            yield "pos_embed.weight", self.pos_embed
+            yield "patch_embed.proj.bias", self.patch_proj_bias
+            yield "pos_embed.weight", self.pos_table
             for i, d in enumerate(self.deepstack):
                 q = f"deepstack_merger_list.{i}."
                 yield q + "norm.weight", d.norm
@@ -390,9 +390,9 @@ class QwenVLModel(QwenModel):
     ``pixel_values`` / ``image_grid_thw`` of all images of the packed batch in order of appearance."""
 
     def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", pctx=None):
-        if pctx is not None and (pctx.tp_size > 1 or pctx.pp_size > 1 or getattr(pctx, "ep_size", 1) > 1):
-            raise NotImplementedError("the vision-language model runs under data and Ulysses sequence parallelism "
-                                      "only (no tensor, pipeline or expert parallelism)")
+        if pctx is not None and (pctx.pp_size > 1 or getattr(pctx, "ep_size", 1) > 1):
+            raise NotImplementedError("the vision-language model runs under data, tensor and Ulysses sequence "
+                                      "parallelism (no pipeline or expert parallelism)")
         super().__init__(cfg, dtype=dtype, device=device, pctx=pctx)
         assert cfg.vision["out_hidden_size"] == cfg.hidden_size
         self.visual = VisionTower(cfg.vision, dtype, device)
@@ -415,14 +415,25 @@ class QwenVLModel(QwenModel):
             image_grid_thw.tolist() if torch.is_tensor(image_grid_thw) else list(image_grid_thw))
         return mrope_position_ids(input_ids.tolist(), meta.cu_cpu.tolist(), grids, self.cfg, video_second_per_grid)
 
-    def embed_inputs(self, input_ids, pixel_values=None, image_grid_thw=None, features=None):
+    def embed_inputs(self, input_ids, pixel_values=None, image_grid_thw=None, features=None,
+                     seq_slice: slice | None = None):
         """``(x, layer_adds)``: token embeddings with the image placeholder rows replaced by the tower's output,
         and (Qwen3-VL) ``(rows, [features…])`` to add to those rows after the first decoder layers.
-        ``features = (feats, deep)`` skips the tower (a caller that cached its output)."""
-        x = fused.embedding(input_ids, self.embed)
+        ``features = (feats, deep)`` skips the tower (a caller that cached its output). ``input_ids`` are all
+        tokens of the micro-batch; the result covers ``seq_slice`` of them (this Ulysses rank's rows), and under
+        tensor parallelism this rank's share of those rows (activations between blocks are token-sharded)."""
+        p = self.pctx
+        lo, hi = (seq_slice.start, seq_slice.stop) if seq_slice is not None else (0, input_ids.shape[0])
+        if p is not None and p.tp_size > 1:
+            from ..parallel.tensor_parallel import vocab_parallel_embedding
+
+            x = vocab_parallel_embedding(input_ids[lo:hi], self.embed, p.tp_fused)
+            n = (hi - lo) // p.tp_size
+            lo, hi = lo + p.tp_rank * n, lo + (p.tp_rank + 1) * n
+        else:
+            x = fused.embedding(input_ids[lo:hi], self.embed)
         if features is None and (pixel_values is None or pixel_values.numel() == 0):
             return x, None
-        p = self.pctx
         if features is not None:
             feats, deep = features
         elif self.shard_vision and p is not None and p.sp_size > 1:
@@ -433,6 +444,10 @@ class QwenVLModel(QwenModel):
         rows = mask.nonzero().squeeze(-1)
         if rows.numel() != feats.shape[0]:
             raise ValueError(f"{rows.numel()} image placeholder tokens but {feats.shape[0]} image features")
+        if lo != 0 or hi != input_ids.shape[0]:
+            keep = ((rows >= lo) & (rows < hi)).nonzero().squeeze(-1)
+            rows = rows.index_select(0, keep) - lo
+            feats, deep = feats.index_select(0, keep), [d.index_select(0, keep) for d in deep]
         adds = (rows, [d.to(x.dtype) for d in deep]) if deep else None
         return x.index_copy(0, rows, feats.to(x.dtype)), adds
 
@@ -489,15 +504,11 @@ class QwenVLModel(QwenModel):
         cos, sin = mrope_tables(mrope_pos, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.mrope_section,
                                 self.cfg.mrope_interleaved)
         rows = torch.arange(input_ids.shape[0], dtype=torch.int32, device=input_ids.device)
-        x, adds = self.embed_inputs(input_ids, pixel_values, image_grid_thw)
+        x, adds = self.embed_inputs(input_ids, pixel_values, image_grid_thw, seq_slice=seq_slice)
         if seq_slice is not None:
             # the rotary table stays whole: local rows index it before the sequence→head exchange, all rows after
             self.pctx.extras["full_positions"] = rows
-            lo, hi = seq_slice.start, seq_slice.stop
-            if adds is not None:
-                keep = ((adds[0] >= lo) & (adds[0] < hi)).nonzero().squeeze(-1)
-                adds = (adds[0].index_select(0, keep) - lo, [f.index_select(0, keep) for f in adds[1]])
-            input_ids, rows, x = input_ids[seq_slice], rows[seq_slice], x[seq_slice]
+            input_ids, rows = input_ids[seq_slice], rows[seq_slice]
         return super().forward(input_ids, rows, meta, attn_fn=attn_fn, embeds=x, rope=(cos, sin), layer_adds=adds)
 
     # ------------------------------------------------------------------ HF layout
@@ -520,8 +531,9 @@ class QwenVLModel(QwenModel):
         for name, t in self.visual.hf_tensors():
             yield self._VIS + name, t
 
-    def to_hf(self) -> Iterator[tuple[str, torch.Tensor]]:
-        return self.to_hf_local(export=True)
+    def _tp_dim(self, hf_name: str) -> int | None:
+        # the tower is replicated over tensor-parallel ranks; decoder names keep their rule under the prefix
+        return None if hf_name.startswith(self._VIS) else super()._tp_dim(hf_name)
 
     @torch.no_grad()
     def load_hf(self, tensors: Iterable[tuple[str, torch.Tensor]], strict: bool = True):
@@ -546,6 +558,10 @@ class QwenVLModel(QwenModel):
                     raise KeyError(f"unexpected tensor {name}")
                 continue
             d = dst[name]
+            dim = self._tp_dim(name)
+            if dim is not None:
+                n = t.shape[dim] // self.pctx.tp_size
+                t = t.narrow(dim, self.pctx.tp_rank * n, n)
             if d.shape != t.shape and name.endswith(("experts.gate_up_proj", "experts.down_proj")) \
                     and t.dim() == 3 and d.shape == t.transpose(1, 2).shape:
                 t = t.transpose(1, 2)  # written output dimension first (what transformers holds in memory)

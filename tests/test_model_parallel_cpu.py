@@ -68,3 +68,20 @@ def test_vision_language_step_under_ulysses(tmp_path, n, preset, extra):
     _run(n, 29680 + n + len(extra), ["--sp", "2", "--preset", preset, "--images"] + extra,
          _ref(tmp_path, preset=preset, images=True, n_mbs=n_mbs,
               extra=["--one-image"] if "--one-image" in extra else []))
+
+
+@pytest.mark.parametrize("n,preset,par", [(2, "tiny-qwen2_5-vl", ["--tp", "2"]),
+                                          (4, "tiny-qwen3-vl", ["--tp", "2", "--sp", "2", "--shard-vision"])])
+def test_vision_language_step_under_tensor_parallelism(tmp_path, n, preset, par):
+    """Image prompts with a tensor-parallel decoder (vocab-parallel embedding, token-sharded activations: the
+    image rows of this rank's tokens get their features; the tower is replicated and its gradients are summed
+    over the group), alone and combined with Ulysses."""
+    _run(n, 29690 + n, par + ["--preset", preset, "--images"], _ref(tmp_path, preset=preset, images=True))
+
+
+def test_vision_language_checkpoint_under_tensor_parallelism():
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", "29699", os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
+           "tiny-qwen3-vl"]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]

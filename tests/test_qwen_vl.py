@@ -146,7 +146,7 @@ def test_engine_trains_on_images(tmp_path):
         assert isinstance(eng.model, QwenVLModel)
         batch = collate_sft(data)
         assert len(batch["multi_modal_input"]) == 6 and batch["multi_modal_input"][2] == {}
-        w0 = eng.model.visual.patch_embed.detach().clone()
+        w0 = eng.model.visual.patch_proj.detach().clone()
         logp = eng.forward(batch)  # [B, L] padded next-token logprobs
         ids, pix = data[1]["input_ids"], data[1]["multi_modal_input"][0]
         meta = VarlenMeta(torch.tensor([0, len(ids)], dtype=torch.int32), "cpu")
@@ -157,7 +157,7 @@ def test_engine_trains_on_images(tmp_path):
         assert torch.allclose(logp[1, :len(ids) - 1], ref, atol=1e-4)
         tr.train(max_steps=6, step_callback=lambda s, st: losses.append(st["step/loss"]))
         assert losses[-1] < losses[0]
-        assert not torch.equal(eng.model.visual.patch_embed, w0), "the vision tower must train"
+        assert not torch.equal(eng.model.visual.patch_proj, w0), "the vision tower must train"
 
 
 def _rollout_engine(device="cpu", preset="tiny-qwen2_5-vl", **over):
@@ -287,14 +287,14 @@ def test_grpo_step_with_images(tmp_path):
     ds.append(dict(prompt="9 8 7 6 5", images=[]))  # one text-only prompt
     seen = []
     with PPOTrainer(cfg, ds) as tr:
-        w0 = tr.actor_engine.model.visual.patch_embed.detach().clone()
+        w0 = tr.actor_engine.model.visual.patch_proj.detach().clone()
         tr.train(workflow=VisionRLVRWorkflow,
                  workflow_kwargs=dict(reward_fn=_even_reward, gconfig=cfg.gconfig, tokenizer=_ToyTok(),
                                       processor=_ToyVLProcessor(), reward_in_process=True),
                  max_steps=2, step_callback=lambda s, st: seen.append(st))
         assert len(seen) == 2 and all(s["step/grad_norm"] > 0 for s in seen)
-        assert not torch.equal(tr.actor_engine.model.visual.patch_embed, w0)
-        assert torch.equal(tr.rollout.model.visual.patch_embed, tr.actor_engine.model.visual.patch_embed)
+        assert not torch.equal(tr.actor_engine.model.visual.patch_proj, w0)
+        assert torch.equal(tr.rollout.model.visual.patch_proj, tr.actor_engine.model.visual.patch_proj)
         # behaviour logprobs (rollout engine: prefill with image features + decode at offset positions) equal the
         # train engine's recomputation on the finished trajectory
         import asyncio
