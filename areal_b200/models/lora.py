@@ -137,8 +137,10 @@ def is_lora_param(name: str) -> bool:
 
 def iter_adapters(model) -> Iterator[tuple[str, torch.Tensor, LoRAAdapter]]:
     """``(hf_prefix, fused_weight, adapter)`` for every adapter of a ``QwenModel``."""
+    # a vision-language checkpoint nests its decoder under `language_model`
+    lm = "language_model." if getattr(model.cfg, "is_vl", False) else ""
     for i, layer in enumerate(model.layers, start=model.layer_start):
-        p = f"base_model.model.model.layers.{i}."
+        p = f"base_model.model.model.{lm}layers.{i}."
         a, m = layer.attn, layer.mlp
         if getattr(a, "lora_qkv", None) is not None:
             yield p + "self_attn.", a.qkv, a.lora_qkv

@@ -584,3 +584,42 @@ def test_parameter_count_includes_the_tower(preset):
     cfg = PRESETS[preset]
     m = build_model(cfg, dtype=torch.float32, seed=None)
     assert cfg.num_params() == sum(p.numel() for p in m.parameters()) and cfg.vision_params() > 0
+
+
+def test_lora_on_the_decoder_of_a_vision_language_model(tmp_path):
+    """Adapters on the decoder's projections, tower and base weights frozen; the adapter checkpoint names the
+    decoder where PEFT finds it in a vision-language model."""
+    import json
+    import os
+
+    from safetensors.torch import load_file
+
+    from areal_b200.api.cli_args import MicroBatchSpec, OptimizerConfig, SFTConfig, TrainEngineConfig, _propagate_names
+    from areal_b200.api.io_struct import SaveLoadMeta
+    from areal_b200.trainer.sl_trainer import SFTTrainer
+
+    cfg = SFTConfig(actor=TrainEngineConfig(backend="fsdp:d1", model_preset="tiny-qwen2_5-vl", init_from_scratch=True,
+                                            dtype="float32", use_lora=True, lora_rank=4, lora_alpha=8,
+                                            target_modules=["q_proj", "v_proj", "down_proj"],
+                                            optimizer=OptimizerConfig(lr=1e-2, warmup_steps_proportion=0.0,
+                                                                      weight_decay=0.0),
+                                            mb_spec=MicroBatchSpec(max_tokens_per_mb=128)))
+    cfg.experiment_name, cfg.trial_name = "t", "t"
+    cfg.cluster.fileroot = str(tmp_path)
+    cfg.train_dataset.batch_size = 6
+    cfg.train_dataset.shuffle = False
+    cfg.total_train_epochs = 5
+    _propagate_names(cfg)
+    losses = []
+    with SFTTrainer(cfg, _vl_items(), None) as tr:
+        eng = tr.engine
+        tower0 = eng.model.visual.patch_proj.detach().clone()
+        tr.train(max_steps=5, step_callback=lambda s, st: losses.append(st["step/loss"]))
+        assert losses[-1] < losses[0]
+        assert torch.equal(eng.model.visual.patch_proj, tower0), "the tower is part of the frozen base"
+        path = str(tmp_path / "ckpt")
+        eng.save(SaveLoadMeta(path=path, weight_format="hf", with_optim=False))
+        ad = load_file(os.path.join(path, "adapter_model.safetensors"))
+        assert "base_model.model.model.language_model.layers.0.self_attn.q_proj.lora_A.weight" in ad
+        assert json.load(open(os.path.join(path, "adapter_config.json")))["r"] == 4
+        assert ModelConfig.from_hf_config(path).is_vl  # the merged model next to it is a full VL checkpoint
