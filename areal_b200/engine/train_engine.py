@@ -438,7 +438,7 @@ class B200TrainEngine(TrainEngine):
             pctx.extras["full_positions"] = pos.to(torch.int32)  # for RoPE after the fused sequence→head exchange
         if self.model_config.is_vl:
             # image features and the per-token rotary table are built for the whole micro-batch, then sliced
-            hidden = self.model(ids, pos, meta, seq_slice=sl, **self._vision_inputs(mb))
+            hidden = self.model(ids, pos, meta, seq_slice=sl, stage_input=stage_input, **self._vision_inputs(mb))
         else:
             hidden = self.model(ids[sl], pos[sl], meta, stage_input=stage_input)  # [n, H]: this Ulysses shard
         if pctx.pp_size > 1 and not pctx.is_last_stage:
@@ -755,9 +755,21 @@ class B200TrainEngine(TrainEngine):
             if self.dp_rank == 0:
                 # with LoRA: the merged model (loadable by any HF consumer, and by the rollout engine's
                 # disk update) plus the adapter alone in the PEFT layout
+                # one writer per pipeline stage (the tensor- / sequence-parallel peers only take part in the
+                # gathers); stages write their own files and the first one indexes them afterwards
+                pctx = self.pctx
+                pp = pctx.pp_size if pctx is not None else 1
+                writer = pctx is None or (pctx.tp_rank == 0 and pctx.sp_rank == 0)
+                tag = f"stage{self.mesh.pp_rank + 1:02d}of{pp:02d}" if pp > 1 else ""
                 with self._merged_weights():
                     save_hf_checkpoint(self.model, self.model_config, meta.path, tokenizer=meta.tokenizer,
-                                       processor=meta.processor)
+                                       processor=meta.processor, write=writer, file_tag=tag)
+                if pp > 1:
+                    from ..utils.hf_io import write_hf_index
+
+                    dist.barrier(group=pctx.pp_group)
+                    if writer and self.mesh.pp_rank == 0:
+                        write_hf_index(meta.path)
                 if self.flat_base is not None:
                     from ..models.lora import save_adapter
 

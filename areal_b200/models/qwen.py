@@ -400,8 +400,8 @@ class QwenModel(nn.Module):
 
         p = self.pctx
         flat_ctx = ParallelContext(tp_group=p.tp_group, tp_rank=p.tp_rank, tp_size=p.tp_size)
-        full = QwenModel(self.cfg, dtype=next(self.parameters()).dtype, device=next(self.parameters()).device,
-                         pctx=flat_ctx if p.tp_size > 1 else None)
+        full = type(self)(self.cfg, dtype=next(self.parameters()).dtype, device=next(self.parameters()).device,
+                          pctx=flat_ctx if p.tp_size > 1 else None)
         full.init_weights(seed, std)
         src = dict(full.named_parameters())
         for name, prm in self.named_parameters():

@@ -390,12 +390,16 @@ class QwenVLModel(QwenModel):
     ``pixel_values`` / ``image_grid_thw`` of all images of the packed batch in order of appearance."""
 
     def __init__(self, cfg: ModelConfig, dtype=torch.bfloat16, device="cpu", pctx=None):
-        if pctx is not None and (pctx.pp_size > 1 or getattr(pctx, "ep_size", 1) > 1):
-            raise NotImplementedError("the vision-language model runs under data, tensor and Ulysses sequence "
-                                      "parallelism (no pipeline or expert parallelism)")
+        if pctx is not None and getattr(pctx, "ep_size", 1) > 1:
+            raise NotImplementedError("the vision-language model runs under data, tensor, pipeline and Ulysses "
+                                      "sequence parallelism (no expert parallelism)")
         super().__init__(cfg, dtype=dtype, device=device, pctx=pctx)
         assert cfg.vision["out_hidden_size"] == cfg.hidden_size
-        self.visual = VisionTower(cfg.vision, dtype, device)
+        # the tower feeds the embeddings: it lives on the first pipeline stage only
+        self.visual = VisionTower(cfg.vision, dtype, device) if self.first_stage else None
+        n_deep = len(cfg.vision.get("deepstack_visual_indexes", [])) if cfg.vision.get("variant") == "qwen3_vl" else 0
+        if self.first_stage and len(self.layers) < n_deep:
+            raise ValueError(f"the first pipeline stage needs at least {n_deep} decoder blocks (deep-stack features)")
         # set by the engine (`shard_vision_across_sp`): the images of a micro-batch are divided over the
         # sequence-parallel ranks instead of every rank running the tower on all of them
         self.shard_vision = False
@@ -403,7 +407,7 @@ class QwenVLModel(QwenModel):
     @torch.no_grad()
     def init_weights(self, seed: int = 0, std: float = 0.02):
         super().init_weights(seed, std)  # draws every matrix, zeroes every bias
-        for name, p in self.visual.named_parameters():
+        for name, p in (self.visual.named_parameters() if self.visual is not None else ()):
             if name.endswith("norm"):
                 p.fill_(1.0)
             elif name.endswith("shift"):
@@ -504,12 +508,16 @@ class QwenVLModel(QwenModel):
         cos, sin = mrope_tables(mrope_pos, self.cfg.rotary_dim, self.cfg.rope_theta, self.cfg.mrope_section,
                                 self.cfg.mrope_interleaved)
         rows = torch.arange(input_ids.shape[0], dtype=torch.int32, device=input_ids.device)
-        x, adds = self.embed_inputs(input_ids, pixel_values, image_grid_thw, seq_slice=seq_slice)
+        if stage_input is not None:
+            x = adds = None  # a later pipeline stage: activations arrive, only the rotary table is built here
+        else:
+            x, adds = self.embed_inputs(input_ids, pixel_values, image_grid_thw, seq_slice=seq_slice)
         if seq_slice is not None:
             # the rotary table stays whole: local rows index it before the sequence→head exchange, all rows after
             self.pctx.extras["full_positions"] = rows
             input_ids, rows = input_ids[seq_slice], rows[seq_slice]
-        return super().forward(input_ids, rows, meta, attn_fn=attn_fn, embeds=x, rope=(cos, sin), layer_adds=adds)
+        return super().forward(input_ids, rows, meta, attn_fn=attn_fn, stage_input=stage_input, embeds=x,
+                               rope=(cos, sin), layer_adds=adds)
 
     # ------------------------------------------------------------------ HF layout
     _LM = "model.language_model."
@@ -528,7 +536,7 @@ class QwenVLModel(QwenModel):
                     p = f"{self._LM}layers.{i}.mlp.experts."
                     yield p + "gate_up_proj", layer.mlp.gate_up.transpose(1, 2)
                     yield p + "down_proj", layer.mlp.down.transpose(1, 2)
-        for name, t in self.visual.hf_tensors():
+        for name, t in (self.visual.hf_tensors() if self.visual is not None else ()):
             yield self._VIS + name, t
 
     def _tp_dim(self, hf_name: str) -> int | None:

@@ -36,8 +36,35 @@ def load_hf_weights(model, path: str, strict: bool = True):
     return model
 
 
+def write_hf_index(path: str):
+    """``model.safetensors.index.json`` over every ``*.safetensors`` file of the directory (pipeline stages write
+    their own files; the index lets HF loaders find every tensor)."""
+    index, total = {}, 0
+    files = sorted(Path(path).glob("*.safetensors"))
+    for f in files:
+        if f.name.startswith("adapter_"):
+            continue
+        with safe_open(str(f), framework="pt", device="cpu") as sf:
+            for name in sf.keys():
+                index[name] = f.name
+                sl = sf.get_slice(name)
+                n = 1
+                for d in sl.get_shape():
+                    n *= d
+                total += n * {"F32": 4, "F64": 8, "I64": 8, "I32": 4}.get(sl.get_dtype(), 2)
+    with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
+        json.dump({"metadata": {"total_size": total}, "weight_map": index}, f, indent=2)
+
+
 def save_hf_checkpoint(model, model_config, path: str, tokenizer=None, max_shard_bytes: int = MAX_SHARD_BYTES,
-                       processor=None):
+                       processor=None, write: bool = True, file_tag: str = ""):
+    """``write=False``: only take part in the collectives of ``model.to_hf()`` (tensor-parallel gathers) without
+    touching the directory. ``file_tag`` keeps the files of several writers apart (one per pipeline stage:
+    ``model-<tag>-00001-of-0000N.safetensors``; call :func:`write_hf_index` once all of them are done)."""
+    if not write:
+        for _ in model.to_hf():
+            pass
+        return
     os.makedirs(path, exist_ok=True)
     shards: list[dict[str, torch.Tensor]] = [{}]
     size = 0
@@ -52,12 +79,15 @@ def save_hf_checkpoint(model, model_config, path: str, tokenizer=None, max_shard
     n = len(shards)
     total = 0
     for i, sh in enumerate(shards):
-        fname = "model.safetensors" if n == 1 else f"model-{i + 1:05d}-of-{n:05d}.safetensors"
+        if file_tag:
+            fname = f"model-{file_tag}-{i + 1:05d}-of-{n:05d}.safetensors"
+        else:
+            fname = "model.safetensors" if n == 1 else f"model-{i + 1:05d}-of-{n:05d}.safetensors"
         save_file(sh, os.path.join(path, fname), metadata={"format": "pt"})
         for k, v in sh.items():
             index[k] = fname
             total += v.numel() * v.element_size()
-    if n > 1:
+    if n > 1 and not file_tag:
         with open(os.path.join(path, "model.safetensors.index.json"), "w") as f:
             json.dump({"metadata": {"total_size": total}, "weight_map": index}, f, indent=2)
     with open(os.path.join(path, "config.json"), "w") as f:

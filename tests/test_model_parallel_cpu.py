@@ -79,9 +79,17 @@ def test_vision_language_step_under_tensor_parallelism(tmp_path, n, preset, par)
     _run(n, 29690 + n, par + ["--preset", preset, "--images"], _ref(tmp_path, preset=preset, images=True))
 
 
-def test_vision_language_checkpoint_under_tensor_parallelism():
-    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
-           "127.0.0.1", "--master-port", "29699", os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
-           "tiny-qwen3-vl"]
+@pytest.mark.parametrize("n,pp,preset", [(2, 1, "tiny-qwen3-vl"), (4, 2, "tiny-qwen3-vl"), (2, 2, "tiny-qwen2")])
+def test_checkpoint_under_tensor_and_pipeline_parallelism(tmp_path, n, pp, preset):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29699 + n + pp), os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
+           preset, str(pp), str(tmp_path / "ckpt")]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+@pytest.mark.parametrize("n,preset,par", [(2, "tiny-qwen3-vl", ["--pp", "2"]), (4, "tiny-qwen2_5-vl", ["--pp", "2", "--tp", "2"])])
+def test_vision_language_step_under_pipeline_parallelism(tmp_path, n, preset, par):
+    """The tower and the deep-stack adds live on the first stage; later stages rebuild only the rotary table."""
+    _run(n, 29705 + n, par + ["--preset", preset, "--images", "--n-mbs", "2"],
+         _ref(tmp_path, preset=preset, images=True, n_mbs=2))
