@@ -752,23 +752,37 @@ class B200TrainEngine(TrainEngine):
 
         os.makedirs(meta.path, exist_ok=True)
         if meta.weight_format == "hf":
-            if self.dp_rank == 0:
+            pctx = self.pctx
+            pp = pctx.pp_size if pctx is not None else 1
+            ep = pctx.ep_size if pctx is not None else 1
+            # savers: the first data-parallel replica; under expert parallelism the first expert-parallel block
+            # (its ranks hold different experts: the first writes everything it has, the others their experts)
+            saver = self.mesh.edp_rank == 0 if ep > 1 else self.dp_rank == 0
+            if saver:
                 # with LoRA: the merged model (loadable by any HF consumer, and by the rollout engine's
-                # disk update) plus the adapter alone in the PEFT layout
-                # one writer per pipeline stage (the tensor- / sequence-parallel peers only take part in the
-                # gathers); stages write their own files and the first one indexes them afterwards
-                pctx = self.pctx
-                pp = pctx.pp_size if pctx is not None else 1
-                writer = pctx is None or (pctx.tp_rank == 0 and pctx.sp_rank == 0)
-                tag = f"stage{self.mesh.pp_rank + 1:02d}of{pp:02d}" if pp > 1 else ""
+                # disk update) plus the adapter alone in the PEFT layout.
+                # One writer per pipeline stage and expert-parallel rank (tensor- / sequence-parallel peers only
+                # take part in the gathers); writers use their own files and the first one indexes them afterwards
+                if ep > 1:
+                    writer = pctx.tp_rank == 0
+                else:
+                    writer = pctx is None or (pctx.tp_rank == 0 and pctx.sp_rank == 0)
+                tag = (f"stage{self.mesh.pp_rank + 1:02d}of{pp:02d}" if pp > 1 else "") + \
+                      (f"ep{pctx.ep_rank + 1:02d}of{ep:02d}" if ep > 1 else "")
+                keep = (lambda name: ".mlp.experts." in name) if (ep > 1 and pctx.ep_rank > 0) else None
                 with self._merged_weights():
                     save_hf_checkpoint(self.model, self.model_config, meta.path, tokenizer=meta.tokenizer,
-                                       processor=meta.processor, write=writer, file_tag=tag)
-                if pp > 1:
+                                       processor=meta.processor, write=writer, file_tag=tag, keep=keep)
+                if pp > 1 or ep > 1:
                     from ..utils.hf_io import write_hf_index
 
-                    dist.barrier(group=pctx.pp_group)
-                    if writer and self.mesh.pp_rank == 0:
+                    if pp > 1:
+                        dist.barrier(group=pctx.pp_group)
+                    if ep > 1:
+                        dist.barrier(group=pctx.ep_group)
+                    if pp > 1 and ep > 1:
+                        dist.barrier(group=pctx.pp_group)
+                    if writer and self.mesh.pp_rank == 0 and (ep == 1 or pctx.ep_rank == 0):
                         write_hf_index(meta.path)
                 if self.flat_base is not None:
                     from ..models.lora import save_adapter

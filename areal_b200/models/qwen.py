@@ -635,8 +635,11 @@ class QwenModel(nn.Module):
             else:
                 Im = cfg.moe_intermediate_size
                 yield p + "mlp.gate.weight", m.router
-                for e in range(cfg.num_experts):
-                    q = p + f"mlp.experts.{e}."
+                # under expert parallelism this rank holds (and names) experts [ep_rank * n, (ep_rank + 1) * n)
+                n_loc = m.gate_up.shape[0]
+                e0 = self.pctx.ep_rank * n_loc if (self.pctx is not None and self.pctx.ep_size > 1) else 0
+                for e in range(n_loc):
+                    q = p + f"mlp.experts.{e0 + e}."
                     yield q + "gate_proj.weight", m.gate_up[e, :Im]
                     yield q + "up_proj.weight", m.gate_up[e, Im:]
                     yield q + "down_proj.weight", m.down[e]
@@ -711,6 +714,8 @@ class QwenModel(nn.Module):
                 seen.add(name)
                 continue  # tied
             if name not in dst:
+                if ".mlp.experts." in name and self.pctx is not None and self.pctx.ep_size > 1:
+                    continue  # an expert that lives on another expert-parallel rank
                 if strict:
                     raise KeyError(f"unexpected tensor {name}")
                 continue

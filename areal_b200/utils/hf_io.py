@@ -57,10 +57,12 @@ def write_hf_index(path: str):
 
 
 def save_hf_checkpoint(model, model_config, path: str, tokenizer=None, max_shard_bytes: int = MAX_SHARD_BYTES,
-                       processor=None, write: bool = True, file_tag: str = ""):
+                       processor=None, write: bool = True, file_tag: str = "", keep=None):
     """``write=False``: only take part in the collectives of ``model.to_hf()`` (tensor-parallel gathers) without
-    touching the directory. ``file_tag`` keeps the files of several writers apart (one per pipeline stage:
-    ``model-<tag>-00001-of-0000N.safetensors``; call :func:`write_hf_index` once all of them are done)."""
+    touching the directory. ``file_tag`` keeps the files of several writers apart (one per pipeline stage or
+    expert-parallel rank: ``model-<tag>-00001-of-0000N.safetensors``; call :func:`write_hf_index` once all of
+    them are done). ``keep(name)`` selects the tensors this writer puts down (an expert-parallel rank other than
+    the first writes only its experts)."""
     if not write:
         for _ in model.to_hf():
             pass
@@ -70,6 +72,8 @@ def save_hf_checkpoint(model, model_config, path: str, tokenizer=None, max_shard
     size = 0
     index: dict[str, str] = {}
     for name, t in model.to_hf():
+        if keep is not None and not keep(name):
+            continue
         nbytes = t.numel() * t.element_size()
         if shards[-1] and size + nbytes > max_shard_bytes:
             shards.append({})

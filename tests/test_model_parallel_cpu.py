@@ -79,11 +79,12 @@ def test_vision_language_step_under_tensor_parallelism(tmp_path, n, preset, par)
     _run(n, 29690 + n, par + ["--preset", preset, "--images"], _ref(tmp_path, preset=preset, images=True))
 
 
-@pytest.mark.parametrize("n,pp,preset", [(2, 1, "tiny-qwen3-vl"), (4, 2, "tiny-qwen3-vl"), (2, 2, "tiny-qwen2")])
-def test_checkpoint_under_tensor_and_pipeline_parallelism(tmp_path, n, pp, preset):
+@pytest.mark.parametrize("n,pp,preset,ep", [(2, 1, "tiny-qwen3-vl", 1), (4, 2, "tiny-qwen3-vl", 1),
+                                            (2, 2, "tiny-qwen2", 1), (2, 1, "tiny-qwen3-moe", 2)])
+def test_checkpoint_under_tensor_pipeline_and_expert_parallelism(tmp_path, n, pp, preset, ep):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29699 + n + pp), os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
-           preset, str(pp), str(tmp_path / "ckpt")]
+           "127.0.0.1", "--master-port", str(29699 + n + pp + 3 * ep), os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
+           preset, str(pp), str(tmp_path / "ckpt"), str(ep)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
