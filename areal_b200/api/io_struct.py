@@ -171,6 +171,7 @@ class SaveLoadMeta:
     processor: Any = None
     base_model_path: str | None = None
     naive_distributed: bool = False
+    async_save: bool = False  # dcp: stage to host memory, write on a background thread
 
 
 @dataclass

@@ -21,7 +21,8 @@ struct PpoLossParams {
   float c_clip;           // <= 1: dual clip disabled
   float behav_cap;        // <= 0: no cap on exp(prox - behave)
   float inv_denom;        // 1 / max(count(loss_mask), 1) fixed before any rejection
-  int use_decoupled;      // 0: proximal == behaviour policy, importance weight 1
+  int use_decoupled;      // bit 0: the ratio's denominator is the proximal policy (else the behaviour policy);
+                          // bit 1: multiply by the behaviour importance weight exp(prox - behave)
 };
 
 // stats[0] = sum loss, [1] = # clipped tokens, [2] = # dual-clipped tokens,
@@ -37,7 +38,7 @@ __global__ void ppo_loss_kernel(const float* __restrict__ logp, const float* __r
     float g = 0.f;
     if (mask[i]) {
       const float lp = logp[i];
-      const float px = p.use_decoupled ? prox[i] : behav[i];
+      const float px = (p.use_decoupled & 1) ? prox[i] : behav[i];
       const float A = adv[i];
       const float ratio = __expf(lp - px);
       const float hi = 1.f + (p.eps_clip_higher >= 0.f ? p.eps_clip_higher : p.eps_clip);
@@ -60,7 +61,7 @@ __global__ void ppo_loss_kernel(const float* __restrict__ logp, const float* __r
       }
       float w = 1.f;
       bool dropped = false;
-      if (p.use_decoupled) {
+      if (p.use_decoupled & 2) {
         w = __expf(px - behav[i]);
         if (p.behav_cap > 0.f && w > p.behav_cap) {
           w = 0.f;

@@ -1,4 +1,6 @@
-"""geometry3k vision-language RL prompts: image(s) + question + gold answer (areal/dataset/geometry3k.py)."""
+"""Vision-language RL prompts of the geometry3k and ViRL39K layouts: image(s) + question + gold answer
+(areal/dataset/geometry3k.py, areal/dataset/virl39k.py). The two corpora use the same record fields, so one
+builder serves both registry keys."""
 from .loaders import load_records
 
 
@@ -13,4 +15,4 @@ def rl(path, split="train", tokenizer=None, max_length=None, processor=None, **k
     return out
 
 
-BUILDERS = {("geometry3k", "rl"): rl}
+BUILDERS = {("geometry3k", "rl"): rl, ("virl39k", "rl"): rl}

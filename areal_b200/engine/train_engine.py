@@ -138,6 +138,10 @@ class B200TrainEngine(TrainEngine):
             self.dp_rank = self.mesh.shard_rank
             self._data_rank, self._data_size = self.mesh.dp_rank, self.mesh.dp_size
             self._mp_group = self.mesh.mp_group
+            # checkpoint coordination spans every train rank (tp / pp / ep peers write their own tensors); the
+            # second group serves writes on a background thread
+            self._all_cpu_group = dist.new_group(ranks, backend="gloo")
+            self._async_ckpt_group = dist.new_group(ranks, backend="gloo")
         elif dist.is_initialized():
             self.rank = dist.get_rank()
             world = dist.get_world_size()
@@ -145,16 +149,20 @@ class B200TrainEngine(TrainEngine):
             self.train_ranks = ranks
             if groups is not None:
                 self._dp_group, self._cpu_group = groups
+                self._async_ckpt_group = None
             else:
+                self._async_ckpt_group = dist.new_group(ranks, backend="gloo")
                 if ranks == list(range(world)):
                     self._dp_group = dist.group.WORLD
                 else:
                     self._dp_group = dist.new_group(ranks)
                 self._cpu_group = dist.new_group(ranks, backend="gloo") if dist.get_backend() != "gloo" \
                     else self._dp_group
+            self._all_cpu_group = self._cpu_group
             self.world_size = len(ranks)
             self.dp_rank = ranks.index(self.rank) if self.rank in ranks else -1
         else:
+            self._all_cpu_group = self._async_ckpt_group = None
             self.train_ranks = [0]
             self.world_size, self.dp_rank = 1, 0
         self.device = torch.device("cuda", torch.cuda.current_device()) if use_cuda else torch.device("cpu")
@@ -566,6 +574,9 @@ class B200TrainEngine(TrainEngine):
 
     def lr_scheduler_step(self):
         self.optimizer.sched_step += 1
+        if self.optimizer.partner is not None:
+            # the expert-weight optimizer follows the same schedule
+            self.optimizer.partner.sched_step = self.optimizer.sched_step
 
     def train_batch(self, input_: dict[str, Any], loss_fn: Callable, loss_weight_fn: Callable) -> dict[str, float]:
         """One optimizer step over ``input_`` (this rank's share of the batch), split into
@@ -770,6 +781,18 @@ class B200TrainEngine(TrainEngine):
                 tag = (f"stage{self.mesh.pp_rank + 1:02d}of{pp:02d}" if pp > 1 else "") + \
                       (f"ep{pctx.ep_rank + 1:02d}of{ep:02d}" if ep > 1 else "")
                 keep = (lambda name: ".mlp.experts." in name) if (ep > 1 and pctx.ep_rank > 0) else None
+                if pp > 1 or ep > 1:
+                    # several writers: the indexing rank clears earlier weight files, then everyone starts
+                    from ..utils.hf_io import remove_weight_files
+
+                    if writer and self.mesh.pp_rank == 0 and (ep == 1 or pctx.ep_rank == 0):
+                        remove_weight_files(meta.path)
+                    if pp > 1:
+                        dist.barrier(group=pctx.pp_group)
+                    if ep > 1:
+                        dist.barrier(group=pctx.ep_group)
+                    if pp > 1 and ep > 1:
+                        dist.barrier(group=pctx.pp_group)
                 with self._merged_weights():
                     save_hf_checkpoint(self.model, self.model_config, meta.path, tokenizer=meta.tokenizer,
                                        processor=meta.processor, write=writer, file_tag=tag, keep=keep)
@@ -789,18 +812,41 @@ class B200TrainEngine(TrainEngine):
 
                     save_adapter(self.model, self.model_config, meta.path, base_model_path=self.config.path or "")
         elif meta.weight_format == "dcp":
-            # sharded: every rank writes its slice of the flat (trainable) weights
-            o, n = self.flat.shard_offset, self.flat.shard_numel
-            torch.save(dict(flat=self.flat.flat[o:o + n].cpu(), offset=o, numel=self.flat.numel,
-                            dp_world=self.world_size, layout=self.flat.named_offsets()),
-                       os.path.join(meta.path, f"model_world_size_{self.world_size}_rank_{self.dp_rank}.pt"))
+            # torch.distributed.checkpoint: named tensors, every rank writes the part of its own flat shard
+            from ..utils.dcp_state import save_engine
+
+            self.wait_for_checkpoint()
+            ex = self._ckpt_executor() if (getattr(meta, "async_save", False) and
+                                           (self._async_ckpt_group is not None or not dist.is_initialized())) else None
+            group = self._async_ckpt_group if ex is not None else self._all_cpu_group
+            self._pending_ckpt = save_engine(self, meta.path, with_optim=meta.with_optim, process_group=group,
+                                             executor=ex)
+            return
         else:
             raise ValueError(f"unknown weight format {meta.weight_format}")
         if meta.with_optim and self.optimizer is not None:
-            sd = {k: (v.cpu() if torch.is_tensor(v) else v) for k, v in self.optimizer.state_dict().items()}
-            torch.save(sd, os.path.join(meta.path, f"optim_world_size_{self.world_size}_rank_{self.dp_rank}.pt"))
+            # beside HF weights the optimizer state goes into a DCP sub-directory (named, reshardable, one
+            # writer per distinct shard under every parallel layout)
+            from ..utils.dcp_state import save_engine
+
+            save_engine(self, os.path.join(meta.path, "optimizer"), with_optim=True, with_model=False,
+                        process_group=self._all_cpu_group)
         if dist.is_initialized() and self.world_size > 1:
             dist.barrier(group=self._cpu_group)
+
+    def _ckpt_executor(self):
+        from concurrent.futures import ThreadPoolExecutor
+
+        if getattr(self, "_ckpt_pool", None) is None:
+            self._ckpt_pool = ThreadPoolExecutor(max_workers=1, thread_name_prefix="dcp-save")
+        return self._ckpt_pool
+
+    def wait_for_checkpoint(self):
+        """Blocks until a checkpoint write that runs in the background has finished (and re-raises its error)."""
+        f = getattr(self, "_pending_ckpt", None)
+        self._pending_ckpt = None
+        if f is not None:
+            f.result()
 
     def load(self, meta: SaveLoadMeta):
         from ..utils.hf_io import load_hf_weights
@@ -814,18 +860,22 @@ class B200TrainEngine(TrainEngine):
             else:
                 load_hf_weights(self.model, meta.path)
         elif meta.weight_format == "dcp":
-            for r in range(self.world_size):
-                f = os.path.join(meta.path, f"model_world_size_{self.world_size}_rank_{r}.pt")
-                sd = torch.load(f, map_location="cpu", weights_only=False)
-                o = sd["offset"]
-                self.flat.flat[o:o + sd["flat"].numel()].copy_(sd["flat"])
+            from ..utils.dcp_state import load_engine
+
+            self.wait_for_checkpoint()
+            load_engine(self, meta.path, with_optim=meta.with_optim, process_group=self._all_cpu_group)
+            return
         else:
             raise ValueError(f"unknown weight format {meta.weight_format}")
         if self.optimizer is not None:
             self.optimizer.refresh_master()
+            if self.optimizer.partner is not None:
+                self.optimizer.partner.refresh_master()
             if meta.with_optim:
-                f = os.path.join(meta.path, f"optim_world_size_{self.world_size}_rank_{self.dp_rank}.pt")
-                self.optimizer.load_state_dict(torch.load(f, map_location=self.device, weights_only=False))
+                from ..utils.dcp_state import load_engine
+
+                load_engine(self, os.path.join(meta.path, "optimizer"), with_optim=True, with_model=False,
+                            process_group=self._all_cpu_group)
 
     # ----------------------------------------------------------------- offload
     def offload(self):
@@ -853,6 +903,3 @@ class B200TrainEngine(TrainEngine):
     def export_stats(self) -> dict[str, float]:
         return stats_tracker.export_all(reduce_group=self._cpu_group)
 
-
-class B200PPOActorEngine(B200TrainEngine):
-    pass

@@ -16,6 +16,8 @@ HF checkpoint names are the interchange format (``to_hf`` / ``from_hf``).
 
 from __future__ import annotations
 
+import re
+
 from typing import Iterable, Iterator
 
 import torch
@@ -700,10 +702,26 @@ class QwenModel(nn.Module):
     def hf_name_map(self) -> dict[str, torch.Tensor]:
         return dict(self.to_hf_local())
 
+    def owned_by_other_stage(self, name: str) -> bool:
+        """True for a checkpoint tensor that belongs to another pipeline stage: a block outside this
+        stage's range, the embedding when this stage has none, the final norm / head off the last stage."""
+        if self.layer_end - self.layer_start == self.cfg.num_hidden_layers:
+            return False
+        m = re.match(r"model\.layers\.(\d+)\.", name)
+        if m is not None:
+            return not (self.layer_start <= int(m.group(1)) < self.layer_end)
+        if name == "model.embed_tokens.weight":
+            return self.embed is None
+        if name in ("model.norm.weight", "lm_head.weight", "score.weight"):
+            return not self.last_stage
+        return False
+
     @torch.no_grad()
     def load_hf(self, tensors: Iterable[tuple[str, torch.Tensor]], strict: bool = True):
         """Copies HF-named tensors into the fused parameters."""
         dst = self.hf_name_map()
+        if self.embed is not None and not self.first_stage:
+            dst["model.embed_tokens.weight"] = self.embed  # the last stage's copy of a tied embedding
         seen = set()
         for name, t in tensors:
             if name.startswith("model.language_model."):  # decoder of a composite checkpoint
@@ -716,6 +734,8 @@ class QwenModel(nn.Module):
             if name not in dst:
                 if ".mlp.experts." in name and self.pctx is not None and self.pctx.ep_size > 1:
                     continue  # an expert that lives on another expert-parallel rank
+                if self.owned_by_other_stage(name):
+                    continue
                 if strict:
                     raise KeyError(f"unexpected tensor {name}")
                 continue

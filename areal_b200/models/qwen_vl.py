@@ -543,6 +543,15 @@ class QwenVLModel(QwenModel):
         # the tower is replicated over tensor-parallel ranks; decoder names keep their rule under the prefix
         return None if hf_name.startswith(self._VIS) else super()._tp_dim(hf_name)
 
+    def _other_stage(self, name: str) -> bool:
+        """A checkpoint tensor of another pipeline stage: decoder tensors by the text model's rule, the vision
+        tower when this stage has none (it lives on the first stage)."""
+        if name.startswith(self._VIS):
+            return self.visual is None
+        if name.startswith(self._LM):
+            return self.owned_by_other_stage("model." + name[len(self._LM):])
+        return self.owned_by_other_stage(name)
+
     @torch.no_grad()
     def load_hf(self, tensors: Iterable[tuple[str, torch.Tensor]], strict: bool = True):
         """Accepts the current layout (``model.language_model.*`` / ``model.visual.*``) and the older one
@@ -556,12 +565,18 @@ class QwenVLModel(QwenModel):
                 yield name, t
 
         dst = dict(self.to_hf_local())
+        if self.embed is not None and not self.first_stage:
+            dst[self._LM + "embed_tokens.weight"] = self.embed  # the last stage's copy of a tied embedding
         seen = set()
         for name, t in rename():
             if name == "lm_head.weight" and self.lm_head is None and self.score is None:
                 seen.add(name)
                 continue
             if name not in dst:
+                if ".mlp.experts." in name and self.pctx is not None and self.pctx.ep_size > 1:
+                    continue  # an expert that lives on another expert-parallel rank
+                if self._other_stage(name):
+                    continue
                 if strict:
                     raise KeyError(f"unexpected tensor {name}")
                 continue

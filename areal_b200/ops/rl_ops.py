@@ -49,13 +49,22 @@ class _PPOLossFused(torch.autograd.Function):
 
 
 def ppo_loss_fused(logp, prox, behav, adv, mask, *, eps_clip, eps_clip_higher=None, c_clip=None,
-                   behav_cap=None, use_decoupled=True, denom=None):
+                   behav_cap=None, use_decoupled=True, behav_weight=None, denom=None):
     """Token-level decoupled PPO loss. Returns ``(loss, stats[6])`` where stats =
-    [loss, #clipped, #dual-clipped, sum importance weight, sum |ratio-1|, #dropped]."""
+    [loss, #clipped, #dual-clipped, sum importance weight, sum |ratio-1|, #dropped].
+
+    ``use_decoupled``: the ratio is taken against ``prox`` (else against ``behav``). ``behav_weight``: the
+    loss is also multiplied by ``exp(prox - behav)``, dropped above ``behav_cap`` — what token-level
+    ratio rejection sampling with action ``mask`` does; the default applies it exactly when a cap is given
+    (without rejection sampling the reference's loss carries no such weight:
+    areal/utils/functional/functional.py:429-559)."""
     if denom is None:
         denom = mask.count_nonzero()
+    if behav_weight is None:
+        behav_weight = behav_cap is not None
+    flags = int(bool(use_decoupled)) | (2 if behav_weight else 0)
     return _PPOLossFused.apply(logp, prox, behav, adv, mask, eps_clip, eps_clip_higher, c_clip,
-                               behav_cap, use_decoupled, float(denom))
+                               behav_cap, flags, float(denom))
 
 
 def group_norm(values: torch.Tensor, group_size: int, *, mean_group=True, std_group=True,

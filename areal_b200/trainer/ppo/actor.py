@@ -225,7 +225,7 @@ def grpo_loss_fn(logprobs: torch.Tensor, entropy: torch.Tensor | None, input_dat
             loss, st = ppo_loss_fused(logprobs.float(), prox, old_logp, adv, loss_mask,
                                       eps_clip=cfg.eps_clip, eps_clip_higher=cfg.eps_clip_higher,
                                       c_clip=cfg.c_clip, behav_cap=(rs.upper if rs is not None else None),
-                                      use_decoupled=decoupled)
+                                      use_decoupled=decoupled, behav_weight=rs is not None)
             _record_fused_stats(st, loss_mask, entropy)
             return loss
         loss, stat = Fn.ppo_actor_loss_fn(logprobs.float(), prox, old_logp, adv, cfg.eps_clip, loss_mask,

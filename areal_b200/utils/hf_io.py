@@ -20,9 +20,36 @@ from safetensors.torch import save_file
 MAX_SHARD_BYTES = 5 * (1 << 30)
 
 
-def iter_hf_tensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
+def weight_files(path: str) -> list[Path]:
+    """The safetensors files that hold the model's weights: those the index names when there is one, else
+    every ``*.safetensors`` file except adapter files (``adapter_model.safetensors`` of a LoRA checkpoint
+    sits beside the merged model and is not part of it)."""
     p = Path(path)
-    files = sorted(p.glob("*.safetensors"))
+    idx = p / "model.safetensors.index.json"
+    if idx.exists():
+        with open(idx) as f:
+            names = sorted(set(json.load(f).get("weight_map", {}).values()))
+        files = [p / n for n in names if (p / n).exists()]
+        if files:
+            return files
+    return [f for f in sorted(p.glob("*.safetensors")) if not f.name.startswith("adapter_")]
+
+
+def remove_weight_files(path: str, tag: str | None = None):
+    """Deletes earlier weight files of a checkpoint directory before it is written again, so that files
+    of another sharding do not linger (``tag``: only the files of that writer)."""
+    p = Path(path)
+    if not p.is_dir():
+        return
+    pat = f"model-{tag}-*.safetensors" if tag else "model*.safetensors"
+    for f in p.glob(pat):
+        f.unlink(missing_ok=True)
+    if not tag:
+        (p / "model.safetensors.index.json").unlink(missing_ok=True)
+
+
+def iter_hf_tensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
+    files = weight_files(path)
     if not files:
         raise FileNotFoundError(f"no .safetensors files under {path}")
     for f in files:
@@ -68,6 +95,8 @@ def save_hf_checkpoint(model, model_config, path: str, tokenizer=None, max_shard
             pass
         return
     os.makedirs(path, exist_ok=True)
+    if not file_tag:
+        remove_weight_files(path)  # several writers: the caller clears the directory once, before any of them
     shards: list[dict[str, torch.Tensor]] = [{}]
     size = 0
     index: dict[str, str] = {}

@@ -4,8 +4,11 @@
 (``recover_checkpoint/``) and a ``RecoverInfo`` record (step position, saver /
 evaluator / stats-logger / dataloader state) under ``recover_info/``; ``load``
 restores them, re-pushes the weights to the rollout engine and tells the
-staleness manager which version it restarts from. A run recovers only with the
-same world size (areal/utils/recover.py:41-445 in the reference).
+staleness manager which version it restarts from. The checkpoint is a
+``torch.distributed.checkpoint`` directory of named tensors, so a run may resume
+at another data-parallel size or parallel layout; generator state is restored
+only when the world size is unchanged (areal/utils/recover.py:41-445 in the
+reference).
 """
 
 from __future__ import annotations

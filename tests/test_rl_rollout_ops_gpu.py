@@ -10,7 +10,7 @@ from areal_b200.ops import _lib, rl_ops, rollout_ops
 pytestmark = pytest.mark.gpu
 
 
-def _ppo_ref(logp, prox, behav, adv, mask, eps, eps_hi, c_clip, cap, decoupled):
+def _ppo_ref(logp, prox, behav, adv, mask, eps, eps_hi, c_clip, cap, decoupled, weight=None):
     px = prox if decoupled else behav
     ratio = torch.exp(logp - px)
     clipped = torch.clamp(ratio, 1 - eps, 1 + (eps if eps_hi is None else eps_hi))
@@ -18,7 +18,7 @@ def _ppo_ref(logp, prox, behav, adv, mask, eps, eps_hi, c_clip, cap, decoupled):
     if c_clip is not None:
         l = torch.min(l, torch.sign(adv) * c_clip * adv)
     m = mask.bool()
-    if decoupled:
+    if cap is not None if weight is None else weight:
         w = torch.exp(px - behav).detach()
         if cap is not None:
             w = torch.where(w > cap, torch.zeros_like(w), w)
@@ -26,21 +26,48 @@ def _ppo_ref(logp, prox, behav, adv, mask, eps, eps_hi, c_clip, cap, decoupled):
     return torch.where(m, l, torch.zeros_like(l)).sum() / max(int(m.sum()), 1)
 
 
-@pytest.mark.parametrize("decoupled,c_clip,cap,eps_hi", [(True, None, 5.0, None), (False, 3.0, None, 0.28),
-                                                          (True, 2.0, None, None)])
-def test_ppo_loss(decoupled, c_clip, cap, eps_hi):
+def _ppo_inputs(n=10007):
     torch.manual_seed(0)
-    n = 10007
     logp = (-torch.rand(n, device="cuda") * 3).requires_grad_()
     prox = logp.detach() + 0.3 * torch.randn(n, device="cuda")
     behav = prox + 0.8 * torch.randn(n, device="cuda")
     adv = torch.randn(n, device="cuda")
     mask = torch.rand(n, device="cuda") > 0.3
+    return logp, prox, behav, adv, mask
+
+
+@pytest.mark.parametrize("decoupled,c_clip,cap,eps_hi,weight", [
+    (True, None, 5.0, None, None), (False, 3.0, None, 0.28, None), (True, 2.0, None, None, None),
+    (True, None, None, None, True)])
+def test_ppo_loss(decoupled, c_clip, cap, eps_hi, weight):
+    logp, prox, behav, adv, mask = _ppo_inputs()
     loss, stats = rl_ops.ppo_loss_fused(logp, prox, behav, adv, mask, eps_clip=0.2, eps_clip_higher=eps_hi,
-                                        c_clip=c_clip, behav_cap=cap, use_decoupled=decoupled)
+                                        c_clip=c_clip, behav_cap=cap, use_decoupled=decoupled,
+                                        behav_weight=weight)
     loss.backward()
     lr = logp.detach().clone().requires_grad_()
-    ref = _ppo_ref(lr, prox, behav, adv, mask, 0.2, eps_hi, c_clip, cap, decoupled)
+    ref = _ppo_ref(lr, prox, behav, adv, mask, 0.2, eps_hi, c_clip, cap, decoupled, weight)
+    ref.backward()
+    torch.testing.assert_close(loss, ref, atol=1e-5, rtol=1e-4)
+    torch.testing.assert_close(logp.grad, lr.grad, atol=1e-7, rtol=1e-3)
+
+
+@pytest.mark.parametrize("with_rs", [False, True])
+def test_ppo_loss_matches_the_functional_form(with_rs):
+    """The fused kernel and ``functional.ppo_actor_loss_fn`` (the CPU path and the numerics specification)
+    compute the same objective with and without rejection sampling: the behaviour importance weight is
+    part of the loss only when rejection sampling is configured."""
+    from areal_b200.api.cli_args import RejectionSamplingConfig
+    from areal_b200.utils import functional as Fn
+
+    logp, prox, behav, adv, mask = _ppo_inputs(4099)
+    rs = RejectionSamplingConfig(level="token", action="mask", metric="ratio", upper=5.0) if with_rs else None
+    loss, _ = rl_ops.ppo_loss_fused(logp, prox, behav, adv, mask, eps_clip=0.2, c_clip=None,
+                                    behav_cap=rs.upper if rs else None, use_decoupled=True,
+                                    behav_weight=rs is not None)
+    loss.backward()
+    lr = logp.detach().clone().requires_grad_()
+    ref, _ = Fn.ppo_actor_loss_fn(lr, prox, behav, adv, 0.2, mask, rejection_sampling=rs)
     ref.backward()
     torch.testing.assert_close(loss, ref, atol=1e-5, rtol=1e-4)
     torch.testing.assert_close(logp.grad, lr.grad, atol=1e-7, rtol=1e-3)
