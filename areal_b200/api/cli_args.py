@@ -458,6 +458,9 @@ class NativeRolloutConfig:
     num_kv_blocks: int | None = None
     # samples of one prompt prefill once and read the same (read-only) prompt pages
     prompt_sharing: bool = True
+    # graph-captured decode steps draw the next token inside the LM-head GEMM (Gumbel-max in the epilogue); off:
+    # logits are written out and the stand-alone sampler runs (always the case with top-k / top-p requests)
+    fused_sampling: bool = True
 
 
 @dataclass

@@ -181,6 +181,157 @@ struct LmDlogitsEpi {
   }
 };
 
+
+// ------------------------------------------------------------------ fused sampling (rollout decode)
+//
+// The decode step's LM head draws the next token inside the GEMM epilogue, so the [B, V] logits are
+// never written either. Sampling from softmax(x / temperature) uses the Gumbel-max identity:
+// argmax_i (x_i / T + g_i) with g_i = -log(-log u_i) i.i.d. is a draw from the softmax. Each
+// (row, vocab split) emits its running max, its sum of exponentials, and the best perturbed score with
+// the index and the (scaled) logit that achieved it; the combine kernel picks the best split and
+// returns log p(token) = x_token / T - logZ under the unfiltered distribution. temperature <= 0 means
+// greedy (no noise, logprob under T = 1). The noise comes from Philox4x32-7 keyed by a seed, with the
+// counter (column / 4, row, step): the step counter lives in device memory and the combine kernel
+// advances it, so a captured CUDA graph draws fresh noise on every replay.
+__device__ __forceinline__ uint4 philox4x32_7(uint4 c, uint2 k) {
+#pragma unroll
+  for (int i = 0; i < 7; ++i) {
+    const uint32_t hi0 = __umulhi(0xD2511F53u, c.x), lo0 = 0xD2511F53u * c.x;
+    const uint32_t hi1 = __umulhi(0xCD9E8D57u, c.z), lo1 = 0xCD9E8D57u * c.z;
+    c = make_uint4(hi1 ^ c.y ^ k.x, lo1, hi0 ^ c.w ^ k.y, lo0);
+    k.x += 0x9E3779B9u;
+    k.y += 0xBB67AE85u;
+  }
+  return c;
+}
+
+// Standard Gumbel variate from 32 random bits. w is uniform on a 2^-23 grid strictly inside (0, 1);
+// E = -log(1 - w) is Exp(1): by its series where w is small (the approximate log loses all relative
+// accuracy next to 1), by the fast log elsewhere.
+__device__ __forceinline__ float gumbel_from_bits(uint32_t r) {
+  const float w = (static_cast<float>(r >> 9) + 0.5f) * 1.1920928955078125e-07f;
+  const float e_small = w * (1.f + w * (0.5f + w * (0.33333334f + 0.25f * w)));
+  const float e = (w < 0.015625f) ? e_small : -__logf(1.f - w);
+  return -__logf(e);
+}
+
+struct LmSampleRec {
+  float m, l, best, bx;
+};
+
+struct LmSampleEpi {
+  LmSampleRec* partials;      // [nsplit, T]
+  int* part_idx;              // [nsplit, T]
+  const float* temperature;   // [T]
+  const unsigned long long* rng;  // [0] seed, [1] step counter
+  int T, N;
+  int nb_per, nsplit;
+  struct State {
+    float m, l, best, bx, inv_t;
+    int bi;
+    uint32_t noisy, k0, k1, c2, c3;
+  };
+  __device__ __forceinline__ bool tile(int cta, int ncta, int it, int tiles_m, int tiles_n,
+                                       int& m_blk, int& n_blk) const {
+    const int item_local = it / nb_per;
+    const int j = it - item_local * nb_per;
+    const long long w = static_cast<long long>(item_local) * ncta + cta;
+    if (w >= static_cast<long long>(tiles_m) * nsplit) return false;
+    m_blk = static_cast<int>(w % tiles_m);
+    n_blk = static_cast<int>(w / tiles_m) * nb_per + j;
+    return true;  // blocks past the last column of a short final split load zeros and are skipped by chunk()
+  }
+  __device__ __forceinline__ bool gate(int, int, volatile int*, int*) const { return true; }
+  __device__ __forceinline__ void begin(State& s, int, int n_blk, int row) const {
+    if (n_blk % nb_per == 0) {
+      s.m = -INFINITY;
+      s.l = 0.f;
+      s.best = -INFINITY;
+      s.bx = 0.f;
+      s.bi = 0x7fffffff;
+      const float t = (row < T) ? temperature[row] : 1.f;
+      s.noisy = (t > 0.f) ? 1u : 0u;
+      s.inv_t = s.noisy ? 1.f / t : 1.f;
+      const unsigned long long seed = rng[0], step = rng[1];
+      s.k0 = static_cast<uint32_t>(seed);
+      s.k1 = static_cast<uint32_t>(seed >> 32);
+      s.c2 = static_cast<uint32_t>(step);
+      s.c3 = static_cast<uint32_t>(step >> 32);
+    }
+  }
+  __device__ __forceinline__ void chunk(State& s, int row, int col0, const float (&v)[32]) const {
+    if (row >= T || col0 >= N) return;
+    float x[32];
+    float cm = -INFINITY;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) {
+      x[i] = (col0 + i < N) ? v[i] * s.inv_t : -INFINITY;
+      cm = fmaxf(cm, x[i]);
+    }
+    const float m_new = fmaxf(s.m, cm);
+    const float sc = (s.m == -INFINITY) ? 0.f : __expf(s.m - m_new);
+    float l = 0.f;
+#pragma unroll
+    for (int i = 0; i < 32; ++i) l += __expf(x[i] - m_new);  // exp(-inf) = 0 for masked columns
+    s.l = s.l * sc + l;
+    s.m = m_new;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      uint32_t r[4] = {0u, 0u, 0u, 0u};
+      if (s.noisy) {
+        const uint4 q = philox4x32_7(make_uint4(static_cast<uint32_t>((col0 >> 2) + j), static_cast<uint32_t>(row),
+                                                s.c2, s.c3), make_uint2(s.k0, s.k1));
+        r[0] = q.x; r[1] = q.y; r[2] = q.z; r[3] = q.w;
+      }
+#pragma unroll
+      for (int t = 0; t < 4; ++t) {
+        const int i = 4 * j + t;
+        const float score = s.noisy ? x[i] + gumbel_from_bits(r[t]) : x[i];
+        if (score > s.best) {  // strict: the smallest index wins a tie
+          s.best = score;
+          s.bx = x[i];
+          s.bi = col0 + i;
+        }
+      }
+    }
+  }
+  __device__ __forceinline__ void end(State& s, int, int n_blk, int row) const {
+    if ((n_blk + 1) % nb_per == 0 && row < T) {
+      const long long at = static_cast<long long>(n_blk / nb_per) * T + row;
+      partials[at] = LmSampleRec{s.m, s.l, s.best, s.bx};
+      part_idx[at] = s.bi;
+    }
+  }
+};
+
+__global__ void lm_sample_combine_kernel(const LmSampleRec* __restrict__ partials, const int* __restrict__ part_idx,
+                                         int nparts, int T, int* __restrict__ tokens, float* __restrict__ logprobs,
+                                         unsigned long long* rng) {
+  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  if (row < T) {
+    float M = -INFINITY, best = -INFINITY, bx = 0.f;
+    int bi = 0;
+    for (int p = 0; p < nparts; ++p) {
+      const LmSampleRec r = partials[static_cast<long long>(p) * T + row];
+      M = fmaxf(M, r.m);
+      if (r.best > best) {
+        best = r.best;
+        bx = r.bx;
+        bi = part_idx[static_cast<long long>(p) * T + row];
+      }
+    }
+    float L = 0.f;
+    for (int p = 0; p < nparts; ++p) {
+      const LmSampleRec r = partials[static_cast<long long>(p) * T + row];
+      L += (r.m == -INFINITY) ? 0.f : r.l * __expf(r.m - M);
+    }
+    tokens[row] = bi;
+    logprobs[row] = bx - (M + logf(L));
+  }
+  // every block of the GEMM that read the counter has finished (stream order): advance it for the next step
+  if (blockIdx.x == 0 && threadIdx.x == 0) rng[1] += 1ull;
+}
+
 template <class Epi>
 static int launch_lm(const void* X, const void* W, int T, int V, int H, long long ldx,
                      long long ldw, const Epi& epi, long long work_items, cudaStream_t stream) {
@@ -256,6 +407,54 @@ int b200_lm_head_stats_peers(const void* X, const void* W, const int* labels, vo
   for (int p = 0; p < n_peers; ++p) epi.peers[p] = reinterpret_cast<float*>(peer_partials[p]);
   return launch_lm(X, W, T, V, H, ldx, ldw, epi, static_cast<long long>(tiles_m) * nsplit, stream);
 }
+
+// Vocab splits of the fused sampling head for (B, V): the split length (in 256-column blocks) that
+// minimises the busiest CTA's number of tiles; ties go to the longer split (fewer partial records).
+int b200_lm_head_sample_nb_per(int B, int V) {
+  const int tiles_m = (B + 127) / 128;
+  const int tiles_n = (V + 255) / 256;
+  const int sms = b200::sm_count();
+  long long best_cost = -1;
+  int best = 1;
+  for (int nb = 1; nb <= tiles_n && nb <= 64; ++nb) {
+    const long long nsplit = (tiles_n + nb - 1) / nb;
+    const long long items = nsplit * tiles_m;
+    const long long cost = ((items + sms - 1) / sms) * nb;
+    if (best_cost < 0 || cost <= best_cost) {
+      best_cost = cost;
+      best = nb;
+    }
+  }
+  return best;
+}
+
+int b200_lm_head_sample_nsplit(int B, int V) {
+  const int tiles_n = (V + 255) / 256;
+  const int nb = b200_lm_head_sample_nb_per(B, V);
+  return (tiles_n + nb - 1) / nb;
+}
+
+// Next-token sampling fused into the LM head: tokens[b] ~ softmax(X[b] W^T / temperature[b]) (argmax when
+// temperature[b] <= 0) and logprobs[b] = log of that probability (under T = 1 for greedy rows).
+// partials: 16 * nsplit * B bytes, part_idx: 4 * nsplit * B bytes with nsplit = b200_lm_head_sample_nsplit(B, V);
+// rng: two 64-bit words on the device (seed, step counter), the counter is advanced by one.
+int b200_lm_head_sample(const void* X, const void* W, const float* temperature, void* partials, int* part_idx,
+                        unsigned long long* rng, int* tokens, float* logprobs, int B, int V, int H,
+                        long long ldx, long long ldw, cudaStream_t stream) {
+  using namespace b200;
+  if (B == 0 || V == 0) return 0;
+  const int tiles_m = (B + 127) / 128;
+  const int nb_per = b200_lm_head_sample_nb_per(B, V);
+  const int nsplit = b200_lm_head_sample_nsplit(B, V);
+  LmSampleEpi epi{reinterpret_cast<LmSampleRec*>(partials), part_idx, temperature, rng, B, V, nb_per, nsplit};
+  int rc = launch_lm(X, W, B, V, H, ldx, ldw, epi, static_cast<long long>(tiles_m) * nsplit, stream);
+  if (rc) return rc;
+  lm_sample_combine_kernel<<<(B + 127) / 128, 128, 0, stream>>>(reinterpret_cast<const LmSampleRec*>(partials),
+                                                                part_idx, nsplit, B, tokens, logprobs, rng);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
 
 int b200_lm_head_combine(const float* partials, int nparts, int T, float* logp, float* entropy,
                          float* logz, float* ey, cudaStream_t stream) {

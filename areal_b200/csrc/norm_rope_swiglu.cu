@@ -608,9 +608,11 @@ extern "C" int b200_rmsnorm_bwd_static(const void* dy, const void* x, const void
   const size_t smem = static_cast<size_t>(wpb) * H * sizeof(float);
   int rc = dispatch_nv(H, [&](auto nv) {
     auto k = rmsnorm_bwd_kernel<decltype(nv)::value>;
-    if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (smem > 48 * 1024)
+      B200_CHECK(cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem));
     k<<<grid, wpb * 32, smem, stream>>>((const __nv_bfloat16*)dy, (const __nv_bfloat16*)x, (const __nv_bfloat16*)w,
                                         rstd, (const __nv_bfloat16*)dres, (__nv_bfloat16*)dx, scratch, T, H);
+    B200_CHECK(cudaGetLastError());
     return 0;
   });
   if (rc) return rc;

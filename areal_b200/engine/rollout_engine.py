@@ -42,6 +42,7 @@ from ..models.config import PRESETS, ModelConfig
 from ..models.qwen import build_model
 from ..ops import _lib
 from ..ops.attention import VarlenMeta
+from ..ops.lm_head import lm_head_sample, new_sampling_rng
 from ..ops.rollout_ops import sample
 from ..utils import logging
 from .flat_params import FlatParams
@@ -156,6 +157,10 @@ class _DecodeGraphs:
         self.bt = torch.zeros((maxb, mb), dtype=torch.int32, device=dev)
         self.temp = torch.ones(maxb, dtype=torch.float32, device=dev)
         self.u = torch.zeros(maxb, dtype=torch.float32, device=dev)
+        pctx = getattr(engine.model, "pctx", None)
+        self.fused_sampling = bool(getattr(engine.ncfg, "fused_sampling", True)) and \
+            (pctx is None or pctx.tp_size == 1) and engine.model_config.hidden_size % 8 == 0
+        self.rng_state = new_sampling_rng(engine.ncfg.seed, dev)
         pin = dict(pin_memory=True)
         self.h_pad_slots = torch.full((maxb,), -1, dtype=torch.int64, **pin)
         self.h_pad_lens = torch.zeros(maxb, dtype=torch.int32, **pin)
@@ -171,6 +176,9 @@ class _DecodeGraphs:
         e = self.e
         hidden = e.model.decode(self.ids[:b], self.pos[:b], e.kv_caches, self.bt[:b], self.seq_lens[:b],
                                 self.slots[:b], max_seq_len=e.ncfg.context_length)
+        if self.fused_sampling:
+            # the token is drawn in the LM-head GEMM's epilogue: no [B, V] logits, no separate sampler pass
+            return lm_head_sample(hidden, e.model.output_weight(), self.temp[:b], self.rng_state)
         logits = e.model.logits(hidden, out_dtype=torch.float32)
         return sample(logits, self.temp[:b], None, None, self.u[:b])
 
@@ -209,7 +217,8 @@ class _DecodeGraphs:
             self.h_temp[:n] = torch.tensor(temps, dtype=torch.float32)
             self.temp[:n].copy_(self.h_temp[:n], non_blocking=True)
             self._last_temps = temps
-        self.u[:b].uniform_(generator=rng)
+        if not self.fused_sampling:
+            self.u[:b].uniform_(generator=rng)
         self.prev_n = n
         g, toks, lps = self.graphs[b]
         g.replay()
@@ -256,7 +265,11 @@ class NativeRolloutEngine(InferenceEngine):
         self._idle.set()
         self._step_lock = threading.Lock()
         # host seconds spent in the phases of decode steps (plan / parameter lookup / stage+replay+sync / commit)
-        self._phase_s = {"plan": 0.0, "params": 0.0, "run": 0.0, "commit_deliver": 0.0, "stage": 0.0, "wait": 0.0}
+        self._phase_s = {"plan": 0.0, "params": 0.0, "run": 0.0, "commit_deliver": 0.0, "stage": 0.0, "wait": 0.0,
+                         "prefill": 0.0, "paused": 0.0, "idle": 0.0}
+        self._prefill_tokens = 0     # tokens that went through prefill steps
+        self._reprefill_tokens = 0   # of those, context re-computed for requests interrupted by a weight update
+        self._t_start = time.perf_counter()
 
     # ------------------------------------------------------------------ setup
     def initialize(self, engine_id: str | None = None, train_data_parallel_size: int | None = None,
@@ -393,7 +406,9 @@ class NativeRolloutEngine(InferenceEngine):
             try:
                 if self._paused.is_set():
                     self._idle.set()
+                    tp = time.perf_counter()
                     time.sleep(0.0005)
+                    self._phase_s["paused"] += time.perf_counter() - tp
                     continue
                 self._idle.clear()
                 with self._step_lock:
@@ -406,8 +421,10 @@ class NativeRolloutEngine(InferenceEngine):
                         worked = self._step()
                 if not worked:
                     self._idle.set()
+                    tp = time.perf_counter()
                     with self._wake:
                         self._wake.wait(timeout=0.002)
+                    self._phase_s["idle"] += time.perf_counter() - tp
             except BaseException as e:  # surface engine failures to every waiter
                 logger.error(f"rollout engine loop failed: {type(e).__name__}: {e}")
                 self._step_error = e
@@ -449,6 +466,7 @@ class NativeRolloutEngine(InferenceEngine):
                 tm["run"] += t2 - t1
                 tm["commit_deliver"] += t3 - t2
                 return True
+        t_slow = time.perf_counter()
         ids = torch.from_numpy(s.tokens[:T].copy()).to(dev, non_blocking=True)
         pos = torch.from_numpy(s.positions[:T].copy()).to(dev, non_blocking=True)
         slots = torch.from_numpy(s.slots[:T].copy()).to(dev, non_blocking=True)
@@ -492,6 +510,11 @@ class NativeRolloutEngine(InferenceEngine):
         self._gen_tokens += n
         self._steps += 1
         self._deliver()
+        if kind == 1:
+            self._prefill_tokens += T
+            self._phase_s["prefill"] += time.perf_counter() - t_slow
+        else:
+            self._phase_s["run"] += time.perf_counter() - t_slow  # an eager decode step (no graph for this batch)
         return True
 
     def _vision_prefill_inputs(self, ids: torch.Tensor, seq_ids: list[int], cu: np.ndarray) -> dict[str, Any]:
@@ -654,6 +677,8 @@ class NativeRolloutEngine(InferenceEngine):
             while self._paused.is_set():
                 await asyncio.sleep(0.001)
             version = self._version
+            if out_tokens:
+                self._reprefill_tokens += len(req.input_ids) + len(out_tokens)
             reason, toks, lps = await self._generate_once(list(req.input_ids) + out_tokens, g,
                                                           max_new - len(out_tokens), images)
             if toks and ttft == float("inf"):
@@ -790,6 +815,9 @@ class NativeRolloutEngine(InferenceEngine):
         st = {f"rollout/{k}": float(v) for k, v in self.sched.stats().items()}
         st["rollout/generated_tokens"] = float(self._gen_tokens)
         st["rollout/engine_steps"] = float(self._steps)
+        st["rollout/prefill_tokens"] = float(self._prefill_tokens)
+        st["rollout/reprefill_tokens"] = float(self._reprefill_tokens)
+        st["rollout/wall_s"] = time.perf_counter() - self._t_start
         for k, v in self._phase_s.items():
             st[f"rollout/host_s/{k}"] = v
         if self._executor is not None:

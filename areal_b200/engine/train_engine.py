@@ -705,7 +705,9 @@ class B200TrainEngine(TrainEngine):
         if meta.type == "disk":
             # one directory per version (`weight_update_v{N}`), the previous one removed once the servers
             # have loaded the new weights
-            vdir = os.path.join(meta.path, f"weight_update_v{meta.version}") if meta.version is not None else meta.path
+            vdir = meta.path
+            if meta.version is not None and not os.path.basename(vdir.rstrip("/")).startswith("weight_update_v"):
+                vdir = os.path.join(vdir, f"weight_update_v{meta.version}")  # `with_version` already names it
             self.save(SaveLoadMeta(path=vdir, weight_format="hf", with_optim=False))
             if dist.is_initialized() and self.world_size > 1:
                 dist.barrier(group=self._cpu_group)

@@ -122,8 +122,10 @@ class RolloutServer:
         while not self._stop.is_set() and (n_steps is None or step < n_steps):
             batch = self.engine.prepare_batch(dataloader, workflow, workflow_kwargs, group_size=group_size)
             parts = split_batch_by_tokens(batch, len(self.trainers), group_size)
+            stats = self.engine.export_stats() if hasattr(self.engine, "export_stats") else {}
             for t, part in zip(self.trainers, parts):
-                dist.send_object_list([part], dst=t, group=self.topo.data_group)
+                # the engine's counters ride along, so the trainer side can report per-role rates
+                dist.send_object_list([part, stats], dst=t, group=self.topo.data_group)
             step += 1
 
     def wait_stop(self, timeout: float | None = None):
@@ -161,14 +163,16 @@ class RemoteRolloutClient(InferenceEngine):
         self._version = 0
         self._table = (ctypes.c_void_p * max(len(weight_ptrs), 1))(*weight_ptrs) if weight_ptrs else None
         self.last_pause_latency = 0.0
+        self.rollout_stats: dict[int, dict[str, float]] = {}  # rollout rank -> its engine's latest counters
 
     def prepare_batch(self, dataloader=None, workflow=None, workflow_kwargs=None, should_accept_fn=None,
                       group_size=1, dynamic_bs=False):
         parts = []
         for g in self.rollouts:
-            msg = [None]
+            msg = [None, None]
             dist.recv_object_list(msg, src=g, group=self.topo.data_group)
             parts.append(msg[0])
+            self.rollout_stats[g] = msg[1] or {}
         return parts[0] if len(parts) == 1 else concat_padded_tensors(parts)
 
     rollout_batch = prepare_batch

@@ -24,7 +24,7 @@ import torch
 import torch.nn as nn
 import torch.nn.functional as F
 
-from ..ops import fused
+from ..ops import _lib, fused
 from ..ops.attention import VarlenMeta, varlen_attention
 from ..ops.gemm import gemm, linear, linear_rmsnorm
 from ..ops.rollout_ops import kv_cache_write, paged_decode
@@ -214,11 +214,15 @@ class MoEMLP(nn.Module):
 
     def _shared(self, x):
         y = linear(fused.swiglu(linear(x, self.shared_gate_up)), self.shared_down)
+        if x.is_cuda:
+            _lib.count_fallback("moe.shared_expert_gate[F.linear]")
         g = torch.sigmoid(F.linear(x.float(), self.shared_gate.float()))
         return (y.float() * g).to(x.dtype)
 
     def route(self, x):
         cfg = self.cfg
+        if x.is_cuda:
+            _lib.count_fallback("moe.router[F.linear fp32]")
         logits = F.linear(x.float(), self.router.float())
         plain = cfg.moe_score_func == "softmax" and cfg.moe_route_scale == 1.0 and self.expert_bias is None
         if not plain:
@@ -488,6 +492,8 @@ class QwenModel(nn.Module):
         return F.linear(hidden, w).to(out_dtype)
 
     def values(self, hidden):
+        if hidden.is_cuda:
+            _lib.count_fallback("critic.value_head[F.linear fp32]")
         return F.linear(hidden.float(), self.score.float()).squeeze(-1)
 
     # -------------------------------------------------- rollout (paged cache)
@@ -504,7 +510,7 @@ class QwenModel(nn.Module):
             return hybrid_prefill(self, input_ids, position_ids, meta, kv_caches, slot_mapping, hybrid_state, state_slots)
         cos, sin = rope if rope is not None else self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
-        x = embeds if embeds is not None else F.embedding(input_ids.long(), self.embed)
+        x = embeds if embeds is not None else fused.embedding(input_ids, self.embed)
         res = None
         for i, layer in enumerate(self.layers):
             if res is None:
@@ -534,7 +540,7 @@ class QwenModel(nn.Module):
                                  hybrid_state, state_slots, max_seq_len)
         cos, sin = self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
-        x = F.embedding(input_ids.long(), self.embed)
+        x = fused.embedding(input_ids, self.embed)
         res = None
         y = None  # normalised input of the next block, when the previous projection already produced it
         # A block of a plain dense model runs 9 kernels here instead of 13: k/v go into the cache from the

@@ -311,7 +311,7 @@ def _run_blocks(model, x, attn_step):
 def hybrid_prefill(model, input_ids, position_ids, meta, kv_caches, slot_mapping, state: HybridState, state_slots):
     cos, sin = model.rope(input_ids.device)
     pos = position_ids.to(torch.int32)
-    x = F.embedding(input_ids.long(), model.embed)
+    x = fused.embedding(input_ids, model.embed)
 
     def step(i, layer, y):
         if isinstance(layer.attn, GatedDeltaNet):
@@ -326,7 +326,7 @@ def hybrid_decode(model, input_ids, position_ids, kv_caches, block_table, seq_le
                   state_slots, max_seq_len=None):
     cos, sin = model.rope(input_ids.device)
     pos = position_ids.to(torch.int32)
-    x = F.embedding(input_ids.long(), model.embed)
+    x = fused.embedding(input_ids, model.embed)
 
     def step(i, layer, y):
         if isinstance(layer.attn, GatedDeltaNet):

@@ -102,6 +102,25 @@ def reset_launch_count() -> None:
     _launch_count = 0
 
 
+_fallbacks: dict[str, int] = {}
+
+
+def count_fallback(op: str) -> None:
+    """Records that an op ran on a PyTorch library operator although its inputs were CUDA tensors (a shape
+    this library's kernels do not cover). The benchmark reports these counts; zero means every hot op ran on
+    the in-tree kernels. The first occurrence of each op is also logged."""
+    n = _fallbacks.get(op, 0)
+    if n == 0:
+        import logging
+
+        logging.getLogger("areal_b200.ops").warning(f"CUDA fallback to a PyTorch operator: {op}")
+    _fallbacks[op] = n + 1
+
+
+def fallback_counts() -> dict[str, int]:
+    return dict(_fallbacks)
+
+
 def read_status() -> int:
     """Synchronises the current stream and returns (and clears) the device status word.
 

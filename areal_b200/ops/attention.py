@@ -138,4 +138,6 @@ def varlen_attention(q, k, v, meta: VarlenMeta, scale: float | None = None):
     scale = scale if scale is not None else 1.0 / math.sqrt(D)
     if _lib.use_cuda_kernels(q, k, v) and q.dtype == torch.bfloat16 and D == 128:
         return _VarlenAttn.apply(q, k, v, meta, scale)
+    if q.is_cuda:
+        _lib.count_fallback(f"varlen_attention[D={D},{str(q.dtype).replace('torch.', '')}]")
     return attention_ref(q, k, v, meta.cu_cpu, scale)

@@ -260,6 +260,25 @@ def swiglu(gu):
 # --------------------------------------------------------------------------- embedding
 
 
+def _embedding_kernel_ok(ids: torch.Tensor, w: torch.Tensor) -> bool:
+    return (_lib.use_cuda_kernels(ids, w) and w.dtype == torch.bfloat16 and w.dim() == 2
+            and w.shape[1] % 8 == 0 and w.is_contiguous())
+
+
+def _embedding_fwd(ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    if not _embedding_kernel_ok(ids, w):
+        if w.is_cuda:
+            _lib.count_fallback(f"embedding_fwd[{str(w.dtype).replace('torch.', '')}]")
+        return torch.nn.functional.embedding(ids, w)
+    flat = ids.reshape(-1).contiguous()
+    out = torch.empty((flat.numel(), w.shape[1]), dtype=w.dtype, device=w.device)
+    rc = _lib.kernels().b200_embedding_fwd(_lib.ptr(flat), _lib.ptr(w), _lib.ptr(out), ctypes.c_int(flat.numel()),
+                                           ctypes.c_int(w.shape[1]), ctypes.c_longlong(w.shape[0]), _lib.stream_ptr())
+    _lib.check(rc, "b200_embedding_fwd")
+    _lib.count_launch()
+    return out.view(*ids.shape, w.shape[1])
+
+
 class _Embedding(torch.autograd.Function):
     """Embedding lookup whose backward scatter-adds straight into the weight's fp32
     ``main_grad`` (when present) instead of materialising a dense ``[V, H]`` gradient."""
@@ -268,22 +287,35 @@ class _Embedding(torch.autograd.Function):
     def forward(ctx, ids, w):
         ctx.save_for_backward(ids)
         ctx.w = w
-        return torch.nn.functional.embedding(ids, w)
+        return _embedding_fwd(ids, w)
 
     @staticmethod
     def backward(ctx, dy):
         (ids,) = ctx.saved_tensors
         w = ctx.w
         main = getattr(w, "main_grad", None)
-        if main is not None:
-            main.index_add_(0, ids.reshape(-1), dy.reshape(-1, dy.shape[-1]).to(torch.float32))
-            return None, None
-        dw = torch.zeros(w.shape, dtype=torch.float32, device=w.device)
-        dw.index_add_(0, ids.reshape(-1), dy.reshape(-1, dy.shape[-1]).to(torch.float32))
-        return None, dw.to(w.dtype)
+        dy2 = dy.reshape(-1, dy.shape[-1])
+        # the kernel's atomic adds sum rows of equal id in varying order: under deterministic mode the
+        # sorted PyTorch scatter runs instead
+        use_kernel = (_embedding_kernel_ok(ids, w) and dy.dtype == torch.bfloat16
+                      and not torch.are_deterministic_algorithms_enabled())
+        target = main if main is not None else torch.zeros(w.shape, dtype=torch.float32, device=w.device)
+        if use_kernel and target.is_contiguous():
+            flat = ids.reshape(-1).contiguous()
+            rc = _lib.kernels().b200_embedding_bwd(_lib.ptr(flat), _lib.ptr(dy2.contiguous()), _lib.ptr(target),
+                                                   ctypes.c_int(flat.numel()), ctypes.c_int(w.shape[1]),
+                                                   ctypes.c_longlong(w.shape[0]), _lib.stream_ptr())
+            _lib.check(rc, "b200_embedding_bwd")
+            _lib.count_launch()
+        else:
+            if w.is_cuda:
+                _lib.count_fallback("embedding_bwd[index_add]")
+            target.index_add_(0, ids.reshape(-1), dy2.to(torch.float32))
+        return None, (None if main is not None else target.to(w.dtype))
 
 
 def embedding(ids: torch.Tensor, w: torch.Tensor) -> torch.Tensor:
+    """``w[ids]`` for ids in ``[0, V)``; ids outside that range give zero rows on the kernel path."""
     if w.requires_grad and torch.is_grad_enabled():
         return _Embedding.apply(ids.long(), w)
-    return torch.nn.functional.embedding(ids.long(), w)
+    return _embedding_fwd(ids.long(), w)

@@ -214,3 +214,57 @@ def lm_head_logprobs(x, w, labels, temperature: float = 1.0, tp_group=None, voca
     if _lib.use_cuda_kernels(x, w) and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0:
         return _LMHead.apply(x, w, labels, temperature, tp_group, vocab_start, tp_fused)
     return lm_head_logprobs_ref(x, w, labels, temperature, tp_group, vocab_start)
+
+
+# --------------------------------------------------------------------------- fused sampling head
+
+
+def new_sampling_rng(seed: int, device) -> torch.Tensor:
+    """State of the fused sampling head: ``[seed, step counter]`` as two 64-bit words on ``device``.
+    Every call of :func:`lm_head_sample` advances the counter by one (on the device, so a captured CUDA
+    graph draws fresh noise at every replay)."""
+    return torch.tensor([int(seed) & 0x7FFFFFFFFFFFFFFF, 0], dtype=torch.int64, device=device)
+
+
+def lm_head_sample_ref(x, w, temperature, rng_state):
+    """PyTorch statement of the fused head: Gumbel-max over ``x @ w.T / temperature`` (argmax where the
+    temperature is not positive) and the token's log-probability under the unfiltered distribution."""
+    logits = x.float() @ w.float().t()
+    t = temperature.float()
+    noisy = t > 0
+    scaled = logits / torch.where(noisy, t, torch.ones_like(t))[:, None]
+    g = torch.Generator(device="cpu").manual_seed(int(rng_state[0]) * 1000003 + int(rng_state[1]))
+    u = torch.rand(scaled.shape, generator=g).clamp_(1e-10, 1 - 1e-7).to(scaled.device)
+    gumbel = -torch.log(-torch.log(u))
+    tokens = torch.where(noisy[:, None], scaled + gumbel, scaled).argmax(-1)
+    logp = torch.log_softmax(scaled, -1).gather(1, tokens[:, None]).squeeze(1)
+    rng_state[1] += 1
+    return tokens.to(torch.int32), logp
+
+
+def lm_head_sample(x: torch.Tensor, w: torch.Tensor, temperature: torch.Tensor, rng_state: torch.Tensor):
+    """Draws ``tokens[b] ~ softmax(x[b] @ w.T / temperature[b])`` inside the LM-head GEMM's epilogue (the
+    ``[B, V]`` logits are never written) and returns ``(tokens int32 [B], logprobs f32 [B])``; rows with
+    ``temperature <= 0`` take the argmax. Top-k / top-p filtering needs the whole row and goes through
+    ``rollout_ops.sample`` on materialised logits instead. The inference servers the reference drives
+    sample on materialised logits (areal/engine/sglang_remote.py:43-127 ``sampling_params``)."""
+    if not (_lib.use_cuda_kernels(x, w) and x.dtype == torch.bfloat16 and x.shape[1] % 8 == 0):
+        return lm_head_sample_ref(x, w, temperature, rng_state)
+    B, H = x.shape
+    V = w.shape[0]
+    lib = _lib.kernels()
+    lib.b200_lm_head_sample_nsplit.restype = ctypes.c_int
+    nsplit = lib.b200_lm_head_sample_nsplit(ctypes.c_int(B), ctypes.c_int(V))
+    partials = torch.empty((nsplit, B, 4), dtype=torch.float32, device=x.device)
+    part_idx = torch.empty((nsplit, B), dtype=torch.int32, device=x.device)
+    tokens = torch.empty(B, dtype=torch.int32, device=x.device)
+    logps = torch.empty(B, dtype=torch.float32, device=x.device)
+    x = x if x.stride(1) == 1 else x.contiguous()
+    lib.b200_lm_head_sample.restype = ctypes.c_int
+    rc = lib.b200_lm_head_sample(_lib.ptr(x), _lib.ptr(w), _lib.ptr(temperature), _lib.ptr(partials),
+                                 _lib.ptr(part_idx), _lib.ptr(rng_state), _lib.ptr(tokens), _lib.ptr(logps),
+                                 ctypes.c_int(B), ctypes.c_int(V), ctypes.c_int(H), ctypes.c_longlong(x.stride(0)),
+                                 ctypes.c_longlong(w.stride(0)), _lib.stream_ptr())
+    _lib.check(rc, "b200_lm_head_sample")
+    _lib.count_launch(2)
+    return tokens, logps

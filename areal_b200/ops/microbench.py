@@ -269,6 +269,27 @@ def bench_sampler(a):
     report("sampler", ms, nbytes=B * V * 4.0, batch=B)
 
 
+def bench_sample_head(a):
+    """Decode LM head + sampling at the Qwen3-1.7B head shape: the fused head (token drawn in the GEMM
+    epilogue) against GEMM -> fp32 logits -> stand-alone sampler. Roofline: one read of the weight matrix."""
+    from .gemm import gemm
+    from .lm_head import lm_head_sample, new_sampling_rng
+    from .rollout_ops import sample
+
+    H, V = 2048, 151936
+    w = (torch.randn(V, H, device="cuda") * 0.02).bfloat16()
+    for B in ((64,) if a.small else (64, 300, 512)):
+        x = torch.randn(B, H, device="cuda").bfloat16()
+        temp = torch.ones(B, device="cuda")
+        u = torch.rand(B, device="cuda")
+        rng = new_sampling_rng(1, "cuda")
+        nbytes = float(V) * H * 2
+        ms = timeit(lambda: lm_head_sample(x, w, temp, rng), a.iters)
+        report("lm_head_sample_fused", ms, flops=2.0 * B * V * H, nbytes=nbytes, batch=B)
+        ms = timeit(lambda: sample(gemm(x, w, out_dtype=torch.float32), temp, None, None, u), a.iters)
+        report("lm_head_gemm_plus_sampler", ms, flops=2.0 * B * V * H, nbytes=nbytes + 2.0 * B * V * 4, batch=B)
+
+
 def bench_ppo_loss(a):
     from .rl_ops import ppo_loss_fused
 
@@ -306,11 +327,16 @@ def bench_decode_step(a):
     slots = bt[:, (ctx - 1) // bs].long() * bs + (ctx - 1) % bs
     temp = torch.ones(B, device="cuda")
     u = torch.rand(B, device="cuda")
+    from .lm_head import lm_head_sample, new_sampling_rng
+
+    rng = new_sampling_rng(1, "cuda")
 
     @torch.no_grad()
     def step():
         h = model.decode(ids, pos, caches, bt, sl, slots, max_seq_len=ctx)
-        return sample(model.logits(h, out_dtype=torch.float32), temp, None, None, u)
+        if getattr(a, "unfused_sampler", False):
+            return sample(model.logits(h, out_dtype=torch.float32), temp, None, None, u)
+        return lm_head_sample(h, model.output_weight(), temp, rng)
 
     kv_bytes = float(B) * ctx * mc.num_key_value_heads * mc.head_dim * 2 * 2 * mc.num_hidden_layers
     w_bytes = mc.num_params() * 2.0
@@ -331,13 +357,15 @@ def bench_decode_step(a):
 
 BENCHES = {"gemm": bench_gemm, "gemm_fp8": bench_gemm_fp8, "grouped_gemm": bench_grouped_gemm, "attn": bench_attn,
            "lm_head": bench_lm_head, "decode": bench_decode, "elementwise": bench_elementwise, "optimizer": bench_optimizer, "kchunk_gemm": bench_kchunk_gemm,
-           "sampler": bench_sampler, "ppo_loss": bench_ppo_loss, "decode_step": bench_decode_step}
+           "sampler": bench_sampler, "sample_head": bench_sample_head, "ppo_loss": bench_ppo_loss,
+           "decode_step": bench_decode_step}
 
 
 def main(argv=None):
     ap = argparse.ArgumentParser(description=__doc__, formatter_class=argparse.RawDescriptionHelpFormatter)
     ap.add_argument("op", choices=sorted(BENCHES) + ["all"])
     ap.add_argument("--small", action="store_true")
+    ap.add_argument("--unfused-sampler", action="store_true", help="decode_step: GEMM + logits + stand-alone sampler")
     ap.add_argument("--iters", type=int, default=10)
     a = ap.parse_args(argv)
     if not torch.cuda.is_available():

@@ -319,7 +319,9 @@ class PPOTrainer:
             if self.critic_engine is not None:
                 self.critic_engine.set_version(new_version)
             self.rollout_client.resume()
-        out = {"step/trained_tokens": float(n_tok), "step/weight_sync_s": float(sync_s),
+        n_resp = int(batch["loss_mask"].sum()) if "loss_mask" in batch else n_tok
+        out = {"step/trained_tokens": float(n_tok), "step/response_tokens": float(n_resp),
+               "step/weight_sync_s": float(sync_s),
                "step/loss": float(train_stats[-1].get("loss", 0.0)),
                "step/grad_norm": float(train_stats[-1].get("grad_norm", 0.0))}
         return out

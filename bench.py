@@ -142,6 +142,61 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples_under_load": len(sm)}
 
 
+_RO_PHASES = {"decode_gpu_wait": "rollout/host_s/wait", "decode_stage": "rollout/host_s/stage",
+              "plan": "rollout/host_s/plan", "params": "rollout/host_s/params",
+              "commit_deliver": "rollout/host_s/commit_deliver", "prefill": "rollout/host_s/prefill",
+              "paused": "rollout/host_s/paused", "idle": "rollout/host_s/idle"}
+
+
+def role_budget(a: dict, b: dict) -> dict:
+    """Per rollout rank: what its engine did between two snapshots of its counters (taken when the first and
+    the last batch of the timed window arrived): generated tokens per second and the share of its wall time
+    spent in each phase of the engine loop."""
+    out = {}
+    for g in b:
+        if g not in a:
+            continue
+        d = lambda k: float(b[g].get(k, 0.0)) - float(a[g].get(k, 0.0))
+        wall = d("rollout/wall_s")
+        if wall <= 0:
+            continue
+        frac = {name: d(key) / wall for name, key in _RO_PHASES.items()}
+        frac["other"] = 1.0 - sum(frac.values())
+        pre = max(d("rollout/prefill_tokens"), 1.0)
+        out[int(g)] = {"wall_s": wall, "generated_tok_s": d("rollout/generated_tokens") / wall,
+                       "decode_steps": d("rollout/engine_steps"),
+                       "tokens_per_decode_step": d("rollout/generated_tokens") / max(d("rollout/engine_steps"), 1.0),
+                       "prefill_tok_s": d("rollout/prefill_tokens") / max(d("rollout/host_s/prefill"), 1e-9),
+                       "reprefill_share_of_prefill_tokens": d("rollout/reprefill_tokens") / pre,
+                       "time_frac": {k: round(v, 4) for k, v in frac.items()}}
+    return out
+
+
+def summarize_roles(roles: list, window_s: float, n_gen: int, n_train: int, trained_tokens: float,
+                    steps: int) -> dict:
+    ro = {}
+    for r in roles:
+        ro.update(r["rollout"])
+    gen = [v["generated_tok_s"] for v in ro.values()]
+    keys = sorted({k for v in ro.values() for k in v["time_frac"]})
+    mean_frac = {k: round(sum(v["time_frac"].get(k, 0.0) for v in ro.values()) / max(len(ro), 1), 4) for k in keys}
+    wait = [r["phase_s"]["timeperf/rollout"] for r in roles]
+    busy = [sum(v for k, v in r["phase_s"].items() if k != "timeperf/rollout") for r in roles]
+    return {
+        "generated_tok_s_per_rollout_gpu": (sum(gen) / len(gen)) if gen else None,
+        "rollout_time_frac": mean_frac,
+        "rollout_tokens_per_decode_step": (sum(v["tokens_per_decode_step"] for v in ro.values()) / len(ro)) if ro else None,
+        "rollout_prefill_tok_s": (sum(v["prefill_tok_s"] for v in ro.values()) / len(ro)) if ro else None,
+        "rollout_reprefill_share_of_prefill_tokens":
+            (sum(v["reprefill_share_of_prefill_tokens"] for v in ro.values()) / len(ro)) if ro else None,
+        "consumed_tok_s_per_trainer_gpu": trained_tokens / max(sum(busy), 1e-9),
+        "trainer_idle_frac": sum(wait) / max(window_s * len(roles), 1e-9),
+        "trainer_phase_s_per_step": {k.split("/")[1]: round(sum(r["phase_s"][k] for r in roles) / len(roles) / steps, 4)
+                                     for k in roles[0]["phase_s"]},
+        "n_rollout_gpus": n_gen, "n_trainer_gpus": n_train,
+    }
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -221,9 +276,26 @@ def main():
             dist.barrier(group=cpu_group)
         torch.cuda.synchronize()
 
+    resp_per_step: list[float] = []
+    phase_keys = ("timeperf/rollout", "timeperf/recompute_logp", "timeperf/compute_advantage", "timeperf/train_step",
+                  "timeperf/update_weights")
+    phases: list[dict] = []
+
+    def rollout_snapshot() -> dict:
+        """Latest counters of the rollout engine(s) this rank is paired with (its own when colocated)."""
+        if trainer.colocated:
+            return {trainer.rank: dict(trainer.rollout.export_stats())}
+        return {g: dict(st) for g, st in getattr(trainer.rollout_client, "rollout_stats", {}).items()}
+
     def on_step(step: int, stats: dict):
         tok_per_step.append(stats.get("step/trained_tokens", 0.0))
+        resp_per_step.append(stats.get("step/response_tokens", 0.0))
         sync_s.append(stats.get("step/weight_sync_s", 0.0))
+        phases.append({k: float(stats.get(k, 0.0)) for k in phase_keys})
+        if step == W - 1:
+            marks["ro0"] = rollout_snapshot()
+        elif step == W + K - 1:
+            marks["ro1"] = rollout_snapshot()
         if step == W - 1:
             fence()
             if trainer.rank == (0 if trainer.colocated else trainer.topo.train_ranks[0]):
@@ -268,6 +340,14 @@ def main():
             dist.all_reduce(t, op=dist.ReduceOp.MAX, group=cpu_group)
             dist.all_reduce(sums, group=cpu_group)
         head = 0 if trainer.colocated else trainer.topo.train_ranks[0]
+        # per-role view: what each rollout GPU did during the timed window, and how the trainer's step splits
+        ro = role_budget(marks.get("ro0", {}), marks.get("ro1", {}))
+        mine = {"rollout": ro, "phase_s": {k: sum(p[k] for p in phases[W:W + K]) for k in phase_keys},
+                "resp_tokens": sum(resp_per_step[W:W + K])}
+        roles = [mine]
+        if dist.is_initialized() and trainer.actor_engine.world_size > 1:
+            roles = [None] * trainer.actor_engine.world_size
+            dist.all_gather_object(roles, mine, group=cpu_group)
         if trainer.rank == head:
             dev_ms, wall_s, sync_max = float(t[0]), float(t[1]), float(t[4])
             value = float(sums[0]) / (dev_ms / 1e3)
@@ -291,6 +371,12 @@ def main():
                         "d2h_bytes_per_step": int(marks["d2h"] / K)},
                 "gpu_launches": int(marks["launches"]),
                 "weight_sync_latency_s": sync_max,
+                "token_accounting": "trained tokens = prompt + response tokens of every sequence of the batch "
+                                    "(the prompt is part of the forward/backward pass); response_tok_s counts "
+                                    "the loss-masked response tokens only",
+                "response_tok_s": sum(r["resp_tokens"] for r in roles) / (dev_ms / 1e3),
+                "roles": summarize_roles(roles, dev_ms / 1e3, n_gen, n_train, float(sums[0]), K),
+                "fallback_ops": _lib.fallback_counts(),
             }
     if os.environ.get("AREAL_B200_BENCH_DIAG"):
         # host-side view of the rollout engine (stderr only): scheduler counters and where its loop spent time

@@ -105,12 +105,15 @@ def test_background_write_uses_the_staged_copy(tmp_path):
     _assert_same(_tensors(os.path.join(d, "ckpt")), _tensors(os.path.join(e, "ckpt")), exact=True)
 
 
-def test_hf_weights_with_dcp_optimizer_state_under_tensor_parallelism(tmp_path):
+@pytest.mark.parametrize("flags", [["--tp", "2"], ["--pp", "2", "--n-mbs", "2"]])
+def test_hf_weights_with_dcp_optimizer_state_under_model_parallelism(tmp_path, flags):
     """``weight_format="hf"`` with ``with_optim``: safetensors for the weights, a DCP sub-directory for the
-    optimizer (tensor-parallel peers write disjoint shards of one tensor, not one file per rank)."""
+    optimizer (tensor-parallel peers write disjoint shards of one tensor, not one file per rank). Under
+    pipeline parallelism every stage loads its own blocks back from the shared directory, the last stage its
+    copy of the tied embedding included."""
     d = str(tmp_path)
-    ref = _run(2, 29740, ["--phase", "train", "--dir", d, "--tp", "2", "--format", "hf"])
-    got = _run(2, 29741, ["--phase", "resume", "--dir", d, "--tp", "2", "--format", "hf"])
+    ref = _run(2, 29740, ["--phase", "train", "--dir", d, "--format", "hf"] + flags)
+    got = _run(2, 29741, ["--phase", "resume", "--dir", d, "--format", "hf"] + flags)
     keys = checkpoint_keys(os.path.join(d, "ckpt", "optimizer"))
     assert any(k.endswith("q_proj.weight.exp_avg") for k in keys) and not any(k.startswith("dcp.model.") for k in keys)
     assert abs(ref[0] - got[0]) < 1e-5 * abs(ref[0]) and abs(ref[2] - got[2]) < 1e-12

@@ -77,3 +77,23 @@ def test_swiglu_fwd_bwd():
     torch.testing.assert_close(y.float(), yr, atol=3e-2, rtol=2e-2)
     torch.testing.assert_close(gu.grad.float(), gr.grad, atol=5e-2, rtol=2e-2)
     assert _lib.read_status() == 0
+
+
+def test_embedding_gather_and_scatter_add():
+    """Row gather and the fp32 scatter-add of its gradient (repeated ids, ids outside the table)."""
+    torch.manual_seed(3)
+    V, H, T = 1000, 256, 777
+    w = torch.randn(V, H, device="cuda", dtype=torch.bfloat16).requires_grad_()
+    w.main_grad = torch.zeros(V, H, device="cuda", dtype=torch.float32)
+    ids = torch.randint(0, 40, (T,), device="cuda")  # many collisions
+    ids[5], ids[9] = -1, V + 3
+    y = fused.embedding(ids, w)
+    ok = (ids >= 0) & (ids < V)
+    ref = torch.where(ok[:, None], w.detach()[ids.clamp(0, V - 1)], torch.zeros((), device="cuda", dtype=w.dtype))
+    assert torch.equal(y, ref)
+    dy = torch.randn(T, H, device="cuda", dtype=torch.bfloat16)
+    y.backward(dy)
+    want = torch.zeros(V, H, device="cuda", dtype=torch.float32)
+    want.index_add_(0, ids[ok], dy[ok].float())
+    torch.testing.assert_close(w.main_grad, want, atol=1e-4, rtol=1e-5)
+    assert w.grad is None

@@ -173,6 +173,45 @@ def test_rollout_engine_receives_merged_weights():
         eng.destroy()
 
 
+def test_disk_weight_update_of_a_lora_engine_ignores_the_adapter_file(tmp_path):
+    """``update_weights(type="disk")`` writes the merged model and, beside it, ``adapter_model.safetensors``; the
+    rollout engine must read only the model's weight files (twice in a row: the second save clears the first
+    one's files before writing)."""
+    from areal_b200.api.cli_args import InferenceEngineConfig, NativeRolloutConfig
+    from areal_b200.api.io_struct import WeightUpdateMeta
+    from areal_b200.engine.rollout_engine import NativeRolloutEngine
+    from areal_b200.engine.train_engine import B200TrainEngine
+    from areal_b200.utils.hf_io import weight_files
+
+    eng = B200TrainEngine(_engine_cfg(use_lora=True, lora_rank=4, lora_alpha=4, target_modules=["q_proj"]))
+    eng.create_process_group()
+    eng.initialize(None, None)
+    rcfg = InferenceEngineConfig(experiment_name="e", trial_name="t", backend="native:d1",
+                                 native=NativeRolloutConfig(model_preset="tiny-qwen2", context_length=128,
+                                                            max_num_seqs=4, max_num_batched_tokens=256,
+                                                            num_kv_blocks=32, seed=1, cuda_graph=False))
+    ro = NativeRolloutEngine(rcfg).initialize(device="cpu")
+    try:
+        with torch.no_grad():
+            for n, p in eng.model.named_parameters():
+                if ".lora_B." in n:
+                    p.normal_(0, 0.1)
+        meta = WeightUpdateMeta(type="disk", path=str(tmp_path / "wu"))
+        eng.connect_engine(ro, meta)
+        for version in (1, 2):
+            eng.update_weights(meta.with_version(version))
+            assert ro.get_version() == version
+            vdir = os.path.join(meta.path, f"weight_update_v{version}")
+            assert os.path.exists(os.path.join(vdir, "adapter_model.safetensors"))
+            assert [f.name for f in weight_files(vdir)] == ["model.safetensors"]
+        got = dict(ro.model.named_parameters())
+        want = eng.model.layers[0].attn.qkv.float() + eng.model.layers[0].attn.lora_qkv.merged_delta()
+        assert torch.allclose(got["layers.0.attn.qkv"].float(), want, atol=1e-2)
+    finally:
+        ro.destroy()
+        eng.destroy()
+
+
 @pytest.mark.gpu
 def test_adapter_cuda_matches_fp32_reference():
     """bf16 adapter on the tcgen05 GEMMs (rank padded to 64, strided slices of the stacked

@@ -79,6 +79,21 @@ def test_static_scratch_matches_regular_entry_point_twice_in_a_row():
     torch.testing.assert_close(got[0][1], wf.grad, rtol=2e-2, atol=0.5)
 
 
+def test_static_scratch_at_the_documented_width_limit():
+    """H = 8192 is the widest row the built-in scratch takes (128 KB of dynamic shared memory per block, which
+    needs the opt-in attribute): same bits as the regular entry point, overwrite and accumulate."""
+    _lib, lib = _lib_and_stream()
+    T, H = 301, 8192
+    for seed, with_res, acc in ((5, True, 0), (6, False, 1)):
+        dy, x, w, rstd, dres = _inputs(T, H, seed, with_res)
+        dw_s = torch.full((H,), 0.25, dtype=torch.float32, device="cuda")
+        dw_r = dw_s.clone()
+        dx_s = _static(_lib, lib, dy, x, w, rstd, dres, dw_s, acc)
+        dx_r = _regular(_lib, lib, dy, x, w, rstd, dres, dw_r, acc)
+        torch.cuda.synchronize()
+        assert torch.equal(dx_s, dx_r) and torch.equal(dw_s, dw_r)
+
+
 def test_static_scratch_rejects_sizes_beyond_its_limit():
     _lib, lib = _lib_and_stream()
     dummy = torch.zeros(8, device="cuda")
