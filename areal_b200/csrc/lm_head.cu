@@ -304,29 +304,48 @@ struct LmSampleEpi {
   }
 };
 
+// One warp per row: the lanes stride over the vocab splits, then merge (max, sum-exp) pairs and the best
+// perturbed score by shuffles (ties go to the lower split, i.e. the smaller token id).
 __global__ void lm_sample_combine_kernel(const LmSampleRec* __restrict__ partials, const int* __restrict__ part_idx,
                                          int nparts, int T, int* __restrict__ tokens, float* __restrict__ logprobs,
                                          unsigned long long* rng) {
-  const int row = blockIdx.x * blockDim.x + threadIdx.x;
+  const int lane = threadIdx.x & 31;
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row < T) {
-    float M = -INFINITY, best = -INFINITY, bx = 0.f;
-    int bi = 0;
-    for (int p = 0; p < nparts; ++p) {
+    float m = -INFINITY, l = 0.f, best = -INFINITY, bx = 0.f;
+    int bp = 0x7fffffff;
+    for (int p = lane; p < nparts; p += 32) {
       const LmSampleRec r = partials[static_cast<long long>(p) * T + row];
-      M = fmaxf(M, r.m);
+      if (r.m != -INFINITY) {
+        const float mn = fmaxf(m, r.m);
+        l = l * ((m == -INFINITY) ? 0.f : __expf(m - mn)) + r.l * __expf(r.m - mn);
+        m = mn;
+      }
       if (r.best > best) {
         best = r.best;
         bx = r.bx;
-        bi = part_idx[static_cast<long long>(p) * T + row];
+        bp = p;
       }
     }
-    float L = 0.f;
-    for (int p = 0; p < nparts; ++p) {
-      const LmSampleRec r = partials[static_cast<long long>(p) * T + row];
-      L += (r.m == -INFINITY) ? 0.f : r.l * __expf(r.m - M);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float m2 = __shfl_xor_sync(0xffffffffu, m, o), l2 = __shfl_xor_sync(0xffffffffu, l, o);
+      const float b2 = __shfl_xor_sync(0xffffffffu, best, o), x2 = __shfl_xor_sync(0xffffffffu, bx, o);
+      const int p2 = __shfl_xor_sync(0xffffffffu, bp, o);
+      const float mn = fmaxf(m, m2);
+      const float s1 = (m == -INFINITY) ? 0.f : __expf(m - mn), s2 = (m2 == -INFINITY) ? 0.f : __expf(m2 - mn);
+      l = l * s1 + l2 * s2;
+      m = mn;
+      if (b2 > best || (b2 == best && p2 < bp)) {
+        best = b2;
+        bx = x2;
+        bp = p2;
+      }
     }
-    tokens[row] = bi;
-    logprobs[row] = bx - (M + logf(L));
+    if (lane == 0) {
+      tokens[row] = (bp == 0x7fffffff) ? 0 : part_idx[static_cast<long long>(bp) * T + row];
+      logprobs[row] = bx - (m + logf(l));
+    }
   }
   // every block of the GEMM that read the counter has finished (stream order): advance it for the next step
   if (blockIdx.x == 0 && threadIdx.x == 0) rng[1] += 1ull;
@@ -409,7 +428,7 @@ int b200_lm_head_stats_peers(const void* X, const void* W, const int* labels, vo
 }
 
 // Vocab splits of the fused sampling head for (B, V): the split length (in 256-column blocks) that
-// minimises the busiest CTA's number of tiles; ties go to the longer split (fewer partial records).
+// minimises the busiest CTA's number of tiles; ties go to the shorter split (more CTAs share the tail).
 int b200_lm_head_sample_nb_per(int B, int V) {
   const int tiles_m = (B + 127) / 128;
   const int tiles_n = (V + 255) / 256;
@@ -420,7 +439,7 @@ int b200_lm_head_sample_nb_per(int B, int V) {
     const long long nsplit = (tiles_n + nb - 1) / nb;
     const long long items = nsplit * tiles_m;
     const long long cost = ((items + sms - 1) / sms) * nb;
-    if (best_cost < 0 || cost <= best_cost) {
+    if (best_cost < 0 || cost < best_cost) {
       best_cost = cost;
       best = nb;
     }
@@ -449,7 +468,7 @@ int b200_lm_head_sample(const void* X, const void* W, const float* temperature, 
   LmSampleEpi epi{reinterpret_cast<LmSampleRec*>(partials), part_idx, temperature, rng, B, V, nb_per, nsplit};
   int rc = launch_lm(X, W, B, V, H, ldx, ldw, epi, static_cast<long long>(tiles_m) * nsplit, stream);
   if (rc) return rc;
-  lm_sample_combine_kernel<<<(B + 127) / 128, 128, 0, stream>>>(reinterpret_cast<const LmSampleRec*>(partials),
+  lm_sample_combine_kernel<<<(B + 3) / 4, 128, 0, stream>>>(reinterpret_cast<const LmSampleRec*>(partials),
                                                                 part_idx, nsplit, B, tokens, logprobs, rng);
   B200_CHECK(cudaGetLastError());
   return 0;

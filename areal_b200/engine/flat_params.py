@@ -172,6 +172,9 @@ class ShardedAdamW:
         self.partner_group = None        # group over which the partner's parameters are disjoint (ep group)
         self.norm_groups: list = []      # further groups that hold disjoint parameters (pipeline stages)
         self.pre_step_hooks: list = []   # run after the autograd gradients were collected
+        # flat ranges (offset, numel) whose gradient another rank of a norm group also holds and counts (the
+        # last pipeline stage's copy of a tied embedding): left out of this rank's share of the squared norm
+        self.norm_exclude: list[tuple[int, int]] = []
         self.total_steps = total_steps
         self.step_count = 0  # optimizer steps taken (bias correction)
         self.sched_step = 0  # scheduler position
@@ -374,10 +377,17 @@ class ShardedAdamW:
 
     def _dedup_replicated_norm(self, nsq: torch.Tensor):
         """The squared norm is summed over the tp group afterwards; entries of the replicated
-        region would count ``tp`` times, so keep only ``1/tp`` of their share here."""
+        region would count ``tp`` times, so keep only ``1/tp`` of their share here. Ranges in
+        ``norm_exclude`` are counted by another rank and dropped entirely."""
+        f = self.flat
+        for off, n in self.norm_exclude:
+            lo, hi = max(off, f.shard_offset), min(off + n, f.shard_offset + f.shard_numel)
+            if hi > lo:
+                part = (self.shard_grad[lo - f.shard_offset: hi - f.shard_offset].double() ** 2).sum().float()
+                assert self.tp_size == 1 or lo >= f.rep_numel, "excluded ranges lie outside the tp-replicated region"
+                nsq.sub_(part)
         if self.tp_size <= 1:
             return
-        f = self.flat
         a, b = f.shard_offset, min(f.shard_offset + f.shard_numel, f.rep_numel)
         if b > a:
             rep = (self.shard_grad[:b - a].double() ** 2).sum().float()

@@ -127,6 +127,18 @@ class B200TrainEngine(TrainEngine):
             # context_parallel_size is Ulysses sequence parallelism for this engine family
             self.mesh = build_mesh(ranks, dp=dp, sp=ps.cp_size, tp=ps.tp_size, pp=ps.pp_size, ep=ps.ep_size)
             self.pctx = self.mesh.ctx
+            if ps.pp_size > 1:
+                # schedule and virtual stages: `archon.pp_schedule` for the Archon-style backend, 1F1B otherwise;
+                # `megatron.virtual_pipeline_parallel_size` chunks per rank select the interleaved order
+                from ..parallel.pipeline import canonical_schedule
+
+                family = (self.config.backend or "").split(":")[0]
+                vpp = max(int(getattr(self.config.megatron, "virtual_pipeline_parallel_size", 1) or 1), 1)
+                name = os.environ.get("AREAL_B200_PP_SCHEDULE") or (
+                    self.config.archon.pp_schedule if family == "archon" else ("Interleaved1F1B" if vpp > 1 else "1F1B"))
+                self._pp_schedule = canonical_schedule(name, vpp)
+                self._vpp = vpp
+                self.pctx.extras["vpp"] = vpp
             if ps.cp_size > 1 and self.config.backend.split(":")[0] == "megatron" and \
                     getattr(self.config.megatron, "cp_comm_type", "a2a") in ("allgather", "p2p"):
                 self.pctx.extras["cp_mode"] = "zigzag"
@@ -287,6 +299,10 @@ class B200TrainEngine(TrainEngine):
                 self.optimizer.norm_groups.append(pctx.pp_group)
                 if self.model_config.tie_word_embeddings and not self.is_critic and self.model.embed is not None:
                     self.optimizer.pre_step_hooks.append(self._sum_tied_embedding_grads)
+                    if not self.model.first_stage:
+                        # both copies apply the summed gradient; the first stage's copy counts in the norm
+                        off = next(o for n_, p_, o, _ in self.flat.entries if p_ is self.model.embed)
+                        self.optimizer.norm_exclude.append((off, self.model.embed.numel()))
         self.ft_spec = ft_spec
         self._initialized = True
         logger.info(f"engine initialised: {self.model_config.num_params() / 1e9:.2f}B params, "
@@ -329,8 +345,21 @@ class B200TrainEngine(TrainEngine):
             from ..utils.data import unpack_to_padded
 
             input_ = unpack_to_padded(input_)
+        spec = self.config.mb_spec
+        if self.pctx is not None and self.pctx.pp_size > 1:
+            # a pipeline fills only with enough micro-batches (2 x stages for the 1F1B family); the interleaved
+            # order moves them through the chunks in groups of `stages`
+            from ..api.cli_args import MicroBatchSpec
+            from ..parallel.pipeline import min_micro_batches
+
+            pp = self.pctx.pp_size
+            need = min_micro_batches(self._pp_schedule, pp, self._vpp)
+            n_seq = int(input_["attention_mask"].shape[0]) // max(spec.granularity, 1)
+            need = min(need, max(n_seq // pp * pp, pp) if self._vpp > 1 else max(n_seq, 1))
+            div = spec.n_mbs_divisor * pp if (self._vpp > 1 and spec.n_mbs_divisor % pp) else spec.n_mbs_divisor
+            spec = MicroBatchSpec.new(spec, n_mbs=max(spec.n_mbs or 1, need), n_mbs_divisor=div)
         mb_list = split_padded_tensor_dict_into_mb_list(
-            input_, self.config.mb_spec,
+            input_, spec,
             group=self._cpu_group if (dist.is_initialized() and self.world_size > 1) else None)
         return mb_list
 
@@ -351,7 +380,8 @@ class B200TrainEngine(TrainEngine):
         out["cu_seqlens"] = meta.cu_seqlens
         return out, meta
 
-    def _forward_mb(self, mb: dict[str, Any], meta: VarlenMeta, need_entropy: bool = True, stage_input=None):
+    def _forward_mb(self, mb: dict[str, Any], meta: VarlenMeta, need_entropy: bool = True, stage_input=None,
+                    chunk: int | None = None):
         """Returns ``(logprobs [T], entropy [T])`` in next-token form, or values for a critic. A
         pipeline stage other than the last returns ``((x, res), None)`` instead."""
         ids = mb["input_ids"]
@@ -366,7 +396,7 @@ class B200TrainEngine(TrainEngine):
             logp, ent = lm_head_logprobs(hidden, self.model.output_weight(), labels,
                                          self.config.temperature)
             return logp, ent
-        return self._forward_mb_parallel(mb, meta, stage_input)
+        return self._forward_mb_parallel(mb, meta, stage_input, chunk)
 
     def _vision_inputs(self, mb: dict[str, Any]) -> dict[str, Any]:
         """Pixel rows and patch grids of the micro-batch's images, concatenated in sequence order.
@@ -418,7 +448,7 @@ class B200TrainEngine(TrainEngine):
         stats_tracker.scalar(**{"tree/node_ratio": tree.num_nodes / max(len(flat_ids), 1)})
         return logp_n.index_select(0, nxt) * has, ent_n.index_select(0, nxt) * has
 
-    def _forward_mb_parallel(self, mb: dict[str, Any], meta: VarlenMeta, stage_input=None):
+    def _forward_mb_parallel(self, mb: dict[str, Any], meta: VarlenMeta, stage_input=None, chunk: int | None = None):
         """Tensor- and/or Ulysses-parallel forward. Every rank of the model-parallel group holds the
         same micro-batch; the packed tokens are padded to a multiple of the shard count, each
         Ulysses rank takes its contiguous slice (tensor parallelism shards further inside the
@@ -448,9 +478,10 @@ class B200TrainEngine(TrainEngine):
             # image features and the per-token rotary table are built for the whole micro-batch, then sliced
             hidden = self.model(ids, pos, meta, seq_slice=sl, stage_input=stage_input, **self._vision_inputs(mb))
         else:
-            hidden = self.model(ids[sl], pos[sl], meta, stage_input=stage_input)  # [n, H]: this Ulysses shard
-        if pctx.pp_size > 1 and not pctx.is_last_stage:
-            return hidden, None  # (x, res) for the next stage
+            kw = {} if chunk is None else {"chunk": chunk}
+            hidden = self.model(ids[sl], pos[sl], meta, stage_input=stage_input, **kw)  # [n, H]: this Ulysses shard
+        if pctx.pp_size > 1 and (not pctx.is_last_stage or (chunk is not None and chunk != self.model.vpp - 1)):
+            return hidden, None  # (x, res) for the next (virtual) stage
         if self.is_critic:
             out, ent = self.model.values(hidden), None
         else:
@@ -506,64 +537,45 @@ class B200TrainEngine(TrainEngine):
         return (Tp // pctx.seq_shards, self.model_config.hidden_size)
 
     def _pipeline_forward_backward(self, mbs, scales, loss_fn, forward_only: bool = False, collect=None):
-        """All-forward-then-all-backward pipeline schedule over NCCL / gloo point-to-point.
-
-        Every stage of a replica holds the same micro-batch list, so activation shapes are known
-        without a handshake. Forward: receive ``(x, res)`` from the previous stage, run the local
-        blocks, send to the next; the last stage computes the loss. Backward (same micro-batch
-        order): receive the activation gradients from the next stage, back-propagate, send the
-        input gradients to the previous stage. Sends of stage ``i`` match receives of stage
-        ``i+1`` in program order, so blocking point-to-point calls cannot deadlock, and stage ``i``
-        works on micro-batch ``k+1`` while stage ``i+1`` works on ``k``. Returns the scaled losses
-        (last stage) or zeros (other stages; the caller broadcasts statistics).
+        """Runs the micro-batches through this rank's pipeline chunks following the configured schedule
+        (``parallel/pipeline.py``: GPipe, 1F1B, interleaved 1F1B over virtual stages) with asynchronous
+        point-to-point transfers. Every stage of a replica holds the same micro-batch list, so activation
+        shapes are known without a handshake. Returns the scaled losses (last stage) or zeros (other stages;
+        the caller broadcasts statistics).
         Reference: areal/engine/megatron_engine.py:882 (mcore schedules) and
-        areal/experimental/models/archon/pipeline_parallel.py:349-494."""
+        areal/experimental/models/archon/pipeline_parallel.py:48-82,349-494."""
+        from ..parallel.pipeline import PipelineRunner
+
         pctx = self.pctx
-        first, last = pctx.is_first_stage, pctx.is_last_stage
+        V = self._vpp
         dtype = next(self.model.parameters()).dtype
-        saved = []
-        losses = []
-        for mb, sc in zip(mbs, scales):
-            dev_mb, meta = self._mb_to_device(mb)
-            stage_in = None
-            if not first:
-                shape = self._stage_shapes(dev_mb["input_ids"].shape[0])
-                buf = torch.empty((2,) + shape, dtype=dtype, device=self.device)
-                dist.recv(buf, src=pctx.pp_prev)
-                x_in = buf[0].clone().requires_grad_(not forward_only)
-                r_in = buf[1].clone().requires_grad_(not forward_only)
-                stage_in = (x_in, r_in)
-            with torch.set_grad_enabled(not forward_only):
-                out, ent = self._forward_mb(dev_mb, meta, stage_input=stage_in)
-            if not last:
-                x, res = out
-                res = res if res is not None else torch.zeros_like(x)
-                dist.send(torch.stack([x.detach(), res.detach()]), dst=pctx.pp_next)
-                saved.append((stage_in, (x, res), None))
-                losses.append(torch.zeros((), device=self.device))
-            else:
-                if collect is not None:
-                    collect(out, ent, dev_mb, meta)
-                    saved.append((stage_in, None, None))
-                    continue
-                loss = loss_fn(out, dev_mb) if self.is_critic else loss_fn(out, ent, dev_mb)
-                saved.append((stage_in, None, loss * sc))
-                losses.append(loss.detach() * sc)
-        if forward_only:
-            return losses
-        for stage_in, outs, loss in saved:
-            if last:
-                loss.backward()
-            else:
-                g = torch.empty((2,) + tuple(outs[0].shape), dtype=dtype, device=self.device)
-                dist.recv(g, src=pctx.pp_next)
-                torch.autograd.backward([outs[0], outs[1]], [g[0], g[1]])
-            if not first:
-                x_in, r_in = stage_in
-                gx = x_in.grad if x_in.grad is not None else torch.zeros_like(x_in)
-                gr = r_in.grad if r_in.grad is not None else torch.zeros_like(r_in)
-                dist.send(torch.stack([gx, gr]), dst=pctx.pp_prev)
-        return losses
+        runner = PipelineRunner(pctx.extras["pp_links"], pctx.pp_rank, pctx.pp_size, V,
+                                "gpipe" if forward_only and V == 1 else self._pp_schedule, dtype, self.device)
+        staged: dict[int, tuple] = {}
+
+        def on_device(i):
+            if i not in staged:
+                staged[i] = self._mb_to_device(mbs[i])
+            return staged[i]
+
+        def forward(i, c, stage_in):
+            dev_mb, meta = on_device(i)
+            out, ent = self._forward_mb(dev_mb, meta, stage_input=stage_in, chunk=c if V > 1 else None)
+            return out if ent is None and isinstance(out, tuple) else (out, ent)
+
+        def finish(i, outs):
+            out, ent = outs
+            dev_mb, meta = on_device(i)
+            if collect is not None:
+                collect(i, out, ent, dev_mb, meta)
+                return None
+            loss = loss_fn(out, dev_mb) if self.is_critic else loss_fn(out, ent, dev_mb)
+            return loss * scales[i]
+
+        results = runner.run(len(mbs), forward, finish, lambda i: self._stage_shapes(int(mbs[i]["cu_seqlens"][-1])),
+                             forward_only=forward_only)
+        zero = torch.zeros((), device=self.device)
+        return [results[i] if (i in results and results[i] is not None) else zero for i in range(len(mbs))]
 
     # ------------------------------------------------------------------ train
     def optimizer_zero_grad(self):
@@ -643,10 +655,10 @@ class B200TrainEngine(TrainEngine):
         ent_result = torch.zeros(B, L, dtype=torch.float32) if return_entropy else None
         row = 0
         pp = self.pctx is not None and self.pctx.pp_size > 1
-        staged = []
+        staged = {}
         if pp:
             self._pipeline_forward_backward(mb_list.mbs, [1.0] * len(mb_list.mbs), None, forward_only=True,
-                                            collect=lambda o, e, m, mt: staged.append((o, e, mt)))
+                                            collect=lambda i, o, e, m, mt: staged.__setitem__(i, (o, e, mt)))
         for i_mb, mb in enumerate(mb_list.mbs):
             if pp:
                 if not self.pctx.is_last_stage:

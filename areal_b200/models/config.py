@@ -312,6 +312,10 @@ PRESETS: dict[str, ModelConfig] = {
                               intermediate_size=688, num_hidden_layers=2, num_attention_heads=4,
                               num_key_value_heads=2, head_dim=64, rope_theta=1e4,
                               tie_word_embeddings=False, attention_bias=True, qk_norm=False),
+    "tiny-qwen2-4l": ModelConfig(model_type="qwen2", vocab_size=1024, hidden_size=256,
+                                 intermediate_size=688, num_hidden_layers=6, num_attention_heads=4,
+                                 num_key_value_heads=2, head_dim=64, rope_theta=1e4,
+                                 tie_word_embeddings=True, attention_bias=True, qk_norm=False),
     "tiny-qwen2_5-vl": ModelConfig(model_type="qwen2_5_vl", vocab_size=1024, hidden_size=256, intermediate_size=688,
                                    num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
                                    rope_theta=1e4, tie_word_embeddings=False, attention_bias=True, qk_norm=False,

@@ -139,7 +139,7 @@ def iter_adapters(model) -> Iterator[tuple[str, torch.Tensor, LoRAAdapter]]:
     """``(hf_prefix, fused_weight, adapter)`` for every adapter of a ``QwenModel``."""
     # a vision-language checkpoint nests its decoder under `language_model`
     lm = "language_model." if getattr(model.cfg, "is_vl", False) else ""
-    for i, layer in enumerate(model.layers, start=model.layer_start):
+    for i, layer in zip(model.layer_ids, model.layers):
         p = f"base_model.model.model.{lm}layers.{i}."
         a, m = layer.attn, layer.mlp
         if getattr(a, "lora_qkv", None) is not None:

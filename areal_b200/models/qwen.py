@@ -320,18 +320,33 @@ class QwenModel(nn.Module):
         pp = pctx.pp_size if pctx is not None else 1
         self.first_stage = pctx.is_first_stage if pp > 1 else True
         self.last_stage = pctx.is_last_stage if pp > 1 else True
+        # virtual stages: every rank holds `vpp` chunks of blocks; chunk v of rank p is virtual stage v * pp + p,
+        # so the embedding still sits on the first rank (its chunk 0) and the head on the last rank (its last chunk)
+        self.vpp = int(pctx.extras.get("vpp", 1)) if pp > 1 else 1
         if pp > 1:
-            # the last stage also runs the LM head (or value head) and the loss: weigh it in units of one block
+            from ..parallel.context import partition_layers
+
+            # the last virtual stage also runs the LM head (or value head) and the loss: weigh it in units of one block
             per_layer = max((cfg.num_params() - cfg.vocab_size * cfg.hidden_size *
                              (1 if (cfg.tie_word_embeddings or cfg.is_critic) else 2)) / cfg.num_hidden_layers, 1.0)
             head = 0.0 if cfg.is_critic else cfg.vocab_size * cfg.hidden_size / per_layer
-            self.layer_start, self.layer_end = pctx.layer_range(cfg.num_hidden_layers, last_extra=head)
+            if self.vpp == 1:
+                self.chunk_ranges = [pctx.layer_range(cfg.num_hidden_layers, last_extra=head)]
+            else:
+                ranges = partition_layers([1.0] * cfg.num_hidden_layers, pp * self.vpp, 0.0, head)
+                self.chunk_ranges = [ranges[v * pp + pctx.pp_rank] for v in range(self.vpp)]
         else:
-            self.layer_start, self.layer_end = 0, cfg.num_hidden_layers
+            self.chunk_ranges = [(0, cfg.num_hidden_layers)]
+        self.layer_ids = [i for a, b in self.chunk_ranges for i in range(a, b)]  # global index of every local block
+        self.chunk_slices, o = [], 0
+        for a, b in self.chunk_ranges:
+            self.chunk_slices.append((o, o + b - a))
+            o += b - a
+        self.layer_start, self.layer_end = self.chunk_ranges[0][0], self.chunk_ranges[-1][1]
         mk = lambda *shape: nn.Parameter(torch.empty(*shape, dtype=dtype, device=device))
         need_embed = self.first_stage or (self.last_stage and cfg.tie_word_embeddings and not cfg.is_critic)
         self.embed = mk(vloc, cfg.hidden_size) if need_embed else None
-        self.layers = nn.ModuleList(Block(cfg, i, dtype, device, pctx) for i in range(self.layer_start, self.layer_end))
+        self.layers = nn.ModuleList(Block(cfg, i, dtype, device, pctx) for i in self.layer_ids)
         self.norm = nn.Parameter(torch.ones(cfg.hidden_size, dtype=dtype, device=device)) if self.last_stage else None
         self.score = self.lm_head = None
         if self.last_stage:
@@ -349,7 +364,7 @@ class QwenModel(nn.Module):
         dev_gen = None
         tp = self.pctx.tp_size if self.pctx is not None else 1
         tp_rank = self.pctx.tp_rank if self.pctx is not None else 0
-        if self.layer_end - self.layer_start != self.cfg.num_hidden_layers:
+        if len(self.layer_ids) != self.cfg.num_hidden_layers:
             return self._init_weights_pipeline(seed, std)
         for name, p in self.named_parameters():
             if ".lora_" in name:
@@ -413,7 +428,7 @@ class QwenModel(nn.Module):
         for name, prm in self.named_parameters():
             if name.startswith("layers."):
                 _, idx, rest = name.split(".", 2)
-                key = f"layers.{int(idx) + self.layer_start}.{rest}"
+                key = f"layers.{self.layer_ids[int(idx)]}.{rest}"
             else:
                 key = name
             prm.copy_(src[key])
@@ -436,14 +451,16 @@ class QwenModel(nn.Module):
 
     # --------------------------------------------------------------- forward
     def forward(self, input_ids, position_ids, meta: VarlenMeta, attn_fn=None, stage_input=None,
-                embeds=None, rope=None, layer_adds=None):
+                embeds=None, rope=None, layer_adds=None, chunk=None):
         """Packed forward; returns the final-normed hidden states ``[T, H]``. On a pipeline stage
         other than the first, ``stage_input = (x, res)`` are the activations received from the
         previous stage; a stage other than the last returns ``(x, res)`` for the next one.
         ``embeds`` replaces the embedding lookup and ``rope = (cos, sin)`` the rotary tables that
         ``position_ids`` index (a vision-language model passes image features merged into the token
         embeddings and one table row per token). ``layer_adds = (rows, [f_0, f_1, …])`` adds ``f_l`` to the
-        hidden states of ``rows`` after block ``l`` (deep-stack vision features)."""
+        hidden states of ``rows`` after block ``l`` (deep-stack vision features). ``chunk`` runs one of this rank's
+        chunks of blocks only (virtual pipeline stages): the embedding belongs to chunk 0 of the first rank, the
+        final norm to the last chunk of the last rank."""
         cos, sin = rope if rope is not None else self.rope(input_ids.device)
         pos = position_ids.to(torch.int32)
         p = self.pctx
@@ -464,7 +481,9 @@ class QwenModel(nn.Module):
         else:
             x, res = fused.embedding(input_ids, self.embed), None
         ckpt_every = getattr(self, "checkpoint_every", 0)
-        for li, layer in enumerate(self.layers):
+        lo, hi = (0, len(self.layers)) if chunk is None else self.chunk_slices[chunk]
+        for li in range(lo, hi):
+            layer = self.layers[li]
             if ckpt_every and torch.is_grad_enabled() and li % ckpt_every == 0:
                 # activation checkpointing: keep only the block's inputs, recompute the rest in backward
                 from torch.utils.checkpoint import checkpoint
@@ -474,7 +493,7 @@ class QwenModel(nn.Module):
                 x, res = layer(x, res, cos, sin, pos, meta, attn_fn)
             if layer_adds is not None and li < len(layer_adds[1]):
                 x = x.index_add(0, layer_adds[0], layer_adds[1][li].to(x.dtype))  # hidden = x + res: add to x
-        if not self.last_stage:
+        if not self.last_stage or (chunk is not None and chunk != self.vpp - 1):
             return x, res
         y, _ = fused.rmsnorm(x, self.norm, self.cfg.rms_norm_eps, residual=res)
         if p is not None and p.tp_size > 1:
@@ -619,7 +638,7 @@ class QwenModel(nn.Module):
             yield "model.embed_tokens.weight", self.embed
         qs, ks = cfg.q_size // tp, cfg.kv_size // tp
         I = cfg.intermediate_size // tp
-        for i, layer in enumerate(self.layers, start=self.layer_start):
+        for i, layer in zip(self.layer_ids, self.layers):
             p = f"model.layers.{i}."
             yield p + "input_layernorm.weight", layer.input_norm
             a = layer.attn
@@ -676,7 +695,7 @@ class QwenModel(nn.Module):
         if self.embed is not None and self.first_stage:
             yield "model.embed_tokens.weight", self.embed
         I = cfg.intermediate_size
-        for i, layer in enumerate(self.layers, start=self.layer_start):
+        for i, layer in zip(self.layer_ids, self.layers):
             p = f"model.layers.{i}."
             yield p + "input_layernorm.weight", nw(layer.input_norm)
             yield from hf_tensors(layer.attn, p, cfg, nw)
@@ -711,11 +730,11 @@ class QwenModel(nn.Module):
     def owned_by_other_stage(self, name: str) -> bool:
         """True for a checkpoint tensor that belongs to another pipeline stage: a block outside this
         stage's range, the embedding when this stage has none, the final norm / head off the last stage."""
-        if self.layer_end - self.layer_start == self.cfg.num_hidden_layers:
+        if len(self.layer_ids) == self.cfg.num_hidden_layers:
             return False
         m = re.match(r"model\.layers\.(\d+)\.", name)
         if m is not None:
-            return not (self.layer_start <= int(m.group(1)) < self.layer_end)
+            return int(m.group(1)) not in self.layer_ids
         if name == "model.embed_tokens.weight":
             return self.embed is None
         if name in ("model.norm.weight", "lm_head.weight", "score.weight"):

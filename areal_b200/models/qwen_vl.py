@@ -531,7 +531,7 @@ class QwenVLModel(QwenModel):
         if self.cfg.is_moe:
             # Qwen3-VL-MoE checkpoints hold all experts of a layer in two tensors, input dimension first:
             # gate_up_proj [E, H, 2I], down_proj [E, I, H] (transposed views of the fused parameters)
-            for i, layer in enumerate(self.layers, start=self.layer_start):
+            for i, layer in zip(self.layer_ids, self.layers):
                 if hasattr(layer.mlp, "router"):
                     p = f"{self._LM}layers.{i}.mlp.experts."
                     yield p + "gate_up_proj", layer.mlp.gate_up.transpose(1, 2)

@@ -175,6 +175,23 @@ def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1,
             g = dist.new_group(pair)
             if me in pair:
                 tie_g = (g, pair.index(me), 2)
+    # pipeline transport: one two-rank group per direction of every neighbour pair (the pair that closes the
+    # ring serves virtual stages), so each group carries one ordered one-way stream of messages
+    links = None
+    if pp > 1 and dist.is_initialized():
+        from .pipeline import PipelineLinks
+
+        stride = dp * sp * tp
+        for j in range(stride):
+            col = [ranks[j + k * stride] for k in range(pp)]
+            edges = []
+            for i in range(pp):
+                pair = [col[i], col[(i + 1) % pp]]
+                edges.append((dist.new_group(pair), dist.new_group(pair)))
+            if me in col:
+                i = col.index(me)
+                links = PipelineLinks(prev=col[i - 1], next=col[(i + 1) % pp], fwd_prev=edges[i - 1][0],
+                                      bwd_prev=edges[i - 1][1], fwd_next=edges[i][0], bwd_next=edges[i][1])
     cpu_sh = (None, 0, 1)
     if cpu_groups and dist.is_initialized() and not backend_is_gloo:
         buckets: dict[Any, list[int]] = {}
@@ -201,6 +218,7 @@ def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1,
         ctx.pp_group, ctx.pp_rank, ctx.pp_size = pp_g[0], p, pp
         ctx.pp_prev, ctx.pp_next = mesh.pp_prev, mesh.pp_next
         ctx.pp_tie_group = tie_g[0]
+        ctx.extras["pp_links"] = links
     if ep > 1:
         ctx.ep_group, ctx.ep_rank, ctx.ep_size = ep_g
         mesh.edp_group, mesh.edp_rank, mesh.edp_size = edp_g

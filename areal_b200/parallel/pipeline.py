@@ -1,0 +1,283 @@
+"""Pipeline-parallel schedules and the executor that runs them over asynchronous point-to-point.
+
+A schedule is, per pipeline rank, an ordered list of actions ``("F" | "B", micro_batch, chunk)``; ``chunk``
+selects one of the rank's ``V`` model chunks (virtual stages: chunk ``v`` of rank ``p`` is virtual stage
+``v * P + p``). Three schedules are built here:
+
+* ``gpipe``: every forward, then every backward (activations of all micro-batches stay alive);
+* ``1f1b``: ``P - 1 - p`` warm-up forwards, then one forward / one backward alternating, then the
+  remaining backwards; at most ``P - p`` micro-batches are alive on rank ``p``;
+* ``interleaved_1f1b``: the same idea over virtual stages, which divides the bubble by ``V``.
+
+Every rank can build every rank's list, so :func:`simulate` replays a whole pipeline on the host and reports
+makespan, bubble fraction and the peak number of live activations (used by the tests and the docs).
+
+Transport. Activations flow p → p+1 and gradients p+1 → p (with virtual stages also P-1 → 0 and back).
+Each *direction* of each neighbour pair has its own two-rank process group, i.e. its own NCCL communicator
+and stream: a group carries one ordered stream of messages one way, sender and receiver enumerate it in the
+same order (both follow the schedule), so plain ``isend`` / ``irecv`` can never wait on each other in a
+cycle and no send has to be grouped with a receive. Receives are posted one action ahead and sends are
+never waited for before the end of the step, so transfers overlap the compute of neighbouring actions.
+``x`` and the residual stream travel as two messages; nothing is stacked or cloned.
+
+Reference: areal/experimental/models/archon/pipeline_parallel.py:48-82 (``build_pipeline_schedule``:
+1F1B, Interleaved1F1B, zero-bubble variants) and :349-494, options areal/api/cli_args.py:537-700; Megatron's
+schedules behind areal/engine/megatron_engine.py:882. The zero-bubble variants split a backward pass into
+input-gradient and weight-gradient halves; here their names select ``interleaved_1f1b``.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+import torch.distributed as dist
+
+Action = tuple[str, int, int]  # kind, micro-batch, chunk
+
+_ALIASES = {
+    "gpipe": "gpipe", "1f1b": "1f1b", "interleaved1f1b": "interleaved_1f1b", "interleaved_1f1b": "interleaved_1f1b",
+    "interleavedzerobubble": "interleaved_1f1b", "zbvzerobubble": "interleaved_1f1b",
+}
+
+
+def canonical_schedule(name: str, virtual: int) -> str:
+    key = _ALIASES.get(str(name).replace("-", "").replace(" ", "").lower())
+    if key is None:
+        raise ValueError(f"unknown pipeline schedule {name!r}; known: GPipe, 1F1B, Interleaved1F1B")
+    if key == "interleaved_1f1b" and virtual == 1:
+        return "1f1b"  # one chunk per rank: the interleaved order degenerates to plain 1F1B
+    if key != "interleaved_1f1b" and virtual > 1:
+        raise ValueError(f"schedule {name!r} runs one model chunk per rank; virtual stages need Interleaved1F1B")
+    return key
+
+
+def build_schedule(name: str, pp_size: int, n_mbs: int, rank: int, virtual: int = 1,
+                   forward_only: bool = False) -> list[Action]:
+    """The action list of pipeline rank ``rank``."""
+    P, M, V = pp_size, n_mbs, virtual
+    kind = canonical_schedule(name, V)
+    if forward_only:
+        if V == 1:
+            return [("F", m, 0) for m in range(M)]
+        return [("F",) + _virtual_to_mb_chunk(k, P, V, True) for k in range(M * V)]
+    if kind == "gpipe":
+        return [("F", m, 0) for m in range(M)] + [("B", m, 0) for m in range(M)]
+    if kind == "1f1b":
+        warm = min(P - 1 - rank, M)
+        acts: list[Action] = [("F", m, 0) for m in range(warm)]
+        for i in range(M - warm):
+            acts.append(("F", warm + i, 0))
+            acts.append(("B", i, 0))
+        acts += [("B", m, 0) for m in range(M - warm, M)]
+        return acts
+    # interleaved 1F1B: micro-batches advance in groups of P through the chunks
+    if M % P != 0:
+        raise ValueError(f"Interleaved1F1B needs a micro-batch count that is a multiple of the pipeline size "
+                         f"(got {M} micro-batches, {P} stages)")
+    total = M * V
+    warm = min((P - 1 - rank) * 2 + (V - 1) * P, total)
+    acts = [("F",) + _virtual_to_mb_chunk(k, P, V, True) for k in range(warm)]
+    for i in range(total - warm):
+        acts.append(("F",) + _virtual_to_mb_chunk(warm + i, P, V, True))
+        acts.append(("B",) + _virtual_to_mb_chunk(i, P, V, False))
+    acts += [("B",) + _virtual_to_mb_chunk(k, P, V, False) for k in range(total - warm, total)]
+    return acts
+
+
+def _virtual_to_mb_chunk(k: int, P: int, V: int, forward: bool) -> tuple[int, int]:
+    """Micro-batch and chunk of the ``k``-th forward (backward) of a rank under the interleaved order."""
+    group, r = divmod(k, P * V)
+    c = r // P
+    return group * P + r % P, (c if forward else V - 1 - c)
+
+
+def min_micro_batches(name: str, pp_size: int, virtual: int = 1) -> int:
+    """Micro-batches below which the pipeline cannot fill: ``2 * pp`` for the 1F1B family (the reference's
+    ``min_n_mbs``), rounded up to a multiple of ``pp`` for the interleaved order."""
+    kind = canonical_schedule(name, virtual)
+    return pp_size if kind == "gpipe" else 2 * pp_size
+
+
+@dataclass
+class SimResult:
+    makespan: float
+    busy: list[float]
+    bubble_fraction: float
+    peak_live: list[int]
+    order: list[tuple[int, Action, float, float]] = field(default_factory=list)
+
+
+def simulate(name: str, pp_size: int, n_mbs: int, virtual: int = 1, f_cost: float = 1.0, b_cost: float = 2.0,
+             comm_cost: float = 0.0) -> SimResult:
+    """Replays the schedule of every rank with per-chunk costs ``f_cost / V`` and ``b_cost / V``: an action
+    starts when the rank is free and its input has arrived. Raises if the schedules deadlock."""
+    P, V = pp_size, virtual
+    acts = [build_schedule(name, P, n_mbs, r, V) for r in range(P)]
+    ptr = [0] * P
+    free = [0.0] * P
+    done: dict[tuple[str, int, int], float] = {}  # (kind, mb, virtual stage) -> finish time
+    live = [0] * P
+    peak = [0] * P
+    busy = [0.0] * P
+    order = []
+    last_vs = P * V - 1
+    remaining = sum(len(a) for a in acts)
+    while remaining:
+        progressed = False
+        for r in range(P):
+            while ptr[r] < len(acts[r]):
+                kind, mb, c = acts[r][ptr[r]]
+                vs = c * P + r
+                if kind == "F":
+                    dep = None if vs == 0 else ("F", mb, vs - 1)
+                else:
+                    dep = ("F", mb, vs) if vs == last_vs else ("B", mb, vs + 1)
+                if dep is not None and dep not in done:
+                    break
+                ready = 0.0 if dep is None else done[dep] + (comm_cost if dep[2] != vs else 0.0)
+                start = max(free[r], ready)
+                cost = (f_cost if kind == "F" else b_cost) / V
+                free[r] = start + cost
+                busy[r] += cost
+                done[(kind, mb, vs)] = free[r]
+                live[r] += 1 if kind == "F" else -1
+                peak[r] = max(peak[r], live[r])
+                order.append((r, (kind, mb, c), start, free[r]))
+                ptr[r] += 1
+                remaining -= 1
+                progressed = True
+        if not progressed:
+            raise RuntimeError(f"pipeline schedule {name} deadlocks at {[a[p] if p < len(a) else None for a, p in zip(acts, ptr)]}")
+    makespan = max(free)
+    return SimResult(makespan, busy, 1.0 - sum(busy) / (P * makespan), peak, order)
+
+
+# --------------------------------------------------------------------------- transport
+
+
+@dataclass
+class PipelineLinks:
+    """The directed two-rank groups of one pipeline column. ``fwd_next``: this rank → next stage (activations
+    out), ``fwd_prev``: previous stage → this rank (activations in), ``bwd_next`` / ``bwd_prev``: the gradient
+    streams the other way. ``prev`` / ``next`` are global ranks (with virtual stages the ring closes: the first
+    rank's ``prev`` is the last rank)."""
+    prev: int | None = None
+    next: int | None = None
+    fwd_prev: Any = None
+    fwd_next: Any = None
+    bwd_prev: Any = None
+    bwd_next: Any = None
+
+
+class _Pending:
+    """Handles of transfers in flight (the tensors stay referenced until the transfer has finished)."""
+
+    def __init__(self):
+        self.items: list[tuple[Any, tuple]] = []
+
+    def add(self, work, *tensors):
+        self.items.append((work, tensors))
+
+    def wait_all(self):
+        for work, _ in self.items:
+            work.wait()
+        self.items.clear()
+
+
+class PipelineRunner:
+    """Runs one optimizer step's micro-batches through this rank's chunks following a schedule.
+
+    ``forward(mb_index, chunk, stage_input) -> outputs``: runs the chunk; returns ``(x, res)`` when the
+    chunk is not the last virtual stage, else whatever ``finish`` needs. ``finish(mb_index, outputs) ->
+    scalar loss | None`` (last virtual stage only; ``None`` in forward-only runs). ``shape_of(mb_index)``:
+    shape of the activations travelling between stages for that micro-batch."""
+
+    def __init__(self, links: PipelineLinks, pp_rank: int, pp_size: int, virtual: int, schedule: str,
+                 dtype: torch.dtype, device: torch.device):
+        self.links, self.rank, self.P, self.V = links, pp_rank, pp_size, virtual
+        self.schedule = schedule
+        self.dtype, self.device = dtype, device
+
+    # -- which virtual stage talks to whom
+    def _vs(self, chunk: int) -> int:
+        return chunk * self.P + self.rank
+
+    def _is_first(self, chunk: int) -> bool:
+        return self._vs(chunk) == 0
+
+    def _is_last(self, chunk: int) -> bool:
+        return self._vs(chunk) == self.P * self.V - 1
+
+    def _recv(self, shape, src: int, group) -> tuple[list, list[torch.Tensor]]:
+        bufs = [torch.empty(shape, dtype=self.dtype, device=self.device) for _ in range(2)]
+        works = [dist.irecv(b, src=src, group=group) for b in bufs]
+        return works, bufs
+
+    def run(self, n_mbs: int, forward: Callable, finish: Callable, shape_of: Callable,
+            forward_only: bool = False) -> dict[int, Any]:
+        L = self.links
+        acts = build_schedule(self.schedule, self.P, n_mbs, self.rank, self.V, forward_only=forward_only)
+        sends = _Pending()
+        posted: dict[int, tuple[list, list[torch.Tensor]]] = {}  # action index -> receive in flight
+        saved: dict[tuple[int, int], tuple] = {}  # (mb, chunk) -> (stage input, outputs, loss)
+        results: dict[int, Any] = {}
+
+        def post(i: int):
+            if i >= len(acts) or i in posted:
+                return
+            kind, mb, c = acts[i]
+            if kind == "F" and not self._is_first(c):
+                posted[i] = self._recv(shape_of(mb), L.prev, L.fwd_prev)
+            elif kind == "B" and not self._is_last(c):
+                posted[i] = self._recv(shape_of(mb), L.next, L.bwd_next)
+
+        post(0)
+        for i, (kind, mb, c) in enumerate(acts):
+            post(i)
+            post(i + 1)  # the next action's input travels while this one computes
+            got = posted.pop(i, None)
+            if got is not None:
+                for w in got[0]:
+                    w.wait()
+            if kind == "F":
+                stage_in = None
+                if got is not None:
+                    x_in, r_in = got[1]
+                    if not forward_only:
+                        x_in.requires_grad_(True)
+                        r_in.requires_grad_(True)
+                    stage_in = (x_in, r_in)
+                with torch.set_grad_enabled(not forward_only):
+                    out = forward(mb, c, stage_in)
+                if not self._is_last(c):
+                    x, res = out
+                    res = res if res is not None else torch.zeros_like(x)
+                    xs, rs = x.detach(), res.detach()
+                    sends.add(dist.isend(xs, dst=L.next, group=L.fwd_next), xs)
+                    sends.add(dist.isend(rs, dst=L.next, group=L.fwd_next), rs)
+                    if not forward_only:
+                        saved[(mb, c)] = (stage_in, (x, res), None)
+                else:
+                    with torch.set_grad_enabled(not forward_only):
+                        loss = finish(mb, out)
+                    results[mb] = loss.detach() if torch.is_tensor(loss) else loss
+                    if not forward_only:
+                        saved[(mb, c)] = (stage_in, None, loss)
+            else:
+                stage_in, outs, loss = saved.pop((mb, c))
+                if self._is_last(c):
+                    loss.backward()
+                else:
+                    gx, gr = got[1]
+                    torch.autograd.backward([outs[0], outs[1]], [gx, gr])
+                if not self._is_first(c):
+                    x_in, r_in = stage_in
+                    gx = x_in.grad if x_in.grad is not None else torch.zeros_like(x_in)
+                    gr = r_in.grad if r_in.grad is not None else torch.zeros_like(r_in)
+                    sends.add(dist.isend(gx, dst=L.prev, group=L.bwd_prev), gx)
+                    sends.add(dist.isend(gr, dst=L.prev, group=L.bwd_prev), gr)
+        sends.wait_all()
+        assert not saved and not posted
+        return results

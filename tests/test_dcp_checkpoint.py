@@ -68,8 +68,8 @@ def test_save_at_two_ranks_load_at_another_size(tmp_path, resume_ws):
     """Saved at dp 2; loaded at dp 1 / dp 4: weights, master copy and Adam moments are bit-equal after the load,
     and the next step lands where the uninterrupted run did."""
     d = str(tmp_path)
-    ref = _run(2, 29710, ["--phase", "train", "--dir", d])
-    got = _run(resume_ws, 29711 + resume_ws, ["--phase", "resume", "--dir", d])
+    ref = _run(2, 29700 + 4 * resume_ws, ["--phase", "train", "--dir", d])
+    got = _run(resume_ws, 29701 + 4 * resume_ws, ["--phase", "resume", "--dir", d])
     saved, reloaded = _tensors(os.path.join(d, "ckpt")), _tensors(os.path.join(d, "reload"))
     assert any(k.endswith(".exp_avg") for k in saved) and any(k.endswith(".master") for k in saved)
     _assert_same(saved, reloaded, exact=True)
@@ -86,8 +86,9 @@ def test_resume_under_model_parallelism_and_on_one_rank(tmp_path, flags, one, pr
     the expert optimizer's counters included); a single process reads the same checkpoint too."""
     d = str(tmp_path)
     common = ["--dir", d, "--preset", preset]
-    ref = _run(2, 29720, ["--phase", "train"] + common + flags)
-    got = _run(2, 29721, ["--phase", "resume"] + common + flags)
+    port = 29720 + 2 * len(flags) + (4 if preset != "tiny-qwen2" else 0)
+    ref = _run(2, port, ["--phase", "train"] + common + flags)
+    got = _run(2, port + 1, ["--phase", "resume"] + common + flags)
     _assert_same(_tensors(os.path.join(d, "ckpt")), _tensors(os.path.join(d, "reload")), exact=True)
     _assert_same(_tensors(os.path.join(d, "after")), _tensors(os.path.join(d, "resumed")), exact=False, tol=1e-5)
     assert abs(ref[0] - got[0]) < 1e-5 * abs(ref[0]) and abs(ref[2] - got[2]) < 1e-12
@@ -112,8 +113,8 @@ def test_hf_weights_with_dcp_optimizer_state_under_model_parallelism(tmp_path, f
     pipeline parallelism every stage loads its own blocks back from the shared directory, the last stage its
     copy of the tied embedding included."""
     d = str(tmp_path)
-    ref = _run(2, 29740, ["--phase", "train", "--dir", d, "--format", "hf"] + flags)
-    got = _run(2, 29741, ["--phase", "resume", "--dir", d, "--format", "hf"] + flags)
+    ref = _run(2, 29740 + len(flags), ["--phase", "train", "--dir", d, "--format", "hf"] + flags)
+    got = _run(2, 29745 + len(flags), ["--phase", "resume", "--dir", d, "--format", "hf"] + flags)
     keys = checkpoint_keys(os.path.join(d, "ckpt", "optimizer"))
     assert any(k.endswith("q_proj.weight.exp_avg") for k in keys) and not any(k.startswith("dcp.model.") for k in keys)
     assert abs(ref[0] - got[0]) < 1e-5 * abs(ref[0]) and abs(ref[2] - got[2]) < 1e-12

@@ -69,6 +69,8 @@ def main():
     ap.add_argument("--images", action="store_true", help="image prompts (vision-language presets)")
     ap.add_argument("--one-image", action="store_true", help="only the first sequence carries an image")
     ap.add_argument("--shard-vision", action="store_true", help="divide the vision tower's images over the sp ranks")
+    ap.add_argument("--vpp", type=int, default=1, help="virtual pipeline stages (model chunks) per rank")
+    ap.add_argument("--schedule", default="", help="pipeline schedule: GPipe | 1F1B | Interleaved1F1B")
     ap.add_argument("--zigzag", action="store_true", help="context parallelism with zig-zag chunks and gathered K/V "
                                                           "(the Megatron-style engine's mode) instead of Ulysses")
     args = ap.parse_args()
@@ -90,6 +92,9 @@ def main():
                                                       warmup_steps_proportion=0.0, lr_scheduler_type="constant"))
     if args.zigzag:
         cfg.backend = "megatron:d1"
+    cfg.megatron.virtual_pipeline_parallel_size = args.vpp
+    if args.schedule:
+        os.environ["AREAL_B200_PP_SCHEDULE"] = args.schedule
     cfg.fsdp.shard_vision_across_sp = args.shard_vision
     eng = B200TrainEngine(cfg)
     batch = global_batch(L=512 if cuda else 48, images=args.images, one_image=args.one_image)
@@ -141,6 +146,9 @@ def main():
             continue
         if mesh.shard_size > 1:
             dist.all_reduce(g, group=mesh.shard_group)
+        if pctx.pp_size > 1 and name == "embed" and eng.model_config.tie_word_embeddings and not args.critic:
+            # tied embedding / head: the first stage holds the lookup's share of the gradient, the last the head's
+            dist.all_reduce(g, group=pctx.pp_tie_group)
         if pctx.tp_size > 1:
             if is_tp_replicated(name):
                 if not name.endswith("score"):
@@ -158,7 +166,7 @@ def main():
     for name, g in full.items():
         if name.startswith("layers."):
             _, idx, rest = name.split(".", 2)
-            name = f"layers.{int(idx) + eng.model.layer_start}.{rest}"
+            name = f"layers.{eng.model.layer_ids[int(idx)]}.{rest}"
         r = ref["grads"][name]
         err = (g - r).abs().max().item()
         assert err <= tol * (r.abs().max().item() + 1e-6) + (1e-3 if cuda else 0), (name, err, r.abs().max().item(), g.abs().max().item(), (g - 2 * r).abs().max().item())
