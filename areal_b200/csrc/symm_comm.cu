@@ -75,6 +75,31 @@ __global__ void push_all_kernel(PeerPtrs dst, int world, const uint4* __restrict
   }
 }
 
+// Plan-driven weight push (trainer -> rollout with re-sharding): segment s copies `rows` rows of
+// `row16` 16-byte vectors from src (row pitch src_pitch16) into every destination buffer at dst_off16
+// (row pitch dst_pitch16). One block per segment piece; the host cuts large segments into pieces so the
+// grid fills the machine. A tensor-parallel shard of a column-split weight lands as a strided block
+// inside the full matrix, a row-split shard or an expert block as a contiguous range.
+struct PushSeg {
+  long long src_off16, dst_off16;
+  long long src_pitch16, dst_pitch16;
+  int rows, row16;
+};
+
+__global__ void push_plan_kernel(PeerPtrs dst, int world, const uint4* __restrict__ src,
+                                 const PushSeg* __restrict__ segs, int nsegs) {
+  for (int s = blockIdx.x; s < nsegs; s += gridDim.x) {
+    const PushSeg g = segs[s];
+    const long long total = static_cast<long long>(g.rows) * g.row16;
+    for (long long i = threadIdx.x; i < total; i += blockDim.x) {
+      const long long r = i / g.row16, c = i - r * g.row16;
+      const uint4 v = src[g.src_off16 + r * g.src_pitch16 + c];
+      const long long at = g.dst_off16 + r * g.dst_pitch16 + c;
+      for (int p = 0; p < world; ++p) reinterpret_cast<uint4*>(dst.p[p])[at] = v;
+    }
+  }
+}
+
 // all-to-all: chunk p of src (chunk16 uint4 each) goes to peer p at slot `rank`.
 __global__ void a2a_push_kernel(PeerPtrs dst, int world, int rank, const uint4* __restrict__ src,
                                 long long chunk16) {
@@ -224,6 +249,21 @@ int b200_push_all(void* const* peer_bufs, int world, const void* src, long long 
   if (bytes == 0) return 0;
   push_all_kernel<<<grid_for(bytes / 16), 256, 0, stream>>>(d, world, (const uint4*)src, bytes / 16,
                                                             dst_offset_bytes / 16);
+  B200_CHECK(cudaGetLastError());
+  return 0;
+}
+
+// segs: device array of `nsegs` PushSeg records (6 x int64-sized fields: src_off16, dst_off16, src_pitch16,
+// dst_pitch16, then rows and row16 as two int32). All offsets and pitches in 16-byte units.
+int b200_push_plan(void* const* peer_bufs, int world, const void* src, const void* segs, int nsegs,
+                   cudaStream_t stream) {
+  using namespace b200;
+  PeerPtrs d;
+  if (!fill(d, peer_bufs, world)) return -100;
+  if (nsegs <= 0) return 0;
+  const int maxg = sm_count() * 8;
+  push_plan_kernel<<<nsegs < maxg ? nsegs : maxg, 512, 0, stream>>>(d, world, (const uint4*)src,
+                                                                    (const PushSeg*)segs, nsegs);
   B200_CHECK(cudaGetLastError());
   return 0;
 }

@@ -34,6 +34,7 @@ from typing import Any
 
 import numpy as np
 import torch
+import torch.distributed as dist
 
 from ..api.cli_args import InferenceEngineConfig, NativeRolloutConfig
 from ..api.engine_api import InferenceEngine
@@ -264,6 +265,7 @@ class NativeRolloutEngine(InferenceEngine):
         self._idle = threading.Event()
         self._idle.set()
         self._step_lock = threading.Lock()
+        self.weight_pusher = None  # (WeightPusher, cpu group) when a colocated trainer is model-parallel
         # host seconds spent in the phases of decode steps (plan / parameter lookup / stage+replay+sync / commit)
         self._phase_s = {"plan": 0.0, "params": 0.0, "run": 0.0, "commit_deliver": 0.0, "stage": 0.0, "wait": 0.0,
                          "prefill": 0.0, "paused": 0.0, "idle": 0.0}
@@ -719,6 +721,18 @@ class NativeRolloutEngine(InferenceEngine):
         copy over NVLink when the two engines sit on different GPUs)."""
         with self._step_lock:
             self._vis_cache.clear()
+        if self.weight_pusher is not None:
+            # a model-parallel trainer on the same GPUs: every trainer rank stores its share of a re-sharding
+            # plan into every rank's rollout buffer (peer memory). All engines pause before anyone writes and
+            # resume only after every write has landed.
+            pusher, group = self.weight_pusher
+            dist.barrier(group=group)
+            pusher.push()
+            torch.cuda.current_stream(self.device).synchronize()
+            dist.barrier(group=group)
+            if version is not None:
+                self._version = version
+            return
         src = getattr(trainer, "weight_flat", trainer.flat).flat
         dst = self.flat.flat
         assert src.numel() >= dst.numel() or dst.numel() >= src.numel()

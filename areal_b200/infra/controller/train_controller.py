@@ -65,6 +65,18 @@ def merge_outputs(outs: list[Any], rows_all: list[list[int]]) -> Any:
             else:
                 merged[idx] = o
         return merged
+    if isinstance(first, dict) and any(torch.is_tensor(v) for v in first.values()):
+        # a batch: per-sample tensors are merged back in the original order, everything else is taken from the
+        # first rank
+        n_rows = [len(r) for r in rows_all]
+        out = {}
+        for k, v in first.items():
+            if torch.is_tensor(v) and v.dim() >= 1 and all(torch.is_tensor(o[k]) and o[k].shape[0] == n
+                                                           for o, n in zip(outs, n_rows)):
+                out[k] = merge_outputs([o[k] for o in outs], rows_all)
+            else:
+                out[k] = v
+        return out
     if isinstance(first, dict):
         keys = first.keys()
         return {k: (sum(float(o[k]) for o in outs) / len(outs)) if isinstance(first[k], (int, float)) else first[k]
@@ -165,6 +177,19 @@ class TrainController:
 
     def eval_batch(self, input_: dict[str, Any], loss_fn, loss_weight_fn):
         return self._data_call("eval_batch", input_, loss_fn, loss_weight_fn)
+
+    # algorithm methods of an actor / critic engine created in the workers (``trainer.ppo.actor.PPOActorEngine``)
+    def compute_logp(self, input_: dict[str, Any], *args, **kwargs):
+        return self._data_call("compute_logp", input_, *args, **kwargs)
+
+    def compute_values(self, input_: dict[str, Any], *args, **kwargs):
+        return self._data_call("compute_values", input_, *args, **kwargs)
+
+    def compute_advantages(self, input_: dict[str, Any], *args, **kwargs):
+        return self._data_call("compute_advantages", input_, *args, **kwargs)
+
+    def ppo_update(self, input_: dict[str, Any], *args, **kwargs):
+        return self._data_call("ppo_update", input_, *args, **kwargs)
 
     def train(self, mode: bool = True):
         self._custom_function_call("train", mode)

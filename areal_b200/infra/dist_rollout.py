@@ -65,15 +65,22 @@ class DisaggTopology:
 
 def exchange_weight_buffers(topo: DisaggTopology, rollout_engine=None, device_index: int = 0) -> list[int]:
     """Collective over the world: rollout ranks export their flat weight buffer, trainer
-    ranks map all of them. Returns the mapped pointers on trainer ranks ([] on rollout ranks)."""
+    ranks map all of them. Returns the mapped pointers on trainer ranks ([] on rollout ranks).
+    The rollout engine's parameter layout travels along (``topo.rollout_layout``): a model-parallel trainer
+    needs it to re-shard on the way (``infra/weight_plan.py``)."""
     handle = None
-    if topo.is_rollout and rollout_engine.flat.cuda:
-        handle = (rollout_engine.flat.param_buf.ipc_handle(), rollout_engine.flat.numel)
+    if topo.is_rollout:
+        from .weight_plan import rollout_layout
+
+        layout = rollout_layout(rollout_engine.flat) if topo.rank == topo.gen_ranks[0] else None
+        handle = (rollout_engine.flat.param_buf.ipc_handle() if rollout_engine.flat.cuda else None,
+                  rollout_engine.flat.numel, layout)
     handles: list[Any] = [None] * topo.world
     dist.all_gather_object(handles, handle, group=topo.all_cpu_group)
+    topo.rollout_layout = handles[topo.gen_ranks[0]][2]
     if topo.is_rollout:
         return []
-    if any(handles[g] is None for g in topo.gen_ranks):
+    if any(handles[g][0] is None for g in topo.gen_ranks):
         return []  # CPU ranks: weights travel over gloo instead (see receive_weights)
     return [open_ipc_handle(handles[g][0], device_index) for g in topo.gen_ranks]
 
@@ -164,6 +171,7 @@ class RemoteRolloutClient(InferenceEngine):
         self._table = (ctypes.c_void_p * max(len(weight_ptrs), 1))(*weight_ptrs) if weight_ptrs else None
         self.last_pause_latency = 0.0
         self.rollout_stats: dict[int, dict[str, float]] = {}  # rollout rank -> its engine's latest counters
+        self._pusher = None
 
     def prepare_batch(self, dataloader=None, workflow=None, workflow_kwargs=None, should_accept_fn=None,
                       group_size=1, dynamic_bs=False):
@@ -201,6 +209,21 @@ class RemoteRolloutClient(InferenceEngine):
         f = getattr(trainer, "weight_flat", trainer.flat)
         itemsize = f.flat.element_size()
         shard = f.flat[f.shard_offset: f.shard_offset + f.shard_numel]
+        ps = getattr(trainer, "parallel", None)
+        if ps is not None and ps.tp_size * ps.pp_size * ps.ep_size > 1:
+            # the trainer holds shards (slices of fused projections, a stage's blocks, some experts): each
+            # rank pushes its share of a re-sharding plan straight into every rollout buffer
+            if not self.weight_ptrs:
+                raise NotImplementedError("re-sharding weight push needs CUDA peer memory")
+            if self._pusher is None:
+                from .weight_plan import WeightPusher
+
+                self._pusher = WeightPusher(trainer, self.weight_ptrs, self.topo.rollout_layout)
+            self._pusher.push()
+            torch.cuda.current_stream().synchronize()
+            if version is not None:
+                self._version = version
+            return
         if not self.weight_ptrs:
             for g in self.led:
                 dist.send_object_list([("weights", f.shard_numel)], dst=g, group=self.topo.ctl_group)

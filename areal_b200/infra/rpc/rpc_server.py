@@ -154,6 +154,8 @@ def create_app() -> FastAPI:
                 out = getattr(engines[name], method)(*args, **kwargs)
             if hasattr(out, "result") and callable(out.result):  # concurrent Future
                 out = out.result()
+            if out is engines[name] or out is getattr(engines[name], "engine", None):
+                out = None  # fluent methods (`initialize`, `train`) return the engine: it stays in this process
             return rtensor.remotize(out) if as_rtensor else out
 
         try:

@@ -16,9 +16,17 @@ Transport. Activations flow p → p+1 and gradients p+1 → p (with virtual stag
 Each *direction* of each neighbour pair has its own two-rank process group, i.e. its own NCCL communicator
 and stream: a group carries one ordered stream of messages one way, sender and receiver enumerate it in the
 same order (both follow the schedule), so plain ``isend`` / ``irecv`` can never wait on each other in a
-cycle and no send has to be grouped with a receive. Receives are posted one action ahead and sends are
-never waited for before the end of the step, so transfers overlap the compute of neighbouring actions.
-``x`` and the residual stream travel as two messages; nothing is stacked or cloned.
+cycle and no send has to be grouped with a receive. Sends are never waited for before the end of the step,
+so a stage goes on computing while its output travels. ``x`` and the residual stream travel as two
+messages; nothing is stacked or cloned.
+
+Two NCCL facts shape the executor. (1) Creating a communicator blocks the host until the peer creates it
+too, so every link is opened by a one-element handshake in a fixed ring order before the first step, not
+lazily in the middle of a schedule. (2) A receive posted ahead of time is a kernel that spins on the device
+until the peer sends; any device-wide synchronisation on this rank (a ``cudaMalloc`` of the caching
+allocator, the first load of a kernel's module) then waits for the peer, and in the steady state of 1F1B the
+peer's send can in turn wait for this rank: a cycle. Receives are therefore posted ahead only on CPU (gloo,
+where they are host-side requests); on CUDA a receive is posted when its action starts.
 
 Reference: areal/experimental/models/archon/pipeline_parallel.py:48-82 (``build_pipeline_schedule``:
 1F1B, Interleaved1F1B, zero-bubble variants) and :349-494, options areal/api/cli_args.py:537-700; Megatron's
@@ -199,6 +207,33 @@ class PipelineRunner:
         self.links, self.rank, self.P, self.V = links, pp_rank, pp_size, virtual
         self.schedule = schedule
         self.dtype, self.device = dtype, device
+        import os
+
+        self.prefetch = (device.type != "cuda") if os.environ.get("AREAL_B200_PP_PREFETCH") is None \
+            else os.environ["AREAL_B200_PP_PREFETCH"] == "1"
+        if not getattr(links, "opened", False):
+            self._open_links()
+            links.opened = True
+
+    def _open_links(self):
+        """One element over every link this rank uses, in ring order (edge i joins stage i and stage i + 1):
+        both ends of an edge reach it as their next step, so the blocking communicator set-up of NCCL happens
+        here, pairwise and in a chain, and never inside a schedule."""
+        L, P = self.links, self.P
+        token = torch.zeros(1, dtype=self.dtype, device=self.device)
+        edges = []  # (edge index, [(group, i_send)])
+        if self.rank < P - 1 or self.V > 1:
+            edges.append((self.rank, [(L.fwd_next, True, L.next), (L.bwd_next, False, L.next)]))
+        if self.rank > 0 or self.V > 1:
+            edges.append(((self.rank - 1) % P, [(L.fwd_prev, False, L.prev), (L.bwd_prev, True, L.prev)]))
+        for _, ops in sorted(edges, key=lambda e: e[0]):
+            for group, sending, peer in ops:
+                if sending:
+                    dist.send(token, dst=peer, group=group)
+                else:
+                    dist.recv(token, src=peer, group=group)
+        if self.device.type == "cuda":
+            torch.cuda.current_stream(self.device).synchronize()
 
     # -- which virtual stage talks to whom
     def _vs(self, chunk: int) -> int:
@@ -233,14 +268,26 @@ class PipelineRunner:
             elif kind == "B" and not self._is_last(c):
                 posted[i] = self._recv(shape_of(mb), L.next, L.bwd_next)
 
+        import os as _os
+        import sys as _sys
+
+        debug = _os.environ.get("AREAL_B200_PP_DEBUG") == "1"
+
+        def note(msg):
+            if debug:
+                print(f"[pp rank {self.rank}] {msg}", file=_sys.stderr, flush=True)
+
         post(0)
         for i, (kind, mb, c) in enumerate(acts):
+            note(f"action {i}: {kind} mb={mb} chunk={c}: posting receives")
             post(i)
-            post(i + 1)  # the next action's input travels while this one computes
+            if self.prefetch:
+                post(i + 1)  # the next action's input travels while this one computes
             got = posted.pop(i, None)
             if got is not None:
                 for w in got[0]:
                     w.wait()
+                note(f"action {i}: input received")
             if kind == "F":
                 stage_in = None
                 if got is not None:
@@ -278,6 +325,8 @@ class PipelineRunner:
                     gr = r_in.grad if r_in.grad is not None else torch.zeros_like(r_in)
                     sends.add(dist.isend(gx, dst=L.prev, group=L.bwd_prev), gx)
                     sends.add(dist.isend(gr, dst=L.prev, group=L.bwd_prev), gr)
+        note("all actions issued: waiting for sends")
         sends.wait_all()
+        note("step done")
         assert not saved and not posted
         return results

@@ -271,3 +271,35 @@ def _record_fused_stats(st: torch.Tensor, loss_mask: torch.Tensor, entropy):
     if entropy is not None:
         m = loss_mask
         stats_tracker.scalar(**{"ppo_actor/entropy": float((entropy.detach().float() * m).sum() / n)})
+
+
+class PPOActorEngine:
+    """A train engine with the actor's algorithm methods on it: the object a single-controller run creates in
+    every worker process (``TrainController("...PPOActorEngine", config.actor, scheduler)``), so that
+    ``compute_logp`` / ``compute_advantages`` / ``ppo_update`` run next to the model and only batches and
+    statistics cross the process boundary. Every other attribute is the engine's.
+    Reference: the ``FSDPPPOActor`` / ``as_controller`` pairing of areal/trainer/rl_trainer.py:876,933-1041."""
+
+    def __init__(self, config: PPOActorConfig):
+        from ...engine.train_engine import B200TrainEngine
+
+        self.engine = B200TrainEngine(config)
+        self.actor = PPOActor(config, self.engine)
+
+    def compute_logp(self, data):
+        return self.actor.compute_logp(data)
+
+    def compute_advantages(self, data):
+        return self.actor.compute_advantages(data)
+
+    def ppo_update(self, data):
+        return self.actor.ppo_update(data)
+
+    def flat_checksum(self) -> float:
+        """Sum of the weights (tests compare replicas with it)."""
+        return float(self.engine.flat.flat.double().sum())
+
+    def __getattr__(self, name):
+        if name in ("engine", "actor"):
+            raise AttributeError(name)
+        return getattr(self.engine, name)

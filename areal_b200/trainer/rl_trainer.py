@@ -82,6 +82,15 @@ class _ListLoader:
 
 
 class PPOTrainer:
+    def __new__(cls, config: PPOConfig, *args, **kwargs):
+        # `scheduler.type` set and no torchrun environment: this process is the controller of a
+        # single-controller run and the engines live in scheduler workers (trainer/controller_mode.py)
+        if cls is PPOTrainer and getattr(config.scheduler, "type", None) and "RANK" not in os.environ:
+            from .controller_mode import ControllerPPOTrainer
+
+            return ControllerPPOTrainer(config, *args, **kwargs)
+        return super().__new__(cls)
+
     def __init__(self, config: PPOConfig, train_dataset, valid_dataset=None, tokenizer=None, processor=None):
         self.tokenizer = tokenizer
         self.processor = processor  # vision-language models: saved next to the weights
@@ -166,6 +175,9 @@ class PPOTrainer:
         elif self.colocated:
             self.rollout_client = self.rollout
             self.weight_meta = WeightUpdateMeta.from_p2p()
+            ps = self.actor_alloc.parallel
+            if ps.tp_size * ps.pp_size * ps.ep_size > 1:
+                self._connect_colocated_model_parallel(use_cuda)
         else:
             dev = torch.cuda.current_device() if use_cuda else 0
             ptrs = exchange_weight_buffers(self.topo, self.rollout, dev)
@@ -200,6 +212,23 @@ class PPOTrainer:
                 save_config(config, get_log_path(config))
             except Exception as e:
                 logger.warning(f"could not save the config: {e}")
+
+    def _connect_colocated_model_parallel(self, use_cuda: bool):
+        """Colocated layout with a tensor- / pipeline- / expert-parallel trainer: every rank's rollout engine
+        holds the whole model, every trainer rank a shard. The ranks exchange handles of their rollout weight
+        buffers so that each trainer rank can store its share of the re-sharding plan into all of them."""
+        if not use_cuda:
+            raise NotImplementedError("a colocated model-parallel trainer pushes weights through CUDA peer memory")
+        from ..infra.weight_plan import WeightPusher, rollout_layout
+        from ..parallel.symm_mem import open_ipc_handle
+
+        flat = self.rollout.flat
+        handles = [None] * self.world
+        group = self.actor_engine._all_cpu_group
+        dist.all_gather_object(handles, flat.param_buf.ipc_handle(), group=group)
+        dev = torch.cuda.current_device()
+        ptrs = [flat.flat.data_ptr() if r == self.rank else open_ipc_handle(h, dev) for r, h in enumerate(handles)]
+        self.rollout.weight_pusher = (WeightPusher(self.actor_engine, ptrs, rollout_layout(flat)), group)
 
     def __enter__(self):
         return self

@@ -18,7 +18,10 @@ the trainer stream over K steps (max over ranks); ``e2e`` is the wall-clock of K
 steps through the public ``PPOTrainer.train`` API, including the pinned-host → device copy
 of every micro-batch and the device → host read of the step's loss / grad-norm.
 
-``--impl reference`` reports why the reference cannot run on this image.
+``--impl reference`` reports why the reference cannot run on this image; ``--impl libstack`` times the
+libraries its stack is built from (vLLM, HF + FSDP2 + flash-attn, NCCL) on the same shapes, as context.
+``--config 3|4|5`` selects the other benchmark configurations (Ulysses, fp8 + tensor parallel, MoE + expert
+parallel); the default is the headline configuration 2.
 """
 
 from __future__ import annotations
@@ -33,8 +36,11 @@ import sys
 import time
 
 REFERENCE_UNAVAILABLE = (
-    "reference not installable offline: its build backend `uv_build` is not in the wheelhouse and its "
-    "config entry point imports hydra/omegaconf (absent); its rollout needs SGLang (absent) or a pinned vLLM")
+    "the reference cannot start on this image: its trainer entry points import hydra and omegaconf "
+    "(areal/api/cli_args.py:14-17), its FSDP engine imports peft (areal/engine/fsdp_engine.py:21), and flask, "
+    "colorlog, tensordict, torchao, ray, megatron-core, mbridge and SGLang are needed further down; none of them is "
+    "installed or in /opt/wheelhouse (pip install of the tree itself also stops at its build backend uv_build). "
+    "vLLM, flash-attn and transformers ARE installed: `--impl libstack` times those libraries on the same shapes")
 
 
 def parse_args():
@@ -42,17 +48,23 @@ def parse_args():
     p.add_argument("--gpus", type=int, default=1)
     p.add_argument("--steps", type=int, default=2)
     p.add_argument("--warmup", type=int, default=3)
-    p.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    p.add_argument("--model", default="qwen3-1.7b")
-    p.add_argument("--prompts-per-gpu", type=int, default=8)
+    p.add_argument("--impl", default="ours", choices=["ours", "reference", "libstack"])
+    p.add_argument("--config", type=int, default=2, choices=[2, 3, 4, 5],
+                   help="benchmark configuration: 2 = Qwen3-1.7B native:dN/2 + fsdp:dN/2 (the headline, default); "
+                        "3 = Qwen3-8B rollout dN/2 + trainer Ulysses cN/2; 4 = Qwen2.5-7B block-scaled fp8, trainer "
+                        "tp2 x dN/4; 5 = Qwen3-30B-A3B, expert-parallel trainer time-sharing the GPUs with rollout")
+    p.add_argument("--model", default=None)
+    p.add_argument("--prompts-per-gpu", type=int, default=None)
     p.add_argument("--group", type=int, default=8)
-    p.add_argument("--prompt-min", type=int, default=128)
-    p.add_argument("--prompt-max", type=int, default=512)
-    p.add_argument("--resp-min", type=int, default=256)
-    p.add_argument("--resp-max", type=int, default=4096)
+    p.add_argument("--prompt-min", type=int, default=None)
+    p.add_argument("--prompt-max", type=int, default=None)
+    p.add_argument("--resp-min", type=int, default=None)
+    p.add_argument("--resp-max", type=int, default=None)
     p.add_argument("--staleness", type=int, default=4)
-    p.add_argument("--max-tokens-per-mb", type=int, default=16384)
+    p.add_argument("--max-tokens-per-mb", type=int, default=None)
     p.add_argument("--kv-gb", type=float, default=0.0, help="KV-cache budget per rollout GPU (0 = automatic)")
+    p.add_argument("--no-fused-comm-check", action="store_true",
+                   help="N >= 2: skip the untimed check of the fused compute+collective kernels")
     p.add_argument("--layers", type=int, default=0, help="debug only: override the layer count (invalidates the result)")
     return p.parse_args()
 
@@ -197,6 +209,49 @@ def summarize_roles(roles: list, window_s: float, n_gen: int, n_train: int, trai
     }
 
 
+# Per configuration: model preset, prompts per GPU (weak scaling: the named global batch at N = 8), prompt and
+# response length ranges, micro-batch token budget.
+CONFIGS = {
+    2: dict(model="qwen3-1.7b", prompts_per_gpu=8, prompt=(128, 512), resp=(256, 4096), mb=16384),
+    3: dict(model="qwen3-8b", prompts_per_gpu=4, prompt=(512, 512), resp=(1024, 16384), mb=32768),
+    4: dict(model="qwen2.5-7b", prompts_per_gpu=4, prompt=(256, 256), resp=(256, 8192), mb=16384),
+    5: dict(model="qwen3-30b-a3b", prompts_per_gpu=2, prompt=(512, 512), resp=(512, 8192), mb=16384),
+}
+
+
+def resolve_config(args, N: int) -> dict:
+    """Fills unset arguments from the chosen configuration and derives the allocation strings for N GPUs."""
+    c = CONFIGS[args.config]
+    args.model = args.model or c["model"]
+    args.prompts_per_gpu = args.prompts_per_gpu or c["prompts_per_gpu"]
+    args.prompt_min = args.prompt_min or c["prompt"][0]
+    args.prompt_max = args.prompt_max or c["prompt"][1]
+    args.resp_min = args.resp_min or c["resp"][0]
+    args.resp_max = args.resp_max or c["resp"][1]
+    args.max_tokens_per_mb = args.max_tokens_per_mb or c["mb"]
+    half = max(N // 2, 1)
+    if args.config == 2:
+        n_gen = n_train = N if N == 1 else half
+        rollout, actor = f"native:d{n_gen}", f"fsdp:d{n_train}"
+    elif args.config == 3:
+        # Ulysses sequence parallelism over all trainer GPUs (d1 x c4 at N = 8)
+        n_gen = n_train = N if N == 1 else half
+        rollout, actor = f"native:d{n_gen}", f"fsdp:d1c{n_train}"
+    elif args.config == 4:
+        # tensor parallel 2 inside the trainer half (d2 x t2 at N = 8); the rollout engine serves one model per GPU
+        if N < 4 or N % 4:
+            raise SystemExit("--config 4 needs a multiple of 4 GPUs (trainer tp 2 on one half, rollout on the other)")
+        n_gen = n_train = half
+        rollout, actor = f"native:d{n_gen}", f"megatron:d{n_train // 2}t2"
+    else:
+        # every GPU hosts a rollout engine and one expert-parallel trainer rank (time-shared)
+        if N < 2:
+            raise SystemExit("--config 5 needs at least 2 GPUs (expert parallelism)")
+        n_gen = n_train = N
+        rollout, actor = f"native:d{N}", f"megatron:d{N}e{N}"
+    return dict(n_gen=n_gen, n_train=n_train, rollout=rollout, actor=actor, colocated=(N == 1 or args.config == 5))
+
+
 def main():
     args = parse_args()
     if args.impl == "reference":
@@ -204,6 +259,12 @@ def main():
         return 0
 
     sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+    if args.impl == "libstack":
+        # context numbers from the installed libraries (vLLM, HF + FSDP2 + flash-attn, NCCL) on the benchmark's
+        # shapes: NOT the reference, never a reference ratio (see baseline/libstack.py)
+        from baseline import libstack
+
+        return libstack.main(args.gpus)
     import torch
     import torch.distributed as dist
 
@@ -218,7 +279,8 @@ def main():
     if world != args.gpus:
         raise SystemExit(f"--gpus {args.gpus} but WORLD_SIZE={world}; launch with torchrun for N > 1")
     N = args.gpus
-    n_gen = n_train = N if N == 1 else N // 2
+    lay = resolve_config(args, N)
+    n_gen, n_train = lay["n_gen"], lay["n_train"]
     group = args.group
     prompts_global = args.prompts_per_gpu * N
     model_over = {"num_hidden_layers": args.layers} if args.layers else {}
@@ -227,7 +289,9 @@ def main():
     kv_per_token = 2 * (args.layers or mc.num_hidden_layers) * mc.num_key_value_heads * mc.head_dim * 2
     per_rollout_seqs = prompts_global * group // n_gen
     inflight = per_rollout_seqs * (args.staleness + 1)
-    kv_gb = args.kv_gb or min(70.0 if N == 1 else 120.0, inflight * (ctx * 0.75) * kv_per_token / 2**30)
+    weights_gb = mc.num_params() * 2 / 2**30
+    kv_cap = (70.0 if args.config != 5 else 40.0) if lay["colocated"] else max(150.0 - weights_gb, 20.0) * 0.8
+    kv_gb = args.kv_gb or min(kv_cap, inflight * (ctx * 0.75) * kv_per_token / 2**30)
     block = 16
     n_blocks = int(kv_gb * 2**30 / (kv_per_token * block))
 
@@ -237,7 +301,7 @@ def main():
     cfg.train_dataset.shuffle = False
     cfg.gconfig = GenerationHyperparameters(n_samples=group, max_new_tokens=args.resp_max, temperature=1.0)
     cfg.actor = PPOActorConfig(
-        experiment_name="bench", trial_name=f"n{N}", backend=f"fsdp:d{n_train}", model_preset=args.model,
+        experiment_name="bench", trial_name=f"n{N}", backend=lay["actor"], model_preset=args.model,
         model_overrides=model_over, init_from_scratch=True, dtype="bfloat16",
         optimizer=OptimizerConfig(lr=1e-6, weight_decay=0.01, gradient_clipping=1.0),
         mb_spec=MicroBatchSpec(max_tokens_per_mb=args.max_tokens_per_mb), ppo_n_minibatches=1,
@@ -247,11 +311,17 @@ def main():
         rejection_sampling=RejectionSamplingConfig(level="token", action="mask", metric="ratio", upper=5.0),
         max_new_tokens=args.resp_max)
     cfg.rollout = InferenceEngineConfig(
-        backend=f"native:d{n_gen}", max_head_offpolicyness=args.staleness,
+        backend=lay["rollout"], max_head_offpolicyness=args.staleness,
         max_concurrent_rollouts=prompts_global * (args.staleness + 1),
         native=NativeRolloutConfig(model_preset=args.model, model_overrides=model_over, context_length=ctx,
                                    max_num_seqs=min(1024, inflight), max_num_batched_tokens=32768,
                                    kv_block_size=block, num_kv_blocks=n_blocks))
+    if args.config == 4:
+        from areal_b200.api.cli_args import FP8EngineConfig
+
+        cfg.actor.megatron.fp8_config = FP8EngineConfig(mode="e4m3", recipe="blockwise")
+    if args.config in (3, 5):
+        cfg.actor.gradient_checkpointing = True  # 16k-token responses / 48 MoE blocks: recompute block activations
     _propagate_names(cfg)
 
     g = torch.Generator().manual_seed(1234)
@@ -263,6 +333,22 @@ def main():
 
     W, K = args.warmup, args.steps
     total_steps = W + 2 * K
+    fused_comm = None
+    if N > 1 and not args.no_fused_comm_check:
+        # Outside the timed region: the fused compute+collective kernels (GEMM->reduce-scatter, all-gather->GEMM,
+        # GEMM->all-to-all, all-to-all->GEMM over NVLink peer memory) checked against NCCL and timed on the N ranks
+        # of this very job. The flagship layout (data-parallel rollout + ZeRO trainer) does not call them, so this
+        # is where a scaling run shows that they work at N ranks.
+        import datetime
+
+        torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", 0)))
+        if not dist.is_initialized():
+            dist.init_process_group(backend="nccl", timeout=datetime.timedelta(seconds=7200))
+        from areal_b200.parallel.selfcheck import fused_comm_check
+
+        fused_comm = fused_comm_check(iters=5)
+        torch.cuda.synchronize()
+        dist.barrier()
     trainer = PPOTrainer(cfg, dataset)
     dev = torch.device("cuda", torch.cuda.current_device())
     marks: dict[str, object] = {}
@@ -331,8 +417,11 @@ def main():
     if trainer.is_trainer:
         dev_ms = marks["ev0"].elapsed_time(marks["ev1"])
         wall_s = marks["t1"] - marks["t0"]
-        tok_value = sum(tok_per_step[W:W + K])
-        tok_e2e = sum(tok_per_step[W + K:W + 2 * K])
+        # ranks of one model-parallel replica (tensor / sequence / pipeline peers) train the same batch: the
+        # replica's head counts its tokens
+        counts = 1.0 if trainer.actor_engine.is_data_parallel_head() else 0.0
+        tok_value = counts * sum(tok_per_step[W:W + K])
+        tok_e2e = counts * sum(tok_per_step[W + K:W + 2 * K])
         t = torch.tensor([dev_ms, wall_s, -tok_value, -tok_e2e, max(sync_s[W:]) if sync_s[W:] else 0.0],
                          dtype=torch.float64)
         sums = torch.tensor([tok_value, tok_e2e], dtype=torch.float64)
@@ -343,7 +432,7 @@ def main():
         # per-role view: what each rollout GPU did during the timed window, and how the trainer's step splits
         ro = role_budget(marks.get("ro0", {}), marks.get("ro1", {}))
         mine = {"rollout": ro, "phase_s": {k: sum(p[k] for p in phases[W:W + K]) for k in phase_keys},
-                "resp_tokens": sum(resp_per_step[W:W + K])}
+                "resp_tokens": counts * sum(resp_per_step[W:W + K])}
         roles = [mine]
         if dist.is_initialized() and trainer.actor_engine.world_size > 1:
             roles = [None] * trainer.actor_engine.world_size
@@ -361,7 +450,9 @@ def main():
                     "model": args.model + ("" if not args.layers else f"[layers={args.layers} DEBUG]"),
                     "global_batch": prompts_global * group, "prompts": prompts_global, "group": group,
                     "seq_len": f"prompt U[{args.prompt_min},{args.prompt_max}] + response U[{args.resp_min},{args.resp_max}] (EOS forced)",
-                    "parallelism": ("colocated native:d1|fsdp:d1" if N == 1 else f"native:d{n_gen}+fsdp:d{n_train}"),
+                    "parallelism": (f"colocated {lay['rollout']}|{lay['actor']}" if lay["colocated"]
+                                    else f"{lay['rollout']}+{lay['actor']}"),
+                    "benchmark_config": args.config,
                     "staleness": args.staleness, "max_tokens_per_mb": args.max_tokens_per_mb,
                     "l2": "no explicit flush: every step streams >3.4 GB of weights plus activations, far above the 126 MB L2",
                     "weight_sync_s_max": sync_max,
@@ -378,6 +469,20 @@ def main():
                 "roles": summarize_roles(roles, dev_ms / 1e3, n_gen, n_train, float(sums[0]), K),
                 "fallback_ops": _lib.fallback_counts(),
             }
+            if fused_comm is not None:
+                fc = fused_comm
+                result["extra_keys"] = {
+                    "fused_comm_ok": fc["ok"], "fused_comm_max_err": fc["max_err"],
+                    "fused_comm_status": fc["status_end"] or fc["status"], "fused_comm_ranks": fc["world"],
+                    "fused_comm_shape": fc["shape"],
+                    "fused_vs_unfused_ms": {k: [round(fc[f"t_{k}_fused_ms"], 4), round(fc[f"t_{k}_nccl_ms"], 4)]
+                                            for k in ("gemm_rs", "ag_gemm", "gemm_a2a", "a2a_gemm")},
+                    "fused_frac_of_roofline": {k: round(fc[f"frac_of_roofline_{k}_fused"], 3)
+                                               for k in ("gemm_rs", "ag_gemm", "gemm_a2a", "a2a_gemm")},
+                    "fused_comm_note": "measured outside the timed region on all ranks of this job; unfused = this "
+                                       "library's GEMM + the NCCL collective; roofline = max(FLOPs / measured bf16 "
+                                       "peak, NVLink bytes / 770 GB/s)",
+                }
     if os.environ.get("AREAL_B200_BENCH_DIAG"):
         # host-side view of the rollout engine (stderr only): scheduler counters and where its loop spent time
         eng = getattr(trainer, "rollout", None)

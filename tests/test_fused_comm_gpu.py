@@ -25,6 +25,7 @@ def test_fused_comm_matches_nccl(tmp_path):
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]
     res = json.load(open(out))
+    assert res["ok"], res
     assert res["status"] == 0 and res["status_end"] == 0
     for k in ("all_gather_err", "all_to_all_err"):
         assert res[k] == 0.0, (k, res[k])

@@ -103,7 +103,10 @@ def main():
         eng.initialize(seed=3)
         data = batch
     else:
-        dist.init_process_group("nccl" if cuda else "gloo")
+        import datetime
+
+        # a short collective timeout: a wedged exchange ends with an error instead of hanging the run
+        dist.init_process_group("nccl" if cuda else "gloo", timeout=datetime.timedelta(seconds=120 if cuda else 600))
         world = dist.get_world_size()
         dp = world // (args.tp * args.sp * args.pp)
         eng.create_process_group(ParallelStrategy(tensor_parallel_size=args.tp, context_parallel_size=args.sp,
