@@ -221,6 +221,10 @@ class B200TrainEngine(TrainEngine):
         if not hasattr(self, "device"):
             self.create_process_group()
         cfg = self.config
+        if getattr(cfg.megatron, "use_deterministic_algorithms", False):
+            from ..utils.determinism import set_deterministic_algorithms
+
+            set_deterministic_algorithms(True)
         self.model_config = resolve_model_config(cfg)
         dtype = torch.float32 if self.device.type == "cpu" else getattr(torch, cfg.dtype)
         t0 = time.perf_counter()
@@ -237,7 +241,14 @@ class B200TrainEngine(TrainEngine):
             from ..utils.hf_io import load_hf_weights
 
             load_hf_weights(self.model, cfg.path)
-        if cfg.gradient_checkpointing:
+        family = (cfg.backend or "").split(":")[0]
+        if family == "archon" and cfg.archon.ac_mode != "none" and self.optimizer_config is not None:
+            # the Archon-style options: none | full | selective (layer- or op-level) | memory_budget
+            from ..models.activation_checkpoint import apply_activation_checkpointing
+
+            apply_activation_checkpointing(self.model, cfg.archon.ac_mode, cfg.archon.selective_ac_option,
+                                           cfg.archon.ac_memory_budget)
+        elif cfg.gradient_checkpointing:
             self.model.checkpoint_every = 1
         if self.model_config.is_vl:
             if cfg.enable_tree_training or (pctx is not None and pctx.extras.get("cp_mode") == "zigzag"):

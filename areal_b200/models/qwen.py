@@ -293,13 +293,18 @@ class Block(nn.Module):
             self.mlp = DenseMLP(h, cfg.intermediate_size, dtype, device, pctx, cfg, layer_idx)
         self.eps = cfg.rms_norm_eps
 
-    def forward(self, x, res, cos, sin, pos, meta, attn_fn=None):
+    def forward(self, x, res, cos, sin, pos, meta, attn_fn=None, recompute_mlp: bool = False):
         if res is None:
             y, res = fused.rmsnorm(x, self.input_norm, self.eps), x
         else:
             y, res = fused.rmsnorm(x, self.input_norm, self.eps, residual=res)
         a = self.attn(y, cos, sin, pos, meta, attn_fn)
         y, res = fused.rmsnorm(a, self.post_norm, self.eps, residual=res)
+        if recompute_mlp and torch.is_grad_enabled():
+            # op-selective activation checkpointing: the MLP half keeps only its input
+            from torch.utils.checkpoint import checkpoint
+
+            return checkpoint(self.mlp, y, use_reentrant=False), res
         return self.mlp(y), res
 
 
@@ -481,14 +486,18 @@ class QwenModel(nn.Module):
         else:
             x, res = fused.embedding(input_ids, self.embed), None
         ckpt_every = getattr(self, "checkpoint_every", 0)
+        policy = getattr(self, "ac_policy", None)
         lo, hi = (0, len(self.layers)) if chunk is None else self.chunk_slices[chunk]
         for li in range(lo, hi):
             layer = self.layers[li]
-            if ckpt_every and torch.is_grad_enabled() and li % ckpt_every == 0:
+            whole = (ckpt_every and li % ckpt_every == 0) or (policy is not None and li in policy.full_layers)
+            if whole and torch.is_grad_enabled():
                 # activation checkpointing: keep only the block's inputs, recompute the rest in backward
                 from torch.utils.checkpoint import checkpoint
 
                 x, res = checkpoint(layer, x, res, cos, sin, pos, meta, attn_fn, use_reentrant=False)
+            elif policy is not None and policy.mlp_only:
+                x, res = layer(x, res, cos, sin, pos, meta, attn_fn, recompute_mlp=True)
             else:
                 x, res = layer(x, res, cos, sin, pos, meta, attn_fn)
             if layer_adds is not None and li < len(layer_adds[1]):

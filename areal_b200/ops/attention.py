@@ -127,6 +127,16 @@ class _VarlenAttn(torch.autograd.Function):
     @staticmethod
     def backward(ctx, do):
         q, k, v, o, lse = ctx.saved_tensors
+        from ..utils.determinism import deterministic_mode
+
+        if deterministic_mode():
+            # the kernel accumulates dQ tiles with floating-point atomics (arrival order): bit-stable runs
+            # recompute the backward through the PyTorch formulation instead
+            with torch.enable_grad():
+                qf, kf, vf = (t.detach().float().requires_grad_() for t in (q, k, v))
+                of = attention_ref(qf, kf, vf, ctx.meta.cu_cpu, ctx.scale)
+                dq, dk, dv = torch.autograd.grad(of, (qf, kf, vf), do.float())
+            return dq.to(q.dtype), dk.to(k.dtype), dv.to(v.dtype), None, None
         dq, dk, dv = _bwd_cuda(q, k, v, o, do, lse, ctx.meta, ctx.scale)
         return dq, dk, dv, None, None
 

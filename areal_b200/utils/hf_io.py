@@ -48,14 +48,54 @@ def remove_weight_files(path: str, tag: str | None = None):
         (p / "model.safetensors.index.json").unlink(missing_ok=True)
 
 
-def iter_hf_tensors(path: str) -> Iterator[tuple[str, torch.Tensor]]:
+def dequant_fp8_blockwise(w: torch.Tensor, scale_inv: torch.Tensor, block: int = 128,
+                          dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+    """``out[i, j] = w[i, j] * scale_inv[i // block, j // block]`` for an e4m3 weight with one fp32 scale per
+    ``block x block`` tile (the layout of block-quantised HF checkpoints: ``<name>.weight`` in float8 beside
+    ``<name>.weight_scale_inv``). Reference: areal/experimental/models/archon/fp8_checkpoint.py:119-150."""
+    M, N = w.shape
+    s = scale_inv.float().repeat_interleave(block, 0)[:M].repeat_interleave(block, 1)[:, :N]
+    return (w.float() * s).to(dtype)
+
+
+_FP8 = tuple(getattr(torch, n) for n in ("float8_e4m3fn", "float8_e5m2") if hasattr(torch, n))
+
+
+def iter_hf_tensors(path: str, dequant_dtype: torch.dtype = torch.bfloat16) -> Iterator[tuple[str, torch.Tensor]]:
+    """``(name, tensor)`` of every weight. Block-quantised fp8 weights are returned dequantised (their
+    ``*_scale_inv`` companions are consumed here and not yielded); the block size comes from ``config.json``
+    (``quantization_config.weight_block_size``, default 128)."""
     files = weight_files(path)
     if not files:
         raise FileNotFoundError(f"no .safetensors files under {path}")
+    block = 128
+    cfg = Path(path) / "config.json"
+    if cfg.exists():
+        try:
+            q = json.load(open(cfg)).get("quantization_config") or {}
+            block = int((q.get("weight_block_size") or [128])[0])
+        except (ValueError, TypeError, json.JSONDecodeError):
+            pass
+    # a weight and its scale may sit in different files: index the scales first
+    scale_file: dict[str, Path] = {}
     for f in files:
         with safe_open(str(f), framework="pt", device="cpu") as sf:
             for name in sf.keys():
-                yield name, sf.get_tensor(name)
+                if name.endswith("_scale_inv"):
+                    scale_file[name] = f
+    for f in files:
+        with safe_open(str(f), framework="pt", device="cpu") as sf:
+            for name in sf.keys():
+                if name in scale_file:
+                    continue
+                t = sf.get_tensor(name)
+                if t.dtype in _FP8:
+                    sname = name + "_scale_inv"
+                    if sname not in scale_file:
+                        raise KeyError(f"{name} is stored in {t.dtype} but {sname} is missing")
+                    with safe_open(str(scale_file[sname]), framework="pt", device="cpu") as ss:
+                        t = dequant_fp8_blockwise(t, ss.get_tensor(sname), block, dequant_dtype)
+                yield name, t
 
 
 def load_hf_weights(model, path: str, strict: bool = True):

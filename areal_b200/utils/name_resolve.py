@@ -16,6 +16,7 @@ import threading
 import time
 import uuid
 from pathlib import Path
+from typing import Any
 
 
 class NameEntryExistsError(Exception):
@@ -180,15 +181,181 @@ class NfsNameRecordRepository(NameRecordRepository):
                 pass
 
 
+class KVNameRecordRepository(NameRecordRepository):
+    """Records in an external key-value service behind a four-call client: ``put(key, value, lease=None)``,
+    ``get(key) -> (value | None, meta)``, ``get_prefix(prefix) -> iterable of (value, meta-with-.key)``,
+    ``delete(key)``, plus ``lease(ttl)`` returning an object with ``refresh()`` / ``revoke()`` for keep-alive
+    entries. That is the interface of the ``etcd3`` client (``Etcd3NameRecordRepository`` opens one); a
+    Ray-backed store only needs the same five calls (``RayNameRecordRepository`` wraps a named actor).
+    Reference: areal/utils/name_resolve.py:412 (etcd3) and :883 (Ray)."""
+
+    def __init__(self, client, keepalive_interval: float = 0.3):
+        self.client = client
+        self._mine: set[str] = set()
+        self._leases: dict[str, Any] = {}
+        self._stop = threading.Event()
+        self._keepalive = None
+        self._interval = keepalive_interval
+
+    @staticmethod
+    def _s(v):
+        return v.decode() if isinstance(v, (bytes, bytearray)) else v
+
+    def add(self, name, value, delete_on_exit=True, keepalive_ttl=None, replace=False):
+        name = name.rstrip("/")
+        if not replace and self.client.get(name)[0] is not None:
+            raise NameEntryExistsError(name)
+        lease = None
+        if keepalive_ttl is not None:
+            lease = self.client.lease(int(max(keepalive_ttl, 1)))
+            self._leases[name] = lease
+            if self._keepalive is None:
+                self._keepalive = threading.Thread(target=self._refresh_loop, daemon=True, name="name-resolve-keepalive")
+                self._keepalive.start()
+        self.client.put(name, str(value), lease=lease)
+        if delete_on_exit:
+            self._mine.add(name)
+
+    def _refresh_loop(self):
+        while not self._stop.wait(self._interval):
+            for lease in list(self._leases.values()):
+                try:
+                    lease.refresh()
+                except Exception:
+                    pass
+
+    def delete(self, name):
+        name = name.rstrip("/")
+        if self.client.get(name)[0] is None:
+            raise NameEntryNotFoundError(name)
+        self.client.delete(name)
+        self._mine.discard(name)
+        lease = self._leases.pop(name, None)
+        if lease is not None:
+            lease.revoke()
+
+    def clear_subtree(self, name_root):
+        for key in self.find_subtree(name_root):
+            self.client.delete(key)
+            self._mine.discard(key)
+
+    def get(self, name):
+        v, _ = self.client.get(name.rstrip("/"))
+        if v is None:
+            raise NameEntryNotFoundError(name)
+        return self._s(v)
+
+    def _prefix(self, name_root):
+        root = name_root.rstrip("/")
+        out = []
+        for v, meta in self.client.get_prefix(root):
+            key = self._s(meta.key)
+            if key == root or key.startswith(root + "/"):
+                out.append((key, self._s(v)))
+        return sorted(out)
+
+    def get_subtree(self, name_root) -> list[str]:
+        return [v for _, v in self._prefix(name_root)]
+
+    def find_subtree(self, name_root) -> list[str]:
+        return [k for k, _ in self._prefix(name_root)]
+
+    def reset(self):
+        self._stop.set()
+        for name in list(self._mine):
+            try:
+                self.client.delete(name)
+            except Exception:
+                pass
+        self._mine.clear()
+        for lease in self._leases.values():
+            try:
+                lease.revoke()
+            except Exception:
+                pass
+        self._leases.clear()
+
+
+class Etcd3NameRecordRepository(KVNameRecordRepository):
+    def __init__(self, addr: str = "localhost:2379", user: str | None = None, password: str | None = None):
+        try:
+            import etcd3
+        except ImportError as e:
+            raise ImportError("name_resolve.type = 'etcd3' needs the `etcd3` package and a reachable etcd "
+                              "server; use 'nfs' (shared directory) where neither is available") from e
+        host, _, port = addr.partition(":")
+        super().__init__(etcd3.client(host=host or "localhost", port=int(port or 2379), user=user, password=password))
+
+
+class RayNameRecordRepository(KVNameRecordRepository):
+    """A detached Ray actor holding the records; every process of the job talks to the same actor."""
+
+    def __init__(self, actor_name: str = "areal_b200_name_resolve", namespace: str = "areal_b200"):
+        try:
+            import ray
+        except ImportError as e:
+            raise ImportError("name_resolve.type = 'ray' needs Ray; use 'nfs' where it is not installed") from e
+
+        @ray.remote
+        class _Store:
+            def __init__(self):
+                self.d = {}
+
+            def put(self, k, v):
+                self.d[k] = v
+
+            def get(self, k):
+                return self.d.get(k)
+
+            def prefix(self, p):
+                return [(k, v) for k, v in self.d.items() if k.startswith(p)]
+
+            def delete(self, k):
+                self.d.pop(k, None)
+
+        actor = _Store.options(name=actor_name, namespace=namespace, lifetime="detached", get_if_exists=True).remote()
+
+        class _Meta:
+            def __init__(self, key):
+                self.key = key
+
+        class _Lease:
+            def refresh(self):
+                pass
+
+            def revoke(self):
+                pass
+
+        class _Client:
+            def put(self, k, v, lease=None):
+                ray.get(actor.put.remote(k, v))
+
+            def get(self, k):
+                return ray.get(actor.get.remote(k)), None
+
+            def get_prefix(self, p):
+                return [(v, _Meta(k)) for k, v in ray.get(actor.prefix.remote(p))]
+
+            def delete(self, k):
+                ray.get(actor.delete.remote(k))
+
+            def lease(self, ttl):
+                return _Lease()
+
+        super().__init__(_Client())
+
+
 def make_repository(cfg) -> NameRecordRepository:
     t = getattr(cfg, "type", "nfs")
     if t == "memory":
         return MemoryNameRecordRepository()
     if t == "nfs":
         return NfsNameRecordRepository(cfg.nfs_record_root)
-    raise NotImplementedError(
-        f"name_resolve type {t!r} needs an external service (etcd3 / Ray) that this package does "
-        "not bundle; use 'nfs' (shared directory) or 'memory'")
+    if t == "etcd3":
+        return Etcd3NameRecordRepository(getattr(cfg, "etcd3_addr", "localhost:2379"))
+    if t == "ray":
+        return RayNameRecordRepository(getattr(cfg, "ray_actor_name", "areal_b200_name_resolve"))
+    raise ValueError(f"unknown name_resolve type {t!r} (memory | nfs | etcd3 | ray)")
 
 
 DEFAULT_REPOSITORY: NameRecordRepository = MemoryNameRecordRepository()

@@ -153,6 +153,107 @@ def train_hf_fsdp2(preset="qwen3-1.7b", tokens_per_mb=16384, n_mbs=10, steps=3, 
             "stack": "HF Qwen3ForCausalLM + FSDP2 (bf16 compute, fp32 master) + torch.optim.AdamW(fused)"}
 
 
+def rollout_ours(preset="qwen3-1.7b", n_groups=80, group=8, prompt=(128, 512), resp=(256, 4096)) -> dict:
+    """This repository's rollout engine under the protocol of :func:`rollout_vllm`: the same 640 requests, all
+    submitted at once, no weight updates in between, rate over the whole call."""
+    import asyncio
+
+    import torch
+
+    from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig, NativeRolloutConfig
+    from areal_b200.api.io_struct import ModelRequest
+    from areal_b200.engine.rollout_engine import NativeRolloutEngine
+    from areal_b200.models.config import PRESETS
+
+    reqs = _lengths(n_groups, group, prompt, resp)
+    mc = PRESETS[preset]
+    ctx = prompt[1] + resp[1] + 64
+    kv_per_token = 2 * mc.num_hidden_layers * mc.num_key_value_heads * mc.head_dim * 2
+    n_blocks = int(min(120.0, len(reqs) * ctx * 0.75 * kv_per_token / 2**30) * 2**30 / (kv_per_token * 16))
+    cfg = InferenceEngineConfig(backend="native:d1", consumer_batch_size=len(reqs), max_concurrent_rollouts=len(reqs),
+                                native=NativeRolloutConfig(model_preset=preset, context_length=ctx, max_num_seqs=1024,
+                                                           max_num_batched_tokens=32768, kv_block_size=16,
+                                                           num_kv_blocks=n_blocks))
+    eng = NativeRolloutEngine(cfg)
+    eng.initialize()
+
+    async def run(items):
+        async def one(ids, n):
+            g = GenerationHyperparameters(n_samples=1, max_new_tokens=n, temperature=1.0, ignore_eos=True)
+            r = await eng.agenerate(ModelRequest(input_ids=ids, gconfig=g))
+            return r.output_len
+
+        return sum(await asyncio.gather(*[one(ids, n) for ids, n in items]))
+
+    asyncio.run(run([(ids, 64) for ids, _ in reqs[:16]]))  # warm-up
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    gen = asyncio.run(run(reqs))
+    dt = time.perf_counter() - t0
+    eng.destroy()
+    torch.cuda.empty_cache()
+    return {"generated_tokens": gen, "seconds": dt, "generated_tok_s": gen / dt, "sequences": len(reqs),
+            "engine": "areal_b200 NativeRolloutEngine"}
+
+
+def train_ours(preset="qwen3-1.7b", tokens_per_mb=16384, n_mbs=10, steps=3, warmup=2, seq=(384, 4608)) -> dict:
+    """This repository's train engine under the protocol of :func:`train_hf_fsdp2`: the same packed
+    micro-batches, one no-grad forward for the proximal log-probabilities, one forward/backward per micro-batch
+    with a clipped-ratio loss, one AdamW step."""
+    import torch
+
+    from areal_b200.api.cli_args import MicroBatchSpec, OptimizerConfig, TrainEngineConfig
+    from areal_b200.engine.train_engine import B200TrainEngine
+
+    cfg = TrainEngineConfig(backend="fsdp:d1", model_preset=preset, init_from_scratch=True, dtype="bfloat16",
+                            optimizer=OptimizerConfig(lr=1e-6, weight_decay=0.01, gradient_clipping=1.0),
+                            mb_spec=MicroBatchSpec(max_tokens_per_mb=tokens_per_mb))
+    eng = B200TrainEngine(cfg)
+    eng.create_process_group()
+    eng.initialize(None, None)
+    g = torch.Generator().manual_seed(7)
+    rows, total = [], 0
+    while len(rows) < 4096:
+        L = int(torch.randint(seq[0], seq[1] + 1, (1,), generator=g))
+        if total + L > tokens_per_mb * n_mbs:
+            break
+        rows.append(torch.randint(0, 150000, (L,), generator=g))
+        total += L
+    Lmax = max(len(r) for r in rows)
+    ids = torch.zeros(len(rows), Lmax, dtype=torch.long)
+    mask = torch.zeros(len(rows), Lmax, dtype=torch.bool)
+    for i, r in enumerate(rows):
+        ids[i, :len(r)] = r
+        mask[i, :len(r)] = True
+    batch = dict(input_ids=ids, attention_mask=mask, loss_mask=mask.long())
+
+    def step():
+        old = eng.forward_batch(batch)  # proximal log-probabilities (no grad)
+        b = dict(batch, prox=old)
+
+        def loss_fn(logp, ent, mb):
+            ratio = torch.exp(logp - mb["prox"].to(logp.device))
+            m = mb["loss_mask"].float()
+            return -(torch.clamp(ratio, 0.8, 1.2) * 0.1 * m).sum() / m.sum()
+
+        return eng.train_batch(b, loss_fn, lambda mb: float(mb["loss_mask"].sum()))
+
+    for _ in range(warmup):
+        step()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step()
+    e1.record()
+    torch.cuda.synchronize()
+    s = e0.elapsed_time(e1) / 1e3 / steps
+    eng.destroy()
+    torch.cuda.empty_cache()
+    return {"tokens_per_step_per_gpu": total, "seconds_per_step": s, "consumed_tok_s_per_gpu": total / s,
+            "stack": "areal_b200 B200TrainEngine (own kernels, flat ZeRO optimizer)"}
+
+
 def broadcast_nccl(nbytes=3_440_000_000, iters=5) -> dict:
     import torch
     import torch.distributed as dist
@@ -188,14 +289,25 @@ def main(n_gpus: int) -> int:
         except Exception as e:
             res["broadcast"] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
     else:
+        import gc
+
         import torch
         import torch.distributed as dist
 
         if dist.is_initialized():
             dist.destroy_process_group()
+        gc.collect()
         torch.cuda.empty_cache()
         for k in ("RANK", "WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT", "LOCAL_RANK"):
             os.environ.pop(k, None)
+        # the same two protocols on this repository's engines, for a like-for-like reading
+        for key, fn in (("train_ours", train_ours), ("rollout_ours", rollout_ours)):
+            try:
+                res[key] = fn()
+            except Exception as e:
+                res[key] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+            gc.collect()
+            torch.cuda.empty_cache()
         try:
             res["rollout"] = rollout_vllm()
         except Exception as e:

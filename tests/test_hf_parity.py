@@ -87,3 +87,33 @@ def test_critic_matches_transformers_token_classification(tmp_path):
         mine = m.values(m(ids, torch.arange(29), meta))
         theirs = hf(input_ids=ids[None]).logits[0, :, 0]
     assert float((mine - theirs).abs().max()) < 2e-4
+
+
+def test_block_quantised_fp8_checkpoint_is_dequantised_on_load(tmp_path):
+    """A checkpoint whose linear weights are float8_e4m3 with one fp32 ``weight_scale_inv`` per 128 x 128 tile
+    (split over two files) loads as bf16 within the quantisation error."""
+    import json
+
+    import torch
+    from safetensors.torch import save_file
+
+    from areal_b200.utils.hf_io import dequant_fp8_blockwise, iter_hf_tensors
+
+    torch.manual_seed(0)
+    w = torch.randn(300, 260) * 0.05
+    nb0, nb1 = 3, 3
+    pad = torch.zeros(nb0 * 128, nb1 * 128)
+    pad[:300, :260] = w
+    amax = pad.view(nb0, 128, nb1, 128).abs().amax(dim=(1, 3)).clamp(min=1e-8)
+    scale_inv = amax / 448.0
+    q = (pad / scale_inv.repeat_interleave(128, 0).repeat_interleave(128, 1))[:300, :260].to(torch.float8_e4m3fn)
+    norm = torch.ones(260, dtype=torch.bfloat16)
+    save_file({"model.layers.0.mlp.down_proj.weight": q, "model.norm.weight": norm}, str(tmp_path / "model-00001-of-00002.safetensors"))
+    save_file({"model.layers.0.mlp.down_proj.weight_scale_inv": scale_inv}, str(tmp_path / "model-00002-of-00002.safetensors"))
+    json.dump({"quantization_config": {"quant_method": "fp8", "weight_block_size": [128, 128]}}, open(tmp_path / "config.json", "w"))
+    got = dict(iter_hf_tensors(str(tmp_path)))
+    assert set(got) == {"model.layers.0.mlp.down_proj.weight", "model.norm.weight"}
+    d = got["model.layers.0.mlp.down_proj.weight"]
+    assert d.dtype == torch.bfloat16 and d.shape == (300, 260)
+    assert (d.float() - w).abs().max() < 0.07 * w.abs().max()
+    assert torch.equal(d, dequant_fp8_blockwise(q, scale_inv))

@@ -106,3 +106,129 @@ def test_validate_installation_reports_success_on_cpu(capsys):
     out = capsys.readouterr().out
     assert rc == 0, out
     assert "import torch" in out
+
+
+def test_determinism_switches_set_and_clear():
+    """``megatron.use_deterministic_algorithms``: fixed NCCL algorithm, cuBLAS workspace, PyTorch's deterministic
+    operators, and the library's flag that routes the two atomically-summing kernels to ordered paths."""
+    import os
+
+    import torch
+
+    from areal_b200.utils import determinism
+
+    old = {k: os.environ.get(k) for k in ("NCCL_ALGO", "CUBLAS_WORKSPACE_CONFIG")}
+    try:
+        os.environ.pop("NCCL_ALGO", None)
+        determinism.set_deterministic_algorithms(True)
+        assert determinism.deterministic_mode() and torch.are_deterministic_algorithms_enabled()
+        assert os.environ["NCCL_ALGO"] == "Ring" and os.environ["CUBLAS_WORKSPACE_CONFIG"] in (":4096:8", ":16:8")
+    finally:
+        determinism.set_deterministic_algorithms(False)
+        for k, v in old.items():
+            if v is None:
+                os.environ.pop(k, None)
+            else:
+                os.environ[k] = v
+    assert not determinism.deterministic_mode() and not torch.are_deterministic_algorithms_enabled()
+
+
+def test_activation_checkpoint_policies_keep_gradients_identical():
+    """none / full / selective (every N-th block, or the MLP half of every block) / memory budget: the same
+    gradients, bit for bit on CPU, whichever parts are recomputed."""
+    import torch
+
+    from areal_b200.models.activation_checkpoint import apply_activation_checkpointing, make_policy
+    from areal_b200.models.config import PRESETS
+    from areal_b200.models.qwen import build_model
+    from areal_b200.ops.attention import VarlenMeta
+
+    assert make_policy(6, "selective", 2).full_layers == {0, 2, 4}
+    assert make_policy(6, "selective", "op").mlp_only and not make_policy(6, "selective", "op").full_layers
+    assert make_policy(8, "memory_budget", budget=0.25).full_layers == set(range(6))
+    assert not make_policy(8, "memory_budget", budget=1.0).active and make_policy(4, "full").full_layers == {0, 1, 2, 3}
+    import pytest
+
+    with pytest.raises(ValueError):
+        make_policy(4, "sometimes")
+    model = build_model(PRESETS["tiny-qwen2-4l"], dtype=torch.float32, device="cpu", seed=1)
+    ids = torch.randint(0, 1000, (50,))
+    pos = torch.cat([torch.arange(30), torch.arange(20)])
+    meta = VarlenMeta([0, 30, 50], torch.device("cpu"))
+    grads = {}
+    for mode, opt, budget in (("none", "op", 0.5), ("full", "op", 0.5), ("selective", 2, 0.5), ("selective", "op", 0.5),
+                              ("memory_budget", "op", 0.4)):
+        apply_activation_checkpointing(model, mode, opt, budget)
+        model.zero_grad()
+        model.train()
+        h = model(ids, pos, meta)
+        model.logits(h).float().square().mean().backward()
+        grads[(mode, opt)] = torch.cat([p.grad.flatten() for p in model.parameters() if p.grad is not None])
+    base = grads[("none", "op")]
+    assert base.abs().sum() > 0
+    for k, g in grads.items():
+        assert torch.equal(g, base), k
+
+
+def test_kv_name_resolve_against_a_fake_etcd_client():
+    """The etcd3 / Ray repositories speak to their service through five calls; a fake with those calls stands in."""
+    import pytest
+
+    from areal_b200.utils import name_resolve as nr
+
+    class Meta:
+        def __init__(self, key):
+            self.key = key.encode()
+
+    class Lease:
+        def __init__(self):
+            self.refreshed, self.revoked = 0, False
+
+        def refresh(self):
+            self.refreshed += 1
+
+        def revoke(self):
+            self.revoked = True
+
+    class FakeEtcd:
+        def __init__(self):
+            self.d, self.leases = {}, []
+
+        def put(self, k, v, lease=None):
+            self.d[k] = v.encode()
+
+        def get(self, k):
+            return self.d.get(k), None
+
+        def get_prefix(self, p):
+            return [(v, Meta(k)) for k, v in self.d.items() if k.startswith(p)]
+
+        def delete(self, k):
+            self.d.pop(k, None)
+
+        def lease(self, ttl):
+            self.leases.append(Lease())
+            return self.leases[-1]
+
+    client = FakeEtcd()
+    repo = nr.KVNameRecordRepository(client, keepalive_interval=0.01)
+    repo.add("exp/trial/servers/a", "host:1", keepalive_ttl=2)
+    repo.add("exp/trial/servers/b", "host:2")
+    repo.add("exp/trial/serversX", "other")
+    with pytest.raises(nr.NameEntryExistsError):
+        repo.add("exp/trial/servers/a", "again")
+    repo.add("exp/trial/servers/a", "host:9", replace=True)
+    assert repo.get("exp/trial/servers/a") == "host:9"
+    assert repo.get_subtree("exp/trial/servers") == ["host:9", "host:2"]          # the sibling prefix is not a child
+    assert repo.find_subtree("exp/trial/servers") == ["exp/trial/servers/a", "exp/trial/servers/b"]
+    import time
+
+    time.sleep(0.05)
+    assert client.leases[0].refreshed > 0
+    repo.delete("exp/trial/servers/b")
+    with pytest.raises(nr.NameEntryNotFoundError):
+        repo.get("exp/trial/servers/b")
+    repo.reset()
+    assert client.d == {} and all(l.revoked for l in client.leases)
+    with pytest.raises(ImportError):
+        nr.Etcd3NameRecordRepository("localhost:2379")

@@ -47,8 +47,9 @@ def test_push_plan_kernel_matches_the_torch_statement():
 
     torch.manual_seed(0)
     src = torch.randn(1 << 20, device="cuda").bfloat16()
-    segs = [Segment(0, 4096, 1, 70000 * 8, 0, 0), Segment(700000, 8, 257, 512, 512, 2048),
-            Segment(900000, 2048 * 300, 64, 1024, 1024, 1024)]
+    # destination ranges do not overlap: [8, 524808) strided, [1000000, 1560000) and [1600000, 1665536) contiguous
+    segs = [Segment(0, 1000000, 1, 70000 * 8, 0, 0), Segment(700000, 8, 257, 512, 512, 2048),
+            Segment(900000, 1600000, 64, 1024, 1024, 1024)]
     dsts = [torch.zeros(1 << 21, device="cuda", dtype=torch.bfloat16) for _ in range(2)]
     want = torch.zeros(1 << 21, device="cuda", dtype=torch.bfloat16)
     for g in segs:
