@@ -49,6 +49,11 @@ struct Request {
   int64_t arrival = 0;
   uint64_t prompt_hash = 0;
   bool kv_ready = false;   // the prompt's K/V have been written (its prefill step was committed)
+  // The first share_len tokens are common to a group of requests (the samples of one prompt). For a fresh
+  // request that is the whole prompt; a request re-submitted after an interruption carries prompt + partial
+  // output as its prompt and names the original prompt's length here.
+  int32_t share_len = 0;
+  uint64_t share_hash = 0;
 };
 
 struct Scheduler {
@@ -57,7 +62,9 @@ struct Scheduler {
   std::vector<int32_t> refcnt;  // pages may be shared by requests with the same prompt (read-only full pages)
   std::unordered_map<uint64_t, int64_t> prompt_leader;  // prompt hash -> request whose prompt pages can be shared
   bool share_prompts = true;
-  int64_t n_forked = 0, n_shared_pages = 0;
+  int64_t n_forked = 0, n_shared_pages = 0, n_dedup_pages = 0;
+  // common-prefix hash -> request whose prefilled prefix pages later arrivals of the group adopt
+  std::unordered_map<uint64_t, int64_t> prefix_leader;
   std::unordered_map<int64_t, Request> reqs;
   std::deque<int64_t> waiting;
   std::vector<int64_t> running;
@@ -129,9 +136,11 @@ void* b200_sched_create(int num_blocks, int block_size, int max_num_seqs, int ma
 
 void b200_sched_destroy(void* h) { delete static_cast<Scheduler*>(h); }
 
-// Returns the request id (> 0) or -1 when the prompt can never fit.
-int64_t b200_sched_add(void* h, const int32_t* prompt, int n_prompt, int max_new_tokens,
-                       int min_new_tokens, const int32_t* stop_ids, int n_stop, int ignore_eos) {
+// Returns the request id (> 0) or -1 when the prompt can never fit. share_len: number of leading tokens that
+// the other samples of the same group also start with (<= 0: the whole prompt).
+int64_t b200_sched_add_shared(void* h, const int32_t* prompt, int n_prompt, int max_new_tokens,
+                              int min_new_tokens, const int32_t* stop_ids, int n_stop, int ignore_eos,
+                              int share_len) {
   auto* s = static_cast<Scheduler*>(h);
   std::lock_guard<std::mutex> lk(s->mu);
   const int64_t total = static_cast<int64_t>(n_prompt) + max_new_tokens;
@@ -154,10 +163,23 @@ int64_t b200_sched_add(void* h, const int32_t* prompt, int n_prompt, int max_new
     hsh *= 1099511628211ull;
   }
   r.prompt_hash = hsh;
+  r.share_len = (share_len <= 0 || share_len > n_prompt) ? n_prompt : share_len;
+  uint64_t ph = 1469598103934665603ull;
+  for (int i = 0; i < r.share_len; ++i) {
+    ph ^= static_cast<uint32_t>(prompt[i]);
+    ph *= 1099511628211ull;
+  }
+  r.share_hash = ph ^ (static_cast<uint64_t>(r.share_len) << 40);
   const int64_t id = r.id;
   s->reqs.emplace(id, std::move(r));
   s->waiting.push_back(id);
   return id;
+}
+
+int64_t b200_sched_add(void* h, const int32_t* prompt, int n_prompt, int max_new_tokens,
+                       int min_new_tokens, const int32_t* stop_ids, int n_stop, int ignore_eos) {
+  return b200_sched_add_shared(h, prompt, n_prompt, max_new_tokens, min_new_tokens, stop_ids, n_stop,
+                               ignore_eos, 0);
 }
 
 struct PlanHeader {
@@ -297,8 +319,14 @@ int b200_sched_plan(void* h, PlanHeader* hdr, int64_t* seq_ids, int32_t* cu_seql
     if (s->running.empty()) return kIdle;
     i = 0;  // re-check from the start with the freed pages
   }
+  // Sequences that share prefix pages sit next to each other in the batch (equal first page): the attention
+  // kernel's blocks of one group then run at about the same time and read the shared pages from L2.
+  std::vector<int64_t> order(s->running.begin(), s->running.end());
+  std::stable_sort(order.begin(), order.end(), [&](int64_t a, int64_t b) {
+    return s->reqs[a].blocks[0] < s->reqs[b].blocks[0];
+  });
   int n = 0;
-  for (int64_t id : s->running) {
+  for (int64_t id : order) {
     Request& r = s->reqs[id];
     const int32_t L = static_cast<int32_t>(r.tokens.size());
     seq_ids[n] = id;
@@ -333,7 +361,41 @@ int b200_sched_commit(void* h, const int32_t* sampled, const float* logprobs, in
     if (it == s->reqs.end()) continue;
     Request& r = it->second;
     if (r.finish != kRunning) continue;  // aborted between plan and commit
-    if (was_prefill) r.kv_ready = true;
+    if (was_prefill) {
+      r.kv_ready = true;
+      // Prefix pages of a group are kept once: the first request of the group to finish its prefill becomes
+      // the holder, later ones (same leading tokens, computed under the same weights) adopt its full prefix
+      // pages and return their own copies. After a weight update every request is re-submitted with
+      // prompt + partial output, so this is what keeps a group's prompt shared for its whole life.
+      const int32_t bs = s->block_size;
+      const int32_t nshare = r.share_len / bs;
+      if (s->share_prompts && nshare > 0 && static_cast<int32_t>(r.blocks.size()) > nshare) {
+        Request* ld = nullptr;
+        auto pl = s->prefix_leader.find(r.share_hash);
+        if (pl != s->prefix_leader.end() && pl->second != r.id) {
+          auto rq = s->reqs.find(pl->second);
+          if (rq != s->reqs.end()) {
+            Request& c = rq->second;
+            if (c.finish == kRunning && c.kv_ready && c.share_len == r.share_len &&
+                static_cast<int32_t>(c.blocks.size()) > nshare &&
+                std::equal(r.tokens.begin(), r.tokens.begin() + r.share_len, c.tokens.begin()))
+              ld = &c;
+          }
+        }
+        if (ld != nullptr) {
+          for (int32_t b = 0; b < nshare; ++b) {
+            const int32_t mine = r.blocks[b], theirs = ld->blocks[b];
+            if (mine == theirs) continue;
+            r.blocks[b] = theirs;
+            s->refcnt[theirs]++;
+            if (--s->refcnt[mine] == 0) s->free_blocks.push_back(mine);
+            s->n_dedup_pages++;
+          }
+        } else {
+          s->prefix_leader[r.share_hash] = r.id;
+        }
+      }
+    }
     r.tokens.push_back(sampled[i]);
     r.logprobs.push_back(logprobs[i]);
     const int32_t n_new = static_cast<int32_t>(r.tokens.size()) - r.prompt_len;
@@ -417,7 +479,8 @@ int b200_sched_take_output(void* h, int64_t id, int32_t* out_tokens, float* out_
 }
 
 // stats[0]=waiting, [1]=running, [2]=free blocks, [3]=preemptions, [4]=live requests,
-// [5]=requests that skipped their prefill by sharing a prompt, [6]=pages shared that way (cumulative)
+// [5]=requests that skipped their prefill by sharing a prompt, [6]=pages shared that way (cumulative),
+// [7]=prefix pages given back after a prefill because another request of the group already held them
 void b200_sched_stats(void* h, int64_t* stats) {
   auto* s = static_cast<Scheduler*>(h);
   std::lock_guard<std::mutex> lk(s->mu);
@@ -428,6 +491,7 @@ void b200_sched_stats(void* h, int64_t* stats) {
   stats[4] = static_cast<int64_t>(s->reqs.size());
   stats[5] = s->n_forked;
   stats[6] = s->n_shared_pages;
+  stats[7] = s->n_dedup_pages;
 }
 
 void b200_sched_set_prompt_sharing(void* h, int on) {

@@ -65,6 +65,7 @@ class PagedScheduler:
         self.lib = _lib.host()
         self.lib.b200_sched_create.restype = ctypes.c_void_p
         self.lib.b200_sched_add.restype = ctypes.c_int64
+        self.lib.b200_sched_add_shared.restype = ctypes.c_int64
         self.lib.b200_sched_pop_finished.restype = ctypes.c_int64
         self.h = ctypes.c_void_p(self.lib.b200_sched_create(num_blocks, block_size, max_num_seqs,
                                                             max_batched_tokens, max_blocks_per_seq))
@@ -90,12 +91,15 @@ class PagedScheduler:
     def _p(a):
         return a.ctypes.data_as(ctypes.c_void_p)
 
-    def add(self, prompt, max_new, min_new, stop_ids, ignore_eos) -> int:
+    def add(self, prompt, max_new, min_new, stop_ids, ignore_eos, share_len: int = 0) -> int:
+        """``share_len``: how many leading tokens the other samples of the same group also start with (0: the
+        whole prompt). A request re-submitted with prompt + partial output passes the original prompt's length,
+        so the group keeps sharing its prompt pages."""
         p = np.ascontiguousarray(prompt, dtype=np.int32)
         s = np.ascontiguousarray(stop_ids, dtype=np.int32)
-        return int(self.lib.b200_sched_add(self.h, self._p(p), ctypes.c_int(len(p)), ctypes.c_int(max_new),
-                                           ctypes.c_int(min_new), self._p(s), ctypes.c_int(len(s)),
-                                           ctypes.c_int(int(ignore_eos))))
+        return int(self.lib.b200_sched_add_shared(self.h, self._p(p), ctypes.c_int(len(p)), ctypes.c_int(max_new),
+                                                  ctypes.c_int(min_new), self._p(s), ctypes.c_int(len(s)),
+                                                  ctypes.c_int(int(ignore_eos)), ctypes.c_int(int(share_len))))
 
     def plan(self) -> int:
         return self.lib.b200_sched_plan(self.h, ctypes.byref(self.hdr), self._p(self.seq_ids), self._p(self.cu),
@@ -128,7 +132,7 @@ class PagedScheduler:
         a = np.zeros(8, dtype=np.int64)
         self.lib.b200_sched_stats(self.h, self._p(a))
         return dict(waiting=int(a[0]), running=int(a[1]), free_blocks=int(a[2]), preemptions=int(a[3]),
-                    live=int(a[4]), prompt_forks=int(a[5]), shared_pages=int(a[6]))
+                    live=int(a[4]), prompt_forks=int(a[5]), shared_pages=int(a[6]), dedup_pages=int(a[7]))
 
     def set_prompt_sharing(self, on: bool):
         self.lib.b200_sched_set_prompt_sharing(self.h, ctypes.c_int(int(on)))
@@ -633,7 +637,7 @@ class NativeRolloutEngine(InferenceEngine):
             loop.call_soon_threadsafe(_set_exception, fut, e)
 
     # --------------------------------------------------------------- generate
-    async def _generate_once(self, input_ids: list[int], g, max_new: int, images=None):
+    async def _generate_once(self, input_ids: list[int], g, max_new: int, images=None, share_len: int = 0):
         if self._step_error is not None:
             raise RuntimeError("rollout engine stopped") from self._step_error
         loop = asyncio.get_running_loop()
@@ -652,7 +656,7 @@ class NativeRolloutEngine(InferenceEngine):
             h.update(images["image_grid_thw"].contiguous().numpy().tobytes())
             mm_state = dict(images, pos3=pos3, delta=int(deltas[0]), key=h.digest())
         with self._lock:
-            rid = self.sched.add(input_ids, max_new, int(g.min_new_tokens), stop, bool(g.ignore_eos))
+            rid = self.sched.add(input_ids, max_new, int(g.min_new_tokens), stop, bool(g.ignore_eos), share_len)
             if rid < 0:
                 raise ValueError(f"prompt of {len(input_ids)} tokens does not fit the rollout engine")
             self._pending[rid] = (loop, fut, {})
@@ -682,7 +686,8 @@ class NativeRolloutEngine(InferenceEngine):
             if out_tokens:
                 self._reprefill_tokens += len(req.input_ids) + len(out_tokens)
             reason, toks, lps = await self._generate_once(list(req.input_ids) + out_tokens, g,
-                                                          max_new - len(out_tokens), images)
+                                                          max_new - len(out_tokens), images,
+                                                          share_len=len(req.input_ids))
             if toks and ttft == float("inf"):
                 ttft = time.perf_counter() - t0
             out_tokens += toks

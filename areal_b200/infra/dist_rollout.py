@@ -40,9 +40,11 @@ logger = logging.getLogger("DistRollout")
 
 
 class DisaggTopology:
-    """Rank layout: ``[0, n_gen)`` rollout, ``[n_gen, n_gen + n_train)`` trainers."""
+    """Rank layout: ``[0, n_gen)`` rollout, ``[n_gen, n_gen + n_train)`` trainers. Rollout ranks are paired
+    with the *heads* of the trainer's data-parallel replicas: under tensor / sequence / pipeline parallelism
+    the ``replica_size`` ranks of a replica train one batch, which its first rank fetches and shares."""
 
-    def __init__(self, n_gen: int, n_train: int):
+    def __init__(self, n_gen: int, n_train: int, replica_size: int = 1, n_replicas: int | None = None):
         self.n_gen, self.n_train = n_gen, n_train
         self.world = dist.get_world_size()
         assert n_gen + n_train == self.world, f"allocation {n_gen}+{n_train} != world {self.world}"
@@ -50,14 +52,19 @@ class DisaggTopology:
         self.gen_ranks = list(range(n_gen))
         self.train_ranks = list(range(n_gen, n_gen + n_train))
         self.is_rollout = self.rank < n_gen
+        n_replicas = n_replicas if n_replicas is not None else max(n_train // max(replica_size, 1), 1)
+        # tp is innermost, then sequence parallel, then data parallel, pipeline stages outermost: the head of
+        # replica d is the rank at offset d * replica_size of the first stage
+        self.train_heads = [self.train_ranks[d * replica_size] for d in range(n_replicas)]
         # gloo groups over the whole world: one for data, one for control
         self.data_group = dist.new_group(list(range(self.world)), backend="gloo")
         self.ctl_group = dist.new_group(list(range(self.world)), backend="gloo")
         self.all_cpu_group = dist.new_group(list(range(self.world)), backend="gloo")
 
     def trainers_of(self, gen_rank: int) -> list[int]:
-        return [t for i, t in enumerate(self.train_ranks) if i % self.n_gen == gen_rank % self.n_gen] \
-            if self.n_train >= self.n_gen else [self.train_ranks[gen_rank % self.n_train]]
+        heads = self.train_heads
+        return [t for i, t in enumerate(heads) if i % self.n_gen == gen_rank % self.n_gen] \
+            if len(heads) >= self.n_gen else [heads[gen_rank % len(heads)]]
 
     def rollouts_of(self, train_rank: int) -> list[int]:
         return [g for g in self.gen_ranks if train_rank in self.trainers_of(g)]

@@ -120,7 +120,10 @@ class PPOTrainer:
         if not self.colocated and n_train + n_gen != self.world:
             raise ValueError(f"allocation {config.rollout.backend}+{config.actor.backend} needs "
                              f"{n_train + n_gen} ranks, world size is {self.world}")
-        self.topo = None if (self.colocated or self.external_rollout) else DisaggTopology(n_gen, n_train)
+        ps_ = self.actor_alloc.parallel
+        replica = ps_.tp_size * ps_.cp_size  # ranks of one replica inside a pipeline stage (tp innermost, then sp)
+        self.topo = None if (self.colocated or self.external_rollout) else DisaggTopology(
+            n_gen, n_train, replica_size=replica, n_replicas=max(n_train // (replica * ps_.pp_size), 1))
         self.is_trainer = self.colocated or self.external_rollout or not self.topo.is_rollout
         self.is_rollout = not self.external_rollout and (self.colocated or self.topo.is_rollout)
         train_ranks = list(range(self.world)) if self.topo is None else self.topo.train_ranks
@@ -182,7 +185,9 @@ class PPOTrainer:
             dev = torch.cuda.current_device() if use_cuda else 0
             ptrs = exchange_weight_buffers(self.topo, self.rollout, dev)
             if self.is_trainer:
-                self.rollout_client = RemoteRolloutClient(self.topo, ptrs, self.train_cpu_group)
+                # pause / resume barriers span EVERY trainer rank: tensor- and pipeline-parallel peers push
+                # their shards too and must not write before the rollout engines have paused
+                self.rollout_client = RemoteRolloutClient(self.topo, ptrs, self.actor_engine._all_cpu_group)
             self.weight_meta = WeightUpdateMeta.from_p2p()
         if self.is_trainer:
             self.actor_engine.connect_engine(self.rollout_client, self.weight_meta)

@@ -236,3 +236,79 @@ def test_engine_prompt_sharing_does_not_change_greedy_outputs():
         assert max(abs(x - y) for x, y in zip(la, lb)) < 1e-4
     # and all copies of one prompt agree with each other
     assert shared[0][0] == shared[1][0] == shared[2][0] and shared[3][0] == shared[4][0] == shared[5][0]
+
+
+def test_scheduler_keeps_a_group_prefix_shared_across_resubmission():
+    """After an interruption the samples of a group come back as prompt + partial output (different requests,
+    same leading tokens). Each is prefilled whole; the first becomes the holder of the group's full prefix
+    pages, the others adopt them and give their own copies back."""
+    import numpy as np
+
+    from areal_b200.engine.rollout_engine import PagedScheduler
+
+    bs = 16
+    s = PagedScheduler(num_blocks=64, block_size=bs, max_num_seqs=16, max_batched_tokens=4096, max_blocks_per_seq=8)
+    prompt = list(range(100, 140))  # 40 tokens: 2 full pages + 8 tokens
+    parts = [[900 + i] * (5 + 7 * i) for i in range(3)]  # partial outputs of different lengths
+    free0 = s.stats()["free_blocks"]
+    ids = [s.add(prompt + part, 4, 0, [], True, share_len=len(prompt)) for part in parts]
+    solo = s.add(list(range(300, 350)), 4, 0, [], True)  # unrelated request: keeps its own pages
+    assert s.plan() == 1 and s.hdr.n_seqs == 4  # different prompts: everyone prefills
+    used_before = free0 - s.stats()["free_blocks"]
+    s.commit(np.full(4, 7, dtype=np.int32), np.zeros(4, dtype=np.float32))
+    st = s.stats()
+    assert st["dedup_pages"] == 4  # two followers x two full prefix pages
+    assert free0 - st["free_blocks"] == used_before - 4
+    assert s.plan() == 2
+    n = s.hdr.n_seqs
+    rows = s.block_table[: n * 8].reshape(n, 8)
+    order = s.seq_ids[:n].tolist()
+    a, b, c = (rows[order.index(i)] for i in ids)
+    assert (a[:2] == b[:2]).all() and (a[:2] == c[:2]).all() and len({int(a[2]), int(b[2]), int(c[2])}) == 3
+    # the group's sequences are adjacent in the decode batch (sorted by their first page)
+    pos = sorted(order.index(i) for i in ids)
+    assert pos[2] - pos[0] == 2 and order.index(solo) not in range(pos[0], pos[2] + 1)
+    for _ in range(8):
+        if s.plan() == 0:
+            break
+        s.commit(np.full(s.hdr.n_seqs, 9, dtype=np.int32), np.zeros(s.hdr.n_seqs, dtype=np.float32))
+    while s.pop_finished() is not None:
+        pass
+    assert s.stats()["free_blocks"] == free0 and s.stats()["live"] == 0  # every page came back exactly once
+    s.close()
+
+
+def test_engine_outputs_do_not_change_when_resubmitted_groups_share_their_prefix():
+    """Greedy continuation of three requests that start with the same 40 tokens and continue differently: with
+    the prefix pages shared after prefill the tokens and logprobs equal those with sharing switched off."""
+    import asyncio
+
+    from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig, NativeRolloutConfig
+    from areal_b200.engine.rollout_engine import NativeRolloutEngine
+
+    def run(share: bool):
+        cfg = InferenceEngineConfig(experiment_name="e", trial_name="t", backend="native:d1", max_concurrent_rollouts=64,
+                                    consumer_batch_size=8,
+                                    native=NativeRolloutConfig(model_preset="tiny-qwen2", context_length=128, max_num_seqs=16,
+                                                               max_num_batched_tokens=1024, num_kv_blocks=128, seed=0,
+                                                               cuda_graph=False))
+        eng = NativeRolloutEngine(cfg).initialize(device="cpu")
+        eng.sched.set_prompt_sharing(share)
+        g = torch.Generator().manual_seed(9)
+        prefix = torch.randint(0, 1000, (40,), generator=g).tolist()
+        tails = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (3, 11, 20)]
+        gc = GenerationHyperparameters(max_new_tokens=10, greedy=True, temperature=0.0, ignore_eos=True)
+
+        async def go():
+            return await asyncio.gather(*[eng._generate_once(prefix + t, gc, 10, share_len=len(prefix)) for t in tails])
+
+        out = asyncio.run(go())
+        st = eng.sched.stats()
+        eng.destroy()
+        return [(toks, lps) for _, toks, lps in out], st
+
+    shared, st_on = run(True)
+    plain, st_off = run(False)
+    assert st_on["dedup_pages"] == 4 and st_off["dedup_pages"] == 0
+    for (ta, la), (tb, lb) in zip(shared, plain):
+        assert ta == tb and max(abs(x - y) for x, y in zip(la, lb)) < 1e-4

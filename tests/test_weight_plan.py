@@ -64,3 +64,30 @@ def test_push_plan_kernel_matches_the_torch_statement():
     assert rc == 0
     torch.cuda.synchronize()
     assert torch.equal(dsts[0], want) and torch.equal(dsts[1], want)
+
+
+def test_rollout_ranks_pair_with_data_parallel_heads_only():
+    """Disaggregated layout with a model-parallel trainer: rollout ranks send batches to (and take control
+    messages from) the first rank of each trainer replica; the other ranks of a replica get the batch from
+    their head and have no rollout partner."""
+    from areal_b200.infra.dist_rollout import DisaggTopology
+
+    def topo(n_gen, n_train, replica, n_replicas):
+        t = object.__new__(DisaggTopology)
+        t.n_gen, t.n_train = n_gen, n_train
+        t.gen_ranks = list(range(n_gen))
+        t.train_ranks = list(range(n_gen, n_gen + n_train))
+        t.train_heads = [t.train_ranks[d * replica] for d in range(n_replicas)]
+        return t
+
+    t = topo(2, 2, 2, 1)  # native:d2 + megatron:d1t2
+    assert t.train_heads == [2] and t.trainers_of(0) == [2] and t.trainers_of(1) == [2]
+    assert t.rollouts_of(2) == [0, 1] and t.rollouts_of(3) == []
+    t = topo(4, 4, 2, 2)  # native:d4 + megatron:d2t2
+    assert t.train_heads == [4, 6]
+    assert [t.trainers_of(g) for g in range(4)] == [[4], [6], [4], [6]]
+    assert t.rollouts_of(4) == [0, 2] and t.rollouts_of(5) == [] and t.rollouts_of(6) == [1, 3]
+    t = topo(4, 4, 1, 4)  # native:d4 + fsdp:d4: one to one
+    assert [t.trainers_of(g) for g in range(4)] == [[4], [5], [6], [7]]
+    t = topo(2, 4, 1, 4)  # more trainers than rollout ranks: a rollout rank feeds two of them
+    assert t.trainers_of(0) == [2, 4] and t.trainers_of(1) == [3, 5]
