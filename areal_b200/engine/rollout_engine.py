@@ -796,6 +796,9 @@ class NativeRolloutEngine(InferenceEngine):
     def wait_for_task(self, task_id: int, timeout: float | None = None, raise_timeout: bool = True):
         return self._executor.wait_for_task(task_id, timeout, raise_timeout)
 
+    def poll_task(self, task_id: int):
+        return self._executor.poll_task(task_id)
+
     def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1):
         return self._executor.rollout_batch(data, workflow, workflow_kwargs, should_accept_fn, group_size)
 

@@ -66,6 +66,43 @@ def resolve_model_config(cfg: TrainEngineConfig) -> ModelConfig:
     return mc
 
 
+class _PinnedStager:
+    """Host→device staging through two reusable pinned arenas instead of one ``cudaHostAlloc`` per tensor."""
+
+    def __init__(self, device, nbytes: int = 8 << 20):
+        self.device = device
+        self.arenas = [torch.empty(nbytes, dtype=torch.uint8, pin_memory=True) for _ in range(2)]
+        self.events = [None, None]
+        self.cur, self.off = 0, 0
+
+    def begin(self):
+        self.cur ^= 1
+        ev = self.events[self.cur]
+        if ev is not None:
+            ev.synchronize()  # the copies issued from this arena two micro-batches ago
+        self.off = 0
+
+    def to_device(self, t: torch.Tensor) -> torch.Tensor:
+        t = t.contiguous()
+        n = t.numel() * t.element_size()
+        start = (self.off + 255) // 256 * 256
+        if start + n > self.arenas[self.cur].numel():
+            if self.off == 0:  # nothing issued from this arena yet: grow it
+                self.arenas[self.cur] = torch.empty(max(2 * self.arenas[self.cur].numel(), start + n), dtype=torch.uint8,
+                                                    pin_memory=True)
+            else:  # rare: fall back to a one-off pinned copy rather than disturb copies in flight
+                return t.pin_memory().to(self.device, non_blocking=True)
+        view = self.arenas[self.cur][start:start + n].view(t.dtype).view(t.shape)
+        view.copy_(t)
+        self.off = start + n
+        return view.to(self.device, non_blocking=True)
+
+    def end(self):
+        ev = torch.cuda.Event()
+        ev.record(torch.cuda.current_stream(self.device))
+        self.events[self.cur] = ev
+
+
 class B200TrainEngine(TrainEngine):
     def __init__(self, config: TrainEngineConfig):
         self.config = config
@@ -379,14 +416,23 @@ class B200TrainEngine(TrainEngine):
         meta = VarlenMeta(cu_cpu.tolist(), self.device)
         out = {}
         cuda = self.device.type == "cuda"
+        if cuda:
+            # one pinned arena per micro-batch in flight (two alternate): the tensors of a micro-batch are laid
+            # out in it and copied asynchronously; an arena is reused once the copies issued from it have finished
+            if getattr(self, "_stager", None) is None:
+                self._stager = _PinnedStager(self.device)
+            self._stager.begin()
         for k, v in mb.items():
             if torch.is_tensor(v):
                 if cuda and not v.is_cuda:
-                    v = v.pin_memory()
                     self.h2d_bytes += v.numel() * v.element_size()
-                out[k] = v.to(self.device, non_blocking=True)
+                    out[k] = self._stager.to_device(v)
+                else:
+                    out[k] = v.to(self.device, non_blocking=True)
             else:
                 out[k] = v
+        if cuda:
+            self._stager.end()
         out = amend_position_ids(out)
         out["cu_seqlens"] = meta.cu_seqlens
         return out, meta
@@ -670,6 +716,9 @@ class B200TrainEngine(TrainEngine):
         if pp:
             self._pipeline_forward_backward(mb_list.mbs, [1.0] * len(mb_list.mbs), None, forward_only=True,
                                             collect=lambda i, o, e, m, mt: staged.__setitem__(i, (o, e, mt)))
+        # the micro-batches run back to back on the device; their outputs cross to the host in ONE copy at the
+        # end (a read per micro-batch would put a host synchronisation between every two forwards)
+        outs, ents, metas = [], [], []
         for i_mb, mb in enumerate(mb_list.mbs):
             if pp:
                 if not self.pctx.is_last_stage:
@@ -678,17 +727,25 @@ class B200TrainEngine(TrainEngine):
             else:
                 dev_mb, meta = self._mb_to_device(mb)
                 out, ent = self._forward_mb(dev_mb, meta)
-            out = out.float().cpu()
-            self.d2h_bytes += out.numel() * 4
-            ent = ent.float().cpu() if (ent is not None and return_entropy) else None
-            cu = meta.cu_cpu
-            for i in range(len(cu) - 1):
-                src = mb_list.forward_indices[row]
-                n = int(cu[i + 1] - cu[i])
-                result[src, :n] = out[cu[i]:cu[i + 1]]
-                if ent is not None:
-                    ent_result[src, :n] = ent[cu[i]:cu[i + 1]]
-                row += 1
+            outs.append(out.float())
+            ents.append(ent.float() if (ent is not None and return_entropy) else None)
+            metas.append(meta)
+        if outs:
+            flat = torch.cat(outs)
+            self.d2h_bytes += flat.numel() * 4
+            flat = flat.cpu()
+            eflat = torch.cat(ents).cpu() if (return_entropy and all(e is not None for e in ents)) else None
+            base = 0
+            for out, meta in zip(outs, metas):
+                cu = meta.cu_cpu
+                for i in range(len(cu) - 1):
+                    src = mb_list.forward_indices[row]
+                    a, b = base + int(cu[i]), base + int(cu[i + 1])
+                    result[src, :b - a] = flat[a:b]
+                    if eflat is not None:
+                        ent_result[src, :b - a] = eflat[a:b]
+                    row += 1
+                base += out.shape[0]
         if pp:
             # the last stage holds the outputs: hand them to every stage of the replica
             src = dist.get_global_rank(self.pctx.pp_group, self.pctx.pp_size - 1)

@@ -42,6 +42,8 @@ class RolloutController:
         self.staleness: StalenessManager | None = None
         self._lock = threading.Lock()
         self._paused = False
+        self._failures_in_a_row = 0
+        self._ready: list[dict[str, Any]] = []
 
     def get_version(self) -> int:
         return self._version
@@ -101,7 +103,7 @@ class RolloutController:
 
     def wait(self, count: int, timeout: float | None = None, raise_timeout: bool = True):
         deadline = None if timeout is None else time.monotonic() + timeout
-        got: list[dict[str, Any]] = []
+        got = self._ready  # trajectories collected by earlier calls that timed out stay here
         while len(got) < count:
             progressed = False
             with self._lock:
@@ -109,16 +111,25 @@ class RolloutController:
             for tid, wid in pending:
                 if len(got) >= count:
                     break
-                r = self.scheduler.call_engine(wid, "wait_for_task", self.role, tid, timeout=0.01,
-                                               raise_timeout=False, return_rtensor=False)
-                if r is None:
-                    # still running, or finished and rejected: ask the worker which
+                state, r = self.scheduler.call_engine(wid, "poll_task", self.role, tid)
+                if state == "running":
                     continue
                 with self._lock:
                     self._pending.remove((tid, wid))
-                self.staleness.on_rollout_accepted()
-                got.append(localize(r))
                 progressed = True
+                if state == "done":
+                    self._failures_in_a_row = 0
+                    self.staleness.on_rollout_accepted()
+                    got.append(localize(r))
+                    continue
+                # dropped by the workflow / acceptance filter, or the episode raised: the sample will never
+                # arrive; free its slot so that prepare_batch submits a replacement
+                self.staleness.on_rollout_rejected()
+                if state == "failed":
+                    self._failures_in_a_row += 1
+                    logger.warning(f"rollout task {tid} on {wid} failed: {r}")
+                    if self._failures_in_a_row >= 16:
+                        raise RuntimeError(f"{self._failures_in_a_row} rollout episodes failed in a row; last: {r}")
             if len(got) >= count:
                 break
             if deadline is not None and time.monotonic() > deadline:
@@ -127,7 +138,8 @@ class RolloutController:
                 return None
             if not progressed:
                 time.sleep(0.01)
-        return concat_padded_tensors(got)
+        take, self._ready = got[:count], got[count:]
+        return concat_padded_tensors(take)
 
     def rollout_batch(self, data: list[dict[str, Any]], workflow=None, workflow_kwargs=None,
                       should_accept_fn=None, group_size: int = 1):

@@ -121,6 +121,8 @@ def resolve_workflow(workflow: Any, workflow_kwargs: dict | None, group_size: in
 
 
 class WorkflowExecutor:
+    MAX_CONSECUTIVE_FAILURES = 64
+
     def __init__(self, config: InferenceEngineConfig, engine):
         self.config = config
         self.engine = engine
@@ -133,6 +135,8 @@ class WorkflowExecutor:
         self._data_iter = None
         self._rng = random.Random(0)
         self._n_failed = 0
+        self._consecutive_failures = 0  # episodes that raised since the last one that did not
+        self._last_error = None
 
     def initialize(self, train_data_parallel_size: int | None = None):
         cfg = self.config
@@ -220,7 +224,12 @@ class WorkflowExecutor:
                 return
             if r.error is not None:
                 self._n_failed += 1
+                self._consecutive_failures += 1
+                self._last_error = r.error
+                with self._lock:
+                    self._by_task[r.task_id] = r  # so that a caller polling this task learns that it failed
                 continue
+            self._consecutive_failures = 0
             with self._lock:
                 self._by_task[r.task_id] = r
                 if r.data is not None:
@@ -233,6 +242,10 @@ class WorkflowExecutor:
         while True:
             self.runner.health_check()
             self._drain()
+            if self._consecutive_failures >= self.MAX_CONSECUTIVE_FAILURES:
+                # a workflow that raises on every episode would otherwise keep this loop waiting forever
+                raise RuntimeError(f"{self._consecutive_failures} rollout episodes failed in a row; "
+                                   f"last error: {self._last_error}")
             with self._lock:
                 if len(self._results) >= count:
                     self._results.sort(key=lambda r: r.create_time)
@@ -264,6 +277,24 @@ class WorkflowExecutor:
                     raise TimeoutError(f"task {task_id} did not finish within {timeout}s")
                 return None
             time.sleep(0.002)
+
+    def poll_task(self, task_id: int) -> tuple[str, Any]:
+        """Non-blocking state of one task: ``("running", None)``, ``("done", trajectory)``, ``("rejected", None)``
+        (the workflow or the acceptance filter dropped the sample) or ``("failed", message)``. A finished task is
+        forgotten once reported. Used by a rollout controller in another process, which must tell a sample that
+        will never arrive from one that is still being generated."""
+        self.runner.health_check()
+        self._drain()
+        with self._lock:
+            r = self._by_task.pop(task_id, None)
+            if r is None:
+                return "running", None
+            if r.error is not None:
+                return "failed", f"{type(r.error).__name__}: {r.error}"
+            if r.data is None:
+                return "rejected", None
+            self._results = [x for x in self._results if x.task_id != task_id]
+            return "done", r.data
 
     def rollout_batch(self, data: list[dict[str, Any]], workflow=None, workflow_kwargs=None,
                       should_accept_fn=None, group_size: int = 1):

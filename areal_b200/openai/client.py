@@ -126,8 +126,9 @@ class ArealOpenAI:
 
     def _tokenize(self, messages, tools):
         kw = {"tools": tools} if tools else {}
-        ids = self.tokenizer.apply_chat_template(messages, tokenize=True, add_generation_prompt=True, **kw)
-        return list(ids)
+        from ..utils.hf_io import chat_template_ids
+
+        return chat_template_ids(self.tokenizer, messages, add_generation_prompt=True, **kw)
 
     def _process_images(self, messages, image_data, tools):
         """Chat template as text, then the processor on text + decoded images: token ids with the image

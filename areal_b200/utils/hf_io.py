@@ -184,3 +184,17 @@ def load_hf_processor_and_tokenizer(path: str, **kwargs):
 
     processor = AutoProcessor.from_pretrained(path, **kwargs)
     return processor, getattr(processor, "tokenizer", None) or load_hf_tokenizer(path, **kwargs)
+
+
+def chat_template_ids(tokenizer, messages, **kwargs) -> list[int]:
+    """Token ids of ``tokenizer.apply_chat_template(messages, tokenize=True, ...)`` as a plain list: depending on
+    the ``transformers`` version the call returns a list, a tensor or a ``BatchEncoding`` holding ``input_ids``."""
+    out = tokenizer.apply_chat_template(messages, tokenize=True, **kwargs)
+    if hasattr(out, "keys") and "input_ids" in out:
+        out = out["input_ids"]
+    if hasattr(out, "tolist"):
+        out = out.tolist()
+    out = list(out)
+    if out and isinstance(out[0], (list, tuple)):
+        out = list(out[0])
+    return [int(t) for t in out]

