@@ -78,8 +78,10 @@ def test_name_resolve(kind, tmp_path):
         repo.wait("exp/t/none", timeout=0.1, poll_frequency=0.02)
     repo.clear_subtree("exp/t")
     assert repo.find_subtree("exp/t") == []
-    with pytest.raises(NotImplementedError):
+    with pytest.raises(ImportError):  # the etcd3 client library is not installed here
         name_resolve.make_repository(NameResolveConfig(type="etcd3"))
+    with pytest.raises(ValueError):
+        name_resolve.make_repository(NameResolveConfig(type="zookeeper"))
 
 
 def test_seeding_is_deterministic_per_key():
