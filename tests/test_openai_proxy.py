@@ -179,3 +179,72 @@ def test_math_agents_single_multi_turn_and_tools():
     assert first.completion["choices"][0]["finish_reason"] == "tool_calls"
     assert first.completion["choices"][0]["message"]["tool_calls"][0]["function"]["name"] == "multiply"
     assert len(eng.prompts[1]) > len(eng.prompts[0])  # assistant turn + the tool's result went back in
+
+
+def test_gateway_routes_session_keys_to_the_worker_that_owns_them():
+    """Two proxy workers behind one gateway. Each worker's online agent announces it as ready; an external user
+    opens a session through the gateway, talks the OpenAI API with the session key, sets a reward and ends the
+    session; the worker's pending ``wait_for_session`` call then returns the session's credentials and the
+    trajectory is exported from THAT worker. Reference: areal/experimental/openai/proxy/proxy_gateway.py."""
+    import asyncio
+
+    import httpx
+
+    from areal_b200.openai.proxy.online_agent import OnlineAgent
+    from areal_b200.openai.proxy.proxy_gateway import create_gateway_app
+
+    workers = {"w0:1": create_proxy_app(Engine(), Tok(), admin_api_key="adm"),
+               "w1:1": create_proxy_app(Engine(), Tok(), admin_api_key="adm")}
+
+    async def forward(method, url, body, headers):
+        host = url.split("//", 1)[1].split("/", 1)[0]
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=workers[host]), base_url=f"http://{host}") as c:
+            r = await c.request(method, "/" + url.split("//", 1)[1].split("/", 1)[1], json=body, headers=headers)
+            return r.status_code, r.content, r.headers.get("content-type", "application/json")
+
+    gw = create_gateway_app(admin_api_key="adm", forward=forward)
+
+    async def scenario():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=gw), base_url="http://gw") as c:
+            adm = {"Authorization": "Bearer adm"}
+            assert (await c.post("/rl/start_session", json={}, headers=adm)).status_code == 503  # nobody is ready
+
+            async def post(url, body, headers):
+                r = await c.post(url.replace("http://gw", ""), json=body, headers=headers)
+                r.raise_for_status()
+                return r.json()
+
+            agents = [OnlineAgent("http://gw", addr, admin_api_key="adm", timeout=30, post=post) for addr in workers]
+            waits = [asyncio.create_task(a.run({})) for a in agents]
+            while (await c.get("/health")).json()["ready_workers"] < 2:
+                await asyncio.sleep(0.01)
+            sessions = []
+            for _ in range(2):
+                s = (await c.post("/rl/start_session", json={}, headers=adm)).json()
+                sessions.append(s)
+            for s in sessions:
+                key = {"Authorization": f"Bearer {s['api_key']}"}
+                r = (await c.post("/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}],
+                                                                "max_tokens": 4}, headers=key)).json()
+                assert r["object"] == "chat.completion"
+                assert (await c.post("/rl/set_reward", json={"reward": 0.5, "interaction_id": r["id"]}, headers=key)).status_code == 200
+            assert (await c.post("/v1/chat/completions", json={"messages": []},
+                                 headers={"Authorization": "Bearer nope"})).status_code == 401
+            for s in sessions:
+                assert (await c.post("/rl/end_session", json={}, headers={"Authorization": f"Bearer {s['api_key']}"})).status_code == 200
+            done = await asyncio.gather(*waits)
+            return sessions, done
+
+    sessions, done = asyncio.run(scenario())
+    # first come first served: the first session went to the worker that announced itself first
+    assert [d["worker_addr"] for d in done] == ["w0:1", "w1:1"]
+    assert {d["api_key"] for d in done} == {s["api_key"] for s in sessions}
+    # each session lives on exactly one worker, from which its trajectory is exported
+    for d in done:
+        app = workers[d["worker_addr"]]
+        c = TestClient(app)
+        ex = c.post("/export_trajectories", json={"session_id": d["session_id"]}, headers={"Authorization": "Bearer adm"})
+        assert ex.status_code == 200 and len(ex.json()["interactions"]) == 1
+        other = workers["w1:1" if d["worker_addr"] == "w0:1" else "w0:1"]
+        assert TestClient(other).post("/export_trajectories", json={"session_id": d["session_id"]},
+                                      headers={"Authorization": "Bearer adm"}).status_code == 404
