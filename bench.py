@@ -346,7 +346,12 @@ def main():
             dist.init_process_group(backend="nccl", timeout=datetime.timedelta(seconds=7200))
         from areal_b200.parallel.selfcheck import fused_comm_check
 
-        fused_comm = fused_comm_check(iters=5)
+        # M x K x N large enough that the timings are bound by the GPU and the links, not by launches; every
+        # per-rank extent stays a multiple of the 128-wide tile up to 8 ranks
+        try:
+            fused_comm = fused_comm_check(M=16384, K=4096, N=4096, iters=5)
+        except (RuntimeError, AssertionError, ValueError) as e:  # same inputs on every rank: all ranks land here
+            fused_comm = {"error": f"{type(e).__name__}: {e}"[:300]}
         torch.cuda.synchronize()
         dist.barrier()
     trainer = PPOTrainer(cfg, dataset)
@@ -469,7 +474,9 @@ def main():
                 "roles": summarize_roles(roles, dev_ms / 1e3, n_gen, n_train, float(sums[0]), K),
                 "fallback_ops": _lib.fallback_counts(),
             }
-            if fused_comm is not None:
+            if fused_comm is not None and "error" in fused_comm:
+                result["extra_keys"] = {"fused_comm_ok": False, "fused_comm_error": fused_comm["error"]}
+            elif fused_comm is not None:
                 fc = fused_comm
                 result["extra_keys"] = {
                     "fused_comm_ok": fc["ok"], "fused_comm_max_err": fc["max_err"],
