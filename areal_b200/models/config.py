@@ -15,7 +15,7 @@ from pathlib import Path
 
 @dataclass
 class ModelConfig:
-    model_type: str = "qwen3"  # qwen2 | qwen3 | qwen3_moe
+    model_type: str = "qwen3"  # qwen2 | qwen3 | qwen3_moe | qwen3_5 | llama | mistral | the vision-language types
     vocab_size: int = 151936
     hidden_size: int = 2048
     intermediate_size: int = 6144
@@ -25,6 +25,9 @@ class ModelConfig:
     head_dim: int = 128
     rms_norm_eps: float = 1e-6
     rope_theta: float = 1e6
+    # frequency scaling of the rotary table (HF `rope_scaling` / `rope_parameters`): rope_type default | linear |
+    # llama3 | yarn with their parameters; empty = unscaled
+    rope_scaling: dict = field(default_factory=dict)
     max_position_embeddings: int = 40960
     tie_word_embeddings: bool = True
     attention_bias: bool = False  # Qwen2: bias on q/k/v
@@ -169,6 +172,26 @@ class ModelConfig:
             mt = "qwen3_5"
         heads = cfg["num_attention_heads"]
         rope_params = cfg.get("rope_parameters") or {}
+        if mt not in _TEXT_TYPES and mt not in _VL_TYPES:
+            raise NotImplementedError(f"model_type {mt!r}: supported are {sorted(_TEXT_TYPES | set(_VL_TYPES))}")
+        if cfg.get("mlp_bias"):
+            raise NotImplementedError("bias on the MLP projections is not supported")
+        window = cfg.get("sliding_window") if cfg.get("use_sliding_window", mt == "mistral") else None
+        if window and window < cfg.get("max_position_embeddings", 0):
+            import warnings
+
+            warnings.warn(f"sliding-window attention is not implemented: sequences longer than the window "
+                          f"({window} tokens) attend to their whole prefix", stacklevel=2)
+        scaling = dict(cfg.get("rope_scaling") or {})
+        if not scaling and rope_params.get("rope_type", "default") != "default":
+            scaling = {k: v for k, v in rope_params.items() if k not in ("rope_theta", "partial_rotary_factor",
+                                                                         "mrope_section", "mrope_interleaved")}
+        if "type" in scaling and "rope_type" not in scaling:
+            scaling["rope_type"] = scaling.pop("type")
+        if scaling.get("rope_type") in (None, "default", "mrope"):
+            scaling = {}
+        elif scaling["rope_type"] not in ("linear", "llama3", "yarn"):
+            raise NotImplementedError(f"rope scaling {scaling['rope_type']!r} is not supported")
         out = cls(
             model_type=mt,
             vocab_size=cfg["vocab_size"],
@@ -180,6 +203,7 @@ class ModelConfig:
             head_dim=cfg.get("head_dim") or cfg["hidden_size"] // heads,
             rms_norm_eps=cfg.get("rms_norm_eps", 1e-6),
             rope_theta=cfg.get("rope_theta") or rope_params.get("rope_theta", 1e4),
+            rope_scaling=scaling,
             max_position_embeddings=cfg.get("max_position_embeddings", 32768),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
             attention_bias=cfg.get("attention_bias", mt in ("qwen2", "qwen2_5_vl", "qwen2_vl")),
@@ -225,7 +249,8 @@ class ModelConfig:
         if self.is_vl:
             return self._to_hf_config_vl()
         arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
-                "qwen3_moe": "Qwen3MoeForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM"}[self.model_type]
+                "qwen3_moe": "Qwen3MoeForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
+                "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM"}[self.model_type]
         if self.model_type == "qwen3_5" and self.is_moe:
             arch = "Qwen3_5MoeForCausalLM"
         d = {
@@ -241,6 +266,11 @@ class ModelConfig:
             "attention_bias": self.attention_bias, "hidden_act": "silu",
             "torch_dtype": "bfloat16",
         }
+        if self.model_type in ("llama", "mistral"):
+            d.update(mlp_bias=False, sliding_window=None)
+        if self.rope_scaling:
+            d["rope_scaling"] = dict(self.rope_scaling)
+            d["rope_parameters"] = dict(self.rope_scaling, rope_theta=self.rope_theta)
         if self.model_type == "qwen3_5":
             # transformers reads the text decoder as `qwen3_5_text` (`qwen3_5_moe_text` with experts), with the
             # rotary settings inside `rope_parameters`
@@ -305,6 +335,7 @@ _VISION_KEYS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_ch
                 "fullatt_block_indexes", "hidden_act", "variant", "num_position_embeddings",
                 "deepstack_visual_indexes")
 _VL_TYPES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe")
+_TEXT_TYPES = {"qwen2", "qwen3", "qwen3_moe", "qwen3_5", "llama", "mistral"}
 
 # Named shapes used by the benchmark configurations (random-init, synthetic data).
 PRESETS: dict[str, ModelConfig] = {
@@ -382,4 +413,14 @@ PRESETS: dict[str, ModelConfig] = {
                                  num_key_value_heads=4, tie_word_embeddings=False,
                                  num_experts=128, num_experts_per_tok=8,
                                  moe_intermediate_size=768),
+    "llama3.1-8b": ModelConfig(model_type="llama", vocab_size=128256, hidden_size=4096, intermediate_size=14336,
+                               num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                               rms_norm_eps=1e-5, rope_theta=5e5, max_position_embeddings=131072,
+                               tie_word_embeddings=False, qk_norm=False,
+                               rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
+                                             "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}),
+    "mistral-7b": ModelConfig(model_type="mistral", vocab_size=32768, hidden_size=4096, intermediate_size=14336,
+                              num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                              rms_norm_eps=1e-5, rope_theta=1e6, max_position_embeddings=32768,
+                              tie_word_embeddings=False, qk_norm=False),
 }

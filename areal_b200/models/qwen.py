@@ -451,7 +451,8 @@ class QwenModel(nn.Module):
     def rope(self, device, max_pos=None):
         max_pos = max_pos or self.cfg.max_position_embeddings
         if self._rope is None or self._rope[0].device != torch.device(device) or self._rope[0].shape[0] < max_pos:
-            self._rope = fused.rope_tables(max_pos, self.cfg.rotary_dim, self.cfg.rope_theta, device)
+            self._rope = fused.rope_tables(max_pos, self.cfg.rotary_dim, self.cfg.rope_theta, device,
+                                            self.cfg.rope_scaling or None)
         return self._rope
 
     # --------------------------------------------------------------- forward

@@ -95,11 +95,62 @@ def rmsnorm(x, w, eps: float = 1e-6, residual=None):
 # --------------------------------------------------------------------------- RoPE
 
 
-def rope_tables(max_pos: int, dim: int, theta: float, device) -> tuple[torch.Tensor, torch.Tensor]:
+def rope_inv_freq(dim: int, theta: float, scaling: dict | None, device) -> tuple[torch.Tensor, float]:
+    """Inverse frequencies of the rotary table and the factor applied to cos / sin.
+
+    ``scaling`` follows the Hugging Face ``rope_scaling`` dictionaries: ``linear`` divides every frequency by
+    ``factor``; ``llama3`` keeps wavelengths below ``original_max / high_freq_factor``, divides those above
+    ``original_max / low_freq_factor`` by ``factor`` and blends in between; ``yarn`` blends interpolated and
+    extrapolated frequencies with a linear ramp over the dimensions between the ``beta_fast`` / ``beta_slow``
+    rotations and scales the table by ``0.1 * ln(factor) + 1`` (or ``attention_factor``)."""
+    import math
+
     inv = 1.0 / (theta ** (torch.arange(0, dim, 2, dtype=torch.float32, device=device) / dim))
+    kind = (scaling or {}).get("rope_type", "default")
+    if kind == "default":
+        return inv, 1.0
+    factor = float(scaling["factor"])
+    if kind == "linear":
+        return inv / factor, 1.0
+    if kind == "llama3":
+        lo, hi = float(scaling.get("low_freq_factor", 1.0)), float(scaling.get("high_freq_factor", 4.0))
+        old_len = float(scaling["original_max_position_embeddings"])
+        wavelen = 2 * math.pi / inv
+        smooth = ((old_len / wavelen - lo) / (hi - lo)).clamp(0.0, 1.0)
+        return (1 - smooth) * inv / factor + smooth * inv, 1.0
+    if kind == "yarn":
+        old_len = float(scaling.get("original_max_position_embeddings") or 0) or None
+        if old_len is None:
+            raise ValueError("yarn rope scaling needs original_max_position_embeddings")
+        fast, slow = float(scaling.get("beta_fast") or 32), float(scaling.get("beta_slow") or 1)
+
+        def correction_dim(rotations):
+            return dim * math.log(old_len / (rotations * 2 * math.pi)) / (2 * math.log(theta))
+
+        low, high = correction_dim(fast), correction_dim(slow)
+        if scaling.get("truncate", True):
+            low, high = math.floor(low), math.ceil(high)
+        low, high = max(low, 0), min(high, dim - 1)
+        if low == high:
+            high += 0.001
+        ramp = ((torch.arange(dim // 2, dtype=torch.float32, device=device) - low) / (high - low)).clamp(0, 1)
+        extrap = 1 - ramp
+        inv = inv / factor * (1 - extrap) + inv * extrap
+        att = scaling.get("attention_factor")
+        if att is None:
+            mscale, mscale_all = scaling.get("mscale"), scaling.get("mscale_all_dim")
+            get = lambda sc, m=1.0: 1.0 if sc <= 1 else 0.1 * m * math.log(sc) + 1.0
+            att = get(factor, mscale) / get(factor, mscale_all) if mscale and mscale_all else get(factor)
+        return inv, float(att)
+    raise NotImplementedError(f"rope scaling {kind!r}")
+
+
+def rope_tables(max_pos: int, dim: int, theta: float, device,
+                scaling: dict | None = None) -> tuple[torch.Tensor, torch.Tensor]:
+    inv, att = rope_inv_freq(dim, theta, scaling, device)
     t = torch.arange(max_pos, dtype=torch.float32, device=device)
     fr = torch.outer(t, inv)
-    return fr.cos().contiguous(), fr.sin().contiguous()
+    return (fr.cos() * att).contiguous(), (fr.sin() * att).contiguous()
 
 
 def _rot_half(x):

@@ -117,3 +117,38 @@ def test_block_quantised_fp8_checkpoint_is_dequantised_on_load(tmp_path):
     assert d.dtype == torch.bfloat16 and d.shape == (300, 260)
     assert (d.float() - w).abs().max() < 0.07 * w.abs().max()
     assert torch.equal(d, dequant_fp8_blockwise(q, scale_inv))
+
+
+def test_llama_matches_transformers(tmp_path):
+    cfg = dataclasses.replace(PRESETS["tiny-qwen2"], model_type="llama", attention_bias=False, qk_norm=False,
+                              tie_word_embeddings=False)
+    hf = _roundtrip(cfg, tmp_path)
+    assert type(hf).__name__ == "LlamaForCausalLM"
+
+
+def test_mistral_matches_transformers(tmp_path):
+    cfg = dataclasses.replace(PRESETS["tiny-qwen2"], model_type="mistral", attention_bias=False, qk_norm=False,
+                              tie_word_embeddings=False)
+    hf = _roundtrip(cfg, tmp_path)
+    assert type(hf).__name__ == "MistralForCausalLM"
+
+
+@pytest.mark.parametrize("scaling", [
+    {"rope_type": "linear", "factor": 4.0},
+    {"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0, "high_freq_factor": 4.0,
+     "original_max_position_embeddings": 16},
+    {"rope_type": "yarn", "factor": 4.0, "original_max_position_embeddings": 16},
+])
+def test_rope_scaling_matches_transformers(tmp_path, scaling):
+    cfg = dataclasses.replace(PRESETS["tiny-qwen2"], model_type="llama", attention_bias=False, qk_norm=False,
+                              tie_word_embeddings=False, rope_scaling=scaling, max_position_embeddings=64)
+    _roundtrip(cfg, tmp_path)
+    assert ModelConfig.from_hf_config(str(tmp_path)).rope_scaling["rope_type"] == scaling["rope_type"]
+
+
+def test_unknown_model_type_and_scaling_are_rejected():
+    base = PRESETS["tiny-qwen2"].to_hf_config()
+    with pytest.raises(NotImplementedError):
+        ModelConfig.from_hf_config(dict(base, model_type="gpt2"))
+    with pytest.raises(NotImplementedError):
+        ModelConfig.from_hf_config(dict(base, rope_scaling={"rope_type": "longrope", "factor": 2.0}))
