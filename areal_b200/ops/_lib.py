@@ -121,6 +121,64 @@ def fallback_counts() -> dict[str, int]:
     return dict(_fallbacks)
 
 
+class KernelArgumentError(RuntimeError):
+    """Checked mode found an argument that would make a kernel read or write outside its buffers."""
+
+
+def checked() -> bool:
+    """Checked mode (``AREAL_B200_CHECKED=1``): before a launch the wrappers validate, on the host, every
+    index that the kernel takes from data (positions, cache slots, page tables, expert ids) against the
+    extent of the buffer it indexes, and the layout of the operands. Each check costs a device
+    synchronisation, so the mode is for tests and debugging; it is skipped while a CUDA graph is captured."""
+    if os.environ.get("AREAL_B200_CHECKED") != "1":
+        return False
+    return not (torch.cuda.is_available() and torch.cuda.is_current_stream_capturing())
+
+
+_checks_run = 0
+
+
+def checks_run() -> int:
+    return _checks_run
+
+
+def check_index(site: str, t: torch.Tensor | None, upper: int, lower: int = 0, where: torch.Tensor | None = None,
+                allow_negative: bool = False) -> None:
+    """Raises unless every element of ``t`` (restricted to ``where``; negative values pass when
+    ``allow_negative`` says that the kernel skips them) lies in ``[lower, upper)``."""
+    global _checks_run
+    if t is None or t.numel() == 0:
+        return
+    _checks_run += 1
+    v = t if where is None else t[where]
+    if v.numel() == 0:
+        return
+    if allow_negative:
+        v = v[v >= 0]
+        if v.numel() == 0:
+            return
+    lo, hi = int(v.min()), int(v.max())
+    if lo < lower or hi >= upper:
+        raise KernelArgumentError(f"{site}: index range [{lo}, {hi}] outside [{lower}, {upper})")
+
+
+def check_operand(site: str, t: torch.Tensor | None, dtype: torch.dtype | None = None, shape: tuple | None = None,
+                  align: int = 16, contiguous: bool = True) -> None:
+    """Layout of one kernel operand: dtype, shape (``None`` entries are free), base alignment, contiguity."""
+    global _checks_run
+    if t is None:
+        return
+    _checks_run += 1
+    if dtype is not None and t.dtype != dtype:
+        raise KernelArgumentError(f"{site}: dtype {t.dtype}, expected {dtype}")
+    if shape is not None and (t.dim() != len(shape) or any(e is not None and e != a for a, e in zip(t.shape, shape))):
+        raise KernelArgumentError(f"{site}: shape {tuple(t.shape)}, expected {shape}")
+    if contiguous and not t.is_contiguous():
+        raise KernelArgumentError(f"{site}: operand is not contiguous (strides {t.stride()})")
+    if align and t.numel() and t.data_ptr() % align:
+        raise KernelArgumentError(f"{site}: base address {t.data_ptr():#x} is not {align}-byte aligned")
+
+
 def read_status() -> int:
     """Synchronises the current stream and returns (and clears) the device status word.
 

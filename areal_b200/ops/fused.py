@@ -184,6 +184,8 @@ class _QKNormRope(torch.autograd.Function):
         k = torch.empty((T, Hkv, D), dtype=qkv.dtype, device=qkv.device)
         rstd = torch.empty(T * (Hq + Hkv) if has_norm else 1, dtype=torch.float32,
                            device=qkv.device)
+        if _lib.checked():
+            _check_rope_args("qknorm_rope", qkv, qw, kw, cos, sin, pos, Hq, Hkv, D)
         lib = _lib.kernels()
         lib.b200_qknorm_rope_fwd.restype = ctypes.c_int
         rc = lib.b200_qknorm_rope_fwd(_lib.ptr(qkv), _lib.ptr(qw), _lib.ptr(kw), _lib.ptr(cos),
@@ -225,6 +227,17 @@ class _QKNormRope(torch.autograd.Function):
         return dqkv, None, None, None, None, None, None, None, None, None
 
 
+def _check_rope_args(site, qkv, qw, kw, cos, sin, pos, Hq, Hkv, D):
+    T = qkv.shape[0]
+    _lib.check_operand(f"{site}.qkv", qkv, torch.bfloat16, (T, (Hq + 2 * Hkv) * D))
+    _lib.check_operand(f"{site}.cos", cos, torch.float32, (None, D // 2), align=8)
+    _lib.check_operand(f"{site}.sin", sin, torch.float32, tuple(cos.shape), align=8)
+    _lib.check_operand(f"{site}.pos", pos, torch.int32, (T,), align=4)
+    _lib.check_operand(f"{site}.q_norm", qw, torch.bfloat16, (D,), align=4)
+    _lib.check_operand(f"{site}.k_norm", kw, torch.bfloat16, (D,), align=4)
+    _lib.check_index(f"{site}.pos", pos, cos.shape[0])
+
+
 def qknorm_rope(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps=1e-6):
     """Splits a fused qkv projection, applies per-head RMSNorm to q and k (when
     ``qw``/``kw`` are given, Qwen3) and rotary embedding; returns ``(q, k, v)``
@@ -248,6 +261,12 @@ def qknorm_rope_kvwrite(qkv, qw, kw, cos, sin, pos, Hq, Hkv, D, eps, slot_mappin
     T = qkv.shape[0]
     q = torch.empty((T, Hq, D), dtype=qkv.dtype, device=qkv.device)
     slots = slot_mapping if slot_mapping.dtype == torch.int64 else slot_mapping.to(torch.int64)
+    if _lib.checked():
+        _check_rope_args("qknorm_rope_kvwrite", qkv, qw, kw, cos, sin, pos, Hq, Hkv, D)
+        _lib.check_operand("qknorm_rope_kvwrite.k_cache", k_cache, torch.bfloat16, (None, Hkv, None, D))
+        _lib.check_operand("qknorm_rope_kvwrite.v_cache", v_cache, torch.bfloat16, tuple(k_cache.shape))
+        _lib.check_index("qknorm_rope_kvwrite.slot_mapping", slots[:T], k_cache.shape[0] * k_cache.shape[2],
+                         allow_negative=True)
     rc = _lib.kernels().b200_qknorm_rope_kvwrite(
         _lib.ptr(qkv), _lib.ptr(qw), _lib.ptr(kw), _lib.ptr(cos), _lib.ptr(sin), _lib.ptr(pos), _lib.ptr(q),
         _lib.ptr(slots.contiguous()), _lib.ptr(k_cache), _lib.ptr(v_cache), ctypes.c_int(T), ctypes.c_int(Hq),

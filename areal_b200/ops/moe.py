@@ -113,6 +113,8 @@ def sort_by_expert(idx: torch.Tensor, num_experts: int) -> ExpertSort:
     s = ExpertSort(n, k, num_experts, max_vm * 128, ints(n), ints(max_vm * 128), ints(num_experts),
                    ints(num_experts + 1), ints(max_vm), ints(1))
     chunk_hist = ints(max((n + 255) // 256, 1) * num_experts)
+    if _lib.checked():
+        _lib.check_index("moe_sort.expert_ids", idx, num_experts)
     rc = _lib.kernels().b200_moe_sort(_lib.ptr(idx), ctypes.c_int(n), ctypes.c_int(num_experts), _lib.ptr(chunk_hist),
                                       _lib.ptr(s.counts), _lib.ptr(s.prow0), _lib.ptr(s.tile_expert),
                                       _lib.ptr(s.num_vm), _lib.ptr(s.dest), _lib.ptr(s.src_of), ctypes.c_int(max_vm),

@@ -24,6 +24,10 @@ def kv_cache_write(k, v, slot_mapping, k_cache, v_cache):
         k_cache[blk, :, off] = k[ok].to(k_cache.dtype)
         v_cache[blk, :, off] = v[ok].to(v_cache.dtype)
         return
+    if _lib.checked():
+        _lib.check_operand("kv_cache_write.k_cache", k_cache, None, (None, Hkv, bs, D))
+        _lib.check_operand("kv_cache_write.v_cache", v_cache, None, tuple(k_cache.shape))
+        _lib.check_index("kv_cache_write.slot_mapping", slot_mapping[:T], k_cache.shape[0] * bs, allow_negative=True)
     lib = _lib.kernels()
     lib.b200_kv_cache_write.restype = ctypes.c_int
     rc = lib.b200_kv_cache_write(_lib.ptr(k), _lib.ptr(v), ctypes.c_longlong(k.stride(0)),
@@ -76,6 +80,16 @@ def paged_decode(q, k_cache, v_cache, block_table, seq_lens, scale=None, nsplit:
         ml_part = torch.empty((B, Hq, nsplit, 2), dtype=torch.float32, device=q.device)
     else:
         o_part = ml_part = None
+    if _lib.checked():
+        max_blocks = block_table.shape[1]
+        _lib.check_operand("paged_decode.block_table", block_table, torch.int32, (None, max_blocks), align=4)
+        _lib.check_operand("paged_decode.seq_lens", seq_lens, torch.int32, None, align=4)
+        _lib.check_operand("paged_decode.k_cache", k_cache, torch.bfloat16, (nb, Hkv, bs, D))
+        _lib.check_operand("paged_decode.v_cache", v_cache, torch.bfloat16, (nb, Hkv, bs, D))
+        lens = seq_lens[:B].long()
+        _lib.check_index("paged_decode.seq_lens", lens, max_blocks * bs + 1)
+        used = torch.arange(max_blocks, device=q.device)[None, :] < ((lens + bs - 1) // bs)[:, None]
+        _lib.check_index("paged_decode.block_table", block_table[:B], nb, where=used)
     lib = _lib.kernels()
     lib.b200_paged_decode.restype = ctypes.c_int
     rc = lib.b200_paged_decode(_lib.ptr(q), _lib.ptr(k_cache), _lib.ptr(v_cache),

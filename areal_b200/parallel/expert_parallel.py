@@ -93,6 +93,9 @@ class EPRank:
         n = s.n
         copy_row = torch.empty(n, dtype=torch.int32, device=self.device)
         x = x if x.stride(1) == 1 else x.contiguous()
+        if _lib.checked():
+            _lib.check_operand("ep_dispatch.idx", idx, torch.int32, None, align=4)
+            _lib.check_index("ep_dispatch.expert_ids", idx, self.el * self.world)
         rc = _lib.kernels().b200_ep_dispatch(_lib.ptr(x), ctypes.c_longlong(x.stride(0)), _lib.ptr(idx), _lib.ptr(w),
                                              _lib.ptr(s.dest), _lib.ptr(s.prow0), _lib.ptr(plan.send_base),
                                              ctypes.c_int(n), ctypes.c_int(s.k), ctypes.c_int(self.H),
