@@ -16,7 +16,7 @@ import os
 from typing import Any, Callable
 
 from .loaders import load_records
-from . import gsm8k, hhrlhf, geometry3k, clevr_count_70k, torl_data, countdown  # noqa: F401
+from . import gsm8k, hhrlhf, geometry3k, clevr_count_70k, torl_data, countdown, agent_tasks  # noqa: F401
 
 _REGISTRY: dict[tuple[str, str], Callable] = {}
 
@@ -29,7 +29,7 @@ def register(name: str, type_: str):
     return deco
 
 
-for _mod in (gsm8k, hhrlhf, geometry3k, clevr_count_70k, torl_data, countdown):
+for _mod in (gsm8k, hhrlhf, geometry3k, clevr_count_70k, torl_data, countdown, agent_tasks):
     for (_n, _t), _f in getattr(_mod, "BUILDERS", {}).items():
         _REGISTRY[(_n, _t)] = _f
 

@@ -3,5 +3,8 @@ chat-completions protocol. They run through :class:`areal_b200.openai.proxy.work
 (inline with an engine-bound client, or against the proxy server's ``base_url``)."""
 
 from .math_agent import CALCULATOR_TOOLS, MathAgent, MathToolAgent, MultiTurnMathAgent, math_reward_fn
+from .search_agent import HttpSearch, LocalCorpus, ReActSearchAgent, qa_reward
+from .terminal_agent import TerminalAgent
 
-__all__ = ["CALCULATOR_TOOLS", "MathAgent", "MathToolAgent", "MultiTurnMathAgent", "math_reward_fn"]
+__all__ = ["CALCULATOR_TOOLS", "MathAgent", "MathToolAgent", "MultiTurnMathAgent", "math_reward_fn",
+           "HttpSearch", "LocalCorpus", "ReActSearchAgent", "qa_reward", "TerminalAgent"]

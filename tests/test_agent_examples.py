@@ -1,0 +1,165 @@
+"""Search and terminal agents: retrieval, scoring, the tool loops against a scripted chat client, datasets."""
+import asyncio
+import json
+import types
+
+import pytest
+
+from areal_b200.dataset import get_custom_dataset
+from areal_b200.infra.sandbox import ShellWorkspace
+from areal_b200.workflow.agents import HttpSearch, LocalCorpus, ReActSearchAgent, TerminalAgent, qa_reward
+from areal_b200.workflow.agents.search_agent import extract_final_answer, normalize_answer, qa_f1, run_search_tool
+from areal_b200.workflow.agents.terminal_agent import run_terminal_tool, score_checks
+
+DOCS = [
+    {"id": "d1", "title": "Eiffel Tower", "text": "The Eiffel Tower is a wrought-iron lattice tower in Paris, France. "
+                                                    "It was completed in 1889 by Gustave Eiffel's company."},
+    {"id": "d2", "title": "Statue of Liberty", "text": "The Statue of Liberty stands in New York Harbor. It was a gift "
+                                                         "from France, dedicated in 1886."},
+    {"id": "d3", "title": "Great Wall", "text": "The Great Wall of China is a series of fortifications built across "
+                                                 "the northern borders of ancient Chinese states."},
+]
+
+
+class ScriptedClient:
+    """Stands in for the chat client: returns the next scripted assistant message and records the requests."""
+
+    def __init__(self, script):
+        self.script, self.requests = list(script), []
+        self.chat = types.SimpleNamespace(completions=types.SimpleNamespace(create=self._create))
+
+    async def _create(self, **kw):
+        self.requests.append(dict(kw, messages=list(kw["messages"])))   # the agent keeps appending to its list
+        msg = self.script.pop(0)
+        calls = [types.SimpleNamespace(id=f"call{i}", function=types.SimpleNamespace(name=n, arguments=json.dumps(a)))
+                 for i, (n, a) in enumerate(msg.get("tool_calls", []))]
+        message = types.SimpleNamespace(content=msg.get("content"), tool_calls=calls or None)
+        return types.SimpleNamespace(id=f"cmpl{len(self.requests)}", choices=[types.SimpleNamespace(message=message)])
+
+
+def test_bm25_ranks_the_matching_passage_first():
+    corpus = LocalCorpus(DOCS)
+    hits = corpus.search("who built the tower in Paris", top_k=2)
+    assert hits[0]["id"] == "d1" and len(hits) <= 2
+    assert corpus.search("zebra quantum")[:1] == []
+    assert corpus.search("France")[0]["id"] in ("d1", "d2")
+    assert "New York Harbor" in corpus.visit("d2") and corpus.visit("nope") is None
+
+
+def test_bm25_prefers_rare_terms_and_from_jsonl(tmp_path):
+    p = tmp_path / "corpus.jsonl"
+    p.write_text("\n".join(json.dumps(d) for d in DOCS))
+    corpus = LocalCorpus.from_jsonl(str(p))
+    # "fortifications" occurs in one passage only, "the" in all: the rare term decides
+    assert corpus.search("the fortifications")[0]["id"] == "d3"
+
+
+def test_answer_scoring():
+    assert normalize_answer("The  Eiffel-Tower!") == "eiffeltower"
+    assert qa_f1("Gustave Eiffel", "gustave eiffel") == 1.0
+    assert 0 < qa_f1("Gustave Eiffel company", "Gustave Eiffel") < 1
+    assert qa_f1("Paris", "London") == 0.0
+    assert extract_final_answer("a <answer>x</answer> b <answer> 1889 </answer>") == "1889"
+    assert qa_reward("I think <answer>1889</answer>", ["1889", "in 1889"]) == 1.0
+    assert qa_reward("1889 without tags", "1889") == 0.0
+    assert qa_reward("<answer>the year 1889</answer>", "1889", metric="em") == 0.0
+
+
+def test_search_tool_reports_errors_as_text():
+    corpus = LocalCorpus(DOCS)
+    assert "[d1]" in run_search_tool(corpus, "search", {"query": "Eiffel"})
+    assert run_search_tool(corpus, "visit", '{"doc_id": "zzz"}') == "error: unknown doc_id"
+    assert run_search_tool(corpus, "search", "{not json").startswith("error:")
+    assert run_search_tool(corpus, "fly", {}).startswith("error: unknown tool")
+
+
+def test_http_backend_uses_the_service_protocol():
+    seen = []
+
+    def post(url, payload):
+        seen.append((url, payload))
+        return {"results": [{"id": "x", "title": "t", "snippet": "s"}]} if url.endswith("/search") else {"text": "full"}
+
+    b = HttpSearch("http://svc:1/", post=post)
+    assert b.search("q", 3)[0]["id"] == "x" and b.visit("x") == "full"
+    assert seen == [("http://svc:1/search", {"query": "q", "top_k": 3}), ("http://svc:1/visit", {"id": "x"})]
+
+
+def test_react_agent_loop_feeds_tool_results_back():
+    client = ScriptedClient([
+        {"tool_calls": [("search", {"query": "Eiffel Tower completed"})]},
+        {"tool_calls": [("visit", {"doc_id": "d1"})]},
+        {"content": "It was finished in <answer>1889</answer>."},
+    ])
+    agent = ReActSearchAgent(LocalCorpus(DOCS), max_turns=5, temperature=1.0, max_tokens=5)
+    data = {"messages": [{"role": "user", "content": "When was the Eiffel Tower completed?"}], "answer": ["1889"]}
+    assert asyncio.run(agent.run(data, client=client)) == 1.0
+    assert len(client.requests) == 3 and "max_tokens" not in client.requests[0]
+    last = client.requests[-1]["messages"]
+    assert [m["role"] for m in last] == ["system", "user", "assistant", "tool", "assistant", "tool"]
+    assert "[d1]" in last[3]["content"] and "wrought-iron" in last[5]["content"]
+
+
+def test_react_agent_without_answer_gets_penalty_and_respects_max_turns():
+    client = ScriptedClient([{"tool_calls": [("search", {"query": "x"})]}] * 3)
+    agent = ReActSearchAgent(LocalCorpus(DOCS), max_turns=3, invalid_penalty=0.5)
+    r = asyncio.run(agent.run({"messages": [{"role": "user", "content": "q"}], "answer": "a"}, client=client))
+    assert r == -0.5 and len(client.requests) == 3
+
+
+def test_shell_workspace_keeps_state_and_fences_paths():
+    with ShellWorkspace(files={"src/a.txt": "hello\n"}) as ws:
+        assert ws.run("cat src/a.txt").stdout == "hello\n"
+        assert ws.run("echo more > b.txt && ls").ok
+        assert ws.read_file("b.txt") == "more\n"
+        assert ws.run("exit 3").exit_code == 3
+        r = ws.run("sleep 30", timeout=0.5)
+        assert r.timed_out and not r.ok
+        with pytest.raises(ValueError):
+            ws.write_file("../escape.txt", "x")
+        root = ws.root
+    import os
+
+    assert not os.path.exists(root)
+
+
+def test_terminal_tools_and_checks():
+    with ShellWorkspace() as ws:
+        assert run_terminal_tool(ws, "write_file", {"path": "f.py", "content": "print(6*7)\n"}) == "ok"
+        out = run_terminal_tool(ws, "bash", {"command": "python3 f.py"})
+        assert out.startswith("exit code 0") and "42" in out
+        assert run_terminal_tool(ws, "read_file", {"path": "f.py"}) == "print(6*7)\n"
+        assert run_terminal_tool(ws, "read_file", {"path": "missing"}).startswith("error:")
+        assert score_checks(ws, ["test -f f.py", "test -f g.py"]) == 0.5
+        assert score_checks(ws, ["test -f f.py", "test -f g.py"], all_or_nothing=True) == 0.0
+        assert score_checks(ws, []) == 0.0
+
+
+def test_terminal_agent_episode_is_rewarded_by_the_checks():
+    client = ScriptedClient([
+        {"tool_calls": [("read_file", {"path": "calc.py"})]},
+        {"tool_calls": [("write_file", {"path": "calc.py", "content": "def add(a, b):\n    return a + b\n"})]},
+        {"tool_calls": [("bash", {"command": "python3 -c 'import calc; print(calc.add(2, 3))'"})]},
+        {"content": "Fixed the add function."},
+    ])
+    task = {"instruction": "calc.add returns the wrong result; fix it.",
+            "files": {"calc.py": "def add(a, b):\n    return a - b\n"},
+            "checks": ["python3 -c 'import calc, sys; sys.exit(calc.add(2, 3) != 5)'", "test -f calc.py"]}
+    assert asyncio.run(TerminalAgent(max_turns=6).run(task, client=client)) == 1.0
+    assert "5" in client.requests[-1]["messages"][-1]["content"]
+    # an agent that does nothing passes only the second check
+    lazy = ScriptedClient([{"content": "done"}])
+    assert asyncio.run(TerminalAgent().run(task, client=lazy)) == 0.5
+
+
+def test_agent_datasets(tmp_path):
+    qa = tmp_path / "hotpot_qa.jsonl"
+    qa.write_text(json.dumps({"question": "q1", "answer": "a1"}) + "\n" +
+                  json.dumps({"question": "q2", "answers": ["a2", "b2"]}) + "\n" + json.dumps({"question": "q3"}) + "\n")
+    items = get_custom_dataset(path=str(qa), type="rl")
+    assert [i["answer"] for i in items] == [["a1"], ["a2", "b2"]]
+    tasks = tmp_path / "terminal_tasks.jsonl"
+    tasks.write_text(json.dumps({"instruction": "do", "files": {"a": "b"}, "checks": ["true"]}) + "\n" +
+                     json.dumps({"instruction": "no checks"}) + "\n")
+    items = get_custom_dataset(path=str(tasks), type="rl")
+    assert len(items) == 1 and items[0]["checks"] == ["true"] and items[0]["messages"][0]["content"] == "do"

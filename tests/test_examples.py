@@ -111,3 +111,24 @@ def test_gsm8k_sft_example_runs_end_to_end_on_cpu(tmp_path):
                  ["total_train_steps=2", "train_dataset.batch_size=4", "actor.model_preset=tiny-qwen2", "actor.path=",
                   "actor.init_from_scratch=true", "actor.dtype=float32", "actor.backend=fsdp:d1",
                   "valid_dataset=null", "saver.freq_epochs=null", "evaluator.freq_epochs=null"])
+
+
+def test_search_agent_example_runs_end_to_end_on_cpu(tmp_path):
+    """The search-agent example through the OpenAI-protocol workflow: a local QA file, a BM25 corpus, the tiny
+    model (whose random text calls no tool and tags no answer, so rewards are 0) — two asynchronous steps."""
+    import json
+
+    qa_dir = tmp_path / "hotpot_qa"
+    qa_dir.mkdir()
+    for split in ("train", "test"):
+        with open(qa_dir / f"{split}.jsonl", "w") as f:
+            for i in range(16):
+                f.write(json.dumps({"question": f"What is {i} plus {i} ?", "answers": [str(2 * i)]}) + "\n")
+    corpus = tmp_path / "corpus.jsonl"
+    corpus.write_text("\n".join(json.dumps({"id": f"d{i}", "title": f"sum {i}", "text": f"{i} plus {i} is {2 * i}"})
+                                for i in range(16)))
+    root = _run_example(os.path.join(ROOT, "examples", "search_agent", "search_agent_rl.py"), "gsm8k_grpo_cpu.yaml",
+                        tmp_path, [f"train_dataset.path={qa_dir}", f"corpus={corpus}", "max_turns=2",
+                                   "total_train_steps=2", "train_dataset.batch_size=4", "gconfig.max_new_tokens=8",
+                                   "saver.freq_epochs=null", "evaluator.freq_epochs=null"])
+    assert glob.glob(str(root / "logs" / "**" / "*.jsonl"), recursive=True)
