@@ -174,12 +174,12 @@ def role_budget(a: dict, b: dict) -> dict:
             continue
         frac = {name: d(key) / wall for name, key in _RO_PHASES.items()}
         frac["other"] = 1.0 - sum(frac.values())
-        pre = max(d("rollout/prefill_tokens"), 1.0)
         out[int(g)] = {"wall_s": wall, "generated_tok_s": d("rollout/generated_tokens") / wall,
                        "decode_steps": d("rollout/engine_steps"),
                        "tokens_per_decode_step": d("rollout/generated_tokens") / max(d("rollout/engine_steps"), 1.0),
                        "prefill_tok_s": d("rollout/prefill_tokens") / max(d("rollout/host_s/prefill"), 1e-9),
-                       "reprefill_share_of_prefill_tokens": d("rollout/reprefill_tokens") / pre,
+                       "prefill_tokens": d("rollout/prefill_tokens"),
+                       "resubmitted_context_tokens": d("rollout/reprefill_tokens"),
                        "time_frac": {k: round(v, 4) for k, v in frac.items()}}
     return out
 
@@ -199,8 +199,11 @@ def summarize_roles(roles: list, window_s: float, n_gen: int, n_train: int, trai
         "rollout_time_frac": mean_frac,
         "rollout_tokens_per_decode_step": (sum(v["tokens_per_decode_step"] for v in ro.values()) / len(ro)) if ro else None,
         "rollout_prefill_tok_s": (sum(v["prefill_tok_s"] for v in ro.values()) / len(ro)) if ro else None,
-        "rollout_reprefill_share_of_prefill_tokens":
-            (sum(v["reprefill_share_of_prefill_tokens"] for v in ro.values()) / len(ro)) if ro else None,
+        # context tokens of requests re-submitted after a weight update (counted when re-submitted; the pages of a
+        # shared prompt are not recomputed) beside the tokens that prefill steps actually computed in the window
+        "rollout_prefill_tokens_per_gpu": (sum(v["prefill_tokens"] for v in ro.values()) / len(ro)) if ro else None,
+        "rollout_resubmitted_context_tokens_per_gpu":
+            (sum(v["resubmitted_context_tokens"] for v in ro.values()) / len(ro)) if ro else None,
         "consumed_tok_s_per_trainer_gpu": trained_tokens / max(sum(busy), 1e-9),
         "trainer_idle_frac": sum(wait) / max(window_s * len(roles), 1e-9),
         "trainer_phase_s_per_step": {k.split("/")[1]: round(sum(r["phase_s"][k] for r in roles) / len(roles) / steps, 4)
