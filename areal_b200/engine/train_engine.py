@@ -175,6 +175,10 @@ class B200TrainEngine(TrainEngine):
                     self.config.archon.pp_schedule if family == "archon" else ("Interleaved1F1B" if vpp > 1 else "1F1B"))
                 self._pp_schedule = canonical_schedule(name, vpp)
                 self._vpp = vpp
+                if self._pp_schedule == "zero_bubble":
+                    from ..ops import wgrad_defer
+
+                    wgrad_defer.arm()  # linear layers get the backward that can park its weight-gradient GEMM
                 self.pctx.extras["vpp"] = vpp
             if ps.cp_size > 1 and self.config.backend.split(":")[0] == "megatron" and \
                     getattr(self.config.megatron, "cp_comm_type", "a2a") in ("allgather", "p2p"):

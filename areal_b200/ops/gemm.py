@@ -19,7 +19,7 @@ import ctypes
 
 import torch
 
-from . import _lib
+from . import _lib, wgrad_defer
 
 
 def _gemm_ref(a, b, a_mn, b_mn, bias, out_dtype, out, accumulate):
@@ -187,7 +187,15 @@ class _Linear(torch.autograd.Function):
             dx = gemm(dy2, w, b_mn=True, out_dtype=x2.dtype).reshape(ctx.in_shape)
         if ctx.needs_input_grad[1]:
             main = getattr(w, "main_grad", None)
-            if main is not None:
+            queue = wgrad_defer.active()
+            if queue is not None and (main is not None or w.is_leaf):
+                # zero-bubble pipeline schedules: the weight-gradient GEMM is parked and runs in a later W action
+                if main is not None:
+                    queue.push(lambda: gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True))
+                else:
+                    queue.push(lambda: wgrad_defer.accumulate(
+                        w, gemm(dy2, x2, a_mn=True, b_mn=True, out_dtype=w.dtype)))
+            elif main is not None:
                 # fp32 main-grad accumulation across micro-batches, fused in the epilogue
                 gemm(dy2, x2, a_mn=True, b_mn=True, out=main, accumulate=True)
                 dw = None
@@ -202,4 +210,6 @@ def linear(x: torch.Tensor, w: torch.Tensor, bias: torch.Tensor | None = None) -
     """``x @ w.T + bias`` with forward and both backward products on the tcgen05 kernel."""
     if x.is_cuda and x.dtype == torch.bfloat16:
         return _Linear.apply(x, w, bias)
+    if wgrad_defer.armed() and torch.is_grad_enabled():
+        return wgrad_defer.SplitLinear.apply(x, w, bias)
     return torch.nn.functional.linear(x, w, bias)

@@ -1,13 +1,18 @@
 """Pipeline-parallel schedules and the executor that runs them over asynchronous point-to-point.
 
-A schedule is, per pipeline rank, an ordered list of actions ``("F" | "B", micro_batch, chunk)``; ``chunk``
-selects one of the rank's ``V`` model chunks (virtual stages: chunk ``v`` of rank ``p`` is virtual stage
-``v * P + p``). Three schedules are built here:
+A schedule is, per pipeline rank, an ordered list of actions ``("F" | "B" | "W", micro_batch, chunk)``;
+``chunk`` selects one of the rank's ``V`` model chunks (virtual stages: chunk ``v`` of rank ``p`` is virtual
+stage ``v * P + p``). Four schedules are built here:
 
 * ``gpipe``: every forward, then every backward (activations of all micro-batches stay alive);
 * ``1f1b``: ``P - 1 - p`` warm-up forwards, then one forward / one backward alternating, then the
   remaining backwards; at most ``P - p`` micro-batches are alive on rank ``p``;
-* ``interleaved_1f1b``: the same idea over virtual stages, which divides the bubble by ``V``.
+* ``interleaved_1f1b``: the same idea over virtual stages, which divides the bubble by ``V``;
+* ``zero_bubble``: the backward pass is split. ``B`` computes only the input gradients (what the previous
+  stage waits for) and parks every linear layer's weight-gradient GEMM (``ops/wgrad_defer.py``); ``W`` runs
+  the parked GEMMs of one micro-batch. Forwards and ``B`` keep the (interleaved) 1F1B order and its
+  activation bound, and each rank's ``W`` actions are placed by a list scheduler wherever the rank would
+  otherwise wait for a neighbour (the ZB-H1 construction, extended to virtual stages).
 
 Every rank can build every rank's list, so :func:`simulate` replays a whole pipeline on the host and reports
 makespan, bubble fraction and the peak number of live activations (used by the tests and the docs).
@@ -30,33 +35,39 @@ where they are host-side requests); on CUDA a receive is posted when its action 
 
 Reference: areal/experimental/models/archon/pipeline_parallel.py:48-82 (``build_pipeline_schedule``:
 1F1B, Interleaved1F1B, zero-bubble variants) and :349-494, options areal/api/cli_args.py:537-700; Megatron's
-schedules behind areal/engine/megatron_engine.py:882. The zero-bubble variants split a backward pass into
-input-gradient and weight-gradient halves; here their names select ``interleaved_1f1b``.
+schedules behind areal/engine/megatron_engine.py:882. The reference's ZBV variant also places the chunks in
+a V shape over the ranks; here both zero-bubble names select the split schedule over the interleaved placement.
 """
 
 from __future__ import annotations
 
+import contextlib
+import functools
 from dataclasses import dataclass, field
 from typing import Any, Callable
 
 import torch
 import torch.distributed as dist
 
+from ..ops.wgrad_defer import WgradQueue
+
 Action = tuple[str, int, int]  # kind, micro-batch, chunk
 
 _ALIASES = {
     "gpipe": "gpipe", "1f1b": "1f1b", "interleaved1f1b": "interleaved_1f1b", "interleaved_1f1b": "interleaved_1f1b",
-    "interleavedzerobubble": "interleaved_1f1b", "zbvzerobubble": "interleaved_1f1b",
+    "interleavedzerobubble": "zero_bubble", "zbvzerobubble": "zero_bubble", "zerobubble": "zero_bubble",
+    "zb1p": "zero_bubble", "zbh1": "zero_bubble", "zero_bubble": "zero_bubble",
 }
 
 
 def canonical_schedule(name: str, virtual: int) -> str:
     key = _ALIASES.get(str(name).replace("-", "").replace(" ", "").lower())
     if key is None:
-        raise ValueError(f"unknown pipeline schedule {name!r}; known: GPipe, 1F1B, Interleaved1F1B")
+        raise ValueError(f"unknown pipeline schedule {name!r}; known: GPipe, 1F1B, Interleaved1F1B, "
+                         f"InterleavedZeroBubble / ZBVZeroBubble")
     if key == "interleaved_1f1b" and virtual == 1:
         return "1f1b"  # one chunk per rank: the interleaved order degenerates to plain 1F1B
-    if key != "interleaved_1f1b" and virtual > 1:
+    if key not in ("interleaved_1f1b", "zero_bubble") and virtual > 1:
         raise ValueError(f"schedule {name!r} runs one model chunk per rank; virtual stages need Interleaved1F1B")
     return key
 
@@ -70,6 +81,13 @@ def build_schedule(name: str, pp_size: int, n_mbs: int, rank: int, virtual: int 
         if V == 1:
             return [("F", m, 0) for m in range(M)]
         return [("F",) + _virtual_to_mb_chunk(k, P, V, True) for k in range(M * V)]
+    if kind == "zero_bubble":
+        import os
+
+        # extra micro-batches of activation memory the list scheduler may use beyond the 1F1B bound (0 = same
+        # memory as 1F1B; every unit lets weight-gradient work slide later and shortens the step a little more)
+        slack = float(os.environ.get("AREAL_B200_PP_ZB_SLACK", "0"))
+        return _zero_bubble_schedules(P, M, V, slack)[rank]
     if kind == "gpipe":
         return [("F", m, 0) for m in range(M)] + [("B", m, 0) for m in range(M)]
     if kind == "1f1b":
@@ -94,6 +112,80 @@ def build_schedule(name: str, pp_size: int, n_mbs: int, rank: int, virtual: int 
     return acts
 
 
+PARKED_WEIGHT = 0.5  # memory of a micro-batch between B and W, as a share of its memory between F and B
+
+
+@functools.lru_cache(maxsize=64)
+def _zero_bubble_schedules(P: int, M: int, V: int, slack: float = 0.0) -> tuple[tuple[Action, ...], ...]:
+    """Action lists of all ranks for the split-backward schedule, by list scheduling on the host.
+
+    Every rank keeps the forward order and the ``B`` order of (interleaved) 1F1B, so the messages of every
+    link keep their order. A micro-batch holds its activations from ``F`` to ``B`` and, from ``B`` to ``W``,
+    what the parked products keep (layer inputs and output gradients, counted as ``PARKED_WEIGHT`` of a full
+    set); a rank starts a forward only if that sum stays within ``cap`` afterwards, the live-activation bound of
+    (interleaved) 1F1B, so the schedule needs no more memory than 1F1B. Time is
+    simulated with unit costs for F, B and W. A free rank takes, in this order: the next ``B`` if its
+    gradient has arrived; the next ``F`` if its input has arrived and the cap allows; a parked ``W``. Only
+    when none applies does it wait for the next arrival. W actions therefore land exactly where 1F1B idles:
+    while the first gradients travel back and during the cool-down."""
+    if V > 1 and M % P != 0:
+        raise ValueError(f"virtual stages need a micro-batch count that is a multiple of the pipeline size "
+                         f"(got {M} micro-batches, {P} stages)")
+    total = M * V
+    order_f = [_virtual_to_mb_chunk(k, P, V, True) if V > 1 else (k, 0) for k in range(total)]
+    order_b = [_virtual_to_mb_chunk(k, P, V, False) if V > 1 else (k, 0) for k in range(total)]
+    cap = [(min((P - 1 - r) * 2 + (V - 1) * P, total) + 1 if V > 1 else min(P - r, M)) + slack for r in range(P)]
+    last_vs = P * V - 1
+    done: dict[tuple[str, int, int], float] = {}
+    nf, nb, nw = [0] * P, [0] * P, [0] * P
+    parked: list[list[tuple[int, int]]] = [[] for _ in range(P)]
+    free = [0.0] * P
+    acts: list[list[Action]] = [[] for _ in range(P)]
+    n_left = 3 * total * P
+    now = 0.0
+    while n_left:
+        progressed = False
+        for r in range(P):
+            if free[r] > now:
+                continue
+            choice = None
+            if nb[r] < total:
+                mb, c = order_b[nb[r]]
+                vs = c * P + r
+                dep = ("F", mb, vs) if vs == last_vs else ("B", mb, vs + 1)
+                if done.get(dep, float("inf")) <= now:
+                    choice = ("B", mb, c)
+            if choice is None and nf[r] < total and (nf[r] - nb[r]) + PARKED_WEIGHT * (nb[r] - nw[r]) + 1 <= cap[r]:
+                mb, c = order_f[nf[r]]
+                vs = c * P + r
+                if vs == 0 or done.get(("F", mb, vs - 1), float("inf")) <= now:
+                    choice = ("F", mb, c)
+            if choice is None and parked[r]:
+                choice = ("W",) + parked[r][0]
+            if choice is None:
+                continue
+            kind, mb, c = choice
+            if kind == "F":
+                nf[r] += 1
+            elif kind == "B":
+                nb[r] += 1
+                parked[r].append((mb, c))
+            else:
+                nw[r] += 1
+                parked[r].pop(0)
+            free[r] = now + 1.0
+            done[(kind, mb, c * P + r)] = free[r]
+            acts[r].append(choice)
+            n_left -= 1
+            progressed = True
+        if n_left and not progressed:  # nobody can start anything at this instant: go to the next completion
+            later = [t for t in free if t > now]
+            if not later:
+                raise RuntimeError(f"zero-bubble list scheduling stalled (P={P}, M={M}, V={V})")
+            now = min(later)
+    return tuple(tuple(a) for a in acts)
+
+
 def _virtual_to_mb_chunk(k: int, P: int, V: int, forward: bool) -> tuple[int, int]:
     """Micro-batch and chunk of the ``k``-th forward (backward) of a rank under the interleaved order."""
     group, r = divmod(k, P * V)
@@ -105,7 +197,7 @@ def min_micro_batches(name: str, pp_size: int, virtual: int = 1) -> int:
     """Micro-batches below which the pipeline cannot fill: ``2 * pp`` for the 1F1B family (the reference's
     ``min_n_mbs``), rounded up to a multiple of ``pp`` for the interleaved order."""
     kind = canonical_schedule(name, virtual)
-    return pp_size if kind == "gpipe" else 2 * pp_size
+    return pp_size if kind == "gpipe" else 2 * pp_size  # zero_bubble included
 
 
 @dataclass
@@ -118,11 +210,15 @@ class SimResult:
 
 
 def simulate(name: str, pp_size: int, n_mbs: int, virtual: int = 1, f_cost: float = 1.0, b_cost: float = 2.0,
-             comm_cost: float = 0.0) -> SimResult:
+             comm_cost: float = 0.0, w_cost: float | None = None) -> SimResult:
     """Replays the schedule of every rank with per-chunk costs ``f_cost / V`` and ``b_cost / V``: an action
-    starts when the rank is free and its input has arrived. Raises if the schedules deadlock."""
+    starts when the rank is free and its input has arrived. In a split-backward schedule ``W`` costs
+    ``w_cost / V`` (default: half of ``b_cost``) and ``B`` the rest. Raises if the schedules deadlock."""
     P, V = pp_size, virtual
     acts = [build_schedule(name, P, n_mbs, r, V) for r in range(P)]
+    split = any(a[0] == "W" for a in acts[0])
+    w_cost = (b_cost / 2 if w_cost is None else w_cost) if split else 0.0
+    costs = {"F": f_cost / V, "B": (b_cost - w_cost) / V, "W": w_cost / V}
     ptr = [0] * P
     free = [0.0] * P
     done: dict[tuple[str, int, int], float] = {}  # (kind, mb, virtual stage) -> finish time
@@ -140,17 +236,19 @@ def simulate(name: str, pp_size: int, n_mbs: int, virtual: int = 1, f_cost: floa
                 vs = c * P + r
                 if kind == "F":
                     dep = None if vs == 0 else ("F", mb, vs - 1)
-                else:
+                elif kind == "B":
                     dep = ("F", mb, vs) if vs == last_vs else ("B", mb, vs + 1)
+                else:
+                    dep = ("B", mb, vs)
                 if dep is not None and dep not in done:
                     break
                 ready = 0.0 if dep is None else done[dep] + (comm_cost if dep[2] != vs else 0.0)
                 start = max(free[r], ready)
-                cost = (f_cost if kind == "F" else b_cost) / V
+                cost = costs[kind]
                 free[r] = start + cost
                 busy[r] += cost
                 done[(kind, mb, vs)] = free[r]
-                live[r] += 1 if kind == "F" else -1
+                live[r] += {"F": 1, "B": -1, "W": 0}[kind]
                 peak[r] = max(peak[r], live[r])
                 order.append((r, (kind, mb, c), start, free[r]))
                 ptr[r] += 1
@@ -258,6 +356,8 @@ class PipelineRunner:
         posted: dict[int, tuple[list, list[torch.Tensor]]] = {}  # action index -> receive in flight
         saved: dict[tuple[int, int], tuple] = {}  # (mb, chunk) -> (stage input, outputs, loss)
         results: dict[int, Any] = {}
+        split = any(a[0] == "W" for a in acts)
+        parked: dict[tuple[int, int], WgradQueue] = {}  # (mb, chunk) -> weight-gradient products of its B action
 
         def post(i: int):
             if i >= len(acts) or i in posted:
@@ -312,13 +412,20 @@ class PipelineRunner:
                     results[mb] = loss.detach() if torch.is_tensor(loss) else loss
                     if not forward_only:
                         saved[(mb, c)] = (stage_in, None, loss)
+            elif kind == "W":
+                parked.pop((mb, c)).run()
             else:
                 stage_in, outs, loss = saved.pop((mb, c))
-                if self._is_last(c):
-                    loss.backward()
-                else:
-                    gx, gr = got[1]
-                    torch.autograd.backward([outs[0], outs[1]], [gx, gr])
+                queue = None
+                if split:
+                    # input gradients now; the linear layers park their weight-gradient GEMMs for the W action
+                    queue = parked[(mb, c)] = WgradQueue()
+                with (queue.collect() if queue is not None else contextlib.nullcontext()):
+                    if self._is_last(c):
+                        loss.backward()
+                    else:
+                        gx, gr = got[1]
+                        torch.autograd.backward([outs[0], outs[1]], [gx, gr])
                 if not self._is_first(c):
                     x_in, r_in = stage_in
                     gx = x_in.grad if x_in.grad is not None else torch.zeros_like(x_in)
@@ -328,5 +435,5 @@ class PipelineRunner:
         note("all actions issued: waiting for sends")
         sends.wait_all()
         note("step done")
-        assert not saved and not posted
+        assert not saved and not posted and not parked
         return results
