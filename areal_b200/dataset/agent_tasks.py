@@ -2,6 +2,8 @@
 
 * ``qa`` (paths containing ``qa``: HotpotQA / NQ / TriviaQA style files): records with ``question`` and
   ``answer`` or ``answers`` become ``{"messages", "answer"}`` with the gold answers as a list.
+* ``code`` (paths containing ``code``: MBPP / APPS style files): records ``{"question" | "prompt", "tests":
+  [{"input", "output"}]}`` become ``{"messages", "tests"}`` for the sandbox reward (``reward/code.py``).
 * ``terminal`` (paths containing ``terminal``): records ``{"instruction", "files", "checks"}`` become
   ``{"messages", "instruction", "files", "checks"}`` for :class:`~areal_b200.workflow.agents.TerminalAgent`.
 
@@ -24,6 +26,22 @@ def qa_rl(path, split="train", tokenizer=None, max_length=None, **kw):
     return out
 
 
+CODE_SUFFIX = ("\nWrite a Python program that reads from standard input and writes the answer to standard output. "
+               "Put the program in one ```python code block.")
+
+
+def code_rl(path, split="train", tokenizer=None, max_length=None, **kw):
+    out = []
+    for r in load_records(path, split):
+        q = r.get("question") or r.get("prompt")
+        if not q or not r.get("tests"):
+            continue
+        if tokenizer is not None and max_length is not None and len(tokenizer.encode(q)) > max_length:
+            continue
+        out.append(dict(messages=[{"role": "user", "content": q + CODE_SUFFIX}], tests=list(r["tests"])))
+    return out
+
+
 def terminal_rl(path, split="train", tokenizer=None, max_length=None, **kw):
     out = []
     for r in load_records(path, split):
@@ -34,4 +52,4 @@ def terminal_rl(path, split="train", tokenizer=None, max_length=None, **kw):
     return out
 
 
-BUILDERS = {("qa", "rl"): qa_rl, ("terminal", "rl"): terminal_rl}
+BUILDERS = {("qa", "rl"): qa_rl, ("terminal", "rl"): terminal_rl, ("code", "rl"): code_rl}

@@ -163,3 +163,69 @@ def test_agent_datasets(tmp_path):
                      json.dumps({"instruction": "no checks"}) + "\n")
     items = get_custom_dataset(path=str(tasks), type="rl")
     assert len(items) == 1 and items[0]["checks"] == ["true"] and items[0]["messages"][0]["content"] == "do"
+
+
+def test_code_reward_runs_the_last_code_block_in_the_sandbox(tmp_path):
+    from areal_b200.reward.code import code_reward_fn, extract_program
+
+    tests = [{"input": "2 3\n", "output": "5"}, {"input": "10 -4\n", "output": "6"}]
+    good = "First idea:\n```python\nprint(1)\n```\nBetter:\n```python\na, b = map(int, input().split())\nprint(a + b)\n```"
+    assert extract_program(good).startswith("a, b")
+    assert code_reward_fn(None, good, None, None, tests=tests) == 1.0
+    half = "```python\nprint(5)\n```"
+    assert code_reward_fn(None, half, None, None, tests=tests) == 0.5
+    assert code_reward_fn(None, half, None, None, tests=tests, all_or_nothing=True) == 0.0
+    assert code_reward_fn(None, "```python\nwhile True: pass\n```", None, None, tests=tests[:1], timeout=0.5) == 0.0
+    assert code_reward_fn(None, "", None, None, tests=tests) == 0.0 and code_reward_fn(None, good, None, None) == 0.0
+    path = tmp_path / "code_tasks.jsonl"
+    path.write_text(json.dumps({"question": "Add two integers.", "tests": tests}) + "\n" + json.dumps({"question": "x"}) + "\n")
+    items = get_custom_dataset(path=str(path), type="rl")
+    assert len(items) == 1 and items[0]["tests"] == tests and "```python" in items[0]["messages"][0]["content"]
+
+
+def test_external_user_lifecycle_against_a_gateway():
+    """The user-side example script drives one episode through an in-process gateway and proxy worker."""
+    import importlib.util
+    import os
+
+    import httpx
+
+    from areal_b200.openai.proxy.online_agent import OnlineAgent
+    from areal_b200.openai.proxy.proxy_gateway import create_gateway_app
+    from areal_b200.openai.proxy.proxy_rollout_server import create_proxy_app
+    from tests.test_openai_proxy import Engine, Tok
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    spec = importlib.util.spec_from_file_location("external_user", os.path.join(root, "examples", "online_proxy",
+                                                                               "external_user.py"))
+    user = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(user)
+    worker = create_proxy_app(Engine(), Tok(), admin_api_key="adm")
+
+    async def forward(method, url, body, headers):
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=worker), base_url="http://w") as c:
+            r = await c.request(method, "/" + url.split("//", 1)[1].split("/", 1)[1], json=body, headers=headers)
+            return r.status_code, r.content, r.headers.get("content-type", "application/json")
+
+    gw = create_gateway_app(admin_api_key="adm", forward=forward)
+
+    async def scenario():
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=gw), base_url="http://gw") as c:
+            async def apost(url, body, headers):
+                r = await c.post(url.replace("http://gw", ""), json=body, headers=headers)
+                r.raise_for_status()
+                return r.json()
+
+            wait = asyncio.create_task(OnlineAgent("http://gw", "w:1", admin_api_key="adm", timeout=30, post=apost).run({}))
+            while (await c.get("/health")).json()["ready_workers"] < 1:
+                await asyncio.sleep(0.01)
+            loop = asyncio.get_running_loop()
+
+            def post(url, body, headers):  # the script is synchronous: hop back onto the loop from its thread
+                return asyncio.run_coroutine_threadsafe(apost(url, body, headers), loop).result(30)
+
+            result = await loop.run_in_executor(None, lambda: user.run_episode("http://gw/", "adm", "hi", "zzz", post, 4))
+            return result, await wait
+
+    result, done = asyncio.run(scenario())
+    assert result["reward"] in (0.0, 1.0) and done["session_id"] == result["session_id"]
