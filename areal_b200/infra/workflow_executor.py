@@ -26,6 +26,8 @@ import threading
 import time
 from typing import Any, Callable
 
+from ..utils.dynamic_import import import_from_string
+
 import torch
 
 from ..api.cli_args import InferenceEngineConfig
@@ -101,8 +103,7 @@ def resolve_workflow(workflow: Any, workflow_kwargs: dict | None, group_size: in
     """Accepts an instance, a class, an import path, or an agent with ``async run``."""
     kwargs = workflow_kwargs or {}
     if isinstance(workflow, str):
-        mod, _, attr = workflow.rpartition(".")
-        workflow = getattr(importlib.import_module(mod), attr)
+        workflow = import_from_string(workflow)
     if isinstance(workflow, type):
         workflow = workflow(**kwargs)
     if not isinstance(workflow, RolloutWorkflow):
@@ -179,8 +180,7 @@ class WorkflowExecutor:
                group_size: int = 1, task_id: int | None = None, is_eval: bool = False) -> int:
         wf = resolve_workflow(workflow, workflow_kwargs, group_size)
         if isinstance(should_accept_fn, str):
-            mod, _, attr = should_accept_fn.rpartition(".")
-            should_accept_fn = getattr(importlib.import_module(mod), attr)
+            should_accept_fn = import_from_string(should_accept_fn)
         tid = task_id if task_id is not None else next(self._ids)
         self.staleness.on_rollout_enqueued()
         try:

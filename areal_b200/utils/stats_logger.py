@@ -1,6 +1,7 @@
 """Rank-0 sink for exported statistics: console table, JSONL file, and TensorBoard /
-Weights & Biases when those packages are importable and enabled
-(areal/utils/stats_logger.py)."""
+Weights & Biases / SwanLab / Trackio when those packages are importable and enabled
+(areal/utils/stats_logger.py). A backend that fails to start is logged and left out; it
+never stops the run."""
 
 from __future__ import annotations
 
@@ -27,6 +28,8 @@ class StatsLogger:
         self._last = time.perf_counter()
         self._tb = None
         self._wandb = None
+        self._swanlab = None
+        self._trackio = None
         self._file = None
         self._start = time.perf_counter()
         if self._is_main():
@@ -64,6 +67,29 @@ class StatsLogger:
                 self._wandb = wandb
             except Exception as e:
                 logger.warning(f"wandb disabled: {e}")
+        sw = self.config.swanlab
+        if (sw.mode or "disabled") != "disabled":
+            try:
+                import swanlab
+
+                if sw.api_key:
+                    swanlab.login(sw.api_key)
+                swanlab.init(project=sw.project or self.config.experiment_name, experiment_name=sw.name or
+                             self.config.trial_name, config=sw.config, logdir=sw.logdir or path, mode=sw.mode)
+                self._swanlab = swanlab
+            except Exception as e:
+                logger.warning(f"swanlab disabled: {e}")
+        tk = self.config.trackio
+        if (tk.mode or "disabled") != "disabled":
+            try:
+                import trackio
+
+                kw = {"space_id": tk.space_id} if tk.space_id else {}
+                trackio.init(project=tk.project or self.config.experiment_name, name=tk.name or
+                             self.config.trial_name, **kw)
+                self._trackio = trackio
+            except Exception as e:
+                logger.warning(f"trackio disabled: {e}")
 
     def state_dict(self):
         return {"last_commit": self._last}
@@ -90,6 +116,10 @@ class StatsLogger:
                     self._tb.add_scalar(k, v, gs)
             if self._wandb:
                 self._wandb.log(item, step=gs)
+            if self._swanlab:
+                self._swanlab.log(item, step=gs)
+            if self._trackio:
+                self._trackio.log(item, step=gs)
 
     @staticmethod
     def _table(d: dict) -> str:
@@ -105,3 +135,7 @@ class StatsLogger:
             self._tb.close()
         if self._wandb:
             self._wandb.finish()
+        if self._swanlab:
+            self._swanlab.finish()
+        if self._trackio:
+            self._trackio.finish()

@@ -39,10 +39,9 @@ class RLVRWorkflow(RolloutWorkflow):
                  tokenizer=None, enable_thinking: bool = False, get_input_ids_fn: Callable | None = None,
                  reward_in_process: bool = False, reward_timeout: float = 15.0):
         if isinstance(reward_fn, str):
-            import importlib
+            from ..utils.dynamic_import import import_from_string
 
-            mod, _, attr = reward_fn.rpartition(".")
-            reward_fn = getattr(importlib.import_module(mod), attr)
+            reward_fn = import_from_string(reward_fn)
         self.reward_fn = reward_fn
         self.gconfig = gconfig.new(n_samples=1)
         self.tokenizer = tokenizer

@@ -1,0 +1,145 @@
+"""Small utilities: parameter estimates, proximal log-prob approximations, address helpers, optional logger
+backends, dynamic imports, token-balanced batch splitting."""
+import dataclasses
+import sys
+import types
+
+import pytest
+import torch
+
+from areal_b200.models.config import PRESETS
+
+
+@pytest.mark.parametrize("preset", ["tiny-qwen2", "tiny-qwen2-4l", "tiny-qwen3-moe", "tiny-qwen2_5-vl"])
+def test_num_params_matches_the_built_model(preset):
+    from areal_b200.models.qwen import build_model
+
+    cfg = PRESETS[preset]
+    model = build_model(cfg, dtype=torch.float32, seed=0)
+    counted = sum(p.numel() for p in model.parameters())
+    assert cfg.num_params() == counted
+    critic = dataclasses.replace(PRESETS["tiny-qwen2"], is_critic=True)
+    assert critic.num_params() == sum(p.numel() for p in build_model(critic, dtype=torch.float32, seed=0).parameters())
+
+
+def test_full_size_presets_have_the_published_sizes():
+    assert abs(PRESETS["qwen3-1.7b"].num_params() / 1e9 - 1.72) < 0.05
+    assert abs(PRESETS["qwen3-8b"].num_params() / 1e9 - 8.19) < 0.1
+    assert abs(PRESETS["qwen2.5-7b"].num_params() / 1e9 - 7.62) < 0.05
+    assert abs(PRESETS["qwen3-30b-a3b"].num_params() / 1e9 - 30.5) < 0.5
+    assert abs(PRESETS["llama3.1-8b"].num_params() / 1e9 - 8.03) < 0.05
+
+
+def test_proximal_logprob_approximations_interpolate_by_version():
+    from areal_b200.utils.functional import compute_prox_logp_approximations
+
+    old = torch.log(torch.tensor([0.5, 0.2, 0.2, 0.2, 0.1]))
+    cur = torch.log(torch.tensor([0.5, 0.4, 0.4, 0.4, 0.3]))
+    versions = torch.tensor([-1, 5, 3, 4, 0])             # prompt token; fresh; 2 back; 1 back; very stale
+    out = compute_prox_logp_approximations(old, cur, versions, current_version=5)
+    alpha = torch.tensor([0.0, 0.0, 0.5, 0.0, 0.8])        # (v_prox - v_b) / (v_theta - v_b) with v_prox = 4
+    assert torch.allclose(out["loglinear"], old + alpha * (cur - old), atol=1e-6)
+    assert torch.allclose(out["linear"].exp(), (1 - alpha) * old.exp() + alpha * cur.exp(), atol=1e-6)
+    assert torch.equal(out["rollout"], old)
+    # both interpolations stay between the behaviour and the current log-prob, the geometric one below the arithmetic
+    lo, hi = torch.minimum(old, cur), torch.maximum(old, cur)
+    for k in ("loglinear", "linear"):
+        assert bool(((out[k] >= lo - 1e-6) & (out[k] <= hi + 1e-6)).all())
+    assert bool((out["loglinear"] <= out["linear"] + 1e-6).all())
+    only = compute_prox_logp_approximations(old, cur, versions, 5, method="linear")
+    assert set(only) == {"linear"}
+    # every token produced by the current weights: the proximal policy is the behaviour policy
+    same = compute_prox_logp_approximations(old, cur, torch.full((5,), 7), 7)
+    assert torch.allclose(same["loglinear"], old)
+
+
+def test_address_helpers_handle_ipv6():
+    from areal_b200.utils.network import find_free_ports, format_addr, format_url, is_ipv6, split_addr
+
+    assert format_addr("10.0.0.1", 80) == "10.0.0.1:80" and format_addr("fe80::1", 80) == "[fe80::1]:80"
+    assert format_addr("[::1]", 8000) == "[::1]:8000"
+    assert split_addr("[fe80::1]:80") == ("fe80::1", 80) and split_addr("host:9") == ("host", 9)
+    assert split_addr("http://[::1]:8000/v1") == ("::1", 8000)
+    assert format_url("::1", 8000, path="/health") == "http://[::1]:8000/health"
+    assert is_ipv6("::1") and is_ipv6("[fe80::1%eth0]") and not is_ipv6("127.0.0.1") and not is_ipv6("host")
+    for bad in ("fe80::1:80", "[::1]", "nohostport"):
+        with pytest.raises(ValueError):
+            split_addr(bad)
+    ports = find_free_ports(3)
+    assert len(set(ports)) == 3 and all(1024 <= p <= 65535 for p in ports)
+
+
+def test_optional_logger_backends_receive_every_commit(tmp_path, monkeypatch):
+    from areal_b200.api.cli_args import StatsLoggerConfig
+    from areal_b200.utils.stats_logger import StatsLogger
+
+    calls = {"swanlab": [], "trackio": []}
+
+    def fake(name):
+        m = types.ModuleType(name)
+        m.init = lambda **kw: calls[name].append(("init", kw))
+        m.log = lambda item, step=None: calls[name].append(("log", step, dict(item)))
+        m.finish = lambda: calls[name].append(("finish",))
+        m.login = lambda key: calls[name].append(("login", key))
+        return m
+
+    monkeypatch.setitem(sys.modules, "swanlab", fake("swanlab"))
+    monkeypatch.setitem(sys.modules, "trackio", fake("trackio"))
+    cfg = StatsLoggerConfig(experiment_name="exp", trial_name="t", fileroot=str(tmp_path))
+    cfg.swanlab.mode, cfg.swanlab.api_key = "local", "k"
+    cfg.trackio.mode, cfg.trackio.space_id = "online", "me/space"
+    lg = StatsLogger(cfg)
+    lg.commit(0, 0, 0, {"loss": 1.5})
+    lg.commit(0, 1, 1, [{"loss": 1.0}, {"loss": 0.5}])
+    lg.close()
+    assert calls["swanlab"][0] == ("login", "k") and calls["swanlab"][1][1]["project"] == "exp"
+    assert calls["trackio"][0][1] == {"project": "exp", "name": "t", "space_id": "me/space"}
+    for name in calls:
+        logs = [c for c in calls[name] if c[0] == "log"]
+        assert [c[1] for c in logs] == [0, 2, 3] and logs[-1][2] == {"loss": 0.5}
+        assert calls[name][-1] == ("finish",)
+    # a backend that cannot start is skipped, the run goes on
+    broken = types.ModuleType("swanlab")
+    broken.init = lambda **kw: (_ for _ in ()).throw(RuntimeError("no server"))
+    monkeypatch.setitem(sys.modules, "swanlab", broken)
+    lg2 = StatsLogger(cfg)
+    lg2.commit(0, 0, 0, {"loss": 1.0})
+    lg2.close()
+
+
+def test_import_from_string_forms(tmp_path):
+    from areal_b200.utils.dynamic_import import import_from_string
+
+    assert import_from_string("areal_b200.reward.gsm8k.gsm8k_reward_fn").__name__ == "gsm8k_reward_fn"
+    assert import_from_string("areal_b200.workflow.rlvr:RLVRWorkflow").__name__ == "RLVRWorkflow"
+    assert import_from_string("os.path:join") is __import__("os").path.join
+    assert import_from_string("areal_b200.utils.network").__name__ == "areal_b200.utils.network"
+    script = tmp_path / "user_code.py"
+    script.write_text("class Agent:\n    tag = 7\n\ndef reward(*a, **k):\n    return 1.0\n")
+    assert import_from_string(f"{script}:Agent.tag") == 7
+    assert import_from_string(f"{script}:reward")() == 1.0
+    assert import_from_string(f"{script}:Agent") is import_from_string(f"{script}:Agent")   # loaded once
+    for bad in ("areal_b200.reward.gsm8k.nope", "no_such_pkg_xyz.f", ""):
+        with pytest.raises((ImportError, ValueError, AttributeError)):
+            import_from_string(bad)
+
+
+def test_batches_are_split_by_tokens_with_groups_kept_together():
+    from areal_b200.infra.dist_rollout import split_batch_by_tokens
+
+    lens = [10, 12, 90, 95, 50, 48, 30, 33]               # 4 groups of 2
+    B, L = len(lens), 100
+    mask = torch.zeros(B, L, dtype=torch.bool)
+    for i, n in enumerate(lens):
+        mask[i, :n] = True
+    batch = {"attention_mask": mask, "input_ids": torch.arange(B)[:, None].expand(B, L).clone(),
+             "rewards": torch.arange(B, dtype=torch.float32), "meta": "kept"}
+    parts = split_batch_by_tokens(batch, 2, group_size=2)
+    assert len(parts) == 2 and all(p["meta"] == "kept" for p in parts)
+    rows = [p["rewards"].long().tolist() for p in parts]
+    assert sorted(sum(rows, [])) == list(range(B)) and all(len(r) == 4 for r in rows)
+    for r in rows:                                         # groups (2k, 2k+1) stay together
+        assert all((i ^ 1) in r for i in r)
+    tokens = [int(p["attention_mask"].sum()) for p in parts]
+    assert sorted(tokens) == [161, 207]                    # 98 + 63 and 185 + 22: the heavy group pairs with the light one
+    assert split_batch_by_tokens(batch, 1)[0] is batch
