@@ -695,6 +695,8 @@ class B200TrainEngine(TrainEngine):
         weights = [float(loss_weight_fn(mb)) for mb in mb_list.mbs]
         acc = torch.zeros(2, dtype=torch.float64)
         for mb, w in zip(mb_list.mbs, weights):
+            if w <= 0:
+                continue  # nothing to score (padding samples of a batch that did not divide over the ranks)
             dev_mb, meta = self._mb_to_device(mb)
             out, ent = self._forward_mb(dev_mb, meta)
             loss = loss_fn(out, dev_mb) if self.is_critic else loss_fn(out, ent, dev_mb)

@@ -50,6 +50,42 @@ def dispatch_batch(batch: dict[str, Any], n_parts: int, group_size: int = 1) -> 
     return parts, rows_all
 
 
+def pad_batch_for_dispatch(batch: dict[str, Any], n_parts: int, group_size: int = 1) -> tuple[dict[str, Any], int]:
+    """Evaluation and inference batches need not divide over the data-parallel ranks (the tail of a validation
+    set, fewer prompts than ranks): appends dummy samples up to the next multiple of ``n_parts`` groups and
+    returns how many rows were added. A dummy sample is a one-token sequence with an all-zero ``loss_mask``, so
+    it carries no loss weight and every per-sample tensor stays aligned with its row."""
+    B = batch["attention_mask"].shape[0]
+    g = max(group_size, 1)
+    assert B % g == 0, f"batch {B} is not a whole number of groups of {g}"
+    n_pad = ((-(B // g)) % n_parts) * g
+    if n_pad == 0:
+        return batch, 0
+    out = {}
+    for k, v in batch.items():
+        if torch.is_tensor(v) and v.dim() >= 1 and v.shape[0] == B:
+            pad = torch.zeros((n_pad,) + tuple(v.shape[1:]), dtype=v.dtype)
+            if k == "attention_mask":
+                pad[:, 0] = 1
+            out[k] = torch.cat([v, pad])
+        elif isinstance(v, list) and len(v) == B:
+            out[k] = list(v) + [None] * n_pad  # per-sample payloads (images): dummies have none
+        else:
+            out[k] = v
+    return out, n_pad
+
+
+def strip_padding(merged: Any, n_real: int, n_pad: int) -> Any:
+    """Drops the rows that :func:`pad_batch_for_dispatch` appended from a merged per-sample result."""
+    if n_pad == 0:
+        return merged
+    if torch.is_tensor(merged) and merged.dim() >= 1 and merged.shape[0] == n_real + n_pad:
+        return merged[:n_real]
+    if isinstance(merged, dict):
+        return {k: strip_padding(v, n_real, n_pad) for k, v in merged.items()}
+    return merged
+
+
 def merge_outputs(outs: list[Any], rows_all: list[list[int]]) -> Any:
     """Inverse of :func:`dispatch_batch` for per-sample tensors; dict stats are averaged."""
     first = outs[0]
@@ -156,8 +192,11 @@ class TrainController:
                 out[k] = v
         return out
 
-    def _data_call(self, method: str, batch: dict[str, Any], *args, **kwargs):
+    def _data_call(self, method: str, batch: dict[str, Any], *args, pad: bool = False, **kwargs):
         dp = self.alloc.parallel.dp_size
+        n_real, n_pad = batch["attention_mask"].shape[0], 0
+        if pad:
+            batch, n_pad = pad_batch_for_dispatch(batch, dp, self.group_size)
         parts, rows = dispatch_batch(batch, dp, self.group_size)
         # every rank of a data-parallel group receives its head's part
         per_rank = len(self.workers) // dp
@@ -166,17 +205,17 @@ class TrainController:
             handles.append((self._ship(w, parts[i // per_rank]),) + args)
         outs = asyncio.run(self._call_all(method, per_worker_args=handles, **kwargs))
         heads = [outs[i * per_rank] for i in range(dp)]
-        return merge_outputs(heads, rows)
+        return strip_padding(merge_outputs(heads, rows), n_real, n_pad)
 
     # ------------------------------------------------------------- engine API
     def train_batch(self, input_: dict[str, Any], loss_fn, loss_weight_fn):
         return self._data_call("train_batch", input_, loss_fn, loss_weight_fn)
 
     def forward_batch(self, input_: dict[str, Any], *args, **kwargs):
-        return self._data_call("forward_batch", input_, *args, **kwargs)
+        return self._data_call("forward_batch", input_, *args, pad=True, **kwargs)
 
     def eval_batch(self, input_: dict[str, Any], loss_fn, loss_weight_fn):
-        return self._data_call("eval_batch", input_, loss_fn, loss_weight_fn)
+        return self._data_call("eval_batch", input_, loss_fn, loss_weight_fn, pad=True)
 
     # algorithm methods of an actor / critic engine created in the workers (``trainer.ppo.actor.PPOActorEngine``)
     def compute_logp(self, input_: dict[str, Any], *args, **kwargs):

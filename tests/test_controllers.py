@@ -4,7 +4,8 @@ import torch
 
 from areal_b200.api.alloc_mode import ModelAllocation, ParallelStrategy
 from areal_b200.api.cli_args import TrainEngineConfig
-from areal_b200.infra.controller.train_controller import TrainController, dispatch_batch, merge_outputs
+from areal_b200.infra.controller.train_controller import (TrainController, dispatch_batch, merge_outputs,
+                                                           pad_batch_for_dispatch, strip_padding)
 from areal_b200.infra.scheduler.local import LocalScheduler
 
 
@@ -29,6 +30,31 @@ def test_dispatch_is_balanced_and_group_atomic_and_merge_inverts():
     assert torch.equal(merged, b["input_ids"].float() * 2)
     st = merge_outputs([{"loss": 1.0, "n": 2.0}, {"loss": 3.0, "n": 4.0}], rows)
     assert st == {"loss": 2.0, "n": 3.0}
+
+
+@pytest.mark.parametrize("n,dp,g,expect_pad", [(8, 4, 1, 0), (7, 4, 1, 1), (2, 4, 1, 2), (6, 4, 2, 2), (6, 3, 2, 0),
+                                               (2, 3, 2, 4)])
+def test_eval_batches_are_padded_with_weightless_samples(n, dp, g, expect_pad):
+    b = _batch([5 + i for i in range(n)])
+    b["loss_mask"] = b["attention_mask"].clone().int()
+    b["images"] = [f"img{i}" for i in range(n)]
+    b["meta"] = "shared"
+    padded, n_pad = pad_batch_for_dispatch(b, dp, g)
+    assert n_pad == expect_pad and padded["attention_mask"].shape[0] == n + n_pad
+    if n_pad == 0:
+        assert padded is b
+        return
+    assert torch.equal(padded["input_ids"][:n], b["input_ids"]) and padded["meta"] == "shared"
+    assert padded["images"] == b["images"] + [None] * n_pad
+    assert padded["attention_mask"][n:].sum(-1).tolist() == [1] * n_pad      # one-token sequences
+    assert int(padded["loss_mask"][n:].sum()) == 0                            # no loss weight
+    parts, rows = dispatch_batch(padded, dp, g)                               # now it divides
+    assert len(parts) == dp
+    merged = merge_outputs([p["input_ids"].float() for p in parts], rows)
+    assert torch.equal(strip_padding(merged, n, n_pad), b["input_ids"].float())
+    assert strip_padding({"x": merged, "s": 1.0}, n, n_pad)["x"].shape[0] == n
+    with pytest.raises(AssertionError):
+        dispatch_batch(b, dp, g)                                              # the unpadded batch does not
 
 
 class _FakeAlloc:
