@@ -187,3 +187,143 @@ def create_gateway_app(token: str | None = None, strategy: str = "round_robin", 
 
     app.state.registry, app.state.sessions, app.state.flags = reg, store, state
     return app
+
+
+class GatewayInferenceEngine:
+    """The trainer's handle on an inference service: the ``InferenceEngine`` calls that workflows and trainers
+    make (``agenerate``, ``submit`` / ``wait`` / ``prepare_batch`` / ``rollout_batch`` through a local
+    :class:`~areal_b200.infra.workflow_executor.WorkflowExecutor`, pause / continue, version) carried out over
+    the gateway's routes, plus the session calls (``start_session`` / ``finish_session``) for multi-turn
+    episodes that should stay on the engine holding their prefix. ``apost(url, body, headers) -> dict`` is the
+    transport (default: aiohttp on the caller's loop).
+    Reference: areal/experimental/inference_service/controller/controller.py (GatewayInferenceController)."""
+
+    supports_images = False
+
+    def __init__(self, config, gateway_url: str, token: str | None = None, apost=None):
+        self.config, self.url, self.token = config, gateway_url.rstrip("/"), token
+        self._apost = apost
+        self._version = 0
+        self._executor = None
+
+    # ---------------------------------------------------------------- transport
+    def _headers(self) -> dict[str, str]:
+        return {"Authorization": f"Bearer {self.token}"} if self.token else {}
+
+    async def _post(self, path: str, body: dict) -> dict:
+        if self._apost is not None:
+            return await self._apost(self.url + path, body, self._headers())
+        from ..infra.utils.http import arequest_with_retry
+        from ..infra.workflow_context import get_aiohttp_session
+
+        session = await get_aiohttp_session()
+        return await arequest_with_retry(session, "POST", self.url + path, json=body, headers=self._headers(),
+                                         timeout=getattr(self.config, "request_timeout", 3600),
+                                         max_retries=getattr(self.config, "request_retries", 3))
+
+    def _post_sync(self, path: str, body: dict) -> dict:
+        try:
+            asyncio.get_running_loop()
+        except RuntimeError:
+            return asyncio.run(self._post_and_close(path, body))
+        # called from a thread that runs a loop (a workflow): hop to a private loop in a helper thread
+        box: dict[str, Any] = {}
+
+        def run():
+            try:
+                box["v"] = asyncio.run(self._post_and_close(path, body))
+            except BaseException as e:  # noqa: BLE001 - re-raised in the caller
+                box["e"] = e
+
+        t = threading.Thread(target=run, daemon=True)
+        t.start()
+        t.join()
+        if "e" in box:
+            raise box["e"]
+        return box["v"]
+
+    async def _post_and_close(self, path: str, body: dict) -> dict:
+        try:
+            return await self._post(path, body)
+        finally:
+            if self._apost is None:
+                from ..infra.workflow_context import close_clients
+
+                await close_clients()
+
+    # ---------------------------------------------------------------- lifecycle
+    def initialize(self, train_data_parallel_size: int | None = None, **_):
+        from ..infra.workflow_executor import WorkflowExecutor
+
+        self._executor = WorkflowExecutor(self.config, self).initialize(train_data_parallel_size)
+        return self
+
+    def destroy(self):
+        if self._executor is not None:
+            self._executor.destroy()
+            self._executor = None
+
+    # ---------------------------------------------------------------- generation
+    async def agenerate(self, req, session_id: str | None = None):
+        body = {"request": serialize_value(req)}
+        sid = session_id or (getattr(req, "metadata", None) or {}).get("session_id")
+        if sid:
+            body["session_id"] = sid
+        out = await self._post("/generate", body)
+        return deserialize_value(out["response"])
+
+    def generate(self, req, session_id: str | None = None):
+        body = {"request": serialize_value(req)}
+        if session_id:
+            body["session_id"] = session_id
+        return deserialize_value(self._post_sync("/generate", body)["response"])
+
+    async def start_session(self, session_id: str | None = None) -> str:
+        return (await self._post("/sessions/start", {"session_id": session_id} if session_id else {}))["session_id"]
+
+    async def finish_session(self, session_id: str, reward: float | None = None) -> dict[str, Any]:
+        """Ends the session; returns its trajectory (token ids, log-probs, loss mask, versions, reward)."""
+        return (await self._post(f"/sessions/{session_id}/finish", {"reward": reward}))["trajectory"]
+
+    # ---------------------------------------------------------------- control
+    def pause_generation(self):
+        self._post_sync("/pause", {})
+
+    def continue_generation(self):
+        self._post_sync("/continue", {})
+
+    def set_version(self, version: int):
+        self._version = int(version)
+        self._post_sync("/set_version", {"version": int(version)})
+
+    def get_version(self) -> int:
+        return self._version
+
+    # ---------------------------------------------------------------- workflow API
+    def submit(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1, task_id=None,
+               is_eval=False, **_) -> int:
+        return self._executor.submit(data, workflow, workflow_kwargs, should_accept_fn, group_size, task_id=task_id,
+                                     is_eval=is_eval)
+
+    def wait(self, count: int, timeout: float | None = None, raise_timeout: bool = True):
+        return self._executor.wait(count, timeout, raise_timeout)
+
+    def wait_for_task(self, task_id: int, timeout: float | None = None, raise_timeout: bool = True):
+        return self._executor.wait_for_task(task_id, timeout, raise_timeout)
+
+    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1):
+        return self._executor.rollout_batch(data, workflow, workflow_kwargs, should_accept_fn, group_size)
+
+    def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1,
+                      dynamic_bs=False):
+        return self._executor.prepare_batch(dataloader, workflow, workflow_kwargs, should_accept_fn, group_size,
+                                            dynamic_bs)
+
+    def pause(self):
+        self._executor.pause()
+
+    def resume(self):
+        self._executor.resume()
+
+    def export_stats(self) -> dict[str, float]:
+        return self._executor.export_stats() if self._executor is not None else {}

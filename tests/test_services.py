@@ -210,3 +210,72 @@ def test_weight_update_service_round_and_metadata():
         assert i("pause_generation") < i("update_weights_from_disk") < i("set_version") < i("continue_generation")
     assert gw.get("/status").json()["version"] == 1
     assert weight_update_service.pair_ranks(2, 5) == {0: [0, 2, 4], 1: [1, 3]}
+
+
+def test_gateway_inference_engine_runs_workflows_through_the_service():
+    """The trainer-side engine object: a workflow's ``agenerate`` calls travel through the gateway to the engine
+    workers; sessions keep their engine; pause / continue / version reach every worker."""
+    import asyncio
+
+    import httpx
+
+    from areal_b200.api.cli_args import InferenceEngineConfig
+    from areal_b200.api.workflow_api import RolloutWorkflow
+
+    net = Net()
+    engines = [EchoEngineApp("e0"), EchoEngineApp("e1")]
+    for i, e in enumerate(engines):
+        net.add(f"e{i}:1", e.app)
+    app = inference_service.create_gateway_app(token="tok", post=net.post)
+
+    async def apost(url, body, headers):
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://gw") as c:
+            r = await c.post(url.replace("http://gw", ""), json=body, headers=headers)
+            if r.status_code >= 400:
+                raise RuntimeError(f"{r.status_code}: {r.text}")
+            return r.json()
+
+    asyncio.run(apost("http://gw/register", {"worker_id": "e0", "addr": "e0:1"}, {"Authorization": "Bearer tok"}))
+    asyncio.run(apost("http://gw/register", {"worker_id": "e1", "addr": "e1:1"}, {"Authorization": "Bearer tok"}))
+    cfg = InferenceEngineConfig(experiment_name="x", trial_name="y", max_concurrent_rollouts=8, consumer_batch_size=4,
+                                max_head_offpolicyness=4)
+    eng = inference_service.GatewayInferenceEngine(cfg, "http://gw", token="tok", apost=apost).initialize()
+    try:
+        bad = inference_service.GatewayInferenceEngine(cfg, "http://gw", token="wrong", apost=apost)
+        with pytest.raises(RuntimeError, match="401"):
+            bad.generate(ModelRequest(input_ids=[1], gconfig=GenerationHyperparameters(max_new_tokens=1)))
+
+        class TwoTurns(RolloutWorkflow):
+            async def arun_episode(self, engine, data):
+                sid = await engine.start_session()
+                g = GenerationHyperparameters(max_new_tokens=2)
+                r1 = await engine.agenerate(ModelRequest(input_ids=data["ids"], gconfig=g), session_id=sid)
+                ids2 = data["ids"] + r1.output_tokens + [99]
+                await engine.agenerate(ModelRequest(input_ids=ids2, gconfig=g), session_id=sid)
+                traj = await engine.finish_session(sid, reward=float(len(data["ids"])))
+                n = len(traj["input_ids"])
+                return dict(input_ids=torch.tensor(traj["input_ids"]).unsqueeze(0),
+                            attention_mask=torch.ones(1, n, dtype=torch.bool),
+                            loss_mask=torch.tensor(traj["loss_mask"]).unsqueeze(0),
+                            logprobs=torch.tensor(traj["logprobs"]).unsqueeze(0),
+                            versions=torch.tensor(traj["versions"]).unsqueeze(0),
+                            rewards=torch.tensor([traj["reward"]]))
+
+        batch = eng.rollout_batch([{"ids": [5, 6, 7]}, {"ids": [1, 2]}, {"ids": [3]}, {"ids": [4, 4, 4, 4]}],
+                                  workflow=TwoTurns())
+        assert batch["input_ids"].shape[0] == 4 and sorted(batch["rewards"].tolist()) == [1.0, 2.0, 3.0, 4.0]
+        row = batch["rewards"].tolist().index(3.0)
+        n = int(batch["attention_mask"][row].sum())
+        assert batch["loss_mask"][row, :n].tolist() == [0, 0, 0, 1, 1, 0, 1, 1]
+        # 8 generate calls, two per session, each session on one engine; round robin used both engines
+        assert sum(e.calls.count("generate") for e in engines) == 8
+        assert all(e.calls.count("generate") % 2 == 0 and e.calls.count("generate") > 0 for e in engines)
+        eng.set_version(3)
+        assert eng.get_version() == 3 and all(e.version == 3 for e in engines)
+        eng.pause_generation()
+        assert app.state.flags["paused"]
+        eng.continue_generation()
+        assert not app.state.flags["paused"]
+        assert all("pause_generation" in e.calls and "continue_generation" in e.calls for e in engines)
+    finally:
+        eng.destroy()
