@@ -206,16 +206,18 @@ class ModelConfig:
             rope_scaling=scaling,
             max_position_embeddings=cfg.get("max_position_embeddings", 32768),
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
-            attention_bias=cfg.get("attention_bias", mt in ("qwen2", "qwen2_5_vl", "qwen2_vl")),
+            attention_bias=cfg.get("attention_bias", mt in ("qwen2", "qwen2_moe", "qwen2_5_vl", "qwen2_vl")),
             qk_norm=mt.startswith("qwen3"),
-            num_experts=cfg.get("num_experts", 0) or 0,
+            num_experts=cfg.get("num_experts", 0) or cfg.get("num_local_experts", 0) or 0,
             num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=cfg.get("moe_intermediate_size", 0) or 0,
-            norm_topk_prob=cfg.get("norm_topk_prob", True),
+            norm_topk_prob=cfg.get("norm_topk_prob", mt != "qwen2_moe"),
             shared_expert_intermediate_size=cfg.get("shared_expert_intermediate_size", 0) or 0,
             decoder_sparse_step=cfg.get("decoder_sparse_step", 1) or 1,
             mlp_only_layers=list(cfg.get("mlp_only_layers", []) or []),
         )
+        if mt == "mixtral":  # every MLP is a mixture whose experts have the dense MLP's width
+            out.moe_intermediate_size = out.intermediate_size
         if mt == "qwen3_5":
             out.layer_types = list(cfg.get("layer_types") or [])
             out.partial_rotary_factor = (cfg.get("partial_rotary_factor")
@@ -250,7 +252,8 @@ class ModelConfig:
             return self._to_hf_config_vl()
         arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                 "qwen3_moe": "Qwen3MoeForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
-                "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM"}[self.model_type]
+                "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
+                "qwen2_moe": "Qwen2MoeForCausalLM", "mixtral": "MixtralForCausalLM"}[self.model_type]
         if self.model_type == "qwen3_5" and self.is_moe:
             arch = "Qwen3_5MoeForCausalLM"
         d = {
@@ -266,8 +269,10 @@ class ModelConfig:
             "attention_bias": self.attention_bias, "hidden_act": "silu",
             "torch_dtype": "bfloat16",
         }
-        if self.model_type in ("llama", "mistral"):
+        if self.model_type in ("llama", "mistral", "mixtral"):
             d.update(mlp_bias=False, sliding_window=None)
+        if self.model_type == "qwen2_moe":
+            d.update(use_sliding_window=False, qkv_bias=self.attention_bias)
         if self.rope_scaling:
             d["rope_scaling"] = dict(self.rope_scaling)
             d["rope_parameters"] = dict(self.rope_scaling, rope_theta=self.rope_theta)
@@ -289,6 +294,9 @@ class ModelConfig:
                      shared_expert_intermediate_size=self.shared_expert_intermediate_size,
                      decoder_sparse_step=self.decoder_sparse_step,
                      mlp_only_layers=self.mlp_only_layers)
+        if self.model_type == "mixtral":
+            d.update(num_local_experts=self.num_experts, intermediate_size=self.moe_intermediate_size,
+                     router_jitter_noise=0.0)
         return d
 
     def _to_hf_config_vl(self) -> dict:
@@ -335,7 +343,7 @@ _VISION_KEYS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_ch
                 "fullatt_block_indexes", "hidden_act", "variant", "num_position_embeddings",
                 "deepstack_visual_indexes")
 _VL_TYPES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe")
-_TEXT_TYPES = {"qwen2", "qwen3", "qwen3_moe", "qwen3_5", "llama", "mistral"}
+_TEXT_TYPES = {"qwen2", "qwen3", "qwen3_moe", "qwen3_5", "llama", "mistral", "qwen2_moe", "mixtral"}
 
 # Named shapes used by the benchmark configurations (random-init, synthetic data).
 PRESETS: dict[str, ModelConfig] = {
@@ -419,6 +427,11 @@ PRESETS: dict[str, ModelConfig] = {
                                tie_word_embeddings=False, qk_norm=False,
                                rope_scaling={"rope_type": "llama3", "factor": 8.0, "low_freq_factor": 1.0,
                                              "high_freq_factor": 4.0, "original_max_position_embeddings": 8192}),
+    "mixtral-8x7b": ModelConfig(model_type="mixtral", vocab_size=32000, hidden_size=4096, intermediate_size=14336,
+                                num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+                                rms_norm_eps=1e-5, rope_theta=1e6, max_position_embeddings=32768,
+                                tie_word_embeddings=False, qk_norm=False, num_experts=8, num_experts_per_tok=2,
+                                moe_intermediate_size=14336),
     "mistral-7b": ModelConfig(model_type="mistral", vocab_size=32768, hidden_size=4096, intermediate_size=14336,
                               num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                               rms_norm_eps=1e-5, rope_theta=1e6, max_position_embeddings=32768,

@@ -630,11 +630,39 @@ class QwenModel(nn.Module):
         for name, t in self.to_hf_local(export=True):
             d = self._tp_dim(name)
             if d is None:
-                yield name, t
+                yield self.checkpoint_name(name), t
             else:
                 parts = [torch.empty_like(t) for _ in range(self.pctx.tp_size)]
                 dist.all_gather(parts, t.contiguous(), group=self.pctx.tp_group)
-                yield name, torch.cat(parts, d)
+                yield self.checkpoint_name(name), torch.cat(parts, d)
+
+    # Families whose checkpoint files name the same tensors differently (Mixtral: ``block_sparse_moe`` with
+    # experts ``w1`` / ``w3`` / ``w2``). Inside the package every tensor goes by the canonical (Qwen-style)
+    # name; the translation happens where tensors enter (``load_hf``) or leave (``to_hf``).
+    _MIXTRAL_PROJ = {"gate_proj": "w1", "up_proj": "w3", "down_proj": "w2"}
+
+    def checkpoint_name(self, name: str) -> str:
+        if self.cfg.model_type != "mixtral" or ".mlp." not in name:
+            return name
+        head, _, tail = name.partition(".mlp.")
+        if tail == "gate.weight":
+            return head + ".block_sparse_moe.gate.weight"
+        m = re.match(r"experts\.(\d+)\.(gate_proj|up_proj|down_proj)\.weight$", tail)
+        if m is not None:
+            return f"{head}.block_sparse_moe.experts.{m.group(1)}.{self._MIXTRAL_PROJ[m.group(2)]}.weight"
+        return name
+
+    def canonical_name(self, name: str) -> str:
+        if self.cfg.model_type != "mixtral" or ".block_sparse_moe." not in name:
+            return name
+        head, _, tail = name.partition(".block_sparse_moe.")
+        if tail == "gate.weight":
+            return head + ".mlp.gate.weight"
+        m = re.match(r"experts\.(\d+)\.(w1|w2|w3)\.weight$", tail)
+        if m is not None:
+            proj = {v: k for k, v in self._MIXTRAL_PROJ.items()}[m.group(2)]
+            return f"{head}.mlp.experts.{m.group(1)}.{proj}.weight"
+        return name
 
     def to_hf_local(self, export: bool = False) -> Iterator[tuple[str, torch.Tensor]]:
         """``(hf_name, view)`` of this rank's (tp-local) parameters. Families whose checkpoints store
@@ -761,6 +789,7 @@ class QwenModel(nn.Module):
         for name, t in tensors:
             if name.startswith("model.language_model."):  # decoder of a composite checkpoint
                 name = "model." + name[len("model.language_model."):]
+            name = self.canonical_name(name)
             if self.cfg.norm_one_plus and name.endswith(self._ONE_PLUS):
                 t = t.float() + 1.0
             if name == "lm_head.weight" and self.lm_head is None and self.score is None:

@@ -152,3 +152,33 @@ def test_unknown_model_type_and_scaling_are_rejected():
         ModelConfig.from_hf_config(dict(base, model_type="gpt2"))
     with pytest.raises(NotImplementedError):
         ModelConfig.from_hf_config(dict(base, rope_scaling={"rope_type": "longrope", "factor": 2.0}))
+
+
+def test_qwen2_moe_matches_transformers(tmp_path):
+    """Shared expert behind a sigmoid gate, top-k probabilities not renormalised, bias on q/k/v."""
+    cfg = dataclasses.replace(PRESETS["tiny-qwen3-moe"], model_type="qwen2_moe", qk_norm=False, attention_bias=True,
+                              norm_topk_prob=False, shared_expert_intermediate_size=96)
+    hf = _roundtrip(cfg, tmp_path)
+    assert type(hf).__name__ == "Qwen2MoeForCausalLM"
+    back = ModelConfig.from_hf_config(str(tmp_path))
+    assert (back.shared_expert_intermediate_size, back.norm_topk_prob, back.attention_bias) == (96, False, True)
+
+
+def test_mixtral_matches_transformers_and_uses_its_checkpoint_names(tmp_path):
+    cfg = dataclasses.replace(PRESETS["tiny-qwen3-moe"], model_type="mixtral", qk_norm=False, attention_bias=False,
+                              norm_topk_prob=True, intermediate_size=128, moe_intermediate_size=128)
+    hf = _roundtrip(cfg, tmp_path)
+    assert type(hf).__name__ == "MixtralForCausalLM"
+    from safetensors import safe_open
+
+    import glob as _glob
+
+    names = set()
+    for f in _glob.glob(str(tmp_path / "*.safetensors")):
+        with safe_open(f, "pt") as sf:
+            names |= set(sf.keys())
+    assert "model.layers.0.block_sparse_moe.gate.weight" in names
+    assert "model.layers.1.block_sparse_moe.experts.7.w3.weight" in names
+    assert not any(".mlp." in n for n in names)
+    back = ModelConfig.from_hf_config(str(tmp_path))
+    assert back.num_experts == 8 and back.moe_intermediate_size == 128 and back.is_moe
