@@ -238,6 +238,27 @@ class _DecodeGraphs:
         return self.h_tok[:n].numpy(), self.h_lp[:n].numpy()
 
 
+def stop_string_cut(tokens: list[int], tokenizer, stops: list[str], skip_special_tokens: bool = True) -> int | None:
+    """Number of leading tokens to keep so that the decoded text ends with the first completed stop string
+    (``None``: no stop string occurs). Stop strings are matched on text, and a string can end inside a token or
+    span several, so the cut is the shortest prefix whose decoding contains one: found by bisection, as
+    containment is monotone in the prefix length. The engine applies it after generation (tokens past the cut
+    were computed and are dropped); stop *token ids* end generation inside the scheduler at no such cost."""
+    if not tokens or not stops:
+        return None
+    has = lambda n: any(s in tokenizer.decode(tokens[:n], skip_special_tokens=skip_special_tokens) for s in stops if s)
+    if not has(len(tokens)):
+        return None
+    lo, hi = 1, len(tokens)
+    while lo < hi:
+        mid = (lo + hi) // 2
+        if has(mid):
+            hi = mid
+        else:
+            lo = mid + 1
+    return lo
+
+
 class NativeRolloutEngine(InferenceEngine):
     def __init__(self, config: InferenceEngineConfig):
         self.config = config
@@ -671,6 +692,10 @@ class NativeRolloutEngine(InferenceEngine):
         g = req.gconfig
         if g.n_samples != 1:
             raise ValueError("agenerate produces one sample; use n_samples=1 and group at the workflow level")
+        if g.frequency_penalty or g.use_beam_search:
+            raise NotImplementedError("the native rollout engine samples without frequency penalty or beam search")
+        if g.stop and (req.tokenizer or getattr(self, "tokenizer", None)) is None:
+            raise ValueError("stop strings need a tokenizer (ModelRequest.tokenizer or the engine's)")
         max_new = min(g.max_new_tokens, max(g.max_tokens - len(req.input_ids), 0))
         images = self._image_inputs(req)
         t0 = time.perf_counter()
@@ -698,6 +723,12 @@ class NativeRolloutEngine(InferenceEngine):
                 break
         if stop_reason == "abort":
             stop_reason = "length"
+        if g.stop:
+            keep = stop_string_cut(out_tokens, req.tokenizer or getattr(self, "tokenizer", None), g.stop,
+                                   bool(getattr(g, "skip_special_tokens", True)))
+            if keep is not None:
+                out_tokens, out_logprobs, out_versions = out_tokens[:keep], out_logprobs[:keep], out_versions[:keep]
+                stop_reason = "stop"
         return ModelResponse(input_tokens=list(req.input_ids), output_tokens=out_tokens,
                              output_logprobs=out_logprobs, output_versions=out_versions,
                              stop_reason=stop_reason, tokenizer=req.tokenizer,

@@ -312,3 +312,50 @@ def test_engine_outputs_do_not_change_when_resubmitted_groups_share_their_prefix
     assert st_on["dedup_pages"] == 4 and st_off["dedup_pages"] == 0
     for (ta, la), (tb, lb) in zip(shared, plain):
         assert ta == tb and max(abs(x - y) for x, y in zip(la, lb)) < 1e-4
+
+
+def test_native_engine_stop_strings_and_unsupported_sampling_options():
+    """Stop strings cut the output at the first token that completes one (matched on decoded text, so a string
+    may span tokens); options the engine does not implement are refused, not ignored."""
+    import asyncio
+
+    from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig, NativeRolloutConfig
+    from areal_b200.api.io_struct import ModelRequest
+    from areal_b200.engine.rollout_engine import NativeRolloutEngine, stop_string_cut
+
+    class Tok:  # token i decodes to one letter; "cd" spans two tokens
+        def decode(self, ids, skip_special_tokens=True):
+            return "".join("abcdefghij"[i % 10] for i in ids)
+
+    assert stop_string_cut([0, 1, 2, 3, 4], Tok(), ["cd"]) == 4
+    assert stop_string_cut([0, 1, 2, 3, 4], Tok(), ["zz", "e"]) == 5
+    assert stop_string_cut([0, 1, 2], Tok(), ["cd"]) is None and stop_string_cut([], Tok(), ["a"]) is None
+    assert stop_string_cut([2, 3, 2, 3], Tok(), ["cd"]) == 2          # the first occurrence wins
+
+    cfg = InferenceEngineConfig(experiment_name="e", trial_name="t", backend="native:d1", max_concurrent_rollouts=8,
+                                consumer_batch_size=4,
+                                native=NativeRolloutConfig(model_preset="tiny-qwen2", context_length=128, max_num_seqs=8,
+                                                           max_num_batched_tokens=512, num_kv_blocks=64, seed=0,
+                                                           cuda_graph=False))
+    eng = NativeRolloutEngine(cfg).initialize(device="cpu")
+    try:
+        prompt = list(range(20, 40))
+        base = GenerationHyperparameters(max_new_tokens=12, greedy=True, temperature=0.0, ignore_eos=True)
+        full = asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base, tokenizer=Tok())))
+        assert len(full.output_tokens) == 12 and full.stop_reason == "length"
+        text = Tok().decode(full.output_tokens)
+        stop = text[4:6]                                              # a two-letter string inside the output
+        first = text.index(stop) + 2
+        cut = asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(stop=[stop]), tokenizer=Tok())))
+        assert cut.stop_reason == "stop" and cut.output_tokens == full.output_tokens[:first]
+        assert len(cut.output_logprobs) == len(cut.output_versions) == first
+        same = asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(stop=["#nothing#"]), tokenizer=Tok())))
+        assert same.output_tokens == full.output_tokens and same.stop_reason == "length"
+        with pytest.raises(ValueError, match="tokenizer"):
+            asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(stop=["x"]))))
+        with pytest.raises(NotImplementedError):
+            asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(frequency_penalty=0.5))))
+        with pytest.raises(NotImplementedError):
+            asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(use_beam_search=True))))
+    finally:
+        eng.destroy()
