@@ -174,7 +174,7 @@ class InferenceEngine(abc.ABC):
         raise NotImplementedError
 
     def rollout_batch(self, data: list[dict[str, Any]], workflow=None, workflow_kwargs=None,
-                      should_accept_fn=None, group_size: int = 1):
+                      should_accept_fn=None, group_size: int = 1, is_eval: bool = False):
         raise NotImplementedError
 
     def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None,

@@ -830,8 +830,10 @@ class NativeRolloutEngine(InferenceEngine):
     def poll_task(self, task_id: int):
         return self._executor.poll_task(task_id)
 
-    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1):
-        return self._executor.rollout_batch(data, workflow, workflow_kwargs, should_accept_fn, group_size)
+    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1,
+                      is_eval=False):
+        return self._executor.rollout_batch(data, workflow, workflow_kwargs, should_accept_fn, group_size,
+                                            is_eval=is_eval)
 
     def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None,
                       group_size=1, dynamic_bs=False):

@@ -99,8 +99,39 @@ class RolloutServer:
         self.topo, self.engine = topo, engine
         self.trainers = topo.trainers_of(topo.rank)
         self._stop = threading.Event()
+        self._eval: tuple | None = None  # (items of this rank, workflow, workflow kwargs)
         self._ctl_thread = threading.Thread(target=self._control_loop, name="rollout-ctl", daemon=True)
         self._ctl_thread.start()
+
+    def set_eval(self, items: list, workflow, workflow_kwargs=None):
+        """What an ``("eval",)`` command runs: this rank's share of the validation set through ``workflow``."""
+        self._eval = (list(items), workflow, workflow_kwargs)
+
+    def _run_eval(self) -> tuple[float, int]:
+        """Sum of rewards and number of scored samples. The episodes run on a private event loop of the control
+        thread, straight against the engine (not through the workflow executor, whose result queue belongs to
+        the training loop on the main thread); generation for training goes on meanwhile."""
+        if self._eval is None or not self._eval[0]:
+            return 0.0, 0
+        import asyncio
+
+        from .workflow_executor import resolve_workflow
+
+        items, workflow, kwargs = self._eval
+        wf = resolve_workflow(workflow, kwargs)
+
+        async def run_all():
+            return await asyncio.gather(*[wf.arun_episode(self.engine, dict(it)) for it in items],
+                                        return_exceptions=True)
+
+        total, n = 0.0, 0
+        for out in asyncio.run(run_all()):
+            if out is None or isinstance(out, BaseException):
+                continue
+            for traj in (out if isinstance(out, list) else [out]):
+                r = traj["rewards"].float()
+                total, n = total + float(r.sum()), n + int(r.numel())
+        return total, n
 
     def _control_loop(self):
         lead = self.trainers[0]
@@ -125,6 +156,8 @@ class RolloutServer:
                 if cmd[1] is not None:
                     self.engine.set_version(cmd[1])
                 self.engine.continue_generation()
+            elif cmd[0] == "eval":
+                dist.send_object_list([("eval_result",) + self._run_eval()], dst=lead, group=self.topo.ctl_group)
             elif cmd[0] == "stop":
                 self._stop.set()
                 return
@@ -250,6 +283,22 @@ class RemoteRolloutClient(InferenceEngine):
         torch.cuda.current_stream().synchronize()
         if version is not None:
             self._version = version
+
+    def evaluate(self) -> tuple[float, int]:
+        """Asks the led rollout ranks to run their share of the validation set; returns the sum of rewards and
+        the sample count over all rollout ranks (reduced over the trainer ranks when they share a group)."""
+        for g in self.led:
+            dist.send_object_list([("eval",)], dst=g, group=self.topo.ctl_group)
+        total, n = 0.0, 0
+        for g in self.led:
+            msg = [None]
+            dist.recv_object_list(msg, src=g, group=self.topo.ctl_group)
+            total, n = total + float(msg[0][1]), n + int(msg[0][2])
+        if self.train_cpu_group is not None:
+            acc = torch.tensor([total, float(n)], dtype=torch.float64)
+            dist.all_reduce(acc, group=self.train_cpu_group)
+            total, n = float(acc[0]), int(acc[1])
+        return total, n
 
     def set_version(self, version: int):
         self._version = version

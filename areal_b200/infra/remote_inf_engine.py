@@ -359,8 +359,10 @@ class RemoteInfEngine(InferenceEngine):
     def wait_for_task(self, task_id: int, timeout: float | None = None, raise_timeout: bool = True):
         return self._executor.wait_for_task(task_id, timeout, raise_timeout)
 
-    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1):
-        return self._executor.rollout_batch(data, workflow, workflow_kwargs, should_accept_fn, group_size)
+    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1,
+                      is_eval=False):
+        return self._executor.rollout_batch(data, workflow, workflow_kwargs, should_accept_fn, group_size,
+                                            is_eval=is_eval)
 
     def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None,
                       group_size=1, dynamic_bs=False):

@@ -138,6 +138,8 @@ class WorkflowExecutor:
         self._n_failed = 0
         self._consecutive_failures = 0  # episodes that raised since the last one that did not
         self._last_error = None
+        self._eval_runner: AsyncTaskRunner | None = None  # evaluation episodes: no staleness gate, own queue
+        self._eval_tasks: set[int] = set()
 
     def initialize(self, train_data_parallel_size: int | None = None):
         cfg = self.config
@@ -155,6 +157,9 @@ class WorkflowExecutor:
         if self.runner is not None:
             self.runner.destroy()
             self.runner = None
+        if self._eval_runner is not None:
+            self._eval_runner.destroy()
+            self._eval_runner = None
 
     # staleness gate: consulted by the runner thread before each task start
     def _admit(self) -> bool:
@@ -182,6 +187,16 @@ class WorkflowExecutor:
         if isinstance(should_accept_fn, str):
             should_accept_fn = import_from_string(should_accept_fn)
         tid = task_id if task_id is not None else next(self._ids)
+        if is_eval:
+            # evaluation samples are not training data: they do not count against the staleness budget and must
+            # not queue behind training episodes that wait for capacity, so they run on a runner of their own
+            if self._eval_runner is None:
+                self._eval_runner = AsyncTaskRunner(max_queue_size=self.runner.max_queue_size)
+                self._eval_runner.initialize()
+            with self._lock:
+                self._eval_tasks.add(tid)
+            self._eval_runner.submit(self._episode, wf, data, should_accept_fn, True, task_id=tid)
+            return tid
         self.staleness.on_rollout_enqueued()
         try:
             self.runner.submit(self._episode, wf, data, should_accept_fn, task_id=tid)
@@ -191,7 +206,7 @@ class WorkflowExecutor:
             raise
         return tid
 
-    async def _episode(self, wf: RolloutWorkflow, data, should_accept_fn):
+    async def _episode(self, wf: RolloutWorkflow, data, should_accept_fn, is_eval: bool = False):
         from ..utils import perf_tracer
 
         accepted = False
@@ -211,29 +226,34 @@ class WorkflowExecutor:
         finally:
             if st is not None:
                 st.end_session(sid, status="accepted" if accepted else "rejected")
-            if accepted:
+            if is_eval:
+                pass
+            elif accepted:
                 self.staleness.on_rollout_accepted()
             else:
                 self.staleness.on_rollout_rejected()
 
     # -------------------------------------------------------------------- wait
     def _drain(self):
-        while True:
-            r = self.runner.poll()
-            if r is None:
-                return
-            if r.error is not None:
-                self._n_failed += 1
-                self._consecutive_failures += 1
-                self._last_error = r.error
+        for runner in (self.runner, self._eval_runner):
+            while runner is not None:
+                r = runner.poll()
+                if r is None:
+                    break
+                if r.error is not None:
+                    self._n_failed += 1
+                    self._consecutive_failures += 1
+                    self._last_error = r.error
+                    with self._lock:
+                        self._by_task[r.task_id] = r  # so that a caller polling this task learns that it failed
+                    continue
+                self._consecutive_failures = 0
                 with self._lock:
-                    self._by_task[r.task_id] = r  # so that a caller polling this task learns that it failed
-                continue
-            self._consecutive_failures = 0
-            with self._lock:
-                self._by_task[r.task_id] = r
-                if r.data is not None:
-                    self._results.append(r)
+                    self._by_task[r.task_id] = r
+                    if r.task_id in self._eval_tasks:
+                        self._eval_tasks.discard(r.task_id)  # fetched by task id only, never part of a batch
+                    elif r.data is not None:
+                        self._results.append(r)
 
     def wait(self, count: int, timeout: float | None = None, raise_timeout: bool = True):
         """Returns ``count`` accepted trajectories concatenated into one padded batch, oldest
@@ -297,9 +317,11 @@ class WorkflowExecutor:
             return "done", r.data
 
     def rollout_batch(self, data: list[dict[str, Any]], workflow=None, workflow_kwargs=None,
-                      should_accept_fn=None, group_size: int = 1):
-        """Synchronous: submits every item and waits for all accepted results."""
-        tids = [self.submit(d, workflow, workflow_kwargs, should_accept_fn, group_size) for d in data]
+                      should_accept_fn=None, group_size: int = 1, is_eval: bool = False):
+        """Synchronous: submits every item and waits for all accepted results. ``is_eval`` keeps the samples
+        out of the staleness accounting and off the training queue."""
+        tids = [self.submit(d, workflow, workflow_kwargs, should_accept_fn, group_size, is_eval=is_eval)
+                for d in data]
         outs = []
         for t in tids:
             r = self.wait_for_task(t, timeout=self.config.request_timeout)

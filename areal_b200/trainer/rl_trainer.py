@@ -284,6 +284,10 @@ class PPOTrainer:
         if not self.is_trainer:
             # rollout-only rank of a disaggregated run: produce batches until told to stop
             server = RolloutServer(self.topo, self.rollout)
+            if eval_workflow is not None and self.valid_dataset is not None:
+                gi, ng = self.topo.gen_ranks.index(self.topo.rank), len(self.topo.gen_ranks)
+                server.set_eval([self.valid_dataset[i] for i in range(gi, len(self.valid_dataset), ng)],
+                                eval_workflow, eval_workflow_kwargs)
             server.serve(self.dataloader, workflow, workflow_kwargs, group_size=group, n_steps=total)
             server.wait_stop(timeout=600)
             return
@@ -362,8 +366,12 @@ class PPOTrainer:
 
     def _evaluate(self, workflow, workflow_kwargs):
         if not self.colocated:
+            # the rollout ranks hold the validation set and the evaluation workflow (``RolloutServer.set_eval``)
+            total, n = self.rollout_client.evaluate()
+            if n:
+                stats_tracker.get("eval").scalar(reward=total / n)
             return
         items = [self.valid_dataset[i] for i in range(self.rank, len(self.valid_dataset), self.world)]
-        batch = self.rollout.rollout_batch(items, workflow, workflow_kwargs)
+        batch = self.rollout.rollout_batch(items, workflow, workflow_kwargs, is_eval=True)
         if batch:
             stats_tracker.get("eval").scalar(reward=float(batch["rewards"].float().mean()))

@@ -314,6 +314,28 @@ def test_engine_outputs_do_not_change_when_resubmitted_groups_share_their_prefix
         assert ta == tb and max(abs(x - y) for x, y in zip(la, lb)) < 1e-4
 
 
+def test_evaluation_episodes_bypass_the_staleness_gate_and_the_training_queue():
+    CountingWorkflow.started = 0
+    eng, ex = _executor(bs=4, eta=0)
+    try:
+        for i in range(12):
+            ex.submit({"i": i}, CountingWorkflow)
+        assert ex.wait(4, timeout=10)["rewards"].shape == (4,)
+        time.sleep(0.1)
+        assert ex.get_capacity() <= 0 and CountingWorkflow.started == 4       # training is gated at version 0
+        # evaluation goes through although 8 training episodes wait for capacity in front of it
+        ev = ex.rollout_batch([{"i": 100 + i} for i in range(5)], CountingWorkflow, is_eval=True)
+        assert sorted(ev["rewards"].tolist()) == [100.0, 101.0, 102.0, 103.0, 104.0]
+        st = ex.export_stats()
+        assert st["rollout/accepted"] == 4 and st["rollout/enqueued"] == 8    # untouched by the evaluation samples
+        assert ex.wait(1, timeout=0.2, raise_timeout=False) is None           # and none of them leaked into a batch
+        eng.version = 1
+        nxt = ex.wait(4, timeout=10)
+        assert nxt["rewards"].max() < 100
+    finally:
+        ex.destroy()
+
+
 def test_native_engine_stop_strings_and_unsupported_sampling_options():
     """Stop strings cut the output at the first token that completes one (matched on decoded text, so a string
     may span tokens); options the engine does not implement are refused, not ignored."""

@@ -37,6 +37,7 @@ def test_colocated_two_ranks(tmp_path):
     assert a["rollout_matches"] and b["rollout_matches"]
     assert a["rollout_version"] == b["rollout_version"] == 2
     assert sum(a["tokens"]) > 0
+    assert all(r is not None and 0.0 <= r <= 1.0 for r in a["eval_reward"])
 
 
 @pytest.mark.slow
@@ -47,3 +48,5 @@ def test_disaggregated_two_ranks(tmp_path):
     assert tr["steps"] == 2 and tr["version"] == 2
     assert gen["rollout_version"] == 2
     assert all(g > 0 for g in tr["grad_norm"])
+    # evaluation runs on the rollout rank (it holds the validation set) and reports to the trainer after every step
+    assert len(tr["eval_reward"]) == 2 and all(r is not None and 0.0 <= r <= 1.0 for r in tr["eval_reward"])

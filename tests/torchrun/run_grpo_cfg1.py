@@ -48,10 +48,13 @@ def main(out_path: str, mode: str):
     for _ in range(16 * 3):
         L = int(torch.randint(32, 65, (1,), generator=g))
         ds.append(dict(input_ids=torch.randint(0, 1024, (L,), generator=g).tolist()))
+    valid = [dict(input_ids=torch.randint(0, 1024, (24,), generator=g).tolist()) for _ in range(6)]
+    cfg.evaluator.freq_steps = 1
     seen = []
-    with PPOTrainer(cfg, ds) as tr:
-        tr.train(workflow=RLVRWorkflow, workflow_kwargs=dict(reward_fn=reward_fn, gconfig=cfg.gconfig,
-                                                            reward_in_process=True),
+    wf_kwargs = dict(reward_fn=reward_fn, gconfig=cfg.gconfig, reward_in_process=True)
+    with PPOTrainer(cfg, ds, valid) as tr:
+        tr.train(workflow=RLVRWorkflow, workflow_kwargs=wf_kwargs, eval_workflow=RLVRWorkflow,
+                 eval_workflow_kwargs=dict(wf_kwargs, gconfig=cfg.gconfig.new(n_samples=1, max_new_tokens=8)),
                  max_steps=2, step_callback=lambda s, st: seen.append(st))
         res = {"rank": tr.rank, "is_trainer": tr.is_trainer}
         if tr.is_trainer:
@@ -59,7 +62,9 @@ def main(out_path: str, mode: str):
             res.update(checksum=float(flat.double().sum()), absum=float(flat.double().abs().sum()),
                        version=tr.actor_engine.get_version(), steps=len(seen),
                        grad_norm=[s["step/grad_norm"] for s in seen], loss=[s["step/loss"] for s in seen],
-                       tokens=[s["step/trained_tokens"] for s in seen])
+                       tokens=[s["step/trained_tokens"] for s in seen],
+                       eval_reward=[next((v for k, v in s.items() if k.startswith("eval") and k.endswith("reward")), None)
+                                    for s in seen])
             if tr.colocated:
                 rflat = tr.rollout.flat.flat
                 res.update(rollout_version=tr.rollout.get_version(),
