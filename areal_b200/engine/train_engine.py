@@ -152,6 +152,9 @@ class B200TrainEngine(TrainEngine):
         self.pctx = None
         ps = self.parallel
         model_parallel = ps.tp_size * ps.cp_size * ps.pp_size * ps.ep_size > 1
+        if getattr(ps, "etp_size", 1) > 1:
+            raise NotImplementedError("expert tensor parallelism (experts split over tensor-parallel ranks) is not "
+                                      "implemented: spread whole experts with e instead")
         if model_parallel:
             assert dist.is_initialized(), "tensor / sequence / pipeline parallelism needs torch.distributed"
             from ..parallel.context import build_mesh
@@ -349,6 +352,9 @@ class B200TrainEngine(TrainEngine):
                 self.optimizer.partner_group = pctx.ep_group
             if pctx is not None and pctx.pp_size > 1:
                 self.optimizer.norm_groups.append(pctx.pp_group)
+                if self.optimizer.partner is not None:
+                    # the experts of other pipeline stages count in the global gradient norm as well
+                    self.optimizer.partner.norm_groups.append(pctx.pp_group)
                 if self.model_config.tie_word_embeddings and not self.is_critic and self.model.embed is not None:
                     self.optimizer.pre_step_hooks.append(self._sum_tied_embedding_grads)
                     if not self.model.first_stage:
@@ -863,7 +869,7 @@ class B200TrainEngine(TrainEngine):
                 # One writer per pipeline stage and expert-parallel rank (tensor- / sequence-parallel peers only
                 # take part in the gathers); writers use their own files and the first one indexes them afterwards
                 if ep > 1:
-                    writer = pctx.tp_rank == 0
+                    writer = True  # every rank of the block holds experts nobody else in it has
                 else:
                     writer = pctx is None or (pctx.tp_rank == 0 and pctx.sp_rank == 0)
                 tag = (f"stage{self.mesh.pp_rank + 1:02d}of{pp:02d}" if pp > 1 else "") + \

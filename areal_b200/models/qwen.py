@@ -287,7 +287,11 @@ class Block(nn.Module):
             self.attn = Attention(cfg, dtype, device, pctx, layer_idx)
         self.post_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
         if cfg.layer_is_moe(layer_idx):
-            assert pctx is None or pctx.tp_size == 1, "MoE layers shard over the expert-parallel group, not tp"
+            if pctx is not None and pctx.tp_size > 1 and pctx.ep_size == 1:
+                # under tensor parallelism every rank holds a different slice of the tokens at this point, so the
+                # experts are spread over those ranks (expert parallelism over the tensor-parallel group, e = t)
+                raise NotImplementedError("mixture layers under tensor parallelism need expert parallelism over the "
+                                          "same ranks: give e = t (or a multiple), e.g. megatron:(attn:d1t4|ffn:d1e4)")
             self.mlp = MoEMLP(cfg, dtype, device, pctx)
         else:
             self.mlp = DenseMLP(h, cfg.intermediate_size, dtype, device, pctx, cfg, layer_idx)
@@ -391,7 +395,7 @@ class QwenModel(nn.Module):
                 # draw the FULL tensor (so values do not depend on the tp size), keep this rank's shard
                 from ..parallel.tensor_parallel import is_tp_replicated, tp_slice
 
-                if not is_tp_replicated(name):
+                if not is_tp_replicated(name) and not is_expert:  # experts are split by expert, not by tp
                     dst = torch.empty(self._full_shape(name, p), dtype=p.dtype, device=p.device)
             if dst.is_cuda:
                 # large models: draw on the device (same seed ⇒ same values on every rank)
@@ -425,9 +429,10 @@ class QwenModel(nn.Module):
         from ..parallel.context import ParallelContext
 
         p = self.pctx
-        flat_ctx = ParallelContext(tp_group=p.tp_group, tp_rank=p.tp_rank, tp_size=p.tp_size)
+        flat_ctx = ParallelContext(tp_group=p.tp_group, tp_rank=p.tp_rank, tp_size=p.tp_size,
+                                   ep_group=p.ep_group, ep_rank=p.ep_rank, ep_size=p.ep_size)
         full = type(self)(self.cfg, dtype=next(self.parameters()).dtype, device=next(self.parameters()).device,
-                          pctx=flat_ctx if p.tp_size > 1 else None)
+                          pctx=flat_ctx if (p.tp_size > 1 or p.ep_size > 1) else None)
         full.init_weights(seed, std)
         src = dict(full.named_parameters())
         for name, prm in self.named_parameters():

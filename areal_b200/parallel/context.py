@@ -122,8 +122,8 @@ class MeshGroups:
     cpu_shard_group: Any = None
     mp_group: Any = None  # every rank of one data-parallel replica (tp x sp x pp): they share a batch
     mp_rank: int = 0
-    # expert parallelism: ep groups are blocks of consecutive ranks of the shard group; ranks with the
-    # same position in different blocks hold the same experts (expert-data-parallel group)
+    # expert parallelism: ep groups are blocks of consecutive ranks of a pipeline stage (tensor-parallel index
+    # fastest); ranks with the same position in different blocks hold the same experts (expert-data-parallel group)
     edp_group: Any = None
     edp_rank: int = 0
     edp_size: int = 1
@@ -164,9 +164,16 @@ def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1,
     sh_g = make(lambda p, d, s, t: (p, t))
     mp_g = make(lambda p, d, s, t: d)
     pp_g = make(lambda p, d, s, t: (d, s, t))
-    assert (dp * sp) % ep == 0, "the expert-parallel size must divide dp x sp"
-    ep_g = make(lambda p, d, s, t: (p, t, (d * sp + s) // ep)) if ep > 1 else (None, 0, 1)
-    edp_g = make(lambda p, d, s, t: (p, t, (d * sp + s) % ep)) if ep > 1 else (None, 0, 1)
+    # Expert parallelism runs over the dp x sp x tp ranks of a pipeline stage, numbered with the tensor-parallel
+    # index fastest: every one of them holds different tokens at a mixture layer (under tensor parallelism the
+    # activations between the two halves of a block are sharded by sequence), so any block of ``ep`` consecutive
+    # ranks can exchange tokens for experts. ``ep = tp`` is the hybrid layout "attention tensor-parallel, experts
+    # expert-parallel on the same GPUs"; with ``tp = 1`` the groups are blocks of the dp x sp ranks.
+    assert (dp * sp * tp) % ep == 0, "the expert-parallel size must divide dp x sp x tp"
+    assert tp == 1 or ep == 1 or ep % tp == 0, \
+        "under tensor parallelism an expert-parallel group is made of whole tensor-parallel groups (e a multiple of t)"
+    ep_g = make(lambda p, d, s, t: (p, ((d * sp + s) * tp + t) // ep)) if ep > 1 else (None, 0, 1)
+    edp_g = make(lambda p, d, s, t: (p, ((d * sp + s) * tp + t) % ep)) if ep > 1 else (None, 0, 1)
     tie_g = (None, 0, 1)
     if pp > 1 and dist.is_initialized():
         stride = dp * sp * tp

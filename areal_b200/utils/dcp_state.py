@@ -195,8 +195,10 @@ class EngineDCPState(Stateful):
         if tp_dim is not None and tp > 1:
             gshape[tp_dim] *= tp
             shift[tp_dim] = tp_rank * shape[tp_dim]
-        elif write and tp > 1 and tp_rank != 0:
-            lo = hi = 0  # replicated over the tensor-parallel group: its first rank writes
+        elif write and tp > 1 and tp_rank != 0 and f is not getattr(e, "flat_experts", None):
+            # replicated over the tensor-parallel group: its first rank writes (expert tensors are not replicated:
+            # under the hybrid layout every tensor-parallel rank holds other experts)
+            lo = hi = 0
         boxes = []
         for box_off, box_sz, start in flat_range_boxes(shape, lo - off, hi - off) if hi > lo else []:
             t = buf[off + start - buf_start: off + start - buf_start + math.prod(box_sz)].view(box_sz)

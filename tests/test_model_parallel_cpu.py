@@ -57,6 +57,37 @@ def test_expert_parallel_step_matches_single_process(tmp_path, n, ep):
     _run(n, 29670 + n, ["--ep", str(ep), "--preset", "tiny-qwen3-moe"], _ref(tmp_path, preset="tiny-qwen3-moe"))
 
 
+@pytest.mark.parametrize("n,args", [(2, ["--tp", "2", "--ep", "2"]), (4, ["--tp", "2", "--ep", "2"]),
+                                    (4, ["--tp", "2", "--ep", "4"]), (4, ["--tp", "2", "--pp", "2", "--ep", "2", "--n-mbs", "2"]),
+                                    (4, ["--pp", "2", "--ep", "2", "--n-mbs", "2"])])
+def test_hybrid_tensor_and_expert_parallel_step_matches_single_process(tmp_path, n, args):
+    """Attention tensor-parallel, experts spread over the same ranks (the ``(attn:..t2|ffn:..e2)`` layout): the
+    token slices that sequence-parallel activations leave on the tensor-parallel ranks are exchanged for experts;
+    expert-parallel groups may also span several tensor-parallel groups, and pipeline stages (whose experts all
+    count in the clipping norm)."""
+    n_mbs = 2 if "--n-mbs" in args else 1
+    _run(n, 29742 + n + 3 * len(args), args + ["--preset", "tiny-qwen3-moe"],
+         _ref(tmp_path, preset="tiny-qwen3-moe", n_mbs=n_mbs))
+
+
+@pytest.mark.parametrize("n,pp,ep,tp", [(2, 1, 2, 2), (4, 2, 2, 2), (4, 1, 4, 2)])
+def test_checkpoint_under_the_hybrid_layout(tmp_path, n, pp, ep, tp):
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
+           "127.0.0.1", "--master-port", str(29760 + n + pp + 3 * ep), os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
+           "tiny-qwen3-moe", str(pp), str(tmp_path / "ckpt"), str(ep), str(tp)]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_mixture_layers_under_tensor_parallelism_need_expert_parallelism():
+    from areal_b200.models.config import PRESETS
+    from areal_b200.models.qwen import build_model
+    from areal_b200.parallel.context import ParallelContext
+
+    with pytest.raises(NotImplementedError, match="e = t"):
+        build_model(PRESETS["tiny-qwen3-moe"], seed=None, pctx=ParallelContext(tp_size=2, tp_rank=0))
+
+
 @pytest.mark.parametrize("n,preset,extra", [(2, "tiny-qwen2_5-vl", []), (2, "tiny-qwen3-vl", ["--shard-vision"]),
                                             (4, "tiny-qwen3-vl", ["--n-mbs", "2"]),
                                             (2, "tiny-qwen2_5-vl", ["--shard-vision", "--one-image"])])

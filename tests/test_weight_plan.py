@@ -15,7 +15,9 @@ WORKER = os.path.join(ROOT, "tests", "torchrun", "run_weight_plan.py")
 
 @pytest.mark.parametrize("n,flags", [(2, ["--tp", "2"]), (4, ["--tp", "2"]), (2, ["--pp", "2"]),
                                      (2, ["--pp", "2", "--vpp", "2"]), (2, ["--ep", "2", "--preset", "tiny-qwen3-moe"]),
-                                     (4, ["--tp", "2", "--pp", "2"])])
+                                     (4, ["--tp", "2", "--pp", "2"]),
+                                     (2, ["--tp", "2", "--ep", "2", "--preset", "tiny-qwen3-moe"]),
+                                     (4, ["--tp", "2", "--ep", "4", "--preset", "tiny-qwen3-moe"])])
 def test_plan_rebuilds_the_full_model_exactly_once(n, flags):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", str(29800 + 3 * n + 5 * len(flags) + len(flags[-1])), WORKER] + flags

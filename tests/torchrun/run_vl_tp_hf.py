@@ -17,12 +17,16 @@ from areal_b200.models.config import PRESETS  # noqa: E402
 from areal_b200.models.qwen import build_model  # noqa: E402
 
 
-def main(preset: str, pp: int = 1, out: str = "", ep: int = 1):
+def main(preset: str, pp: int = 1, out: str = "", ep: int = 1, tp: int = 0):
     dist.init_process_group("gloo")
     cfg = TrainEngineConfig(experiment_name="t", trial_name="t", path="", init_from_scratch=True, dtype="float32",
                             model_preset=preset, optimizer=OptimizerConfig(lr=1e-3))
     eng = B200TrainEngine(cfg)
-    if ep > 1:  # expert parallelism lives inside the data-parallel ranks
+    if ep > 1 and tp > 1:  # hybrid: attention tensor-parallel, experts spread over the same ranks
+        world = dist.get_world_size()
+        eng.create_process_group(ParallelStrategy(tensor_parallel_size=tp, pipeline_parallel_size=pp,
+                                                  data_parallel_size=world // (tp * pp), expert_parallel_size=ep))
+    elif ep > 1:  # expert parallelism lives inside the data-parallel ranks
         eng.create_process_group(ParallelStrategy(data_parallel_size=dist.get_world_size(), expert_parallel_size=ep))
     else:
         eng.create_process_group(ParallelStrategy(tensor_parallel_size=dist.get_world_size() // pp,
@@ -69,4 +73,4 @@ def main(preset: str, pp: int = 1, out: str = "", ep: int = 1):
 
 if __name__ == "__main__":
     main(sys.argv[1], int(sys.argv[2]) if len(sys.argv) > 2 else 1, sys.argv[3] if len(sys.argv) > 3 else "",
-         int(sys.argv[4]) if len(sys.argv) > 4 else 1)
+         int(sys.argv[4]) if len(sys.argv) > 4 else 1, int(sys.argv[5]) if len(sys.argv) > 5 else 0)
