@@ -50,3 +50,20 @@ def test_disaggregated_two_ranks(tmp_path):
     assert all(g > 0 for g in tr["grad_norm"])
     # evaluation runs on the rollout rank (it holds the validation set) and reports to the trainer after every step
     assert len(tr["eval_reward"]) == 2 and all(r is not None and 0.0 <= r <= 1.0 for r in tr["eval_reward"])
+
+
+@pytest.mark.slow
+def test_disaggregated_four_ranks(tmp_path):
+    """Two rollout ranks feed two data-parallel trainer ranks: both trainers end with the same weights, both rollout
+    engines reach the trainer's version, and the evaluation result is the same on every trainer (summed over the
+    rollout ranks that ran it)."""
+    res = _run(tmp_path, "disagg", 4, 29613)
+    gens = [r for r in res if not r["is_trainer"]]
+    trs = [r for r in res if r["is_trainer"]]
+    assert len(gens) == 2 and len(trs) == 2
+    assert all(g["rollout_version"] == 2 for g in gens)
+    a, b = trs
+    assert a["steps"] == b["steps"] == 2 and a["version"] == b["version"] == 2
+    assert a["checksum"] == pytest.approx(b["checksum"], rel=1e-9, abs=1e-9)
+    assert a["grad_norm"] == pytest.approx(b["grad_norm"], rel=1e-5)
+    assert a["eval_reward"] == b["eval_reward"] and all(r is not None for r in a["eval_reward"])
