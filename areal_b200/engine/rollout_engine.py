@@ -272,7 +272,8 @@ class NativeRolloutEngine(InferenceEngine):
         self._wake = threading.Condition()
         self._thread: threading.Thread | None = None
         self._pending: dict[int, tuple[asyncio.AbstractEventLoop, asyncio.Future, dict]] = {}
-        self._params: dict[int, tuple[float, int, float]] = {}
+        self._params: dict[int, tuple[float, int, float, float]] = {}  # temperature, top-k, top-p, frequency penalty
+        self._hist: dict[int, collections.Counter] = {}  # requests with a frequency penalty: counts of their output tokens
         # vision-language requests: rid → pixel rows, patch grids, position triples of the prompt and the offset
         # of the positions that follow it
         self._mm: dict[int, dict[str, Any]] = {}
@@ -477,9 +478,9 @@ class NativeRolloutEngine(InferenceEngine):
             t0 = time.perf_counter()
             seq_ids = s.seq_ids[:n].tolist()
             with self._lock:
-                pr = [self._params.get(r, (1.0, 0, 1.0)) for r in seq_ids]
+                pr = [self._params.get(r, (1.0, 0, 1.0, 0.0)) for r in seq_ids]
             b = self._graphs.bucket(n)
-            if b is not None and not any(p[1] > 0 or p[2] < 1.0 for p in pr):
+            if b is not None and not any(p[1] > 0 or p[2] < 1.0 or p[3] for p in pr):
                 t1 = time.perf_counter()
                 toks, lps = self._graphs.run(n, b, s, [p[0] for p in pr], self._rng)
                 t2 = time.perf_counter()
@@ -525,15 +526,29 @@ class NativeRolloutEngine(InferenceEngine):
                                        max_seq_len=int(s.hdr.max_seq_len), **extra)
         logits = self.model.logits(hidden, out_dtype=torch.float32)
         with self._lock:
-            pr = [self._params.get(r, (1.0, 0, 1.0)) for r in seq_ids]
+            pr = [self._params.get(r, (1.0, 0, 1.0, 0.0)) for r in seq_ids]
         temp = torch.tensor([p[0] for p in pr], dtype=torch.float32, device=dev)
         need_k = any(p[1] > 0 for p in pr)
         need_p = any(p[2] < 1.0 for p in pr)
         top_k = torch.tensor([p[1] for p in pr], dtype=torch.int32, device=dev) if need_k else None
         top_p = torch.tensor([p[2] for p in pr], dtype=torch.float32, device=dev) if need_p else None
+        penalised = [(i, r, p[3]) for i, (r, p) in enumerate(zip(seq_ids, pr)) if p[3]]
+        for i, r, pen in penalised:
+            # frequency penalty: every earlier occurrence of a token in this request's output lowers its logit
+            with self._lock:
+                seen = dict(self._hist.get(r) or {})
+            if seen:
+                idx = torch.tensor(list(seen.keys()), dtype=torch.long, device=dev)
+                cnt = torch.tensor(list(seen.values()), dtype=logits.dtype, device=dev)
+                logits[i, idx] -= pen * cnt
         u = torch.rand(n, device=dev, generator=self._rng, dtype=torch.float32)
         toks, lps = sample(logits, temp, top_k, top_p, u)
-        s.commit(toks.cpu().numpy(), lps.cpu().numpy())
+        toks_h = toks.cpu().numpy()
+        with self._lock:
+            for i, r, _ in penalised:
+                if r in self._hist:
+                    self._hist[r][int(toks_h[i])] += 1
+        s.commit(toks_h, lps.cpu().numpy())
         self._gen_tokens += n
         self._steps += 1
         self._deliver()
@@ -644,6 +659,7 @@ class NativeRolloutEngine(InferenceEngine):
             with self._lock:
                 entry = self._pending.pop(rid, None)
                 self._params.pop(rid, None)
+                self._hist.pop(rid, None)
                 self._mm.pop(rid, None)
             if entry is None:
                 continue
@@ -658,7 +674,8 @@ class NativeRolloutEngine(InferenceEngine):
             loop.call_soon_threadsafe(_set_exception, fut, e)
 
     # --------------------------------------------------------------- generate
-    async def _generate_once(self, input_ids: list[int], g, max_new: int, images=None, share_len: int = 0):
+    async def _generate_once(self, input_ids: list[int], g, max_new: int, images=None, share_len: int = 0,
+                             history: list[int] | None = None):
         if self._step_error is not None:
             raise RuntimeError("rollout engine stopped") from self._step_error
         loop = asyncio.get_running_loop()
@@ -681,7 +698,9 @@ class NativeRolloutEngine(InferenceEngine):
             if rid < 0:
                 raise ValueError(f"prompt of {len(input_ids)} tokens does not fit the rollout engine")
             self._pending[rid] = (loop, fut, {})
-            self._params[rid] = (temp, top_k, float(g.top_p))
+            self._params[rid] = (temp, top_k, float(g.top_p), float(g.frequency_penalty or 0.0))
+            if g.frequency_penalty:
+                self._hist[rid] = collections.Counter(history or [])
             if mm_state is not None:
                 self._mm[rid] = mm_state
         with self._wake:
@@ -692,8 +711,8 @@ class NativeRolloutEngine(InferenceEngine):
         g = req.gconfig
         if g.n_samples != 1:
             raise ValueError("agenerate produces one sample; use n_samples=1 and group at the workflow level")
-        if g.frequency_penalty or g.use_beam_search:
-            raise NotImplementedError("the native rollout engine samples without frequency penalty or beam search")
+        if g.use_beam_search:
+            raise NotImplementedError("the native rollout engine samples; it has no beam search")
         if g.stop and (req.tokenizer or getattr(self, "tokenizer", None)) is None:
             raise ValueError("stop strings need a tokenizer (ModelRequest.tokenizer or the engine's)")
         max_new = min(g.max_new_tokens, max(g.max_tokens - len(req.input_ids), 0))
@@ -712,7 +731,7 @@ class NativeRolloutEngine(InferenceEngine):
                 self._reprefill_tokens += len(req.input_ids) + len(out_tokens)
             reason, toks, lps = await self._generate_once(list(req.input_ids) + out_tokens, g,
                                                           max_new - len(out_tokens), images,
-                                                          share_len=len(req.input_ids))
+                                                          share_len=len(req.input_ids), history=out_tokens)
             if toks and ttft == float("inf"):
                 ttft = time.perf_counter() - t0
             out_tokens += toks

@@ -375,8 +375,14 @@ def test_native_engine_stop_strings_and_unsupported_sampling_options():
         assert same.output_tokens == full.output_tokens and same.stop_reason == "length"
         with pytest.raises(ValueError, match="tokenizer"):
             asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(stop=["x"]))))
-        with pytest.raises(NotImplementedError):
-            asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(frequency_penalty=0.5))))
+        # frequency penalty: a huge penalty forbids any repeated output token (greedy decoding of a random tiny
+        # model repeats itself quickly without it)
+        free = asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(max_new_tokens=40))))
+        pen = asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(max_new_tokens=40,
+                                                                                         frequency_penalty=1e4))))
+        assert len(set(pen.output_tokens)) == 40 and pen.output_tokens[0] == free.output_tokens[0]
+        assert len(set(free.output_tokens)) < 40 or free.output_tokens == pen.output_tokens
+        assert not eng._hist                                             # the history is dropped with the request
         with pytest.raises(NotImplementedError):
             asyncio.run(eng.agenerate(ModelRequest(input_ids=prompt, gconfig=base.new(use_beam_search=True))))
     finally:
