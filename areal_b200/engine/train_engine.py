@@ -151,10 +151,7 @@ class B200TrainEngine(TrainEngine):
         self.mesh = None
         self.pctx = None
         ps = self.parallel
-        model_parallel = ps.tp_size * ps.cp_size * ps.pp_size * ps.ep_size > 1
-        if getattr(ps, "etp_size", 1) > 1:
-            raise NotImplementedError("expert tensor parallelism (experts split over tensor-parallel ranks) is not "
-                                      "implemented: spread whole experts with e instead")
+        model_parallel = ps.tp_size * ps.cp_size * ps.pp_size * ps.ep_size * getattr(ps, "etp_size", 1) > 1
         if model_parallel:
             assert dist.is_initialized(), "tensor / sequence / pipeline parallelism needs torch.distributed"
             from ..parallel.context import build_mesh
@@ -165,7 +162,8 @@ class B200TrainEngine(TrainEngine):
             self.train_ranks = ranks
             dp = len(ranks) // (ps.tp_size * ps.cp_size * ps.pp_size)
             # context_parallel_size is Ulysses sequence parallelism for this engine family
-            self.mesh = build_mesh(ranks, dp=dp, sp=ps.cp_size, tp=ps.tp_size, pp=ps.pp_size, ep=ps.ep_size)
+            self.mesh = build_mesh(ranks, dp=dp, sp=ps.cp_size, tp=ps.tp_size, pp=ps.pp_size, ep=ps.ep_size,
+                                   etp=getattr(ps, "etp_size", 1))
             self.pctx = self.mesh.ctx
             if ps.pp_size > 1:
                 # schedule and virtual stages: `archon.pp_schedule` for the Archon-style backend, 1F1B otherwise;
@@ -304,7 +302,8 @@ class B200TrainEngine(TrainEngine):
             from ..parallel.tensor_parallel import is_tp_replicated
 
             rep_first = is_tp_replicated
-        ep = pctx.ep_size if pctx is not None else 1
+        # experts that differ between ranks (expert parallelism and / or expert tensor parallelism) live apart
+        ep = (pctx.ep_size * pctx.etp_size) if pctx is not None else 1
         is_expert = (lambda n: n.endswith(("mlp.gate_up", "mlp.down")) and ".mlp." in n and
                      dict(self.model.named_parameters())[n].dim() == 3)
         self.flat_base = None
@@ -334,7 +333,7 @@ class B200TrainEngine(TrainEngine):
             edp = self.mesh.edp_group if self.mesh.edp_size > 1 else "local"
             self.flat_experts = FlatParams(self.model, edp, with_grads=self.optimizer_config is not None,
                                            select=is_expert)
-            if self.device.type == "cuda":
+            if self.device.type == "cuda" and pctx.ep_size > 1:
                 from ..parallel.expert_parallel import EPGroupState
 
                 mc = self.model_config
@@ -349,7 +348,9 @@ class B200TrainEngine(TrainEngine):
                                           prefetch=int(getattr(fs, "optim_step_prefetch_layers", 1)))
             if self.flat_experts is not None:
                 self.optimizer.partner = ShardedAdamW(self.flat_experts, self.optimizer_config, total_steps=total)
-                self.optimizer.partner_group = pctx.ep_group
+                # the ranks whose expert parameters differ from this rank's: the expert-parallel group times the
+                # expert-tensor-parallel group
+                self.optimizer.partner_group = pctx.extras.get("emp_group", pctx.ep_group)
             if pctx is not None and pctx.pp_size > 1:
                 self.optimizer.norm_groups.append(pctx.pp_group)
                 if self.optimizer.partner is not None:
@@ -869,7 +870,9 @@ class B200TrainEngine(TrainEngine):
                 # One writer per pipeline stage and expert-parallel rank (tensor- / sequence-parallel peers only
                 # take part in the gathers); writers use their own files and the first one indexes them afterwards
                 if ep > 1:
-                    writer = True  # every rank of the block holds experts nobody else in it has
+                    # every expert-parallel rank of the block holds experts nobody else in it has; the ranks that
+                    # hold slices of the same experts gather them, and the first of them writes
+                    writer = pctx.etp_rank == 0
                 else:
                     writer = pctx is None or (pctx.tp_rank == 0 and pctx.sp_rank == 0)
                 tag = (f"stage{self.mesh.pp_rank + 1:02d}of{pp:02d}" if pp > 1 else "") + \

@@ -53,13 +53,28 @@ def _global_name(name: str, layer_ids: list[int]) -> str:
 
 
 def param_segments(name: str, shape: tuple[int, ...], full_shape: tuple[int, ...], cfg, tp_rank: int, tp: int,
-                   ep_rank: int, ep: int) -> list[tuple[int, int, int, int, int, int]] | None:
+                   ep_rank: int, ep: int, etp_rank: int = 0, etp: int = 1
+                   ) -> list[tuple[int, int, int, int, int, int]] | None:
     """Segments of one parameter shard relative to the starts of the source and destination tensors, as
     ``(src, dst, rows, row, src_pitch, dst_pitch)``; ``None`` when this shard is a replica that the first
     tensor-parallel rank pushes."""
     n = math.prod(shape) if shape else 1
-    if ep > 1 and len(shape) == 3 and name.endswith(("mlp.gate_up", "mlp.down")):
-        return [(0, ep_rank * n, 1, n, n, n)]  # this rank's experts, a contiguous block of the stacked tensor
+    if ep * etp > 1 and len(shape) == 3 and name.endswith(("mlp.gate_up", "mlp.down")):
+        if etp == 1:
+            return [(0, ep_rank * n, 1, n, n, n)]  # this rank's experts, a contiguous block of the stacked tensor
+        # expert tensor parallelism: per expert, the slice of the gate rows and of the up rows (contiguous blocks
+        # of whole rows), or a column block of the down projection (strided)
+        e_loc, segs = shape[0], []
+        per_src, per_dst = shape[1] * shape[2], full_shape[1] * full_shape[2]
+        for e in range(e_loc):
+            s0, d0 = e * per_src, (ep_rank * e_loc + e) * per_dst
+            if name.endswith("mlp.gate_up"):
+                half, full_half, cols = shape[1] // 2, full_shape[1] // 2, shape[2]
+                segs.append((s0, d0 + etp_rank * half * cols, 1, half * cols, 0, 0))
+                segs.append((s0 + half * cols, d0 + (full_half + etp_rank * half) * cols, 1, half * cols, 0, 0))
+            else:
+                segs.append((s0, d0 + etp_rank * shape[2], shape[1], shape[2], shape[2], full_shape[2]))
+        return segs
     if tp == 1 or tuple(shape) == tuple(full_shape):
         if tp > 1 and tp_rank != 0:
             return None
@@ -90,6 +105,8 @@ def build_plan(engine, layout: dict[str, tuple[int, tuple[int, ...]]]) -> dict[i
     tp_rank = pctx.tp_rank if pctx is not None else 0
     ep = pctx.ep_size if pctx is not None else 1
     ep_rank = pctx.ep_rank if pctx is not None else 0
+    etp = pctx.etp_size if pctx is not None else 1
+    etp_rank = pctx.etp_rank if pctx is not None else 0
     model, cfg = engine.model, engine.model_config
     layer_ids = list(getattr(model, "layer_ids", range(cfg.num_hidden_layers)))
     plans: dict[int, tuple[object, list[Segment]]] = {}
@@ -106,7 +123,7 @@ def build_plan(engine, layout: dict[str, tuple[int, tuple[int, ...]]]) -> dict[i
             if gname not in layout:
                 raise KeyError(f"the rollout engine has no parameter {gname}")
             dst_off, full_shape = layout[gname]
-            rel = param_segments(name, tuple(p.shape), tuple(full_shape), cfg, tp_rank, tp, ep_rank, ep)
+            rel = param_segments(name, tuple(p.shape), tuple(full_shape), cfg, tp_rank, tp, ep_rank, ep, etp_rank, etp)
             if rel is None:
                 continue
             for s, d, rows, row, sp, dp in rel:

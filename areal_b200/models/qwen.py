@@ -18,7 +18,7 @@ from __future__ import annotations
 
 import re
 
-from typing import Iterable, Iterator
+from typing import Any, Iterable, Iterator
 
 import torch
 import torch.nn as nn
@@ -191,11 +191,15 @@ class MoEMLP(nn.Module):
         self.pctx = pctx
         E, I, H = cfg.num_experts, cfg.moe_intermediate_size, cfg.hidden_size
         ep = pctx.ep_size if pctx is not None else 1
+        etp = pctx.etp_size if pctx is not None else 1
         assert E % ep == 0, "the expert count must divide by the expert-parallel size"
+        assert I % etp == 0, "the expert width must divide by the expert-tensor-parallel size"
         self.router = nn.Parameter(torch.empty(E, H, dtype=dtype, device=device))
-        # under expert parallelism this rank owns experts [ep_rank * E/ep, (ep_rank + 1) * E/ep)
-        self.gate_up = nn.Parameter(torch.empty(E // ep, 2 * I, H, dtype=dtype, device=device))
-        self.down = nn.Parameter(torch.empty(E // ep, H, I, dtype=dtype, device=device))
+        # under expert parallelism this rank owns experts [ep_rank * E/ep, (ep_rank + 1) * E/ep); under expert
+        # tensor parallelism it holds rows [etp_rank * I/etp, (etp_rank + 1) * I/etp) of their gate and up
+        # projections and the matching columns of their down projection
+        self.gate_up = nn.Parameter(torch.empty(E // ep, 2 * I // etp, H, dtype=dtype, device=device))
+        self.down = nn.Parameter(torch.empty(E // ep, H, I // etp, dtype=dtype, device=device))
         self.last_routing = None  # (topk_idx, topk_w) of the last forward, for stats / replay
         # aux-loss-free balancing: a selection-only bias, a buffer (not trained by the optimizer, replicated)
         if cfg.moe_load_balance_coeff > 0:
@@ -264,12 +268,23 @@ class MoEMLP(nn.Module):
         idx, w = self.route(x)
         self.last_routing = (idx.detach(), w.detach())
         p = self.pctx
-        if p is not None and p.ep_size > 1:
-            from ..parallel.expert_parallel import ep_moe_forward
 
-            y = ep_moe_forward(x, idx, w, self.gate_up, self.down, p.extras.get("ep_state", p.ep_group))
+        def experts(x_, idx_, w_):
+            if p is not None and p.ep_size > 1:
+                from ..parallel.expert_parallel import ep_moe_forward
+
+                return ep_moe_forward(x_, idx_, w_, self.gate_up, self.down, p.extras.get("ep_state", p.ep_group))
+            return moe_experts_forward(x_, idx_, w_, self.gate_up, self.down)
+
+        if p is not None and p.etp_size > 1:
+            # expert tensor parallelism: the ranks of the group hold slices of the same experts, so they pool their
+            # tokens (each routed its own), every rank applies its slice to all of them and the partial outputs are
+            # summed back to the rank each token came from
+            from ..parallel.expert_parallel import etp_moe_forward
+
+            y = etp_moe_forward(x, idx, w, p.etp_group, experts)
         else:
-            y = moe_experts_forward(x, idx, w, self.gate_up, self.down)
+            y = experts(x, idx, w)
         return y if self.shared_gate_up is None else y + self._shared(x)
 
 
@@ -287,7 +302,7 @@ class Block(nn.Module):
             self.attn = Attention(cfg, dtype, device, pctx, layer_idx)
         self.post_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
         if cfg.layer_is_moe(layer_idx):
-            if pctx is not None and pctx.tp_size > 1 and pctx.ep_size == 1:
+            if pctx is not None and pctx.tp_size > 1 and pctx.ep_size * pctx.etp_size == 1:
                 # under tensor parallelism every rank holds a different slice of the tokens at this point, so the
                 # experts are spread over those ranks (expert parallelism over the tensor-parallel group, e = t)
                 raise NotImplementedError("mixture layers under tensor parallelism need expert parallelism over the "
@@ -388,9 +403,13 @@ class QwenModel(nn.Module):
                 continue
             dst = p
             ep = self.pctx.ep_size if self.pctx is not None else 1
-            is_expert = ep > 1 and name.endswith(("mlp.gate_up", "mlp.down")) and p.dim() == 3
+            etp = self.pctx.etp_size if self.pctx is not None else 1
+            is_expert = ep * etp > 1 and name.endswith(("mlp.gate_up", "mlp.down")) and p.dim() == 3
             if is_expert:
-                dst = torch.empty((p.shape[0] * ep,) + tuple(p.shape[1:]), dtype=p.dtype, device=p.device)
+                # the full stack of experts at full width: values do not depend on the layout
+                full = [p.shape[0] * ep, p.shape[1], p.shape[2]]
+                full[1 if name.endswith("gate_up") else 2] *= etp
+                dst = torch.empty(tuple(full), dtype=p.dtype, device=p.device)
             if tp > 1:
                 # draw the FULL tensor (so values do not depend on the tp size), keep this rank's shard
                 from ..parallel.tensor_parallel import is_tp_replicated, tp_slice
@@ -411,7 +430,12 @@ class QwenModel(nn.Module):
                     flat[s:s + n].copy_(torch.empty(n, dtype=torch.float32).normal_(0.0, std, generator=g))
             if is_expert:
                 n = p.shape[0]
-                p.copy_(dst[self.pctx.ep_rank * n:(self.pctx.ep_rank + 1) * n])
+                mine = dst[self.pctx.ep_rank * n:(self.pctx.ep_rank + 1) * n]
+                if etp > 1:
+                    from ..parallel.tensor_parallel import expert_slice
+
+                    mine = expert_slice(name, mine, self.pctx.etp_rank, etp)
+                p.copy_(mine)
             elif dst is not p:
                 p.copy_(tp_slice(name, dst, self.cfg, tp_rank, tp))
         for li, layer in enumerate(self.layers):
@@ -430,9 +454,10 @@ class QwenModel(nn.Module):
 
         p = self.pctx
         flat_ctx = ParallelContext(tp_group=p.tp_group, tp_rank=p.tp_rank, tp_size=p.tp_size,
-                                   ep_group=p.ep_group, ep_rank=p.ep_rank, ep_size=p.ep_size)
+                                   ep_group=p.ep_group, ep_rank=p.ep_rank, ep_size=p.ep_size,
+                                   etp_group=p.etp_group, etp_rank=p.etp_rank, etp_size=p.etp_size)
         full = type(self)(self.cfg, dtype=next(self.parameters()).dtype, device=next(self.parameters()).device,
-                          pctx=flat_ctx if (p.tp_size > 1 or p.ep_size > 1) else None)
+                          pctx=flat_ctx if (p.tp_size > 1 or p.ep_size > 1 or p.etp_size > 1) else None)
         full.init_weights(seed, std)
         src = dict(full.named_parameters())
         for name, prm in self.named_parameters():
@@ -626,6 +651,21 @@ class QwenModel(nn.Module):
             return 1
         return None
 
+    def shard_spec(self, hf_name: str) -> tuple[int, int, int, Any] | None:
+        """``(dimension, rank, size, group)`` of the split of an HF tensor over a model-parallel group, ``None``
+        for a tensor this rank holds whole: dense projections over the tensor-parallel group, the projections of
+        one expert over the expert-tensor-parallel group."""
+        p = self.pctx
+        if p is None:
+            return None
+        if ".experts." in hf_name:
+            if p.etp_size == 1:
+                return None
+            dim = 1 if hf_name.endswith("down_proj.weight") else 0
+            return dim, p.etp_rank, p.etp_size, p.etp_group
+        dim = self._tp_dim(hf_name)
+        return None if dim is None else (dim, p.tp_rank, p.tp_size, p.tp_group)
+
     def to_hf(self) -> Iterator[tuple[str, torch.Tensor]]:
         """Yields ``(hf_name, tensor)`` in HF checkpoint naming: views of the fused parameters, or,
         under tensor parallelism, full tensors gathered over the tp group (a collective: every tp
@@ -633,12 +673,13 @@ class QwenModel(nn.Module):
         import torch.distributed as dist
 
         for name, t in self.to_hf_local(export=True):
-            d = self._tp_dim(name)
-            if d is None:
+            spec = self.shard_spec(name)
+            if spec is None:
                 yield self.checkpoint_name(name), t
             else:
-                parts = [torch.empty_like(t) for _ in range(self.pctx.tp_size)]
-                dist.all_gather(parts, t.contiguous(), group=self.pctx.tp_group)
+                d, _, size, group = spec
+                parts = [torch.empty_like(t) for _ in range(size)]
+                dist.all_gather(parts, t.contiguous(), group=group)
                 yield self.checkpoint_name(name), torch.cat(parts, d)
 
     # Families whose checkpoint files name the same tensors differently (Mixtral: ``block_sparse_moe`` with
@@ -703,7 +744,7 @@ class QwenModel(nn.Module):
                 yield p + "mlp.up_proj.weight", m.gate_up[I:]
                 yield p + "mlp.down_proj.weight", m.down
             else:
-                Im = cfg.moe_intermediate_size
+                Im = m.gate_up.shape[1] // 2  # the local width under expert tensor parallelism
                 yield p + "mlp.gate.weight", m.router
                 # under expert parallelism this rank holds (and names) experts [ep_rank * n, (ep_rank + 1) * n)
                 n_loc = m.gate_up.shape[0]
@@ -809,10 +850,11 @@ class QwenModel(nn.Module):
                     raise KeyError(f"unexpected tensor {name}")
                 continue
             d = dst[name]
-            dim = self._tp_dim(name)
-            if dim is not None:
-                n = t.shape[dim] // self.pctx.tp_size
-                t = t.narrow(dim, self.pctx.tp_rank * n, n)
+            spec = self.shard_spec(name)
+            if spec is not None:
+                dim, rank, size, _ = spec
+                n = t.shape[dim] // size
+                t = t.narrow(dim, rank * n, n)
             if d.shape != t.shape:
                 raise ValueError(f"{name}: shape {tuple(t.shape)} != {tuple(d.shape)}")
             d.copy_(t.to(device=d.device, dtype=d.dtype))

@@ -61,6 +61,10 @@ class ParallelContext:
     ep_group: Any = None
     ep_rank: int = 0
     ep_size: int = 1
+    # expert tensor parallelism: the ranks that hold slices (of the intermediate dimension) of the same experts
+    etp_group: Any = None
+    etp_rank: int = 0
+    etp_size: int = 1
     pp_group: Any = None
     pp_rank: int = 0
     pp_size: int = 1
@@ -130,7 +134,7 @@ class MeshGroups:
 
 
 def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1, cpu_groups: bool = True,
-               ep: int = 1) -> MeshGroups:
+               ep: int = 1, etp: int = 1) -> MeshGroups:
     """Creates every group of a ``pp x dp x sp x tp`` mesh over ``ranks``. Collective over the
     WHOLE world (``dist.new_group`` semantics): every process must call it with the same arguments,
     whether or not it belongs to ``ranks``."""
@@ -165,15 +169,23 @@ def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1,
     mp_g = make(lambda p, d, s, t: d)
     pp_g = make(lambda p, d, s, t: (d, s, t))
     # Expert parallelism runs over the dp x sp x tp ranks of a pipeline stage, numbered with the tensor-parallel
-    # index fastest: every one of them holds different tokens at a mixture layer (under tensor parallelism the
-    # activations between the two halves of a block are sharded by sequence), so any block of ``ep`` consecutive
-    # ranks can exchange tokens for experts. ``ep = tp`` is the hybrid layout "attention tensor-parallel, experts
-    # expert-parallel on the same GPUs"; with ``tp = 1`` the groups are blocks of the dp x sp ranks.
-    assert (dp * sp * tp) % ep == 0, "the expert-parallel size must divide dp x sp x tp"
-    assert tp == 1 or ep == 1 or ep % tp == 0, \
-        "under tensor parallelism an expert-parallel group is made of whole tensor-parallel groups (e a multiple of t)"
-    ep_g = make(lambda p, d, s, t: (p, ((d * sp + s) * tp + t) // ep)) if ep > 1 else (None, 0, 1)
-    edp_g = make(lambda p, d, s, t: (p, ((d * sp + s) * tp + t) % ep)) if ep > 1 else (None, 0, 1)
+    # index fastest (q): every one of them holds different tokens at a mixture layer (under tensor parallelism the
+    # activations between the two halves of a block are sharded by sequence), so any block of ranks can exchange
+    # tokens for experts. ``ep = tp`` is the hybrid layout "attention tensor-parallel, experts expert-parallel on the
+    # same GPUs"; with ``tp = 1`` the groups are blocks of the dp x sp ranks. With expert tensor parallelism the
+    # block of ``ep * etp`` ranks factors with the etp index fastest: ``etp`` consecutive ranks hold slices of the
+    # same experts (they gather their tokens, apply their slice and reduce), and the ranks with the same slice index
+    # form the expert-parallel group.
+    emp = ep * etp
+    assert (dp * sp * tp) % emp == 0, "ep x etp must divide dp x sp x tp"
+    assert etp == 1 or tp % etp == 0, "an expert-tensor-parallel group lies inside a tensor-parallel group"
+    assert tp == 1 or emp == 1 or emp % tp == 0, \
+        "under tensor parallelism the ranks sharing a set of experts are whole tensor-parallel groups (e x etp a multiple of t)"
+    qof = lambda d, s, t: (d * sp + s) * tp + t
+    ep_g = make(lambda p, d, s, t: (p, qof(d, s, t) // emp, qof(d, s, t) % etp)) if ep > 1 else (None, 0, 1)
+    etp_g = make(lambda p, d, s, t: (p, qof(d, s, t) // etp)) if etp > 1 else (None, 0, 1)
+    emp_g = make(lambda p, d, s, t: (p, qof(d, s, t) // emp)) if emp > 1 else (None, 0, 1)
+    edp_g = make(lambda p, d, s, t: (p, qof(d, s, t) % emp)) if emp > 1 else (None, 0, 1)
     tie_g = (None, 0, 1)
     if pp > 1 and dist.is_initialized():
         stride = dp * sp * tp
@@ -228,5 +240,9 @@ def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1,
         ctx.extras["pp_links"] = links
     if ep > 1:
         ctx.ep_group, ctx.ep_rank, ctx.ep_size = ep_g
+    if etp > 1:
+        ctx.etp_group, ctx.etp_rank, ctx.etp_size = etp_g
+    if emp > 1:
         mesh.edp_group, mesh.edp_rank, mesh.edp_size = edp_g
+        ctx.extras["emp_group"] = emp_g[0]  # every rank whose expert parameters differ from this rank's
     return mesh

@@ -255,9 +255,20 @@ def ep_moe_forward(x, idx, w, gate_up_local, down_local, st):
 
 
 def _gather_var(t: torch.Tensor, group) -> tuple[torch.Tensor, list[int]]:
-    parts: list = [None] * dist.get_world_size(group)
-    dist.all_gather_object(parts, t.detach().cpu(), group=group)
-    return torch.cat(parts, 0).to(t.device), [p.shape[0] for p in parts]
+    """Concatenation of every rank's rows and the row counts (tensor collectives: counts first, then the rows
+    padded to the largest count)."""
+    P = dist.get_world_size(group)
+    t = t.detach().contiguous()
+    n = torch.tensor([t.shape[0]], dtype=torch.int64, device=t.device)
+    ns = [torch.empty_like(n) for _ in range(P)]
+    dist.all_gather(ns, n, group=group)
+    sizes = [int(v) for v in ns]
+    m = max(sizes)
+    if t.shape[0] < m:
+        t = torch.cat((t, t.new_zeros((m - t.shape[0],) + tuple(t.shape[1:]))), 0)
+    parts = [torch.empty_like(t) for _ in range(P)]
+    dist.all_gather(parts, t, group=group)
+    return torch.cat([p[:k] for p, k in zip(parts, sizes)], 0), sizes
 
 
 class _GatherVar(torch.autograd.Function):
@@ -305,4 +316,16 @@ def _ep_moe_gathered(x, idx, w, gate_up_local, down_local, group):
     local = (idx_all >= r * el) & (idx_all < (r + 1) * el)
     part = M.moe_experts_ref(x_all, torch.where(local, idx_all - r * el, torch.zeros_like(idx_all)),
                              w_all * local, gate_up_local, down_local)
+    return _ReduceSlice.apply(part, group, sizes).to(x.dtype)
+
+
+def etp_moe_forward(x, idx, w, group, experts):
+    """Expert tensor parallelism around ``experts(x, idx, w)`` (the local or expert-parallel mixture over this
+    rank's SLICE of the expert weights, whose output is therefore a partial sum): the ranks of ``group`` pool
+    their tokens with the routing each computed for its own, apply their slices to all of them and get back the
+    sum of the partial outputs for their own rows. Row counts may differ between ranks."""
+    x_all = _GatherVar.apply(x, group)
+    w_all = _GatherVar.apply(w.float(), group)
+    idx_all, sizes = _gather_var(idx, group)
+    part = experts(x_all, idx_all, w_all.to(w.dtype))
     return _ReduceSlice.apply(part, group, sizes).to(x.dtype)

@@ -244,5 +244,25 @@ def tp_unslice(name: str, shards: list[torch.Tensor], cfg) -> torch.Tensor:
     return shards[0]
 
 
+def expert_slice(name: str, full: torch.Tensor, rank: int, size: int) -> torch.Tensor:
+    """Slice ``rank`` of ``size`` of stacked expert weights along the expert width: ``gate_up [E, 2I, H]`` keeps
+    rows ``[rank * I/size, (rank + 1) * I/size)`` of the gate half and of the up half, ``down [E, H, I]`` the
+    matching columns."""
+    if name.endswith("gate_up"):
+        I = full.shape[1] // 2
+        n = I // size
+        return torch.cat((full[:, rank * n:(rank + 1) * n], full[:, I + rank * n: I + (rank + 1) * n]), 1)
+    n = full.shape[2] // size
+    return full[:, :, rank * n:(rank + 1) * n]
+
+
+def expert_unslice(name: str, shards: list[torch.Tensor]) -> torch.Tensor:
+    """Inverse of :func:`expert_slice` over all ranks' shards."""
+    if name.endswith("gate_up"):
+        n = shards[0].shape[1] // 2
+        return torch.cat([s[:, :n] for s in shards] + [s[:, n:] for s in shards], 1)
+    return torch.cat(shards, 2)
+
+
 def is_tp_replicated(name: str) -> bool:
     return not name.endswith(("embed", "lm_head", "attn.qkv", "attn.qkv_bias", "attn.o", "mlp.gate_up", "mlp.down"))

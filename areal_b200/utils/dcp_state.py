@@ -166,7 +166,8 @@ class EngineDCPState(Stateful):
             covered[id(f)].append((off, off + v.numel()))
             if name == tied_copy and not for_load:
                 continue
-            yield name, f, off, tuple(v.shape), model._tp_dim(name)
+            spec = model.shard_spec(name) if hasattr(model, "shard_spec") else None
+            yield name, f, off, tuple(v.shape), (None if spec is None else spec[:3])
         tp = e.pctx.tp_size if e.pctx is not None else 1
         for f in flats:
             spans = sorted(covered[id(f)])
@@ -192,9 +193,12 @@ class EngineDCPState(Stateful):
         tp_rank = e.pctx.tp_rank if e.pctx is not None else 0
         gshape = list(shape)
         shift = [0] * len(shape)
-        if tp_dim is not None and tp > 1:
-            gshape[tp_dim] *= tp
-            shift[tp_dim] = tp_rank * shape[tp_dim]
+        if tp_dim is not None:
+            # ``tp_dim`` is ``(dimension, rank, size)`` of the split over the tensor-parallel group (dense
+            # projections) or the expert-tensor-parallel group (one expert's projections)
+            dim, srank, ssize = tp_dim
+            gshape[dim] *= ssize
+            shift[dim] = srank * shape[dim]
         elif write and tp > 1 and tp_rank != 0 and f is not getattr(e, "flat_experts", None):
             # replicated over the tensor-parallel group: its first rank writes (expert tensors are not replicated:
             # under the hybrid layout every tensor-parallel rank holds other experts)

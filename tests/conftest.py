@@ -33,3 +33,12 @@ def pytest_sessionstart(session):
     from areal_b200 import build as _build
 
     _build.build()
+
+
+def free_port() -> int:
+    """A TCP port that is free right now (for torchrun rendezvous of tests that may run side by side)."""
+    import socket
+
+    with socket.socket() as sock:
+        sock.bind(("127.0.0.1", 0))
+        return sock.getsockname()[1]

@@ -6,6 +6,8 @@ import subprocess
 import sys
 
 import pytest
+
+from tests.conftest import free_port
 import torch
 
 from areal_b200.utils.dcp_state import checkpoint_keys, flat_range_boxes, load_full_tensors
@@ -20,7 +22,7 @@ def _run(n, port, args):
         cmd = [sys.executable, WORKER] + args
     else:
         cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-               "--master-addr", "127.0.0.1", "--master-port", str(port), WORKER] + args
+               "--master-addr", "127.0.0.1", "--master-port", str(free_port()), WORKER] + args
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
     return [float(x) for x in r.stdout.strip().splitlines()[-1].split()[1:]]
@@ -80,14 +82,15 @@ def test_save_at_two_ranks_load_at_another_size(tmp_path, resume_ws):
 @pytest.mark.parametrize("flags,one,preset", [(["--tp", "2"], [], "tiny-qwen2"),
                                               (["--pp", "2", "--n-mbs", "2"], ["--n-mbs", "2"], "tiny-qwen2"),
                                               (["--ep", "2"], [], "tiny-qwen3-moe"),
-                                              (["--tp", "2", "--ep", "2"], [], "tiny-qwen3-moe")])
+                                              (["--tp", "2", "--ep", "2"], [], "tiny-qwen3-moe"),
+                                              (["--tp", "2", "--etp", "2"], [], "tiny-qwen3-moe")])
 def test_resume_under_model_parallelism_and_on_one_rank(tmp_path, flags, one, preset):
     """Two steps, checkpoint, third step on two ranks under tensor / pipeline / expert parallelism. Resuming from
     the checkpoint under the same layout gives the same third step (scheduler and, under expert parallelism,
     the expert optimizer's counters included); a single process reads the same checkpoint too."""
     d = str(tmp_path)
     common = ["--dir", d, "--preset", preset]
-    port = 29720 + 2 * len(flags) + (4 if preset != "tiny-qwen2" else 0) + (10 if "--tp" in flags and "--ep" in flags else 0)
+    port = 29720 + 2 * len(flags) + (4 if preset != "tiny-qwen2" else 0) + (10 if "--tp" in flags and "--ep" in flags else 0) + (20 if "--etp" in flags else 0)
     ref = _run(2, port, ["--phase", "train"] + common + flags)
     got = _run(2, port + 1, ["--phase", "resume"] + common + flags)
     _assert_same(_tensors(os.path.join(d, "ckpt")), _tensors(os.path.join(d, "reload")), exact=True)

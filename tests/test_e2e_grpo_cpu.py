@@ -7,6 +7,8 @@ import sys
 
 import pytest
 
+from tests.conftest import free_port
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
@@ -16,7 +18,7 @@ def _run(tmp_path, mode, nproc, port):
     env.pop("CUDA_VISIBLE_DEVICES", None)
     env["CUDA_VISIBLE_DEVICES"] = ""
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port),
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()),
            os.path.join(ROOT, "tests", "torchrun", "run_grpo_cfg1.py"), out, mode]
     r = subprocess.run(cmd, env=env, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0, r.stdout[-3000:] + r.stderr[-3000:]

@@ -7,6 +7,8 @@ import sys
 
 import pytest
 
+from tests.conftest import free_port
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "torchrun", "run_model_parallel.py")
 
@@ -23,7 +25,7 @@ def _ref(tmp_path, critic=False, n_mbs=1, preset="tiny-qwen2", images=False, ext
 
 def _run(n, port, args, ref):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-           "--master-addr", "127.0.0.1", "--master-port", str(port), WORKER] + args + [ref]
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()), WORKER] + args + [ref]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
@@ -59,22 +61,27 @@ def test_expert_parallel_step_matches_single_process(tmp_path, n, ep):
 
 @pytest.mark.parametrize("n,args", [(2, ["--tp", "2", "--ep", "2"]), (4, ["--tp", "2", "--ep", "2"]),
                                     (4, ["--tp", "2", "--ep", "4"]), (4, ["--tp", "2", "--pp", "2", "--ep", "2", "--n-mbs", "2"]),
-                                    (4, ["--pp", "2", "--ep", "2", "--n-mbs", "2"])])
+                                    (4, ["--pp", "2", "--ep", "2", "--n-mbs", "2"]),
+                                    (2, ["--tp", "2", "--etp", "2"]), (4, ["--tp", "2", "--ep", "2", "--etp", "2"]),
+                                    (4, ["--tp", "2", "--etp", "2"])])
 def test_hybrid_tensor_and_expert_parallel_step_matches_single_process(tmp_path, n, args):
     """Attention tensor-parallel, experts spread over the same ranks (the ``(attn:..t2|ffn:..e2)`` layout): the
     token slices that sequence-parallel activations leave on the tensor-parallel ranks are exchanged for experts;
     expert-parallel groups may also span several tensor-parallel groups, and pipeline stages (whose experts all
-    count in the clipping norm)."""
+    count in the clipping norm). ``--etp``: expert tensor parallelism, the ranks of a group hold slices of the same
+    experts, pool their tokens and sum their partial outputs."""
     n_mbs = 2 if "--n-mbs" in args else 1
     _run(n, 29742 + n + 3 * len(args), args + ["--preset", "tiny-qwen3-moe"],
          _ref(tmp_path, preset="tiny-qwen3-moe", n_mbs=n_mbs))
 
 
-@pytest.mark.parametrize("n,pp,ep,tp", [(2, 1, 2, 2), (4, 2, 2, 2), (4, 1, 4, 2)])
-def test_checkpoint_under_the_hybrid_layout(tmp_path, n, pp, ep, tp):
+@pytest.mark.parametrize("n,pp,ep,tp,etp", [(2, 1, 2, 2, 1), (4, 2, 2, 2, 1), (4, 1, 4, 2, 1), (2, 1, 1, 2, 2),
+                                            (4, 1, 2, 2, 2)])
+def test_checkpoint_under_the_hybrid_layout(tmp_path, n, pp, ep, tp, etp):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29760 + n + pp + 3 * ep), os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
-           "tiny-qwen3-moe", str(pp), str(tmp_path / "ckpt"), str(ep), str(tp)]
+           "127.0.0.1", "--master-port", str(free_port()),
+           os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
+           "tiny-qwen3-moe", str(pp), str(tmp_path / "ckpt"), str(ep), str(tp), str(etp)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
@@ -114,7 +121,7 @@ def test_vision_language_step_under_tensor_parallelism(tmp_path, n, preset, par)
                                             (2, 2, "tiny-qwen2", 1), (2, 1, "tiny-qwen3-moe", 2)])
 def test_checkpoint_under_tensor_pipeline_and_expert_parallelism(tmp_path, n, pp, preset, ep):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
-           "127.0.0.1", "--master-port", str(29699 + n + pp + 3 * ep), os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
+           "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
            preset, str(pp), str(tmp_path / "ckpt"), str(ep)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]

@@ -27,7 +27,8 @@ def _run(cmd):
                                                (["--pp", "2"], "tiny-qwen2", 2), (["--ep", "2"], "tiny-qwen3-moe", 1),
                                                (["--pp", "2", "--vpp", "2"], "tiny-qwen2-4l", 4),
                                                (["--pp", "2", "--schedule", "ZB1P"], "tiny-qwen2-4l", 4),
-                                               (["--tp", "2", "--ep", "2"], "tiny-qwen3-moe", 1)])
+                                               (["--tp", "2", "--ep", "2"], "tiny-qwen3-moe", 1),
+                                               (["--tp", "2", "--etp", "2"], "tiny-qwen3-moe", 1)])
 def test_two_gpu_step_matches_one_gpu(tmp_path, args, preset, n_mbs):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")

@@ -9,6 +9,8 @@ import sys
 import pytest
 import torch
 
+from tests.conftest import free_port
+
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 WORKER = os.path.join(ROOT, "tests", "torchrun", "run_weight_plan.py")
 
@@ -17,10 +19,12 @@ WORKER = os.path.join(ROOT, "tests", "torchrun", "run_weight_plan.py")
                                      (2, ["--pp", "2", "--vpp", "2"]), (2, ["--ep", "2", "--preset", "tiny-qwen3-moe"]),
                                      (4, ["--tp", "2", "--pp", "2"]),
                                      (2, ["--tp", "2", "--ep", "2", "--preset", "tiny-qwen3-moe"]),
-                                     (4, ["--tp", "2", "--ep", "4", "--preset", "tiny-qwen3-moe"])])
+                                     (4, ["--tp", "2", "--ep", "4", "--preset", "tiny-qwen3-moe"]),
+                                     (2, ["--tp", "2", "--etp", "2", "--preset", "tiny-qwen3-moe"]),
+                                     (4, ["--tp", "2", "--ep", "2", "--etp", "2", "--preset", "tiny-qwen3-moe"])])
 def test_plan_rebuilds_the_full_model_exactly_once(n, flags):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
-           "--master-addr", "127.0.0.1", "--master-port", str(29800 + 3 * n + 5 * len(flags) + len(flags[-1])), WORKER] + flags
+           "--master-addr", "127.0.0.1", "--master-port", str(free_port()), WORKER] + flags
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 

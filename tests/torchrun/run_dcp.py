@@ -42,6 +42,7 @@ def main():
     ap.add_argument("--sp", type=int, default=1)
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--etp", type=int, default=1)
     ap.add_argument("--preset", default="tiny-qwen2")
     ap.add_argument("--n-mbs", type=int, default=1)
     ap.add_argument("--async-save", action="store_true")
@@ -59,7 +60,8 @@ def main():
         dp = world // (args.tp * args.sp * args.pp)
         eng.create_process_group(ParallelStrategy(tensor_parallel_size=args.tp, context_parallel_size=args.sp,
                                                   pipeline_parallel_size=args.pp, data_parallel_size=dp,
-                                                  expert_parallel_size=args.ep))
+                                                  expert_parallel_size=args.ep,
+                                                  expert_tensor_parallel_size=args.etp))
     else:
         dp = 1
         eng.create_process_group()

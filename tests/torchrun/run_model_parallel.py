@@ -61,6 +61,7 @@ def main():
     ap.add_argument("--sp", type=int, default=1)
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--etp", type=int, default=1, help="expert tensor parallelism: ranks that hold slices of the same experts")
     ap.add_argument("--preset", default="tiny-qwen2")
     ap.add_argument("--device", default="cpu", choices=["cpu", "cuda"])
     ap.add_argument("--no-bias", action="store_true", help="Qwen3-style attention (no qkv bias): enables the fused Ulysses projection")
@@ -111,7 +112,8 @@ def main():
         dp = world // (args.tp * args.sp * args.pp)
         eng.create_process_group(ParallelStrategy(tensor_parallel_size=args.tp, context_parallel_size=args.sp,
                                                   pipeline_parallel_size=args.pp, data_parallel_size=dp,
-                                                  expert_parallel_size=args.ep))
+                                                  expert_parallel_size=args.ep,
+                                                  expert_tensor_parallel_size=args.etp))
         eng.initialize(seed=3)
         d = eng.data_parallel_rank
         data = {k: v[d::dp] for k, v in batch.items()}  # tensors and the per-sequence image list alike
@@ -140,12 +142,20 @@ def main():
     full = {}
     for name, g in captured.items():
         g = g.clone()
-        if pctx.ep_size > 1 and g.dim() == 3 and ".mlp." in name:
+        if pctx.ep_size * pctx.etp_size > 1 and g.dim() == 3 and ".mlp." in name:
             if mesh.edp_size > 1:
                 dist.all_reduce(g, group=mesh.edp_group)
-            parts = [torch.empty_like(g) for _ in range(pctx.ep_size)]
-            dist.all_gather(parts, g.contiguous(), group=pctx.ep_group)
-            full[name] = torch.cat(parts, 0)
+            if pctx.etp_size > 1:
+                from areal_b200.parallel.tensor_parallel import expert_unslice
+
+                parts = [torch.empty_like(g) for _ in range(pctx.etp_size)]
+                dist.all_gather(parts, g.contiguous(), group=pctx.etp_group)
+                g = expert_unslice(name, parts)
+            if pctx.ep_size > 1:
+                parts = [torch.empty_like(g) for _ in range(pctx.ep_size)]
+                dist.all_gather(parts, g.contiguous(), group=pctx.ep_group)
+                g = torch.cat(parts, 0)
+            full[name] = g
             continue
         if mesh.shard_size > 1:
             dist.all_reduce(g, group=mesh.shard_group)

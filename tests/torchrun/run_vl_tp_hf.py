@@ -17,15 +17,16 @@ from areal_b200.models.config import PRESETS  # noqa: E402
 from areal_b200.models.qwen import build_model  # noqa: E402
 
 
-def main(preset: str, pp: int = 1, out: str = "", ep: int = 1, tp: int = 0):
+def main(preset: str, pp: int = 1, out: str = "", ep: int = 1, tp: int = 0, etp: int = 1):
     dist.init_process_group("gloo")
     cfg = TrainEngineConfig(experiment_name="t", trial_name="t", path="", init_from_scratch=True, dtype="float32",
                             model_preset=preset, optimizer=OptimizerConfig(lr=1e-3))
     eng = B200TrainEngine(cfg)
-    if ep > 1 and tp > 1:  # hybrid: attention tensor-parallel, experts spread over the same ranks
+    if ep * etp > 1 and tp > 1:  # hybrid: attention tensor-parallel, experts spread / split over the same ranks
         world = dist.get_world_size()
         eng.create_process_group(ParallelStrategy(tensor_parallel_size=tp, pipeline_parallel_size=pp,
-                                                  data_parallel_size=world // (tp * pp), expert_parallel_size=ep))
+                                                  data_parallel_size=world // (tp * pp), expert_parallel_size=ep,
+                                                  expert_tensor_parallel_size=etp))
     elif ep > 1:  # expert parallelism lives inside the data-parallel ranks
         eng.create_process_group(ParallelStrategy(data_parallel_size=dist.get_world_size(), expert_parallel_size=ep))
     else:
@@ -56,10 +57,10 @@ def main(preset: str, pp: int = 1, out: str = "", ep: int = 1, tp: int = 0):
             loaded = load_hf_weights(build_model(PRESETS[preset], dtype=torch.float32, seed=9), out)
             for (n1, p1), (_, p2) in zip(ref.named_parameters(), loaded.named_parameters()):
                 assert torch.equal(p1, p2), n1
-            if pp > 1 or ep > 1:
+            if (pp > 1 or ep > 1) and etp == 1:
                 idx = json.load(open(os.path.join(out, "model.safetensors.index.json")))["weight_map"]
                 assert set(idx) == set(want) and len(set(idx.values())) == pp * ep
-        if ep > 1:
+        if ep * etp > 1:
             # and back into an expert-parallel model: every rank picks its own experts out of the directory
             other = build_model(PRESETS[preset], dtype=torch.float32, seed=9, pctx=eng.pctx)
             load_hf_weights(other, out)
@@ -73,4 +74,5 @@ def main(preset: str, pp: int = 1, out: str = "", ep: int = 1, tp: int = 0):
 
 if __name__ == "__main__":
     main(sys.argv[1], int(sys.argv[2]) if len(sys.argv) > 2 else 1, sys.argv[3] if len(sys.argv) > 3 else "",
-         int(sys.argv[4]) if len(sys.argv) > 4 else 1, int(sys.argv[5]) if len(sys.argv) > 5 else 0)
+         int(sys.argv[4]) if len(sys.argv) > 4 else 1, int(sys.argv[5]) if len(sys.argv) > 5 else 0,
+         int(sys.argv[6]) if len(sys.argv) > 6 else 1)

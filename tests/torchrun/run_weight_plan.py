@@ -24,6 +24,7 @@ def main():
     ap.add_argument("--tp", type=int, default=1)
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--etp", type=int, default=1)
     ap.add_argument("--vpp", type=int, default=1)
     ap.add_argument("--preset", default="tiny-qwen2-4l")
     args = ap.parse_args()
@@ -35,7 +36,8 @@ def main():
     eng = B200TrainEngine(cfg)
     dp = world // (args.tp * args.pp)
     eng.create_process_group(ParallelStrategy(tensor_parallel_size=args.tp, pipeline_parallel_size=args.pp,
-                                              data_parallel_size=dp, expert_parallel_size=args.ep))
+                                              data_parallel_size=dp, expert_parallel_size=args.ep,
+                                              expert_tensor_parallel_size=args.etp))
     eng.initialize(seed=3)
     # what the rollout engine holds: the whole model in one flat buffer
     full = build_model(PRESETS[args.preset], dtype=torch.float32, device="cpu", seed=3)
