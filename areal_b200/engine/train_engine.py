@@ -313,8 +313,7 @@ class B200TrainEngine(TrainEngine):
             # `self.flat` — the buffer the optimizer shards — holds the adapters only
             from ..models.lora import is_lora_param
 
-            assert tp == 1 and ep == 1 and (pctx is None or pctx.pp_size == 1), \
-                "LoRA training runs under data / sequence parallelism only"
+            assert tp == 1 and ep == 1, "LoRA training runs under data / sequence / pipeline parallelism"
             for n, p_ in self.model.named_parameters():
                 if not is_lora_param(n):
                     p_.requires_grad_(False)
@@ -356,7 +355,8 @@ class B200TrainEngine(TrainEngine):
                 if self.optimizer.partner is not None:
                     # the experts of other pipeline stages count in the global gradient norm as well
                     self.optimizer.partner.norm_groups.append(pctx.pp_group)
-                if self.model_config.tie_word_embeddings and not self.is_critic and self.model.embed is not None:
+                if self.model_config.tie_word_embeddings and not self.is_critic and self.model.embed is not None \
+                        and self.model.embed.requires_grad:  # (frozen under LoRA: nothing to sum)
                     self.optimizer.pre_step_hooks.append(self._sum_tied_embedding_grads)
                     if not self.model.first_stage:
                         # both copies apply the summed gradient; the first stage's copy counts in the norm
@@ -907,7 +907,8 @@ class B200TrainEngine(TrainEngine):
                 if self.flat_base is not None:
                     from ..models.lora import save_adapter
 
-                    save_adapter(self.model, self.model_config, meta.path, base_model_path=self.config.path or "")
+                    save_adapter(self.model, self.model_config, meta.path, base_model_path=self.config.path or "",
+                                 gather_group=pctx.pp_group if pp > 1 else None)
         elif meta.weight_format == "dcp":
             # torch.distributed.checkpoint: named tensors, every rank writes the part of its own flat shard
             from ..utils.dcp_state import save_engine

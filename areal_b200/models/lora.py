@@ -169,15 +169,25 @@ def merged(model):
                 w.copy_(old)
 
 
-def save_adapter(model, cfg, path: str, base_model_path: str = ""):
-    """Writes ``adapter_model.safetensors`` + ``adapter_config.json`` (the layout PEFT reads)."""
+def save_adapter(model, cfg, path: str, base_model_path: str = "", gather_group=None):
+    """Writes ``adapter_model.safetensors`` + ``adapter_config.json`` (the layout PEFT reads). Under pipeline
+    parallelism the stages hold different layers' adapters: ``gather_group`` (the pipeline group; collective) brings
+    them to its first rank, which writes the one file."""
     from safetensors.torch import save_file
 
-    os.makedirs(path, exist_ok=True)
     tensors = {}
     for prefix, _, ad in iter_adapters(model):
         for n, t in ad.peft_tensors(prefix):
             tensors[n] = t.detach().to("cpu").contiguous().clone()
+    if gather_group is not None:
+        import torch.distributed as dist
+
+        parts = [None] * dist.get_world_size(gather_group)
+        dist.all_gather_object(parts, tensors, group=gather_group)
+        if dist.get_rank(gather_group) != 0:
+            return
+        tensors = {k: v for part in parts for k, v in part.items()}
+    os.makedirs(path, exist_ok=True)
     save_file(tensors, os.path.join(path, "adapter_model.safetensors"), metadata={"format": "pt"})
     conf = {"peft_type": "LORA", "task_type": "CAUSAL_LM", "r": cfg.lora_rank, "lora_alpha": cfg.lora_alpha,
             "target_modules": list(normalize_targets(cfg.lora_targets)), "lora_dropout": 0.0, "bias": "none",

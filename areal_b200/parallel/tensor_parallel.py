@@ -244,6 +244,13 @@ def tp_unslice(name: str, shards: list[torch.Tensor], cfg) -> torch.Tensor:
     return shards[0]
 
 
+def tp_slice_lora_b(name: str) -> bool:
+    """Whether the ``lora_B`` factor with this parameter name is split over the tensor-parallel group (the adapters
+    of column-parallel projections: B follows the output rows; those of row-parallel projections keep B whole and
+    split A along the input)."""
+    return ".lora_qkv." in name or ".lora_gate_up." in name
+
+
 def expert_slice(name: str, full: torch.Tensor, rank: int, size: int) -> torch.Tensor:
     """Slice ``rank`` of ``size`` of stacked expert weights along the expert width: ``gate_up [E, 2I, H]`` keeps
     rows ``[rank * I/size, (rank + 1) * I/size)`` of the gate half and of the up half, ``down [E, H, I]`` the

@@ -180,6 +180,10 @@ class EngineDCPState(Stateful):
 
                     if not is_tp_replicated(pname):
                         raise NotImplementedError(f"parameter {pname} has no checkpoint name under tensor parallelism")
+                if pname.startswith("layers.") and hasattr(model, "layer_ids"):
+                    # a pipeline stage numbers its blocks from 0: the checkpoint name carries the global index
+                    _, idx, rest = pname.split(".", 2)
+                    pname = f"layers.{model.layer_ids[int(idx)]}.{rest}"
                 yield "_native." + pname, f, o, tuple(p.shape), None
 
     def _handle(self, f, off: int, shape: tuple[int, ...], tp_dim: int | None, buf: torch.Tensor, buf_start: int,

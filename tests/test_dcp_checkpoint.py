@@ -83,7 +83,8 @@ def test_save_at_two_ranks_load_at_another_size(tmp_path, resume_ws):
                                               (["--pp", "2", "--n-mbs", "2"], ["--n-mbs", "2"], "tiny-qwen2"),
                                               (["--ep", "2"], [], "tiny-qwen3-moe"),
                                               (["--tp", "2", "--ep", "2"], [], "tiny-qwen3-moe"),
-                                              (["--tp", "2", "--etp", "2"], [], "tiny-qwen3-moe")])
+                                              (["--tp", "2", "--etp", "2"], [], "tiny-qwen3-moe"),
+                                              (["--pp", "2", "--n-mbs", "2", "--lora"], ["--n-mbs", "2", "--lora"], "tiny-qwen2-4l")])
 def test_resume_under_model_parallelism_and_on_one_rank(tmp_path, flags, one, preset):
     """Two steps, checkpoint, third step on two ranks under tensor / pipeline / expert parallelism. Resuming from
     the checkpoint under the same layout gives the same third step (scheduler and, under expert parallelism,

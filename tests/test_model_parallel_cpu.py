@@ -86,6 +86,14 @@ def test_checkpoint_under_the_hybrid_layout(tmp_path, n, pp, ep, tp, etp):
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
 
+@pytest.mark.parametrize("n,args", [(2, ["--pp", "2"]), (4, ["--pp", "2"])])
+def test_lora_step_under_model_parallelism_matches_single_process(tmp_path, n, args):
+    """Adapters on every dense projection, base frozen: the adapter gradients (both factors; B is given non-zero
+    values that depend only on the parameter's global name), the loss and the clipping norm over all stages."""
+    _run(n, 0, args + ["--lora", "--n-mbs", "2", "--preset", "tiny-qwen2-4l"],
+         _ref(tmp_path, preset="tiny-qwen2-4l", n_mbs=2, extra=["--lora"]))
+
+
 def test_mixture_layers_under_tensor_parallelism_need_expert_parallelism():
     from areal_b200.models.config import PRESETS
     from areal_b200.models.qwen import build_model

@@ -43,6 +43,7 @@ def main():
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--ep", type=int, default=1)
     ap.add_argument("--etp", type=int, default=1)
+    ap.add_argument("--lora", action="store_true")
     ap.add_argument("--preset", default="tiny-qwen2")
     ap.add_argument("--n-mbs", type=int, default=1)
     ap.add_argument("--async-save", action="store_true")
@@ -52,6 +53,8 @@ def main():
                             model_preset=args.preset, mb_spec=MicroBatchSpec(n_mbs=args.n_mbs),
                             optimizer=OptimizerConfig(lr=2e-3, weight_decay=0.01, gradient_clipping=1.0,
                                                       warmup_steps_proportion=0.5, lr_scheduler_type="cosine"))
+    if args.lora:
+        cfg.use_lora, cfg.lora_rank, cfg.lora_alpha, cfg.target_modules = True, 4, 8, ["q_proj", "v_proj", "down_proj"]
     eng = B200TrainEngine(cfg)
     multi = "RANK" in os.environ
     if multi:

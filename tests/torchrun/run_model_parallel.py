@@ -53,6 +53,33 @@ def weight_fn(mb):
     return float(mb["loss_mask"].sum())
 
 
+def perturb_lora_b(eng):
+    """Adapters start with B = 0 (the adapted model equals the base model), which leaves A without a gradient:
+    give B values that depend only on the parameter's global name, so that every layout sees the same adapter."""
+    import zlib
+
+    from areal_b200.parallel.tensor_parallel import tp_slice_lora_b
+
+    pctx = eng.pctx
+    with torch.no_grad():
+        for name, p in eng.model.named_parameters():
+            if ".lora_B." not in name:
+                continue
+            gname = name
+            if name.startswith("layers."):
+                _, idx, rest = name.split(".", 2)
+                gname = f"layers.{eng.model.layer_ids[int(idx)]}.{rest}"
+            tp = pctx.tp_size if pctx is not None else 1
+            g = torch.Generator().manual_seed(zlib.crc32(gname.encode()))
+            full_rows = p.shape[0] * (tp if tp_slice_lora_b(gname) else 1)
+            full = torch.randn(full_rows, p.shape[1], generator=g) * 0.05
+            full[:, eng.model_config.lora_rank:] = 0  # the rank padding stays zero
+            if tp > 1 and tp_slice_lora_b(gname):
+                n = p.shape[0]
+                full = full[pctx.tp_rank * n:(pctx.tp_rank + 1) * n]
+            p.copy_(full.to(p.dtype))
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("file")
@@ -61,6 +88,7 @@ def main():
     ap.add_argument("--sp", type=int, default=1)
     ap.add_argument("--pp", type=int, default=1)
     ap.add_argument("--ep", type=int, default=1)
+    ap.add_argument("--lora", action="store_true", help="low-rank adapters on every dense projection, base frozen")
     ap.add_argument("--etp", type=int, default=1, help="expert tensor parallelism: ranks that hold slices of the same experts")
     ap.add_argument("--preset", default="tiny-qwen2")
     ap.add_argument("--device", default="cpu", choices=["cpu", "cuda"])
@@ -91,6 +119,8 @@ def main():
                             model_preset=args.preset, mb_spec=MicroBatchSpec(n_mbs=args.n_mbs), is_critic=args.critic,
                             optimizer=OptimizerConfig(lr=1e-3, weight_decay=0.0, gradient_clipping=1.0,
                                                       warmup_steps_proportion=0.0, lr_scheduler_type="constant"))
+    if args.lora:
+        cfg.use_lora, cfg.lora_rank, cfg.lora_alpha, cfg.target_modules = True, 8, 16, ["all-linear"]
     if args.zigzag:
         cfg.backend = "megatron:d1"
     cfg.megatron.virtual_pipeline_parallel_size = args.vpp
@@ -117,6 +147,8 @@ def main():
         eng.initialize(seed=3)
         d = eng.data_parallel_rank
         data = {k: v[d::dp] for k, v in batch.items()}  # tensors and the per-sequence image list alike
+    if args.lora:
+        perturb_lora_b(eng)
     captured = {}
     orig_step = eng.optimizer.step
 
