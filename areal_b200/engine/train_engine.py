@@ -313,14 +313,14 @@ class B200TrainEngine(TrainEngine):
             # `self.flat` — the buffer the optimizer shards — holds the adapters only
             from ..models.lora import is_lora_param
 
-            assert tp == 1 and ep == 1, "LoRA training runs under data / sequence / pipeline parallelism"
+            assert ep == 1, "LoRA training does not combine with expert parallelism"
             for n, p_ in self.model.named_parameters():
                 if not is_lora_param(n):
                     p_.requires_grad_(False)
-            self.flat_base = FlatParams(self.model, self._dp_group, with_grads=False,
+            self.flat_base = FlatParams(self.model, self._dp_group, with_grads=False, replicated_first=rep_first,
                                         select=lambda n: not is_lora_param(n))
             self.flat = FlatParams(self.model, self._dp_group, with_grads=self.optimizer_config is not None,
-                                   select=is_lora_param)
+                                   replicated_first=rep_first, select=is_lora_param)
         else:
             self.flat = FlatParams(self.model, self._dp_group, with_grads=self.optimizer_config is not None,
                                    replicated_first=rep_first,
@@ -908,7 +908,7 @@ class B200TrainEngine(TrainEngine):
                     from ..models.lora import save_adapter
 
                     save_adapter(self.model, self.model_config, meta.path, base_model_path=self.config.path or "",
-                                 gather_group=pctx.pp_group if pp > 1 else None)
+                                 gather_group=pctx.pp_group if pp > 1 else None, write=writer)
         elif meta.weight_format == "dcp":
             # torch.distributed.checkpoint: named tensors, every rank writes the part of its own flat shard
             from ..utils.dcp_state import save_engine

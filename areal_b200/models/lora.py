@@ -58,8 +58,15 @@ class LoRAAdapter(nn.Module):
     ``targeted``: the module names that get an adapter (the others contribute zeros)."""
 
     def __init__(self, in_features: int, blocks: Sequence[tuple[str, int]], targeted: Sequence[str],
-                 rank: int, alpha: float, dtype, device, seed: int = 0):
+                 rank: int, alpha: float, dtype, device, seed: int = 0, tp_mode: str | None = None, pctx=None):
+        """``tp_mode`` (tensor parallelism; ``in_features`` and the block sizes are then the LOCAL ones):
+        ``"column"``: the fused weight is split by output rows, the input arrives as this rank's token slice.
+        ``A`` is replicated, every ``B`` holds this rank's rows; the tokens are gathered first.
+        ``"row"``: the fused weight is split along its input, the output leaves as this rank's token slice.
+        ``A`` holds this rank's input columns, ``B`` is replicated; the rank-sized partial products are summed
+        and scattered by token before ``B`` is applied."""
         super().__init__()
+        self.tp_mode, self.pctx = tp_mode, pctx
         self.in_features = in_features
         self.blocks = list(blocks)
         self.names = [n for n, _ in self.blocks if n in targeted]
@@ -74,22 +81,34 @@ class LoRAAdapter(nn.Module):
         # A: uniform(-1/sqrt(in), 1/sqrt(in)) (kaiming with a=sqrt(5), the PEFT default); B: zeros, so
         # the adapted model starts equal to the base model
         g = torch.Generator(device="cpu").manual_seed(seed)
-        bound = 1.0 / math.sqrt(in_features)
+        tp = pctx.tp_size if (pctx is not None and tp_mode == "row") else 1
+        full_in = in_features * tp  # a row-parallel adapter draws the whole A and keeps its columns
+        bound = 1.0 / math.sqrt(full_in)
         with torch.no_grad():
             for i in range(k):
-                a = (torch.rand(rank, in_features, generator=g) * 2 - 1) * bound
+                a = (torch.rand(rank, full_in, generator=g) * 2 - 1) * bound
+                if tp > 1:
+                    a = a[:, pctx.tp_rank * in_features:(pctx.tp_rank + 1) * in_features]
                 self.lora_A[i * self.rp: i * self.rp + rank].copy_(a.to(dtype))
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         """Delta of the fused projection's output, ``[T, sum(outs)]``."""
+        if self.tp_mode == "column":
+            from ..parallel.tensor_parallel import gather_seq
+
+            x = gather_seq(x, self.pctx.tp_fused)
         u = linear(x, self.lora_A)
+        if self.tp_mode == "row":
+            from ..parallel.tensor_parallel import scatter_seq_sum
+
+            u = scatter_seq_sum(u, self.pctx.tp_fused)
         parts, i = [], 0
         for n, o in self.blocks:
             if n in self.lora_B:
                 parts.append(linear(u[:, i * self.rp:(i + 1) * self.rp], self.lora_B[n]))
                 i += 1
             else:
-                parts.append(x.new_zeros(x.shape[0], o))
+                parts.append(u.new_zeros(u.shape[0], o))
         d = parts[0] if len(parts) == 1 else torch.cat(parts, dim=-1)
         return d * self.scale
 
@@ -106,29 +125,56 @@ class LoRAAdapter(nn.Module):
                 rows.append(torch.zeros(o, self.in_features, dtype=torch.float32, device=self.lora_A.device))
         return rows[0] if len(rows) == 1 else torch.cat(rows, 0)
 
+    def _tp(self) -> tuple[int, int, object]:
+        p = self.pctx
+        return (p.tp_size, p.tp_rank, p.tp_group) if (p is not None and self.tp_mode and p.tp_size > 1) else (1, 0, None)
+
     def peft_tensors(self, prefix: str) -> Iterator[tuple[str, torch.Tensor]]:
-        """``(name, tensor)`` in the adapter-checkpoint naming, padding removed."""
+        """``(name, tensor)`` in the adapter-checkpoint naming, padding removed; under tensor parallelism the
+        full factors (a collective over the tensor-parallel group: every rank of it must iterate)."""
+        tp, _, group = self._tp()
+
+        def full(t, dim):
+            if tp == 1:
+                return t
+            import torch.distributed as dist
+
+            parts = [torch.empty_like(t) for _ in range(tp)]
+            dist.all_gather(parts, t.contiguous(), group=group)
+            return torch.cat(parts, dim)
+
         for i, n in enumerate(self.names):
-            yield f"{prefix}{n}.lora_A.weight", self.lora_A[i * self.rp: i * self.rp + self.rank]
-            yield f"{prefix}{n}.lora_B.weight", self.lora_B[n][:, :self.rank]
+            a, b = self.lora_A[i * self.rp: i * self.rp + self.rank], self.lora_B[n][:, :self.rank]
+            yield f"{prefix}{n}.lora_A.weight", (full(a, 1) if self.tp_mode == "row" else a)
+            yield f"{prefix}{n}.lora_B.weight", (full(b, 0) if self.tp_mode == "column" else b)
 
     @torch.no_grad()
     def load_peft(self, tensors: dict[str, torch.Tensor], prefix: str):
+        tp, r, _ = self._tp()
         for i, n in enumerate(self.names):
             a, b = tensors[f"{prefix}{n}.lora_A.weight"], tensors[f"{prefix}{n}.lora_B.weight"]
+            if tp > 1 and self.tp_mode == "row":
+                a = a[:, r * self.in_features:(r + 1) * self.in_features]
+            if tp > 1 and self.tp_mode == "column":
+                rows = self.lora_B[n].shape[0]
+                b = b[r * rows:(r + 1) * rows]
             assert a.shape == (self.rank, self.in_features) and b.shape[1] == self.rank
             self.lora_A[i * self.rp: i * self.rp + self.rank].copy_(a)
             self.lora_B[n][:, :self.rank].copy_(b)
 
 
-def make_adapter(cfg, in_features, blocks, dtype, device, seed) -> LoRAAdapter | None:
+def make_adapter(cfg, in_features, blocks, dtype, device, seed, tp_mode: str | None = None,
+                 pctx=None) -> LoRAAdapter | None:
     """Adapter for a fused weight, or ``None`` when LoRA is off or no sub-block is targeted."""
     if not getattr(cfg, "lora_rank", 0):
         return None
     targets = normalize_targets(cfg.lora_targets)
     if not any(n in targets for n, _ in blocks):
         return None
-    return LoRAAdapter(in_features, blocks, targets, cfg.lora_rank, cfg.lora_alpha, dtype, device, seed)
+    if pctx is None or pctx.tp_size == 1:
+        tp_mode = None
+    return LoRAAdapter(in_features, blocks, targets, cfg.lora_rank, cfg.lora_alpha, dtype, device, seed,
+                       tp_mode=tp_mode, pctx=pctx if tp_mode else None)
 
 
 def is_lora_param(name: str) -> bool:
@@ -169,7 +215,7 @@ def merged(model):
                 w.copy_(old)
 
 
-def save_adapter(model, cfg, path: str, base_model_path: str = "", gather_group=None):
+def save_adapter(model, cfg, path: str, base_model_path: str = "", gather_group=None, write: bool = True):
     """Writes ``adapter_model.safetensors`` + ``adapter_config.json`` (the layout PEFT reads). Under pipeline
     parallelism the stages hold different layers' adapters: ``gather_group`` (the pipeline group; collective) brings
     them to its first rank, which writes the one file."""
@@ -179,6 +225,8 @@ def save_adapter(model, cfg, path: str, base_model_path: str = "", gather_group=
     for prefix, _, ad in iter_adapters(model):
         for n, t in ad.peft_tensors(prefix):
             tensors[n] = t.detach().to("cpu").contiguous().clone()
+    if not write:
+        return  # a tensor-parallel peer: it only took part in the gathers above
     if gather_group is not None:
         import torch.distributed as dist
 

@@ -63,8 +63,9 @@ class Attention(nn.Module):
         from .lora import make_adapter
 
         self.lora_qkv = make_adapter(cfg, h, [("q_proj", qs), ("k_proj", ks), ("v_proj", ks)], dtype, device,
-                                     seed=2 * layer_idx + 1000)
-        self.lora_o = make_adapter(cfg, qs, [("o_proj", h)], dtype, device, seed=2 * layer_idx + 1001)
+                                     seed=2 * layer_idx + 1000, tp_mode="column", pctx=pctx)
+        self.lora_o = make_adapter(cfg, qs, [("o_proj", h)], dtype, device, seed=2 * layer_idx + 1001,
+                                   tp_mode="row", pctx=pctx)
 
     def _tp(self):
         p = self.pctx
@@ -143,7 +144,8 @@ class Attention(nn.Module):
         if tp is not None:
             from ..parallel.tensor_parallel import row_parallel_linear
 
-            return row_parallel_linear(a, self.o, tp)
+            y = row_parallel_linear(a, self.o, tp)
+            return y if self.lora_o is None else y + self.lora_o(a)
         y = _dense(a, self.o, None, self.cfg)
         return y if self.lora_o is None else y + self.lora_o(a)
 
@@ -160,17 +162,21 @@ class DenseMLP(nn.Module):
         from .lora import make_adapter
 
         self.lora_gate_up = make_adapter(cfg, hidden, [("gate_proj", inter // tp), ("up_proj", inter // tp)],
-                                         dtype, device, seed=2 * layer_idx + 2000)
+                                         dtype, device, seed=2 * layer_idx + 2000, tp_mode="column", pctx=pctx)
         self.lora_down = make_adapter(cfg, inter // tp, [("down_proj", hidden)], dtype, device,
-                                      seed=2 * layer_idx + 2001)
+                                      seed=2 * layer_idx + 2001, tp_mode="row", pctx=pctx)
 
     def forward(self, x):
         p = self.pctx
         if p is not None and p.tp_size > 1:
             from ..parallel.tensor_parallel import column_parallel_linear, row_parallel_linear
 
-            return row_parallel_linear(fused.swiglu(column_parallel_linear(x, self.gate_up, p.tp_fused)),
-                                       self.down, p.tp_fused)
+            gu = column_parallel_linear(x, self.gate_up, p.tp_fused)
+            if self.lora_gate_up is not None:
+                gu = gu + self.lora_gate_up(x)
+            a = fused.swiglu(gu)
+            y = row_parallel_linear(a, self.down, p.tp_fused)
+            return y if self.lora_down is None else y + self.lora_down(a)
         dense = (lambda t, w: _dense(t, w, None, self.cfg)) if (self.cfg is not None and self.cfg.fp8) else linear
         gu = dense(x, self.gate_up)
         if self.lora_gate_up is not None:

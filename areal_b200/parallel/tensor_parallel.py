@@ -231,6 +231,9 @@ def tp_unslice(name: str, shards: list[torch.Tensor], cfg) -> torch.Tensor:
     size = len(shards)
     if size == 1:
         return shards[0]
+    if ".lora_" in name:
+        d = lora_tp_dim(name)
+        return shards[0] if d is None else torch.cat(shards, d)
     if name.endswith(("embed", "lm_head")):
         return torch.cat(shards, 0)
     if name.endswith(("attn.qkv", "attn.qkv_bias")):
@@ -271,5 +274,17 @@ def expert_unslice(name: str, shards: list[torch.Tensor]) -> torch.Tensor:
     return torch.cat(shards, 2)
 
 
+def lora_tp_dim(name: str) -> int | None:
+    """Dimension along which a low-rank adapter factor is split over the tensor-parallel group: ``B`` of a
+    column-parallel projection by rows, ``A`` of a row-parallel projection by columns; ``None``: replicated."""
+    if (".lora_qkv." in name or ".lora_gate_up." in name) and ".lora_B." in name:
+        return 0
+    if (".lora_o." in name or ".lora_down." in name) and name.endswith("lora_A"):
+        return 1
+    return None
+
+
 def is_tp_replicated(name: str) -> bool:
+    if ".lora_" in name:
+        return lora_tp_dim(name) is None
     return not name.endswith(("embed", "lm_head", "attn.qkv", "attn.qkv_bias", "attn.o", "mlp.gate_up", "mlp.down"))

@@ -175,16 +175,21 @@ class EngineDCPState(Stateful):
                 got = sum(min(b, o + n) - max(a, o) for a, b in spans if a < o + n and b > o)
                 if got >= n:
                     continue
+                spec = None
                 if tp > 1:
-                    from ..parallel.tensor_parallel import is_tp_replicated
+                    from ..parallel.tensor_parallel import is_tp_replicated, lora_tp_dim
 
                     if not is_tp_replicated(pname):
-                        raise NotImplementedError(f"parameter {pname} has no checkpoint name under tensor parallelism")
+                        d = lora_tp_dim(pname) if ".lora_" in pname else None
+                        if d is None:
+                            raise NotImplementedError(
+                                f"parameter {pname} has no checkpoint name under tensor parallelism")
+                        spec = (d, e.pctx.tp_rank, tp)  # a low-rank adapter factor split over the tp group
                 if pname.startswith("layers.") and hasattr(model, "layer_ids"):
                     # a pipeline stage numbers its blocks from 0: the checkpoint name carries the global index
                     _, idx, rest = pname.split(".", 2)
                     pname = f"layers.{model.layer_ids[int(idx)]}.{rest}"
-                yield "_native." + pname, f, o, tuple(p.shape), None
+                yield "_native." + pname, f, o, tuple(p.shape), spec
 
     def _handle(self, f, off: int, shape: tuple[int, ...], tp_dim: int | None, buf: torch.Tensor, buf_start: int,
                 write: bool) -> ShardedView | None:

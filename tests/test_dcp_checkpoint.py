@@ -84,7 +84,8 @@ def test_save_at_two_ranks_load_at_another_size(tmp_path, resume_ws):
                                               (["--ep", "2"], [], "tiny-qwen3-moe"),
                                               (["--tp", "2", "--ep", "2"], [], "tiny-qwen3-moe"),
                                               (["--tp", "2", "--etp", "2"], [], "tiny-qwen3-moe"),
-                                              (["--pp", "2", "--n-mbs", "2", "--lora"], ["--n-mbs", "2", "--lora"], "tiny-qwen2-4l")])
+                                              (["--pp", "2", "--n-mbs", "2", "--lora"], ["--n-mbs", "2", "--lora"], "tiny-qwen2-4l"),
+                                              (["--tp", "2", "--lora"], ["--lora"], "tiny-qwen2-4l")])
 def test_resume_under_model_parallelism_and_on_one_rank(tmp_path, flags, one, preset):
     """Two steps, checkpoint, third step on two ranks under tensor / pipeline / expert parallelism. Resuming from
     the checkpoint under the same layout gives the same third step (scheduler and, under expert parallelism,
@@ -197,3 +198,31 @@ def test_recover_handler_round_trip_through_dcp(tmp_path):
     sa = a.train_batch(batch_of(1), loss_fn, lambda mb: float(mb["loss_mask"].sum()))
     sb = b.train_batch(batch_of(1), loss_fn, lambda mb: float(mb["loss_mask"].sum()))
     assert sa["loss"] == sb["loss"] and torch.equal(a.flat.flat, b.flat.flat)
+
+
+@pytest.mark.parametrize("n,flags", [(2, ["--tp", "2"]), (4, ["--tp", "2", "--pp", "2"])])
+def test_lora_adapter_file_is_the_same_under_model_parallelism(tmp_path, n, flags):
+    """Two training steps with adapters under tensor (and pipeline) parallelism write the PEFT adapter file and the
+    merged model that one process writes: factors split over tensor-parallel ranks are gathered, the stages'
+    adapters end up in one file."""
+    from safetensors.torch import load_file
+
+    from areal_b200.utils.hf_io import iter_hf_tensors
+
+    one, par = str(tmp_path / "one"), str(tmp_path / "par")
+    common = ["--phase", "train", "--format", "hf", "--lora", "--preset", "tiny-qwen2-4l", "--n-mbs", "2"]
+    _run(1, 0, common + ["--dir", one])
+    _run(n, 0, common + ["--dir", par] + flags)
+    a = load_file(os.path.join(one, "ckpt", "adapter_model.safetensors"))
+    b = load_file(os.path.join(par, "ckpt", "adapter_model.safetensors"))
+    assert set(a) == set(b) and len(a) == 6 * 3 * 2          # 6 layers x (q, v, down) x (A, B)
+    for k in a:
+        assert a[k].shape == b[k].shape, k
+        # A's first gradients are products with B = 0 plus rounding: Adam turns that noise into steps of up to
+        # lr = 2e-3 per element in either direction, so A may differ by a few 1e-5 between layouts
+        assert (a[k].double() - b[k].double()).abs().max() <= 1e-3 * a[k].abs().max() + 5e-5, k
+    assert any(v.abs().max() > 0 for k, v in a.items() if "lora_B" in k)   # the adapters did train
+    wa, wb = dict(iter_hf_tensors(os.path.join(one, "ckpt"))), dict(iter_hf_tensors(os.path.join(par, "ckpt")))
+    assert set(wa) == set(wb)
+    for k in wa:
+        assert (wa[k].double() - wb[k].double()).abs().max() <= 1e-3 * wa[k].abs().max() + 5e-5, k

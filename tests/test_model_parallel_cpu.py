@@ -86,10 +86,13 @@ def test_checkpoint_under_the_hybrid_layout(tmp_path, n, pp, ep, tp, etp):
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
 
-@pytest.mark.parametrize("n,args", [(2, ["--pp", "2"]), (4, ["--pp", "2"])])
+@pytest.mark.parametrize("n,args", [(2, ["--pp", "2"]), (4, ["--pp", "2"]), (2, ["--tp", "2"]),
+                                    (4, ["--tp", "2", "--pp", "2"]), (4, ["--tp", "2"])])
 def test_lora_step_under_model_parallelism_matches_single_process(tmp_path, n, args):
     """Adapters on every dense projection, base frozen: the adapter gradients (both factors; B is given non-zero
-    values that depend only on the parameter's global name), the loss and the clipping norm over all stages."""
+    values that depend only on the parameter's global name), the loss and the clipping norm over all stages. Under
+    tensor parallelism the adapter of a column-parallel projection gathers the token slices and keeps B by rows, that
+    of a row-parallel projection keeps A by columns and sums / scatters the rank-sized partial products."""
     _run(n, 0, args + ["--lora", "--n-mbs", "2", "--preset", "tiny-qwen2-4l"],
          _ref(tmp_path, preset="tiny-qwen2-4l", n_mbs=2, extra=["--lora"]))
 

@@ -28,13 +28,15 @@ def _run(cmd):
                                                (["--pp", "2", "--vpp", "2"], "tiny-qwen2-4l", 4),
                                                (["--pp", "2", "--schedule", "ZB1P"], "tiny-qwen2-4l", 4),
                                                (["--tp", "2", "--ep", "2"], "tiny-qwen3-moe", 1),
-                                               (["--tp", "2", "--etp", "2"], "tiny-qwen3-moe", 1)])
+                                               (["--tp", "2", "--etp", "2"], "tiny-qwen3-moe", 1),
+                                               (["--tp", "2", "--lora"], "tiny-qwen2-4l", 1)])
 def test_two_gpu_step_matches_one_gpu(tmp_path, args, preset, n_mbs):
     if torch.cuda.device_count() < 2:
         pytest.skip("needs 2 GPUs")
     ref = str(tmp_path / "ref.pt")
-    common = ["--device", "cuda", "--preset", preset, "--n-mbs", str(n_mbs)] + (["--no-bias"] if "--no-bias" in args else [])
-    args = [a for a in args if a != "--no-bias"]
+    shared = [a for a in args if a in ("--no-bias", "--lora")]   # flags that the single-GPU reference run takes too
+    common = ["--device", "cuda", "--preset", preset, "--n-mbs", str(n_mbs)] + shared
+    args = [a for a in args if a not in shared]
     env_free = [sys.executable, WORKER, "--ref"] + common + [ref]
     clean = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
     r = subprocess.run(env_free, env=clean, capture_output=True, text=True, timeout=300)
