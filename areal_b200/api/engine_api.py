@@ -126,15 +126,97 @@ class TrainEngine(abc.ABC):
         pass
 
     def config_perf_tracer(self, config, rank: int, role: str):
-        pass
+        from ..utils import perf_tracer
+
+        perf_tracer.configure(config, rank=rank, role=role)
 
     def save_perf_tracer(self, step: int | None = None, force: bool = False):
-        pass
+        from ..utils import perf_tracer
+
+        perf_tracer.save(step=step, force=force)
+
+    @property
+    def initialized(self) -> bool:
+        """True once ``initialize()`` has completed."""
+        return bool(getattr(self, "_initialized", False))
+
+    def get_device_stats(self):
+        from .io_struct import DeviceRuntimeInfo
+
+        return DeviceRuntimeInfo.get_current()
+
+    def start_memory_profile(self, max_entries: int = 100000) -> None:
+        """Starts recording allocator events of this process's device (no-op without CUDA)."""
+        import torch
+
+        if torch.cuda.is_available():
+            torch.cuda.memory._record_memory_history(max_entries=max_entries)
+
+    def stop_memory_profile(self, snapshot_dir: str) -> None:
+        """Dumps the recorded allocator history as ``snapshot_dir/memory_rank{r}.pickle`` and stops recording."""
+        import os
+
+        import torch
+
+        if not torch.cuda.is_available():
+            return
+        os.makedirs(snapshot_dir, exist_ok=True)
+        rank = int(os.environ.get("RANK", 0))
+        torch.cuda.memory._dump_snapshot(os.path.join(snapshot_dir, f"memory_rank{rank}.pickle"))
+        torch.cuda.memory._record_memory_history(enabled=None)
+
+    # rollout through the connected inference engine, with the data management of a model-parallel trainer: the
+    # data-parallel heads roll out, the other ranks of a replica receive the head's batch
+    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, group_size: int = 1):
+        return self._rollout_via_engine("rollout_batch", data, workflow, workflow_kwargs, group_size=group_size)
+
+    def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None,
+                      group_size: int = 1, dynamic_bs: bool = False):
+        return self._rollout_via_engine("prepare_batch", dataloader, workflow, workflow_kwargs,
+                                        should_accept_fn=should_accept_fn, group_size=group_size,
+                                        dynamic_bs=dynamic_bs)
+
+    def _rollout_via_engine(self, method: str, source, workflow, workflow_kwargs, **kw):
+        engine = getattr(self, "rollout_engine", None)
+        if engine is None:
+            raise RuntimeError(f"{method}() needs a connected inference engine: call connect_engine() first")
+        from ..utils.data import broadcast_tensor_container
+
+        batch = None
+        if self.is_data_parallel_head():
+            batch = getattr(engine, method)(source, workflow, workflow_kwargs, **kw)
+        group = self.context_and_model_parallel_group
+        if group is None:
+            return batch
+        return broadcast_tensor_container(batch, src_rank=self.current_data_parallel_head(), group=group)
 
 
 class InferenceEngine(abc.ABC):
     def initialize(self, *args, **kwargs):
         raise NotImplementedError
+
+    @property
+    def initialized(self) -> bool:
+        """True once ``initialize()`` has completed (the engine has its workflow executor)."""
+        return getattr(self, "_executor", None) is not None
+
+    @property
+    def workflow_executor(self):
+        """The executor that runs rollout workflows against this engine."""
+        ex = getattr(self, "_executor", None)
+        if ex is None:
+            raise RuntimeError("the engine is not initialized")
+        return ex
+
+    def config_perf_tracer(self, config, rank: int, role: str):
+        from ..utils import perf_tracer
+
+        perf_tracer.configure(config, rank=rank, role=role)
+
+    def save_perf_tracer(self, step: int | None = None, force: bool = False):
+        from ..utils import perf_tracer
+
+        perf_tracer.save(step=step, force=force)
 
     def destroy(self):
         pass

@@ -204,17 +204,28 @@ class LocalInfServerInfo:
 
 @dataclass
 class DeviceRuntimeInfo:
+    """Memory of the current device in ``unit`` (GB / MB / KB): allocated and reserved by the caching allocator, used
+    on the device by anyone, and its capacity."""
     mem_allocated: float = 0.0
     mem_reserved: float = 0.0
+    mem_used: float = 0.0
     mem_total: float = 0.0
+    unit: str = "GB"
     ts: float = field(default_factory=time.time)
 
     @classmethod
-    def get_current(cls) -> "DeviceRuntimeInfo":
+    def get_current(cls, unit: str = "GB") -> "DeviceRuntimeInfo":
         import torch
 
+        div = {"GB": 1024 ** 3, "MB": 1024 ** 2, "KB": 1024}.get(unit)
+        if div is None:
+            raise ValueError(f"unsupported unit {unit!r}: GB, MB or KB")
         if not torch.cuda.is_available():
-            return cls()
+            return cls(unit=unit)
         free, total = torch.cuda.mem_get_info()
-        return cls(mem_allocated=torch.cuda.memory_allocated() / 2**30,
-                   mem_reserved=torch.cuda.memory_reserved() / 2**30, mem_total=total / 2**30)
+        return cls(mem_allocated=torch.cuda.memory_allocated() / div, mem_reserved=torch.cuda.memory_reserved() / div,
+                   mem_used=(total - free) / div, mem_total=total / div, unit=unit)
+
+    def log(self, label: str = "") -> str:
+        return (f"{label}{' ' if label else ''}memory [{self.unit}]: allocated {self.mem_allocated:.2f}, reserved "
+                f"{self.mem_reserved:.2f}, used on device {self.mem_used:.2f} of {self.mem_total:.2f}")

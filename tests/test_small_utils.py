@@ -143,3 +143,58 @@ def test_batches_are_split_by_tokens_with_groups_kept_together():
     tokens = [int(p["attention_mask"].sum()) for p in parts]
     assert sorted(tokens) == [161, 207]                    # 98 + 63 and 185 + 22: the heavy group pairs with the light one
     assert split_batch_by_tokens(batch, 1)[0] is batch
+
+
+def test_engine_api_conveniences(tmp_path):
+    """``initialized``, device statistics, perf-tracer hooks and rollout forwarded through the connected engine."""
+    from areal_b200.api.cli_args import (InferenceEngineConfig, NativeRolloutConfig, OptimizerConfig, PerfTracerConfig,
+                                         TrainEngineConfig)
+    from areal_b200.api.io_struct import DeviceRuntimeInfo, WeightUpdateMeta
+    from areal_b200.engine.rollout_engine import NativeRolloutEngine
+    from areal_b200.engine.train_engine import B200TrainEngine
+    from areal_b200.infra.workflow_executor import WorkflowExecutor
+    from areal_b200.workflow.rlvr import RLVRWorkflow
+
+    info = DeviceRuntimeInfo.get_current("MB")
+    assert info.unit == "MB" and "memory [MB]" in info.log("step 0")
+    with pytest.raises(ValueError):
+        DeviceRuntimeInfo.get_current("TB")
+    eng = B200TrainEngine(TrainEngineConfig(experiment_name="e", trial_name="t", path="", init_from_scratch=True,
+                                            dtype="float32", model_preset="tiny-qwen2", optimizer=OptimizerConfig()))
+    assert not eng.initialized
+    eng.create_process_group()
+    eng.initialize(seed=0)
+    assert eng.initialized and eng.get_device_stats().unit == "GB"
+    eng.start_memory_profile()
+    eng.stop_memory_profile(str(tmp_path / "mem"))            # no CUDA here: both are no-ops
+    with pytest.raises(RuntimeError, match="connect_engine"):
+        eng.rollout_batch([{"input_ids": [1, 2, 3]}], workflow=None)
+    rcfg = InferenceEngineConfig(experiment_name="e", trial_name="t", backend="native:d1", max_concurrent_rollouts=8,
+                                 consumer_batch_size=2,
+                                 native=NativeRolloutConfig(model_preset="tiny-qwen2", context_length=64, max_num_seqs=8,
+                                                            max_num_batched_tokens=256, num_kv_blocks=32, seed=0,
+                                                            cuda_graph=False))
+    ro = NativeRolloutEngine(rcfg)
+    assert not ro.initialized
+    with pytest.raises(RuntimeError):
+        ro.workflow_executor
+    ro.initialize(device="cpu")
+    try:
+        assert ro.initialized and isinstance(ro.workflow_executor, WorkflowExecutor)
+        eng.connect_engine(ro, WeightUpdateMeta(type="colocated") if hasattr(WeightUpdateMeta, "type") else None)
+        from areal_b200.api.cli_args import GenerationHyperparameters
+
+        g = GenerationHyperparameters(max_new_tokens=4, greedy=True, ignore_eos=True)
+        wf = RLVRWorkflow(reward_fn=lambda *a, **k: 1.0, gconfig=g, reward_in_process=True)
+        batch = eng.rollout_batch([{"input_ids": [5, 6, 7]}, {"input_ids": [8, 9]}], workflow=wf)
+        assert batch["input_ids"].shape[0] == 2 and batch["rewards"].tolist() == [1.0, 1.0]
+        eng.config_perf_tracer(PerfTracerConfig(experiment_name="e", trial_name="t", fileroot=str(tmp_path), enabled=True),
+                               rank=0, role="actor")
+        eng.save_perf_tracer(step=0, force=True)
+        ro.save_perf_tracer(force=True)
+    finally:
+        from areal_b200.utils import perf_tracer
+
+        perf_tracer.configure(None)
+        ro.destroy()
+        eng.destroy()
