@@ -1036,6 +1036,25 @@ def config_to_dict(cfg) -> dict:
     return asdict(cfg)
 
 
+def conf_as_dict(cfg) -> dict:
+    """A configuration (dataclass tree or plain mapping) as nested dicts."""
+    return dict(cfg) if isinstance(cfg, dict) else asdict(cfg)
+
+
+def get_py_cmd(module: str, args: dict[str, Any]) -> list[str]:
+    """``python3 -m module --flag value ...`` from a mapping: ``None`` / ``False`` / empty values are left out,
+    ``True`` becomes a bare flag, lists become one flag followed by their items; underscores turn into dashes."""
+    cmd = ["python3", "-m", module]
+    for k, v in args.items():
+        if v is None or v is False or v == "" or (isinstance(v, (list, tuple)) and not v):
+            continue
+        cmd.append("--" + k.replace("_", "-"))
+        if v is True:
+            continue
+        cmd.extend(str(x) for x in v) if isinstance(v, (list, tuple)) else cmd.append(str(v))
+    return cmd
+
+
 def get_log_path(cfg) -> str:
     root = cfg.cluster.fileroot if hasattr(cfg, "cluster") else cfg.fileroot
     path = os.path.join(root, "logs", getpass.getuser(), cfg.experiment_name, cfg.trial_name)

@@ -229,3 +229,20 @@ class DeviceRuntimeInfo:
     def log(self, label: str = "") -> str:
         return (f"{label}{' ' if label else ''}memory [{self.unit}]: allocated {self.mem_allocated:.2f}, reserved "
                 f"{self.mem_reserved:.2f}, used on device {self.mem_used:.2f} of {self.mem_total:.2f}")
+
+
+def get_versioned_lora_name(lora_name: str, version: int) -> str:
+    """Name under which version ``version`` of an adapter is registered with an inference server."""
+    return f"{lora_name}-v{version}"
+
+
+_IMAGE_MAGIC = (("iVBOR", "image/png"), ("/9j/", "image/jpeg"), ("R0lGOD", "image/gif"), ("UklGR", "image/webp"),
+                ("Qk", "image/bmp"))
+
+
+def detect_image_mime(base64_data: str) -> str:
+    """MIME type of a base64-encoded image, from the encoding of its magic bytes (JPEG when unknown)."""
+    for prefix, mime in _IMAGE_MAGIC:
+        if base64_data.startswith(prefix):
+            return mime
+    return "image/jpeg"

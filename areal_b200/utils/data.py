@@ -519,3 +519,134 @@ def cycle_dataloader(dataloader, num_cycles: int | None = None):
         for batch in dataloader:
             yield batch
         epoch += 1
+
+
+# ------------------------------------------------------------------ container helpers
+# Small conveniences over dicts / lists of tensors that workflow and reward code uses (areal/utils/data.py has
+# helpers of the same names; these are written against this package's batch conventions).
+def list_of_dict2dict_of_list(items: Sequence[dict[str, Any]]) -> dict[str, list[Any]]:
+    """``[{a: 1, b: 2}, {a: 3, b: 4}]`` → ``{a: [1, 3], b: [2, 4]}``; every item must have the same keys."""
+    if not items:
+        return {}
+    keys = list(items[0].keys())
+    for it in items:
+        if set(it.keys()) != set(keys):
+            raise ValueError(f"items have different keys: {sorted(it.keys())} vs {sorted(keys)}")
+    return {k: [it[k] for it in items] for k in keys}
+
+
+def dict_of_list2list_of_dict(d: dict[str, Sequence[Any]]) -> list[dict[str, Any]]:
+    """Inverse of :func:`list_of_dict2dict_of_list`; every list must have the same length."""
+    if not d:
+        return []
+    n = {len(v) for v in d.values()}
+    if len(n) != 1:
+        raise ValueError(f"lists have different lengths: { {k: len(v) for k, v in d.items()} }")
+    return [{k: v[i] for k, v in d.items()} for i in range(n.pop())]
+
+
+def dict_map(fn, d: dict[str, Any]) -> dict[str, Any]:
+    return {k: fn(v) for k, v in d.items()}
+
+
+def tensor_container_to(data: Any, *args, **kwargs) -> Any:
+    """``.to(*args, **kwargs)`` on every tensor inside nested dicts / lists / tuples; other leaves pass through."""
+    if torch.is_tensor(data):
+        return data.to(*args, **kwargs)
+    if isinstance(data, dict):
+        return {k: tensor_container_to(v, *args, **kwargs) for k, v in data.items()}
+    if isinstance(data, (list, tuple)):
+        return type(data)(tensor_container_to(v, *args, **kwargs) for v in data)
+    return data
+
+
+def pad_and_stack_tensors_along_first_dim(tensors: Sequence[torch.Tensor], pad_value: float = 0.0) -> torch.Tensor:
+    """Stacks tensors whose first dimension differs, padding at the end: ``[n_i, ...]`` → ``[len, max n_i, ...]``."""
+    n = max(t.shape[0] for t in tensors)
+    out = tensors[0].new_full((len(tensors), n) + tuple(tensors[0].shape[1:]), pad_value)
+    for i, t in enumerate(tensors):
+        out[i, : t.shape[0]] = t
+    return out
+
+
+def unpad_input(x: torch.Tensor, attention_mask: torch.Tensor):
+    """Padded ``[B, L, ...]`` → packed ``[T, ...]`` with the flat indices of the kept positions, ``cu_seqlens``
+    (int32) and the longest sequence (the calling convention of variable-length attention)."""
+    mask = attention_mask.bool()
+    lens = mask.sum(-1).to(torch.int32)
+    idx = mask.reshape(-1).nonzero(as_tuple=False).squeeze(-1)
+    cu = torch.zeros(lens.numel() + 1, dtype=torch.int32, device=lens.device)
+    cu[1:] = lens.cumsum(0)
+    flat = x.reshape((-1,) + tuple(x.shape[2:]))
+    return flat[idx], idx, cu, int(lens.max()) if lens.numel() else 0
+
+
+def pad_input(packed: torch.Tensor, indices: torch.Tensor, batch: int, seqlen: int) -> torch.Tensor:
+    """Inverse of :func:`unpad_input`: scatters packed rows back into a zero ``[batch, seqlen, ...]`` tensor."""
+    out = packed.new_zeros((batch * seqlen,) + tuple(packed.shape[1:]))
+    out[indices] = packed
+    return out.reshape((batch, seqlen) + tuple(packed.shape[1:]))
+
+
+def unpack_sequence(x: torch.Tensor, cu_seqlens: torch.Tensor | Sequence[int] | None = None,
+                    lens: Sequence[int] | None = None, dim: int = 0) -> list[torch.Tensor]:
+    """Cuts a packed tensor into its sequences along ``dim``, by ``cu_seqlens`` or by ``lens``."""
+    if lens is None:
+        cu = cu_seqlens.tolist() if torch.is_tensor(cu_seqlens) else list(cu_seqlens)
+        lens = [b - a for a, b in zip(cu[:-1], cu[1:])]
+    return list(torch.split(x, [int(n) for n in lens], dim=dim))
+
+
+def split_batch(data: dict[str, Any], n: int) -> list[dict[str, Any]]:
+    """``n`` consecutive parts of a padded batch with sizes as equal as possible (tensors and per-sample lists are
+    cut along the batch dimension, everything else is shared)."""
+    B = get_batch_size(data)
+    if not 1 <= n <= max(B, 1):
+        raise ValueError(f"cannot split a batch of {B} into {n} parts")
+    sizes = [B // n + (1 if i < B % n else 0) for i in range(n)]
+    out, a = [], 0
+    for s in sizes:
+        out.append({k: (v[a:a + s] if (torch.is_tensor(v) and v.dim() >= 1 and v.shape[0] == B) or
+                        (isinstance(v, list) and len(v) == B) else v) for k, v in data.items()})
+        a += s
+    return out
+
+
+def concat_batch(parts: Sequence[dict[str, Any]], pad_value: float = 0.0) -> dict[str, Any]:
+    """Inverse of :func:`split_batch` (sequence dimensions are padded to the longest part)."""
+    return concat_padded_tensors(list(parts), pad_value)
+
+
+def make_dummy_eval_item(template: dict[str, Any]) -> dict[str, Any]:
+    """A sample shaped like ``template`` that carries no loss weight: a one-token sequence with an all-zero
+    ``loss_mask``. Evaluation batches that do not divide over the data-parallel ranks are topped up with these."""
+    out: dict[str, Any] = {}
+    for k, v in template.items():
+        if torch.is_tensor(v) and v.dim() >= 2:
+            z = torch.zeros((1, 1) + tuple(v.shape[2:]), dtype=v.dtype)
+            if k == "attention_mask":
+                z[:] = 1
+            out[k] = z
+        elif torch.is_tensor(v) and v.dim() == 1:
+            out[k] = torch.zeros(1, dtype=v.dtype)
+        elif isinstance(v, list):
+            out[k] = [None]
+        else:
+            out[k] = v
+    return out
+
+
+def broadcast_tensor(t: torch.Tensor | None, src_rank: int = 0, group: dist.ProcessGroup | None = None,
+                     device=None) -> torch.Tensor:
+    """Broadcasts one tensor whose shape and dtype the receivers do not know (metadata first, then the data)."""
+    if not dist.is_initialized() or dist.get_world_size(group) == 1:
+        return t
+    meta = [None]
+    if dist.get_rank() == src_rank:
+        meta = [(tuple(t.shape), t.dtype)]
+    dist.broadcast_object_list(meta, src=src_rank, group=group)
+    shape, dtype = meta[0]
+    dev = device if device is not None else (t.device if t is not None else _device_for(group))
+    buf = t.to(dev).contiguous() if dist.get_rank() == src_rank else torch.empty(shape, dtype=dtype, device=dev)
+    dist.broadcast(buf, src=src_rank, group=group)
+    return buf

@@ -78,3 +78,40 @@ def split_addr(addr: str) -> tuple[str, int]:
 
 def format_url(host: str, port: int, scheme: str = "http", path: str = "") -> str:
     return f"{scheme}://{format_addr(host, port)}{path}"
+
+
+# names the reference's utilities go by (areal/utils/network.py)
+format_hostport = format_addr
+split_hostport = split_addr
+
+
+def format_host_for_url(host: str) -> str:
+    """``host`` as it appears inside a URL: IPv6 literals in brackets."""
+    host = host.strip("[]")
+    return f"[{host}]" if ":" in host else host
+
+
+def is_port_free(port: int, host: str = "") -> bool:
+    with socket.socket(socket.AF_INET6 if is_ipv6(host) else socket.AF_INET) as s:
+        s.setsockopt(socket.SOL_SOCKET, socket.SO_REUSEADDR, 1)
+        try:
+            s.bind((host.strip("[]"), port))
+            return True
+        except OSError:
+            return False
+
+
+def get_loopback_ip(prefer_ipv6: bool = False) -> str:
+    """``127.0.0.1``, or ``::1`` when asked for and the host has an IPv6 loopback."""
+    if prefer_ipv6 and socket.has_ipv6:
+        try:
+            with socket.socket(socket.AF_INET6) as s:
+                s.bind(("::1", 0))
+                return "::1"
+        except OSError:
+            pass
+    return "127.0.0.1"
+
+
+def gethostname() -> str:
+    return socket.gethostname()

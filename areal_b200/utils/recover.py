@@ -140,6 +140,23 @@ class RecoverHandler:
         return info
 
 
+def check_if_auto_recover(config: RecoverConfig) -> bool:
+    """Whether a usable recover checkpoint of this experiment / trial exists: the recover info loads, names a step
+    that was completed, and the checkpoint directory it points to is there."""
+    root = os.path.join(RecoverHandler.recover_root(config), "recover_info")
+    try:
+        info = RecoverInfo.load(root)
+    except InvalidRecoverInfo:
+        return False
+    if info.last_step_info.global_step < 0:
+        return False
+    ckpt = (info.checkpoint_info or {}).get("path")
+    return ckpt is None or os.path.exists(ckpt)
+
+
+InValidRecoverInfo = InvalidRecoverInfo  # the spelling used by the reference
+
+
 def check_if_recover(config: RecoverConfig, run_id: int = 0) -> bool:
     if config.mode in ("disabled", "off"):
         return False

@@ -1,6 +1,7 @@
 """Small utilities: parameter estimates, proximal log-prob approximations, address helpers, optional logger
 backends, dynamic imports, token-balanced batch splitting."""
 import dataclasses
+import os
 import sys
 import types
 
@@ -198,3 +199,77 @@ def test_engine_api_conveniences(tmp_path):
         perf_tracer.configure(None)
         ro.destroy()
         eng.destroy()
+
+
+def test_container_and_padding_helpers():
+    from areal_b200.utils import data as D
+
+    items = [{"a": 1, "b": "x"}, {"a": 2, "b": "y"}]
+    d = D.list_of_dict2dict_of_list(items)
+    assert d == {"a": [1, 2], "b": ["x", "y"]} and D.dict_of_list2list_of_dict(d) == items
+    with pytest.raises(ValueError):
+        D.list_of_dict2dict_of_list([{"a": 1}, {"b": 2}])
+    with pytest.raises(ValueError):
+        D.dict_of_list2list_of_dict({"a": [1], "b": [1, 2]})
+    assert D.dict_map(lambda v: v * 2, {"a": 1}) == {"a": 2}
+    moved = D.tensor_container_to({"x": torch.ones(2), "l": [torch.zeros(1), "s"], "n": 3}, torch.float64)
+    assert moved["x"].dtype == torch.float64 and moved["l"][0].dtype == torch.float64 and moved["l"][1] == "s"
+    st = D.pad_and_stack_tensors_along_first_dim([torch.ones(2, 3), torch.ones(4, 3)], pad_value=-1)
+    assert st.shape == (2, 4, 3) and (st[0, 2:] == -1).all()
+    mask = torch.tensor([[1, 1, 1, 0], [1, 0, 0, 0], [1, 1, 0, 0]])
+    x = torch.arange(12.0).reshape(3, 4, 1) + 1
+    packed, idx, cu, mx = D.unpad_input(x, mask)
+    assert packed.squeeze(-1).tolist() == [1, 2, 3, 5, 9, 10] and cu.tolist() == [0, 3, 4, 6] and mx == 3
+    back = D.pad_input(packed, idx, 3, 4)
+    assert torch.equal(back, x * mask[..., None])
+    seqs = D.unpack_sequence(packed, cu)
+    assert [s.shape[0] for s in seqs] == [3, 1, 2] and [s.shape[0] for s in D.unpack_sequence(packed, lens=[2, 4])] == [2, 4]
+    batch = {"input_ids": torch.arange(10).reshape(5, 2), "attention_mask": torch.ones(5, 2, dtype=torch.bool),
+             "images": list("abcde"), "meta": "m"}
+    parts = D.split_batch(batch, 3)
+    assert [p["input_ids"].shape[0] for p in parts] == [2, 2, 1] and parts[2]["images"] == ["e"] and parts[0]["meta"] == "m"
+    whole = D.concat_batch([{k: v for k, v in p.items() if torch.is_tensor(v)} for p in parts])
+    assert torch.equal(whole["input_ids"], batch["input_ids"])
+    with pytest.raises(ValueError):
+        D.split_batch(batch, 6)
+    dummy = D.make_dummy_eval_item({"input_ids": torch.ones(1, 7, dtype=torch.long), "attention_mask": torch.ones(1, 7, dtype=torch.bool),
+                                    "loss_mask": torch.ones(1, 7, dtype=torch.int32), "rewards": torch.ones(1), "images": ["i"]})
+    assert dummy["input_ids"].shape == (1, 1) and bool(dummy["attention_mask"].all()) and int(dummy["loss_mask"].sum()) == 0
+    assert dummy["images"] == [None] and D.broadcast_tensor(torch.ones(2)).tolist() == [1.0, 1.0]
+
+
+def test_more_small_helpers(tmp_path):
+    from areal_b200.api.cli_args import RecoverConfig, conf_as_dict, get_py_cmd
+    from areal_b200.api.io_struct import StepInfo, detect_image_mime, get_versioned_lora_name
+    from areal_b200.utils import network as N
+    from areal_b200.utils.recover import InValidRecoverInfo, InvalidRecoverInfo, RecoverHandler, RecoverInfo, check_if_auto_recover
+
+    assert N.format_hostport("::1", 5) == "[::1]:5" and N.split_hostport("[::1]:5") == ("::1", 5)
+    assert N.format_host_for_url("fe80::1") == "[fe80::1]" and N.format_host_for_url("h") == "h"
+    port = N.find_free_ports(1)[0]
+    assert N.is_port_free(port, "127.0.0.1")
+    import socket
+
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", port))
+        s.listen()
+        assert not N.is_port_free(port, "127.0.0.1")
+    assert N.get_loopback_ip() == "127.0.0.1" and N.get_loopback_ip(True) in ("::1", "127.0.0.1") and N.gethostname()
+    assert get_versioned_lora_name("ad", 3) == "ad-v3"
+    import base64
+
+    assert detect_image_mime(base64.b64encode(b"\x89PNG\r\n\x1a\n0000").decode()) == "image/png"
+    assert detect_image_mime(base64.b64encode(b"\xff\xd8\xff\xe0data").decode()) == "image/jpeg"
+    assert detect_image_mime(base64.b64encode(b"GIF89a....").decode()) == "image/gif"
+    assert detect_image_mime("????") == "image/jpeg"
+    assert get_py_cmd("pkg.mod", {"model_path": "/m", "tp": 2, "trust": True, "skip": False, "none": None, "ids": [1, 2],
+                                  "empty": []}) == ["python3", "-m", "pkg.mod", "--model-path", "/m", "--tp", "2",
+                                                    "--trust", "--ids", "1", "2"]
+    cfg = RecoverConfig(experiment_name="e", trial_name="t", fileroot=str(tmp_path), mode="auto")
+    assert conf_as_dict(cfg)["mode"] == "auto" and conf_as_dict({"a": 1}) == {"a": 1}
+    assert InValidRecoverInfo is InvalidRecoverInfo and not check_if_auto_recover(cfg)
+    root = os.path.join(RecoverHandler.recover_root(cfg), "recover_info")
+    RecoverInfo(last_step_info=StepInfo(0, 1, 1, 4), checkpoint_info={"path": str(tmp_path / "missing")}).dump(root)
+    assert not check_if_auto_recover(cfg)                       # the checkpoint it names is gone
+    os.makedirs(tmp_path / "missing")
+    assert check_if_auto_recover(cfg)
