@@ -48,37 +48,8 @@ from .ppo.critic import PPOCritic
 logger = logging.getLogger("PPOTrainer")
 
 
-class _ListLoader:
-    """Minimal stateful dataloader over an in-memory dataset (list of dict items)."""
-
-    def __init__(self, dataset, batch_size: int, shuffle: bool, seed: int, rank: int = 0, world: int = 1,
-                 drop_last: bool = True):
-        self.dataset, self.batch_size, self.shuffle = dataset, batch_size, shuffle
-        self.seed, self.rank, self.world, self.drop_last = seed, rank, world, drop_last
-        self.epoch = 0
-        self.sampler = self
-
-    def set_epoch(self, e: int):
-        self.epoch = e
-
-    def __len__(self):
-        n = len(self.dataset) // self.world
-        return n // self.batch_size if self.drop_last else -(-n // self.batch_size)
-
-    def __iter__(self):
-        idx = list(range(len(self.dataset)))
-        if self.shuffle:
-            g = torch.Generator().manual_seed(self.seed + self.epoch)
-            idx = torch.randperm(len(idx), generator=g).tolist()
-        idx = idx[self.rank::self.world]
-        for i in range(0, len(idx) - (self.batch_size - 1 if self.drop_last else 0), self.batch_size):
-            yield [self.dataset[j] for j in idx[i:i + self.batch_size]]
-
-    def state_dict(self):
-        return {"epoch": self.epoch}
-
-    def load_state_dict(self, s):
-        self.epoch = s["epoch"]
+# the loader lives in utils/dataloader.py (mid-epoch state, exact evaluation split); the old private name stays
+from ..utils.dataloader import StatefulListLoader as _ListLoader  # noqa: E402
 
 
 class PPOTrainer:

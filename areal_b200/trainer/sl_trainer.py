@@ -129,6 +129,9 @@ class _SLTrainer:
         start = info.last_step_info.global_step + 1 if info is not None else 0
         spe = self.ft_spec.steps_per_epoch
         step = 0
+        # this loop replays the epochs from the start and skips the steps that were already taken, so the loader
+        # starts over too (its restored position would otherwise be skipped a second time)
+        self.train_loader.load_state_dict({"epoch": 0, "position": 0})
         for epoch in range(cfg.total_train_epochs):
             self.train_loader.set_epoch(epoch)
             for epoch_step, items in enumerate(self.train_loader):

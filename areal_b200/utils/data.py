@@ -514,7 +514,8 @@ def cycle_dataloader(dataloader, num_cycles: int | None = None):
     epoch = 0
     while num_cycles is None or epoch < num_cycles:
         sampler = getattr(dataloader, "sampler", None)
-        if sampler is not None and hasattr(sampler, "set_epoch"):
+        # a loader that advances its own epoch (and may have been restored in the middle of one) is left alone
+        if sampler is not None and hasattr(sampler, "set_epoch") and not getattr(dataloader, "auto_epoch", False):
             sampler.set_epoch(epoch)
         for batch in dataloader:
             yield batch

@@ -273,3 +273,56 @@ def test_more_small_helpers(tmp_path):
     assert not check_if_auto_recover(cfg)                       # the checkpoint it names is gone
     os.makedirs(tmp_path / "missing")
     assert check_if_auto_recover(cfg)
+
+
+def test_stateful_loader_resumes_mid_epoch_and_splits_evaluation_exactly():
+    from areal_b200.utils.data import cycle_dataloader
+    from areal_b200.utils.dataloader import StatefulListLoader, create_dataloader
+
+    data = list(range(23))
+    # training: both ranks get the same number of batches, disjoint samples, a new order every epoch
+    loaders = [StatefulListLoader(data, 3, shuffle=True, seed=7, rank=r, world=2) for r in range(2)]
+    assert len(loaders[0]) == len(loaders[1]) == 3                      # 22 usable samples -> 11 per rank -> 3 batches
+    e0 = [list(ld) for ld in loaders]
+    assert all(len(b) == 3 for ep in e0 for b in ep) and len(e0[0]) == len(e0[1]) == 3
+    seen = [x for ep in e0 for b in ep for x in b]
+    assert len(set(seen)) == len(seen) == 18
+    e1 = list(loaders[0])
+    assert loaders[0].epoch == 2 and e1 != e0[0]
+    # a checkpoint in the middle of an epoch continues with the next batch of the same permutation
+    a = StatefulListLoader(data, 2, shuffle=True, seed=1)
+    it = iter(a)
+    first = [next(it), next(it)]
+    state = a.state_dict()
+    assert state == {"epoch": 0, "position": 2}
+    rest = list(it)
+    b = StatefulListLoader(data, 2, shuffle=True, seed=1)
+    b.load_state_dict(state)
+    assert list(b) == rest and b.epoch == 1 and b.position == 0
+    # the endless iterator keeps a restored loader's place and moves through epochs
+    c = StatefulListLoader(data, 2, shuffle=True, seed=1)
+    c.load_state_dict(state)
+    cyc = cycle_dataloader(c)
+    got = [next(cyc) for _ in range(len(rest) + 2)]
+    fresh = StatefulListLoader(data, 2, shuffle=True, seed=1)
+    fresh.set_epoch(1)
+    assert got[: len(rest)] == rest and got[len(rest):] == [next(i) for i in [iter(fresh)] * 2]
+    assert first[0] not in rest
+    # evaluation: every sample exactly once, ranks differ by at most one, nothing padded
+    ev = [StatefulListLoader(data, 4, shuffle=False, rank=r, world=3, drop_last=False) for r in range(3)]
+    per_rank = [[x for bt in ld for x in bt] for ld in ev]
+    assert sorted(x for pr in per_rank for x in pr) == data and {len(pr) for pr in per_rank} == {7, 8}
+    assert [len(ld) for ld in ev] == [2, 2, 2]
+
+    class ValidDatasetConfig:
+        batch_size, shuffle, drop_last = 6, False, True
+
+    class TrainDatasetConfig:
+        batch_size, shuffle, drop_last = 6, True, True
+
+    v = create_dataloader(data, 1, 3, ValidDatasetConfig())
+    assert (v.batch_size, v.drop_last, v.shuffle) == (2, False, False)
+    t = create_dataloader(data, 0, 3, TrainDatasetConfig(), collate_fn=lambda items: sum(items))
+    assert t.drop_last and isinstance(next(iter(t)), int)
+    with pytest.raises(ValueError):
+        create_dataloader(data, 0, 4, TrainDatasetConfig())
