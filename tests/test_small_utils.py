@@ -326,3 +326,76 @@ def test_stateful_loader_resumes_mid_epoch_and_splits_evaluation_exactly():
     assert t.drop_last and isinstance(next(iter(t)), int)
     with pytest.raises(ValueError):
         create_dataloader(data, 0, 4, TrainDatasetConfig())
+
+
+def test_tiny_utility_modules(tmp_path, monkeypatch):
+    from areal_b200.utils import constants, environ, errors, fs, image, pkg_version, printing, wrapper
+    from areal_b200.utils.math import align, ceil_div
+
+    assert ceil_div(7, 2) == 4 and ceil_div(8, 2) == 4 and align(17, 16) == 32 and align(32, 16) == 32
+    e = errors.EngineError("update", "timeout", "no ack")
+    assert "sub_error: timeout" in str(e) and isinstance(errors._Structured.from_dict(e.to_dict()), errors.EngineError)
+    assert isinstance(errors.FrameworkError.from_dict(errors.FrameworkError("a", "b", "c").to_dict()), errors.FrameworkError)
+    monkeypatch.setenv("X_FLAG", "TRUE")
+    assert environ.get_bool_env_var("X_FLAG") and not environ.get_bool_env_var("X_MISSING")
+    monkeypatch.setenv("X_FLAG", "maybe")
+    assert not environ.get_bool_env_var("X_FLAG")
+    monkeypatch.delenv("RANK", raising=False)
+    monkeypatch.delenv("AREAL_SPMD_MODE", raising=False)
+    assert environ.is_single_controller() and not environ.is_in_ci()
+    monkeypatch.setenv("RANK", "0")
+    assert not environ.is_single_controller()
+    table = printing.tabulate_stats({f"k{i}": float(i) for i in range(5)}, col=2)
+    assert "k0" in table and "k4" in table and "4.0000e+00" in table and printing.tabulate_stats({}) == "(no stats)"
+    from PIL import Image
+
+    a, b = Image.new("RGB", (4, 2), (255, 0, 0)), Image.new("RGB", (2, 6), (0, 255, 0))
+    enc = image.image2base64([a, b])
+    assert len(enc) == 2 and image.base642image("data:image/png;base64," + enc[0]).size == (4, 2)
+    from areal_b200.api.io_struct import detect_image_mime
+
+    assert detect_image_mime(enc[0]) == "image/png"
+    padded = image.pad_images_batch_to_max_size([a, b])
+    assert [p.size for p in padded] == [(4, 6), (4, 6)] and padded[0].getpixel((0, 0)) == (0, 0, 0)
+    assert padded[0].getpixel((0, 2)) == (255, 0, 0)
+
+    class Engine:
+        @wrapper.wrapable()
+        def step(self, x):
+            return x + 1
+
+        @wrapper.wrapable("renamed")
+        def other(self):
+            return "o"
+
+        def hidden(self):
+            return None
+
+    class Proxy:
+        pass
+
+    calls = []
+
+    def via_rpc(*args, **kwargs):
+        calls.append(wrapper.wrap_get_method_name(kwargs))
+        fn = wrapper.wrap_get_method(kwargs)
+        return fn(*args, **wrapper.wrap_remove_meta(kwargs))
+
+    p = Proxy()
+    assert sorted(wrapper.wrap(p, Engine(), via_rpc)) == ["renamed", "step"]
+    assert p.step(1) == 2 and p.renamed() == "o" and calls == ["step", "renamed"] and not hasattr(p, "hidden")
+    q = Proxy()
+    wrapper.wrap(q, Engine())
+    assert q.step(x=4) == 5
+    assert pkg_version.is_available("torch") and not pkg_version.is_available("surely_not_a_package_xyz")
+    assert pkg_version.compare_versions("2.11.0+cu128", "2.9") == 1 and pkg_version.compare_versions("1.2.0rc1", "1.2.0") == -1
+    assert pkg_version.compare_versions("v0.5", "0.5.0") == 0 and pkg_version.compare_versions("1.0.post1", "1.0") == 1
+    assert pkg_version.is_version_greater_or_equal("torch", "2.0") and pkg_version.is_version_less("torch", "99")
+    with pytest.raises(ValueError):
+        pkg_version.compare_versions("abc", "1.0")
+    assert os.path.isdir(fs.get_user_tmp())
+    fs.validate_shared_path(str(tmp_path / "new" / "dir"), "fileroot", n_nodes=2)   # an ancestor exists and is writable
+    with pytest.raises(ValueError):
+        fs.validate_shared_path("", "fileroot")
+    assert fs.is_network_fs(str(tmp_path)) in (True, False, None)
+    assert constants.DEFAULT_VECTORIZED_ALIGNMENT_BYTES == 16 and "recompute" in constants.PROX_LOGP_METHODS_ALL
