@@ -264,6 +264,122 @@ class SessionTracer:
                                         status=r.status, phases=r.phases, meta=r.meta)) + "\n")
 
 
+# --------------------------------------------------------------------------- task / session context
+# Workflow code does not carry ids around: the executor binds the task and session of the running episode to the
+# coroutine's context, and ``trace_session_phase`` / ``trace_session_event`` anywhere below it (a workflow, an
+# agent, a reward call) land in that session's record. Reference: the module-level helpers of
+# areal/utils/perf_tracer.py (register_task / register_session, set_/get_task_id, set_/get_session_id,
+# session_context, trace_session_phase, atrace_session_phase, trace_session_event).
+import contextvars
+import itertools
+
+_TASK_ID: contextvars.ContextVar = contextvars.ContextVar("areal_b200_task_id", default=None)
+_SESSION_ID: contextvars.ContextVar = contextvars.ContextVar("areal_b200_session_id", default=None)
+_task_counter = itertools.count()
+
+
+def is_configured() -> bool:
+    return _GLOBAL is not None and _GLOBAL.enabled
+
+
+def reset() -> None:
+    """Flushes and drops the global tracer (tests; re-configuration inside one process)."""
+    global _GLOBAL
+    if _GLOBAL is not None:
+        _GLOBAL.save(force=True)
+    _GLOBAL = None
+    _TASK_ID.set(None)
+    _SESSION_ID.set(None)
+
+
+def register_task() -> int:
+    """A new task id (one per submitted episode, shared by the sessions that retry it), bound to this context."""
+    tid = next(_task_counter)
+    _TASK_ID.set(tid)
+    return tid
+
+
+def set_task_id(task_id: int | None) -> None:
+    _TASK_ID.set(task_id)
+
+
+def get_task_id() -> int | None:
+    return _TASK_ID.get()
+
+
+def register_session(task_id: int | None = None, **meta) -> int | None:
+    """Starts a session record for ``task_id`` (default: the context's task) and binds it to this context;
+    ``None`` when session tracing is off."""
+    st = get_session_tracer()
+    if st is None:
+        return None
+    sid = st.start_session(task_id if task_id is not None else _TASK_ID.get(), **meta)
+    _SESSION_ID.set(sid)
+    return sid
+
+
+def set_session_id(session_id: int | None) -> None:
+    _SESSION_ID.set(session_id)
+
+
+def get_session_id() -> int | None:
+    return _SESSION_ID.get()
+
+
+@contextlib.contextmanager
+def session_context(task_id: int | None = None, **meta):
+    """One traced session around a block: registered on entry, ended on exit with status ``accepted`` (``failed``
+    if the block raises; set ``ctx["status"]`` inside the block for ``rejected``)."""
+    st = get_session_tracer()
+    sid = None if st is None else st.start_session(task_id if task_id is not None else _TASK_ID.get(), **meta)
+    ctx = {"session_id": sid, "status": "accepted"}
+    tok = _SESSION_ID.set(sid)
+    try:
+        yield ctx
+    except BaseException:
+        ctx["status"] = "failed"
+        raise
+    finally:
+        _SESSION_ID.reset(tok)
+        if st is not None and sid is not None:
+            st.end_session(sid, status=ctx["status"])
+
+
+trace_session = session_context
+
+
+@contextlib.contextmanager
+def trace_session_phase(name: str, **meta):
+    """A named phase (generate, reward, tool call ...) of the context's session; a no-op outside a session."""
+    st, sid = get_session_tracer(), _SESSION_ID.get()
+    if st is None or sid is None:
+        yield
+        return
+    with st.phase(sid, name, **meta):
+        yield
+
+
+@contextlib.asynccontextmanager
+async def atrace_session_phase(name: str, **meta):
+    with trace_session_phase(name, **meta):
+        yield
+
+
+def trace_session_event(name: str, **meta) -> None:
+    """A zero-length phase: marks a moment of the context's session."""
+    with trace_session_phase(name, **meta):
+        pass
+
+
+@contextlib.asynccontextmanager
+async def atrace_scope(name: str, category: "Category | str" = None, args: dict | None = None):
+    with trace_scope(name, category if category is not None else Category.MISC, args):
+        yield
+
+
+PerfTraceCategory = Category
+
+
 # --------------------------------------------------------------------------- converter
 
 

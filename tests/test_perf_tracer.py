@@ -145,3 +145,57 @@ def test_trainer_writes_perf_trace_sessions_and_torch_profile(tmp_path):
     assert all(math.isfinite(e.get("dur", 0.0)) for e in events)
     profs = glob.glob(str(tmp_path / "**" / "torch_profile_step1_r0.json"), recursive=True)
     assert len(profs) == 1 and os.path.getsize(profs[0]) > 1000
+
+
+def test_task_and_session_ids_follow_the_coroutine_context(tmp_path):
+    """Two episodes run concurrently; each binds its task and session to its own context, and phases traced deep
+    inside (no ids passed around) land in the right session."""
+    pt.reset()
+    assert not pt.is_configured() and pt.register_session() is None
+    with pt.trace_session_phase("ignored"):          # outside a configured tracer: a no-op
+        pass
+    pt.configure(_cfg(tmp_path, session_tracer=SessionTracerConfig(enabled=True, flush_threshold=100)), rank=0, role="rollout")
+    assert pt.is_configured()
+
+    async def reward(name):
+        async with pt.atrace_session_phase("reward", who=name):
+            await asyncio.sleep(0.001)
+
+    async def episode(name, reject):
+        tid = pt.register_task()
+        with pt.session_context(who=name) as ctx:
+            assert pt.get_task_id() == tid and pt.get_session_id() == ctx["session_id"]
+            with pt.trace_session_phase("generate", who=name):
+                await asyncio.sleep(0.002)
+            await reward(name)
+            pt.trace_session_event("scored", who=name)
+            if reject:
+                ctx["status"] = "rejected"
+        assert pt.get_session_id() is None or pt.get_session_id() != ctx["session_id"]
+        return tid
+
+    async def boom():
+        pt.register_task()
+        with pt.trace_session():
+            raise ValueError("x")
+
+    async def main():
+        tids = await asyncio.gather(episode("a", False), episode("b", True))
+        try:
+            await boom()
+        except ValueError:
+            pass
+        return tids
+
+    tids = asyncio.run(main())
+    assert tids[0] != tids[1]
+    pt.save(force=True)
+    path = pt.get_session_tracer().path
+    recs = [json.loads(line) for line in open(path)]
+    by = {r["meta"].get("who"): r for r in recs}
+    assert by["a"]["status"] == "accepted" and by["b"]["status"] == "rejected" and by[None]["status"] == "failed"
+    for who in ("a", "b"):
+        assert [p["name"] for p in by[who]["phases"]] == ["generate", "reward", "scored"]
+        assert all(p["who"] == who for p in by[who]["phases"]) and by[who]["task_id"] in tids
+    pt.reset()
+    assert pt.get_tracer() is None and pt.get_task_id() is None
