@@ -39,3 +39,23 @@ def recover_flag(exp, trial):
 
 def distributed_lock(exp, trial, name):
     return f"{_root(exp, trial)}/locks/{name}"
+
+
+def registry_root(user: str | None = None):
+    """Root under which every experiment of ``user`` registers (trial discovery across experiments)."""
+    import getpass
+
+    return f"registry/{user or getpass.getuser()}"
+
+
+def trial_registry(exp, trial):
+    """Record announcing that the trial exists (written by its launcher, listed by monitoring tools)."""
+    import getpass
+
+    return f"{registry_root(getpass.getuser())}/{exp}/{trial}"
+
+
+def worker_discovery(exp, trial, role, idx="*"):
+    """Key (or key prefix with ``idx="*"``) under which the workers of a role publish their addresses."""
+    base = workers(exp, trial, role)
+    return base if idx == "*" else worker(exp, trial, role, idx)

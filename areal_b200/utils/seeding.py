@@ -41,3 +41,22 @@ def get_shuffle_seed() -> int:
     if _BASE_SEED is None:
         raise RuntimeError("set_random_seed has not been called")
     return _mix(_BASE_SEED, "shuffle")
+
+
+class Shuffler:
+    """A stream of shuffle seeds derived from a key: call ``next_shuffle()`` once per epoch (or per shuffle); two
+    shufflers with the same key produce the same stream."""
+
+    def __init__(self, key: str = "default"):
+        self.base_key, self.cnt = key, 0
+
+    def next_shuffle(self) -> int:
+        seed = _mix(0, f"{self.base_key}_{self.cnt}")
+        self.cnt += 1
+        return seed
+
+    def state_dict(self) -> dict:
+        return {"key": self.base_key, "cnt": self.cnt}
+
+    def load_state_dict(self, s: dict) -> None:
+        self.base_key, self.cnt = s["key"], int(s["cnt"])

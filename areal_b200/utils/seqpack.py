@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import ctypes
 import heapq
-from typing import Sequence
+from typing import Any, Sequence
 
 import numpy as np
 
@@ -216,3 +216,53 @@ def allocate(sizes: Sequence[int], capacity: int | None, min_groups: int, algori
         half = len(heavy) // 2
         groups += [heavy[:half], heavy[half:]]
     return groups
+
+
+# ------------------------------------------------------------------ further partition helpers
+def get_allocate_fn(algorithm: str = "ffd"):
+    """``ffd_allocate`` or ``kk_allocate`` by name (the value of ``MicroBatchSpec.packing_algorithm``)."""
+    table = {"ffd": ffd_allocate, "kk": kk_allocate}
+    if algorithm not in table:
+        raise ValueError(f"unknown packing algorithm {algorithm!r}; supported: {sorted(table)}")
+    return table[algorithm]
+
+
+def partition_balanced_tuples(sizes: Sequence[int], k: int, min_size: int = 1) -> list[tuple[int, int]]:
+    """:func:`partition_balanced` as ``(start, end)`` pairs."""
+    b = partition_balanced(sizes, k, min_size)
+    return list(zip(b[:-1], b[1:]))
+
+
+def min_abs_diff_partition(sizes: Sequence[int], k: int, min_size: int = 1) -> list[tuple[int, int]]:
+    """Contiguous split of a 1-D array into ``k`` non-empty ranges of at least ``min_size`` items whose largest sum
+    is as small as possible (micro-batches of a pipeline, shards of a sorted batch)."""
+    arr = np.asarray(sizes)
+    if arr.ndim != 1:
+        raise ValueError(f"the array to be partitioned must be 1-D, got shape {arr.shape}")
+    if len(arr) < k * max(min_size, 1):
+        raise ValueError(f"cannot split {len(arr)} items into {k} parts of at least {min_size}")
+    parts = partition_balanced_tuples(arr.tolist(), k, min_size)
+    assert parts[0][0] == 0 and parts[-1][1] == len(arr) and all(a[1] == b[0] for a, b in zip(parts, parts[1:]))
+    return parts
+
+
+def reorder_to_balanced_batches(seqlens: Sequence[int], n_seqs_per_batch: int) -> tuple[np.ndarray, int]:
+    """A permutation that groups sequences into consecutive batches of ``n_seqs_per_batch`` with token counts as
+    equal as possible (longest first, each into the lightest batch that still has room), and the largest difference
+    between two batches' token counts. Batches are returned heaviest first."""
+    lens = np.asarray(seqlens, dtype=np.int64)
+    n_bins = -(-len(lens) // n_seqs_per_batch)
+    bins: list[list[int]] = [[] for _ in range(n_bins)]
+    load = np.zeros(n_bins, dtype=np.int64)
+    for i in np.argsort(-lens, kind="stable"):
+        open_bins = [b for b in range(n_bins) if len(bins[b]) < n_seqs_per_batch]
+        b = min(open_bins, key=lambda j: (load[j], j))
+        bins[b].append(int(i))
+        load[b] += lens[i]
+    order = np.argsort(-load, kind="stable")
+    perm = np.array([i for b in order for i in bins[b]], dtype=np.int64)
+    return perm, int(load.max() - load.min()) if n_bins else 0
+
+
+def flat2d(rows: Sequence[Sequence[Any]]) -> list[Any]:
+    return [x for row in rows for x in row]

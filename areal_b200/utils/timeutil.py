@@ -74,3 +74,90 @@ class EpochStepTimeFreqCtl:
         self._epoch.load_state_dict(s["epoch"])
         self._step.load_state_dict(s["step"])
         self._time.load_state_dict(s["time"])
+
+
+# ------------------------------------------------------------------ value schedules
+# Scalars that follow the training step (a KL coefficient, a clip range, a sampling temperature).
+import dataclasses as _dc
+import math as _math
+
+
+@_dc.dataclass
+class Scheduler:
+    """``get(step)`` for ``step`` in ``[0, total_iters]``; steps outside that range are an error."""
+    init_value: float
+    total_iters: int
+
+    @property
+    def final_value(self) -> float:
+        return self.get(self.total_iters)
+
+    def get(self, step: int) -> float:
+        if step < 0 or step > self.total_iters:
+            raise ValueError(f"step {step} outside [0, {self.total_iters}]")
+        return float(self._get(step))
+
+    def _get(self, step: int) -> float:
+        raise NotImplementedError
+
+
+@_dc.dataclass
+class ConstantScheduler(Scheduler):
+    def _get(self, step: int) -> float:
+        return self.init_value
+
+
+@_dc.dataclass
+class LinearScheduler(Scheduler):
+    end_value: float = 0.0
+
+    def _get(self, step: int) -> float:
+        return self.init_value + (self.end_value - self.init_value) * step / max(self.total_iters, 1)
+
+
+@_dc.dataclass
+class ExponentialScheduler(Scheduler):
+    decay: float = 1.0
+
+    def _get(self, step: int) -> float:
+        return self.init_value * self.decay ** step
+
+
+@_dc.dataclass
+class CosineDecayScheduler(Scheduler):
+    end_value: float = 0.0
+
+    def _get(self, step: int) -> float:
+        t = step / max(self.total_iters, 1)
+        return self.end_value + 0.5 * (self.init_value - self.end_value) * (1 + _math.cos(_math.pi * t))
+
+
+class ChainedScheduler:
+    """Schedules one after the other; each must start where its predecessor ended."""
+
+    def __init__(self, schedulers):
+        self.schedulers = list(schedulers)
+        for a, b in zip(self.schedulers, self.schedulers[1:]):
+            if abs(a.final_value - b.init_value) > 1e-8 * max(1.0, abs(a.final_value)):
+                raise ValueError(f"schedule ends at {a.final_value} but the next one starts at {b.init_value}")
+
+    @property
+    def total_iters(self) -> int:
+        return sum(s.total_iters for s in self.schedulers)
+
+    @property
+    def init_value(self) -> float:
+        return self.schedulers[0].init_value
+
+    @property
+    def final_value(self) -> float:
+        return self.schedulers[-1].final_value
+
+    def get(self, step: int) -> float:
+        if step < 0 or step > self.total_iters:
+            raise ValueError(f"step {step} outside [0, {self.total_iters}]")
+        for s in self.schedulers:
+            if step <= s.total_iters:
+                return s.get(step)
+            step -= s.total_iters
+        return self.final_value

@@ -399,3 +399,48 @@ def test_tiny_utility_modules(tmp_path, monkeypatch):
         fs.validate_shared_path("", "fileroot")
     assert fs.is_network_fs(str(tmp_path)) in (True, False, None)
     assert constants.DEFAULT_VECTORIZED_ALIGNMENT_BYTES == 16 and "recompute" in constants.PROX_LOGP_METHODS_ALL
+
+
+def test_partition_schedule_and_seed_helpers():
+    import numpy as np
+
+    from areal_b200.utils import names, seqpack, timeutil
+    from areal_b200.utils.seeding import Shuffler
+
+    assert seqpack.get_allocate_fn("ffd") is seqpack.ffd_allocate and seqpack.get_allocate_fn("kk") is seqpack.kk_allocate
+    with pytest.raises(ValueError):
+        seqpack.get_allocate_fn("best")
+    parts = seqpack.min_abs_diff_partition([5, 1, 1, 1, 5, 1, 1, 5], 3)
+    assert parts[0][0] == 0 and parts[-1][1] == 8 and len(parts) == 3
+    sums = [sum([5, 1, 1, 1, 5, 1, 1, 5][a:b]) for a, b in parts]
+    assert max(sums) == 7                                          # [5,1,1] [1,5,1] [1,5] or as good
+    with pytest.raises(ValueError):
+        seqpack.min_abs_diff_partition([1, 2], 3)
+    with pytest.raises(ValueError):
+        seqpack.min_abs_diff_partition(np.ones((2, 2)), 1)
+    lens = [100, 90, 10, 10, 50, 50, 40, 60]
+    perm, diff = seqpack.reorder_to_balanced_batches(lens, 2)
+    assert sorted(perm.tolist()) == list(range(8))
+    loads = [sum(lens[i] for i in perm[j:j + 2]) for j in range(0, 8, 2)]
+    assert max(loads) - min(loads) == diff and diff <= 10 and loads == sorted(loads, reverse=True)
+    assert seqpack.flat2d([[1, 2], [3]]) == [1, 2, 3]
+    lin = timeutil.LinearScheduler(1.0, 10, end_value=0.0)
+    assert lin.get(0) == 1.0 and abs(lin.get(5) - 0.5) < 1e-12 and lin.final_value == 0.0
+    cos = timeutil.CosineDecayScheduler(1.0, 10, end_value=0.2)
+    assert cos.get(0) == 1.0 and abs(cos.get(5) - 0.6) < 1e-12 and abs(cos.get(10) - 0.2) < 1e-12
+    assert abs(timeutil.ExponentialScheduler(2.0, 4, decay=0.5).get(3) - 0.25) < 1e-12
+    ch = timeutil.ChainedScheduler([timeutil.ConstantScheduler(1.0, 3), lin])
+    assert ch.total_iters == 13 and ch.get(2) == 1.0 and abs(ch.get(8) - 0.5) < 1e-12 and ch.final_value == 0.0
+    with pytest.raises(ValueError):
+        timeutil.ChainedScheduler([lin, timeutil.ConstantScheduler(1.0, 3)])   # 0.0 does not meet 1.0
+    with pytest.raises(ValueError):
+        lin.get(11)
+    a, b = Shuffler("k"), Shuffler("k")
+    sa = [a.next_shuffle() for _ in range(3)]
+    assert sa == [b.next_shuffle() for _ in range(3)] and len(set(sa)) == 3 and Shuffler("other").next_shuffle() != sa[0]
+    c = Shuffler("k")
+    c.load_state_dict({"key": "k", "cnt": 2})
+    assert c.next_shuffle() == sa[2]
+    assert names.trial_registry("e", "t").endswith("/e/t") and names.trial_registry("e", "t").startswith(names.registry_root())
+    assert names.worker_discovery("e", "t", "rollout") == names.workers("e", "t", "rollout")
+    assert names.worker_discovery("e", "t", "rollout", 3) == names.worker("e", "t", "rollout", 3)
