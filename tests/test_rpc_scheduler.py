@@ -50,6 +50,46 @@ def test_rtensor_local_roundtrip():
         rtensor.localize(h)
 
 
+def test_rtensor_shards_on_several_owners_backend_buffer_and_removal():
+    """A handle over the rows of two workers: localising fetches each owner once (all its shards in one request),
+    pads the ragged sequence dimension and concatenates; a second localise is served from the fetch buffer."""
+    mem = rtensor.MemoryBackend()
+    prev = rtensor.set_backend(mem)
+    rtensor.clear_fetch_buffer()
+    try:
+        a1, a2, b1 = torch.ones(2, 3), torch.full((1, 3), 2.0), torch.full((2, 5), 3.0)
+        s1, s2 = rtensor.store(a1, "w0:1"), rtensor.store(a2, "w0:1")
+        s3 = rtensor.store(b1, "w1:1")
+        assert (s1.addr, s1.rows) == ("w0:1", 2) and len(mem.stores["w0:1"]) == 2
+        parts = [rtensor.RTensor(s.shard_id, s.addr, tuple(t.shape), "float32") for s, t in ((s1, a1), (s2, a2), (s3, b1))]
+        h = rtensor.RTensor.cat(parts)
+        assert h.shape == (5, 5) and len(h.shard_infos()) == 3
+        wire = deserialize_value(serialize_value({"x": h}))["x"]
+        assert [s.shard_id for s in wire.shard_infos()] == [s1.shard_id, s2.shard_id, s3.shard_id]
+        before = rtensor.fetch_buffer_stats()
+        full = wire.to_local()
+        assert full.shape == (5, 5) and full[:2, :3].eq(1).all() and full[:3, 3:].eq(0).all() and full[3:].eq(3).all()
+        assert mem.fetches == 2                                       # one request per owner, not per shard
+        again = rtensor.localize({"x": h})["x"]
+        st = rtensor.fetch_buffer_stats()
+        assert torch.equal(again, full) and mem.fetches == 2 and st["hits"] - before["hits"] == 3 and st["entries"] == 3
+        assert sorted(rtensor.flatten_shard_ids({"x": h, "y": [parts[0]]})) == sorted([s1.shard_id, s2.shard_id, s3.shard_id, s1.shard_id])
+        rtensor.remove([s1, s2])
+        assert len(mem.stores["w0:1"]) == 0 and rtensor.fetch_buffer_stats()["entries"] == 1
+        with pytest.raises(KeyError):
+            wire.to_local()
+        local = rtensor.store(torch.zeros(4))
+        assert rtensor.storage_stats()["entries"] >= 1 and rtensor.fetch([local])[0].shape == (4,)
+        rtensor.remove([local])
+        with pytest.raises(ValueError):
+            rtensor.RTensor.cat([])
+        with pytest.raises(ImportError):
+            rtensor.RayRTensorBackend()
+    finally:
+        rtensor.set_backend(prev)
+        rtensor.clear_fetch_buffer()
+
+
 @pytest.fixture
 def sched(tmp_path):
     s = LocalScheduler(gpu_devices=[0, 1], log_dir=str(tmp_path), startup_timeout=60)
