@@ -318,3 +318,86 @@ class RemoteRolloutClient(InferenceEngine):
 
     def export_stats(self) -> dict[str, float]:
         return {"rollout/pause_latency": self.last_pause_latency}
+
+
+# --------------------------------------------------------------------------- rollout under a model-parallel trainer
+class RedistributedData:
+    """What :func:`redistribute_trajectories` returns: every rank's share (``all_data``), this rank's own
+    (``data``), the row indices of the pooled batch that went to each rank (``group_indices``) and this rank's
+    index."""
+
+    def __init__(self, all_data: list[dict[str, Any]], data: dict[str, Any], rank: int, group_indices: list[list[int]]):
+        self.all_data, self.data, self.rank, self.group_indices = all_data, data, rank, group_indices
+
+
+def redistribute_trajectories(batch: dict[str, Any] | None, group=None, granularity: int = 1,
+                              algorithm: str = "greedy") -> RedistributedData:
+    """Pools the batches that the data-parallel heads rolled out and deals them out again so that every rank trains
+    on about the same number of tokens: sequence lengths of asynchronous rollouts vary a lot, and the step takes as
+    long as the most loaded rank. ``granularity`` consecutive samples (a sample group) stay on one rank.
+    ``algorithm``: ``greedy`` (largest first into the lightest rank, equal sample counts) or ``kk``
+    (Karmarkar-Karp). ``group``: the data-parallel group (``None`` with one rank: the batch comes back as it is)."""
+    from ..utils.data import all_gather_tensor_container
+    from ..utils.seqpack import kk_allocate
+
+    world = dist.get_world_size(group) if (dist.is_initialized() and group is not None) else 1
+    rank = dist.get_rank(group) if world > 1 else 0
+    pooled = all_gather_tensor_container(batch, group) if world > 1 else [batch]
+    pooled = [b for b in pooled if b]
+    if not pooled:
+        return RedistributedData([], {}, rank, [])
+    whole = pooled[0] if len(pooled) == 1 else concat_padded_tensors(pooled)
+    if world == 1:
+        B = whole["attention_mask"].shape[0]
+        return RedistributedData([whole], whole, 0, [list(range(B))])
+    B = whole["attention_mask"].shape[0]
+    g = max(granularity, 1)
+    assert B % g == 0 and (B // g) >= world, f"{B} samples in groups of {g} cannot feed {world} ranks"
+    lens = whole["attention_mask"].sum(-1).tolist()
+    units = [int(sum(lens[i:i + g])) for i in range(0, B, g)]
+    parts = kk_allocate(units, world, equal_size=True) if algorithm == "kk" else \
+        balanced_greedy_partition(units, world, equal_size=(len(units) % world == 0))
+    indices = [[u * g + j for u in sorted(p) for j in range(g)] for p in parts]
+    shares = []
+    for rows in indices:
+        idx = torch.tensor(rows, dtype=torch.long)
+        shares.append({k: (v[idx] if torch.is_tensor(v) and v.dim() >= 1 and v.shape[0] == B else
+                           ([v[i] for i in rows] if isinstance(v, list) and len(v) == B else v))
+                       for k, v in whole.items()})
+    return RedistributedData(shares, shares[rank], rank, indices)
+
+
+class DistRolloutCoordinator:
+    """Rollout for a trainer with model parallelism: only the data-parallel heads talk to the inference engine, the
+    trajectories are re-balanced over the data-parallel ranks by token count, and every rank of a replica
+    (tensor / sequence / pipeline peers) receives its head's share.
+    Reference: areal/infra/dist_rollout.py (DistRolloutCoordinator :97, redistribute_trajectories)."""
+
+    def __init__(self, rollout_engine: InferenceEngine, train_engine):
+        self.rollout_engine, self.train_engine = rollout_engine, train_engine
+
+    def _finish(self, batch, granularity: int):
+        from ..utils.data import broadcast_tensor_container
+
+        te = self.train_engine
+        if te.is_data_parallel_head():
+            dp_group = te.data_parallel_group if te.data_parallel_world_size > 1 else None
+            batch = redistribute_trajectories(batch, dp_group, granularity).data
+        group = te.context_and_model_parallel_group
+        if group is None:
+            return batch
+        return broadcast_tensor_container(batch, src_rank=te.current_data_parallel_head(), group=group)
+
+    def rollout_batch(self, data, workflow=None, workflow_kwargs=None, group_size: int = 1):
+        batch = None
+        if self.train_engine.is_data_parallel_head():
+            batch = self.rollout_engine.rollout_batch(data, workflow, workflow_kwargs, group_size=group_size)
+        return self._finish(batch, group_size)
+
+    def prepare_batch(self, dataloader, workflow=None, workflow_kwargs=None, should_accept_fn=None,
+                      group_size: int = 1, dynamic_bs: bool = False):
+        batch = None
+        if self.train_engine.is_data_parallel_head():
+            batch = self.rollout_engine.prepare_batch(dataloader, workflow, workflow_kwargs, should_accept_fn,
+                                                      group_size=group_size, dynamic_bs=dynamic_bs)
+        return self._finish(batch, group_size)

@@ -444,3 +444,42 @@ def test_partition_schedule_and_seed_helpers():
     assert names.trial_registry("e", "t").endswith("/e/t") and names.trial_registry("e", "t").startswith(names.registry_root())
     assert names.worker_discovery("e", "t", "rollout") == names.workers("e", "t", "rollout")
     assert names.worker_discovery("e", "t", "rollout", 3) == names.worker("e", "t", "rollout", 3)
+
+
+def test_trajectories_are_rebalanced_over_data_parallel_ranks():
+    import subprocess
+    import sys
+
+    from tests.conftest import free_port
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+           "--master-port", str(free_port()), os.path.join(root, "tests", "torchrun", "run_redistribute.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-1500:] + r.stderr[-2500:]
+    # one rank: nothing to do
+    from areal_b200.infra.dist_rollout import DistRolloutCoordinator, redistribute_trajectories
+
+    b = {"attention_mask": torch.ones(3, 4, dtype=torch.bool), "x": torch.arange(3)}
+    out = redistribute_trajectories(b)
+    assert out.data is b and out.group_indices == [[0, 1, 2]]
+    assert redistribute_trajectories(None).data == {}
+
+    class Eng:
+        data_parallel_world_size, data_parallel_group, context_and_model_parallel_group = 1, None, None
+
+        def is_data_parallel_head(self):
+            return True
+
+        def current_data_parallel_head(self):
+            return 0
+
+    class Ro:
+        def rollout_batch(self, data, workflow=None, workflow_kwargs=None, group_size=1):
+            return dict(b, n=len(data))
+
+        def prepare_batch(self, dl, workflow=None, workflow_kwargs=None, should_accept_fn=None, group_size=1, dynamic_bs=False):
+            return dict(b, dyn=dynamic_bs)
+
+    co = DistRolloutCoordinator(Ro(), Eng())
+    assert co.rollout_batch([1, 2])["n"] == 2 and co.prepare_batch(None, dynamic_bs=True)["dyn"] is True
