@@ -234,8 +234,16 @@ class PPOTrainer:
         eng = self.actor_engine
         mp = getattr(eng, "context_and_model_parallel_group", None)
         if mp is None or dist.get_world_size(mp) == 1:
-            return self.rollout_client.prepare_batch(self.dataloader, workflow, workflow_kwargs,
-                                                     group_size=group, dynamic_bs=cfg.dynamic_bs)
+            batch = self.rollout_client.prepare_batch(self.dataloader, workflow, workflow_kwargs,
+                                                      group_size=group, dynamic_bs=cfg.dynamic_bs)
+            if self.colocated and eng.mesh is None and eng.world_size > 1 and not cfg.dynamic_bs \
+                    and os.environ.get("AREAL_B200_BALANCE_DP", "1") == "1":
+                # every rank rolled out its own prompts; response lengths differ a lot, and the step takes as long
+                # as the most loaded rank: deal the pooled samples out again by token count (sample groups intact)
+                from ..infra.dist_rollout import redistribute_trajectories
+
+                batch = redistribute_trajectories(batch, eng.cpu_group, granularity=group).data
+            return batch
         box = [None]
         if eng.is_data_parallel_head():
             box[0] = self.rollout_client.prepare_batch(self.dataloader, workflow, workflow_kwargs,
