@@ -303,3 +303,22 @@ class PPOActorEngine:
         if name in ("engine", "actor"):
             raise AttributeError(name)
         return getattr(self.engine, name)
+
+
+# controller-side handles of single-controller mode: a ``TrainController`` whose workers run the engine classes
+# above; ``compute_logp`` / ``compute_advantages`` / ``ppo_update`` are forwarded to every data-parallel rank with
+# the batch split by tokens (infra/controller/train_controller.py)
+def _controller(engine_cls_name: str):
+    from ...infra.controller.train_controller import TrainController
+
+    class _Ctl(TrainController):
+        def __init__(self, config, scheduler, engine: str | type | None = None):
+            super().__init__(engine or f"{__name__}.{engine_cls_name}", config, scheduler)
+
+    return _Ctl
+
+
+PPOActorController = _controller("PPOActorEngine")
+PPOActorController.__name__ = PPOActorController.__qualname__ = "PPOActorController"
+PPOActorControllerV2 = PPOActorController
+from ...utils.functional import compute_prox_logp_approximations  # noqa: E402,F401  (re-exported)

@@ -50,3 +50,45 @@ def critic_loss_fn(values: torch.Tensor, input_data: dict[str, Any], eps_clip: f
         stats_tracker.stat(value_loss=stat["loss"], new_values=values.detach().float(),
                            returns=input_data["returns"].float(), denominator="n_valid_tokens")
     return loss
+
+
+ppo_loss_fn = critic_loss_fn  # the name of the reference's critic loss (areal/trainer/ppo/critic.py:105)
+
+
+class PPOCriticEngine:
+    """A train engine (``is_critic``) with the critic's algorithm methods on it: what a single-controller run creates
+    in every worker process, so that ``compute_values`` / ``ppo_update`` run next to the model."""
+
+    def __init__(self, config: PPOCriticConfig):
+        from ...engine.train_engine import B200TrainEngine
+
+        config.is_critic = True
+        self.engine = B200TrainEngine(config)
+        self.critic = PPOCritic(config, self.engine)
+
+    def compute_values(self, data):
+        return self.critic.compute_values(data)
+
+    def ppo_update(self, data):
+        return self.critic.ppo_update(data)
+
+    def __getattr__(self, name):
+        if name in ("engine", "critic"):
+            raise AttributeError(name)
+        return getattr(self.engine, name)
+
+
+def _critic_controller():
+    from ...infra.controller.train_controller import TrainController
+
+    class PPOCriticController(TrainController):
+        """Controller-side handle whose workers run :class:`PPOCriticEngine`."""
+
+        def __init__(self, config, scheduler, engine: str | type | None = None):
+            super().__init__(engine or f"{__name__}.PPOCriticEngine", config, scheduler)
+
+    return PPOCriticController
+
+
+PPOCriticController = _critic_controller()
+PPOCriticControllerV2 = PPOCriticController

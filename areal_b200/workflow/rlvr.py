@@ -34,6 +34,14 @@ def default_get_input_ids(data: dict[str, Any], tokenizer, enable_thinking: bool
     return list(tokenizer.encode(data["prompt"]))
 
 
+def default_data_extract_prompt_fn(data: dict[str, Any]):
+    """The prompt of a dataset item as chat messages (``messages``) or, for pre-tokenised items, its ids."""
+    return data["messages"] if "messages" in data else data.get("input_ids", data.get("prompt"))
+
+
+default_get_input_ids_fn = default_get_input_ids  # the name the reference uses
+
+
 class RLVRWorkflow(RolloutWorkflow):
     def __init__(self, reward_fn: Callable[..., float] | str, gconfig: GenerationHyperparameters,
                  tokenizer=None, enable_thinking: bool = False, get_input_ids_fn: Callable | None = None,

@@ -483,3 +483,21 @@ def test_trajectories_are_rebalanced_over_data_parallel_ranks():
 
     co = DistRolloutCoordinator(Ro(), Eng())
     assert co.rollout_batch([1, 2])["n"] == 2 and co.prepare_batch(None, dynamic_bs=True)["dyn"] is True
+
+
+def test_reference_named_entry_points_exist_and_work():
+    from areal_b200.reward import MathVerifyWorker, get_math_verify_worker
+    from areal_b200.trainer.ppo.actor import PPOActorController, PPOActorControllerV2, compute_prox_logp_approximations
+    from areal_b200.trainer.ppo.critic import PPOCriticController, PPOCriticEngine, critic_loss_fn, ppo_loss_fn
+    from areal_b200.infra.controller.train_controller import TrainController
+    from areal_b200.workflow.rlvr import default_data_extract_prompt_fn, default_get_input_ids, default_get_input_ids_fn
+
+    w = get_math_verify_worker()
+    assert w is get_math_verify_worker() and isinstance(w, MathVerifyWorker)
+    assert w.verify("so the result is \\boxed{42}", "42") == 1.0 and w.verify("it is \\boxed{41}", "42") == 0.0
+    assert w.verify(None, "42") == 0.0 and w.verify("\\boxed{\\frac{1}{2}}", "0.5") == 1.0
+    assert issubclass(PPOActorController, TrainController) and PPOActorControllerV2 is PPOActorController
+    assert issubclass(PPOCriticController, TrainController) and ppo_loss_fn is critic_loss_fn and callable(compute_prox_logp_approximations)
+    assert hasattr(PPOCriticEngine, "compute_values") and default_get_input_ids_fn is default_get_input_ids
+    assert default_data_extract_prompt_fn({"messages": [{"role": "user", "content": "q"}]})[0]["content"] == "q"
+    assert default_data_extract_prompt_fn({"input_ids": [1, 2]}) == [1, 2]
