@@ -142,3 +142,6 @@ def create_gateway_app(admin_api_key: str = "areal-admin-key", forward: Forwarde
 
     app.state.ready, app.state.routes = ready, routes
     return app
+
+
+create_proxy_gateway_app = create_gateway_app  # the name of the reference's factory

@@ -73,33 +73,22 @@ class OpenAIProxyWorkflow(RolloutWorkflow):
         return client.export_interactions(self.export_style, self.turn_discount)
 
     async def _run_online(self, data):
-        import aiohttp
-
-        from ...infra.rpc.serialization import deserialize_value
+        from ...utils.data import concat_padded_tensors
+        from .client_session import OpenAIProxyClient
 
         assert self.proxy_url, "online mode needs proxy_url"
-        admin = {"Authorization": f"Bearer {self.admin_api_key}"}
-        async with aiohttp.ClientSession() as http:
-            async with http.post(f"{self.proxy_url}/rl/start_session", json={}, headers=admin) as r:
-                r.raise_for_status()
-                sess = await r.json()
-            reward = await self.agent.run(data, base_url=f"{self.proxy_url}/v1", api_key=sess["api_key"],
-                                          http_client=http)
-            key = {"Authorization": f"Bearer {sess['api_key']}"}
-            if isinstance(reward, dict):
+        async with OpenAIProxyClient(self.proxy_url, self.admin_api_key) as sess:
+            reward = await self.agent.run(data, base_url=sess.base_url, api_key=sess.session_api_key)
+            if isinstance(reward, dict) and "session_id" in reward and "api_key" in reward:
+                # an online agent that waited at the gateway: the external user's session is the one to export
+                await sess.end()  # the workflow's own (unused) session
+                sess.session_id, sess._key = reward["session_id"], reward["api_key"]
+            elif isinstance(reward, dict):
                 for k, v in reward.items():
-                    await http.post(f"{self.proxy_url}/rl/set_reward", json={"interaction_id": k, "reward": v}, headers=key)
+                    await sess.set_reward(k, v)
             elif reward is not None:
-                await http.post(f"{self.proxy_url}/rl/set_reward", json={"reward": float(reward)}, headers=key)
-            await http.post(f"{self.proxy_url}/rl/end_session", json={}, headers=key)
-            async with http.post(f"{self.proxy_url}/export_trajectories",
-                                 json={"session_id": sess["session_id"], "discount": self.turn_discount,
-                                       "style": self.export_style}, headers=admin) as r:
-                r.raise_for_status()
-                out = await r.json()
-        inter = {k: deserialize_value(v) for k, v in out["interactions"].items()}
+                await sess.set_last_reward(float(reward))
+            inter = await sess.export_interactions(self.turn_discount, self.export_style)
         if not inter:
             return None
-        from ...utils.data import concat_padded_tensors
-
         return concat_padded_tensors(list(inter.values()))

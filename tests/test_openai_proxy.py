@@ -248,3 +248,65 @@ def test_gateway_routes_session_keys_to_the_worker_that_owns_them():
         other = workers["w1:1" if d["worker_addr"] == "w0:1" else "w0:1"]
         assert TestClient(other).post("/export_trajectories", json={"session_id": d["session_id"]},
                                       headers={"Authorization": "Bearer adm"}).status_code == 404
+
+
+def test_proxy_client_session_and_online_workflow_mode():
+    """The client of one proxy session (start, talk with the session key, reward, export), and the workflow's
+    ``online`` mode built on it, against an in-process proxy server."""
+    import asyncio
+
+    import httpx
+
+    from areal_b200.openai.proxy.client_session import (OpenAIProxyClient, ProxyRequestError, post_json_with_retry,
+                                                        set_last_interaction_reward, should_retry)
+
+    app = create_proxy_app(Engine(), Tok(), admin_api_key="adm")
+    attempts = {"n": 0}
+
+    async def post(url, body, headers):
+        async with httpx.AsyncClient(transport=httpx.ASGITransport(app=app), base_url="http://px") as c:
+            r = await c.post(url.replace("http://px", ""), json=body, headers=headers)
+            if r.status_code >= 400:
+                raise ProxyRequestError(url, r.status_code, r.text)
+            return r.json()
+
+    async def flaky(url, body, headers):
+        attempts["n"] += 1
+        if attempts["n"] < 3:
+            raise ProxyRequestError(url, 503, "busy")
+        return await post(url, body, headers)
+
+    class Agent:
+        async def run(self, data, base_url=None, api_key=None, **extra):
+            assert base_url == "http://px/v1"
+            out = await post(base_url + "/chat/completions", {"messages": data["messages"], "max_tokens": 4},
+                             {"Authorization": f"Bearer {api_key}"})
+            assert out["object"] == "chat.completion"
+            return 0.75
+
+    async def scenario():
+        assert should_retry(ProxyRequestError("u", 503, "")) and not should_retry(ProxyRequestError("u", 401, ""))
+        adm = {"Authorization": "Bearer adm"}
+        assert (await post_json_with_retry("http://px/grant_capacity", {}, adm, post=flaky, delay=0.001)) is not None
+        assert attempts["n"] == 3                                    # two 503 answers were retried
+        with pytest.raises(ProxyRequestError):
+            async with OpenAIProxyClient("http://px", "wrong-key", post=post, retries=0):
+                pass
+        async with OpenAIProxyClient("http://px/", "adm", post=post) as s:
+            key = {"Authorization": f"Bearer {s.session_api_key}"}
+            r = await post(s.base_url + "/chat/completions", {"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4}, key)
+            await s.set_reward(r["id"], 0.25)
+            await set_last_interaction_reward("http://px", s.session_api_key, 0.5, post=post)
+            inter = await s.export_interactions(discount=0.9)
+        assert len(inter) == 1 and float(next(iter(inter.values()))["rewards"][0]) == 0.5
+        wf = OpenAIProxyWorkflow(Agent(), mode="online", proxy_url="http://px", admin_api_key="adm")
+        import areal_b200.openai.proxy.client_session as cs
+
+        orig, cs.post_json = cs.post_json, post
+        try:
+            traj = await wf.arun_episode(None, {"messages": [{"role": "user", "content": "q"}]})
+        finally:
+            cs.post_json = orig
+        assert traj["rewards"].tolist() == [0.75] and traj["input_ids"].shape[0] == 1
+
+    asyncio.run(scenario())
