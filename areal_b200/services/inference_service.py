@@ -7,7 +7,10 @@
                the pause flag that makes new requests wait while weights are being swapped, and
                the export of a finished session as a training trajectory;
 * gateway    – public routes: ``/generate``, ``/sessions/*``, ``/pause``, ``/continue``,
-               ``/set_version``, ``/workers``.
+               ``/set_version``, ``/workers``; with a tokenizer also ``/v1/chat/completions`` (OpenAI
+               protocol over the engines, recorded per session and exported as training tensors by
+               ``/sessions/{id}/export_chat``) with *external models*: chat requests that name a
+               configured external model are forwarded to that provider instead.
 Reference: areal/experimental/inference_service/{gateway,router,data_proxy,controller}.
 """
 
@@ -97,7 +100,13 @@ class SessionStore:
         return dict(input_ids=seq, logprobs=logp, loss_mask=mask, versions=ver, reward=s.reward)
 
 
-def create_gateway_app(token: str | None = None, strategy: str = "round_robin", post=None) -> FastAPI:
+def create_gateway_app(token: str | None = None, strategy: str = "round_robin", post=None, tokenizer=None,
+                       external_models: dict[str, dict] | None = None, external_post=None) -> FastAPI:
+    """``tokenizer``: turns on ``POST /v1/chat/completions`` (OpenAI protocol; ``session_id`` in the body or an
+    ``X-Session-Id`` header keeps a conversation on one engine and records it for export).
+    ``external_models``: ``{model name: {"url": ..., "api_key": ...}}``: chat requests that name such a model
+    are forwarded to that OpenAI-compatible endpoint instead of the engines (a user simulator or a judge that
+    is not the policy); they are not recorded. ``external_post(url, body, headers) -> dict`` is its transport."""
     app = FastAPI()
     reg = WorkerRegistry(strategy)
     store = SessionStore()
@@ -184,6 +193,77 @@ def create_gateway_app(token: str | None = None, strategy: str = "round_robin", 
             post(f"http://{w['addr']}/call", {"method": "set_version", "args": serialize_value([v]),
                                               "kwargs": serialize_value({})})
         return {"version": v}
+
+    external = dict(external_models or {})
+    external_post = external_post or (lambda url, body, headers: request_with_retry(
+        "POST", url, json=body, headers=headers, max_retries=2, timeout=600).json())
+    chat_clients: dict[str, Any] = {}  # session id -> the OpenAI-protocol client that records its completions
+
+    class _RoutedEngine:
+        """What the protocol client sees as its engine: generation goes through the registry, pinned to a session."""
+
+        def __init__(self, sid):
+            self.sid = sid
+
+        async def agenerate(self, req):
+            while state["paused"]:
+                resume.clear()
+                await asyncio.wait_for(resume.wait(), timeout=3600)
+            import dataclasses
+
+            wire = dataclasses.replace(req, tokenizer=None)  # the engine worker has its own; it does not travel
+            resp = await asyncio.get_running_loop().run_in_executor(None, lambda: call_engine("generate", self.sid, wire))
+            resp.tokenizer = req.tokenizer
+            return resp
+
+        def get_version(self):
+            return state["version"]
+
+    @app.post("/v1/chat/completions")
+    async def chat_completions(req: Request):
+        auth(req)
+        b = await req.json()
+        model = b.get("model", "default")
+        if model in external:
+            ext = external[model]
+            body = {k: v for k, v in b.items() if k != "session_id"}
+            body["model"] = ext.get("model", model)
+            headers = {"Authorization": f"Bearer {ext['api_key']}"} if ext.get("api_key") else {}
+            return await asyncio.get_running_loop().run_in_executor(
+                None, lambda: external_post(ext["url"].rstrip("/") + "/chat/completions", body, headers))
+        if tokenizer is None:
+            raise HTTPException(status_code=501, detail="this gateway was started without a tokenizer")
+        from ..openai.client import ArealOpenAI
+
+        sid = b.get("session_id") or req.headers.get("x-session-id")
+        client = chat_clients.get(sid) if sid else None
+        if client is None:
+            client = ArealOpenAI(_RoutedEngine(sid), tokenizer)
+            if sid:
+                store.get(sid)  # 404 for a session that was never started
+                chat_clients[sid] = client
+        return await client._complete(b["messages"], model=model, tools=b.get("tools"),
+                                      max_new=b.get("max_completion_tokens") or b.get("max_tokens"),
+                                      temperature=b.get("temperature"), top_p=b.get("top_p"), stop=b.get("stop"),
+                                      as_dict=True)
+
+    @app.post("/sessions/{sid}/export_chat")
+    async def export_chat(sid: str, req: Request):
+        """Ends a chat session: rewards the last completion (``reward``) or single ones (``rewards``: id → value)
+        and returns the recorded completions as training tensors."""
+        auth(req)
+        b = await req.json() if await req.body() else {}
+        client = chat_clients.pop(sid, None)
+        if client is None:
+            raise HTTPException(status_code=404, detail=f"session {sid} has no chat completions")
+        for k, v in (b.get("rewards") or {}).items():
+            client.set_reward(k, float(v))
+        if b.get("reward") is not None:
+            client.set_last_reward(float(b["reward"]))
+        inter = client.export_interactions(b.get("style", "individual"), float(b.get("discount", 1.0)))
+        store.pop(sid)
+        reg.end_session(sid)
+        return {"interactions": {k: serialize_value(v.to_tensor_dict()) for k, v in inter.items()}}
 
     app.state.registry, app.state.sessions, app.state.flags = reg, store, state
     return app

@@ -279,3 +279,47 @@ def test_gateway_inference_engine_runs_workflows_through_the_service():
         assert all("pause_generation" in e.calls and "continue_generation" in e.calls for e in engines)
     finally:
         eng.destroy()
+
+
+def test_inference_gateway_speaks_the_chat_protocol_and_forwards_external_models():
+    """Chat completions on the gateway: a session's turns stay on one engine and come back as training tensors;
+    a request that names an external model goes to that provider untouched and is not recorded."""
+    from tests.test_openai_proxy import Tok
+
+    net = Net()
+    engines = [EchoEngineApp("e0"), EchoEngineApp("e1")]
+    for i, e in enumerate(engines):
+        net.add(f"e{i}:1", e.app)
+    sent = []
+
+    def provider(url, body, headers):
+        sent.append((url, body, headers))
+        return {"id": "ext-1", "object": "chat.completion", "model": body["model"],
+                "choices": [{"index": 0, "finish_reason": "stop", "message": {"role": "assistant", "content": "judge says yes"}}]}
+
+    gw = TestClient(inference_service.create_gateway_app(
+        post=net.post, tokenizer=Tok(), external_post=provider,
+        external_models={"judge": {"url": "https://provider/v1/", "api_key": "sk-x", "model": "big-judge"}}))
+    for i in range(2):
+        gw.post("/register", json={"worker_id": f"e{i}", "addr": f"e{i}:1"})
+    sid = gw.post("/sessions/start", json={}).json()["session_id"]
+    msgs = [{"role": "user", "content": "hi"}]
+    c1 = gw.post("/v1/chat/completions", json={"messages": msgs, "session_id": sid, "max_tokens": 4}).json()
+    assert c1["object"] == "chat.completion" and c1["choices"][0]["message"]["role"] == "assistant"
+    msgs += [c1["choices"][0]["message"], {"role": "user", "content": "more"}]
+    c2 = gw.post("/v1/chat/completions", json={"messages": msgs, "max_tokens": 4}, headers={"X-Session-Id": sid}).json()
+    assert sorted(e.calls.count("generate") for e in engines) == [0, 2]            # one engine served both turns
+    ext = gw.post("/v1/chat/completions", json={"messages": msgs, "model": "judge", "session_id": sid, "temperature": 0}).json()
+    assert ext["choices"][0]["message"]["content"] == "judge says yes"
+    url, body, headers = sent[0]
+    assert url == "https://provider/v1/chat/completions" and body["model"] == "big-judge" and "session_id" not in body
+    assert headers == {"Authorization": "Bearer sk-x"} and sum(e.calls.count("generate") for e in engines) == 2
+    out = gw.post(f"/sessions/{sid}/export_chat", json={"reward": 1.0, "rewards": {c1["id"]: 0.25}, "discount": 1.0}).json()
+    inter = {k: deserialize_value(v) for k, v in out["interactions"].items()}
+    assert set(inter) == {c1["id"], c2["id"]}
+    assert float(inter[c2["id"]]["rewards"][0]) == 1.0 and float(inter[c1["id"]]["rewards"][0]) == 0.25
+    assert int(inter[c1["id"]]["loss_mask"].sum()) == 2                            # the echo engine produced two tokens
+    assert gw.post(f"/sessions/{sid}/export_chat", json={}).status_code == 404
+    assert gw.post("/v1/chat/completions", json={"messages": msgs, "session_id": "nope"}).status_code == 404
+    plain = TestClient(inference_service.create_gateway_app(post=net.post))
+    assert plain.post("/v1/chat/completions", json={"messages": msgs}).status_code == 501
