@@ -103,6 +103,15 @@ class _PinnedStager:
         self.events[self.cur] = ev
 
 
+def _resolve_fn(fn):
+    """A loss or weight function given by import path (a controller or a service sent it from another process)."""
+    if isinstance(fn, str):
+        from ..utils.dynamic_import import import_from_string
+
+        return import_from_string(fn)
+    return fn
+
+
 class B200TrainEngine(TrainEngine):
     def __init__(self, config: TrainEngineConfig):
         self.config = config
@@ -664,6 +673,7 @@ class B200TrainEngine(TrainEngine):
         for critics); ``loss_weight_fn(mb) -> weight`` (e.g. the number of loss tokens).
         The total loss is the weight-averaged loss over all micro-batches of all ranks."""
         assert self.optimizer is not None, "engine was created without an optimizer"
+        loss_fn, loss_weight_fn = _resolve_fn(loss_fn), _resolve_fn(loss_weight_fn)
         self.model.train()
         mb_list = self._prepare_mb_list(input_)
         weights = [float(loss_weight_fn(mb)) for mb in mb_list.mbs]
@@ -697,6 +707,7 @@ class B200TrainEngine(TrainEngine):
 
     @torch.no_grad()
     def eval_batch(self, input_: dict[str, Any], loss_fn: Callable, loss_weight_fn: Callable):
+        loss_fn, loss_weight_fn = _resolve_fn(loss_fn), _resolve_fn(loss_weight_fn)
         self.model.eval()
         mb_list = self._prepare_mb_list(input_)
         weights = [float(loss_weight_fn(mb)) for mb in mb_list.mbs]
@@ -757,6 +768,12 @@ class B200TrainEngine(TrainEngine):
                     result[src, :b - a] = flat[a:b]
                     if eflat is not None:
                         ent_result[src, :b - a] = eflat[a:b]
+                    if not self.is_critic and b > a:
+                        # a sequence's last position has no next token: what the packed computation put there
+                        # belongs to its neighbour in the micro-batch, so it is cleared
+                        result[src, b - a - 1] = 0.0
+                        if eflat is not None:
+                            ent_result[src, b - a - 1] = 0.0
                     row += 1
                 base += out.shape[0]
         if pp:

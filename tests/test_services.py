@@ -323,3 +323,77 @@ def test_inference_gateway_speaks_the_chat_protocol_and_forwards_external_models
     assert gw.post("/v1/chat/completions", json={"messages": msgs, "session_id": "nope"}).status_code == 404
     plain = TestClient(inference_service.create_gateway_app(post=net.post))
     assert plain.post("/v1/chat/completions", json={"messages": msgs}).status_code == 501
+
+
+def sft_token_weight(mb):
+    return float(mb["loss_mask"].sum())
+
+
+def sft_mean_loss(logprobs, entropy, mb):
+    # position t holds log p(x[t+1] | x[<=t]): the mask of the NEXT token applies (a sequence's first token is
+    # never a target, so rolling the packed mask also clears every sequence's last position)
+    m = torch.roll(mb["loss_mask"], -1).float()
+    return -(logprobs * m).sum() / m.sum().clamp(min=1)
+
+
+def test_gateway_train_engine_drives_real_engines_through_the_service(tmp_path):
+    """The trainer-side handle of a training service over two real (CPU) train engines: a step through the
+    gateway equals the step of one engine on the whole batch, loss functions travel by import path, and an
+    evaluation batch that does not divide over the workers is padded and trimmed."""
+    from fastapi import FastAPI, Request
+
+    from areal_b200.api.cli_args import OptimizerConfig, TrainEngineConfig
+    from areal_b200.engine.train_engine import B200TrainEngine
+
+    def make_engine():
+        e = B200TrainEngine(TrainEngineConfig(experiment_name="e", trial_name="t", path="", init_from_scratch=True,
+                                              dtype="float32", model_preset="tiny-qwen2",
+                                              optimizer=OptimizerConfig(lr=1e-3, warmup_steps_proportion=0.0)))
+        e.create_process_group()
+        e.initialize(seed=5)
+        return e
+
+    def worker_app(eng):
+        app = FastAPI()
+
+        @app.post("/call")
+        async def call(req: Request):
+            b = await req.json()
+            out = getattr(eng, b["method"])(*deserialize_value(b["args"]), **deserialize_value(b["kwargs"]))
+            return {"result": serialize_value(out if not isinstance(out, B200TrainEngine) else None)}
+
+        return app
+
+    net = Net()
+    engines = [make_engine(), make_engine()]
+    for i, e in enumerate(engines):
+        net.add(f"t{i}:1", worker_app(e))
+    gw_app = training_service.create_gateway_app(token="tok", post=net.post)
+    gw = TestClient(gw_app)
+    hdr = {"Authorization": "Bearer tok"}
+    for i in range(2):
+        gw.post("/register", json={"worker_id": f"t{i}", "addr": f"t{i}:1", "rank": i}, headers=hdr)
+    client = training_service.GatewayTrainEngine(
+        "http://gw", token="tok", post=lambda url, body, headers: gw.post(url.replace("http://gw", ""), json=body, headers=headers).json())
+    assert client.n_workers() == 2
+    g = torch.Generator().manual_seed(0)
+    B, L = 5, 12
+    batch = {"input_ids": torch.randint(0, 1000, (B, L), generator=g), "attention_mask": torch.ones(B, L, dtype=torch.bool),
+             "loss_mask": torch.ones(B, L, dtype=torch.int32)}
+    batch["loss_mask"][:, 0] = 0
+    lp = client.forward_batch(batch)                                  # 5 samples over 2 workers: padded to 6, trimmed
+    ref = make_engine()
+    assert lp.shape == (B, L) and torch.allclose(lp, ref.forward_batch(batch), atol=1e-5)
+    # these two workers are separate processes without a common process group, so each scores its own share (in a
+    # deployment they are data-parallel ranks and all-reduce); the gateway reports the first rank's figure
+    from areal_b200.infra.controller.train_controller import dispatch_batch, pad_batch_for_dispatch
+
+    share0 = dispatch_batch(pad_batch_for_dispatch(batch, 2)[0], 2)[0][0]
+    ev = client.eval_batch(batch, sft_mean_loss, sft_token_weight)
+    assert abs(float(ev) - float(ref.eval_batch(share0, sft_mean_loss, sft_token_weight))) < 1e-4
+    with pytest.raises(ValueError, match="importable"):
+        client.train_batch(batch, lambda *a: 0.0, sft_token_weight)
+    client.set_version(4)
+    assert client.get_version() == 4 and all(e.get_version() == 4 for e in engines)
+    for e in engines + [ref]:
+        e.destroy()
