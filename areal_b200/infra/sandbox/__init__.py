@@ -5,7 +5,8 @@ This package has no network dependency: :class:`LocalSandbox` runs the snippet i
 interpreter process with CPU-time / memory / file-size limits, an empty environment, a private
 working directory and a wall-clock time-out, and returns stdout / stderr / exit code. It is a
 resource fence, not a security boundary against hostile code; deployments that need one put the
-same interface in front of a container or remote service (``SandboxClient`` protocol)."""
+same interface in front of a container or remote service (``SandboxClient`` protocol): ``sandbox/remote.py`` has
+an HTTP runner service around any sandbox and the matching client."""
 
 from __future__ import annotations
 

@@ -229,3 +229,37 @@ def test_external_user_lifecycle_against_a_gateway():
 
     result, done = asyncio.run(scenario())
     assert result["reward"] in (0.0, 1.0) and done["session_id"] == result["session_id"]
+
+
+def test_remote_sandbox_service_and_client():
+    from fastapi.testclient import TestClient
+
+    from areal_b200.infra.sandbox import code_reward
+    from areal_b200.infra.sandbox.remote import RemoteSandbox, create_runner_app
+    from areal_b200.reward.code import code_reward_fn
+
+    srv = TestClient(create_runner_app(token="tok", max_timeout=2.0))
+    assert srv.post("/run", json={"code": "print(1)"}).status_code == 401
+
+    def post(url, body, headers):
+        r = srv.post(url.replace("http://sb", ""), json=body, headers=headers)
+        r.raise_for_status()
+        return r.json()
+
+    sb = RemoteSandbox("http://sb/", "tok", post=post)
+    r = sb.run("import sys\nprint(int(sys.stdin.read()) * 2)", stdin="21")
+    assert r.ok and r.stdout.strip() == "42"
+    assert sb.run("raise SystemExit(3)").exit_code == 3
+    slow = sb.run("while True: pass", timeout=30.0)                 # the service caps the time-out at 2 s
+    assert slow.timed_out and not slow.ok
+    rs = sb.run_batch([{"code": "print('a')"}, {"code": "print('b')"}, {"code": "1/0"}])
+    assert [x.stdout.strip() for x in rs[:2]] == ["a", "b"] and not rs[2].ok
+    assert srv.get("/health").json()["runs"] == 6
+    assert code_reward(sb, "print(input()[::-1])", [("abc", "cba"), ("xy", "yx")]) == 1.0
+    tests = [{"input": "2 3\n", "output": "5"}]
+    good = "```python\na, b = map(int, input().split())\nprint(a + b)\n```"
+    assert code_reward_fn(None, good, None, None, tests=tests, sandbox=sb) == 1.0
+    down = RemoteSandbox("http://sb", "wrong", post=post)            # a refused request is a failed run, not an exception
+    bad = down.run("print(1)")
+    assert not bad.ok and "sandbox service error" in bad.stderr and code_reward_fn(None, good, None, None, tests=tests, sandbox=down) == 0.0
+    assert asyncio.run(sb.arun("print(7)")).stdout.strip() == "7"
