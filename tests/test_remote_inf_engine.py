@@ -248,3 +248,54 @@ def test_trainer_with_external_http_server(tmp_path, monkeypatch):
         assert not torch.equal(srv.engine.flat.flat, before)
     finally:
         srv.stop()
+
+
+def test_vllm_server_control_routes_against_a_stub_engine_client(tmp_path):
+    """The routes ``VLLMBackend`` calls, mounted on an app whose ``engine_client`` is a stub with vLLM's
+    asynchronous interface: pause aborts, an update reloads every worker from the path and drops the prefix
+    cache (pausing around it when the caller did not), versions are kept, the collective routes say 501."""
+    from fastapi import FastAPI
+    from fastapi.testclient import TestClient
+
+    from areal_b200.api.io_struct import WeightUpdateMeta
+    from areal_b200.engine.vllm_server import attach_areal_routes
+
+    class StubEngine:
+        def __init__(self):
+            self.calls = []
+
+        async def pause_generation(self, *, mode="abort", wait_for_inflight_requests=False, clear_cache=True):
+            self.calls.append(("pause", mode))
+
+        async def resume_generation(self):
+            self.calls.append(("resume",))
+
+        async def collective_rpc(self, method, timeout=None, args=(), kwargs=None):
+            self.calls.append(("rpc", method, dict(kwargs or {})))
+
+        async def reset_prefix_cache(self):
+            self.calls.append(("reset_prefix_cache",))
+
+    app = FastAPI()
+    c = TestClient(attach_areal_routes(app))
+    assert c.post("/areal_pause_generation", json={}).status_code == 503          # no engine yet
+    eng = app.state.engine_client = StubEngine()
+    be = VLLMBackend()
+    # the sequence the remote engine issues for a disk update: pause, update, resume
+    assert c.post(be.pause().endpoint, json=be.pause().payload).json()["paused"] is True
+    up = be.update_from_disk(WeightUpdateMeta(type="disk", path=str(tmp_path / "v3")))
+    r = c.post(up.endpoint, json=dict(up.payload, version=3)).json()
+    assert r["success"] and r["model_path"].endswith("v3")
+    assert c.post(be.resume().endpoint, json={}).json()["paused"] is False
+    assert eng.calls == [("pause", "abort"), ("rpc", "reload_weights", {"weights_path": str(tmp_path / "v3")}),
+                         ("reset_prefix_cache",), ("resume",)]
+    assert c.post("/areal_get_version", json={}).json()["version"] == 3
+    # an update without a pause before it pauses and resumes by itself
+    eng.calls.clear()
+    c.post("/areal_update_weights", json={"model_path": "/ckpt/v4"})
+    assert [x[0] for x in eng.calls] == ["pause", "rpc", "reset_prefix_cache", "resume"]
+    assert c.post("/areal_update_weights", json={}).status_code == 400
+    assert c.post("/areal_set_version", json={"version": 9}).json()["version"] == 9
+    for route in ("/areal_init_weights_update_group", "/areal_set_update_weight_meta", "/areal_update_weights_xccl"):
+        assert c.post(route, json={}).status_code == 501
+    assert c.post("/areal_update_weights_lora", json={"lora_name": "a"}).status_code == 400
