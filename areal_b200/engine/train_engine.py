@@ -936,6 +936,8 @@ class B200TrainEngine(TrainEngine):
             group = self._async_ckpt_group if ex is not None else self._all_cpu_group
             self._pending_ckpt = save_engine(self, meta.path, with_optim=meta.with_optim, process_group=group,
                                              executor=ex)
+            if meta.with_optim:
+                self._save_rng(meta.path)
             return
         else:
             raise ValueError(f"unknown weight format {meta.weight_format}")
@@ -946,8 +948,20 @@ class B200TrainEngine(TrainEngine):
 
             save_engine(self, os.path.join(meta.path, "optimizer"), with_optim=True, with_model=False,
                         process_group=self._all_cpu_group)
+            self._save_rng(meta.path)
         if dist.is_initialized() and self.world_size > 1:
             dist.barrier(group=self._cpu_group)
+
+    def _save_rng(self, path: str):
+        # a checkpoint with optimizer state is one a run resumes from: it also carries every rank's generators
+        from ..utils.rng_state import save_rng_state
+
+        save_rng_state(path, self.rank, self.world_size, self.device)
+
+    def _load_rng(self, path: str):
+        from ..utils.rng_state import load_rng_state
+
+        load_rng_state(path, self.rank, self.world_size, self.device)
 
     def _ckpt_executor(self):
         from concurrent.futures import ThreadPoolExecutor
@@ -979,6 +993,8 @@ class B200TrainEngine(TrainEngine):
 
             self.wait_for_checkpoint()
             load_engine(self, meta.path, with_optim=meta.with_optim, process_group=self._all_cpu_group)
+            if meta.with_optim:
+                self._load_rng(meta.path)
             return
         else:
             raise ValueError(f"unknown weight format {meta.weight_format}")
@@ -991,6 +1007,7 @@ class B200TrainEngine(TrainEngine):
 
                 load_engine(self, os.path.join(meta.path, "optimizer"), with_optim=True, with_model=False,
                             process_group=self._all_cpu_group)
+                self._load_rng(meta.path)
 
     # ----------------------------------------------------------------- offload
     def offload(self):

@@ -188,12 +188,21 @@ def test_recover_handler_round_trip_through_dcp(tmp_path):
     a = make(3)
     a.train_batch(batch_of(0), loss_fn, lambda mb: float(mb["loss_mask"].sum()))
     a.set_version(1)
+    import random
+
+    import numpy as np
+
     assert RecoverHandler(rc, ft).dump(a, StepInfo(0, 0, 0, 6), force=True)
+    # what the generators would have produced next, had the run gone on
+    expect = (random.random(), float(np.random.rand()), torch.rand(3))
     ckpt = RecoverHandler(rc, ft)._ckpt_path()
+    assert os.path.exists(os.path.join(ckpt, "rng", "rank00000.pt")), "every rank's generator states are in it"
     assert os.path.exists(os.path.join(ckpt, ".metadata")), "the recover checkpoint is a DCP directory"
     b = make(9)
     info = RecoverHandler(rc, ft).load(b)
     assert info is not None and b.get_version() == 1 and b.optimizer.step_count == 1
+    got = (random.random(), float(np.random.rand()), torch.rand(3))       # the streams continue where they were
+    assert got[0] == expect[0] and got[1] == expect[1] and torch.equal(got[2], expect[2])
     assert torch.equal(a.flat.flat, b.flat.flat) and torch.equal(a.optimizer.exp_avg, b.optimizer.exp_avg)
     sa = a.train_batch(batch_of(1), loss_fn, lambda mb: float(mb["loss_mask"].sum()))
     sb = b.train_batch(batch_of(1), loss_fn, lambda mb: float(mb["loss_mask"].sum()))
