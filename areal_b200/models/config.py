@@ -62,6 +62,22 @@ class ModelConfig:
     moe_load_balance_coeff: float = 0.0
     # shared expert that every token passes through, scaled by a sigmoid gate (Qwen2-MoE / Qwen3.5-MoE); 0 = none
     shared_expert_intermediate_size: int = 0
+    shared_expert_gated: bool = True  # DeepSeek-V3: the shared experts' output is added as it is
+    # group-limited routing (DeepSeek-V3): experts form `moe_n_group` groups, a token may only pick from its
+    # `moe_topk_group` best groups (a group's score: the sum of its two best experts); `moe_expert_bias`: the
+    # checkpoint carries the selection bias (`e_score_correction_bias`)
+    moe_n_group: int = 1
+    moe_topk_group: int = 1
+    moe_expert_bias: bool = False
+    # multi-head latent attention (DeepSeek-V3): queries and keys / values go through low-rank bottlenecks; a head's
+    # query / key is a `qk_nope_head_dim` part without position plus a `qk_rope_head_dim` rotary part (the key's
+    # rotary part is shared by all heads); `kv_lora_rank > 0` selects it, `q_lora_rank = 0` keeps a plain q projection
+    q_lora_rank: int = 0
+    kv_lora_rank: int = 0
+    qk_nope_head_dim: int = 0
+    qk_rope_head_dim: int = 0
+    v_head_dim: int = 0
+    rope_interleave: bool = False  # rotary pairs are neighbours (2i, 2i + 1) in the checkpoint's q / k layout
     decoder_sparse_step: int = 1
     mlp_only_layers: list[int] = field(default_factory=list)
     # critic / reward model: scalar head instead of the LM head
@@ -96,8 +112,25 @@ class ModelConfig:
         return self.attn_output_gate or any(t == "linear_attention" for t in self.layer_types)
 
     @property
+    def is_mla(self) -> bool:
+        return self.kv_lora_rank > 0
+
+    @property
     def rotary_dim(self) -> int:
+        if self.is_mla:
+            return self.qk_rope_head_dim
         return int(self.head_dim * self.partial_rotary_factor) // 2 * 2
+
+    def attn_params(self) -> int:
+        h, nh = self.hidden_size, self.num_attention_heads
+        if self.is_mla:
+            qk = self.qk_nope_head_dim + self.qk_rope_head_dim
+            q = (h * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * nh * qk) if self.q_lora_rank \
+                else h * nh * qk
+            kv = h * (self.kv_lora_rank + self.qk_rope_head_dim) + self.kv_lora_rank \
+                + self.kv_lora_rank * nh * (self.qk_nope_head_dim + self.v_head_dim)
+            return q + kv + nh * self.v_head_dim * h
+        return h * (self.q_size + 2 * self.kv_size) + self.q_size * h
 
     @property
     def q_size(self) -> int:
@@ -109,7 +142,7 @@ class ModelConfig:
 
     def num_params(self) -> int:
         h, L = self.hidden_size, self.num_hidden_layers
-        attn = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        attn = self.attn_params()
         if self.attention_bias:
             attn += self.q_size + 2 * self.kv_size
         if self.qk_norm:
@@ -117,7 +150,7 @@ class ModelConfig:
         dense_mlp = 3 * h * self.intermediate_size
         moe_mlp = self.num_experts * 3 * h * self.moe_intermediate_size + h * self.num_experts
         if self.shared_expert_intermediate_size:
-            moe_mlp += 3 * h * self.shared_expert_intermediate_size + h
+            moe_mlp += 3 * h * self.shared_expert_intermediate_size + (h if self.shared_expert_gated else 0)
         n = 0
         for i in range(L):
             n += attn + 2 * h + (moe_mlp if self.layer_is_moe(i) else dense_mlp)
@@ -149,10 +182,12 @@ class ModelConfig:
     def flops_per_token(self, seq_len: int, backward: bool = True) -> float:
         """Model FLOPs per token for a sequence of ``seq_len`` (causal attention)."""
         h, L = self.hidden_size, self.num_hidden_layers
-        lin = h * (self.q_size + 2 * self.kv_size) + self.q_size * h
+        lin = self.attn_params()
         act_mlp = (3 * h * self.moe_intermediate_size * self.num_experts_per_tok
                    if self.is_moe else 3 * h * self.intermediate_size)
-        per_layer = 2 * (lin + act_mlp) + 4 * self.q_size * (seq_len / 2)
+        qk_v = (self.num_attention_heads * (self.qk_nope_head_dim + self.qk_rope_head_dim + self.v_head_dim) / 2
+                if self.is_mla else self.q_size)
+        per_layer = 2 * (lin + act_mlp) + 4 * qk_v * (seq_len / 2)
         total = L * per_layer + 2 * h * self.vocab_size
         return total * (3 if backward else 1)
 
@@ -208,7 +243,8 @@ class ModelConfig:
             tie_word_embeddings=cfg.get("tie_word_embeddings", False),
             attention_bias=cfg.get("attention_bias", mt in ("qwen2", "qwen2_moe", "qwen2_5_vl", "qwen2_vl")),
             qk_norm=mt.startswith("qwen3"),
-            num_experts=cfg.get("num_experts", 0) or cfg.get("num_local_experts", 0) or 0,
+            num_experts=cfg.get("num_experts", 0) or cfg.get("num_local_experts", 0)
+            or cfg.get("n_routed_experts", 0) or 0,
             num_experts_per_tok=cfg.get("num_experts_per_tok", 0) or 0,
             moe_intermediate_size=cfg.get("moe_intermediate_size", 0) or 0,
             norm_topk_prob=cfg.get("norm_topk_prob", mt != "qwen2_moe"),
@@ -218,6 +254,20 @@ class ModelConfig:
         )
         if mt == "mixtral":  # every MLP is a mixture whose experts have the dense MLP's width
             out.moe_intermediate_size = out.intermediate_size
+        if mt == "deepseek_v3":
+            if cfg.get("attention_bias"):
+                raise NotImplementedError("bias on the latent-attention projections is not supported")
+            out.qk_norm = False
+            out.moe_score_func, out.moe_expert_bias, out.shared_expert_gated = "sigmoid", True, False
+            out.moe_route_scale = float(cfg.get("routed_scaling_factor", 1.0))
+            out.moe_n_group, out.moe_topk_group = int(cfg.get("n_group") or 1), int(cfg.get("topk_group") or 1)
+            out.shared_expert_intermediate_size = int(cfg.get("n_shared_experts") or 0) * out.moe_intermediate_size
+            out.mlp_only_layers = list(range(int(cfg.get("first_k_dense_replace") or 0)))
+            out.q_lora_rank = int(cfg.get("q_lora_rank") or 0)
+            for key in ("kv_lora_rank", "qk_nope_head_dim", "qk_rope_head_dim", "v_head_dim"):
+                setattr(out, key, int(cfg[key]))
+            out.head_dim = out.qk_nope_head_dim + out.qk_rope_head_dim
+            out.rope_interleave = bool(cfg.get("rope_interleave", True))
         if mt == "qwen3_5":
             out.layer_types = list(cfg.get("layer_types") or [])
             out.partial_rotary_factor = (cfg.get("partial_rotary_factor")
@@ -253,7 +303,8 @@ class ModelConfig:
         arch = {"qwen2": "Qwen2ForCausalLM", "qwen3": "Qwen3ForCausalLM",
                 "qwen3_moe": "Qwen3MoeForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
                 "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
-                "qwen2_moe": "Qwen2MoeForCausalLM", "mixtral": "MixtralForCausalLM"}[self.model_type]
+                "qwen2_moe": "Qwen2MoeForCausalLM", "mixtral": "MixtralForCausalLM",
+                "deepseek_v3": "DeepseekV3ForCausalLM"}[self.model_type]
         if self.model_type == "qwen3_5" and self.is_moe:
             arch = "Qwen3_5MoeForCausalLM"
         d = {
@@ -294,6 +345,18 @@ class ModelConfig:
                      shared_expert_intermediate_size=self.shared_expert_intermediate_size,
                      decoder_sparse_step=self.decoder_sparse_step,
                      mlp_only_layers=self.mlp_only_layers)
+        if self.model_type == "deepseek_v3":
+            for key in ("num_experts", "shared_expert_intermediate_size", "decoder_sparse_step", "mlp_only_layers"):
+                d.pop(key, None)
+            d.update(n_routed_experts=self.num_experts, routed_scaling_factor=self.moe_route_scale,
+                     n_shared_experts=self.shared_expert_intermediate_size // max(self.moe_intermediate_size, 1),
+                     n_group=self.moe_n_group, topk_group=self.moe_topk_group,
+                     first_k_dense_replace=len(self.mlp_only_layers), q_lora_rank=self.q_lora_rank or None,
+                     kv_lora_rank=self.kv_lora_rank, qk_nope_head_dim=self.qk_nope_head_dim,
+                     qk_rope_head_dim=self.qk_rope_head_dim, v_head_dim=self.v_head_dim,
+                     head_dim=self.qk_rope_head_dim, rope_interleave=self.rope_interleave)
+            if not self.rope_scaling:
+                d["rope_parameters"] = {"rope_type": "default", "rope_theta": self.rope_theta}
         if self.model_type == "mixtral":
             d.update(num_local_experts=self.num_experts, intermediate_size=self.moe_intermediate_size,
                      router_jitter_noise=0.0)
@@ -343,7 +406,7 @@ _VISION_KEYS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_ch
                 "fullatt_block_indexes", "hidden_act", "variant", "num_position_embeddings",
                 "deepstack_visual_indexes")
 _VL_TYPES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe")
-_TEXT_TYPES = {"qwen2", "qwen3", "qwen3_moe", "qwen3_5", "llama", "mistral", "qwen2_moe", "mixtral"}
+_TEXT_TYPES = {"qwen2", "qwen3", "qwen3_moe", "qwen3_5", "llama", "mistral", "qwen2_moe", "mixtral", "deepseek_v3"}
 
 # Named shapes used by the benchmark configurations (random-init, synthetic data).
 PRESETS: dict[str, ModelConfig] = {
@@ -432,6 +495,27 @@ PRESETS: dict[str, ModelConfig] = {
                                 rms_norm_eps=1e-5, rope_theta=1e6, max_position_embeddings=32768,
                                 tie_word_embeddings=False, qk_norm=False, num_experts=8, num_experts_per_tok=2,
                                 moe_intermediate_size=14336),
+    # DeepSeek-V3 architecture at test size: latent attention, one dense
+    # layer, then mixtures with grouped sigmoid routing and an ungated shared expert
+    "tiny-deepseek-v3": ModelConfig(model_type="deepseek_v3", vocab_size=1024, hidden_size=256, intermediate_size=512,
+                                    num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=4, head_dim=48,
+                                    rope_theta=1e4, tie_word_embeddings=False, qk_norm=False, num_experts=8,
+                                    num_experts_per_tok=2, moe_intermediate_size=64, moe_score_func="sigmoid",
+                                    moe_route_scale=2.5, moe_n_group=4, moe_topk_group=2, moe_expert_bias=True,
+                                    shared_expert_intermediate_size=64, shared_expert_gated=False,
+                                    mlp_only_layers=[0], q_lora_rank=96, kv_lora_rank=64, qk_nope_head_dim=32,
+                                    qk_rope_head_dim=16, v_head_dim=32, rope_interleave=True),
+    "deepseek-v3": ModelConfig(model_type="deepseek_v3", vocab_size=129280, hidden_size=7168, intermediate_size=18432,
+                               num_hidden_layers=61, num_attention_heads=128, num_key_value_heads=128, head_dim=192,
+                               rope_theta=1e4, max_position_embeddings=163840, tie_word_embeddings=False,
+                               qk_norm=False, num_experts=256, num_experts_per_tok=8, moe_intermediate_size=2048,
+                               moe_score_func="sigmoid", moe_route_scale=2.5, moe_n_group=8, moe_topk_group=4,
+                               moe_expert_bias=True, shared_expert_intermediate_size=2048, shared_expert_gated=False,
+                               mlp_only_layers=[0, 1, 2], q_lora_rank=1536, kv_lora_rank=512, qk_nope_head_dim=128,
+                               qk_rope_head_dim=64, v_head_dim=128, rope_interleave=True,
+                               rope_scaling={"rope_type": "yarn", "factor": 40.0, "beta_fast": 32, "beta_slow": 1,
+                                             "mscale": 1.0, "mscale_all_dim": 1.0,
+                                             "original_max_position_embeddings": 4096}),
     "mistral-7b": ModelConfig(model_type="mistral", vocab_size=32768, hidden_size=4096, intermediate_size=14336,
                               num_hidden_layers=32, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
                               rms_norm_eps=1e-5, rope_theta=1e6, max_position_embeddings=32768,

@@ -208,7 +208,7 @@ class MoEMLP(nn.Module):
         self.down = nn.Parameter(torch.empty(E // ep, H, I // etp, dtype=dtype, device=device))
         self.last_routing = None  # (topk_idx, topk_w) of the last forward, for stats / replay
         # aux-loss-free balancing: a selection-only bias, a buffer (not trained by the optimizer, replicated)
-        if cfg.moe_load_balance_coeff > 0:
+        if cfg.moe_load_balance_coeff > 0 or cfg.moe_expert_bias:
             self.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32, device=device))
         else:
             self.expert_bias = None
@@ -218,12 +218,15 @@ class MoEMLP(nn.Module):
         if Is:
             self.shared_gate_up = nn.Parameter(torch.empty(2 * Is, H, dtype=dtype, device=device))
             self.shared_down = nn.Parameter(torch.empty(H, Is, dtype=dtype, device=device))
-            self.shared_gate = nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
+            self.shared_gate = (nn.Parameter(torch.empty(1, H, dtype=dtype, device=device))
+                                if cfg.shared_expert_gated else None)
         else:
             self.shared_gate_up = self.shared_down = self.shared_gate = None
 
     def _shared(self, x):
         y = linear(fused.swiglu(linear(x, self.shared_gate_up)), self.shared_down)
+        if self.shared_gate is None:
+            return y
         if x.is_cuda:
             _lib.count_fallback("moe.shared_expert_gate[F.linear]")
         g = torch.sigmoid(F.linear(x.float(), self.shared_gate.float()))
@@ -234,7 +237,8 @@ class MoEMLP(nn.Module):
         if x.is_cuda:
             _lib.count_fallback("moe.router[F.linear fp32]")
         logits = F.linear(x.float(), self.router.float())
-        plain = cfg.moe_score_func == "softmax" and cfg.moe_route_scale == 1.0 and self.expert_bias is None
+        plain = (cfg.moe_score_func == "softmax" and cfg.moe_route_scale == 1.0 and self.expert_bias is None
+                 and cfg.moe_n_group <= 1)
         if not plain:
             return self._route_general(logits)
         if not (torch.is_grad_enabled() and (x.requires_grad or self.router.requires_grad)):
@@ -257,12 +261,21 @@ class MoEMLP(nn.Module):
         cfg = self.cfg
         scores = torch.sigmoid(logits) if cfg.moe_score_func == "sigmoid" else logits.softmax(-1)
         pick = scores if self.expert_bias is None else scores + self.expert_bias
+        if cfg.moe_n_group > 1:
+            # group-limited routing: a group scores the sum of its two best experts; experts outside the token's
+            # best `moe_topk_group` groups cannot be picked
+            G = cfg.moe_n_group
+            grouped = pick.view(-1, G, cfg.num_experts // G)
+            best = grouped.topk(min(2, grouped.shape[-1]), dim=-1).values.sum(-1).topk(cfg.moe_topk_group, dim=-1).indices
+            allowed = torch.zeros(grouped.shape[:2], dtype=torch.bool, device=pick.device).scatter_(1, best, True)
+            pick = grouped.masked_fill(~allowed[..., None], 0.0).view_as(pick)
         idx = pick.topk(cfg.num_experts_per_tok, dim=-1).indices
         w = scores.gather(-1, idx)
         if cfg.norm_topk_prob:
             w = w / (w.sum(-1, keepdim=True) + 1e-20)
         w = w * cfg.moe_route_scale
-        if self.expert_bias is not None and self.training and torch.is_grad_enabled():
+        if (self.expert_bias is not None and cfg.moe_load_balance_coeff > 0 and self.training
+                and torch.is_grad_enabled()):
             with torch.no_grad():
                 load = torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).float()
                 self.expert_bias.add_(cfg.moe_load_balance_coeff * torch.sign(load.mean() - load))
@@ -304,6 +317,10 @@ class Block(nn.Module):
 
             kind = GatedDeltaNet if cfg.layer_type(layer_idx) == "linear_attention" else GatedAttention
             self.attn = kind(cfg, dtype, device, pctx, layer_idx)
+        elif cfg.is_mla:
+            from .mla import MLAttention
+
+            self.attn = MLAttention(cfg, dtype, device, pctx, layer_idx)
         else:
             self.attn = Attention(cfg, dtype, device, pctx, layer_idx)
         self.post_norm = nn.Parameter(torch.ones(h, dtype=dtype, device=device))
@@ -569,6 +586,9 @@ class QwenModel(nn.Module):
         paged caches; returns hidden states of all tokens. Hybrid models also take the per-sequence
         state of their linear-attention layers and the slot of every sequence in it. ``embeds`` /
         ``rope`` as in :meth:`forward` (image features merged into the embeddings, one rotary row per token)."""
+        if self.cfg.is_mla:
+            raise NotImplementedError("the rollout engine has no latent KV cache: serve latent-attention models "
+                                      "(DeepSeek-V3) with an external server (`vllm:` rollout backend)")
         if self.cfg.is_hybrid:
             from .qwen3_5 import hybrid_prefill
 
@@ -687,6 +707,16 @@ class QwenModel(nn.Module):
                 parts = [torch.empty_like(t) for _ in range(size)]
                 dist.all_gather(parts, t.contiguous(), group=group)
                 yield self.checkpoint_name(name), torch.cat(parts, d)
+        yield from self._selection_biases()
+
+    def _selection_biases(self):
+        """The routers' selection biases of a family whose checkpoints carry them: buffers, not parameters (no
+        gradient, not in the flat weight buffer), so they travel beside ``to_hf_local``'s tensors."""
+        if not self.cfg.moe_expert_bias:
+            return
+        for i, layer in zip(self.layer_ids, self.layers):
+            if getattr(layer.mlp, "expert_bias", None) is not None:
+                yield f"model.layers.{i}.mlp.gate.e_score_correction_bias", layer.mlp.expert_bias
 
     # Families whose checkpoint files name the same tensors differently (Mixtral: ``block_sparse_moe`` with
     # experts ``w1`` / ``w3`` / ``w2``). Inside the package every tensor goes by the canonical (Qwen-style)
@@ -732,17 +762,20 @@ class QwenModel(nn.Module):
             p = f"model.layers.{i}."
             yield p + "input_layernorm.weight", layer.input_norm
             a = layer.attn
-            yield p + "self_attn.q_proj.weight", a.qkv[:qs]
-            yield p + "self_attn.k_proj.weight", a.qkv[qs:qs + ks]
-            yield p + "self_attn.v_proj.weight", a.qkv[qs + ks:]
-            if a.qkv_bias is not None:
-                yield p + "self_attn.q_proj.bias", a.qkv_bias[:qs]
-                yield p + "self_attn.k_proj.bias", a.qkv_bias[qs:qs + ks]
-                yield p + "self_attn.v_proj.bias", a.qkv_bias[qs + ks:]
-            if a.q_norm is not None:
-                yield p + "self_attn.q_norm.weight", a.q_norm
-                yield p + "self_attn.k_norm.weight", a.k_norm
-            yield p + "self_attn.o_proj.weight", a.o
+            if hasattr(a, "hf_tensors"):  # latent attention names its own projections
+                yield from a.hf_tensors(p)
+            else:
+                yield p + "self_attn.q_proj.weight", a.qkv[:qs]
+                yield p + "self_attn.k_proj.weight", a.qkv[qs:qs + ks]
+                yield p + "self_attn.v_proj.weight", a.qkv[qs + ks:]
+                if a.qkv_bias is not None:
+                    yield p + "self_attn.q_proj.bias", a.qkv_bias[:qs]
+                    yield p + "self_attn.k_proj.bias", a.qkv_bias[qs:qs + ks]
+                    yield p + "self_attn.v_proj.bias", a.qkv_bias[qs + ks:]
+                if a.q_norm is not None:
+                    yield p + "self_attn.q_norm.weight", a.q_norm
+                    yield p + "self_attn.k_norm.weight", a.k_norm
+                yield p + "self_attn.o_proj.weight", a.o
             yield p + "post_attention_layernorm.weight", layer.post_norm
             m = layer.mlp
             if isinstance(m, DenseMLP):
@@ -772,10 +805,12 @@ class QwenModel(nn.Module):
         if getattr(m, "shared_gate_up", None) is None:
             return
         Is = self.cfg.shared_expert_intermediate_size
-        yield p + "mlp.shared_expert.gate_proj.weight", m.shared_gate_up[:Is]
-        yield p + "mlp.shared_expert.up_proj.weight", m.shared_gate_up[Is:]
-        yield p + "mlp.shared_expert.down_proj.weight", m.shared_down
-        yield p + "mlp.shared_expert_gate.weight", m.shared_gate
+        q = p + ("mlp.shared_expert." if m.shared_gate is not None else "mlp.shared_experts.")
+        yield q + "gate_proj.weight", m.shared_gate_up[:Is]
+        yield q + "up_proj.weight", m.shared_gate_up[Is:]
+        yield q + "down_proj.weight", m.shared_down
+        if m.shared_gate is not None:
+            yield p + "mlp.shared_expert_gate.weight", m.shared_gate
 
     def _to_hf_hybrid(self, export: bool):
         from .qwen3_5 import hf_tensors
@@ -837,6 +872,7 @@ class QwenModel(nn.Module):
         dst = self.hf_name_map()
         if self.embed is not None and not self.first_stage:
             dst["model.embed_tokens.weight"] = self.embed  # the last stage's copy of a tied embedding
+        dst.update(self._selection_biases())
         seen = set()
         for name, t in tensors:
             if name.startswith("model.language_model."):  # decoder of a composite checkpoint

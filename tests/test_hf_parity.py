@@ -182,3 +182,48 @@ def test_mixtral_matches_transformers_and_uses_its_checkpoint_names(tmp_path):
     assert not any(".mlp." in n for n in names)
     back = ModelConfig.from_hf_config(str(tmp_path))
     assert back.num_experts == 8 and back.moe_intermediate_size == 128 and back.is_moe
+
+
+def test_deepseek_v3_matches_transformers(tmp_path):
+    """Latent attention (low-rank query and key / value paths, a rotary part beside a position-free part, rotary
+    pairs interleaved in the checkpoint), a dense first layer, then mixtures with sigmoid scores, group-limited
+    routing, the checkpoint's selection bias, a scale on the routing weights and an ungated shared expert."""
+    cfg = PRESETS["tiny-deepseek-v3"]
+    torch.manual_seed(0)
+    m = build_model(cfg, dtype=torch.float32, seed=1)
+    with torch.no_grad():
+        for n, p in m.named_parameters():
+            if n.endswith("norm") or "_norm" in n:
+                p.add_(torch.randn_like(p) * 0.1)
+        for layer in m.layers:   # a bias large enough to change which experts win
+            if getattr(layer.mlp, "expert_bias", None) is not None:
+                layer.mlp.expert_bias.copy_(torch.randn(cfg.num_experts) * 0.2)
+    save_hf_checkpoint(m, cfg, str(tmp_path))
+    hf = transformers.AutoModelForCausalLM.from_pretrained(str(tmp_path), torch_dtype=torch.float32).eval()
+    assert type(hf).__name__ == "DeepseekV3ForCausalLM"
+    ids = torch.randint(0, cfg.vocab_size, (41,), generator=torch.Generator().manual_seed(2))
+    mine = _logits(m, ids)
+    with torch.no_grad():
+        theirs = hf(input_ids=ids[None]).logits[0]
+    assert float((mine - theirs).abs().max()) < 2e-4
+    back = ModelConfig.from_hf_config(str(tmp_path))
+    assert back.is_mla and (back.q_lora_rank, back.kv_lora_rank, back.qk_nope_head_dim, back.qk_rope_head_dim,
+                            back.v_head_dim) == (96, 64, 32, 16, 32)
+    assert (back.moe_n_group, back.moe_topk_group, back.moe_route_scale, back.mlp_only_layers,
+            back.shared_expert_gated, back.moe_expert_bias) == (4, 2, 2.5, [0], False, True)
+    m2 = build_model(back, dtype=torch.float32, seed=None)
+    load_hf_weights(m2, str(tmp_path))
+    assert torch.allclose(_logits(m2, ids), mine, atol=1e-5)
+    assert torch.equal(m2.layers[1].mlp.expert_bias, m.layers[1].mlp.expert_bias)
+
+
+def test_deepseek_v3_without_query_bottleneck_and_with_yarn(tmp_path):
+    """``q_lora_rank`` absent (the Lite models' plain query projection), rotary pairs not interleaved, and a YaRN
+    table whose magnitude factor enters the softmax scale."""
+    cfg = dataclasses.replace(PRESETS["tiny-deepseek-v3"], q_lora_rank=0, rope_interleave=False,
+                              max_position_embeddings=256,
+                              rope_scaling={"rope_type": "yarn", "factor": 4.0, "beta_fast": 32, "beta_slow": 1,
+                                            "mscale": 1.0, "mscale_all_dim": 0.7,
+                                            "original_max_position_embeddings": 64})
+    hf = _roundtrip(cfg, tmp_path)
+    assert type(hf).__name__ == "DeepseekV3ForCausalLM" and not hasattr(hf.model.layers[0].self_attn, "q_a_proj")

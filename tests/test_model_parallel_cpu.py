@@ -128,8 +128,31 @@ def test_vision_language_step_under_tensor_parallelism(tmp_path, n, preset, par)
     _run(n, 29690 + n, par + ["--preset", preset, "--images"], _ref(tmp_path, preset=preset, images=True))
 
 
+@pytest.mark.parametrize("n,args", [(2, ["--ep", "2"]), (2, ["--sp", "2"]), (2, ["--pp", "2", "--n-mbs", "2"])])
+def test_latent_attention_family_step_matches_single_process(tmp_path, n, args):
+    """DeepSeek-V3 architecture (latent attention, grouped sigmoid routing, ungated shared expert, dense first
+    layer) under expert, Ulysses and pipeline parallelism."""
+    _run(n, 0, args + ["--preset", "tiny-deepseek-v3"], _ref(tmp_path, preset="tiny-deepseek-v3", n_mbs=2))
+
+
+def test_latent_attention_refuses_tensor_parallelism_and_the_rollout_engine():
+    import torch
+
+    from areal_b200.models.config import PRESETS
+    from areal_b200.models.qwen import build_model
+    from areal_b200.parallel.context import ParallelContext
+
+    cfg = PRESETS["tiny-deepseek-v3"]
+    with pytest.raises(NotImplementedError, match="tensor parallelism"):
+        build_model(cfg, dtype=torch.float32, seed=None, pctx=ParallelContext(tp_size=2, tp_rank=0))
+    m = build_model(cfg, dtype=torch.float32, seed=0)
+    with pytest.raises(NotImplementedError, match="external server"):
+        m.prefill(torch.zeros(4, dtype=torch.long), torch.arange(4), None, None, None)
+
+
 @pytest.mark.parametrize("n,pp,preset,ep", [(2, 1, "tiny-qwen3-vl", 1), (4, 2, "tiny-qwen3-vl", 1),
-                                            (2, 2, "tiny-qwen2", 1), (2, 1, "tiny-qwen3-moe", 2)])
+                                            (2, 2, "tiny-qwen2", 1), (2, 1, "tiny-qwen3-moe", 2),
+                                            (2, 2, "tiny-deepseek-v3", 1), (2, 1, "tiny-deepseek-v3", 2)])
 def test_checkpoint_under_tensor_pipeline_and_expert_parallelism(tmp_path, n, pp, preset, ep):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
