@@ -78,6 +78,13 @@ class ModelConfig:
     qk_rope_head_dim: int = 0
     v_head_dim: int = 0
     rope_interleave: bool = False  # rotary pairs are neighbours (2i, 2i + 1) in the checkpoint's q / k layout
+    # Bailing hybrid: layers come in groups of `lightning_group_size`; all but the last of a group use lightning
+    # (linear) attention with heads of `lightning_head_dim` and a gate norm over `lightning_norm_groups` groups of
+    # heads, the last uses latent attention. 0 / 1 = no lightning layers
+    lightning_group_size: int = 0
+    lightning_head_dim: int = 128
+    lightning_norm_groups: int = 1
+    moe_group_score_top: int = 2  # a group's score: the sum of its this many best experts
     decoder_sparse_step: int = 1
     mlp_only_layers: list[int] = field(default_factory=list)
     # critic / reward model: scalar head instead of the LM head
@@ -104,6 +111,10 @@ class ModelConfig:
         return (self.is_moe and i not in self.mlp_only_layers
                 and (i + 1) % max(self.decoder_sparse_step, 1) == 0)
 
+    def layer_is_lightning(self, i: int) -> bool:
+        g = self.lightning_group_size
+        return g > 1 and (i + 1) % g != 0
+
     def layer_type(self, i: int) -> str:
         return self.layer_types[i] if self.layer_types else "full_attention"
 
@@ -121,8 +132,11 @@ class ModelConfig:
             return self.qk_rope_head_dim
         return int(self.head_dim * self.partial_rotary_factor) // 2 * 2
 
-    def attn_params(self) -> int:
+    def attn_params(self, layer: int | None = None) -> int:
         h, nh = self.hidden_size, self.num_attention_heads
+        if layer is not None and self.layer_is_lightning(layer):
+            d = nh * self.lightning_head_dim
+            return 5 * d * h + d + 2 * self.lightning_head_dim
         if self.is_mla:
             qk = self.qk_nope_head_dim + self.qk_rope_head_dim
             q = (h * self.q_lora_rank + self.q_lora_rank + self.q_lora_rank * nh * qk) if self.q_lora_rank \
@@ -153,7 +167,8 @@ class ModelConfig:
             moe_mlp += 3 * h * self.shared_expert_intermediate_size + (h if self.shared_expert_gated else 0)
         n = 0
         for i in range(L):
-            n += attn + 2 * h + (moe_mlp if self.layer_is_moe(i) else dense_mlp)
+            a = self.attn_params(i) if self.layer_is_lightning(i) else attn
+            n += a + 2 * h + (moe_mlp if self.layer_is_moe(i) else dense_mlp)
         n += self.vocab_size * h + h
         if not self.tie_word_embeddings and not self.is_critic:
             n += self.vocab_size * h
@@ -201,6 +216,8 @@ class ModelConfig:
         if "text_config" in cfg:  # composite (vision-language) checkpoints nest the decoder's config
             cfg = cfg["text_config"]
         mt = cfg.get("model_type", "qwen3")
+        if mt in ("bailing_moe_linear", "bailing_hybrid"):
+            mt = "bailing_hybrid"
         if top.get("model_type") in _VL_TYPES:
             mt = top["model_type"]
         if mt.startswith("qwen3_5"):
@@ -254,6 +271,30 @@ class ModelConfig:
         )
         if mt == "mixtral":  # every MLP is a mixture whose experts have the dense MLP's width
             out.moe_intermediate_size = out.intermediate_size
+        if mt == "bailing_hybrid":
+            if cfg.get("use_qkv_bias") or cfg.get("use_bias"):
+                raise NotImplementedError("bias on the Bailing projections is not supported")
+            out.qk_norm = False
+            out.moe_score_func = cfg.get("scoring_func") or cfg.get("score_function") or "sigmoid"
+            out.moe_expert_bias, out.shared_expert_gated = True, False
+            out.moe_route_scale = float(cfg.get("routed_scaling_factor") or 1.0)
+            out.moe_n_group, out.moe_topk_group = int(cfg.get("n_group") or 1), int(cfg.get("topk_group") or 1)
+            out.moe_group_score_top = max(out.num_experts_per_tok // max(out.moe_topk_group, 1), 1)
+            shared = cfg.get("moe_shared_expert_intermediate_size")
+            out.shared_expert_intermediate_size = int(shared) if shared else \
+                int(cfg.get("num_shared_experts") or 0) * (out.moe_intermediate_size or out.intermediate_size)
+            out.mlp_only_layers = list(range(int(cfg.get("first_k_dense_replace") or 0)))
+            out.q_lora_rank = int(cfg.get("q_lora_rank") or 0)
+            out.kv_lora_rank = int(cfg.get("kv_lora_rank") or 512)
+            out.qk_nope_head_dim = int(cfg.get("qk_nope_head_dim") or 128)
+            out.qk_rope_head_dim = int(cfg.get("qk_rope_head_dim") or 64)
+            out.v_head_dim = int(cfg.get("v_head_dim") or 128)
+            out.rope_interleave = True
+            out.lightning_group_size = int(cfg.get("layer_group_size") or 1)
+            out.lightning_head_dim = int(cfg.get("attn_head_dim") or cfg.get("head_dim") or 256)
+            out.head_dim = out.qk_nope_head_dim + out.qk_rope_head_dim
+            out.partial_rotary_factor = float(cfg.get("partial_rotary_factor") or 0.5)
+            out.lightning_norm_groups = int(cfg.get("linear_attn_norm_group_size") or cfg.get("group_norm_size") or 1)
         if mt == "deepseek_v3":
             if cfg.get("attention_bias"):
                 raise NotImplementedError("bias on the latent-attention projections is not supported")
@@ -304,7 +345,7 @@ class ModelConfig:
                 "qwen3_moe": "Qwen3MoeForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
                 "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
                 "qwen2_moe": "Qwen2MoeForCausalLM", "mixtral": "MixtralForCausalLM",
-                "deepseek_v3": "DeepseekV3ForCausalLM"}[self.model_type]
+                "deepseek_v3": "DeepseekV3ForCausalLM", "bailing_hybrid": "BailingMoeV2_5ForCausalLM"}[self.model_type]
         if self.model_type == "qwen3_5" and self.is_moe:
             arch = "Qwen3_5MoeForCausalLM"
         d = {
@@ -357,6 +398,19 @@ class ModelConfig:
                      head_dim=self.qk_rope_head_dim, rope_interleave=self.rope_interleave)
             if not self.rope_scaling:
                 d["rope_parameters"] = {"rope_type": "default", "rope_theta": self.rope_theta}
+        if self.model_type == "bailing_hybrid":
+            for key in ("shared_expert_intermediate_size", "decoder_sparse_step", "mlp_only_layers", "head_dim"):
+                d.pop(key, None)
+            d.update(model_type="bailing_hybrid", scoring_func=self.moe_score_func,
+                     routed_scaling_factor=self.moe_route_scale, n_group=self.moe_n_group,
+                     topk_group=self.moe_topk_group,
+                     moe_shared_expert_intermediate_size=self.shared_expert_intermediate_size,
+                     first_k_dense_replace=len(self.mlp_only_layers), q_lora_rank=self.q_lora_rank or None,
+                     kv_lora_rank=self.kv_lora_rank, qk_nope_head_dim=self.qk_nope_head_dim,
+                     qk_rope_head_dim=self.qk_rope_head_dim, v_head_dim=self.v_head_dim,
+                     layer_group_size=self.lightning_group_size, attn_head_dim=self.lightning_head_dim,
+                     partial_rotary_factor=self.partial_rotary_factor,
+                     linear_attn_norm_group_size=self.lightning_norm_groups)
         if self.model_type == "mixtral":
             d.update(num_local_experts=self.num_experts, intermediate_size=self.moe_intermediate_size,
                      router_jitter_noise=0.0)
@@ -406,7 +460,7 @@ _VISION_KEYS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_ch
                 "fullatt_block_indexes", "hidden_act", "variant", "num_position_embeddings",
                 "deepstack_visual_indexes")
 _VL_TYPES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe")
-_TEXT_TYPES = {"qwen2", "qwen3", "qwen3_moe", "qwen3_5", "llama", "mistral", "qwen2_moe", "mixtral", "deepseek_v3"}
+_TEXT_TYPES = {"qwen2", "qwen3", "qwen3_moe", "qwen3_5", "llama", "mistral", "qwen2_moe", "mixtral", "deepseek_v3", "bailing_hybrid"}
 
 # Named shapes used by the benchmark configurations (random-init, synthetic data).
 PRESETS: dict[str, ModelConfig] = {
@@ -505,6 +559,17 @@ PRESETS: dict[str, ModelConfig] = {
                                     shared_expert_intermediate_size=64, shared_expert_gated=False,
                                     mlp_only_layers=[0], q_lora_rank=96, kv_lora_rank=64, qk_nope_head_dim=32,
                                     qk_rope_head_dim=16, v_head_dim=32, rope_interleave=True),
+    # Bailing hybrid architecture at test size: groups of two layers (lightning attention, then latent attention)
+    "tiny-bailing-hybrid": ModelConfig(model_type="bailing_hybrid", vocab_size=1024, hidden_size=256,
+                                       intermediate_size=512, num_hidden_layers=4, num_attention_heads=4,
+                                       num_key_value_heads=4, head_dim=48, rope_theta=1e4, tie_word_embeddings=False,
+                                       qk_norm=False, num_experts=8, num_experts_per_tok=2, moe_intermediate_size=64,
+                                       moe_score_func="sigmoid", moe_route_scale=2.5, moe_n_group=4, moe_topk_group=2,
+                                       moe_group_score_top=1, moe_expert_bias=True, shared_expert_intermediate_size=64,
+                                       shared_expert_gated=False, mlp_only_layers=[0], q_lora_rank=96, kv_lora_rank=64,
+                                       qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, rope_interleave=True,
+                                       lightning_group_size=2, lightning_head_dim=32, lightning_norm_groups=2,
+                                       partial_rotary_factor=0.5, max_position_embeddings=32768),
     "deepseek-v3": ModelConfig(model_type="deepseek_v3", vocab_size=129280, hidden_size=7168, intermediate_size=18432,
                                num_hidden_layers=61, num_attention_heads=128, num_key_value_heads=128, head_dim=192,
                                rope_theta=1e4, max_position_embeddings=163840, tie_word_embeddings=False,

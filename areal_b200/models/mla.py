@@ -114,14 +114,17 @@ class MLAttention(nn.Module):
         return linear(a, self.o)
 
     def hf_tensors(self, p: str):
-        """``(checkpoint name, tensor)`` of this layer, ``p`` = ``model.layers.<i>.``."""
+        """``(checkpoint name, tensor)`` of this layer, ``p`` = ``model.layers.<i>.``. Bailing checkpoints call the
+        module ``attention`` and its output projection ``dense``."""
+        bailing = self.cfg.model_type == "bailing_hybrid"
+        p = p + ("attention." if bailing else "self_attn.")
         if self.q is None:
-            yield p + "self_attn.q_a_proj.weight", self.q_a
-            yield p + "self_attn.q_a_layernorm.weight", self.q_a_norm
-            yield p + "self_attn.q_b_proj.weight", self.q_b
+            yield p + "q_a_proj.weight", self.q_a
+            yield p + "q_a_layernorm.weight", self.q_a_norm
+            yield p + "q_b_proj.weight", self.q_b
         else:
-            yield p + "self_attn.q_proj.weight", self.q
-        yield p + "self_attn.kv_a_proj_with_mqa.weight", self.kv_a
-        yield p + "self_attn.kv_a_layernorm.weight", self.kv_a_norm
-        yield p + "self_attn.kv_b_proj.weight", self.kv_b
-        yield p + "self_attn.o_proj.weight", self.o
+            yield p + "q_proj.weight", self.q
+        yield p + "kv_a_proj_with_mqa.weight", self.kv_a
+        yield p + "kv_a_layernorm.weight", self.kv_a_norm
+        yield p + "kv_b_proj.weight", self.kv_b
+        yield p + ("dense.weight" if bailing else "o_proj.weight"), self.o

@@ -266,7 +266,7 @@ class MoEMLP(nn.Module):
             # best `moe_topk_group` groups cannot be picked
             G = cfg.moe_n_group
             grouped = pick.view(-1, G, cfg.num_experts // G)
-            best = grouped.topk(min(2, grouped.shape[-1]), dim=-1).values.sum(-1).topk(cfg.moe_topk_group, dim=-1).indices
+            best = grouped.topk(min(cfg.moe_group_score_top, grouped.shape[-1]), dim=-1).values.sum(-1).topk(cfg.moe_topk_group, dim=-1).indices
             allowed = torch.zeros(grouped.shape[:2], dtype=torch.bool, device=pick.device).scatter_(1, best, True)
             pick = grouped.masked_fill(~allowed[..., None], 0.0).view_as(pick)
         idx = pick.topk(cfg.num_experts_per_tok, dim=-1).indices
@@ -317,6 +317,10 @@ class Block(nn.Module):
 
             kind = GatedDeltaNet if cfg.layer_type(layer_idx) == "linear_attention" else GatedAttention
             self.attn = kind(cfg, dtype, device, pctx, layer_idx)
+        elif cfg.layer_is_lightning(layer_idx):
+            from .lightning import LightningAttention
+
+            self.attn = LightningAttention(cfg, dtype, device, pctx, layer_idx)
         elif cfg.is_mla:
             from .mla import MLAttention
 
@@ -707,7 +711,8 @@ class QwenModel(nn.Module):
                 parts = [torch.empty_like(t) for _ in range(size)]
                 dist.all_gather(parts, t.contiguous(), group=group)
                 yield self.checkpoint_name(name), torch.cat(parts, d)
-        yield from self._selection_biases()
+        for name, t in self._selection_biases():
+            yield self.checkpoint_name(name), t
 
     def _selection_biases(self):
         """The routers' selection biases of a family whose checkpoints carry them: buffers, not parameters (no
@@ -723,7 +728,15 @@ class QwenModel(nn.Module):
     # name; the translation happens where tensors enter (``load_hf``) or leave (``to_hf``).
     _MIXTRAL_PROJ = {"gate_proj": "w1", "up_proj": "w3", "down_proj": "w2"}
 
+    _BAILING_NAMES = (("model.embed_tokens.weight", "model.word_embeddings.weight"),
+                      (".mlp.gate.e_score_correction_bias", ".mlp.gate.expert_bias"))
+
     def checkpoint_name(self, name: str) -> str:
+        if self.cfg.model_type == "bailing_hybrid":
+            for ours, theirs in self._BAILING_NAMES:
+                if name.endswith(ours):
+                    return name[: len(name) - len(ours)] + theirs
+            return name
         if self.cfg.model_type != "mixtral" or ".mlp." not in name:
             return name
         head, _, tail = name.partition(".mlp.")
@@ -735,6 +748,11 @@ class QwenModel(nn.Module):
         return name
 
     def canonical_name(self, name: str) -> str:
+        if self.cfg.model_type == "bailing_hybrid":
+            for ours, theirs in self._BAILING_NAMES:
+                if name.endswith(theirs):
+                    return name[: len(name) - len(theirs)] + ours
+            return name
         if self.cfg.model_type != "mixtral" or ".block_sparse_moe." not in name:
             return name
         head, _, tail = name.partition(".block_sparse_moe.")

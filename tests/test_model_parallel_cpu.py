@@ -152,7 +152,8 @@ def test_latent_attention_refuses_tensor_parallelism_and_the_rollout_engine():
 
 @pytest.mark.parametrize("n,pp,preset,ep", [(2, 1, "tiny-qwen3-vl", 1), (4, 2, "tiny-qwen3-vl", 1),
                                             (2, 2, "tiny-qwen2", 1), (2, 1, "tiny-qwen3-moe", 2),
-                                            (2, 2, "tiny-deepseek-v3", 1), (2, 1, "tiny-deepseek-v3", 2)])
+                                            (2, 2, "tiny-deepseek-v3", 1), (2, 1, "tiny-deepseek-v3", 2),
+                                            (2, 2, "tiny-bailing-hybrid", 1), (2, 1, "tiny-bailing-hybrid", 2)])
 def test_checkpoint_under_tensor_pipeline_and_expert_parallelism(tmp_path, n, pp, preset, ep):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(free_port()), os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
