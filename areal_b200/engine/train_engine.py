@@ -177,12 +177,16 @@ class B200TrainEngine(TrainEngine):
             if ps.pp_size > 1:
                 # schedule and virtual stages: `archon.pp_schedule` for the Archon-style backend, 1F1B otherwise;
                 # `megatron.virtual_pipeline_parallel_size` chunks per rank select the interleaved order
-                from ..parallel.pipeline import canonical_schedule
+                from ..parallel.pipeline import canonical_schedule, placement_of
 
                 family = (self.config.backend or "").split(":")[0]
                 vpp = max(int(getattr(self.config.megatron, "virtual_pipeline_parallel_size", 1) or 1), 1)
                 name = os.environ.get("AREAL_B200_PP_SCHEDULE") or (
                     self.config.archon.pp_schedule if family == "archon" else ("Interleaved1F1B" if vpp > 1 else "1F1B"))
+                self._pp_placement = placement_of(name)
+                if self._pp_placement == "v":
+                    vpp = 2  # the V-shaped placement is defined for two chunks per rank
+                    self.pctx.extras["pp_placement"] = "v"
                 self._pp_schedule = canonical_schedule(name, vpp)
                 self._vpp = vpp
                 if self._pp_schedule == "zero_bubble":
@@ -365,7 +369,8 @@ class B200TrainEngine(TrainEngine):
                     # the experts of other pipeline stages count in the global gradient norm as well
                     self.optimizer.partner.norm_groups.append(pctx.pp_group)
                 if self.model_config.tie_word_embeddings and not self.is_critic and self.model.embed is not None \
-                        and self.model.embed.requires_grad:  # (frozen under LoRA: nothing to sum)
+                        and self.model.embed.requires_grad and pctx.last_stage_rank != 0:
+                    # (frozen under LoRA: nothing to sum; V-shaped placement: embedding and head share one copy)
                     self.optimizer.pre_step_hooks.append(self._sum_tied_embedding_grads)
                     if not self.model.first_stage:
                         # both copies apply the summed gradient; the first stage's copy counts in the norm
@@ -627,7 +632,8 @@ class B200TrainEngine(TrainEngine):
         V = self._vpp
         dtype = next(self.model.parameters()).dtype
         runner = PipelineRunner(pctx.extras["pp_links"], pctx.pp_rank, pctx.pp_size, V,
-                                "gpipe" if forward_only and V == 1 else self._pp_schedule, dtype, self.device)
+                                "gpipe" if forward_only and V == 1 else self._pp_schedule, dtype, self.device,
+                                placement=getattr(self, "_pp_placement", "interleaved"))
         staged: dict[int, tuple] = {}
 
         def on_device(i):
@@ -778,7 +784,7 @@ class B200TrainEngine(TrainEngine):
                 base += out.shape[0]
         if pp:
             # the last stage holds the outputs: hand them to every stage of the replica
-            src = dist.get_global_rank(self.pctx.pp_group, self.pctx.pp_size - 1)
+            src = dist.get_global_rank(self.pctx.pp_group, self.pctx.last_stage_rank)
             for t in ([result] + ([ent_result] if return_entropy else [])):
                 dev = t.to(self.device)
                 dist.broadcast(dev, src=src, group=self.pctx.pp_group)

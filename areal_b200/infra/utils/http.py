@@ -17,11 +17,12 @@ class HTTPRequestError(RuntimeError):
 
 
 def request_with_retry(method: str, url: str, *, json: Any = None, timeout: float = 30.0, max_retries: int = 3,
-                       backoff: float = 0.5, retry_statuses=(502, 503, 504)) -> requests.Response:
+                       backoff: float = 0.5, retry_statuses=(502, 503, 504),
+                       headers: dict[str, str] | None = None) -> requests.Response:
     last: Exception | None = None
     for attempt in range(max_retries + 1):
         try:
-            r = requests.request(method, url, json=json, timeout=timeout)
+            r = requests.request(method, url, json=json, timeout=timeout, headers=headers or None)
             if r.status_code in retry_statuses and attempt < max_retries:
                 last = HTTPRequestError(url, r.status_code, r.text[:200])
             else:
@@ -37,14 +38,16 @@ def request_with_retry(method: str, url: str, *, json: Any = None, timeout: floa
 
 
 async def arequest_with_retry(session, method: str, url: str, *, json: Any = None, timeout: float = 30.0,
-                              max_retries: int = 3, backoff: float = 0.5, retry_statuses=(502, 503, 504)) -> Any:
+                              max_retries: int = 3, backoff: float = 0.5, retry_statuses=(502, 503, 504),
+                              headers: dict[str, str] | None = None) -> Any:
     """aiohttp variant; returns the decoded JSON body."""
     import aiohttp
 
     last: Exception | None = None
     for attempt in range(max_retries + 1):
         try:
-            async with session.request(method, url, json=json, timeout=aiohttp.ClientTimeout(total=timeout)) as r:
+            async with session.request(method, url, json=json, headers=headers or None,
+                                       timeout=aiohttp.ClientTimeout(total=timeout)) as r:
                 if r.status in retry_statuses and attempt < max_retries:
                     last = HTTPRequestError(url, r.status, (await r.text())[:200])
                 else:

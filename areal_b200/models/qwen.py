@@ -372,7 +372,8 @@ class QwenModel(nn.Module):
         self.first_stage = pctx.is_first_stage if pp > 1 else True
         self.last_stage = pctx.is_last_stage if pp > 1 else True
         # virtual stages: every rank holds `vpp` chunks of blocks; chunk v of rank p is virtual stage v * pp + p,
-        # so the embedding still sits on the first rank (its chunk 0) and the head on the last rank (its last chunk)
+        # so the embedding still sits on the first rank (its chunk 0) and the head on the last rank (its last chunk);
+        # with the V-shaped placement (chunk 1 of rank p = stage 2 pp - 1 - p) the first rank holds both
         self.vpp = int(pctx.extras.get("vpp", 1)) if pp > 1 else 1
         if pp > 1:
             from ..parallel.context import partition_layers
@@ -384,8 +385,11 @@ class QwenModel(nn.Module):
             if self.vpp == 1:
                 self.chunk_ranges = [pctx.layer_range(cfg.num_hidden_layers, last_extra=head)]
             else:
+                from ..parallel.pipeline import stage_of
+
                 ranges = partition_layers([1.0] * cfg.num_hidden_layers, pp * self.vpp, 0.0, head)
-                self.chunk_ranges = [ranges[v * pp + pctx.pp_rank] for v in range(self.vpp)]
+                placement = pctx.extras.get("pp_placement", "interleaved")
+                self.chunk_ranges = [ranges[stage_of(pctx.pp_rank, v, pp, placement)] for v in range(self.vpp)]
         else:
             self.chunk_ranges = [(0, cfg.num_hidden_layers)]
         self.layer_ids = [i for a, b in self.chunk_ranges for i in range(a, b)]  # global index of every local block

@@ -84,8 +84,14 @@ class ParallelContext:
         return self.pp_rank == 0
 
     @property
+    def last_stage_rank(self) -> int:
+        """Pipeline rank that holds the last (virtual) stage: the last rank, or, when the two chunks of every rank
+        are placed in a V over the ranks, the first."""
+        return 0 if self.extras.get("pp_placement") == "v" else self.pp_size - 1
+
+    @property
     def is_last_stage(self) -> bool:
-        return self.pp_rank == self.pp_size - 1
+        return self.pp_rank == self.last_stage_rank
     # FusedCommContext of the tp group (CUDA only; None ⇒ NCCL / gloo collectives)
     tp_fused: Any = None
     sp_fused: Any = None
@@ -206,11 +212,14 @@ def build_mesh(ranks: list[int], dp: int, sp: int = 1, tp: int = 1, pp: int = 1,
             edges = []
             for i in range(pp):
                 pair = [col[i], col[(i + 1) % pp]]
-                edges.append((dist.new_group(pair), dist.new_group(pair)))
+                # activations down, gradients up, and the same again for chunks placed on the way back up (V shape)
+                edges.append(tuple(dist.new_group(pair) for _ in range(4)))
             if me in col:
                 i = col.index(me)
                 links = PipelineLinks(prev=col[i - 1], next=col[(i + 1) % pp], fwd_prev=edges[i - 1][0],
-                                      bwd_prev=edges[i - 1][1], fwd_next=edges[i][0], bwd_next=edges[i][1])
+                                      bwd_prev=edges[i - 1][1], fwd_next=edges[i][0], bwd_next=edges[i][1],
+                                      vfwd_prev=edges[i - 1][2], vbwd_prev=edges[i - 1][3],
+                                      vfwd_next=edges[i][2], vbwd_next=edges[i][3])
     cpu_sh = (None, 0, 1)
     if cpu_groups and dist.is_initialized() and not backend_is_gloo:
         buckets: dict[Any, list[int]] = {}

@@ -35,8 +35,19 @@ where they are host-side requests); on CUDA a receive is posted when its action 
 
 Reference: areal/experimental/models/archon/pipeline_parallel.py:48-82 (``build_pipeline_schedule``:
 1F1B, Interleaved1F1B, zero-bubble variants) and :349-494, options areal/api/cli_args.py:537-700; Megatron's
-schedules behind areal/engine/megatron_engine.py:882. The reference's ZBV variant also places the chunks in
-a V shape over the ranks; here both zero-bubble names select the split schedule over the interleaved placement.
+schedules behind areal/engine/megatron_engine.py:882.
+
+Placement. With the interleaved placement chunk ``v`` of rank ``p`` is virtual stage ``v * P + p`` (activations
+always flow to the next rank, and from the last rank back to the first). ``ZBVZeroBubble`` uses the V-shaped
+placement instead (two chunks per rank): chunk 0 of rank ``p`` is stage ``p``, chunk 1 is stage ``2P - 1 - p``, so
+activations run down the ranks and back up, the first rank holds the embedding AND the head / loss (a tied
+embedding needs no second copy), the turn-around on the last rank is a local hand-over, and every rank holds the
+same amount of live activations (the reference puts the last stage on rank 0 the same way,
+areal/experimental/engine/archon_engine.py:930-938). Its schedule comes from a list scheduler as well
+(:func:`_v_schedules`): the first rank keeps at most ``P`` micro-batches in flight, which bounds every rank's
+live activations by ``2P`` chunks (``P`` stages' worth, the 1F1B peak), and weight-gradient work fills the gaps.
+The chunks going back up send activations to the PREVIOUS rank and gradients to the NEXT, over two more one-way
+groups per neighbour pair.
 """
 
 from __future__ import annotations
@@ -56,8 +67,29 @@ Action = tuple[str, int, int]  # kind, micro-batch, chunk
 _ALIASES = {
     "gpipe": "gpipe", "1f1b": "1f1b", "interleaved1f1b": "interleaved_1f1b", "interleaved_1f1b": "interleaved_1f1b",
     "interleavedzerobubble": "zero_bubble", "zbvzerobubble": "zero_bubble", "zerobubble": "zero_bubble",
-    "zb1p": "zero_bubble", "zbh1": "zero_bubble", "zero_bubble": "zero_bubble",
+    "zb1p": "zero_bubble", "zbh1": "zero_bubble", "zero_bubble": "zero_bubble", "zbv": "zero_bubble",
 }
+
+
+_V_PLACED = {"zbvzerobubble", "zbv"}
+
+
+def placement_of(name: str) -> str:
+    """``"v"`` for the schedules that place their two chunks per rank in a V over the ranks, else
+    ``"interleaved"``."""
+    return "v" if str(name).replace("-", "").replace("_", "").replace(" ", "").lower() in _V_PLACED else "interleaved"
+
+
+def stage_of(rank: int, chunk: int, P: int, placement: str = "interleaved") -> int:
+    if placement == "v":
+        return rank if chunk == 0 else 2 * P - 1 - rank
+    return chunk * P + rank
+
+
+def rank_of(stage: int, P: int, placement: str = "interleaved") -> int:
+    if placement == "v":
+        return stage if stage < P else 2 * P - 1 - stage
+    return stage % P
 
 
 def canonical_schedule(name: str, virtual: int) -> str:
@@ -73,10 +105,17 @@ def canonical_schedule(name: str, virtual: int) -> str:
 
 
 def build_schedule(name: str, pp_size: int, n_mbs: int, rank: int, virtual: int = 1,
-                   forward_only: bool = False) -> list[Action]:
+                   forward_only: bool = False, placement: str = "interleaved") -> list[Action]:
     """The action list of pipeline rank ``rank``."""
     P, M, V = pp_size, n_mbs, virtual
     kind = canonical_schedule(name, V)
+    if placement == "v":
+        import os
+
+        if V != 2 or (kind != "zero_bubble" and not forward_only):
+            raise ValueError("the V-shaped placement runs two chunks per rank under the zero-bubble schedule")
+        slack = float(os.environ.get("AREAL_B200_PP_ZB_SLACK", "0"))
+        return list(_v_schedules(P, M, slack, forward_only)[rank])
     if forward_only:
         if V == 1:
             return [("F", m, 0) for m in range(M)]
@@ -186,6 +225,85 @@ def _zero_bubble_schedules(P: int, M: int, V: int, slack: float = 0.0) -> tuple[
     return tuple(tuple(a) for a in acts)
 
 
+@functools.lru_cache(maxsize=64)
+def _v_schedules(P: int, M: int, slack: float = 0.0, forward_only: bool = False) -> tuple[tuple[Action, ...], ...]:
+    """Action lists of all ranks for the V-shaped placement (chunk 0 of rank ``p`` = stage ``p``, chunk 1 = stage
+    ``2P - 1 - p``), by list scheduling with unit costs.
+
+    Every rank runs the forwards of a chunk in micro-batch order and its backwards likewise, so every one-way
+    link carries its messages in one order on both ends. A free rank takes, in this order: a backward whose
+    gradient has arrived (the older micro-batch first); the forward of its returning chunk (stages ``P..2P-1``:
+    these finish micro-batches); the forward of its outgoing chunk; a parked weight-gradient product. Memory: the
+    first rank admits a new micro-batch only while fewer than ``P (+ slack)`` are in flight, which bounds the live
+    activations of EVERY rank by ``2 (P + slack)`` chunks; a forward also waits (and weight-gradient work runs
+    first) while live activations plus ``PARKED_WEIGHT`` per parked product would pass that bound."""
+    last = 2 * P - 1
+    cap = 2 * (P + slack)
+    done: dict[tuple[str, int, int], float] = {}
+    nf = [[0, 0] for _ in range(P)]
+    nb = [[0, 0] for _ in range(P)]
+    parked: list[list[tuple[int, int]]] = [[] for _ in range(P)]
+    free = [0.0] * P
+    acts: list[list[Action]] = [[] for _ in range(P)]
+    n_left = (2 * M if forward_only else 6 * M) * P
+    now = 0.0
+    stage = lambda r, c: r if c == 0 else last - r
+    while n_left:
+        progressed = False
+        for r in range(P):
+            if free[r] > now:
+                continue
+            choice = None
+            if not forward_only:
+                ready = []
+                for c in (0, 1):
+                    if nb[r][c] < M:
+                        mb, st = nb[r][c], stage(r, c)
+                        dep = ("F", mb, st) if st == last else ("B", mb, st + 1)
+                        if done.get(dep, float("inf")) <= now:
+                            ready.append((mb, c))
+                if ready:
+                    mb, c = min(ready)
+                    choice = ("B", mb, c)
+            if choice is None:
+                live = (nf[r][0] - nb[r][0]) + (nf[r][1] - nb[r][1])
+                room = forward_only or live + PARKED_WEIGHT * len(parked[r]) + 1 <= cap
+                for c in (1, 0):
+                    if nf[r][c] >= M or not room:
+                        continue
+                    mb, st = nf[r][c], stage(r, c)
+                    if st == 0:
+                        if not forward_only and nf[0][0] - nb[0][0] >= P + slack:
+                            continue  # the first rank keeps at most P (+ slack) micro-batches in flight
+                    elif done.get(("F", mb, st - 1), float("inf")) > now:
+                        continue
+                    choice = ("F", mb, c)
+                    break
+            if choice is None and parked[r]:
+                choice = ("W",) + parked[r][0]
+            if choice is None:
+                continue
+            kind, mb, c = choice
+            if kind == "F":
+                nf[r][c] += 1
+            elif kind == "B":
+                nb[r][c] += 1
+                parked[r].append((mb, c))
+            else:
+                parked[r].pop(0)
+            free[r] = now + 1.0
+            done[(kind, mb, stage(r, c))] = free[r]
+            acts[r].append(choice)
+            n_left -= 1
+            progressed = True
+        if n_left and not progressed:
+            later = [t for t in free if t > now]
+            if not later:
+                raise RuntimeError(f"V-placement list scheduling stalled (P={P}, M={M})")
+            now = min(later)
+    return tuple(tuple(a) for a in acts)
+
+
 def _virtual_to_mb_chunk(k: int, P: int, V: int, forward: bool) -> tuple[int, int]:
     """Micro-batch and chunk of the ``k``-th forward (backward) of a rank under the interleaved order."""
     group, r = divmod(k, P * V)
@@ -210,12 +328,13 @@ class SimResult:
 
 
 def simulate(name: str, pp_size: int, n_mbs: int, virtual: int = 1, f_cost: float = 1.0, b_cost: float = 2.0,
-             comm_cost: float = 0.0, w_cost: float | None = None) -> SimResult:
+             comm_cost: float = 0.0, w_cost: float | None = None, placement: str | None = None) -> SimResult:
     """Replays the schedule of every rank with per-chunk costs ``f_cost / V`` and ``b_cost / V``: an action
     starts when the rank is free and its input has arrived. In a split-backward schedule ``W`` costs
     ``w_cost / V`` (default: half of ``b_cost``) and ``B`` the rest. Raises if the schedules deadlock."""
     P, V = pp_size, virtual
-    acts = [build_schedule(name, P, n_mbs, r, V) for r in range(P)]
+    placement = placement or placement_of(name)
+    acts = [build_schedule(name, P, n_mbs, r, V, placement=placement) for r in range(P)]
     split = any(a[0] == "W" for a in acts[0])
     w_cost = (b_cost / 2 if w_cost is None else w_cost) if split else 0.0
     costs = {"F": f_cost / V, "B": (b_cost - w_cost) / V, "W": w_cost / V}
@@ -233,7 +352,7 @@ def simulate(name: str, pp_size: int, n_mbs: int, virtual: int = 1, f_cost: floa
         for r in range(P):
             while ptr[r] < len(acts[r]):
                 kind, mb, c = acts[r][ptr[r]]
-                vs = c * P + r
+                vs = stage_of(r, c, P, placement)
                 if kind == "F":
                     dep = None if vs == 0 else ("F", mb, vs - 1)
                 elif kind == "B":
@@ -242,7 +361,7 @@ def simulate(name: str, pp_size: int, n_mbs: int, virtual: int = 1, f_cost: floa
                     dep = ("B", mb, vs)
                 if dep is not None and dep not in done:
                     break
-                ready = 0.0 if dep is None else done[dep] + (comm_cost if dep[2] != vs else 0.0)
+                ready = 0.0 if dep is None else done[dep] + (comm_cost if rank_of(dep[2], P, placement) != r else 0.0)
                 start = max(free[r], ready)
                 cost = costs[kind]
                 free[r] = start + cost
@@ -275,6 +394,11 @@ class PipelineLinks:
     fwd_next: Any = None
     bwd_prev: Any = None
     bwd_next: Any = None
+    # the V-shaped placement's returning chunks: activations next → this → prev, gradients prev → this → next
+    vfwd_next: Any = None
+    vfwd_prev: Any = None
+    vbwd_prev: Any = None
+    vbwd_next: Any = None
 
 
 class _Pending:
@@ -301,17 +425,18 @@ class PipelineRunner:
     shape of the activations travelling between stages for that micro-batch."""
 
     def __init__(self, links: PipelineLinks, pp_rank: int, pp_size: int, virtual: int, schedule: str,
-                 dtype: torch.dtype, device: torch.device):
+                 dtype: torch.dtype, device: torch.device, placement: str = "interleaved"):
         self.links, self.rank, self.P, self.V = links, pp_rank, pp_size, virtual
-        self.schedule = schedule
+        self.schedule, self.placement = schedule, placement
         self.dtype, self.device = dtype, device
         import os
 
         self.prefetch = (device.type != "cuda") if os.environ.get("AREAL_B200_PP_PREFETCH") is None \
             else os.environ["AREAL_B200_PP_PREFETCH"] == "1"
-        if not getattr(links, "opened", False):
+        flag = "opened_v" if placement == "v" else "opened"
+        if not getattr(links, flag, False):
             self._open_links()
-            links.opened = True
+            setattr(links, flag, True)
 
     def _open_links(self):
         """One element over every link this rank uses, in ring order (edge i joins stage i and stage i + 1):
@@ -320,10 +445,18 @@ class PipelineRunner:
         L, P = self.links, self.P
         token = torch.zeros(1, dtype=self.dtype, device=self.device)
         edges = []  # (edge index, [(group, i_send)])
-        if self.rank < P - 1 or self.V > 1:
-            edges.append((self.rank, [(L.fwd_next, True, L.next), (L.bwd_next, False, L.next)]))
-        if self.rank > 0 or self.V > 1:
-            edges.append(((self.rank - 1) % P, [(L.fwd_prev, False, L.prev), (L.bwd_prev, True, L.prev)]))
+        if self.placement == "v":  # no ring-closing edge; the two extra streams of every neighbour pair
+            if self.rank < P - 1:
+                edges.append((self.rank, [(L.fwd_next, True, L.next), (L.bwd_next, False, L.next),
+                                          (L.vfwd_next, False, L.next), (L.vbwd_next, True, L.next)]))
+            if self.rank > 0:
+                edges.append((self.rank - 1, [(L.fwd_prev, False, L.prev), (L.bwd_prev, True, L.prev),
+                                              (L.vfwd_prev, True, L.prev), (L.vbwd_prev, False, L.prev)]))
+        else:
+            if self.rank < P - 1 or self.V > 1:
+                edges.append((self.rank, [(L.fwd_next, True, L.next), (L.bwd_next, False, L.next)]))
+            if self.rank > 0 or self.V > 1:
+                edges.append(((self.rank - 1) % P, [(L.fwd_prev, False, L.prev), (L.bwd_prev, True, L.prev)]))
         for _, ops in sorted(edges, key=lambda e: e[0]):
             for group, sending, peer in ops:
                 if sending:
@@ -335,7 +468,29 @@ class PipelineRunner:
 
     # -- which virtual stage talks to whom
     def _vs(self, chunk: int) -> int:
-        return chunk * self.P + self.rank
+        return stage_of(self.rank, chunk, self.P, self.placement)
+
+    def _fwd_route(self, chunk: int):
+        """``(source, destination)`` of a chunk's forward: ``None`` (first / last stage), ``"local"`` (the other
+        chunk of this rank) or ``(peer rank, group)``. Gradients travel the same edges the other way
+        (:meth:`_bwd_route`)."""
+        L, P, r = self.links, self.P, self.rank
+        if self.placement == "v":
+            if chunk == 0:
+                return (None if r == 0 else (L.prev, L.fwd_prev)), ("local" if r == P - 1 else (L.next, L.fwd_next))
+            return ("local" if r == P - 1 else (L.next, L.vfwd_next)), (None if r == 0 else (L.prev, L.vfwd_prev))
+        return (None if self._is_first(chunk) else (L.prev, L.fwd_prev)), \
+            (None if self._is_last(chunk) else (L.next, L.fwd_next))
+
+    def _bwd_route(self, chunk: int):
+        """``(where the output gradient comes from, where the input gradient goes)``."""
+        L, P, r = self.links, self.P, self.rank
+        if self.placement == "v":
+            if chunk == 0:
+                return ("local" if r == P - 1 else (L.next, L.bwd_next)), (None if r == 0 else (L.prev, L.bwd_prev))
+            return (None if r == 0 else (L.prev, L.vbwd_prev)), ("local" if r == P - 1 else (L.next, L.vbwd_next))
+        return (None if self._is_last(chunk) else (L.next, L.bwd_next)), \
+            (None if self._is_first(chunk) else (L.prev, L.bwd_prev))
 
     def _is_first(self, chunk: int) -> bool:
         return self._vs(chunk) == 0
@@ -351,7 +506,10 @@ class PipelineRunner:
     def run(self, n_mbs: int, forward: Callable, finish: Callable, shape_of: Callable,
             forward_only: bool = False) -> dict[int, Any]:
         L = self.links
-        acts = build_schedule(self.schedule, self.P, n_mbs, self.rank, self.V, forward_only=forward_only)
+        acts = build_schedule(self.schedule, self.P, n_mbs, self.rank, self.V, forward_only=forward_only,
+                              placement=self.placement)
+        handed_f: dict[int, tuple] = {}  # micro-batch -> activations handed from this rank's chunk 0 to its chunk 1
+        handed_b: dict[int, tuple] = {}  # micro-batch -> gradients handed back
         sends = _Pending()
         posted: dict[int, tuple[list, list[torch.Tensor]]] = {}  # action index -> receive in flight
         saved: dict[tuple[int, int], tuple] = {}  # (mb, chunk) -> (stage input, outputs, loss)
@@ -363,10 +521,9 @@ class PipelineRunner:
             if i >= len(acts) or i in posted:
                 return
             kind, mb, c = acts[i]
-            if kind == "F" and not self._is_first(c):
-                posted[i] = self._recv(shape_of(mb), L.prev, L.fwd_prev)
-            elif kind == "B" and not self._is_last(c):
-                posted[i] = self._recv(shape_of(mb), L.next, L.bwd_next)
+            src = self._fwd_route(c)[0] if kind == "F" else (self._bwd_route(c)[0] if kind == "B" else None)
+            if isinstance(src, tuple):
+                posted[i] = self._recv(shape_of(mb), src[0], src[1])
 
         import os as _os
         import sys as _sys
@@ -390,8 +547,9 @@ class PipelineRunner:
                 note(f"action {i}: input received")
             if kind == "F":
                 stage_in = None
-                if got is not None:
-                    x_in, r_in = got[1]
+                src, dst = self._fwd_route(c)
+                if got is not None or src == "local":
+                    x_in, r_in = handed_f.pop(mb) if src == "local" else got[1]
                     if not forward_only:
                         x_in.requires_grad_(True)
                         r_in.requires_grad_(True)
@@ -402,8 +560,11 @@ class PipelineRunner:
                     x, res = out
                     res = res if res is not None else torch.zeros_like(x)
                     xs, rs = x.detach(), res.detach()
-                    sends.add(dist.isend(xs, dst=L.next, group=L.fwd_next), xs)
-                    sends.add(dist.isend(rs, dst=L.next, group=L.fwd_next), rs)
+                    if dst == "local":
+                        handed_f[mb] = (xs, rs)  # the turn of the V: this rank's other chunk is the next stage
+                    else:
+                        sends.add(dist.isend(xs, dst=dst[0], group=dst[1]), xs)
+                        sends.add(dist.isend(rs, dst=dst[0], group=dst[1]), rs)
                     if not forward_only:
                         saved[(mb, c)] = (stage_in, (x, res), None)
                 else:
@@ -421,19 +582,23 @@ class PipelineRunner:
                     # input gradients now; the linear layers park their weight-gradient GEMMs for the W action
                     queue = parked[(mb, c)] = WgradQueue()
                 with (queue.collect() if queue is not None else contextlib.nullcontext()):
+                    gsrc, gdst = self._bwd_route(c)
                     if self._is_last(c):
                         loss.backward()
                     else:
-                        gx, gr = got[1]
+                        gx, gr = handed_b.pop(mb) if gsrc == "local" else got[1]
                         torch.autograd.backward([outs[0], outs[1]], [gx, gr])
                 if not self._is_first(c):
                     x_in, r_in = stage_in
                     gx = x_in.grad if x_in.grad is not None else torch.zeros_like(x_in)
                     gr = r_in.grad if r_in.grad is not None else torch.zeros_like(r_in)
-                    sends.add(dist.isend(gx, dst=L.prev, group=L.bwd_prev), gx)
-                    sends.add(dist.isend(gr, dst=L.prev, group=L.bwd_prev), gr)
+                    if gdst == "local":
+                        handed_b[mb] = (gx, gr)
+                    else:
+                        sends.add(dist.isend(gx, dst=gdst[0], group=gdst[1]), gx)
+                        sends.add(dist.isend(gr, dst=gdst[0], group=gdst[1]), gr)
         note("all actions issued: waiting for sends")
         sends.wait_all()
         note("step done")
-        assert not saved and not posted and not parked
+        assert not saved and not posted and not parked and not handed_f and not handed_b
         return results

@@ -4,7 +4,10 @@ talks to an OpenAI-compatible ``base_url``) on worker processes, one session per
 * worker  – ``/run`` instantiates the runnable (import path + kwargs), gives it the session's
             ``base_url`` / ``api_key`` and returns its reward;
 * gateway – ``/sessions/start`` picks a worker (least loaded), ``/sessions/{id}/run`` forwards
-            with session affinity, ``/sessions/{id}/end`` releases the session.
+            with session affinity, ``/sessions/{id}/end`` releases the session. With ``agent=`` it also serves
+            ``/v1/responses`` (the OpenAI Responses protocol): ``user`` names the conversation, the gateway keeps
+            its history (the data-proxy role) and hands ``{"input", "history"}`` to the agent on the session's
+            worker; the agent's text comes back as a ``response`` object.
 Reference: areal/experimental/agent_service/{gateway,router,data_proxy,worker}, protocol.py.
 """
 
@@ -55,7 +58,28 @@ def create_worker_app() -> FastAPI:
     return app
 
 
-def create_gateway_app(token: str | None = None, post=None) -> FastAPI:
+def _input_messages(inp) -> list[dict]:
+    """The ``input`` of a Responses request as chat messages: a string, or items ``{"type": "message", "role",
+    "content"}`` whose content is a string or a list of ``input_text`` parts."""
+    if isinstance(inp, str):
+        return [{"role": "user", "content": inp}]
+    out = []
+    for item in inp or []:
+        if isinstance(item, str):
+            out.append({"role": "user", "content": item})
+            continue
+        if item.get("type", "message") != "message":
+            continue
+        c = item.get("content", "")
+        if isinstance(c, list):
+            c = "".join(part.get("text", "") for part in c if isinstance(part, dict))
+        out.append({"role": item.get("role", "user"), "content": c})
+    return out
+
+
+def create_gateway_app(token: str | None = None, post=None, agent: str | None = None,
+                       agent_kwargs: dict | None = None, base_url: str | None = None,
+                       api_key: str | None = None, max_history: int = 64) -> FastAPI:
     app = FastAPI()
     reg = WorkerRegistry("least_loaded")
     auth = make_auth(token)
@@ -97,5 +121,46 @@ def create_gateway_app(token: str | None = None, post=None) -> FastAPI:
         reg.end_session(sid)
         return {"runs": info["runs"]}
 
+    conversations: dict[str, list[dict]] = {}
+
+    @app.post("/v1/responses")
+    async def responses(req: Request):
+        auth(req)
+        if agent is None:
+            raise HTTPException(status_code=501, detail="this gateway was started without an agent")
+        b = await req.json()
+        user = str(b.get("user") or uuid.uuid4().hex)
+        new = _input_messages(b.get("input"))
+        if not new:
+            raise HTTPException(status_code=400, detail="`input` holds no message")
+        history = conversations.setdefault(user, [])
+        if user not in sessions:
+            sessions[user] = {"base_url": base_url, "api_key": api_key, "runs": 0}
+            reg.pick(user)
+        sessions[user]["runs"] += 1
+        payload = {"agent": agent, "agent_kwargs": serialize_value(agent_kwargs or {}),
+                   "data": serialize_value({"input": new, "history": list(history), "model": b.get("model")}),
+                   "base_url": base_url, "api_key": api_key}
+        out = deserialize_value(forward(reg, "/run", payload, user, post=post)["result"])
+        text = out.get("output_text", "") if isinstance(out, dict) else str(out)
+        history.extend(new)
+        history.append({"role": "assistant", "content": text})
+        del history[:-max_history]
+        rid = "resp_" + uuid.uuid4().hex
+        return {"id": rid, "object": "response", "status": "completed", "model": b.get("model") or "agent",
+                "user": user, "output_text": text,
+                "output": [{"type": "message", "id": "msg_" + rid[5:], "role": "assistant", "status": "completed",
+                            "content": [{"type": "output_text", "text": text, "annotations": []}]}],
+                "metadata": {k: v for k, v in out.items() if k != "output_text"} if isinstance(out, dict) else {}}
+
+    @app.post("/v1/conversations/{user}/reset")
+    async def reset(user: str, req: Request):
+        auth(req)
+        n = len(conversations.pop(user, []))
+        if sessions.pop(user, None) is not None:
+            reg.end_session(user)
+        return {"dropped_messages": n}
+
     app.state.registry = reg
+    app.state.conversations = conversations
     return app

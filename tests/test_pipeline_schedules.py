@@ -49,13 +49,13 @@ def test_1f1b_bounds_live_activations_and_interleaving_shrinks_the_bubble():
 
 def test_zero_bubble_fills_idle_time_with_weight_gradients_at_the_memory_of_1f1b():
     for P, M, V, base in [(4, 8, 1, "1F1B"), (8, 32, 1, "1F1B"), (4, 8, 2, "Interleaved1F1B"), (2, 4, 2, "Interleaved1F1B")]:
-        z, o = simulate("ZBVZeroBubble", P, M, V), simulate(base, P, M, V)
+        z, o = simulate("InterleavedZeroBubble", P, M, V), simulate(base, P, M, V)
         assert z.makespan < o.makespan and z.bubble_fraction < 0.75 * o.bubble_fraction
         assert abs(sum(z.busy) - sum(o.busy)) < 1e-9                    # same work, less waiting
         assert z.peak_live == o.peak_live                                # F-to-B activations: the 1F1B bound
         # same order of forwards and of input-gradient passes on every rank: messages on every link keep their order
         for r in range(P):
-            za, oa = build_schedule("ZBVZeroBubble", P, M, r, V), build_schedule(base, P, M, r, V)
+            za, oa = build_schedule("InterleavedZeroBubble", P, M, r, V), build_schedule(base, P, M, r, V)
             assert [a for a in za if a[0] == "F"] == [a for a in oa if a[0] == "F"]
             assert [a for a in za if a[0] == "B"] == [a for a in oa if a[0] == "B"]
     # memory: live activations plus half a set per parked micro-batch never exceed the 1F1B bound of the rank
@@ -65,6 +65,37 @@ def test_zero_bubble_fills_idle_time_with_weight_gradients_at_the_memory_of_1f1b
         for kind, _, _ in build_schedule("ZB1P", P, M, r):
             nf, nb, nw = nf + (kind == "F"), nb + (kind == "B"), nw + (kind == "W")
             assert (nf - nb) + 0.5 * (nb - nw) <= P - r
+
+
+def test_v_shaped_placement_halves_the_bubble_at_balanced_memory():
+    """ZBVZeroBubble: chunk 0 of rank p is stage p, chunk 1 stage 2P - 1 - p. Against the split schedule over the
+    interleaved placement it waits about half as long, and no rank holds more than 2P live chunks (P stages' worth,
+    what plain 1F1B holds on its first rank), where the interleaved placement piles ~3P on the first rank."""
+    from areal_b200.parallel.pipeline import placement_of, rank_of, stage_of
+
+    assert placement_of("ZBVZeroBubble") == "v" and placement_of("InterleavedZeroBubble") == "interleaved"
+    assert [stage_of(r, c, 4, "v") for c in (0, 1) for r in range(4)] == [0, 1, 2, 3, 7, 6, 5, 4]
+    assert [rank_of(s, 4, "v") for s in range(8)] == [0, 1, 2, 3, 3, 2, 1, 0]
+    for P, M in [(2, 4), (4, 8), (4, 16), (8, 32)]:
+        v, i = simulate("ZBVZeroBubble", P, M, 2), simulate("InterleavedZeroBubble", P, M, 2)
+        assert v.bubble_fraction < 0.6 * i.bubble_fraction, (P, M, v.bubble_fraction, i.bubble_fraction)
+        assert abs(sum(v.busy) - sum(i.busy)) < 1e-9
+        assert max(v.peak_live) <= 2 * P < max(i.peak_live)
+        for r in range(P):
+            acts = build_schedule("ZBVZeroBubble", P, M, r, 2, placement="v")
+            assert sorted(acts) == sorted((k, m, c) for k in "FBW" for m in range(M) for c in (0, 1))
+            for kind in "FB":            # every stream of every link is in micro-batch order on both ends
+                for c in (0, 1):
+                    assert [a[1] for a in acts if a[0] == kind and a[2] == c] == list(range(M))
+            live = parked = 0            # live activations plus half a set per parked product stay within 2P chunks
+            for kind, _, _ in acts:
+                live += (kind == "F") - (kind == "B")
+                parked += (kind == "B") - (kind == "W")
+                assert live + 0.5 * parked <= 2 * P + 0.5
+    fwd = [build_schedule("ZBVZeroBubble", 4, 8, r, 2, forward_only=True, placement="v") for r in range(4)]
+    assert all(sorted(a) == sorted(("F", m, c) for m in range(8) for c in (0, 1)) for a in fwd)
+    with pytest.raises(ValueError, match="two chunks"):
+        simulate("ZBVZeroBubble", 4, 8, 1)
 
 
 def test_weight_gradient_products_can_be_parked_and_run_later():
@@ -139,7 +170,9 @@ def _ref(tmp_path, n_mbs):
                                      (2, ["--pp", "2", "--vpp", "2", "--schedule", "Interleaved1F1B"]),
                                      (4, ["--pp", "4", "--schedule", "1F1B"]),
                                      (2, ["--pp", "2", "--schedule", "ZB1P"]),
-                                     (4, ["--pp", "4", "--schedule", "ZBVZeroBubble"]),
+                                     (4, ["--pp", "4", "--schedule", "ZB1P"]),
+                                     (2, ["--pp", "2", "--schedule", "ZBVZeroBubble"]),
+                                     (3, ["--pp", "3", "--schedule", "ZBVZeroBubble"]),
                                      (2, ["--pp", "2", "--vpp", "2", "--schedule", "InterleavedZeroBubble"]),
                                      (4, ["--pp", "2", "--tp", "2", "--vpp", "2"])])
 def test_step_with_eight_micro_batches_matches_single_process(tmp_path, n, flags):

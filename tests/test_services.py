@@ -397,3 +397,58 @@ def test_gateway_train_engine_drives_real_engines_through_the_service(tmp_path):
     assert client.get_version() == 4 and all(e.get_version() == 4 for e in engines)
     for e in engines + [ref]:
         e.destroy()
+
+
+def test_agent_service_speaks_the_responses_protocol_and_keeps_the_conversation():
+    """``/v1/responses``: ``user`` names the conversation, the gateway keeps its history and hands it to the agent on
+    the session's worker; the example agent calls its chat endpoint, runs the calculator the model asks for, and its
+    answer comes back as a ``response`` object."""
+    import os
+    import sys
+
+    sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+    from examples.agent_service import agent as agent_mod
+
+    seen = []
+
+    def fake_chat(url, body):
+        seen.append((url, [dict(m) for m in body["messages"]]))
+        last = body["messages"][-1]["content"]
+        if last.startswith("<result>"):
+            text = f"The answer is {last[8:-9]}."
+        elif "17 * 23" in last:
+            text = "Let me compute. <calc>17 * 23</calc> (waiting)"
+        else:
+            text = f"You have sent {sum(m['role'] == 'user' for m in body['messages'])} messages."
+        return {"choices": [{"message": {"role": "assistant", "content": text}}]}
+
+    orig = agent_mod.ChatAgent.__init__
+    agent_mod.ChatAgent.__init__ = lambda self, **kw: orig(self, post=fake_chat, **kw)
+    try:
+        net = Net()
+        net.add("a0:1", agent_service.create_worker_app())
+        net.add("a1:1", agent_service.create_worker_app())
+        gw = TestClient(agent_service.create_gateway_app(post=net.post, agent="examples.agent_service.agent.ChatAgent",
+                                                         agent_kwargs={"model": "m"}, base_url="http://llm/v1"))
+        for i in range(2):
+            gw.post("/register", json={"worker_id": f"a{i}", "addr": f"a{i}:1"})
+        r = gw.post("/v1/responses", json={"input": [{"type": "message", "content": "What is 17 * 23?"}],
+                                           "user": "alice", "model": "m"}).json()
+        assert r["object"] == "response" and r["output_text"] == "The answer is 391."
+        assert r["output"][0]["content"][0] == {"type": "output_text", "text": "The answer is 391.", "annotations": []}
+        assert r["metadata"]["tool_calls"] == 1 and seen[0][0] == "http://llm/v1/chat/completions"
+        # the second turn of the same user sees the first; another user starts empty
+        r2 = gw.post("/v1/responses", json={"input": "and how many messages so far?", "user": "alice"}).json()
+        assert r2["output_text"] == "You have sent 2 messages."
+        r3 = gw.post("/v1/responses", json={"input": [{"type": "message", "role": "user",
+                                                       "content": [{"type": "input_text", "text": "hello"}]}],
+                                            "user": "bob"}).json()
+        assert r3["output_text"] == "You have sent 1 messages."
+        assert len(gw.app.state.conversations["alice"]) == 4
+        assert gw.post("/v1/conversations/alice/reset", json={}).json()["dropped_messages"] == 4
+        assert gw.post("/v1/responses", json={"input": [], "user": "bob"}).status_code == 400
+    finally:
+        agent_mod.ChatAgent.__init__ = orig
+    bare = TestClient(agent_service.create_gateway_app(post=net.post))
+    assert bare.post("/v1/responses", json={"input": "hi"}).status_code == 501
+    assert agent_mod.calculate("2 ** 10 - 24") == "1000" and agent_mod.calculate("__import__('os')").startswith("error")

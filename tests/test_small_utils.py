@@ -501,3 +501,29 @@ def test_reference_named_entry_points_exist_and_work():
     assert hasattr(PPOCriticEngine, "compute_values") and default_get_input_ids_fn is default_get_input_ids
     assert default_data_extract_prompt_fn({"messages": [{"role": "user", "content": "q"}]})[0]["content"] == "q"
     assert default_data_extract_prompt_fn({"input_ids": [1, 2]}) == [1, 2]
+
+
+def test_http_helper_passes_headers(monkeypatch):
+    """The gateway-side engines authenticate with a bearer header: the retrying helper has to carry it."""
+    import requests
+
+    from areal_b200.infra.utils import http
+
+    seen = {}
+
+    class R:
+        status_code = 200
+        text = "{}"
+
+        def json(self):
+            return {}
+
+    def fake(method, url, **kw):
+        seen.update(kw, method=method, url=url)
+        return R()
+
+    monkeypatch.setattr(requests, "request", fake)
+    http.request_with_retry("POST", "http://x/y", json={"a": 1}, headers={"Authorization": "Bearer t"}, max_retries=0)
+    assert seen["headers"] == {"Authorization": "Bearer t"} and seen["json"] == {"a": 1}
+    http.request_with_retry("GET", "http://x/y", max_retries=0)
+    assert seen["headers"] is None

@@ -163,14 +163,19 @@ def main():
         return orig_step(*a, **k)
 
     eng.optimizer.step = step
+    # per-token outputs before the step (under pipeline parallelism: computed on the last stage, handed to all)
+    before = None if (args.images or cuda) else eng.forward_batch(data)
     lf = (lambda v, mb: ((v - 0.3) ** 2 * mb["loss_mask"].float()).sum() / mb["loss_mask"].sum()) if args.critic else loss_fn
     stats = eng.train_batch(data, lf, weight_fn)
     if args.ref:
-        torch.save(dict(loss=stats["loss"], grad_norm=stats["grad_norm"], grads=captured), args.file)
+        torch.save(dict(loss=stats["loss"], grad_norm=stats["grad_norm"], grads=captured, before=before), args.file)
         print("ref", stats["loss"], stats["grad_norm"])
         return
     ref = torch.load(args.file, map_location="cuda" if cuda else "cpu")
     pctx, mesh = eng.pctx, eng.mesh
+    if before is not None and ref.get("before") is not None:
+        want = ref["before"][eng.data_parallel_rank::mesh.dp_size]
+        assert (before - want).abs().max() < 2e-4, ("forward_batch", float((before - want).abs().max()))
     full = {}
     for name, g in captured.items():
         g = g.clone()
@@ -191,7 +196,8 @@ def main():
             continue
         if mesh.shard_size > 1:
             dist.all_reduce(g, group=mesh.shard_group)
-        if pctx.pp_size > 1 and name == "embed" and eng.model_config.tie_word_embeddings and not args.critic:
+        if pctx.pp_size > 1 and name == "embed" and eng.model_config.tie_word_embeddings and not args.critic \
+                and pctx.last_stage_rank != 0:  # (V-shaped placement: one copy serves the lookup and the head)
             # tied embedding / head: the first stage holds the lookup's share of the gradient, the last the head's
             dist.all_reduce(g, group=pctx.pp_tie_group)
         if pctx.tp_size > 1:
