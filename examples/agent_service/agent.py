@@ -78,5 +78,10 @@ class ChatAgent:
         return {"output_text": text.strip(), "tool_calls": calls}
 
 
-def describe() -> str:
-    return json.dumps({"agent": "examples.agent_service.agent.ChatAgent", "tools": ["calc"]})
+def main():
+    """Prints what to pass to the service (`agent=` of ``create_gateway_app``)."""
+    print(json.dumps({"agent": "examples.agent_service.agent.ChatAgent", "tools": ["calc"]}))
+
+
+if __name__ == "__main__":
+    main()

@@ -22,7 +22,29 @@ def _cls(path):
     return GRPOConfig
 
 
-@pytest.mark.parametrize("path", sorted(glob.glob(os.path.join(ROOT, "examples", "**", "*.yaml"), recursive=True)))
+def test_skypilot_task_files_parse_and_name_existing_files():
+    import re
+
+    import yaml
+
+    files = sorted(glob.glob(os.path.join(ROOT, "examples", "skypilot", "*.sky.yaml")))
+    assert len(files) == 2
+    for f in files:
+        task = yaml.safe_load(open(f))
+        assert task["resources"]["accelerators"].startswith("B200:") and "torch.distributed.run" in task["run"]
+        named = re.findall(r"(examples/[\w/.]+\.(?:py|yaml))", task["run"])
+        assert len(named) == 2 and all(os.path.exists(os.path.join(ROOT, n)) for n in named), named
+        # the overrides after the config path are fields of the experiment config
+        overrides = [w for w in task["run"].replace("\\\n", " ").split() if "=" in w and not w.startswith("--")
+                     and "$(" not in w and not w.startswith("HEAD_IP")]
+        env = {k: str(v) for k, v in task.get("envs", {}).items()}
+        overrides = [re.sub(r"\$(\w+)", lambda m: env.get(m.group(1), "x"), w) for w in overrides]
+        cfg, _ = load_expr_config(["--config", os.path.join(ROOT, named[1])] + overrides, GRPOConfig)
+        assert cfg.trial_name == "sky0"
+
+
+@pytest.mark.parametrize("path", sorted(p for p in glob.glob(os.path.join(ROOT, "examples", "**", "*.yaml"), recursive=True)
+                                        if not p.endswith(".sky.yaml")))
 def test_yaml_loads(path):
     cfg, _ = load_expr_config(["--config", path, "trial_name=t"], _cls(path))
     assert cfg.experiment_name and cfg.trial_name == "t"
