@@ -6,6 +6,8 @@
   [{"input", "output"}]}`` become ``{"messages", "tests"}`` for the sandbox reward (``reward/code.py``).
 * ``terminal`` (paths containing ``terminal``): records ``{"instruction", "files", "checks"}`` become
   ``{"messages", "instruction", "files", "checks"}`` for :class:`~areal_b200.workflow.agents.TerminalAgent`.
+* ``desk`` (paths containing ``desk``): service-desk task records (``workflow/agents/service_desk_agent.py``); a
+  path of the form ``generate:desk:<n>:<seed>`` generates them instead of reading a file.
 
 Role in the reference: the dataset preparation inside examples/search_agent/tongyi_deepresearch/train.py
 and examples/terminal_bench/train.py.
@@ -52,4 +54,20 @@ def terminal_rl(path, split="train", tokenizer=None, max_length=None, **kw):
     return out
 
 
-BUILDERS = {("qa", "rl"): qa_rl, ("terminal", "rl"): terminal_rl, ("code", "rl"): code_rl}
+def desk_rl(path, split="train", tokenizer=None, max_length=None, **kw):
+    if str(path).startswith("generate:desk"):
+        from ..workflow.agents.service_desk_agent import make_desk_tasks
+
+        parts = str(path).split(":")
+        n = int(parts[2]) if len(parts) > 2 else 256
+        seed = int(parts[3]) if len(parts) > 3 else 0
+        return make_desk_tasks(n, seed + (0 if split == "train" else 1_000_003))
+    out = []
+    for r in load_records(path, split):
+        if "db" not in r or "opening" not in r:
+            continue
+        out.append(dict(r, messages=r.get("messages") or [{"role": "user", "content": r["opening"]}]))
+    return out
+
+
+BUILDERS = {("qa", "rl"): qa_rl, ("terminal", "rl"): terminal_rl, ("code", "rl"): code_rl, ("desk", "rl"): desk_rl}

@@ -263,3 +263,74 @@ def test_remote_sandbox_service_and_client():
     bad = down.run("print(1)")
     assert not bad.ok and "sandbox service error" in bad.stderr and code_reward_fn(None, good, None, None, tests=tests, sandbox=down) == 0.0
     assert asyncio.run(sb.arun("print(7)")).stdout.strip() == "7"
+
+
+def test_service_desk_domain_policy_and_reward():
+    """The tools keep the data consistent but do not enforce the policy; the reward compares the final database with
+    what the task's reference actions produce and checks what the agent told the customer."""
+    from areal_b200.workflow.agents.service_desk_agent import (DeskDB, ScriptedUser, STOP, desk_reward,
+                                                               expected_state, make_desk_tasks)
+
+    tasks = make_desk_tasks(8, seed=3)
+    assert [t["kind"] for t in tasks[:4]] == ["cancel_ok", "cancel_refuse", "change", "bags"]
+    assert make_desk_tasks(8, seed=3) == tasks and make_desk_tasks(8, seed=4) != tasks
+    ok, refuse, change, bags = tasks[:4]
+    rid = next(iter(refuse["db"]["reservations"]))
+    db = DeskDB(refuse["db"])
+    seats = db.data["flights"][db.data["reservations"][rid]["flight_number"]]["seats"]
+    assert desk_reward(refuse, db.data, ["I am sorry, this reservation cannot be cancelled."]) == 1.0
+    assert json.loads(db.call("get_reservation_details", {"reservation_id": rid}))["insurance"] is False
+    assert json.loads(db.call("cancel_reservation", json.dumps({"reservation_id": rid}))) == {"status": "cancelled"}
+    assert db.data["flights"][db.data["reservations"][rid]["flight_number"]]["seats"] == seats + 1
+    assert desk_reward(refuse, db.data, []) == 0.0                      # the forbidden cancellation went through
+    assert db.call("cancel_reservation", {"reservation_id": rid}).startswith("error:")
+    assert db.call("get_user_details", {"user_id": "nobody"}).startswith("error:") and \
+        db.call("drop_tables", {}).startswith("error:")
+    # the reference actions reach the reference state; the required information must have been said
+    db = DeskDB(change["db"])
+    a = change["expected_actions"][0]
+    assert "price_difference" in json.loads(db.call(a["name"], a["arguments"]))
+    assert db.data == expected_state(change)
+    assert desk_reward(change, db.data, [f"Done, you are now on {change['outputs'][0]}."]) == 1.0
+    assert desk_reward(change, db.data, ["Done."]) == 0.0
+    assert db.call("change_flight", {"reservation_id": a["arguments"]["reservation_id"], "flight_number": "ZZ1"}).startswith("error:")
+    user = ScriptedUser(bags)
+    assert asyncio.run(user.respond("May I have your user id?")).startswith("My user id is user_")
+    assert "reservation is R" in asyncio.run(user.respond("Thanks. Which reservation is it about?"))
+    assert "in total" in asyncio.run(user.respond("How many bags do you need?"))
+    assert asyncio.run(user.respond("I will set it to that. Do you confirm?")) == "Yes, please go ahead."
+    assert asyncio.run(user.respond("Done. Goodbye!")) == STOP
+
+
+def test_service_desk_agent_episodes_against_a_scripted_client():
+    from areal_b200.workflow.agents import ServiceDeskAgent, make_desk_tasks
+
+    ok, refuse, change, bags = make_desk_tasks(4, seed=5)
+    rid = next(iter(ok["db"]["reservations"]))
+    good = ScriptedClient([
+        {"content": "Sure. May I have your user id?"},
+        {"tool_calls": [("get_user_details", {"user_id": ok["user_id"]})]},
+        {"content": "Thank you. Which reservation would you like to cancel?"},
+        {"tool_calls": [("get_reservation_details", {"reservation_id": rid})]},
+        {"content": "This reservation can be cancelled. Shall I proceed?"},
+        {"tool_calls": [("cancel_reservation", {"reservation_id": rid})]},
+        {"content": "It is cancelled. Goodbye!"},
+    ])
+    assert asyncio.run(ServiceDeskAgent().run(ok, client=good)) == 1.0
+    # the customer's answers reached the agent, and the tool result followed the call
+    seen = [m for m in good.requests[-1]["messages"] if m["role"] == "user"]
+    assert [m["content"] for m in seen][1:] == [ok["facts"]["user id"], ok["facts"]["reservation"], "Yes, please go ahead."]
+    assert good.requests[-1]["messages"][-1]["role"] == "tool" and good.requests[0]["tools"]
+    # cancelling where the policy forbids it costs the reward; refusing earns it
+    rid2 = next(iter(refuse["db"]["reservations"]))
+    bad = ScriptedClient([{"tool_calls": [("cancel_reservation", {"reservation_id": rid2})]}, {"content": "Done, goodbye."}])
+    assert asyncio.run(ServiceDeskAgent().run(refuse, client=bad)) == 0.0
+    polite = ScriptedClient([{"content": "I am sorry: economy without insurance, booked more than a day ago, cannot be "
+                                         "cancelled. Goodbye."}])
+    assert asyncio.run(ServiceDeskAgent().run(refuse, client=polite)) == 1.0
+    # an agent that never finishes is cut off at max_turns with the database untouched
+    looping = ScriptedClient([{"tool_calls": [("get_user_details", {"user_id": bags["user_id"]})]}] * 5)
+    assert asyncio.run(ServiceDeskAgent(max_turns=5).run(bags, client=looping)) == 0.0
+    items = get_custom_dataset(path="generate:desk:6:1", type="rl")
+    assert len(items) == 6 and items[0]["messages"][0]["content"] == items[0]["opening"]
+    assert get_custom_dataset(path="generate:desk:6:1", type="rl", split="test") != items
