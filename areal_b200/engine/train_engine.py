@@ -363,6 +363,21 @@ class B200TrainEngine(TrainEngine):
                 # the ranks whose expert parameters differ from this rank's: the expert-parallel group times the
                 # expert-tensor-parallel group
                 self.optimizer.partner_group = pctx.extras.get("emp_group", pctx.ep_group)
+            balanced = [l.mlp for l in getattr(self.model, "layers", []) if getattr(l.mlp, "load_acc", None) is not None]
+            if balanced:
+                # aux-loss-free balancing: one bias update per optimizer step, from the token counts of every rank
+                # that holds the layer (data / sequence / tensor parallel peers routed other tokens)
+                groups = []
+                if self.mesh is not None:
+                    if self.mesh.shard_size > 1:
+                        groups.append(self.mesh.shard_group)
+                    if pctx.tp_size > 1:
+                        groups.append(pctx.tp_group)
+                elif dist.is_initialized() and self.world_size > 1:
+                    groups.append(self._dp_group)
+                for m in balanced:
+                    m.defer_bias_update = True
+                self.optimizer.pre_step_hooks.append(lambda: [m.update_expert_bias(groups) for m in balanced])
             if pctx is not None and pctx.pp_size > 1:
                 self.optimizer.norm_groups.append(pctx.pp_group)
                 if self.optimizer.partner is not None:

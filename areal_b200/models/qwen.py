@@ -212,6 +212,14 @@ class MoEMLP(nn.Module):
             self.register_buffer("expert_bias", torch.zeros(E, dtype=torch.float32, device=device))
         else:
             self.expert_bias = None
+        # tokens routed to every expert since the last bias update. A stand-alone module updates the bias after
+        # every training forward; a train engine sets `defer_bias_update` and updates once per optimizer step from
+        # the counts of ALL ranks that hold this layer (`update_expert_bias`), so the replicas' biases stay equal
+        if cfg.moe_load_balance_coeff > 0:
+            self.register_buffer("load_acc", torch.zeros(E, dtype=torch.float32, device=device), persistent=False)
+        else:
+            self.load_acc = None
+        self.defer_bias_update = False
         # shared expert: a dense SwiGLU MLP applied to every token, scaled by sigmoid(x . w_gate); replicated
         # over the expert-parallel group (every rank applies it to its own tokens)
         Is = cfg.shared_expert_intermediate_size
@@ -274,12 +282,27 @@ class MoEMLP(nn.Module):
         if cfg.norm_topk_prob:
             w = w / (w.sum(-1, keepdim=True) + 1e-20)
         w = w * cfg.moe_route_scale
-        if (self.expert_bias is not None and cfg.moe_load_balance_coeff > 0 and self.training
-                and torch.is_grad_enabled()):
+        if self.load_acc is not None and self.training and torch.is_grad_enabled():
             with torch.no_grad():
-                load = torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).float()
-                self.expert_bias.add_(cfg.moe_load_balance_coeff * torch.sign(load.mean() - load))
+                self.load_acc.add_(torch.bincount(idx.reshape(-1), minlength=cfg.num_experts).float())
+            if not self.defer_bias_update:
+                self.update_expert_bias()
         return idx.to(torch.int32), w
+
+    @torch.no_grad()
+    def update_expert_bias(self, groups=()):
+        """``bias += coeff * sign(mean load - load)`` from the tokens counted since the last call, summed over
+        ``groups`` (the process groups whose ranks hold replicas of this layer and routed other tokens)."""
+        if self.load_acc is None:
+            return
+        import torch.distributed as dist
+
+        load = self.load_acc
+        for g in groups:
+            dist.all_reduce(load, group=g)
+        if float(load.sum()) > 0:
+            self.expert_bias.add_(self.cfg.moe_load_balance_coeff * torch.sign(load.mean() - load))
+        load.zero_()
 
     def forward(self, x):
         from ..ops.moe import moe_experts_forward
@@ -718,10 +741,11 @@ class QwenModel(nn.Module):
         for name, t in self._selection_biases():
             yield self.checkpoint_name(name), t
 
-    def _selection_biases(self):
+    def _selection_biases(self, always: bool = False):
         """The routers' selection biases of a family whose checkpoints carry them: buffers, not parameters (no
-        gradient, not in the flat weight buffer), so they travel beside ``to_hf_local``'s tensors."""
-        if not self.cfg.moe_expert_bias:
+        gradient, not in the flat weight buffer), so they travel beside ``to_hf_local``'s tensors. ``always``: also
+        those of a model that only balances with them during training (recover checkpoints keep them)."""
+        if not (self.cfg.moe_expert_bias or always):
             return
         for i, layer in zip(self.layer_ids, self.layers):
             if getattr(layer.mlp, "expert_bias", None) is not None:

@@ -241,6 +241,11 @@ class EngineDCPState(Stateful):
                         st[key] = self._handle(f, off, shape, tp_dim, buf, so, write)
                 optim_state[name] = st
         sd: dict[str, Any] = {"model": model_sd} if self.with_model else {}
+        if self.with_model and hasattr(e.model, "_selection_biases"):
+            # routers' selection biases: replicated buffers outside the flat buffers, named by global layer
+            biases = dict(e.model._selection_biases(always=True))
+            if biases:
+                sd["buffers"] = biases
         if self.with_optim:
             sd["optim"] = {"state": optim_state, "meta": self._optim_meta()}
         rank = dist.get_rank() if dist.is_initialized() else 0

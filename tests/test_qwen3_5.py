@@ -402,3 +402,74 @@ def test_router_variants_sigmoid_scale_and_bias_balancing():
         mlp(x.detach())
     assert torch.equal(mlp.expert_bias, frozen)
     assert "expert_bias" in mlp.state_dict() and "expert_bias" not in dict(mlp.named_parameters())
+
+
+def test_balancing_bias_update_can_be_deferred_to_the_optimizer_step():
+    """Under a train engine the bias moves once per optimizer step, from the accumulated token counts (summed over
+    the ranks that hold the layer), not after every forward."""
+    from areal_b200.models.qwen import MoEMLP
+
+    cfg = dataclasses.replace(PRESETS["tiny-qwen3-moe"], moe_score_func="sigmoid", moe_load_balance_coeff=0.01)
+    torch.manual_seed(0)
+    mlp = MoEMLP(cfg, torch.float32, "cpu")
+    for p in mlp.parameters():
+        torch.nn.init.normal_(p, std=0.05)
+    mlp.train()
+    mlp.defer_bias_update = True
+    x = torch.randn(32, cfg.hidden_size)
+    mlp(x).sum().backward()
+    mlp(x).sum().backward()
+    assert torch.equal(mlp.expert_bias, torch.zeros(cfg.num_experts))
+    assert float(mlp.load_acc.sum()) == 2 * 32 * cfg.num_experts_per_tok
+    load = mlp.load_acc.clone()
+    mlp.update_expert_bias()
+    assert torch.equal(mlp.expert_bias, 0.01 * torch.sign(load.mean() - load)) and float(mlp.load_acc.sum()) == 0
+    mlp.update_expert_bias()                                   # nothing counted: nothing moves
+    assert torch.equal(mlp.expert_bias, 0.01 * torch.sign(load.mean() - load))
+
+
+def test_engine_updates_the_balancing_bias_per_step_and_checkpoints_it(tmp_path):
+    from areal_b200.api.cli_args import OptimizerConfig, TrainEngineConfig
+    from areal_b200.api.io_struct import SaveLoadMeta
+    from areal_b200.engine.train_engine import B200TrainEngine
+
+    def make(seed):
+        e = B200TrainEngine(TrainEngineConfig(experiment_name="t", trial_name="t", path="", init_from_scratch=True,
+                                              dtype="float32", model_preset="tiny-qwen3-moe",
+                                              model_overrides={"moe_load_balance_coeff": 0.02},
+                                              optimizer=OptimizerConfig(lr=1e-3, warmup_steps_proportion=0.0)))
+        e.create_process_group()
+        e.initialize(seed=seed)
+        return e
+
+    eng = make(1)
+    mlps = [l.mlp for l in eng.model.layers]
+    assert all(m.defer_bias_update and m.expert_bias is not None for m in mlps)
+    g = torch.Generator().manual_seed(0)
+    ids = torch.randint(0, 1024, (4, 40), generator=g)
+    batch = dict(input_ids=ids, attention_mask=torch.ones_like(ids), loss_mask=torch.ones_like(ids))
+    loss = lambda lp, ent, mb: -(lp * mb["loss_mask"].float()).sum() / mb["loss_mask"].sum()  # noqa: E731
+    eng.train_batch(batch, loss, lambda mb: float(mb["loss_mask"].sum()))
+    b1 = [m.expert_bias.clone() for m in mlps]
+    for b in b1:   # exactly one update: every entry is 0 or +-coeff
+        assert b.abs().sum() > 0 and torch.all((b.abs() < 1e-9) | ((b.abs() - 0.02).abs() < 1e-6)), b
+    assert all(float(m.load_acc.sum()) == 0 for m in mlps)
+    path = str(tmp_path / "ck")
+    eng.save(SaveLoadMeta(path=path, weight_format="dcp", with_optim=True))
+    other = make(2)
+    other.load(SaveLoadMeta(path=path, weight_format="dcp", with_optim=True))
+    assert all(torch.equal(l.mlp.expert_bias, b) for l, b in zip(other.model.layers, b1))
+
+
+def test_balancing_bias_is_the_same_on_all_data_parallel_ranks():
+    import os
+    import subprocess
+    import sys
+
+    from tests.conftest import free_port
+
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
+           "127.0.0.1", "--master-port", str(free_port()), os.path.join(root, "tests", "torchrun", "run_moe_bias.py")]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
+    assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
