@@ -357,7 +357,7 @@ class NativeRolloutEngine(InferenceEngine):
         self._rng = torch.Generator(device=self.device).manual_seed(ncfg.seed)
         self._graphs = None
         self.launches_per_decode = 0
-        if (self.device.type == "cuda" and ncfg.cuda_graph and not mc.is_hybrid and not mc.is_vl
+        if (self.device.type == "cuda" and ncfg.cuda_graph and not mc.is_hybrid and not mc.is_vl and not mc.is_mla
                 and _lib.use_cuda_kernels(next(self.model.parameters()))):
             self._capture_graphs()
         self._thread = threading.Thread(target=self._loop, name="rollout-engine", daemon=True)
@@ -880,7 +880,7 @@ class NativeRolloutEngine(InferenceEngine):
             nblocks = self.sched.stats()["free_blocks"]
             self.kv_caches = self._alloc_kv(nblocks, dtype)
             if (self.device.type == "cuda" and self.ncfg.cuda_graph and not self.model_config.is_hybrid
-                    and not self.model_config.is_vl
+                    and not self.model_config.is_vl and not self.model_config.is_mla
                     and _lib.use_cuda_kernels(next(self.model.parameters()))):
                 self._capture_graphs()
         self.continue_generation()

@@ -13,8 +13,10 @@ The attention itself is the packed causal attention op with ``v`` zero-padded to
 head width; the padded columns of the output are dropped), so every attention variant that plugs into a block
 (Ulysses exchange, tree attention) also takes this layer. Head widths other than 128 take the op's general path.
 Runs under data, sequence (Ulysses), pipeline and expert parallelism; not under tensor parallelism (its
-projections would have to be split by head behind the replicated bottlenecks), and the rollout engine does not
-serve it (no latent KV cache): such models are served by an external server.
+projections would have to be split by head behind the replicated bottlenecks). The rollout engine serves it with
+the EXPANDED keys and values in its paged cache (per head: the full-width key, the value padded to that width),
+not with the compressed latent: simple and exact, at ``heads * 2 * (nope + rope)`` cache elements per token
+instead of ``kv_lora_rank + rope``; decode steps run eagerly on the paged-attention op's general path.
 
 Checkpoint names follow Hugging Face's DeepseekV3 (``self_attn.{q_a_proj,q_a_layernorm,q_b_proj,
 kv_a_proj_with_mqa,kv_a_layernorm,kv_b_proj,o_proj}``).
@@ -74,6 +76,7 @@ class MLAttention(nn.Module):
         self.kv_a_norm = ones(cfg.kv_lora_rank)
         self.kv_b = mk(nh * (self.dn + self.dv), cfg.kv_lora_rank)
         self.o = mk(h, nh * self.dv)
+        self.lora_o = None  # (the decode loop asks)
         # softmax scale relative to the attention op's default 1/sqrt(width): the YaRN magnitude correction
         self.q_scale = 1.0
         sc = cfg.rope_scaling or {}
@@ -104,14 +107,29 @@ class MLAttention(nn.Module):
         k = torch.cat((kv[..., :self.dn], k_rot.expand(T, self.nh, self.dr)), dim=-1)
         return q, k, kv[..., self.dn:]
 
-    def forward(self, x, cos, sin, pos, meta: VarlenMeta, attn_fn=None):
+    def project_qkv(self, x, cos, sin, pos):
+        """``q, k, v`` of one width (``v`` zero-padded): what the attention ops and the paged cache take."""
         q, k, v = self.project(x, cos, sin, pos)
         pad = q.shape[-1] - self.dv
         if pad:
             v = F.pad(v, (0, pad))
-        a = (attn_fn or varlen_attention)(q.contiguous(), k.contiguous(), v.contiguous(), meta)
-        a = a[..., :self.dv].reshape(a.shape[0], self.nh * self.dv)
-        return linear(a, self.o)
+        return q.contiguous(), k.contiguous(), v.contiguous()
+
+    def project_q_write_kv(self, x, cos, sin, pos, slot_mapping, k_cache, v_cache):
+        """Decode step: returns ``q``; the new tokens' keys and (padded) values go into the paged caches."""
+        from ..ops.rollout_ops import kv_cache_write
+
+        q, k, v = self.project_qkv(x, cos, sin, pos)
+        kv_cache_write(k, v, slot_mapping, k_cache, v_cache)
+        return q
+
+    def out_proj(self, a):
+        """Output projection of an attention result ``[T, heads, nope + rope]``: the padding columns are dropped."""
+        return linear(a[..., :self.dv].reshape(a.shape[0], self.nh * self.dv), self.o)
+
+    def forward(self, x, cos, sin, pos, meta: VarlenMeta, attn_fn=None):
+        q, k, v = self.project_qkv(x, cos, sin, pos)
+        return self.out_proj((attn_fn or varlen_attention)(q, k, v, meta))
 
     def hf_tensors(self, p: str):
         """``(checkpoint name, tensor)`` of this layer, ``p`` = ``model.layers.<i>.``. Bailing checkpoints call the

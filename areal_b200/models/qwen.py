@@ -617,9 +617,9 @@ class QwenModel(nn.Module):
         paged caches; returns hidden states of all tokens. Hybrid models also take the per-sequence
         state of their linear-attention layers and the slot of every sequence in it. ``embeds`` /
         ``rope`` as in :meth:`forward` (image features merged into the embeddings, one rotary row per token)."""
-        if self.cfg.is_mla:
-            raise NotImplementedError("the rollout engine has no latent KV cache: serve latent-attention models "
-                                      "(DeepSeek-V3) with an external server (`vllm:` rollout backend)")
+        if self.cfg.lightning_group_size > 1:
+            raise NotImplementedError("the rollout engine keeps no lightning-attention state: serve the Bailing "
+                                      "hybrid with an external server (`vllm:` rollout backend)")
         if self.cfg.is_hybrid:
             from .qwen3_5 import hybrid_prefill
 
@@ -636,7 +636,8 @@ class QwenModel(nn.Module):
             q, k, v = layer.attn.project_qkv(y, cos, sin, pos)
             kv_cache_write(k, v, slot_mapping, kv_caches[i][0], kv_caches[i][1])
             a = varlen_attention(q, k, v, meta)
-            a = linear(a.reshape(a.shape[0], -1), layer.attn.o)
+            a = layer.attn.out_proj(a) if hasattr(layer.attn, "out_proj") else \
+                linear(a.reshape(a.shape[0], -1), layer.attn.o)
             y, res = fused.rmsnorm(a, layer.post_norm, layer.eps, residual=res)
             x = layer.mlp(y)
             if layer_adds is not None and i < len(layer_adds[1]):
@@ -663,7 +664,7 @@ class QwenModel(nn.Module):
         # q/k-norm + RoPE kernel, and each residual add + RMSNorm runs inside the split-K reduction of the
         # projection in front of it (o-proj → post-norm, down-proj → the next block's input norm).
         tp1 = self.pctx is None or self.pctx.tp_size == 1
-        plain = tp1 and not self.cfg.fp8 and not self.cfg.is_hybrid
+        plain = tp1 and not self.cfg.fp8 and not self.cfg.is_hybrid and not self.cfg.is_mla
         n_layers = len(self.layers)
         for i, layer in enumerate(self.layers):
             if y is None:
@@ -674,11 +675,13 @@ class QwenModel(nn.Module):
             q = layer.attn.project_q_write_kv(y, cos, sin, pos, slot_mapping, kv_caches[i][0], kv_caches[i][1])
             a = paged_decode(q, kv_caches[i][0], kv_caches[i][1], block_table, seq_lens,
                              max_seq_len=max_seq_len)
-            a = a.reshape(a.shape[0], -1)
-            if plain and layer.attn.lora_o is None:
-                y, res = linear_rmsnorm(a, layer.attn.o, layer.post_norm, layer.eps, res)
+            if hasattr(layer.attn, "out_proj"):  # latent attention: drops the value padding itself
+                y, res = fused.rmsnorm(layer.attn.out_proj(a), layer.post_norm, layer.eps, residual=res)
+            elif plain and layer.attn.lora_o is None:
+                y, res = linear_rmsnorm(a.reshape(a.shape[0], -1), layer.attn.o, layer.post_norm, layer.eps, res)
             else:
-                y, res = fused.rmsnorm(linear(a, layer.attn.o), layer.post_norm, layer.eps, residual=res)
+                y, res = fused.rmsnorm(linear(a.reshape(a.shape[0], -1), layer.attn.o), layer.post_norm, layer.eps,
+                                       residual=res)
             m = layer.mlp
             if plain and isinstance(m, DenseMLP) and m.lora_gate_up is None and m.lora_down is None:
                 nxt_w, nxt_eps = ((self.layers[i + 1].input_norm, self.layers[i + 1].eps) if i + 1 < n_layers

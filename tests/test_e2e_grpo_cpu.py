@@ -12,9 +12,10 @@ from tests.conftest import free_port
 ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 
 
-def _run(tmp_path, mode, nproc, port):
+def _run(tmp_path, mode, nproc, port, preset="tiny-qwen2"):
     out = str(tmp_path / f"res_{mode}")
-    env = dict(os.environ, AREAL_B200_FILEROOT=str(tmp_path), OMP_NUM_THREADS="2", AREAL_LOG_LEVEL="WARNING")
+    env = dict(os.environ, AREAL_B200_FILEROOT=str(tmp_path), OMP_NUM_THREADS="2", AREAL_LOG_LEVEL="WARNING",
+               AREAL_B200_TEST_PRESET=preset)
     env.pop("CUDA_VISIBLE_DEVICES", None)
     env["CUDA_VISIBLE_DEVICES"] = ""
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={nproc}",
@@ -40,6 +41,21 @@ def test_colocated_two_ranks(tmp_path):
     assert a["rollout_version"] == b["rollout_version"] == 2
     assert sum(a["tokens"]) > 0
     assert all(r is not None and 0.0 <= r <= 1.0 for r in a["eval_reward"])
+
+
+@pytest.mark.slow
+@pytest.mark.parametrize("mode", ["colocated", "disagg"])
+def test_deepseek_v3_family_trains_and_generates_in_one_job(tmp_path, mode):
+    """Latent attention + grouped sigmoid routing through the whole loop: the rollout engine generates, the trainer
+    steps, the new weights reach the engine (a flat copy when colocated, pushed to the rollout rank otherwise)."""
+    res = _run(tmp_path, mode, 2, 0, preset="tiny-deepseek-v3")
+    trainers = [r for r in res if r["is_trainer"]]
+    assert all(r["steps"] == 2 and r["version"] == 2 and all(g > 0 for g in r["grad_norm"]) for r in trainers)
+    assert all(r["rollout_version"] == 2 for r in res if "rollout_version" in r)
+    if mode == "colocated":
+        assert all(r["rollout_matches"] for r in trainers)
+        assert trainers[0]["checksum"] == pytest.approx(trainers[1]["checksum"], rel=1e-9, abs=1e-9)
+    assert sum(trainers[0]["tokens"]) > 0
 
 
 @pytest.mark.slow

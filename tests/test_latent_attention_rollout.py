@@ -1,0 +1,67 @@
+"""The rollout engine serves latent-attention (DeepSeek-V3 family) models: expanded keys and padded values in the
+paged cache, grouped sigmoid routing in its MoE layers. Greedy continuations must be the ones a full forward of the
+same model picks token by token."""
+import asyncio
+
+import pytest
+import torch
+
+from areal_b200.ops.attention import VarlenMeta
+
+
+def test_rollout_engine_serves_the_deepseek_v3_family_on_cpu():
+    from areal_b200.api.cli_args import GenerationHyperparameters, InferenceEngineConfig, NativeRolloutConfig
+    from areal_b200.api.io_struct import ModelRequest
+    from areal_b200.engine.rollout_engine import NativeRolloutEngine
+
+    cfg = InferenceEngineConfig(experiment_name="e", trial_name="t", backend="native:d1", max_concurrent_rollouts=16,
+                                consumer_batch_size=4,
+                                native=NativeRolloutConfig(model_preset="tiny-deepseek-v3", context_length=128,
+                                                           max_num_seqs=8, max_num_batched_tokens=512,
+                                                           num_kv_blocks=64, seed=3, cuda_graph=False))
+    eng = NativeRolloutEngine(cfg).initialize(device="cpu")
+    try:
+        mc = eng.model_config
+        # the cache holds full-width keys / padded values of every head
+        assert tuple(eng.kv_caches[0][0].shape[1::2]) == (mc.num_attention_heads, mc.qk_nope_head_dim + mc.qk_rope_head_dim)
+        with torch.no_grad():   # a selection bias that changes which experts win
+            for layer in eng.model.layers:
+                if getattr(layer.mlp, "expert_bias", None) is not None:
+                    layer.mlp.expert_bias.copy_(torch.randn(mc.num_experts, generator=torch.Generator().manual_seed(1)) * 0.2)
+        g = torch.Generator().manual_seed(7)
+        prompts = [torch.randint(0, 1000, (n,), generator=g).tolist() for n in (5, 19, 2, 33)]
+        gc = GenerationHyperparameters(max_new_tokens=9, greedy=True, ignore_eos=True)
+
+        async def go():
+            return await asyncio.gather(*[eng.agenerate(ModelRequest(rid=str(i), input_ids=p, gconfig=gc))
+                                          for i, p in enumerate(prompts)])
+
+        outs = asyncio.run(go())
+        model = eng.model
+        for p, r in zip(prompts, outs):
+            seq = list(p)
+            for _ in range(9):
+                ids = torch.tensor(seq)
+                meta = VarlenMeta(torch.tensor([0, len(seq)], dtype=torch.int32), "cpu")
+                with torch.no_grad():
+                    h = model(ids, torch.arange(len(seq)), meta)
+                    seq.append(int(model.logits(h[-1:]).argmax(-1)))
+            assert r.output_tokens == seq[len(p):], (r.output_tokens, seq[len(p):])
+            # and the reported log-probabilities are those of the full forward
+            ids = torch.tensor(seq)
+            with torch.no_grad():
+                h = model(ids, torch.arange(len(seq)), VarlenMeta(torch.tensor([0, len(seq)], dtype=torch.int32), "cpu"))
+                lp = torch.log_softmax(model.logits(h).float(), -1)
+            want = lp[len(p) - 1:-1].gather(1, ids[len(p):, None]).squeeze(1)
+            assert float((torch.tensor(r.output_logprobs) - want).abs().max()) < 1e-3
+    finally:
+        eng.destroy()
+
+
+def test_the_bailing_hybrid_is_not_served_by_the_rollout_engine():
+    from areal_b200.models.config import PRESETS
+    from areal_b200.models.qwen import build_model
+
+    m = build_model(PRESETS["tiny-bailing-hybrid"], dtype=torch.float32, seed=0)
+    with pytest.raises(NotImplementedError, match="external server"):
+        m.prefill(torch.zeros(4, dtype=torch.long), torch.arange(4), None, None, None)

@@ -25,6 +25,7 @@ def reward_fn(prompt, completion, prompt_ids, completion_ids, **kw):
 def main(out_path: str, mode: str):
     torch.set_num_threads(2)
     world = int(os.environ["WORLD_SIZE"])
+    preset = os.environ.get("AREAL_B200_TEST_PRESET", "tiny-qwen2")
     cfg = GRPOConfig(experiment_name="cfg1", trial_name=mode)
     cfg.seed = 0
     cfg.cluster.fileroot = os.environ.get("AREAL_B200_FILEROOT", "/tmp/areal_b200_test")
@@ -32,14 +33,14 @@ def main(out_path: str, mode: str):
     cfg.train_dataset.shuffle = False
     cfg.gconfig = GenerationHyperparameters(n_samples=4, max_new_tokens=32, temperature=1.0, ignore_eos=True)
     n_gen, n_train = (world, world) if mode == "colocated" else (world // 2, world // 2)
-    cfg.actor = PPOActorConfig(backend=f"fsdp:d{n_train}", model_preset="tiny-qwen2", init_from_scratch=True,
+    cfg.actor = PPOActorConfig(backend=f"fsdp:d{n_train}", model_preset=preset, init_from_scratch=True,
                                optimizer=OptimizerConfig(lr=1e-3, warmup_steps_proportion=0.0),
                                mb_spec=MicroBatchSpec(max_tokens_per_mb=1024), ppo_n_minibatches=1,
                                reward_norm=NormConfig(mean_level="group", std_level="group", group_size=4),
                                kl_ctl=0.0, use_decoupled_loss=True, recompute_logprob=True)
     cfg.rollout = InferenceEngineConfig(backend=f"native:d{n_gen}", max_head_offpolicyness=0,
                                         max_concurrent_rollouts=64,
-                                        native=NativeRolloutConfig(model_preset="tiny-qwen2", context_length=128,
+                                        native=NativeRolloutConfig(model_preset=preset, context_length=128,
                                                                    max_num_seqs=32, max_num_batched_tokens=2048,
                                                                    num_kv_blocks=256, seed=0))
     _propagate_names(cfg)
@@ -67,8 +68,10 @@ def main(out_path: str, mode: str):
                                     for s in seen])
             if tr.colocated:
                 rflat = tr.rollout.flat.flat
-                res.update(rollout_version=tr.rollout.get_version(),
-                           rollout_matches=bool(torch.equal(rflat[: flat.numel()], flat)))
+                differing = [n for n, p_, o, k in tr.actor_engine.flat.entries
+                             if not torch.equal(rflat[o:o + k], flat[o:o + k])]
+                res.update(rollout_version=tr.rollout.get_version(), differing=differing[:8],
+                           rollout_matches=bool(not differing and len(tr.actor_engine.flat.entries) > 0))
         else:
             res.update(rollout_version=tr.rollout.get_version())
         with open(f"{out_path}.{tr.rank}", "w") as f:
