@@ -338,13 +338,16 @@ class NativeRolloutEngine(InferenceEngine):
         self.hybrid_state = None
         self._state_slot: dict[int, int] = {}
         self._free_state_slots: list[int] = []
-        if mc.is_hybrid:
-            from ..models.qwen3_5 import HybridState
+        if mc.has_recurrent_state:
+            if mc.is_hybrid:
+                from ..models.qwen3_5 import HybridState as State
+            else:
+                from ..models.lightning import LightningState as State
 
-            self.hybrid_state = HybridState(mc, ncfg.max_num_seqs, dtype, self.device)
+            self.hybrid_state = State(mc, ncfg.max_num_seqs, dtype, self.device)
             self._free_state_slots = list(range(ncfg.max_num_seqs - 1, -1, -1))
         # prompts are shared by token ids: two prompts with equal ids but different images must not share pages
-        self.sched.set_prompt_sharing(bool(getattr(ncfg, "prompt_sharing", True)) and not mc.is_hybrid
+        self.sched.set_prompt_sharing(bool(getattr(ncfg, "prompt_sharing", True)) and not mc.has_recurrent_state
                                       and not mc.is_vl)
         # The engine thread shares the interpreter with trainer / workflow threads; CPython hands the GIL over
         # every 5 ms by default, which is half a decode step. A shorter interval keeps the step loop's short
@@ -357,7 +360,8 @@ class NativeRolloutEngine(InferenceEngine):
         self._rng = torch.Generator(device=self.device).manual_seed(ncfg.seed)
         self._graphs = None
         self.launches_per_decode = 0
-        if (self.device.type == "cuda" and ncfg.cuda_graph and not mc.is_hybrid and not mc.is_vl and not mc.is_mla
+        if (self.device.type == "cuda" and ncfg.cuda_graph and not mc.has_recurrent_state and not mc.is_vl
+                and not mc.is_mla
                 and _lib.use_cuda_kernels(next(self.model.parameters()))):
             self._capture_graphs()
         self._thread = threading.Thread(target=self._loop, name="rollout-engine", daemon=True)
@@ -879,7 +883,7 @@ class NativeRolloutEngine(InferenceEngine):
             dtype = next(self.model.parameters()).dtype
             nblocks = self.sched.stats()["free_blocks"]
             self.kv_caches = self._alloc_kv(nblocks, dtype)
-            if (self.device.type == "cuda" and self.ncfg.cuda_graph and not self.model_config.is_hybrid
+            if (self.device.type == "cuda" and self.ncfg.cuda_graph and not self.model_config.has_recurrent_state
                     and not self.model_config.is_vl and not self.model_config.is_mla
                     and _lib.use_cuda_kernels(next(self.model.parameters()))):
                 self._capture_graphs()

@@ -115,7 +115,14 @@ class ModelConfig:
         g = self.lightning_group_size
         return g > 1 and (i + 1) % g != 0
 
+    @property
+    def has_recurrent_state(self) -> bool:
+        """Some layers carry a per-sequence recurrent state through generation (linear-attention layers)."""
+        return self.is_hybrid or self.lightning_group_size > 1
+
     def layer_type(self, i: int) -> str:
+        if self.layer_is_lightning(i):
+            return "lightning_attention"
         return self.layer_types[i] if self.layer_types else "full_attention"
 
     @property

@@ -16,6 +16,10 @@ Sequence parallelism (Ulysses): the recurrence needs every token of a sequence, 
 q / k / v are rotated on the rank that holds the tokens, exchanged tokens → heads (each rank then runs ``heads /
 sp`` heads over the whole packed stream with their slice of the decays), and the outputs are exchanged back.
 
+Generation: the rollout engine keeps the state ``S [heads, head_dim, head_dim]`` (fp32) of every running sequence
+per lightning layer (:class:`LightningState`); a prefill leaves the state after the prompt's last token there, a decode
+step reads, advances and writes it back.
+
 Checkpoint names: ``attention.{query_key_value,query_layernorm,key_layernorm,g_proj,g_norm,dense}``.
 Reference: areal/models/mcore/lightning_attention.py:100-125 (slopes), :241-342 (core, decay per layer),
 :345-385 (group norm), :387-672 (layer, head <-> sequence exchange under context parallelism).
@@ -71,6 +75,15 @@ def _rope_partial(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, rot: in
     return torch.cat((out, x[..., rot:]), dim=-1) if rot < x.shape[-1] else out
 
 
+class LightningState:
+    """``rec[i] [slots, heads, head_dim, head_dim]`` fp32 for lightning layer ``i``, ``None`` for the others."""
+
+    def __init__(self, cfg: ModelConfig, max_slots: int, dtype, device):
+        D = cfg.lightning_head_dim
+        self.rec = [torch.zeros(max_slots, cfg.num_attention_heads, D, D, dtype=torch.float32, device=device)
+                    if cfg.layer_is_lightning(i) else None for i in range(cfg.num_hidden_layers)]
+
+
 class LightningAttention(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype, device, pctx=None, layer_idx: int = 0):
         super().__init__()
@@ -104,7 +117,7 @@ class LightningAttention(nn.Module):
                                              device)
         return self._tables
 
-    def forward(self, x, cos, sin, pos, meta: VarlenMeta, attn_fn=None):
+    def _qkv(self, x, pos):
         cfg, T, nh, D = self.cfg, x.shape[0], self.nh, self.D
         qkv = linear(x, self.qkv).view(T, 3, nh, D)
         q = fused.rmsnorm(qkv[:, 0].contiguous(), self.q_norm, cfg.rms_norm_eps)
@@ -114,6 +127,40 @@ class LightningAttention(nn.Module):
             p = pos.long()
             c, s = self._rope_tables(x.device, int(p.max()) + 1 if p.numel() else 1)
             q, k = _rope_partial(q, c[p], s[p], self.rot), _rope_partial(k, c[p], s[p], self.rot)
+        return q, k, v
+
+    def _gate_out(self, o, x):
+        T, nh, D = x.shape[0], self.nh, self.D
+        o = group_rmsnorm(o, self.g_norm, self.n_groups, self.cfg.rms_norm_eps)
+        o = o * torch.sigmoid(linear(x, self.gate).view(T, nh, D).float()).to(o.dtype)
+        return linear(o.reshape(T, nh * D), self.o)
+
+    @torch.no_grad()
+    def prefill(self, x, pos, meta: VarlenMeta, rec: torch.Tensor, slots: torch.Tensor):
+        """Prompt forward of a rollout engine: also leaves every sequence's final state in ``rec[slots]``."""
+        from ..ops.linear_attn import linear_attn_prefill
+
+        q, k, v = self._qkv(x, pos)
+        a = self.log_decay.exp()[None, :].expand(q.shape[0], -1)
+        o, final = linear_attn_prefill(q.contiguous(), k.contiguous(), v.contiguous(), a, None, meta.cu_seqlens,
+                                       self.D ** -0.5, mode="simple_gla")
+        rec[slots] = final
+        return self._gate_out(o, x)
+
+    @torch.no_grad()
+    def step(self, x, pos, rec: torch.Tensor, slots: torch.Tensor):
+        """One new token per sequence: advances ``rec[slots]``."""
+        from ..ops.linear_attn import linear_attn_step
+
+        q, k, v = self._qkv(x, pos)
+        a = self.log_decay.exp()[None, :].expand(q.shape[0], -1)
+        o, new = linear_attn_step(q, k, v, a, None, rec[slots], self.D ** -0.5, mode="simple_gla")
+        rec[slots] = new
+        return self._gate_out(o, x)
+
+    def forward(self, x, cos, sin, pos, meta: VarlenMeta, attn_fn=None):
+        T, nh, D = x.shape[0], self.nh, self.D
+        q, k, v = self._qkv(x, pos)
         g = self.log_decay
         pc = self.pctx
         sharded = pc is not None and pc.sp_size > 1
@@ -128,9 +175,7 @@ class LightningAttention(nn.Module):
                         mode="simple_gla")
         if sharded:
             o = head_to_seq(o.contiguous(), pc)
-        o = group_rmsnorm(o, self.g_norm, self.n_groups, cfg.rms_norm_eps)
-        o = o * torch.sigmoid(linear(x, self.gate).view(T, nh, D).float()).to(o.dtype)
-        return linear(o.reshape(T, nh * D), self.o)
+        return self._gate_out(o, x)
 
     def hf_tensors(self, p: str):
         yield p + "attention.query_key_value.weight", self.qkv

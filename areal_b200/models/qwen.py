@@ -617,9 +617,6 @@ class QwenModel(nn.Module):
         paged caches; returns hidden states of all tokens. Hybrid models also take the per-sequence
         state of their linear-attention layers and the slot of every sequence in it. ``embeds`` /
         ``rope`` as in :meth:`forward` (image features merged into the embeddings, one rotary row per token)."""
-        if self.cfg.lightning_group_size > 1:
-            raise NotImplementedError("the rollout engine keeps no lightning-attention state: serve the Bailing "
-                                      "hybrid with an external server (`vllm:` rollout backend)")
         if self.cfg.is_hybrid:
             from .qwen3_5 import hybrid_prefill
 
@@ -633,11 +630,14 @@ class QwenModel(nn.Module):
                 y, res = fused.rmsnorm(x, layer.input_norm, layer.eps), x
             else:
                 y, res = fused.rmsnorm(x, layer.input_norm, layer.eps, residual=res)
-            q, k, v = layer.attn.project_qkv(y, cos, sin, pos)
-            kv_cache_write(k, v, slot_mapping, kv_caches[i][0], kv_caches[i][1])
-            a = varlen_attention(q, k, v, meta)
-            a = layer.attn.out_proj(a) if hasattr(layer.attn, "out_proj") else \
-                linear(a.reshape(a.shape[0], -1), layer.attn.o)
+            if hasattr(layer.attn, "prefill"):  # a layer with recurrent state (lightning attention)
+                a = layer.attn.prefill(y, pos, meta, hybrid_state.rec[i], state_slots)
+            else:
+                q, k, v = layer.attn.project_qkv(y, cos, sin, pos)
+                kv_cache_write(k, v, slot_mapping, kv_caches[i][0], kv_caches[i][1])
+                a = varlen_attention(q, k, v, meta)
+                a = layer.attn.out_proj(a) if hasattr(layer.attn, "out_proj") else \
+                    linear(a.reshape(a.shape[0], -1), layer.attn.o)
             y, res = fused.rmsnorm(a, layer.post_norm, layer.eps, residual=res)
             x = layer.mlp(y)
             if layer_adds is not None and i < len(layer_adds[1]):
@@ -672,6 +672,12 @@ class QwenModel(nn.Module):
                     y, res = fused.rmsnorm(x, layer.input_norm, layer.eps), x
                 else:
                     y, res = fused.rmsnorm(x, layer.input_norm, layer.eps, residual=res)
+            if hasattr(layer.attn, "step"):  # lightning attention: advances the sequence's recurrent state
+                a = layer.attn.step(y, pos, hybrid_state.rec[i], state_slots)
+                y, res = fused.rmsnorm(a, layer.post_norm, layer.eps, residual=res)
+                x = layer.mlp(y)
+                y = None
+                continue
             q = layer.attn.project_q_write_kv(y, cos, sin, pos, slot_mapping, kv_caches[i][0], kv_caches[i][1])
             a = paged_decode(q, kv_caches[i][0], kv_caches[i][1], block_table, seq_lens,
                              max_seq_len=max_seq_len)

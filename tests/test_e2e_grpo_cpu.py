@@ -44,11 +44,13 @@ def test_colocated_two_ranks(tmp_path):
 
 
 @pytest.mark.slow
-@pytest.mark.parametrize("mode", ["colocated", "disagg"])
-def test_deepseek_v3_family_trains_and_generates_in_one_job(tmp_path, mode):
-    """Latent attention + grouped sigmoid routing through the whole loop: the rollout engine generates, the trainer
-    steps, the new weights reach the engine (a flat copy when colocated, pushed to the rollout rank otherwise)."""
-    res = _run(tmp_path, mode, 2, 0, preset="tiny-deepseek-v3")
+@pytest.mark.parametrize("mode,preset", [("colocated", "tiny-deepseek-v3"), ("disagg", "tiny-deepseek-v3"),
+                                         ("colocated", "tiny-bailing-hybrid")])
+def test_latent_and_lightning_attention_families_train_and_generate_in_one_job(tmp_path, mode, preset):
+    """Latent attention + grouped sigmoid routing (and lightning layers with their per-sequence state) through the
+    whole loop: the rollout engine generates, the trainer steps, the new weights reach the engine (a flat copy when
+    colocated, pushed to the rollout rank otherwise)."""
+    res = _run(tmp_path, mode, 2, 0, preset=preset)
     trainers = [r for r in res if r["is_trainer"]]
     assert all(r["steps"] == 2 and r["version"] == 2 and all(g > 0 for g in r["grad_norm"]) for r in trainers)
     assert all(r["rollout_version"] == 2 for r in res if "rollout_version" in r)
