@@ -80,7 +80,7 @@ def param_segments(name: str, shape: tuple[int, ...], full_shape: tuple[int, ...
             return None
         return [(0, 0, 1, n, n, n)]
     cols = shape[-1] if len(shape) > 1 else 1
-    if name.endswith(("embed", "lm_head")):
+    if name.endswith(("embed", "lm_head", "attn.q_b", "attn.kv_b", "attn.q")):  # contiguous blocks of rows
         return [(0, tp_rank * n, 1, n, n, n)]
     if name.endswith(("attn.qkv", "attn.qkv_bias")):
         nq, nk = cfg.q_size // tp, cfg.kv_size // tp

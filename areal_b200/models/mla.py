@@ -12,8 +12,11 @@ part (``qk_rope_head_dim``; the key's rotary part is computed once and shared by
 The attention itself is the packed causal attention op with ``v`` zero-padded to the query width (the op wants one
 head width; the padded columns of the output are dropped), so every attention variant that plugs into a block
 (Ulysses exchange, tree attention) also takes this layer. Head widths other than 128 take the op's general path.
-Runs under data, sequence (Ulysses), pipeline and expert parallelism; not under tensor parallelism (its
-projections would have to be split by head behind the replicated bottlenecks). The rollout engine serves it with
+Runs under data, sequence (Ulysses), pipeline, expert and tensor parallelism. Under tensor parallelism
+(sequence-parallel activations: every rank holds a slice of the tokens between blocks) the projections INTO the
+bottlenecks and their norms are replicated and run on the rank's own tokens; the projections out of them are split
+by head and gather the tokens (column-parallel); the shared rotary key is gathered to all tokens with a backward
+that sums the ranks' partial gradients; the output projection is row-parallel. The rollout engine serves it with
 the EXPANDED keys and values in its paged cache (per head: the full-width key, the value padded to that width),
 not with the compressed latent: simple and exact, at ``heads * 2 * (nope + rope)`` cache elements per token
 instead of ``kv_lora_rank + rope``; decode steps run eagerly on the paged-attention op's general path.
@@ -54,13 +57,12 @@ def rope_rotate(x: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, interleav
 class MLAttention(nn.Module):
     def __init__(self, cfg: ModelConfig, dtype, device, pctx=None, layer_idx: int = 0):
         super().__init__()
-        if pctx is not None and pctx.tp_size > 1:
-            raise NotImplementedError("latent attention does not run under tensor parallelism: use data, sequence, "
-                                      "pipeline and expert parallelism for this family")
+        tp = pctx.tp_size if pctx is not None else 1
+        assert cfg.num_attention_heads % tp == 0, "tensor parallelism needs the head count to divide by its size"
         if cfg.lora_rank > 0 and any(t in ("q_proj", "k_proj", "v_proj", "o_proj") for t in (cfg.lora_targets or [])):
             raise NotImplementedError("latent attention takes no LoRA adapters: target the MLP projections")
         self.cfg, self.pctx = cfg, pctx
-        h, nh = cfg.hidden_size, cfg.num_attention_heads
+        h, nh = cfg.hidden_size, cfg.num_attention_heads // tp   # nh: this rank's heads
         self.nh, self.dn, self.dr, self.dv = nh, cfg.qk_nope_head_dim, cfg.qk_rope_head_dim, cfg.v_head_dim
         assert self.dr % 2 == 0 and self.dv <= self.dn + self.dr
         mk = lambda *shape: nn.Parameter(torch.empty(*shape, dtype=dtype, device=device))
@@ -85,18 +87,34 @@ class MLAttention(nn.Module):
             m = 1.0 if f <= 1 else 0.1 * float(sc["mscale_all_dim"]) * math.log(f) + 1.0
             self.q_scale = m * m
 
+    def _tp(self):
+        p = self.pctx
+        return p.tp_fused if (p is not None and p.tp_size > 1) else None
+
     def project(self, x, cos, sin, pos):
-        """``q, k [T, heads, nope + rope]`` and ``v [T, heads, v]`` of the tokens in ``x``."""
-        cfg, T = self.cfg, x.shape[0]
-        if self.q is None:
-            q = linear(fused.rmsnorm(linear(x, self.q_a), self.q_a_norm, cfg.rms_norm_eps), self.q_b)
+        """``q, k [T, heads, nope + rope]`` and ``v [T, heads, v]``: this rank's heads of ALL tokens of the
+        sequence-parallel shard (``x`` holds this rank's tokens only under tensor parallelism; ``pos`` always the
+        positions of all of them)."""
+        cfg = self.cfg
+        tp = self._tp()
+        if tp is not None:
+            from ..parallel.tensor_parallel import column_parallel_linear, gather_seq
+
+            up = lambda t, w: column_parallel_linear(t, w, tp)   # gathers the tokens, multiplies by this rank's rows
         else:
-            q = linear(x, self.q)
+            up = linear
+        if self.q is None:
+            q = up(fused.rmsnorm(linear(x, self.q_a), self.q_a_norm, cfg.rms_norm_eps), self.q_b)
+        else:
+            q = up(x, self.q)
+        T = q.shape[0]
         q = q.view(T, self.nh, self.dn + self.dr)
         ckv = linear(x, self.kv_a)
         c, k_rot = ckv[:, :cfg.kv_lora_rank], ckv[:, cfg.kv_lora_rank:]
-        kv = linear(fused.rmsnorm(c.contiguous(), self.kv_a_norm, cfg.rms_norm_eps), self.kv_b)
+        kv = up(fused.rmsnorm(c.contiguous(), self.kv_a_norm, cfg.rms_norm_eps), self.kv_b)
         kv = kv.view(T, self.nh, self.dn + self.dv)
+        if tp is not None:
+            k_rot = gather_seq(k_rot.contiguous(), tp)   # shared by every head on every rank: gradients are summed
         cs, sn = cos[pos.long()], sin[pos.long()]
         q_rot = rope_rotate(q[..., self.dn:], cs, sn, cfg.rope_interleave)
         k_rot = rope_rotate(k_rot[:, None, :], cs, sn, cfg.rope_interleave)
@@ -125,7 +143,13 @@ class MLAttention(nn.Module):
 
     def out_proj(self, a):
         """Output projection of an attention result ``[T, heads, nope + rope]``: the padding columns are dropped."""
-        return linear(a[..., :self.dv].reshape(a.shape[0], self.nh * self.dv), self.o)
+        a = a[..., :self.dv].reshape(a.shape[0], self.nh * self.dv)
+        tp = self._tp()
+        if tp is not None:
+            from ..parallel.tensor_parallel import row_parallel_linear
+
+            return row_parallel_linear(a, self.o, tp)
+        return linear(a, self.o)
 
     def forward(self, x, cos, sin, pos, meta: VarlenMeta, attn_fn=None):
         q, k, v = self.project_qkv(x, cos, sin, pos)

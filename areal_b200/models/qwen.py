@@ -704,13 +704,14 @@ class QwenModel(nn.Module):
 
     # ------------------------------------------------------ HF name mapping
     _TP_DIM0 = ("embed_tokens.weight", "lm_head.weight", "q_proj.weight", "k_proj.weight", "v_proj.weight",
-                "q_proj.bias", "k_proj.bias", "v_proj.bias", "gate_proj.weight", "up_proj.weight")
+                "q_proj.bias", "k_proj.bias", "v_proj.bias", "gate_proj.weight", "up_proj.weight",
+                "q_b_proj.weight", "kv_b_proj.weight")
     _TP_DIM1 = ("o_proj.weight", "down_proj.weight")
 
     def _tp_dim(self, hf_name: str) -> int | None:
         """Dimension along which an HF tensor is split over the tp group (None: replicated)."""
-        if self.pctx is None or self.pctx.tp_size == 1 or ".experts." in hf_name:
-            return None
+        if self.pctx is None or self.pctx.tp_size == 1 or ".experts." in hf_name or "shared_expert" in hf_name:
+            return None  # (experts are split by expert; a shared expert is replicated over the group)
         if hf_name.endswith(self._TP_DIM0):
             return 0
         if hf_name.endswith(self._TP_DIM1):

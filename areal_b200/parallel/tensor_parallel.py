@@ -199,13 +199,18 @@ def vocab_parallel_embedding(ids, embed_shard, fctx):
 # --------------------------------------------------------------------------- weight sharding
 
 
+# latent attention: the projections out of the bottlenecks (and a plain query projection) are split by head, i.e. by
+# contiguous blocks of rows; the projections into the bottlenecks and their norms are replicated
+_MLA_BY_HEAD = ("attn.q_b", "attn.kv_b", "attn.q")
+
+
 def tp_slice(name: str, full: torch.Tensor, cfg, rank: int, size: int) -> torch.Tensor:
     """The tp shard of a (fused) parameter of ``models.qwen``; ``name`` is the parameter's
     attribute path suffix (``embed``, ``attn.qkv``, ``attn.o``, ``mlp.gate_up``, ...)."""
     if size == 1:
         return full
     D = cfg.head_dim
-    if name.endswith(("embed", "lm_head")):
+    if name.endswith(("embed", "lm_head") + _MLA_BY_HEAD):
         n = full.shape[0] // size
         return full[rank * n:(rank + 1) * n]
     if name.endswith(("attn.qkv", "attn.qkv_bias")):
@@ -234,7 +239,7 @@ def tp_unslice(name: str, shards: list[torch.Tensor], cfg) -> torch.Tensor:
     if ".lora_" in name:
         d = lora_tp_dim(name)
         return shards[0] if d is None else torch.cat(shards, d)
-    if name.endswith(("embed", "lm_head")):
+    if name.endswith(("embed", "lm_head") + _MLA_BY_HEAD):
         return torch.cat(shards, 0)
     if name.endswith(("attn.qkv", "attn.qkv_bias")):
         nq, nk = cfg.q_size // size, cfg.kv_size // size
@@ -287,4 +292,5 @@ def lora_tp_dim(name: str) -> int | None:
 def is_tp_replicated(name: str) -> bool:
     if ".lora_" in name:
         return lora_tp_dim(name) is None
-    return not name.endswith(("embed", "lm_head", "attn.qkv", "attn.qkv_bias", "attn.o", "mlp.gate_up", "mlp.down"))
+    return not name.endswith(("embed", "lm_head", "attn.qkv", "attn.qkv_bias", "attn.o", "mlp.gate_up", "mlp.down")
+                             + _MLA_BY_HEAD)

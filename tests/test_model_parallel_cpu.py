@@ -75,13 +75,16 @@ def test_hybrid_tensor_and_expert_parallel_step_matches_single_process(tmp_path,
          _ref(tmp_path, preset="tiny-qwen3-moe", n_mbs=n_mbs))
 
 
-@pytest.mark.parametrize("n,pp,ep,tp,etp", [(2, 1, 2, 2, 1), (4, 2, 2, 2, 1), (4, 1, 4, 2, 1), (2, 1, 1, 2, 2),
-                                            (4, 1, 2, 2, 2)])
-def test_checkpoint_under_the_hybrid_layout(tmp_path, n, pp, ep, tp, etp):
+@pytest.mark.parametrize("n,pp,ep,tp,etp,preset", [(2, 1, 2, 2, 1, "tiny-qwen3-moe"), (4, 2, 2, 2, 1, "tiny-qwen3-moe"),
+                                                   (4, 1, 4, 2, 1, "tiny-qwen3-moe"), (2, 1, 1, 2, 2, "tiny-qwen3-moe"),
+                                                   (4, 1, 2, 2, 2, "tiny-qwen3-moe"),
+                                                   # latent attention split by head, a replicated shared expert
+                                                   (2, 1, 2, 2, 1, "tiny-deepseek-v3"), (4, 2, 2, 2, 1, "tiny-deepseek-v3")])
+def test_checkpoint_under_the_hybrid_layout(tmp_path, n, pp, ep, tp, etp, preset):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr",
            "127.0.0.1", "--master-port", str(free_port()),
            os.path.join(ROOT, "tests", "torchrun", "run_vl_tp_hf.py"),
-           "tiny-qwen3-moe", str(pp), str(tmp_path / "ckpt"), str(ep), str(tp), str(etp)]
+           preset, str(pp), str(tmp_path / "ckpt"), str(ep), str(tp), str(etp)]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=600)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
 
@@ -128,23 +131,26 @@ def test_vision_language_step_under_tensor_parallelism(tmp_path, n, preset, par)
     _run(n, 29690 + n, par + ["--preset", preset, "--images"], _ref(tmp_path, preset=preset, images=True))
 
 
-@pytest.mark.parametrize("n,args", [(2, ["--ep", "2"]), (2, ["--sp", "2"]), (2, ["--pp", "2", "--n-mbs", "2"])])
+@pytest.mark.parametrize("n,args", [(2, ["--ep", "2"]), (2, ["--sp", "2"]), (2, ["--pp", "2", "--n-mbs", "2"]),
+                                    (2, ["--tp", "2", "--ep", "2"]), (2, ["--tp", "2", "--etp", "2"]),
+                                    (4, ["--tp", "2", "--ep", "2", "--pp", "2", "--n-mbs", "2"])])
 def test_latent_attention_family_step_matches_single_process(tmp_path, n, args):
     """DeepSeek-V3 architecture (latent attention, grouped sigmoid routing, ungated shared expert, dense first
-    layer) under expert, Ulysses and pipeline parallelism."""
+    layer) under expert, Ulysses, pipeline and tensor parallelism (bottlenecks replicated, heads split, the shared
+    rotary key gathered; experts over the tensor-parallel ranks)."""
     _run(n, 0, args + ["--preset", "tiny-deepseek-v3"], _ref(tmp_path, preset="tiny-deepseek-v3", n_mbs=2))
 
 
-def test_latent_attention_refuses_tensor_parallelism():
+def test_lightning_attention_refuses_tensor_parallelism():
     import torch
 
     from areal_b200.models.config import PRESETS
     from areal_b200.models.qwen import build_model
     from areal_b200.parallel.context import ParallelContext
 
-    cfg = PRESETS["tiny-deepseek-v3"]
     with pytest.raises(NotImplementedError, match="tensor parallelism"):
-        build_model(cfg, dtype=torch.float32, seed=None, pctx=ParallelContext(tp_size=2, tp_rank=0))
+        build_model(PRESETS["tiny-bailing-hybrid"], dtype=torch.float32, seed=None,
+                    pctx=ParallelContext(tp_size=2, tp_rank=0, ep_size=2))
 
 
 @pytest.mark.parametrize("n,pp,preset,ep", [(2, 1, "tiny-qwen3-vl", 1), (4, 2, "tiny-qwen3-vl", 1),

@@ -21,7 +21,9 @@ WORKER = os.path.join(ROOT, "tests", "torchrun", "run_weight_plan.py")
                                      (2, ["--tp", "2", "--ep", "2", "--preset", "tiny-qwen3-moe"]),
                                      (4, ["--tp", "2", "--ep", "4", "--preset", "tiny-qwen3-moe"]),
                                      (2, ["--tp", "2", "--etp", "2", "--preset", "tiny-qwen3-moe"]),
-                                     (4, ["--tp", "2", "--ep", "2", "--etp", "2", "--preset", "tiny-qwen3-moe"])])
+                                     (4, ["--tp", "2", "--ep", "2", "--etp", "2", "--preset", "tiny-qwen3-moe"]),
+                                     (2, ["--tp", "2", "--ep", "2", "--preset", "tiny-deepseek-v3"]),
+                                     (2, ["--pp", "2", "--preset", "tiny-bailing-hybrid"])])
 def test_plan_rebuilds_the_full_model_exactly_once(n, flags):
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}",
            "--master-addr", "127.0.0.1", "--master-port", str(free_port()), WORKER] + flags
