@@ -23,8 +23,8 @@ The routes only use the engine client's public asynchronous interface (``pause_g
 ``app.state.engine_client`` like vLLM's own routes, so they can be mounted on any app that provides one
 (``attach_areal_routes``); the tests mount them on a stub.
 
-Reference: the vLLM server extension with the same route names in areal/engine/vllm_ext/ (SURVEY: "vLLM server
-ext").
+Reference: the vLLM server extension with the same route names, areal/engine/vllm_ext/areal_vllm_server.py and
+areal/engine/vllm_ext/vllm_worker_extension.py.
 """
 
 from __future__ import annotations
