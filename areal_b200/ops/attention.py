@@ -73,6 +73,31 @@ def attention_ref(q, k, v, cu_seqlens, scale=None):
     return out.to(q.dtype)
 
 
+def attention_sdpa(q, k, v, cu_seqlens, scale=None):
+    """Per-sequence ``scaled_dot_product_attention`` (PyTorch's fused kernels: no ``L x L`` score tensor): the
+    general path for head widths the tcgen05 kernels do not cover once sequences are too long for
+    :func:`attention_ref`'s fp32 scores. Differentiable; grouped-query heads are expanded by view."""
+    T, Hq, D = q.shape
+    Hkv = k.shape[1]
+    scale = scale if scale is not None else 1.0 / math.sqrt(D)
+    g = Hq // Hkv
+    outs = []
+    cu = [int(x) for x in cu_seqlens]
+    for s, e in zip(cu[:-1], cu[1:]):
+        if e == s:
+            continue
+        qs = q[s:e].transpose(0, 1).unsqueeze(0)                                   # [1, Hq, L, D]
+        ks = k[s:e].transpose(0, 1).repeat_interleave(g, dim=0).unsqueeze(0) if g > 1 else k[s:e].transpose(0, 1).unsqueeze(0)
+        vs = v[s:e].transpose(0, 1).repeat_interleave(g, dim=0).unsqueeze(0) if g > 1 else v[s:e].transpose(0, 1).unsqueeze(0)
+        o = torch.nn.functional.scaled_dot_product_attention(qs, ks, vs, is_causal=True, scale=scale)
+        outs.append(o.squeeze(0).transpose(0, 1))
+    return torch.cat(outs, 0) if outs else torch.zeros_like(q)
+
+
+# above this many bytes of fp32 scores for one sequence the general path switches to `attention_sdpa`
+_REF_SCORE_BYTES = 1 << 30
+
+
 def _fwd_cuda(q, k, v, meta: VarlenMeta, scale):
     T, Hq, D = q.shape
     Hkv = k.shape[1]
@@ -150,4 +175,8 @@ def varlen_attention(q, k, v, meta: VarlenMeta, scale: float | None = None):
         return _VarlenAttn.apply(q, k, v, meta, scale)
     if q.is_cuda:
         _lib.count_fallback(f"varlen_attention[D={D},{str(q.dtype).replace('torch.', '')}]")
+        cu = meta.cu_cpu
+        longest = max((int(b) - int(a) for a, b in zip(cu[:-1], cu[1:])), default=0)
+        if longest * longest * q.shape[1] * 4 > _REF_SCORE_BYTES:
+            return attention_sdpa(q, k, v, cu, scale)
     return attention_ref(q, k, v, meta.cu_cpu, scale)

@@ -527,3 +527,24 @@ def test_http_helper_passes_headers(monkeypatch):
     assert seen["headers"] == {"Authorization": "Bearer t"} and seen["json"] == {"a": 1}
     http.request_with_retry("GET", "http://x/y", max_retries=0)
     assert seen["headers"] is None
+
+
+def test_sdpa_general_attention_path_matches_the_reference():
+    """The path long sequences take when the head width has no tcgen05 kernel: same values and gradients as the
+    fp32 reference, with grouped-query heads and several packed sequences (one of them empty)."""
+    import torch
+
+    from areal_b200.ops.attention import attention_ref, attention_sdpa
+
+    g = torch.Generator().manual_seed(0)
+    cu = [0, 17, 17, 60, 64]
+    q = torch.randn(64, 6, 48, generator=g, requires_grad=True)
+    k = torch.randn(64, 2, 48, generator=g, requires_grad=True)
+    v = torch.randn(64, 2, 48, generator=g, requires_grad=True)
+    want = attention_ref(q, k, v, cu, 0.11)
+    got = attention_sdpa(q, k, v, cu, 0.11)
+    assert torch.allclose(got, want, atol=1e-5)
+    w = torch.randn(64, 6, 48, generator=g)
+    gw = torch.autograd.grad((want * w).sum(), (q, k, v))
+    gg = torch.autograd.grad((got * w).sum(), (q, k, v))
+    assert all(torch.allclose(a, b, atol=1e-5) for a, b in zip(gw, gg))
