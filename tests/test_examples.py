@@ -154,3 +154,19 @@ def test_search_agent_example_runs_end_to_end_on_cpu(tmp_path):
                                    "total_train_steps=2", "train_dataset.batch_size=4", "gconfig.max_new_tokens=8",
                                    "saver.freq_epochs=null", "evaluator.freq_epochs=null"])
     assert glob.glob(str(root / "logs" / "**" / "*.jsonl"), recursive=True)
+
+
+def test_service_desk_example_runs_end_to_end_on_cpu(tmp_path):
+    """The service-desk example through the OpenAI-protocol workflow with generated tasks and the scripted customer:
+    two asynchronous steps. (The tiny model's random text calls no tool; the refusal tasks, whose reference is to
+    change nothing, are the ones it can score on.)"""
+    import json
+
+    root = _run_example(os.path.join(ROOT, "examples", "service_desk", "service_desk_rl.py"), "gsm8k_grpo_cpu.yaml",
+                        tmp_path, ["train_dataset.path=generate:desk:16:0", "valid_dataset=null",
+                                   "total_train_steps=2", "train_dataset.batch_size=4", "gconfig.max_new_tokens=8",
+                                   "saver.freq_epochs=null", "evaluator.freq_epochs=null"])
+    logs = glob.glob(str(root / "logs" / "**" / "*.jsonl"), recursive=True)
+    assert logs
+    recs = [json.loads(l) for l in open(logs[0]) if l.strip()]
+    assert len(recs) >= 2
