@@ -302,13 +302,20 @@ class ModelConfig:
             out.head_dim = out.qk_nope_head_dim + out.qk_rope_head_dim
             out.partial_rotary_factor = float(cfg.get("partial_rotary_factor") or 0.5)
             out.lightning_norm_groups = int(cfg.get("linear_attn_norm_group_size") or cfg.get("group_norm_size") or 1)
-        if mt == "deepseek_v3":
+        if mt in ("deepseek_v2", "deepseek_v3"):
             if cfg.get("attention_bias"):
                 raise NotImplementedError("bias on the latent-attention projections is not supported")
             out.qk_norm = False
-            out.moe_score_func, out.moe_expert_bias, out.shared_expert_gated = "sigmoid", True, False
+            out.shared_expert_gated = False
+            if mt == "deepseek_v3":  # sigmoid scores, a selection bias, groups scored by their two best experts
+                out.moe_score_func, out.moe_expert_bias = "sigmoid", True
+                out.moe_n_group, out.moe_topk_group = int(cfg.get("n_group") or 1), int(cfg.get("topk_group") or 1)
+            else:  # V2: softmax scores, never renormalised unless asked; groups (if any) scored by their best expert
+                out.norm_topk_prob = bool(cfg.get("norm_topk_prob", False))
+                out.moe_group_score_top = 1
+                if cfg.get("topk_method", "greedy") == "group_limited_greedy":
+                    out.moe_n_group, out.moe_topk_group = int(cfg.get("n_group") or 1), int(cfg.get("topk_group") or 1)
             out.moe_route_scale = float(cfg.get("routed_scaling_factor", 1.0))
-            out.moe_n_group, out.moe_topk_group = int(cfg.get("n_group") or 1), int(cfg.get("topk_group") or 1)
             out.shared_expert_intermediate_size = int(cfg.get("n_shared_experts") or 0) * out.moe_intermediate_size
             out.mlp_only_layers = list(range(int(cfg.get("first_k_dense_replace") or 0)))
             out.q_lora_rank = int(cfg.get("q_lora_rank") or 0)
@@ -352,7 +359,7 @@ class ModelConfig:
                 "qwen3_moe": "Qwen3MoeForCausalLM", "qwen3_5": "Qwen3_5ForCausalLM",
                 "llama": "LlamaForCausalLM", "mistral": "MistralForCausalLM",
                 "qwen2_moe": "Qwen2MoeForCausalLM", "mixtral": "MixtralForCausalLM",
-                "deepseek_v3": "DeepseekV3ForCausalLM", "bailing_hybrid": "BailingMoeV2_5ForCausalLM"}[self.model_type]
+                "deepseek_v3": "DeepseekV3ForCausalLM", "deepseek_v2": "DeepseekV2ForCausalLM", "bailing_hybrid": "BailingMoeV2_5ForCausalLM"}[self.model_type]
         if self.model_type == "qwen3_5" and self.is_moe:
             arch = "Qwen3_5MoeForCausalLM"
         d = {
@@ -393,7 +400,9 @@ class ModelConfig:
                      shared_expert_intermediate_size=self.shared_expert_intermediate_size,
                      decoder_sparse_step=self.decoder_sparse_step,
                      mlp_only_layers=self.mlp_only_layers)
-        if self.model_type == "deepseek_v3":
+        if self.model_type in ("deepseek_v2", "deepseek_v3"):
+            if self.model_type == "deepseek_v2":
+                d["topk_method"] = "group_limited_greedy" if self.moe_n_group > 1 else "greedy"
             for key in ("num_experts", "shared_expert_intermediate_size", "decoder_sparse_step", "mlp_only_layers"):
                 d.pop(key, None)
             d.update(n_routed_experts=self.num_experts, routed_scaling_factor=self.moe_route_scale,
@@ -467,7 +476,7 @@ _VISION_KEYS = ("depth", "hidden_size", "intermediate_size", "num_heads", "in_ch
                 "fullatt_block_indexes", "hidden_act", "variant", "num_position_embeddings",
                 "deepstack_visual_indexes")
 _VL_TYPES = ("qwen2_5_vl", "qwen2_vl", "qwen3_vl", "qwen3_vl_moe")
-_TEXT_TYPES = {"qwen2", "qwen3", "qwen3_moe", "qwen3_5", "llama", "mistral", "qwen2_moe", "mixtral", "deepseek_v3", "bailing_hybrid"}
+_TEXT_TYPES = {"qwen2", "qwen3", "qwen3_moe", "qwen3_5", "llama", "mistral", "qwen2_moe", "mixtral", "deepseek_v2", "deepseek_v3", "bailing_hybrid"}
 
 # Named shapes used by the benchmark configurations (random-init, synthetic data).
 PRESETS: dict[str, ModelConfig] = {
@@ -577,6 +586,18 @@ PRESETS: dict[str, ModelConfig] = {
                                        qk_nope_head_dim=32, qk_rope_head_dim=16, v_head_dim=32, rope_interleave=True,
                                        lightning_group_size=2, lightning_head_dim=32, lightning_norm_groups=2,
                                        partial_rotary_factor=0.5, max_position_embeddings=32768),
+    # DeepSeek-V2-Lite: latent attention without the query bottleneck, softmax routing, two shared experts
+    "deepseek-v2-lite": ModelConfig(model_type="deepseek_v2", vocab_size=102400, hidden_size=2048,
+                                    intermediate_size=10944, num_hidden_layers=27, num_attention_heads=16,
+                                    num_key_value_heads=16, head_dim=192, rope_theta=1e4,
+                                    max_position_embeddings=163840, tie_word_embeddings=False, qk_norm=False,
+                                    num_experts=64, num_experts_per_tok=6, moe_intermediate_size=1408,
+                                    norm_topk_prob=False, moe_group_score_top=1, shared_expert_intermediate_size=2816,
+                                    shared_expert_gated=False, mlp_only_layers=[0], kv_lora_rank=512,
+                                    qk_nope_head_dim=128, qk_rope_head_dim=64, v_head_dim=128, rope_interleave=True,
+                                    rope_scaling={"rope_type": "yarn", "factor": 40.0, "beta_fast": 32, "beta_slow": 1,
+                                                  "mscale": 0.707, "mscale_all_dim": 0.707,
+                                                  "original_max_position_embeddings": 4096}),
     "deepseek-v3": ModelConfig(model_type="deepseek_v3", vocab_size=129280, hidden_size=7168, intermediate_size=18432,
                                num_hidden_layers=61, num_attention_heads=128, num_key_value_heads=128, head_dim=192,
                                rope_theta=1e4, max_position_embeddings=163840, tie_word_embeddings=False,

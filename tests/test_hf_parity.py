@@ -227,3 +227,42 @@ def test_deepseek_v3_without_query_bottleneck_and_with_yarn(tmp_path):
                                             "original_max_position_embeddings": 64})
     hf = _roundtrip(cfg, tmp_path)
     assert type(hf).__name__ == "DeepseekV3ForCausalLM" and not hasattr(hf.model.layers[0].self_attn, "q_a_proj")
+
+
+def test_deepseek_v2_matches_transformers(tmp_path):
+    """The V2 generation of the family: softmax scores that are scaled but not renormalised, no selection bias;
+    V2-Lite's plain query projection."""
+    cfg = dataclasses.replace(PRESETS["tiny-deepseek-v3"], model_type="deepseek_v2", moe_score_func="softmax",
+                              moe_expert_bias=False, moe_group_score_top=1, norm_topk_prob=False, q_lora_rank=0,
+                              moe_n_group=1, moe_topk_group=1)
+    hf = _roundtrip(cfg, tmp_path)
+    assert type(hf).__name__ == "DeepseekV2ForCausalLM"
+    back = ModelConfig.from_hf_config(str(tmp_path))
+    assert dataclasses.asdict(back) == dataclasses.asdict(cfg)
+    assert PRESETS["deepseek-v2-lite"].num_params() / 1e9 == pytest.approx(15.7, abs=0.2)
+
+
+def test_deepseek_v2_group_limited_routing_rule():
+    """``group_limited_greedy`` (the larger V2 models): a group is scored by its best expert, tokens pick among the
+    experts of their best groups, weights are the plain softmax scores times the scale. (Checked against the rule
+    itself: the ``transformers`` class cannot run this branch, it reads an attribute it never sets.)"""
+    from areal_b200.models.qwen import MoEMLP
+
+    cfg = dataclasses.replace(PRESETS["tiny-deepseek-v3"], model_type="deepseek_v2", moe_score_func="softmax",
+                              moe_expert_bias=False, moe_group_score_top=1, norm_topk_prob=False, moe_n_group=4,
+                              moe_topk_group=2)
+    back = ModelConfig.from_hf_config(cfg.to_hf_config())
+    assert (back.moe_n_group, back.moe_topk_group, back.moe_group_score_top, back.moe_score_func) == (4, 2, 1, "softmax")
+    torch.manual_seed(0)
+    mlp = MoEMLP(cfg, torch.float32, "cpu").eval()
+    torch.nn.init.normal_(mlp.router, std=0.5)
+    x = torch.randn(50, cfg.hidden_size)
+    with torch.no_grad():
+        idx, w = mlp.route(x)
+    p = torch.softmax(x @ mlp.router.T, -1)
+    best_groups = p.view(50, 4, 2).max(-1).values.topk(2, -1).indices           # [50, 2]
+    assert bool(((idx.long() // 2)[:, :, None] == best_groups[:, None, :]).any(-1).all())
+    masked = p.view(50, 4, 2).masked_fill(~torch.zeros(50, 4, dtype=torch.bool).scatter_(1, best_groups, True)[..., None], 0.0)
+    want = masked.view(50, 8).topk(cfg.num_experts_per_tok, -1)
+    assert torch.equal(idx.long().sort(-1).values, want.indices.sort(-1).values)
+    assert torch.allclose(w.sort(-1).values, (want.values * cfg.moe_route_scale).sort(-1).values, atol=1e-6)
