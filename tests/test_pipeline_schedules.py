@@ -173,6 +173,7 @@ def _ref(tmp_path, n_mbs):
                                      (4, ["--pp", "4", "--schedule", "ZB1P"]),
                                      (2, ["--pp", "2", "--schedule", "ZBVZeroBubble"]),
                                      (3, ["--pp", "3", "--schedule", "ZBVZeroBubble"]),
+                                     (4, ["--pp", "2", "--tp", "2", "--schedule", "ZBVZeroBubble"]),
                                      (2, ["--pp", "2", "--vpp", "2", "--schedule", "InterleavedZeroBubble"]),
                                      (4, ["--pp", "2", "--tp", "2", "--vpp", "2"])])
 def test_step_with_eight_micro_batches_matches_single_process(tmp_path, n, flags):
