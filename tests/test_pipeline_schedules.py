@@ -184,3 +184,20 @@ def test_step_with_eight_micro_batches_matches_single_process(tmp_path, n, flags
            "--n-mbs", "8", "--preset", "tiny-qwen2-4l"] + flags + [ref]
     r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
     assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]
+
+
+def test_v_shaped_placement_with_expert_parallelism_matches_single_process(tmp_path):
+    """ZBVZeroBubble over two pipeline ranks whose stages spread their experts over two expert-parallel ranks (a
+    four-block MoE model: one block per stage): the experts' own flat buffer, optimizer and gradient norm follow the
+    V-shaped layer assignment."""
+    ref = str(tmp_path / "ref.pt")
+    env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK")}
+    common = ["--n-mbs", "4", "--layers", "4", "--preset", "tiny-qwen3-moe"]
+    r = subprocess.run([sys.executable, WORKER, "--ref"] + common + [ref], env=env, capture_output=True, text=True,
+                       timeout=300)
+    assert r.returncode == 0, r.stdout[-2000:] + r.stderr[-2000:]
+    cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=4", "--master-addr",
+           "127.0.0.1", "--master-port", str(_free_port()), WORKER] + common + \
+          ["--pp", "2", "--ep", "2", "--schedule", "ZBVZeroBubble", ref]
+    r = subprocess.run(cmd, capture_output=True, text=True, timeout=900)
+    assert r.returncode == 0 and "OK" in r.stdout, r.stdout[-2000:] + r.stderr[-3000:]

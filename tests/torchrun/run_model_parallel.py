@@ -98,6 +98,7 @@ def main():
     ap.add_argument("--images", action="store_true", help="image prompts (vision-language presets)")
     ap.add_argument("--one-image", action="store_true", help="only the first sequence carries an image")
     ap.add_argument("--shard-vision", action="store_true", help="divide the vision tower's images over the sp ranks")
+    ap.add_argument("--layers", type=int, default=0, help="override the preset's number of blocks")
     ap.add_argument("--vpp", type=int, default=1, help="virtual pipeline stages (model chunks) per rank")
     ap.add_argument("--schedule", default="", help="pipeline schedule: GPipe | 1F1B | Interleaved1F1B")
     ap.add_argument("--zigzag", action="store_true", help="context parallelism with zig-zag chunks and gathered K/V "
@@ -114,6 +115,8 @@ def main():
         os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
         if "LOCAL_RANK" in os.environ:
             torch.cuda.set_device(int(os.environ["LOCAL_RANK"]))
+    if args.layers:
+        over["num_hidden_layers"] = args.layers
     cfg = TrainEngineConfig(experiment_name="t", trial_name="t", path="", init_from_scratch=True,
                             dtype="bfloat16" if cuda else "float32", model_overrides=over,
                             model_preset=args.preset, mb_spec=MicroBatchSpec(n_mbs=args.n_mbs), is_critic=args.critic,
