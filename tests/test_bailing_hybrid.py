@@ -137,10 +137,12 @@ def _ref(tmp_path):
     return f
 
 
-@pytest.mark.parametrize("args", [["--sp", "2"], ["--ep", "2"], ["--pp", "2", "--n-mbs", "2"]])
+@pytest.mark.parametrize("args", [["--sp", "2"], ["--ep", "2"], ["--pp", "2", "--n-mbs", "2"],
+                                  ["--pp", "2", "--n-mbs", "4", "--schedule", "ZBVZeroBubble"]])
 def test_training_step_under_parallel_layouts_matches_single_process(tmp_path, args):
     """Ulysses (the recurrence runs on heads / 2 over the whole stream after a tokens → heads exchange), expert and
-    pipeline parallelism: loss, gradient norm and every gradient as in one process."""
+    pipeline parallelism (also with one block per stage in the V-shaped placement: the per-layer decays follow the
+    global layer index): loss, gradient norm and every gradient as in one process."""
     cmd = [sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr",
            "127.0.0.1", "--master-port", str(free_port()), WORKER] + args + ["--preset", "tiny-bailing-hybrid",
                                                                              _ref(tmp_path)]
